@@ -1,0 +1,332 @@
+/* ling_b200.h -- C ABI of the B200 (sm_100a) ragged speculative verify step.
+ *
+ * The reference engine (dreamference/ling-engine) is one statically linked C++ program with no FFI; the
+ * boundary it offers for this path is the public C++ surface its scheduler calls.  Every entry point below
+ * names the reference declaration it stands in for (file:line inside the reference project).  A C++ facade
+ * with the reference's own names (ling::Engine, ling::KvPool, ling::serve::*) lives beside the kernels and
+ * forwards to these functions.
+ *
+ * Conventions: plain pointers and sizes, int status codes (0 = LING_B200_OK), never throws, no allocation
+ * after ling_b200_create() unless a function says otherwise.  One thread drives one context, one step in
+ * flight (src/serve/main.cpp:357-377 in the reference: a single engine thread).
+ */
+#ifndef LING_B200_H_
+#define LING_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------------------------------------ limits */
+#define LING_B200_MAX_LAYERS 128
+#define LING_B200_MAX_SEQS 64        /* sequences per step (reference: kernels.cuh:52 kMaxSeqs = 4)          */
+#define LING_B200_MAX_TREE_ROWS 32   /* rows of one sequence's tree (kernels.cuh:107 kMaxStreamRows = 32)    */
+#define LING_B200_MAX_TREE_VARIANTS 32 /* kernels.cuh:118 kMaxTreeVariants                                   */
+#define LING_B200_MAX_ROWS 2048      /* packed rows of one step (all sequences)                              */
+
+/* ------------------------------------------------------------------------------------------------ status */
+enum {
+  LING_B200_OK = 0,
+  LING_B200_ERR_ARG = 1,          /* bad argument: nothing was launched or changed                          */
+  LING_B200_ERR_CUDA = 2,         /* a CUDA call failed: see ling_b200_last_error()                          */
+  LING_B200_ERR_POOL = 3,         /* KvPoolExhausted (engine.hpp:227-232): nothing launched, nothing changed */
+  LING_B200_ERR_DEVICE_FLAG = 4,  /* a kernel's bounded wait ran out or a bounds check tripped               */
+  LING_B200_ERR_UNSUPPORTED = 5
+};
+/* per-sequence status in ling_b200_seq_result */
+enum { LING_B200_SEQ_OK = 0, LING_B200_SEQ_NONFINITE = 1 /* NonFiniteLogits, sampling.hpp:22-25 */ };
+
+/* ------------------------------------------------------------------------------------------------ model  */
+/* ModelConfig of the reference (src/core/model.hpp:43-62), as a POD. */
+typedef struct ling_b200_model_config {
+  int hidden, intermediate, layers, vocab;
+  int heads, kv_heads, head_dim, rotary_dim;
+  float rope_theta, eps;
+  int lin_k_heads, lin_v_heads, lin_k_dim, lin_v_dim, conv_kernel; /* conv_kernel must be 4 */
+  unsigned char full_attention[LING_B200_MAX_LAYERS];             /* per layer: 1 = gated GQA attention  */
+} ling_b200_model_config;
+
+/* EngineOptions (src/core/engine.hpp:56-187), the fields this path reads. */
+typedef struct ling_b200_options {
+  int sessions;      /* resident session slots: each owns a page table, DeltaNet state and conv window */
+  int max_context;   /* positions one session's page table can map                                    */
+  int page_tokens;   /* positions per KV page: 16 or 64 (reference: compile-time 64, kernels.cuh:57)  */
+  int pool_pages;    /* usable pages (ids 1..pool_pages); page 0 is reserved (kv_pool.hpp:4-5)         */
+  int max_seqs;      /* most sequences in one step  (<= LING_B200_MAX_SEQS)                            */
+  int max_rows;      /* most packed rows in one step (<= LING_B200_MAX_ROWS)                           */
+  int gemm_impl;     /* 0 = tcgen05/TMEM/TMA (the product path); 1 = plain CUDA-core GEMM (cross-check) */
+  int use_graph;     /* 1 = replay the step as one CUDA graph (engine.hpp:125 step_graphs)             */
+  int device;        /* CUDA device ordinal                                                           */
+  int debug_rows;    /* rows for which logits and per-layer taps can be kept (0: neither is available)   */
+  int pdl;           /* 1 = programmatic dependent launch (launch.cuh:1-98 in the reference): a GEMM prefetches its
+                        weight tiles while the kernel before it finishes                                 */
+  int reserved[5];
+} ling_b200_options;
+
+typedef struct ling_b200_ctx ling_b200_ctx;
+
+/* Engine::Engine (src/core/engine.cpp:129-434): everything is allocated here, nothing while serving. */
+int ling_b200_create(const ling_b200_model_config* cfg, const ling_b200_options* opt, ling_b200_ctx** out);
+void ling_b200_destroy(ling_b200_ctx* ctx);
+/* The last error's text (thread-local for calls without a context). */
+const char* ling_b200_last_error(void);
+/* Library/ABI version, and whether the CUDA kernels are present (always 1: there is no CPU path). */
+int ling_b200_abi_version(void);
+
+/* Tensor names for ling_b200_set_tensor (LayerWeights, src/core/model.hpp:86-104). */
+enum {
+  LING_B200_T_EMBED = 0,   /* [vocab][hidden]   kept BF16                                   */
+  LING_B200_T_FINAL_NORM,  /* [hidden]          BF16                                        */
+  LING_B200_T_LM_HEAD,     /* [vocab][hidden]   FP8 E4M3 + fp32 scale per 1x128             */
+  LING_B200_T_INPUT_NORM,  /* [hidden]                                                      */
+  LING_B200_T_POST_NORM,   /* [hidden]                                                      */
+  LING_B200_T_GATE,        /* [intermediate][hidden] FP8                                    */
+  LING_B200_T_UP,          /* [intermediate][hidden] FP8                                    */
+  LING_B200_T_DOWN,        /* [hidden][intermediate] FP8                                    */
+  LING_B200_T_IN_QKV,      /* [C][hidden] FP8, C = 2*Hk*Dk + HV*Dv, channels q|k|v          */
+  LING_B200_T_IN_Z,        /* [HV*Dv][hidden] FP8                                           */
+  LING_B200_T_OUT,         /* [hidden][HV*Dv] FP8                                           */
+  LING_B200_T_IN_A,        /* [HV][hidden] BF16                                             */
+  LING_B200_T_IN_B,        /* [HV][hidden] BF16                                             */
+  LING_B200_T_CONV,        /* [C][4] BF16                                                   */
+  LING_B200_T_A_LOG,       /* [HV] BF16                                                     */
+  LING_B200_T_DT_BIAS,     /* [HV] BF16                                                     */
+  LING_B200_T_LIN_NORM,    /* [Dv] BF16                                                     */
+  LING_B200_T_Q,           /* [Hq*2*D][hidden] FP8, per head: D query rows then D gate rows */
+  LING_B200_T_K,           /* [Hkv*D][hidden] FP8                                           */
+  LING_B200_T_V,           /* [Hkv*D][hidden] FP8                                           */
+  LING_B200_T_O,           /* [hidden][Hq*D] FP8                                            */
+  LING_B200_T_Q_NORM,      /* [D] BF16                                                      */
+  LING_B200_T_K_NORM,      /* [D] BF16                                                      */
+  LING_B200_T_COUNT
+};
+
+/* Model::Model upload (src/core/model.cu:265-276): one tensor from host fp32 [rows][cols]; matrices are
+ * rounded to BF16 first and then to FP8 E4M3 with one fp32 scale (amax/448) per row per 128 columns, on the
+ * device; the rest are kept as BF16.  `layer` is ignored for the three global tensors. */
+int ling_b200_set_tensor(ling_b200_ctx* ctx, int layer, int tensor, const float* host, int rows, int cols);
+/* Every tensor filled on the device from the counter-based generator keyed by (seed, layer, tensor, index):
+ * matrices N(0, 0.02) rounded to BF16 (an Irwin-Hall sum of 12 uniforms, exact integer arithmetic, so the
+ * host restates any element bit for bit); norms N(0, 0.02); conv N(0, 0.3); A_log, dt_bias N(0, 0.5).
+ * Stands in for the checkpoints (absent). */
+int ling_b200_synth_weights(ling_b200_ctx* ctx, uint64_t seed);
+/* A matrix's device encoding back on the host (parity of the quantizer): codes [rows][cols] and scales
+ * [rows][ceil(cols/128)].  Either pointer may be NULL. */
+int ling_b200_get_matrix(ling_b200_ctx* ctx, int layer, int tensor, uint8_t* codes, float* scales, int rows, int cols);
+/* Bytes of weights one step streams (GEMM codes + block scales + BF16 extras + nothing of the embedding). */
+size_t ling_b200_weight_bytes(const ling_b200_ctx* ctx);
+
+/* ------------------------------------------------------------------------------------------------ sessions */
+/* kv_table_set (src/core/kernels.cuh:156-161, kernels.cu:501-509): table[slot][idx[i]] = page[i]; the entries
+ * are ordered on the step stream before the next step reads them.  page 0 = unmapped. */
+int ling_b200_kv_table_set(ling_b200_ctx* ctx, int slot, const int* idx, const int* page, int n);
+/* Copy-on-write page copies returned by KvPool::ensure (kv_pool.hpp:24-26, engine.cpp:858-866): whole pages,
+ * every full-attention layer's K and V codes and scales, src[i] into dst[i]. */
+int ling_b200_kv_pages_copy(ling_b200_ctx* ctx, const int* src, const int* dst, int n);
+/* The K and V of positions [from, from+n) of one full-attention layer (index among the attention layers)
+ * written through the slot's page table from host fp32 [n][kv_heads][head_dim] (K already normed and
+ * rotated).  Quantized as the step quantizes them: E4M3 codes, one fp32 scale amax/448 per (position, head).
+ * What a prefill would have left; tests and benches build contexts with it. */
+int ling_b200_kv_write(ling_b200_ctx* ctx, int slot, int attn_layer, int from, int n, const float* k, const float* v);
+/* The same positions read back dequantized (fp32), or as codes+scales when the float pointers are NULL. */
+int ling_b200_kv_read(ling_b200_ctx* ctx, int slot, int attn_layer, int from, int n, float* k, float* v,
+                      uint8_t* kcodes, float* kscales, uint8_t* vcodes, float* vscales);
+/* Positions [0, n) of every attention layer of a slot filled on the device from the generator (N(0,1) values). */
+int ling_b200_synth_kv(ling_b200_ctx* ctx, int slot, int n, uint64_t seed);
+/* One DeltaNet layer's (index among the DeltaNet layers) state [HV][Dk][Dv] and conv window [C][3] of a slot
+ * (engine.cpp:226-229).  NULL pointers are skipped. */
+int ling_b200_state_write(ling_b200_ctx* ctx, int slot, int gdn_layer, const float* state, const float* conv);
+int ling_b200_state_read(ling_b200_ctx* ctx, int slot, int gdn_layer, float* state, float* conv);
+int ling_b200_synth_state(ling_b200_ctx* ctx, int slot, uint64_t seed); /* state N(0,0.1), window N(0,1) */
+/* Engine::state_hash (engine.cpp:954-971): FNV-1a over every DeltaNet and conv state of a slot, bit for bit. */
+int ling_b200_state_hash(ling_b200_ctx* ctx, int slot, uint64_t* hash);
+
+/* ------------------------------------------------------------------------------------------------ the step */
+/* One sequence of a step: Engine::SeqStep (engine.hpp:337-344) after the drafter has produced its tree
+ * (DraftTree, tree.hpp:41-48: parent index < child index, row 0 the anchor, rows 1..chain the chain). */
+typedef struct ling_b200_seq_step {
+  int slot;          /* session slot                                                           */
+  int pos;           /* positions already in the cache: the anchor's slot (Session::pos)        */
+  int rope_delta;    /* DevPos::rdelta (kernels.cuh:27-29)                                      */
+  int n_rows;        /* 1..32                                                                   */
+  int chain;         /* DraftTree::E                                                            */
+  const int* tokens; /* [n_rows]                                                                */
+  const int* parent; /* [n_rows], parent[0] = -1                                                */
+  const int* force_argmax; /* NULL, or [n_rows]: replaces the device argmax before acceptance (a test and
+                              benchmark hook that imposes an accepted length)                    */
+} ling_b200_seq_step;
+
+typedef struct ling_b200_seq_result {
+  int status;                                   /* LING_B200_SEQ_*                                  */
+  int n_path;                                   /* accepted path rows, the anchor included (>= 1)   */
+  int path[LING_B200_MAX_TREE_ROWS];            /* accept_tree_greedy's rows (tree.cpp:148-166)      */
+  int next_token;                               /* the token after the path                          */
+  int n_out;                                    /* = n_path                                          */
+  int out[LING_B200_MAX_TREE_ROWS + 1];         /* SeqStep::out: accepted drafts, then next_token    */
+} ling_b200_seq_result;
+
+/* Flags of ling_b200_verify_step. */
+enum {
+  LING_B200_STEP_COMMIT = 1,       /* compaction + DeltaNet commit inside the step (speculate.cpp:1004-1020,516-529) */
+  LING_B200_STEP_KEEP_LOGITS = 2,  /* also materialize logits[rows][vocab] (SeqStep::row_logits)                    */
+  LING_B200_STEP_KEEP_TAPS = 4     /* keep per-layer residual rows for ling_b200_read_tap (debug / parity)          */
+};
+
+/* Engine::speculate_batch (speculate.cpp:1101-1282) from its verify on: pack the trees, one forward pass over
+ * all rows, argmax, greedy tree acceptance, KV compaction and DeltaNet commit.  Host buffers in, host buffers
+ * out; the page tables must already map [pos, pos + n_rows) of every sequence (kv_ensure, engine.cpp:841-869).
+ * Returns after the result is on the host. */
+int ling_b200_verify_step(ling_b200_ctx* ctx, const ling_b200_seq_step* seqs, int n_seqs, int flags,
+                          ling_b200_seq_result* results);
+/* The same step split for measurement with inputs resident in HBM: stage() copies the descriptors,
+ * launch() enqueues the step (graph replay) on the context's stream, fetch() waits and reads the results. */
+int ling_b200_step_stage(ling_b200_ctx* ctx, const ling_b200_seq_step* seqs, int n_seqs, int flags);
+int ling_b200_step_launch(ling_b200_ctx* ctx);
+int ling_b200_step_fetch(ling_b200_ctx* ctx, ling_b200_seq_result* results);
+
+/* kernels::TreeDesc (src/core/kernels.cuh:119-130), the same field order, so a describe_tree result compares
+ * with memcmp. */
+typedef struct ling_b200_tree_desc {
+  int n;
+  int depth[LING_B200_MAX_TREE_ROWS];
+  int var[LING_B200_MAX_TREE_ROWS];
+  int nvar;
+  int path[LING_B200_MAX_TREE_VARIANTS][LING_B200_MAX_TREE_ROWS];
+  int ngdn;
+  int gdn_len[LING_B200_MAX_TREE_VARIANTS];
+  int gdn_step[LING_B200_MAX_TREE_VARIANTS][2 * LING_B200_MAX_TREE_ROWS];
+} ling_b200_tree_desc;
+#define LING_B200_TREE_LEAF (1 << 8)
+#define LING_B200_TREE_WRITE (1 << 9)
+
+/* What the last step built and computed, read back for parity checks. */
+/* describe_tree's result for sequence i of the last step, built on the device (tree.cpp:81-146). */
+int ling_b200_read_tree_desc(ling_b200_ctx* ctx, int seq, ling_b200_tree_desc* out);
+/* Packing of the last step (speculate.cpp:1190-1201; kernels.cuh:58-78): row0[n_seqs+1], and per packed row its
+ * sequence, depth, RoPE position, cache slot and ancestor mask (bit j set: row row0+j of its sequence is on the
+ * row's root-to-row path, the row itself included).  NULL pointers are skipped. */
+int ling_b200_read_packing(ling_b200_ctx* ctx, int* row0, int* token, int* seq_of, int* depth, int* rope_pos,
+                           int* cache_slot, uint32_t* anc_mask);
+/* Per packed row: argmax id and value (topk_rows K=1, topk.cu:83-129). */
+int ling_b200_read_argmax(ling_b200_ctx* ctx, int* ids, float* vals);
+/* logits[rows][vocab] of the last step (needs LING_B200_STEP_KEEP_LOGITS). */
+int ling_b200_read_logits(ling_b200_ctx* ctx, float* out);
+/* Residual stream after layer `layer` (0..layers-1), or the final-normed rows for layer = layers;
+ * [rows][hidden] (needs LING_B200_STEP_KEEP_TAPS). */
+int ling_b200_read_tap(ling_b200_ctx* ctx, int layer, float* out);
+
+/* ------------------------------------------------------------------------------------------------ timing */
+/* Device time of the last n launch() calls, measured with CUDA events on the context's stream. */
+int ling_b200_timer_begin(ling_b200_ctx* ctx);
+int ling_b200_timer_end(ling_b200_ctx* ctx, float* ms);
+/* Per-kernel-family device time of one eager (non-graph) replay of the staged step, by CUDA events around each
+ * family's launches: [0] weight GEMMs, [1] attention, [2] DeltaNet, [3] norms/quant/elementwise,
+ * [4] head+argmax, [5] pack/accept/compact/commit.  Also the number of kernel launches in one step. */
+int ling_b200_profile_step(ling_b200_ctx* ctx, float ms[8], int* launches);
+int ling_b200_step_launch_count(ling_b200_ctx* ctx);
+/* Writes more than L2 between timed steps (the bench's flush). */
+int ling_b200_flush_l2(ling_b200_ctx* ctx);
+int ling_b200_sync(ling_b200_ctx* ctx);
+
+/* ------------------------------------------------------------------------------------------------ kernels */
+/* The kernel layer of the reference is free functions over raw device pointers (src/core/kernels.cuh:82-578).
+ * These take HOST buffers, run the kernel once on the device and copy the result back, for parity tests. */
+
+/* y[M][N] = x[M][K] . W[N][K]^T with x quantized to E4M3 per row per 128 columns and W per row per 128 columns
+ * (stream_gemm_fp8, stream_gemm.cu:674-703, at this build's numerics).  impl as ling_b200_options.gemm_impl.
+ * splits: the K split (0 = the library's choice for the shape). */
+int ling_b200_gemm_fp8_host(int device, int impl, int splits, const float* x, const float* w, float* y, int M, int N, int K);
+/* The same GEMM timed on the device with resident operands: ms per launch over `iters` launches. */
+int ling_b200_gemm_fp8_bench(int device, int impl, int splits, int M, int N, int K, int iters, float* ms_per_launch);
+
+/* gdn_conv_tree + gdn_recurrent_tree (kernels.cuh:131-136): one sequence, one layer.  pre [n][C], g and beta
+ * [n][HV] (g = log decay), state [HV][Dk][Dv], conv [C][3]; out core [n][HV*Dv] and post [n][C]. */
+int ling_b200_gdn_tree_host(int device, int Hk, int HV, int Dk, int Dv, const ling_b200_tree_desc* td,
+                            const float* pre, const float* convw, const float* g, const float* beta,
+                            const float* state, const float* conv, float* post, float* core);
+/* Engine::commit (speculate.cpp:516-529) for one layer: rows path[0..n) replayed, state and window written. */
+int ling_b200_gdn_commit_host(int device, int Hk, int HV, int Dk, int Dv, const int* path, int n, int rows,
+                              const float* pre, const float* post, const float* g, const float* beta,
+                              float* state, float* conv);
+/* topk_rows K=1 (topk.cu:83-129): ids/vals per row, ties to the lower id, NaN skipped. */
+int ling_b200_argmax_host(int device, const float* logits, int rows, int vocab, int* ids, float* vals);
+
+/* ------------------------------------------------------------------------------------------------ host logic */
+/* describe_tree (tree.cpp:81-146) on the host: returns 0 or LING_B200_ERR_ARG (too many rows/leaves/paths). */
+int ling_b200_describe_tree(const int* parent, int n_rows, int chain, ling_b200_tree_desc* out);
+/* accept_tree_greedy (tree.cpp:148-166): path out (<= n_rows entries), returns the path length. */
+int ling_b200_accept_tree_greedy(const int* parent, const int* token, int n_rows, const int* argmax, int* path,
+                                 int* next);
+/* lookup_propose (lookup.cpp:7-24): returns the number of proposed tokens written to out (<= max). */
+int ling_b200_lookup_propose(const int* seq, int len, int max, int ngram, int* out, int* match);
+/* build_tree (tree.cpp:30-79). shape = {nodes, width, max_depth, chain}; returns rows, fills parent/depth/token/pick. */
+int ling_b200_build_tree(int anchor, const int* cand, const float* scores, int E, int K16, const int* chain_tokens,
+                         const int* chain_picks, int nodes, double temp, int width, int max_depth, int chain,
+                         int max_rows, int* parent, int* depth, int* token, int* pick, double* extra_mass);
+
+/* KvPool (src/core/kv_pool.hpp:20-83), handle based.  Tables are caller-owned int arrays with their length. */
+typedef struct ling_b200_kvpool ling_b200_kvpool;
+ling_b200_kvpool* ling_b200_kvpool_create(int pages, int page_tokens);
+void ling_b200_kvpool_destroy(ling_b200_kvpool* p);
+int ling_b200_kvpool_capacity(const ling_b200_kvpool* p);
+int ling_b200_kvpool_free_pages(const ling_b200_kvpool* p);
+int ling_b200_kvpool_pending_pages(const ling_b200_kvpool* p);
+int ling_b200_kvpool_refs(const ling_b200_kvpool* p, int page);
+int ling_b200_kvpool_needed(const ling_b200_kvpool* p, const int* table, int len, int from, int to);
+/* ensure: table has room for cap entries; *len is updated. copies: [2*max_copies] (src,dst); returns 1/0, or <0 on a bad range. */
+int ling_b200_kvpool_ensure(ling_b200_kvpool* p, int* table, int* len, int cap, int from, int to, int* copies,
+                            int max_copies, int* n_copies);
+int ling_b200_kvpool_share(ling_b200_kvpool* p, int* dst, int* dst_len, int cap, const int* src, int src_len, int n);
+void ling_b200_kvpool_truncate(ling_b200_kvpool* p, int* table, int len, int n);
+void ling_b200_kvpool_unshare(ling_b200_kvpool* p, int* table, int len, int n);
+int ling_b200_kvpool_net_need(const ling_b200_kvpool* p, const int* table, int len, int pages);
+int ling_b200_kvpool_resume_need(const ling_b200_kvpool* p, const int* table, int len, int reuse, int pages,
+                                 const int* donor, int donor_len);
+int ling_b200_kvpool_reclaimable(const ling_b200_kvpool* p, const int* const* tables, const int* lens, int n);
+int ling_b200_kvpool_retain(ling_b200_kvpool* p, int page);
+int ling_b200_kvpool_release(ling_b200_kvpool* p, int page);
+void ling_b200_kvpool_retire(ling_b200_kvpool* p);
+
+/* select_batch / pair_order (src/serve/pairing.hpp:46-75): candidates as three parallel arrays. Returns the count. */
+int ling_b200_pair_order(const int* batchable, const int* recent, const long* last, int n, int fair, int* order);
+int ling_b200_select_batch(const int* batchable, const int* recent, const long* last, int n, int self, int fit,
+                           int fair, int* batch);
+/* kv_verdict / kv_last_resort (src/serve/kv_policy.hpp:38-93): verdict 0 Go, 1 Retire, 2 Reclaim, 3 Wait. */
+int ling_b200_kv_verdict(int need, int free_pages, int pending, int idle);
+int ling_b200_kv_last_resort(const long* admitted, const int* waiting, const int* need, int n, int free_pages,
+                             int pending, int idle);
+/* plan_memory + plan_kv_pool + refusal (src/serve/admission.hpp:94-124,202-232): returns pages; fills the plan. */
+typedef struct ling_b200_memory_plan {
+  size_t weights, per_session, sessions, scratch, kv_pool;
+  int session_count;
+  long kv_pool_pages;
+  size_t total;
+  int refused; /* start_plan's refusal is non-empty */
+} ling_b200_memory_plan;
+int ling_b200_start_plan(const ling_b200_model_config* cfg, size_t weight_bytes, size_t scratch, int drafter,
+                         int sessions, int max_context, long avail_mb, long reserve_mb, int kv_on,
+                         size_t store_bytes, long pool_mb, int page_tokens, int kv_elem_bytes,
+                         ling_b200_memory_plan* out);
+/* choose_size (admission.hpp:262-310): given values < 0 mean "not given". */
+int ling_b200_choose_size(const ling_b200_model_config* cfg, size_t weight_bytes, size_t scratch, int drafter,
+                          long avail_mb, long reserve_mb, int full_context, int sessions, int max_context,
+                          int auto_size, int kv_on, size_t store_bytes, long pool_mb, int page_tokens,
+                          int kv_elem_bytes, int* out_sessions, int* out_context, int* sessions_auto,
+                          int* context_auto, int* sized);
+/* format_step (src/serve/step_trace.hpp:66-87): one trace line into buf; returns its length. */
+int ling_b200_format_step(double t, long pass, const char* kind, size_t turn, const int* sessions, const int* rows,
+                          const int* tokens, const int* left, int n,
+                          const int* cand /* [n_cand][3]: session, state, recent */, const long* cand_request,
+                          const long* cand_last, int n_cand, double ms, int side, char* buf, int buf_len);
+
+/* Device memory helpers for callers without a CUDA binding (tests): device count, and name of device 0. */
+int ling_b200_device_count(void);
+int ling_b200_device_name(int device, char* buf, int len);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LING_B200_H_ */

@@ -1,0 +1,362 @@
+"""ctypes binding of libling_b200.so, the C-ABI library of the B200 verify step.
+
+The product is the shared library (CUDA C++ for sm_100a, see csrc/ and include/ling_b200.h); this module only loads it
+for the Python-driven tests and benchmark.  There is no CPU path: if the library is missing, importing `lib()` raises.
+"""
+import ctypes as C
+import os
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libling_b200.so")
+
+MAX_LAYERS, MAX_SEQS, MAX_TREE_ROWS, MAX_TREE_VARIANTS = 128, 64, 32, 32
+TREE_LEAF, TREE_WRITE = 1 << 8, 1 << 9
+STEP_COMMIT, STEP_KEEP_LOGITS, STEP_KEEP_TAPS = 1, 2, 4
+OK, ERR_ARG, ERR_CUDA, ERR_POOL, ERR_DEVICE_FLAG, ERR_UNSUPPORTED = range(6)
+
+(T_EMBED, T_FINAL_NORM, T_LM_HEAD, T_INPUT_NORM, T_POST_NORM, T_GATE, T_UP, T_DOWN, T_IN_QKV, T_IN_Z, T_OUT, T_IN_A,
+ T_IN_B, T_CONV, T_A_LOG, T_DT_BIAS, T_LIN_NORM, T_Q, T_K, T_V, T_O, T_Q_NORM, T_K_NORM, T_COUNT) = range(24)
+MATRIX_TENSORS = {T_LM_HEAD, T_GATE, T_UP, T_DOWN, T_IN_QKV, T_IN_Z, T_OUT, T_Q, T_K, T_V, T_O}
+
+
+class ModelConfig(C.Structure):
+    _fields_ = [("hidden", C.c_int), ("intermediate", C.c_int), ("layers", C.c_int), ("vocab", C.c_int),
+                ("heads", C.c_int), ("kv_heads", C.c_int), ("head_dim", C.c_int), ("rotary_dim", C.c_int),
+                ("rope_theta", C.c_float), ("eps", C.c_float),
+                ("lin_k_heads", C.c_int), ("lin_v_heads", C.c_int), ("lin_k_dim", C.c_int), ("lin_v_dim", C.c_int),
+                ("conv_kernel", C.c_int), ("full_attention", C.c_ubyte * MAX_LAYERS)]
+
+    @property
+    def conv_channels(self):
+        return 2 * self.lin_k_heads * self.lin_k_dim + self.lin_v_heads * self.lin_v_dim
+
+    @property
+    def value_size(self):
+        return self.lin_v_heads * self.lin_v_dim
+
+    def attn_layers(self):
+        return [l for l in range(self.layers) if self.full_attention[l]]
+
+    def gdn_layers(self):
+        return [l for l in range(self.layers) if not self.full_attention[l]]
+
+
+class Options(C.Structure):
+    _fields_ = [("sessions", C.c_int), ("max_context", C.c_int), ("page_tokens", C.c_int), ("pool_pages", C.c_int),
+                ("max_seqs", C.c_int), ("max_rows", C.c_int), ("gemm_impl", C.c_int), ("use_graph", C.c_int),
+                ("device", C.c_int), ("debug_rows", C.c_int), ("pdl", C.c_int), ("reserved", C.c_int * 5)]
+
+
+class SeqStep(C.Structure):
+    _fields_ = [("slot", C.c_int), ("pos", C.c_int), ("rope_delta", C.c_int), ("n_rows", C.c_int), ("chain", C.c_int),
+                ("tokens", C.POINTER(C.c_int)), ("parent", C.POINTER(C.c_int)), ("force_argmax", C.POINTER(C.c_int))]
+
+
+class SeqResult(C.Structure):
+    _fields_ = [("status", C.c_int), ("n_path", C.c_int), ("path", C.c_int * MAX_TREE_ROWS), ("next_token", C.c_int),
+                ("n_out", C.c_int), ("out", C.c_int * (MAX_TREE_ROWS + 1))]
+
+
+class TreeDesc(C.Structure):
+    _fields_ = [("n", C.c_int), ("depth", C.c_int * MAX_TREE_ROWS), ("var", C.c_int * MAX_TREE_ROWS), ("nvar", C.c_int),
+                ("path", (C.c_int * MAX_TREE_ROWS) * MAX_TREE_VARIANTS), ("ngdn", C.c_int),
+                ("gdn_len", C.c_int * MAX_TREE_VARIANTS), ("gdn_step", (C.c_int * (2 * MAX_TREE_ROWS)) * MAX_TREE_VARIANTS)]
+
+
+class MemoryPlan(C.Structure):
+    _fields_ = [("weights", C.c_size_t), ("per_session", C.c_size_t), ("sessions", C.c_size_t), ("scratch", C.c_size_t),
+                ("kv_pool", C.c_size_t), ("session_count", C.c_int), ("kv_pool_pages", C.c_long), ("total", C.c_size_t),
+                ("refused", C.c_int)]
+
+
+def make_config(hidden, intermediate, layers, vocab, heads, kv_heads, head_dim, rotary_dim, lin_k_heads, lin_v_heads,
+                lin_k_dim, lin_v_dim, full_attention, rope_theta=1e7, eps=1e-6):
+    cfg = ModelConfig(hidden, intermediate, layers, vocab, heads, kv_heads, head_dim, rotary_dim, rope_theta, eps,
+                      lin_k_heads, lin_v_heads, lin_k_dim, lin_v_dim, 4)
+    for l, f in enumerate(full_attention):
+        cfg.full_attention[l] = 1 if f else 0
+    return cfg
+
+
+def toy_config():
+    """The CPU-runnable toy: 4 layers (0-2 gated DeltaNet, 3 gated GQA attention), hidden 256, 4 q / 1 kv heads of 64,
+    DeltaNet 2 qk + 4 v heads of 64, FFN 704, vocabulary 4096."""
+    return make_config(256, 704, 4, 4096, 4, 1, 64, 16, 2, 4, 64, 64, [0, 0, 0, 1])
+
+
+def config_27b(layers=64):
+    """The 27B-class hybrid: 3:1 gated DeltaNet (16 qk / 48 v heads, dim 128) to gated GQA attention (24 q / 4 kv heads,
+    dim 256), hidden 5120, FFN 17408, vocabulary 248320."""
+    return make_config(5120, 17408, layers, 248320, 24, 4, 256, 64, 16, 48, 128, 128,
+                       [(l % 4) == 3 for l in range(layers)])
+
+
+_lib = None
+
+
+def lib():
+    """Loads the library; raises (no fallback) when it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError("libling_b200.so is missing: build it with `python ling-engine_b200/build.py` "
+                           "(there is no CPU fallback)")
+    L = C.CDLL(LIB_PATH)
+    L.ling_b200_last_error.restype = C.c_char_p
+    L.ling_b200_weight_bytes.restype = C.c_size_t
+    L.ling_b200_weight_bytes.argtypes = [C.c_void_p]
+    L.ling_b200_create.argtypes = [C.POINTER(ModelConfig), C.POINTER(Options), C.POINTER(C.c_void_p)]
+    L.ling_b200_destroy.argtypes = [C.c_void_p]
+    L.ling_b200_kvpool_create.restype = C.c_void_p
+    for name in ("destroy", "capacity", "free_pages", "pending_pages", "refs", "needed", "ensure", "share", "truncate",
+                 "unshare", "net_need", "resume_need", "reclaimable", "retain", "release", "retire"):
+        getattr(L, "ling_b200_kvpool_" + name).argtypes = None
+    _lib = L
+    return L
+
+
+def last_error():
+    return lib().ling_b200_last_error().decode()
+
+
+class LingError(RuntimeError):
+    pass
+
+
+def check(rc, what=""):
+    if rc != OK:
+        raise LingError("%s failed (status %d): %s" % (what, rc, last_error()))
+
+
+def _ip(a):
+    return a.ctypes.data_as(C.POINTER(C.c_int))
+
+
+def _fp(a):
+    return a.ctypes.data_as(C.POINTER(C.c_float)) if a is not None else None
+
+
+def _bp(a):
+    return a.ctypes.data_as(C.POINTER(C.c_ubyte)) if a is not None else None
+
+
+def make_steps(seqs):
+    """seqs: list of dicts {slot, pos, tokens, parent, chain, rope_delta=0, force=None} -> (ctypes array, keepalive)."""
+    arr = (SeqStep * len(seqs))()
+    keep = []
+    for i, s in enumerate(seqs):
+        tok = np.ascontiguousarray(s["tokens"], dtype=np.int32)
+        par = np.ascontiguousarray(s["parent"], dtype=np.int32)
+        keep += [tok, par]
+        arr[i].slot, arr[i].pos, arr[i].rope_delta = s["slot"], s["pos"], s.get("rope_delta", 0)
+        arr[i].n_rows, arr[i].chain = len(tok), s["chain"]
+        arr[i].tokens, arr[i].parent = _ip(tok), _ip(par)
+        if s.get("force") is not None:
+            f = np.ascontiguousarray(s["force"], dtype=np.int32)
+            keep.append(f)
+            arr[i].force_argmax = _ip(f)
+    return arr, keep
+
+
+class Context:
+    """One engine context on one GPU (ling_b200_create .. ling_b200_destroy)."""
+
+    def __init__(self, cfg, sessions=4, max_context=2048, page_tokens=16, pool_pages=512, max_seqs=4, max_rows=128,
+                 gemm_impl=0, use_graph=1, device=0, debug_rows=0, pdl=0):
+        self.cfg = cfg
+        self.opt = Options(sessions, max_context, page_tokens, pool_pages, max_seqs, max_rows, gemm_impl, use_graph,
+                           device, debug_rows, pdl)
+        self.h = C.c_void_p()
+        rc = lib().ling_b200_create(C.byref(cfg), C.byref(self.opt), C.byref(self.h))
+        if rc != OK:
+            err = last_error()
+            if self.h:
+                lib().ling_b200_destroy(self.h)
+            self.h = None
+            raise LingError("ling_b200_create failed (status %d): %s" % (rc, err))
+        self.last_rows = 0
+        self.last_seqs = 0
+
+    def close(self):
+        if self.h:
+            lib().ling_b200_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # ---- weights
+    def set_tensor(self, layer, tensor, a):
+        a = np.ascontiguousarray(a, dtype=np.float32)
+        rows, cols = (a.shape if a.ndim == 2 else (1, a.size))
+        check(lib().ling_b200_set_tensor(self.h, layer, tensor, _fp(a), rows, cols), "set_tensor")
+
+    def synth_weights(self, seed):
+        check(lib().ling_b200_synth_weights(self.h, C.c_uint64(seed)), "synth_weights")
+
+    def get_matrix(self, layer, tensor, rows, cols):
+        codes = np.zeros((rows, cols), np.uint8)
+        scales = np.zeros((rows, (cols + 127) // 128), np.float32)
+        check(lib().ling_b200_get_matrix(self.h, layer, tensor, _bp(codes), _fp(scales), rows, cols), "get_matrix")
+        return codes, scales
+
+    def weight_bytes(self):
+        return lib().ling_b200_weight_bytes(self.h)
+
+    # ---- sessions
+    def kv_table_set(self, slot, idx, pages):
+        idx = np.ascontiguousarray(idx, np.int32)
+        pages = np.ascontiguousarray(pages, np.int32)
+        check(lib().ling_b200_kv_table_set(self.h, slot, _ip(idx), _ip(pages), len(idx)), "kv_table_set")
+
+    def kv_pages_copy(self, src, dst):
+        src = np.ascontiguousarray(src, np.int32)
+        dst = np.ascontiguousarray(dst, np.int32)
+        check(lib().ling_b200_kv_pages_copy(self.h, _ip(src), _ip(dst), len(src)), "kv_pages_copy")
+
+    def kv_write(self, slot, attn_layer, start, k, v):
+        k = np.ascontiguousarray(k, np.float32)
+        v = np.ascontiguousarray(v, np.float32)
+        check(lib().ling_b200_kv_write(self.h, slot, attn_layer, start, k.shape[0], _fp(k), _fp(v)), "kv_write")
+
+    def kv_read(self, slot, attn_layer, start, n, codes=False):
+        hk, d = self.cfg.kv_heads, self.cfg.head_dim
+        if codes:
+            kc, vc = np.zeros((n, hk, d), np.uint8), np.zeros((n, hk, d), np.uint8)
+            ks, vs = np.zeros((n, hk), np.float32), np.zeros((n, hk), np.float32)
+            check(lib().ling_b200_kv_read(self.h, slot, attn_layer, start, n, None, None, _bp(kc), _fp(ks), _bp(vc), _fp(vs)),
+                  "kv_read")
+            return kc, ks, vc, vs
+        k, v = np.zeros((n, hk, d), np.float32), np.zeros((n, hk, d), np.float32)
+        check(lib().ling_b200_kv_read(self.h, slot, attn_layer, start, n, _fp(k), _fp(v), None, None, None, None), "kv_read")
+        return k, v
+
+    def synth_kv(self, slot, n, seed):
+        check(lib().ling_b200_synth_kv(self.h, slot, n, C.c_uint64(seed)), "synth_kv")
+
+    def state_write(self, slot, gdn_layer, state=None, conv=None):
+        s = None if state is None else np.ascontiguousarray(state, np.float32)
+        w = None if conv is None else np.ascontiguousarray(conv, np.float32)
+        check(lib().ling_b200_state_write(self.h, slot, gdn_layer, _fp(s), _fp(w)), "state_write")
+
+    def state_read(self, slot, gdn_layer):
+        c = self.cfg
+        s = np.zeros((c.lin_v_heads, c.lin_k_dim, c.lin_v_dim), np.float32)
+        w = np.zeros((c.conv_channels, 3), np.float32)
+        check(lib().ling_b200_state_read(self.h, slot, gdn_layer, _fp(s), _fp(w)), "state_read")
+        return s, w
+
+    def synth_state(self, slot, seed):
+        check(lib().ling_b200_synth_state(self.h, slot, C.c_uint64(seed)), "synth_state")
+
+    def state_hash(self, slot):
+        h = C.c_uint64()
+        check(lib().ling_b200_state_hash(self.h, slot, C.byref(h)), "state_hash")
+        return h.value
+
+    # ---- the step
+    def verify_step(self, seqs, flags=STEP_COMMIT):
+        arr, keep = make_steps(seqs)
+        res = (SeqResult * len(seqs))()
+        check(lib().ling_b200_verify_step(self.h, arr, len(seqs), flags, res), "verify_step")
+        self.last_rows = sum(len(s["tokens"]) for s in seqs)
+        self.last_seqs = len(seqs)
+        return list(res)
+
+    def stage(self, seqs, flags=STEP_COMMIT):
+        arr, keep = make_steps(seqs)
+        check(lib().ling_b200_step_stage(self.h, arr, len(seqs), flags), "step_stage")
+        self.last_rows = sum(len(s["tokens"]) for s in seqs)
+        self.last_seqs = len(seqs)
+
+    def launch(self):
+        check(lib().ling_b200_step_launch(self.h), "step_launch")
+
+    def fetch(self):
+        res = (SeqResult * self.last_seqs)()
+        check(lib().ling_b200_step_fetch(self.h, res), "step_fetch")
+        return list(res)
+
+    def read_tree_desc(self, seq):
+        t = TreeDesc()
+        check(lib().ling_b200_read_tree_desc(self.h, seq, C.byref(t)), "read_tree_desc")
+        return t
+
+    def read_packing(self):
+        n, s = self.last_rows, self.last_seqs
+        out = {"row0": np.zeros(s + 1, np.int32)}
+        for k in ("token", "seq_of", "depth", "rope_pos", "cache_slot"):
+            out[k] = np.zeros(n, np.int32)
+        out["anc"] = np.zeros(n, np.uint32)
+        check(lib().ling_b200_read_packing(self.h, _ip(out["row0"]), _ip(out["token"]), _ip(out["seq_of"]), _ip(out["depth"]),
+                                           _ip(out["rope_pos"]), _ip(out["cache_slot"]),
+                                           out["anc"].ctypes.data_as(C.POINTER(C.c_uint32))), "read_packing")
+        return out
+
+    def read_argmax(self):
+        ids, vals = np.zeros(self.last_rows, np.int32), np.zeros(self.last_rows, np.float32)
+        check(lib().ling_b200_read_argmax(self.h, _ip(ids), _fp(vals)), "read_argmax")
+        return ids, vals
+
+    def read_logits(self):
+        out = np.zeros((self.last_rows, self.cfg.vocab), np.float32)
+        check(lib().ling_b200_read_logits(self.h, _fp(out)), "read_logits")
+        return out
+
+    def read_tap(self, layer):
+        out = np.zeros((self.last_rows, self.cfg.hidden), np.float32)
+        check(lib().ling_b200_read_tap(self.h, layer, _fp(out)), "read_tap")
+        return out
+
+    # ---- timing
+    def timer_begin(self):
+        check(lib().ling_b200_timer_begin(self.h), "timer_begin")
+
+    def timer_end(self):
+        ms = C.c_float()
+        check(lib().ling_b200_timer_end(self.h, C.byref(ms)), "timer_end")
+        return ms.value
+
+    def profile_step(self):
+        ms = (C.c_float * 8)()
+        n = C.c_int()
+        check(lib().ling_b200_profile_step(self.h, ms, C.byref(n)), "profile_step")
+        return list(ms), n.value
+
+    def launch_count(self):
+        return lib().ling_b200_step_launch_count(self.h)
+
+    def flush_l2(self):
+        check(lib().ling_b200_flush_l2(self.h), "flush_l2")
+
+    def sync(self):
+        check(lib().ling_b200_sync(self.h), "sync")
+
+
+# ---- kernel-level helpers (host buffers in, host buffers out)
+def gemm_fp8(x, w, impl=0, splits=0, device=0):
+    x = np.ascontiguousarray(x, np.float32)
+    w = np.ascontiguousarray(w, np.float32)
+    y = np.zeros((x.shape[0], w.shape[0]), np.float32)
+    check(lib().ling_b200_gemm_fp8_host(device, impl, splits, _fp(x), _fp(w), _fp(y), x.shape[0], w.shape[0], x.shape[1]),
+          "gemm_fp8_host")
+    return y
+
+
+def gemm_fp8_bench(M, N, K, impl=0, splits=0, iters=20, device=0):
+    ms = C.c_float()
+    check(lib().ling_b200_gemm_fp8_bench(device, impl, splits, M, N, K, iters, C.byref(ms)), "gemm_fp8_bench")
+    return ms.value
+
+
+def describe_tree(parent, chain):
+    par = np.ascontiguousarray(parent, np.int32)
+    t = TreeDesc()
+    rc = lib().ling_b200_describe_tree(_ip(par), len(par), chain, C.byref(t))
+    return rc, t

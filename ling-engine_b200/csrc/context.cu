@@ -1,0 +1,1077 @@
+// context.cu -- the engine context behind the C ABI: every device buffer allocated at creation (the reference allocates
+// nothing while serving, src/core/engine.cpp:169 in the reference project), weights, the paged FP8 KV pool and the
+// DeltaNet state slots, and the verify step as one enqueue function that is captured into a CUDA graph per
+// capacity class (the reference replays three graphs per step with two host syncs, src/core/speculate.cpp:473-514;
+// here packing, forward pass, argmax, acceptance, compaction and commit are one graph and one sync).
+#include <algorithm>
+#include <cstring>
+#include <map>
+#include <vector>
+
+#include "gemm.h"
+#include "kernels.h"
+
+namespace lb {
+
+thread_local std::string g_error;
+void set_error(const std::string& what) { g_error = what; }
+
+namespace {
+
+template <typename T>
+int dev_alloc(T** p, size_t n, bool zero = true) {
+  *p = nullptr;
+  if (n == 0) n = 1;
+  if (!cuda_ok(cudaMalloc(reinterpret_cast<void**>(p), n * sizeof(T)), "cudaMalloc")) return LING_B200_ERR_CUDA;
+  if (zero && !cuda_ok(cudaMemset(*p, 0, n * sizeof(T)), "cudaMemset")) return LING_B200_ERR_CUDA;
+  return LING_B200_OK;
+}
+#define LB_TRY(call)                      \
+  do {                                    \
+    const int rc__ = (call);              \
+    if (rc__ != LING_B200_OK) return rc__; \
+  } while (0)
+
+struct LayerW {
+  bool full = false;
+  __nv_bfloat16 *input_norm = nullptr, *post_norm = nullptr;
+  Fp8Matrix gu, down;       // gate|up fused along N, down
+  Fp8Matrix in, out;        // DeltaNet: in_qkv|in_z fused, out
+  __nv_bfloat16 *in_a = nullptr, *in_b = nullptr, *conv = nullptr, *A_log = nullptr, *dt_bias = nullptr, *lin_norm = nullptr;
+  Fp8Matrix qkv, o;         // attention: q|k|v fused, o
+  __nv_bfloat16 *q_norm = nullptr, *k_norm = nullptr;
+};
+
+enum Family { kFamGemm = 0, kFamAttn, kFamGdn, kFamElem, kFamHead, kFamStep, kFamCount };
+
+}  // namespace
+}  // namespace lb
+
+using namespace lb;
+
+struct ling_b200_ctx {
+  ling_b200_model_config cfg{};
+  ling_b200_options opt{};
+  ModelDims d{};
+  int sm_count = 148;
+  cudaStream_t stream = nullptr;
+  std::vector<void*> owned;  // every device allocation, freed at destroy
+  std::vector<int> attn_index, gdn_index;
+
+  // weights
+  std::vector<LayerW> layers;
+  __nv_bfloat16 *embed = nullptr, *final_norm = nullptr;
+  Fp8Matrix head;
+  float* upload = nullptr;  // staging for ling_b200_set_tensor (largest tensor)
+  size_t upload_floats = 0;
+
+  // activations
+  float *h = nullptr, *xn = nullptr, *core = nullptr;
+  __half* qh = nullptr;
+  Fp8Acts xq_h, xq_v, xq_a, xq_i;
+  float* planes[2] = {nullptr, nullptr};
+  size_t plane_floats = 0;
+  float *pre = nullptr, *post = nullptr, *g = nullptr, *beta = nullptr;  // [n_gdn][rows][..], saved for the commit
+  float *part_o = nullptr, *part_ml = nullptr;
+  int chunk_slots = 0;
+  HeadEpilogue head_ep;
+  float* logits = nullptr;
+  float* taps = nullptr;
+  float* flush = nullptr;
+  size_t flush_floats = 0;
+
+  // sessions
+  KvPoolDev kv;
+  float *gdn_state = nullptr, *conv_state = nullptr;  // [slot][gdn layer][...]
+  size_t state_layer = 0, conv_layer = 0;             // floats per layer
+
+  // the step
+  StepBuffers sb;
+  uint8_t* stage_dev = nullptr;   // host-written block: n_seqs, seqs, parent, token, force
+  uint8_t* stage_host = nullptr;  // pinned mirror
+  size_t stage_bytes = 0;
+  ling_b200_seq_result* results_host = nullptr;  // pinned
+  int* err_host = nullptr;                       // pinned
+  int staged_seqs = 0, staged_rows = 0, staged_flags = 0, last_rows = 0, last_seqs = 0, last_flags = 0;
+  std::map<std::pair<int, int>, cudaGraphExec_t> graphs;  // (row class, flags)
+  int launches_per_step = 0;
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+
+  // profiling of one eager replay
+  bool profiling = false;
+  std::vector<std::pair<int, std::pair<cudaEvent_t, cudaEvent_t>>> prof;
+
+  template <typename T>
+  int alloc(T** p, size_t n, bool zero = true) {
+    const int rc = dev_alloc(p, n, zero);
+    if (rc == LING_B200_OK) owned.push_back(*p);
+    return rc;
+  }
+  int alloc_matrix(Fp8Matrix& w, int N, int K) {
+    w.N = N, w.K = K, w.N_pad = round_up(N, kTileN), w.K_pad = round_up(K, kBlockK), w.KB = w.K_pad / kBlockK;
+    w.splits = opt.gemm_impl == 1 ? 1 : choose_splits(w.N_pad, w.KB, sm_count);  // the CUDA-core GEMM never splits K
+    LB_TRY(alloc(&w.codes, size_t(w.N_pad) * w.K_pad));
+    LB_TRY(alloc(&w.scales, size_t(w.KB) * w.N_pad));
+    return make_weight_map(w);
+  }
+  int alloc_acts(Fp8Acts& x, int K) {
+    x.K = K, x.K_pad = round_up(K, kBlockK), x.KB = x.K_pad / kBlockK, x.rows_alloc = d.rows_alloc;
+    LB_TRY(alloc(&x.codes, size_t(x.rows_alloc) * x.K_pad));
+    LB_TRY(alloc(&x.scales, size_t(x.KB) * x.rows_alloc));
+    return make_acts_maps(x);
+  }
+  QuantOut qout(const Fp8Acts& x) const { return QuantOut{x.codes, x.scales, x.K, x.K_pad, x.rows_alloc}; }
+};
+
+namespace {
+
+int row_class(int M) { return M <= 128 ? token_tile(M) : round_up(M, 128); }
+
+struct Timed {
+  ling_b200_ctx* c;
+  bool on;
+  cudaEvent_t a = nullptr, b = nullptr;
+  Timed(ling_b200_ctx* ctx, int fam) : c(ctx), on(ctx->profiling) {
+    ++c->launches_per_step;
+    if (!on) return;
+    cudaEventCreate(&a), cudaEventCreate(&b);
+    cudaEventRecord(a, c->stream);
+    c->prof.push_back({fam, {a, b}});
+  }
+  ~Timed() {
+    if (on) cudaEventRecord(b, c->stream);
+  }
+};
+
+Planes planes_of(const ling_b200_ctx* c, int which, const Fp8Matrix& w, bool head = false) {
+  Planes p;
+  p.p = c->planes[which];
+  p.n = head ? 1 : w.splits;
+  p.ld = w.N_pad;
+  p.stride = size_t(c->d.rows_alloc) * w.N_pad;
+  return p;
+}
+
+int run_gemm(ling_b200_ctx* c, const Fp8Matrix& w, const Fp8Acts& x, int which, int rows, const HeadEpilogue* head = nullptr) {
+  Timed t(c, head ? kFamHead : kFamGemm);
+  GemmCall g;
+  g.W = &w, g.X = &x, g.M = rows;
+  g.out = head ? c->logits : c->planes[which];
+  g.ld = head ? w.N : w.N_pad;
+  g.split_stride = size_t(c->d.rows_alloc) * w.N_pad;
+  g.head = head;
+  g.impl = c->opt.gemm_impl;
+  g.err_flag = c->sb.err;
+  g.pdl = c->opt.pdl != 0 && c->opt.gemm_impl == 0;
+  return gemm_launch(g, c->stream);
+}
+
+// The whole step on the context's stream.  rows = the capacity class (grids and GEMM extents); the kernels read the
+// real extents from device memory.  Order of the forward pass: src/core/engine.cpp:1288-1745 (verify branch).
+int enqueue_step(ling_b200_ctx* c, int rows, int flags) {
+  const ModelDims& d = c->d;
+  cudaStream_t s = c->stream;
+  const int* n_rows = c->sb.n_rows_total;
+  const bool taps = (flags & LING_B200_STEP_KEEP_TAPS) != 0;
+  const bool keep_logits = (flags & LING_B200_STEP_KEEP_LOGITS) != 0;
+  c->launches_per_step = 0;
+  {
+    Timed t(c, kFamStep);
+    LB_TRY(pack_launch(c->sb, d, s));
+  }
+  Planes none;
+  none.p = nullptr;
+  Planes carry = none;  // the previous layer's down projection, still to be added to the residual
+  for (int l = 0; l < c->cfg.layers; ++l) {
+    const LayerW& L = c->layers[l];
+    {
+      Timed t(c, kFamElem);
+      LB_TRY(norm_quant_launch(c->h, carry, l == 0 ? c->sb.token : nullptr, c->embed, L.input_norm, L.full ? nullptr : c->xn,
+                               c->qout(c->xq_h), n_rows, rows, d.H, d.eps, s));
+    }
+    if (L.full) {
+      const int al = c->attn_index[l];
+      LB_TRY(run_gemm(c, L.qkv, c->xq_h, 0, rows));
+      const Planes p0 = planes_of(c, 0, L.qkv);
+      {
+        Timed t(c, kFamAttn);
+        LB_TRY(attn_prepare_launch(p0, c->sb, d, al, L.q_norm, L.k_norm, c->qh, c->kv, rows, s));
+      }
+      {
+        Timed t(c, kFamAttn);
+        LB_TRY(attention_launch(c->qh, c->sb, d, al, c->kv, c->part_o, c->part_ml, c->chunk_slots, c->sm_count * 2, s));
+      }
+      {
+        Timed t(c, kFamAttn);
+        LB_TRY(attn_combine_launch(c->part_o, c->part_ml, p0, c->sb, d, c->qout(c->xq_a), rows, s));
+      }
+      LB_TRY(run_gemm(c, L.o, c->xq_a, 1, rows));
+      carry = planes_of(c, 1, L.o);
+    } else {
+      const int gl = c->gdn_index[l];
+      LB_TRY(run_gemm(c, L.in, c->xq_h, 0, rows));
+      const Planes p0 = planes_of(c, 0, L.in);
+      float* pre = c->pre + size_t(gl) * d.rows_alloc * d.C;
+      float* post = c->post + size_t(gl) * d.rows_alloc * d.C;
+      float* g = c->g + size_t(gl) * d.rows_alloc * d.HV;
+      float* beta = c->beta + size_t(gl) * d.rows_alloc * d.HV;
+      {
+        Timed t(c, kFamGdn);
+        LB_TRY(ab_gating_launch(c->xn, L.in_a, L.in_b, L.A_log, L.dt_bias, g, beta, n_rows, rows, d.H, d.HV, s));
+      }
+      {
+        Timed t(c, kFamGdn);
+        LB_TRY(conv_tree_launch(p0, c->sb, d, L.conv, c->conv_state + size_t(gl) * c->conv_layer, c->conv_layer * d.n_gdn, pre,
+                                post, s));
+      }
+      {
+        Timed t(c, kFamGdn);
+        LB_TRY(gdn_tree_launch(post, g, beta, c->sb, d, c->gdn_state + size_t(gl) * c->state_layer, c->state_layer * d.n_gdn,
+                               c->core, c->sm_count * 4, s));
+      }
+      {
+        Timed t(c, kFamGdn);
+        LB_TRY(gated_norm_quant_launch(c->core, p0, d.C, L.lin_norm, c->qout(c->xq_v), n_rows, rows, d.HV, d.Dv, d.eps, s));
+      }
+      LB_TRY(run_gemm(c, L.out, c->xq_v, 1, rows));
+      carry = planes_of(c, 1, L.out);
+    }
+    {
+      Timed t(c, kFamElem);
+      LB_TRY(norm_quant_launch(c->h, carry, nullptr, nullptr, L.post_norm, nullptr, c->qout(c->xq_h), n_rows, rows, d.H, d.eps, s));
+    }
+    LB_TRY(run_gemm(c, L.gu, c->xq_h, 0, rows));
+    {
+      Timed t(c, kFamElem);
+      LB_TRY(silu_mul_quant_launch(planes_of(c, 0, L.gu), d.I, c->qout(c->xq_i), n_rows, rows, s));
+    }
+    LB_TRY(run_gemm(c, L.down, c->xq_i, 1, rows));
+    carry = planes_of(c, 1, L.down);
+    if (taps) {
+      Timed t(c, kFamElem);
+      LB_TRY(tap_launch(c->h, carry, c->taps + size_t(l) * c->opt.debug_rows * d.H, n_rows, std::min(rows, c->opt.debug_rows),
+                        d.H, s));
+    }
+  }
+  {
+    Timed t(c, kFamElem);
+    LB_TRY(norm_quant_launch(c->h, carry, nullptr, nullptr, c->final_norm, c->xn, c->qout(c->xq_h), n_rows, rows, d.H, d.eps, s));
+  }
+  if (taps) {
+    Timed t(c, kFamElem);
+    LB_TRY(copy_rows_launch(c->xn, c->taps + size_t(c->cfg.layers) * c->opt.debug_rows * d.H, n_rows,
+                            std::min(rows, c->opt.debug_rows), d.H, s));
+  }
+  HeadEpilogue ep = c->head_ep;
+  ep.store_logits = keep_logits;
+  LB_TRY(run_gemm(c, c->head, c->xq_h, 0, keep_logits ? std::min(rows, c->opt.debug_rows) : rows, &ep));
+  {
+    Timed t(c, kFamHead);
+    LB_TRY(argmax_reduce_launch(ep.tile_val, ep.tile_idx, c->head.N_pad / kTileN, ep.rows_alloc, c->sb.argmax_id,
+                                c->sb.argmax_val, n_rows, rows, s));
+  }
+  {
+    Timed t(c, kFamStep);
+    LB_TRY(accept_launch(c->sb, d, 0, s));
+  }
+  if (flags & LING_B200_STEP_COMMIT) {
+    {
+      Timed t(c, kFamStep);
+      LB_TRY(kv_compact_launch(c->sb, d, c->kv, s));
+    }
+    {
+      Timed t(c, kFamStep);
+      LB_TRY(conv_commit_launch(c->sb, d, c->pre, size_t(d.rows_alloc) * d.C, c->conv_state, c->conv_layer * d.n_gdn,
+                                c->conv_layer, s));
+    }
+    {
+      Timed t(c, kFamStep);
+      LB_TRY(gdn_commit_launch(c->sb, d, c->post, c->g, c->beta, size_t(d.rows_alloc) * d.C, size_t(d.rows_alloc) * d.HV,
+                               c->gdn_state, c->state_layer * d.n_gdn, c->state_layer, c->sm_count * 4, s));
+    }
+  }
+  return LING_B200_OK;
+}
+
+int check_ctx(const ling_b200_ctx* c) {
+  if (!c) {
+    set_error("null context");
+    return LING_B200_ERR_ARG;
+  }
+  return LING_B200_OK;
+}
+
+// A tensor's place in the fused matrices: destination matrix, first row.
+struct MatSlot {
+  Fp8Matrix* w = nullptr;
+  int row_off = 0, rows = 0, cols = 0;
+};
+MatSlot mat_slot(ling_b200_ctx* c, int layer, int tensor) {
+  const ModelDims& d = c->d;
+  MatSlot m;
+  if (tensor == LING_B200_T_LM_HEAD) return MatSlot{&c->head, 0, d.V, d.H};
+  if (layer < 0 || layer >= c->cfg.layers) return m;
+  LayerW& L = c->layers[layer];
+  switch (tensor) {
+    case LING_B200_T_GATE: return MatSlot{&L.gu, 0, d.I, d.H};
+    case LING_B200_T_UP: return MatSlot{&L.gu, d.I, d.I, d.H};
+    case LING_B200_T_DOWN: return MatSlot{&L.down, 0, d.H, d.I};
+  }
+  if (L.full) {
+    switch (tensor) {
+      case LING_B200_T_Q: return MatSlot{&L.qkv, 0, d.Hq * 2 * d.D, d.H};
+      case LING_B200_T_K: return MatSlot{&L.qkv, d.Hq * 2 * d.D, d.Hkv * d.D, d.H};
+      case LING_B200_T_V: return MatSlot{&L.qkv, d.Hq * 2 * d.D + d.Hkv * d.D, d.Hkv * d.D, d.H};
+      case LING_B200_T_O: return MatSlot{&L.o, 0, d.H, d.Hq * d.D};
+    }
+  } else {
+    switch (tensor) {
+      case LING_B200_T_IN_QKV: return MatSlot{&L.in, 0, d.C, d.H};
+      case LING_B200_T_IN_Z: return MatSlot{&L.in, d.C, d.Vs, d.H};
+      case LING_B200_T_OUT: return MatSlot{&L.out, 0, d.H, d.Vs};
+    }
+  }
+  return m;
+}
+struct VecSlot {
+  __nv_bfloat16* p = nullptr;
+  size_t n = 0;
+  float std_ = 0.02f, bias = 0.f;
+};
+VecSlot vec_slot(ling_b200_ctx* c, int layer, int tensor) {
+  const ModelDims& d = c->d;
+  if (tensor == LING_B200_T_EMBED) return VecSlot{c->embed, size_t(d.V) * d.H};
+  if (tensor == LING_B200_T_FINAL_NORM) return VecSlot{c->final_norm, size_t(d.H)};
+  if (layer < 0 || layer >= c->cfg.layers) return VecSlot{};
+  LayerW& L = c->layers[layer];
+  switch (tensor) {
+    case LING_B200_T_INPUT_NORM: return VecSlot{L.input_norm, size_t(d.H)};
+    case LING_B200_T_POST_NORM: return VecSlot{L.post_norm, size_t(d.H)};
+  }
+  if (L.full) {
+    switch (tensor) {
+      case LING_B200_T_Q_NORM: return VecSlot{L.q_norm, size_t(d.D)};
+      case LING_B200_T_K_NORM: return VecSlot{L.k_norm, size_t(d.D)};
+    }
+  } else {
+    switch (tensor) {
+      case LING_B200_T_IN_A: return VecSlot{L.in_a, size_t(d.HV) * d.H};
+      case LING_B200_T_IN_B: return VecSlot{L.in_b, size_t(d.HV) * d.H};
+      case LING_B200_T_CONV: return VecSlot{L.conv, size_t(d.C) * 4, 0.3f};
+      case LING_B200_T_A_LOG: return VecSlot{L.A_log, size_t(d.HV), 0.5f};
+      case LING_B200_T_DT_BIAS: return VecSlot{L.dt_bias, size_t(d.HV), 0.5f};
+      case LING_B200_T_LIN_NORM: return VecSlot{L.lin_norm, size_t(d.Dv), 0.02f, 1.f};
+    }
+  }
+  return VecSlot{};
+}
+
+const int kLayerTensorsFull[] = {LING_B200_T_INPUT_NORM, LING_B200_T_POST_NORM, LING_B200_T_GATE, LING_B200_T_UP,
+                                 LING_B200_T_DOWN,       LING_B200_T_Q,         LING_B200_T_K,    LING_B200_T_V,
+                                 LING_B200_T_O,          LING_B200_T_Q_NORM,    LING_B200_T_K_NORM};
+const int kLayerTensorsGdn[] = {LING_B200_T_INPUT_NORM, LING_B200_T_POST_NORM, LING_B200_T_GATE,   LING_B200_T_UP,
+                                LING_B200_T_DOWN,       LING_B200_T_IN_QKV,    LING_B200_T_IN_Z,   LING_B200_T_OUT,
+                                LING_B200_T_IN_A,       LING_B200_T_IN_B,      LING_B200_T_CONV,   LING_B200_T_A_LOG,
+                                LING_B200_T_DT_BIAS,    LING_B200_T_LIN_NORM};
+
+int synth_tensor(ling_b200_ctx* c, uint64_t seed, int layer, int tensor) {
+  const uint64_t key = stream_key(seed, weight_stream(layer, tensor));
+  const MatSlot m = mat_slot(c, layer, tensor);
+  if (m.w) return quant_weight_launch(nullptr, key, 0.02f, 1, m.w->codes, m.w->scales, m.row_off, m.rows, m.cols, m.w->N_pad,
+                                      m.w->K_pad, c->stream);
+  const VecSlot v = vec_slot(c, layer, tensor);
+  if (v.p) return fill_bf16_launch(nullptr, key, v.std_, v.bias, 1, v.p, v.n, c->stream);
+  set_error("synth: unknown tensor");
+  return LING_B200_ERR_ARG;
+}
+
+int finish(ling_b200_ctx* c) {
+  LB_CUDA(cudaStreamSynchronize(c->stream));
+  return LING_B200_OK;
+}
+
+}  // namespace
+
+// ================================================================================================ C ABI
+extern "C" {
+
+const char* ling_b200_last_error(void) { return g_error.c_str(); }
+int ling_b200_abi_version(void) { return 1; }
+
+int ling_b200_device_count(void) {
+  int n = 0;
+  if (cudaGetDeviceCount(&n) != cudaSuccess) return 0;
+  return n;
+}
+int ling_b200_device_name(int device, char* buf, int len) {
+  cudaDeviceProp p;
+  LB_CUDA(cudaGetDeviceProperties(&p, device));
+  std::snprintf(buf, size_t(len), "%s (sm_%d%d, %d SMs)", p.name, p.major, p.minor, p.multiProcessorCount);
+  return LING_B200_OK;
+}
+
+int ling_b200_create(const ling_b200_model_config* cfg, const ling_b200_options* opt, ling_b200_ctx** out) {
+  if (!cfg || !opt || !out) {
+    set_error("create: null argument");
+    return LING_B200_ERR_ARG;
+  }
+  *out = nullptr;
+  const int G = cfg->kv_heads > 0 ? cfg->heads / cfg->kv_heads : 0;
+  const bool ok = cfg->layers >= 1 && cfg->layers <= LING_B200_MAX_LAYERS && cfg->hidden % 4 == 0 && cfg->hidden <= 8192 &&
+                  cfg->intermediate % 4 == 0 && cfg->conv_kernel == 4 && cfg->kv_heads > 0 && cfg->heads % cfg->kv_heads == 0 &&
+                  (cfg->head_dim == 64 || cfg->head_dim == 128 || cfg->head_dim == 256) && cfg->rotary_dim % 2 == 0 &&
+                  cfg->rotary_dim <= cfg->head_dim && (cfg->lin_k_dim == 64 || cfg->lin_k_dim == 128) &&
+                  cfg->lin_v_dim % 32 == 0 && cfg->lin_v_dim <= 128 && cfg->lin_k_heads > 0 &&
+                  cfg->lin_v_heads % cfg->lin_k_heads == 0 && G >= 1 && opt->sessions >= 1 &&
+                  (opt->page_tokens == 16 || opt->page_tokens == 32 || opt->page_tokens == 64) && opt->pool_pages >= 1 &&
+                  opt->max_seqs >= 1 && opt->max_seqs <= LING_B200_MAX_SEQS && opt->max_rows >= 1 &&
+                  opt->max_rows <= LING_B200_MAX_ROWS && opt->max_context >= 1 && opt->debug_rows >= 0;
+  if (!ok) {
+    set_error("create: unsupported model configuration or options");
+    return LING_B200_ERR_ARG;
+  }
+  LB_CUDA(cudaSetDevice(opt->device));
+  cudaDeviceProp prop;
+  LB_CUDA(cudaGetDeviceProperties(&prop, opt->device));
+  if (prop.major != 10) {
+    set_error(std::string("this library is built for sm_100a (B200) only; device is ") + prop.name);
+    return LING_B200_ERR_UNSUPPORTED;
+  }
+  ling_b200_ctx* c = new ling_b200_ctx;
+  *out = c;  // the caller destroys it also after a failed creation
+  c->cfg = *cfg, c->opt = *opt;
+  c->sm_count = prop.multiProcessorCount;
+  ModelDims& d = c->d;
+  d.H = cfg->hidden, d.I = cfg->intermediate, d.V = cfg->vocab, d.Hq = cfg->heads, d.Hkv = cfg->kv_heads, d.D = cfg->head_dim;
+  d.rot = cfg->rotary_dim, d.Hk = cfg->lin_k_heads, d.HV = cfg->lin_v_heads, d.Dk = cfg->lin_k_dim, d.Dv = cfg->lin_v_dim;
+  d.C = 2 * d.Hk * d.Dk + d.HV * d.Dv, d.Vs = d.HV * d.Dv;
+  d.theta = cfg->rope_theta, d.eps = cfg->eps;
+  d.page_tokens = opt->page_tokens, d.pool_pages = opt->pool_pages;
+  d.max_pages = ceil_div(opt->max_context, opt->page_tokens);
+  d.rows_alloc = round_up(opt->max_rows, 128);
+  d.max_seqs = opt->max_seqs;
+  c->layers.resize(cfg->layers);
+  c->attn_index.assign(cfg->layers, -1), c->gdn_index.assign(cfg->layers, -1);
+  d.n_attn = d.n_gdn = 0;
+  for (int l = 0; l < cfg->layers; ++l) {
+    c->layers[l].full = cfg->full_attention[l] != 0;
+    if (c->layers[l].full) c->attn_index[l] = d.n_attn++;
+    else c->gdn_index[l] = d.n_gdn++;
+  }
+  LB_CUDA(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
+  LB_CUDA(cudaEventCreate(&c->ev0));
+  LB_CUDA(cudaEventCreate(&c->ev1));
+
+  // ---- weights
+  size_t biggest = size_t(d.V) * d.H;
+  LB_TRY(c->alloc(&c->embed, size_t(d.V) * d.H));
+  LB_TRY(c->alloc(&c->final_norm, size_t(d.H)));
+  LB_TRY(c->alloc_matrix(c->head, d.V, d.H));
+  c->head.splits = 1;
+  size_t max_plane = 0;  // floats of the largest GEMM output (all K splits); the head writes no planes
+  for (int l = 0; l < cfg->layers; ++l) {
+    LayerW& L = c->layers[l];
+    LB_TRY(c->alloc(&L.input_norm, size_t(d.H)));
+    LB_TRY(c->alloc(&L.post_norm, size_t(d.H)));
+    LB_TRY(c->alloc_matrix(L.gu, 2 * d.I, d.H));
+    LB_TRY(c->alloc_matrix(L.down, d.H, d.I));
+    std::vector<Fp8Matrix*> mats = {&L.gu, &L.down};
+    if (L.full) {
+      LB_TRY(c->alloc_matrix(L.qkv, d.Hq * 2 * d.D + 2 * d.Hkv * d.D, d.H));
+      LB_TRY(c->alloc_matrix(L.o, d.H, d.Hq * d.D));
+      LB_TRY(c->alloc(&L.q_norm, size_t(d.D)));
+      LB_TRY(c->alloc(&L.k_norm, size_t(d.D)));
+      mats.push_back(&L.qkv), mats.push_back(&L.o);
+    } else {
+      LB_TRY(c->alloc_matrix(L.in, d.C + d.Vs, d.H));
+      LB_TRY(c->alloc_matrix(L.out, d.H, d.Vs));
+      LB_TRY(c->alloc(&L.in_a, size_t(d.HV) * d.H));
+      LB_TRY(c->alloc(&L.in_b, size_t(d.HV) * d.H));
+      LB_TRY(c->alloc(&L.conv, size_t(d.C) * 4));
+      LB_TRY(c->alloc(&L.A_log, size_t(d.HV)));
+      LB_TRY(c->alloc(&L.dt_bias, size_t(d.HV)));
+      LB_TRY(c->alloc(&L.lin_norm, size_t(d.Dv)));
+      mats.push_back(&L.in), mats.push_back(&L.out);
+    }
+    for (Fp8Matrix* w : mats) max_plane = std::max(max_plane, size_t(w->splits) * d.rows_alloc * w->N_pad);
+  }
+  biggest = std::max(biggest, size_t(2) * d.I * d.H);
+  c->upload_floats = std::min(biggest, size_t(64) << 20);  // 256 MB of staging; larger tensors go in row bands
+  LB_TRY(c->alloc(&c->upload, c->upload_floats, false));
+
+  // ---- activations
+  LB_TRY(c->alloc(&c->h, size_t(d.rows_alloc) * d.H));
+  LB_TRY(c->alloc(&c->xn, size_t(d.rows_alloc) * d.H));
+  LB_TRY(c->alloc(&c->core, size_t(d.rows_alloc) * d.Vs));
+  LB_TRY(c->alloc(&c->qh, size_t(d.rows_alloc) * d.Hq * d.D));
+  LB_TRY(c->alloc_acts(c->xq_h, d.H));
+  LB_TRY(c->alloc_acts(c->xq_v, d.Vs));
+  LB_TRY(c->alloc_acts(c->xq_a, d.Hq * d.D));
+  LB_TRY(c->alloc_acts(c->xq_i, d.I));
+  c->plane_floats = max_plane;
+  LB_TRY(c->alloc(&c->planes[0], max_plane));
+  LB_TRY(c->alloc(&c->planes[1], max_plane));
+  LB_TRY(c->alloc(&c->pre, size_t(d.n_gdn) * d.rows_alloc * d.C));
+  LB_TRY(c->alloc(&c->post, size_t(d.n_gdn) * d.rows_alloc * d.C));
+  LB_TRY(c->alloc(&c->g, size_t(d.n_gdn) * d.rows_alloc * d.HV));
+  LB_TRY(c->alloc(&c->beta, size_t(d.n_gdn) * d.rows_alloc * d.HV));
+  // Chunk slots of the flash-decoding partials: every mapped position in chunks of kAttnChunk plus, per sequence, one
+  // partly filled chunk and the in-flight chunk; per kv head.
+  const size_t pool_positions = size_t(d.pool_pages) * d.page_tokens;
+  c->chunk_slots = int((pool_positions / kAttnChunk + size_t(2) * d.max_seqs) * d.Hkv);
+  const size_t rmax = size_t(kTreeRows) * (d.Hq / d.Hkv);
+  LB_TRY(c->alloc(&c->part_o, size_t(c->chunk_slots) * rmax * d.D, false));
+  LB_TRY(c->alloc(&c->part_ml, size_t(c->chunk_slots) * rmax * 2, false));
+  c->head_ep.rows_alloc = d.rows_alloc;
+  LB_TRY(c->alloc(&c->head_ep.tile_val, size_t(c->head.N_pad / kTileN) * d.rows_alloc));
+  LB_TRY(c->alloc(&c->head_ep.tile_idx, size_t(c->head.N_pad / kTileN) * d.rows_alloc));
+  if (opt->debug_rows > 0) {
+    LB_TRY(c->alloc(&c->logits, size_t(opt->debug_rows) * d.V));
+    LB_TRY(c->alloc(&c->taps, size_t(cfg->layers + 1) * opt->debug_rows * d.H));
+  }
+  c->flush_floats = size_t(192) << 18;  // 192 MiB: more than the 126 MB L2
+  LB_TRY(c->alloc(&c->flush, c->flush_floats, false));
+
+  // ---- sessions
+  const size_t kv_slots = size_t(d.n_attn) * 2 * d.Hkv * (d.pool_pages + 1) * d.page_tokens;
+  LB_TRY(c->alloc(&c->kv.codes, kv_slots * d.D));
+  LB_TRY(c->alloc(&c->kv.scales, kv_slots));
+  LB_TRY(c->alloc(&c->kv.tables, size_t(opt->sessions) * d.max_pages));
+  c->state_layer = size_t(d.HV) * d.Dk * d.Dv;
+  c->conv_layer = size_t(d.C) * 3;
+  LB_TRY(c->alloc(&c->gdn_state, size_t(opt->sessions) * d.n_gdn * c->state_layer));
+  LB_TRY(c->alloc(&c->conv_state, size_t(opt->sessions) * d.n_gdn * c->conv_layer));
+
+  // ---- the step's descriptors: one host-written block
+  const size_t ms = size_t(d.max_seqs);
+  size_t off = 0;
+  auto take = [&](size_t bytes) {
+    const size_t at = off;
+    off += (bytes + 15) / 16 * 16;
+    return at;
+  };
+  const size_t o_n = take(sizeof(int)), o_seqs = take(ms * sizeof(SeqDev)), o_par = take(ms * kTreeRows * 4);
+  const size_t o_tok = take(ms * kTreeRows * 4), o_force = take(ms * kTreeRows * 4);
+  c->stage_bytes = off;
+  LB_TRY(c->alloc(&c->stage_dev, c->stage_bytes));
+  LB_CUDA(cudaMallocHost(reinterpret_cast<void**>(&c->stage_host), c->stage_bytes));
+  std::memset(c->stage_host, 0, c->stage_bytes);
+  LB_CUDA(cudaMallocHost(reinterpret_cast<void**>(&c->results_host), ms * sizeof(ling_b200_seq_result)));
+  LB_CUDA(cudaMallocHost(reinterpret_cast<void**>(&c->err_host), sizeof(int)));
+  StepBuffers& sb = c->sb;
+  sb.n_seqs = reinterpret_cast<int*>(c->stage_dev + o_n);
+  sb.seqs = reinterpret_cast<SeqDev*>(c->stage_dev + o_seqs);
+  sb.in_parent = reinterpret_cast<int*>(c->stage_dev + o_par);
+  sb.in_token = reinterpret_cast<int*>(c->stage_dev + o_tok);
+  sb.in_force = reinterpret_cast<int*>(c->stage_dev + o_force);
+  LB_TRY(c->alloc(&sb.row0, ms + 1));
+  LB_TRY(c->alloc(&sb.n_rows_total, 1));
+  LB_TRY(c->alloc(&sb.token, size_t(d.rows_alloc)));
+  LB_TRY(c->alloc(&sb.seq_of, size_t(d.rows_alloc)));
+  LB_TRY(c->alloc(&sb.local, size_t(d.rows_alloc)));
+  LB_TRY(c->alloc(&sb.depth, size_t(d.rows_alloc)));
+  LB_TRY(c->alloc(&sb.rope_pos, size_t(d.rows_alloc)));
+  LB_TRY(c->alloc(&sb.cache_slot, size_t(d.rows_alloc)));
+  LB_TRY(c->alloc(&sb.anc, size_t(d.rows_alloc)));
+  LB_TRY(c->alloc(&sb.trees, ms));
+  LB_TRY(c->alloc(&sb.argmax_id, size_t(d.rows_alloc)));
+  LB_TRY(c->alloc(&sb.argmax_val, size_t(d.rows_alloc)));
+  LB_TRY(c->alloc(&sb.results, ms));
+  LB_TRY(c->alloc(&sb.err, 1));
+  LB_CUDA(cudaDeviceSynchronize());
+  return LING_B200_OK;
+}
+
+void ling_b200_destroy(ling_b200_ctx* c) {
+  if (!c) return;
+  cudaSetDevice(c->opt.device);
+  if (c->stream) cudaStreamSynchronize(c->stream);
+  for (auto& kvp : c->graphs) cudaGraphExecDestroy(kvp.second);
+  for (void* p : c->owned) cudaFree(p);
+  if (c->stage_host) cudaFreeHost(c->stage_host);
+  if (c->results_host) cudaFreeHost(c->results_host);
+  if (c->err_host) cudaFreeHost(c->err_host);
+  if (c->ev0) cudaEventDestroy(c->ev0);
+  if (c->ev1) cudaEventDestroy(c->ev1);
+  if (c->stream) cudaStreamDestroy(c->stream);
+  delete c;
+}
+
+size_t ling_b200_weight_bytes(const ling_b200_ctx* c) {
+  if (!c) return 0;
+  const ModelDims& d = c->d;
+  size_t b = c->head.bytes() + size_t(d.H) * 2;
+  for (const LayerW& L : c->layers) {
+    b += L.gu.bytes() + L.down.bytes() + size_t(2) * d.H * 2;
+    if (L.full) b += L.qkv.bytes() + L.o.bytes() + size_t(2) * d.D * 2;
+    else b += L.in.bytes() + L.out.bytes() + (size_t(2) * d.HV * d.H + size_t(d.C) * 4 + 2 * d.HV + d.Dv) * 2;
+  }
+  return b;
+}
+
+int ling_b200_set_tensor(ling_b200_ctx* c, int layer, int tensor, const float* host, int rows, int cols) {
+  LB_TRY(check_ctx(c));
+  if (!host || rows < 1 || cols < 1) {
+    set_error("set_tensor: bad argument");
+    return LING_B200_ERR_ARG;
+  }
+  const MatSlot m = mat_slot(c, layer, tensor);
+  if (m.w) {
+    if (rows != m.rows || cols != m.cols) {
+      set_error("set_tensor: shape mismatch");
+      return LING_B200_ERR_ARG;
+    }
+    const int band = int(std::max<size_t>(1, c->upload_floats / size_t(cols)));
+    for (int r = 0; r < rows; r += band) {
+      const int nr = std::min(band, rows - r);
+      LB_CUDA(cudaMemcpyAsync(c->upload, host + size_t(r) * cols, size_t(nr) * cols * 4, cudaMemcpyHostToDevice, c->stream));
+      LB_TRY(quant_weight_launch(c->upload, 0, 0.f, 0, m.w->codes, m.w->scales, m.row_off + r, nr, cols, m.w->N_pad, m.w->K_pad,
+                                 c->stream));
+      LB_TRY(finish(c));
+    }
+    return LING_B200_OK;
+  }
+  const VecSlot v = vec_slot(c, layer, tensor);
+  if (!v.p || size_t(rows) * cols != v.n) {
+    set_error("set_tensor: unknown tensor or shape mismatch");
+    return LING_B200_ERR_ARG;
+  }
+  for (size_t at = 0; at < v.n; at += c->upload_floats) {
+    const size_t n = std::min(c->upload_floats, v.n - at);
+    LB_CUDA(cudaMemcpyAsync(c->upload, host + at, n * 4, cudaMemcpyHostToDevice, c->stream));
+    LB_TRY(fill_bf16_launch(c->upload, 0, 0.f, 0.f, 0, v.p + at, n, c->stream));
+    LB_TRY(finish(c));
+  }
+  return LING_B200_OK;
+}
+
+int ling_b200_synth_weights(ling_b200_ctx* c, uint64_t seed) {
+  LB_TRY(check_ctx(c));
+  LB_TRY(synth_tensor(c, seed, -1, LING_B200_T_EMBED));
+  LB_TRY(synth_tensor(c, seed, -1, LING_B200_T_FINAL_NORM));
+  LB_TRY(synth_tensor(c, seed, -1, LING_B200_T_LM_HEAD));
+  for (int l = 0; l < c->cfg.layers; ++l) {
+    if (c->layers[l].full) {
+      for (int t : kLayerTensorsFull) LB_TRY(synth_tensor(c, seed, l, t));
+    } else {
+      for (int t : kLayerTensorsGdn) LB_TRY(synth_tensor(c, seed, l, t));
+    }
+  }
+  return finish(c);
+}
+
+int ling_b200_get_matrix(ling_b200_ctx* c, int layer, int tensor, uint8_t* codes, float* scales, int rows, int cols) {
+  LB_TRY(check_ctx(c));
+  const MatSlot m = mat_slot(c, layer, tensor);
+  if (!m.w || rows != m.rows || cols != m.cols) {
+    set_error("get_matrix: unknown matrix or shape mismatch");
+    return LING_B200_ERR_ARG;
+  }
+  LB_TRY(finish(c));
+  const Fp8Matrix& w = *m.w;
+  if (codes)
+    LB_CUDA(cudaMemcpy2D(codes, size_t(cols), w.codes + size_t(m.row_off) * w.K_pad, size_t(w.K_pad), size_t(cols), size_t(rows),
+                         cudaMemcpyDeviceToHost));
+  if (scales) {
+    const int KB = ceil_div(cols, 128);
+    std::vector<float> tmp(size_t(KB) * rows);
+    LB_CUDA(cudaMemcpy2D(tmp.data(), size_t(rows) * 4, w.scales + m.row_off, size_t(w.N_pad) * 4, size_t(rows) * 4, size_t(KB),
+                         cudaMemcpyDeviceToHost));
+    for (int r = 0; r < rows; ++r)
+      for (int b = 0; b < KB; ++b) scales[size_t(r) * KB + b] = tmp[size_t(b) * rows + r];
+  }
+  return LING_B200_OK;
+}
+
+// ------------------------------------------------------------------------------------------------ sessions
+int ling_b200_kv_table_set(ling_b200_ctx* c, int slot, const int* idx, const int* page, int n) {
+  LB_TRY(check_ctx(c));
+  if (slot < 0 || slot >= c->opt.sessions || n < 0) {
+    set_error("kv_table_set: bad slot");
+    return LING_B200_ERR_ARG;
+  }
+  for (int i = 0; i < n; ++i)
+    if (idx[i] < 0 || idx[i] >= c->d.max_pages || page[i] < 0 || page[i] > c->d.pool_pages) {
+      set_error("kv_table_set: entry out of range");
+      return LING_B200_ERR_ARG;
+    }
+  // Ordered on the step stream before the next step reads the table; runs of consecutive indices go as one copy.
+  for (int i = 0; i < n;) {
+    int j = i + 1;
+    while (j < n && idx[j] == idx[j - 1] + 1) ++j;
+    LB_CUDA(cudaMemcpyAsync(c->kv.tables + size_t(slot) * c->d.max_pages + idx[i], page + i, size_t(j - i) * 4,
+                            cudaMemcpyHostToDevice, c->stream));
+    i = j;
+  }
+  return finish(c);  // the caller's arrays may be reused at once
+}
+
+int ling_b200_kv_pages_copy(ling_b200_ctx* c, const int* src, const int* dst, int n) {
+  LB_TRY(check_ctx(c));
+  for (int i = 0; i < n; ++i) {
+    if (src[i] < 1 || src[i] > c->d.pool_pages || dst[i] < 1 || dst[i] > c->d.pool_pages) {
+      set_error("kv_pages_copy: page out of range");
+      return LING_B200_ERR_ARG;
+    }
+    LB_TRY(kv_page_copy_launch(c->d, c->kv, src[i], dst[i], c->stream));
+  }
+  return LING_B200_OK;
+}
+
+static int check_positions(ling_b200_ctx* c, int slot, int al, int from, int n) {
+  if (slot < 0 || slot >= c->opt.sessions || al < 0 || al >= c->d.n_attn || from < 0 || n < 0 ||
+      from + n > c->d.max_pages * c->d.page_tokens) {
+    set_error("kv: slot, layer or positions out of range");
+    return LING_B200_ERR_ARG;
+  }
+  return LING_B200_OK;
+}
+
+static int read_err(ling_b200_ctx* c) {
+  LB_CUDA(cudaMemcpyAsync(c->err_host, c->sb.err, sizeof(int), cudaMemcpyDeviceToHost, c->stream));
+  LB_TRY(finish(c));
+  if (*c->err_host != 0) {
+    set_error("device error word = " + std::to_string(*c->err_host) +
+              " (1-4: a GEMM wait ran out; 5: unmapped page; 6: bad tree; 7: token out of range)");
+    LB_CUDA(cudaMemsetAsync(c->sb.err, 0, sizeof(int), c->stream));
+    return LING_B200_ERR_DEVICE_FLAG;
+  }
+  return LING_B200_OK;
+}
+
+int ling_b200_kv_write(ling_b200_ctx* c, int slot, int al, int from, int n, const float* k, const float* v) {
+  LB_TRY(check_ctx(c));
+  LB_TRY(check_positions(c, slot, al, from, n));
+  const ModelDims& d = c->d;
+  const size_t per = size_t(d.Hkv) * d.D;
+  const int band = int(std::max<size_t>(1, c->upload_floats / (2 * per)));
+  for (int i = 0; i < n; i += band) {
+    const int nb = std::min(band, n - i);
+    float* dk = c->upload;
+    float* dv = c->upload + size_t(nb) * per;
+    LB_CUDA(cudaMemcpyAsync(dk, k + size_t(i) * per, size_t(nb) * per * 4, cudaMemcpyHostToDevice, c->stream));
+    LB_CUDA(cudaMemcpyAsync(dv, v + size_t(i) * per, size_t(nb) * per * 4, cudaMemcpyHostToDevice, c->stream));
+    LB_TRY(kv_write_launch(dk, dv, 0, 0, 0, d, al, slot, from + i, nb, c->kv, c->sb.err, c->stream));
+    LB_TRY(finish(c));
+  }
+  return read_err(c);
+}
+
+int ling_b200_synth_kv(ling_b200_ctx* c, int slot, int n, uint64_t seed) {
+  LB_TRY(check_ctx(c));
+  const ModelDims& d = c->d;
+  if (d.n_attn == 0) return LING_B200_OK;
+  LB_TRY(check_positions(c, slot, 0, 0, n));
+  for (int al = 0; al < d.n_attn; ++al) {
+    const uint64_t base = kStreamKv + (uint64_t(slot) * d.n_attn + al) * 2;
+    LB_TRY(kv_write_launch(nullptr, nullptr, stream_key(seed, base), stream_key(seed, base + 1), 1, d, al, slot, 0, n, c->kv,
+                           c->sb.err, c->stream));
+  }
+  return read_err(c);
+}
+
+int ling_b200_kv_read(ling_b200_ctx* c, int slot, int al, int from, int n, float* k, float* v, uint8_t* kcodes, float* kscales,
+                      uint8_t* vcodes, float* vscales) {
+  LB_TRY(check_ctx(c));
+  LB_TRY(check_positions(c, slot, al, from, n));
+  LB_TRY(finish(c));
+  const ModelDims& d = c->d;
+  std::vector<int> table(d.max_pages);
+  LB_CUDA(cudaMemcpy(table.data(), c->kv.tables + size_t(slot) * d.max_pages, table.size() * 4, cudaMemcpyDeviceToHost));
+  std::vector<uint8_t> codes(d.D);
+  for (int i = 0; i < n; ++i)
+    for (int hh = 0; hh < d.Hkv; ++hh)
+      for (int kvi = 0; kvi < 2; ++kvi) {
+        const int pos = from + i;
+        const size_t at = kv_slot_index(d, al, kvi, hh, table[pos / d.page_tokens], pos % d.page_tokens);
+        float sc;
+        LB_CUDA(cudaMemcpy(codes.data(), c->kv.codes + at * d.D, d.D, cudaMemcpyDeviceToHost));
+        LB_CUDA(cudaMemcpy(&sc, c->kv.scales + at, 4, cudaMemcpyDeviceToHost));
+        const size_t o = size_t(i) * d.Hkv + hh;
+        float* f = kvi ? v : k;
+        uint8_t* cc = kvi ? vcodes : kcodes;
+        float* ss = kvi ? vscales : kscales;
+        if (ss) ss[o] = sc;
+        for (int dd = 0; dd < d.D; ++dd) {
+          if (cc) cc[o * d.D + dd] = codes[dd];
+          if (f) {
+            const int code = codes[dd], e = (code >> 3) & 15, mm = code & 7;
+            float val = e == 0 ? std::ldexp(float(mm), -9) : std::ldexp(1.f + mm / 8.f, e - 7);
+            if (e == 15 && mm == 7) val = NAN;
+            f[o * d.D + dd] = (code & 0x80 ? -val : val) * sc;
+          }
+        }
+      }
+  return LING_B200_OK;
+}
+
+int ling_b200_state_write(ling_b200_ctx* c, int slot, int gl, const float* state, const float* conv) {
+  LB_TRY(check_ctx(c));
+  if (slot < 0 || slot >= c->opt.sessions || gl < 0 || gl >= c->d.n_gdn) {
+    set_error("state: slot or layer out of range");
+    return LING_B200_ERR_ARG;
+  }
+  const size_t at = size_t(slot) * c->d.n_gdn + gl;
+  if (state) LB_CUDA(cudaMemcpyAsync(c->gdn_state + at * c->state_layer, state, c->state_layer * 4, cudaMemcpyHostToDevice, c->stream));
+  if (conv) LB_CUDA(cudaMemcpyAsync(c->conv_state + at * c->conv_layer, conv, c->conv_layer * 4, cudaMemcpyHostToDevice, c->stream));
+  return finish(c);
+}
+int ling_b200_state_read(ling_b200_ctx* c, int slot, int gl, float* state, float* conv) {
+  LB_TRY(check_ctx(c));
+  if (slot < 0 || slot >= c->opt.sessions || gl < 0 || gl >= c->d.n_gdn) {
+    set_error("state: slot or layer out of range");
+    return LING_B200_ERR_ARG;
+  }
+  const size_t at = size_t(slot) * c->d.n_gdn + gl;
+  if (state) LB_CUDA(cudaMemcpyAsync(state, c->gdn_state + at * c->state_layer, c->state_layer * 4, cudaMemcpyDeviceToHost, c->stream));
+  if (conv) LB_CUDA(cudaMemcpyAsync(conv, c->conv_state + at * c->conv_layer, c->conv_layer * 4, cudaMemcpyDeviceToHost, c->stream));
+  return finish(c);
+}
+int ling_b200_synth_state(ling_b200_ctx* c, int slot, uint64_t seed) {
+  LB_TRY(check_ctx(c));
+  if (slot < 0 || slot >= c->opt.sessions) {
+    set_error("state: slot out of range");
+    return LING_B200_ERR_ARG;
+  }
+  for (int gl = 0; gl < c->d.n_gdn; ++gl) {
+    const size_t at = size_t(slot) * c->d.n_gdn + gl;
+    LB_TRY(fill_f32_launch(stream_key(seed, kStreamState + uint64_t(slot) * c->d.n_gdn + gl), 0.1f,
+                           c->gdn_state + at * c->state_layer, c->state_layer, c->stream));
+    LB_TRY(fill_f32_launch(stream_key(seed, kStreamConv + uint64_t(slot) * c->d.n_gdn + gl), 1.f,
+                           c->conv_state + at * c->conv_layer, c->conv_layer, c->stream));
+  }
+  return finish(c);
+}
+// Engine::state_hash (src/core/engine.cpp:954-971): FNV-1a, byte by byte, each DeltaNet layer's state then its window.
+int ling_b200_state_hash(ling_b200_ctx* c, int slot, uint64_t* hash) {
+  LB_TRY(check_ctx(c));
+  if (slot < 0 || slot >= c->opt.sessions || !hash) {
+    set_error("state_hash: bad argument");
+    return LING_B200_ERR_ARG;
+  }
+  LB_TRY(finish(c));
+  uint64_t hh = 1469598103934665603ull;
+  std::vector<float> buf(std::max(c->state_layer, c->conv_layer));
+  for (int gl = 0; gl < c->d.n_gdn; ++gl) {
+    const size_t at = size_t(slot) * c->d.n_gdn + gl;
+    for (int part = 0; part < 2; ++part) {
+      const size_t n = part ? c->conv_layer : c->state_layer;
+      LB_CUDA(cudaMemcpy(buf.data(), part ? c->conv_state + at * c->conv_layer : c->gdn_state + at * c->state_layer, n * 4,
+                         cudaMemcpyDeviceToHost));
+      const unsigned char* b = reinterpret_cast<const unsigned char*>(buf.data());
+      for (size_t i = 0; i < n * 4; ++i) hh = (hh ^ b[i]) * 1099511628211ull;
+    }
+  }
+  *hash = hh;
+  return LING_B200_OK;
+}
+
+// ------------------------------------------------------------------------------------------------ the step
+int ling_b200_step_stage(ling_b200_ctx* c, const ling_b200_seq_step* seqs, int n_seqs, int flags) {
+  LB_TRY(check_ctx(c));
+  const ModelDims& d = c->d;
+  if (!seqs || n_seqs < 1 || n_seqs > d.max_seqs) {
+    set_error("step: sequence count out of range");
+    return LING_B200_ERR_ARG;
+  }
+  if ((flags & (LING_B200_STEP_KEEP_LOGITS | LING_B200_STEP_KEEP_TAPS)) && c->opt.debug_rows <= 0) {
+    set_error("step: logits/taps need options.debug_rows > 0");
+    return LING_B200_ERR_ARG;
+  }
+  int rows = 0;
+  for (int s = 0; s < n_seqs; ++s) {
+    const ling_b200_seq_step& q = seqs[s];
+    if (q.slot < 0 || q.slot >= c->opt.sessions || q.n_rows < 1 || q.n_rows > kTreeRows || q.pos < 0 || !q.tokens || !q.parent ||
+        q.chain < 0 || q.pos + q.n_rows > d.max_pages * d.page_tokens) {
+      set_error("step: bad sequence entry");
+      return LING_B200_ERR_ARG;
+    }
+    for (int t = 0; t < s; ++t)
+      if (seqs[t].slot == q.slot) {
+        set_error("step: a session twice");  // speculate_batch's rule (src/core/speculate.cpp:1107-1108)
+        return LING_B200_ERR_ARG;
+      }
+    rows += q.n_rows;
+  }
+  if (rows > c->opt.max_rows) {
+    set_error("step: more rows than options.max_rows");
+    return LING_B200_ERR_ARG;
+  }
+  if ((flags & (LING_B200_STEP_KEEP_LOGITS | LING_B200_STEP_KEEP_TAPS)) && rows > c->opt.debug_rows) {
+    set_error("step: more rows than options.debug_rows");
+    return LING_B200_ERR_ARG;
+  }
+  uint8_t* hb = c->stage_host;
+  const uint8_t* db = c->stage_dev;
+  auto host_of = [&](const void* dev) { return hb + (reinterpret_cast<const uint8_t*>(dev) - db); };
+  *reinterpret_cast<int*>(host_of(c->sb.n_seqs)) = n_seqs;
+  SeqDev* hs = reinterpret_cast<SeqDev*>(host_of(c->sb.seqs));
+  int* hp = reinterpret_cast<int*>(host_of(c->sb.in_parent));
+  int* ht = reinterpret_cast<int*>(host_of(c->sb.in_token));
+  int* hf = reinterpret_cast<int*>(host_of(c->sb.in_force));
+  for (int s = 0; s < n_seqs; ++s) {
+    const ling_b200_seq_step& q = seqs[s];
+    hs[s] = SeqDev{q.slot, q.pos, q.rope_delta, q.n_rows, q.chain, q.force_argmax ? 1 : 0};
+    for (int r = 0; r < kTreeRows; ++r) {
+      hp[s * kTreeRows + r] = r < q.n_rows ? (r == 0 ? -1 : q.parent[r]) : 0;
+      ht[s * kTreeRows + r] = r < q.n_rows ? q.tokens[r] : 0;
+      hf[s * kTreeRows + r] = (r < q.n_rows && q.force_argmax) ? q.force_argmax[r] : 0;
+    }
+  }
+  c->staged_seqs = n_seqs, c->staged_rows = rows, c->staged_flags = flags;
+  LB_CUDA(cudaMemcpyAsync(c->stage_dev, c->stage_host, c->stage_bytes, cudaMemcpyHostToDevice, c->stream));
+  return LING_B200_OK;
+}
+
+int ling_b200_step_launch(ling_b200_ctx* c) {
+  LB_TRY(check_ctx(c));
+  if (c->staged_seqs < 1) {
+    set_error("step: nothing staged");
+    return LING_B200_ERR_ARG;
+  }
+  const int rows = row_class(c->staged_rows), flags = c->staged_flags;
+  c->last_rows = c->staged_rows, c->last_seqs = c->staged_seqs, c->last_flags = flags;
+  if (!c->opt.use_graph) return enqueue_step(c, rows, flags);
+  const auto key = std::make_pair(rows, flags);
+  auto it = c->graphs.find(key);
+  if (it == c->graphs.end()) {
+    cudaGraph_t graph = nullptr;
+    LB_CUDA(cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
+    const int rc = enqueue_step(c, rows, flags);
+    const cudaError_t e = cudaStreamEndCapture(c->stream, &graph);
+    if (rc != LING_B200_OK) {
+      if (graph) cudaGraphDestroy(graph);
+      return rc;
+    }
+    LB_CUDA(e);
+    cudaGraphExec_t exec = nullptr;
+    const cudaError_t ie = cudaGraphInstantiate(&exec, graph, 0);
+    cudaGraphDestroy(graph);
+    LB_CUDA(ie);
+    it = c->graphs.emplace(key, exec).first;
+  }
+  LB_CUDA(cudaGraphLaunch(it->second, c->stream));
+  return LING_B200_OK;
+}
+
+int ling_b200_step_fetch(ling_b200_ctx* c, ling_b200_seq_result* results) {
+  LB_TRY(check_ctx(c));
+  if (c->last_seqs < 1) {
+    set_error("step: nothing launched");
+    return LING_B200_ERR_ARG;
+  }
+  LB_CUDA(cudaMemcpyAsync(c->results_host, c->sb.results, size_t(c->last_seqs) * sizeof(ling_b200_seq_result),
+                          cudaMemcpyDeviceToHost, c->stream));
+  LB_TRY(read_err(c));
+  if (results) std::memcpy(results, c->results_host, size_t(c->last_seqs) * sizeof(ling_b200_seq_result));
+  return LING_B200_OK;
+}
+
+int ling_b200_verify_step(ling_b200_ctx* c, const ling_b200_seq_step* seqs, int n_seqs, int flags, ling_b200_seq_result* results) {
+  LB_TRY(ling_b200_step_stage(c, seqs, n_seqs, flags));
+  LB_TRY(ling_b200_step_launch(c));
+  return ling_b200_step_fetch(c, results);
+}
+
+int ling_b200_step_launch_count(ling_b200_ctx* c) { return c ? c->launches_per_step : 0; }
+
+int ling_b200_profile_step(ling_b200_ctx* c, float ms[8], int* launches) {
+  LB_TRY(check_ctx(c));
+  if (c->staged_seqs < 1) {
+    set_error("profile: nothing staged");
+    return LING_B200_ERR_ARG;
+  }
+  LB_TRY(finish(c));
+  c->profiling = true;
+  c->prof.clear();
+  const int rc = enqueue_step(c, row_class(c->staged_rows), c->staged_flags & ~LING_B200_STEP_COMMIT);
+  c->profiling = false;
+  const int fin = finish(c);
+  for (int i = 0; i < 8; ++i) ms[i] = 0.f;
+  for (auto& p : c->prof) {
+    float t = 0.f;
+    if (rc == LING_B200_OK && fin == LING_B200_OK) cudaEventElapsedTime(&t, p.second.first, p.second.second);
+    ms[p.first] += t;
+    cudaEventDestroy(p.second.first), cudaEventDestroy(p.second.second);
+  }
+  if (launches) *launches = c->launches_per_step;
+  c->prof.clear();
+  return rc != LING_B200_OK ? rc : fin;
+}
+
+int ling_b200_timer_begin(ling_b200_ctx* c) {
+  LB_TRY(check_ctx(c));
+  LB_CUDA(cudaEventRecord(c->ev0, c->stream));
+  return LING_B200_OK;
+}
+int ling_b200_timer_end(ling_b200_ctx* c, float* ms) {
+  LB_TRY(check_ctx(c));
+  LB_CUDA(cudaEventRecord(c->ev1, c->stream));
+  LB_CUDA(cudaEventSynchronize(c->ev1));
+  LB_CUDA(cudaEventElapsedTime(ms, c->ev0, c->ev1));
+  return LING_B200_OK;
+}
+int ling_b200_flush_l2(ling_b200_ctx* c) {
+  LB_TRY(check_ctx(c));
+  return flush_launch(c->flush, c->flush_floats, c->stream);
+}
+int ling_b200_sync(ling_b200_ctx* c) {
+  LB_TRY(check_ctx(c));
+  return finish(c);
+}
+
+// ------------------------------------------------------------------------------------------------ read-backs
+int ling_b200_read_tree_desc(ling_b200_ctx* c, int seq, ling_b200_tree_desc* out) {
+  LB_TRY(check_ctx(c));
+  if (seq < 0 || seq >= c->last_seqs || !out) {
+    set_error("read_tree_desc: bad sequence index");
+    return LING_B200_ERR_ARG;
+  }
+  LB_TRY(finish(c));
+  LB_CUDA(cudaMemcpy(out, c->sb.trees + seq, sizeof(ling_b200_tree_desc), cudaMemcpyDeviceToHost));
+  return LING_B200_OK;
+}
+int ling_b200_read_packing(ling_b200_ctx* c, int* row0, int* token, int* seq_of, int* depth, int* rope_pos, int* cache_slot,
+                           uint32_t* anc_mask) {
+  LB_TRY(check_ctx(c));
+  LB_TRY(finish(c));
+  const size_t n = size_t(c->last_rows);
+  if (row0) LB_CUDA(cudaMemcpy(row0, c->sb.row0, size_t(c->last_seqs + 1) * 4, cudaMemcpyDeviceToHost));
+  if (token) LB_CUDA(cudaMemcpy(token, c->sb.token, n * 4, cudaMemcpyDeviceToHost));
+  if (seq_of) LB_CUDA(cudaMemcpy(seq_of, c->sb.seq_of, n * 4, cudaMemcpyDeviceToHost));
+  if (depth) LB_CUDA(cudaMemcpy(depth, c->sb.depth, n * 4, cudaMemcpyDeviceToHost));
+  if (rope_pos) LB_CUDA(cudaMemcpy(rope_pos, c->sb.rope_pos, n * 4, cudaMemcpyDeviceToHost));
+  if (cache_slot) LB_CUDA(cudaMemcpy(cache_slot, c->sb.cache_slot, n * 4, cudaMemcpyDeviceToHost));
+  if (anc_mask) LB_CUDA(cudaMemcpy(anc_mask, c->sb.anc, n * 4, cudaMemcpyDeviceToHost));
+  return LING_B200_OK;
+}
+int ling_b200_read_argmax(ling_b200_ctx* c, int* ids, float* vals) {
+  LB_TRY(check_ctx(c));
+  LB_TRY(finish(c));
+  if (ids) LB_CUDA(cudaMemcpy(ids, c->sb.argmax_id, size_t(c->last_rows) * 4, cudaMemcpyDeviceToHost));
+  if (vals) LB_CUDA(cudaMemcpy(vals, c->sb.argmax_val, size_t(c->last_rows) * 4, cudaMemcpyDeviceToHost));
+  return LING_B200_OK;
+}
+int ling_b200_read_logits(ling_b200_ctx* c, float* out) {
+  LB_TRY(check_ctx(c));
+  if (!(c->last_flags & LING_B200_STEP_KEEP_LOGITS) || !c->logits) {
+    set_error("read_logits: the last step did not keep logits");
+    return LING_B200_ERR_ARG;
+  }
+  LB_TRY(finish(c));
+  LB_CUDA(cudaMemcpy(out, c->logits, size_t(c->last_rows) * c->d.V * 4, cudaMemcpyDeviceToHost));
+  return LING_B200_OK;
+}
+int ling_b200_read_tap(ling_b200_ctx* c, int layer, float* out) {
+  LB_TRY(check_ctx(c));
+  if (!(c->last_flags & LING_B200_STEP_KEEP_TAPS) || !c->taps || layer < 0 || layer > c->cfg.layers) {
+    set_error("read_tap: the last step did not keep taps, or bad layer");
+    return LING_B200_ERR_ARG;
+  }
+  LB_TRY(finish(c));
+  LB_CUDA(cudaMemcpy(out, c->taps + size_t(layer) * c->opt.debug_rows * c->d.H, size_t(c->last_rows) * c->d.H * 4,
+                     cudaMemcpyDeviceToHost));
+  return LING_B200_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,537 @@
+// gemm.cu -- the block-scaled FP8 weight GEMM (see gemm.h) for sm_100a.
+//
+// Kernel shape (one CTA = one 128-row weight tile x one K split x one token tile):
+//   warp 0   TMA producer: per 128-wide K block, one 128x128B weight tile and one NTx128B activation tile into a
+//            128B-swizzled stage, completion counted on the stage's mbarrier (no multicast, no cluster).
+//   warp 1   MMA issuer (one elected lane): four tcgen05.mma kind::f8f6f4 (K = 32 each) per stage into one of two TMEM
+//            accumulator buffers, then tcgen05.commit to the stage's "empty" barrier and the buffer's "full" barrier.
+//            Also owns the TMEM allocation.
+//   warps 2-5 epilogue: tcgen05.ld of the finished buffer, acc += partial * (weight scale * activation scale) in
+//            registers (the 1x128 fp32 block scales are not a native tcgen05 scale format, so each K block is
+//            promoted in fp32), release of the buffer; at the end the store (and, for the LM head, the per-tile argmax).
+// Every wait is bounded by a wall-clock limit; a wait that runs out records a code in the device error word, the
+// CTA drains its outstanding copies, frees its TMEM and returns.
+#include "gemm.h"
+
+#include <cfloat>
+#include <mutex>
+
+#include "../../include/ling_b200.h"
+
+namespace lb {
+
+// ---------------------------------------------------------------------------------------------- PTX wrappers
+namespace {
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ uint64_t global_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s: far beyond any healthy step
+
+// Bounded wait.  Returns false when the limit ran out or (with `abort`) another role already gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = global_ns();
+  for (uint32_t spin = 1;; ++spin) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((spin & 255u) == 0) {
+      if (abort && *abort) return false;
+      if (global_ns() - t0 > kWaitLimitNs) return false;
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y), "l"(policy)
+      : "memory");
+}
+__device__ __forceinline__ uint64_t policy_evict_first() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ uint64_t policy_evict_last() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+
+// Shared-memory matrix descriptor of a K-major tile of 128-byte rows under the 128B swizzle: 8-row groups are
+// 1024 bytes apart (stride byte offset), the leading byte offset is unused for swizzled K-major operands.
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= uint64_t((smem_addr & 0x3FFFFu) >> 4);  // start address, 16-byte units
+  d |= uint64_t(1024 >> 4) << 32;              // stride byte offset
+  d |= uint64_t(1) << 46;                      // descriptor version (sm_100)
+  d |= uint64_t(2) << 61;                      // layout: SWIZZLE_128B
+  return d;
+}
+// Instruction descriptor, kind::f8f6f4: D = fp32, A = B = E4M3, both K-major, M = 128, N = nt.
+__host__ __device__ constexpr uint32_t umma_idesc_e4m3(int nt) {
+  return (1u << 4) | (0u << 7) | (0u << 10) | (uint32_t(nt >> 3) << 17) | (uint32_t(128 >> 4) << 24);
+}
+__device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+constexpr int kABytes = kTileN * kBlockK;  // 16 KiB
+__host__ __device__ constexpr int tmem_cols(int nt) { return 2 * nt <= 32 ? 32 : 2 * nt <= 64 ? 64 : 2 * nt <= 128 ? 128 : 256; }
+__host__ __device__ constexpr int stages_for(int nt) { return nt == 32 ? 5 : nt == 64 ? 4 : nt == 96 ? 3 : 6; }
+__host__ __device__ constexpr int ctas_per_sm(int nt) { return nt == 128 ? 1 : 2; }
+constexpr int kGemmThreads = 192;
+
+struct HeadArgs {
+  float* tile_val;
+  int* tile_idx;
+  int rows_alloc;
+  int store_logits;
+};
+
+constexpr size_t gemm_smem_bytes(int nt) {
+  return size_t(stages_for(nt)) * (kABytes + nt * kBlockK) + 1024 /* alignment slack */ + 512 /* barriers */ +
+         size_t(4) * nt * 8 /* head argmax scratch */;
+}
+
+template <int NT>
+__global__ void __launch_bounds__(kGemmThreads, ctas_per_sm(NT))
+    gemm_fp8_tcgen05_kernel(const __grid_constant__ CUtensorMap mapW, const __grid_constant__ CUtensorMap mapX,
+                            const float* __restrict__ ws, const float* __restrict__ xs, float* __restrict__ out, int ld,
+                            size_t split_stride, int M, int N, int N_pad, int KB, int splits, int xrows, HeadArgs head,
+                            int* err_flag, int pdl) {
+  constexpr int STAGES = stages_for(NT);
+  constexpr int kBBytes = NT * kBlockK;
+  constexpr int kStageBytes = kABytes + kBBytes;
+  constexpr int kTmemCols = tmem_cols(NT);
+
+  extern __shared__ uint8_t smem_raw[];
+  // 128B-swizzled tiles need 1024-byte alignment; the dynamic segment's base is not guaranteed to have it.
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint8_t* tiles = smem;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * kStageBytes);
+  uint64_t* empty = full + STAGES;
+  uint64_t* tmem_full = empty + STAGES;
+  uint64_t* tmem_empty = tmem_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* red_val = reinterpret_cast<float*>(tmem_slot + 4);  // [4][NT]
+  int* red_idx = reinterpret_cast<int*>(red_val + 4 * NT);   // [4][NT]
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile_n = blockIdx.x, split = blockIdx.y, tile_m = blockIdx.z;
+  const int kb0 = int(int64_t(KB) * split / splits), kb1 = int(int64_t(KB) * (split + 1) / splits);
+  const int nslab = kb1 - kb0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tmem_full[b], 1);
+      mbar_init(&tmem_empty[b], 4);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {  // TMEM allocation: one warp, the whole warp executes it
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    tc_fence_before();
+  }
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      const uint64_t pol_w = policy_evict_first();  // weights are read once per step
+      const uint64_t pol_x = policy_evict_last();   // the activation tile is re-read by every CTA
+      const int wy = tile_n * kTileN, xy = tile_m * NT;
+      int i = 0;
+      bool ok = true;
+      if (pdl) {
+        // Weights do not depend on the previous kernel: fill the pipeline with weight tiles first, wait for the
+        // previous kernel, then fetch the activation tiles of those stages.
+        const int pre = nslab < STAGES ? nslab : STAGES;
+        for (int s = 0; s < pre; ++s) {
+          mbar_expect_tx(&full[s], kStageBytes);
+          tma_load_2d(tiles + s * kStageBytes, &mapW, &full[s], (kb0 + s) * kBlockK, wy, pol_w);
+        }
+        grid_dep_wait();
+        for (int s = 0; s < pre; ++s)
+          tma_load_2d(tiles + s * kStageBytes + kABytes, &mapX, &full[s], (kb0 + s) * kBlockK, xy, pol_x);
+        i = pre;
+      }
+      for (; i < nslab && ok; ++i) {
+        const int s = i % STAGES;
+        const uint32_t ph = (i / STAGES) & 1;
+        ok = mbar_wait(&empty[s], ph ^ 1, abort_flag);
+        if (!ok) {
+          dev_fail(err_flag, kDevWaitEmpty);
+          *abort_flag = 1;
+          break;
+        }
+        mbar_expect_tx(&full[s], kStageBytes);
+        tma_load_2d(tiles + s * kStageBytes, &mapW, &full[s], (kb0 + i) * kBlockK, wy, pol_w);
+        tma_load_2d(tiles + s * kStageBytes + kABytes, &mapX, &full[s], (kb0 + i) * kBlockK, xy, pol_x);
+      }
+      // Every copy this lane issued has landed before it leaves (also when a role gave up): the last STAGES
+      // stages' barriers complete exactly once more and are never re-armed.  Bounded like every other wait.
+      for (int j = (i > STAGES ? i - STAGES : 0); j < i; ++j) mbar_wait(&full[j % STAGES], (j / STAGES) & 1, nullptr);
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (pdl) grid_dep_wait();
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_e4m3(NT);
+      for (int i = 0; i < nslab; ++i) {
+        const int s = i % STAGES, buf = i & 1;
+        const uint32_t ph = (i / STAGES) & 1, bph = (i >> 1) & 1;
+        if (!mbar_wait(&tmem_empty[buf], bph ^ 1, abort_flag)) {
+          dev_fail(err_flag, kDevWaitTmemEmpty);
+          *abort_flag = 1;
+          break;
+        }
+        if (!mbar_wait(&full[s], ph, abort_flag)) {
+          dev_fail(err_flag, kDevWaitFull);
+          *abort_flag = 1;
+          break;
+        }
+        tc_fence_after();
+        const uint64_t adesc = umma_desc_sw128(smem_u32(tiles + s * kStageBytes));
+        const uint64_t bdesc = umma_desc_sw128(smem_u32(tiles + s * kStageBytes + kABytes));
+        const uint32_t d = tmem_base + uint32_t(buf * NT);
+#pragma unroll
+        for (int k = 0; k < kBlockK / 32; ++k)  // K = 32 bytes per instruction: advance the start address by 32 B
+          umma_f8(d, adesc + uint64_t(k * 2), bdesc + uint64_t(k * 2), idesc, k > 0 ? 1u : 0u);
+        umma_commit(&empty[s]);         // the stage may be refilled once these MMAs have read it
+        umma_commit(&tmem_full[buf]);   // the accumulator is complete
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue warps (TMEM lane quarter = warp % 4)
+    if (pdl) grid_dep_wait();
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const int n = tile_n * kTileN + row;
+    const int m0 = tile_m * NT;
+    float acc[NT];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) acc[j] = 0.f;
+    bool ok = true;
+    for (int i = 0; i < nslab && ok; ++i) {
+      const int buf = i & 1, kb = kb0 + i;
+      const uint32_t bph = (i >> 1) & 1;
+      const float wsc = __ldg(ws + size_t(kb) * N_pad + n);
+      const float4* xs4 = reinterpret_cast<const float4*>(xs + size_t(kb) * xrows + m0);
+      ok = mbar_wait(&tmem_full[buf], bph, abort_flag);
+      if (!ok) {
+        dev_fail(err_flag, kDevWaitTmemFull);
+        *abort_flag = 1;
+        break;
+      }
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(buf * NT);
+#pragma unroll
+      for (int c = 0; c < NT / 16; ++c) {
+        uint32_t v[16];
+        tmem_ld16(taddr + c * 16, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float4 s4 = __ldg(xs4 + c * 4 + q);
+          acc[c * 16 + q * 4 + 0] = fmaf(__uint_as_float(v[q * 4 + 0]), wsc * s4.x, acc[c * 16 + q * 4 + 0]);
+          acc[c * 16 + q * 4 + 1] = fmaf(__uint_as_float(v[q * 4 + 1]), wsc * s4.y, acc[c * 16 + q * 4 + 1]);
+          acc[c * 16 + q * 4 + 2] = fmaf(__uint_as_float(v[q * 4 + 2]), wsc * s4.z, acc[c * 16 + q * 4 + 2]);
+          acc[c * 16 + q * 4 + 3] = fmaf(__uint_as_float(v[q * 4 + 3]), wsc * s4.w, acc[c * 16 + q * 4 + 3]);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+    }
+    if (ok) {
+      const bool store = head.tile_val == nullptr || head.store_logits;
+      if (store && n < N) {
+        float* o = out + size_t(split) * split_stride + n;
+#pragma unroll
+        for (int j = 0; j < NT; ++j)
+          if (m0 + j < M) o[size_t(m0 + j) * ld] = acc[j];
+      }
+      if (head.tile_val != nullptr) {
+        // Per token row: the best (value, id) among this tile's 128 vocabulary rows; larger value first, equal
+        // values to the lower id, NaN skipped.
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+          float v = acc[j];
+          int id = n;
+          if (!(n < N) || v != v) {
+            v = -FLT_MAX;
+            id = 0x7fffffff;
+          }
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) {
+            const float v2 = __shfl_xor_sync(0xffffffffu, v, o);
+            const int i2 = __shfl_xor_sync(0xffffffffu, id, o);
+            if (v2 > v || (v2 == v && i2 < id)) v = v2, id = i2;
+          }
+          if (lane == 0) red_val[quarter * NT + j] = v, red_idx[quarter * NT + j] = id;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (warp == 2) {
+          for (int j = lane; j < NT; j += 32) {
+            float v = red_val[j];
+            int id = red_idx[j];
+#pragma unroll
+            for (int q = 1; q < 4; ++q) {
+              const float v2 = red_val[q * NT + j];
+              const int i2 = red_idx[q * NT + j];
+              if (v2 > v || (v2 == v && i2 < id)) v = v2, id = i2;
+            }
+            if (m0 + j < M) {
+              head.tile_val[size_t(tile_n) * head.rows_alloc + m0 + j] = v;
+              head.tile_idx[size_t(tile_n) * head.rows_alloc + m0 + j] = id;
+            }
+          }
+        }
+      }
+    }
+  }
+  if (pdl) grid_dep_launch();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------------------------- CUDA-core GEMM
+// The same arithmetic on CUDA cores: one block = one 128-row weight tile x 8 token rows, a warp per weight row,
+// lanes split the 128-wide block four codes each.  Exists to cross-check the tensor-core kernel, not to be fast.
+__global__ void __launch_bounds__(256)
+    gemm_fp8_simt_kernel(const uint8_t* __restrict__ w, const float* __restrict__ ws, const uint8_t* __restrict__ x,
+                         const float* __restrict__ xs, float* __restrict__ out, int ld, int M, int N, int N_pad,
+                         int K_pad, int KB, int xrows, HeadArgs head) {
+  __shared__ float red_val[8][8];
+  __shared__ int red_idx[8][8];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.y * 8;
+  float bestv[8];
+  int besti[8];
+#pragma unroll
+  for (int r = 0; r < 8; ++r) bestv[r] = -FLT_MAX, besti[r] = 0x7fffffff;
+  for (int rr = 0; rr < 16; ++rr) {
+    const int n = blockIdx.x * kTileN + warp * 16 + rr;
+    float acc[8];
+#pragma unroll
+    for (int r = 0; r < 8; ++r) acc[r] = 0.f;
+    for (int kb = 0; kb < KB; ++kb) {
+      const uint32_t wc = *reinterpret_cast<const uint32_t*>(w + size_t(n) * K_pad + kb * kBlockK + lane * 4);
+      float wf[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) wf[i] = from_e4m3(uint8_t(wc >> (8 * i)));
+      const float wsc = ws[size_t(kb) * N_pad + n];
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        const int m = m0 + r;
+        if (m >= M) continue;  // uniform across the warp
+        const uint32_t xc = *reinterpret_cast<const uint32_t*>(x + size_t(m) * K_pad + kb * kBlockK + lane * 4);
+        float p = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) p = fmaf(wf[i], from_e4m3(uint8_t(xc >> (8 * i))), p);
+        p = warp_sum(p);
+        acc[r] = fmaf(p, wsc * xs[size_t(kb) * xrows + m], acc[r]);
+      }
+    }
+    const bool store = head.tile_val == nullptr || head.store_logits;
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+      const int m = m0 + r;
+      if (m >= M || n >= N) continue;
+      if (store && lane == 0) out[size_t(m) * ld + n] = acc[r];
+      const float v = acc[r];
+      if (v == v && (v > bestv[r] || (v == bestv[r] && n < besti[r]))) bestv[r] = v, besti[r] = n;
+    }
+  }
+  if (head.tile_val == nullptr) return;
+  if (lane == 0)
+    for (int r = 0; r < 8; ++r) red_val[warp][r] = bestv[r], red_idx[warp][r] = besti[r];
+  __syncthreads();
+  if (threadIdx.x < 8 && m0 + threadIdx.x < M) {
+    const int r = threadIdx.x;
+    float v = red_val[0][r];
+    int id = red_idx[0][r];
+    for (int q = 1; q < 8; ++q)
+      if (red_val[q][r] > v || (red_val[q][r] == v && red_idx[q][r] < id)) v = red_val[q][r], id = red_idx[q][r];
+    head.tile_val[size_t(blockIdx.x) * head.rows_alloc + m0 + r] = v;
+    head.tile_idx[size_t(blockIdx.x) * head.rows_alloc + m0 + r] = id;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+int encode_2d(CUtensorMap* map, void* base, uint64_t inner, uint64_t rows, uint32_t box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) {
+    set_error("cuTensorMapEncodeTiled is not available from the driver");
+    return LING_B200_ERR_CUDA;
+  }
+  const cuuint64_t dims[2] = {inner, rows};
+  const cuuint64_t strides[1] = {inner};  // bytes between rows
+  const cuuint32_t box[2] = {kBlockK, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled failed with code " + std::to_string(int(r)));
+    return LING_B200_ERR_CUDA;
+  }
+  return LING_B200_OK;
+}
+
+template <int NT>
+int launch_tc(const GemmCall& c, cudaStream_t stream) {
+  static bool attr_set = false;  // per process; the attribute is per function
+  const size_t smem = gemm_smem_bytes(NT);
+  if (!attr_set) {
+    LB_CUDA(cudaFuncSetAttribute(gemm_fp8_tcgen05_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+    attr_set = true;
+  }
+  const Fp8Matrix& W = *c.W;
+  const Fp8Acts& X = *c.X;
+  HeadArgs h{nullptr, nullptr, 0, 0};
+  if (c.head) h = HeadArgs{c.head->tile_val, c.head->tile_idx, c.head->rows_alloc, c.head->store_logits ? 1 : 0};
+  const int splits = c.head ? 1 : W.splits;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(W.N_pad / kTileN, splits, ceil_div(c.M, NT));
+  cfg.blockDim = dim3(kGemmThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = c.pdl ? 1 : 0;
+  LB_CUDA(cudaLaunchKernelEx(&cfg, gemm_fp8_tcgen05_kernel<NT>, W.map, X.map[NT / 32 - 1], (const float*)W.scales,
+                             (const float*)X.scales, c.out, c.ld, c.split_stride, c.M, W.N, W.N_pad, W.KB, splits,
+                             X.rows_alloc, h, c.err_flag, c.pdl ? 1 : 0));
+  return LING_B200_OK;
+}
+
+}  // namespace
+
+int make_weight_map(Fp8Matrix& w) { return encode_2d(&w.map, w.codes, uint64_t(w.K_pad), uint64_t(w.N_pad), kTileN); }
+
+int make_acts_maps(Fp8Acts& x) {
+  for (int i = 0; i < 4; ++i) {
+    const int nt = 32 * (i + 1);
+    if (const int r = encode_2d(&x.map[i], x.codes, uint64_t(x.K_pad), uint64_t(x.rows_alloc), uint32_t(nt))) return r;
+  }
+  return LING_B200_OK;
+}
+
+int token_tile(int M) { return M <= 32 ? 32 : M <= 64 ? 64 : M <= 96 ? 96 : 128; }
+
+int choose_splits(int N_pad, int KB, int sm_count) {
+  const int tiles = N_pad / kTileN;
+  // Two resident CTAs per SM for the narrow token tiles: aim at about 2 x SMs work items, keep at least four
+  // K blocks per split so that the prologue and the partial-sum traffic stay small.
+  int s = (2 * sm_count + tiles / 2) / tiles;
+  s = std::min(s, KB / 4);
+  s = std::max(s, 1);
+  return std::min(s, 16);
+}
+
+int gemm_launch(const GemmCall& c, cudaStream_t stream) {
+  const Fp8Matrix& W = *c.W;
+  const Fp8Acts& X = *c.X;
+  if (W.K_pad != X.K_pad || c.M < 1 || c.M > X.rows_alloc) {
+    set_error("gemm: shape mismatch");
+    return LING_B200_ERR_ARG;
+  }
+  if (c.impl == 1) {
+    HeadArgs h{nullptr, nullptr, 0, 0};
+    if (c.head) h = HeadArgs{c.head->tile_val, c.head->tile_idx, c.head->rows_alloc, c.head->store_logits ? 1 : 0};
+    const dim3 grid(W.N_pad / kTileN, ceil_div(c.M, 8));
+    gemm_fp8_simt_kernel<<<grid, 256, 0, stream>>>(W.codes, W.scales, X.codes, X.scales, c.out, c.ld, c.M, W.N, W.N_pad,
+                                                   W.K_pad, W.KB, X.rows_alloc, h);
+    LB_LAUNCH("gemm_fp8_simt_kernel");
+    return LING_B200_OK;
+  }
+  switch (token_tile(c.M)) {
+    case 32: return launch_tc<32>(c, stream);
+    case 64: return launch_tc<64>(c, stream);
+    case 96: return launch_tc<96>(c, stream);
+    default: return launch_tc<128>(c, stream);
+  }
+}
+
+}  // namespace lb

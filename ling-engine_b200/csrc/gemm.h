@@ -1,0 +1,66 @@
+// Block-scaled FP8 weight GEMM of the verify step: y[m][n] = sum over 128-wide K blocks of
+// dot(x8[m][blk], w8[n][blk]) * xs[blk][m] * ws[blk][n].
+//
+// Stands in for the reference's weight-streaming rows GEMM (src/core/stream_gemm.cu:181-349,674-703 in the
+// reference project), rebuilt for sm_100a: weights are the MMA's M dimension (128 rows a tile), the packed token
+// rows its N dimension, operands arrive by TMA into 128B-swizzled shared memory, each 128-wide K block is one
+// tcgen05.mma group into a TMEM accumulator that four epilogue warps drain and promote with the two block scales.
+#pragma once
+
+#include "common.cuh"
+
+namespace lb {
+
+constexpr int kTileN = 128;   // weight rows per tile (the MMA's M)
+constexpr int kBlockK = 128;  // K per block scale and per pipeline stage (bytes: E4M3)
+
+// One FP8 weight matrix on the device, padded to whole tiles (padding rows/columns are zero codes).
+struct Fp8Matrix {
+  uint8_t* codes = nullptr;  // [N_pad][K_pad]
+  float* scales = nullptr;   // [KB][N_pad]   (block-major: one stage reads 128 consecutive floats)
+  int N = 0, K = 0, N_pad = 0, K_pad = 0, KB = 0;
+  int splits = 1;            // fixed K split of this shape (never depends on the row count: row invariance)
+  CUtensorMap map;           // {K_pad, N_pad}, box {128, 128}, 128B swizzle
+  size_t bytes() const { return size_t(N_pad) * K_pad + size_t(KB) * N_pad * 4; }
+};
+
+// Quantized activations: codes [rows_alloc][K_pad], scales [KB][rows_alloc].
+struct Fp8Acts {
+  uint8_t* codes = nullptr;
+  float* scales = nullptr;
+  int rows_alloc = 0, K = 0, K_pad = 0, KB = 0;
+  CUtensorMap map[4];  // box rows 32, 64, 96, 128
+};
+
+// Optional fused epilogue of the LM head: per (tile, row) the best (value, vocabulary id), ties to the lower id,
+// NaN skipped (reference rule: src/core/topk.cu:19,58).
+struct HeadEpilogue {
+  float* tile_val = nullptr;  // [N_pad/128][rows_alloc]
+  int* tile_idx = nullptr;
+  int rows_alloc = 0;
+  bool store_logits = false;
+};
+
+struct GemmCall {
+  const Fp8Matrix* W = nullptr;
+  const Fp8Acts* X = nullptr;
+  int M = 0;                // real rows
+  float* out = nullptr;     // [splits][M][ld]; column n of the matrix lands at out[m * ld + n]
+  int ld = 0;
+  size_t split_stride = 0;  // floats between split planes
+  const HeadEpilogue* head = nullptr;
+  int impl = 0;             // 0 tcgen05, 1 CUDA cores
+  int* err_flag = nullptr;
+  bool pdl = false;         // launched with programmatic stream serialization: weights are prefetched before the wait
+};
+
+// Creates the tensor maps (driver entry point fetched at run time; no link against libcuda).
+int make_weight_map(Fp8Matrix& w);
+int make_acts_maps(Fp8Acts& x);
+// The K split used for a shape: enough tiles x splits to cover the SMs about twice, at least 4 K blocks a split.
+int choose_splits(int N_pad, int KB, int sm_count);
+int gemm_launch(const GemmCall& c, cudaStream_t stream);
+// Token rows per MMA (the N of the instruction) used for M rows: 32, 64, 96 or 128.
+int token_tile(int M);
+
+}  // namespace lb

@@ -1,0 +1,275 @@
+// kernel_abi.cu -- kernel-level entry points of the C ABI: each runs one of the step's kernels on host buffers (copy in,
+// launch, copy out), the way the reference's model-free kernel tests drive its kernel layer on random data
+// (tests/stream_tests.cu, tests/tree_tests.cu in the reference project).  They allocate and free their own scratch.
+#include <vector>
+
+#include "gemm.h"
+#include "kernels.h"
+
+using namespace lb;
+
+namespace {
+
+struct Scratch {  // device allocations freed on scope exit
+  std::vector<void*> p;
+  ~Scratch() {
+    for (void* q : p) cudaFree(q);
+  }
+  template <typename T>
+  T* get(size_t n, bool zero = true) {
+    void* q = nullptr;
+    if (cudaMalloc(&q, std::max<size_t>(n, 1) * sizeof(T)) != cudaSuccess) return nullptr;
+    if (zero) cudaMemset(q, 0, std::max<size_t>(n, 1) * sizeof(T));
+    p.push_back(q);
+    return static_cast<T*>(q);
+  }
+  template <typename T>
+  T* put(const T* host, size_t n) {
+    T* q = get<T>(n, false);
+    if (q && cudaMemcpy(q, host, n * sizeof(T), cudaMemcpyHostToDevice) != cudaSuccess) return nullptr;
+    return q;
+  }
+};
+
+int check_device(int device) {
+  LB_CUDA(cudaSetDevice(device));
+  cudaDeviceProp prop;
+  LB_CUDA(cudaGetDeviceProperties(&prop, device));
+  if (prop.major != 10) {
+    set_error(std::string("this library is built for sm_100a (B200) only; device is ") + prop.name);
+    return LING_B200_ERR_UNSUPPORTED;
+  }
+  return LING_B200_OK;
+}
+#define LB_TRY(call)                      \
+  do {                                    \
+    const int rc__ = (call);              \
+    if (rc__ != LING_B200_OK) return rc__; \
+  } while (0)
+#define LB_PTR(p)                          \
+  do {                                     \
+    if (!(p)) {                            \
+      set_error("device allocation failed"); \
+      return LING_B200_ERR_CUDA;           \
+    }                                      \
+  } while (0)
+
+struct GemmSetup {
+  Fp8Matrix W;
+  Fp8Acts X;
+  float* out = nullptr;
+  int* err = nullptr;
+};
+
+int setup_gemm(Scratch& sc, GemmSetup& g, int M, int N, int K, int splits) {
+  int sms = 148;
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0);
+  Fp8Matrix& W = g.W;
+  W.N = N, W.K = K, W.N_pad = round_up(N, kTileN), W.K_pad = round_up(K, kBlockK), W.KB = W.K_pad / kBlockK;
+  W.splits = splits > 0 ? std::min(splits, W.KB) : choose_splits(W.N_pad, W.KB, sms);
+  W.codes = sc.get<uint8_t>(size_t(W.N_pad) * W.K_pad);
+  W.scales = sc.get<float>(size_t(W.KB) * W.N_pad);
+  Fp8Acts& X = g.X;
+  X.K = K, X.K_pad = W.K_pad, X.KB = W.KB, X.rows_alloc = round_up(M, 128);
+  X.codes = sc.get<uint8_t>(size_t(X.rows_alloc) * X.K_pad);
+  X.scales = sc.get<float>(size_t(X.KB) * X.rows_alloc);
+  g.out = sc.get<float>(size_t(W.splits) * X.rows_alloc * W.N_pad);
+  g.err = sc.get<int>(1);
+  LB_PTR(W.codes && W.scales && X.codes && X.scales && g.out && g.err);
+  LB_TRY(make_weight_map(W));
+  return make_acts_maps(X);
+}
+
+}  // namespace
+
+extern "C" {
+
+int ling_b200_gemm_fp8_host(int device, int impl, int splits, const float* x, const float* w, float* y, int M, int N, int K) {
+  if (!x || !w || !y || M < 1 || N < 1 || K < 1 || M > LING_B200_MAX_ROWS) {
+    set_error("gemm_fp8_host: bad argument");
+    return LING_B200_ERR_ARG;
+  }
+  LB_TRY(check_device(device));
+  Scratch sc;
+  GemmSetup g;
+  LB_TRY(setup_gemm(sc, g, M, N, K, splits));
+  float* dw = sc.put(w, size_t(N) * K);
+  float* dx = sc.put(x, size_t(M) * K);
+  LB_PTR(dw && dx);
+  LB_TRY(quant_weight_launch(dw, 0, 0.f, 0, g.W.codes, g.W.scales, 0, N, K, g.W.N_pad, g.W.K_pad, 0));
+  LB_TRY(quant_acts_launch(dx, M, QuantOut{g.X.codes, g.X.scales, K, g.X.K_pad, g.X.rows_alloc}, 0));
+  GemmCall c;
+  c.W = &g.W, c.X = &g.X, c.M = M, c.out = g.out, c.ld = g.W.N_pad;
+  c.split_stride = size_t(g.X.rows_alloc) * g.W.N_pad;
+  c.impl = impl, c.err_flag = g.err;
+  LB_TRY(gemm_launch(c, 0));
+  LB_CUDA(cudaDeviceSynchronize());
+  int err = 0;
+  LB_CUDA(cudaMemcpy(&err, g.err, 4, cudaMemcpyDeviceToHost));
+  if (err) {
+    set_error("gemm: device error word = " + std::to_string(err));
+    return LING_B200_ERR_DEVICE_FLAG;
+  }
+  const int planes = impl == 1 ? 1 : g.W.splits;
+  std::vector<float> host(size_t(planes) * c.split_stride);
+  LB_CUDA(cudaMemcpy(host.data(), g.out, host.size() * 4, cudaMemcpyDeviceToHost));
+  for (int m = 0; m < M; ++m)
+    for (int n = 0; n < N; ++n) {
+      float v = 0.f;
+      for (int p = 0; p < planes; ++p) v += host[size_t(p) * c.split_stride + size_t(m) * g.W.N_pad + n];  // plane order
+      y[size_t(m) * N + n] = v;
+    }
+  return LING_B200_OK;
+}
+
+int ling_b200_gemm_fp8_bench(int device, int impl, int splits, int M, int N, int K, int iters, float* ms_per_launch) {
+  if (M < 1 || N < 1 || K < 1 || iters < 1 || !ms_per_launch || M > LING_B200_MAX_ROWS) {
+    set_error("gemm_fp8_bench: bad argument");
+    return LING_B200_ERR_ARG;
+  }
+  LB_TRY(check_device(device));
+  Scratch sc;
+  GemmSetup g;
+  LB_TRY(setup_gemm(sc, g, M, N, K, splits));
+  float* dx = sc.get<float>(size_t(M) * K, false);
+  LB_PTR(dx);
+  LB_TRY(fill_f32_launch(stream_key(1, 7), 1.f, dx, size_t(M) * K, 0));
+  LB_TRY(quant_weight_launch(nullptr, stream_key(1, 9), 0.02f, 1, g.W.codes, g.W.scales, 0, N, K, g.W.N_pad, g.W.K_pad, 0));
+  LB_TRY(quant_acts_launch(dx, M, QuantOut{g.X.codes, g.X.scales, K, g.X.K_pad, g.X.rows_alloc}, 0));
+  GemmCall c;
+  c.W = &g.W, c.X = &g.X, c.M = M, c.out = g.out, c.ld = g.W.N_pad;
+  c.split_stride = size_t(g.X.rows_alloc) * g.W.N_pad;
+  c.impl = impl, c.err_flag = g.err;
+  cudaEvent_t a, b;
+  LB_CUDA(cudaEventCreate(&a));
+  LB_CUDA(cudaEventCreate(&b));
+  for (int i = 0; i < 3; ++i) LB_TRY(gemm_launch(c, 0));
+  LB_CUDA(cudaEventRecord(a, 0));
+  for (int i = 0; i < iters; ++i) LB_TRY(gemm_launch(c, 0));
+  LB_CUDA(cudaEventRecord(b, 0));
+  LB_CUDA(cudaEventSynchronize(b));
+  float ms = 0.f;
+  LB_CUDA(cudaEventElapsedTime(&ms, a, b));
+  cudaEventDestroy(a), cudaEventDestroy(b);
+  int err = 0;
+  LB_CUDA(cudaMemcpy(&err, g.err, 4, cudaMemcpyDeviceToHost));
+  if (err) {
+    set_error("gemm: device error word = " + std::to_string(err));
+    return LING_B200_ERR_DEVICE_FLAG;
+  }
+  *ms_per_launch = ms / iters;
+  return LING_B200_OK;
+}
+
+namespace {
+// A one-sequence StepBuffers for the DeltaNet kernels.
+struct OneSeq {
+  StepBuffers sb;
+  ModelDims d{};
+  int build(Scratch& sc, int Hk, int HV, int Dk, int Dv, int n_rows, int chain, const ling_b200_tree_desc* td,
+            const ling_b200_seq_result* res) {
+    d.Hk = Hk, d.HV = HV, d.Dk = Dk, d.Dv = Dv, d.C = 2 * Hk * Dk + HV * Dv, d.Vs = HV * Dv;
+    d.max_seqs = 1, d.n_gdn = 1, d.rows_alloc = n_rows;
+    const int one = 1;
+    const SeqDev q{0, 0, 0, n_rows, chain, 0};
+    const int row0[2] = {0, n_rows};
+    sb.n_seqs = sc.put(&one, 1);
+    sb.seqs = sc.put(&q, 1);
+    sb.row0 = sc.put(row0, 2);
+    sb.n_rows_total = sc.put(&n_rows, 1);
+    sb.trees = td ? sc.put(td, 1) : sc.get<ling_b200_tree_desc>(1);
+    sb.results = res ? sc.put(res, 1) : sc.get<ling_b200_seq_result>(1);
+    sb.err = sc.get<int>(1);
+    LB_PTR(sb.n_seqs && sb.seqs && sb.row0 && sb.n_rows_total && sb.trees && sb.results && sb.err);
+    return LING_B200_OK;
+  }
+};
+bool gdn_dims_ok(int Hk, int HV, int Dk, int Dv) {
+  return Hk > 0 && HV % Hk == 0 && (Dk == 64 || Dk == 128) && Dv % 32 == 0 && Dv <= 128;
+}
+}  // namespace
+
+int ling_b200_gdn_tree_host(int device, int Hk, int HV, int Dk, int Dv, const ling_b200_tree_desc* td, const float* pre,
+                            const float* convw, const float* g, const float* beta, const float* state, const float* conv,
+                            float* post, float* core) {
+  if (!td || !pre || !convw || !g || !beta || !state || !conv || !post || !core || !gdn_dims_ok(Hk, HV, Dk, Dv) || td->n < 1 ||
+      td->n > kTreeRows) {
+    set_error("gdn_tree_host: bad argument");
+    return LING_B200_ERR_ARG;
+  }
+  LB_TRY(check_device(device));
+  Scratch sc;
+  OneSeq o;
+  LB_TRY(o.build(sc, Hk, HV, Dk, Dv, td->n, 0, td, nullptr));
+  const int n = td->n, C = o.d.C, Vs = o.d.Vs;
+  float* d_in = sc.put(pre, size_t(n) * C);
+  float* d_w32 = sc.put(convw, size_t(C) * 4);
+  __nv_bfloat16* d_w = sc.get<__nv_bfloat16>(size_t(C) * 4);
+  float* d_g = sc.put(g, size_t(n) * HV);
+  float* d_b = sc.put(beta, size_t(n) * HV);
+  float* d_state = sc.put(state, size_t(HV) * Dk * Dv);
+  float* d_conv = sc.put(conv, size_t(C) * 3);
+  float* d_pre = sc.get<float>(size_t(n) * C);
+  float* d_post = sc.get<float>(size_t(n) * C);
+  float* d_core = sc.get<float>(size_t(n) * Vs);
+  LB_PTR(d_in && d_w32 && d_w && d_g && d_b && d_state && d_conv && d_pre && d_post && d_core);
+  LB_TRY(fill_bf16_launch(d_w32, 0, 0.f, 0.f, 0, d_w, size_t(C) * 4, 0));
+  Planes in;
+  in.p = d_in, in.n = 1, in.stride = 0, in.ld = C;
+  LB_TRY(conv_tree_launch(in, o.sb, o.d, d_w, d_conv, 0, d_pre, d_post, 0));
+  LB_TRY(gdn_tree_launch(d_post, d_g, d_b, o.sb, o.d, d_state, 0, d_core, 148 * 4, 0));
+  LB_CUDA(cudaDeviceSynchronize());
+  LB_CUDA(cudaMemcpy(post, d_post, size_t(n) * C * 4, cudaMemcpyDeviceToHost));
+  LB_CUDA(cudaMemcpy(core, d_core, size_t(n) * Vs * 4, cudaMemcpyDeviceToHost));
+  return LING_B200_OK;
+}
+
+int ling_b200_gdn_commit_host(int device, int Hk, int HV, int Dk, int Dv, const int* path, int n, int rows, const float* pre,
+                              const float* post, const float* g, const float* beta, float* state, float* conv) {
+  if (!path || !pre || !post || !g || !beta || !state || !conv || !gdn_dims_ok(Hk, HV, Dk, Dv) || n < 1 || n > kTreeRows ||
+      rows < 1 || rows > kTreeRows) {
+    set_error("gdn_commit_host: bad argument");
+    return LING_B200_ERR_ARG;
+  }
+  LB_TRY(check_device(device));
+  Scratch sc;
+  OneSeq o;
+  ling_b200_seq_result res{};
+  res.status = 0, res.n_path = n;
+  for (int j = 0; j < n; ++j) res.path[j] = path[j];
+  LB_TRY(o.build(sc, Hk, HV, Dk, Dv, rows, 0, nullptr, &res));
+  const int C = o.d.C;
+  float* d_pre = sc.put(pre, size_t(rows) * C);
+  float* d_post = sc.put(post, size_t(rows) * C);
+  float* d_g = sc.put(g, size_t(rows) * HV);
+  float* d_b = sc.put(beta, size_t(rows) * HV);
+  float* d_state = sc.put(state, size_t(HV) * Dk * Dv);
+  float* d_conv = sc.put(conv, size_t(C) * 3);
+  LB_PTR(d_pre && d_post && d_g && d_b && d_state && d_conv);
+  LB_TRY(conv_commit_launch(o.sb, o.d, d_pre, 0, d_conv, 0, 0, 0));
+  LB_TRY(gdn_commit_launch(o.sb, o.d, d_post, d_g, d_b, 0, 0, d_state, 0, 0, 148 * 4, 0));
+  LB_CUDA(cudaDeviceSynchronize());
+  LB_CUDA(cudaMemcpy(state, d_state, size_t(HV) * Dk * Dv * 4, cudaMemcpyDeviceToHost));
+  LB_CUDA(cudaMemcpy(conv, d_conv, size_t(C) * 3 * 4, cudaMemcpyDeviceToHost));
+  return LING_B200_OK;
+}
+
+int ling_b200_argmax_host(int device, const float* logits, int rows, int vocab, int* ids, float* vals) {
+  if (!logits || !ids || !vals || rows < 1 || vocab < 1) {
+    set_error("argmax_host: bad argument");
+    return LING_B200_ERR_ARG;
+  }
+  LB_TRY(check_device(device));
+  Scratch sc;
+  float* d_l = sc.put(logits, size_t(rows) * vocab);
+  int* d_i = sc.get<int>(rows);
+  float* d_v = sc.get<float>(rows);
+  LB_PTR(d_l && d_i && d_v);
+  LB_TRY(argmax_rows_launch(d_l, rows, vocab, d_i, d_v, 0));
+  LB_CUDA(cudaDeviceSynchronize());
+  LB_CUDA(cudaMemcpy(ids, d_i, size_t(rows) * 4, cudaMemcpyDeviceToHost));
+  LB_CUDA(cudaMemcpy(vals, d_v, size_t(rows) * 4, cudaMemcpyDeviceToHost));
+  return LING_B200_OK;
+}
+
+}  // extern "C"

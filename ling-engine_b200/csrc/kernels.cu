@@ -1,0 +1,1280 @@
+// kernels.cu -- the verify step's non-GEMM kernels for sm_100a: ragged packing and tree description on the device,
+// fused residual + RMSNorm + FP8 quantization, the gated-DeltaNet conv/recurrence over trees and its commit,
+// tree-masked attention over the paged FP8 KV cache, argmax, greedy acceptance and KV compaction.
+// Every kernel reads its real extents (rows, sequences) from device memory, so one captured graph serves any step
+// of the same capacity class.  Citations name the reference project's files (dreamference/ling-engine).
+#include "kernels.h"
+
+#include <cfloat>
+
+namespace lb {
+namespace {
+
+constexpr int kLeaf = LING_B200_TREE_LEAF, kWrite = LING_B200_TREE_WRITE;
+
+__device__ __forceinline__ float plane_sum(const Planes& a, int m, int c) {
+  float v = 0.f;
+  for (int p = 0; p < a.n; ++p) v += a.p[size_t(p) * a.stride + size_t(m) * a.ld + c];
+  return v;
+}
+__device__ __forceinline__ float4 plane_sum4(const Planes& a, int m, int c) {
+  float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int p = 0; p < a.n; ++p) {
+    const float4 t = *reinterpret_cast<const float4*>(a.p + size_t(p) * a.stride + size_t(m) * a.ld + c);
+    v.x += t.x, v.y += t.y, v.z += t.z, v.w += t.w;
+  }
+  return v;
+}
+
+// One warp owns one 128-column block of row m: lane l holds columns c .. c+3 (c = block * 128 + l * 4).
+// scale = amax / 448 (1 for an all-zero block), codes = E4M3(x / scale); columns at or past K are zero codes.
+__device__ __forceinline__ void quant_store4(float4 x, int c, int m, const QuantOut& q) {
+  const int lane = threadIdx.x & 31;
+  if (c >= q.K) x = make_float4(0.f, 0.f, 0.f, 0.f);
+  float amax = fmaxf(fmaxf(fabsf(x.x), fabsf(x.y)), fmaxf(fabsf(x.z), fabsf(x.w)));
+  amax = warp_max(amax);
+  const float sc = amax > 0.f ? amax / 448.f : 1.f;
+  if (c < q.K_pad) {
+    uchar4 o;
+    o.x = to_e4m3(__fdiv_rn(x.x, sc)), o.y = to_e4m3(__fdiv_rn(x.y, sc));
+    o.z = to_e4m3(__fdiv_rn(x.z, sc)), o.w = to_e4m3(__fdiv_rn(x.w, sc));
+    *reinterpret_cast<uchar4*>(q.codes + size_t(m) * q.K_pad + c) = o;
+    if (lane == 0) q.scales[size_t(c >> 7) * q.rows_alloc + m] = sc;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------- packing
+// One warp per sequence.  Packing as src/core/speculate.cpp:1190-1201 and src/core/kernels.cuh:58-78 define it
+// (rows concatenated, row0 prefix sums; a tree row's RoPE position is pos + depth, its cache slot pos + row index,
+// src/core/kernels.cuh:109-118), and describe_tree (src/core/tree.cpp:81-146) by lane 0 with children as bit masks.
+__global__ void __launch_bounds__(32) pack_kernel(StepBuffers sb, ModelDims d) {
+  __shared__ int par[kTreeRows], dep[kTreeRows];
+  __shared__ uint32_t kids[kTreeRows];
+  const int s = blockIdx.x, lane = threadIdx.x;
+  const int nseq = *sb.n_seqs;
+  int r0 = 0, total = 0;
+  for (int t = 0; t < nseq; ++t) {
+    if (t == s) r0 = total;
+    total += sb.seqs[t].n_rows;
+  }
+  if (s == 0 && lane == 0) {
+    sb.row0[nseq] = total;
+    *sb.n_rows_total = total;
+  }
+  if (s >= nseq) return;
+  const SeqDev q = sb.seqs[s];
+  const int n = q.n_rows;
+  if (lane == 0) sb.row0[s] = r0;
+  if (lane < n) {
+    int p = lane == 0 ? -1 : sb.in_parent[s * kTreeRows + lane];
+    if (lane > 0 && (p < 0 || p >= lane)) {
+      dev_fail(sb.err, kDevBadTree);
+      p = 0;
+    }
+    par[lane] = p;
+  }
+  __syncwarp();
+  if (lane < n) {
+    uint32_t mask = 0;
+    int dd = -1;
+    for (int a = lane; a >= 0; a = par[a]) mask |= 1u << a, ++dd;
+    dep[lane] = dd;
+    uint32_t km = 0;
+    for (int r = lane + 1; r < n; ++r)
+      if (par[r] == lane) km |= 1u << r;
+    kids[lane] = km;
+    int tok = sb.in_token[s * kTreeRows + lane];
+    if (tok < 0 || tok >= d.V) {
+      dev_fail(sb.err, kDevBadToken);
+      tok = 0;
+    }
+    const int row = r0 + lane;
+    sb.token[row] = tok;
+    sb.seq_of[row] = s;
+    sb.local[row] = lane;
+    sb.depth[row] = dd;
+    sb.rope_pos[row] = q.pos + dd + q.rope_delta;
+    sb.cache_slot[row] = q.pos + lane;
+    sb.anc[row] = mask;
+  }
+  ling_b200_tree_desc& T = sb.trees[s];
+  int* raw = reinterpret_cast<int*>(&T);
+  for (int i = lane; i < int(sizeof(ling_b200_tree_desc) / 4); i += 32) raw[i] = 0;
+  __syncwarp();
+  if (lane != 0) return;
+  T.n = n;
+  int leaf_var[kTreeRows];
+  int nvar = 0;
+  bool bad = false;
+  for (int r = 0; r < n; ++r) {
+    T.depth[r] = dep[r];
+    leaf_var[r] = -1;
+    if (kids[r]) continue;
+    if (nvar >= LING_B200_MAX_TREE_VARIANTS) {
+      bad = true;
+      break;
+    }
+    leaf_var[r] = nvar;
+    for (int a = r; a >= 0; a = par[a]) T.path[nvar][dep[a]] = a;
+    ++nvar;
+  }
+  T.nvar = nvar;
+  if (!bad)
+    for (int r = 0; r < n; ++r) {
+      int a = r;
+      while (kids[a]) a = __ffs(kids[a]) - 1;
+      T.var[r] = leaf_var[a];
+    }
+  uint32_t written = 0, covered = 0;
+  int ngdn = 0;
+  int nodes[kTreeRows];
+  auto emit = [&](int cnt) {
+    int* steps = T.gdn_step[ngdn];
+    int len = 0;
+    for (int i = 0; i < cnt; ++i) {
+      const int w = nodes[i];
+      steps[len++] = w | ((written >> w) & 1u ? 0 : kWrite);
+      written |= 1u << w, covered |= 1u << w;
+      for (uint32_t km = kids[w]; km; km &= km - 1) {
+        const int c = __ffs(km) - 1;
+        if (kids[c] == 0 && !((written >> c) & 1u)) {
+          steps[len++] = c | kLeaf | kWrite;
+          written |= 1u << c, covered |= 1u << c;
+        }
+      }
+    }
+    T.gdn_len[ngdn++] = len;
+  };
+  int cnt = 0;
+  for (int r = 0; r <= q.chain && r < n; ++r) nodes[cnt++] = r;
+  emit(cnt);
+  for (int r = 0; r < n && !bad; ++r) {
+    if (((covered >> r) & 1u) || kids[r] == 0) continue;
+    cnt = dep[r] + 1;
+    for (int a = r, i = cnt - 1; a >= 0; a = par[a], --i) nodes[i] = a;
+    for (int a = r;;) {
+      int nxt = -1;
+      for (uint32_t km = kids[a]; km; km &= km - 1) {
+        const int c = __ffs(km) - 1;
+        if (kids[c]) {
+          nxt = c;
+          break;
+        }
+      }
+      if (nxt < 0) break;
+      nodes[cnt++] = nxt;
+      a = nxt;
+    }
+    if (ngdn >= LING_B200_MAX_TREE_VARIANTS) {
+      bad = true;
+      break;
+    }
+    emit(cnt);
+  }
+  T.ngdn = ngdn;
+  if (bad || written != (n == 32 ? 0xffffffffu : ((1u << n) - 1u))) dev_fail(sb.err, kDevBadTree);
+}
+
+// ---------------------------------------------------------------------------------------------- norms
+// h[m] (+= the previous GEMM's partial sums, or = the embedding row) -> Gemma RMSNorm x * rsqrt(mean x^2 + eps) *
+// (1 + w) (src/core/kernels.cu:280-301) -> fp32 copy (for the BF16 a/b projections) and the FP8 copy for the GEMMs
+// (the reference's rmsnorm_half, src/core/stream_gemm.cu:383-418, at block-scaled FP8 instead of scaled FP16).
+constexpr int kNormChunks = 8;  // float4 chunks per thread: H <= 8192
+__global__ void __launch_bounds__(256)
+    norm_quant_kernel(float* __restrict__ h, Planes add, const int* __restrict__ ids, const __nv_bfloat16* __restrict__ embed,
+                      const __nv_bfloat16* __restrict__ w, float* __restrict__ xn, QuantOut q, const int* __restrict__ n_rows,
+                      int H, float eps) {
+  __shared__ float red[32];
+  const int m = blockIdx.x;
+  if (m >= *n_rows) return;
+  float4 v[kNormChunks];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < kNormChunks; ++j) {
+    const int c = j * 1024 + threadIdx.x * 4;
+    v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (c < H) {
+      if (ids) {
+        const __nv_bfloat16* e = embed + size_t(ids[m]) * H + c;
+        v[j] = make_float4(__bfloat162float(e[0]), __bfloat162float(e[1]), __bfloat162float(e[2]), __bfloat162float(e[3]));
+      } else {
+        v[j] = *reinterpret_cast<const float4*>(h + size_t(m) * H + c);
+        if (add.p) {
+          const float4 t = plane_sum4(add, m, c);
+          v[j].x += t.x, v[j].y += t.y, v[j].z += t.z, v[j].w += t.w;
+        }
+      }
+      *reinterpret_cast<float4*>(h + size_t(m) * H + c) = v[j];
+      ss += v[j].x * v[j].x + v[j].y * v[j].y + v[j].z * v[j].z + v[j].w * v[j].w;
+    }
+  }
+  const float rstd = rsqrtf(block_sum(ss, red) / H + eps);
+#pragma unroll
+  for (int j = 0; j < kNormChunks; ++j) {
+    const int c = j * 1024 + threadIdx.x * 4;
+    if (c - (threadIdx.x & 31) * 4 >= q.K_pad) break;  // warp-uniform: the warp's block starts past the padding
+    float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (c < H) {
+      x.x = v[j].x * rstd * (1.f + __bfloat162float(w[c]));
+      x.y = v[j].y * rstd * (1.f + __bfloat162float(w[c + 1]));
+      x.z = v[j].z * rstd * (1.f + __bfloat162float(w[c + 2]));
+      x.w = v[j].w * rstd * (1.f + __bfloat162float(w[c + 3]));
+      if (xn) *reinterpret_cast<float4*>(xn + size_t(m) * H + c) = x;
+    }
+    quant_store4(x, c, m, q);
+  }
+}
+
+__global__ void __launch_bounds__(256)
+    tap_kernel(const float* __restrict__ h, Planes add, float* __restrict__ out, const int* __restrict__ n_rows, int H) {
+  const int m = blockIdx.x;
+  if (m >= *n_rows) return;
+  for (int c = threadIdx.x; c < H; c += blockDim.x)
+    out[size_t(m) * H + c] = h[size_t(m) * H + c] + (add.p ? plane_sum(add, m, c) : 0.f);
+}
+
+// a = xn . W_a^T, b = xn . W_b^T against BF16 weights with fp32 accumulation (src/core/kernels.cu:200-253), then the
+// gating g = -exp(A_log) * softplus(a + dt_bias), beta = sigmoid(b) (src/core/kernels.cu:385-395).  One warp per
+// (row, value head).
+__global__ void __launch_bounds__(256)
+    ab_gating_kernel(const float* __restrict__ xn, const __nv_bfloat16* __restrict__ wa, const __nv_bfloat16* __restrict__ wb,
+                     const __nv_bfloat16* __restrict__ A_log, const __nv_bfloat16* __restrict__ dt_bias, float* __restrict__ g,
+                     float* __restrict__ beta, const int* __restrict__ n_rows, int H, int HV) {
+  const int hv = blockIdx.x, m = blockIdx.y * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (m >= *n_rows) return;
+  const float* x = xn + size_t(m) * H;
+  const __nv_bfloat16* a = wa + size_t(hv) * H;
+  const __nv_bfloat16* b = wb + size_t(hv) * H;
+  float sa = 0.f, sb2 = 0.f;
+  for (int c = lane * 4; c < H; c += 128) {
+    const float4 xv = *reinterpret_cast<const float4*>(x + c);
+    sa += xv.x * __bfloat162float(a[c]) + xv.y * __bfloat162float(a[c + 1]) + xv.z * __bfloat162float(a[c + 2]) +
+          xv.w * __bfloat162float(a[c + 3]);
+    sb2 += xv.x * __bfloat162float(b[c]) + xv.y * __bfloat162float(b[c + 1]) + xv.z * __bfloat162float(b[c + 2]) +
+           xv.w * __bfloat162float(b[c + 3]);
+  }
+  sa = warp_sum(sa), sb2 = warp_sum(sb2);
+  if (lane == 0) {
+    const float xx = sa + __bfloat162float(dt_bias[hv]);
+    const float sp = xx <= 20.f ? log1pf(__expf(xx)) : xx;
+    g[size_t(m) * HV + hv] = -__expf(__bfloat162float(A_log[hv])) * sp;
+    beta[size_t(m) * HV + hv] = 1.f / (1.f + __expf(-sb2));
+  }
+}
+
+// ---------------------------------------------------------------------------------------------- DeltaNet
+// The verify's conv over each sequence's tree (src/core/kernels.cu:365-383): a row's taps are the raw inputs of its
+// ancestors at depths d-3 .. d-1 (the variant's path) or the session's window before depth 0; the window is left
+// unwritten.  Also materializes the raw inputs (`pre`) from the GEMM's partial sums: the commit replays them.
+__global__ void __launch_bounds__(256)
+    conv_tree_kernel(Planes in, StepBuffers sb, int C, const __nv_bfloat16* __restrict__ convw,
+                     const float* __restrict__ conv_state, size_t slot_stride, float* __restrict__ pre, float* __restrict__ post) {
+  const int s = blockIdx.y, c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (s >= *sb.n_seqs || c >= C) return;
+  const SeqDev q = sb.seqs[s];
+  const int r0 = sb.row0[s];
+  const ling_b200_tree_desc* td = sb.trees + s;
+  const float* win = conv_state + size_t(q.slot) * slot_stride;
+  const float w0 = __bfloat162float(convw[c * 4]), w1 = __bfloat162float(convw[c * 4 + 1]);
+  const float w2 = __bfloat162float(convw[c * 4 + 2]), w3 = __bfloat162float(convw[c * 4 + 3]);
+  for (int t = 0; t < q.n_rows; ++t) {
+    const float xv = plane_sum(in, r0 + t, c);
+    pre[size_t(r0 + t) * C + c] = xv;
+    const int dd = td->depth[t];
+    const int* path = td->path[td->var[t]];
+    float tap[3];
+#pragma unroll
+    for (int j = 0; j < 3; ++j) {
+      const int dj = dd - 3 + j;
+      tap[j] = dj >= 0 ? pre[size_t(r0 + path[dj]) * C + c] : win[c * 3 + 3 + dj];
+    }
+    post[size_t(r0 + t) * C + c] = silu(w0 * tap[0] + w1 * tap[1] + w2 * tap[2] + w3 * xv);
+  }
+}
+
+// One token of the gated delta rule for 32 value columns of a head; each lane holds its column of the state
+// (src/core/kernels.cu:402-453): q and k L2-normalized (eps 1e-6), q also scaled by 1/sqrt(Dk); S *= decay;
+// kv = S^T k; d = (v - kv) beta; S += k d^T; o = S^T q.  advance = false is the leaf rule
+// (src/core/attention_body.cuh:575-603): the output from the parent's state, which stays as it was.
+template <int DK>
+__device__ __forceinline__ float delta_token(float (&S)[DK], const float* __restrict__ row, int h, int hv, int Hk, int Dv,
+                                             int v, float gval, float bval, float* qs, float* ks, bool advance) {
+  constexpr int PER = DK / 32;
+  const int lane = threadIdx.x & 31;
+  float qv[PER], kv2[PER];
+  float qn = 0.f, kn = 0.f;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    qv[i] = row[h * DK + lane * PER + i];
+    kv2[i] = row[Hk * DK + h * DK + lane * PER + i];
+    qn += qv[i] * qv[i], kn += kv2[i] * kv2[i];
+  }
+  qn = warp_sum(qn), kn = warp_sum(kn);
+  const float qr = rsqrtf(qn + 1e-6f) * rsqrtf(float(DK)), kr = rsqrtf(kn + 1e-6f);
+  __syncwarp();
+#pragma unroll
+  for (int i = 0; i < PER; ++i) qs[lane * PER + i] = qv[i] * qr, ks[lane * PER + i] = kv2[i] * kr;
+  __syncwarp();
+  const float decay = __expf(gval);
+  const float vv = row[2 * Hk * DK + hv * Dv + v];
+  float kv = 0.f, o = 0.f;
+  if (advance) {
+#pragma unroll
+    for (int k = 0; k < DK; ++k) {
+      S[k] *= decay;
+      kv = fmaf(S[k], ks[k], kv);
+    }
+    const float dlt = (vv - kv) * bval;
+#pragma unroll
+    for (int k = 0; k < DK; ++k) {
+      S[k] = fmaf(dlt, ks[k], S[k]);
+      o = fmaf(S[k], qs[k], o);
+    }
+  } else {
+#pragma unroll
+    for (int k = 0; k < DK; ++k) kv = fmaf(S[k] * decay, ks[k], kv);
+    const float dlt = (vv - kv) * bval;
+#pragma unroll
+    for (int k = 0; k < DK; ++k) o = fmaf(fmaf(dlt, ks[k], S[k] * decay), qs[k], o);
+  }
+  return o;
+}
+
+// The verify's recurrence over every sequence's tree (src/core/kernels.cu:455-477): a work item is (sequence, DeltaNet
+// path, value head, 32 value columns); its warp walks the path's steps from the session's state (never written here)
+// and writes the rows flagged kWrite.  A fixed grid of warps strides over the items.
+template <int DK>
+__global__ void __launch_bounds__(128)
+    gdn_tree_kernel(const float* __restrict__ post, const float* __restrict__ g, const float* __restrict__ beta, StepBuffers sb,
+                    int Hk, int HV, int Dv, const float* __restrict__ state, size_t slot_stride, float* __restrict__ core) {
+  __shared__ int pbase[LING_B200_MAX_SEQS + 1];
+  __shared__ float qs_all[4][DK], ks_all[4][DK];
+  __shared__ int steps_all[4][2 * kTreeRows];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nseq = *sb.n_seqs;
+  if (threadIdx.x == 0) {
+    int acc = 0;
+    for (int s = 0; s < nseq; ++s) {
+      pbase[s] = acc;
+      acc += sb.trees[s].ngdn;
+    }
+    pbase[nseq] = acc;
+  }
+  __syncthreads();
+  float* qs = qs_all[warp];
+  float* ks = ks_all[warp];
+  int* steps = steps_all[warp];
+  const int parts = Dv / 32, C = 2 * Hk * DK + HV * Dv;
+  const int per_path = HV * parts;
+  const int total = pbase[nseq] * per_path;
+  for (int item = blockIdx.x * 4 + warp; item < total; item += gridDim.x * 4) {
+    const int pg = item / per_path, rem = item % per_path, hv = rem / parts, v = (rem % parts) * 32 + lane;
+    int s = 0;
+    while (pbase[s + 1] <= pg) ++s;
+    const int pth = pg - pbase[s], h = hv / (HV / Hk);
+    const ling_b200_tree_desc* td = sb.trees + s;
+    const int r0 = sb.row0[s];
+    const float* st = state + size_t(sb.seqs[s].slot) * slot_stride + size_t(hv) * DK * Dv;
+    float S[DK];
+#pragma unroll
+    for (int k = 0; k < DK; ++k) S[k] = st[size_t(k) * Dv + v];
+    const int len = td->gdn_len[pth];
+    __syncwarp();
+    for (int i = lane; i < len; i += 32) steps[i] = td->gdn_step[pth][i];
+    __syncwarp();
+    for (int i = 0; i < len; ++i) {
+      const int st_i = steps[i], t = st_i & 0xff;
+      const size_t row = size_t(r0 + t);
+      const float o = delta_token<DK>(S, post + row * C, h, hv, Hk, Dv, v, g[row * HV + hv], beta[row * HV + hv], qs, ks,
+                                      (st_i & kLeaf) == 0);
+      if (st_i & kWrite) core[row * HV * Dv + size_t(hv) * Dv + v] = o;
+    }
+  }
+}
+
+// Engine::commit (src/core/speculate.cpp:516-529), the recurrence half: the accepted rows path[0..n) replayed from the
+// session's state over their saved conv outputs, the state written back.  Item = (sequence, layer, head, 32 columns).
+template <int DK>
+__global__ void __launch_bounds__(128)
+    gdn_commit_kernel(const float* __restrict__ post, const float* __restrict__ g, const float* __restrict__ beta,
+                      size_t post_layer_stride, size_t g_layer_stride, StepBuffers sb, int Hk, int HV, int Dv, int n_gdn,
+                      float* __restrict__ state, size_t slot_stride, size_t layer_stride) {
+  __shared__ float qs_all[4][DK], ks_all[4][DK];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nseq = *sb.n_seqs;
+  float* qs = qs_all[warp];
+  float* ks = ks_all[warp];
+  const int parts = Dv / 32, C = 2 * Hk * DK + HV * Dv;
+  const int per_seq = n_gdn * HV * parts;
+  const int total = nseq * per_seq;
+  for (int item = blockIdx.x * 4 + warp; item < total; item += gridDim.x * 4) {
+    const int s = item / per_seq;
+    int rem = item % per_seq;
+    const int gl = rem / (HV * parts);
+    rem %= HV * parts;
+    const int hv = rem / parts, v = (rem % parts) * 32 + lane, h = hv / (HV / Hk);
+    const ling_b200_seq_result* R = sb.results + s;
+    if (R->status != 0) continue;
+    const int r0 = sb.row0[s], n = R->n_path;
+    float* st = state + size_t(sb.seqs[s].slot) * slot_stride + size_t(gl) * layer_stride + size_t(hv) * DK * Dv;
+    float S[DK];
+#pragma unroll
+    for (int k = 0; k < DK; ++k) S[k] = st[size_t(k) * Dv + v];
+    const float* P = post + size_t(gl) * post_layer_stride;
+    const float* G = g + size_t(gl) * g_layer_stride;
+    const float* B = beta + size_t(gl) * g_layer_stride;
+    for (int j = 0; j < n; ++j) {
+      const size_t row = size_t(r0 + R->path[j]);
+      delta_token<DK>(S, P + row * C, h, hv, Hk, Dv, v, G[row * HV + hv], B[row * HV + hv], qs, ks, true);
+    }
+#pragma unroll
+    for (int k = 0; k < DK; ++k) st[size_t(k) * Dv + v] = S[k];
+  }
+}
+
+// The conv half of the commit: the window advanced over the accepted rows' raw inputs (src/core/kernels.cu:320-338).
+__global__ void __launch_bounds__(256)
+    conv_commit_kernel(StepBuffers sb, int C, const float* __restrict__ pre, size_t layer_stride, float* __restrict__ conv_state,
+                       size_t slot_stride, size_t conv_layer_stride) {
+  const int s = blockIdx.y, gl = blockIdx.z, c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (s >= *sb.n_seqs || c >= C) return;
+  const ling_b200_seq_result* R = sb.results + s;
+  if (R->status != 0) return;
+  const int r0 = sb.row0[s];
+  float* win = conv_state + size_t(sb.seqs[s].slot) * slot_stride + size_t(gl) * conv_layer_stride + size_t(c) * 3;
+  float s0 = win[0], s1 = win[1], s2 = win[2];
+  const float* P = pre + size_t(gl) * layer_stride;
+  for (int j = 0; j < R->n_path; ++j) {
+    s0 = s1, s1 = s2;
+    s2 = P[size_t(r0 + R->path[j]) * C + c];
+  }
+  win[0] = s0, win[1] = s1, win[2] = s2;
+}
+
+// rmsnorm(core) * w * silu(z) per (row, value head) over Dv with the plain weight (src/core/kernels.cu:543-554), then
+// the FP8 copy for the out projection.  A warp covers 128 columns: one head (Dv = 128) or several.
+__global__ void __launch_bounds__(256)
+    gated_norm_quant_kernel(const float* __restrict__ core, Planes z, int z_col, const __nv_bfloat16* __restrict__ w, QuantOut q,
+                            const int* __restrict__ n_rows, int Vs, int Dv, float eps) {
+  const int m = blockIdx.x;
+  if (m >= *n_rows) return;
+  const int seg = Dv / 4;  // lanes per head
+  for (int c0 = 0; c0 < q.K_pad; c0 += 1024) {
+    const int c = c0 + threadIdx.x * 4;
+    if (c - (threadIdx.x & 31) * 4 >= q.K_pad) break;
+    float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 zz = x;
+    if (c < Vs) {
+      x = *reinterpret_cast<const float4*>(core + size_t(m) * Vs + c);
+      zz = plane_sum4(z, m, z_col + c);
+    }
+    float ss = x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
+    for (int o = seg >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float rstd = rsqrtf(ss / Dv + eps);
+    if (c < Vs) {
+      const int dd = c % Dv;
+      x.x = x.x * rstd * __bfloat162float(w[dd]) * silu(zz.x);
+      x.y = x.y * rstd * __bfloat162float(w[dd + 1]) * silu(zz.y);
+      x.z = x.z * rstd * __bfloat162float(w[dd + 2]) * silu(zz.z);
+      x.w = x.w * rstd * __bfloat162float(w[dd + 3]) * silu(zz.w);
+    }
+    quant_store4(x, c, m, q);
+  }
+}
+
+// silu(gate) * up (src/core/kernels.cu:308-312) from the gate|up GEMM's partial sums, and its FP8 copy.
+__global__ void __launch_bounds__(256)
+    silu_mul_quant_kernel(Planes gu, int I, QuantOut q, const int* __restrict__ n_rows) {
+  const int m = blockIdx.x;
+  if (m >= *n_rows) return;
+  for (int c0 = 0; c0 < q.K_pad; c0 += 1024) {
+    const int c = c0 + threadIdx.x * 4;
+    if (c - (threadIdx.x & 31) * 4 >= q.K_pad) break;
+    float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (c < I) {
+      const float4 a = plane_sum4(gu, m, c), b = plane_sum4(gu, m, I + c);
+      x = make_float4(silu(a.x) * b.x, silu(a.y) * b.y, silu(a.z) * b.z, silu(a.w) * b.w);
+    }
+    quant_store4(x, c, m, q);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------- attention
+__device__ __forceinline__ float block_max(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = lane < warps ? red[lane] : 0.f;
+  return warp_max(t);
+}
+
+// attn_prepare (src/core/kernels.cu:558-596, src/core/attention_body.cuh:54-99): per head RMSNorm with (1 + w) and the
+// rotation of the first `rot` dims for q and k; K (rotated) and V (raw) go to cache slot pos + row index through the
+// page table as E4M3 with one fp32 scale per (position, head); q is kept as FP16 for the tensor-core score product.
+// Block = one (row, head): heads [0, Hq) are q, then Hkv k heads, then Hkv v heads.
+__global__ void attn_prepare_kernel(Planes qkv, StepBuffers sb, ModelDims d, int al, const __nv_bfloat16* __restrict__ q_norm,
+                                    const __nv_bfloat16* __restrict__ k_norm, __half* __restrict__ q, KvPoolDev kv) {
+  extern __shared__ float xs[];
+  __shared__ float red[32];
+  const int m = blockIdx.x, slot = blockIdx.y, dd = threadIdx.x;
+  if (m >= *sb.n_rows_total) return;
+  const int D = d.D, Hq = d.Hq, Hkv = d.Hkv;
+  const bool is_q = slot < Hq, is_v = slot >= Hq + Hkv;
+  const int head = is_q ? slot : (is_v ? slot - Hq - Hkv : slot - Hq);
+  const int col = is_q ? head * 2 * D + dd : (is_v ? Hq * 2 * D + Hkv * D + head * D + dd : Hq * 2 * D + head * D + dd);
+  float x = plane_sum(qkv, m, col);
+  if (!is_v) {
+    const float rstd = rsqrtf(block_sum(x * x, red) / D + d.eps);
+    xs[dd] = x * rstd * (1.f + __bfloat162float((is_q ? q_norm : k_norm)[dd]));
+    __syncthreads();
+    x = xs[dd];
+    if (dd < d.rot) {
+      const int half = d.rot / 2, i = dd % half;
+      const float inv_freq = powf(d.theta, -2.f * i / d.rot);
+      float sn, cs;
+      sincosf(float(sb.rope_pos[m]) * inv_freq, &sn, &cs);
+      x = dd < half ? xs[dd] * cs - xs[dd + half] * sn : xs[dd] * cs + xs[dd - half] * sn;
+    }
+    if (is_q) {
+      q[(size_t(m) * Hq + head) * D + dd] = __float2half_rn(x);
+      return;
+    }
+  }
+  const float amax = block_max(fabsf(x), red);
+  const float sc = amax > 0.f ? amax / 448.f : 1.f;
+  const int s = sb.seq_of[m], pos = sb.cache_slot[m];
+  const int page = kv.tables[size_t(sb.seqs[s].slot) * d.max_pages + pos / d.page_tokens];
+  if (page <= 0 || page > d.pool_pages) {
+    if (dd == 0) dev_fail(sb.err, kDevBadPage);
+    return;
+  }
+  const size_t at = kv_slot_index(d, al, is_v ? 1 : 0, head, page, pos % d.page_tokens);
+  kv.codes[at * D + dd] = to_e4m3(__fdiv_rn(x, sc));
+  if (dd == 0) kv.scales[at] = sc;
+}
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, int src_bytes) {
+  const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(dst));
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(a), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async4(void* dst, const void* src, int src_bytes) {
+  const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(dst));
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(a), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                        uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
+  const __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+constexpr float kPScale = 256.f;  // p * v_scale is carried in FP16 times this power of two (kept clear of subnormals)
+
+// Tree-masked attention over the paged FP8 cache, flash-decoding style (the reference's attention_rows,
+// src/core/kernels.cu:919-961 with body src/core/attention_body.cuh:262-501, rebuilt for an FP8 cache and any number
+// of sequences).  Work item = (sequence, kv head, key chunk, 64 query rows); the query rows of a kv head are
+// (token row, q head of the group) pairs, so one pass over a K/V tile serves every row of the tree and every q head
+// of the group.  Context chunks hold kAttnChunk keys; the last chunk of a sequence is its in-flight rows (cache slots
+// pos .. pos + n_rows), visible to a row only where its ancestor mask has the bit.  K/V tiles come through cp.async in
+// 16-byte pieces into double-buffered shared memory and stay E4M3 there; fragments are converted on load
+// (cvt.f16x2.e4m3x2) and the per-position scales are applied to scores and probabilities in fp32.
+// Output: per (chunk slot, query row) the unnormalized sum and (max, denominator); attn_combine_kernel merges chunks.
+template <int D, int G>
+__global__ void __launch_bounds__(128, (D > 128 ? 2 : 4))
+    attention_kernel(const __half* __restrict__ q, StepBuffers sb, ModelDims d, int al, KvPoolDev kv, float* __restrict__ part_o,
+                     float* __restrict__ part_ml, int chunk_slots) {
+  constexpr int QS = D + 8;    // halves per Q row in shared memory
+  constexpr int KS = D + 16;   // bytes per K/V row in shared memory
+  constexpr int RMAX = kTreeRows * G;
+  extern __shared__ __align__(16) uint8_t smem[];
+  __half* Qs = reinterpret_cast<__half*>(smem);                     // [64][QS]
+  uint8_t* Ks8 = smem + size_t(kAttnRowTile) * QS * 2;              // [2][64][KS]
+  uint8_t* Vs8 = Ks8 + 2 * kAttnKeyTile * KS;                       // [2][64][KS]
+  float* ksc = reinterpret_cast<float*>(Vs8 + 2 * kAttnKeyTile * KS);  // [2][64]
+  float* vsc = ksc + 2 * kAttnKeyTile;                              // [2][64]
+  __shared__ int cbase[LING_B200_MAX_SEQS + 1], ibase[LING_B200_MAX_SEQS + 1];
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g8 = lane >> 2, t4 = lane & 3;
+  const int nseq = *sb.n_seqs;
+  if (threadIdx.x == 0) {
+    int cb = 0, ib = 0;
+    for (int s = 0; s < nseq; ++s) {
+      cbase[s] = cb, ibase[s] = ib;
+      const int nch = (sb.seqs[s].pos + kAttnChunk - 1) / kAttnChunk + 1;
+      const int nrg = (sb.seqs[s].n_rows * G + kAttnRowTile - 1) / kAttnRowTile;
+      cb += nch, ib += d.Hkv * nch * nrg;
+    }
+    cbase[nseq] = cb, ibase[nseq] = ib;
+  }
+  __syncthreads();
+  const float inv_sqrt_d = rsqrtf(float(D));
+  const size_t page_elems = size_t(d.page_tokens);
+
+  for (int item = blockIdx.x; item < ibase[nseq]; item += gridDim.x) {
+    int s = 0;
+    while (ibase[s + 1] <= item) ++s;
+    const SeqDev sq = sb.seqs[s];
+    const int nch = (sq.pos + kAttnChunk - 1) / kAttnChunk + 1;
+    const int nrg = (sq.n_rows * G + kAttnRowTile - 1) / kAttnRowTile;
+    const int loc = item - ibase[s];
+    const int hk = loc / (nch * nrg), ch = (loc % (nch * nrg)) / nrg, rg = loc % nrg;
+    const int slot_idx = cbase[s] * d.Hkv + hk * nch + ch;
+    if (slot_idx >= chunk_slots) {
+      if (threadIdx.x == 0) dev_fail(sb.err, kDevBadPage);
+      continue;
+    }
+    const bool tail = ch == nch - 1;
+    const int key_base = tail ? sq.pos : ch * kAttnChunk;
+    const int key_count = tail ? sq.n_rows : min(kAttnChunk, sq.pos - key_base);
+    const int R = sq.n_rows * G, r_begin = rg * kAttnRowTile, r0 = sb.row0[s];
+    const int* table = kv.tables + size_t(sq.slot) * d.max_pages;
+
+    __syncthreads();  // the previous item's readers of Qs and the tiles are done
+    for (int idx = threadIdx.x; idx < kAttnRowTile * (D / 8); idx += 128) {
+      const int r = idx / (D / 8), part = idx % (D / 8);
+      uint4 val = make_uint4(0, 0, 0, 0);
+      const int rr = r_begin + r;
+      if (rr < R) val = *reinterpret_cast<const uint4*>(q + (size_t(r0 + rr / G) * d.Hq + hk * G + rr % G) * D + part * 8);
+      *reinterpret_cast<uint4*>(Qs + size_t(r) * QS + part * 8) = val;
+    }
+    auto load_tile = [&](int tile, int buf) {
+      const int k0 = tile * kAttnKeyTile;
+      for (int idx = threadIdx.x; idx < kAttnKeyTile * (D / 16); idx += 128) {
+        const int key = idx / (D / 16), part = idx % (D / 16);
+        const bool valid = k0 + key < key_count;
+        const int pos = key_base + k0 + key;
+        size_t at = 0;
+        if (valid) {
+          int page = table[pos / d.page_tokens];
+          if (page < 0 || page > d.pool_pages) page = 0;  // lands in the reserved page, as an unmapped position does
+          at = size_t(page) * page_elems + pos % d.page_tokens;
+        }
+        const size_t kat = kv_slot_index(d, al, 0, hk, 0, 0) + at, vat = kv_slot_index(d, al, 1, hk, 0, 0) + at;
+        cp_async16(Ks8 + (size_t(buf) * kAttnKeyTile + key) * KS + part * 16, kv.codes + kat * D + part * 16, valid ? 16 : 0);
+        cp_async16(Vs8 + (size_t(buf) * kAttnKeyTile + key) * KS + part * 16, kv.codes + vat * D + part * 16, valid ? 16 : 0);
+        if (part == 0) {
+          cp_async4(ksc + buf * kAttnKeyTile + key, kv.scales + kat, valid ? 4 : 0);
+          cp_async4(vsc + buf * kAttnKeyTile + key, kv.scales + vat, valid ? 4 : 0);
+        }
+      }
+      cp_async_commit();
+    };
+
+    float O[D / 8][4];
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) O[i][0] = O[i][1] = O[i][2] = O[i][3] = 0.f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    // this thread's two query rows and their ancestor masks (tail chunk only)
+    const int rowA = r_begin + warp * 16 + g8, rowB = rowA + 8;
+    uint32_t ancA = 0xffffffffu, ancB = 0xffffffffu;
+    if (tail) {
+      ancA = rowA < R ? sb.anc[r0 + rowA / G] : 0u;
+      ancB = rowB < R ? sb.anc[r0 + rowB / G] : 0u;
+    }
+    const bool warp_active = r_begin + warp * 16 < R;
+
+    const int ntiles = (key_count + kAttnKeyTile - 1) / kAttnKeyTile;
+    load_tile(0, 0);
+    for (int tile = 0; tile < ntiles; ++tile) {
+      const int buf = tile & 1;
+      if (tile + 1 < ntiles) {
+        load_tile(tile + 1, buf ^ 1);
+        cp_async_wait<1>();
+      } else {
+        cp_async_wait<0>();
+      }
+      __syncthreads();
+      if (warp_active) {
+        const uint8_t* Kt = Ks8 + size_t(buf) * kAttnKeyTile * KS;
+        const uint8_t* Vt = Vs8 + size_t(buf) * kAttnKeyTile * KS;
+        float S[8][4];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) S[i][0] = S[i][1] = S[i][2] = S[i][3] = 0.f;
+        const __half* qa = Qs + size_t(warp * 16 + g8) * QS;
+#pragma unroll 4
+        for (int kt = 0; kt < D / 16; ++kt) {
+          const uint32_t a0 = *reinterpret_cast<const uint32_t*>(qa + kt * 16 + 2 * t4);
+          const uint32_t a1 = *reinterpret_cast<const uint32_t*>(qa + 8 * QS + kt * 16 + 2 * t4);
+          const uint32_t a2 = *reinterpret_cast<const uint32_t*>(qa + kt * 16 + 8 + 2 * t4);
+          const uint32_t a3 = *reinterpret_cast<const uint32_t*>(qa + 8 * QS + kt * 16 + 8 + 2 * t4);
+#pragma unroll
+          for (int nt = 0; nt < 8; ++nt) {
+            const uint8_t* kr = Kt + size_t(nt * 8 + g8) * KS + kt * 16 + 2 * t4;
+            const uint32_t b0 = e4m3x2_to_h2(*reinterpret_cast<const uint16_t*>(kr));
+            const uint32_t b1 = e4m3x2_to_h2(*reinterpret_cast<const uint16_t*>(kr + 8));
+            mma_f16(S[nt], a0, a1, a2, a3, b0, b1);
+          }
+        }
+        // scores: scale, mask, running max
+        const int k0 = tile * kAttnKeyTile;
+        float tmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int key = nt * 8 + 2 * t4 + (e & 1);
+            const uint32_t anc = (e < 2) ? ancA : ancB;
+            const bool vis = (k0 + key < key_count) && (!tail || ((anc >> (k0 + key)) & 1u));
+            const float sv = vis ? S[nt][e] * (ksc[buf * kAttnKeyTile + key] * inv_sqrt_d) : -INFINITY;
+            S[nt][e] = sv;
+            tmax[e >> 1] = fmaxf(tmax[e >> 1], sv);
+          }
+        float corr[2], muse[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 1));
+          tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 2));
+          const float mnew = fmaxf(m_run[r], tmax[r]);
+          muse[r] = mnew == -INFINITY ? 0.f : mnew;
+          corr[r] = __expf(m_run[r] - muse[r]);  // exp(-inf) = 0 on the first tile
+          m_run[r] = mnew;
+        }
+        float lsum[2] = {0.f, 0.f};
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int key = nt * 8 + 2 * t4 + (e & 1);
+            const float p = __expf(S[nt][e] - muse[e >> 1]);
+            lsum[e >> 1] += p;
+            S[nt][e] = p * (vsc[buf * kAttnKeyTile + key] * kPScale);
+          }
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          lsum[r] += __shfl_xor_sync(0xffffffffu, lsum[r], 1);
+          lsum[r] += __shfl_xor_sync(0xffffffffu, lsum[r], 2);
+          l_run[r] = l_run[r] * corr[r] + lsum[r];
+        }
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) O[i][0] *= corr[0], O[i][1] *= corr[0], O[i][2] *= corr[1], O[i][3] *= corr[1];
+        // O += P . V
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+          const uint32_t a0 = pack_h2(S[2 * kk][0], S[2 * kk][1]), a1 = pack_h2(S[2 * kk][2], S[2 * kk][3]);
+          const uint32_t a2 = pack_h2(S[2 * kk + 1][0], S[2 * kk + 1][1]), a3 = pack_h2(S[2 * kk + 1][2], S[2 * kk + 1][3]);
+          const uint8_t* v0 = Vt + size_t(kk * 16 + 2 * t4) * KS + g8;
+#pragma unroll
+          for (int nt = 0; nt < D / 8; ++nt) {
+            const uint8_t* vp = v0 + nt * 8;
+            const uint16_t p0 = uint16_t(vp[0]) | (uint16_t(vp[KS]) << 8);
+            const uint16_t p1 = uint16_t(vp[8 * KS]) | (uint16_t(vp[9 * KS]) << 8);
+            mma_f16(O[nt], a0, a1, a2, a3, e4m3x2_to_h2(p0), e4m3x2_to_h2(p1));
+          }
+        }
+      }
+      __syncthreads();
+    }
+    if (warp_active) {
+      float* po = part_o + size_t(slot_idx) * RMAX * D;
+      float* pm = part_ml + size_t(slot_idx) * RMAX * 2;
+#pragma unroll
+      for (int nt = 0; nt < D / 8; ++nt) {
+        if (rowA < R) *reinterpret_cast<float2*>(po + size_t(rowA) * D + nt * 8 + 2 * t4) = make_float2(O[nt][0], O[nt][1]);
+        if (rowB < R) *reinterpret_cast<float2*>(po + size_t(rowB) * D + nt * 8 + 2 * t4) = make_float2(O[nt][2], O[nt][3]);
+      }
+      if (t4 == 0) {
+        if (rowA < R) pm[rowA * 2] = m_run[0], pm[rowA * 2 + 1] = l_run[0];
+        if (rowB < R) pm[rowB * 2] = m_run[1], pm[rowB * 2 + 1] = l_run[1];
+      }
+    }
+  }
+}
+
+// Merges a row's chunks in order (the reference's attention_combine, src/core/attention_body.cuh:506-525), applies the
+// output gate out * sigmoid(gate) (src/core/kernels.cu:314-318; the gate is the second D values of each q head's
+// projection) and writes the FP8 copy for the o projection.  One block per packed row.
+template <int G>
+__global__ void __launch_bounds__(256)
+    attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, Planes qkv, StepBuffers sb,
+                        ModelDims d, QuantOut q) {
+  extern __shared__ float rowbuf[];  // [Hq * D]
+  constexpr int RMAX = kTreeRows * G;
+  const int m = blockIdx.x;
+  if (m >= *sb.n_rows_total) return;
+  const int s = sb.seq_of[m], local = sb.local[m], D = d.D;
+  int cb = 0;
+  for (int t = 0; t < s; ++t) cb += (sb.seqs[t].pos + kAttnChunk - 1) / kAttnChunk + 1;
+  const int nch = (sb.seqs[s].pos + kAttnChunk - 1) / kAttnChunk + 1;
+  for (int idx = threadIdx.x; idx < d.Hq * D; idx += blockDim.x) {
+    const int hq = idx / D, dd = idx % D, hk = hq / G, r = local * G + hq % G;
+    const size_t base = size_t(cb) * d.Hkv + size_t(hk) * nch;
+    float mx = -INFINITY;
+    for (int c = 0; c < nch; ++c) mx = fmaxf(mx, part_ml[((base + c) * RMAX + r) * 2]);
+    float num = 0.f, den = 0.f;
+    for (int c = 0; c < nch; ++c) {
+      const float mc = part_ml[((base + c) * RMAX + r) * 2];
+      if (mc == -INFINITY) continue;  // an empty chunk
+      const float wgt = __expf(mc - mx);
+      den += part_ml[((base + c) * RMAX + r) * 2 + 1] * wgt;
+      num += part_o[((base + c) * RMAX + r) * D + dd] * wgt;
+    }
+    const float gate = plane_sum(qkv, m, hq * 2 * D + D + dd);
+    rowbuf[idx] = (num / den) * (1.f / kPScale) * sigmoidf(gate);
+  }
+  __syncthreads();
+  for (int c0 = 0; c0 < q.K_pad; c0 += 1024) {
+    const int c = c0 + threadIdx.x * 4;
+    if (c - (threadIdx.x & 31) * 4 >= q.K_pad) break;
+    float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (c < q.K) x = *reinterpret_cast<const float4*>(rowbuf + c);
+    quant_store4(x, c, m, q);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------- argmax / accept
+__device__ __forceinline__ bool better(float v, int i, float v2, int i2) { return v > v2 || (v == v2 && i < i2); }
+
+// Second stage of the argmax: merges the head GEMM's per-tile winners with the first stage's comparison, so the result
+// does not depend on the tiling (src/core/topk.cu:1-9,19).
+__global__ void __launch_bounds__(256)
+    argmax_reduce_kernel(const float* __restrict__ tile_val, const int* __restrict__ tile_idx, int tiles, int rows_alloc,
+                         int* __restrict__ ids, float* __restrict__ vals, const int* __restrict__ n_rows) {
+  __shared__ float sv[256];
+  __shared__ int si[256];
+  const int m = blockIdx.x;
+  if (m >= *n_rows) return;
+  float bv = -FLT_MAX;
+  int bi = 0x7fffffff;
+  for (int t = threadIdx.x; t < tiles; t += blockDim.x) {
+    const float v = tile_val[size_t(t) * rows_alloc + m];
+    const int i = tile_idx[size_t(t) * rows_alloc + m];
+    if (v == v && better(v, i, bv, bi)) bv = v, bi = i;
+  }
+  sv[threadIdx.x] = bv, si[threadIdx.x] = bi;
+  __syncthreads();
+  for (int o = 128; o > 0; o >>= 1) {
+    if (threadIdx.x < o && better(sv[threadIdx.x + o], si[threadIdx.x + o], sv[threadIdx.x], si[threadIdx.x]))
+      sv[threadIdx.x] = sv[threadIdx.x + o], si[threadIdx.x] = si[threadIdx.x + o];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) ids[m] = si[0], vals[m] = sv[0];
+}
+
+// topk_rows with K = 1 over materialized logits (src/core/topk.cu:83-129): one block per row.
+__global__ void __launch_bounds__(256)
+    argmax_rows_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ ids, float* __restrict__ vals) {
+  __shared__ float sv[256];
+  __shared__ int si[256];
+  const int m = blockIdx.x;
+  float bv = -FLT_MAX;
+  int bi = 0x7fffffff;
+  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+    const float v = logits[size_t(m) * vocab + i];
+    if (v == v && better(v, i, bv, bi)) bv = v, bi = i;
+  }
+  sv[threadIdx.x] = bv, si[threadIdx.x] = bi;
+  __syncthreads();
+  for (int o = 128; o > 0; o >>= 1) {
+    if (threadIdx.x < o && better(sv[threadIdx.x + o], si[threadIdx.x + o], sv[threadIdx.x], si[threadIdx.x]))
+      sv[threadIdx.x] = sv[threadIdx.x + o], si[threadIdx.x] = si[threadIdx.x + o];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) ids[m] = si[0], vals[m] = sv[0];
+}
+
+// One thread per sequence: the finiteness guard over its rows (require_finite_topk, src/core/sampling.cpp:20-23), then
+// accept_tree_greedy (src/core/tree.cpp:148-166): from the root, the first child in row order whose token is the current
+// row's argmax; `next` is the argmax that no child matched.  out = the accepted drafts, then next
+// (src/core/speculate.cpp:1066-1067).
+__global__ void accept_kernel(StepBuffers sb, int vocab) {
+  const int s = blockIdx.x * blockDim.x + threadIdx.x;
+  if (s >= *sb.n_seqs) return;
+  const SeqDev q = sb.seqs[s];
+  const int r0 = sb.row0[s], n = q.n_rows;
+  ling_b200_seq_result R;
+  R.status = LING_B200_SEQ_OK, R.n_path = 0, R.next_token = 0, R.n_out = 0;
+  for (int i = 0; i < kTreeRows; ++i) R.path[i] = 0;
+  for (int i = 0; i < kTreeRows + 1; ++i) R.out[i] = 0;
+  for (int r = 0; r < n; ++r) {
+    const float v = sb.argmax_val[r0 + r];
+    const int id = sb.argmax_id[r0 + r];
+    if (!isfinite(v) || v == -FLT_MAX || id < 0 || id >= vocab) R.status = LING_B200_SEQ_NONFINITE;
+  }
+  if (R.status == LING_B200_SEQ_OK) {
+    const int* par = sb.in_parent + s * kTreeRows;
+    const int* tok = sb.in_token + s * kTreeRows;
+    const int* forced = sb.in_force + s * kTreeRows;
+    int u = 0;
+    R.path[R.n_path++] = 0;
+    for (;;) {
+      const int x = q.has_force ? forced[u] : sb.argmax_id[r0 + u];
+      int child = -1;
+      for (int c = u + 1; c < n; ++c)
+        if (par[c] == u && tok[c] == x) {
+          child = c;
+          break;
+        }
+      if (child < 0) {
+        R.next_token = x;
+        break;
+      }
+      R.path[R.n_path++] = child;
+      u = child;
+    }
+    for (int j = 1; j < R.n_path; ++j) R.out[R.n_out++] = tok[R.path[j]];
+    R.out[R.n_out++] = R.next_token;
+  }
+  sb.results[s] = R;
+}
+
+// tree_gather for the KV cache (src/core/kernels.cu:481-498): cache slot pos + path[j] moves to pos + j, j ascending,
+// through the page table (source and destination may sit in different pages); codes and the per-position scale.
+// Block = one (sequence, layer, K|V, kv head).
+__global__ void __launch_bounds__(64) kv_compact_kernel(StepBuffers sb, ModelDims d, KvPoolDev kv) {
+  const int s = blockIdx.y;
+  if (s >= *sb.n_seqs) return;
+  const ling_b200_seq_result* R = sb.results + s;
+  if (R->status != 0) return;
+  const int hk = blockIdx.x % d.Hkv, kvi = (blockIdx.x / d.Hkv) % 2, al = blockIdx.x / (2 * d.Hkv);
+  const SeqDev q = sb.seqs[s];
+  const int* table = kv.tables + size_t(q.slot) * d.max_pages;
+  for (int j = 1; j < R->n_path; ++j) {
+    const int src = q.pos + R->path[j], dst = q.pos + j;
+    if (src != dst) {
+      const size_t a = kv_slot_index(d, al, kvi, hk, table[src / d.page_tokens], src % d.page_tokens);
+      const size_t b = kv_slot_index(d, al, kvi, hk, table[dst / d.page_tokens], dst % d.page_tokens);
+      for (int i = threadIdx.x; i < d.D / 4; i += blockDim.x)
+        reinterpret_cast<uint32_t*>(kv.codes + b * d.D)[i] = reinterpret_cast<const uint32_t*>(kv.codes + a * d.D)[i];
+      if (threadIdx.x == 0) kv.scales[b] = kv.scales[a];
+    }
+    __syncthreads();
+  }
+}
+
+// ---------------------------------------------------------------------------------------------- weights, synthetic data
+// One warp per (row, 128-column block): BF16 rounding, scale = amax / 448, E4M3 codes; padding columns get zero codes.
+// The source is a host-supplied fp32 matrix [rows][K] or the generator.  Row r lands at row row_off + r of the
+// destination, whose scales are stored block-major with stride N_pad (several tensors share one fused matrix).
+__global__ void __launch_bounds__(256)
+    quant_weight_kernel(const float* __restrict__ src, uint64_t key, float std_, int from_generator, uint8_t* __restrict__ codes,
+                        float* __restrict__ scales, int row_off, int K, int N_pad, int K_pad) {
+  const int r = blockIdx.x, n = row_off + r, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, KB = K_pad / 128;
+  for (int kb = blockIdx.y * 8 + warp; kb < KB; kb += gridDim.y * 8) {
+    const int c = kb * 128 + lane * 4;
+    float x[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      x[i] = 0.f;
+      if (c + i < K) {
+        const size_t e = size_t(r) * K + c + i;
+        x[i] = bf16_round(from_generator ? synth_z(key, e) * std_ : src[e]);
+      }
+    }
+    const float amax = warp_max(fmaxf(fmaxf(fabsf(x[0]), fabsf(x[1])), fmaxf(fabsf(x[2]), fabsf(x[3]))));
+    const float sc = amax > 0.f ? amax / 448.f : 1.f;
+    uchar4 o;
+    o.x = to_e4m3(__fdiv_rn(x[0], sc)), o.y = to_e4m3(__fdiv_rn(x[1], sc));
+    o.z = to_e4m3(__fdiv_rn(x[2], sc)), o.w = to_e4m3(__fdiv_rn(x[3], sc));
+    *reinterpret_cast<uchar4*>(codes + size_t(n) * K_pad + c) = o;
+    if (lane == 0) scales[size_t(kb) * N_pad + n] = sc;
+  }
+}
+
+// Plain fp32 rows to the activation encoding (codes [rows][K_pad], scales [KB][rows_alloc]).
+__global__ void __launch_bounds__(256) quant_acts_kernel(const float* __restrict__ x, QuantOut q) {
+  const int m = blockIdx.x;
+  for (int c0 = 0; c0 < q.K_pad; c0 += 1024) {
+    const int c = c0 + threadIdx.x * 4;
+    if (c - (threadIdx.x & 31) * 4 >= q.K_pad) break;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (c < q.K) {
+      const float* r = x + size_t(m) * q.K + c;
+      v = make_float4(r[0], c + 1 < q.K ? r[1] : 0.f, c + 2 < q.K ? r[2] : 0.f, c + 3 < q.K ? r[3] : 0.f);
+    }
+    quant_store4(v, c, m, q);
+  }
+}
+
+__global__ void fill_bf16_kernel(const float* __restrict__ src, uint64_t key, float std_, float bias, int from_generator,
+                                 __nv_bfloat16* __restrict__ dst, size_t n) {
+  for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < n; i += size_t(gridDim.x) * blockDim.x)
+    dst[i] = __float2bfloat16(from_generator ? synth_z(key, i) * std_ + bias : src[i]);
+}
+__global__ void fill_f32_kernel(uint64_t key, float std_, float* __restrict__ dst, size_t n) {
+  for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < n; i += size_t(gridDim.x) * blockDim.x)
+    dst[i] = synth_z(key, i) * std_;
+}
+
+// K and V of positions [from, from + n) of one attention layer into the slot's pages, quantized as the step quantizes
+// them.  Block = (position, kv head, K|V), one thread per dim.
+__global__ void kv_write_kernel(const float* __restrict__ k, const float* __restrict__ v, uint64_t key_k, uint64_t key_v,
+                                int from_generator, ModelDims d, int al, int slot, int from, KvPoolDev kv, int* err) {
+  __shared__ float red[32];
+  const int i = blockIdx.x, h = blockIdx.y, kvi = blockIdx.z, dd = threadIdx.x, pos = from + i;
+  const size_t e = (size_t(from_generator ? pos : i) * d.Hkv + h) * d.D + dd;
+  const float x = from_generator ? synth_z(kvi ? key_v : key_k, e) : (kvi ? v : k)[e];
+  const float amax = block_max(fabsf(x), red);
+  const float sc = amax > 0.f ? amax / 448.f : 1.f;
+  const int page = kv.tables[size_t(slot) * d.max_pages + pos / d.page_tokens];
+  if (page <= 0 || page > d.pool_pages) {
+    if (dd == 0) dev_fail(err, kDevBadPage);
+    return;
+  }
+  const size_t at = kv_slot_index(d, al, kvi, h, page, pos % d.page_tokens);
+  kv.codes[at * d.D + dd] = to_e4m3(__fdiv_rn(x, sc));
+  if (dd == 0) kv.scales[at] = sc;
+}
+
+// A whole page copied for copy-on-write (the reference's kv_pages_copy role, src/core/kernels.cu:513-527).
+__global__ void kv_page_copy_kernel(ModelDims d, KvPoolDev kv, int src, int dst) {
+  const int lane_kv = blockIdx.x;  // (layer, K|V, head)
+  const size_t a = (size_t(lane_kv) * (d.pool_pages + 1) + src) * d.page_tokens;
+  const size_t b = (size_t(lane_kv) * (d.pool_pages + 1) + dst) * d.page_tokens;
+  const int words = d.page_tokens * d.D / 4;
+  for (int i = threadIdx.x; i < words; i += blockDim.x)
+    reinterpret_cast<uint32_t*>(kv.codes + b * d.D)[i] = reinterpret_cast<const uint32_t*>(kv.codes + a * d.D)[i];
+  for (int i = threadIdx.x; i < d.page_tokens; i += blockDim.x) kv.scales[b + i] = kv.scales[a + i];
+}
+
+__global__ void flush_kernel(float* __restrict__ buf, size_t n) {
+  for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < n; i += size_t(gridDim.x) * blockDim.x) buf[i] = float(i);
+}
+
+template <int D, int G>
+constexpr size_t attn_smem() {
+  return size_t(kAttnRowTile) * (D + 8) * 2 + size_t(4) * kAttnKeyTile * (D + 16) + size_t(4) * kAttnKeyTile * 4;
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------------------------- launchers
+int pack_launch(const StepBuffers& sb, const ModelDims& d, cudaStream_t s) {
+  pack_kernel<<<d.max_seqs, 32, 0, s>>>(sb, d);
+  LB_LAUNCH("pack_kernel");
+  return LING_B200_OK;
+}
+
+int norm_quant_launch(float* h, const Planes& add, const int* ids, const __nv_bfloat16* embed, const __nv_bfloat16* w,
+                      float* xn, const QuantOut& q, const int* n_rows, int rows_grid, int H, float eps, cudaStream_t s) {
+  norm_quant_kernel<<<rows_grid, 256, 0, s>>>(h, add, ids, embed, w, xn, q, n_rows, H, eps);
+  LB_LAUNCH("norm_quant_kernel");
+  return LING_B200_OK;
+}
+
+int tap_launch(const float* h, const Planes& add, float* out, const int* n_rows, int rows_grid, int H, cudaStream_t s) {
+  tap_kernel<<<rows_grid, 256, 0, s>>>(h, add, out, n_rows, H);
+  LB_LAUNCH("tap_kernel");
+  return LING_B200_OK;
+}
+
+int copy_rows_launch(const float* src, float* out, const int* n_rows, int rows_grid, int H, cudaStream_t s) {
+  Planes none;
+  tap_kernel<<<rows_grid, 256, 0, s>>>(src, none, out, n_rows, H);
+  LB_LAUNCH("tap_kernel");
+  return LING_B200_OK;
+}
+
+int ab_gating_launch(const float* xn, const __nv_bfloat16* wa, const __nv_bfloat16* wb, const __nv_bfloat16* A_log,
+                     const __nv_bfloat16* dt_bias, float* g, float* beta, const int* n_rows, int rows_grid, int H, int HV,
+                     cudaStream_t s) {
+  ab_gating_kernel<<<dim3(HV, ceil_div(rows_grid, 8)), 256, 0, s>>>(xn, wa, wb, A_log, dt_bias, g, beta, n_rows, H, HV);
+  LB_LAUNCH("ab_gating_kernel");
+  return LING_B200_OK;
+}
+
+int conv_tree_launch(const Planes& in, const StepBuffers& sb, const ModelDims& d, const __nv_bfloat16* convw,
+                     const float* conv_state, size_t conv_slot_stride, float* pre, float* post, cudaStream_t s) {
+  conv_tree_kernel<<<dim3(ceil_div(d.C, 256), d.max_seqs), 256, 0, s>>>(in, sb, d.C, convw, conv_state, conv_slot_stride, pre,
+                                                                        post);
+  LB_LAUNCH("conv_tree_kernel");
+  return LING_B200_OK;
+}
+
+int gdn_tree_launch(const float* post, const float* g, const float* beta, const StepBuffers& sb, const ModelDims& d,
+                    const float* state, size_t state_slot_stride, float* core, int grid, cudaStream_t s) {
+  if (d.Dk == 128)
+    gdn_tree_kernel<128><<<grid, 128, 0, s>>>(post, g, beta, sb, d.Hk, d.HV, d.Dv, state, state_slot_stride, core);
+  else if (d.Dk == 64)
+    gdn_tree_kernel<64><<<grid, 128, 0, s>>>(post, g, beta, sb, d.Hk, d.HV, d.Dv, state, state_slot_stride, core);
+  else {
+    set_error("DeltaNet key dim must be 64 or 128");
+    return LING_B200_ERR_UNSUPPORTED;
+  }
+  LB_LAUNCH("gdn_tree_kernel");
+  return LING_B200_OK;
+}
+
+int gated_norm_quant_launch(const float* core, const Planes& z, int z_col, const __nv_bfloat16* w, const QuantOut& q,
+                            const int* n_rows, int rows_grid, int HV, int Dv, float eps, cudaStream_t s) {
+  gated_norm_quant_kernel<<<rows_grid, 256, 0, s>>>(core, z, z_col, w, q, n_rows, HV * Dv, Dv, eps);
+  LB_LAUNCH("gated_norm_quant_kernel");
+  return LING_B200_OK;
+}
+
+int attn_prepare_launch(const Planes& qkv, const StepBuffers& sb, const ModelDims& d, int al, const __nv_bfloat16* q_norm,
+                        const __nv_bfloat16* k_norm, __half* q, const KvPoolDev& kv, int rows_grid, cudaStream_t s) {
+  attn_prepare_kernel<<<dim3(rows_grid, d.Hq + 2 * d.Hkv), d.D, d.D * sizeof(float), s>>>(qkv, sb, d, al, q_norm, k_norm, q, kv);
+  LB_LAUNCH("attn_prepare_kernel");
+  return LING_B200_OK;
+}
+
+template <int D, int G>
+static int attention_launch_t(const __half* q, const StepBuffers& sb, const ModelDims& d, int al, const KvPoolDev& kv,
+                              float* part_o, float* part_ml, int chunk_slots, int grid, cudaStream_t s) {
+  static bool attr = false;
+  constexpr size_t smem = attn_smem<D, G>();
+  if (!attr) {
+    LB_CUDA(cudaFuncSetAttribute(attention_kernel<D, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+    attr = true;
+  }
+  attention_kernel<D, G><<<grid, 128, smem, s>>>(q, sb, d, al, kv, part_o, part_ml, chunk_slots);
+  LB_LAUNCH("attention_kernel");
+  return LING_B200_OK;
+}
+
+int attention_launch(const __half* q, const StepBuffers& sb, const ModelDims& d, int al, const KvPoolDev& kv, float* part_o,
+                     float* part_ml, int chunk_slots, int grid, cudaStream_t s) {
+  const int G = d.Hq / d.Hkv;
+  if (d.D == 256 && G == 6) return attention_launch_t<256, 6>(q, sb, d, al, kv, part_o, part_ml, chunk_slots, grid, s);
+  if (d.D == 64 && G == 4) return attention_launch_t<64, 4>(q, sb, d, al, kv, part_o, part_ml, chunk_slots, grid, s);
+  if (d.D == 128 && G == 4) return attention_launch_t<128, 4>(q, sb, d, al, kv, part_o, part_ml, chunk_slots, grid, s);
+  if (d.D == 128 && G == 8) return attention_launch_t<128, 8>(q, sb, d, al, kv, part_o, part_ml, chunk_slots, grid, s);
+  set_error("attention: unsupported (head_dim, q heads per kv head); built: (256,6), (64,4), (128,4), (128,8)");
+  return LING_B200_ERR_UNSUPPORTED;
+}
+
+int attn_combine_launch(const float* part_o, const float* part_ml, const Planes& qkv, const StepBuffers& sb,
+                        const ModelDims& d, const QuantOut& q, int rows_grid, cudaStream_t s) {
+  const int G = d.Hq / d.Hkv;
+  const size_t smem = size_t(d.Hq) * d.D * 4;
+  if (G == 6) {
+    static bool attr = false;
+    if (!attr) {
+      LB_CUDA(cudaFuncSetAttribute(attn_combine_kernel<6>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
+      attr = true;
+    }
+    attn_combine_kernel<6><<<rows_grid, 256, smem, s>>>(part_o, part_ml, qkv, sb, d, q);
+  } else if (G == 4) {
+    attn_combine_kernel<4><<<rows_grid, 256, smem, s>>>(part_o, part_ml, qkv, sb, d, q);
+  } else if (G == 8) {
+    attn_combine_kernel<8><<<rows_grid, 256, smem, s>>>(part_o, part_ml, qkv, sb, d, q);
+  } else {
+    set_error("attention combine: unsupported group size");
+    return LING_B200_ERR_UNSUPPORTED;
+  }
+  LB_LAUNCH("attn_combine_kernel");
+  return LING_B200_OK;
+}
+
+int silu_mul_quant_launch(const Planes& gu, int I, const QuantOut& q, const int* n_rows, int rows_grid, cudaStream_t s) {
+  silu_mul_quant_kernel<<<rows_grid, 256, 0, s>>>(gu, I, q, n_rows);
+  LB_LAUNCH("silu_mul_quant_kernel");
+  return LING_B200_OK;
+}
+
+int argmax_reduce_launch(const float* tile_val, const int* tile_idx, int tiles, int rows_alloc, int* ids, float* vals,
+                         const int* n_rows, int rows_grid, cudaStream_t s) {
+  argmax_reduce_kernel<<<rows_grid, 256, 0, s>>>(tile_val, tile_idx, tiles, rows_alloc, ids, vals, n_rows);
+  LB_LAUNCH("argmax_reduce_kernel");
+  return LING_B200_OK;
+}
+
+int argmax_rows_launch(const float* logits, int rows, int vocab, int* ids, float* vals, cudaStream_t s) {
+  argmax_rows_kernel<<<rows, 256, 0, s>>>(logits, vocab, ids, vals);
+  LB_LAUNCH("argmax_rows_kernel");
+  return LING_B200_OK;
+}
+
+int accept_launch(const StepBuffers& sb, const ModelDims& d, int, cudaStream_t s) {
+  accept_kernel<<<1, 64, 0, s>>>(sb, d.V);
+  LB_LAUNCH("accept_kernel");
+  return LING_B200_OK;
+}
+
+int kv_compact_launch(const StepBuffers& sb, const ModelDims& d, const KvPoolDev& kv, cudaStream_t s) {
+  if (d.n_attn == 0) return LING_B200_OK;
+  kv_compact_kernel<<<dim3(d.n_attn * 2 * d.Hkv, d.max_seqs), 64, 0, s>>>(sb, d, kv);
+  LB_LAUNCH("kv_compact_kernel");
+  return LING_B200_OK;
+}
+
+int conv_commit_launch(const StepBuffers& sb, const ModelDims& d, const float* pre, size_t layer_stride, float* conv_state,
+                       size_t conv_slot_stride, size_t conv_layer_stride, cudaStream_t s) {
+  if (d.n_gdn == 0) return LING_B200_OK;
+  conv_commit_kernel<<<dim3(ceil_div(d.C, 256), d.max_seqs, d.n_gdn), 256, 0, s>>>(sb, d.C, pre, layer_stride, conv_state,
+                                                                                  conv_slot_stride, conv_layer_stride);
+  LB_LAUNCH("conv_commit_kernel");
+  return LING_B200_OK;
+}
+
+int gdn_commit_launch(const StepBuffers& sb, const ModelDims& d, const float* post, const float* g, const float* beta,
+                      size_t post_layer_stride, size_t g_layer_stride, float* state, size_t state_slot_stride,
+                      size_t state_layer_stride, int grid, cudaStream_t s) {
+  if (d.n_gdn == 0) return LING_B200_OK;
+  if (d.Dk == 128)
+    gdn_commit_kernel<128><<<grid, 128, 0, s>>>(post, g, beta, post_layer_stride, g_layer_stride, sb, d.Hk, d.HV, d.Dv, d.n_gdn,
+                                                state, state_slot_stride, state_layer_stride);
+  else if (d.Dk == 64)
+    gdn_commit_kernel<64><<<grid, 128, 0, s>>>(post, g, beta, post_layer_stride, g_layer_stride, sb, d.Hk, d.HV, d.Dv, d.n_gdn,
+                                               state, state_slot_stride, state_layer_stride);
+  else {
+    set_error("DeltaNet key dim must be 64 or 128");
+    return LING_B200_ERR_UNSUPPORTED;
+  }
+  LB_LAUNCH("gdn_commit_kernel");
+  return LING_B200_OK;
+}
+
+int quant_weight_launch(const float* src_f32, uint64_t key, float std_, int from_generator, uint8_t* codes, float* scales,
+                        int row_off, int rows, int K, int N_pad, int K_pad, cudaStream_t s) {
+  const int KB = K_pad / 128;
+  quant_weight_kernel<<<dim3(rows, std::min(ceil_div(KB, 8), 8)), 256, 0, s>>>(src_f32, key, std_, from_generator, codes, scales,
+                                                                               row_off, K, N_pad, K_pad);
+  LB_LAUNCH("quant_weight_kernel");
+  return LING_B200_OK;
+}
+
+int quant_acts_launch(const float* x, int rows, const QuantOut& q, cudaStream_t s) {
+  quant_acts_kernel<<<rows, 256, 0, s>>>(x, q);
+  LB_LAUNCH("quant_acts_kernel");
+  return LING_B200_OK;
+}
+
+int fill_bf16_launch(const float* src_f32, uint64_t key, float std_, float bias, int from_generator, __nv_bfloat16* dst,
+                     size_t n, cudaStream_t s) {
+  const int grid = int(std::min<size_t>((n + 255) / 256, 148 * 16));
+  fill_bf16_kernel<<<std::max(grid, 1), 256, 0, s>>>(src_f32, key, std_, bias, from_generator, dst, n);
+  LB_LAUNCH("fill_bf16_kernel");
+  return LING_B200_OK;
+}
+
+int fill_f32_launch(uint64_t key, float std_, float* dst, size_t n, cudaStream_t s) {
+  const int grid = int(std::min<size_t>((n + 255) / 256, 148 * 16));
+  fill_f32_kernel<<<std::max(grid, 1), 256, 0, s>>>(key, std_, dst, n);
+  LB_LAUNCH("fill_f32_kernel");
+  return LING_B200_OK;
+}
+
+int kv_write_launch(const float* k, const float* v, uint64_t key_k, uint64_t key_v, int from_generator, const ModelDims& d,
+                    int al, int slot, int from, int n, const KvPoolDev& kv, int* err, cudaStream_t s) {
+  if (n <= 0) return LING_B200_OK;
+  kv_write_kernel<<<dim3(n, d.Hkv, 2), d.D, 0, s>>>(k, v, key_k, key_v, from_generator, d, al, slot, from, kv, err);
+  LB_LAUNCH("kv_write_kernel");
+  return LING_B200_OK;
+}
+
+int kv_page_copy_launch(const ModelDims& d, const KvPoolDev& kv, int src, int dst, cudaStream_t s) {
+  if (d.n_attn == 0) return LING_B200_OK;
+  kv_page_copy_kernel<<<d.n_attn * 2 * d.Hkv, 256, 0, s>>>(d, kv, src, dst);
+  LB_LAUNCH("kv_page_copy_kernel");
+  return LING_B200_OK;
+}
+
+int flush_launch(float* buf, size_t n, cudaStream_t s) {
+  flush_kernel<<<148 * 8, 256, 0, s>>>(buf, n);
+  LB_LAUNCH("flush_kernel");
+  return LING_B200_OK;
+}
+
+}  // namespace lb

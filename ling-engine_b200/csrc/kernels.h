@@ -1,0 +1,126 @@
+// Launchers of the verify step's non-GEMM kernels (sm_100a).  Raw device pointers + a stream, like the reference's
+// kernel layer (src/core/kernels.cuh:82-578 in the reference project); shapes come from the structs below.
+#pragma once
+
+#include "../../include/ling_b200.h"
+#include "common.cuh"
+
+namespace lb {
+
+constexpr int kTreeRows = LING_B200_MAX_TREE_ROWS;
+constexpr int kAttnChunk = 512;    // context keys per flash-decoding chunk
+constexpr int kAttnKeyTile = 64;   // keys per shared-memory tile
+constexpr int kAttnRowTile = 64;   // query rows (token rows x q heads of one kv head) per CTA
+
+// One sequence of the staged step as the device sees it.
+struct SeqDev {
+  int slot, pos, rope_delta, n_rows, chain, has_force;
+};
+
+// The step's device-resident description.  Host-written parts arrive with one copy from pinned memory; the packed
+// arrays are built by pack_kernel.
+struct StepBuffers {
+  // host-written (one contiguous block, see Context::stage)
+  int* n_seqs = nullptr;      // [1]
+  SeqDev* seqs = nullptr;     // [max_seqs]
+  int* in_parent = nullptr;   // [max_seqs][32]
+  int* in_token = nullptr;    // [max_seqs][32]
+  int* in_force = nullptr;    // [max_seqs][32]
+  // built on the device
+  int* row0 = nullptr;        // [max_seqs + 1]
+  int* n_rows_total = nullptr;  // [1]
+  int* token = nullptr;       // [rows]
+  int* seq_of = nullptr;      // [rows]
+  int* local = nullptr;       // [rows] row index inside its sequence
+  int* depth = nullptr;       // [rows]
+  int* rope_pos = nullptr;    // [rows]
+  int* cache_slot = nullptr;  // [rows]
+  uint32_t* anc = nullptr;    // [rows]
+  ling_b200_tree_desc* trees = nullptr;  // [max_seqs]
+  // results
+  int* argmax_id = nullptr;   // [rows]
+  float* argmax_val = nullptr;
+  ling_b200_seq_result* results = nullptr;  // [max_seqs]
+  int* err = nullptr;         // [1] device error word
+};
+
+struct ModelDims {
+  int H, I, V, Hq, Hkv, D, rot, Hk, HV, Dk, Dv, C, Vs;
+  float theta, eps;
+  int n_attn, n_gdn;
+  int page_tokens, pool_pages, max_pages;  // max_pages: entries of one slot's page table
+  int rows_alloc;                          // allocated packed rows (multiple of 128)
+  int max_seqs;
+};
+
+// The paged FP8 KV pool: codes [attn layer][K|V][kv head][page][token][D], scales [..][token] (fp32).
+struct KvPoolDev {
+  uint8_t* codes = nullptr;
+  float* scales = nullptr;
+  int* tables = nullptr;  // [sessions][max_pages] page ids, 0 = unmapped
+};
+__host__ __device__ __forceinline__ size_t kv_slot_index(const ModelDims& d, int al, int kv, int h, int page, int tok) {
+  return (((size_t(al) * 2 + kv) * d.Hkv + h) * size_t(d.pool_pages + 1) + page) * d.page_tokens + tok;
+}
+
+// A GEMM output as its consumers see it: `planes` partial sums (the K splits) to be added in order.
+struct Planes {
+  const float* p = nullptr;
+  int n = 1;
+  size_t stride = 0;  // floats between planes
+  int ld = 0;         // floats between rows
+};
+
+// Quantized activation destination.
+struct QuantOut {
+  uint8_t* codes;
+  float* scales;
+  int K, K_pad, rows_alloc;
+};
+
+int pack_launch(const StepBuffers& sb, const ModelDims& d, cudaStream_t s);
+// h (+= planes) -> h; xn = rmsnorm(h) (1 + w); xq = quant(xn).  ids != nullptr: h = embedding rows instead.
+int norm_quant_launch(float* h, const Planes& add, const int* ids, const __nv_bfloat16* embed, const __nv_bfloat16* w,
+                      float* xn, const QuantOut& q, const int* n_rows, int rows_grid, int H, float eps, cudaStream_t s);
+// tap[m][:] = h[m][:] + planes (debug copy of the residual after a layer)
+int tap_launch(const float* h, const Planes& add, float* out, const int* n_rows, int rows_grid, int H, cudaStream_t s);
+int copy_rows_launch(const float* src, float* out, const int* n_rows, int rows_grid, int H, cudaStream_t s);
+int ab_gating_launch(const float* xn, const __nv_bfloat16* wa, const __nv_bfloat16* wb, const __nv_bfloat16* A_log,
+                     const __nv_bfloat16* dt_bias, float* g, float* beta, const int* n_rows, int rows_grid, int H, int HV,
+                     cudaStream_t s);
+int conv_tree_launch(const Planes& in, const StepBuffers& sb, const ModelDims& d, const __nv_bfloat16* convw,
+                     const float* conv_state, size_t conv_slot_stride, float* pre, float* post, cudaStream_t s);
+int gdn_tree_launch(const float* post, const float* g, const float* beta, const StepBuffers& sb, const ModelDims& d,
+                    const float* state, size_t state_slot_stride, float* core, int grid, cudaStream_t s);
+int gated_norm_quant_launch(const float* core, const Planes& z, int z_col, const __nv_bfloat16* w, const QuantOut& q,
+                            const int* n_rows, int rows_grid, int HV, int Dv, float eps, cudaStream_t s);
+int attn_prepare_launch(const Planes& qkv, const StepBuffers& sb, const ModelDims& d, int al, const __nv_bfloat16* q_norm,
+                        const __nv_bfloat16* k_norm, __half* q, const KvPoolDev& kv, int rows_grid, cudaStream_t s);
+int attention_launch(const __half* q, const StepBuffers& sb, const ModelDims& d, int al, const KvPoolDev& kv, float* part_o,
+                     float* part_ml, int chunk_slots, int grid, cudaStream_t s);
+int attn_combine_launch(const float* part_o, const float* part_ml, const Planes& qkv, const StepBuffers& sb,
+                        const ModelDims& d, const QuantOut& q, int rows_grid, cudaStream_t s);
+int silu_mul_quant_launch(const Planes& gu, int I, const QuantOut& q, const int* n_rows, int rows_grid, cudaStream_t s);
+int argmax_reduce_launch(const float* tile_val, const int* tile_idx, int tiles, int rows_alloc, int* ids, float* vals,
+                         const int* n_rows, int rows_grid, cudaStream_t s);
+int argmax_rows_launch(const float* logits, int rows, int vocab, int* ids, float* vals, cudaStream_t s);
+int accept_launch(const StepBuffers& sb, const ModelDims& d, int commit, cudaStream_t s);
+int kv_compact_launch(const StepBuffers& sb, const ModelDims& d, const KvPoolDev& kv, cudaStream_t s);
+int conv_commit_launch(const StepBuffers& sb, const ModelDims& d, const float* pre, size_t layer_stride, float* conv_state,
+                       size_t conv_slot_stride, size_t conv_layer_stride, cudaStream_t s);
+int gdn_commit_launch(const StepBuffers& sb, const ModelDims& d, const float* post, const float* g, const float* beta,
+                      size_t post_layer_stride, size_t g_layer_stride, float* state, size_t state_slot_stride,
+                      size_t state_layer_stride, int grid, cudaStream_t s);
+// weights and synthetic data
+int quant_weight_launch(const float* src_f32, uint64_t key, float std_, int from_generator, uint8_t* codes, float* scales,
+                        int row_off, int rows, int K, int N_pad, int K_pad, cudaStream_t s);
+int quant_acts_launch(const float* x, int rows, const QuantOut& q, cudaStream_t s);
+int fill_bf16_launch(const float* src_f32, uint64_t key, float std_, float bias, int from_generator, __nv_bfloat16* dst,
+                     size_t n, cudaStream_t s);
+int fill_f32_launch(uint64_t key, float std_, float* dst, size_t n, cudaStream_t s);
+int kv_write_launch(const float* k, const float* v, uint64_t key_k, uint64_t key_v, int from_generator, const ModelDims& d,
+                    int al, int slot, int from, int n, const KvPoolDev& kv, int* err, cudaStream_t s);
+int kv_page_copy_launch(const ModelDims& d, const KvPoolDev& kv, int src, int dst, cudaStream_t s);
+int flush_launch(float* buf, size_t n, cudaStream_t s);
+
+}  // namespace lb

@@ -1,0 +1,225 @@
+"""ctypes binding of the CPU oracle (libling_oracle.so) and of the reference's own host code (oracle/_ref).
+
+TEST INFRASTRUCTURE ONLY: imported by tests/, by __graft_entry__.smoke() and by bench.py's CPU-baseline / reference
+legs, as the checker.  The product (ling-engine_b200/) never imports this module.
+"""
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB = os.path.join(HERE, "libling_oracle.so")
+REF = os.path.join(HERE, "_ref", "libling_ref.so")
+
+
+def build(ref=True):
+    """Compiles the oracle, and the reference's host sources where the reference project is mounted."""
+    subprocess.run(["make", "-C", HERE, "-s"], check=True)
+    if ref and os.path.isdir(os.environ.get("LING_REFERENCE", "/root/reference")):
+        subprocess.run(["make", "-C", HERE, "-s", "ref", "REF=" + os.environ.get("LING_REFERENCE", "/root/reference")],
+                       check=False)
+
+
+_lo = None
+_ref = None
+
+
+def lo():
+    global _lo
+    if _lo is None:
+        if not os.path.exists(LIB):
+            build(ref=False)
+        L = C.CDLL(LIB)
+        L.lo_create.restype = C.c_void_p
+        L.lo_e4m3_decode.restype = C.c_float
+        L.lo_e4m3_encode.argtypes = [C.c_float]
+        L.lo_e4m3_encode.restype = C.c_uint8
+        L.lo_bf16_round.argtypes = [C.c_float]
+        L.lo_bf16_round.restype = C.c_float
+        L.lo_weight_stream.restype = C.c_uint64
+        L.lo_synth.argtypes = [C.c_uint64, C.c_uint64, C.c_size_t, C.c_size_t, C.c_float, C.c_float, C.c_int,
+                               C.POINTER(C.c_float)]
+        _lo = L
+    return _lo
+
+
+def ref():
+    """The reference's host code, or None where it was not built (e.g. on a machine without the reference project)."""
+    global _ref
+    if _ref is None and os.path.exists(REF):
+        L = C.CDLL(REF)
+        L.ref_kvpool_create.restype = C.c_void_p
+        _ref = L
+    return _ref
+
+
+def _ip(a):
+    return a.ctypes.data_as(C.POINTER(C.c_int)) if a is not None else None
+
+
+def _fp(a):
+    return a.ctypes.data_as(C.POINTER(C.c_float)) if a is not None else None
+
+
+def _bp(a):
+    return a.ctypes.data_as(C.POINTER(C.c_ubyte)) if a is not None else None
+
+
+def synth(seed, stream, offset, n, std, bias=0.0, bf16=True):
+    out = np.zeros(n, np.float32)
+    lo().lo_synth(seed, stream, offset, n, std, bias, 1 if bf16 else 0, _fp(out))
+    return out
+
+
+def weight_stream(layer, tensor):
+    return lo().lo_weight_stream(layer, tensor)
+
+
+def quant_rows(x, bf16_first=False):
+    x = np.ascontiguousarray(x, np.float32)
+    rows, cols = x.shape
+    codes = np.zeros((rows, cols), np.uint8)
+    scales = np.zeros((rows, (cols + 127) // 128), np.float32)
+    lo().lo_quant_rows(_fp(x), rows, cols, 1 if bf16_first else 0, _bp(codes), _fp(scales))
+    return codes, scales
+
+
+def e4m3_decode_table():
+    return np.array([lo().lo_e4m3_decode(C.c_uint8(c)) for c in range(256)], np.float32)
+
+
+def gemm_fp8(x, w):
+    x = np.ascontiguousarray(x, np.float32)
+    w = np.ascontiguousarray(w, np.float32)
+    y = np.zeros((x.shape[0], w.shape[0]), np.float32)
+    lo().lo_gemm_fp8(_fp(x), _fp(w), _fp(y), x.shape[0], w.shape[0], x.shape[1])
+    return y
+
+
+def argmax(logits):
+    logits = np.ascontiguousarray(logits, np.float32)
+    ids, vals = np.zeros(logits.shape[0], np.int32), np.zeros(logits.shape[0], np.float32)
+    lo().lo_argmax(_fp(logits), logits.shape[0], logits.shape[1], _ip(ids), _fp(vals))
+    return ids, vals
+
+
+class Model:
+    """The oracle's model + sessions; the same method names as the product binding's Context."""
+
+    def __init__(self, cfg, opt, structs):
+        self.cfg, self.opt, self.S = cfg, opt, structs
+        self.h = C.c_void_p(lo().lo_create(C.byref(cfg), C.byref(opt)))
+        self.last_rows = 0
+        self.last_seqs = 0
+
+    def close(self):
+        if self.h:
+            lo().lo_destroy(self.h)
+            self.h = None
+
+    def set_tensor(self, layer, tensor, a):
+        a = np.ascontiguousarray(a, dtype=np.float32)
+        rows, cols = (a.shape if a.ndim == 2 else (1, a.size))
+        assert lo().lo_set_tensor(self.h, layer, tensor, _fp(a), rows, cols) == 0
+
+    def synth_weights(self, seed):
+        assert lo().lo_synth_weights(self.h, C.c_uint64(seed)) == 0
+
+    def synth_weights_layers(self, seed, layers, head_rows):
+        arr = np.ascontiguousarray(layers, np.int32)
+        assert lo().lo_synth_weights_layers(self.h, C.c_uint64(seed), _ip(arr), len(arr), head_rows) == 0
+
+    def get_matrix(self, layer, tensor, rows, cols):
+        codes = np.zeros((rows, cols), np.uint8)
+        scales = np.zeros((rows, (cols + 127) // 128), np.float32)
+        assert lo().lo_get_matrix(self.h, layer, tensor, _bp(codes), _fp(scales), rows, cols) == 0
+        return codes, scales
+
+    def kv_table_set(self, slot, idx, pages):
+        idx = np.ascontiguousarray(idx, np.int32)
+        pages = np.ascontiguousarray(pages, np.int32)
+        assert lo().lo_kv_table_set(self.h, slot, _ip(idx), _ip(pages), len(idx)) == 0
+
+    def kv_write(self, slot, attn_layer, start, k, v):
+        k = np.ascontiguousarray(k, np.float32)
+        v = np.ascontiguousarray(v, np.float32)
+        assert lo().lo_kv_write(self.h, slot, attn_layer, start, k.shape[0], _fp(k), _fp(v)) == 0
+
+    def kv_read(self, slot, attn_layer, start, n, codes=False):
+        hk, d = self.cfg.kv_heads, self.cfg.head_dim
+        if codes:
+            kc, vc = np.zeros((n, hk, d), np.uint8), np.zeros((n, hk, d), np.uint8)
+            ks, vs = np.zeros((n, hk), np.float32), np.zeros((n, hk), np.float32)
+            lo().lo_kv_read(self.h, slot, attn_layer, start, n, None, None, _bp(kc), _fp(ks), _bp(vc), _fp(vs))
+            return kc, ks, vc, vs
+        k, v = np.zeros((n, hk, d), np.float32), np.zeros((n, hk, d), np.float32)
+        lo().lo_kv_read(self.h, slot, attn_layer, start, n, _fp(k), _fp(v), None, None, None, None)
+        return k, v
+
+    def synth_kv(self, slot, n, seed):
+        assert lo().lo_synth_kv(self.h, slot, n, C.c_uint64(seed)) == 0
+
+    def state_write(self, slot, gdn_layer, state=None, conv=None):
+        s = None if state is None else np.ascontiguousarray(state, np.float32)
+        w = None if conv is None else np.ascontiguousarray(conv, np.float32)
+        assert lo().lo_state_write(self.h, slot, gdn_layer, _fp(s), _fp(w)) == 0
+
+    def state_read(self, slot, gdn_layer):
+        c = self.cfg
+        s = np.zeros((c.lin_v_heads, c.lin_k_dim, c.lin_v_dim), np.float32)
+        w = np.zeros((c.conv_channels, 3), np.float32)
+        assert lo().lo_state_read(self.h, slot, gdn_layer, _fp(s), _fp(w)) == 0
+        return s, w
+
+    def synth_state(self, slot, seed):
+        assert lo().lo_synth_state(self.h, slot, C.c_uint64(seed)) == 0
+
+    def state_hash(self, slot):
+        h = C.c_uint64()
+        lo().lo_state_hash(self.h, slot, C.byref(h))
+        return h.value
+
+    def verify_step(self, seqs, flags=1, make_steps=None):
+        arr, keep = make_steps(seqs)
+        res = (self.S.SeqResult * len(seqs))()
+        assert lo().lo_verify_step(self.h, arr, len(seqs), flags, res) == 0
+        self.last_rows = sum(len(s["tokens"]) for s in seqs)
+        self.last_seqs = len(seqs)
+        return list(res)
+
+    def verify_step_sample(self, seqs, layers, head_rows, make_steps=None):
+        arr, keep = make_steps(seqs)
+        la = np.ascontiguousarray(layers, np.int32)
+        assert lo().lo_verify_step_sample(self.h, arr, len(seqs), _ip(la), len(la), head_rows) == 0
+
+    def read_tree_desc(self, seq):
+        t = self.S.TreeDesc()
+        assert lo().lo_read_tree_desc(self.h, seq, C.byref(t)) == 0
+        return t
+
+    def read_packing(self):
+        n, s = self.last_rows, self.last_seqs
+        out = {"row0": np.zeros(s + 1, np.int32)}
+        for k in ("token", "seq_of", "depth", "rope_pos", "cache_slot"):
+            out[k] = np.zeros(n, np.int32)
+        out["anc"] = np.zeros(n, np.uint32)
+        lo().lo_read_packing(self.h, _ip(out["row0"]), _ip(out["token"]), _ip(out["seq_of"]), _ip(out["depth"]),
+                             _ip(out["rope_pos"]), _ip(out["cache_slot"]), out["anc"].ctypes.data_as(C.POINTER(C.c_uint32)))
+        return out
+
+    def read_argmax(self):
+        ids, vals = np.zeros(self.last_rows, np.int32), np.zeros(self.last_rows, np.float32)
+        lo().lo_read_argmax(self.h, _ip(ids), _fp(vals))
+        return ids, vals
+
+    def read_logits(self):
+        out = np.zeros((self.last_rows, self.cfg.vocab), np.float32)
+        lo().lo_read_logits(self.h, _fp(out))
+        return out
+
+    def read_tap(self, layer):
+        out = np.zeros((self.last_rows, self.cfg.hidden), np.float32)
+        assert lo().lo_read_tap(self.h, layer, _fp(out)) == 0
+        return out
