@@ -1,0 +1,446 @@
+#!/usr/bin/env python
+"""Benchmark of the ragged speculative verify step on B200.
+
+    python bench.py --gpus 1 --steps 20 --warmup 5                 # our CUDA path, 27B-class single-stream verify
+    python bench.py --impl reference --steps 2 --warmup 1          # the CPU restatement timed on the host cores
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
+        bench.py --gpus N --steps K --warmup W                     # N sequence-sharded replicas, no collective
+
+A step is one verify pass over one packed batch: pack the trees, 64-layer forward, argmax, greedy tree acceptance,
+KV compaction and DeltaNet commit.  Rank 0 prints ONE JSON line.
+
+  value      packed rows verified per second over all GPUs, inputs resident in HBM (descriptors staged once, the timed
+             region is K graph replays bracketed by CUDA events on the launching stream; max over ranks)
+  e2e        the same through the host-buffer entry point ling_b200_verify_step (descriptor H2D copy, graph replay,
+             result D2H copy inside the timed region)
+  roofline   the weight GEMM (gemm_fp8_tcgen05_kernel): algorithmic bytes = FP8 codes + fp32 block scales of every
+             matrix one step streams, divided by the GEMM launches' device time measured with CUDA events around each
+             launch of one eager replay, against the measured HBM copy bandwidth
+  cpu_baseline the scalar C++ restatement of the same step (oracle/, test infrastructure) timed on this box's host
+             cores on a bounded sample (one DeltaNet layer, one attention layer, a slice of the LM head), scaled by the
+             layer counts; a reported baseline, not a target
+
+Inputs are synthetic (seeded): they stand in for the reference's private replay workload, whose shapes they take.
+Weights are 26.4 GB, far larger than the 126 MB L2, so consecutive steps cannot hit in L2 (no flush between steps).
+"""
+import argparse
+import importlib
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+METRIC = "verify_step_tokens_per_s"
+UNIT = "tokens/s"
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        return float(json.load(open(path))["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+def chain_plus_branch(chain_rows, branch_rows):
+    parent = [-1] + list(range(chain_rows - 1))
+    for b in range(branch_rows):
+        parent.append(0 if b == 0 else chain_rows + b - 1)
+    return parent
+
+
+def workload(name, rank, vocab):
+    """The sequences of one step (per GPU).  Token ids uniform over the vocabulary; accepted lengths imposed so that the
+    compaction and the commit do representative work (6 drafts + the anchor, the reference's ~6.7 tokens per step)."""
+    rng = np.random.default_rng(1000 + rank)
+    if name == "single":      # single-stream 27B-class verify: context 8192, 16-token chain + 8-node lookup branch
+        specs = [(8192, chain_plus_branch(16, 8), 15)]
+    elif name == "ragged4":   # 4 sequences sharing one weight read: trees of 24, 17, 9 and 24 nodes = 74 rows
+        specs = [(2048, chain_plus_branch(16, 8), 15), (9216, chain_plus_branch(12, 5), 11), (31000, chain_plus_branch(9, 0), 8),
+                 (60000, chain_plus_branch(16, 8), 15)]
+    elif name == "toy":
+        specs = [(c, chain_plus_branch(16, 4), 15) for c in (3, 37, 512, 1029)]
+    else:
+        raise SystemExit("unknown workload " + name)
+    seqs = []
+    for s, (ctx, parent, chain) in enumerate(specs):
+        n = len(parent)
+        tokens = rng.integers(0, vocab, n).astype(np.int32)
+        accept = int(rng.integers(1, chain + 2)) if name == "ragged4" else min(7, chain + 1)
+        force = rng.integers(0, vocab, n).astype(np.int32)
+        for r in range(accept - 1):
+            force[r] = tokens[r + 1]
+        force[accept - 1] = (int(tokens[accept]) + 1) % vocab if accept < n else 0
+        seqs.append({"slot": s, "pos": ctx, "tokens": tokens, "parent": np.array(parent, np.int32), "chain": chain,
+                     "force": force, "accept": accept})
+    return seqs
+
+
+class ClockSampler:
+    """nvidia-smi sampled during the timed region (read-only)."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc = index, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "--query-gpu=" + self.Q, "--format=csv,noheader,nounits", "-lms", "100",
+                                          "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out = self.proc.communicate(timeout=5)[0]
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out = self.proc.communicate()[0]
+        sm, mx, reasons = [], [], set()
+        for line in out.splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9 or not f[1].isdigit():
+                continue
+            sm.append(int(f[1])), mx.append(int(f[2]))
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v == "Active":
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def dist_env():
+    return int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+
+
+class Dist:
+    """torch.distributed only as plumbing: a barrier and a max / sum over ranks.  NCCL on GPUs; `backend="gloo"` is the
+    CPU stand-in the multi-rank tests use.  Not used at one GPU: the replicas exchange no data."""
+
+    def __init__(self, world, local_rank, backend="nccl"):
+        self.world, self.backend = world, backend
+        if world > 1:
+            import torch
+            import torch.distributed as dist
+            if backend == "nccl":
+                torch.cuda.set_device(local_rank)
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            dist.init_process_group(backend)
+            self.torch, self.dist = torch, dist
+            self.device = "cuda" if backend == "nccl" else "cpu"
+
+    def barrier(self):
+        if self.world > 1:
+            self.dist.barrier()
+            if self.backend == "nccl":
+                self.torch.cuda.synchronize()
+
+    def _reduce(self, x, op):
+        if self.world == 1:
+            return x
+        t = self.torch.tensor([x], dtype=self.torch.float64, device=self.device)
+        self.dist.all_reduce(t, op=op)
+        return float(t.item())
+
+    def max(self, x):
+        return self._reduce(x, self.dist.ReduceOp.MAX if self.world > 1 else None)
+
+    def sum(self, x):
+        return self._reduce(x, self.dist.ReduceOp.SUM if self.world > 1 else None)
+
+    def close(self):
+        if self.world > 1:
+            self.dist.destroy_process_group()
+
+
+def model_for(lbm, name, layers):
+    if name == "toy":
+        return lbm.toy_config()
+    return lbm.config_27b(layers)
+
+
+def algorithmic_bytes(cfg, seqs, weight_bytes):
+    """Weight bytes one step streams (FP8 codes + fp32 scale per 1x128 + BF16 extras) plus the FP8 KV of the context
+    (codes + one fp32 scale per position and head), and the DeltaNet state traffic reported beside it."""
+    n_attn = len(cfg.attn_layers())
+    n_gdn = cfg.layers - n_attn
+    kv_per_token = n_attn * 2 * cfg.kv_heads * (cfg.head_dim + 4)
+    kv = sum(q["pos"] for q in seqs) * kv_per_token
+    state = n_gdn * cfg.lin_v_heads * cfg.lin_k_dim * cfg.lin_v_dim * 4
+    return {"weights": weight_bytes, "kv": kv, "state_verify_read": state * len(seqs), "state_commit_rw": 2 * state * len(seqs)}
+
+
+class CpuSample:
+    """The oracle on a bounded sample of the same step (one DeltaNet layer, one attention layer, a slice of the LM head),
+    scaled to the whole model by the layer counts and the vocabulary."""
+
+    def __init__(self, lbm, cfg, seqs, threads):
+        from oracle import lo as lom
+        self.lom, self.lbm, self.cfg, self.threads = lom, lbm, cfg, threads
+        lom.lo().lo_set_threads(threads)
+        self.attn, self.gdn = cfg.attn_layers(), cfg.gdn_layers()
+        self.layers = self.gdn[:1] + self.attn[:1]
+        self.head_rows = min(cfg.vocab, 8192)
+        max_ctx = max(q["pos"] for q in seqs) + 64
+        pages = sum((q["pos"] + 32 + 15) // 16 for q in seqs) + 1
+        opt = lbm.Options(len(seqs), max_ctx, 16, pages, len(seqs), sum(len(q["tokens"]) for q in seqs), 0, 0, 0, 0, 0)
+        self.m = lom.Model(cfg, opt, lbm)
+        self.m.synth_weights_layers(0, self.layers, self.head_rows)
+        page = 1
+        self.seqs = []
+        for q in seqs:
+            n = (q["pos"] + 32 + 15) // 16
+            self.m.kv_table_set(q["slot"], np.arange(n, dtype=np.int32), np.arange(page, page + n, dtype=np.int32))
+            page += n
+            if q["pos"] > 0:
+                self.m.synth_kv(q["slot"], q["pos"], 0)
+            self.m.synth_state(q["slot"], 0)
+            self.seqs.append(dict(q, tokens=q["tokens"] % self.head_rows, force=None))
+        self.rows = sum(len(q["tokens"]) for q in seqs)
+
+    def time_once(self):
+        """Returns (tokens/s of the whole step as estimated, estimated seconds per step, measured seconds)."""
+        times = {}
+        for name, ls, hr in (("gdn", self.gdn[:1], 0), ("attn", self.attn[:1], 0), ("head", [], self.head_rows)):
+            t0 = time.perf_counter()
+            self.m.verify_step_sample(self.seqs, ls if ls else [-1], hr, make_steps=self.lbm.make_steps)
+            times[name] = time.perf_counter() - t0
+        est = (len(self.gdn) * times["gdn"] + len(self.attn) * times["attn"] +
+               times["head"] * (self.cfg.vocab / self.head_rows))
+        return self.rows / est, est, sum(times.values())
+
+    def describe(self, measured):
+        return ("oracle step on layers %s + %d of %d LM-head rows, %d rows; scaled by %d DeltaNet + %d attention layers and the "
+                "vocabulary (%.1f s of CPU work measured per sample)" % (self.layers, self.head_rows, self.cfg.vocab, self.rows,
+                                                                         len(self.gdn), len(self.attn), measured))
+
+    def close(self):
+        self.m.close()
+        self.lom.lo().lo_set_threads(1)
+
+
+def cpu_sample(lbm, cfg, seqs, threads):
+    c = CpuSample(lbm, cfg, seqs, threads)
+    v, est, measured = c.time_once()
+    desc = c.describe(measured)
+    c.close()
+    return v, est, desc
+
+
+def run_reference(args, rank, world):
+    """The reference has no CPU (and no sm_100a) implementation of the forward pass; its stand-in is the scalar C++
+    restatement under oracle/ (kind "port"), timed on all host cores.  Every step is the same bounded sample."""
+    if rank != 0:
+        return
+    lbm = importlib.import_module("ling-engine_b200")
+    cfg = model_for(lbm, args.workload, args.layers)
+    seqs = workload(args.workload, 0, cfg.vocab)
+    threads = max(1, min(os.cpu_count() or 1, 64))
+    c = CpuSample(lbm, cfg, seqs, threads)
+    for _ in range(min(args.warmup, 1)):
+        c.time_once()
+    vals = [c.time_once() for _ in range(max(1, min(args.steps, 5)))]
+    v = statistics.median(x[0] for x in vals)
+    est = statistics.median(x[1] for x in vals)
+    sample = c.describe(statistics.median(x[2] for x in vals))
+    c.close()
+    line = {"impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": est * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "fp8_e4m3 (fp32 accumulate)", "data": "synthetic",
+            "config": {"workload": args.workload, "model": "27B-class hybrid, %d layers" % cfg.layers if args.workload != "toy" else "toy",
+                       "rows": c.rows, "parallelism": "host threads", "timed_steps": len(vals)},
+            "cpu_baseline": {"value": v, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+            "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args, rank, local_rank, world):
+    lbm = importlib.import_module("ling-engine_b200")
+    lbm.lib()
+    if lbm.lib().ling_b200_device_count() < 1:
+        raise SystemExit("bench.py: no CUDA device; the product has no CPU path")
+    dist = Dist(world, local_rank)
+    cfg = model_for(lbm, args.workload, args.layers)
+    seqs = workload(args.workload, rank, cfg.vocab)
+    rows = sum(len(q["tokens"]) for q in seqs)
+    page_tokens = 16
+    pages = sum((q["pos"] + 64 + page_tokens - 1) // page_tokens for q in seqs) + 1
+    ctx = lbm.Context(cfg, sessions=len(seqs), max_context=max(q["pos"] for q in seqs) + 64, page_tokens=page_tokens,
+                      pool_pages=pages, max_seqs=len(seqs), max_rows=max(rows, 32), gemm_impl=args.gemm_impl, use_graph=1,
+                      device=local_rank, debug_rows=0, pdl=args.pdl)
+    ctx.synth_weights(0)
+    page = 1
+    for q in seqs:
+        n = (q["pos"] + 64 + page_tokens - 1) // page_tokens
+        ctx.kv_table_set(q["slot"], np.arange(n, dtype=np.int32), np.arange(page, page + n, dtype=np.int32))
+        page += n
+        ctx.synth_kv(q["slot"], q["pos"], rank)
+        ctx.synth_state(q["slot"], rank)
+    flags = lbm.STEP_COMMIT
+    clocks = ClockSampler(local_rank)
+
+    # ---- device-timed: descriptors staged once, K graph replays
+    ctx.stage(seqs, flags)
+    for _ in range(args.warmup if args.quick else max(args.warmup, 3)):
+        ctx.launch()
+    res = ctx.fetch()
+    assert all(r.status == 0 and r.n_path == q["accept"] for r, q in zip(res, seqs)), "acceptance differs from the imposed paths"
+    dist.barrier()
+    clocks.start()
+    ctx.sync()
+    ctx.timer_begin()
+    for _ in range(args.steps):
+        ctx.launch()
+    ms = ctx.timer_end()
+    ctx.sync()
+    dist.barrier()
+    ms = dist.max(ms)
+    launches = ctx.launch_count()
+
+    if args.quick:
+        clk = clocks.stop()
+        if rank == 0:
+            print(json.dumps({"metric": METRIC, "value": dist.sum(rows) / (ms / args.steps * 1e-3), "unit": UNIT,
+                              "ms_per_step": ms / args.steps, "launches_per_step": launches, "quick": True, "clocks": clk}), flush=True)
+        ctx.close()
+        dist.close()
+        return
+
+    # ---- end to end: host buffers in, host buffers out, every step
+    for _ in range(2):
+        ctx.verify_step(seqs, flags)
+    dist.barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        ctx.verify_step(seqs, flags)
+    e2e_s = dist.max(time.perf_counter() - t0)
+    clk = clocks.stop()
+    dist.barrier()
+
+    # ---- the GEMM's own time: one eager replay with CUDA events around every launch
+    ctx.stage(seqs, flags)
+    fam, _ = ctx.profile_step()
+    ctx.fetch()
+    peak, peak_kind = measured_peaks()
+    wbytes = ctx.weight_bytes()
+    alg = algorithmic_bytes(cfg, seqs, wbytes)
+    n_gemm = 4 * cfg.layers + 1
+    gemm_ms = fam[0] + fam[4]  # weight GEMMs + the head GEMM with its fused argmax
+    achieved = wbytes / (gemm_ms * 1e-3) / 1e9 if gemm_ms > 0 else 0.0
+    step_ms = ms / args.steps
+    total_rows = dist.sum(rows)
+    total_accept = dist.sum(sum(q["accept"] for q in seqs))
+    if rank == 0:
+        cpu_v, cpu_est, cpu_desc = (None, None, "skipped (--no-cpu-baseline)")
+        cores = max(1, min(os.cpu_count() or 1, 64))
+        if not args.no_cpu_baseline and world == 1:
+            cpu_v, cpu_est, cpu_desc = cpu_sample(lbm, cfg, seqs, cores)
+        line = {
+            "metric": METRIC, "value": total_rows / (step_ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": step_ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "fp8_e4m3 (fp32 accumulate)", "data": "synthetic",
+            "config": {"workload": args.workload, "model": "27B-class hybrid, %d layers" % cfg.layers if args.workload != "toy" else "toy",
+                       "rows_per_gpu": rows, "sequences_per_gpu": len(seqs), "contexts": [q["pos"] for q in seqs],
+                       "parallelism": "replicas, sequences sharded over %d GPU(s), no collective" % world,
+                       "l2": "inputs larger than L2 (weights %.1f GB per step), no flush" % (wbytes / 1e9),
+                       "pdl": args.pdl, "gemm_impl": "tcgen05" if args.gemm_impl == 0 else "cuda-core cross-check"},
+            "accepted_tokens_per_s": total_accept / (step_ms * 1e-3),
+            "hbm_fraction_weights_plus_kv": (alg["weights"] + alg["kv"]) / (step_ms * 1e-3) / 1e9 / peak,
+            "algorithmic_bytes": alg,
+            "family_ms": {"weight_gemms": fam[0], "attention": fam[1], "deltanet": fam[2], "norm_quant_elementwise": fam[3],
+                          "head_argmax": fam[4], "pack_accept_compact_commit": fam[5]},
+            "e2e": {"value": total_rows * args.steps / e2e_s, "unit": UNIT, "ms_per_step": e2e_s / args.steps * 1e3,
+                    "h2d_bytes_per_step": int(ctx_stage_bytes(lbm, len(seqs))), "d2h_bytes_per_step": int(len(seqs) * __import__("ctypes").sizeof(lbm.SeqResult) + 4)},
+            "gpu_launches": launches * args.steps,
+            "launches_per_step": launches,
+            "roofline": {"bound": "hbm", "kernel": "gemm_fp8_tcgen05_kernel (%d launches per step)" % n_gemm,
+                         "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind,
+                         "traffic": None, "bytes_per_launch_avg": wbytes / n_gemm, "ms_per_launch_avg": gemm_ms / n_gemm},
+            "cpu_baseline": {"value": cpu_v, "unit": UNIT, "cores": cores, "kind": "port", "sample": cpu_desc,
+                             "est_ms_per_step": None if cpu_est is None else cpu_est * 1e3},
+            "clocks": clk,
+        }
+        print(json.dumps(line), flush=True)
+    ctx.close()
+    dist.close()
+
+
+def run_micro_gemm(args):
+    """One weight GEMM alone (synthetic FP8 weights and activations resident in HBM), `iters` launches back to back after
+    three warm-up launches; the small case the profiler captures.  A matrix smaller than L2 is served from L2 here."""
+    lbm = importlib.import_module("ling-engine_b200")
+    M, N, K = (int(x) for x in args.shape.split(","))
+    ms = lbm.gemm_fp8_bench(M, N, K, impl=args.gemm_impl, splits=0, iters=args.iters)
+    peak, kind = measured_peaks()
+    nbytes = N * K + (K // 128) * N * 4
+    print(json.dumps({"micro": "gemm_fp8_tcgen05_kernel", "shape": [M, N, K], "iters": args.iters, "us_per_launch": ms * 1e3,
+                      "weight_bytes": nbytes, "GB_per_s": nbytes / (ms * 1e-3) / 1e9, "frac_of_%s_hbm" % kind: nbytes / (ms * 1e-3) / 1e9 / peak,
+                      "larger_than_l2": nbytes > 126e6}), flush=True)
+
+
+def ctx_stage_bytes(lbm, n_seqs):
+    # the host-written descriptor block: count, per-sequence records, parent / token / forced-argmax rows
+    return 16 + ((n_seqs * 24 + 15) // 16) * 16 + 3 * n_seqs * 32 * 4
+
+
+def shard_sequences(contexts, world):
+    """Sequence sharding for a many-sequence batch: sequences are independent (own KV pages, own state slot, own tree), so
+    each goes whole to one GPU; longest context first onto the GPU with the fewest KV positions so far (KV bytes are what
+    differs between sequences; the weights are replicated).  Returns, per rank, the indices of its sequences."""
+    order = sorted(range(len(contexts)), key=lambda i: (-contexts[i], i))
+    load, shards = [0] * world, [[] for _ in range(world)]
+    for i in order:
+        r = min(range(world), key=lambda k: (load[k], k))
+        shards[r].append(i)
+        load[r] += contexts[i]
+    return [sorted(s) for s in shards]
+
+
+def aggregate(dist, rows, accepted, ms_total, steps):
+    """The whole-job figures from per-rank ones: units summed over ranks, time the maximum over ranks."""
+    ms = dist.max(ms_total)
+    return {"rows_per_s": dist.sum(rows) * steps / (ms * 1e-3), "accepted_per_s": dist.sum(accepted) * steps / (ms * 1e-3),
+            "ms_per_step": ms / steps}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="single", choices=["single", "ragged4", "toy"])
+    ap.add_argument("--layers", type=int, default=64, help="layers of the 27B-class stack (64 = the named configuration)")
+    ap.add_argument("--gemm-impl", type=int, default=0)
+    ap.add_argument("--pdl", type=int, default=0)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--quick", action="store_true", help="device-timed steps only (no end-to-end, per-family or CPU legs): "
+                    "the short run the profiler's launch list is taken from")
+    ap.add_argument("--micro", default="", choices=["", "gemm"], help="time one kernel alone on resident operands")
+    ap.add_argument("--shape", default="24,34816,5120", help="--micro gemm: rows,N,K (default: the gate|up projection)")
+    ap.add_argument("--iters", type=int, default=20)
+    args = ap.parse_args()
+    rank, local_rank, world = dist_env()
+    if args.micro == "gemm":
+        return run_micro_gemm(args)
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    if world != args.gpus and world > 1:
+        raise SystemExit("bench.py: --gpus %d but WORLD_SIZE=%d" % (args.gpus, world))
+    run_ours(args, rank, local_rank, world)
+
+
+if __name__ == "__main__":
+    main()

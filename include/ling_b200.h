@@ -243,11 +243,13 @@ int ling_b200_gemm_fp8_host(int device, int impl, int splits, const float* x, co
 int ling_b200_gemm_fp8_bench(int device, int impl, int splits, int M, int N, int K, int iters, float* ms_per_launch);
 
 /* gdn_conv_tree + gdn_recurrent_tree (kernels.cuh:131-136): one sequence, one layer.  pre [n][C], g and beta
- * [n][HV] (g = log decay), state [HV][Dk][Dv], conv [C][3]; out core [n][HV*Dv] and post [n][C]. */
+ * [n][HV] (g = log decay), state [HV][Dk][Dv], conv [C][3]; out core [n][HV*Dv] and post [n][C] (the conv outputs with
+ * the q and k channels already L2-normalized per head, q also scaled by 1/sqrt(Dk): what the recurrence consumes). */
 int ling_b200_gdn_tree_host(int device, int Hk, int HV, int Dk, int Dv, const ling_b200_tree_desc* td,
                             const float* pre, const float* convw, const float* g, const float* beta,
                             const float* state, const float* conv, float* post, float* core);
-/* Engine::commit (speculate.cpp:516-529) for one layer: rows path[0..n) replayed, state and window written. */
+/* Engine::commit (speculate.cpp:516-529) for one layer: rows path[0..n) replayed, state and window written.
+ * `post` as ling_b200_gdn_tree_host returns it. */
 int ling_b200_gdn_commit_host(int device, int Hk, int HV, int Dk, int Dv, const int* path, int n, int rows,
                               const float* pre, const float* post, const float* g, const float* beta,
                               float* state, float* conv);

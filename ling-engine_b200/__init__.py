@@ -165,7 +165,9 @@ class Context:
     """One engine context on one GPU (ling_b200_create .. ling_b200_destroy)."""
 
     def __init__(self, cfg, sessions=4, max_context=2048, page_tokens=16, pool_pages=512, max_seqs=4, max_rows=128,
-                 gemm_impl=0, use_graph=1, device=0, debug_rows=0, pdl=0):
+                 gemm_impl=None, use_graph=1, device=0, debug_rows=0, pdl=0):
+        if gemm_impl is None:  # a debugging knob: LING_B200_GEMM_IMPL=1 runs the CUDA-core cross-check GEMM instead
+            gemm_impl = int(os.environ.get("LING_B200_GEMM_IMPL", "0"))
         self.cfg = cfg
         self.opt = Options(sessions, max_context, page_tokens, pool_pages, max_seqs, max_rows, gemm_impl, use_graph,
                            device, debug_rows, pdl)

@@ -11,6 +11,7 @@
 #include <cstdint>
 #include <cstdio>
 #include <string>
+#include <utility>
 
 namespace lb {
 
@@ -117,6 +118,34 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
   __syncthreads();
   float t = lane < warps ? red[lane] : 0.f;
   return warp_sum(t);
+}
+
+// ---------------------------------------------------------------------------------------------- dependent launch
+// Programmatic dependent launch (the reference's launch.cuh:1-98 discipline, here for every kernel of the step): a kernel
+// launched with the attribute may start while its predecessor is still running.  Every kernel's first statement is
+// pdl_sync(): it lets its own successor be scheduled (griddepcontrol.launch_dependents) and then waits until the
+// predecessor has completed and its writes are visible (griddepcontrol.wait).  Because every kernel waits, completion is
+// transitive along the stream.  The weight GEMM alone does work before its wait: it prefetches weights, which no kernel
+// of the step writes.  Without the launch attribute both instructions are no-ops.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_sync() {
+  pdl_trigger();
+  pdl_wait();
+}
+void set_pdl(bool on);  // process-wide, like the reference's kernels::set_pdl (src/core/kernels.cuh:82-83)
+bool pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid, cfg.blockDim = block, cfg.dynamicSmemBytes = smem, cfg.stream = stream;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(std::forward<Args>(args))...);
 }
 
 inline int ceil_div(int a, int b) { return (a + b - 1) / b; }

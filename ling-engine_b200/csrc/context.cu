@@ -15,6 +15,9 @@ namespace lb {
 
 thread_local std::string g_error;
 void set_error(const std::string& what) { g_error = what; }
+static bool g_pdl = false;
+void set_pdl(bool on) { g_pdl = on; }
+bool pdl_enabled() { return g_pdl; }
 
 namespace {
 
@@ -72,7 +75,7 @@ struct ling_b200_ctx {
   float* planes[2] = {nullptr, nullptr};
   size_t plane_floats = 0;
   float *pre = nullptr, *post = nullptr, *g = nullptr, *beta = nullptr;  // [n_gdn][rows][..], saved for the commit
-  float *part_o = nullptr, *part_ml = nullptr;
+  float *part_o = nullptr, *part_ml = nullptr, *attn_w = nullptr;
   int chunk_slots = 0;
   HeadEpilogue head_ep;
   float* logits = nullptr;
@@ -162,13 +165,19 @@ int run_gemm(ling_b200_ctx* c, const Fp8Matrix& w, const Fp8Acts& x, int which, 
   g.head = head;
   g.impl = c->opt.gemm_impl;
   g.err_flag = c->sb.err;
-  g.pdl = c->opt.pdl != 0 && c->opt.gemm_impl == 0;
   return gemm_launch(g, c->stream);
 }
 
 // The whole step on the context's stream.  rows = the capacity class (grids and GEMM extents); the kernels read the
 // real extents from device memory.  Order of the forward pass: src/core/engine.cpp:1288-1745 (verify branch).
+int enqueue_step_body(ling_b200_ctx* c, int rows, int flags);
 int enqueue_step(ling_b200_ctx* c, int rows, int flags) {
+  set_pdl(c->opt.pdl != 0);
+  const int rc = enqueue_step_body(c, rows, flags);
+  set_pdl(false);
+  return rc;
+}
+int enqueue_step_body(ling_b200_ctx* c, int rows, int flags) {
   const ModelDims& d = c->d;
   cudaStream_t s = c->stream;
   const int* n_rows = c->sb.n_rows_total;
@@ -203,7 +212,7 @@ int enqueue_step(ling_b200_ctx* c, int rows, int flags) {
       }
       {
         Timed t(c, kFamAttn);
-        LB_TRY(attn_combine_launch(c->part_o, c->part_ml, p0, c->sb, d, c->qout(c->xq_a), rows, s));
+        LB_TRY(attn_combine_launch(c->part_o, c->part_ml, p0, c->sb, d, c->qout(c->xq_a), c->attn_w, rows, s));
       }
       LB_TRY(run_gemm(c, L.o, c->xq_a, 1, rows));
       carry = planes_of(c, 1, L.o);
@@ -222,7 +231,7 @@ int enqueue_step(ling_b200_ctx* c, int rows, int flags) {
       {
         Timed t(c, kFamGdn);
         LB_TRY(conv_tree_launch(p0, c->sb, d, L.conv, c->conv_state + size_t(gl) * c->conv_layer, c->conv_layer * d.n_gdn, pre,
-                                post, s));
+                                post, rows, s));
       }
       {
         Timed t(c, kFamGdn);
@@ -425,7 +434,8 @@ int ling_b200_create(const ling_b200_model_config* cfg, const ling_b200_options*
                   cfg->lin_v_heads % cfg->lin_k_heads == 0 && G >= 1 && opt->sessions >= 1 &&
                   (opt->page_tokens == 16 || opt->page_tokens == 32 || opt->page_tokens == 64) && opt->pool_pages >= 1 &&
                   opt->max_seqs >= 1 && opt->max_seqs <= LING_B200_MAX_SEQS && opt->max_rows >= 1 &&
-                  opt->max_rows <= LING_B200_MAX_ROWS && opt->max_context >= 1 && opt->debug_rows >= 0;
+                  opt->max_rows <= LING_B200_MAX_ROWS && opt->max_context >= 1 && opt->debug_rows >= 0 &&
+                  opt->max_context / kAttnChunk + 2 <= kMaxChunks;
   if (!ok) {
     set_error("create: unsupported model configuration or options");
     return LING_B200_ERR_ARG;
@@ -458,6 +468,8 @@ int ling_b200_create(const ling_b200_model_config* cfg, const ling_b200_options*
     if (c->layers[l].full) c->attn_index[l] = d.n_attn++;
     else c->gdn_index[l] = d.n_gdn++;
   }
+  LB_TRY(gemm_init());
+  LB_TRY(kernels_init());
   LB_CUDA(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
   LB_CUDA(cudaEventCreate(&c->ev0));
   LB_CUDA(cudaEventCreate(&c->ev1));
@@ -522,6 +534,7 @@ int ling_b200_create(const ling_b200_model_config* cfg, const ling_b200_options*
   const size_t rmax = size_t(kTreeRows) * (d.Hq / d.Hkv);
   LB_TRY(c->alloc(&c->part_o, size_t(c->chunk_slots) * rmax * d.D, false));
   LB_TRY(c->alloc(&c->part_ml, size_t(c->chunk_slots) * rmax * 2, false));
+  LB_TRY(c->alloc(&c->attn_w, size_t(d.rows_alloc) * d.Hq * kMaxChunks, false));
   c->head_ep.rows_alloc = d.rows_alloc;
   LB_TRY(c->alloc(&c->head_ep.tile_val, size_t(c->head.N_pad / kTileN) * d.rows_alloc));
   LB_TRY(c->alloc(&c->head_ep.tile_idx, size_t(c->head.N_pad / kTileN) * d.rows_alloc));

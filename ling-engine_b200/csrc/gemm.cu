@@ -121,8 +121,11 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
       : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// Asks the TMA unit to bring one tile of a tensor map into L2 (no shared-memory destination, nothing to wait on).
+__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* map, int x, int y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];" ::"l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y)
+               : "memory");
+}
 
 constexpr int kABytes = kTileN * kBlockK;  // 16 KiB
 __host__ __device__ constexpr int tmem_cols(int nt) { return 2 * nt <= 32 ? 32 : 2 * nt <= 64 ? 64 : 2 * nt <= 128 ? 128 : 256; }
@@ -147,7 +150,8 @@ __global__ void __launch_bounds__(kGemmThreads, ctas_per_sm(NT))
     gemm_fp8_tcgen05_kernel(const __grid_constant__ CUtensorMap mapW, const __grid_constant__ CUtensorMap mapX,
                             const float* __restrict__ ws, const float* __restrict__ xs, float* __restrict__ out, int ld,
                             size_t split_stride, int M, int N, int N_pad, int KB, int splits, int xrows, HeadArgs head,
-                            int* err_flag, int pdl) {
+                            int* err_flag, int pdl, int l2_slabs) {
+  pdl_trigger();  // the next kernel may be scheduled as soon as every CTA of this one has started
   constexpr int STAGES = stages_for(NT);
   constexpr int kBBytes = NT * kBlockK;
   constexpr int kStageBytes = kABytes + kBBytes;
@@ -201,15 +205,19 @@ __global__ void __launch_bounds__(kGemmThreads, ctas_per_sm(NT))
       const int wy = tile_n * kTileN, xy = tile_m * NT;
       int i = 0;
       bool ok = true;
+      if (!pdl) pdl_wait();
       if (pdl) {
-        // Weights do not depend on the previous kernel: fill the pipeline with weight tiles first, wait for the
-        // previous kernel, then fetch the activation tiles of those stages.
+        // Weights do not depend on the previous kernel: fill the pipeline with weight tiles and ask for the next
+        // l2_slabs tiles to be brought into L2, then wait for the previous kernel and fetch the activation tiles of the
+        // filled stages.  While the kernels between two GEMMs run, HBM keeps streaming the next GEMM's weights.
         const int pre = nslab < STAGES ? nslab : STAGES;
         for (int s = 0; s < pre; ++s) {
           mbar_expect_tx(&full[s], kStageBytes);
           tma_load_2d(tiles + s * kStageBytes, &mapW, &full[s], (kb0 + s) * kBlockK, wy, pol_w);
         }
-        grid_dep_wait();
+        const int l2_end = nslab < pre + l2_slabs ? nslab : pre + l2_slabs;
+        for (int s = pre; s < l2_end; ++s) tma_prefetch_l2_2d(&mapW, (kb0 + s) * kBlockK, wy);
+        pdl_wait();
         for (int s = 0; s < pre; ++s)
           tma_load_2d(tiles + s * kStageBytes + kABytes, &mapX, &full[s], (kb0 + s) * kBlockK, xy, pol_x);
         i = pre;
@@ -232,8 +240,7 @@ __global__ void __launch_bounds__(kGemmThreads, ctas_per_sm(NT))
       for (int j = (i > STAGES ? i - STAGES : 0); j < i; ++j) mbar_wait(&full[j % STAGES], (j / STAGES) & 1, nullptr);
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (pdl) grid_dep_wait();
+    // ------------------------------------------------------------------ MMA issuer (touches shared memory and TMEM only)
     if (lane == 0) {
       constexpr uint32_t idesc = umma_idesc_e4m3(NT);
       for (int i = 0; i < nslab; ++i) {
@@ -262,7 +269,7 @@ __global__ void __launch_bounds__(kGemmThreads, ctas_per_sm(NT))
     }
   } else {
     // ------------------------------------------------------------------ epilogue warps (TMEM lane quarter = warp % 4)
-    if (pdl) grid_dep_wait();
+    pdl_wait();  // the activation scales and the output planes belong to the kernels before this one
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
     const int n = tile_n * kTileN + row;
@@ -302,8 +309,8 @@ __global__ void __launch_bounds__(kGemmThreads, ctas_per_sm(NT))
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty[buf]);
     }
-    if (ok) {
-      const bool store = head.tile_val == nullptr || head.store_logits;
+    {
+      const bool store = ok && (head.tile_val == nullptr || head.store_logits);
       if (store && n < N) {
         float* o = out + size_t(split) * split_stride + n;
 #pragma unroll
@@ -312,12 +319,13 @@ __global__ void __launch_bounds__(kGemmThreads, ctas_per_sm(NT))
       }
       if (head.tile_val != nullptr) {
         // Per token row: the best (value, id) among this tile's 128 vocabulary rows; larger value first, equal
-        // values to the lower id, NaN skipped.
+        // values to the lower id, NaN skipped.  All four epilogue warps take part whatever happened before, so the
+        // named barrier below is always complete.
 #pragma unroll
         for (int j = 0; j < NT; ++j) {
           float v = acc[j];
           int id = n;
-          if (!(n < N) || v != v) {
+          if (!ok || !(n < N) || v != v) {
             v = -FLT_MAX;
             id = 0x7fffffff;
           }
@@ -349,7 +357,6 @@ __global__ void __launch_bounds__(kGemmThreads, ctas_per_sm(NT))
       }
     }
   }
-  if (pdl) grid_dep_launch();
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -365,6 +372,7 @@ __global__ void __launch_bounds__(256)
     gemm_fp8_simt_kernel(const uint8_t* __restrict__ w, const float* __restrict__ ws, const uint8_t* __restrict__ x,
                          const float* __restrict__ xs, float* __restrict__ out, int ld, int M, int N, int N_pad,
                          int K_pad, int KB, int xrows, HeadArgs head) {
+  pdl_sync();  // first statement: see common.cuh
   __shared__ float red_val[8][8];
   __shared__ int red_idx[8][8];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -458,13 +466,15 @@ int encode_2d(CUtensorMap* map, void* base, uint64_t inner, uint64_t rows, uint3
 }
 
 template <int NT>
+int init_tc() {
+  LB_CUDA(cudaFuncSetAttribute(gemm_fp8_tcgen05_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               int(gemm_smem_bytes(NT))));
+  return LING_B200_OK;
+}
+
+template <int NT>
 int launch_tc(const GemmCall& c, cudaStream_t stream) {
-  static bool attr_set = false;  // per process; the attribute is per function
   const size_t smem = gemm_smem_bytes(NT);
-  if (!attr_set) {
-    LB_CUDA(cudaFuncSetAttribute(gemm_fp8_tcgen05_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
-    attr_set = true;
-  }
   const Fp8Matrix& W = *c.W;
   const Fp8Acts& X = *c.X;
   HeadArgs h{nullptr, nullptr, 0, 0};
@@ -479,14 +489,27 @@ int launch_tc(const GemmCall& c, cudaStream_t stream) {
   at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   at[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = at;
-  cfg.numAttrs = c.pdl ? 1 : 0;
+  const bool pdl = pdl_enabled();
+  cfg.numAttrs = pdl ? 1 : 0;
+  // L2 prefetch budget of one GEMM: about 40 MB of weight tiles beyond the pipeline stages, spread over its CTAs
+  const int ctas = int(cfg.gridDim.x * cfg.gridDim.y);
+  const int l2_slabs = std::min(64, int((size_t(40) << 20) / (size_t(ctas) * kABytes)));
   LB_CUDA(cudaLaunchKernelEx(&cfg, gemm_fp8_tcgen05_kernel<NT>, W.map, X.map[NT / 32 - 1], (const float*)W.scales,
                              (const float*)X.scales, c.out, c.ld, c.split_stride, c.M, W.N, W.N_pad, W.KB, splits,
-                             X.rows_alloc, h, c.err_flag, c.pdl ? 1 : 0));
+                             X.rows_alloc, h, c.err_flag, pdl ? 1 : 0, pdl && cfg.gridDim.z == 1 ? l2_slabs : 0));
   return LING_B200_OK;
 }
 
 }  // namespace
+
+// Opts the kernels into their dynamic shared memory; called once per device before the first launch (never inside a
+// stream capture).
+int gemm_init() {
+  if (const int r = init_tc<32>()) return r;
+  if (const int r = init_tc<64>()) return r;
+  if (const int r = init_tc<96>()) return r;
+  return init_tc<128>();
+}
 
 int make_weight_map(Fp8Matrix& w) { return encode_2d(&w.map, w.codes, uint64_t(w.K_pad), uint64_t(w.N_pad), kTileN); }
 
@@ -507,7 +530,7 @@ int choose_splits(int N_pad, int KB, int sm_count) {
   int s = (2 * sm_count + tiles / 2) / tiles;
   s = std::min(s, KB / 4);
   s = std::max(s, 1);
-  return std::min(s, 16);
+  return std::min(s, 8);  // consumers add at most 8 partial planes
 }
 
 int gemm_launch(const GemmCall& c, cudaStream_t stream) {
@@ -521,9 +544,9 @@ int gemm_launch(const GemmCall& c, cudaStream_t stream) {
     HeadArgs h{nullptr, nullptr, 0, 0};
     if (c.head) h = HeadArgs{c.head->tile_val, c.head->tile_idx, c.head->rows_alloc, c.head->store_logits ? 1 : 0};
     const dim3 grid(W.N_pad / kTileN, ceil_div(c.M, 8));
-    gemm_fp8_simt_kernel<<<grid, 256, 0, stream>>>(W.codes, W.scales, X.codes, X.scales, c.out, c.ld, c.M, W.N, W.N_pad,
-                                                   W.K_pad, W.KB, X.rows_alloc, h);
-    LB_LAUNCH("gemm_fp8_simt_kernel");
+    LB_CUDA(launch_kernel(gemm_fp8_simt_kernel, grid, dim3(256), size_t(0), stream, (const uint8_t*)W.codes,
+                          (const float*)W.scales, (const uint8_t*)X.codes, (const float*)X.scales, c.out, c.ld, c.M, W.N, W.N_pad,
+                          W.K_pad, W.KB, X.rows_alloc, h));
     return LING_B200_OK;
   }
   switch (token_tile(c.M)) {

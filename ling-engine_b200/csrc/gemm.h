@@ -51,7 +51,6 @@ struct GemmCall {
   const HeadEpilogue* head = nullptr;
   int impl = 0;             // 0 tcgen05, 1 CUDA cores
   int* err_flag = nullptr;
-  bool pdl = false;         // launched with programmatic stream serialization: weights are prefetched before the wait
 };
 
 // Creates the tensor maps (driver entry point fetched at run time; no link against libcuda).
@@ -59,6 +58,7 @@ int make_weight_map(Fp8Matrix& w);
 int make_acts_maps(Fp8Acts& x);
 // The K split used for a shape: enough tiles x splits to cover the SMs about twice, at least 4 K blocks a split.
 int choose_splits(int N_pad, int KB, int sm_count);
+int gemm_init();
 int gemm_launch(const GemmCall& c, cudaStream_t stream);
 // Token rows per MMA (the N of the instruction) used for M rows: 32, 64, 96 or 128.
 int token_tile(int M);

@@ -39,7 +39,8 @@ int check_device(int device) {
     set_error(std::string("this library is built for sm_100a (B200) only; device is ") + prop.name);
     return LING_B200_ERR_UNSUPPORTED;
   }
-  return LING_B200_OK;
+  if (const int r = gemm_init()) return r;
+  return kernels_init();
 }
 #define LB_TRY(call)                      \
   do {                                    \
@@ -177,10 +178,14 @@ struct OneSeq {
     sb.seqs = sc.put(&q, 1);
     sb.row0 = sc.put(row0, 2);
     sb.n_rows_total = sc.put(&n_rows, 1);
+    int seq_of[kTreeRows] = {}, local[kTreeRows];
+    for (int r = 0; r < kTreeRows; ++r) local[r] = r;
+    sb.seq_of = sc.put(seq_of, kTreeRows);
+    sb.local = sc.put(local, kTreeRows);
     sb.trees = td ? sc.put(td, 1) : sc.get<ling_b200_tree_desc>(1);
     sb.results = res ? sc.put(res, 1) : sc.get<ling_b200_seq_result>(1);
     sb.err = sc.get<int>(1);
-    LB_PTR(sb.n_seqs && sb.seqs && sb.row0 && sb.n_rows_total && sb.trees && sb.results && sb.err);
+    LB_PTR(sb.n_seqs && sb.seqs && sb.row0 && sb.n_rows_total && sb.trees && sb.results && sb.err && sb.seq_of && sb.local);
     return LING_B200_OK;
   }
 };
@@ -216,7 +221,7 @@ int ling_b200_gdn_tree_host(int device, int Hk, int HV, int Dk, int Dv, const li
   LB_TRY(fill_bf16_launch(d_w32, 0, 0.f, 0.f, 0, d_w, size_t(C) * 4, 0));
   Planes in;
   in.p = d_in, in.n = 1, in.stride = 0, in.ld = C;
-  LB_TRY(conv_tree_launch(in, o.sb, o.d, d_w, d_conv, 0, d_pre, d_post, 0));
+  LB_TRY(conv_tree_launch(in, o.sb, o.d, d_w, d_conv, 0, d_pre, d_post, n, 0));
   LB_TRY(gdn_tree_launch(d_post, d_g, d_b, o.sb, o.d, d_state, 0, d_core, 148 * 4, 0));
   LB_CUDA(cudaDeviceSynchronize());
   LB_CUDA(cudaMemcpy(post, d_post, size_t(n) * C * 4, cudaMemcpyDeviceToHost));

@@ -12,17 +12,27 @@ namespace {
 
 constexpr int kLeaf = LING_B200_TREE_LEAF, kWrite = LING_B200_TREE_WRITE;
 
+// A GEMM output is up to kMaxPlanes partial sums (its K splits).  The loads are issued together and added in plane order,
+// so a consumer pays one memory latency, not one per plane, and the sum is the same whoever computes it.
 __device__ __forceinline__ float plane_sum(const Planes& a, int m, int c) {
+  float t[kMaxPlanes];
+  const float* base = a.p + size_t(m) * a.ld + c;
+#pragma unroll
+  for (int p = 0; p < kMaxPlanes; ++p) t[p] = p < a.n ? base[size_t(p) * a.stride] : 0.f;
   float v = 0.f;
-  for (int p = 0; p < a.n; ++p) v += a.p[size_t(p) * a.stride + size_t(m) * a.ld + c];
+#pragma unroll
+  for (int p = 0; p < kMaxPlanes; ++p) v += t[p];
   return v;
 }
 __device__ __forceinline__ float4 plane_sum4(const Planes& a, int m, int c) {
+  float4 t[kMaxPlanes];
+  const float* base = a.p + size_t(m) * a.ld + c;
+#pragma unroll
+  for (int p = 0; p < kMaxPlanes; ++p)
+    t[p] = p < a.n ? *reinterpret_cast<const float4*>(base + size_t(p) * a.stride) : make_float4(0.f, 0.f, 0.f, 0.f);
   float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (int p = 0; p < a.n; ++p) {
-    const float4 t = *reinterpret_cast<const float4*>(a.p + size_t(p) * a.stride + size_t(m) * a.ld + c);
-    v.x += t.x, v.y += t.y, v.z += t.z, v.w += t.w;
-  }
+#pragma unroll
+  for (int p = 0; p < kMaxPlanes; ++p) v.x += t[p].x, v.y += t[p].y, v.z += t[p].z, v.w += t[p].w;
   return v;
 }
 
@@ -48,6 +58,7 @@ __device__ __forceinline__ void quant_store4(float4 x, int c, int m, const Quant
 // (rows concatenated, row0 prefix sums; a tree row's RoPE position is pos + depth, its cache slot pos + row index,
 // src/core/kernels.cuh:109-118), and describe_tree (src/core/tree.cpp:81-146) by lane 0 with children as bit masks.
 __global__ void __launch_bounds__(32) pack_kernel(StepBuffers sb, ModelDims d) {
+  pdl_sync();  // first statement: see common.cuh
   __shared__ int par[kTreeRows], dep[kTreeRows];
   __shared__ uint32_t kids[kTreeRows];
   const int s = blockIdx.x, lane = threadIdx.x;
@@ -184,6 +195,7 @@ __global__ void __launch_bounds__(256)
     norm_quant_kernel(float* __restrict__ h, Planes add, const int* __restrict__ ids, const __nv_bfloat16* __restrict__ embed,
                       const __nv_bfloat16* __restrict__ w, float* __restrict__ xn, QuantOut q, const int* __restrict__ n_rows,
                       int H, float eps) {
+  pdl_sync();  // first statement: see common.cuh
   __shared__ float red[32];
   const int m = blockIdx.x;
   if (m >= *n_rows) return;
@@ -227,6 +239,7 @@ __global__ void __launch_bounds__(256)
 
 __global__ void __launch_bounds__(256)
     tap_kernel(const float* __restrict__ h, Planes add, float* __restrict__ out, const int* __restrict__ n_rows, int H) {
+  pdl_sync();  // first statement: see common.cuh
   const int m = blockIdx.x;
   if (m >= *n_rows) return;
   for (int c = threadIdx.x; c < H; c += blockDim.x)
@@ -240,6 +253,7 @@ __global__ void __launch_bounds__(256)
     ab_gating_kernel(const float* __restrict__ xn, const __nv_bfloat16* __restrict__ wa, const __nv_bfloat16* __restrict__ wb,
                      const __nv_bfloat16* __restrict__ A_log, const __nv_bfloat16* __restrict__ dt_bias, float* __restrict__ g,
                      float* __restrict__ beta, const int* __restrict__ n_rows, int H, int HV) {
+  pdl_sync();  // first statement: see common.cuh
   const int hv = blockIdx.x, m = blockIdx.y * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (m >= *n_rows) return;
   const float* x = xn + size_t(m) * H;
@@ -265,92 +279,109 @@ __global__ void __launch_bounds__(256)
 // ---------------------------------------------------------------------------------------------- DeltaNet
 // The verify's conv over each sequence's tree (src/core/kernels.cu:365-383): a row's taps are the raw inputs of its
 // ancestors at depths d-3 .. d-1 (the variant's path) or the session's window before depth 0; the window is left
-// unwritten.  Also materializes the raw inputs (`pre`) from the GEMM's partial sums: the commit replays them.
+// unwritten.  A tree row carries no state from the row before it, so every (row, channel) is independent: one thread
+// each, the taps summed from the GEMM's partial planes.  Also materializes the raw inputs (`pre`, which the commit's
+// window update replays) and L2-normalizes the q and k channels per head (eps 1e-6, q also times 1/sqrt(Dk), the
+// normalization src/core/kernels.cu:420-431 applies inside the recurrence), so `post` holds q^, k^ and v.
 __global__ void __launch_bounds__(256)
-    conv_tree_kernel(Planes in, StepBuffers sb, int C, const __nv_bfloat16* __restrict__ convw,
+    conv_tree_kernel(Planes in, StepBuffers sb, int C, int Hk, int Dk, const __nv_bfloat16* __restrict__ convw,
                      const float* __restrict__ conv_state, size_t slot_stride, float* __restrict__ pre, float* __restrict__ post) {
-  const int s = blockIdx.y, c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (s >= *sb.n_seqs || c >= C) return;
-  const SeqDev q = sb.seqs[s];
-  const int r0 = sb.row0[s];
-  const ling_b200_tree_desc* td = sb.trees + s;
-  const float* win = conv_state + size_t(q.slot) * slot_stride;
-  const float w0 = __bfloat162float(convw[c * 4]), w1 = __bfloat162float(convw[c * 4 + 1]);
-  const float w2 = __bfloat162float(convw[c * 4 + 2]), w3 = __bfloat162float(convw[c * 4 + 3]);
-  for (int t = 0; t < q.n_rows; ++t) {
-    const float xv = plane_sum(in, r0 + t, c);
-    pre[size_t(r0 + t) * C + c] = xv;
+  pdl_sync();  // first statement: see common.cuh
+  __shared__ float wsum[8];
+  const int m = blockIdx.y, c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (m >= *sb.n_rows_total) return;
+  const int s = sb.seq_of[m], t = sb.local[m], r0 = sb.row0[s];
+  float o = 0.f;
+  if (c < C) {
+    const ling_b200_tree_desc* td = sb.trees + s;
     const int dd = td->depth[t];
     const int* path = td->path[td->var[t]];
+    const float* win = conv_state + size_t(sb.seqs[s].slot) * slot_stride;
+    const float xv = plane_sum(in, m, c);
+    pre[size_t(m) * C + c] = xv;
     float tap[3];
 #pragma unroll
     for (int j = 0; j < 3; ++j) {
       const int dj = dd - 3 + j;
-      tap[j] = dj >= 0 ? pre[size_t(r0 + path[dj]) * C + c] : win[c * 3 + 3 + dj];
+      tap[j] = dj >= 0 ? plane_sum(in, r0 + path[dj], c) : win[c * 3 + 3 + dj];
     }
-    post[size_t(r0 + t) * C + c] = silu(w0 * tap[0] + w1 * tap[1] + w2 * tap[2] + w3 * xv);
+    o = silu(__bfloat162float(convw[c * 4]) * tap[0] + __bfloat162float(convw[c * 4 + 1]) * tap[1] +
+             __bfloat162float(convw[c * 4 + 2]) * tap[2] + __bfloat162float(convw[c * 4 + 3]) * xv);
   }
+  const int qk = 2 * Hk * Dk;
+  const float sq = warp_sum(c < qk ? o * o : 0.f);
+  if ((threadIdx.x & 31) == 0) wsum[threadIdx.x >> 5] = sq;
+  __syncthreads();
+  if (c < qk) {
+    const int wph = Dk / 32, first = ((threadIdx.x >> 5) / wph) * wph;  // warps per head; heads are aligned to the block
+    float tot = 0.f;
+    for (int w = 0; w < wph; ++w) tot += wsum[first + w];
+    o *= rsqrtf(tot + 1e-6f) * (c < Hk * Dk ? rsqrtf(float(Dk)) : 1.f);
+  }
+  if (c < C) post[size_t(m) * C + c] = o;
 }
 
-// One token of the gated delta rule for 32 value columns of a head; each lane holds its column of the state
-// (src/core/kernels.cu:402-453): q and k L2-normalized (eps 1e-6), q also scaled by 1/sqrt(Dk); S *= decay;
-// kv = S^T k; d = (v - kv) beta; S += k d^T; o = S^T q.  advance = false is the leaf rule
+// One token of the gated delta rule (src/core/kernels.cu:402-453) for 8 value columns of a head.  A warp is 8 columns x 4
+// quarters of the key dimension: lane = quarter * 8 + column holds S[quarter * DK/4 .. +DK/4][column], so the two
+// dependent dot products are DK/4 long (four interleaved partial sums each) plus two shuffles.  q^ and k^ arrive
+// normalized.  S *= decay; kv = S^T k; d = (v - kv) beta; S += k d^T; o = S^T q.  advance = false is the leaf rule
 // (src/core/attention_body.cuh:575-603): the output from the parent's state, which stays as it was.
 template <int DK>
-__device__ __forceinline__ float delta_token(float (&S)[DK], const float* __restrict__ row, int h, int hv, int Hk, int Dv,
-                                             int v, float gval, float bval, float* qs, float* ks, bool advance) {
-  constexpr int PER = DK / 32;
-  const int lane = threadIdx.x & 31;
-  float qv[PER], kv2[PER];
-  float qn = 0.f, kn = 0.f;
+struct DeltaIn {
+  float k[DK / 4], q[DK / 4];
+  float v, g, beta;
+  __device__ __forceinline__ void load(const float* __restrict__ row, const float* __restrict__ g_row, const float* __restrict__ b_row,
+                                       int h, int hv, int Hk, int Dv, int col, int quarter) {
+    constexpr int KL = DK / 4;
+    const float4* kp = reinterpret_cast<const float4*>(row + Hk * DK + h * DK + quarter * KL);
+    const float4* qp = reinterpret_cast<const float4*>(row + h * DK + quarter * KL);
 #pragma unroll
-  for (int i = 0; i < PER; ++i) {
-    qv[i] = row[h * DK + lane * PER + i];
-    kv2[i] = row[Hk * DK + h * DK + lane * PER + i];
-    qn += qv[i] * qv[i], kn += kv2[i] * kv2[i];
-  }
-  qn = warp_sum(qn), kn = warp_sum(kn);
-  const float qr = rsqrtf(qn + 1e-6f) * rsqrtf(float(DK)), kr = rsqrtf(kn + 1e-6f);
-  __syncwarp();
-#pragma unroll
-  for (int i = 0; i < PER; ++i) qs[lane * PER + i] = qv[i] * qr, ks[lane * PER + i] = kv2[i] * kr;
-  __syncwarp();
-  const float decay = __expf(gval);
-  const float vv = row[2 * Hk * DK + hv * Dv + v];
-  float kv = 0.f, o = 0.f;
-  if (advance) {
-#pragma unroll
-    for (int k = 0; k < DK; ++k) {
-      S[k] *= decay;
-      kv = fmaf(S[k], ks[k], kv);
+    for (int i = 0; i < KL / 4; ++i) {
+      const float4 a = kp[i], b = qp[i];
+      k[4 * i] = a.x, k[4 * i + 1] = a.y, k[4 * i + 2] = a.z, k[4 * i + 3] = a.w;
+      q[4 * i] = b.x, q[4 * i + 1] = b.y, q[4 * i + 2] = b.z, q[4 * i + 3] = b.w;
     }
-    const float dlt = (vv - kv) * bval;
-#pragma unroll
-    for (int k = 0; k < DK; ++k) {
-      S[k] = fmaf(dlt, ks[k], S[k]);
-      o = fmaf(S[k], qs[k], o);
-    }
-  } else {
-#pragma unroll
-    for (int k = 0; k < DK; ++k) kv = fmaf(S[k] * decay, ks[k], kv);
-    const float dlt = (vv - kv) * bval;
-#pragma unroll
-    for (int k = 0; k < DK; ++k) o = fmaf(fmaf(dlt, ks[k], S[k] * decay), qs[k], o);
+    v = row[2 * Hk * DK + hv * Dv + col];
+    g = g_row[hv], beta = b_row[hv];
   }
+};
+template <int DK>
+__device__ __forceinline__ float delta_token(float (&S)[DK / 4], const DeltaIn<DK>& x, bool advance) {
+  constexpr int KL = DK / 4;
+  const float decay = __expf(x.g);
+  float part[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int i = 0; i < KL; ++i) part[i & 3] = fmaf(S[i] * decay, x.k[i], part[i & 3]);
+  float kv = (part[0] + part[1]) + (part[2] + part[3]);
+  kv += __shfl_xor_sync(0xffffffffu, kv, 8);
+  kv += __shfl_xor_sync(0xffffffffu, kv, 16);
+  const float dlt = (x.v - kv) * x.beta;
+  part[0] = part[1] = part[2] = part[3] = 0.f;
+#pragma unroll
+  for (int i = 0; i < KL; ++i) {
+    const float sn = fmaf(dlt, x.k[i], S[i] * decay);
+    part[i & 3] = fmaf(sn, x.q[i], part[i & 3]);
+    if (advance) S[i] = sn;
+  }
+  float o = (part[0] + part[1]) + (part[2] + part[3]);
+  o += __shfl_xor_sync(0xffffffffu, o, 8);
+  o += __shfl_xor_sync(0xffffffffu, o, 16);
   return o;
 }
 
 // The verify's recurrence over every sequence's tree (src/core/kernels.cu:455-477): a work item is (sequence, DeltaNet
-// path, value head, 32 value columns); its warp walks the path's steps from the session's state (never written here)
-// and writes the rows flagged kWrite.  A fixed grid of warps strides over the items.
+// path, value head, 8 value columns); its warp walks the path's steps from the session's state (never written here) and
+// writes the rows flagged kWrite.  The next step's inputs are loaded while the current one is computed.  A fixed grid
+// of warps strides over the items.
 template <int DK>
 __global__ void __launch_bounds__(128)
     gdn_tree_kernel(const float* __restrict__ post, const float* __restrict__ g, const float* __restrict__ beta, StepBuffers sb,
                     int Hk, int HV, int Dv, const float* __restrict__ state, size_t slot_stride, float* __restrict__ core) {
+  pdl_sync();  // first statement: see common.cuh
+  constexpr int KL = DK / 4;
   __shared__ int pbase[LING_B200_MAX_SEQS + 1];
-  __shared__ float qs_all[4][DK], ks_all[4][DK];
   __shared__ int steps_all[4][2 * kTreeRows];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, quarter = lane >> 3, cl = lane & 7;
   const int nseq = *sb.n_seqs;
   if (threadIdx.x == 0) {
     int acc = 0;
@@ -361,74 +392,89 @@ __global__ void __launch_bounds__(128)
     pbase[nseq] = acc;
   }
   __syncthreads();
-  float* qs = qs_all[warp];
-  float* ks = ks_all[warp];
   int* steps = steps_all[warp];
-  const int parts = Dv / 32, C = 2 * Hk * DK + HV * Dv;
-  const int per_path = HV * parts;
+  const int groups = Dv / 8, C = 2 * Hk * DK + HV * Dv;
+  const int per_path = HV * groups;
   const int total = pbase[nseq] * per_path;
   for (int item = blockIdx.x * 4 + warp; item < total; item += gridDim.x * 4) {
-    const int pg = item / per_path, rem = item % per_path, hv = rem / parts, v = (rem % parts) * 32 + lane;
+    const int pg = item / per_path, rem = item % per_path, hv = rem / groups, col = (rem % groups) * 8 + cl;
     int s = 0;
     while (pbase[s + 1] <= pg) ++s;
     const int pth = pg - pbase[s], h = hv / (HV / Hk);
     const ling_b200_tree_desc* td = sb.trees + s;
-    const int r0 = sb.row0[s];
+    const size_t r0 = size_t(sb.row0[s]);
     const float* st = state + size_t(sb.seqs[s].slot) * slot_stride + size_t(hv) * DK * Dv;
-    float S[DK];
+    float S[KL];
 #pragma unroll
-    for (int k = 0; k < DK; ++k) S[k] = st[size_t(k) * Dv + v];
+    for (int i = 0; i < KL; ++i) S[i] = st[size_t(quarter * KL + i) * Dv + col];
     const int len = td->gdn_len[pth];
     __syncwarp();
     for (int i = lane; i < len; i += 32) steps[i] = td->gdn_step[pth][i];
     __syncwarp();
+    DeltaIn<DK> nxt;
+    if (len > 0) {
+      const size_t row = r0 + (steps[0] & 0xff);
+      nxt.load(post + row * C, g + row * HV, beta + row * HV, h, hv, Hk, Dv, col, quarter);
+    }
     for (int i = 0; i < len; ++i) {
-      const int st_i = steps[i], t = st_i & 0xff;
-      const size_t row = size_t(r0 + t);
-      const float o = delta_token<DK>(S, post + row * C, h, hv, Hk, Dv, v, g[row * HV + hv], beta[row * HV + hv], qs, ks,
-                                      (st_i & kLeaf) == 0);
-      if (st_i & kWrite) core[row * HV * Dv + size_t(hv) * Dv + v] = o;
+      const DeltaIn<DK> cur = nxt;
+      const int st_i = steps[i];
+      if (i + 1 < len) {
+        const size_t row = r0 + (steps[i + 1] & 0xff);
+        nxt.load(post + row * C, g + row * HV, beta + row * HV, h, hv, Hk, Dv, col, quarter);
+      }
+      const float o = delta_token<DK>(S, cur, (st_i & kLeaf) == 0);
+      if ((st_i & kWrite) && quarter == 0) core[(r0 + (st_i & 0xff)) * HV * Dv + size_t(hv) * Dv + col] = o;
     }
   }
 }
 
 // Engine::commit (src/core/speculate.cpp:516-529), the recurrence half: the accepted rows path[0..n) replayed from the
-// session's state over their saved conv outputs, the state written back.  Item = (sequence, layer, head, 32 columns).
+// session's state over their saved conv outputs, the state written back.  Item = (sequence, layer, head, 8 columns).
 template <int DK>
 __global__ void __launch_bounds__(128)
     gdn_commit_kernel(const float* __restrict__ post, const float* __restrict__ g, const float* __restrict__ beta,
                       size_t post_layer_stride, size_t g_layer_stride, StepBuffers sb, int Hk, int HV, int Dv, int n_gdn,
                       float* __restrict__ state, size_t slot_stride, size_t layer_stride) {
-  __shared__ float qs_all[4][DK], ks_all[4][DK];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  pdl_sync();  // first statement: see common.cuh
+  constexpr int KL = DK / 4;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, quarter = lane >> 3, cl = lane & 7;
   const int nseq = *sb.n_seqs;
-  float* qs = qs_all[warp];
-  float* ks = ks_all[warp];
-  const int parts = Dv / 32, C = 2 * Hk * DK + HV * Dv;
-  const int per_seq = n_gdn * HV * parts;
+  const int groups = Dv / 8, C = 2 * Hk * DK + HV * Dv;
+  const int per_seq = n_gdn * HV * groups;
   const int total = nseq * per_seq;
   for (int item = blockIdx.x * 4 + warp; item < total; item += gridDim.x * 4) {
     const int s = item / per_seq;
     int rem = item % per_seq;
-    const int gl = rem / (HV * parts);
-    rem %= HV * parts;
-    const int hv = rem / parts, v = (rem % parts) * 32 + lane, h = hv / (HV / Hk);
+    const int gl = rem / (HV * groups);
+    rem %= HV * groups;
+    const int hv = rem / groups, col = (rem % groups) * 8 + cl, h = hv / (HV / Hk);
     const ling_b200_seq_result* R = sb.results + s;
     if (R->status != 0) continue;
-    const int r0 = sb.row0[s], n = R->n_path;
+    const size_t r0 = size_t(sb.row0[s]);
+    const int n = R->n_path;
     float* st = state + size_t(sb.seqs[s].slot) * slot_stride + size_t(gl) * layer_stride + size_t(hv) * DK * Dv;
-    float S[DK];
+    float S[KL];
 #pragma unroll
-    for (int k = 0; k < DK; ++k) S[k] = st[size_t(k) * Dv + v];
+    for (int i = 0; i < KL; ++i) S[i] = st[size_t(quarter * KL + i) * Dv + col];
     const float* P = post + size_t(gl) * post_layer_stride;
     const float* G = g + size_t(gl) * g_layer_stride;
     const float* B = beta + size_t(gl) * g_layer_stride;
+    DeltaIn<DK> nxt;
+    if (n > 0) {
+      const size_t row = r0 + R->path[0];
+      nxt.load(P + row * C, G + row * HV, B + row * HV, h, hv, Hk, Dv, col, quarter);
+    }
     for (int j = 0; j < n; ++j) {
-      const size_t row = size_t(r0 + R->path[j]);
-      delta_token<DK>(S, P + row * C, h, hv, Hk, Dv, v, G[row * HV + hv], B[row * HV + hv], qs, ks, true);
+      const DeltaIn<DK> cur = nxt;
+      if (j + 1 < n) {
+        const size_t row = r0 + R->path[j + 1];
+        nxt.load(P + row * C, G + row * HV, B + row * HV, h, hv, Hk, Dv, col, quarter);
+      }
+      delta_token<DK>(S, cur, true);
     }
 #pragma unroll
-    for (int k = 0; k < DK; ++k) st[size_t(k) * Dv + v] = S[k];
+    for (int i = 0; i < KL; ++i) st[size_t(quarter * KL + i) * Dv + col] = S[i];
   }
 }
 
@@ -436,6 +482,7 @@ __global__ void __launch_bounds__(128)
 __global__ void __launch_bounds__(256)
     conv_commit_kernel(StepBuffers sb, int C, const float* __restrict__ pre, size_t layer_stride, float* __restrict__ conv_state,
                        size_t slot_stride, size_t conv_layer_stride) {
+  pdl_sync();  // first statement: see common.cuh
   const int s = blockIdx.y, gl = blockIdx.z, c = blockIdx.x * blockDim.x + threadIdx.x;
   if (s >= *sb.n_seqs || c >= C) return;
   const ling_b200_seq_result* R = sb.results + s;
@@ -456,6 +503,7 @@ __global__ void __launch_bounds__(256)
 __global__ void __launch_bounds__(256)
     gated_norm_quant_kernel(const float* __restrict__ core, Planes z, int z_col, const __nv_bfloat16* __restrict__ w, QuantOut q,
                             const int* __restrict__ n_rows, int Vs, int Dv, float eps) {
+  pdl_sync();  // first statement: see common.cuh
   const int m = blockIdx.x;
   if (m >= *n_rows) return;
   const int seg = Dv / 4;  // lanes per head
@@ -485,6 +533,7 @@ __global__ void __launch_bounds__(256)
 // silu(gate) * up (src/core/kernels.cu:308-312) from the gate|up GEMM's partial sums, and its FP8 copy.
 __global__ void __launch_bounds__(256)
     silu_mul_quant_kernel(Planes gu, int I, QuantOut q, const int* __restrict__ n_rows) {
+  pdl_sync();  // first statement: see common.cuh
   const int m = blockIdx.x;
   if (m >= *n_rows) return;
   for (int c0 = 0; c0 < q.K_pad; c0 += 1024) {
@@ -516,6 +565,7 @@ __device__ __forceinline__ float block_max(float v, float* red) {
 // Block = one (row, head): heads [0, Hq) are q, then Hkv k heads, then Hkv v heads.
 __global__ void attn_prepare_kernel(Planes qkv, StepBuffers sb, ModelDims d, int al, const __nv_bfloat16* __restrict__ q_norm,
                                     const __nv_bfloat16* __restrict__ k_norm, __half* __restrict__ q, KvPoolDev kv) {
+  pdl_sync();  // first statement: see common.cuh
   extern __shared__ float xs[];
   __shared__ float red[32];
   const int m = blockIdx.x, slot = blockIdx.y, dd = threadIdx.x;
@@ -594,6 +644,7 @@ template <int D, int G>
 __global__ void __launch_bounds__(128, (D > 128 ? 2 : 4))
     attention_kernel(const __half* __restrict__ q, StepBuffers sb, ModelDims d, int al, KvPoolDev kv, float* __restrict__ part_o,
                      float* __restrict__ part_ml, int chunk_slots) {
+  pdl_sync();  // first statement: see common.cuh
   constexpr int QS = D + 8;    // halves per Q row in shared memory
   constexpr int KS = D + 16;   // bytes per K/V row in shared memory
   constexpr int RMAX = kTreeRows * G;
@@ -793,11 +844,13 @@ __global__ void __launch_bounds__(128, (D > 128 ? 2 : 4))
 
 // Merges a row's chunks in order (the reference's attention_combine, src/core/attention_body.cuh:506-525), applies the
 // output gate out * sigmoid(gate) (src/core/kernels.cu:314-318; the gate is the second D values of each q head's
-// projection) and writes the FP8 copy for the o projection.  One block per packed row.
+// projection) and writes the FP8 copy for the o projection.  One block per packed row: first every (q head, chunk)
+// weight exp(m_c - max) / sum, then the weighted sum over chunks with independent loads.
 template <int G>
 __global__ void __launch_bounds__(256)
     attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, Planes qkv, StepBuffers sb,
-                        ModelDims d, QuantOut q) {
+                        ModelDims d, QuantOut q, float* __restrict__ wbuf) {
+  pdl_sync();  // first statement: see common.cuh
   extern __shared__ float rowbuf[];  // [Hq * D]
   constexpr int RMAX = kTreeRows * G;
   const int m = blockIdx.x;
@@ -806,21 +859,34 @@ __global__ void __launch_bounds__(256)
   int cb = 0;
   for (int t = 0; t < s; ++t) cb += (sb.seqs[t].pos + kAttnChunk - 1) / kAttnChunk + 1;
   const int nch = (sb.seqs[s].pos + kAttnChunk - 1) / kAttnChunk + 1;
+  float* wrow = wbuf + size_t(m) * d.Hq * kMaxChunks;  // [Hq][nch] weights of this row
+  // one warp per q head: max over chunks, then the normalized weights
+  for (int hq = threadIdx.x >> 5; hq < d.Hq; hq += blockDim.x >> 5) {
+    const int lane = threadIdx.x & 31, hk = hq / G, r = local * G + hq % G;
+    const size_t base = size_t(cb) * d.Hkv + size_t(hk) * nch;
+    float mx = -INFINITY;
+    for (int c = lane; c < nch; c += 32) mx = fmaxf(mx, part_ml[((base + c) * RMAX + r) * 2]);
+    mx = warp_max(mx);
+    float den = 0.f;
+    for (int c = lane; c < nch; c += 32) {
+      const float mc = part_ml[((base + c) * RMAX + r) * 2];
+      const float wgt = mc == -INFINITY ? 0.f : __expf(mc - mx);  // an empty chunk weighs nothing
+      den += part_ml[((base + c) * RMAX + r) * 2 + 1] * wgt;
+      wrow[hq * kMaxChunks + c] = wgt;
+    }
+    den = warp_sum(den);
+    const float inv = 1.f / (den * kPScale);
+    for (int c = lane; c < nch; c += 32) wrow[hq * kMaxChunks + c] *= inv;
+  }
+  __syncthreads();
   for (int idx = threadIdx.x; idx < d.Hq * D; idx += blockDim.x) {
     const int hq = idx / D, dd = idx % D, hk = hq / G, r = local * G + hq % G;
     const size_t base = size_t(cb) * d.Hkv + size_t(hk) * nch;
-    float mx = -INFINITY;
-    for (int c = 0; c < nch; ++c) mx = fmaxf(mx, part_ml[((base + c) * RMAX + r) * 2]);
-    float num = 0.f, den = 0.f;
-    for (int c = 0; c < nch; ++c) {
-      const float mc = part_ml[((base + c) * RMAX + r) * 2];
-      if (mc == -INFINITY) continue;  // an empty chunk
-      const float wgt = __expf(mc - mx);
-      den += part_ml[((base + c) * RMAX + r) * 2 + 1] * wgt;
-      num += part_o[((base + c) * RMAX + r) * D + dd] * wgt;
-    }
+    float num = 0.f;
+#pragma unroll 4
+    for (int c = 0; c < nch; ++c) num = fmaf(part_o[((base + c) * RMAX + r) * D + dd], wrow[hq * kMaxChunks + c], num);
     const float gate = plane_sum(qkv, m, hq * 2 * D + D + dd);
-    rowbuf[idx] = (num / den) * (1.f / kPScale) * sigmoidf(gate);
+    rowbuf[idx] = num * sigmoidf(gate);
   }
   __syncthreads();
   for (int c0 = 0; c0 < q.K_pad; c0 += 1024) {
@@ -840,6 +906,7 @@ __device__ __forceinline__ bool better(float v, int i, float v2, int i2) { retur
 __global__ void __launch_bounds__(256)
     argmax_reduce_kernel(const float* __restrict__ tile_val, const int* __restrict__ tile_idx, int tiles, int rows_alloc,
                          int* __restrict__ ids, float* __restrict__ vals, const int* __restrict__ n_rows) {
+  pdl_sync();  // first statement: see common.cuh
   __shared__ float sv[256];
   __shared__ int si[256];
   const int m = blockIdx.x;
@@ -864,6 +931,7 @@ __global__ void __launch_bounds__(256)
 // topk_rows with K = 1 over materialized logits (src/core/topk.cu:83-129): one block per row.
 __global__ void __launch_bounds__(256)
     argmax_rows_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ ids, float* __restrict__ vals) {
+  pdl_sync();  // first statement: see common.cuh
   __shared__ float sv[256];
   __shared__ int si[256];
   const int m = blockIdx.x;
@@ -888,6 +956,7 @@ __global__ void __launch_bounds__(256)
 // row's argmax; `next` is the argmax that no child matched.  out = the accepted drafts, then next
 // (src/core/speculate.cpp:1066-1067).
 __global__ void accept_kernel(StepBuffers sb, int vocab) {
+  pdl_sync();  // first statement: see common.cuh
   const int s = blockIdx.x * blockDim.x + threadIdx.x;
   if (s >= *sb.n_seqs) return;
   const SeqDev q = sb.seqs[s];
@@ -932,6 +1001,7 @@ __global__ void accept_kernel(StepBuffers sb, int vocab) {
 // through the page table (source and destination may sit in different pages); codes and the per-position scale.
 // Block = one (sequence, layer, K|V, kv head).
 __global__ void __launch_bounds__(64) kv_compact_kernel(StepBuffers sb, ModelDims d, KvPoolDev kv) {
+  pdl_sync();  // first statement: see common.cuh
   const int s = blockIdx.y;
   if (s >= *sb.n_seqs) return;
   const ling_b200_seq_result* R = sb.results + s;
@@ -959,6 +1029,7 @@ __global__ void __launch_bounds__(64) kv_compact_kernel(StepBuffers sb, ModelDim
 __global__ void __launch_bounds__(256)
     quant_weight_kernel(const float* __restrict__ src, uint64_t key, float std_, int from_generator, uint8_t* __restrict__ codes,
                         float* __restrict__ scales, int row_off, int K, int N_pad, int K_pad) {
+  pdl_sync();  // first statement: see common.cuh
   const int r = blockIdx.x, n = row_off + r, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, KB = K_pad / 128;
   for (int kb = blockIdx.y * 8 + warp; kb < KB; kb += gridDim.y * 8) {
     const int c = kb * 128 + lane * 4;
@@ -983,6 +1054,7 @@ __global__ void __launch_bounds__(256)
 
 // Plain fp32 rows to the activation encoding (codes [rows][K_pad], scales [KB][rows_alloc]).
 __global__ void __launch_bounds__(256) quant_acts_kernel(const float* __restrict__ x, QuantOut q) {
+  pdl_sync();  // first statement: see common.cuh
   const int m = blockIdx.x;
   for (int c0 = 0; c0 < q.K_pad; c0 += 1024) {
     const int c = c0 + threadIdx.x * 4;
@@ -998,10 +1070,12 @@ __global__ void __launch_bounds__(256) quant_acts_kernel(const float* __restrict
 
 __global__ void fill_bf16_kernel(const float* __restrict__ src, uint64_t key, float std_, float bias, int from_generator,
                                  __nv_bfloat16* __restrict__ dst, size_t n) {
+  pdl_sync();  // first statement: see common.cuh
   for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < n; i += size_t(gridDim.x) * blockDim.x)
     dst[i] = __float2bfloat16(from_generator ? synth_z(key, i) * std_ + bias : src[i]);
 }
 __global__ void fill_f32_kernel(uint64_t key, float std_, float* __restrict__ dst, size_t n) {
+  pdl_sync();  // first statement: see common.cuh
   for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < n; i += size_t(gridDim.x) * blockDim.x)
     dst[i] = synth_z(key, i) * std_;
 }
@@ -1010,6 +1084,7 @@ __global__ void fill_f32_kernel(uint64_t key, float std_, float* __restrict__ ds
 // them.  Block = (position, kv head, K|V), one thread per dim.
 __global__ void kv_write_kernel(const float* __restrict__ k, const float* __restrict__ v, uint64_t key_k, uint64_t key_v,
                                 int from_generator, ModelDims d, int al, int slot, int from, KvPoolDev kv, int* err) {
+  pdl_sync();  // first statement: see common.cuh
   __shared__ float red[32];
   const int i = blockIdx.x, h = blockIdx.y, kvi = blockIdx.z, dd = threadIdx.x, pos = from + i;
   const size_t e = (size_t(from_generator ? pos : i) * d.Hkv + h) * d.D + dd;
@@ -1028,6 +1103,7 @@ __global__ void kv_write_kernel(const float* __restrict__ k, const float* __rest
 
 // A whole page copied for copy-on-write (the reference's kv_pages_copy role, src/core/kernels.cu:513-527).
 __global__ void kv_page_copy_kernel(ModelDims d, KvPoolDev kv, int src, int dst) {
+  pdl_sync();  // first statement: see common.cuh
   const int lane_kv = blockIdx.x;  // (layer, K|V, head)
   const size_t a = (size_t(lane_kv) * (d.pool_pages + 1) + src) * d.page_tokens;
   const size_t b = (size_t(lane_kv) * (d.pool_pages + 1) + dst) * d.page_tokens;
@@ -1038,6 +1114,7 @@ __global__ void kv_page_copy_kernel(ModelDims d, KvPoolDev kv, int src, int dst)
 }
 
 __global__ void flush_kernel(float* __restrict__ buf, size_t n) {
+  pdl_sync();  // first statement: see common.cuh
   for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < n; i += size_t(gridDim.x) * blockDim.x) buf[i] = float(i);
 }
 
@@ -1050,27 +1127,27 @@ constexpr size_t attn_smem() {
 
 // ---------------------------------------------------------------------------------------------- launchers
 int pack_launch(const StepBuffers& sb, const ModelDims& d, cudaStream_t s) {
-  pack_kernel<<<d.max_seqs, 32, 0, s>>>(sb, d);
+  LB_CUDA(launch_kernel(pack_kernel, dim3(d.max_seqs), dim3(32), size_t(0), s, sb, d));
   LB_LAUNCH("pack_kernel");
   return LING_B200_OK;
 }
 
 int norm_quant_launch(float* h, const Planes& add, const int* ids, const __nv_bfloat16* embed, const __nv_bfloat16* w,
                       float* xn, const QuantOut& q, const int* n_rows, int rows_grid, int H, float eps, cudaStream_t s) {
-  norm_quant_kernel<<<rows_grid, 256, 0, s>>>(h, add, ids, embed, w, xn, q, n_rows, H, eps);
+  LB_CUDA(launch_kernel(norm_quant_kernel, dim3(rows_grid), dim3(256), size_t(0), s, h, add, ids, embed, w, xn, q, n_rows, H, eps));
   LB_LAUNCH("norm_quant_kernel");
   return LING_B200_OK;
 }
 
 int tap_launch(const float* h, const Planes& add, float* out, const int* n_rows, int rows_grid, int H, cudaStream_t s) {
-  tap_kernel<<<rows_grid, 256, 0, s>>>(h, add, out, n_rows, H);
+  LB_CUDA(launch_kernel(tap_kernel, dim3(rows_grid), dim3(256), size_t(0), s, h, add, out, n_rows, H));
   LB_LAUNCH("tap_kernel");
   return LING_B200_OK;
 }
 
 int copy_rows_launch(const float* src, float* out, const int* n_rows, int rows_grid, int H, cudaStream_t s) {
   Planes none;
-  tap_kernel<<<rows_grid, 256, 0, s>>>(src, none, out, n_rows, H);
+  LB_CUDA(launch_kernel(tap_kernel, dim3(rows_grid), dim3(256), size_t(0), s, src, none, out, n_rows, H));
   LB_LAUNCH("tap_kernel");
   return LING_B200_OK;
 }
@@ -1078,15 +1155,14 @@ int copy_rows_launch(const float* src, float* out, const int* n_rows, int rows_g
 int ab_gating_launch(const float* xn, const __nv_bfloat16* wa, const __nv_bfloat16* wb, const __nv_bfloat16* A_log,
                      const __nv_bfloat16* dt_bias, float* g, float* beta, const int* n_rows, int rows_grid, int H, int HV,
                      cudaStream_t s) {
-  ab_gating_kernel<<<dim3(HV, ceil_div(rows_grid, 8)), 256, 0, s>>>(xn, wa, wb, A_log, dt_bias, g, beta, n_rows, H, HV);
+  LB_CUDA(launch_kernel(ab_gating_kernel, dim3(dim3(HV, ceil_div(rows_grid, 8))), dim3(256), size_t(0), s, xn, wa, wb, A_log, dt_bias, g, beta, n_rows, H, HV));
   LB_LAUNCH("ab_gating_kernel");
   return LING_B200_OK;
 }
 
 int conv_tree_launch(const Planes& in, const StepBuffers& sb, const ModelDims& d, const __nv_bfloat16* convw,
-                     const float* conv_state, size_t conv_slot_stride, float* pre, float* post, cudaStream_t s) {
-  conv_tree_kernel<<<dim3(ceil_div(d.C, 256), d.max_seqs), 256, 0, s>>>(in, sb, d.C, convw, conv_state, conv_slot_stride, pre,
-                                                                        post);
+                     const float* conv_state, size_t conv_slot_stride, float* pre, float* post, int rows_grid, cudaStream_t s) {
+  LB_CUDA(launch_kernel(conv_tree_kernel, dim3(dim3(ceil_div(d.C, 256), rows_grid)), dim3(256), size_t(0), s, in, sb, d.C, d.Hk, d.Dk, convw, conv_state, conv_slot_stride, pre, post));
   LB_LAUNCH("conv_tree_kernel");
   return LING_B200_OK;
 }
@@ -1094,9 +1170,9 @@ int conv_tree_launch(const Planes& in, const StepBuffers& sb, const ModelDims& d
 int gdn_tree_launch(const float* post, const float* g, const float* beta, const StepBuffers& sb, const ModelDims& d,
                     const float* state, size_t state_slot_stride, float* core, int grid, cudaStream_t s) {
   if (d.Dk == 128)
-    gdn_tree_kernel<128><<<grid, 128, 0, s>>>(post, g, beta, sb, d.Hk, d.HV, d.Dv, state, state_slot_stride, core);
+    LB_CUDA(launch_kernel(gdn_tree_kernel<128>, dim3(grid), dim3(128), size_t(0), s, post, g, beta, sb, d.Hk, d.HV, d.Dv, state, state_slot_stride, core));
   else if (d.Dk == 64)
-    gdn_tree_kernel<64><<<grid, 128, 0, s>>>(post, g, beta, sb, d.Hk, d.HV, d.Dv, state, state_slot_stride, core);
+    LB_CUDA(launch_kernel(gdn_tree_kernel<64>, dim3(grid), dim3(128), size_t(0), s, post, g, beta, sb, d.Hk, d.HV, d.Dv, state, state_slot_stride, core));
   else {
     set_error("DeltaNet key dim must be 64 or 128");
     return LING_B200_ERR_UNSUPPORTED;
@@ -1107,14 +1183,14 @@ int gdn_tree_launch(const float* post, const float* g, const float* beta, const 
 
 int gated_norm_quant_launch(const float* core, const Planes& z, int z_col, const __nv_bfloat16* w, const QuantOut& q,
                             const int* n_rows, int rows_grid, int HV, int Dv, float eps, cudaStream_t s) {
-  gated_norm_quant_kernel<<<rows_grid, 256, 0, s>>>(core, z, z_col, w, q, n_rows, HV * Dv, Dv, eps);
+  LB_CUDA(launch_kernel(gated_norm_quant_kernel, dim3(rows_grid), dim3(256), size_t(0), s, core, z, z_col, w, q, n_rows, HV * Dv, Dv, eps));
   LB_LAUNCH("gated_norm_quant_kernel");
   return LING_B200_OK;
 }
 
 int attn_prepare_launch(const Planes& qkv, const StepBuffers& sb, const ModelDims& d, int al, const __nv_bfloat16* q_norm,
                         const __nv_bfloat16* k_norm, __half* q, const KvPoolDev& kv, int rows_grid, cudaStream_t s) {
-  attn_prepare_kernel<<<dim3(rows_grid, d.Hq + 2 * d.Hkv), d.D, d.D * sizeof(float), s>>>(qkv, sb, d, al, q_norm, k_norm, q, kv);
+  LB_CUDA(launch_kernel(attn_prepare_kernel, dim3(dim3(rows_grid, d.Hq + 2 * d.Hkv)), dim3(d.D), size_t(d.D * sizeof(float)), s, qkv, sb, d, al, q_norm, k_norm, q, kv));
   LB_LAUNCH("attn_prepare_kernel");
   return LING_B200_OK;
 }
@@ -1122,14 +1198,18 @@ int attn_prepare_launch(const Planes& qkv, const StepBuffers& sb, const ModelDim
 template <int D, int G>
 static int attention_launch_t(const __half* q, const StepBuffers& sb, const ModelDims& d, int al, const KvPoolDev& kv,
                               float* part_o, float* part_ml, int chunk_slots, int grid, cudaStream_t s) {
-  static bool attr = false;
   constexpr size_t smem = attn_smem<D, G>();
-  if (!attr) {
-    LB_CUDA(cudaFuncSetAttribute(attention_kernel<D, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
-    attr = true;
-  }
-  attention_kernel<D, G><<<grid, 128, smem, s>>>(q, sb, d, al, kv, part_o, part_ml, chunk_slots);
+  LB_CUDA(launch_kernel(attention_kernel<D, G>, dim3(grid), dim3(128), size_t(smem), s, q, sb, d, al, kv, part_o, part_ml, chunk_slots));
   LB_LAUNCH("attention_kernel");
+  return LING_B200_OK;
+}
+
+// Opts the attention kernels into their dynamic shared memory (once per device, never inside a stream capture).
+int kernels_init() {
+  LB_CUDA(cudaFuncSetAttribute(attention_kernel<256, 6>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(attn_smem<256, 6>())));
+  LB_CUDA(cudaFuncSetAttribute(attention_kernel<64, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(attn_smem<64, 4>())));
+  LB_CUDA(cudaFuncSetAttribute(attention_kernel<128, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(attn_smem<128, 4>())));
+  LB_CUDA(cudaFuncSetAttribute(attention_kernel<128, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(attn_smem<128, 8>())));
   return LING_B200_OK;
 }
 
@@ -1145,20 +1225,19 @@ int attention_launch(const __half* q, const StepBuffers& sb, const ModelDims& d,
 }
 
 int attn_combine_launch(const float* part_o, const float* part_ml, const Planes& qkv, const StepBuffers& sb,
-                        const ModelDims& d, const QuantOut& q, int rows_grid, cudaStream_t s) {
+                        const ModelDims& d, const QuantOut& q, float* wbuf, int rows_grid, cudaStream_t s) {
   const int G = d.Hq / d.Hkv;
   const size_t smem = size_t(d.Hq) * d.D * 4;
+  if (smem > 48 * 1024) {
+    set_error("attention combine: heads x head_dim too large for one row buffer");
+    return LING_B200_ERR_UNSUPPORTED;
+  }
   if (G == 6) {
-    static bool attr = false;
-    if (!attr) {
-      LB_CUDA(cudaFuncSetAttribute(attn_combine_kernel<6>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
-      attr = true;
-    }
-    attn_combine_kernel<6><<<rows_grid, 256, smem, s>>>(part_o, part_ml, qkv, sb, d, q);
+    LB_CUDA(launch_kernel(attn_combine_kernel<6>, dim3(rows_grid), dim3(256), size_t(smem), s, part_o, part_ml, qkv, sb, d, q, wbuf));
   } else if (G == 4) {
-    attn_combine_kernel<4><<<rows_grid, 256, smem, s>>>(part_o, part_ml, qkv, sb, d, q);
+    LB_CUDA(launch_kernel(attn_combine_kernel<4>, dim3(rows_grid), dim3(256), size_t(smem), s, part_o, part_ml, qkv, sb, d, q, wbuf));
   } else if (G == 8) {
-    attn_combine_kernel<8><<<rows_grid, 256, smem, s>>>(part_o, part_ml, qkv, sb, d, q);
+    LB_CUDA(launch_kernel(attn_combine_kernel<8>, dim3(rows_grid), dim3(256), size_t(smem), s, part_o, part_ml, qkv, sb, d, q, wbuf));
   } else {
     set_error("attention combine: unsupported group size");
     return LING_B200_ERR_UNSUPPORTED;
@@ -1168,33 +1247,33 @@ int attn_combine_launch(const float* part_o, const float* part_ml, const Planes&
 }
 
 int silu_mul_quant_launch(const Planes& gu, int I, const QuantOut& q, const int* n_rows, int rows_grid, cudaStream_t s) {
-  silu_mul_quant_kernel<<<rows_grid, 256, 0, s>>>(gu, I, q, n_rows);
+  LB_CUDA(launch_kernel(silu_mul_quant_kernel, dim3(rows_grid), dim3(256), size_t(0), s, gu, I, q, n_rows));
   LB_LAUNCH("silu_mul_quant_kernel");
   return LING_B200_OK;
 }
 
 int argmax_reduce_launch(const float* tile_val, const int* tile_idx, int tiles, int rows_alloc, int* ids, float* vals,
                          const int* n_rows, int rows_grid, cudaStream_t s) {
-  argmax_reduce_kernel<<<rows_grid, 256, 0, s>>>(tile_val, tile_idx, tiles, rows_alloc, ids, vals, n_rows);
+  LB_CUDA(launch_kernel(argmax_reduce_kernel, dim3(rows_grid), dim3(256), size_t(0), s, tile_val, tile_idx, tiles, rows_alloc, ids, vals, n_rows));
   LB_LAUNCH("argmax_reduce_kernel");
   return LING_B200_OK;
 }
 
 int argmax_rows_launch(const float* logits, int rows, int vocab, int* ids, float* vals, cudaStream_t s) {
-  argmax_rows_kernel<<<rows, 256, 0, s>>>(logits, vocab, ids, vals);
+  LB_CUDA(launch_kernel(argmax_rows_kernel, dim3(rows), dim3(256), size_t(0), s, logits, vocab, ids, vals));
   LB_LAUNCH("argmax_rows_kernel");
   return LING_B200_OK;
 }
 
 int accept_launch(const StepBuffers& sb, const ModelDims& d, int, cudaStream_t s) {
-  accept_kernel<<<1, 64, 0, s>>>(sb, d.V);
+  LB_CUDA(launch_kernel(accept_kernel, dim3(1), dim3(64), size_t(0), s, sb, d.V));
   LB_LAUNCH("accept_kernel");
   return LING_B200_OK;
 }
 
 int kv_compact_launch(const StepBuffers& sb, const ModelDims& d, const KvPoolDev& kv, cudaStream_t s) {
   if (d.n_attn == 0) return LING_B200_OK;
-  kv_compact_kernel<<<dim3(d.n_attn * 2 * d.Hkv, d.max_seqs), 64, 0, s>>>(sb, d, kv);
+  LB_CUDA(launch_kernel(kv_compact_kernel, dim3(dim3(d.n_attn * 2 * d.Hkv, d.max_seqs)), dim3(64), size_t(0), s, sb, d, kv));
   LB_LAUNCH("kv_compact_kernel");
   return LING_B200_OK;
 }
@@ -1202,8 +1281,7 @@ int kv_compact_launch(const StepBuffers& sb, const ModelDims& d, const KvPoolDev
 int conv_commit_launch(const StepBuffers& sb, const ModelDims& d, const float* pre, size_t layer_stride, float* conv_state,
                        size_t conv_slot_stride, size_t conv_layer_stride, cudaStream_t s) {
   if (d.n_gdn == 0) return LING_B200_OK;
-  conv_commit_kernel<<<dim3(ceil_div(d.C, 256), d.max_seqs, d.n_gdn), 256, 0, s>>>(sb, d.C, pre, layer_stride, conv_state,
-                                                                                  conv_slot_stride, conv_layer_stride);
+  LB_CUDA(launch_kernel(conv_commit_kernel, dim3(dim3(ceil_div(d.C, 256), d.max_seqs, d.n_gdn)), dim3(256), size_t(0), s, sb, d.C, pre, layer_stride, conv_state, conv_slot_stride, conv_layer_stride));
   LB_LAUNCH("conv_commit_kernel");
   return LING_B200_OK;
 }
@@ -1213,11 +1291,9 @@ int gdn_commit_launch(const StepBuffers& sb, const ModelDims& d, const float* po
                       size_t state_layer_stride, int grid, cudaStream_t s) {
   if (d.n_gdn == 0) return LING_B200_OK;
   if (d.Dk == 128)
-    gdn_commit_kernel<128><<<grid, 128, 0, s>>>(post, g, beta, post_layer_stride, g_layer_stride, sb, d.Hk, d.HV, d.Dv, d.n_gdn,
-                                                state, state_slot_stride, state_layer_stride);
+    LB_CUDA(launch_kernel(gdn_commit_kernel<128>, dim3(grid), dim3(128), size_t(0), s, post, g, beta, post_layer_stride, g_layer_stride, sb, d.Hk, d.HV, d.Dv, d.n_gdn, state, state_slot_stride, state_layer_stride));
   else if (d.Dk == 64)
-    gdn_commit_kernel<64><<<grid, 128, 0, s>>>(post, g, beta, post_layer_stride, g_layer_stride, sb, d.Hk, d.HV, d.Dv, d.n_gdn,
-                                               state, state_slot_stride, state_layer_stride);
+    LB_CUDA(launch_kernel(gdn_commit_kernel<64>, dim3(grid), dim3(128), size_t(0), s, post, g, beta, post_layer_stride, g_layer_stride, sb, d.Hk, d.HV, d.Dv, d.n_gdn, state, state_slot_stride, state_layer_stride));
   else {
     set_error("DeltaNet key dim must be 64 or 128");
     return LING_B200_ERR_UNSUPPORTED;
@@ -1229,14 +1305,13 @@ int gdn_commit_launch(const StepBuffers& sb, const ModelDims& d, const float* po
 int quant_weight_launch(const float* src_f32, uint64_t key, float std_, int from_generator, uint8_t* codes, float* scales,
                         int row_off, int rows, int K, int N_pad, int K_pad, cudaStream_t s) {
   const int KB = K_pad / 128;
-  quant_weight_kernel<<<dim3(rows, std::min(ceil_div(KB, 8), 8)), 256, 0, s>>>(src_f32, key, std_, from_generator, codes, scales,
-                                                                               row_off, K, N_pad, K_pad);
+  LB_CUDA(launch_kernel(quant_weight_kernel, dim3(dim3(rows, std::min(ceil_div(KB, 8), 8))), dim3(256), size_t(0), s, src_f32, key, std_, from_generator, codes, scales, row_off, K, N_pad, K_pad));
   LB_LAUNCH("quant_weight_kernel");
   return LING_B200_OK;
 }
 
 int quant_acts_launch(const float* x, int rows, const QuantOut& q, cudaStream_t s) {
-  quant_acts_kernel<<<rows, 256, 0, s>>>(x, q);
+  LB_CUDA(launch_kernel(quant_acts_kernel, dim3(rows), dim3(256), size_t(0), s, x, q));
   LB_LAUNCH("quant_acts_kernel");
   return LING_B200_OK;
 }
@@ -1244,14 +1319,14 @@ int quant_acts_launch(const float* x, int rows, const QuantOut& q, cudaStream_t 
 int fill_bf16_launch(const float* src_f32, uint64_t key, float std_, float bias, int from_generator, __nv_bfloat16* dst,
                      size_t n, cudaStream_t s) {
   const int grid = int(std::min<size_t>((n + 255) / 256, 148 * 16));
-  fill_bf16_kernel<<<std::max(grid, 1), 256, 0, s>>>(src_f32, key, std_, bias, from_generator, dst, n);
+  LB_CUDA(launch_kernel(fill_bf16_kernel, dim3(std::max(grid, 1)), dim3(256), size_t(0), s, src_f32, key, std_, bias, from_generator, dst, n));
   LB_LAUNCH("fill_bf16_kernel");
   return LING_B200_OK;
 }
 
 int fill_f32_launch(uint64_t key, float std_, float* dst, size_t n, cudaStream_t s) {
   const int grid = int(std::min<size_t>((n + 255) / 256, 148 * 16));
-  fill_f32_kernel<<<std::max(grid, 1), 256, 0, s>>>(key, std_, dst, n);
+  LB_CUDA(launch_kernel(fill_f32_kernel, dim3(std::max(grid, 1)), dim3(256), size_t(0), s, key, std_, dst, n));
   LB_LAUNCH("fill_f32_kernel");
   return LING_B200_OK;
 }
@@ -1259,20 +1334,20 @@ int fill_f32_launch(uint64_t key, float std_, float* dst, size_t n, cudaStream_t
 int kv_write_launch(const float* k, const float* v, uint64_t key_k, uint64_t key_v, int from_generator, const ModelDims& d,
                     int al, int slot, int from, int n, const KvPoolDev& kv, int* err, cudaStream_t s) {
   if (n <= 0) return LING_B200_OK;
-  kv_write_kernel<<<dim3(n, d.Hkv, 2), d.D, 0, s>>>(k, v, key_k, key_v, from_generator, d, al, slot, from, kv, err);
+  LB_CUDA(launch_kernel(kv_write_kernel, dim3(dim3(n, d.Hkv, 2)), dim3(d.D), size_t(0), s, k, v, key_k, key_v, from_generator, d, al, slot, from, kv, err));
   LB_LAUNCH("kv_write_kernel");
   return LING_B200_OK;
 }
 
 int kv_page_copy_launch(const ModelDims& d, const KvPoolDev& kv, int src, int dst, cudaStream_t s) {
   if (d.n_attn == 0) return LING_B200_OK;
-  kv_page_copy_kernel<<<d.n_attn * 2 * d.Hkv, 256, 0, s>>>(d, kv, src, dst);
+  LB_CUDA(launch_kernel(kv_page_copy_kernel, dim3(d.n_attn * 2 * d.Hkv), dim3(256), size_t(0), s, d, kv, src, dst));
   LB_LAUNCH("kv_page_copy_kernel");
   return LING_B200_OK;
 }
 
 int flush_launch(float* buf, size_t n, cudaStream_t s) {
-  flush_kernel<<<148 * 8, 256, 0, s>>>(buf, n);
+  LB_CUDA(launch_kernel(flush_kernel, dim3(148 * 8), dim3(256), size_t(0), s, buf, n));
   LB_LAUNCH("flush_kernel");
   return LING_B200_OK;
 }

@@ -11,6 +11,8 @@ constexpr int kTreeRows = LING_B200_MAX_TREE_ROWS;
 constexpr int kAttnChunk = 512;    // context keys per flash-decoding chunk
 constexpr int kAttnKeyTile = 64;   // keys per shared-memory tile
 constexpr int kAttnRowTile = 64;   // query rows (token rows x q heads of one kv head) per CTA
+constexpr int kMaxChunks = 320;    // chunks of one sequence: 131,072 positions / kAttnChunk + the partial and in-flight chunks
+constexpr int kMaxPlanes = 8;      // most K splits of one GEMM (partial-sum planes a consumer adds)
 
 // One sequence of the staged step as the device sees it.
 struct SeqDev {
@@ -78,6 +80,7 @@ struct QuantOut {
   int K, K_pad, rows_alloc;
 };
 
+int kernels_init();
 int pack_launch(const StepBuffers& sb, const ModelDims& d, cudaStream_t s);
 // h (+= planes) -> h; xn = rmsnorm(h) (1 + w); xq = quant(xn).  ids != nullptr: h = embedding rows instead.
 int norm_quant_launch(float* h, const Planes& add, const int* ids, const __nv_bfloat16* embed, const __nv_bfloat16* w,
@@ -89,7 +92,7 @@ int ab_gating_launch(const float* xn, const __nv_bfloat16* wa, const __nv_bfloat
                      const __nv_bfloat16* dt_bias, float* g, float* beta, const int* n_rows, int rows_grid, int H, int HV,
                      cudaStream_t s);
 int conv_tree_launch(const Planes& in, const StepBuffers& sb, const ModelDims& d, const __nv_bfloat16* convw,
-                     const float* conv_state, size_t conv_slot_stride, float* pre, float* post, cudaStream_t s);
+                     const float* conv_state, size_t conv_slot_stride, float* pre, float* post, int rows_grid, cudaStream_t s);
 int gdn_tree_launch(const float* post, const float* g, const float* beta, const StepBuffers& sb, const ModelDims& d,
                     const float* state, size_t state_slot_stride, float* core, int grid, cudaStream_t s);
 int gated_norm_quant_launch(const float* core, const Planes& z, int z_col, const __nv_bfloat16* w, const QuantOut& q,
@@ -99,7 +102,7 @@ int attn_prepare_launch(const Planes& qkv, const StepBuffers& sb, const ModelDim
 int attention_launch(const __half* q, const StepBuffers& sb, const ModelDims& d, int al, const KvPoolDev& kv, float* part_o,
                      float* part_ml, int chunk_slots, int grid, cudaStream_t s);
 int attn_combine_launch(const float* part_o, const float* part_ml, const Planes& qkv, const StepBuffers& sb,
-                        const ModelDims& d, const QuantOut& q, int rows_grid, cudaStream_t s);
+                        const ModelDims& d, const QuantOut& q, float* wbuf, int rows_grid, cudaStream_t s);
 int silu_mul_quant_launch(const Planes& gu, int I, const QuantOut& q, const int* n_rows, int rows_grid, cudaStream_t s);
 int argmax_reduce_launch(const float* tile_val, const int* tile_idx, int tiles, int rows_alloc, int* ids, float* vals,
                          const int* n_rows, int rows_grid, cudaStream_t s);

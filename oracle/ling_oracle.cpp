@@ -88,7 +88,8 @@ float bf16r(float x) {  // round to nearest even to BF16 (__float2bfloat16)
 // One fp32 scale per row per 128 columns; the last block may be short.
 void quant_rows(const float* x, int rows, int cols, bool bf16_first, uint8_t* codes, float* scales) {
   const int KB = (cols + 127) / 128;
-  for (int r = 0; r < rows; ++r)
+  parallel_for(rows, [&](int r_lo, int r_hi) {
+  for (int r = r_lo; r < r_hi; ++r)
     for (int b = 0; b < KB; ++b) {
       const int k0 = b * 128, k1 = std::min(cols, k0 + 128);
       float amax = 0.f;
@@ -103,6 +104,7 @@ void quant_rows(const float* x, int rows, int cols, bool bf16_first, uint8_t* co
         codes[size_t(r) * cols + k] = e4m3(v / sc);
       }
     }
+  });
 }
 
 // ---------------------------------------------------------------------------------------------- generator
@@ -250,10 +252,14 @@ void lo_quant_rows(const float* x, int rows, int cols, int bf16_first, uint8_t* 
 }
 void lo_synth(uint64_t seed, uint64_t stream, size_t offset, size_t n, float std_, float bias, int bf16, float* out) {
   const uint64_t key = stream_key(seed, stream);
-  for (size_t i = 0; i < n; ++i) {
-    const float v = synth_z(key, offset + i) * std_ + bias;
-    out[i] = bf16 ? bf16r(v) : v;
-  }
+  const int chunks = int(std::min<size_t>(n / 4096 + 1, 1 << 20));
+  parallel_for(chunks, [&](int c_lo, int c_hi) {
+    const size_t lo = n * size_t(c_lo) / chunks, hi = n * size_t(c_hi) / chunks;
+    for (size_t i = lo; i < hi; ++i) {
+      const float v = synth_z(key, offset + i) * std_ + bias;
+      out[i] = bf16 ? bf16r(v) : v;
+    }
+  });
 }
 uint64_t lo_weight_stream(int layer, int tensor) { return uint64_t(layer + 1) * 64 + uint64_t(tensor); }
 

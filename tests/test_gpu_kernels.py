@@ -1,0 +1,187 @@
+"""Kernel-level parity on the GPU, through the C ABI: the tcgen05 block-scaled FP8 GEMM, the DeltaNet tree replay and
+commit, and the argmax, each against the CPU oracle on the same seeded inputs.  Modelled on the reference's model-free
+kernel tests (tests/stream_tests.cu, tests/tree_tests.cu in the reference project): a loose comparison with a host
+reference plus bit-exact invariants (row invariance across M)."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+import helpers
+
+pytestmark = pytest.mark.gpu
+
+# GEMM tolerance: both sides multiply the same E4M3 codes; the only differences are fp32 accumulation order inside the
+# tensor core and the order of the 128-wide block sums, so the bar is tight: 1e-4 of the row's rms plus 1e-5 relative.
+GEMM_RTOL, GEMM_ATOL_RMS = 1e-5, 1e-4
+
+
+def close_rows(y, ref, rtol, atol_rms):
+    rms = np.sqrt((ref.astype(np.float64) ** 2).mean(axis=1, keepdims=True)) + 1e-30
+    return bool((np.abs(y - ref) <= rtol * np.abs(ref) + atol_rms * rms).all())
+
+
+SHAPES = [(24, 256, 256), (80, 1408, 256), (80, 256, 704), (1, 128, 128), (33, 640, 256), (100, 512, 512), (130, 256, 384),
+          (7, 384, 1152), (24, 2048, 5120), (24, 640, 17408), (74, 1024, 6144)]
+
+
+@pytest.mark.parametrize("impl", [0, 1])
+@pytest.mark.parametrize("M,N,K", SHAPES)
+def test_gemm_matches_oracle(gpu, lb, lo, impl, M, N, K):
+    rng = np.random.default_rng(M * 131 + N * 17 + K)
+    x = rng.standard_normal((M, K)).astype(np.float32) * np.exp(rng.standard_normal((M, 1))).astype(np.float32)
+    w = (rng.standard_normal((N, K)) * 0.02).astype(np.float32)
+    x[0, :min(K, 128)] = 0.0                       # an all-zero activation block (scale 1)
+    ref = lo.gemm_fp8(x, w)
+    y = lb.gemm_fp8(x, w, impl=impl)
+    assert close_rows(y, ref, GEMM_RTOL, GEMM_ATOL_RMS), float(np.abs(y - ref).max())
+
+
+def test_gemm_rows_are_invariant_to_the_row_count(gpu, lb):
+    # the reference's central invariant (src/core/stream_gemm.cu:10-13): a row's result is bit for bit the same whatever
+    # M is and whoever its batch-mates are, including across the token-tile sizes 32, 64, 96 and 128
+    rng = np.random.default_rng(9)
+    K, N = 1024, 768
+    x = rng.standard_normal((128, K)).astype(np.float32)
+    w = (rng.standard_normal((N, K)) * 0.02).astype(np.float32)
+    full = lb.gemm_fp8(x, w, impl=0, splits=3)
+    for M in (1, 24, 33, 80, 97):
+        part = lb.gemm_fp8(x[:M], w, impl=0, splits=3)
+        assert np.array_equal(part, full[:M]), M
+    two_tiles = lb.gemm_fp8(np.concatenate([x, x[:40]]), w, impl=0, splits=3)
+    assert np.array_equal(two_tiles[:128], full) and np.array_equal(two_tiles[128:], full[:40])
+
+
+def test_gemm_k_split_changes_only_the_summation_order(gpu, lb, lo):
+    rng = np.random.default_rng(10)
+    x = rng.standard_normal((24, 2048)).astype(np.float32)
+    w = (rng.standard_normal((256, 2048)) * 0.02).astype(np.float32)
+    ref = lo.gemm_fp8(x, w)
+    for splits in (1, 2, 4, 16):
+        assert close_rows(lb.gemm_fp8(x, w, impl=0, splits=splits), ref, GEMM_RTOL, GEMM_ATOL_RMS)
+
+
+def test_weight_and_activation_quantizers_are_bit_exact(gpu, lb, lo):
+    # the product quantizes on the device, the oracle on the host: same codes, same scales
+    cfg = lb.toy_config()
+    ctx = lb.Context(cfg)
+    opt = lb.Options(4, 2048, 16, 512, 4, 128, 0, 0, 0, 0, 0)
+    m = lo.Model(cfg, opt, lb)
+    helpers.load_weights_from_host(lb, lo, cfg, 0, [ctx, m])
+    for layer, tensor, rows, cols in [(0, lb.T_GATE, 704, 256), (0, lb.T_UP, 704, 256), (0, lb.T_DOWN, 256, 704),
+                                      (1, lb.T_IN_QKV, 512, 256), (1, lb.T_IN_Z, 256, 256), (2, lb.T_OUT, 256, 256),
+                                      (3, lb.T_Q, 512, 256), (3, lb.T_K, 64, 256), (3, lb.T_V, 64, 256), (3, lb.T_O, 256, 256),
+                                      (-1, lb.T_LM_HEAD, 4096, 256)]:
+        a, b = ctx.get_matrix(layer, tensor, rows, cols), m.get_matrix(layer, tensor, rows, cols)
+        assert np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1]), (layer, tensor)
+    ctx.close(), m.close()
+
+
+def test_device_generator_matches_host_generator(gpu, lb, lo):
+    cfg = lb.toy_config()
+    a, b = lb.Context(cfg), lb.Context(cfg)
+    opt = lb.Options(4, 2048, 16, 512, 4, 128, 0, 0, 0, 0, 0)
+    m = lo.Model(cfg, opt, lb)
+    a.synth_weights(5)
+    helpers.load_weights_from_host(lb, lo, cfg, 5, [b])
+    m.synth_weights(5)
+    for layer, tensor, rows, cols in [(0, lb.T_GATE, 704, 256), (0, lb.T_DOWN, 256, 704), (3, lb.T_Q, 512, 256),
+                                      (-1, lb.T_LM_HEAD, 4096, 256)]:
+        x, y, z = (t.get_matrix(layer, tensor, rows, cols) for t in (a, b, m))
+        assert np.array_equal(x[0], y[0]) and np.array_equal(x[1], y[1]) and np.array_equal(x[0], z[0])
+    # synthetic KV and state: device fill == host fill
+    for t in (a, m):
+        helpers.map_pages([t], 1, 100, 16, 7)
+        t.synth_kv(1, 100, 11)
+        t.synth_state(1, 11)
+    for x, y in zip(a.kv_read(1, 0, 0, 100, codes=True), m.kv_read(1, 0, 0, 100, codes=True)):
+        assert np.array_equal(x, y)
+    for g in range(3):
+        for x, y in zip(a.state_read(1, g), m.state_read(1, g)):
+            assert np.array_equal(x, y)
+    assert a.state_hash(1) == m.state_hash(1)
+    a.close(), b.close(), m.close()
+
+
+# DeltaNet tolerance: fp32 FMA chains on the device against double accumulation in the oracle, over up to 17 dependent
+# steps: 2e-4 of the tensor's rms.
+GDN_TOL = 2e-4
+
+
+def gdn_inputs(rng, Hk, HV, Dk, Dv, n):
+    Cn = 2 * Hk * Dk + HV * Dv
+    return dict(pre=rng.standard_normal((n, Cn)).astype(np.float32), convw=(rng.standard_normal((Cn, 4)) * 0.3).astype(np.float32),
+                g=np.log(1.0 / (1.0 + np.exp(-rng.standard_normal((n, HV))))).astype(np.float32),   # alpha = sigmoid(N(0,1))
+                beta=(1.0 / (1.0 + np.exp(-rng.standard_normal((n, HV))))).astype(np.float32),
+                state=(rng.standard_normal((HV, Dk, Dv)) * 0.1).astype(np.float32),
+                conv=rng.standard_normal((Cn, 3)).astype(np.float32))
+
+
+def fp(a):
+    return a.ctypes.data_as(C.POINTER(C.c_float))
+
+
+@pytest.mark.parametrize("Hk,HV,Dk,Dv", [(2, 4, 64, 64), (4, 12, 128, 128)])
+@pytest.mark.parametrize("shape", ["two_branch", "chain", "random", "single"])
+def test_gdn_tree_and_commit_match_oracle(gpu, lb, lo, Hk, HV, Dk, Dv, shape):
+    rng = np.random.default_rng(Dk + len(shape))
+    if shape == "two_branch":
+        parent, chain = helpers.chain_plus_branch(16, 4), 15
+    elif shape == "chain":
+        parent, chain = helpers.chain_plus_branch(12, 0), 11
+    elif shape == "single":
+        parent, chain = [-1], 0
+    else:
+        parent, chain = helpers.random_tree(rng, 24, 7), 7
+    n = len(parent)
+    rc, td = lb.describe_tree(parent, chain)
+    assert rc == 0
+    d = gdn_inputs(rng, Hk, HV, Dk, Dv, n)
+    d["convw"] = np.array([lo.lo().lo_bf16_round(float(v)) for v in d["convw"].ravel()], np.float32).reshape(d["convw"].shape)
+    Cn, Vs = d["pre"].shape[1], HV * Dv
+    post_o, core_o = np.zeros((n, Cn), np.float32), np.zeros((n, Vs), np.float32)
+    lo.lo().lo_gdn_tree(Hk, HV, Dk, Dv, C.byref(td), fp(d["pre"]), fp(d["convw"]), fp(d["g"]), fp(d["beta"]), fp(d["state"]),
+                        fp(d["conv"]), fp(post_o), fp(core_o))
+    post_g, core_g = np.zeros_like(post_o), np.zeros_like(core_o)
+    lb.check(lb.lib().ling_b200_gdn_tree_host(0, Hk, HV, Dk, Dv, C.byref(td), fp(d["pre"]), fp(d["convw"]), fp(d["g"]),
+                                              fp(d["beta"]), fp(d["state"]), fp(d["conv"]), fp(post_g), fp(core_g)), "gdn_tree_host")
+    # the device's `post` carries q and k already L2-normalized per head (q also times 1/sqrt(Dk)); v is the raw conv output
+    post_n = post_o.copy()
+    for h in range(2 * Hk):
+        seg = post_o[:, h * Dk:(h + 1) * Dk].astype(np.float64)
+        scale = 1.0 / np.sqrt((seg ** 2).sum(axis=1, keepdims=True) + 1e-6) / (np.sqrt(Dk) if h < Hk else 1.0)
+        post_n[:, h * Dk:(h + 1) * Dk] = (seg * scale).astype(np.float32)
+    assert np.abs(post_g - post_n).max() <= 1e-5 * max(1.0, np.abs(post_n).max())
+    assert np.abs(core_g - core_o).max() <= GDN_TOL * np.sqrt((core_o ** 2).mean())
+    # commit of an accepted path: the rows of variant 0's path up to a random length
+    path = [td.path[td.nvar - 1][j] for j in range(td.depth[[r for r in range(n) if td.var[r] == td.nvar - 1][-1]] + 1)]
+    path = path[:int(rng.integers(1, len(path) + 1))]
+    pa = np.array(path, np.int32)
+    so, wo = d["state"].copy(), d["conv"].copy()
+    lo.lo().lo_gdn_commit(Hk, HV, Dk, Dv, pa.ctypes.data_as(C.POINTER(C.c_int)), len(path), n, fp(d["pre"]), fp(post_o), fp(d["g"]),
+                          fp(d["beta"]), fp(so), fp(wo))
+    sg, wg = d["state"].copy(), d["conv"].copy()
+    lb.check(lb.lib().ling_b200_gdn_commit_host(0, Hk, HV, Dk, Dv, pa.ctypes.data_as(C.POINTER(C.c_int)), len(path), n,
+                                                fp(d["pre"]), fp(post_g), fp(d["g"]), fp(d["beta"]), fp(sg), fp(wg)), "gdn_commit_host")
+    assert np.array_equal(wg, wo)                                  # the window is a copy: bit-exact
+    assert np.abs(sg - so).max() <= GDN_TOL * np.sqrt((so ** 2).mean())
+
+
+def test_argmax_ties_nan_and_inf(gpu, lb, lo):
+    # ties to the lower id, NaN skipped, inf kept, a row without a candidate comes back as (-FLT_MAX, 0x7fffffff)
+    # (src/core/topk.cu:19,58 in the reference project); on the 248,320-token vocabulary like tests/stream_tests.cu:728-757
+    rng = np.random.default_rng(12)
+    V = 248320
+    logits = rng.standard_normal((6, V)).astype(np.float32)
+    logits[0, [5, 77777, 200000]] = 9.0
+    logits[1, :] = np.nan
+    logits[2, 1000] = np.nan
+    logits[2, 123456] = np.inf
+    logits[3, :] = -np.inf
+    logits[4, V - 1] = 50.0
+    logits[5, :] = 1.25
+    ids, vals = np.zeros(6, np.int32), np.zeros(6, np.float32)
+    lb.check(lb.lib().ling_b200_argmax_host(0, fp(logits), 6, V, ids.ctypes.data_as(C.POINTER(C.c_int)), fp(vals)), "argmax_host")
+    oi, ov = lo.argmax(logits)
+    assert np.array_equal(ids, oi) and np.array_equal(vals, ov)
+    assert list(ids[:2]) == [5, 0x7fffffff] and ids[2] == 123456 and ids[4] == V - 1 and ids[5] == 0

@@ -1,0 +1,311 @@
+"""The whole verify step on the GPU, through the C ABI, against the CPU oracle on the same seeded inputs.
+
+Bars: packing, positions, masks, tree descriptions, accepted paths and emitted tokens bit-exact; hidden states, logits
+and DeltaNet states within the tolerances below.
+
+Why the floating-point bars have two tiers.  Device and oracle compute the same formulas on the same FP8 codes, and where
+nothing else intervenes they agree to ~1e-6 of a row's rms (the first tier: the MEDIAN row of the first layer's output
+must agree to 1e-4).  But every layer rounds its activations to E4M3 five times, and an fp32 difference of one ulp that
+straddles a rounding boundary flips a code by a whole FP8 step (6-12% of that element).  That happens to about two
+elements in 10^5, moves a few outputs of that row by up to ~0.1 of the row's rms and then propagates.  So the second tier
+bounds the whole tensor's relative L2 error and each row's worst element instead of asking for ulp-level agreement."""
+import numpy as np
+import pytest
+
+import helpers
+
+pytestmark = pytest.mark.gpu
+
+CLEAN_TOL = 1e-4    # tier 1: the median row of the first layer's output, max |gpu - oracle| / the row's rms
+REL_L2_TOL = 5e-2   # tier 2: ||gpu - oracle||_2 / ||oracle||_2 over a whole tensor (hidden states, logits, DeltaNet states);
+                    # measured: up to 2.2e-2 two layers deep at hidden 5120, where SwiGLU's heavy-tailed outputs make one flip count
+ROW_MAX_TOL = 0.3   # tier 2: the worst element of any row, as a fraction of that row's rms (an FP8 step on a large element)
+
+
+def row_errs(a, b):
+    rms = np.sqrt((b.astype(np.float64) ** 2).mean(axis=1)) + 1e-30
+    return np.abs(a.astype(np.float64) - b).max(axis=1) / rms
+
+
+def rel_l2(a, b):
+    return float(np.linalg.norm((a.astype(np.float64) - b).ravel()) / (np.linalg.norm(b.astype(np.float64).ravel()) + 1e-30))
+
+
+def assert_close(a, b, what):
+    assert np.isfinite(a).all(), what
+    assert rel_l2(a, b) <= REL_L2_TOL, (what, rel_l2(a, b))
+    flat_a, flat_b = a.reshape(a.shape[0], -1), b.reshape(b.shape[0], -1)
+    assert row_errs(flat_a, flat_b).max() <= ROW_MAX_TOL, (what, float(row_errs(flat_a, flat_b).max()))
+
+
+@pytest.fixture(scope="module")
+def toy(gpu, lb, lo):
+    cfg = lb.toy_config()
+    ctx = lb.Context(cfg, debug_rows=128)
+    opt = lb.Options(4, 2048, 16, 512, 4, 128, 0, 0, 0, 128, 0)
+    m = lo.Model(cfg, opt, lb)
+    helpers.load_weights_from_host(lb, lo, cfg, 0, [ctx, m])
+    yield cfg, ctx, m
+    ctx.close(), m.close()
+
+
+def check_step(lb, cfg, ctx, m, seqs, flags, seed=0):
+    helpers.setup_sessions([ctx, m], cfg, seqs, 16, seed)
+    ro = m.verify_step(seqs, flags=flags, make_steps=lb.make_steps)
+    rg = ctx.verify_step(seqs, flags=flags)
+    # integer work: bit-exact
+    pg, po = ctx.read_packing(), m.read_packing()
+    for k in po:
+        assert np.array_equal(pg[k], po[k]), k
+    for s in range(len(seqs)):
+        assert bytes(ctx.read_tree_desc(s)) == bytes(m.read_tree_desc(s)), s
+    # hidden states and logits: tier 1 on the first layer, tier 2 everywhere
+    assert np.median(row_errs(ctx.read_tap(0), m.read_tap(0))) <= CLEAN_TOL
+    for l in range(cfg.layers + 1):
+        assert_close(ctx.read_tap(l), m.read_tap(l), "residual after layer %d" % l)
+    lg, lo_ = ctx.read_logits(), m.read_logits()
+    assert_close(lg, lo_, "logits")
+    # the fused argmax equals the argmax of the device's own logits exactly (ties to the lower id)
+    ids, vals = ctx.read_argmax()
+    assert np.array_equal(ids, lg.argmax(axis=1)) and np.array_equal(vals, lg.max(axis=1))
+    # against the oracle's argmax: identical wherever the oracle's top-2 margin is clear of that row's own error; a
+    # near-tie is flagged, not failed silently: the device's pick must then be within that error of the oracle's maximum
+    oi, _ = m.read_argmax()
+    srt = np.sort(lo_, axis=1)
+    margin = srt[:, -1] - srt[:, -2]
+    tol = np.abs(lg - lo_).max(axis=1)
+    clear = margin > 2 * tol
+    assert np.array_equal(ids[clear], oi[clear])
+    near = np.flatnonzero(~clear)
+    assert (lo_[near, ids[near]] >= srt[near, -1] - 2 * tol[near]).all()
+    assert clear.mean() >= 0.5, "too many near-ties for the argmax comparison to mean anything"
+    return rg, ro, ids, oi
+
+
+def assert_results_equal(rg, ro):
+    for a, b in zip(rg, ro):
+        assert a.status == b.status and a.n_path == b.n_path and list(a.path)[:a.n_path] == list(b.path)[:b.n_path]
+        assert a.next_token == b.next_token and list(a.out)[:a.n_out] == list(b.out)[:b.n_out]
+
+
+def test_toy_step_matches_oracle(toy, lb):
+    cfg, ctx, m = toy
+    rng = np.random.default_rng(0)
+    seqs = helpers.toy_sequences(rng, cfg.vocab)     # contexts [3, 37, 512, 1029], 16-row chain + 4-row branch each
+    rg, ro, ids, oi = check_step(lb, cfg, ctx, m, seqs, lb.STEP_KEEP_LOGITS | lb.STEP_KEEP_TAPS)
+    if np.array_equal(ids, oi):
+        assert_results_equal(rg, ro)
+
+
+def test_imposed_acceptance_compaction_and_commit(toy, lb):
+    cfg, ctx, m = toy
+    rng = np.random.default_rng(1)
+    seqs = helpers.toy_sequences(rng, cfg.vocab)
+    want = [[0, 16, 17, 18], [0, 1, 2, 3, 4, 5, 6, 7, 8, 9], [0], [0, 16, 17, 18, 19]]
+    for q, path in zip(seqs, want):
+        f = rng.integers(0, cfg.vocab, 20).astype(np.int32)
+        for a, b in zip(path[:-1], path[1:]):
+            f[a] = q["tokens"][b]
+        f[path[-1]] = 4000 + len(path)      # matches no child
+        q["force"] = f
+    rg, ro, _, _ = check_step(lb, cfg, ctx, m, seqs, lb.STEP_COMMIT | lb.STEP_KEEP_LOGITS | lb.STEP_KEEP_TAPS)
+    assert_results_equal(rg, ro)
+    for r, path in zip(rg, want):
+        assert list(r.path)[:r.n_path] == path and r.next_token == 4000 + len(path) and r.n_out == len(path)
+    for s, q in enumerate(seqs):
+        for g in range(3):
+            (sg, wg), (so, wo) = ctx.state_read(s, g), m.state_read(s, g)
+            assert_close(sg, so, "DeltaNet state")
+            assert_close(wg.T, wo.T, "conv window")
+        # the accepted rows' K/V sit at pos .. pos + n after compaction (an FP8 step apart at most, where a code flipped)
+        kg, vg = ctx.kv_read(s, 0, q["pos"], len(want[s]))
+        ko, vo = m.kv_read(s, 0, q["pos"], len(want[s]))
+        assert rel_l2(kg, ko) <= 2 * REL_L2_TOL and rel_l2(vg, vo) <= 2 * REL_L2_TOL
+        assert np.abs(kg - ko).max() <= 0.13 * np.abs(ko).max() and np.abs(vg - vo).max() <= 0.13 * np.abs(vo).max()
+        # the context itself is untouched
+        for a, b in zip(ctx.kv_read(s, 0, 0, q["pos"], codes=True), m.kv_read(s, 0, 0, q["pos"], codes=True)):
+            assert np.array_equal(a, b)
+
+
+def test_compaction_moves_exact_bytes(toy, lb):
+    # tree_gather is a copy: after accepting [0, 16, 17] the cache holds at pos+1, pos+2 exactly the codes and scales the
+    # verify wrote at pos+16, pos+17
+    cfg, ctx, m = toy
+    rng = np.random.default_rng(2)
+    q = helpers.toy_sequences(rng, cfg.vocab, contexts=(37,))[0]
+    helpers.setup_sessions([ctx], cfg, [q], 16, 0)
+    ctx.verify_step([q], flags=0)
+    before = ctx.kv_read(0, 0, 37, 20, codes=True)
+    f = np.zeros(20, np.int32)
+    f[0], f[16], f[17] = q["tokens"][16], q["tokens"][17], 1
+    helpers.setup_sessions([ctx], cfg, [q], 16, 0)
+    ctx.verify_step([dict(q, force=f)], flags=lb.STEP_COMMIT)
+    after = ctx.kv_read(0, 0, 37, 20, codes=True)
+    for a, b in zip(after, before):
+        assert np.array_equal(a[1], b[16]) and np.array_equal(a[2], b[17]) and np.array_equal(a[0], b[0])
+        assert np.array_equal(a[3:], b[3:])
+
+
+def test_graph_replay_equals_eager_launches(gpu, toy, lb, lo):
+    cfg, ctx, m = toy
+    eager = lb.Context(cfg, debug_rows=128, use_graph=0)
+    helpers.load_weights_from_host(lb, lo, cfg, 0, [eager])
+    rng = np.random.default_rng(3)
+    seqs = helpers.toy_sequences(rng, cfg.vocab)
+    outs = []
+    for c in (ctx, eager, ctx):   # the second pass on `ctx` replays the captured graph
+        helpers.setup_sessions([c], cfg, seqs, 16, 0)
+        c.verify_step(seqs, flags=lb.STEP_COMMIT | lb.STEP_KEEP_LOGITS)
+        outs.append((c.read_logits(), [c.state_hash(s) for s in range(4)]))
+    assert np.array_equal(outs[0][0], outs[1][0]) and outs[0][1] == outs[1][1]
+    assert np.array_equal(outs[0][0], outs[2][0]) and outs[0][1] == outs[2][1]
+    assert ctx.launch_count() == eager.launch_count() > 40
+    eager.close()
+
+
+def test_variants_agree(gpu, toy, lb, lo):
+    # the CUDA-core GEMM (cross-check) within tolerance of the tensor-core path; programmatic dependent launch bit-exact
+    cfg, ctx, m = toy
+    rng = np.random.default_rng(4)
+    seqs = helpers.toy_sequences(rng, cfg.vocab)
+    helpers.setup_sessions([ctx], cfg, seqs, 16, 0)
+    ctx.verify_step(seqs, flags=lb.STEP_KEEP_LOGITS)
+    base = ctx.read_logits()
+    for kw, exact in ((dict(gemm_impl=1), False), (dict(pdl=1), True), (dict(pdl=1, use_graph=0), True)):
+        other = lb.Context(cfg, debug_rows=128, **kw)
+        helpers.load_weights_from_host(lb, lo, cfg, 0, [other])
+        helpers.setup_sessions([other], cfg, seqs, 16, 0)
+        other.verify_step(seqs, flags=lb.STEP_KEEP_LOGITS)
+        lg = other.read_logits()
+        if exact:
+            assert np.array_equal(lg, base), kw
+        else:
+            assert_close(lg, base, str(kw))
+        other.close()
+
+
+def test_rows_do_not_depend_on_batch_mates(toy, lb):
+    # each sequence's rows are bit for bit what the sequence gets alone (src/core/engine.hpp:330-336 in the reference)
+    cfg, ctx, m = toy
+    rng = np.random.default_rng(5)
+    seqs = helpers.toy_sequences(rng, cfg.vocab)
+    helpers.setup_sessions([ctx], cfg, seqs, 16, 0)
+    ctx.verify_step(seqs, flags=lb.STEP_KEEP_LOGITS)
+    batch, row0 = ctx.read_logits(), ctx.read_packing()["row0"]
+    for s in (0, 2, 3):
+        helpers.setup_sessions([ctx], cfg, seqs, 16, 0)
+        ctx.verify_step([seqs[s]], flags=lb.STEP_KEEP_LOGITS)
+        assert np.array_equal(ctx.read_logits(), batch[row0[s]:row0[s + 1]]), s
+
+
+def test_ragged_random_trees_and_multiple_steps(toy, lb):
+    cfg, ctx, m = toy
+    rng = np.random.default_rng(6)
+    seqs = []
+    for s, (ctx_len, n) in enumerate(zip((0, 15, 16, 700), (1, 32, 9, 17))):
+        chain = int(rng.integers(0, n))
+        seqs.append({"slot": s, "pos": ctx_len, "tokens": rng.integers(0, cfg.vocab, n).astype(np.int32),
+                     "parent": np.array(helpers.random_tree(rng, n, chain), np.int32), "chain": chain})
+    helpers.setup_sessions([ctx, m], cfg, seqs, 16, 1, extra_rows=96)
+    for step in range(3):
+        for q in seqs:   # impose a random accepted path through each tree
+            n, par = len(q["tokens"]), q["parent"]
+            f, u = rng.integers(0, cfg.vocab, n).astype(np.int32), 0
+            while True:
+                kids = [c for c in range(n) if par[c] == u]
+                if not kids or rng.random() < 0.25:
+                    f[u] = -1 if False else int(cfg.vocab - 1 - step)
+                    break
+                c = kids[int(rng.integers(0, len(kids)))]
+                f[u] = q["tokens"][c]
+                u = c
+            q["force"] = f
+        ro = m.verify_step(seqs, flags=lb.STEP_COMMIT, make_steps=lb.make_steps)
+        rg = ctx.verify_step(seqs, flags=lb.STEP_COMMIT)
+        assert_results_equal(rg, ro)
+        for s in range(4):
+            assert bytes(ctx.read_tree_desc(s)) == bytes(m.read_tree_desc(s))
+        for q, r in zip(seqs, rg):   # the engine advances each session by its accepted rows (speculate.cpp:1060-1061)
+            q["pos"] += r.n_path
+            n = int(rng.integers(1, 33))
+            chain = int(rng.integers(0, n))
+            q["tokens"] = rng.integers(0, cfg.vocab, n).astype(np.int32)
+            q["tokens"][0] = r.next_token % cfg.vocab
+            q["parent"], q["chain"] = np.array(helpers.random_tree(rng, n, chain), np.int32), chain
+    for s in range(4):
+        for g in range(3):
+            (sg, wg), (so, wo) = ctx.state_read(s, g), m.state_read(s, g)
+            assert_close(sg, so, "DeltaNet state after three steps")
+
+
+def test_a_non_finite_row_fails_only_its_sequence(gpu, lb, lo):
+    # NonFiniteLogits (src/core/speculate.cpp:1214-1219,1266-1272): the sequence gets an error, nothing of it is committed,
+    # the others commit.  The failure is made on the host: a NaN in one token's embedding row.
+    cfg = lb.toy_config()
+    ctx = lb.Context(cfg)
+    ctx.synth_weights(0)
+    emb = lo.synth(0, lo.weight_stream(-1, lb.T_EMBED), 0, cfg.vocab * cfg.hidden, 0.02).reshape(cfg.vocab, cfg.hidden)
+    emb[17, 3] = np.nan
+    ctx.set_tensor(-1, lb.T_EMBED, emb)
+    rng = np.random.default_rng(7)
+    seqs = helpers.toy_sequences(rng, cfg.vocab, contexts=(20, 40))
+    seqs[0]["tokens"][:] = np.where(seqs[0]["tokens"] == 17, 18, seqs[0]["tokens"])
+    seqs[1]["tokens"][5] = 17
+    helpers.setup_sessions([ctx], cfg, seqs, 16, 0)
+    h = [ctx.state_hash(0), ctx.state_hash(1)]
+    res = ctx.verify_step(seqs, flags=lb.STEP_COMMIT)
+    assert res[0].status == 0 and res[1].status == 1 and res[1].n_path == 0
+    assert ctx.state_hash(0) != h[0] and ctx.state_hash(1) == h[1]
+    ctx.close()
+
+
+def test_errors_are_reported_not_faulted(gpu, lb):
+    cfg = lb.toy_config()
+    ctx = lb.Context(cfg, sessions=2, max_seqs=2, max_rows=40)
+    ctx.synth_weights(0)
+    q = {"slot": 0, "pos": 5, "tokens": np.zeros(4, np.int32), "parent": np.array([-1, 0, 1, 2], np.int32), "chain": 3}
+    with pytest.raises(lb.LingError):   # the same session twice (speculate.cpp:1107-1108)
+        ctx.verify_step([q, dict(q)])
+    with pytest.raises(lb.LingError):   # more rows than the context was created for
+        ctx.verify_step([dict(q, tokens=np.zeros(32, np.int32), parent=np.arange(-1, 31, dtype=np.int32), chain=31),
+                         dict(q, slot=1, tokens=np.zeros(32, np.int32), parent=np.arange(-1, 31, dtype=np.int32), chain=31)])
+    with pytest.raises(lb.LingError):   # logits were not asked for at creation
+        ctx.verify_step([q], flags=lb.STEP_KEEP_LOGITS)
+    # positions without a mapped page: the kernels record a code in the device error word and skip the access
+    with pytest.raises(lb.LingError, match="device error word = 5"):
+        ctx.verify_step([q], flags=0)
+    helpers.map_pages([ctx], 0, 64, 16, 1)
+    ctx.synth_kv(0, 5, 0)
+    res = ctx.verify_step([q], flags=0)   # the context is usable afterwards
+    assert res[0].status == 0 and res[0].n_path >= 1
+    with pytest.raises(lb.LingError, match="device error word = 6"):   # a parent that does not precede its row
+        ctx.verify_step([dict(q, parent=np.array([-1, 0, 3, 2], np.int32))], flags=0)
+    ctx.close()
+
+
+def test_27b_shaped_layers_match_oracle(gpu, lb, lo):
+    # the 27B-class head shapes (attention 24 q / 4 kv heads of 256, DeltaNet 16 qk / 48 v heads of 128, hidden 5120) on a
+    # short stack with a narrower FFN and vocabulary so that the oracle finishes in seconds
+    cfg = lb.make_config(5120, 4352, 4, 8192, 24, 4, 256, 64, 16, 48, 128, 128, [0, 0, 0, 1])
+    ctx = lb.Context(cfg, sessions=2, max_context=4096, page_tokens=16, pool_pages=300, max_seqs=2, max_rows=64, debug_rows=64)
+    opt = lb.Options(2, 4096, 16, 300, 2, 64, 0, 0, 0, 64, 0)
+    m = lo.Model(cfg, opt, lb)
+    lo.lo().lo_set_threads(8)
+    ctx.synth_weights(3)
+    m.synth_weights(3)
+    rng = np.random.default_rng(8)
+    seqs = [{"slot": 0, "pos": 1500, "tokens": rng.integers(0, 8192, 24).astype(np.int32),
+             "parent": np.array(helpers.chain_plus_branch(16, 8), np.int32), "chain": 15},
+            {"slot": 1, "pos": 530, "tokens": rng.integers(0, 8192, 9).astype(np.int32),
+             "parent": np.array(helpers.random_tree(rng, 9, 3), np.int32), "chain": 3}]
+    f = rng.integers(0, 8192, 24).astype(np.int32)
+    f[0], f[16], f[17], f[18] = seqs[0]["tokens"][16], seqs[0]["tokens"][17], seqs[0]["tokens"][18], 1
+    seqs[0]["force"] = f
+    rg, ro, _, _ = check_step(lb, cfg, ctx, m, seqs, lb.STEP_COMMIT | lb.STEP_KEEP_LOGITS | lb.STEP_KEEP_TAPS, seed=3)
+    assert list(rg[0].path)[:rg[0].n_path] == [0, 16, 17, 18] == list(ro[0].path)[:ro[0].n_path]
+    for s in range(2):
+        for g in range(3):
+            (sg, _), (so, _) = ctx.state_read(s, g), m.state_read(s, g)
+            assert_close(sg, so, "DeltaNet state")
+    lo.lo().lo_set_threads(1)
+    ctx.close(), m.close()
