@@ -381,12 +381,14 @@ def run_micro_gemm(args):
     three warm-up launches; the small case the profiler captures.  A matrix smaller than L2 is served from L2 here."""
     lbm = importlib.import_module("ling-engine_b200")
     M, N, K = (int(x) for x in args.shape.split(","))
+    lbm.lib().ling_b200_set_pdl(args.pdl)
     ms = lbm.gemm_fp8_bench(M, N, K, impl=args.gemm_impl, splits=0, iters=args.iters)
+    lbm.lib().ling_b200_set_pdl(0)
     peak, kind = measured_peaks()
     nbytes = N * K + (K // 128) * N * 4
     print(json.dumps({"micro": "gemm_fp8_tcgen05_kernel", "shape": [M, N, K], "iters": args.iters, "us_per_launch": ms * 1e3,
                       "weight_bytes": nbytes, "GB_per_s": nbytes / (ms * 1e-3) / 1e9, "frac_of_%s_hbm" % kind: nbytes / (ms * 1e-3) / 1e9 / peak,
-                      "larger_than_l2": nbytes > 126e6}), flush=True)
+                      "larger_than_l2": nbytes > 126e6, "pdl": args.pdl}), flush=True)
 
 
 def ctx_stage_bytes(lbm, n_seqs):

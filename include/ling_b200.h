@@ -75,6 +75,10 @@ void ling_b200_destroy(ling_b200_ctx* ctx);
 const char* ling_b200_last_error(void);
 /* Library/ABI version, and whether the CUDA kernels are present (always 1: there is no CPU path). */
 int ling_b200_abi_version(void);
+/* kernels::set_pdl / pdl_enabled (src/core/kernels.cuh:82-83): programmatic dependent launch for launches made outside a
+ * context's step (the kernel-level entry points below); process-wide.  A context's step follows its own options.pdl. */
+void ling_b200_set_pdl(int on);
+int ling_b200_pdl_enabled(void);
 
 /* Tensor names for ling_b200_set_tensor (LayerWeights, src/core/model.hpp:86-104). */
 enum {
@@ -227,6 +231,10 @@ int ling_b200_timer_end(ling_b200_ctx* ctx, float* ms);
  * [4] head+argmax, [5] pack/accept/compact/commit.  Also the number of kernel launches in one step. */
 int ling_b200_profile_step(ling_b200_ctx* ctx, float ms[8], int* launches);
 int ling_b200_step_launch_count(ling_b200_ctx* ctx);
+/* Debugging aid (the reference's LING_MK_TIMES, engine.hpp:637-642): with LING_B200_TIMELINE=1 in the environment when
+ * the context is created, replays the staged step once and returns four GPU-timer stamps (ns) per weight-GEMM launch:
+ * first CTA start, first and last producer past the dependency wait, last CTA end.  Returns the launches written. */
+int ling_b200_gemm_timeline(ling_b200_ctx* ctx, unsigned long long* out, int max_launches);
 /* Writes more than L2 between timed steps (the bench's flush). */
 int ling_b200_flush_l2(ling_b200_ctx* ctx);
 int ling_b200_sync(ling_b200_ctx* ctx);
@@ -241,6 +249,13 @@ int ling_b200_sync(ling_b200_ctx* ctx);
 int ling_b200_gemm_fp8_host(int device, int impl, int splits, const float* x, const float* w, float* y, int M, int N, int K);
 /* The same GEMM timed on the device with resident operands: ms per launch over `iters` launches. */
 int ling_b200_gemm_fp8_bench(int device, int impl, int splits, int M, int N, int K, int iters, float* ms_per_launch);
+
+/* attention_rows(_seqs) + attention_combine (kernels.cuh:223-290; kernels.cu:919-961) for one full-attention layer (index
+ * among the attention layers): q [rows][heads][head_dim] (normed, rotated); every row attends to its sequence's context
+ * [0, pos) and to the in-flight positions pos + j of its own root-to-row path, as the slot's cache holds them (write them
+ * with ling_b200_kv_write first); out [rows][heads][head_dim], before the output gate. */
+int ling_b200_attention_host(ling_b200_ctx* ctx, const ling_b200_seq_step* seqs, int n_seqs, int attn_layer, const float* q,
+                             float* out);
 
 /* gdn_conv_tree + gdn_recurrent_tree (kernels.cuh:131-136): one sequence, one layer.  pre [n][C], g and beta
  * [n][HV] (g = log decay), state [HV][Dk][Dv], conv [C][3]; out core [n][HV*Dv] and post [n][C] (the conv outputs with

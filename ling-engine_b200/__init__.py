@@ -285,6 +285,16 @@ class Context:
         check(lib().ling_b200_step_fetch(self.h, res), "step_fetch")
         return list(res)
 
+    def attention(self, seqs, attn_layer, q):
+        """One attention layer alone on the slot's cache: q [rows][heads][head_dim] -> out, before the output gate."""
+        arr, keep = make_steps(seqs)
+        q = np.ascontiguousarray(q, np.float32)
+        out = np.zeros_like(q)
+        check(lib().ling_b200_attention_host(self.h, arr, len(seqs), attn_layer, _fp(q), _fp(out)), "attention_host")
+        self.last_rows = sum(len(s["tokens"]) for s in seqs)
+        self.last_seqs = len(seqs)
+        return out
+
     def read_tree_desc(self, seq):
         t = TreeDesc()
         check(lib().ling_b200_read_tree_desc(self.h, seq, C.byref(t)), "read_tree_desc")

@@ -4,6 +4,7 @@
 // capacity class (the reference replays three graphs per step with two host syncs, src/core/speculate.cpp:473-514;
 // here packing, forward pass, argmax, acceptance, compaction and commit are one graph and one sync).
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <vector>
@@ -75,7 +76,7 @@ struct ling_b200_ctx {
   float* planes[2] = {nullptr, nullptr};
   size_t plane_floats = 0;
   float *pre = nullptr, *post = nullptr, *g = nullptr, *beta = nullptr;  // [n_gdn][rows][..], saved for the commit
-  float *part_o = nullptr, *part_ml = nullptr, *attn_w = nullptr;
+  float *part_o = nullptr, *part_ml = nullptr;
   int chunk_slots = 0;
   HeadEpilogue head_ep;
   float* logits = nullptr;
@@ -99,6 +100,11 @@ struct ling_b200_ctx {
   std::map<std::pair<int, int>, cudaGraphExec_t> graphs;  // (row class, flags)
   int launches_per_step = 0;
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+
+  // GEMM timeline (LING_B200_TIMELINE=1 at creation): four %globaltimer stamps per GEMM launch of the last step
+  unsigned long long* timeline = nullptr;
+  int timeline_next = 0;
+  static constexpr int kTimelineLaunches = 1024;
 
   // profiling of one eager replay
   bool profiling = false;
@@ -165,6 +171,7 @@ int run_gemm(ling_b200_ctx* c, const Fp8Matrix& w, const Fp8Acts& x, int which, 
   g.head = head;
   g.impl = c->opt.gemm_impl;
   g.err_flag = c->sb.err;
+  if (c->timeline && c->timeline_next < ling_b200_ctx::kTimelineLaunches) g.timeline = c->timeline + 4 * size_t(c->timeline_next++);
   return gemm_launch(g, c->stream);
 }
 
@@ -184,6 +191,7 @@ int enqueue_step_body(ling_b200_ctx* c, int rows, int flags) {
   const bool taps = (flags & LING_B200_STEP_KEEP_TAPS) != 0;
   const bool keep_logits = (flags & LING_B200_STEP_KEEP_LOGITS) != 0;
   c->launches_per_step = 0;
+  c->timeline_next = 0;
   {
     Timed t(c, kFamStep);
     LB_TRY(pack_launch(c->sb, d, s));
@@ -212,7 +220,7 @@ int enqueue_step_body(ling_b200_ctx* c, int rows, int flags) {
       }
       {
         Timed t(c, kFamAttn);
-        LB_TRY(attn_combine_launch(c->part_o, c->part_ml, p0, c->sb, d, c->qout(c->xq_a), c->attn_w, rows, s));
+        LB_TRY(attn_combine_launch(c->part_o, c->part_ml, p0, c->sb, d, c->qout(c->xq_a), nullptr, rows, s));
       }
       LB_TRY(run_gemm(c, L.o, c->xq_a, 1, rows));
       carry = planes_of(c, 1, L.o);
@@ -405,6 +413,8 @@ int finish(ling_b200_ctx* c) {
 extern "C" {
 
 const char* ling_b200_last_error(void) { return g_error.c_str(); }
+void ling_b200_set_pdl(int on) { set_pdl(on != 0); }
+int ling_b200_pdl_enabled(void) { return pdl_enabled() ? 1 : 0; }
 int ling_b200_abi_version(void) { return 1; }
 
 int ling_b200_device_count(void) {
@@ -434,8 +444,7 @@ int ling_b200_create(const ling_b200_model_config* cfg, const ling_b200_options*
                   cfg->lin_v_heads % cfg->lin_k_heads == 0 && G >= 1 && opt->sessions >= 1 &&
                   (opt->page_tokens == 16 || opt->page_tokens == 32 || opt->page_tokens == 64) && opt->pool_pages >= 1 &&
                   opt->max_seqs >= 1 && opt->max_seqs <= LING_B200_MAX_SEQS && opt->max_rows >= 1 &&
-                  opt->max_rows <= LING_B200_MAX_ROWS && opt->max_context >= 1 && opt->debug_rows >= 0 &&
-                  opt->max_context / kAttnChunk + 2 <= kMaxChunks;
+                  opt->max_rows <= LING_B200_MAX_ROWS && opt->max_context >= 1 && opt->debug_rows >= 0;
   if (!ok) {
     set_error("create: unsupported model configuration or options");
     return LING_B200_ERR_ARG;
@@ -534,7 +543,6 @@ int ling_b200_create(const ling_b200_model_config* cfg, const ling_b200_options*
   const size_t rmax = size_t(kTreeRows) * (d.Hq / d.Hkv);
   LB_TRY(c->alloc(&c->part_o, size_t(c->chunk_slots) * rmax * d.D, false));
   LB_TRY(c->alloc(&c->part_ml, size_t(c->chunk_slots) * rmax * 2, false));
-  LB_TRY(c->alloc(&c->attn_w, size_t(d.rows_alloc) * d.Hq * kMaxChunks, false));
   c->head_ep.rows_alloc = d.rows_alloc;
   LB_TRY(c->alloc(&c->head_ep.tile_val, size_t(c->head.N_pad / kTileN) * d.rows_alloc));
   LB_TRY(c->alloc(&c->head_ep.tile_idx, size_t(c->head.N_pad / kTileN) * d.rows_alloc));
@@ -542,6 +550,8 @@ int ling_b200_create(const ling_b200_model_config* cfg, const ling_b200_options*
     LB_TRY(c->alloc(&c->logits, size_t(opt->debug_rows) * d.V));
     LB_TRY(c->alloc(&c->taps, size_t(cfg->layers + 1) * opt->debug_rows * d.H));
   }
+  if (const char* tl = std::getenv("LING_B200_TIMELINE"); tl && tl[0] == '1')
+    LB_TRY(c->alloc(&c->timeline, size_t(4) * ling_b200_ctx::kTimelineLaunches));
   c->flush_floats = size_t(192) << 18;  // 192 MiB: more than the 126 MB L2
   LB_TRY(c->alloc(&c->flush, c->flush_floats, false));
 
@@ -796,10 +806,12 @@ int ling_b200_kv_read(ling_b200_ctx* c, int slot, int al, int from, int n, float
     for (int hh = 0; hh < d.Hkv; ++hh)
       for (int kvi = 0; kvi < 2; ++kvi) {
         const int pos = from + i;
-        const size_t at = kv_slot_index(d, al, kvi, hh, table[pos / d.page_tokens], pos % d.page_tokens);
+        const int page = table[pos / d.page_tokens], tok = pos % d.page_tokens;
         float sc;
-        LB_CUDA(cudaMemcpy(codes.data(), c->kv.codes + at * d.D, d.D, cudaMemcpyDeviceToHost));
-        LB_CUDA(cudaMemcpy(&sc, c->kv.scales + at, 4, cudaMemcpyDeviceToHost));
+        // a K position's bytes are contiguous; a V position's bytes are page_tokens apart (the V page is [D][token])
+        LB_CUDA(cudaMemcpy2D(codes.data(), 1, c->kv.codes + kv_code_index(d, al, kvi, hh, page, tok, 0), kvi ? size_t(d.page_tokens) : 1, 1,
+                             size_t(d.D), cudaMemcpyDeviceToHost));
+        LB_CUDA(cudaMemcpy(&sc, c->kv.scales + kv_slot_index(d, al, kvi, hh, page, tok), 4, cudaMemcpyDeviceToHost));
         const size_t o = size_t(i) * d.Hkv + hh;
         float* f = kvi ? v : k;
         uint8_t* cc = kvi ? vcodes : kcodes;
@@ -988,6 +1000,21 @@ int ling_b200_verify_step(ling_b200_ctx* c, const ling_b200_seq_step* seqs, int 
 
 int ling_b200_step_launch_count(ling_b200_ctx* c) { return c ? c->launches_per_step : 0; }
 
+// Debugging aid (needs LING_B200_TIMELINE=1 when the context is created): clears the stamps, replays the staged step once
+// and returns, per GEMM launch in order, {first CTA start, first and last producer past the dependency wait, last CTA end}
+// in nanoseconds of the GPU's global timer.  Returns the number of launches written.
+int ling_b200_gemm_timeline(ling_b200_ctx* c, unsigned long long* out, int max_launches) {
+  if (!c || !c->timeline || !out) return 0;
+  if (finish(c) != LING_B200_OK) return 0;
+  std::vector<unsigned long long> init(size_t(4) * ling_b200_ctx::kTimelineLaunches);
+  for (size_t i = 0; i < init.size(); i += 4) init[i] = init[i + 1] = ~0ull, init[i + 2] = init[i + 3] = 0;
+  if (cudaMemcpy(c->timeline, init.data(), init.size() * 8, cudaMemcpyHostToDevice) != cudaSuccess) return 0;
+  if (ling_b200_step_launch(c) != LING_B200_OK || finish(c) != LING_B200_OK) return 0;
+  const int n = std::min(max_launches, c->timeline_next > 0 ? c->timeline_next : 4 * c->cfg.layers + 1);
+  if (cudaMemcpy(out, c->timeline, size_t(n) * 32, cudaMemcpyDeviceToHost) != cudaSuccess) return 0;
+  return n;
+}
+
 int ling_b200_profile_step(ling_b200_ctx* c, float ms[8], int* launches) {
   LB_TRY(check_ctx(c));
   if (c->staged_seqs < 1) {
@@ -1031,6 +1058,34 @@ int ling_b200_flush_l2(ling_b200_ctx* c) {
 int ling_b200_sync(ling_b200_ctx* c) {
   LB_TRY(check_ctx(c));
   return finish(c);
+}
+
+// One attention layer alone, for parity checks: packs `seqs` on the device, takes q [rows][heads][head_dim] from the host,
+// runs the tree attention over the slot's cache (context and in-flight positions as the cache holds them) and returns
+// the merged rows before the output gate.
+int ling_b200_attention_host(ling_b200_ctx* c, const ling_b200_seq_step* seqs, int n_seqs, int attn_layer, const float* q, float* out) {
+  LB_TRY(ling_b200_step_stage(c, seqs, n_seqs, 0));
+  const ModelDims& d = c->d;
+  if (attn_layer < 0 || attn_layer >= d.n_attn || !q || !out) {
+    set_error("attention_host: bad argument");
+    return LING_B200_ERR_ARG;
+  }
+  const int rows = c->staged_rows, cls = row_class(rows);
+  const size_t n = size_t(rows) * d.Hq * d.D;
+  if (n > c->upload_floats || n > c->plane_floats) {
+    set_error("attention_host: too many rows for the staging buffers");
+    return LING_B200_ERR_ARG;
+  }
+  c->last_rows = rows, c->last_seqs = n_seqs, c->last_flags = 0;
+  LB_TRY(pack_launch(c->sb, d, c->stream));
+  LB_CUDA(cudaMemcpyAsync(c->upload, q, n * 4, cudaMemcpyHostToDevice, c->stream));
+  LB_TRY(f32_to_half_launch(c->upload, c->qh, n, c->stream));
+  LB_TRY(attention_launch(c->qh, c->sb, d, attn_layer, c->kv, c->part_o, c->part_ml, c->chunk_slots, c->sm_count * 2, c->stream));
+  Planes none;
+  none.p = nullptr;
+  LB_TRY(attn_combine_launch(c->part_o, c->part_ml, none, c->sb, d, c->qout(c->xq_a), c->planes[0], cls, c->stream));
+  LB_CUDA(cudaMemcpyAsync(out, c->planes[0], n * 4, cudaMemcpyDeviceToHost, c->stream));
+  return read_err(c);
 }
 
 // ------------------------------------------------------------------------------------------------ read-backs

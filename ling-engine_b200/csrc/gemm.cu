@@ -150,8 +150,11 @@ __global__ void __launch_bounds__(kGemmThreads, ctas_per_sm(NT))
     gemm_fp8_tcgen05_kernel(const __grid_constant__ CUtensorMap mapW, const __grid_constant__ CUtensorMap mapX,
                             const float* __restrict__ ws, const float* __restrict__ xs, float* __restrict__ out, int ld,
                             size_t split_stride, int M, int N, int N_pad, int KB, int splits, int xrows, HeadArgs head,
-                            int* err_flag, int pdl, int l2_slabs) {
+                            int* err_flag, int pdl, int l2_slabs, unsigned long long* timeline) {
   pdl_trigger();  // the next kernel may be scheduled as soon as every CTA of this one has started
+  // Optional timeline (debugging aid, like the reference's per-block %globaltimer stamps, src/core/engine.hpp:637-642):
+  // [0] first CTA's start, [1] first producer past the dependency wait, [2] last producer past it, [3] last CTA's end.
+  if (timeline && threadIdx.x == 0) atomicMin(timeline, global_ns());
   constexpr int STAGES = stages_for(NT);
   constexpr int kBBytes = NT * kBlockK;
   constexpr int kStageBytes = kABytes + kBBytes;
@@ -171,7 +174,8 @@ __global__ void __launch_bounds__(kGemmThreads, ctas_per_sm(NT))
   int* red_idx = reinterpret_cast<int*>(red_val + 4 * NT);   // [4][NT]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tile_n = blockIdx.x, split = blockIdx.y, tile_m = blockIdx.z;
+  // token tiles vary fastest: the CTAs that share a weight tile run together, so only the first of them reads it from HBM
+  const int tile_n = blockIdx.z, split = blockIdx.y, tile_m = blockIdx.x;
   const int kb0 = int(int64_t(KB) * split / splits), kb1 = int(int64_t(KB) * (split + 1) / splits);
   const int nslab = kb1 - kb0;
 
@@ -205,7 +209,13 @@ __global__ void __launch_bounds__(kGemmThreads, ctas_per_sm(NT))
       const int wy = tile_n * kTileN, xy = tile_m * NT;
       int i = 0;
       bool ok = true;
-      if (!pdl) pdl_wait();
+      if (!pdl) {
+        pdl_wait();
+        if (timeline) {
+          const unsigned long long t = global_ns();
+          atomicMin(timeline + 1, t), atomicMax(timeline + 2, t);
+        }
+      }
       if (pdl) {
         // Weights do not depend on the previous kernel: fill the pipeline with weight tiles and ask for the next
         // l2_slabs tiles to be brought into L2, then wait for the previous kernel and fetch the activation tiles of the
@@ -218,6 +228,10 @@ __global__ void __launch_bounds__(kGemmThreads, ctas_per_sm(NT))
         const int l2_end = nslab < pre + l2_slabs ? nslab : pre + l2_slabs;
         for (int s = pre; s < l2_end; ++s) tma_prefetch_l2_2d(&mapW, (kb0 + s) * kBlockK, wy);
         pdl_wait();
+        if (timeline) {
+          const unsigned long long t = global_ns();
+          atomicMin(timeline + 1, t), atomicMax(timeline + 2, t);
+        }
         for (int s = 0; s < pre; ++s)
           tma_load_2d(tiles + s * kStageBytes + kABytes, &mapX, &full[s], (kb0 + s) * kBlockK, xy, pol_x);
         i = pre;
@@ -359,6 +373,7 @@ __global__ void __launch_bounds__(kGemmThreads, ctas_per_sm(NT))
   }
   tc_fence_before();
   __syncthreads();
+  if (timeline && threadIdx.x == 0) atomicMax(timeline + 3, global_ns());
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
@@ -481,7 +496,7 @@ int launch_tc(const GemmCall& c, cudaStream_t stream) {
   if (c.head) h = HeadArgs{c.head->tile_val, c.head->tile_idx, c.head->rows_alloc, c.head->store_logits ? 1 : 0};
   const int splits = c.head ? 1 : W.splits;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(W.N_pad / kTileN, splits, ceil_div(c.M, NT));
+  cfg.gridDim = dim3(ceil_div(c.M, NT), splits, W.N_pad / kTileN);
   cfg.blockDim = dim3(kGemmThreads);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
@@ -492,11 +507,12 @@ int launch_tc(const GemmCall& c, cudaStream_t stream) {
   const bool pdl = pdl_enabled();
   cfg.numAttrs = pdl ? 1 : 0;
   // L2 prefetch budget of one GEMM: about 40 MB of weight tiles beyond the pipeline stages, spread over its CTAs
-  const int ctas = int(cfg.gridDim.x * cfg.gridDim.y);
+  const int ctas = int(cfg.gridDim.z * cfg.gridDim.y);
   const int l2_slabs = std::min(64, int((size_t(40) << 20) / (size_t(ctas) * kABytes)));
   LB_CUDA(cudaLaunchKernelEx(&cfg, gemm_fp8_tcgen05_kernel<NT>, W.map, X.map[NT / 32 - 1], (const float*)W.scales,
                              (const float*)X.scales, c.out, c.ld, c.split_stride, c.M, W.N, W.N_pad, W.KB, splits,
-                             X.rows_alloc, h, c.err_flag, pdl ? 1 : 0, pdl && cfg.gridDim.z == 1 ? l2_slabs : 0));
+                             X.rows_alloc, h, c.err_flag, pdl ? 1 : 0, pdl && cfg.gridDim.x == 1 ? l2_slabs : 0,
+                             c.timeline));
   return LING_B200_OK;
 }
 
@@ -525,12 +541,13 @@ int token_tile(int M) { return M <= 32 ? 32 : M <= 64 ? 64 : M <= 96 ? 96 : 128;
 
 int choose_splits(int N_pad, int KB, int sm_count) {
   const int tiles = N_pad / kTileN;
-  // Two resident CTAs per SM for the narrow token tiles: aim at about 2 x SMs work items, keep at least four
-  // K blocks per split so that the prologue and the partial-sum traffic stay small.
-  int s = (2 * sm_count + tiles / 2) / tiles;
+  // Two CTAs are resident per SM for the narrow token tiles: as many splits as keep tiles x splits within one wave
+  // (2 x SMs), at least four K blocks per split so that the prologue and the partial-sum traffic stay small, at most
+  // kMaxPlanes-many planes for the consumers to add.
+  int s = (2 * sm_count) / tiles;
   s = std::min(s, KB / 4);
   s = std::max(s, 1);
-  return std::min(s, 8);  // consumers add at most 8 partial planes
+  return std::min(s, 8);
 }
 
 int gemm_launch(const GemmCall& c, cudaStream_t stream) {

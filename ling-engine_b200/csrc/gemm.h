@@ -51,6 +51,7 @@ struct GemmCall {
   const HeadEpilogue* head = nullptr;
   int impl = 0;             // 0 tcgen05, 1 CUDA cores
   int* err_flag = nullptr;
+  unsigned long long* timeline = nullptr;  // four stamps of this launch (debugging aid), or nullptr
 };
 
 // Creates the tensor maps (driver entry point fetched at run time; no link against libcuda).

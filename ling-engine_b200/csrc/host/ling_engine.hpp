@@ -9,6 +9,7 @@
 #include <deque>
 #include <exception>
 #include <functional>
+#include <memory>
 #include <span>
 #include <stdexcept>
 #include <string>

@@ -5,6 +5,8 @@
 // of the same capacity class.  Citations name the reference project's files (dreamference/ling-engine).
 #include "kernels.h"
 
+#include <cooperative_groups.h>
+
 #include <cfloat>
 
 namespace lb {
@@ -190,51 +192,54 @@ __global__ void __launch_bounds__(32) pack_kernel(StepBuffers sb, ModelDims d) {
 // h[m] (+= the previous GEMM's partial sums, or = the embedding row) -> Gemma RMSNorm x * rsqrt(mean x^2 + eps) *
 // (1 + w) (src/core/kernels.cu:280-301) -> fp32 copy (for the BF16 a/b projections) and the FP8 copy for the GEMMs
 // (the reference's rmsnorm_half, src/core/stream_gemm.cu:383-418, at block-scaled FP8 instead of scaled FP16).
-constexpr int kNormChunks = 8;  // float4 chunks per thread: H <= 8192
+// One thread-block cluster per row: CTA j of the cluster owns columns [1024 j, 1024 j + 1024) (four per thread), the
+// partial sums of squares meet through distributed shared memory, and every CTA normalizes and quantizes its own 1024
+// columns (eight 128-column blocks, one per warp).  H <= 8192 keeps the cluster within the portable size of 8.
 __global__ void __launch_bounds__(256)
     norm_quant_kernel(float* __restrict__ h, Planes add, const int* __restrict__ ids, const __nv_bfloat16* __restrict__ embed,
                       const __nv_bfloat16* __restrict__ w, float* __restrict__ xn, QuantOut q, const int* __restrict__ n_rows,
                       int H, float eps) {
   pdl_sync();  // first statement: see common.cuh
+  namespace cg = cooperative_groups;
   __shared__ float red[32];
-  const int m = blockIdx.x;
-  if (m >= *n_rows) return;
-  float4 v[kNormChunks];
-  float ss = 0.f;
-#pragma unroll
-  for (int j = 0; j < kNormChunks; ++j) {
-    const int c = j * 1024 + threadIdx.x * 4;
-    v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (c < H) {
-      if (ids) {
-        const __nv_bfloat16* e = embed + size_t(ids[m]) * H + c;
-        v[j] = make_float4(__bfloat162float(e[0]), __bfloat162float(e[1]), __bfloat162float(e[2]), __bfloat162float(e[3]));
-      } else {
-        v[j] = *reinterpret_cast<const float4*>(h + size_t(m) * H + c);
-        if (add.p) {
-          const float4 t = plane_sum4(add, m, c);
-          v[j].x += t.x, v[j].y += t.y, v[j].z += t.z, v[j].w += t.w;
-        }
+  __shared__ float part;
+  const int m = blockIdx.y;
+  if (m >= *n_rows) return;  // the whole cluster shares the row, so it leaves together
+  const int c = blockIdx.x * 1024 + threadIdx.x * 4;
+  float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (c < H) {
+    if (ids) {
+      const __nv_bfloat16* e = embed + size_t(ids[m]) * H + c;
+      v = make_float4(__bfloat162float(e[0]), __bfloat162float(e[1]), __bfloat162float(e[2]), __bfloat162float(e[3]));
+    } else {
+      v = *reinterpret_cast<const float4*>(h + size_t(m) * H + c);
+      if (add.p) {
+        const float4 t = plane_sum4(add, m, c);
+        v.x += t.x, v.y += t.y, v.z += t.z, v.w += t.w;
       }
-      *reinterpret_cast<float4*>(h + size_t(m) * H + c) = v[j];
-      ss += v[j].x * v[j].x + v[j].y * v[j].y + v[j].z * v[j].z + v[j].w * v[j].w;
     }
+    *reinterpret_cast<float4*>(h + size_t(m) * H + c) = v;
   }
-  const float rstd = rsqrtf(block_sum(ss, red) / H + eps);
-#pragma unroll
-  for (int j = 0; j < kNormChunks; ++j) {
-    const int c = j * 1024 + threadIdx.x * 4;
-    if (c - (threadIdx.x & 31) * 4 >= q.K_pad) break;  // warp-uniform: the warp's block starts past the padding
-    float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (c < H) {
-      x.x = v[j].x * rstd * (1.f + __bfloat162float(w[c]));
-      x.y = v[j].y * rstd * (1.f + __bfloat162float(w[c + 1]));
-      x.z = v[j].z * rstd * (1.f + __bfloat162float(w[c + 2]));
-      x.w = v[j].w * rstd * (1.f + __bfloat162float(w[c + 3]));
-      if (xn) *reinterpret_cast<float4*>(xn + size_t(m) * H + c) = x;
-    }
-    quant_store4(x, c, m, q);
+  const float ss = block_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w, red);
+  float total = ss;
+  if (gridDim.x > 1) {
+    cg::cluster_group cluster = cg::this_cluster();
+    if (threadIdx.x == 0) part = ss;
+    cluster.sync();
+    total = 0.f;
+    for (unsigned r = 0; r < cluster.num_blocks(); ++r) total += *cluster.map_shared_rank(&part, r);  // rank order: every CTA gets the same sum
+    cluster.sync();  // no CTA leaves while its partial may still be read
   }
+  const float rstd = rsqrtf(total / H + eps);
+  float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (c < H) {
+    x.x = v.x * rstd * (1.f + __bfloat162float(w[c]));
+    x.y = v.y * rstd * (1.f + __bfloat162float(w[c + 1]));
+    x.z = v.z * rstd * (1.f + __bfloat162float(w[c + 2]));
+    x.w = v.w * rstd * (1.f + __bfloat162float(w[c + 3]));
+    if (xn) *reinterpret_cast<float4*>(xn + size_t(m) * H + c) = x;
+  }
+  if (c - (threadIdx.x & 31) * 4 < q.K_pad) quant_store4(x, c, m, q);
 }
 
 __global__ void __launch_bounds__(256)
@@ -247,28 +252,32 @@ __global__ void __launch_bounds__(256)
 }
 
 // a = xn . W_a^T, b = xn . W_b^T against BF16 weights with fp32 accumulation (src/core/kernels.cu:200-253), then the
-// gating g = -exp(A_log) * softplus(a + dt_bias), beta = sigmoid(b) (src/core/kernels.cu:385-395).  One warp per
-// (row, value head).
-__global__ void __launch_bounds__(256)
+// gating g = -exp(A_log) * softplus(a + dt_bias), beta = sigmoid(b) (src/core/kernels.cu:385-395).  One block per
+// (value head, row): 128 threads split the hidden dimension four columns at a time.
+__global__ void __launch_bounds__(128)
     ab_gating_kernel(const float* __restrict__ xn, const __nv_bfloat16* __restrict__ wa, const __nv_bfloat16* __restrict__ wb,
                      const __nv_bfloat16* __restrict__ A_log, const __nv_bfloat16* __restrict__ dt_bias, float* __restrict__ g,
                      float* __restrict__ beta, const int* __restrict__ n_rows, int H, int HV) {
   pdl_sync();  // first statement: see common.cuh
-  const int hv = blockIdx.x, m = blockIdx.y * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  __shared__ float red[32];
+  const int hv = blockIdx.x, m = blockIdx.y;
   if (m >= *n_rows) return;
   const float* x = xn + size_t(m) * H;
   const __nv_bfloat16* a = wa + size_t(hv) * H;
   const __nv_bfloat16* b = wb + size_t(hv) * H;
   float sa = 0.f, sb2 = 0.f;
-  for (int c = lane * 4; c < H; c += 128) {
+#pragma unroll 4
+  for (int c = threadIdx.x * 4; c < H; c += 512) {
     const float4 xv = *reinterpret_cast<const float4*>(x + c);
-    sa += xv.x * __bfloat162float(a[c]) + xv.y * __bfloat162float(a[c + 1]) + xv.z * __bfloat162float(a[c + 2]) +
-          xv.w * __bfloat162float(a[c + 3]);
-    sb2 += xv.x * __bfloat162float(b[c]) + xv.y * __bfloat162float(b[c + 1]) + xv.z * __bfloat162float(b[c + 2]) +
-           xv.w * __bfloat162float(b[c + 3]);
+    const uint2 ar = *reinterpret_cast<const uint2*>(a + c), br = *reinterpret_cast<const uint2*>(b + c);
+    const __nv_bfloat162 a01 = *reinterpret_cast<const __nv_bfloat162*>(&ar.x), a23 = *reinterpret_cast<const __nv_bfloat162*>(&ar.y);
+    const __nv_bfloat162 b01 = *reinterpret_cast<const __nv_bfloat162*>(&br.x), b23 = *reinterpret_cast<const __nv_bfloat162*>(&br.y);
+    sa += xv.x * __low2float(a01) + xv.y * __high2float(a01) + xv.z * __low2float(a23) + xv.w * __high2float(a23);
+    sb2 += xv.x * __low2float(b01) + xv.y * __high2float(b01) + xv.z * __low2float(b23) + xv.w * __high2float(b23);
   }
-  sa = warp_sum(sa), sb2 = warp_sum(sb2);
-  if (lane == 0) {
+  sa = block_sum(sa, red);
+  sb2 = block_sum(sb2, red);
+  if (threadIdx.x == 0) {
     const float xx = sa + __bfloat162float(dt_bias[hv]);
     const float sp = xx <= 20.f ? log1pf(__expf(xx)) : xx;
     g[size_t(m) * HV + hv] = -__expf(__bfloat162float(A_log[hv])) * sp;
@@ -324,64 +333,92 @@ __global__ void __launch_bounds__(256)
 // One token of the gated delta rule (src/core/kernels.cu:402-453) for 8 value columns of a head.  A warp is 8 columns x 4
 // quarters of the key dimension: lane = quarter * 8 + column holds S[quarter * DK/4 .. +DK/4][column], so the two
 // dependent dot products are DK/4 long (four interleaved partial sums each) plus two shuffles.  q^ and k^ arrive
-// normalized.  S *= decay; kv = S^T k; d = (v - kv) beta; S += k d^T; o = S^T q.  advance = false is the leaf rule
-// (src/core/attention_body.cuh:575-603): the output from the parent's state, which stays as it was.
+// normalized, staged in shared memory with each quarter's segment padded by 16 bytes so that the four quarters of a warp
+// read four different bank groups.  S *= decay; kv = S^T k; d = (v - kv) beta; S += k d^T; o = S^T q.  advance = false is
+// the leaf rule (src/core/attention_body.cuh:575-603): the output from the parent's state, which stays as it was.
 template <int DK>
-struct DeltaIn {
-  float k[DK / 4], q[DK / 4];
-  float v, g, beta;
-  __device__ __forceinline__ void load(const float* __restrict__ row, const float* __restrict__ g_row, const float* __restrict__ b_row,
-                                       int h, int hv, int Hk, int Dv, int col, int quarter) {
-    constexpr int KL = DK / 4;
-    const float4* kp = reinterpret_cast<const float4*>(row + Hk * DK + h * DK + quarter * KL);
-    const float4* qp = reinterpret_cast<const float4*>(row + h * DK + quarter * KL);
+struct GdnStage {
+  static constexpr int KL = DK / 4, SEG = KL + 4, ROW = 8 * SEG;  // floats per step: q quarters 0-3, then k quarters 0-3
+  // Stages `len` steps' q^, k^, v, g, beta of (key head h, value head hv) into shared memory, all threads of the block.
+  __device__ static void load(const float* __restrict__ post, const float* __restrict__ g, const float* __restrict__ beta, int C,
+                              int Hk, int HV, int Dv, int h, int hv, size_t r0, const int* rows, int len, float* qk, float* vv,
+                              float* gb) {
+    constexpr int V4 = 2 * DK / 4;  // float4 pieces of one step's q and k
+    for (int idx = threadIdx.x; idx < len * V4; idx += blockDim.x) {
+      const int i = idx / V4, part = idx % V4, isk = part >= DK / 4, e = (isk ? part - DK / 4 : part) * 4;
+      const float* src = post + (r0 + rows[i]) * C + (isk ? Hk * DK : 0) + h * DK + e;
+      *reinterpret_cast<float4*>(qk + size_t(i) * ROW + (isk ? 4 * SEG : 0) + (e / KL) * SEG + e % KL) =
+          *reinterpret_cast<const float4*>(src);
+    }
+    for (int idx = threadIdx.x; idx < len * (Dv / 4); idx += blockDim.x) {
+      const int i = idx / (Dv / 4), e = (idx % (Dv / 4)) * 4;
+      *reinterpret_cast<float4*>(vv + size_t(i) * Dv + e) =
+          *reinterpret_cast<const float4*>(post + (r0 + rows[i]) * C + 2 * Hk * DK + hv * Dv + e);
+    }
+    for (int i = threadIdx.x; i < len; i += blockDim.x) {
+      gb[2 * i] = g[(r0 + rows[i]) * HV + hv];
+      gb[2 * i + 1] = beta[(r0 + rows[i]) * HV + hv];
+    }
+  }
+  __device__ __forceinline__ static float token(float (&S)[KL], const float* qk_i, float v, float gval, float bval, int quarter,
+                                                bool advance) {
+    const float4* kp = reinterpret_cast<const float4*>(qk_i + 4 * SEG + quarter * SEG);
+    const float4* qp = reinterpret_cast<const float4*>(qk_i + quarter * SEG);
+    const float decay = __expf(gval);
+    float k[KL], Sd[KL], part[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int i = 0; i < KL / 4; ++i) {
-      const float4 a = kp[i], b = qp[i];
+      const float4 a = kp[i];
       k[4 * i] = a.x, k[4 * i + 1] = a.y, k[4 * i + 2] = a.z, k[4 * i + 3] = a.w;
-      q[4 * i] = b.x, q[4 * i + 1] = b.y, q[4 * i + 2] = b.z, q[4 * i + 3] = b.w;
     }
-    v = row[2 * Hk * DK + hv * Dv + col];
-    g = g_row[hv], beta = b_row[hv];
+#pragma unroll
+    for (int i = 0; i < KL; ++i) {
+      Sd[i] = S[i] * decay;
+      part[i & 3] = fmaf(Sd[i], k[i], part[i & 3]);
+    }
+    float kv = (part[0] + part[1]) + (part[2] + part[3]);
+    kv += __shfl_xor_sync(0xffffffffu, kv, 8);
+    kv += __shfl_xor_sync(0xffffffffu, kv, 16);
+    const float dlt = (v - kv) * bval;
+    part[0] = part[1] = part[2] = part[3] = 0.f;
+#pragma unroll
+    for (int i = 0; i < KL / 4; ++i) {
+      const float4 qv = qp[i];
+      const float qq[4] = {qv.x, qv.y, qv.z, qv.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float sn = fmaf(dlt, k[4 * i + j], Sd[4 * i + j]);
+        part[j] = fmaf(sn, qq[j], part[j]);
+        if (advance) S[4 * i + j] = sn;
+      }
+    }
+    float o = (part[0] + part[1]) + (part[2] + part[3]);
+    o += __shfl_xor_sync(0xffffffffu, o, 8);
+    o += __shfl_xor_sync(0xffffffffu, o, 16);
+    return o;
   }
+  static size_t smem_bytes(int Dv) { return size_t(2 * kTreeRows) * (ROW + Dv + 2) * 4; }
 };
-template <int DK>
-__device__ __forceinline__ float delta_token(float (&S)[DK / 4], const DeltaIn<DK>& x, bool advance) {
-  constexpr int KL = DK / 4;
-  const float decay = __expf(x.g);
-  float part[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-  for (int i = 0; i < KL; ++i) part[i & 3] = fmaf(S[i] * decay, x.k[i], part[i & 3]);
-  float kv = (part[0] + part[1]) + (part[2] + part[3]);
-  kv += __shfl_xor_sync(0xffffffffu, kv, 8);
-  kv += __shfl_xor_sync(0xffffffffu, kv, 16);
-  const float dlt = (x.v - kv) * x.beta;
-  part[0] = part[1] = part[2] = part[3] = 0.f;
-#pragma unroll
-  for (int i = 0; i < KL; ++i) {
-    const float sn = fmaf(dlt, x.k[i], S[i] * decay);
-    part[i & 3] = fmaf(sn, x.q[i], part[i & 3]);
-    if (advance) S[i] = sn;
-  }
-  float o = (part[0] + part[1]) + (part[2] + part[3]);
-  o += __shfl_xor_sync(0xffffffffu, o, 8);
-  o += __shfl_xor_sync(0xffffffffu, o, 16);
-  return o;
-}
 
 // The verify's recurrence over every sequence's tree (src/core/kernels.cu:455-477): a work item is (sequence, DeltaNet
-// path, value head, 8 value columns); its warp walks the path's steps from the session's state (never written here) and
-// writes the rows flagged kWrite.  The next step's inputs are loaded while the current one is computed.  A fixed grid
-// of warps strides over the items.
+// path, value head); its block (one warp per 8 value columns) first stages the whole path's inputs in shared memory with
+// one round of coalesced loads, then walks the steps from the session's state (never written here) and writes the rows
+// flagged kWrite.  A fixed grid of blocks strides over the items.
+constexpr int kGdnCols = 32;  // value columns per block of the DeltaNet kernels (4 warps x 8 columns)
 template <int DK>
 __global__ void __launch_bounds__(128)
     gdn_tree_kernel(const float* __restrict__ post, const float* __restrict__ g, const float* __restrict__ beta, StepBuffers sb,
                     int Hk, int HV, int Dv, const float* __restrict__ state, size_t slot_stride, float* __restrict__ core) {
   pdl_sync();  // first statement: see common.cuh
-  constexpr int KL = DK / 4;
+  using St = GdnStage<DK>;
+  constexpr int KL = St::KL;
+  extern __shared__ __align__(16) float gsm[];
+  float* qk = gsm;                                         // [64][ROW]
+  float* vv = qk + size_t(2 * kTreeRows) * St::ROW;        // [64][Dv]
+  float* gb = vv + size_t(2 * kTreeRows) * Dv;             // [64][2]
   __shared__ int pbase[LING_B200_MAX_SEQS + 1];
-  __shared__ int steps_all[4][2 * kTreeRows];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, quarter = lane >> 3, cl = lane & 7;
+  __shared__ int steps[2 * kTreeRows], rows[2 * kTreeRows];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, quarter = lane >> 3;
   const int nseq = *sb.n_seqs;
   if (threadIdx.x == 0) {
     int acc = 0;
@@ -392,87 +429,76 @@ __global__ void __launch_bounds__(128)
     pbase[nseq] = acc;
   }
   __syncthreads();
-  int* steps = steps_all[warp];
-  const int groups = Dv / 8, C = 2 * Hk * DK + HV * Dv;
-  const int per_path = HV * groups;
-  const int total = pbase[nseq] * per_path;
-  for (int item = blockIdx.x * 4 + warp; item < total; item += gridDim.x * 4) {
-    const int pg = item / per_path, rem = item % per_path, hv = rem / groups, col = (rem % groups) * 8 + cl;
+  const int C = 2 * Hk * DK + HV * Dv, groups = Dv / kGdnCols;
+  const int total = pbase[nseq] * HV * groups;
+  for (int item = blockIdx.x; item < total; item += gridDim.x) {
+    const int pg = item / (HV * groups), hv = (item / groups) % HV, col = (item % groups) * kGdnCols + warp * 8 + (lane & 7);
     int s = 0;
     while (pbase[s + 1] <= pg) ++s;
     const int pth = pg - pbase[s], h = hv / (HV / Hk);
     const ling_b200_tree_desc* td = sb.trees + s;
     const size_t r0 = size_t(sb.row0[s]);
+    const int len = td->gdn_len[pth];
+    __syncthreads();  // the previous item's readers of the staged inputs are done
+    for (int i = threadIdx.x; i < len; i += blockDim.x) {
+      steps[i] = td->gdn_step[pth][i];
+      rows[i] = steps[i] & 0xff;
+    }
     const float* st = state + size_t(sb.seqs[s].slot) * slot_stride + size_t(hv) * DK * Dv;
     float S[KL];
 #pragma unroll
     for (int i = 0; i < KL; ++i) S[i] = st[size_t(quarter * KL + i) * Dv + col];
-    const int len = td->gdn_len[pth];
-    __syncwarp();
-    for (int i = lane; i < len; i += 32) steps[i] = td->gdn_step[pth][i];
-    __syncwarp();
-    DeltaIn<DK> nxt;
-    if (len > 0) {
-      const size_t row = r0 + (steps[0] & 0xff);
-      nxt.load(post + row * C, g + row * HV, beta + row * HV, h, hv, Hk, Dv, col, quarter);
-    }
+    __syncthreads();
+    St::load(post, g, beta, C, Hk, HV, Dv, h, hv, r0, rows, len, qk, vv, gb);
+    __syncthreads();
     for (int i = 0; i < len; ++i) {
-      const DeltaIn<DK> cur = nxt;
       const int st_i = steps[i];
-      if (i + 1 < len) {
-        const size_t row = r0 + (steps[i + 1] & 0xff);
-        nxt.load(post + row * C, g + row * HV, beta + row * HV, h, hv, Hk, Dv, col, quarter);
-      }
-      const float o = delta_token<DK>(S, cur, (st_i & kLeaf) == 0);
+      const float o = St::token(S, qk + size_t(i) * St::ROW, vv[size_t(i) * Dv + col], gb[2 * i], gb[2 * i + 1], quarter,
+                                (st_i & kLeaf) == 0);
       if ((st_i & kWrite) && quarter == 0) core[(r0 + (st_i & 0xff)) * HV * Dv + size_t(hv) * Dv + col] = o;
     }
   }
 }
 
 // Engine::commit (src/core/speculate.cpp:516-529), the recurrence half: the accepted rows path[0..n) replayed from the
-// session's state over their saved conv outputs, the state written back.  Item = (sequence, layer, head, 8 columns).
+// session's state over their saved conv outputs, the state written back.  Item = (sequence, layer, value head).
 template <int DK>
 __global__ void __launch_bounds__(128)
     gdn_commit_kernel(const float* __restrict__ post, const float* __restrict__ g, const float* __restrict__ beta,
                       size_t post_layer_stride, size_t g_layer_stride, StepBuffers sb, int Hk, int HV, int Dv, int n_gdn,
                       float* __restrict__ state, size_t slot_stride, size_t layer_stride) {
   pdl_sync();  // first statement: see common.cuh
-  constexpr int KL = DK / 4;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, quarter = lane >> 3, cl = lane & 7;
+  using St = GdnStage<DK>;
+  constexpr int KL = St::KL;
+  extern __shared__ __align__(16) float gsm[];
+  float* qk = gsm;
+  float* vv = qk + size_t(2 * kTreeRows) * St::ROW;
+  float* gb = vv + size_t(2 * kTreeRows) * Dv;
+  __shared__ int rows[2 * kTreeRows];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, quarter = lane >> 3;
   const int nseq = *sb.n_seqs;
-  const int groups = Dv / 8, C = 2 * Hk * DK + HV * Dv;
+  const int C = 2 * Hk * DK + HV * Dv, groups = Dv / kGdnCols;
   const int per_seq = n_gdn * HV * groups;
   const int total = nseq * per_seq;
-  for (int item = blockIdx.x * 4 + warp; item < total; item += gridDim.x * 4) {
-    const int s = item / per_seq;
-    int rem = item % per_seq;
-    const int gl = rem / (HV * groups);
-    rem %= HV * groups;
-    const int hv = rem / groups, col = (rem % groups) * 8 + cl, h = hv / (HV / Hk);
+  for (int item = blockIdx.x; item < total; item += gridDim.x) {
+    const int s = item / per_seq, gl = (item % per_seq) / (HV * groups), hv = (item / groups) % HV, h = hv / (HV / Hk);
+    const int col = (item % groups) * kGdnCols + warp * 8 + (lane & 7);
     const ling_b200_seq_result* R = sb.results + s;
-    if (R->status != 0) continue;
+    if (R->status != 0) continue;  // block-uniform
     const size_t r0 = size_t(sb.row0[s]);
     const int n = R->n_path;
+    __syncthreads();
+    for (int i = threadIdx.x; i < n; i += blockDim.x) rows[i] = R->path[i];
     float* st = state + size_t(sb.seqs[s].slot) * slot_stride + size_t(gl) * layer_stride + size_t(hv) * DK * Dv;
     float S[KL];
 #pragma unroll
     for (int i = 0; i < KL; ++i) S[i] = st[size_t(quarter * KL + i) * Dv + col];
-    const float* P = post + size_t(gl) * post_layer_stride;
-    const float* G = g + size_t(gl) * g_layer_stride;
-    const float* B = beta + size_t(gl) * g_layer_stride;
-    DeltaIn<DK> nxt;
-    if (n > 0) {
-      const size_t row = r0 + R->path[0];
-      nxt.load(P + row * C, G + row * HV, B + row * HV, h, hv, Hk, Dv, col, quarter);
-    }
-    for (int j = 0; j < n; ++j) {
-      const DeltaIn<DK> cur = nxt;
-      if (j + 1 < n) {
-        const size_t row = r0 + R->path[j + 1];
-        nxt.load(P + row * C, G + row * HV, B + row * HV, h, hv, Hk, Dv, col, quarter);
-      }
-      delta_token<DK>(S, cur, true);
-    }
+    __syncthreads();
+    St::load(post + size_t(gl) * post_layer_stride, g + size_t(gl) * g_layer_stride, beta + size_t(gl) * g_layer_stride, C, Hk, HV,
+             Dv, h, hv, r0, rows, n, qk, vv, gb);
+    __syncthreads();
+    for (int i = 0; i < n; ++i)
+      St::token(S, qk + size_t(i) * St::ROW, vv[size_t(i) * Dv + col], gb[2 * i], gb[2 * i + 1], quarter, true);
 #pragma unroll
     for (int i = 0; i < KL; ++i) st[size_t(quarter * KL + i) * Dv + col] = S[i];
   }
@@ -507,9 +533,9 @@ __global__ void __launch_bounds__(256)
   const int m = blockIdx.x;
   if (m >= *n_rows) return;
   const int seg = Dv / 4;  // lanes per head
-  for (int c0 = 0; c0 < q.K_pad; c0 += 1024) {
-    const int c = c0 + threadIdx.x * 4;
-    if (c - (threadIdx.x & 31) * 4 >= q.K_pad) break;
+  {
+    const int c = blockIdx.y * 1024 + threadIdx.x * 4;
+    if (c - (threadIdx.x & 31) * 4 >= q.K_pad) return;  // warp-uniform
     float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
     float4 zz = x;
     if (c < Vs) {
@@ -536,9 +562,9 @@ __global__ void __launch_bounds__(256)
   pdl_sync();  // first statement: see common.cuh
   const int m = blockIdx.x;
   if (m >= *n_rows) return;
-  for (int c0 = 0; c0 < q.K_pad; c0 += 1024) {
-    const int c = c0 + threadIdx.x * 4;
-    if (c - (threadIdx.x & 31) * 4 >= q.K_pad) break;
+  {
+    const int c = blockIdx.y * 1024 + threadIdx.x * 4;
+    if (c - (threadIdx.x & 31) * 4 >= q.K_pad) return;  // warp-uniform
     float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
     if (c < I) {
       const float4 a = plane_sum4(gu, m, c), b = plane_sum4(gu, m, I + c);
@@ -600,9 +626,8 @@ __global__ void attn_prepare_kernel(Planes qkv, StepBuffers sb, ModelDims d, int
     if (dd == 0) dev_fail(sb.err, kDevBadPage);
     return;
   }
-  const size_t at = kv_slot_index(d, al, is_v ? 1 : 0, head, page, pos % d.page_tokens);
-  kv.codes[at * D + dd] = to_e4m3(__fdiv_rn(x, sc));
-  if (dd == 0) kv.scales[at] = sc;
+  kv.codes[kv_code_index(d, al, is_v ? 1 : 0, head, page, pos % d.page_tokens, dd)] = to_e4m3(__fdiv_rn(x, sc));
+  if (dd == 0) kv.scales[kv_slot_index(d, al, is_v ? 1 : 0, head, page, pos % d.page_tokens)] = sc;
 }
 
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, int src_bytes) {
@@ -636,9 +661,14 @@ constexpr float kPScale = 256.f;  // p * v_scale is carried in FP16 times this p
 // of sequences).  Work item = (sequence, kv head, key chunk, 64 query rows); the query rows of a kv head are
 // (token row, q head of the group) pairs, so one pass over a K/V tile serves every row of the tree and every q head
 // of the group.  Context chunks hold kAttnChunk keys; the last chunk of a sequence is its in-flight rows (cache slots
-// pos .. pos + n_rows), visible to a row only where its ancestor mask has the bit.  K/V tiles come through cp.async in
-// 16-byte pieces into double-buffered shared memory and stay E4M3 there; fragments are converted on load
-// (cvt.f16x2.e4m3x2) and the per-position scales are applied to scores and probabilities in fp32.
+// pos .. pos + n_rows), read from the 16-aligned position below pos so that every copy stays 16-byte aligned; a row sees
+// an in-flight key only where its ancestor mask has the bit.  K tiles ([key][D]) and V tiles ([D][key], the pool's V
+// layout) arrive by 16-byte cp.async into double-buffered shared memory and stay E4M3 there; fragments are converted on
+// load (cvt.f16x2.e4m3x2) and the per-position scales are applied to scores and probabilities in fp32.
+// Shared-memory traffic is what bounds the inner loops, so the fragment loads are wide: the reduction index of
+// Q.K^T is permuted within each group of 16 dims (thread t of a quad takes physical dims 4t .. 4t+3 as logical k
+// 2t, 2t+1, 2t+8, 2t+9: one 64-bit load of Q and one 32-bit load of K per MMA), and the V fragment of 16 keys is one
+// 128-bit load shared by the quad.
 // Output: per (chunk slot, query row) the unnormalized sum and (max, denominator); attn_combine_kernel merges chunks.
 template <int D, int G>
 __global__ void __launch_bounds__(128, (D > 128 ? 2 : 4))
@@ -646,14 +676,15 @@ __global__ void __launch_bounds__(128, (D > 128 ? 2 : 4))
                      float* __restrict__ part_ml, int chunk_slots) {
   pdl_sync();  // first statement: see common.cuh
   constexpr int QS = D + 8;    // halves per Q row in shared memory
-  constexpr int KS = D + 16;   // bytes per K/V row in shared memory
+  constexpr int KS = D + 16;   // bytes per K row (one key) in shared memory
+  constexpr int VS = kAttnKeyTile + 16;  // bytes per V row (one dim, 64 keys) in shared memory
   constexpr int RMAX = kTreeRows * G;
   extern __shared__ __align__(16) uint8_t smem[];
-  __half* Qs = reinterpret_cast<__half*>(smem);                     // [64][QS]
-  uint8_t* Ks8 = smem + size_t(kAttnRowTile) * QS * 2;              // [2][64][KS]
-  uint8_t* Vs8 = Ks8 + 2 * kAttnKeyTile * KS;                       // [2][64][KS]
-  float* ksc = reinterpret_cast<float*>(Vs8 + 2 * kAttnKeyTile * KS);  // [2][64]
-  float* vsc = ksc + 2 * kAttnKeyTile;                              // [2][64]
+  __half* Qs = reinterpret_cast<__half*>(smem);                         // [64][QS]
+  uint8_t* Ks8 = smem + size_t(kAttnRowTile) * QS * 2;                  // [2][64][KS]
+  uint8_t* Vs8 = Ks8 + 2 * kAttnKeyTile * KS;                           // [2][D][VS]
+  float* ksc = reinterpret_cast<float*>(Vs8 + 2 * D * VS);              // [2][64]
+  float* vsc = ksc + 2 * kAttnKeyTile;                                  // [2][64]
   __shared__ int cbase[LING_B200_MAX_SEQS + 1], ibase[LING_B200_MAX_SEQS + 1];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g8 = lane >> 2, t4 = lane & 3;
@@ -670,7 +701,7 @@ __global__ void __launch_bounds__(128, (D > 128 ? 2 : 4))
   }
   __syncthreads();
   const float inv_sqrt_d = rsqrtf(float(D));
-  const size_t page_elems = size_t(d.page_tokens);
+  const int pt = d.page_tokens;
 
   for (int item = blockIdx.x; item < ibase[nseq]; item += gridDim.x) {
     int s = 0;
@@ -686,10 +717,13 @@ __global__ void __launch_bounds__(128, (D > 128 ? 2 : 4))
       continue;
     }
     const bool tail = ch == nch - 1;
-    const int key_base = tail ? sq.pos : ch * kAttnChunk;
-    const int key_count = tail ? sq.n_rows : min(kAttnChunk, sq.pos - key_base);
+    // keys [key_base + key_lo, key_base + key_hi) count; a tail chunk starts at the 16-aligned position below pos
+    const int key_base = tail ? (sq.pos & ~15) : ch * kAttnChunk;
+    const int key_lo = tail ? sq.pos - key_base : 0;
+    const int key_hi = tail ? key_lo + sq.n_rows : min(kAttnChunk, sq.pos - key_base);
     const int R = sq.n_rows * G, r_begin = rg * kAttnRowTile, r0 = sb.row0[s];
     const int* table = kv.tables + size_t(sq.slot) * d.max_pages;
+    const size_t kpage0 = kv_slot_index(d, al, 0, hk, 0, 0), vpage0 = kv_slot_index(d, al, 1, hk, 0, 0);
 
     __syncthreads();  // the previous item's readers of Qs and the tiles are done
     for (int idx = threadIdx.x; idx < kAttnRowTile * (D / 8); idx += 128) {
@@ -699,27 +733,42 @@ __global__ void __launch_bounds__(128, (D > 128 ? 2 : 4))
       if (rr < R) val = *reinterpret_cast<const uint4*>(q + (size_t(r0 + rr / G) * d.Hq + hk * G + rr % G) * D + part * 8);
       *reinterpret_cast<uint4*>(Qs + size_t(r) * QS + part * 8) = val;
     }
+    auto page_of = [&](int pos) {
+      int page = table[pos / pt];
+      return (page < 0 || page > d.pool_pages) ? 0 : page;  // an unmapped position lands in the reserved page
+    };
     auto load_tile = [&](int tile, int buf) {
       const int k0 = tile * kAttnKeyTile;
+      // K: one key's D bytes are contiguous in its page
       for (int idx = threadIdx.x; idx < kAttnKeyTile * (D / 16); idx += 128) {
         const int key = idx / (D / 16), part = idx % (D / 16);
-        const bool valid = k0 + key < key_count;
+        const bool valid = k0 + key < key_hi;
         const int pos = key_base + k0 + key;
-        size_t at = 0;
-        if (valid) {
-          int page = table[pos / d.page_tokens];
-          if (page < 0 || page > d.pool_pages) page = 0;  // lands in the reserved page, as an unmapped position does
-          at = size_t(page) * page_elems + pos % d.page_tokens;
-        }
-        const size_t kat = kv_slot_index(d, al, 0, hk, 0, 0) + at, vat = kv_slot_index(d, al, 1, hk, 0, 0) + at;
-        cp_async16(Ks8 + (size_t(buf) * kAttnKeyTile + key) * KS + part * 16, kv.codes + kat * D + part * 16, valid ? 16 : 0);
-        cp_async16(Vs8 + (size_t(buf) * kAttnKeyTile + key) * KS + part * 16, kv.codes + vat * D + part * 16, valid ? 16 : 0);
+        const size_t at = valid ? size_t(page_of(pos)) * pt + pos % pt : 0;
+        cp_async16(Ks8 + (size_t(buf) * kAttnKeyTile + key) * KS + part * 16, kv.codes + (kpage0 + at) * D + part * 16, valid ? 16 : 0);
         if (part == 0) {
-          cp_async4(ksc + buf * kAttnKeyTile + key, kv.scales + kat, valid ? 4 : 0);
-          cp_async4(vsc + buf * kAttnKeyTile + key, kv.scales + vat, valid ? 4 : 0);
+          cp_async4(ksc + buf * kAttnKeyTile + key, kv.scales + kpage0 + at, valid ? 4 : 0);
+          cp_async4(vsc + buf * kAttnKeyTile + key, kv.scales + vpage0 + at, valid ? 4 : 0);
         }
       }
+      // V: one dim's 16 consecutive positions are contiguous in their page (pages hold a multiple of 16 positions)
+      for (int idx = threadIdx.x; idx < D * (kAttnKeyTile / 16); idx += 128) {
+        const int dd = idx / (kAttnKeyTile / 16), kc = (idx % (kAttnKeyTile / 16)) * 16;
+        const bool valid = k0 + kc < key_hi;
+        const int pos = key_base + k0 + kc;
+        const size_t src = valid ? (vpage0 + size_t(page_of(pos)) * pt) * D + size_t(dd) * pt + pos % pt : 0;
+        cp_async16(Vs8 + (size_t(buf) * D + dd) * VS + kc, kv.codes + src, valid ? 16 : 0);
+      }
       cp_async_commit();
+    };
+    // Positions past key_hi inside the last 16-position piece hold whatever the page held; their probability is zero,
+    // but 0 x NaN is NaN, so their V codes are cleared before use.
+    auto clear_v_tail = [&](int tile, int buf) {
+      const int k0 = tile * kAttnKeyTile, first = key_hi - k0;  // first invalid key of this tile
+      if (first >= kAttnKeyTile || (first & 15) == 0) return;
+      const int last = (first | 15) + 1;
+      for (int idx = threadIdx.x; idx < D * (last - first); idx += 128)
+        Vs8[(size_t(buf) * D + idx / (last - first)) * VS + first + idx % (last - first)] = 0;
     };
 
     float O[D / 8][4];
@@ -735,7 +784,7 @@ __global__ void __launch_bounds__(128, (D > 128 ? 2 : 4))
     }
     const bool warp_active = r_begin + warp * 16 < R;
 
-    const int ntiles = (key_count + kAttnKeyTile - 1) / kAttnKeyTile;
+    const int ntiles = (key_hi + kAttnKeyTile - 1) / kAttnKeyTile;
     load_tile(0, 0);
     for (int tile = 0; tile < ntiles; ++tile) {
       const int buf = tile & 1;
@@ -746,25 +795,26 @@ __global__ void __launch_bounds__(128, (D > 128 ? 2 : 4))
         cp_async_wait<0>();
       }
       __syncthreads();
+      if (tile == ntiles - 1) {
+        clear_v_tail(tile, buf);
+        __syncthreads();
+      }
       if (warp_active) {
         const uint8_t* Kt = Ks8 + size_t(buf) * kAttnKeyTile * KS;
-        const uint8_t* Vt = Vs8 + size_t(buf) * kAttnKeyTile * KS;
+        const uint8_t* Vt = Vs8 + size_t(buf) * D * VS;
         float S[8][4];
 #pragma unroll
         for (int i = 0; i < 8; ++i) S[i][0] = S[i][1] = S[i][2] = S[i][3] = 0.f;
-        const __half* qa = Qs + size_t(warp * 16 + g8) * QS;
+        const __half* qa = Qs + size_t(warp * 16 + g8) * QS + 4 * t4;
+        const uint8_t* ka = Kt + size_t(g8) * KS + 4 * t4;
 #pragma unroll 4
         for (int kt = 0; kt < D / 16; ++kt) {
-          const uint32_t a0 = *reinterpret_cast<const uint32_t*>(qa + kt * 16 + 2 * t4);
-          const uint32_t a1 = *reinterpret_cast<const uint32_t*>(qa + 8 * QS + kt * 16 + 2 * t4);
-          const uint32_t a2 = *reinterpret_cast<const uint32_t*>(qa + kt * 16 + 8 + 2 * t4);
-          const uint32_t a3 = *reinterpret_cast<const uint32_t*>(qa + 8 * QS + kt * 16 + 8 + 2 * t4);
+          const uint2 qA = *reinterpret_cast<const uint2*>(qa + kt * 16);           // row g8:     (a0, a2)
+          const uint2 qB = *reinterpret_cast<const uint2*>(qa + 8 * QS + kt * 16);  // row g8 + 8: (a1, a3)
 #pragma unroll
           for (int nt = 0; nt < 8; ++nt) {
-            const uint8_t* kr = Kt + size_t(nt * 8 + g8) * KS + kt * 16 + 2 * t4;
-            const uint32_t b0 = e4m3x2_to_h2(*reinterpret_cast<const uint16_t*>(kr));
-            const uint32_t b1 = e4m3x2_to_h2(*reinterpret_cast<const uint16_t*>(kr + 8));
-            mma_f16(S[nt], a0, a1, a2, a3, b0, b1);
+            const uint32_t kw = *reinterpret_cast<const uint32_t*>(ka + size_t(nt * 8) * KS + kt * 16);
+            mma_f16(S[nt], qA.x, qB.x, qA.y, qB.y, e4m3x2_to_h2(uint16_t(kw)), e4m3x2_to_h2(uint16_t(kw >> 16)));
           }
         }
         // scores: scale, mask, running max
@@ -775,8 +825,9 @@ __global__ void __launch_bounds__(128, (D > 128 ? 2 : 4))
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const int key = nt * 8 + 2 * t4 + (e & 1);
+            const int kk = k0 + key;  // index inside the chunk
             const uint32_t anc = (e < 2) ? ancA : ancB;
-            const bool vis = (k0 + key < key_count) && (!tail || ((anc >> (k0 + key)) & 1u));
+            const bool vis = kk >= key_lo && kk < key_hi && (!tail || ((anc >> (kk - key_lo)) & 1u));
             const float sv = vis ? S[nt][e] * (ksc[buf * kAttnKeyTile + key] * inv_sqrt_d) : -INFINITY;
             S[nt][e] = sv;
             tmax[e >> 1] = fmaxf(tmax[e >> 1], sv);
@@ -809,18 +860,18 @@ __global__ void __launch_bounds__(128, (D > 128 ? 2 : 4))
         }
 #pragma unroll
         for (int i = 0; i < D / 8; ++i) O[i][0] *= corr[0], O[i][1] *= corr[0], O[i][2] *= corr[1], O[i][3] *= corr[1];
-        // O += P . V
+        // O += P . V: the quad shares one 128-bit load of 16 keys of dim nt * 8 + g8 and picks its bytes
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {
           const uint32_t a0 = pack_h2(S[2 * kk][0], S[2 * kk][1]), a1 = pack_h2(S[2 * kk][2], S[2 * kk][3]);
           const uint32_t a2 = pack_h2(S[2 * kk + 1][0], S[2 * kk + 1][1]), a3 = pack_h2(S[2 * kk + 1][2], S[2 * kk + 1][3]);
-          const uint8_t* v0 = Vt + size_t(kk * 16 + 2 * t4) * KS + g8;
+          const uint8_t* v0 = Vt + size_t(g8) * VS + kk * 16;
 #pragma unroll
           for (int nt = 0; nt < D / 8; ++nt) {
-            const uint8_t* vp = v0 + nt * 8;
-            const uint16_t p0 = uint16_t(vp[0]) | (uint16_t(vp[KS]) << 8);
-            const uint16_t p1 = uint16_t(vp[8 * KS]) | (uint16_t(vp[9 * KS]) << 8);
-            mma_f16(O[nt], a0, a1, a2, a3, e4m3x2_to_h2(p0), e4m3x2_to_h2(p1));
+            const uint4 vw = *reinterpret_cast<const uint4*>(v0 + size_t(nt * 8) * VS);
+            const uint32_t lo = (t4 & 2) ? vw.y : vw.x, hi = (t4 & 2) ? vw.w : vw.z;  // keys 2t.. and 2t + 8..
+            const int sh = (t4 & 1) * 16;
+            mma_f16(O[nt], a0, a1, a2, a3, e4m3x2_to_h2(uint16_t(lo >> sh)), e4m3x2_to_h2(uint16_t(hi >> sh)));
           }
         }
       }
@@ -844,58 +895,50 @@ __global__ void __launch_bounds__(128, (D > 128 ? 2 : 4))
 
 // Merges a row's chunks in order (the reference's attention_combine, src/core/attention_body.cuh:506-525), applies the
 // output gate out * sigmoid(gate) (src/core/kernels.cu:314-318; the gate is the second D values of each q head's
-// projection) and writes the FP8 copy for the o projection.  One block per packed row: first every (q head, chunk)
-// weight exp(m_c - max) / sum, then the weighted sum over chunks with independent loads.
+// projection) and writes the FP8 copy for the o projection.  One block per (packed row, 1024 output columns); a thread
+// owns four columns of one head, a warp one 128-column quantization block.
 template <int G>
 __global__ void __launch_bounds__(256)
     attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, Planes qkv, StepBuffers sb,
-                        ModelDims d, QuantOut q, float* __restrict__ wbuf) {
+                        ModelDims d, QuantOut q, float* __restrict__ raw) {
   pdl_sync();  // first statement: see common.cuh
-  extern __shared__ float rowbuf[];  // [Hq * D]
   constexpr int RMAX = kTreeRows * G;
   const int m = blockIdx.x;
   if (m >= *sb.n_rows_total) return;
-  const int s = sb.seq_of[m], local = sb.local[m], D = d.D;
-  int cb = 0;
-  for (int t = 0; t < s; ++t) cb += (sb.seqs[t].pos + kAttnChunk - 1) / kAttnChunk + 1;
-  const int nch = (sb.seqs[s].pos + kAttnChunk - 1) / kAttnChunk + 1;
-  float* wrow = wbuf + size_t(m) * d.Hq * kMaxChunks;  // [Hq][nch] weights of this row
-  // one warp per q head: max over chunks, then the normalized weights
-  for (int hq = threadIdx.x >> 5; hq < d.Hq; hq += blockDim.x >> 5) {
-    const int lane = threadIdx.x & 31, hk = hq / G, r = local * G + hq % G;
-    const size_t base = size_t(cb) * d.Hkv + size_t(hk) * nch;
+  const int c = blockIdx.y * 1024 + threadIdx.x * 4;
+  if (c - (threadIdx.x & 31) * 4 >= q.K_pad) return;  // warp-uniform
+  float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (c < q.K) {
+    const int s = sb.seq_of[m], local = sb.local[m], D = d.D;
+    int cb = 0;
+    for (int t = 0; t < s; ++t) cb += (sb.seqs[t].pos + kAttnChunk - 1) / kAttnChunk + 1;
+    const int nch = (sb.seqs[s].pos + kAttnChunk - 1) / kAttnChunk + 1;
+    const int hq = c / D, dd = c % D, hk = hq / G, r = local * G + hq % G;
+    const float* ml = part_ml + ((size_t(cb) * d.Hkv + size_t(hk) * nch) * RMAX + r) * 2;
+    const float* po = part_o + ((size_t(cb) * d.Hkv + size_t(hk) * nch) * RMAX + r) * D + dd;
     float mx = -INFINITY;
-    for (int c = lane; c < nch; c += 32) mx = fmaxf(mx, part_ml[((base + c) * RMAX + r) * 2]);
-    mx = warp_max(mx);
-    float den = 0.f;
-    for (int c = lane; c < nch; c += 32) {
-      const float mc = part_ml[((base + c) * RMAX + r) * 2];
-      const float wgt = mc == -INFINITY ? 0.f : __expf(mc - mx);  // an empty chunk weighs nothing
-      den += part_ml[((base + c) * RMAX + r) * 2 + 1] * wgt;
-      wrow[hq * kMaxChunks + c] = wgt;
-    }
-    den = warp_sum(den);
-    const float inv = 1.f / (den * kPScale);
-    for (int c = lane; c < nch; c += 32) wrow[hq * kMaxChunks + c] *= inv;
-  }
-  __syncthreads();
-  for (int idx = threadIdx.x; idx < d.Hq * D; idx += blockDim.x) {
-    const int hq = idx / D, dd = idx % D, hk = hq / G, r = local * G + hq % G;
-    const size_t base = size_t(cb) * d.Hkv + size_t(hk) * nch;
-    float num = 0.f;
 #pragma unroll 4
-    for (int c = 0; c < nch; ++c) num = fmaf(part_o[((base + c) * RMAX + r) * D + dd], wrow[hq * kMaxChunks + c], num);
-    const float gate = plane_sum(qkv, m, hq * 2 * D + D + dd);
-    rowbuf[idx] = num * sigmoidf(gate);
+    for (int ch = 0; ch < nch; ++ch) mx = fmaxf(mx, ml[size_t(ch) * RMAX * 2]);
+    float den = 0.f;
+    float4 num = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+    for (int ch = 0; ch < nch; ++ch) {
+      const float mc = ml[size_t(ch) * RMAX * 2];
+      const float wgt = mc == -INFINITY ? 0.f : __expf(mc - mx);  // an empty chunk weighs nothing
+      den = fmaf(ml[size_t(ch) * RMAX * 2 + 1], wgt, den);
+      const float4 o = *reinterpret_cast<const float4*>(po + size_t(ch) * RMAX * D);
+      num.x = fmaf(o.x, wgt, num.x), num.y = fmaf(o.y, wgt, num.y), num.z = fmaf(o.z, wgt, num.z), num.w = fmaf(o.w, wgt, num.w);
+    }
+    const float inv = 1.f / (den * kPScale);
+    x = make_float4(num.x * inv, num.y * inv, num.z * inv, num.w * inv);
+    if (raw) {
+      *reinterpret_cast<float4*>(raw + size_t(m) * q.K + c) = x;
+    } else {
+      const float4 gate = plane_sum4(qkv, m, hq * 2 * D + D + dd);
+      x = make_float4(x.x * sigmoidf(gate.x), x.y * sigmoidf(gate.y), x.z * sigmoidf(gate.z), x.w * sigmoidf(gate.w));
+    }
   }
-  __syncthreads();
-  for (int c0 = 0; c0 < q.K_pad; c0 += 1024) {
-    const int c = c0 + threadIdx.x * 4;
-    if (c - (threadIdx.x & 31) * 4 >= q.K_pad) break;
-    float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (c < q.K) x = *reinterpret_cast<const float4*>(rowbuf + c);
-    quant_store4(x, c, m, q);
-  }
+  quant_store4(x, c, m, q);
 }
 
 // ---------------------------------------------------------------------------------------------- argmax / accept
@@ -1012,11 +1055,11 @@ __global__ void __launch_bounds__(64) kv_compact_kernel(StepBuffers sb, ModelDim
   for (int j = 1; j < R->n_path; ++j) {
     const int src = q.pos + R->path[j], dst = q.pos + j;
     if (src != dst) {
-      const size_t a = kv_slot_index(d, al, kvi, hk, table[src / d.page_tokens], src % d.page_tokens);
-      const size_t b = kv_slot_index(d, al, kvi, hk, table[dst / d.page_tokens], dst % d.page_tokens);
-      for (int i = threadIdx.x; i < d.D / 4; i += blockDim.x)
-        reinterpret_cast<uint32_t*>(kv.codes + b * d.D)[i] = reinterpret_cast<const uint32_t*>(kv.codes + a * d.D)[i];
-      if (threadIdx.x == 0) kv.scales[b] = kv.scales[a];
+      const int pa = table[src / d.page_tokens], pb = table[dst / d.page_tokens];
+      const int ta = src % d.page_tokens, tb = dst % d.page_tokens;
+      for (int i = threadIdx.x; i < d.D; i += blockDim.x)
+        kv.codes[kv_code_index(d, al, kvi, hk, pb, tb, i)] = kv.codes[kv_code_index(d, al, kvi, hk, pa, ta, i)];
+      if (threadIdx.x == 0) kv.scales[kv_slot_index(d, al, kvi, hk, pb, tb)] = kv.scales[kv_slot_index(d, al, kvi, hk, pa, ta)];
     }
     __syncthreads();
   }
@@ -1096,9 +1139,8 @@ __global__ void kv_write_kernel(const float* __restrict__ k, const float* __rest
     if (dd == 0) dev_fail(err, kDevBadPage);
     return;
   }
-  const size_t at = kv_slot_index(d, al, kvi, h, page, pos % d.page_tokens);
-  kv.codes[at * d.D + dd] = to_e4m3(__fdiv_rn(x, sc));
-  if (dd == 0) kv.scales[at] = sc;
+  kv.codes[kv_code_index(d, al, kvi, h, page, pos % d.page_tokens, dd)] = to_e4m3(__fdiv_rn(x, sc));
+  if (dd == 0) kv.scales[kv_slot_index(d, al, kvi, h, page, pos % d.page_tokens)] = sc;
 }
 
 // A whole page copied for copy-on-write (the reference's kv_pages_copy role, src/core/kernels.cu:513-527).
@@ -1113,6 +1155,11 @@ __global__ void kv_page_copy_kernel(ModelDims d, KvPoolDev kv, int src, int dst)
   for (int i = threadIdx.x; i < d.page_tokens; i += blockDim.x) kv.scales[b + i] = kv.scales[a + i];
 }
 
+__global__ void f32_to_half_kernel(const float* __restrict__ src, __half* __restrict__ dst, size_t n) {
+  pdl_sync();  // first statement: see common.cuh
+  for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < n; i += size_t(gridDim.x) * blockDim.x) dst[i] = __float2half_rn(src[i]);
+}
+
 __global__ void flush_kernel(float* __restrict__ buf, size_t n) {
   pdl_sync();  // first statement: see common.cuh
   for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < n; i += size_t(gridDim.x) * blockDim.x) buf[i] = float(i);
@@ -1120,7 +1167,8 @@ __global__ void flush_kernel(float* __restrict__ buf, size_t n) {
 
 template <int D, int G>
 constexpr size_t attn_smem() {
-  return size_t(kAttnRowTile) * (D + 8) * 2 + size_t(4) * kAttnKeyTile * (D + 16) + size_t(4) * kAttnKeyTile * 4;
+  return size_t(kAttnRowTile) * (D + 8) * 2 + size_t(2) * kAttnKeyTile * (D + 16) + size_t(2) * D * (kAttnKeyTile + 16) +
+         size_t(4) * kAttnKeyTile * 4;
 }
 
 }  // namespace
@@ -1134,7 +1182,13 @@ int pack_launch(const StepBuffers& sb, const ModelDims& d, cudaStream_t s) {
 
 int norm_quant_launch(float* h, const Planes& add, const int* ids, const __nv_bfloat16* embed, const __nv_bfloat16* w,
                       float* xn, const QuantOut& q, const int* n_rows, int rows_grid, int H, float eps, cudaStream_t s) {
-  LB_CUDA(launch_kernel(norm_quant_kernel, dim3(rows_grid), dim3(256), size_t(0), s, h, add, ids, embed, w, xn, q, n_rows, H, eps));
+  const int chunks = ceil_div(q.K_pad, 1024);
+  if (chunks > 8) {
+    set_error("norm: hidden size above 8192");
+    return LING_B200_ERR_UNSUPPORTED;
+  }
+  LB_CUDA(launch_kernel_cluster(norm_quant_kernel, dim3(chunks, rows_grid), dim3(256), size_t(0), chunks, s, h, add, ids, embed, w, xn,
+                                q, n_rows, H, eps));
   LB_LAUNCH("norm_quant_kernel");
   return LING_B200_OK;
 }
@@ -1155,7 +1209,7 @@ int copy_rows_launch(const float* src, float* out, const int* n_rows, int rows_g
 int ab_gating_launch(const float* xn, const __nv_bfloat16* wa, const __nv_bfloat16* wb, const __nv_bfloat16* A_log,
                      const __nv_bfloat16* dt_bias, float* g, float* beta, const int* n_rows, int rows_grid, int H, int HV,
                      cudaStream_t s) {
-  LB_CUDA(launch_kernel(ab_gating_kernel, dim3(dim3(HV, ceil_div(rows_grid, 8))), dim3(256), size_t(0), s, xn, wa, wb, A_log, dt_bias, g, beta, n_rows, H, HV));
+  LB_CUDA(launch_kernel(ab_gating_kernel, dim3(HV, rows_grid), dim3(128), size_t(0), s, xn, wa, wb, A_log, dt_bias, g, beta, n_rows, H, HV));
   LB_LAUNCH("ab_gating_kernel");
   return LING_B200_OK;
 }
@@ -1170,9 +1224,9 @@ int conv_tree_launch(const Planes& in, const StepBuffers& sb, const ModelDims& d
 int gdn_tree_launch(const float* post, const float* g, const float* beta, const StepBuffers& sb, const ModelDims& d,
                     const float* state, size_t state_slot_stride, float* core, int grid, cudaStream_t s) {
   if (d.Dk == 128)
-    LB_CUDA(launch_kernel(gdn_tree_kernel<128>, dim3(grid), dim3(128), size_t(0), s, post, g, beta, sb, d.Hk, d.HV, d.Dv, state, state_slot_stride, core));
+    LB_CUDA(launch_kernel(gdn_tree_kernel<128>, dim3(grid), dim3(128), GdnStage<128>::smem_bytes(d.Dv), s, post, g, beta, sb, d.Hk, d.HV, d.Dv, state, state_slot_stride, core));
   else if (d.Dk == 64)
-    LB_CUDA(launch_kernel(gdn_tree_kernel<64>, dim3(grid), dim3(128), size_t(0), s, post, g, beta, sb, d.Hk, d.HV, d.Dv, state, state_slot_stride, core));
+    LB_CUDA(launch_kernel(gdn_tree_kernel<64>, dim3(grid), dim3(128), GdnStage<64>::smem_bytes(d.Dv), s, post, g, beta, sb, d.Hk, d.HV, d.Dv, state, state_slot_stride, core));
   else {
     set_error("DeltaNet key dim must be 64 or 128");
     return LING_B200_ERR_UNSUPPORTED;
@@ -1183,7 +1237,7 @@ int gdn_tree_launch(const float* post, const float* g, const float* beta, const 
 
 int gated_norm_quant_launch(const float* core, const Planes& z, int z_col, const __nv_bfloat16* w, const QuantOut& q,
                             const int* n_rows, int rows_grid, int HV, int Dv, float eps, cudaStream_t s) {
-  LB_CUDA(launch_kernel(gated_norm_quant_kernel, dim3(rows_grid), dim3(256), size_t(0), s, core, z, z_col, w, q, n_rows, HV * Dv, Dv, eps));
+  LB_CUDA(launch_kernel(gated_norm_quant_kernel, dim3(rows_grid, ceil_div(q.K_pad, 1024)), dim3(256), size_t(0), s, core, z, z_col, w, q, n_rows, HV * Dv, Dv, eps));
   LB_LAUNCH("gated_norm_quant_kernel");
   return LING_B200_OK;
 }
@@ -1206,6 +1260,10 @@ static int attention_launch_t(const __half* q, const StepBuffers& sb, const Mode
 
 // Opts the attention kernels into their dynamic shared memory (once per device, never inside a stream capture).
 int kernels_init() {
+  LB_CUDA(cudaFuncSetAttribute(gdn_tree_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(GdnStage<128>::smem_bytes(128))));
+  LB_CUDA(cudaFuncSetAttribute(gdn_tree_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(GdnStage<64>::smem_bytes(128))));
+  LB_CUDA(cudaFuncSetAttribute(gdn_commit_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(GdnStage<128>::smem_bytes(128))));
+  LB_CUDA(cudaFuncSetAttribute(gdn_commit_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(GdnStage<64>::smem_bytes(128))));
   LB_CUDA(cudaFuncSetAttribute(attention_kernel<256, 6>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(attn_smem<256, 6>())));
   LB_CUDA(cudaFuncSetAttribute(attention_kernel<64, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(attn_smem<64, 4>())));
   LB_CUDA(cudaFuncSetAttribute(attention_kernel<128, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(attn_smem<128, 4>())));
@@ -1225,29 +1283,21 @@ int attention_launch(const __half* q, const StepBuffers& sb, const ModelDims& d,
 }
 
 int attn_combine_launch(const float* part_o, const float* part_ml, const Planes& qkv, const StepBuffers& sb,
-                        const ModelDims& d, const QuantOut& q, float* wbuf, int rows_grid, cudaStream_t s) {
+                        const ModelDims& d, const QuantOut& q, float* raw, int rows_grid, cudaStream_t s) {
   const int G = d.Hq / d.Hkv;
-  const size_t smem = size_t(d.Hq) * d.D * 4;
-  if (smem > 48 * 1024) {
-    set_error("attention combine: heads x head_dim too large for one row buffer");
-    return LING_B200_ERR_UNSUPPORTED;
-  }
-  if (G == 6) {
-    LB_CUDA(launch_kernel(attn_combine_kernel<6>, dim3(rows_grid), dim3(256), size_t(smem), s, part_o, part_ml, qkv, sb, d, q, wbuf));
-  } else if (G == 4) {
-    LB_CUDA(launch_kernel(attn_combine_kernel<4>, dim3(rows_grid), dim3(256), size_t(smem), s, part_o, part_ml, qkv, sb, d, q, wbuf));
-  } else if (G == 8) {
-    LB_CUDA(launch_kernel(attn_combine_kernel<8>, dim3(rows_grid), dim3(256), size_t(smem), s, part_o, part_ml, qkv, sb, d, q, wbuf));
-  } else {
+  const dim3 grid(rows_grid, ceil_div(q.K_pad, 1024));
+  if (G == 6) LB_CUDA(launch_kernel(attn_combine_kernel<6>, grid, dim3(256), size_t(0), s, part_o, part_ml, qkv, sb, d, q, raw));
+  else if (G == 4) LB_CUDA(launch_kernel(attn_combine_kernel<4>, grid, dim3(256), size_t(0), s, part_o, part_ml, qkv, sb, d, q, raw));
+  else if (G == 8) LB_CUDA(launch_kernel(attn_combine_kernel<8>, grid, dim3(256), size_t(0), s, part_o, part_ml, qkv, sb, d, q, raw));
+  else {
     set_error("attention combine: unsupported group size");
     return LING_B200_ERR_UNSUPPORTED;
   }
-  LB_LAUNCH("attn_combine_kernel");
   return LING_B200_OK;
 }
 
 int silu_mul_quant_launch(const Planes& gu, int I, const QuantOut& q, const int* n_rows, int rows_grid, cudaStream_t s) {
-  LB_CUDA(launch_kernel(silu_mul_quant_kernel, dim3(rows_grid), dim3(256), size_t(0), s, gu, I, q, n_rows));
+  LB_CUDA(launch_kernel(silu_mul_quant_kernel, dim3(rows_grid, ceil_div(q.K_pad, 1024)), dim3(256), size_t(0), s, gu, I, q, n_rows));
   LB_LAUNCH("silu_mul_quant_kernel");
   return LING_B200_OK;
 }
@@ -1291,9 +1341,9 @@ int gdn_commit_launch(const StepBuffers& sb, const ModelDims& d, const float* po
                       size_t state_layer_stride, int grid, cudaStream_t s) {
   if (d.n_gdn == 0) return LING_B200_OK;
   if (d.Dk == 128)
-    LB_CUDA(launch_kernel(gdn_commit_kernel<128>, dim3(grid), dim3(128), size_t(0), s, post, g, beta, post_layer_stride, g_layer_stride, sb, d.Hk, d.HV, d.Dv, d.n_gdn, state, state_slot_stride, state_layer_stride));
+    LB_CUDA(launch_kernel(gdn_commit_kernel<128>, dim3(grid), dim3(128), GdnStage<128>::smem_bytes(d.Dv), s, post, g, beta, post_layer_stride, g_layer_stride, sb, d.Hk, d.HV, d.Dv, d.n_gdn, state, state_slot_stride, state_layer_stride));
   else if (d.Dk == 64)
-    LB_CUDA(launch_kernel(gdn_commit_kernel<64>, dim3(grid), dim3(128), size_t(0), s, post, g, beta, post_layer_stride, g_layer_stride, sb, d.Hk, d.HV, d.Dv, d.n_gdn, state, state_slot_stride, state_layer_stride));
+    LB_CUDA(launch_kernel(gdn_commit_kernel<64>, dim3(grid), dim3(128), GdnStage<64>::smem_bytes(d.Dv), s, post, g, beta, post_layer_stride, g_layer_stride, sb, d.Hk, d.HV, d.Dv, d.n_gdn, state, state_slot_stride, state_layer_stride));
   else {
     set_error("DeltaNet key dim must be 64 or 128");
     return LING_B200_ERR_UNSUPPORTED;
@@ -1343,6 +1393,11 @@ int kv_page_copy_launch(const ModelDims& d, const KvPoolDev& kv, int src, int ds
   if (d.n_attn == 0) return LING_B200_OK;
   LB_CUDA(launch_kernel(kv_page_copy_kernel, dim3(d.n_attn * 2 * d.Hkv), dim3(256), size_t(0), s, d, kv, src, dst));
   LB_LAUNCH("kv_page_copy_kernel");
+  return LING_B200_OK;
+}
+
+int f32_to_half_launch(const float* src, __half* dst, size_t n, cudaStream_t s) {
+  LB_CUDA(launch_kernel(f32_to_half_kernel, dim3(int(std::min<size_t>((n + 255) / 256, 148 * 8))), dim3(256), size_t(0), s, src, dst, n));
   return LING_B200_OK;
 }
 

@@ -11,7 +11,6 @@ constexpr int kTreeRows = LING_B200_MAX_TREE_ROWS;
 constexpr int kAttnChunk = 512;    // context keys per flash-decoding chunk
 constexpr int kAttnKeyTile = 64;   // keys per shared-memory tile
 constexpr int kAttnRowTile = 64;   // query rows (token rows x q heads of one kv head) per CTA
-constexpr int kMaxChunks = 320;    // chunks of one sequence: 131,072 positions / kAttnChunk + the partial and in-flight chunks
 constexpr int kMaxPlanes = 8;      // most K splits of one GEMM (partial-sum planes a consumer adds)
 
 // One sequence of the staged step as the device sees it.
@@ -55,7 +54,10 @@ struct ModelDims {
   int max_seqs;
 };
 
-// The paged FP8 KV pool: codes [attn layer][K|V][kv head][page][token][D], scales [..][token] (fp32).
+// The paged FP8 KV pool.  Codes: [attn layer][K|V][kv head][page] pages of page_tokens * D bytes; a K page is [token][D]
+// (a key's D bytes contiguous: the score product reduces over D), a V page is [D][token] (one dim's tokens contiguous: the
+// value product reduces over tokens), so both land in shared memory by 16-byte copies in the order the MMA fragments
+// read them.  Scales: [..][page][token] fp32, one per (position, head).
 struct KvPoolDev {
   uint8_t* codes = nullptr;
   float* scales = nullptr;
@@ -63,6 +65,12 @@ struct KvPoolDev {
 };
 __host__ __device__ __forceinline__ size_t kv_slot_index(const ModelDims& d, int al, int kv, int h, int page, int tok) {
   return (((size_t(al) * 2 + kv) * d.Hkv + h) * size_t(d.pool_pages + 1) + page) * d.page_tokens + tok;
+}
+
+// Byte offset of element (position token `tok` of page `page`, dim dd) of K (kv = 0) or V (kv = 1).
+__host__ __device__ __forceinline__ size_t kv_code_index(const ModelDims& d, int al, int kv, int h, int page, int tok, int dd) {
+  const size_t page_base = kv_slot_index(d, al, kv, h, page, 0) * d.D;
+  return kv ? page_base + size_t(dd) * d.page_tokens + tok : page_base + size_t(tok) * d.D + dd;
 }
 
 // A GEMM output as its consumers see it: `planes` partial sums (the K splits) to be added in order.
@@ -101,8 +109,10 @@ int attn_prepare_launch(const Planes& qkv, const StepBuffers& sb, const ModelDim
                         const __nv_bfloat16* k_norm, __half* q, const KvPoolDev& kv, int rows_grid, cudaStream_t s);
 int attention_launch(const __half* q, const StepBuffers& sb, const ModelDims& d, int al, const KvPoolDev& kv, float* part_o,
                      float* part_ml, int chunk_slots, int grid, cudaStream_t s);
+// raw != nullptr: also the merged rows before the output gate, [rows][Hq * D] (the gate is then not applied: qkv.p may be null)
 int attn_combine_launch(const float* part_o, const float* part_ml, const Planes& qkv, const StepBuffers& sb,
-                        const ModelDims& d, const QuantOut& q, float* wbuf, int rows_grid, cudaStream_t s);
+                        const ModelDims& d, const QuantOut& q, float* raw, int rows_grid, cudaStream_t s);
+int f32_to_half_launch(const float* src, __half* dst, size_t n, cudaStream_t s);
 int silu_mul_quant_launch(const Planes& gu, int I, const QuantOut& q, const int* n_rows, int rows_grid, cudaStream_t s);
 int argmax_reduce_launch(const float* tile_val, const int* tile_idx, int tiles, int rows_alloc, int* ids, float* vals,
                          const int* n_rows, int rows_grid, cudaStream_t s);

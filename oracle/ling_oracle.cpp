@@ -819,17 +819,10 @@ void norm_rope(const float* x, const float* w, float* out, int D, int rot, float
   }
 }
 
-int step_impl(lo_model* m, const lo_seq_step* seqs, int n_seqs, int flags, lo_seq_result* results,
-              const StepScope& scope) {
-  const lo_model_config& c = m->cfg;
-  const int H = c.hidden, I = c.intermediate, Hq = c.heads, Hkv = c.kv_heads, D = c.head_dim;
-  const int Hk = c.lin_k_heads, HV = c.lin_v_heads, Dk = c.lin_k_dim, Dv = c.lin_v_dim, C = m->C(), Vs = m->Vs();
-  const int G = Hq / Hkv, pt = m->opt.page_tokens;
+// Packing (src/core/speculate.cpp:1190-1201, src/core/kernels.cuh:58-78): rows concatenated sequence by sequence; a
+// row's RoPE position is pos + depth (+ rope delta), its cache slot pos + row index (src/core/kernels.cuh:109-118).
+int pack_step(lo_model* m, const lo_seq_step* seqs, int n_seqs) {
   if (n_seqs < 1 || n_seqs > m->opt.max_seqs) return 1;
-
-  // Packing (src/core/speculate.cpp:1190-1201, src/core/kernels.cuh:58-78): rows concatenated sequence by
-  // sequence; a row's RoPE position is pos + depth (+ rope delta), its cache slot pos + row index
-  // (src/core/kernels.cuh:109-118).
   m->n_seqs = n_seqs;
   m->row0.assign(n_seqs + 1, 0);
   m->trees.assign(n_seqs, lo_tree_desc{});
@@ -852,6 +845,59 @@ int step_impl(lo_model* m, const lo_seq_step* seqs, int n_seqs, int flags, lo_se
       m->cache_slot[row] = seqs[s].pos + r;
       for (int a = r; a >= 0; a = (a == 0 ? -1 : seqs[s].parent[a])) m->anc[row] |= 1u << a;
     }
+  return 0;
+}
+
+// Row r sees the context [0, pos) and the rows of its own root-to-row path (src/core/attention_body.cuh:175-195,289-294);
+// scores q.k / sqrt(D), softmax and the value sum in double; K and V as the cache holds them (E4M3 codes x the
+// position's scale).  out [M][Hq][D], before the output gate.
+void attend(lo_model* m, const lo_seq_step* seqs, int al, const float* q, float* out) {
+  const lo_model_config& c = m->cfg;
+  const int Hq = c.heads, D = c.head_dim, G = c.heads / c.kv_heads, pt = m->opt.page_tokens, M = m->rows;
+  const float inv_sqrt_d = 1.f / std::sqrt(float(D));
+  parallel_for(M, [&](int r_lo, int r_hi) {
+    for (int r = r_lo; r < r_hi; ++r) {
+      const int s = m->seq_of[r], slot = seqs[s].slot, pos0 = seqs[s].pos;
+      std::vector<int> keys;
+      for (int p = 0; p < pos0; ++p) keys.push_back(p);
+      for (int j = 0; j < seqs[s].n_rows; ++j)
+        if (m->anc[r] >> j & 1) keys.push_back(pos0 + j);
+      std::vector<float> sc(keys.size());
+      std::vector<double> acc(D);
+      for (int hq = 0; hq < Hq; ++hq) {
+        const int hk = hq / G;
+        const float* qv = &q[(size_t(r) * Hq + hq) * D];
+        float mx = -INFINITY;
+        for (size_t i = 0; i < keys.size(); ++i) {
+          const size_t at = m->kv_index(al, 0, hk, m->tables[slot][keys[i] / pt], keys[i] % pt);
+          double dot = 0;
+          for (int d = 0; d < D; ++d) dot += double(qv[d]) * g_dec[m->kv_codes[at * D + d]];
+          sc[i] = float(dot) * m->kv_scales[at] * inv_sqrt_d;
+          mx = std::max(mx, sc[i]);
+        }
+        double den = 0;
+        std::fill(acc.begin(), acc.end(), 0.0);
+        for (size_t i = 0; i < keys.size(); ++i) {
+          const size_t at = m->kv_index(al, 1, hk, m->tables[slot][keys[i] / pt], keys[i] % pt);
+          const double p = std::exp(double(sc[i] - mx));
+          den += p;
+          const double pv = p * m->kv_scales[at];
+          for (int d = 0; d < D; ++d) acc[d] += pv * g_dec[m->kv_codes[at * D + d]];
+        }
+        for (int d = 0; d < D; ++d) out[(size_t(r) * Hq + hq) * D + d] = float(acc[d] / den);
+      }
+    }
+  });
+}
+
+int step_impl(lo_model* m, const lo_seq_step* seqs, int n_seqs, int flags, lo_seq_result* results,
+              const StepScope& scope) {
+  const lo_model_config& c = m->cfg;
+  const int H = c.hidden, I = c.intermediate, Hq = c.heads, Hkv = c.kv_heads, D = c.head_dim;
+  const int Hk = c.lin_k_heads, HV = c.lin_v_heads, Dk = c.lin_k_dim, Dv = c.lin_v_dim, C = m->C(), Vs = m->Vs();
+  const int G = Hq / Hkv, pt = m->opt.page_tokens;
+  if (const int rc = pack_step(m, seqs, n_seqs)) return rc;
+  const int M = m->rows;
 
   // B.1 embedding (src/core/kernels.cu:280-286)
   std::vector<float> h(size_t(M) * H), xn(size_t(M) * H);
@@ -889,45 +935,13 @@ int step_impl(lo_model* m, const lo_seq_step* seqs, int n_seqs, int flags, lo_se
           kv_store(m, seqs[s].slot, al, 1, hk, m->cache_slot[r], &vv[(size_t(r) * Hkv + hk) * D]);
         }
       }
-      // Row r sees the context [0, pos) and the rows of its own root-to-row path (src/core/attention_body.cuh:
-      // 175-195,289-294); scores q.k / sqrt(D), softmax and the value sum in fp32/double.
       std::vector<float> att(size_t(M) * Hq * D);
-      const float inv_sqrt_d = 1.f / std::sqrt(float(D));
-      parallel_for(M, [&](int r_lo, int r_hi) {
-      for (int r = r_lo; r < r_hi; ++r) {
-        const int s = m->seq_of[r], slot = seqs[s].slot, pos0 = seqs[s].pos;
-        std::vector<int> keys;
-        for (int p = 0; p < pos0; ++p) keys.push_back(p);
-        for (int j = 0; j < seqs[s].n_rows; ++j)
-          if (m->anc[r] >> j & 1) keys.push_back(pos0 + j);
-        std::vector<float> sc(keys.size());
-        std::vector<double> acc(D);
-        for (int hq = 0; hq < Hq; ++hq) {
-          const int hk = hq / G;
-          const float* qv = &q[(size_t(r) * Hq + hq) * D];
-          float mx = -INFINITY;
-          for (size_t i = 0; i < keys.size(); ++i) {
-            const size_t at = m->kv_index(al, 0, hk, m->tables[slot][keys[i] / pt], keys[i] % pt);
-            double dot = 0;
-            for (int d = 0; d < D; ++d) dot += double(qv[d]) * g_dec[m->kv_codes[at * D + d]];
-            sc[i] = float(dot) * m->kv_scales[at] * inv_sqrt_d;
-            mx = std::max(mx, sc[i]);
-          }
-          double den = 0;
-          std::fill(acc.begin(), acc.end(), 0.0);
-          for (size_t i = 0; i < keys.size(); ++i) {
-            const size_t at = m->kv_index(al, 1, hk, m->tables[slot][keys[i] / pt], keys[i] % pt);
-            const double p = std::exp(double(sc[i] - mx));
-            den += p;
-            const double pv = p * m->kv_scales[at];
-            for (int d = 0; d < D; ++d) acc[d] += pv * g_dec[m->kv_codes[at * D + d]];
-          }
-          // out * sigmoid(gate) (src/core/kernels.cu:314-318); the gate is the head's second D values
-          const float* gate = &qg[(size_t(r) * Hq + hq) * 2 * D + D];
-          for (int d = 0; d < D; ++d) att[(size_t(r) * Hq + hq) * D + d] = float(acc[d] / den) * sigmoid(gate[d]);
-        }
-      }
-      });
+      attend(m, seqs, al, q.data(), att.data());
+      // out * sigmoid(gate) (src/core/kernels.cu:314-318); the gate is the head's second D values
+      for (int r = 0; r < M; ++r)
+        for (int hq = 0; hq < Hq; ++hq)
+          for (int d = 0; d < D; ++d)
+            att[(size_t(r) * Hq + hq) * D + d] *= sigmoid(qg[(size_t(r) * Hq + hq) * 2 * D + D + d]);
       QAct aq;
       aq.set(att.data(), M, Hq * D);
       std::vector<float> o(size_t(M) * H);
@@ -1054,6 +1068,15 @@ int lo_verify_step_sample(lo_model* m, const lo_seq_step* seqs, int n_seqs, cons
   StepScope sc;
   sc.layers = layers, sc.n_layers = n_layers, sc.head_rows = head_rows;
   return step_impl(m, seqs, n_seqs, 0, nullptr, sc);
+}
+
+// The attention of one layer alone: packing of `seqs`, then every row over its context and its path's in-flight rows as
+// the cache holds them; q and out are [rows][heads][head_dim], out before the output gate.
+int lo_attention(lo_model* m, const lo_seq_step* seqs, int n_seqs, int attn_layer, const float* q, float* out) {
+  if (attn_layer < 0 || attn_layer >= m->n_attn) return 1;
+  if (const int rc = pack_step(m, seqs, n_seqs)) return rc;
+  attend(m, seqs, attn_layer, q, out);
+  return 0;
 }
 
 int lo_read_tree_desc(lo_model* m, int seq, lo_tree_desc* out) {

@@ -116,6 +116,7 @@ int lo_verify_step(lo_model* m, const lo_seq_step* seqs, int n_seqs, int flags, 
 /* the same step restricted to a sample: only the listed layers run and only head_rows vocabulary rows are scored */
 int lo_verify_step_sample(lo_model* m, const lo_seq_step* seqs, int n_seqs, const int* layers, int n_layers,
                           int head_rows);
+int lo_attention(lo_model* m, const lo_seq_step* seqs, int n_seqs, int attn_layer, const float* q, float* out);
 int lo_read_tree_desc(lo_model* m, int seq, lo_tree_desc* out);
 int lo_read_packing(lo_model* m, int* row0, int* token, int* seq_of, int* depth, int* rope_pos, int* cache_slot,
                     uint32_t* anc_mask);

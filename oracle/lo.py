@@ -194,6 +194,15 @@ class Model:
         la = np.ascontiguousarray(layers, np.int32)
         assert lo().lo_verify_step_sample(self.h, arr, len(seqs), _ip(la), len(la), head_rows) == 0
 
+    def attention(self, seqs, attn_layer, q, make_steps=None):
+        arr, keep = make_steps(seqs)
+        q = np.ascontiguousarray(q, np.float32)
+        out = np.zeros_like(q)
+        assert lo().lo_attention(self.h, arr, len(seqs), attn_layer, _fp(q), _fp(out)) == 0
+        self.last_rows = sum(len(s["tokens"]) for s in seqs)
+        self.last_seqs = len(seqs)
+        return out
+
     def read_tree_desc(self, seq):
         t = self.S.TreeDesc()
         assert lo().lo_read_tree_desc(self.h, seq, C.byref(t)) == 0

@@ -185,3 +185,50 @@ def test_argmax_ties_nan_and_inf(gpu, lb, lo):
     oi, ov = lo.argmax(logits)
     assert np.array_equal(ids, oi) and np.array_equal(vals, ov)
     assert list(ids[:2]) == [5, 0x7fffffff] and ids[2] == 123456 and ids[4] == V - 1 and ids[5] == 0
+
+
+# Attention tolerance: both sides read the same E4M3 cache; the device rounds q and the probabilities to FP16 for the
+# tensor-core products (relative 2^-11 each) where the oracle keeps fp32/double: 6e-3 of a row's rms (measured: 3e-3).
+ATTN_TOL = 6e-3
+
+
+@pytest.mark.parametrize("shape", ["toy", "27b"])
+def test_tree_attention_matches_oracle(gpu, lb, lo, shape):
+    if shape == "toy":     # 4 q heads / 1 kv head of 64, 16-position pages
+        cfg = lb.make_config(256, 704, 1, 4096, 4, 1, 64, 16, 2, 4, 64, 64, [1])
+        contexts, page_tokens = (0, 3, 37, 511, 512, 1029), 16
+    else:                  # 24 q heads / 4 kv heads of 256 (six query heads per kv head), 64-position pages
+        cfg = lb.make_config(5120, 128, 1, 4096, 24, 4, 256, 64, 16, 48, 128, 128, [1])
+        contexts, page_tokens = (1500, 17, 530), 64
+    n_seq = len(contexts)
+    pool = sum((c + 48) // page_tokens + 2 for c in contexts) + 1
+    ctx = lb.Context(cfg, sessions=n_seq, max_context=2048, page_tokens=page_tokens, pool_pages=pool, max_seqs=n_seq,
+                     max_rows=32 * n_seq)
+    opt = lb.Options(n_seq, 2048, page_tokens, pool, n_seq, 32 * n_seq, 0, 0, 0, 0, 0)
+    m = lo.Model(cfg, opt, lb)
+    rng = np.random.default_rng(len(shape))
+    seqs, page = [], 1
+    for s, c in enumerate(contexts):
+        n = int(rng.integers(1, 33)) if s else 32
+        chain = int(rng.integers(0, n))
+        seqs.append({"slot": s, "pos": c, "tokens": np.zeros(n, np.int32), "parent": np.array(helpers.random_tree(rng, n, chain), np.int32),
+                     "chain": chain})
+        page += helpers.map_pages([ctx, m], s, c + 32, page_tokens, page)
+        for t in (ctx, m):
+            if c:
+                t.synth_kv(s, c, 5)
+            # the in-flight rows' K and V, as the step's prepare kernel would have left them
+            k = rng.standard_normal((n, cfg.kv_heads, cfg.head_dim)).astype(np.float32) if t is ctx else k
+            v = (rng.standard_normal((n, cfg.kv_heads, cfg.head_dim)) * 3).astype(np.float32) if t is ctx else v
+            t.kv_write(s, 0, c, k, v)
+    for a, b in zip(ctx.kv_read(n_seq - 1, 0, 0, contexts[-1] + 5), m.kv_read(n_seq - 1, 0, 0, contexts[-1] + 5)):
+        assert np.array_equal(a, b)        # the two caches hold the same values (the V page layout differs, the content does not)
+    rows = sum(len(q["tokens"]) for q in seqs)
+    q = rng.standard_normal((rows, cfg.heads, cfg.head_dim)).astype(np.float32)
+    out_o = m.attention(seqs, 0, q, make_steps=lb.make_steps)
+    out_g = ctx.attention(seqs, 0, q)
+    flat_o, flat_g = out_o.reshape(rows, -1), out_g.reshape(rows, -1)
+    rms = np.sqrt((flat_o.astype(np.float64) ** 2).mean(axis=1, keepdims=True))
+    assert np.isfinite(out_g).all()
+    assert (np.abs(flat_g - flat_o) <= ATTN_TOL * rms).all(), float((np.abs(flat_g - flat_o) / rms).max())
+    ctx.close(), m.close()

@@ -7,8 +7,11 @@ Why the floating-point bars have two tiers.  Device and oracle compute the same 
 nothing else intervenes they agree to ~1e-6 of a row's rms (the first tier: the MEDIAN row of the first layer's output
 must agree to 1e-4).  But every layer rounds its activations to E4M3 five times, and an fp32 difference of one ulp that
 straddles a rounding boundary flips a code by a whole FP8 step (6-12% of that element).  That happens to about two
-elements in 10^5, moves a few outputs of that row by up to ~0.1 of the row's rms and then propagates.  So the second tier
-bounds the whole tensor's relative L2 error and each row's worst element instead of asking for ulp-level agreement."""
+elements in 10^5, moves a few outputs of that row by up to ~0.1 of the row's rms and then propagates through the
+recurrence and the layers.  The second tier is therefore calibrated on the oracle itself: the same step is run on the
+oracle a second time with every DeltaNet state scaled by (1 + 4e-6), and the device's deviation from the oracle may be at
+most twice the oracle's own response to that perturbation (plus a small floor), tensor by tensor.  Measured at hidden
+5120, four layers deep: the oracle's own response is 5e-2 in relative L2 and 0.3 of a row's rms in the worst element."""
 import numpy as np
 import pytest
 
@@ -17,9 +20,10 @@ import helpers
 pytestmark = pytest.mark.gpu
 
 CLEAN_TOL = 1e-4    # tier 1: the median row of the first layer's output, max |gpu - oracle| / the row's rms
-REL_L2_TOL = 5e-2   # tier 2: ||gpu - oracle||_2 / ||oracle||_2 over a whole tensor (hidden states, logits, DeltaNet states);
-                    # measured: up to 2.2e-2 two layers deep at hidden 5120, where SwiGLU's heavy-tailed outputs make one flip count
-ROW_MAX_TOL = 0.3   # tier 2: the worst element of any row, as a fraction of that row's rms (an FP8 step on a large element)
+PERTURB = 4e-6      # tier 2: the relative perturbation of the DeltaNet states in the oracle's calibration run
+FACTOR = 2.0        # tier 2: the device may deviate from the oracle by this many times the oracle's own response ...
+REL_L2_FLOOR, ROW_MAX_FLOOR = 2e-3, 2e-2   # ... plus these floors (relative L2 of a tensor; worst element / row rms)
+REL_L2_TOL, ROW_MAX_TOL = 5e-2, 0.3        # fixed bars where no calibration run is made (toy shapes, states, variants)
 
 
 def row_errs(a, b):
@@ -31,11 +35,17 @@ def rel_l2(a, b):
     return float(np.linalg.norm((a.astype(np.float64) - b).ravel()) / (np.linalg.norm(b.astype(np.float64).ravel()) + 1e-30))
 
 
-def assert_close(a, b, what):
+def assert_close(a, b, what, perturbed=None):
+    """a: device, b: oracle, perturbed: the oracle's calibration run (None: the fixed bars)."""
     assert np.isfinite(a).all(), what
-    assert rel_l2(a, b) <= REL_L2_TOL, (what, rel_l2(a, b))
     flat_a, flat_b = a.reshape(a.shape[0], -1), b.reshape(b.shape[0], -1)
-    assert row_errs(flat_a, flat_b).max() <= ROW_MAX_TOL, (what, float(row_errs(flat_a, flat_b).max()))
+    l2_bar, max_bar = REL_L2_TOL, ROW_MAX_TOL
+    if perturbed is not None:
+        flat_p = perturbed.reshape(perturbed.shape[0], -1)
+        l2_bar = FACTOR * rel_l2(perturbed, b) + REL_L2_FLOOR
+        max_bar = FACTOR * float(row_errs(flat_p, flat_b).max()) + ROW_MAX_FLOOR
+    assert rel_l2(a, b) <= l2_bar, (what, rel_l2(a, b), l2_bar)
+    assert row_errs(flat_a, flat_b).max() <= max_bar, (what, float(row_errs(flat_a, flat_b).max()), max_bar)
 
 
 @pytest.fixture(scope="module")
@@ -50,6 +60,15 @@ def toy(gpu, lb, lo):
 
 
 def check_step(lb, cfg, ctx, m, seqs, flags, seed=0):
+    # the oracle's calibration run first (no commit): the same step with every DeltaNet state scaled by (1 + PERTURB)
+    helpers.setup_sessions([m], cfg, seqs, 16, seed)
+    n_gdn = sum(1 for l in range(cfg.layers) if not cfg.full_attention[l])
+    for q in seqs:
+        for g in range(n_gdn):
+            st, _ = m.state_read(q["slot"], g)
+            m.state_write(q["slot"], g, st * np.float32(1 + PERTURB))
+    m.verify_step(seqs, flags=lb.STEP_KEEP_LOGITS | lb.STEP_KEEP_TAPS, make_steps=lb.make_steps)
+    cal_taps, cal_logits = [m.read_tap(l) for l in range(cfg.layers + 1)], m.read_logits()
     helpers.setup_sessions([ctx, m], cfg, seqs, 16, seed)
     ro = m.verify_step(seqs, flags=flags, make_steps=lb.make_steps)
     rg = ctx.verify_step(seqs, flags=flags)
@@ -62,9 +81,9 @@ def check_step(lb, cfg, ctx, m, seqs, flags, seed=0):
     # hidden states and logits: tier 1 on the first layer, tier 2 everywhere
     assert np.median(row_errs(ctx.read_tap(0), m.read_tap(0))) <= CLEAN_TOL
     for l in range(cfg.layers + 1):
-        assert_close(ctx.read_tap(l), m.read_tap(l), "residual after layer %d" % l)
+        assert_close(ctx.read_tap(l), m.read_tap(l), "residual after layer %d" % l, cal_taps[l])
     lg, lo_ = ctx.read_logits(), m.read_logits()
-    assert_close(lg, lo_, "logits")
+    assert_close(lg, lo_, "logits", cal_logits)
     # the fused argmax equals the argmax of the device's own logits exactly (ties to the lower id)
     ids, vals = ctx.read_argmax()
     assert np.array_equal(ids, lg.argmax(axis=1)) and np.array_equal(vals, lg.max(axis=1))
