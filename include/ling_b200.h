@@ -250,6 +250,25 @@ int ling_b200_gemm_fp8_host(int device, int impl, int splits, const float* x, co
 /* The same GEMM timed on the device with resident operands: ms per launch over `iters` launches. */
 int ling_b200_gemm_fp8_bench(int device, int impl, int splits, int M, int N, int K, int iters, float* ms_per_launch);
 
+/* No counterpart in the reference.  The same block-scaled FP8 GEMM for hosts that must not allocate device memory on
+ * this path: a serving loop that gave the whole device to its own arena at start-up, a real-time thread for which an
+ * allocation's implicit synchronization is not acceptable, a sandboxed plugin that receives buffers but may not create
+ * them.  The K splits' partial-sum planes, which the other entry points allocate, live in a 16 MiB __device__ array built
+ * into the library (every GPU that loads it carries the array until the process exits).  This call makes no cudaMalloc /
+ * cudaFree and calls no allocating library routine.
+ *   All pointers are DEVICE pointers in the library's operand layouts, padded with zero codes:
+ *   w_codes [N_pad][K_pad] E4M3, w_scales [K_pad/128][N_pad] fp32, x_codes [128][K_pad] E4M3 (rows >= M unused),
+ *   x_scales [K_pad/128][128] fp32, y [M][N] fp32; N_pad, K_pad = N, K rounded up to 128.
+ *   Limits: M <= LING_B200_NOALLOC_MAX_ROWS and N_pad <= 32768 (one plane must fit the array); beyond them the call
+ *   returns LING_B200_ERR_ARG and touches nothing.  The K split is the regular one unless the array holds fewer planes.
+ *   The first call on a device looks the array's address up (cudaGetSymbolAddress) and sets kernel attributes: make it
+ *   before any stream capture.  The call enqueues on `stream` (NULL = the default stream), waits for it and returns the
+ *   status.  Every call shares the array: calls that overlap on the GPU race.  Nothing in it needs clearing by the caller. */
+#define LING_B200_NOALLOC_MAX_ROWS 128
+#define LING_B200_NOALLOC_SCRATCH_BYTES (16u << 20)
+int ling_b200_gemm_fp8_noalloc(const uint8_t* w_codes, const float* w_scales, const uint8_t* x_codes, const float* x_scales,
+                               float* y, int M, int N, int K, void* stream);
+
 /* attention_rows(_seqs) + attention_combine (kernels.cuh:223-290; kernels.cu:919-961) for one full-attention layer (index
  * among the attention layers): q [rows][heads][head_dim] (normed, rotated); every row attends to its sequence's context
  * [0, pos) and to the in-flight positions pos + j of its own root-to-row path, as the slot's cache holds them (write them
