@@ -249,6 +249,11 @@ int ling_b200_sync(ling_b200_ctx* ctx);
 int ling_b200_gemm_fp8_host(int device, int impl, int splits, const float* x, const float* w, float* y, int M, int N, int K);
 /* The same GEMM timed on the device with resident operands: ms per launch over `iters` launches. */
 int ling_b200_gemm_fp8_bench(int device, int impl, int splits, int M, int N, int K, int iters, float* ms_per_launch);
+/* The GEMM's response to weights already in L2: per iteration [flush 1: write 256 MiB, flush 2: read 256 MiB] -> ask for the first `slabs` K
+ * blocks of every CTA's range to be brought into L2 (mode 0: TMA prefetch, 1: plain loads; slabs 0: nothing) -> a
+ * one-thread kernel that spins delay_us -> the GEMM, timed alone with events.  Mean ms of the GEMM over iters. */
+int ling_b200_gemm_prefetch_bench(int device, int M, int N, int K, int slabs, int mode, int delay_us, int flush, int iters,
+                                  float* ms_per_launch);
 
 /* No counterpart in the reference.  The same block-scaled FP8 GEMM for hosts that must not allocate device memory on
  * this path: a serving loop that gave the whole device to its own arena at start-up, a real-time thread for which an

@@ -367,6 +367,12 @@ def gemm_fp8_bench(M, N, K, impl=0, splits=0, iters=20, device=0):
     return ms.value
 
 
+def gemm_prefetch_bench(M, N, K, slabs, mode=0, delay_us=30, flush=1, iters=10, device=0):
+    ms = C.c_float()
+    check(lib().ling_b200_gemm_prefetch_bench(device, M, N, K, slabs, mode, delay_us, flush, iters, C.byref(ms)), "gemm_prefetch_bench")
+    return ms.value
+
+
 def describe_tree(parent, chain):
     par = np.ascontiguousarray(parent, np.int32)
     t = TreeDesc()

@@ -3,8 +3,8 @@
 // Kernel shape (one CTA = one 128-row weight tile x one K split x one token tile):
 //   warp 0   TMA producer: per 128-wide K block, one 128x128B weight tile and one NTx128B activation tile into a
 //            128B-swizzled stage, completion counted on the stage's mbarrier (no multicast, no cluster).
-//   warp 1   MMA issuer (one elected lane): four tcgen05.mma kind::f8f6f4 (K = 32 each) per stage into one of two TMEM
-//            accumulator buffers, then tcgen05.commit to the stage's "empty" barrier and the buffer's "full" barrier.
+//   warp 1   MMA issuer (one elected lane): four tcgen05.mma kind::f8f6f4 (K = 32 each) per stage into one of the TMEM
+//            accumulator buffers (four; two for the 96-row token tile), then tcgen05.commit to the stage's "empty" barrier and the buffer's "full" barrier.
 //            Also owns the TMEM allocation.
 //   warps 2-5 epilogue: tcgen05.ld of the finished buffer, acc += partial * (weight scale * activation scale) in
 //            registers (the 1x128 fp32 block scales are not a native tcgen05 scale format, so each K block is
@@ -120,6 +120,30 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
       : "r"(taddr)
       : "memory");
 }
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, "
+      "%19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]),
+        "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]),
+        "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+}
+template <int CH>
+__device__ __forceinline__ void tmem_ld(uint32_t taddr, uint32_t (&v)[CH]) {
+  if constexpr (CH == 32) tmem_ld32(taddr, v);
+  else tmem_ld16(taddr, v);
+}
+__device__ __forceinline__ void ldgsts16(void* dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void ldgsts_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void ldgsts_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 // Asks the TMA unit to bring one tile of a tensor map into L2 (no shared-memory destination, nothing to wait on).
 __device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* map, int x, int y) {
@@ -128,7 +152,13 @@ __device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* map, int x
 }
 
 constexpr int kABytes = kTileN * kBlockK;  // 16 KiB
-__host__ __device__ constexpr int tmem_cols(int nt) { return 2 * nt <= 32 ? 32 : 2 * nt <= 64 ? 64 : 2 * nt <= 128 ? 128 : 256; }
+// TMEM accumulator buffers per CTA: the MMA of K block i + bufs may start as soon as the epilogue has drained block i,
+// so the epilogue's latency per block is spread over `bufs` blocks.  Columns are allocated in powers of two; two CTAs
+// share an SM's 512 columns for the narrow token tiles.
+__host__ __device__ constexpr int acc_bufs(int nt) { return nt == 96 ? 2 : 4; }
+__host__ __device__ constexpr int tmem_cols(int nt) { return nt == 32 ? 128 : nt == 128 ? 512 : 256; }
+constexpr int kScaleAhead = 4;  // K blocks by which the epilogue's scale loads run ahead of its accumulator reads
+constexpr int kScaleRing = 8;   // slots of each epilogue warp's activation-scale ring (> kScaleAhead)
 __host__ __device__ constexpr int stages_for(int nt) { return nt == 32 ? 5 : nt == 64 ? 4 : nt == 96 ? 3 : 6; }
 __host__ __device__ constexpr int ctas_per_sm(int nt) { return nt == 128 ? 1 : 2; }
 constexpr int kGemmThreads = 192;
@@ -142,7 +172,7 @@ struct HeadArgs {
 
 constexpr size_t gemm_smem_bytes(int nt) {
   return size_t(stages_for(nt)) * (kABytes + nt * kBlockK) + 1024 /* alignment slack */ + 512 /* barriers */ +
-         size_t(4) * nt * 8 /* head argmax scratch */;
+         size_t(4) * nt * 8 /* head argmax scratch */ + size_t(4) * kScaleRing * nt * 4 /* activation-scale rings */;
 }
 
 template <int NT>
@@ -167,11 +197,13 @@ __global__ void __launch_bounds__(kGemmThreads, ctas_per_sm(NT))
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * kStageBytes);
   uint64_t* empty = full + STAGES;
   uint64_t* tmem_full = empty + STAGES;
-  uint64_t* tmem_empty = tmem_full + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  constexpr int BUFS = acc_bufs(NT);
+  uint64_t* tmem_empty = tmem_full + 4;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* red_val = reinterpret_cast<float*>(tmem_slot + 4);  // [4][NT]
   int* red_idx = reinterpret_cast<int*>(red_val + 4 * NT);   // [4][NT]
+  float* xs_ring = reinterpret_cast<float*>(smem + STAGES * kStageBytes + 512 + 4 * NT * 8);  // [4 warps][kScaleRing][NT]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // token tiles vary fastest: the CTAs that share a weight tile run together, so only the first of them reads it from HBM
@@ -184,7 +216,7 @@ __global__ void __launch_bounds__(kGemmThreads, ctas_per_sm(NT))
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
     }
-    for (int b = 0; b < 2; ++b) {
+    for (int b = 0; b < BUFS; ++b) {
       mbar_init(&tmem_full[b], 1);
       mbar_init(&tmem_empty[b], 4);
     }
@@ -258,8 +290,8 @@ __global__ void __launch_bounds__(kGemmThreads, ctas_per_sm(NT))
     if (lane == 0) {
       constexpr uint32_t idesc = umma_idesc_e4m3(NT);
       for (int i = 0; i < nslab; ++i) {
-        const int s = i % STAGES, buf = i & 1;
-        const uint32_t ph = (i / STAGES) & 1, bph = (i >> 1) & 1;
+        const int s = i % STAGES, buf = i % BUFS;
+        const uint32_t ph = (i / STAGES) & 1, bph = (i / BUFS) & 1;
         if (!mbar_wait(&tmem_empty[buf], bph ^ 1, abort_flag)) {
           dev_fail(err_flag, kDevWaitTmemEmpty);
           *abort_flag = 1;
@@ -291,12 +323,32 @@ __global__ void __launch_bounds__(kGemmThreads, ctas_per_sm(NT))
     float acc[NT];
 #pragma unroll
     for (int j = 0; j < NT; ++j) acc[j] = 0.f;
+    // The block scales run ahead of the accumulators: this row's weight scale of the next kScaleAhead K blocks sits in
+    // registers, the token rows' activation scales arrive by cp.async in this warp's ring in shared memory.  Neither
+    // load is then on the per-block critical path (wait for the MMA, read TMEM, promote, release the buffer).
+    float* ring = xs_ring + (warp - 2) * kScaleRing * NT;
+    auto fetch_xs = [&](int i) {
+      if (i < nslab && lane < NT / 4) ldgsts16(ring + (i % kScaleRing) * NT + lane * 4, xs + size_t(kb0 + i) * xrows + m0 + lane * 4);
+      ldgsts_commit();
+    };
+    float wq[kScaleAhead];
+#pragma unroll
+    for (int j = 0; j < kScaleAhead; ++j) {
+      wq[j] = j < nslab ? __ldg(ws + size_t(kb0 + j) * N_pad + n) : 0.f;
+      fetch_xs(j);
+    }
     bool ok = true;
     for (int i = 0; i < nslab && ok; ++i) {
-      const int buf = i & 1, kb = kb0 + i;
-      const uint32_t bph = (i >> 1) & 1;
-      const float wsc = __ldg(ws + size_t(kb) * N_pad + n);
-      const float4* xs4 = reinterpret_cast<const float4*>(xs + size_t(kb) * xrows + m0);
+      const int buf = i % BUFS;
+      const uint32_t bph = (i / BUFS) & 1;
+      const float wsc = wq[0];
+#pragma unroll
+      for (int j = 0; j + 1 < kScaleAhead; ++j) wq[j] = wq[j + 1];
+      wq[kScaleAhead - 1] = i + kScaleAhead < nslab ? __ldg(ws + size_t(kb0 + i + kScaleAhead) * N_pad + n) : 0.f;
+      fetch_xs(i + kScaleAhead);
+      ldgsts_wait<kScaleAhead>();  // the group of block i has landed (this lane's part)
+      __syncwarp();                // ... and every lane's part
+      const float4* xs4 = reinterpret_cast<const float4*>(ring + (i % kScaleRing) * NT);
       ok = mbar_wait(&tmem_full[buf], bph, abort_flag);
       if (!ok) {
         dev_fail(err_flag, kDevWaitTmemFull);
@@ -305,24 +357,27 @@ __global__ void __launch_bounds__(kGemmThreads, ctas_per_sm(NT))
       }
       tc_fence_after();
       const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(buf * NT);
+      // columns per TMEM read: the whole accumulator for the 32-row token tile, 16 at a time for the wider ones (registers)
+      constexpr int CH = NT == 32 ? 32 : 16;
 #pragma unroll
-      for (int c = 0; c < NT / 16; ++c) {
-        uint32_t v[16];
-        tmem_ld16(taddr + c * 16, v);
+      for (int c = 0; c < NT / CH; ++c) {
+        uint32_t v[CH];
+        tmem_ld<CH>(taddr + c * CH, v);
         tmem_ld_wait();
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const float4 s4 = __ldg(xs4 + c * 4 + q);
-          acc[c * 16 + q * 4 + 0] = fmaf(__uint_as_float(v[q * 4 + 0]), wsc * s4.x, acc[c * 16 + q * 4 + 0]);
-          acc[c * 16 + q * 4 + 1] = fmaf(__uint_as_float(v[q * 4 + 1]), wsc * s4.y, acc[c * 16 + q * 4 + 1]);
-          acc[c * 16 + q * 4 + 2] = fmaf(__uint_as_float(v[q * 4 + 2]), wsc * s4.z, acc[c * 16 + q * 4 + 2]);
-          acc[c * 16 + q * 4 + 3] = fmaf(__uint_as_float(v[q * 4 + 3]), wsc * s4.w, acc[c * 16 + q * 4 + 3]);
+        for (int q = 0; q < CH / 4; ++q) {
+          const float4 s4 = xs4[c * (CH / 4) + q];
+          acc[c * CH + q * 4 + 0] = fmaf(__uint_as_float(v[q * 4 + 0]), wsc * s4.x, acc[c * CH + q * 4 + 0]);
+          acc[c * CH + q * 4 + 1] = fmaf(__uint_as_float(v[q * 4 + 1]), wsc * s4.y, acc[c * CH + q * 4 + 1]);
+          acc[c * CH + q * 4 + 2] = fmaf(__uint_as_float(v[q * 4 + 2]), wsc * s4.z, acc[c * CH + q * 4 + 2]);
+          acc[c * CH + q * 4 + 3] = fmaf(__uint_as_float(v[q * 4 + 3]), wsc * s4.w, acc[c * CH + q * 4 + 3]);
         }
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty[buf]);
     }
+    ldgsts_wait<0>();
     {
       const bool store = ok && (head.tile_val == nullptr || head.store_logits);
       if (store && n < N) {
@@ -377,6 +432,59 @@ __global__ void __launch_bounds__(kGemmThreads, ctas_per_sm(NT))
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------------------------- L2 prefetch
+// Brings the weight tiles a GEMM will read first into L2 ahead of the GEMM, from a parallel branch of the step's graph,
+// so that HBM keeps streaming weights while the small kernels between two GEMMs run.  Unit u = (K block j of every
+// CTA's range, CTA): the first `slabs` K blocks of every (tile, split) pair, earliest K blocks first -- the order in
+// which a one-wave GEMM consumes them.  mode 0: one TMA prefetch instruction per 16 KiB tile (no SM data path);
+// mode 1: plain loads of one word per 32-byte sector (the same bytes through the load/store units; a cross-check of
+// what the TMA prefetch achieves).  Reads weights only, which no kernel of a step writes.
+__global__ void __launch_bounds__(128)
+    weight_prefetch_kernel(const __grid_constant__ CUtensorMap mapW, const uint8_t* __restrict__ codes, int K_pad, int tiles,
+                           int splits, int KB, int slabs, int mode, int* sink) {
+  const int ctas = tiles * splits;
+  const int units = ctas * slabs;
+  if (mode == 0) {
+    for (int u = blockIdx.x * blockDim.x + threadIdx.x; u < units; u += gridDim.x * blockDim.x) {
+      const int j = u / ctas, c = u % ctas, split = c % splits, tile = c / splits;
+      const int kb0 = int(int64_t(KB) * split / splits), kb1 = int(int64_t(KB) * (split + 1) / splits);
+      if (kb0 + j < kb1) tma_prefetch_l2_2d(&mapW, (kb0 + j) * kBlockK, tile * kTileN);
+    }
+    return;
+  }
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31, warps = (gridDim.x * blockDim.x) >> 5;
+  int acc = 0;
+  for (int u = warp; u < units; u += warps) {
+    const int j = u / ctas, c = u % ctas, split = c % splits, tile = c / splits;
+    const int kb0 = int(int64_t(KB) * split / splits), kb1 = int(int64_t(KB) * (split + 1) / splits);
+    if (kb0 + j >= kb1) continue;
+    const uint8_t* base = codes + size_t(tile) * kTileN * K_pad + size_t(kb0 + j) * kBlockK;
+#pragma unroll 4
+    for (int i = lane; i < kTileN * 4; i += 32)  // 128 rows x 4 sectors
+      acc ^= __ldcg(reinterpret_cast<const int*>(base + size_t(i >> 2) * K_pad + (i & 3) * 32));
+  }
+  if (acc == 0x5a5a5a5a && sink) *sink = acc;  // keeps the loads alive
+}
+
+// Reads a buffer larger than L2: afterwards L2 holds clean lines of that buffer (a write flush leaves dirty lines whose
+// write-back then competes with the kernel being timed).
+__global__ void __launch_bounds__(256) read_flush_kernel(const int4* __restrict__ buf, size_t n, int* sink) {
+  int acc = 0;
+  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += size_t(gridDim.x) * blockDim.x) {
+    const int4 v = __ldcg(buf + i);
+    acc ^= v.x ^ v.y ^ v.z ^ v.w;
+  }
+  if (acc == 0x5a5a5a5a && sink) *sink = acc;
+}
+
+// Spins for about `ns` nanoseconds (bounded by construction); a stand-in for the kernels between two GEMMs in the
+// prefetch micro-benchmark.
+__global__ void delay_kernel(unsigned long long ns) {
+  const unsigned long long t0 = global_ns();
+  while (global_ns() - t0 < ns) {
   }
 }
 
@@ -534,6 +642,29 @@ int make_acts_maps(Fp8Acts& x) {
     const int nt = 32 * (i + 1);
     if (const int r = encode_2d(&x.map[i], x.codes, uint64_t(x.K_pad), uint64_t(x.rows_alloc), uint32_t(nt))) return r;
   }
+  return LING_B200_OK;
+}
+
+int weight_prefetch_launch(const Fp8Matrix& W, int splits, int slabs, int mode, int* sink, cudaStream_t stream) {
+  if (slabs < 1) return LING_B200_OK;
+  const int tiles = W.N_pad / kTileN;
+  const int units = tiles * splits * slabs;
+  const int per_block = mode == 0 ? 128 : 4;
+  const int blocks = std::max(1, std::min(ceil_div(units, per_block), mode == 0 ? 148 : 148 * 8));
+  weight_prefetch_kernel<<<blocks, 128, 0, stream>>>(W.map, W.codes, W.K_pad, tiles, splits, W.KB, slabs, mode, sink);
+  LB_LAUNCH("weight_prefetch_kernel");
+  return LING_B200_OK;
+}
+
+int read_flush_launch(const float* buf, size_t n, int* sink, cudaStream_t stream) {
+  read_flush_kernel<<<148 * 8, 256, 0, stream>>>(reinterpret_cast<const int4*>(buf), n / 4, sink);
+  LB_LAUNCH("read_flush_kernel");
+  return LING_B200_OK;
+}
+
+int delay_launch(unsigned long long ns, cudaStream_t stream) {
+  delay_kernel<<<1, 1, 0, stream>>>(ns > 10000000ull ? 10000000ull : ns);
+  LB_LAUNCH("delay_kernel");
   return LING_B200_OK;
 }
 

@@ -162,6 +162,57 @@ int ling_b200_gemm_fp8_bench(int device, int impl, int splits, int M, int N, int
   return LING_B200_OK;
 }
 
+int ling_b200_gemm_prefetch_bench(int device, int M, int N, int K, int slabs, int mode, int delay_us, int flush, int iters,
+                                  float* ms_per_launch) {
+  if (M < 1 || N < 1 || K < 1 || iters < 1 || iters > 1000 || !ms_per_launch || M > LING_B200_MAX_ROWS || slabs < 0 ||
+      delay_us < 0 || delay_us > 10000) {
+    set_error("gemm_prefetch_bench: bad argument");
+    return LING_B200_ERR_ARG;
+  }
+  LB_TRY(check_device(device));
+  Scratch sc;
+  GemmSetup g;
+  LB_TRY(setup_gemm(sc, g, M, N, K, 0));
+  const size_t flush_n = size_t(64) << 20;  // 256 MiB of floats: twice the L2
+  float* dx = sc.get<float>(size_t(M) * K, false);
+  float* fl = sc.get<float>(flush_n, true);
+  int* sink = sc.get<int>(1);
+  LB_PTR(dx && fl && sink);
+  LB_TRY(fill_f32_launch(stream_key(1, 7), 1.f, dx, size_t(M) * K, 0));
+  LB_TRY(quant_weight_launch(nullptr, stream_key(1, 9), 0.02f, 1, g.W.codes, g.W.scales, 0, N, K, g.W.N_pad, g.W.K_pad, 0));
+  LB_TRY(quant_acts_launch(dx, M, QuantOut{g.X.codes, g.X.scales, K, g.X.K_pad, g.X.rows_alloc}, 0));
+  GemmCall c;
+  c.W = &g.W, c.X = &g.X, c.M = M, c.out = g.out, c.ld = g.W.N_pad;
+  c.split_stride = size_t(g.X.rows_alloc) * g.W.N_pad;
+  c.impl = 0, c.err_flag = g.err;
+  cudaEvent_t a, b;
+  LB_CUDA(cudaEventCreate(&a));
+  LB_CUDA(cudaEventCreate(&b));
+  double total = 0.0;
+  for (int i = 0; i < iters + 2; ++i) {
+    if (flush == 1) LB_TRY(flush_launch(fl, flush_n, 0));
+    if (flush == 2) LB_TRY(read_flush_launch(fl, flush_n, sink, 0));
+    LB_TRY(weight_prefetch_launch(g.W, g.W.splits, slabs, mode, sink, 0));
+    LB_TRY(delay_launch(uint64_t(delay_us) * 1000ull, 0));
+    LB_CUDA(cudaEventRecord(a, 0));
+    LB_TRY(gemm_launch(c, 0));
+    LB_CUDA(cudaEventRecord(b, 0));
+    LB_CUDA(cudaEventSynchronize(b));
+    float ms = 0.f;
+    LB_CUDA(cudaEventElapsedTime(&ms, a, b));
+    if (i >= 2) total += ms;
+  }
+  cudaEventDestroy(a), cudaEventDestroy(b);
+  int err = 0;
+  LB_CUDA(cudaMemcpy(&err, g.err, 4, cudaMemcpyDeviceToHost));
+  if (err) {
+    set_error("gemm: device error word = " + std::to_string(err));
+    return LING_B200_ERR_DEVICE_FLAG;
+  }
+  *ms_per_launch = float(total / iters);
+  return LING_B200_OK;
+}
+
 namespace {
 // A one-sequence StepBuffers for the DeltaNet kernels.
 struct OneSeq {

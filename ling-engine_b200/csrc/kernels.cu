@@ -656,35 +656,52 @@ __device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
 
 constexpr float kPScale = 256.f;  // p * v_scale is carried in FP16 times this power of two (kept clear of subnormals)
 
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+  const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(p));
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(a));
+}
+// Position of reduction index c (0..15) inside its group of 16 after the permutation that makes a thread's four
+// B-fragment values of one m16n8k16 MMA (logical k 2t, 2t+1, 2t+8, 2t+9) four consecutive bytes 4t .. 4t+3 of the FP8
+// operand: physical c = 4t + j sits at logical 2t + j (j < 2) or 8 + 2t + j - 2 (j >= 2).
+__host__ __device__ constexpr int perm16(int c) { return (c & 3) < 2 ? 2 * (c >> 2) + (c & 3) : 8 + 2 * (c >> 2) + (c & 3) - 2; }
+
 // Tree-masked attention over the paged FP8 cache, flash-decoding style (the reference's attention_rows,
 // src/core/kernels.cu:919-961 with body src/core/attention_body.cuh:262-501, rebuilt for an FP8 cache and any number
-// of sequences).  Work item = (sequence, kv head, key chunk, 64 query rows); the query rows of a kv head are
+// of sequences).  Work item = (sequence, kv head, key chunk, kAttnRowTile query rows); the query rows of a kv head are
 // (token row, q head of the group) pairs, so one pass over a K/V tile serves every row of the tree and every q head
 // of the group.  Context chunks hold kAttnChunk keys; the last chunk of a sequence is its in-flight rows (cache slots
 // pos .. pos + n_rows), read from the 16-aligned position below pos so that every copy stays 16-byte aligned; a row sees
 // an in-flight key only where its ancestor mask has the bit.  K tiles ([key][D]) and V tiles ([D][key], the pool's V
 // layout) arrive by 16-byte cp.async into double-buffered shared memory and stay E4M3 there; fragments are converted on
 // load (cvt.f16x2.e4m3x2) and the per-position scales are applied to scores and probabilities in fp32.
-// Shared-memory traffic is what bounds the inner loops, so the fragment loads are wide: the reduction index of
-// Q.K^T is permuted within each group of 16 dims (thread t of a quad takes physical dims 4t .. 4t+3 as logical k
-// 2t, 2t+1, 2t+8, 2t+9: one 64-bit load of Q and one 32-bit load of K per MMA), and the V fragment of 16 keys is one
-// 128-bit load shared by the quad.
+// The FP8 -> FP16 conversion unit is what bounds the inner loops, so every converted fragment is used for all query
+// rows of the CTA: for Q.K^T the four warps split the tile's 64 keys (16 each) and each multiplies them with all the
+// rows; the probabilities go through shared memory as FP16; for P.V the warps split the head dimension (D/4 each) and
+// each again covers all rows.  The reduction index of both products is permuted within groups of 16 (perm16) so that a
+// thread's B fragment is one 32-bit load of four consecutive FP8 bytes: Q is stored permuted along d, P along keys.
 // Output: per (chunk slot, query row) the unnormalized sum and (max, denominator); attn_combine_kernel merges chunks.
 template <int D, int G>
-__global__ void __launch_bounds__(128, (D > 128 ? 2 : 4))
+__global__ void __launch_bounds__(128, 2)
     attention_kernel(const __half* __restrict__ q, StepBuffers sb, ModelDims d, int al, KvPoolDev kv, float* __restrict__ part_o,
                      float* __restrict__ part_ml, int chunk_slots) {
   pdl_sync();  // first statement: see common.cuh
-  constexpr int QS = D + 8;    // halves per Q row in shared memory
-  constexpr int KS = D + 16;   // bytes per K row (one key) in shared memory
+  constexpr int QS = D + 8;              // halves per Q row in shared memory
+  constexpr int KS = D + 16;             // bytes per K row (one key) in shared memory
   constexpr int VS = kAttnKeyTile + 16;  // bytes per V row (one dim, 64 keys) in shared memory
+  constexpr int PS = kAttnKeyTile + 8;   // halves per P row in shared memory
+  constexpr int MT = kAttnRowTile / 16;  // m16 row tiles per CTA
+  constexpr int NTO = D / 32;            // n8 output tiles per warp (D/4 dims)
   constexpr int RMAX = kTreeRows * G;
   extern __shared__ __align__(16) uint8_t smem[];
-  __half* Qs = reinterpret_cast<__half*>(smem);                         // [64][QS]
-  uint8_t* Ks8 = smem + size_t(kAttnRowTile) * QS * 2;                  // [2][64][KS]
-  uint8_t* Vs8 = Ks8 + 2 * kAttnKeyTile * KS;                           // [2][D][VS]
-  float* ksc = reinterpret_cast<float*>(Vs8 + 2 * D * VS);              // [2][64]
-  float* vsc = ksc + 2 * kAttnKeyTile;                                  // [2][64]
+  __half* Qs = reinterpret_cast<__half*>(smem);                          // [RowTile][QS], d permuted within 16s
+  __half* Ps = Qs + kAttnRowTile * QS;                                   // [RowTile][PS], keys permuted within 16s
+  uint8_t* Ks8 = reinterpret_cast<uint8_t*>(Ps + kAttnRowTile * PS);     // [2][64][KS]
+  uint8_t* Vs8 = Ks8 + 2 * kAttnKeyTile * KS;                            // [2][D][VS]
+  float* ksc = reinterpret_cast<float*>(Vs8 + 2 * D * VS);               // [2][64]
+  float* vsc = ksc + 2 * kAttnKeyTile;                                   // [2][64]
+  float* redm = vsc + 2 * kAttnKeyTile;                                  // [4 warps][RowTile]
   __shared__ int cbase[LING_B200_MAX_SEQS + 1], ibase[LING_B200_MAX_SEQS + 1];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g8 = lane >> 2, t4 = lane & 3;
@@ -702,6 +719,9 @@ __global__ void __launch_bounds__(128, (D > 128 ? 2 : 4))
   __syncthreads();
   const float inv_sqrt_d = rsqrtf(float(D));
   const int pt = d.page_tokens;
+  // ldmatrix row addresses of this lane inside a 16x16 A tile: matrices 0..3 = (rows 0-7, k 0-7), (rows 8-15, k 0-7),
+  // (rows 0-7, k 8-15), (rows 8-15, k 8-15)
+  const int lm_row = (lane & 7) + ((lane >> 3) & 1) * 8, lm_col = (lane >> 4) * 8;
 
   for (int item = blockIdx.x; item < ibase[nseq]; item += gridDim.x) {
     int s = 0;
@@ -722,6 +742,7 @@ __global__ void __launch_bounds__(128, (D > 128 ? 2 : 4))
     const int key_lo = tail ? sq.pos - key_base : 0;
     const int key_hi = tail ? key_lo + sq.n_rows : min(kAttnChunk, sq.pos - key_base);
     const int R = sq.n_rows * G, r_begin = rg * kAttnRowTile, r0 = sb.row0[s];
+    const int mt_n = min(MT, (R - r_begin + 15) / 16);  // row tiles that hold a real row
     const int* table = kv.tables + size_t(sq.slot) * d.max_pages;
     const size_t kpage0 = kv_slot_index(d, al, 0, hk, 0, 0), vpage0 = kv_slot_index(d, al, 1, hk, 0, 0);
 
@@ -731,7 +752,10 @@ __global__ void __launch_bounds__(128, (D > 128 ? 2 : 4))
       uint4 val = make_uint4(0, 0, 0, 0);
       const int rr = r_begin + r;
       if (rr < R) val = *reinterpret_cast<const uint4*>(q + (size_t(r0 + rr / G) * d.Hq + hk * G + rr % G) * D + part * 8);
-      *reinterpret_cast<uint4*>(Qs + size_t(r) * QS + part * 8) = val;
+      // physical dims 8 * (part & 1) + {0,1 | 2,3 | 4,5 | 6,7} of the 16-group go to their permuted places
+      uint32_t* dst = reinterpret_cast<uint32_t*>(Qs + size_t(r) * QS + (part >> 1) * 16);
+      const int c0 = (part & 1) * 8;
+      dst[perm16(c0) >> 1] = val.x, dst[perm16(c0 + 2) >> 1] = val.y, dst[perm16(c0 + 4) >> 1] = val.z, dst[perm16(c0 + 6) >> 1] = val.w;
     }
     auto page_of = [&](int pos) {
       int page = table[pos / pt];
@@ -771,18 +795,21 @@ __global__ void __launch_bounds__(128, (D > 128 ? 2 : 4))
         Vs8[(size_t(buf) * D + idx / (last - first)) * VS + first + idx % (last - first)] = 0;
     };
 
-    float O[D / 8][4];
+    // This thread's rows: row tile mt holds rows mt * 16 + g8 (index 2 * mt) and + 8 (index 2 * mt + 1), the same in
+    // every warp; O[mt][nt] covers output dims warp * D/4 + nt * 8 + 2 * t4 .. + 1.
+    float O[MT][NTO][4];
 #pragma unroll
-    for (int i = 0; i < D / 8; ++i) O[i][0] = O[i][1] = O[i][2] = O[i][3] = 0.f;
-    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
-    // this thread's two query rows and their ancestor masks (tail chunk only)
-    const int rowA = r_begin + warp * 16 + g8, rowB = rowA + 8;
-    uint32_t ancA = 0xffffffffu, ancB = 0xffffffffu;
-    if (tail) {
-      ancA = rowA < R ? sb.anc[r0 + rowA / G] : 0u;
-      ancB = rowB < R ? sb.anc[r0 + rowB / G] : 0u;
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int i = 0; i < NTO; ++i) O[mt][i][0] = O[mt][i][1] = O[mt][i][2] = O[mt][i][3] = 0.f;
+    float m_run[2 * MT], l_run[2 * MT];
+    uint32_t anc[2 * MT];
+#pragma unroll
+    for (int r = 0; r < 2 * MT; ++r) {
+      m_run[r] = -INFINITY, l_run[r] = 0.f;
+      const int row = r_begin + (r >> 1) * 16 + g8 + (r & 1) * 8;
+      anc[r] = !tail ? 0xffffffffu : (row < R ? sb.anc[r0 + row / G] : 0u);
     }
-    const bool warp_active = r_begin + warp * 16 < R;
 
     const int ntiles = (key_hi + kAttnKeyTile - 1) / kAttnKeyTile;
     load_tile(0, 0);
@@ -799,97 +826,135 @@ __global__ void __launch_bounds__(128, (D > 128 ? 2 : 4))
         clear_v_tail(tile, buf);
         __syncthreads();
       }
-      if (warp_active) {
-        const uint8_t* Kt = Ks8 + size_t(buf) * kAttnKeyTile * KS;
-        const uint8_t* Vt = Vs8 + size_t(buf) * D * VS;
-        float S[8][4];
+      const uint8_t* Kt = Ks8 + size_t(buf) * kAttnKeyTile * KS;
+      const uint8_t* Vt = Vs8 + size_t(buf) * D * VS;
+      // ---- S = Q . K^T for this warp's 16 keys (two n8 tiles) and every row tile
+      float S[MT][2][4];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) S[i][0] = S[i][1] = S[i][2] = S[i][3] = 0.f;
-        const __half* qa = Qs + size_t(warp * 16 + g8) * QS + 4 * t4;
-        const uint8_t* ka = Kt + size_t(g8) * KS + 4 * t4;
+      for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) S[mt][nt][0] = S[mt][nt][1] = S[mt][nt][2] = S[mt][nt][3] = 0.f;
+      const uint8_t* ka = Kt + size_t(warp * 16 + g8) * KS + 4 * t4;
+      const __half* qa = Qs + size_t(lm_row) * QS + lm_col;
 #pragma unroll 4
-        for (int kt = 0; kt < D / 16; ++kt) {
-          const uint2 qA = *reinterpret_cast<const uint2*>(qa + kt * 16);           // row g8:     (a0, a2)
-          const uint2 qB = *reinterpret_cast<const uint2*>(qa + 8 * QS + kt * 16);  // row g8 + 8: (a1, a3)
+      for (int kt = 0; kt < D / 16; ++kt) {
+        uint32_t bk[2][2];
 #pragma unroll
-          for (int nt = 0; nt < 8; ++nt) {
-            const uint32_t kw = *reinterpret_cast<const uint32_t*>(ka + size_t(nt * 8) * KS + kt * 16);
-            mma_f16(S[nt], qA.x, qB.x, qA.y, qB.y, e4m3x2_to_h2(uint16_t(kw)), e4m3x2_to_h2(uint16_t(kw >> 16)));
+        for (int nt = 0; nt < 2; ++nt) {
+          const uint32_t kw = *reinterpret_cast<const uint32_t*>(ka + size_t(nt * 8) * KS + kt * 16);
+          bk[nt][0] = e4m3x2_to_h2(uint16_t(kw)), bk[nt][1] = e4m3x2_to_h2(uint16_t(kw >> 16));
+        }
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+          if (mt < mt_n) {
+            uint32_t a[4];
+            ldmatrix_x4(a, qa + size_t(mt * 16) * QS + kt * 16);
+            mma_f16(S[mt][0], a[0], a[1], a[2], a[3], bk[0][0], bk[0][1]);
+            mma_f16(S[mt][1], a[0], a[1], a[2], a[3], bk[1][0], bk[1][1]);
           }
         }
-        // scores: scale, mask, running max
-        const int k0 = tile * kAttnKeyTile;
-        float tmax[2] = {-INFINITY, -INFINITY};
+      }
+      // ---- scale and mask; the tile's row maxima go through shared memory (each warp saw a quarter of the keys)
+      const int k0 = tile * kAttnKeyTile;
+      float kscl[2][2], vscl[2][2];
+      bool inrange[2][2];
 #pragma unroll
-        for (int nt = 0; nt < 8; ++nt)
+      for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int key = nt * 8 + 2 * t4 + (e & 1);
-            const int kk = k0 + key;  // index inside the chunk
-            const uint32_t anc = (e < 2) ? ancA : ancB;
-            const bool vis = kk >= key_lo && kk < key_hi && (!tail || ((anc >> (kk - key_lo)) & 1u));
-            const float sv = vis ? S[nt][e] * (ksc[buf * kAttnKeyTile + key] * inv_sqrt_d) : -INFINITY;
-            S[nt][e] = sv;
-            tmax[e >> 1] = fmaxf(tmax[e >> 1], sv);
-          }
-        float corr[2], muse[2];
+        for (int e = 0; e < 2; ++e) {
+          const int key = warp * 16 + nt * 8 + 2 * t4 + e;
+          kscl[nt][e] = ksc[buf * kAttnKeyTile + key] * inv_sqrt_d;
+          vscl[nt][e] = vsc[buf * kAttnKeyTile + key] * kPScale;
+          inrange[nt][e] = k0 + key >= key_lo && k0 + key < key_hi;
+        }
+      const int kbit = k0 + warp * 16 + 2 * t4 - key_lo;  // + nt * 8 + e: the key's bit in the ancestor mask (tail chunk)
 #pragma unroll
-        for (int r = 0; r < 2; ++r) {
-          tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 1));
-          tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 2));
-          const float mnew = fmaxf(m_run[r], tmax[r]);
-          muse[r] = mnew == -INFINITY ? 0.f : mnew;
-          corr[r] = __expf(m_run[r] - muse[r]);  // exp(-inf) = 0 on the first tile
+      for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          float tm = -INFINITY;
+#pragma unroll
+          for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const int bit = kbit + nt * 8 + e;
+              const bool vis = inrange[nt][e] && (!tail || ((anc[2 * mt + h] >> (bit & 31)) & 1u));
+              const float sv = vis ? S[mt][nt][2 * h + e] * kscl[nt][e] : -INFINITY;
+              S[mt][nt][2 * h + e] = sv;
+              tm = fmaxf(tm, sv);
+            }
+          tm = fmaxf(tm, __shfl_xor_sync(0xffffffffu, tm, 1));
+          tm = fmaxf(tm, __shfl_xor_sync(0xffffffffu, tm, 2));
+          if (t4 == 0) redm[warp * kAttnRowTile + mt * 16 + h * 8 + g8] = tm;
+        }
+      __syncthreads();
+      // ---- probabilities (FP16, times the key's V scale) to shared memory at their permuted key positions
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int r = 2 * mt + h, row = mt * 16 + h * 8 + g8;
+          const float tmax = fmaxf(fmaxf(redm[row], redm[kAttnRowTile + row]), fmaxf(redm[2 * kAttnRowTile + row], redm[3 * kAttnRowTile + row]));
+          const float mnew = fmaxf(m_run[r], tmax);
+          const float muse = mnew == -INFINITY ? 0.f : mnew;
+          const float corr = __expf(m_run[r] - muse);  // exp(-inf) = 0 on the first tile
           m_run[r] = mnew;
-        }
-        float lsum[2] = {0.f, 0.f};
+          float lsum = 0.f;
 #pragma unroll
-        for (int nt = 0; nt < 8; ++nt)
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int key = nt * 8 + 2 * t4 + (e & 1);
-            const float p = __expf(S[nt][e] - muse[e >> 1]);
-            lsum[e >> 1] += p;
-            S[nt][e] = p * (vsc[buf * kAttnKeyTile + key] * kPScale);
+          for (int nt = 0; nt < 2; ++nt) {
+            const float p0 = __expf(S[mt][nt][2 * h] - muse), p1 = __expf(S[mt][nt][2 * h + 1] - muse);
+            lsum += p0 + p1;
+            *reinterpret_cast<uint32_t*>(Ps + size_t(row) * PS + warp * 16 + perm16(nt * 8 + 2 * t4)) = pack_h2(p0 * vscl[nt][0], p1 * vscl[nt][1]);
           }
+          l_run[r] = l_run[r] * corr + lsum;  // this thread's keys only; summed over the quad and the warps at the end
 #pragma unroll
-        for (int r = 0; r < 2; ++r) {
-          lsum[r] += __shfl_xor_sync(0xffffffffu, lsum[r], 1);
-          lsum[r] += __shfl_xor_sync(0xffffffffu, lsum[r], 2);
-          l_run[r] = l_run[r] * corr[r] + lsum[r];
+          for (int i = 0; i < NTO; ++i) O[mt][i][2 * h] *= corr, O[mt][i][2 * h + 1] *= corr;
         }
+      __syncthreads();
+      // ---- O += P . V for this warp's D/4 output dims and every row tile
+      const uint8_t* va = Vt + size_t(warp * (D / 4) + g8) * VS + 4 * t4;
+      const __half* pa = Ps + size_t(lm_row) * PS + lm_col;
 #pragma unroll
-        for (int i = 0; i < D / 8; ++i) O[i][0] *= corr[0], O[i][1] *= corr[0], O[i][2] *= corr[1], O[i][3] *= corr[1];
-        // O += P . V: the quad shares one 128-bit load of 16 keys of dim nt * 8 + g8 and picks its bytes
+      for (int kk = 0; kk < kAttnKeyTile / 16; ++kk) {
+        uint32_t a[MT][4];
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk) {
-          const uint32_t a0 = pack_h2(S[2 * kk][0], S[2 * kk][1]), a1 = pack_h2(S[2 * kk][2], S[2 * kk][3]);
-          const uint32_t a2 = pack_h2(S[2 * kk + 1][0], S[2 * kk + 1][1]), a3 = pack_h2(S[2 * kk + 1][2], S[2 * kk + 1][3]);
-          const uint8_t* v0 = Vt + size_t(g8) * VS + kk * 16;
+        for (int mt = 0; mt < MT; ++mt)
+          if (mt < mt_n) ldmatrix_x4(a[mt], pa + size_t(mt * 16) * PS + kk * 16);
 #pragma unroll
-          for (int nt = 0; nt < D / 8; ++nt) {
-            const uint4 vw = *reinterpret_cast<const uint4*>(v0 + size_t(nt * 8) * VS);
-            const uint32_t lo = (t4 & 2) ? vw.y : vw.x, hi = (t4 & 2) ? vw.w : vw.z;  // keys 2t.. and 2t + 8..
-            const int sh = (t4 & 1) * 16;
-            mma_f16(O[nt], a0, a1, a2, a3, e4m3x2_to_h2(uint16_t(lo >> sh)), e4m3x2_to_h2(uint16_t(hi >> sh)));
-          }
+        for (int nt = 0; nt < NTO; ++nt) {
+          const uint32_t vw = *reinterpret_cast<const uint32_t*>(va + size_t(nt * 8) * VS + kk * 16);
+          const uint32_t b0 = e4m3x2_to_h2(uint16_t(vw)), b1 = e4m3x2_to_h2(uint16_t(vw >> 16));
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt)
+            if (mt < mt_n) mma_f16(O[mt][nt], a[mt][0], a[mt][1], a[mt][2], a[mt][3], b0, b1);
         }
       }
       __syncthreads();
     }
-    if (warp_active) {
-      float* po = part_o + size_t(slot_idx) * RMAX * D;
-      float* pm = part_ml + size_t(slot_idx) * RMAX * 2;
+    // ---- denominators: over the quad, then over the warps (through redm, free after the last tile's barrier)
 #pragma unroll
-      for (int nt = 0; nt < D / 8; ++nt) {
-        if (rowA < R) *reinterpret_cast<float2*>(po + size_t(rowA) * D + nt * 8 + 2 * t4) = make_float2(O[nt][0], O[nt][1]);
-        if (rowB < R) *reinterpret_cast<float2*>(po + size_t(rowB) * D + nt * 8 + 2 * t4) = make_float2(O[nt][2], O[nt][3]);
-      }
-      if (t4 == 0) {
-        if (rowA < R) pm[rowA * 2] = m_run[0], pm[rowA * 2 + 1] = l_run[0];
-        if (rowB < R) pm[rowB * 2] = m_run[1], pm[rowB * 2 + 1] = l_run[1];
-      }
+    for (int r = 0; r < 2 * MT; ++r) {
+      l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+      l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+      if (t4 == 0) redm[warp * kAttnRowTile + (r >> 1) * 16 + (r & 1) * 8 + g8] = l_run[r];
     }
+    __syncthreads();
+    float* po = part_o + size_t(slot_idx) * RMAX * D;
+    float* pm = part_ml + size_t(slot_idx) * RMAX * 2;
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int lrow = mt * 16 + h * 8 + g8, row = r_begin + lrow;
+        if (row >= R) continue;
+#pragma unroll
+        for (int nt = 0; nt < NTO; ++nt)
+          *reinterpret_cast<float2*>(po + size_t(row) * D + warp * (D / 4) + nt * 8 + 2 * t4) = make_float2(O[mt][nt][2 * h], O[mt][nt][2 * h + 1]);
+        if (warp == 0 && t4 == 0) {
+          pm[row * 2] = m_run[2 * mt + h];
+          pm[row * 2 + 1] = redm[lrow] + redm[kAttnRowTile + lrow] + redm[2 * kAttnRowTile + lrow] + redm[3 * kAttnRowTile + lrow];
+        }
+      }
   }
 }
 
@@ -1167,8 +1232,8 @@ __global__ void flush_kernel(float* __restrict__ buf, size_t n) {
 
 template <int D, int G>
 constexpr size_t attn_smem() {
-  return size_t(kAttnRowTile) * (D + 8) * 2 + size_t(2) * kAttnKeyTile * (D + 16) + size_t(2) * D * (kAttnKeyTile + 16) +
-         size_t(4) * kAttnKeyTile * 4;
+  return size_t(kAttnRowTile) * (D + 8) * 2 + size_t(kAttnRowTile) * (kAttnKeyTile + 8) * 2 + size_t(2) * kAttnKeyTile * (D + 16) +
+         size_t(2) * D * (kAttnKeyTile + 16) + size_t(4) * kAttnKeyTile * 4 + size_t(4) * kAttnRowTile * 4;
 }
 
 }  // namespace

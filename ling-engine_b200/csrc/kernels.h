@@ -10,7 +10,7 @@ namespace lb {
 constexpr int kTreeRows = LING_B200_MAX_TREE_ROWS;
 constexpr int kAttnChunk = 512;    // context keys per flash-decoding chunk
 constexpr int kAttnKeyTile = 64;   // keys per shared-memory tile
-constexpr int kAttnRowTile = 64;   // query rows (token rows x q heads of one kv head) per CTA
+constexpr int kAttnRowTile = 48;   // query rows (token rows x q heads of one kv head) per CTA: three m16 tiles
 constexpr int kMaxPlanes = 8;      // most K splits of one GEMM (partial-sum planes a consumer adds)
 
 // One sequence of the staged step as the device sees it.
