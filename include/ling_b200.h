@@ -251,9 +251,12 @@ int ling_b200_gemm_fp8_host(int device, int impl, int splits, const float* x, co
 int ling_b200_gemm_fp8_bench(int device, int impl, int splits, int M, int N, int K, int iters, float* ms_per_launch);
 /* The GEMM's response to weights already in L2: per iteration [flush 1: write 256 MiB, flush 2: read 256 MiB] -> ask for the first `slabs` K
  * blocks of every CTA's range to be brought into L2 (mode 0: TMA prefetch, 1: plain loads; slabs 0: nothing) -> a
- * one-thread kernel that spins delay_us -> the GEMM, timed alone with events.  Mean ms of the GEMM over iters. */
+ * one-thread kernel that spins delay_us -> the GEMM, timed alone with events.  Mean ms of the GEMM over iters.
+ * stamps16 (or NULL): %globaltimer stamps of the last iteration's GEMM: [0] first CTA's start, [3] last CTA's end,
+ * [4..9] CTA (0,0,0): start, set-up done, first stage landed, last MMA issued, last accumulator ready, end;
+ * [10] max over CTAs of first-stage latency, [11] max CTA lifetime, [12] last CTA's start, [13] first CTA's end. */
 int ling_b200_gemm_prefetch_bench(int device, int M, int N, int K, int slabs, int mode, int delay_us, int flush, int iters,
-                                  float* ms_per_launch);
+                                  float* ms_per_launch, unsigned long long* stamps16);
 
 /* No counterpart in the reference.  The same block-scaled FP8 GEMM for hosts that must not allocate device memory on
  * this path: a serving loop that gave the whole device to its own arena at start-up, a real-time thread for which an

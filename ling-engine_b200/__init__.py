@@ -367,10 +367,12 @@ def gemm_fp8_bench(M, N, K, impl=0, splits=0, iters=20, device=0):
     return ms.value
 
 
-def gemm_prefetch_bench(M, N, K, slabs, mode=0, delay_us=30, flush=1, iters=10, device=0):
+def gemm_prefetch_bench(M, N, K, slabs, mode=0, delay_us=30, flush=1, iters=10, device=0, stamps=False):
     ms = C.c_float()
-    check(lib().ling_b200_gemm_prefetch_bench(device, M, N, K, slabs, mode, delay_us, flush, iters, C.byref(ms)), "gemm_prefetch_bench")
-    return ms.value
+    st = (C.c_ulonglong * 16)()
+    check(lib().ling_b200_gemm_prefetch_bench(device, M, N, K, slabs, mode, delay_us, flush, iters, C.byref(ms), st if stamps else None),
+          "gemm_prefetch_bench")
+    return (ms.value, list(st)) if stamps else ms.value
 
 
 def describe_tree(parent, chain):

@@ -104,6 +104,7 @@ struct ling_b200_ctx {
   // GEMM timeline (LING_B200_TIMELINE=1 at creation): four %globaltimer stamps per GEMM launch of the last step
   unsigned long long* timeline = nullptr;
   int timeline_next = 0;
+
   static constexpr int kTimelineLaunches = 1024;
 
   // profiling of one eager replay
@@ -260,7 +261,7 @@ int enqueue_step_body(ling_b200_ctx* c, int rows, int flags) {
     LB_TRY(run_gemm(c, L.gu, c->xq_h, 0, rows));
     {
       Timed t(c, kFamElem);
-      LB_TRY(silu_mul_quant_launch(planes_of(c, 0, L.gu), d.I, c->qout(c->xq_i), n_rows, rows, s));
+      LB_TRY(silu_mul_quant_launch(planes_of(c, 0, L.gu), d.I, round_up(d.I, kTileN), c->qout(c->xq_i), n_rows, rows, s));
     }
     LB_TRY(run_gemm(c, L.down, c->xq_i, 1, rows));
     carry = planes_of(c, 1, L.down);
@@ -331,7 +332,7 @@ MatSlot mat_slot(ling_b200_ctx* c, int layer, int tensor) {
   LayerW& L = c->layers[layer];
   switch (tensor) {
     case LING_B200_T_GATE: return MatSlot{&L.gu, 0, d.I, d.H};
-    case LING_B200_T_UP: return MatSlot{&L.gu, d.I, d.I, d.H};
+    case LING_B200_T_UP: return MatSlot{&L.gu, round_up(d.I, kTileN), d.I, d.H};  // on a tile boundary
     case LING_B200_T_DOWN: return MatSlot{&L.down, 0, d.H, d.I};
   }
   if (L.full) {
@@ -494,7 +495,7 @@ int ling_b200_create(const ling_b200_model_config* cfg, const ling_b200_options*
     LayerW& L = c->layers[l];
     LB_TRY(c->alloc(&L.input_norm, size_t(d.H)));
     LB_TRY(c->alloc(&L.post_norm, size_t(d.H)));
-    LB_TRY(c->alloc_matrix(L.gu, 2 * d.I, d.H));
+    LB_TRY(c->alloc_matrix(L.gu, round_up(d.I, kTileN) + d.I, d.H));
     LB_TRY(c->alloc_matrix(L.down, d.H, d.I));
     std::vector<Fp8Matrix*> mats = {&L.gu, &L.down};
     if (L.full) {

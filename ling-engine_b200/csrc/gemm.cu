@@ -169,7 +169,6 @@ struct HeadArgs {
   int rows_alloc;
   int store_logits;
 };
-
 constexpr size_t gemm_smem_bytes(int nt) {
   return size_t(stages_for(nt)) * (kABytes + nt * kBlockK) + 1024 /* alignment slack */ + 512 /* barriers */ +
          size_t(4) * nt * 8 /* head argmax scratch */ + size_t(4) * kScaleRing * nt * 4 /* activation-scale rings */;
@@ -180,15 +179,30 @@ __global__ void __launch_bounds__(kGemmThreads, ctas_per_sm(NT))
     gemm_fp8_tcgen05_kernel(const __grid_constant__ CUtensorMap mapW, const __grid_constant__ CUtensorMap mapX,
                             const float* __restrict__ ws, const float* __restrict__ xs, float* __restrict__ out, int ld,
                             size_t split_stride, int M, int N, int N_pad, int KB, int splits, int xrows, HeadArgs head,
-                            int* err_flag, int pdl, int l2_slabs, unsigned long long* timeline) {
+                            int* err_flag, int pdl, int l2_slabs, unsigned long long* timeline, int detail) {
   pdl_trigger();  // the next kernel may be scheduled as soon as every CTA of this one has started
   // Optional timeline (debugging aid, like the reference's per-block %globaltimer stamps, src/core/engine.hpp:637-642):
   // [0] first CTA's start, [1] first producer past the dependency wait, [2] last producer past it, [3] last CTA's end.
-  if (timeline && threadIdx.x == 0) atomicMin(timeline, global_ns());
+  // With `detail` (the isolated micro-benchmark only) twelve more: [4..9] CTA (0,0,0)'s start, end of set-up, first stage
+  // landed, last MMA issued, last accumulator ready, end; [10] max over CTAs of (first stage landed - start), [11] max CTA
+  // lifetime, [12] last CTA's start, [13] first CTA's end.
+  unsigned long long t_start = 0;
+  const bool cta0 = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+  if (timeline && threadIdx.x == 0) {
+    t_start = global_ns();
+    atomicMin(timeline, t_start);
+    if (detail) {
+      atomicMax(timeline + 12, t_start);
+      if (cta0) timeline[4] = t_start;
+    }
+  }
+  if (timeline && detail && threadIdx.x == 32) t_start = global_ns();
   constexpr int STAGES = stages_for(NT);
   constexpr int kBBytes = NT * kBlockK;
-  constexpr int kStageBytes = kABytes + kBBytes;
+  constexpr int kWBytes = kABytes;  // weight bytes per stage, then the activation tile
+  constexpr int kStageBytes = kWBytes + kBBytes;
   constexpr int kTmemCols = tmem_cols(NT);
+  constexpr int ACCW = NT;  // TMEM columns per accumulator buffer
 
   extern __shared__ uint8_t smem_raw[];
   // 128B-swizzled tiles need 1024-byte alignment; the dynamic segment's base is not guaranteed to have it.
@@ -212,6 +226,8 @@ __global__ void __launch_bounds__(kGemmThreads, ctas_per_sm(NT))
   const int nslab = kb1 - kb0;
 
   if (threadIdx.x == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&mapW)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&mapX)) : "memory");
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
@@ -232,6 +248,7 @@ __global__ void __launch_bounds__(kGemmThreads, ctas_per_sm(NT))
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (timeline && detail && cta0 && threadIdx.x == 0) timeline[5] = global_ns();
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -265,7 +282,7 @@ __global__ void __launch_bounds__(kGemmThreads, ctas_per_sm(NT))
           atomicMin(timeline + 1, t), atomicMax(timeline + 2, t);
         }
         for (int s = 0; s < pre; ++s)
-          tma_load_2d(tiles + s * kStageBytes + kABytes, &mapX, &full[s], (kb0 + s) * kBlockK, xy, pol_x);
+          tma_load_2d(tiles + s * kStageBytes + kWBytes, &mapX, &full[s], (kb0 + s) * kBlockK, xy, pol_x);
         i = pre;
       }
       for (; i < nslab && ok; ++i) {
@@ -279,7 +296,7 @@ __global__ void __launch_bounds__(kGemmThreads, ctas_per_sm(NT))
         }
         mbar_expect_tx(&full[s], kStageBytes);
         tma_load_2d(tiles + s * kStageBytes, &mapW, &full[s], (kb0 + i) * kBlockK, wy, pol_w);
-        tma_load_2d(tiles + s * kStageBytes + kABytes, &mapX, &full[s], (kb0 + i) * kBlockK, xy, pol_x);
+        tma_load_2d(tiles + s * kStageBytes + kWBytes, &mapX, &full[s], (kb0 + i) * kBlockK, xy, pol_x);
       }
       // Every copy this lane issued has landed before it leaves (also when a role gave up): the last STAGES
       // stages' barriers complete exactly once more and are never re-armed.  Bounded like every other wait.
@@ -303,15 +320,22 @@ __global__ void __launch_bounds__(kGemmThreads, ctas_per_sm(NT))
           break;
         }
         tc_fence_after();
+        if (timeline && detail && i == 0) {
+          const unsigned long long t = global_ns();
+          atomicMax(timeline + 10, t - t_start);
+          if (cta0) timeline[6] = t;
+        }
         const uint64_t adesc = umma_desc_sw128(smem_u32(tiles + s * kStageBytes));
-        const uint64_t bdesc = umma_desc_sw128(smem_u32(tiles + s * kStageBytes + kABytes));
-        const uint32_t d = tmem_base + uint32_t(buf * NT);
+        const uint64_t bdesc = umma_desc_sw128(smem_u32(tiles + s * kStageBytes + kWBytes));
+        const uint32_t d = tmem_base + uint32_t(buf * ACCW);
 #pragma unroll
         for (int k = 0; k < kBlockK / 32; ++k)  // K = 32 bytes per instruction: advance the start address by 32 B
           umma_f8(d, adesc + uint64_t(k * 2), bdesc + uint64_t(k * 2), idesc, k > 0 ? 1u : 0u);
+
         umma_commit(&empty[s]);         // the stage may be refilled once these MMAs have read it
         umma_commit(&tmem_full[buf]);   // the accumulator is complete
       }
+      if (timeline && detail && cta0) timeline[7] = global_ns();
     }
   } else {
     // ------------------------------------------------------------------ epilogue warps (TMEM lane quarter = warp % 4)
@@ -356,7 +380,8 @@ __global__ void __launch_bounds__(kGemmThreads, ctas_per_sm(NT))
         break;
       }
       tc_fence_after();
-      const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(buf * NT);
+      if (timeline && detail && cta0 && i == nslab - 1 && threadIdx.x == 64) timeline[8] = global_ns();
+      const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(buf * ACCW);
       // columns per TMEM read: the whole accumulator for the 32-row token tile, 16 at a time for the wider ones (registers)
       constexpr int CH = NT == 32 ? 32 : 16;
 #pragma unroll
@@ -428,7 +453,15 @@ __global__ void __launch_bounds__(kGemmThreads, ctas_per_sm(NT))
   }
   tc_fence_before();
   __syncthreads();
-  if (timeline && threadIdx.x == 0) atomicMax(timeline + 3, global_ns());
+  if (timeline && threadIdx.x == 0) {
+    const unsigned long long t = global_ns();
+    atomicMax(timeline + 3, t);
+    if (detail) {
+      atomicMax(timeline + 11, t - t_start);
+      atomicMin(timeline + 13, t);
+      if (cta0) timeline[9] = t;
+    }
+  }
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
@@ -620,7 +653,7 @@ int launch_tc(const GemmCall& c, cudaStream_t stream) {
   LB_CUDA(cudaLaunchKernelEx(&cfg, gemm_fp8_tcgen05_kernel<NT>, W.map, X.map[NT / 32 - 1], (const float*)W.scales,
                              (const float*)X.scales, c.out, c.ld, c.split_stride, c.M, W.N, W.N_pad, W.KB, splits,
                              X.rows_alloc, h, c.err_flag, pdl ? 1 : 0, pdl && cfg.gridDim.x == 1 ? l2_slabs : 0,
-                             c.timeline));
+                             c.timeline, c.timeline_detail ? 1 : 0));
   return LING_B200_OK;
 }
 

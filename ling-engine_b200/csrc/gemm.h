@@ -52,6 +52,7 @@ struct GemmCall {
   int impl = 0;             // 0 tcgen05, 1 CUDA cores
   int* err_flag = nullptr;
   unsigned long long* timeline = nullptr;  // four stamps of this launch (debugging aid), or nullptr
+  bool timeline_detail = false;            // `timeline` has 16 slots; per-CTA phases are recorded too (micro-benchmark only)
 };
 
 // Creates the tensor maps (driver entry point fetched at run time; no link against libcuda).

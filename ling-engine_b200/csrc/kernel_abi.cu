@@ -163,7 +163,7 @@ int ling_b200_gemm_fp8_bench(int device, int impl, int splits, int M, int N, int
 }
 
 int ling_b200_gemm_prefetch_bench(int device, int M, int N, int K, int slabs, int mode, int delay_us, int flush, int iters,
-                                  float* ms_per_launch) {
+                                  float* ms_per_launch, unsigned long long* stamps16) {
   if (M < 1 || N < 1 || K < 1 || iters < 1 || iters > 1000 || !ms_per_launch || M > LING_B200_MAX_ROWS || slabs < 0 ||
       delay_us < 0 || delay_us > 10000) {
     set_error("gemm_prefetch_bench: bad argument");
@@ -185,6 +185,12 @@ int ling_b200_gemm_prefetch_bench(int device, int M, int N, int K, int slabs, in
   c.W = &g.W, c.X = &g.X, c.M = M, c.out = g.out, c.ld = g.W.N_pad;
   c.split_stride = size_t(g.X.rows_alloc) * g.W.N_pad;
   c.impl = 0, c.err_flag = g.err;
+  unsigned long long* tl = nullptr;
+  if (stamps16) {
+    tl = sc.get<unsigned long long>(16);
+    LB_PTR(tl);
+    c.timeline = tl, c.timeline_detail = true;
+  }
   cudaEvent_t a, b;
   LB_CUDA(cudaEventCreate(&a));
   LB_CUDA(cudaEventCreate(&b));
@@ -194,6 +200,12 @@ int ling_b200_gemm_prefetch_bench(int device, int M, int N, int K, int slabs, in
     if (flush == 2) LB_TRY(read_flush_launch(fl, flush_n, sink, 0));
     LB_TRY(weight_prefetch_launch(g.W, g.W.splits, slabs, mode, sink, 0));
     LB_TRY(delay_launch(uint64_t(delay_us) * 1000ull, 0));
+    if (tl) {
+      unsigned long long init[16];
+      for (int j = 0; j < 16; ++j) init[j] = (j == 0 || j == 1 || j == 13) ? ~0ull : 0ull;
+      LB_CUDA(cudaMemcpyAsync(tl, init, sizeof(init), cudaMemcpyHostToDevice, 0));
+      LB_CUDA(cudaStreamSynchronize(0));
+    }
     LB_CUDA(cudaEventRecord(a, 0));
     LB_TRY(gemm_launch(c, 0));
     LB_CUDA(cudaEventRecord(b, 0));
@@ -210,6 +222,7 @@ int ling_b200_gemm_prefetch_bench(int device, int M, int N, int K, int slabs, in
     return LING_B200_ERR_DEVICE_FLAG;
   }
   *ms_per_launch = float(total / iters);
+  if (tl) LB_CUDA(cudaMemcpy(stamps16, tl, 128, cudaMemcpyDeviceToHost));
   return LING_B200_OK;
 }
 

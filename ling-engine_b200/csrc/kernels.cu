@@ -195,6 +195,8 @@ __global__ void __launch_bounds__(32) pack_kernel(StepBuffers sb, ModelDims d) {
 // One thread-block cluster per row: CTA j of the cluster owns columns [1024 j, 1024 j + 1024) (four per thread), the
 // partial sums of squares meet through distributed shared memory, and every CTA normalizes and quantizes its own 1024
 // columns (eight 128-column blocks, one per warp).  H <= 8192 keeps the cluster within the portable size of 8.
+// (Measured against one block per row: a single SM's L2 bandwidth makes that form ~3 us slower per launch at 5120 columns
+// and seven partial-sum planes.)
 __global__ void __launch_bounds__(256)
     norm_quant_kernel(float* __restrict__ h, Planes add, const int* __restrict__ ids, const __nv_bfloat16* __restrict__ embed,
                       const __nv_bfloat16* __restrict__ w, float* __restrict__ xn, QuantOut q, const int* __restrict__ n_rows,
@@ -558,7 +560,7 @@ __global__ void __launch_bounds__(256)
 
 // silu(gate) * up (src/core/kernels.cu:308-312) from the gate|up GEMM's partial sums, and its FP8 copy.
 __global__ void __launch_bounds__(256)
-    silu_mul_quant_kernel(Planes gu, int I, QuantOut q, const int* __restrict__ n_rows) {
+    silu_mul_quant_kernel(Planes gu, int I, int up_col0, QuantOut q, const int* __restrict__ n_rows) {
   pdl_sync();  // first statement: see common.cuh
   const int m = blockIdx.x;
   if (m >= *n_rows) return;
@@ -567,7 +569,7 @@ __global__ void __launch_bounds__(256)
     if (c - (threadIdx.x & 31) * 4 >= q.K_pad) return;  // warp-uniform
     float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
     if (c < I) {
-      const float4 a = plane_sum4(gu, m, c), b = plane_sum4(gu, m, I + c);
+      const float4 a = plane_sum4(gu, m, c), b = plane_sum4(gu, m, up_col0 + c);
       x = make_float4(silu(a.x) * b.x, silu(a.y) * b.y, silu(a.z) * b.z, silu(a.w) * b.w);
     }
     quant_store4(x, c, m, q);
@@ -676,14 +678,16 @@ __host__ __device__ constexpr int perm16(int c) { return (c & 3) < 2 ? 2 * (c >>
 // an in-flight key only where its ancestor mask has the bit.  K tiles ([key][D]) and V tiles ([D][key], the pool's V
 // layout) arrive by 16-byte cp.async into double-buffered shared memory and stay E4M3 there; fragments are converted on
 // load (cvt.f16x2.e4m3x2) and the per-position scales are applied to scores and probabilities in fp32.
-// The FP8 -> FP16 conversion unit is what bounds the inner loops, so every converted fragment is used for all query
-// rows of the CTA: for Q.K^T the four warps split the tile's 64 keys (16 each) and each multiplies them with all the
-// rows; the probabilities go through shared memory as FP16; for P.V the warps split the head dimension (D/4 each) and
-// each again covers all rows.  The reduction index of both products is permuted within groups of 16 (perm16) so that a
-// thread's B fragment is one 32-bit load of four consecutive FP8 bytes: Q is stored permuted along d, P along keys.
+// Every converted fragment is used for all query rows of the CTA: for Q.K^T the warps split the tile's 64 keys and each
+// multiplies its keys with all the rows; the probabilities go through shared memory as FP16; for P.V the warps split
+// the head dimension and each again covers all rows.  (Measured: four warps of ~240 registers beat eight of 128 --
+// the eight-warp form re-reads the Q and P fragments twice as often and executed 1.5x the instructions.)  The reduction index of both
+// products is permuted within groups of 16 (perm16) so that a thread's B fragment is one 32-bit load of four
+// consecutive FP8 bytes: Q is stored permuted along d, P along keys.
 // Output: per (chunk slot, query row) the unnormalized sum and (max, denominator); attn_combine_kernel merges chunks.
+constexpr int kAttnThreads = 128;
 template <int D, int G>
-__global__ void __launch_bounds__(128, 2)
+__global__ void __launch_bounds__(kAttnThreads, 2)
     attention_kernel(const __half* __restrict__ q, StepBuffers sb, ModelDims d, int al, KvPoolDev kv, float* __restrict__ part_o,
                      float* __restrict__ part_ml, int chunk_slots) {
   pdl_sync();  // first statement: see common.cuh
@@ -692,8 +696,12 @@ __global__ void __launch_bounds__(128, 2)
   constexpr int VS = kAttnKeyTile + 16;  // bytes per V row (one dim, 64 keys) in shared memory
   constexpr int PS = kAttnKeyTile + 8;   // halves per P row in shared memory
   constexpr int MT = kAttnRowTile / 16;  // m16 row tiles per CTA
-  constexpr int NTO = D / 32;            // n8 output tiles per warp (D/4 dims)
+  constexpr int NW = kAttnThreads / 32;  // warps
+  constexpr int DW = D / NW;             // output dims per warp
+  constexpr int NTO = DW / 8;            // n8 output tiles per warp
   constexpr int RMAX = kTreeRows * G;
+  constexpr int NKT = kAttnKeyTile / (8 * NW);  // n8 key tiles per warp in Q.K^T
+  static_assert(kAttnKeyTile % (8 * NW) == 0 && DW % 8 == 0 && (NKT == 1 || NKT == 2), "warps split 64 keys and D dims");
   extern __shared__ __align__(16) uint8_t smem[];
   __half* Qs = reinterpret_cast<__half*>(smem);                          // [RowTile][QS], d permuted within 16s
   __half* Ps = Qs + kAttnRowTile * QS;                                   // [RowTile][PS], keys permuted within 16s
@@ -701,12 +709,12 @@ __global__ void __launch_bounds__(128, 2)
   uint8_t* Vs8 = Ks8 + 2 * kAttnKeyTile * KS;                            // [2][D][VS]
   float* ksc = reinterpret_cast<float*>(Vs8 + 2 * D * VS);               // [2][64]
   float* vsc = ksc + 2 * kAttnKeyTile;                                   // [2][64]
-  float* redm = vsc + 2 * kAttnKeyTile;                                  // [4 warps][RowTile]
+  float* redm = vsc + 2 * kAttnKeyTile;                                  // [NW][RowTile]
   __shared__ int cbase[LING_B200_MAX_SEQS + 1], ibase[LING_B200_MAX_SEQS + 1];
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g8 = lane >> 2, t4 = lane & 3;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g8 = lane >> 2, t4 = lane & 3;
   const int nseq = *sb.n_seqs;
-  if (threadIdx.x == 0) {
+  if (tid == 0) {
     int cb = 0, ib = 0;
     for (int s = 0; s < nseq; ++s) {
       cbase[s] = cb, ibase[s] = ib;
@@ -718,10 +726,14 @@ __global__ void __launch_bounds__(128, 2)
   }
   __syncthreads();
   const float inv_sqrt_d = rsqrtf(float(D));
-  const int pt = d.page_tokens;
+  const int pt = d.page_tokens, lp = 31 - __clz(pt), pmask = pt - 1;  // pages hold 16, 32 or 64 positions
   // ldmatrix row addresses of this lane inside a 16x16 A tile: matrices 0..3 = (rows 0-7, k 0-7), (rows 8-15, k 0-7),
   // (rows 0-7, k 8-15), (rows 8-15, k 8-15)
   const int lm_row = (lane & 7) + ((lane >> 3) & 1) * 8, lm_col = (lane >> 4) * 8;
+  // this thread's part in the tile copies: K = (key, 16-byte part of its D bytes), V = (dim, 16 positions)
+  constexpr int PK = D / 16, KPI = kAttnThreads / PK;
+  const int k_part = tid % PK, k_key0 = tid / PK;
+  const int v_kc = (tid & 3) * 16, v_dd0 = tid >> 2;
 
   for (int item = blockIdx.x; item < ibase[nseq]; item += gridDim.x) {
     int s = 0;
@@ -733,7 +745,7 @@ __global__ void __launch_bounds__(128, 2)
     const int hk = loc / (nch * nrg), ch = (loc % (nch * nrg)) / nrg, rg = loc % nrg;
     const int slot_idx = cbase[s] * d.Hkv + hk * nch + ch;
     if (slot_idx >= chunk_slots) {
-      if (threadIdx.x == 0) dev_fail(sb.err, kDevBadPage);
+      if (tid == 0) dev_fail(sb.err, kDevBadPage);
       continue;
     }
     const bool tail = ch == nch - 1;
@@ -744,10 +756,13 @@ __global__ void __launch_bounds__(128, 2)
     const int R = sq.n_rows * G, r_begin = rg * kAttnRowTile, r0 = sb.row0[s];
     const int mt_n = min(MT, (R - r_begin + 15) / 16);  // row tiles that hold a real row
     const int* table = kv.tables + size_t(sq.slot) * d.max_pages;
-    const size_t kpage0 = kv_slot_index(d, al, 0, hk, 0, 0), vpage0 = kv_slot_index(d, al, 1, hk, 0, 0);
+    const uint8_t* kcodes = kv.codes + kv_slot_index(d, al, 0, hk, 0, 0) * D;
+    const uint8_t* vcodes = kv.codes + kv_slot_index(d, al, 1, hk, 0, 0) * D;
+    const float* kscales = kv.scales + kv_slot_index(d, al, 0, hk, 0, 0);
+    const float* vscales = kv.scales + kv_slot_index(d, al, 1, hk, 0, 0);
 
     __syncthreads();  // the previous item's readers of Qs and the tiles are done
-    for (int idx = threadIdx.x; idx < kAttnRowTile * (D / 8); idx += 128) {
+    for (int idx = tid; idx < kAttnRowTile * (D / 8); idx += kAttnThreads) {
       const int r = idx / (D / 8), part = idx % (D / 8);
       uint4 val = make_uint4(0, 0, 0, 0);
       const int rr = r_begin + r;
@@ -758,30 +773,35 @@ __global__ void __launch_bounds__(128, 2)
       dst[perm16(c0) >> 1] = val.x, dst[perm16(c0 + 2) >> 1] = val.y, dst[perm16(c0 + 4) >> 1] = val.z, dst[perm16(c0 + 6) >> 1] = val.w;
     }
     auto page_of = [&](int pos) {
-      int page = table[pos / pt];
+      const int page = table[pos >> lp];
       return (page < 0 || page > d.pool_pages) ? 0 : page;  // an unmapped position lands in the reserved page
     };
     auto load_tile = [&](int tile, int buf) {
       const int k0 = tile * kAttnKeyTile;
       // K: one key's D bytes are contiguous in its page
-      for (int idx = threadIdx.x; idx < kAttnKeyTile * (D / 16); idx += 128) {
-        const int key = idx / (D / 16), part = idx % (D / 16);
+#pragma unroll
+      for (int it = 0; it < kAttnKeyTile / KPI; ++it) {
+        const int key = it * KPI + k_key0;
         const bool valid = k0 + key < key_hi;
         const int pos = key_base + k0 + key;
-        const size_t at = valid ? size_t(page_of(pos)) * pt + pos % pt : 0;
-        cp_async16(Ks8 + (size_t(buf) * kAttnKeyTile + key) * KS + part * 16, kv.codes + (kpage0 + at) * D + part * 16, valid ? 16 : 0);
-        if (part == 0) {
-          cp_async4(ksc + buf * kAttnKeyTile + key, kv.scales + kpage0 + at, valid ? 4 : 0);
-          cp_async4(vsc + buf * kAttnKeyTile + key, kv.scales + vpage0 + at, valid ? 4 : 0);
+        const size_t at = valid ? (size_t(page_of(pos)) << lp) + (pos & pmask) : 0;
+        cp_async16(Ks8 + (size_t(buf) * kAttnKeyTile + key) * KS + k_part * 16, kcodes + at * D + k_part * 16, valid ? 16 : 0);
+        if (k_part == 0) {
+          cp_async4(ksc + buf * kAttnKeyTile + key, kscales + at, valid ? 4 : 0);
+          cp_async4(vsc + buf * kAttnKeyTile + key, vscales + at, valid ? 4 : 0);
         }
       }
-      // V: one dim's 16 consecutive positions are contiguous in their page (pages hold a multiple of 16 positions)
-      for (int idx = threadIdx.x; idx < D * (kAttnKeyTile / 16); idx += 128) {
-        const int dd = idx / (kAttnKeyTile / 16), kc = (idx % (kAttnKeyTile / 16)) * 16;
-        const bool valid = k0 + kc < key_hi;
-        const int pos = key_base + k0 + kc;
-        const size_t src = valid ? (vpage0 + size_t(page_of(pos)) * pt) * D + size_t(dd) * pt + pos % pt : 0;
-        cp_async16(Vs8 + (size_t(buf) * D + dd) * VS + kc, kv.codes + src, valid ? 16 : 0);
+      // V: one dim's 16 consecutive positions are contiguous in their page (pages hold a multiple of 16 positions); this
+      // thread's 16 positions are the same for all its dims
+      {
+        const bool valid = k0 + v_kc < key_hi;
+        const int pos = key_base + k0 + v_kc;
+        const uint8_t* src = vcodes + (valid ? (size_t(page_of(pos)) << lp) * D + (pos & pmask) : 0);
+#pragma unroll
+        for (int it = 0; it < D / (kAttnThreads / 4); ++it) {
+          const int dd = it * (kAttnThreads / 4) + v_dd0;
+          cp_async16(Vs8 + (size_t(buf) * D + dd) * VS + v_kc, src + (valid ? size_t(dd) << lp : 0), valid ? 16 : 0);
+        }
       }
       cp_async_commit();
     };
@@ -791,12 +811,12 @@ __global__ void __launch_bounds__(128, 2)
       const int k0 = tile * kAttnKeyTile, first = key_hi - k0;  // first invalid key of this tile
       if (first >= kAttnKeyTile || (first & 15) == 0) return;
       const int last = (first | 15) + 1;
-      for (int idx = threadIdx.x; idx < D * (last - first); idx += 128)
+      for (int idx = tid; idx < D * (last - first); idx += kAttnThreads)
         Vs8[(size_t(buf) * D + idx / (last - first)) * VS + first + idx % (last - first)] = 0;
     };
 
     // This thread's rows: row tile mt holds rows mt * 16 + g8 (index 2 * mt) and + 8 (index 2 * mt + 1), the same in
-    // every warp; O[mt][nt] covers output dims warp * D/4 + nt * 8 + 2 * t4 .. + 1.
+    // every warp; O[mt][nt] covers output dims warp * DW + nt * 8 + 2 * t4 .. + 1.
     float O[MT][NTO][4];
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt)
@@ -828,19 +848,19 @@ __global__ void __launch_bounds__(128, 2)
       }
       const uint8_t* Kt = Ks8 + size_t(buf) * kAttnKeyTile * KS;
       const uint8_t* Vt = Vs8 + size_t(buf) * D * VS;
-      // ---- S = Q . K^T for this warp's 16 keys (two n8 tiles) and every row tile
-      float S[MT][2][4];
+      // ---- S = Q . K^T for this warp's 8 * NKT keys and every row tile
+      float S[MT][NKT][4];
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-        for (int nt = 0; nt < 2; ++nt) S[mt][nt][0] = S[mt][nt][1] = S[mt][nt][2] = S[mt][nt][3] = 0.f;
-      const uint8_t* ka = Kt + size_t(warp * 16 + g8) * KS + 4 * t4;
+        for (int nt = 0; nt < NKT; ++nt) S[mt][nt][0] = S[mt][nt][1] = S[mt][nt][2] = S[mt][nt][3] = 0.f;
+      const uint8_t* ka = Kt + size_t(warp * 8 * NKT + g8) * KS + 4 * t4;
       const __half* qa = Qs + size_t(lm_row) * QS + lm_col;
 #pragma unroll 4
       for (int kt = 0; kt < D / 16; ++kt) {
-        uint32_t bk[2][2];
+        uint32_t bk[NKT][2];
 #pragma unroll
-        for (int nt = 0; nt < 2; ++nt) {
+        for (int nt = 0; nt < NKT; ++nt) {
           const uint32_t kw = *reinterpret_cast<const uint32_t*>(ka + size_t(nt * 8) * KS + kt * 16);
           bk[nt][0] = e4m3x2_to_h2(uint16_t(kw)), bk[nt][1] = e4m3x2_to_h2(uint16_t(kw >> 16));
         }
@@ -849,36 +869,35 @@ __global__ void __launch_bounds__(128, 2)
           if (mt < mt_n) {
             uint32_t a[4];
             ldmatrix_x4(a, qa + size_t(mt * 16) * QS + kt * 16);
-            mma_f16(S[mt][0], a[0], a[1], a[2], a[3], bk[0][0], bk[0][1]);
-            mma_f16(S[mt][1], a[0], a[1], a[2], a[3], bk[1][0], bk[1][1]);
+#pragma unroll
+            for (int nt = 0; nt < NKT; ++nt) mma_f16(S[mt][nt], a[0], a[1], a[2], a[3], bk[nt][0], bk[nt][1]);
           }
         }
       }
-      // ---- scale and mask; the tile's row maxima go through shared memory (each warp saw a quarter of the keys)
+      // ---- scale and mask; the tile's row maxima go through shared memory (each warp saw a part of the keys)
       const int k0 = tile * kAttnKeyTile;
-      float kscl[2][2], vscl[2][2];
-      bool inrange[2][2];
+      float kscl[NKT][2], vscl[NKT][2];
+      bool inrange[NKT][2];
 #pragma unroll
-      for (int nt = 0; nt < 2; ++nt)
+      for (int nt = 0; nt < NKT; ++nt)
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
-          const int key = warp * 16 + nt * 8 + 2 * t4 + e;
+          const int key = warp * 8 * NKT + nt * 8 + 2 * t4 + e;
           kscl[nt][e] = ksc[buf * kAttnKeyTile + key] * inv_sqrt_d;
           vscl[nt][e] = vsc[buf * kAttnKeyTile + key] * kPScale;
           inrange[nt][e] = k0 + key >= key_lo && k0 + key < key_hi;
         }
-      const int kbit = k0 + warp * 16 + 2 * t4 - key_lo;  // + nt * 8 + e: the key's bit in the ancestor mask (tail chunk)
+      const int kbit = k0 + warp * 8 * NKT + 2 * t4 - key_lo;  // + nt * 8 + e: the key's bit in the ancestor mask (tail chunk)
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           float tm = -INFINITY;
 #pragma unroll
-          for (int nt = 0; nt < 2; ++nt)
+          for (int nt = 0; nt < NKT; ++nt)
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
-              const int bit = kbit + nt * 8 + e;
-              const bool vis = inrange[nt][e] && (!tail || ((anc[2 * mt + h] >> (bit & 31)) & 1u));
+              const bool vis = inrange[nt][e] && (!tail || ((anc[2 * mt + h] >> ((kbit + nt * 8 + e) & 31)) & 1u));
               const float sv = vis ? S[mt][nt][2 * h + e] * kscl[nt][e] : -INFINITY;
               S[mt][nt][2 * h + e] = sv;
               tm = fmaxf(tm, sv);
@@ -894,25 +913,28 @@ __global__ void __launch_bounds__(128, 2)
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           const int r = 2 * mt + h, row = mt * 16 + h * 8 + g8;
-          const float tmax = fmaxf(fmaxf(redm[row], redm[kAttnRowTile + row]), fmaxf(redm[2 * kAttnRowTile + row], redm[3 * kAttnRowTile + row]));
+          float tmax = redm[row];
+#pragma unroll
+          for (int w = 1; w < NW; ++w) tmax = fmaxf(tmax, redm[w * kAttnRowTile + row]);
           const float mnew = fmaxf(m_run[r], tmax);
           const float muse = mnew == -INFINITY ? 0.f : mnew;
           const float corr = __expf(m_run[r] - muse);  // exp(-inf) = 0 on the first tile
           m_run[r] = mnew;
           float lsum = 0.f;
 #pragma unroll
-          for (int nt = 0; nt < 2; ++nt) {
+          for (int nt = 0; nt < NKT; ++nt) {
             const float p0 = __expf(S[mt][nt][2 * h] - muse), p1 = __expf(S[mt][nt][2 * h + 1] - muse);
             lsum += p0 + p1;
-            *reinterpret_cast<uint32_t*>(Ps + size_t(row) * PS + warp * 16 + perm16(nt * 8 + 2 * t4)) = pack_h2(p0 * vscl[nt][0], p1 * vscl[nt][1]);
+            const int key = warp * 8 * NKT + nt * 8 + 2 * t4;  // even: the pair stays adjacent under perm16
+            *reinterpret_cast<uint32_t*>(Ps + size_t(row) * PS + (key & ~15) + perm16(key & 15)) = pack_h2(p0 * vscl[nt][0], p1 * vscl[nt][1]);
           }
           l_run[r] = l_run[r] * corr + lsum;  // this thread's keys only; summed over the quad and the warps at the end
 #pragma unroll
           for (int i = 0; i < NTO; ++i) O[mt][i][2 * h] *= corr, O[mt][i][2 * h + 1] *= corr;
         }
       __syncthreads();
-      // ---- O += P . V for this warp's D/4 output dims and every row tile
-      const uint8_t* va = Vt + size_t(warp * (D / 4) + g8) * VS + 4 * t4;
+      // ---- O += P . V for this warp's D / NW output dims and every row tile
+      const uint8_t* va = Vt + size_t(warp * DW + g8) * VS + 4 * t4;
       const __half* pa = Ps + size_t(lm_row) * PS + lm_col;
 #pragma unroll
       for (int kk = 0; kk < kAttnKeyTile / 16; ++kk) {
@@ -949,10 +971,13 @@ __global__ void __launch_bounds__(128, 2)
         if (row >= R) continue;
 #pragma unroll
         for (int nt = 0; nt < NTO; ++nt)
-          *reinterpret_cast<float2*>(po + size_t(row) * D + warp * (D / 4) + nt * 8 + 2 * t4) = make_float2(O[mt][nt][2 * h], O[mt][nt][2 * h + 1]);
+          *reinterpret_cast<float2*>(po + size_t(row) * D + warp * DW + nt * 8 + 2 * t4) = make_float2(O[mt][nt][2 * h], O[mt][nt][2 * h + 1]);
         if (warp == 0 && t4 == 0) {
+          float l = redm[lrow];
+#pragma unroll
+          for (int w = 1; w < NW; ++w) l += redm[w * kAttnRowTile + lrow];
           pm[row * 2] = m_run[2 * mt + h];
-          pm[row * 2 + 1] = redm[lrow] + redm[kAttnRowTile + lrow] + redm[2 * kAttnRowTile + lrow] + redm[3 * kAttnRowTile + lrow];
+          pm[row * 2 + 1] = l;
         }
       }
   }
@@ -1233,7 +1258,7 @@ __global__ void flush_kernel(float* __restrict__ buf, size_t n) {
 template <int D, int G>
 constexpr size_t attn_smem() {
   return size_t(kAttnRowTile) * (D + 8) * 2 + size_t(kAttnRowTile) * (kAttnKeyTile + 8) * 2 + size_t(2) * kAttnKeyTile * (D + 16) +
-         size_t(2) * D * (kAttnKeyTile + 16) + size_t(4) * kAttnKeyTile * 4 + size_t(4) * kAttnRowTile * 4;
+         size_t(2) * D * (kAttnKeyTile + 16) + size_t(4) * kAttnKeyTile * 4 + size_t(kAttnThreads / 32) * kAttnRowTile * 4;
 }
 
 }  // namespace
@@ -1318,7 +1343,7 @@ template <int D, int G>
 static int attention_launch_t(const __half* q, const StepBuffers& sb, const ModelDims& d, int al, const KvPoolDev& kv,
                               float* part_o, float* part_ml, int chunk_slots, int grid, cudaStream_t s) {
   constexpr size_t smem = attn_smem<D, G>();
-  LB_CUDA(launch_kernel(attention_kernel<D, G>, dim3(grid), dim3(128), size_t(smem), s, q, sb, d, al, kv, part_o, part_ml, chunk_slots));
+  LB_CUDA(launch_kernel(attention_kernel<D, G>, dim3(grid), dim3(kAttnThreads), size_t(smem), s, q, sb, d, al, kv, part_o, part_ml, chunk_slots));
   LB_LAUNCH("attention_kernel");
   return LING_B200_OK;
 }
@@ -1361,8 +1386,8 @@ int attn_combine_launch(const float* part_o, const float* part_ml, const Planes&
   return LING_B200_OK;
 }
 
-int silu_mul_quant_launch(const Planes& gu, int I, const QuantOut& q, const int* n_rows, int rows_grid, cudaStream_t s) {
-  LB_CUDA(launch_kernel(silu_mul_quant_kernel, dim3(rows_grid, ceil_div(q.K_pad, 1024)), dim3(256), size_t(0), s, gu, I, q, n_rows));
+int silu_mul_quant_launch(const Planes& gu, int I, int up_col0, const QuantOut& q, const int* n_rows, int rows_grid, cudaStream_t s) {
+  LB_CUDA(launch_kernel(silu_mul_quant_kernel, dim3(rows_grid, ceil_div(q.K_pad, 1024)), dim3(256), size_t(0), s, gu, I, up_col0, q, n_rows));
   LB_LAUNCH("silu_mul_quant_kernel");
   return LING_B200_OK;
 }

@@ -113,7 +113,7 @@ int attention_launch(const __half* q, const StepBuffers& sb, const ModelDims& d,
 int attn_combine_launch(const float* part_o, const float* part_ml, const Planes& qkv, const StepBuffers& sb,
                         const ModelDims& d, const QuantOut& q, float* raw, int rows_grid, cudaStream_t s);
 int f32_to_half_launch(const float* src, __half* dst, size_t n, cudaStream_t s);
-int silu_mul_quant_launch(const Planes& gu, int I, const QuantOut& q, const int* n_rows, int rows_grid, cudaStream_t s);
+int silu_mul_quant_launch(const Planes& gu, int I, int up_col0, const QuantOut& q, const int* n_rows, int rows_grid, cudaStream_t s);
 int argmax_reduce_launch(const float* tile_val, const int* tile_idx, int tiles, int rows_alloc, int* ids, float* vals,
                          const int* n_rows, int rows_grid, cudaStream_t s);
 int argmax_rows_launch(const float* logits, int rows, int vocab, int* ids, float* vals, cudaStream_t s);
