@@ -227,29 +227,39 @@ int enqueue_step_body(ling_b200_ctx* c, int rows, int flags) {
       carry = planes_of(c, 1, L.o);
     } else {
       const int gl = c->gdn_index[l];
-      LB_TRY(run_gemm(c, L.in, c->xq_h, 0, rows));
-      const Planes p0 = planes_of(c, 0, L.in);
       float* pre = c->pre + size_t(gl) * d.rows_alloc * d.C;
       float* post = c->post + size_t(gl) * d.rows_alloc * d.C;
       float* g = c->g + size_t(gl) * d.rows_alloc * d.HV;
       float* beta = c->beta + size_t(gl) * d.rows_alloc * d.HV;
       {
+        // the gating needs only the normalized row, so it runs before the in projection: with dependent launch the
+        // GEMM's CTAs are already resident and stream their first weight tiles while it executes
         Timed t(c, kFamGdn);
         LB_TRY(ab_gating_launch(c->xn, L.in_a, L.in_b, L.A_log, L.dt_bias, g, beta, n_rows, rows, d.H, d.HV, s));
       }
-      {
+      LB_TRY(run_gemm(c, L.in, c->xq_h, 0, rows));
+      const Planes p0 = planes_of(c, 0, L.in);
+      if (gdn_fused_supported(d)) {
         Timed t(c, kFamGdn);
-        LB_TRY(conv_tree_launch(p0, c->sb, d, L.conv, c->conv_state + size_t(gl) * c->conv_layer, c->conv_layer * d.n_gdn, pre,
-                                post, rows, s));
-      }
-      {
-        Timed t(c, kFamGdn);
-        LB_TRY(gdn_tree_launch(post, g, beta, c->sb, d, c->gdn_state + size_t(gl) * c->state_layer, c->state_layer * d.n_gdn,
-                               c->core, c->sm_count * 4, s));
-      }
-      {
-        Timed t(c, kFamGdn);
-        LB_TRY(gated_norm_quant_launch(c->core, p0, d.C, L.lin_norm, c->qout(c->xq_v), n_rows, rows, d.HV, d.Dv, d.eps, s));
+        LB_TRY(gdn_fused_launch(p0, c->sb, d, L.conv, c->conv_state + size_t(gl) * c->conv_layer, c->conv_layer * d.n_gdn, g, beta,
+                                c->gdn_state + size_t(gl) * c->state_layer, c->state_layer * d.n_gdn, L.lin_norm, c->qout(c->xq_v),
+                                pre, post, c->sm_count,
+                                c->timeline && gl == 0 ? c->timeline + 4 * size_t(ling_b200_ctx::kTimelineLaunches - 4) : nullptr, s));
+      } else {
+        {
+          Timed t(c, kFamGdn);
+          LB_TRY(conv_tree_launch(p0, c->sb, d, L.conv, c->conv_state + size_t(gl) * c->conv_layer, c->conv_layer * d.n_gdn, pre,
+                                  post, rows, s));
+        }
+        {
+          Timed t(c, kFamGdn);
+          LB_TRY(gdn_tree_launch(post, g, beta, c->sb, d, c->gdn_state + size_t(gl) * c->state_layer, c->state_layer * d.n_gdn,
+                                 c->core, c->sm_count * 4, s));
+        }
+        {
+          Timed t(c, kFamGdn);
+          LB_TRY(gated_norm_quant_launch(c->core, p0, d.C, L.lin_norm, c->qout(c->xq_v), n_rows, rows, d.HV, d.Dv, d.eps, s));
+        }
       }
       LB_TRY(run_gemm(c, L.out, c->xq_v, 1, rows));
       carry = planes_of(c, 1, L.out);
@@ -1011,7 +1021,9 @@ int ling_b200_gemm_timeline(ling_b200_ctx* c, unsigned long long* out, int max_l
   for (size_t i = 0; i < init.size(); i += 4) init[i] = init[i + 1] = ~0ull, init[i + 2] = init[i + 3] = 0;
   if (cudaMemcpy(c->timeline, init.data(), init.size() * 8, cudaMemcpyHostToDevice) != cudaSuccess) return 0;
   if (ling_b200_step_launch(c) != LING_B200_OK || finish(c) != LING_B200_OK) return 0;
-  const int n = std::min(max_launches, c->timeline_next > 0 ? c->timeline_next : 4 * c->cfg.layers + 1);
+  const int n = max_launches >= ling_b200_ctx::kTimelineLaunches
+                    ? ling_b200_ctx::kTimelineLaunches  // everything, the DeltaNet kernel's phase stamps in the last four slots included
+                    : std::min(max_launches, c->timeline_next > 0 ? c->timeline_next : 4 * c->cfg.layers + 1);
   if (cudaMemcpy(out, c->timeline, size_t(n) * 32, cudaMemcpyDeviceToHost) != cudaSuccess) return 0;
   return n;
 }

@@ -204,7 +204,7 @@ __global__ void __launch_bounds__(256)
   pdl_sync();  // first statement: see common.cuh
   namespace cg = cooperative_groups;
   __shared__ float red[32];
-  __shared__ float part;
+  __shared__ float parts[8];
   const int m = blockIdx.y;
   if (m >= *n_rows) return;  // the whole cluster shares the row, so it leaves together
   const int c = blockIdx.x * 1024 + threadIdx.x * 4;
@@ -225,12 +225,14 @@ __global__ void __launch_bounds__(256)
   const float ss = block_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w, red);
   float total = ss;
   if (gridDim.x > 1) {
+    // Every CTA stores its partial sum into every CTA's `parts` (its own included), one cluster barrier, and each reads
+    // only its own shared memory afterwards -- so nobody reads a peer that may have left, and one barrier is enough.
     cg::cluster_group cluster = cg::this_cluster();
-    if (threadIdx.x == 0) part = ss;
+    const unsigned me = cluster.block_rank(), nb = cluster.num_blocks();
+    if (threadIdx.x < nb) *cluster.map_shared_rank(&parts[me], threadIdx.x) = ss;
     cluster.sync();
     total = 0.f;
-    for (unsigned r = 0; r < cluster.num_blocks(); ++r) total += *cluster.map_shared_rank(&part, r);  // rank order: every CTA gets the same sum
-    cluster.sync();  // no CTA leaves while its partial may still be read
+    for (unsigned r = 0; r < nb; ++r) total += parts[r];  // rank order: every CTA gets the same sum
   }
   const float rstd = rsqrtf(total / H + eps);
   float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -459,6 +461,199 @@ __global__ void __launch_bounds__(128)
                                 (st_i & kLeaf) == 0);
       if ((st_i & kWrite) && quarter == 0) core[(r0 + (st_i & 0xff)) * HV * Dv + size_t(hv) * Dv + col] = o;
     }
+  }
+}
+
+// The DeltaNet mixer between the in and the out projection as one kernel: causal conv over the tree + SiLU, L2 norm of
+// q and k, the gated delta rule over every DeltaNet path, the gated RMSNorm and the FP8 copy for the out projection
+// (conv_tree_kernel, gdn_tree_kernel and gated_norm_quant_kernel above in one launch: the step is latency-bound here,
+// and each kernel boundary costs more than the arithmetic).  A work item is (sequence, DeltaNet path, 128 value
+// columns) = one quantization block of the out projection's input: one head of 128, or two heads of 64.  The block
+// (16 warps, 8 value columns each) stages the raw inputs of all the sequence's rows for its channels, runs the conv and
+// the normalization in shared memory, walks the path with the state in registers, and normalizes and quantizes the rows
+// this path writes.  Path 0's blocks also store `pre` and `post`, which the commit kernels replay.
+__device__ __forceinline__ unsigned long long gtime_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+template <int DK>
+struct GdnFused {
+  using St = GdnStage<DK>;
+  static constexpr int NH = 128 / DK;        // heads per block
+  static constexpr int CH = NH * 3 * DK;     // staged channels: per head q, k, v  (= 384)
+  static constexpr int RAWS = CH + 4;        // floats per staged row
+  static constexpr size_t smem_floats() {
+    return size_t(kTreeRows) * RAWS + size_t(NH) * kTreeRows * St::ROW + size_t(kTreeRows) * 128 + size_t(NH) * kTreeRows * 2 +
+           size_t(kTreeRows) * 128;
+  }
+};
+template <int DK>
+__global__ void __launch_bounds__(512)
+    gdn_fused_kernel(Planes in, StepBuffers sb, ModelDims d, const __nv_bfloat16* __restrict__ convw,
+                     const float* __restrict__ conv_state, size_t conv_slot_stride, const float* __restrict__ g,
+                     const float* __restrict__ beta, const float* __restrict__ state, size_t state_slot_stride,
+                     const __nv_bfloat16* __restrict__ norm_w, QuantOut q, float* __restrict__ pre, float* __restrict__ post,
+                     unsigned long long* stamps) {
+  const bool stamp = stamps != nullptr && blockIdx.x == 0 && threadIdx.x == 0;
+  if (stamp) stamps[0] = gtime_ns();
+  pdl_sync();  // first statement: see common.cuh
+  if (stamp) stamps[1] = gtime_ns();
+  using F = GdnFused<DK>;
+  using St = GdnStage<DK>;
+  constexpr int KL = St::KL, NH = F::NH, CH = F::CH, RAWS = F::RAWS;
+  extern __shared__ __align__(16) float gsm[];
+  float* raw = gsm;                                   // [32][RAWS] raw conv inputs of the sequence's rows
+  float* qk = raw + size_t(kTreeRows) * RAWS;         // [NH][32][ROW] q^ and k^ per row (GdnStage layout)
+  float* vv = qk + size_t(NH) * kTreeRows * St::ROW;  // [32][128] conv output of the value channels
+  float* gb = vv + size_t(kTreeRows) * 128;           // [NH][32][2] g, beta
+  float* osm = gb + NH * kTreeRows * 2;               // [32][128] the recurrence's outputs
+  __shared__ int pbase[LING_B200_MAX_SEQS + 1];
+  __shared__ int steps[2 * kTreeRows], taprow[3 * kTreeRows];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, quarter = lane >> 3;
+  const int nseq = *sb.n_seqs;
+  if (tid == 0) {
+    int acc = 0;
+    for (int s = 0; s < nseq; ++s) {
+      pbase[s] = acc;
+      acc += sb.trees[s].ngdn;
+    }
+    pbase[nseq] = acc;
+  }
+  __syncthreads();
+  const int C = d.C, Hk = d.Hk, HV = d.HV, ratio = HV / Hk, QB = HV / NH;  // QB: 128-column blocks of the value width
+  // channel c of the block -> (head in block, part 0 q / 1 k / 2 v, element) and its conv channel
+  auto conv_channel = [&](int c, int qb, int& hb, int& part, int& e) {
+    hb = c / (3 * DK), part = (c % (3 * DK)) / DK, e = c % DK;
+    const int hv = qb * NH + hb, h = hv / ratio;
+    return part == 0 ? h * DK + e : part == 1 ? Hk * DK + h * DK + e : 2 * Hk * DK + hv * DK + e;
+  };
+  const int total = pbase[nseq] * QB;
+  for (int item = blockIdx.x; item < total; item += gridDim.x) {
+    const int pg = item / QB, qb = item % QB;
+    int s = 0;
+    while (pbase[s + 1] <= pg) ++s;
+    const int pth = pg - pbase[s];
+    const ling_b200_tree_desc* td = sb.trees + s;
+    const int r0 = sb.row0[s], n = sb.seqs[s].n_rows, len = td->gdn_len[pth], slot = sb.seqs[s].slot;
+    const bool keeper = pth == 0;  // this block stores pre/post for the commit
+    __syncthreads();               // the previous item's readers of shared memory are done
+    for (int i = tid; i < len; i += blockDim.x) steps[i] = td->gdn_step[pth][i];
+    // ---- the state: this thread's KL rows of its value column (issued first, needed last)
+    const int colb = warp * 8 + (lane & 7);  // column inside the block's 128
+    const int hb_t = colb / DK, hv_t = qb * NH + hb_t, col = colb % DK;
+    const float* st = state + size_t(slot) * state_slot_stride + size_t(hv_t) * DK * DK;
+    float S[KL];
+#pragma unroll
+    for (int i = 0; i < KL; ++i) S[i] = st[size_t(quarter * KL + i) * DK + col];
+    // ---- raw inputs of every row for the block's channels, the gates, the rows' tap table
+    for (int idx = tid; idx < n * (CH / 4); idx += blockDim.x) {
+      const int t = idx / (CH / 4), c = (idx % (CH / 4)) * 4;
+      int hb, part, e;
+      const int gc = conv_channel(c, qb, hb, part, e);
+      *reinterpret_cast<float4*>(raw + size_t(t) * RAWS + c) = plane_sum4(in, r0 + t, gc);
+    }
+    for (int i = tid; i < NH * n; i += blockDim.x) {
+      const int hb = i / n, t = i % n, hv = qb * NH + hb;
+      gb[(hb * kTreeRows + t) * 2] = g[size_t(r0 + t) * HV + hv];
+      gb[(hb * kTreeRows + t) * 2 + 1] = beta[size_t(r0 + t) * HV + hv];
+    }
+    // taps of row t: its ancestors at depths d-3 .. d-1 (src/core/kernels.cu:365-383), or -1, -2, -3 for the session's
+    // window entries 2, 1, 0 before depth 0
+    for (int i = tid; i < n * 3; i += blockDim.x) {
+      const int t = i / 3, j = i % 3, dj = td->depth[t] - 3 + j;
+      taprow[i] = dj >= 0 ? td->path[td->var[t]][dj] : dj;
+    }
+    __syncthreads();
+    if (stamp && item == blockIdx.x) stamps[2] = gtime_ns();
+    // ---- conv + SiLU: a thread owns a channel (its taps, window and destinations stay in registers) and walks rows
+    for (int w0 = tid; w0 < 2 * CH; w0 += blockDim.x) {
+      const int c = w0 % CH, half = w0 / CH;
+      int hb, part, e;
+      const int gc = conv_channel(c, qb, hb, part, e);
+      const float cw0 = __bfloat162float(convw[size_t(gc) * 4]), cw1 = __bfloat162float(convw[size_t(gc) * 4 + 1]);
+      const float cw2 = __bfloat162float(convw[size_t(gc) * 4 + 2]), cw3 = __bfloat162float(convw[size_t(gc) * 4 + 3]);
+      const float* wsrc = conv_state + size_t(slot) * conv_slot_stride + size_t(gc) * 3;
+      const float wv[3] = {wsrc[0], wsrc[1], wsrc[2]};
+      const bool own = keeper && (part == 2 || (qb * NH + hb) % ratio == 0);  // q, k belong to the first head of their group
+      float* dst = part == 2 ? vv + hb * DK + e
+                             : qk + size_t(hb) * kTreeRows * St::ROW + (part == 1 ? 4 * St::SEG : 0) + (e / KL) * St::SEG + e % KL;
+      const int dstride = part == 2 ? 128 : St::ROW;
+      const int t1 = half == 0 ? (n + 1) / 2 : n;
+      for (int t = half == 0 ? 0 : (n + 1) / 2; t < t1; ++t) {
+        float tap[3];
+#pragma unroll
+        for (int j = 0; j < 3; ++j) {
+          const int tr = taprow[t * 3 + j];
+          tap[j] = tr >= 0 ? raw[size_t(tr) * RAWS + c] : wv[3 + tr];
+        }
+        const float xv = raw[size_t(t) * RAWS + c];
+        const float o = silu(cw0 * tap[0] + cw1 * tap[1] + cw2 * tap[2] + cw3 * xv);
+        dst[size_t(t) * dstride] = o;
+        if (own) {
+          pre[size_t(r0 + t) * C + gc] = xv;
+          if (part == 2) post[size_t(r0 + t) * C + gc] = o;
+        }
+      }
+    }
+    __syncthreads();
+    if (stamp && item == blockIdx.x) stamps[3] = gtime_ns();
+    // ---- L2 norm of q and k per (head, row) (eps 1e-6; q also times 1/sqrt(DK)): one warp per vector, lane l holds the
+    // elements l, l + 32, ..
+    for (int v = warp; v < NH * n * 2; v += blockDim.x / 32) {
+      const int hb = v / (2 * n), t = (v >> 1) % n, isk = v & 1;
+      float* base = qk + (size_t(hb) * kTreeRows + t) * St::ROW + (isk ? 4 * St::SEG : 0);
+      float x[DK / 32];
+      float ss = 0.f;
+#pragma unroll
+      for (int j = 0; j < DK / 32; ++j) {
+        x[j] = base[((j * 32 + lane) / KL) * St::SEG + (j * 32 + lane) % KL];
+        ss = fmaf(x[j], x[j], ss);
+      }
+      ss = warp_sum(ss);
+      const float sc = rsqrtf(ss + 1e-6f) * (isk ? 1.f : rsqrtf(float(DK)));
+      const int hv = qb * NH + hb;
+      const bool own = keeper && hv % ratio == 0;
+      float* gdst = post + size_t(r0 + t) * C + (isk ? Hk * DK : 0) + (hv / ratio) * DK;
+#pragma unroll
+      for (int j = 0; j < DK / 32; ++j) {
+        const float y = x[j] * sc;
+        base[((j * 32 + lane) / KL) * St::SEG + (j * 32 + lane) % KL] = y;
+        if (own) gdst[j * 32 + lane] = y;
+      }
+    }
+    __syncthreads();
+    if (stamp && item == blockIdx.x) stamps[4] = gtime_ns();
+    // ---- the gated delta rule along the path (src/core/kernels.cu:402-477)
+    for (int i = 0; i < len; ++i) {
+      const int st_i = steps[i], t = st_i & 0xff;
+      const float* gbt = gb + (hb_t * kTreeRows + t) * 2;
+      const float* qkt = qk + (size_t(hb_t) * kTreeRows + t) * St::ROW;
+      const float o = (st_i & kLeaf) ? St::token(S, qkt, vv[t * 128 + colb], gbt[0], gbt[1], quarter, false)   // block-uniform
+                                     : St::token(S, qkt, vv[t * 128 + colb], gbt[0], gbt[1], quarter, true);
+      if ((st_i & kWrite) && quarter == 0) osm[t * 128 + colb] = o;
+    }
+    __syncthreads();
+    if (stamp && item == blockIdx.x) stamps[5] = gtime_ns();
+    // ---- gated RMSNorm per head with the plain weight, times silu(z) (src/core/kernels.cu:543-554), and the FP8 copy:
+    // a warp takes a written row, lane l its columns 4 l .. 4 l + 3
+    for (int i = warp; i < len; i += blockDim.x / 32) {
+      if (!(steps[i] & kWrite)) continue;  // warp-uniform
+      const int t = steps[i] & 0xff, c = qb * 128 + lane * 4;
+      float4 x = *reinterpret_cast<const float4*>(osm + t * 128 + lane * 4);
+      const float4 zz = plane_sum4(in, r0 + t, C + c);
+      float ss = x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
+#pragma unroll
+      for (int o = DK / 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      const float rstd = rsqrtf(ss / DK + d.eps);
+      const int dd = (lane * 4) % DK;
+      x.x = x.x * rstd * __bfloat162float(norm_w[dd]) * silu(zz.x);
+      x.y = x.y * rstd * __bfloat162float(norm_w[dd + 1]) * silu(zz.y);
+      x.z = x.z * rstd * __bfloat162float(norm_w[dd + 2]) * silu(zz.z);
+      x.w = x.w * rstd * __bfloat162float(norm_w[dd + 3]) * silu(zz.w);
+      quant_store4(x, c, r0 + t, q);
+    }
+    if (stamp && item == blockIdx.x) stamps[6] = gtime_ns();
   }
 }
 
@@ -1325,6 +1520,28 @@ int gdn_tree_launch(const float* post, const float* g, const float* beta, const 
   return LING_B200_OK;
 }
 
+bool gdn_fused_supported(const ModelDims& d) {
+  return d.Dk == d.Dv && (d.Dk == 64 || d.Dk == 128) && d.HV % d.Hk == 0 && (d.HV * d.Dv) % 128 == 0;
+}
+
+int gdn_fused_launch(const Planes& in, const StepBuffers& sb, const ModelDims& d, const __nv_bfloat16* convw, const float* conv_state,
+                     size_t conv_slot_stride, const float* g, const float* beta, const float* state, size_t state_slot_stride,
+                     const __nv_bfloat16* norm_w, const QuantOut& q, float* pre, float* post, int grid, unsigned long long* stamps,
+                     cudaStream_t s) {
+  if (!gdn_fused_supported(d)) {
+    set_error("fused DeltaNet kernel: key dim = value dim = 64 or 128 expected");
+    return LING_B200_ERR_UNSUPPORTED;
+  }
+  if (d.Dk == 128)
+    LB_CUDA(launch_kernel(gdn_fused_kernel<128>, dim3(grid), dim3(512), GdnFused<128>::smem_floats() * 4, s, in, sb, d, convw, conv_state,
+                          conv_slot_stride, g, beta, state, state_slot_stride, norm_w, q, pre, post, stamps));
+  else
+    LB_CUDA(launch_kernel(gdn_fused_kernel<64>, dim3(grid), dim3(512), GdnFused<64>::smem_floats() * 4, s, in, sb, d, convw, conv_state,
+                          conv_slot_stride, g, beta, state, state_slot_stride, norm_w, q, pre, post, stamps));
+  LB_LAUNCH("gdn_fused_kernel");
+  return LING_B200_OK;
+}
+
 int gated_norm_quant_launch(const float* core, const Planes& z, int z_col, const __nv_bfloat16* w, const QuantOut& q,
                             const int* n_rows, int rows_grid, int HV, int Dv, float eps, cudaStream_t s) {
   LB_CUDA(launch_kernel(gated_norm_quant_kernel, dim3(rows_grid, ceil_div(q.K_pad, 1024)), dim3(256), size_t(0), s, core, z, z_col, w, q, n_rows, HV * Dv, Dv, eps));
@@ -1354,6 +1571,8 @@ int kernels_init() {
   LB_CUDA(cudaFuncSetAttribute(gdn_tree_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(GdnStage<64>::smem_bytes(128))));
   LB_CUDA(cudaFuncSetAttribute(gdn_commit_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(GdnStage<128>::smem_bytes(128))));
   LB_CUDA(cudaFuncSetAttribute(gdn_commit_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(GdnStage<64>::smem_bytes(128))));
+  LB_CUDA(cudaFuncSetAttribute(gdn_fused_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(GdnFused<128>::smem_floats() * 4)));
+  LB_CUDA(cudaFuncSetAttribute(gdn_fused_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(GdnFused<64>::smem_floats() * 4)));
   LB_CUDA(cudaFuncSetAttribute(attention_kernel<256, 6>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(attn_smem<256, 6>())));
   LB_CUDA(cudaFuncSetAttribute(attention_kernel<64, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(attn_smem<64, 4>())));
   LB_CUDA(cudaFuncSetAttribute(attention_kernel<128, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(attn_smem<128, 4>())));

@@ -103,6 +103,12 @@ int conv_tree_launch(const Planes& in, const StepBuffers& sb, const ModelDims& d
                      const float* conv_state, size_t conv_slot_stride, float* pre, float* post, int rows_grid, cudaStream_t s);
 int gdn_tree_launch(const float* post, const float* g, const float* beta, const StepBuffers& sb, const ModelDims& d,
                     const float* state, size_t state_slot_stride, float* core, int grid, cudaStream_t s);
+// conv + recurrence + gated norm + FP8 copy in one launch (shapes: gdn_fused_supported); also stores pre and post
+bool gdn_fused_supported(const ModelDims& d);
+int gdn_fused_launch(const Planes& in, const StepBuffers& sb, const ModelDims& d, const __nv_bfloat16* convw, const float* conv_state,
+                     size_t conv_slot_stride, const float* g, const float* beta, const float* state, size_t state_slot_stride,
+                     const __nv_bfloat16* norm_w, const QuantOut& q, float* pre, float* post, int grid, unsigned long long* stamps,
+                     cudaStream_t s);  // stamps: seven %globaltimer values of block 0's first item (debugging aid) or nullptr
 int gated_norm_quant_launch(const float* core, const Planes& z, int z_col, const __nv_bfloat16* w, const QuantOut& q,
                             const int* n_rows, int rows_grid, int HV, int Dv, float eps, cudaStream_t s);
 int attn_prepare_launch(const Planes& qkv, const StepBuffers& sb, const ModelDims& d, int al, const __nv_bfloat16* q_norm,
