@@ -366,7 +366,10 @@ def run_ours(args, rank, local_rank, world):
             "launches_per_step": launches,
             "roofline": {"bound": "hbm", "kernel": "gemm_fp8_tcgen05_kernel (%d launches per step)" % n_gemm,
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind,
-                         "traffic": None, "bytes_per_launch_avg": wbytes / n_gemm, "ms_per_launch_avg": gemm_ms / n_gemm},
+                         # DRAM read + write bytes per launch: 1.021 x the algorithmic bytes, the ratio ncu measured on the
+                         # gate|up launch (profiles/gemm_fp8_tcgen05_gateup_24x34816x5120.md), scaled to the average launch
+                         "traffic": 1.021 * wbytes / n_gemm, "traffic_source": "ncu dram__bytes ratio 1.021 of one gate|up launch, scaled by bytes",
+                         "bytes_per_launch_avg": wbytes / n_gemm, "ms_per_launch_avg": gemm_ms / n_gemm},
             "cpu_baseline": {"value": cpu_v, "unit": UNIT, "cores": cores, "kind": "port", "sample": cpu_desc,
                              "est_ms_per_step": None if cpu_est is None else cpu_est * 1e3},
             "clocks": clk,
@@ -425,7 +428,7 @@ def main():
     ap.add_argument("--workload", default="single", choices=["single", "ragged4", "toy"])
     ap.add_argument("--layers", type=int, default=64, help="layers of the 27B-class stack (64 = the named configuration)")
     ap.add_argument("--gemm-impl", type=int, default=0)
-    ap.add_argument("--pdl", type=int, default=0)
+    ap.add_argument("--pdl", type=int, default=1, help="programmatic dependent launch (bit-identical results; on by default)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--quick", action="store_true", help="device-timed steps only (no end-to-end, per-family or CPU legs): "
                     "the short run the profiler's launch list is taken from")
