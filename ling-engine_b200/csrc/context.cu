@@ -217,7 +217,12 @@ int enqueue_step_body(ling_b200_ctx* c, int rows, int flags) {
       }
       {
         Timed t(c, kFamAttn);
-        LB_TRY(attention_launch(c->qh, c->sb, d, al, c->kv, c->part_o, c->part_ml, c->chunk_slots, c->sm_count * 2, s));
+        // tcgen05/TMEM attention; the mma.sync form stays as the cross-check implementation (gemm_impl = 1)
+        if (c->opt.gemm_impl == 0 && attention_tc_supported(d))
+          LB_TRY(attention_tc_launch(c->qh, c->sb, d, al, c->kv, c->part_o, c->part_ml, c->chunk_slots, c->sm_count,
+                                     c->timeline && al == 0 ? c->timeline + 4 * size_t(ling_b200_ctx::kTimelineLaunches - 8) : nullptr, s));
+        else
+          LB_TRY(attention_launch(c->qh, c->sb, d, al, c->kv, c->part_o, c->part_ml, c->chunk_slots, c->sm_count * 2, s));
       }
       {
         Timed t(c, kFamAttn);
@@ -1093,7 +1098,10 @@ int ling_b200_attention_host(ling_b200_ctx* c, const ling_b200_seq_step* seqs, i
   LB_TRY(pack_launch(c->sb, d, c->stream));
   LB_CUDA(cudaMemcpyAsync(c->upload, q, n * 4, cudaMemcpyHostToDevice, c->stream));
   LB_TRY(f32_to_half_launch(c->upload, c->qh, n, c->stream));
-  LB_TRY(attention_launch(c->qh, c->sb, d, attn_layer, c->kv, c->part_o, c->part_ml, c->chunk_slots, c->sm_count * 2, c->stream));
+  if (c->opt.gemm_impl == 0 && attention_tc_supported(d))
+    LB_TRY(attention_tc_launch(c->qh, c->sb, d, attn_layer, c->kv, c->part_o, c->part_ml, c->chunk_slots, c->sm_count, nullptr, c->stream));
+  else
+    LB_TRY(attention_launch(c->qh, c->sb, d, attn_layer, c->kv, c->part_o, c->part_ml, c->chunk_slots, c->sm_count * 2, c->stream));
   Planes none;
   none.p = nullptr;
   LB_TRY(attn_combine_launch(c->part_o, c->part_ml, none, c->sb, d, c->qout(c->xq_a), c->planes[0], cls, c->stream));

@@ -851,7 +851,6 @@ __device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
   return *reinterpret_cast<const uint32_t*>(&h);
 }
 
-constexpr float kPScale = 256.f;  // p * v_scale is carried in FP16 times this power of two (kept clear of subnormals)
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
   const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -1567,6 +1566,7 @@ static int attention_launch_t(const __half* q, const StepBuffers& sb, const Mode
 
 // Opts the attention kernels into their dynamic shared memory (once per device, never inside a stream capture).
 int kernels_init() {
+  if (const int r = attention_tc_init()) return r;
   LB_CUDA(cudaFuncSetAttribute(gdn_tree_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(GdnStage<128>::smem_bytes(128))));
   LB_CUDA(cudaFuncSetAttribute(gdn_tree_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(GdnStage<64>::smem_bytes(128))));
   LB_CUDA(cudaFuncSetAttribute(gdn_commit_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(GdnStage<128>::smem_bytes(128))));

@@ -11,6 +11,7 @@ constexpr int kTreeRows = LING_B200_MAX_TREE_ROWS;
 constexpr int kAttnChunk = 512;    // context keys per flash-decoding chunk
 constexpr int kAttnKeyTile = 64;   // keys per shared-memory tile
 constexpr int kAttnRowTile = 48;   // query rows (token rows x q heads of one kv head) per CTA: three m16 tiles
+constexpr float kPScale = 256.f;   // attention: p * v_scale is carried in FP16 times this power of two (clear of subnormals)
 constexpr int kMaxPlanes = 8;      // most K splits of one GEMM (partial-sum planes a consumer adds)
 
 // One sequence of the staged step as the device sees it.
@@ -116,6 +117,11 @@ int attn_prepare_launch(const Planes& qkv, const StepBuffers& sb, const ModelDim
 int attention_launch(const __half* q, const StepBuffers& sb, const ModelDims& d, int al, const KvPoolDev& kv, float* part_o,
                      float* part_ml, int chunk_slots, int grid, cudaStream_t s);
 // raw != nullptr: also the merged rows before the output gate, [rows][Hq * D] (the gate is then not applied: qkv.p may be null)
+// The tcgen05/TMEM form of the same attention (attention_tc.cu): same inputs, same partial outputs.
+int attention_tc_init();
+bool attention_tc_supported(const ModelDims& d);
+int attention_tc_launch(const __half* q, const StepBuffers& sb, const ModelDims& d, int al, const KvPoolDev& kv, float* part_o,
+                        float* part_ml, int chunk_slots, int grid, unsigned long long* stamps, cudaStream_t s);  // stamps: see the kernel
 int attn_combine_launch(const float* part_o, const float* part_ml, const Planes& qkv, const StepBuffers& sb,
                         const ModelDims& d, const QuantOut& q, float* raw, int rows_grid, cudaStream_t s);
 int f32_to_half_launch(const float* src, __half* dst, size_t n, cudaStream_t s);

@@ -192,8 +192,10 @@ def test_argmax_ties_nan_and_inf(gpu, lb, lo):
 ATTN_TOL = 6e-3
 
 
+# impl 0: the tcgen05/TMEM kernel (the product path); impl 1: the mma.sync kernel kept as its cross-check
+@pytest.mark.parametrize("impl", [0, 1])
 @pytest.mark.parametrize("shape", ["toy", "27b"])
-def test_tree_attention_matches_oracle(gpu, lb, lo, shape):
+def test_tree_attention_matches_oracle(gpu, lb, lo, shape, impl):
     if shape == "toy":     # 4 q heads / 1 kv head of 64, 16-position pages
         cfg = lb.make_config(256, 704, 1, 4096, 4, 1, 64, 16, 2, 4, 64, 64, [1])
         contexts, page_tokens = (0, 3, 37, 511, 512, 1029), 16
@@ -203,7 +205,7 @@ def test_tree_attention_matches_oracle(gpu, lb, lo, shape):
     n_seq = len(contexts)
     pool = sum((c + 48) // page_tokens + 2 for c in contexts) + 1
     ctx = lb.Context(cfg, sessions=n_seq, max_context=2048, page_tokens=page_tokens, pool_pages=pool, max_seqs=n_seq,
-                     max_rows=32 * n_seq)
+                     max_rows=32 * n_seq, gemm_impl=impl)
     opt = lb.Options(n_seq, 2048, page_tokens, pool, n_seq, 32 * n_seq, 0, 0, 0, 0, 0)
     m = lo.Model(cfg, opt, lb)
     rng = np.random.default_rng(len(shape))
