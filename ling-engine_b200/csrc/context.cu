@@ -226,7 +226,8 @@ int enqueue_step_body(ling_b200_ctx* c, int rows, int flags) {
       }
       {
         Timed t(c, kFamAttn);
-        LB_TRY(attn_combine_launch(c->part_o, c->part_ml, p0, c->sb, d, c->qout(c->xq_a), nullptr, rows, s));
+        LB_TRY(attn_combine_launch(c->part_o, c->part_ml, p0, c->sb, d, c->qout(c->xq_a), nullptr, rows,
+                                   c->opt.max_context / kAttnChunk + 2, s));
       }
       LB_TRY(run_gemm(c, L.o, c->xq_a, 1, rows));
       carry = planes_of(c, 1, L.o);
@@ -1104,7 +1105,8 @@ int ling_b200_attention_host(ling_b200_ctx* c, const ling_b200_seq_step* seqs, i
     LB_TRY(attention_launch(c->qh, c->sb, d, attn_layer, c->kv, c->part_o, c->part_ml, c->chunk_slots, c->sm_count * 2, c->stream));
   Planes none;
   none.p = nullptr;
-  LB_TRY(attn_combine_launch(c->part_o, c->part_ml, none, c->sb, d, c->qout(c->xq_a), c->planes[0], cls, c->stream));
+  LB_TRY(attn_combine_launch(c->part_o, c->part_ml, none, c->sb, d, c->qout(c->xq_a), c->planes[0], cls,
+                             c->opt.max_context / kAttnChunk + 2, c->stream));
   LB_CUDA(cudaMemcpyAsync(out, c->planes[0], n * 4, cudaMemcpyDeviceToHost, c->stream));
   return read_err(c);
 }

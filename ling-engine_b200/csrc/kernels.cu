@@ -1177,47 +1177,90 @@ __global__ void __launch_bounds__(kAttnThreads, 2)
   }
 }
 
-// Merges a row's chunks in order (the reference's attention_combine, src/core/attention_body.cuh:506-525), applies the
-// output gate out * sigmoid(gate) (src/core/kernels.cu:314-318; the gate is the second D values of each q head's
-// projection) and writes the FP8 copy for the o projection.  One block per (packed row, 1024 output columns); a thread
-// owns four columns of one head, a warp one 128-column quantization block.
+// Merges a row's chunks (the reference's attention_combine, src/core/attention_body.cuh:506-525), applies the output gate
+// out * sigmoid(gate) (src/core/kernels.cu:314-318; the gate is the second D values of each q head's projection) and
+// writes the FP8 copy for the o projection.  One block per (packed row, 128 or D output columns, whichever is larger):
+// a long context has hundreds of chunks, so the chunks are spread over the block -- a thread owns four columns and one of
+// NG chunk groups (chunk c belongs to group c mod NG); the chunk weights exp(m_c - max) are computed once per block in
+// shared memory; the groups' sums meet in shared memory and are added in group order, so the result does not depend on
+// how the block is scheduled.  The first group's threads (whole warps of 128 columns) finish and quantize.
 template <int G>
 __global__ void __launch_bounds__(256)
     attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, Planes qkv, StepBuffers sb,
-                        ModelDims d, QuantOut q, float* __restrict__ raw) {
+                        ModelDims d, QuantOut q, float* __restrict__ raw, int max_chunks) {
   pdl_sync();  // first statement: see common.cuh
   constexpr int RMAX = kTreeRows * G;
+  extern __shared__ __align__(16) float csm[];  // [HB][max_chunks] chunk weights, [4] denominators, [NG][CB] partial sums (max_chunks a multiple of 4)
+  __shared__ float red[32];
   const int m = blockIdx.x;
   if (m >= *sb.n_rows_total) return;
-  const int c = blockIdx.y * 1024 + threadIdx.x * 4;
-  if (c - (threadIdx.x & 31) * 4 >= q.K_pad) return;  // warp-uniform
+  const int D = d.D, CB = D > 128 ? D : 128, HB = CB / D;  // columns and heads of this block
+  const int CT = CB / 4, NG = blockDim.x / CT;              // column threads, chunk groups
+  const int ct = threadIdx.x % CT, grp = threadIdx.x / CT;
+  const int c0 = blockIdx.y * CB;
+  if (c0 >= q.K_pad) return;
+  const int s = sb.seq_of[m], local = sb.local[m];
+  int cb = 0;
+  for (int t = 0; t < s; ++t) cb += (sb.seqs[t].pos + kAttnChunk - 1) / kAttnChunk + 1;
+  const int nch = min(max_chunks, (sb.seqs[s].pos + kAttnChunk - 1) / kAttnChunk + 1);
+  float* wgt = csm;                       // [HB][max_chunks]
+  float* den = csm + HB * max_chunks;     // [HB]
+  float* acc = den + 4;                   // [NG][CB], 16-byte aligned: max_chunks is a multiple of 4
+  // ---- chunk weights and denominators per head of the block
+  for (int hb = 0; hb < HB; ++hb) {
+    const int hq = c0 / D + hb;
+    if (hq * D >= q.K) {  // a head past the real columns (padding): weights zero
+      for (int ch = threadIdx.x; ch < nch; ch += blockDim.x) wgt[hb * max_chunks + ch] = 0.f;
+      if (threadIdx.x == 0) den[hb] = 1.f;
+      __syncthreads();
+      continue;
+    }
+    const int hk = hq / G, r = local * G + hq % G;
+    const float* ml = part_ml + ((size_t(cb) * d.Hkv + size_t(hk) * nch) * RMAX + r) * 2;
+    float mx = -INFINITY;
+    for (int ch = threadIdx.x; ch < nch; ch += blockDim.x) mx = fmaxf(mx, ml[size_t(ch) * RMAX * 2]);
+    mx = block_max(mx, red);
+    float dsum = 0.f;
+    for (int ch = threadIdx.x; ch < nch; ch += blockDim.x) {
+      const float mc = ml[size_t(ch) * RMAX * 2];
+      const float w = mc == -INFINITY ? 0.f : __expf(mc - mx);  // an empty chunk weighs nothing
+      wgt[hb * max_chunks + ch] = w;
+      dsum = fmaf(ml[size_t(ch) * RMAX * 2 + 1], w, dsum);
+    }
+    dsum = block_sum(dsum, red);
+    if (threadIdx.x == 0) den[hb] = dsum;
+    __syncthreads();
+  }
+  // ---- numerators: this thread's four columns over its group's chunks
+  const int c = c0 + ct * 4;
+  float4 num = make_float4(0.f, 0.f, 0.f, 0.f);
+  const int hb = (ct * 4) / D;
+  if (c < q.K) {
+    const int hq = c / D, dd = c % D, hk = hq / G, r = local * G + hq % G;
+    const float* po = part_o + ((size_t(cb) * d.Hkv + size_t(hk) * nch) * RMAX + r) * D + dd;
+    const float* w = wgt + hb * max_chunks;
+#pragma unroll 4
+    for (int ch = grp; ch < nch; ch += NG) {
+      const float4 o = *reinterpret_cast<const float4*>(po + size_t(ch) * RMAX * D);
+      const float wc = w[ch];
+      num.x = fmaf(o.x, wc, num.x), num.y = fmaf(o.y, wc, num.y), num.z = fmaf(o.z, wc, num.z), num.w = fmaf(o.w, wc, num.w);
+    }
+  }
+  *reinterpret_cast<float4*>(acc + grp * CB + ct * 4) = num;
+  __syncthreads();
+  if (grp != 0) return;  // whole warps: CT is a multiple of 32
   float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
   if (c < q.K) {
-    const int s = sb.seq_of[m], local = sb.local[m], D = d.D;
-    int cb = 0;
-    for (int t = 0; t < s; ++t) cb += (sb.seqs[t].pos + kAttnChunk - 1) / kAttnChunk + 1;
-    const int nch = (sb.seqs[s].pos + kAttnChunk - 1) / kAttnChunk + 1;
-    const int hq = c / D, dd = c % D, hk = hq / G, r = local * G + hq % G;
-    const float* ml = part_ml + ((size_t(cb) * d.Hkv + size_t(hk) * nch) * RMAX + r) * 2;
-    const float* po = part_o + ((size_t(cb) * d.Hkv + size_t(hk) * nch) * RMAX + r) * D + dd;
-    float mx = -INFINITY;
-#pragma unroll 4
-    for (int ch = 0; ch < nch; ++ch) mx = fmaxf(mx, ml[size_t(ch) * RMAX * 2]);
-    float den = 0.f;
-    float4 num = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 4
-    for (int ch = 0; ch < nch; ++ch) {
-      const float mc = ml[size_t(ch) * RMAX * 2];
-      const float wgt = mc == -INFINITY ? 0.f : __expf(mc - mx);  // an empty chunk weighs nothing
-      den = fmaf(ml[size_t(ch) * RMAX * 2 + 1], wgt, den);
-      const float4 o = *reinterpret_cast<const float4*>(po + size_t(ch) * RMAX * D);
-      num.x = fmaf(o.x, wgt, num.x), num.y = fmaf(o.y, wgt, num.y), num.z = fmaf(o.z, wgt, num.z), num.w = fmaf(o.w, wgt, num.w);
+    for (int g2 = 0; g2 < NG; ++g2) {
+      const float4 a = *reinterpret_cast<const float4*>(acc + g2 * CB + ct * 4);
+      x.x += a.x, x.y += a.y, x.z += a.z, x.w += a.w;
     }
-    const float inv = 1.f / (den * kPScale);
-    x = make_float4(num.x * inv, num.y * inv, num.z * inv, num.w * inv);
+    const float inv = 1.f / (den[hb] * kPScale);
+    x = make_float4(x.x * inv, x.y * inv, x.z * inv, x.w * inv);
     if (raw) {
       *reinterpret_cast<float4*>(raw + size_t(m) * q.K + c) = x;
     } else {
+      const int hq = c / D, dd = c % D;
       const float4 gate = plane_sum4(qkv, m, hq * 2 * D + D + dd);
       x = make_float4(x.x * sigmoidf(gate.x), x.y * sigmoidf(gate.y), x.z * sigmoidf(gate.z), x.w * sigmoidf(gate.w));
     }
@@ -1592,16 +1635,28 @@ int attention_launch(const __half* q, const StepBuffers& sb, const ModelDims& d,
 }
 
 int attn_combine_launch(const float* part_o, const float* part_ml, const Planes& qkv, const StepBuffers& sb,
-                        const ModelDims& d, const QuantOut& q, float* raw, int rows_grid, cudaStream_t s) {
+                        const ModelDims& d, const QuantOut& q, float* raw, int rows_grid, int max_chunks, cudaStream_t s) {
   const int G = d.Hq / d.Hkv;
-  const dim3 grid(rows_grid, ceil_div(q.K_pad, 1024));
-  if (G == 6) LB_CUDA(launch_kernel(attn_combine_kernel<6>, grid, dim3(256), size_t(0), s, part_o, part_ml, qkv, sb, d, q, raw));
-  else if (G == 4) LB_CUDA(launch_kernel(attn_combine_kernel<4>, grid, dim3(256), size_t(0), s, part_o, part_ml, qkv, sb, d, q, raw));
-  else if (G == 8) LB_CUDA(launch_kernel(attn_combine_kernel<8>, grid, dim3(256), size_t(0), s, part_o, part_ml, qkv, sb, d, q, raw));
+  const int CB = d.D > 128 ? d.D : 128, HB = CB / d.D, NG = 256 / (CB / 4);
+  if (CB % 128 != 0 || 256 % (CB / 4) != 0 || CB % d.D != 0) {
+    set_error("attention combine: head dim must be 64, 128 or 256");
+    return LING_B200_ERR_UNSUPPORTED;
+  }
+  const dim3 grid(rows_grid, ceil_div(q.K_pad, CB));
+  max_chunks = round_up(max_chunks, 4);  // keeps the float4 partial sums behind the weights 16-byte aligned
+  const size_t smem = (size_t(HB) * max_chunks + 4 + size_t(NG) * CB) * sizeof(float);
+  if (smem > 48 * 1024) {
+    set_error("attention combine: too many chunks for one sequence");
+    return LING_B200_ERR_UNSUPPORTED;
+  }
+  if (G == 6) LB_CUDA(launch_kernel(attn_combine_kernel<6>, grid, dim3(256), smem, s, part_o, part_ml, qkv, sb, d, q, raw, max_chunks));
+  else if (G == 4) LB_CUDA(launch_kernel(attn_combine_kernel<4>, grid, dim3(256), smem, s, part_o, part_ml, qkv, sb, d, q, raw, max_chunks));
+  else if (G == 8) LB_CUDA(launch_kernel(attn_combine_kernel<8>, grid, dim3(256), smem, s, part_o, part_ml, qkv, sb, d, q, raw, max_chunks));
   else {
     set_error("attention combine: unsupported group size");
     return LING_B200_ERR_UNSUPPORTED;
   }
+  LB_LAUNCH("attn_combine_kernel");
   return LING_B200_OK;
 }
 

@@ -122,8 +122,9 @@ int attention_tc_init();
 bool attention_tc_supported(const ModelDims& d);
 int attention_tc_launch(const __half* q, const StepBuffers& sb, const ModelDims& d, int al, const KvPoolDev& kv, float* part_o,
                         float* part_ml, int chunk_slots, int grid, unsigned long long* stamps, cudaStream_t s);  // stamps: see the kernel
+// max_chunks: the most flash-decoding chunks one sequence can have (context capacity / kAttnChunk + 1)
 int attn_combine_launch(const float* part_o, const float* part_ml, const Planes& qkv, const StepBuffers& sb,
-                        const ModelDims& d, const QuantOut& q, float* raw, int rows_grid, cudaStream_t s);
+                        const ModelDims& d, const QuantOut& q, float* raw, int rows_grid, int max_chunks, cudaStream_t s);
 int f32_to_half_launch(const float* src, __half* dst, size_t n, cudaStream_t s);
 int silu_mul_quant_launch(const Planes& gu, int I, int up_col0, const QuantOut& q, const int* n_rows, int rows_grid, cudaStream_t s);
 int argmax_reduce_launch(const float* tile_val, const int* tile_idx, int tiles, int rows_alloc, int* ids, float* vals,
