@@ -16,8 +16,9 @@
 //            as FP16 into the A tiles; the two halves of a row meet through shared memory.
 //   O += P.V into TMEM columns 256..256+D (MMA N = D); between the two sub-chunks of a chunk the rows whose maximum
 //            grew are rescaled in TMEM (tcgen05.ld / tcgen05.st).
-//   overlap  operand buffers are double: while the tensor core works on tile t the threads convert tile t + 1;
-//            tcgen05.commit on one mbarrier per buffer; cp.async runs two to three tiles ahead.
+//   overlap  in the operand loops warp 0 only issues MMAs and warps 1-7 stage and convert; operand buffers are double, so
+//            the tensor core works on tile t while tile t + 1 is converted (named barriers between the two roles,
+//            tcgen05.commit on one mbarrier per buffer); cp.async runs two to three tiles ahead.
 // Every wait is bounded; a wait that runs out records a code in the device error word and the CTA frees its TMEM and
 // leaves.  No TMA, no cluster, no multicast.
 #include "kernels.h"
@@ -45,6 +46,12 @@ template <int N>
 __device__ __forceinline__ void cp_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
+// 2^x for x <= 0 (also -inf -> 0); results below the normal range flush to zero, which a probability may
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ uint32_t h2_bits(float lo, float hi) {
   const __half2 h = __floats2half2_rn(lo, hi);
   return *reinterpret_cast<const uint32_t*>(&h);
@@ -64,6 +71,12 @@ __device__ __forceinline__ void convert16(const uint4& in, int valid, uint4& lo,
   hi = make_uint4(e4m3x2_to_h2(uint16_t(w[2])), e4m3x2_to_h2(uint16_t(w[2] >> 16)), e4m3x2_to_h2(uint16_t(w[3])),
                   e4m3x2_to_h2(uint16_t(w[3] >> 16)));
 }
+
+// Named barriers of the operand loops: id 1 = the staging/converting warps among themselves; ids 2 and 3 (by operand
+// buffer) = "tile converted": the converting warps arrive, the issuing warp waits.  Counts are whole warps.
+constexpr int kTcWorkers = kTcThreads - 32;  // warps 1-7 stage and convert; warp 0 issues the MMAs
+__device__ __forceinline__ void named_sync(int id, int count) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory"); }
+__device__ __forceinline__ void named_arrive(int id, int count) { asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(count) : "memory"); }
 
 template <int D>
 struct TcSmem {
@@ -104,6 +117,8 @@ __global__ void __launch_bounds__(kTcThreads, 1)
   __shared__ volatile int failed;  // a bounded wait ran out: no further waits, no output; every thread still takes every barrier
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const bool worker = warp > 0;  // operand loops: warps 1-7 stage and convert, warp 0 issues (all eight run the softmax)
+  const int wtid = tid - 32;
   const int nseq = *sb.n_seqs;
   if (tid == 0) {
     int cb = 0, ib = 0;
@@ -172,29 +187,34 @@ __global__ void __launch_bounds__(kTcThreads, 1)
     };
     // cp.async of one 64-key tile's codes into a staging slot: K as [key][D], V as [D][64 keys]; one commit group each.
     // A position at or past key_hi is zero-filled.
+    // K: two threads per key (one page lookup each), eight 16-byte pieces of the key's D bytes per thread for D = 256
     auto stage_k = [&](int k0, uint8_t* dst, bool scales, int sc_off) {
-      constexpr int PK = D / 16;
-      for (int idx = tid; idx < kTcKeys * PK; idx += kTcThreads) {
-        const int key = idx / PK, part = idx % PK;
+      constexpr int PK = D / 16, TPK = PK >= 8 ? 2 : 1, PPT = PK / TPK;  // pieces per key, threads per key, pieces per thread
+      if (wtid < kTcKeys * TPK) {
+        const int key = wtid / TPK, part0 = (wtid % TPK) * PPT;
         const bool valid = k0 + key < key_hi;
         const int pos = key_base + k0 + key;
         const size_t at = valid ? (size_t(page_of(pos)) << lp) + (pos & pmask) : 0;
-        cp16(dst + size_t(key) * D + part * 16, kcodes + at * D + part * 16, valid ? 16 : 0);
-        if (scales && part == 0) {
+        const uint8_t* src = kcodes + at * D + part0 * 16;
+        uint8_t* to = dst + size_t(key) * D + part0 * 16;
+#pragma unroll
+        for (int i = 0; i < PPT; ++i) cp16(to + i * 16, src + i * 16, valid ? 16 : 0);
+        if (scales && part0 == 0) {
           cp4(ksc + sc_off + key, kscales + at, valid ? 4 : 0);
           cp4(vsc + sc_off + key, vscales + at, valid ? 4 : 0);
         }
       }
       cp_commit();
     };
+    // V: a thread's 16 positions (one page lookup) are the same for all its dims
     auto stage_v = [&](int k0, uint8_t* dst) {
-      for (int idx = tid; idx < D * 4; idx += kTcThreads) {
-        const int dd = idx >> 2, kc = (idx & 3) * 16;
-        const bool valid = k0 + kc < key_hi;
-        const int pos = key_base + k0 + kc;
-        const uint8_t* src = vcodes + (valid ? (size_t(page_of(pos)) << lp) * D + (size_t(dd) << lp) + (pos & pmask) : 0);
-        cp16(dst + size_t(dd) * 64 + kc, src, valid ? 16 : 0);
-      }
+      static_assert(kTcWorkers % 4 == 0, "a thread keeps its 16-position piece across dims");
+      const int kc = (wtid & 3) * 16;
+      const bool valid = k0 + kc < key_hi;
+      const int pos = key_base + k0 + kc;
+      const uint8_t* src = vcodes + (valid ? (size_t(page_of(pos)) << lp) * D + (pos & pmask) : 0);
+      for (int dd = wtid >> 2; dd < D; dd += kTcWorkers / 4)
+        cp16(dst + size_t(dd) * 64 + kc, src + (valid ? size_t(dd) << lp : 0), valid ? 16 : 0);
       cp_commit();
     };
 
@@ -214,64 +234,79 @@ __global__ void __launch_bounds__(kTcThreads, 1)
       __syncthreads();
       // ---- Q into its swizzled tiles by cp.async (rows past R zero-filled), K tiles 0 and 1 on their way -- unless the
       // previous sub-chunk's P.V loop already sent for them
-      for (int idx = tid; idx < kTcRows * (D / 8); idx += kTcThreads) {
-        const int r = idx / (D / 8), piece = idx % (D / 8), rr = r_begin + r;
-        const __half* src = rr < R ? q + (size_t(r0 + rr / G) * d.Hq + hk * G + rr % G) * D + piece * 8 : q;
-        cp16(qv + size_t(piece >> 3) * (kTcRows * 128) + sw128_offset(r, piece & 7), src, rr < R ? 16 : 0);
-      }
       const bool k_prefetched = sub > 0;  // (a sub-chunk with a successor always has four tiles)
-      if (!k_prefetched) {
-        stage_k(sub0, stage, true, 0);  // one group with the Q copies
-        if (nt > 1) stage_k(sub0 + kTcKeys, stage + L::kSlot, true, kTcKeys);
-        else cp_commit();
-      } else {
-        cp_commit();  // the Q copies alone, after the two K groups
+      if (worker) {
+        for (int idx = wtid; idx < kTcRows * (D / 8); idx += kTcWorkers) {
+          const int r = idx / (D / 8), piece = idx % (D / 8), rr = r_begin + r;
+          const __half* src = rr < R ? q + (size_t(r0 + rr / G) * d.Hq + hk * G + rr % G) * D + piece * 8 : q;
+          cp16(qv + size_t(piece >> 3) * (kTcRows * 128) + sw128_offset(r, piece & 7), src, rr < R ? 16 : 0);
+        }
+        if (!k_prefetched) {
+          stage_k(sub0, stage, true, 0);  // one group with the Q copies
+          if (nt > 1) stage_k(sub0 + kTcKeys, stage + L::kSlot, true, kTcKeys);
+          else cp_commit();
+          if (nt > 2) stage_k(sub0 + 2 * kTcKeys, stage + 2 * L::kSlot, true, 2 * kTcKeys);
+          else cp_commit();
+        } else {
+          cp_commit();  // the Q copies alone, after the three K groups
+        }
       }
       if (stamp && item == int(blockIdx.x) && sub < 2) stamps[2 + 4 * sub] = global_ns();
       // ---- S = Q.K^T, tile by tile; staging slot t & 3 holds K tile t
       const uint32_t first_qk = mma_count;
       for (int t = 0; t < nt; ++t) {
-        if (t + 2 < nt) stage_k(sub0 + (t + 2) * kTcKeys, stage + size_t((t + 2) & 3) * L::kSlot, true, (t + 2) * kTcKeys);
-        else cp_commit();
-        // tile t's group has landed (this thread's copies); with prefetched K tiles the Q group is the second youngest
-        if (t == 0 && k_prefetched) cp_wait<1>();
-        else cp_wait<2>();
-        __syncthreads();
-        if (mma_count >= first_qk + 2) wait_group(mma_count - 2);  // the MMAs that read this K buffer two tiles ago
         uint8_t* kt = kp + size_t(t & 1) * (size_t(KB) * kTcKeys * 128);
-        const uint8_t* src = stage + size_t(t & 3) * L::kSlot;
-        for (int idx = tid; idx < kTcKeys * (D / 16); idx += kTcThreads) {
-          const int key = idx / (D / 16), part = idx % (D / 16);
-          uint4 lo, hi;
-          convert16(*reinterpret_cast<const uint4*>(src + size_t(key) * D + part * 16), 16, lo, hi);
-          uint8_t* blk = kt + size_t(part >> 2) * (kTcKeys * 128);
-          *reinterpret_cast<uint4*>(blk + sw128_offset(key, (part & 3) * 2)) = lo;
-          *reinterpret_cast<uint4*>(blk + sw128_offset(key, (part & 3) * 2 + 1)) = hi;
-        }
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        __syncthreads();
-        if (tid == 0) {
-          tc_fence_after();
-          constexpr uint32_t idesc = umma_idesc_f16(kTcKeys);
-#pragma unroll
-          for (int kb = 0; kb < KB; ++kb) {
-            const uint64_t adesc = umma_desc_sw128(smem_u32(qv + size_t(kb) * (kTcRows * 128)));
-            const uint64_t bdesc = umma_desc_sw128(smem_u32(kt + size_t(kb) * (kTcKeys * 128)));
-#pragma unroll
-            for (int k = 0; k < 4; ++k)  // K = 16 halves = 32 bytes per instruction
-              umma_f16(tmem_base + kScol + uint32_t(t * kTcKeys), adesc + uint64_t(k * 2), bdesc + uint64_t(k * 2), idesc,
-                       (kb | k) ? 1u : 0u);
+        if (worker) {
+          // tile t's group has landed (this thread's copies): the copies run three tiles ahead, and tile t + 3 is sent for
+          // after the barrier, when every thread is done with the staging slot it reuses (tile t - 1's).  With prefetched K
+          // tiles the Q group is the youngest.
+          if (t == 0 && k_prefetched) cp_wait<0>();
+          else cp_wait<2>();
+          named_sync(1, kTcWorkers);
+          if (t + 3 < nt) stage_k(sub0 + (t + 3) * kTcKeys, stage + size_t((t + 3) & 3) * L::kSlot, true, (t + 3) * kTcKeys);
+          else cp_commit();
+          if (mma_count >= first_qk + 2) wait_group(mma_count - 2);  // the MMAs that read this K buffer two tiles ago
+          const uint8_t* src = stage + size_t(t & 3) * L::kSlot;
+          for (int idx = wtid; idx < kTcKeys * (D / 16); idx += kTcWorkers) {
+            const int key = idx / (D / 16), part = idx % (D / 16);
+            uint4 lo, hi;
+            convert16(*reinterpret_cast<const uint4*>(src + size_t(key) * D + part * 16), 16, lo, hi);
+            uint8_t* blk = kt + size_t(part >> 2) * (kTcKeys * 128);
+            *reinterpret_cast<uint4*>(blk + sw128_offset(key, (part & 3) * 2)) = lo;
+            *reinterpret_cast<uint4*>(blk + sw128_offset(key, (part & 3) * 2 + 1)) = hi;
           }
-          umma_commit(&bar[mma_count & 1]);
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          named_arrive(2 + (t & 1), kTcThreads);
+        } else {
+          named_sync(2 + (t & 1), kTcThreads);  // the tile (and, at t = 0, Q) is in shared memory, fenced for the tensor core
+          if (lane == 0) {
+            tc_fence_after();
+            constexpr uint32_t idesc = umma_idesc_f16(kTcKeys);
+#pragma unroll
+            for (int kb = 0; kb < KB; ++kb) {
+              const uint64_t adesc = umma_desc_sw128(smem_u32(qv + size_t(kb) * (kTcRows * 128)));
+              const uint64_t bdesc = umma_desc_sw128(smem_u32(kt + size_t(kb) * (kTcKeys * 128)));
+#pragma unroll
+              for (int k = 0; k < 4; ++k)  // K = 16 halves = 32 bytes per instruction
+                umma_f16(tmem_base + kScol + uint32_t(t * kTcKeys), adesc + uint64_t(k * 2), bdesc + uint64_t(k * 2), idesc,
+                         (kb | k) ? 1u : 0u);
+            }
+            umma_commit(&bar[mma_count & 1]);
+          }
+          __syncwarp();
         }
         ++mma_count;
       }
       // ---- the V tiles start moving while the softmax runs; staging slots are free once their K tile was converted
       cp_wait<0>();
       __syncthreads();
-      stage_v(sub0, stage);
-      if (nt > 1) stage_v(sub0 + kTcKeys, stage + L::kSlot);
-      else cp_commit();
+      if (worker) {
+        stage_v(sub0, stage);
+        if (nt > 1) stage_v(sub0 + kTcKeys, stage + L::kSlot);
+        else cp_commit();
+        if (nt > 2) stage_v(sub0 + 2 * kTcKeys, stage + 2 * L::kSlot);
+        else cp_commit();
+      }
       // per key of the sub-chunk: score scale in the log2 domain and an additive mask (0, or -inf outside the chunk's
       // keys), and the V scale the probabilities carry
       for (int k = tid; k < nt * kTcKeys; k += kTcThreads) {
@@ -297,9 +332,9 @@ __global__ void __launch_bounds__(kTcThreads, 1)
           tmem_ld_wait();
           if (!tail) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const float2 kc = kcoef[c * 32 + j];
-              mx = fmaxf(mx, fmaf(__uint_as_float(v[j]), kc.x, kc.y));
+            for (int j = 0; j < 32; j += 2) {
+              const float4 kc = *reinterpret_cast<const float4*>(kcoef + c * 32 + j);  // two keys
+              mx = fmaxf(mx, fmaxf(fmaf(__uint_as_float(v[j]), kc.x, kc.y), fmaf(__uint_as_float(v[j + 1]), kc.z, kc.w)));
             }
           } else {
 #pragma unroll
@@ -340,18 +375,22 @@ __global__ void __launch_bounds__(kTcThreads, 1)
           tmem_ld_wait();
           uint32_t pk[16];
 #pragma unroll
-          for (int j = 0; j < 32; j += 2) {
-            float p[2];
+          for (int j = 0; j < 32; j += 4) {
+            const float4 k01 = *reinterpret_cast<const float4*>(kcoef + c * 32 + j);      // keys j, j + 1
+            const float4 k23 = *reinterpret_cast<const float4*>(kcoef + c * 32 + j + 2);  // keys j + 2, j + 3
+            const float4 vc = *reinterpret_cast<const float4*>(vcoef + c * 32 + j);
+            float s2[4] = {fmaf(__uint_as_float(v[j]), k01.x, k01.y), fmaf(__uint_as_float(v[j + 1]), k01.z, k01.w),
+                           fmaf(__uint_as_float(v[j + 2]), k23.x, k23.y), fmaf(__uint_as_float(v[j + 3]), k23.z, k23.w)};
+            if (tail) {
 #pragma unroll
-            for (int e = 0; e < 2; ++e) {
-              const float2 kc = kcoef[c * 32 + j + e];
-              float s2 = fmaf(__uint_as_float(v[j + e]), kc.x, kc.y);
-              if (tail && !((anc >> ((sub0 + c * 32 + j + e - key_lo) & 31)) & 1u)) s2 = -INFINITY;
-              p[e] = exp2f(s2 - muse);
-              lsum += p[e];
-              p[e] *= vcoef[c * 32 + j + e];
+              for (int e = 0; e < 4; ++e)
+                if (!((anc >> ((sub0 + c * 32 + j + e - key_lo) & 31)) & 1u)) s2[e] = -INFINITY;
             }
-            pk[j >> 1] = h2_bits(p[0], p[1]);
+            const float p0 = ex2_approx(s2[0] - muse), p1 = ex2_approx(s2[1] - muse), p2 = ex2_approx(s2[2] - muse),
+                        p3 = ex2_approx(s2[3] - muse);
+            lsum += (p0 + p1) + (p2 + p3);
+            pk[j >> 1] = h2_bits(p0 * vc.x, p1 * vc.y);
+            pk[(j >> 1) + 1] = h2_bits(p2 * vc.z, p3 * vc.w);
           }
           // 32 keys = four 16-byte chunks of this row in P tile c / 2
           uint8_t* ptile = kp + size_t(c >> 1) * (kTcRows * 128);
@@ -365,34 +404,44 @@ __global__ void __launch_bounds__(kTcThreads, 1)
       if (stamp && item == int(blockIdx.x) && sub < 2) stamps[4 + 4 * sub] = global_ns();
       // ---- O += P.V, tile by tile; staging slot t & 3 holds V tile t, the Q region the two V^T operand tiles
       const uint32_t first_pv = mma_count;
+      // the P tiles are written and fenced, the S reads are done
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncthreads();
       for (int t = 0; t < nt; ++t) {
-        if (t + 2 < nt) stage_v(sub0 + (t + 2) * kTcKeys, stage + size_t((t + 2) & 3) * L::kSlot);
-        else if (sub + 1 < nsub) stage_k(sub0 + kTcSub + (t - 2) * kTcKeys, stage + size_t(t - 2) * L::kSlot, true, (t - 2) * kTcKeys);
-        else cp_commit();  // (slots 0 and 1: V tiles 0 and 1 were converted two iterations ago; the scales were copied to kcoef)
-        cp_wait<2>();
-        __syncthreads();  // also: the P tiles are written (first pass) and the S reads are done
-        if (mma_count >= first_pv + 2) wait_group(mma_count - 2);
         uint8_t* vt = qv + size_t(t & 1) * (size_t(D) * 128);
-        const uint8_t* src = stage + size_t(t & 3) * L::kSlot;
-        const int tile0 = sub0 + t * kTcKeys;
-        for (int idx = tid; idx < D * 4; idx += kTcThreads) {
-          const int dd = idx >> 2, piece = idx & 3;
-          uint4 lo, hi;
-          convert16(*reinterpret_cast<const uint4*>(src + size_t(dd) * 64 + piece * 16), key_hi - (tile0 + piece * 16), lo, hi);
-          *reinterpret_cast<uint4*>(vt + sw128_offset(dd, piece * 2)) = lo;
-          *reinterpret_cast<uint4*>(vt + sw128_offset(dd, piece * 2 + 1)) = hi;
-        }
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        __syncthreads();
-        if (tid == 0) {
-          tc_fence_after();
-          constexpr uint32_t idesc = umma_idesc_f16(D);
-          const uint64_t adesc = umma_desc_sw128(smem_u32(kp + size_t(t) * (kTcRows * 128)));
-          const uint64_t bdesc = umma_desc_sw128(smem_u32(vt));
+        if (worker) {
+          cp_wait<2>();
+          named_sync(1, kTcWorkers);
+          // after the barrier tile t - 1's slot is free: V tile t + 3, or the next sub-chunk's K tiles 0..2 (its scales go to
+          // ksc / vsc, which the softmax no longer reads: it copied them into kcoef / vcoef)
+          if (t + 3 < nt) stage_v(sub0 + (t + 3) * kTcKeys, stage + size_t((t + 3) & 3) * L::kSlot);
+          else if (sub + 1 < nsub && t >= 1) stage_k(sub0 + kTcSub + (t - 1) * kTcKeys, stage + size_t(t - 1) * L::kSlot, true, (t - 1) * kTcKeys);
+          else cp_commit();
+          if (mma_count >= first_pv + 2) wait_group(mma_count - 2);
+          const uint8_t* src = stage + size_t(t & 3) * L::kSlot;
+          const int tile0 = sub0 + t * kTcKeys;
+          for (int idx = wtid; idx < D * 4; idx += kTcWorkers) {
+            const int dd = idx >> 2, piece = idx & 3;
+            uint4 lo, hi;
+            convert16(*reinterpret_cast<const uint4*>(src + size_t(dd) * 64 + piece * 16), key_hi - (tile0 + piece * 16), lo, hi);
+            *reinterpret_cast<uint4*>(vt + sw128_offset(dd, piece * 2)) = lo;
+            *reinterpret_cast<uint4*>(vt + sw128_offset(dd, piece * 2 + 1)) = hi;
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          named_arrive(2 + (t & 1), kTcThreads);
+        } else {
+          named_sync(2 + (t & 1), kTcThreads);
+          if (lane == 0) {
+            tc_fence_after();
+            constexpr uint32_t idesc = umma_idesc_f16(D);
+            const uint64_t adesc = umma_desc_sw128(smem_u32(kp + size_t(t) * (kTcRows * 128)));
+            const uint64_t bdesc = umma_desc_sw128(smem_u32(vt));
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
-            umma_f16(tmem_base + kOcol, adesc + uint64_t(k * 2), bdesc + uint64_t(k * 2), idesc, (sub | t | k) ? 1u : 0u);
-          umma_commit(&bar[mma_count & 1]);
+            for (int k = 0; k < 4; ++k)
+              umma_f16(tmem_base + kOcol, adesc + uint64_t(k * 2), bdesc + uint64_t(k * 2), idesc, (sub | t | k) ? 1u : 0u);
+            umma_commit(&bar[mma_count & 1]);
+          }
+          __syncwarp();
         }
         ++mma_count;
       }

@@ -220,7 +220,7 @@ int enqueue_step_body(ling_b200_ctx* c, int rows, int flags) {
         // tcgen05/TMEM attention; the mma.sync form stays as the cross-check implementation (gemm_impl = 1)
         if (c->opt.gemm_impl == 0 && attention_tc_supported(d))
           LB_TRY(attention_tc_launch(c->qh, c->sb, d, al, c->kv, c->part_o, c->part_ml, c->chunk_slots, c->sm_count,
-                                     c->timeline && al == 0 ? c->timeline + 4 * size_t(ling_b200_ctx::kTimelineLaunches - 8) : nullptr, s));
+                                     c->timeline && al == 0 ? c->timeline + 4 * size_t(ling_b200_ctx::kTimelineLaunches - 16) : nullptr, s));
         else
           LB_TRY(attention_launch(c->qh, c->sb, d, al, c->kv, c->part_o, c->part_ml, c->chunk_slots, c->sm_count * 2, s));
       }
