@@ -401,6 +401,44 @@ struct GdnStage {
     o += __shfl_xor_sync(0xffffffffu, o, 16);
     return o;
   }
+  // The same step with one reduction round instead of two: o = S'^T q = (S d)^T q + delta (k . q), so the two dot products
+  // over the decayed state run side by side and k . q (`kq`, the same for every value column) comes precomputed.  The
+  // state update is the arithmetic of token() bit for bit; only o is rounded differently.
+  __device__ __forceinline__ static float token2(float (&S)[KL], const float* qk_i, float v, float gval, float bval, float kq,
+                                                 int quarter, bool advance) {
+    const float4* kp = reinterpret_cast<const float4*>(qk_i + 4 * SEG + quarter * SEG);
+    const float4* qp = reinterpret_cast<const float4*>(qk_i + quarter * SEG);
+    const float decay = __expf(gval);
+    // packed fp32x2 arithmetic (two IEEE operations per instruction on sm_100): element pairs (4i, 4i+1) and (4i+2, 4i+3),
+    // so the four partial sums per dot product are the ones token() keeps
+    const float2 decay2 = make_float2(decay, decay);
+    float2 k2[KL / 2], Sd2[KL / 2];
+    float2 pk2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)}, pq2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+#pragma unroll
+    for (int i = 0; i < KL / 4; ++i) {
+      const float4 a = kp[i], b = qp[i];
+      k2[2 * i] = make_float2(a.x, a.y), k2[2 * i + 1] = make_float2(a.z, a.w);
+      Sd2[2 * i] = __fmul2_rn(make_float2(S[4 * i], S[4 * i + 1]), decay2);
+      Sd2[2 * i + 1] = __fmul2_rn(make_float2(S[4 * i + 2], S[4 * i + 3]), decay2);
+      pk2[0] = __ffma2_rn(Sd2[2 * i], k2[2 * i], pk2[0]);
+      pk2[1] = __ffma2_rn(Sd2[2 * i + 1], k2[2 * i + 1], pk2[1]);
+      pq2[0] = __ffma2_rn(Sd2[2 * i], make_float2(b.x, b.y), pq2[0]);
+      pq2[1] = __ffma2_rn(Sd2[2 * i + 1], make_float2(b.z, b.w), pq2[1]);
+    }
+    float kv = (pk2[0].x + pk2[0].y) + (pk2[1].x + pk2[1].y), sq = (pq2[0].x + pq2[0].y) + (pq2[1].x + pq2[1].y);
+    kv += __shfl_xor_sync(0xffffffffu, kv, 8), sq += __shfl_xor_sync(0xffffffffu, sq, 8);
+    kv += __shfl_xor_sync(0xffffffffu, kv, 16), sq += __shfl_xor_sync(0xffffffffu, sq, 16);
+    const float dlt = (v - kv) * bval;
+    if (advance) {
+      const float2 dlt2 = make_float2(dlt, dlt);
+#pragma unroll
+      for (int m = 0; m < KL / 2; ++m) {
+        const float2 sn = __ffma2_rn(dlt2, k2[m], Sd2[m]);
+        S[2 * m] = sn.x, S[2 * m + 1] = sn.y;
+      }
+    }
+    return fmaf(dlt, kq, sq);
+  }
   static size_t smem_bytes(int Dv) { return size_t(2 * kTreeRows) * (ROW + Dv + 2) * 4; }
 };
 
@@ -471,7 +509,7 @@ __global__ void __launch_bounds__(128)
 // columns) = one quantization block of the out projection's input: one head of 128, or two heads of 64.  The block
 // (16 warps, 8 value columns each) stages the raw inputs of all the sequence's rows for its channels, runs the conv and
 // the normalization in shared memory, walks the path with the state in registers, and normalizes and quantizes the rows
-// this path writes.  Path 0's blocks also store `pre` and `post`, which the commit kernels replay.
+// this path writes, for which it also stores `pre` and `post`, which the commit kernels replay.
 __device__ __forceinline__ unsigned long long gtime_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
@@ -509,7 +547,9 @@ __global__ void __launch_bounds__(512)
   float* gb = vv + size_t(kTreeRows) * 128;           // [NH][32][2] g, beta
   float* osm = gb + NH * kTreeRows * 2;               // [32][128] the recurrence's outputs
   __shared__ int pbase[LING_B200_MAX_SEQS + 1];
-  __shared__ int steps[2 * kTreeRows], taprow[3 * kTreeRows];
+  __shared__ int steps[2 * kTreeRows], taprow[3 * kTreeRows], prow[kTreeRows], pinfo[2];
+  __shared__ float kqs[2 * kTreeRows];  // k^ . q^ per (head in block, row)
+  __shared__ int tdepth[kTreeRows], tvar[kTreeRows], tpath[LING_B200_MAX_TREE_VARIANTS * kTreeRows];  // the tree, staged once per item
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, quarter = lane >> 3;
   const int nseq = *sb.n_seqs;
   if (tid == 0) {
@@ -536,9 +576,10 @@ __global__ void __launch_bounds__(512)
     const int pth = pg - pbase[s];
     const ling_b200_tree_desc* td = sb.trees + s;
     const int r0 = sb.row0[s], n = sb.seqs[s].n_rows, len = td->gdn_len[pth], slot = sb.seqs[s].slot;
-    const bool keeper = pth == 0;  // this block stores pre/post for the commit
-    __syncthreads();               // the previous item's readers of shared memory are done
+    __syncthreads();  // the previous item's readers of shared memory are done
     for (int i = tid; i < len; i += blockDim.x) steps[i] = td->gdn_step[pth][i];
+    for (int i = tid; i < n; i += blockDim.x) tdepth[i] = td->depth[i], tvar[i] = td->var[i];
+    for (int i = tid; i < LING_B200_MAX_TREE_VARIANTS * kTreeRows; i += blockDim.x) tpath[i] = td->path[i / kTreeRows][i % kTreeRows];
     // ---- the state: this thread's KL rows of its value column (issued first, needed last)
     const int colb = warp * 8 + (lane & 7);  // column inside the block's 128
     const int hb_t = colb / DK, hv_t = qb * NH + hb_t, col = colb % DK;
@@ -546,7 +587,8 @@ __global__ void __launch_bounds__(512)
     float S[KL];
 #pragma unroll
     for (int i = 0; i < KL; ++i) S[i] = st[size_t(quarter * KL + i) * DK + col];
-    // ---- raw inputs of every row for the block's channels, the gates, the rows' tap table
+    // ---- raw inputs of every row of the sequence for the block's channels, and the gates: issued together with the loads
+    // above (no dependence on the path), so the item start costs one memory round trip less than staging the path's rows only
     for (int idx = tid; idx < n * (CH / 4); idx += blockDim.x) {
       const int t = idx / (CH / 4), c = (idx % (CH / 4)) * 4;
       int hb, part, e;
@@ -558,29 +600,46 @@ __global__ void __launch_bounds__(512)
       gb[(hb * kTreeRows + t) * 2] = g[size_t(r0 + t) * HV + hv];
       gb[(hb * kTreeRows + t) * 2 + 1] = beta[size_t(r0 + t) * HV + hv];
     }
+    __syncthreads();
+    // the distinct rows of this path (a row's taps are its ancestors, which the path contains) and those it writes: only
+    // these are convolved and normalized here; a row's `pre` / `post` are stored by the path that writes the row
+    if (tid == 0) {
+      uint32_t seen = 0, wr = 0;
+      int np_ = 0;
+      for (int i = 0; i < len; ++i) {
+        const int t = steps[i] & 0xff;
+        if (!((seen >> t) & 1u)) seen |= 1u << t, prow[np_++] = t;
+        if (steps[i] & kWrite) wr |= 1u << t;
+      }
+      pinfo[0] = np_, pinfo[1] = int(wr);
+    }
+    __syncthreads();
+    const int np = pinfo[0];
+    const uint32_t wmask = uint32_t(pinfo[1]);
     // taps of row t: its ancestors at depths d-3 .. d-1 (src/core/kernels.cu:365-383), or -1, -2, -3 for the session's
     // window entries 2, 1, 0 before depth 0
-    for (int i = tid; i < n * 3; i += blockDim.x) {
-      const int t = i / 3, j = i % 3, dj = td->depth[t] - 3 + j;
-      taprow[i] = dj >= 0 ? td->path[td->var[t]][dj] : dj;
+    for (int i = tid; i < np * 3; i += blockDim.x) {
+      const int t = prow[i / 3], j = i % 3, dj = tdepth[t] - 3 + j;
+      taprow[t * 3 + j] = dj >= 0 ? tpath[tvar[t] * kTreeRows + dj] : dj;
     }
     __syncthreads();
     if (stamp && item == blockIdx.x) stamps[2] = gtime_ns();
-    // ---- conv + SiLU: a thread owns a channel (its taps, window and destinations stay in registers) and walks rows
-    for (int w0 = tid; w0 < 2 * CH; w0 += blockDim.x) {
-      const int c = w0 % CH, half = w0 / CH;
+    // ---- conv + SiLU: a thread owns a channel (its taps, window and destinations stay in registers) and walks a quarter
+    // of the path's rows: 4 x 384 slots = three per thread
+    for (int w0 = tid; w0 < 4 * CH; w0 += blockDim.x) {
+      const int c = w0 % CH, qr = w0 / CH;
       int hb, part, e;
       const int gc = conv_channel(c, qb, hb, part, e);
       const float cw0 = __bfloat162float(convw[size_t(gc) * 4]), cw1 = __bfloat162float(convw[size_t(gc) * 4 + 1]);
       const float cw2 = __bfloat162float(convw[size_t(gc) * 4 + 2]), cw3 = __bfloat162float(convw[size_t(gc) * 4 + 3]);
       const float* wsrc = conv_state + size_t(slot) * conv_slot_stride + size_t(gc) * 3;
       const float wv[3] = {wsrc[0], wsrc[1], wsrc[2]};
-      const bool own = keeper && (part == 2 || (qb * NH + hb) % ratio == 0);  // q, k belong to the first head of their group
+      const bool own = part == 2 || (qb * NH + hb) % ratio == 0;  // q, k channels belong to the first head of their group
       float* dst = part == 2 ? vv + hb * DK + e
                              : qk + size_t(hb) * kTreeRows * St::ROW + (part == 1 ? 4 * St::SEG : 0) + (e / KL) * St::SEG + e % KL;
       const int dstride = part == 2 ? 128 : St::ROW;
-      const int t1 = half == 0 ? (n + 1) / 2 : n;
-      for (int t = half == 0 ? 0 : (n + 1) / 2; t < t1; ++t) {
+      for (int li = (np * qr) / 4; li < (np * (qr + 1)) / 4; ++li) {
+        const int t = prow[li];
         float tap[3];
 #pragma unroll
         for (int j = 0; j < 3; ++j) {
@@ -590,7 +649,7 @@ __global__ void __launch_bounds__(512)
         const float xv = raw[size_t(t) * RAWS + c];
         const float o = silu(cw0 * tap[0] + cw1 * tap[1] + cw2 * tap[2] + cw3 * xv);
         dst[size_t(t) * dstride] = o;
-        if (own) {
+        if (own && ((wmask >> t) & 1u)) {
           pre[size_t(r0 + t) * C + gc] = xv;
           if (part == 2) post[size_t(r0 + t) * C + gc] = o;
         }
@@ -598,29 +657,37 @@ __global__ void __launch_bounds__(512)
     }
     __syncthreads();
     if (stamp && item == blockIdx.x) stamps[3] = gtime_ns();
-    // ---- L2 norm of q and k per (head, row) (eps 1e-6; q also times 1/sqrt(DK)): one warp per vector, lane l holds the
-    // elements l, l + 32, ..
-    for (int v = warp; v < NH * n * 2; v += blockDim.x / 32) {
-      const int hb = v / (2 * n), t = (v >> 1) % n, isk = v & 1;
-      float* base = qk + (size_t(hb) * kTreeRows + t) * St::ROW + (isk ? 4 * St::SEG : 0);
-      float x[DK / 32];
-      float ss = 0.f;
+    // ---- L2 norm of q and k per (head, row) (eps 1e-6; q also times 1/sqrt(DK)) and their dot product: one warp per
+    // (head, row), lane l holds the elements l, l + 32, ..
+    for (int v = warp; v < NH * np; v += blockDim.x / 32) {
+      const int hb = v / np, t = prow[v % np];
+      float* qb_ = qk + (size_t(hb) * kTreeRows + t) * St::ROW;
+      float* kb_ = qb_ + 4 * St::SEG;
+      float xq[DK / 32], xk[DK / 32];
+      float sq = 0.f, sk = 0.f;
 #pragma unroll
       for (int j = 0; j < DK / 32; ++j) {
-        x[j] = base[((j * 32 + lane) / KL) * St::SEG + (j * 32 + lane) % KL];
-        ss = fmaf(x[j], x[j], ss);
+        const int off = ((j * 32 + lane) / KL) * St::SEG + (j * 32 + lane) % KL;
+        xq[j] = qb_[off], xk[j] = kb_[off];
+        sq = fmaf(xq[j], xq[j], sq), sk = fmaf(xk[j], xk[j], sk);
       }
-      ss = warp_sum(ss);
-      const float sc = rsqrtf(ss + 1e-6f) * (isk ? 1.f : rsqrtf(float(DK)));
+      sq = warp_sum(sq), sk = warp_sum(sk);
+      const float cq = rsqrtf(sq + 1e-6f) * rsqrtf(float(DK)), ck = rsqrtf(sk + 1e-6f);
       const int hv = qb * NH + hb;
-      const bool own = keeper && hv % ratio == 0;
-      float* gdst = post + size_t(r0 + t) * C + (isk ? Hk * DK : 0) + (hv / ratio) * DK;
+      const bool own = hv % ratio == 0 && ((wmask >> t) & 1u);
+      float* gq = post + size_t(r0 + t) * C + (hv / ratio) * DK;
+      float* gk = gq + Hk * DK;
+      float dot = 0.f;
 #pragma unroll
       for (int j = 0; j < DK / 32; ++j) {
-        const float y = x[j] * sc;
-        base[((j * 32 + lane) / KL) * St::SEG + (j * 32 + lane) % KL] = y;
-        if (own) gdst[j * 32 + lane] = y;
+        const int off = ((j * 32 + lane) / KL) * St::SEG + (j * 32 + lane) % KL;
+        const float yq = xq[j] * cq, yk = xk[j] * ck;
+        qb_[off] = yq, kb_[off] = yk;
+        dot = fmaf(yq, yk, dot);
+        if (own) gq[j * 32 + lane] = yq, gk[j * 32 + lane] = yk;
       }
+      dot = warp_sum(dot);
+      if (lane == 0) kqs[hb * kTreeRows + t] = dot;
     }
     __syncthreads();
     if (stamp && item == blockIdx.x) stamps[4] = gtime_ns();
@@ -629,8 +696,9 @@ __global__ void __launch_bounds__(512)
       const int st_i = steps[i], t = st_i & 0xff;
       const float* gbt = gb + (hb_t * kTreeRows + t) * 2;
       const float* qkt = qk + (size_t(hb_t) * kTreeRows + t) * St::ROW;
-      const float o = (st_i & kLeaf) ? St::token(S, qkt, vv[t * 128 + colb], gbt[0], gbt[1], quarter, false)   // block-uniform
-                                     : St::token(S, qkt, vv[t * 128 + colb], gbt[0], gbt[1], quarter, true);
+      const float kq = kqs[hb_t * kTreeRows + t];
+      const float o = (st_i & kLeaf) ? St::token2(S, qkt, vv[t * 128 + colb], gbt[0], gbt[1], kq, quarter, false)   // block-uniform
+                                     : St::token2(S, qkt, vv[t * 128 + colb], gbt[0], gbt[1], kq, quarter, true);
       if ((st_i & kWrite) && quarter == 0) osm[t * 128 + colb] = o;
     }
     __syncthreads();
