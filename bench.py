@@ -65,6 +65,17 @@ def workload(name, rank, vocab):
     elif name == "ragged4":   # 4 sequences sharing one weight read: trees of 24, 17, 9 and 24 nodes = 74 rows
         specs = [(2048, chain_plus_branch(16, 8), 15), (9216, chain_plus_branch(12, 5), 11), (31000, chain_plus_branch(9, 0), 8),
                  (60000, chain_plus_branch(16, 8), 15)]
+    elif name == "churn64":   # 64 sequences of a continuous-batching server, sharded by sequence over the GPUs: contexts
+        # lognormal (median 6k, at most 128k), trees of 1-32 nodes (a chain plus a lookup branch off the anchor)
+        world = max(1, int(os.environ.get("WORLD_SIZE", 1)))
+        all_rng = np.random.default_rng(64)
+        ctxs = np.clip(all_rng.lognormal(np.log(6000.0), 1.0, 64), 256, 131072 - 64).astype(int)
+        sizes = all_rng.integers(1, 33, 64)
+        specs = []
+        for i in range(rank, 64, world):
+            n = int(sizes[i])
+            chain_rows = max(1, (2 * n + 2) // 3)
+            specs.append((int(ctxs[i]), chain_plus_branch(chain_rows, n - chain_rows), chain_rows - 1))
     elif name == "toy":
         specs = [(c, chain_plus_branch(16, 4), 15) for c in (3, 37, 512, 1029)]
     else:
@@ -73,7 +84,7 @@ def workload(name, rank, vocab):
     for s, (ctx, parent, chain) in enumerate(specs):
         n = len(parent)
         tokens = rng.integers(0, vocab, n).astype(np.int32)
-        accept = int(rng.integers(1, chain + 2)) if name == "ragged4" else min(7, chain + 1)
+        accept = int(rng.integers(1, chain + 2)) if name in ("ragged4", "churn64") else min(7, chain + 1)
         force = rng.integers(0, vocab, n).astype(np.int32)
         for r in range(accept - 1):
             force[r] = tokens[r + 1]
@@ -81,6 +92,59 @@ def workload(name, rank, vocab):
         seqs.append({"slot": s, "pos": ctx, "tokens": tokens, "parent": np.array(parent, np.int32), "chain": chain,
                      "force": force, "accept": accept})
     return seqs
+
+
+class PagePool:
+    """The KV page pool (ling_b200_kvpool_*, the reference's KvPool) with one caller-owned page table per session slot."""
+
+    def __init__(self, lbm, pages, page_tokens, slots, cap):
+        import ctypes as C
+        self.C, self.L, self.cap = C, lbm.lib(), cap
+        self.h = C.c_void_p(self.L.ling_b200_kvpool_create(pages, page_tokens))
+        self.tab = [(C.c_int * cap)() for _ in range(slots)]
+        self.len = [C.c_int(0) for _ in range(slots)]
+
+    def ensure(self, slot, upto):
+        """Maps positions [0, upto); returns the table, or None when the pool cannot cover it (nothing changes then)."""
+        nc = self.C.c_int(0)
+        if self.L.ling_b200_kvpool_ensure(self.h, self.tab[slot], self.C.byref(self.len[slot]), self.cap, 0, upto, None, 0,
+                                          self.C.byref(nc)) != 1:
+            return None
+        return np.array(self.tab[slot][:self.len[slot].value], np.int32)
+
+    def drop(self, slot):
+        pages = set(p for p in self.tab[slot][:self.len[slot].value] if p)
+        self.L.ling_b200_kvpool_truncate(self.h, self.tab[slot], self.len[slot].value, 0)
+        self.len[slot].value = 0
+        return pages
+
+    def retire(self):
+        self.L.ling_b200_kvpool_retire(self.h)
+
+
+def churn_step(ctx, pool, seqs, rng, max_context):
+    """Completions and admissions between two steps: ~10 % of the sequences finish, their pages go back to the pool (deferred
+    retire), and the same session slots are admitted again with a new context length on whatever pages the pool hands out.
+    The admitted sequence's KV is what the reused pages hold (valid FP8 codes): the prefill that would write it is not part
+    of this path.  Returns (admitted, pages reused)."""
+    k = max(1, len(seqs) // 10)
+    done = [int(i) for i in rng.choice(len(seqs), k, replace=False)]
+    freed = set()
+    for i in done:
+        freed |= pool.drop(seqs[i]["slot"])
+    pool.retire()
+    reused = 0
+    for i in done:
+        q = seqs[i]
+        pos = int(np.clip(rng.lognormal(np.log(6000.0), 1.0), 256, max_context - 64))
+        table = pool.ensure(q["slot"], pos + 64)
+        while table is None:   # the pool cannot take this context: admit a shorter one
+            pos //= 2
+            table = pool.ensure(q["slot"], pos + 64)
+        q["pos"] = pos
+        reused += len(freed & set(int(p) for p in table))
+        ctx.kv_table_set(q["slot"], np.arange(len(table), dtype=np.int32), table)
+    return len(done), reused
 
 
 class ClockSampler:
@@ -277,15 +341,18 @@ def run_ours(args, rank, local_rank, world):
     rows = sum(len(q["tokens"]) for q in seqs)
     page_tokens = 16
     pages = sum((q["pos"] + 64 + page_tokens - 1) // page_tokens for q in seqs) + 1
-    ctx = lbm.Context(cfg, sessions=len(seqs), max_context=max(q["pos"] for q in seqs) + 64, page_tokens=page_tokens,
+    churn = args.workload == "churn64"
+    max_context = 131072 if churn else max(q["pos"] for q in seqs) + 64
+    if churn:
+        pages = int(pages * 1.25)   # room for admissions that are longer than the completions they replace
+    ctx = lbm.Context(cfg, sessions=len(seqs), max_context=max_context, page_tokens=page_tokens,
                       pool_pages=pages, max_seqs=len(seqs), max_rows=max(rows, 32), gemm_impl=args.gemm_impl, use_graph=1,
                       device=local_rank, debug_rows=0, pdl=args.pdl)
     ctx.synth_weights(0)
-    page = 1
+    pool = PagePool(lbm, pages, page_tokens, len(seqs), max_context // page_tokens)  # ids 1 .. pages - 1 (page 0 is reserved)
     for q in seqs:
-        n = (q["pos"] + 64 + page_tokens - 1) // page_tokens
-        ctx.kv_table_set(q["slot"], np.arange(n, dtype=np.int32), np.arange(page, page + n, dtype=np.int32))
-        page += n
+        table = pool.ensure(q["slot"], q["pos"] + 64)
+        ctx.kv_table_set(q["slot"], np.arange(len(table), dtype=np.int32), table)
         ctx.synth_kv(q["slot"], q["pos"], rank)
         ctx.synth_state(q["slot"], rank)
     flags = lbm.STEP_COMMIT
@@ -322,8 +389,12 @@ def run_ours(args, rank, local_rank, world):
     for _ in range(2):
         ctx.verify_step(seqs, flags)
     dist.barrier()
+    churn_rng, admitted, reused = np.random.default_rng(7 + rank), 0, 0
     t0 = time.perf_counter()
     for _ in range(args.steps):
+        if churn:   # ~10 % of the sequences complete and as many are admitted on the pages they gave back
+            a, r = churn_step(ctx, pool, seqs, churn_rng, max_context)
+            admitted, reused = admitted + a, reused + r
         ctx.verify_step(seqs, flags)
     e2e_s = dist.max(time.perf_counter() - t0)
     clk = clocks.stop()
@@ -345,7 +416,9 @@ def run_ours(args, rank, local_rank, world):
     if rank == 0:
         cpu_v, cpu_est, cpu_desc = (None, None, "skipped (--no-cpu-baseline)")
         cores = max(1, min(os.cpu_count() or 1, 64))
-        if not args.no_cpu_baseline and world == 1:
+        if churn:
+            cpu_desc = "skipped: 64 sequences of up to 128k context do not fit a bounded CPU sample"
+        elif not args.no_cpu_baseline and world == 1:
             cpu_v, cpu_est, cpu_desc = cpu_sample(lbm, cfg, seqs, cores)
         line = {
             "metric": METRIC, "value": total_rows / (step_ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
@@ -355,6 +428,8 @@ def run_ours(args, rank, local_rank, world):
                        "rows_per_gpu": rows, "sequences_per_gpu": len(seqs), "contexts": [q["pos"] for q in seqs],
                        "parallelism": "replicas, sequences sharded over %d GPU(s), no collective" % world,
                        "l2": "inputs larger than L2 (weights %.1f GB per step), no flush" % (wbytes / 1e9),
+                       "churn": ({"admitted_per_step": admitted / args.steps, "pages_reused_per_step": reused / args.steps}
+                                 if churn else None),
                        "pdl": args.pdl, "gemm_impl": "tcgen05" if args.gemm_impl == 0 else "cuda-core cross-check"},
             "accepted_tokens_per_s": total_accept / (step_ms * 1e-3),
             "hbm_fraction_weights_plus_kv": (alg["weights"] + alg["kv"]) / (step_ms * 1e-3) / 1e9 / peak,
@@ -426,7 +501,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="single", choices=["single", "ragged4", "toy"])
+    ap.add_argument("--workload", default="single", choices=["single", "ragged4", "churn64", "toy"])
     ap.add_argument("--layers", type=int, default=64, help="layers of the 27B-class stack (64 = the named configuration)")
     ap.add_argument("--gemm-impl", type=int, default=0)
     ap.add_argument("--pdl", type=int, default=1, help="programmatic dependent launch (bit-identical results; on by default)")
