@@ -230,6 +230,10 @@ int ling_b200_timer_end(ling_b200_ctx* ctx, float* ms);
  * family's launches: [0] weight GEMMs, [1] attention, [2] DeltaNet, [3] norms/quant/elementwise,
  * [4] head+argmax, [5] pack/accept/compact/commit.  Also the number of kernel launches in one step. */
 int ling_b200_profile_step(ling_b200_ctx* ctx, float ms[8], int* launches);
+/* The weight GEMMs of one step (4 per layer + the LM head, in the step's order, on the staged step's row class and the
+ * activations the last step left) captured as one graph and replayed `iters` times on the context's stream between two
+ * CUDA events after one warm-up replay: ms per pass.  The GEMM's streaming rate with nothing between the launches. */
+int ling_b200_gemm_chain_ms(ling_b200_ctx* ctx, int iters, float* ms);
 int ling_b200_step_launch_count(ling_b200_ctx* ctx);
 /* Debugging aid (the reference's LING_MK_TIMES, engine.hpp:637-642): with LING_B200_TIMELINE=1 in the environment when
  * the context is created, replays the staged step once and returns four GPU-timer stamps (ns) per weight-GEMM launch:

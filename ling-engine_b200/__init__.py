@@ -335,6 +335,11 @@ class Context:
         check(lib().ling_b200_timer_end(self.h, C.byref(ms)), "timer_end")
         return ms.value
 
+    def gemm_chain_ms(self, iters=5):
+        ms = C.c_float()
+        check(lib().ling_b200_gemm_chain_ms(self.h, iters, C.byref(ms)), "gemm_chain_ms")
+        return ms.value
+
     def profile_step(self):
         ms = (C.c_float * 8)()
         n = C.c_int()

@@ -1058,6 +1058,55 @@ int ling_b200_profile_step(ling_b200_ctx* c, float ms[8], int* launches) {
   return rc != LING_B200_OK ? rc : fin;
 }
 
+int ling_b200_gemm_chain_ms(ling_b200_ctx* c, int iters, float* ms) {
+  LB_TRY(check_ctx(c));
+  if (c->staged_seqs < 1 || iters < 1 || !ms) {
+    set_error("gemm_chain: nothing staged, or bad argument");
+    return LING_B200_ERR_ARG;
+  }
+  LB_TRY(finish(c));
+  const int rows = row_class(c->staged_rows);
+  set_pdl(c->opt.pdl != 0);
+  int rc = LING_B200_OK;
+  auto chain = [&]() -> int {
+    for (const LayerW& L : c->layers) {
+      LB_TRY(run_gemm(c, L.full ? L.qkv : L.in, c->xq_h, 0, rows));
+      LB_TRY(run_gemm(c, L.full ? L.o : L.out, L.full ? c->xq_a : c->xq_v, 1, rows));
+      LB_TRY(run_gemm(c, L.gu, c->xq_h, 0, rows));
+      LB_TRY(run_gemm(c, L.down, c->xq_i, 1, rows));
+    }
+    HeadEpilogue ep = c->head_ep;
+    ep.store_logits = false;
+    return run_gemm(c, c->head, c->xq_h, 0, rows, &ep);
+  };
+  // captured once and replayed, like the step itself (launching 257 kernels from the host one by one would time the host)
+  cudaGraph_t graph = nullptr;
+  cudaGraphExec_t exec = nullptr;
+  if (!cuda_ok(cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal), "cudaStreamBeginCapture")) {
+    set_pdl(false);
+    return LING_B200_ERR_CUDA;
+  }
+  rc = chain();
+  const cudaError_t ce = cudaStreamEndCapture(c->stream, &graph);
+  set_pdl(false);
+  if (rc == LING_B200_OK && !cuda_ok(ce, "cudaStreamEndCapture")) rc = LING_B200_ERR_CUDA;
+  if (rc == LING_B200_OK && !cuda_ok(cudaGraphInstantiate(&exec, graph, 0), "cudaGraphInstantiate")) rc = LING_B200_ERR_CUDA;
+  if (graph) cudaGraphDestroy(graph);
+  float t = 0.f;
+  if (rc == LING_B200_OK) {
+    cudaGraphLaunch(exec, c->stream);  // warm-up
+    cudaEventRecord(c->ev0, c->stream);
+    for (int i = 0; i < iters; ++i) cudaGraphLaunch(exec, c->stream);
+    cudaEventRecord(c->ev1, c->stream);
+    if (!cuda_ok(cudaEventSynchronize(c->ev1), "cudaEventSynchronize") || !cuda_ok(cudaEventElapsedTime(&t, c->ev0, c->ev1), "cudaEventElapsedTime"))
+      rc = LING_B200_ERR_CUDA;
+  }
+  if (exec) cudaGraphExecDestroy(exec);
+  LB_TRY(rc);
+  *ms = t / iters;
+  return read_err(c);
+}
+
 int ling_b200_timer_begin(ling_b200_ctx* c) {
   LB_TRY(check_ctx(c));
   LB_CUDA(cudaEventRecord(c->ev0, c->stream));
