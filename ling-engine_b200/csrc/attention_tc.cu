@@ -28,7 +28,7 @@ namespace lb {
 namespace {
 using namespace tc;
 
-constexpr int kTcRows = 128;     // query rows per item = the MMA's M
+constexpr int kTcRows = kAttnTcRows;  // query rows per item = the MMA's M
 constexpr int kTcKeys = 64;      // keys per operand tile
 constexpr int kTcSub = 256;      // keys per sub-chunk = S columns in TMEM
 constexpr int kTcThreads = 256;  // warps 0-3 also run the softmax (one per TMEM lane quarter)
@@ -115,16 +115,19 @@ __global__ void __launch_bounds__(kTcThreads, 1)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + 2);
   __shared__ int cbase[LING_B200_MAX_SEQS + 1], ibase[LING_B200_MAX_SEQS + 1];
   __shared__ volatile int failed;  // a bounded wait ran out: no further waits, no output; every thread still takes every barrier
+  __shared__ int chunk_sh;         // keys per chunk of this step (attn_chunk_keys)
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const bool worker = warp > 0;  // operand loops: warps 1-7 stage and convert, warp 0 issues (all eight run the softmax)
   const int wtid = tid - 32;
   const int nseq = *sb.n_seqs;
   if (tid == 0) {
+    const int chunk = attn_chunk_keys(sb, nseq, d.Hkv, G, kTcRows, int(gridDim.x));
+    chunk_sh = chunk;
     int cb = 0, ib = 0;
     for (int s = 0; s < nseq; ++s) {
       cbase[s] = cb, ibase[s] = ib;
-      const int nch = (sb.seqs[s].pos + kAttnChunk - 1) / kAttnChunk + 1;
+      const int nch = (sb.seqs[s].pos + chunk - 1) / chunk + 1;
       const int nrg = (sb.seqs[s].n_rows * G + kTcRows - 1) / kTcRows;
       cb += nch, ib += d.Hkv * nch * nrg;
     }
@@ -142,6 +145,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  const int chunk = chunk_sh;
   const float inv_sqrt_d = rsqrtf(float(D));
   const int pt = d.page_tokens, lp = 31 - __clz(pt), pmask = pt - 1;
   if (stamp) stamps[1] = global_ns();
@@ -161,7 +165,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
     int s = 0;
     while (ibase[s + 1] <= item) ++s;
     const SeqDev sq = sb.seqs[s];
-    const int nch = (sq.pos + kAttnChunk - 1) / kAttnChunk + 1;
+    const int nch = (sq.pos + chunk - 1) / chunk + 1;
     const int nrg = (sq.n_rows * G + kTcRows - 1) / kTcRows;
     const int loc = item - ibase[s];
     const int hk = loc / (nch * nrg), ch = (loc % (nch * nrg)) / nrg, rg = loc % nrg;
@@ -172,9 +176,9 @@ __global__ void __launch_bounds__(kTcThreads, 1)
     }
     const bool tail = ch == nch - 1;
     // keys [key_base + key_lo, key_base + key_hi) count; a tail chunk starts at the 16-aligned position below pos
-    const int key_base = tail ? (sq.pos & ~15) : ch * kAttnChunk;
+    const int key_base = tail ? (sq.pos & ~15) : ch * chunk;
     const int key_lo = tail ? sq.pos - key_base : 0;
-    const int key_hi = tail ? key_lo + sq.n_rows : min(kAttnChunk, sq.pos - key_base);
+    const int key_hi = tail ? key_lo + sq.n_rows : min(chunk, sq.pos - key_base);
     const int R = sq.n_rows * G, r_begin = rg * kTcRows, r0 = sb.row0[s];
     const int* table = kv.tables + size_t(sq.slot) * d.max_pages;
     const uint8_t* kcodes = kv.codes + kv_slot_index(d, al, 0, hk, 0, 0) * D;

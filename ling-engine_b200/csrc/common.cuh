@@ -7,6 +7,7 @@
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
 #include <cuda_runtime.h>
+#include <cstdlib>
 
 #include <cstdint>
 #include <cstdio>
@@ -26,9 +27,16 @@ inline bool cuda_ok(cudaError_t e, const char* what) {
   do {                                                  \
     if (!::lb::cuda_ok((call), #call)) return LING_B200_ERR_CUDA; \
   } while (0)
+// LING_B200_SYNC_LAUNCHES (debugging aid, eager launches only -- not under graph capture): the device is synchronized after
+// every launch, so an asynchronous fault is reported with the name of the kernel that raised it.
+inline bool sync_launches() {
+  static const bool on = std::getenv("LING_B200_SYNC_LAUNCHES") != nullptr;
+  return on;
+}
 #define LB_LAUNCH(name)                                                 \
   do {                                                                  \
     if (!::lb::cuda_ok(cudaGetLastError(), name)) return LING_B200_ERR_CUDA; \
+    if (::lb::sync_launches() && !::lb::cuda_ok(cudaDeviceSynchronize(), name)) return LING_B200_ERR_CUDA; \
   } while (0)
 
 // Device-side error word: kernels never trap; a bounded wait that runs out or a bounds check that trips records a
@@ -125,8 +133,9 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 // launched with the attribute may start while its predecessor is still running.  Every kernel's first statement is
 // pdl_sync(): it lets its own successor be scheduled (griddepcontrol.launch_dependents) and then waits until the
 // predecessor has completed and its writes are visible (griddepcontrol.wait).  Because every kernel waits, completion is
-// transitive along the stream.  The weight GEMM alone does work before its wait: it prefetches weights, which no kernel
-// of the step writes.  Without the launch attribute both instructions are no-ops.
+// transitive along the stream.  Only loads of data that no kernel of the step writes (weights) are issued before the
+// wait: the weight GEMM prefetches its first tiles there, the norm kernel its weight row.  Without the launch attribute
+// both instructions are no-ops.
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_sync() {

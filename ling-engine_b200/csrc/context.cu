@@ -209,6 +209,7 @@ int enqueue_step_body(ling_b200_ctx* c, int rows, int flags) {
     }
     if (L.full) {
       const int al = c->attn_index[l];
+      const bool tc = c->opt.gemm_impl == 0 && attention_tc_supported(d);
       LB_TRY(run_gemm(c, L.qkv, c->xq_h, 0, rows));
       const Planes p0 = planes_of(c, 0, L.qkv);
       {
@@ -218,7 +219,7 @@ int enqueue_step_body(ling_b200_ctx* c, int rows, int flags) {
       {
         Timed t(c, kFamAttn);
         // tcgen05/TMEM attention; the mma.sync form stays as the cross-check implementation (gemm_impl = 1)
-        if (c->opt.gemm_impl == 0 && attention_tc_supported(d))
+        if (tc)
           LB_TRY(attention_tc_launch(c->qh, c->sb, d, al, c->kv, c->part_o, c->part_ml, c->chunk_slots, c->sm_count,
                                      c->timeline && al == 0 ? c->timeline + 4 * size_t(ling_b200_ctx::kTimelineLaunches - 16) : nullptr, s));
         else
@@ -227,7 +228,8 @@ int enqueue_step_body(ling_b200_ctx* c, int rows, int flags) {
       {
         Timed t(c, kFamAttn);
         LB_TRY(attn_combine_launch(c->part_o, c->part_ml, p0, c->sb, d, c->qout(c->xq_a), nullptr, rows,
-                                   c->opt.max_context / kAttnChunk + 2, s));
+                                   c->opt.max_context / kAttnChunkShort + 2, tc ? kAttnTcRows : kAttnRowTile,
+                                   tc ? c->sm_count : c->sm_count * 2, s));
       }
       LB_TRY(run_gemm(c, L.o, c->xq_a, 1, rows));
       carry = planes_of(c, 1, L.o);
@@ -249,7 +251,7 @@ int enqueue_step_body(ling_b200_ctx* c, int rows, int flags) {
         Timed t(c, kFamGdn);
         LB_TRY(gdn_fused_launch(p0, c->sb, d, L.conv, c->conv_state + size_t(gl) * c->conv_layer, c->conv_layer * d.n_gdn, g, beta,
                                 c->gdn_state + size_t(gl) * c->state_layer, c->state_layer * d.n_gdn, L.lin_norm, c->qout(c->xq_v),
-                                pre, post, c->sm_count,
+                                pre, post, c->opt.sessions, c->sm_count,
                                 c->timeline && gl == 0 ? c->timeline + 4 * size_t(ling_b200_ctx::kTimelineLaunches - 4) : nullptr, s));
       } else {
         {
@@ -554,9 +556,10 @@ int ling_b200_create(const ling_b200_model_config* cfg, const ling_b200_options*
   LB_TRY(c->alloc(&c->g, size_t(d.n_gdn) * d.rows_alloc * d.HV));
   LB_TRY(c->alloc(&c->beta, size_t(d.n_gdn) * d.rows_alloc * d.HV));
   // Chunk slots of the flash-decoding partials: every mapped position in chunks of kAttnChunk plus, per sequence, one
-  // partly filled chunk and the in-flight chunk; per kv head.
+  // partly filled chunk and the in-flight chunk; per kv head.  A step on the short chunks (attn_chunk_keys) has at most
+  // one slot per CTA of the attention grid.
   const size_t pool_positions = size_t(d.pool_pages) * d.page_tokens;
-  c->chunk_slots = int((pool_positions / kAttnChunk + size_t(2) * d.max_seqs) * d.Hkv);
+  c->chunk_slots = std::max(int((pool_positions / kAttnChunk + size_t(2) * d.max_seqs) * d.Hkv), 2 * c->sm_count);
   const size_t rmax = size_t(kTreeRows) * (d.Hq / d.Hkv);
   LB_TRY(c->alloc(&c->part_o, size_t(c->chunk_slots) * rmax * d.D, false));
   LB_TRY(c->alloc(&c->part_ml, size_t(c->chunk_slots) * rmax * 2, false));
@@ -567,8 +570,10 @@ int ling_b200_create(const ling_b200_model_config* cfg, const ling_b200_options*
     LB_TRY(c->alloc(&c->logits, size_t(opt->debug_rows) * d.V));
     LB_TRY(c->alloc(&c->taps, size_t(cfg->layers + 1) * opt->debug_rows * d.H));
   }
-  if (const char* tl = std::getenv("LING_B200_TIMELINE"); tl && tl[0] == '1')
+  if (const char* tl = std::getenv("LING_B200_TIMELINE"); tl && tl[0] == '1') {
     LB_TRY(c->alloc(&c->timeline, size_t(4) * ling_b200_ctx::kTimelineLaunches));
+    LB_TRY(kernels_norm_stamps(c->timeline + 4 * size_t(ling_b200_ctx::kTimelineLaunches - 24)));
+  }
   c->flush_floats = size_t(192) << 18;  // 192 MiB: more than the 126 MB L2
   LB_TRY(c->alloc(&c->flush, c->flush_floats, false));
 
@@ -626,6 +631,7 @@ void ling_b200_destroy(ling_b200_ctx* c) {
   if (!c) return;
   cudaSetDevice(c->opt.device);
   if (c->stream) cudaStreamSynchronize(c->stream);
+  if (c->timeline) kernels_norm_stamps(nullptr);
   for (auto& kvp : c->graphs) cudaGraphExecDestroy(kvp.second);
   for (void* p : c->owned) cudaFree(p);
   if (c->stage_host) cudaFreeHost(c->stage_host);
@@ -1148,14 +1154,16 @@ int ling_b200_attention_host(ling_b200_ctx* c, const ling_b200_seq_step* seqs, i
   LB_TRY(pack_launch(c->sb, d, c->stream));
   LB_CUDA(cudaMemcpyAsync(c->upload, q, n * 4, cudaMemcpyHostToDevice, c->stream));
   LB_TRY(f32_to_half_launch(c->upload, c->qh, n, c->stream));
-  if (c->opt.gemm_impl == 0 && attention_tc_supported(d))
+  const bool tc = c->opt.gemm_impl == 0 && attention_tc_supported(d);
+  if (tc)
     LB_TRY(attention_tc_launch(c->qh, c->sb, d, attn_layer, c->kv, c->part_o, c->part_ml, c->chunk_slots, c->sm_count, nullptr, c->stream));
   else
     LB_TRY(attention_launch(c->qh, c->sb, d, attn_layer, c->kv, c->part_o, c->part_ml, c->chunk_slots, c->sm_count * 2, c->stream));
   Planes none;
   none.p = nullptr;
   LB_TRY(attn_combine_launch(c->part_o, c->part_ml, none, c->sb, d, c->qout(c->xq_a), c->planes[0], cls,
-                             c->opt.max_context / kAttnChunk + 2, c->stream));
+                             c->opt.max_context / kAttnChunkShort + 2, tc ? kAttnTcRows : kAttnRowTile,
+                             tc ? c->sm_count : c->sm_count * 2, c->stream));
   LB_CUDA(cudaMemcpyAsync(out, c->planes[0], n * 4, cudaMemcpyDeviceToHost, c->stream));
   return read_err(c);
 }

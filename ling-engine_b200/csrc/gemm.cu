@@ -142,7 +142,7 @@ __global__ void __launch_bounds__(kGemmThreads, ctas_per_sm(NT))
         // Weights do not depend on the previous kernel: fill the pipeline with weight tiles and ask for the next
         // l2_slabs tiles to be brought into L2, then wait for the previous kernel and fetch the activation tiles of the
         // filled stages.  While the kernels between two GEMMs run, HBM keeps streaming the next GEMM's weights.
-        const int pre = nslab < STAGES ? nslab : STAGES;
+        const int pre = min(min(nslab, STAGES), pdl - 1);
         for (int s = 0; s < pre; ++s) {
           mbar_expect_tx(&full[s], kStageBytes);
           tma_load_2d(tiles + s * kStageBytes, &mapW, &full[s], (kb0 + s) * kBlockK, wy, pol_w);
@@ -522,11 +522,20 @@ int launch_tc(const GemmCall& c, cudaStream_t stream) {
   cfg.numAttrs = pdl ? 1 : 0;
   // L2 prefetch budget of one GEMM: about 40 MB of weight tiles beyond the pipeline stages, spread over its CTAs
   const int ctas = int(cfg.gridDim.z * cfg.gridDim.y);
-  const int l2_slabs = std::min(64, int((size_t(40) << 20) / (size_t(ctas) * kABytes)));
+  static const int l2_mb = [] {
+    const char* e = std::getenv("LING_B200_L2_PREFETCH_MB");  // tuning aid; the default was measured best for the 27B shapes
+    return e ? std::atoi(e) : 16;
+  }();
+  const int l2_slabs = std::min(64, int((size_t(l2_mb) << 20) / (size_t(ctas) * kABytes)));
+  static const int pre_stages = [] {
+    const char* e = std::getenv("LING_B200_PREFILL_STAGES");  // tuning aid: pipeline stages filled before the dependency wait
+    return e ? std::max(0, std::min(30, std::atoi(e))) : 30;
+  }();
   LB_CUDA(cudaLaunchKernelEx(&cfg, gemm_fp8_tcgen05_kernel<NT>, W.map, X.map[NT / 32 - 1], (const float*)W.scales,
                              (const float*)X.scales, c.out, c.ld, c.split_stride, c.M, W.N, W.N_pad, W.KB, splits,
-                             X.rows_alloc, h, c.err_flag, pdl ? 1 : 0, pdl && cfg.gridDim.x == 1 ? l2_slabs : 0,
+                             X.rows_alloc, h, c.err_flag, pdl ? 1 + pre_stages : 0, pdl && cfg.gridDim.x == 1 ? l2_slabs : 0,
                              c.timeline, c.timeline_detail ? 1 : 0));
+  LB_LAUNCH("gemm_fp8_tcgen05_kernel");
   return LING_B200_OK;
 }
 

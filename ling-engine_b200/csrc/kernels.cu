@@ -197,32 +197,53 @@ __global__ void __launch_bounds__(32) pack_kernel(StepBuffers sb, ModelDims d) {
 // columns (eight 128-column blocks, one per warp).  H <= 8192 keeps the cluster within the portable size of 8.
 // (Measured against one block per row: a single SM's L2 bandwidth makes that form ~3 us slower per launch at 5120 columns
 // and seven partial-sum planes.)
+__device__ __forceinline__ unsigned long long gtime_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// Debugging aid: where set (kernels_norm_stamps), block (0, 0) of every norm_quant launch leaves five %globaltimer
+// stamps there -- entry, dependency wait passed, row loaded, cluster reduction done, end -- so the last launch's remain.
+__device__ unsigned long long* g_norm_stamps = nullptr;
 __global__ void __launch_bounds__(256)
     norm_quant_kernel(float* __restrict__ h, Planes add, const int* __restrict__ ids, const __nv_bfloat16* __restrict__ embed,
                       const __nv_bfloat16* __restrict__ w, float* __restrict__ xn, QuantOut q, const int* __restrict__ n_rows,
                       int H, float eps) {
-  pdl_sync();  // first statement: see common.cuh
+  unsigned long long* st = nullptr;
+  if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) st = g_norm_stamps;
+  if (st) st[0] = gtime_ns();
+  // the norm weight is constant over the step: fetched before the dependency wait, so its latency hides behind the wait
+  const int m = blockIdx.y;
+  const int c = blockIdx.x * 1024 + threadIdx.x * 4;
+  uint2 wraw = make_uint2(0u, 0u);
+  if (c < H) wraw = *reinterpret_cast<const uint2*>(w + c);
+  pdl_sync();
+  if (st) st[1] = gtime_ns();
   namespace cg = cooperative_groups;
   __shared__ float red[32];
   __shared__ float parts[8];
-  const int m = blockIdx.y;
-  if (m >= *n_rows) return;  // the whole cluster shares the row, so it leaves together
-  const int c = blockIdx.x * 1024 + threadIdx.x * 4;
+  // The row count is requested together with the row (every row of the grid is allocated): one memory round trip, not
+  // two -- behind a GEMM that is already prefetching its weights a round trip costs microseconds.
+  const int nr = *n_rows;
   float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-  if (c < H) {
-    if (ids) {
+  if (ids) {
+    if (m >= nr) return;
+    if (c < H) {
       const __nv_bfloat16* e = embed + size_t(ids[m]) * H + c;
       v = make_float4(__bfloat162float(e[0]), __bfloat162float(e[1]), __bfloat162float(e[2]), __bfloat162float(e[3]));
-    } else {
-      v = *reinterpret_cast<const float4*>(h + size_t(m) * H + c);
-      if (add.p) {
-        const float4 t = plane_sum4(add, m, c);
-        v.x += t.x, v.y += t.y, v.z += t.z, v.w += t.w;
-      }
     }
-    *reinterpret_cast<float4*>(h + size_t(m) * H + c) = v;
+  } else if (c < H) {
+    v = *reinterpret_cast<const float4*>(h + size_t(m) * H + c);
+    if (add.p) {
+      const float4 t = plane_sum4(add, m, c);
+      v.x += t.x, v.y += t.y, v.z += t.z, v.w += t.w;
+    }
   }
-  const float ss = block_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w, red);
+  if (m >= nr) return;  // the whole cluster shares the row, so it leaves together
+  if (c < H) *reinterpret_cast<float4*>(h + size_t(m) * H + c) = v;
+  const float sq = v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+  if (st && sq >= 0.f) st[2] = gtime_ns();
+  const float ss = block_sum(sq, red);
   float total = ss;
   if (gridDim.x > 1) {
     // Every CTA stores its partial sum into every CTA's `parts` (its own included), one cluster barrier, and each reads
@@ -234,16 +255,19 @@ __global__ void __launch_bounds__(256)
     total = 0.f;
     for (unsigned r = 0; r < nb; ++r) total += parts[r];  // rank order: every CTA gets the same sum
   }
+  if (st) st[3] = gtime_ns();
   const float rstd = rsqrtf(total / H + eps);
   float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
   if (c < H) {
-    x.x = v.x * rstd * (1.f + __bfloat162float(w[c]));
-    x.y = v.y * rstd * (1.f + __bfloat162float(w[c + 1]));
-    x.z = v.z * rstd * (1.f + __bfloat162float(w[c + 2]));
-    x.w = v.w * rstd * (1.f + __bfloat162float(w[c + 3]));
+    const __nv_bfloat162 w01 = *reinterpret_cast<const __nv_bfloat162*>(&wraw.x), w23 = *reinterpret_cast<const __nv_bfloat162*>(&wraw.y);
+    x.x = v.x * rstd * (1.f + __low2float(w01));
+    x.y = v.y * rstd * (1.f + __high2float(w01));
+    x.z = v.z * rstd * (1.f + __low2float(w23));
+    x.w = v.w * rstd * (1.f + __high2float(w23));
     if (xn) *reinterpret_cast<float4*>(xn + size_t(m) * H + c) = x;
   }
   if (c - (threadIdx.x & 31) * 4 < q.K_pad) quant_store4(x, c, m, q);
+  if (st) st[4] = gtime_ns();
 }
 
 __global__ void __launch_bounds__(256)
@@ -265,12 +289,12 @@ __global__ void __launch_bounds__(128)
   pdl_sync();  // first statement: see common.cuh
   __shared__ float red[32];
   const int hv = blockIdx.x, m = blockIdx.y;
-  if (m >= *n_rows) return;
+  const int nr = *n_rows;  // requested together with the row (every row of the grid is allocated): one round trip
   const float* x = xn + size_t(m) * H;
   const __nv_bfloat16* a = wa + size_t(hv) * H;
   const __nv_bfloat16* b = wb + size_t(hv) * H;
   float sa = 0.f, sb2 = 0.f;
-#pragma unroll 4
+#pragma unroll 5
   for (int c = threadIdx.x * 4; c < H; c += 512) {
     const float4 xv = *reinterpret_cast<const float4*>(x + c);
     const uint2 ar = *reinterpret_cast<const uint2*>(a + c), br = *reinterpret_cast<const uint2*>(b + c);
@@ -279,6 +303,7 @@ __global__ void __launch_bounds__(128)
     sa += xv.x * __low2float(a01) + xv.y * __high2float(a01) + xv.z * __low2float(a23) + xv.w * __high2float(a23);
     sb2 += xv.x * __low2float(b01) + xv.y * __high2float(b01) + xv.z * __low2float(b23) + xv.w * __high2float(b23);
   }
+  if (m >= nr) return;
   sa = block_sum(sa, red);
   sb2 = block_sum(sb2, red);
   if (threadIdx.x == 0) {
@@ -510,11 +535,6 @@ __global__ void __launch_bounds__(128)
 // (16 warps, 8 value columns each) stages the raw inputs of all the sequence's rows for its channels, runs the conv and
 // the normalization in shared memory, walks the path with the state in registers, and normalizes and quantizes the rows
 // this path writes, for which it also stores `pre` and `post`, which the commit kernels replay.
-__device__ __forceinline__ unsigned long long gtime_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
 template <int DK>
 struct GdnFused {
   using St = GdnStage<DK>;
@@ -532,14 +552,38 @@ __global__ void __launch_bounds__(512)
                      const float* __restrict__ conv_state, size_t conv_slot_stride, const float* __restrict__ g,
                      const float* __restrict__ beta, const float* __restrict__ state, size_t state_slot_stride,
                      const __nv_bfloat16* __restrict__ norm_w, QuantOut q, float* __restrict__ pre, float* __restrict__ post,
-                     unsigned long long* stamps) {
+                     int n_slots, unsigned long long* stamps) {
   const bool stamp = stamps != nullptr && blockIdx.x == 0 && threadIdx.x == 0;
   if (stamp) stamps[0] = gtime_ns();
-  pdl_sync();  // first statement: see common.cuh
-  if (stamp) stamps[1] = gtime_ns();
   using F = GdnFused<DK>;
   using St = GdnStage<DK>;
   constexpr int KL = St::KL, NH = F::NH, CH = F::CH, RAWS = F::RAWS;
+  // ---- Before the dependency wait: the state of the block's first item, 64 KB that come from HBM.  No kernel of the step
+  // writes the state before the commit at its end, so a value loaded here is the value after the wait; what may be stale
+  // this early is the step's description that says WHICH state the item needs, so the choice is checked again behind the
+  // wait and the state is reloaded if it was wrong (indices are clamped, so a stale description cannot lead outside).
+  const int colb_ = (threadIdx.x >> 5) * 8 + (threadIdx.x & 7), quarter_ = (threadIdx.x & 31) >> 3;
+  int spec_slot = -1, spec_hv = -1;
+  float S[KL];
+  {
+    const int QB_ = d.HV / NH, pg0 = int(blockIdx.x) / QB_, qb0 = int(blockIdx.x) % QB_;
+    const int ns = min(max(*sb.n_seqs, 0), d.max_seqs);
+    int s0 = -1, acc = 0;
+    for (int s = 0; s < ns; ++s) {
+      const int k = min(max(sb.trees[s].ngdn, 0), LING_B200_MAX_TREE_VARIANTS);
+      if (s0 < 0 && pg0 < acc + k) s0 = s;
+      acc += k;
+    }
+    const int sl = s0 >= 0 ? sb.seqs[s0].slot : -1;
+    if (sl >= 0 && sl < n_slots) {
+      spec_slot = sl, spec_hv = qb0 * NH + colb_ / DK;
+      const float* st = state + size_t(sl) * state_slot_stride + size_t(spec_hv) * DK * DK;
+#pragma unroll
+      for (int i = 0; i < KL; ++i) S[i] = st[size_t(quarter_ * KL + i) * DK + colb_ % DK];
+    }
+  }
+  pdl_sync();
+  if (stamp) stamps[1] = gtime_ns();
   extern __shared__ __align__(16) float gsm[];
   float* raw = gsm;                                   // [32][RAWS] raw conv inputs of the sequence's rows
   float* qk = raw + size_t(kTreeRows) * RAWS;         // [NH][32][ROW] q^ and k^ per row (GdnStage layout)
@@ -577,28 +621,49 @@ __global__ void __launch_bounds__(512)
     const ling_b200_tree_desc* td = sb.trees + s;
     const int r0 = sb.row0[s], n = sb.seqs[s].n_rows, len = td->gdn_len[pth], slot = sb.seqs[s].slot;
     __syncthreads();  // the previous item's readers of shared memory are done
-    for (int i = tid; i < len; i += blockDim.x) steps[i] = td->gdn_step[pth][i];
-    for (int i = tid; i < n; i += blockDim.x) tdepth[i] = td->depth[i], tvar[i] = td->var[i];
-    for (int i = tid; i < LING_B200_MAX_TREE_VARIANTS * kTreeRows; i += blockDim.x) tpath[i] = td->path[i / kTreeRows][i % kTreeRows];
-    // ---- the state: this thread's KL rows of its value column (issued first, needed last)
+    // ---- Everything the item needs from memory is requested here in one go -- the tree, the state (this thread's KL rows
+    // of its value column), the raw inputs of every row of the sequence for the block's channels (no dependence on the
+    // path: one round trip less than staging the path's rows only) and the gates -- and only then stored to shared
+    // memory: a load behind a dependent store would cost a further round trip each time.
+    static_assert(2 * kTreeRows <= 512 && LING_B200_MAX_TREE_VARIANTS * kTreeRows == 1024 && NH * kTreeRows <= 512, "elements per thread");
+    const int v_step = tid < len ? td->gdn_step[pth][tid] : 0;
+    const int v_depth = tid < n ? td->depth[tid] : 0, v_var = tid < n ? td->var[tid] : 0;
+    const int v_path0 = td->path[tid / kTreeRows][tid % kTreeRows], v_path1 = td->path[(tid + 512) / kTreeRows][tid % kTreeRows];
     const int colb = warp * 8 + (lane & 7);  // column inside the block's 128
     const int hb_t = colb / DK, hv_t = qb * NH + hb_t, col = colb % DK;
-    const float* st = state + size_t(slot) * state_slot_stride + size_t(hv_t) * DK * DK;
-    float S[KL];
+    if (item != int(blockIdx.x) || slot != spec_slot || hv_t != spec_hv) {  // not what was loaded before the wait
+      const float* st = state + size_t(slot) * state_slot_stride + size_t(hv_t) * DK * DK;
 #pragma unroll
-    for (int i = 0; i < KL; ++i) S[i] = st[size_t(quarter * KL + i) * DK + col];
-    // ---- raw inputs of every row of the sequence for the block's channels, and the gates: issued together with the loads
-    // above (no dependence on the path), so the item start costs one memory round trip less than staging the path's rows only
-    for (int idx = tid; idx < n * (CH / 4); idx += blockDim.x) {
-      const int t = idx / (CH / 4), c = (idx % (CH / 4)) * 4;
-      int hb, part, e;
-      const int gc = conv_channel(c, qb, hb, part, e);
-      *reinterpret_cast<float4*>(raw + size_t(t) * RAWS + c) = plane_sum4(in, r0 + t, gc);
+      for (int i = 0; i < KL; ++i) S[i] = st[size_t(quarter * KL + i) * DK + col];
     }
-    for (int i = tid; i < NH * n; i += blockDim.x) {
-      const int hb = i / n, t = i % n, hv = qb * NH + hb;
-      gb[(hb * kTreeRows + t) * 2] = g[size_t(r0 + t) * HV + hv];
-      gb[(hb * kTreeRows + t) * 2 + 1] = beta[size_t(r0 + t) * HV + hv];
+    float v_g = 0.f, v_beta = 0.f;
+    if (tid < NH * n) {
+      const int hv = qb * NH + tid / n, t = tid % n;
+      v_g = g[size_t(r0 + t) * HV + hv], v_beta = beta[size_t(r0 + t) * HV + hv];
+    }
+    {
+      constexpr int RAWL = (kTreeRows * (CH / 4) + 511) / 512;
+      float4 rawv[RAWL];
+#pragma unroll
+      for (int k = 0; k < RAWL; ++k) {
+        const int idx = tid + k * 512;
+        if (idx < n * (CH / 4)) {
+          int hb, part, e;
+          rawv[k] = plane_sum4(in, r0 + idx / (CH / 4), conv_channel((idx % (CH / 4)) * 4, qb, hb, part, e));
+        }
+      }
+      if (tid < len) steps[tid] = v_step;
+      if (tid < n) tdepth[tid] = v_depth, tvar[tid] = v_var;
+      tpath[tid] = v_path0, tpath[tid + 512] = v_path1;
+      if (tid < NH * n) {
+        const int hb = tid / n, t = tid % n;
+        gb[(hb * kTreeRows + t) * 2] = v_g, gb[(hb * kTreeRows + t) * 2 + 1] = v_beta;
+      }
+#pragma unroll
+      for (int k = 0; k < RAWL; ++k) {
+        const int idx = tid + k * 512;
+        if (idx < n * (CH / 4)) *reinterpret_cast<float4*>(raw + size_t(idx / (CH / 4)) * RAWS + (idx % (CH / 4)) * 4) = rawv[k];
+      }
     }
     __syncthreads();
     // the distinct rows of this path (a row's taps are its ancestors, which the path contains) and those it writes: only
@@ -826,7 +891,7 @@ __global__ void __launch_bounds__(256)
     silu_mul_quant_kernel(Planes gu, int I, int up_col0, QuantOut q, const int* __restrict__ n_rows) {
   pdl_sync();  // first statement: see common.cuh
   const int m = blockIdx.x;
-  if (m >= *n_rows) return;
+  const int nr = *n_rows;  // requested together with the row (every row of the grid is allocated): one round trip
   {
     const int c = blockIdx.y * 1024 + threadIdx.x * 4;
     if (c - (threadIdx.x & 31) * 4 >= q.K_pad) return;  // warp-uniform
@@ -835,6 +900,7 @@ __global__ void __launch_bounds__(256)
       const float4 a = plane_sum4(gu, m, c), b = plane_sum4(gu, m, up_col0 + c);
       x = make_float4(silu(a.x) * b.x, silu(a.y) * b.y, silu(a.z) * b.z, silu(a.w) * b.w);
     }
+    if (m >= nr) return;
     quant_store4(x, c, m, q);
   }
 }
@@ -935,7 +1001,7 @@ __host__ __device__ constexpr int perm16(int c) { return (c & 3) < 2 ? 2 * (c >>
 // src/core/kernels.cu:919-961 with body src/core/attention_body.cuh:262-501, rebuilt for an FP8 cache and any number
 // of sequences).  Work item = (sequence, kv head, key chunk, kAttnRowTile query rows); the query rows of a kv head are
 // (token row, q head of the group) pairs, so one pass over a K/V tile serves every row of the tree and every q head
-// of the group.  Context chunks hold kAttnChunk keys; the last chunk of a sequence is its in-flight rows (cache slots
+// of the group.  Context chunks hold kAttnChunk keys (kAttnChunkShort in a step of few sequences, attn_chunk_keys); the last chunk of a sequence is its in-flight rows (cache slots
 // pos .. pos + n_rows), read from the 16-aligned position below pos so that every copy stays 16-byte aligned; a row sees
 // an in-flight key only where its ancestor mask has the bit.  K tiles ([key][D]) and V tiles ([D][key], the pool's V
 // layout) arrive by 16-byte cp.async into double-buffered shared memory and stay E4M3 there; fragments are converted on
@@ -973,20 +1039,24 @@ __global__ void __launch_bounds__(kAttnThreads, 2)
   float* vsc = ksc + 2 * kAttnKeyTile;                                   // [2][64]
   float* redm = vsc + 2 * kAttnKeyTile;                                  // [NW][RowTile]
   __shared__ int cbase[LING_B200_MAX_SEQS + 1], ibase[LING_B200_MAX_SEQS + 1];
+  __shared__ int chunk_sh;  // keys per chunk of this step (attn_chunk_keys)
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g8 = lane >> 2, t4 = lane & 3;
   const int nseq = *sb.n_seqs;
   if (tid == 0) {
+    const int chunk = attn_chunk_keys(sb, nseq, d.Hkv, G, kAttnRowTile, int(gridDim.x));
+    chunk_sh = chunk;
     int cb = 0, ib = 0;
     for (int s = 0; s < nseq; ++s) {
       cbase[s] = cb, ibase[s] = ib;
-      const int nch = (sb.seqs[s].pos + kAttnChunk - 1) / kAttnChunk + 1;
+      const int nch = (sb.seqs[s].pos + chunk - 1) / chunk + 1;
       const int nrg = (sb.seqs[s].n_rows * G + kAttnRowTile - 1) / kAttnRowTile;
       cb += nch, ib += d.Hkv * nch * nrg;
     }
     cbase[nseq] = cb, ibase[nseq] = ib;
   }
   __syncthreads();
+  const int chunk = chunk_sh;
   const float inv_sqrt_d = rsqrtf(float(D));
   const int pt = d.page_tokens, lp = 31 - __clz(pt), pmask = pt - 1;  // pages hold 16, 32 or 64 positions
   // ldmatrix row addresses of this lane inside a 16x16 A tile: matrices 0..3 = (rows 0-7, k 0-7), (rows 8-15, k 0-7),
@@ -1001,7 +1071,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2)
     int s = 0;
     while (ibase[s + 1] <= item) ++s;
     const SeqDev sq = sb.seqs[s];
-    const int nch = (sq.pos + kAttnChunk - 1) / kAttnChunk + 1;
+    const int nch = (sq.pos + chunk - 1) / chunk + 1;
     const int nrg = (sq.n_rows * G + kAttnRowTile - 1) / kAttnRowTile;
     const int loc = item - ibase[s];
     const int hk = loc / (nch * nrg), ch = (loc % (nch * nrg)) / nrg, rg = loc % nrg;
@@ -1012,9 +1082,9 @@ __global__ void __launch_bounds__(kAttnThreads, 2)
     }
     const bool tail = ch == nch - 1;
     // keys [key_base + key_lo, key_base + key_hi) count; a tail chunk starts at the 16-aligned position below pos
-    const int key_base = tail ? (sq.pos & ~15) : ch * kAttnChunk;
+    const int key_base = tail ? (sq.pos & ~15) : ch * chunk;
     const int key_lo = tail ? sq.pos - key_base : 0;
-    const int key_hi = tail ? key_lo + sq.n_rows : min(kAttnChunk, sq.pos - key_base);
+    const int key_hi = tail ? key_lo + sq.n_rows : min(chunk, sq.pos - key_base);
     const int R = sq.n_rows * G, r_begin = rg * kAttnRowTile, r0 = sb.row0[s];
     const int mt_n = min(MT, (R - r_begin + 15) / 16);  // row tiles that hold a real row
     const int* table = kv.tables + size_t(sq.slot) * d.max_pages;
@@ -1255,7 +1325,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2)
 template <int G>
 __global__ void __launch_bounds__(256)
     attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, Planes qkv, StepBuffers sb,
-                        ModelDims d, QuantOut q, float* __restrict__ raw, int max_chunks) {
+                        ModelDims d, QuantOut q, float* __restrict__ raw, int max_chunks, int tile_rows, int budget) {
   pdl_sync();  // first statement: see common.cuh
   constexpr int RMAX = kTreeRows * G;
   extern __shared__ __align__(16) float csm[];  // [HB][max_chunks] chunk weights, [4] denominators, [NG][CB] partial sums (max_chunks a multiple of 4)
@@ -1268,9 +1338,10 @@ __global__ void __launch_bounds__(256)
   const int c0 = blockIdx.y * CB;
   if (c0 >= q.K_pad) return;
   const int s = sb.seq_of[m], local = sb.local[m];
+  const int chunk = attn_chunk_keys(sb, *sb.n_seqs, d.Hkv, G, tile_rows, budget);
   int cb = 0;
-  for (int t = 0; t < s; ++t) cb += (sb.seqs[t].pos + kAttnChunk - 1) / kAttnChunk + 1;
-  const int nch = min(max_chunks, (sb.seqs[s].pos + kAttnChunk - 1) / kAttnChunk + 1);
+  for (int t = 0; t < s; ++t) cb += (sb.seqs[t].pos + chunk - 1) / chunk + 1;
+  const int nch = min(max_chunks, (sb.seqs[s].pos + chunk - 1) / chunk + 1);
   float* wgt = csm;                       // [HB][max_chunks]
   float* den = csm + HB * max_chunks;     // [HB]
   float* acc = den + 4;                   // [NG][CB], 16-byte aligned: max_chunks is a multiple of 4
@@ -1575,6 +1646,11 @@ int pack_launch(const StepBuffers& sb, const ModelDims& d, cudaStream_t s) {
   return LING_B200_OK;
 }
 
+int kernels_norm_stamps(unsigned long long* stamps) {
+  LB_CUDA(cudaMemcpyToSymbol(g_norm_stamps, &stamps, sizeof(stamps)));
+  return LING_B200_OK;
+}
+
 int norm_quant_launch(float* h, const Planes& add, const int* ids, const __nv_bfloat16* embed, const __nv_bfloat16* w,
                       float* xn, const QuantOut& q, const int* n_rows, int rows_grid, int H, float eps, cudaStream_t s) {
   const int chunks = ceil_div(q.K_pad, 1024);
@@ -1636,18 +1712,18 @@ bool gdn_fused_supported(const ModelDims& d) {
 
 int gdn_fused_launch(const Planes& in, const StepBuffers& sb, const ModelDims& d, const __nv_bfloat16* convw, const float* conv_state,
                      size_t conv_slot_stride, const float* g, const float* beta, const float* state, size_t state_slot_stride,
-                     const __nv_bfloat16* norm_w, const QuantOut& q, float* pre, float* post, int grid, unsigned long long* stamps,
-                     cudaStream_t s) {
+                     const __nv_bfloat16* norm_w, const QuantOut& q, float* pre, float* post, int n_slots, int grid,
+                     unsigned long long* stamps, cudaStream_t s) {
   if (!gdn_fused_supported(d)) {
     set_error("fused DeltaNet kernel: key dim = value dim = 64 or 128 expected");
     return LING_B200_ERR_UNSUPPORTED;
   }
   if (d.Dk == 128)
     LB_CUDA(launch_kernel(gdn_fused_kernel<128>, dim3(grid), dim3(512), GdnFused<128>::smem_floats() * 4, s, in, sb, d, convw, conv_state,
-                          conv_slot_stride, g, beta, state, state_slot_stride, norm_w, q, pre, post, stamps));
+                          conv_slot_stride, g, beta, state, state_slot_stride, norm_w, q, pre, post, n_slots, stamps));
   else
     LB_CUDA(launch_kernel(gdn_fused_kernel<64>, dim3(grid), dim3(512), GdnFused<64>::smem_floats() * 4, s, in, sb, d, convw, conv_state,
-                          conv_slot_stride, g, beta, state, state_slot_stride, norm_w, q, pre, post, stamps));
+                          conv_slot_stride, g, beta, state, state_slot_stride, norm_w, q, pre, post, n_slots, stamps));
   LB_LAUNCH("gdn_fused_kernel");
   return LING_B200_OK;
 }
@@ -1703,7 +1779,8 @@ int attention_launch(const __half* q, const StepBuffers& sb, const ModelDims& d,
 }
 
 int attn_combine_launch(const float* part_o, const float* part_ml, const Planes& qkv, const StepBuffers& sb,
-                        const ModelDims& d, const QuantOut& q, float* raw, int rows_grid, int max_chunks, cudaStream_t s) {
+                        const ModelDims& d, const QuantOut& q, float* raw, int rows_grid, int max_chunks, int tile_rows, int budget,
+                        cudaStream_t s) {
   const int G = d.Hq / d.Hkv;
   const int CB = d.D > 128 ? d.D : 128, HB = CB / d.D, NG = 256 / (CB / 4);
   if (CB % 128 != 0 || 256 % (CB / 4) != 0 || CB % d.D != 0) {
@@ -1717,9 +1794,9 @@ int attn_combine_launch(const float* part_o, const float* part_ml, const Planes&
     set_error("attention combine: too many chunks for one sequence");
     return LING_B200_ERR_UNSUPPORTED;
   }
-  if (G == 6) LB_CUDA(launch_kernel(attn_combine_kernel<6>, grid, dim3(256), smem, s, part_o, part_ml, qkv, sb, d, q, raw, max_chunks));
-  else if (G == 4) LB_CUDA(launch_kernel(attn_combine_kernel<4>, grid, dim3(256), smem, s, part_o, part_ml, qkv, sb, d, q, raw, max_chunks));
-  else if (G == 8) LB_CUDA(launch_kernel(attn_combine_kernel<8>, grid, dim3(256), smem, s, part_o, part_ml, qkv, sb, d, q, raw, max_chunks));
+  if (G == 6) LB_CUDA(launch_kernel(attn_combine_kernel<6>, grid, dim3(256), smem, s, part_o, part_ml, qkv, sb, d, q, raw, max_chunks, tile_rows, budget));
+  else if (G == 4) LB_CUDA(launch_kernel(attn_combine_kernel<4>, grid, dim3(256), smem, s, part_o, part_ml, qkv, sb, d, q, raw, max_chunks, tile_rows, budget));
+  else if (G == 8) LB_CUDA(launch_kernel(attn_combine_kernel<8>, grid, dim3(256), smem, s, part_o, part_ml, qkv, sb, d, q, raw, max_chunks, tile_rows, budget));
   else {
     set_error("attention combine: unsupported group size");
     return LING_B200_ERR_UNSUPPORTED;

@@ -9,6 +9,8 @@ namespace lb {
 
 constexpr int kTreeRows = LING_B200_MAX_TREE_ROWS;
 constexpr int kAttnChunk = 512;    // context keys per flash-decoding chunk
+constexpr int kAttnChunkShort = 256;  // ... of a step with so few sequences that the shorter chunks still fit one wave of CTAs
+constexpr int kAttnTcRows = 128;   // query rows per work item of the tcgen05 attention (the MMA's M)
 constexpr int kAttnKeyTile = 64;   // keys per shared-memory tile
 constexpr int kAttnRowTile = 48;   // query rows (token rows x q heads of one kv head) per CTA: three m16 tiles
 constexpr float kPScale = 256.f;   // attention: p * v_scale is carried in FP16 times this power of two (clear of subnormals)
@@ -45,6 +47,23 @@ struct StepBuffers {
   ling_b200_seq_result* results = nullptr;  // [max_seqs]
   int* err = nullptr;         // [1] device error word
 };
+
+#ifdef __CUDACC__
+// Keys per flash-decoding chunk of the staged step.  A step with few sequences has too few (sequence, kv head, 512-key
+// chunk) items to occupy the SMs, and its attention time is one item's latency: when the items of 256-key chunks still fit
+// one wave of `budget` CTAs the step uses those.  The attention kernel (tile_rows query rows per item) and the combine
+// behind it evaluate the same rule on the same device-resident extents.
+__device__ __forceinline__ int attn_chunk_keys(const StepBuffers& sb, int nseq, int Hkv, int G, int tile_rows, int budget) {
+  if (nseq * Hkv * 2 > budget) return kAttnChunk;
+  int items = 0;
+  for (int s = 0; s < nseq; ++s) {
+    const int nch = (sb.seqs[s].pos + kAttnChunkShort - 1) / kAttnChunkShort + 1;
+    const int nrg = (sb.seqs[s].n_rows * G + tile_rows - 1) / tile_rows;
+    items += Hkv * nch * nrg;
+  }
+  return items <= budget ? kAttnChunkShort : kAttnChunk;
+}
+#endif
 
 struct ModelDims {
   int H, I, V, Hq, Hkv, D, rot, Hk, HV, Dk, Dv, C, Vs;
@@ -97,6 +116,7 @@ int norm_quant_launch(float* h, const Planes& add, const int* ids, const __nv_bf
 // tap[m][:] = h[m][:] + planes (debug copy of the residual after a layer)
 int tap_launch(const float* h, const Planes& add, float* out, const int* n_rows, int rows_grid, int H, cudaStream_t s);
 int copy_rows_launch(const float* src, float* out, const int* n_rows, int rows_grid, int H, cudaStream_t s);
+int kernels_norm_stamps(unsigned long long* stamps);  // debugging aid: five %globaltimer stamps of norm_quant's block (0, 0), or nullptr
 int ab_gating_launch(const float* xn, const __nv_bfloat16* wa, const __nv_bfloat16* wb, const __nv_bfloat16* A_log,
                      const __nv_bfloat16* dt_bias, float* g, float* beta, const int* n_rows, int rows_grid, int H, int HV,
                      cudaStream_t s);
@@ -108,8 +128,8 @@ int gdn_tree_launch(const float* post, const float* g, const float* beta, const 
 bool gdn_fused_supported(const ModelDims& d);
 int gdn_fused_launch(const Planes& in, const StepBuffers& sb, const ModelDims& d, const __nv_bfloat16* convw, const float* conv_state,
                      size_t conv_slot_stride, const float* g, const float* beta, const float* state, size_t state_slot_stride,
-                     const __nv_bfloat16* norm_w, const QuantOut& q, float* pre, float* post, int grid, unsigned long long* stamps,
-                     cudaStream_t s);  // stamps: seven %globaltimer values of block 0's first item (debugging aid) or nullptr
+                     const __nv_bfloat16* norm_w, const QuantOut& q, float* pre, float* post, int n_slots, int grid,
+                     unsigned long long* stamps, cudaStream_t s);  // n_slots: sessions the state holds; stamps: seven %globaltimer values of block 0's first item (debugging aid) or nullptr
 int gated_norm_quant_launch(const float* core, const Planes& z, int z_col, const __nv_bfloat16* w, const QuantOut& q,
                             const int* n_rows, int rows_grid, int HV, int Dv, float eps, cudaStream_t s);
 int attn_prepare_launch(const Planes& qkv, const StepBuffers& sb, const ModelDims& d, int al, const __nv_bfloat16* q_norm,
@@ -122,9 +142,11 @@ int attention_tc_init();
 bool attention_tc_supported(const ModelDims& d);
 int attention_tc_launch(const __half* q, const StepBuffers& sb, const ModelDims& d, int al, const KvPoolDev& kv, float* part_o,
                         float* part_ml, int chunk_slots, int grid, unsigned long long* stamps, cudaStream_t s);  // stamps: see the kernel
-// max_chunks: the most flash-decoding chunks one sequence can have (context capacity / kAttnChunk + 1)
+// max_chunks: the most flash-decoding chunks one sequence can have (context capacity / kAttnChunkShort + 2);
+// tile_rows, budget: the query rows per item and the grid of the attention kernel whose partials are merged (attn_chunk_keys)
 int attn_combine_launch(const float* part_o, const float* part_ml, const Planes& qkv, const StepBuffers& sb,
-                        const ModelDims& d, const QuantOut& q, float* raw, int rows_grid, int max_chunks, cudaStream_t s);
+                        const ModelDims& d, const QuantOut& q, float* raw, int rows_grid, int max_chunks, int tile_rows, int budget,
+                        cudaStream_t s);
 int f32_to_half_launch(const float* src, __half* dst, size_t n, cudaStream_t s);
 int silu_mul_quant_launch(const Planes& gu, int I, int up_col0, const QuantOut& q, const int* n_rows, int rows_grid, cudaStream_t s);
 int argmax_reduce_launch(const float* tile_val, const int* tile_idx, int tiles, int rows_alloc, int* ids, float* vals,
