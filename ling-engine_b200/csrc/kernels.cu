@@ -217,11 +217,13 @@ __global__ void __launch_bounds__(256)
   const int c = blockIdx.x * 1024 + threadIdx.x * 4;
   uint2 wraw = make_uint2(0u, 0u);
   if (c < H) wraw = *reinterpret_cast<const uint2*>(w + c);
+  // first half of a cluster barrier whose second half stands before the first store into a peer's shared memory: by then
+  // every CTA of the cluster has started (the condition for touching its shared memory), and nobody has waited for it
+  if (gridDim.x > 1) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   pdl_sync();
   if (st) st[1] = gtime_ns();
   namespace cg = cooperative_groups;
-  __shared__ float red[32];
-  __shared__ float parts[8];
+  __shared__ __align__(16) float parts[64];  // [CTA of the cluster][warp]
   // The row count is requested together with the row (every row of the grid is allocated): one memory round trip, not
   // two -- behind a GEMM that is already prefetching its weights a round trip costs microseconds.
   const int nr = *n_rows;
@@ -243,17 +245,27 @@ __global__ void __launch_bounds__(256)
   if (c < H) *reinterpret_cast<float4*>(h + size_t(m) * H + c) = v;
   const float sq = v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
   if (st && sq >= 0.f) st[2] = gtime_ns();
-  const float ss = block_sum(sq, red);
-  float total = ss;
+  // Sum of squares over the row: every warp pushes its partial sum into every CTA of the cluster (its own included)
+  // through distributed shared memory, one cluster barrier, and each CTA adds the partials from its own shared memory
+  // in (CTA, warp) order -- the same sum everywhere, nobody reads a peer that may have left, one barrier in all.
+  const float wsum = warp_sum(sq);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float total = 0.f;
   if (gridDim.x > 1) {
-    // Every CTA stores its partial sum into every CTA's `parts` (its own included), one cluster barrier, and each reads
-    // only its own shared memory afterwards -- so nobody reads a peer that may have left, and one barrier is enough.
     cg::cluster_group cluster = cg::this_cluster();
     const unsigned me = cluster.block_rank(), nb = cluster.num_blocks();
-    if (threadIdx.x < nb) *cluster.map_shared_rank(&parts[me], threadIdx.x) = ss;
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    if (lane < nb) *cluster.map_shared_rank(&parts[me * 8 + warp], lane) = wsum;
     cluster.sync();
-    total = 0.f;
-    for (unsigned r = 0; r < nb; ++r) total += parts[r];  // rank order: every CTA gets the same sum
+    for (unsigned r = 0; r < nb; ++r) {
+      const float4 a = *reinterpret_cast<const float4*>(&parts[r * 8]), b4 = *reinterpret_cast<const float4*>(&parts[r * 8 + 4]);
+      total += ((a.x + a.y) + (a.z + a.w)) + ((b4.x + b4.y) + (b4.z + b4.w));
+    }
+  } else {
+    if (lane == 0) parts[warp] = wsum;
+    __syncthreads();
+    const float4 a = *reinterpret_cast<const float4*>(&parts[0]), b4 = *reinterpret_cast<const float4*>(&parts[4]);
+    total = ((a.x + a.y) + (a.z + a.w)) + ((b4.x + b4.y) + (b4.z + b4.w));
   }
   if (st) st[3] = gtime_ns();
   const float rstd = rsqrtf(total / H + eps);
@@ -543,7 +555,7 @@ struct GdnFused {
   static constexpr int RAWS = CH + 4;        // floats per staged row
   static constexpr size_t smem_floats() {
     return size_t(kTreeRows) * RAWS + size_t(NH) * kTreeRows * St::ROW + size_t(kTreeRows) * 128 + size_t(NH) * kTreeRows * 2 +
-           size_t(kTreeRows) * 128;
+           size_t(kTreeRows) * 128 + size_t(CH) * 8;
   }
 };
 template <int DK>
@@ -562,6 +574,32 @@ __global__ void __launch_bounds__(512)
   // writes the state before the commit at its end, so a value loaded here is the value after the wait; what may be stale
   // this early is the step's description that says WHICH state the item needs, so the choice is checked again behind the
   // wait and the state is reloaded if it was wrong (indices are clamped, so a stale description cannot lead outside).
+  extern __shared__ __align__(16) float gsm[];
+  float* raw = gsm;                                   // [32][RAWS] raw conv inputs of the sequence's rows
+  float* qk = raw + size_t(kTreeRows) * RAWS;         // [NH][32][ROW] q^ and k^ per row (GdnStage layout)
+  float* vv = qk + size_t(NH) * kTreeRows * St::ROW;  // [32][128] conv output of the value channels
+  float* gb = vv + size_t(kTreeRows) * 128;           // [NH][32][2] g, beta
+  float* osm = gb + NH * kTreeRows * 2;               // [32][128] the recurrence's outputs
+  float* cwin = osm + size_t(kTreeRows) * 128;        // [CH][8] per channel: the four conv taps' weights, the session's window
+  // channel c of the block -> (head in block, part 0 q / 1 k / 2 v, element) and its conv channel
+  auto conv_channel = [&](int c, int qb, int& hb, int& part, int& e) {
+    hb = c / (3 * DK), part = (c % (3 * DK)) / DK, e = c % DK;
+    const int hv = qb * NH + hb, h = hv / (d.HV / d.Hk);
+    return part == 0 ? h * DK + e : part == 1 ? d.Hk * DK + h * DK + e : 2 * d.Hk * DK + hv * DK + e;
+  };
+  // weights and window (taps before depth 0) of the block's channels into shared memory
+  auto load_conv_consts = [&](int qb, int slot) {
+    for (int c = threadIdx.x; c < CH; c += blockDim.x) {
+      int hb, part, e;
+      const int gc = conv_channel(c, qb, hb, part, e);
+      const uint2 wr = *reinterpret_cast<const uint2*>(convw + size_t(gc) * 4);
+      const float* wsrc = conv_state + size_t(slot) * conv_slot_stride + size_t(gc) * 3;
+      const float w0 = wsrc[0], w1 = wsrc[1], w2 = wsrc[2];
+      const __nv_bfloat162 c01 = *reinterpret_cast<const __nv_bfloat162*>(&wr.x), c23 = *reinterpret_cast<const __nv_bfloat162*>(&wr.y);
+      *reinterpret_cast<float4*>(cwin + c * 8) = make_float4(__low2float(c01), __high2float(c01), __low2float(c23), __high2float(c23));
+      *reinterpret_cast<float4*>(cwin + c * 8 + 4) = make_float4(w0, w1, w2, 0.f);
+    }
+  };
   const int colb_ = (threadIdx.x >> 5) * 8 + (threadIdx.x & 7), quarter_ = (threadIdx.x & 31) >> 3;
   int spec_slot = -1, spec_hv = -1;
   float S[KL];
@@ -580,16 +618,11 @@ __global__ void __launch_bounds__(512)
       const float* st = state + size_t(sl) * state_slot_stride + size_t(spec_hv) * DK * DK;
 #pragma unroll
       for (int i = 0; i < KL; ++i) S[i] = st[size_t(quarter_ * KL + i) * DK + colb_ % DK];
+      load_conv_consts(qb0, sl);  // the conv's constants of the same item, with the same check behind the wait
     }
   }
   pdl_sync();
   if (stamp) stamps[1] = gtime_ns();
-  extern __shared__ __align__(16) float gsm[];
-  float* raw = gsm;                                   // [32][RAWS] raw conv inputs of the sequence's rows
-  float* qk = raw + size_t(kTreeRows) * RAWS;         // [NH][32][ROW] q^ and k^ per row (GdnStage layout)
-  float* vv = qk + size_t(NH) * kTreeRows * St::ROW;  // [32][128] conv output of the value channels
-  float* gb = vv + size_t(kTreeRows) * 128;           // [NH][32][2] g, beta
-  float* osm = gb + NH * kTreeRows * 2;               // [32][128] the recurrence's outputs
   __shared__ int pbase[LING_B200_MAX_SEQS + 1];
   __shared__ int steps[2 * kTreeRows], taprow[3 * kTreeRows], prow[kTreeRows], pinfo[2];
   __shared__ float kqs[2 * kTreeRows];  // k^ . q^ per (head in block, row)
@@ -606,12 +639,6 @@ __global__ void __launch_bounds__(512)
   }
   __syncthreads();
   const int C = d.C, Hk = d.Hk, HV = d.HV, ratio = HV / Hk, QB = HV / NH;  // QB: 128-column blocks of the value width
-  // channel c of the block -> (head in block, part 0 q / 1 k / 2 v, element) and its conv channel
-  auto conv_channel = [&](int c, int qb, int& hb, int& part, int& e) {
-    hb = c / (3 * DK), part = (c % (3 * DK)) / DK, e = c % DK;
-    const int hv = qb * NH + hb, h = hv / ratio;
-    return part == 0 ? h * DK + e : part == 1 ? Hk * DK + h * DK + e : 2 * Hk * DK + hv * DK + e;
-  };
   const int total = pbase[nseq] * QB;
   for (int item = blockIdx.x; item < total; item += gridDim.x) {
     const int pg = item / QB, qb = item % QB;
@@ -631,6 +658,7 @@ __global__ void __launch_bounds__(512)
     const int v_path0 = td->path[tid / kTreeRows][tid % kTreeRows], v_path1 = td->path[(tid + 512) / kTreeRows][tid % kTreeRows];
     const int colb = warp * 8 + (lane & 7);  // column inside the block's 128
     const int hb_t = colb / DK, hv_t = qb * NH + hb_t, col = colb % DK;
+    if (item != int(blockIdx.x) || slot != spec_slot) load_conv_consts(qb, slot);
     if (item != int(blockIdx.x) || slot != spec_slot || hv_t != spec_hv) {  // not what was loaded before the wait
       const float* st = state + size_t(slot) * state_slot_stride + size_t(hv_t) * DK * DK;
 #pragma unroll
@@ -695,10 +723,9 @@ __global__ void __launch_bounds__(512)
       const int c = w0 % CH, qr = w0 / CH;
       int hb, part, e;
       const int gc = conv_channel(c, qb, hb, part, e);
-      const float cw0 = __bfloat162float(convw[size_t(gc) * 4]), cw1 = __bfloat162float(convw[size_t(gc) * 4 + 1]);
-      const float cw2 = __bfloat162float(convw[size_t(gc) * 4 + 2]), cw3 = __bfloat162float(convw[size_t(gc) * 4 + 3]);
-      const float* wsrc = conv_state + size_t(slot) * conv_slot_stride + size_t(gc) * 3;
-      const float wv[3] = {wsrc[0], wsrc[1], wsrc[2]};
+      const float4 cw = *reinterpret_cast<const float4*>(cwin + c * 8);
+      const float4 win = *reinterpret_cast<const float4*>(cwin + c * 8 + 4);
+      const float cw0 = cw.x, cw1 = cw.y, cw2 = cw.z, cw3 = cw.w;
       const bool own = part == 2 || (qb * NH + hb) % ratio == 0;  // q, k channels belong to the first head of their group
       float* dst = part == 2 ? vv + hb * DK + e
                              : qk + size_t(hb) * kTreeRows * St::ROW + (part == 1 ? 4 * St::SEG : 0) + (e / KL) * St::SEG + e % KL;
@@ -709,7 +736,7 @@ __global__ void __launch_bounds__(512)
 #pragma unroll
         for (int j = 0; j < 3; ++j) {
           const int tr = taprow[t * 3 + j];
-          tap[j] = tr >= 0 ? raw[size_t(tr) * RAWS + c] : wv[3 + tr];
+          tap[j] = tr >= 0 ? raw[size_t(tr) * RAWS + c] : (tr == -1 ? win.z : tr == -2 ? win.y : win.x);
         }
         const float xv = raw[size_t(t) * RAWS + c];
         const float o = silu(cw0 * tap[0] + cw1 * tap[1] + cw2 * tap[2] + cw3 * xv);
