@@ -298,7 +298,17 @@ __global__ void __launch_bounds__(128)
     ab_gating_kernel(const float* __restrict__ xn, const __nv_bfloat16* __restrict__ wa, const __nv_bfloat16* __restrict__ wb,
                      const __nv_bfloat16* __restrict__ A_log, const __nv_bfloat16* __restrict__ dt_bias, float* __restrict__ g,
                      float* __restrict__ beta, const int* __restrict__ n_rows, int H, int HV) {
-  pdl_sync();  // first statement: see common.cuh
+  // The head's two weight rows are constant over the step and come from HBM: the first row's block asks for them to be
+  // brought into L2 before the dependency wait, so that behind it every block of the head finds them there.
+  if (blockIdx.y == 0) {
+    const char* pa = reinterpret_cast<const char*>(wa + size_t(blockIdx.x) * H);
+    const char* pb = reinterpret_cast<const char*>(wb + size_t(blockIdx.x) * H);
+    for (int o = threadIdx.x * 128; o < H * 2; o += blockDim.x * 128) {
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(pa + o));
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(pb + o));
+    }
+  }
+  pdl_sync();
   __shared__ float red[32];
   const int hv = blockIdx.x, m = blockIdx.y;
   const int nr = *n_rows;  // requested together with the row (every row of the grid is allocated): one round trip
