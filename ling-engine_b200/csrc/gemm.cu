@@ -34,7 +34,11 @@ constexpr int kScaleAhead = 4;  // K blocks by which the epilogue's scale loads 
 constexpr int kScaleRing = 8;   // slots of each epilogue warp's activation-scale ring (> kScaleAhead)
 __host__ __device__ constexpr int stages_for(int nt) { return nt == 32 ? 5 : nt == 64 ? 4 : nt == 96 ? 3 : 6; }
 __host__ __device__ constexpr int ctas_per_sm(int nt) { return nt == 128 ? 1 : 2; }
-constexpr int kGemmThreads = 192;
+// Epilogue warps: a warp reads the TMEM lane quarter warp % 4; the widest token tile has two warps per quarter, each
+// promoting half of the accumulator's columns -- at 128 rows the per-block promotion (TMEM read + one FMA per element)
+// takes as long as the block's MMAs, and the halves run on different schedulers.
+__host__ __device__ constexpr int epi_warps(int nt) { return nt == 128 ? 8 : 4; }
+__host__ __device__ constexpr int gemm_threads(int nt) { return 64 + 32 * epi_warps(nt); }
 
 struct HeadArgs {
   float* tile_val;
@@ -48,7 +52,7 @@ constexpr size_t gemm_smem_bytes(int nt) {
 }
 
 template <int NT>
-__global__ void __launch_bounds__(kGemmThreads, ctas_per_sm(NT))
+__global__ void __launch_bounds__(gemm_threads(NT), ctas_per_sm(NT))
     gemm_fp8_tcgen05_kernel(const __grid_constant__ CUtensorMap mapW, const __grid_constant__ CUtensorMap mapX,
                             const float* __restrict__ ws, const float* __restrict__ xs, float* __restrict__ out, int ld,
                             size_t split_stride, int M, int N, int N_pad, int KB, int splits, int xrows, HeadArgs head,
@@ -107,7 +111,7 @@ __global__ void __launch_bounds__(kGemmThreads, ctas_per_sm(NT))
     }
     for (int b = 0; b < BUFS; ++b) {
       mbar_init(&tmem_full[b], 1);
-      mbar_init(&tmem_empty[b], 4);
+      mbar_init(&tmem_empty[b], epi_warps(NT));
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -213,19 +217,21 @@ __global__ void __launch_bounds__(kGemmThreads, ctas_per_sm(NT))
   } else {
     // ------------------------------------------------------------------ epilogue warps (TMEM lane quarter = warp % 4)
     pdl_wait();  // the activation scales and the output planes belong to the kernels before this one
+    constexpr int EW = epi_warps(NT), NTH = NT / (EW / 4);  // columns (token rows) of the accumulator this warp promotes
     const int quarter = warp & 3;
+    const int col0 = ((warp - 2) >> 2) * NTH;
     const int row = quarter * 32 + lane;
     const int n = tile_n * kTileN + row;
-    const int m0 = tile_m * NT;
-    float acc[NT];
+    const int m0 = tile_m * NT + col0;
+    float acc[NTH];
 #pragma unroll
-    for (int j = 0; j < NT; ++j) acc[j] = 0.f;
+    for (int j = 0; j < NTH; ++j) acc[j] = 0.f;
     // The block scales run ahead of the accumulators: this row's weight scale of the next kScaleAhead K blocks sits in
     // registers, the token rows' activation scales arrive by cp.async in this warp's ring in shared memory.  Neither
     // load is then on the per-block critical path (wait for the MMA, read TMEM, promote, release the buffer).
-    float* ring = xs_ring + (warp - 2) * kScaleRing * NT;
+    float* ring = xs_ring + (warp - 2) * kScaleRing * NTH;
     auto fetch_xs = [&](int i) {
-      if (i < nslab && lane < NT / 4) ldgsts16(ring + (i % kScaleRing) * NT + lane * 4, xs + size_t(kb0 + i) * xrows + m0 + lane * 4);
+      if (i < nslab && lane < NTH / 4) ldgsts16(ring + (i % kScaleRing) * NTH + lane * 4, xs + size_t(kb0 + i) * xrows + m0 + lane * 4);
       ldgsts_commit();
     };
     float wq[kScaleAhead];
@@ -245,7 +251,7 @@ __global__ void __launch_bounds__(kGemmThreads, ctas_per_sm(NT))
       fetch_xs(i + kScaleAhead);
       ldgsts_wait<kScaleAhead>();  // the group of block i has landed (this lane's part)
       __syncwarp();                // ... and every lane's part
-      const float4* xs4 = reinterpret_cast<const float4*>(ring + (i % kScaleRing) * NT);
+      const float4* xs4 = reinterpret_cast<const float4*>(ring + (i % kScaleRing) * NTH);
       ok = mbar_wait(&tmem_full[buf], bph, abort_flag);
       if (!ok) {
         dev_fail(err_flag, kDevWaitTmemFull);
@@ -254,11 +260,11 @@ __global__ void __launch_bounds__(kGemmThreads, ctas_per_sm(NT))
       }
       tc_fence_after();
       if (timeline && detail && cta0 && i == nslab - 1 && threadIdx.x == 64) timeline[8] = global_ns();
-      const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(buf * ACCW);
+      const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(buf * ACCW + col0);
       // columns per TMEM read: the whole accumulator for the 32-row token tile, 16 at a time for the wider ones (registers)
       constexpr int CH = NT == 32 ? 32 : 16;
 #pragma unroll
-      for (int c = 0; c < NT / CH; ++c) {
+      for (int c = 0; c < NTH / CH; ++c) {
         uint32_t v[CH];
         tmem_ld<CH>(taddr + c * CH, v);
         tmem_ld_wait();
@@ -281,15 +287,15 @@ __global__ void __launch_bounds__(kGemmThreads, ctas_per_sm(NT))
       if (store && n < N) {
         float* o = out + size_t(split) * split_stride + n;
 #pragma unroll
-        for (int j = 0; j < NT; ++j)
+        for (int j = 0; j < NTH; ++j)
           if (m0 + j < M) o[size_t(m0 + j) * ld] = acc[j];
       }
       if (head.tile_val != nullptr) {
         // Per token row: the best (value, id) among this tile's 128 vocabulary rows; larger value first, equal
-        // values to the lower id, NaN skipped.  All four epilogue warps take part whatever happened before, so the
+        // values to the lower id, NaN skipped.  All epilogue warps take part whatever happened before, so the
         // named barrier below is always complete.
 #pragma unroll
-        for (int j = 0; j < NT; ++j) {
+        for (int j = 0; j < NTH; ++j) {
           float v = acc[j];
           int id = n;
           if (!ok || !(n < N) || v != v) {
@@ -302,10 +308,11 @@ __global__ void __launch_bounds__(kGemmThreads, ctas_per_sm(NT))
             const int i2 = __shfl_xor_sync(0xffffffffu, id, o);
             if (v2 > v || (v2 == v && i2 < id)) v = v2, id = i2;
           }
-          if (lane == 0) red_val[quarter * NT + j] = v, red_idx[quarter * NT + j] = id;
+          if (lane == 0) red_val[quarter * NT + col0 + j] = v, red_idx[quarter * NT + col0 + j] = id;
         }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+        asm volatile("bar.sync 1, %0;" ::"n"(EW * 32) : "memory");
         if (warp == 2) {
+          const int m0 = tile_m * NT;  // all columns of the tile
           for (int j = lane; j < NT; j += 32) {
             float v = red_val[j];
             int id = red_idx[j];
@@ -511,7 +518,7 @@ int launch_tc(const GemmCall& c, cudaStream_t stream) {
   const int splits = c.head ? 1 : W.splits;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(ceil_div(c.M, NT), splits, W.N_pad / kTileN);
-  cfg.blockDim = dim3(kGemmThreads);
+  cfg.blockDim = dim3(gemm_threads(NT));
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute at[1];
