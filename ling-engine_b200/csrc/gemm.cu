@@ -34,10 +34,10 @@ constexpr int kScaleAhead = 4;  // K blocks by which the epilogue's scale loads 
 constexpr int kScaleRing = 8;   // slots of each epilogue warp's activation-scale ring (> kScaleAhead)
 __host__ __device__ constexpr int stages_for(int nt) { return nt == 32 ? 5 : nt == 64 ? 4 : nt == 96 ? 3 : 6; }
 __host__ __device__ constexpr int ctas_per_sm(int nt) { return nt == 128 ? 1 : 2; }
-// Epilogue warps: a warp reads the TMEM lane quarter warp % 4; the widest token tile has two warps per quarter, each
+// Epilogue warps: a warp reads the TMEM lane quarter warp % 4; the two widest token tiles have two warps per quarter, each
 // promoting half of the accumulator's columns -- at 128 rows the per-block promotion (TMEM read + one FMA per element)
 // takes as long as the block's MMAs, and the halves run on different schedulers.
-__host__ __device__ constexpr int epi_warps(int nt) { return nt == 128 ? 8 : 4; }
+__host__ __device__ constexpr int epi_warps(int nt) { return nt >= 96 ? 8 : 4; }
 __host__ __device__ constexpr int gemm_threads(int nt) { return 64 + 32 * epi_warps(nt); }
 
 struct HeadArgs {
