@@ -30,8 +30,12 @@ constexpr int kABytes = kTileN * kBlockK;  // 16 KiB
 // share an SM's 512 columns for the narrow token tiles.
 __host__ __device__ constexpr int acc_bufs(int nt) { return nt == 96 ? 2 : 4; }
 __host__ __device__ constexpr int tmem_cols(int nt) { return nt == 32 ? 128 : nt == 128 ? 512 : 256; }
-constexpr int kScaleAhead = 4;  // K blocks by which the epilogue's scale loads run ahead of its accumulator reads
-constexpr int kScaleRing = 8;   // slots of each epilogue warp's activation-scale ring (> kScaleAhead)
+// K blocks by which the epilogue's scale loads run ahead of its accumulator reads, and the slots of each epilogue warp's
+// activation-scale ring (> the lookahead).  With HBM saturated by the weight stream a scale takes microseconds to arrive
+// (a K block lasts ~0.7 us): four blocks of lookahead left the epilogue waiting for scales (GEMM chain of the 27B step 5.20
+// ms, 4.99 with seven, the most the eight-slot ring allows; the narrow tile has the shared memory for sixteen slots).
+__host__ __device__ constexpr int scale_ring(int nt) { return nt == 32 ? 16 : 8; }
+__host__ __device__ constexpr int scale_ahead(int nt) { return nt == 32 ? 12 : 7; }
 __host__ __device__ constexpr int stages_for(int nt) { return nt == 32 ? 5 : nt == 64 ? 4 : nt == 96 ? 3 : 6; }
 __host__ __device__ constexpr int ctas_per_sm(int nt) { return nt == 128 ? 1 : 2; }
 // Epilogue warps: a warp reads the TMEM lane quarter warp % 4; the two widest token tiles have two warps per quarter, each
@@ -48,7 +52,7 @@ struct HeadArgs {
 };
 constexpr size_t gemm_smem_bytes(int nt) {
   return size_t(stages_for(nt)) * (kABytes + nt * kBlockK) + 1024 /* alignment slack */ + 512 /* barriers */ +
-         size_t(4) * nt * 8 /* head argmax scratch */ + size_t(4) * kScaleRing * nt * 4 /* activation-scale rings */;
+         size_t(4) * nt * 8 /* head argmax scratch */ + size_t(4) * scale_ring(nt) * nt * 4 /* activation-scale rings */;
 }
 
 template <int NT>
@@ -75,6 +79,7 @@ __global__ void __launch_bounds__(gemm_threads(NT), ctas_per_sm(NT))
   }
   if (timeline && detail && threadIdx.x == 32) t_start = global_ns();
   constexpr int STAGES = stages_for(NT);
+  constexpr int kScaleRing = scale_ring(NT), kScaleAhead = scale_ahead(NT);
   constexpr int kBBytes = NT * kBlockK;
   constexpr int kWBytes = kABytes;  // weight bytes per stage, then the activation tile
   constexpr int kStageBytes = kWBytes + kBBytes;
@@ -216,6 +221,10 @@ __global__ void __launch_bounds__(gemm_threads(NT), ctas_per_sm(NT))
     }
   } else {
     // ------------------------------------------------------------------ epilogue warps (TMEM lane quarter = warp % 4)
+    // The tile's weight scales (128 floats per K block, constant over the step) are requested into L2 before the wait:
+    // the register ring below then reads them at L2 latency however busy HBM is.
+    for (int j = threadIdx.x - 64; j < nslab * 4; j += epi_warps(NT) * 32)
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(ws + size_t(kb0 + (j >> 2)) * N_pad + tile_n * kTileN + (j & 3) * 32));
     pdl_wait();  // the activation scales and the output planes belong to the kernels before this one
     constexpr int EW = epi_warps(NT), NTH = NT / (EW / 4);  // columns (token rows) of the accumulator this warp promotes
     const int quarter = warp & 3;
@@ -262,7 +271,8 @@ __global__ void __launch_bounds__(gemm_threads(NT), ctas_per_sm(NT))
       if (timeline && detail && cta0 && i == nslab - 1 && threadIdx.x == 64) timeline[8] = global_ns();
       const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(buf * ACCW + col0);
       // columns per TMEM read: the whole accumulator for the 32-row token tile, 16 at a time for the wider ones (registers)
-      constexpr int CH = NT == 32 ? 32 : 16;
+      constexpr int CH = NTH == 32 ? 32 : 16;
+      static_assert(NTH % CH == 0, "whole TMEM reads");
 #pragma unroll
       for (int c = 0; c < NTH / CH; ++c) {
         uint32_t v[CH];
