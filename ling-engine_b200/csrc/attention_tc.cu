@@ -31,6 +31,7 @@ using namespace tc;
 constexpr int kTcRows = kAttnTcRows;  // query rows per item = the MMA's M
 constexpr int kTcKeys = 64;      // keys per operand tile
 constexpr int kTcSub = 256;      // keys per sub-chunk = S columns in TMEM
+constexpr int kTcPages = kAttnChunk / 16 + 4;  // page ids of one chunk (pages hold 16 positions or more; a tail chunk starts unaligned)
 constexpr int kTcThreads = 256;  // warps 0-3 also run the softmax (one per TMEM lane quarter)
 constexpr int kTcStage = 4;      // 16 KiB-class slots of the FP8 staging ring
 constexpr float kLog2e = 1.4426950408889634f, kLn2 = 0.6931471805599453f;
@@ -116,6 +117,8 @@ __global__ void __launch_bounds__(kTcThreads, 1)
   __shared__ int cbase[LING_B200_MAX_SEQS + 1], ibase[LING_B200_MAX_SEQS + 1];
   __shared__ volatile int failed;  // a bounded wait ran out: no further waits, no output; every thread still takes every barrier
   __shared__ int chunk_sh;         // keys per chunk of this step (attn_chunk_keys)
+  __shared__ int pages_sm[2][kTcPages];
+  int items_done = 0;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const bool worker = warp > 0;  // operand loops: warps 1-7 stage and convert, warp 0 issues (all eight run the softmax)
@@ -185,10 +188,17 @@ __global__ void __launch_bounds__(kTcThreads, 1)
     const uint8_t* vcodes = kv.codes + kv_slot_index(d, al, 1, hk, 0, 0) * D;
     const float* kscales = kv.scales + kv_slot_index(d, al, 0, hk, 0, 0);
     const float* vscales = kv.scales + kv_slot_index(d, al, 1, hk, 0, 0);
-    auto page_of = [&](int pos) {
-      const int page = table[pos >> lp];
-      return (page < 0 || page > d.pool_pages) ? 0 : page;  // an unmapped position lands in the reserved page
-    };
+    // The chunk's page ids, looked up once per item into shared memory (two sets, alternating by item, so that a thread
+    // still staging the previous item's last tile is not overtaken): a lookup per staged tile was a dependent global load
+    // ahead of every tile's copies.  The first use is behind the block barrier that opens the sub-chunk loop.
+    int* pages = pages_sm[items_done & 1];
+    const int page0 = key_base >> lp;
+    for (int i = tid; i <= ((key_base + max(key_hi, 1) - 1) >> lp) - page0 && i < kTcPages; i += kTcThreads) {
+      const int page = table[page0 + i];
+      pages[i] = (page < 0 || page > d.pool_pages) ? 0 : page;  // an unmapped position lands in the reserved page
+    }
+    ++items_done;
+    auto page_of = [&](int pos) { return pages[min((pos >> lp) - page0, kTcPages - 1)]; };
     // cp.async of one 64-key tile's codes into a staging slot: K as [key][D], V as [D][64 keys]; one commit group each.
     // A position at or past key_hi is zero-filled.
     // K: two threads per key (one page lookup each), eight 16-byte pieces of the key's D bytes per thread for D = 256
