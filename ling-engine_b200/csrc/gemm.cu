@@ -44,6 +44,16 @@ __host__ __device__ constexpr int ctas_per_sm(int nt) { return nt == 128 ? 1 : 2
 __host__ __device__ constexpr int epi_warps(int nt) { return nt >= 96 ? 8 : 4; }
 __host__ __device__ constexpr int gemm_threads(int nt) { return 64 + 32 * epi_warps(nt); }
 
+// acc[j] += v[j] * (wsc * s[j]) for four accumulator columns, as two packed fp32x2 multiplies and two packed FMAs (each
+// lane rounds like the scalar instructions, so the result is the scalar one; the promotion is instruction-bound)
+__device__ __forceinline__ void promote4(float* acc, const uint32_t* v, float wsc, const float4& s4) {
+  const float2 w2 = make_float2(wsc, wsc);
+  const float2 c01 = __fmul2_rn(w2, make_float2(s4.x, s4.y)), c23 = __fmul2_rn(w2, make_float2(s4.z, s4.w));
+  const float2 a01 = __ffma2_rn(make_float2(__uint_as_float(v[0]), __uint_as_float(v[1])), c01, make_float2(acc[0], acc[1]));
+  const float2 a23 = __ffma2_rn(make_float2(__uint_as_float(v[2]), __uint_as_float(v[3])), c23, make_float2(acc[2], acc[3]));
+  acc[0] = a01.x, acc[1] = a01.y, acc[2] = a23.x, acc[3] = a23.y;
+}
+
 struct HeadArgs {
   float* tile_val;
   int* tile_idx;
@@ -273,23 +283,39 @@ __global__ void __launch_bounds__(gemm_threads(NT), ctas_per_sm(NT))
       // columns per TMEM read: the whole accumulator for the 32-row token tile, 16 at a time for the wider ones (registers)
       constexpr int CH = NTH == 32 ? 32 : 16;
       static_assert(NTH % CH == 0, "whole TMEM reads");
+      // Where the registers allow it (the narrowest and the widest tile) the warp's whole part of the accumulator is read
+      // at once and the buffer handed back to the MMA issuer before the promotion; otherwise 16 columns at a time.
+      constexpr bool kWhole = NT == 32 || NT == 128;
+      if constexpr (kWhole) {
+        uint32_t v[NTH / CH][CH];
 #pragma unroll
-      for (int c = 0; c < NTH / CH; ++c) {
-        uint32_t v[CH];
-        tmem_ld<CH>(taddr + c * CH, v);
+        for (int c = 0; c < NTH / CH; ++c) tmem_ld<CH>(taddr + c * CH, v[c]);
         tmem_ld_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tmem_empty[buf]);
 #pragma unroll
-        for (int q = 0; q < CH / 4; ++q) {
-          const float4 s4 = xs4[c * (CH / 4) + q];
-          acc[c * CH + q * 4 + 0] = fmaf(__uint_as_float(v[q * 4 + 0]), wsc * s4.x, acc[c * CH + q * 4 + 0]);
-          acc[c * CH + q * 4 + 1] = fmaf(__uint_as_float(v[q * 4 + 1]), wsc * s4.y, acc[c * CH + q * 4 + 1]);
-          acc[c * CH + q * 4 + 2] = fmaf(__uint_as_float(v[q * 4 + 2]), wsc * s4.z, acc[c * CH + q * 4 + 2]);
-          acc[c * CH + q * 4 + 3] = fmaf(__uint_as_float(v[q * 4 + 3]), wsc * s4.w, acc[c * CH + q * 4 + 3]);
+        for (int q = 0; q < NTH / 4; ++q) {
+          const float4 s4 = xs4[q];
+          const uint32_t* vq = &v[(q * 4) / CH][(q * 4) % CH];
+          promote4(acc + q * 4, vq, wsc, s4);
         }
+      } else {
+#pragma unroll
+        for (int c = 0; c < NTH / CH; ++c) {
+          uint32_t v[CH];
+          tmem_ld<CH>(taddr + c * CH, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int q = 0; q < CH / 4; ++q) {
+            const float4 s4 = xs4[c * (CH / 4) + q];
+            promote4(acc + c * CH + q * 4, v + q * 4, wsc, s4);
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tmem_empty[buf]);
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&tmem_empty[buf]);
     }
     ldgsts_wait<0>();
     {
