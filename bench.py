@@ -14,10 +14,11 @@ KV compaction and DeltaNet commit.  Rank 0 prints ONE JSON line.
   e2e        the same through the host-buffer entry point ling_b200_verify_step (descriptor H2D copy, graph replay,
              result D2H copy inside the timed region)
   roofline   the weight GEMM (gemm_fp8_tcgen05_kernel): algorithmic bytes = FP8 codes + fp32 block scales of every
-             matrix one step streams, divided by the GEMM launches' device time measured with CUDA events around each
-             launch of one eager replay (each launch then carries its own ramp-up and an event gap: conservative), against
-             the measured HBM copy bandwidth; back_to_back = the same 257 launches with nothing between them, timed by two
-             events: the kernel's streaming rate, which dependent launch lets the step approach
+             matrix one step streams, divided by the device time of the step's 257 GEMM launches in the step's order and
+             with the step's launch attributes (dependent launch), nothing else between them, measured with two CUDA
+             events on the launching stream around five passes (average launch duration = that time / 257), against the
+             measured HBM copy bandwidth; per_launch_events = the same launches in one eager replay with an event pair
+             around EACH launch (every launch then carries its own ramp-up and an event gap: a lower bound)
   cpu_baseline the scalar C++ restatement of the same step (oracle/, test infrastructure) timed on this box's host
              cores on a bounded sample (one DeltaNet layer, one attention layer, a slice of the LM head), scaled by the
              layer counts; a reported baseline, not a target
@@ -412,8 +413,9 @@ def run_ours(args, rank, local_rank, world):
     wbytes = ctx.weight_bytes()
     alg = algorithmic_bytes(cfg, seqs, wbytes)
     n_gemm = 4 * cfg.layers + 1
-    gemm_ms = fam[0] + fam[4]  # weight GEMMs + the head GEMM with its fused argmax
-    achieved = wbytes / (gemm_ms * 1e-3) / 1e9 if gemm_ms > 0 else 0.0
+    gemm_ms = fam[0] + fam[4]  # weight GEMMs + the head GEMM with its fused argmax, an event pair around each launch
+    per_launch = wbytes / (gemm_ms * 1e-3) / 1e9 if gemm_ms > 0 else 0.0
+    achieved = wbytes / (chain_ms * 1e-3) / 1e9 if chain_ms > 0 else 0.0
     step_ms = ms / args.steps
     total_rows = dist.sum(rows)
     total_accept = dist.sum(sum(q["accept"] for q in seqs))
@@ -449,10 +451,10 @@ def run_ours(args, rank, local_rank, world):
                          # DRAM read + write bytes per launch: 1.021 x the algorithmic bytes, the ratio ncu measured on the
                          # gate|up launch (profiles/gemm_fp8_tcgen05_gateup_24x34816x5120.md), scaled to the average launch
                          "traffic": 1.021 * wbytes / n_gemm, "traffic_source": "ncu dram__bytes ratio 1.021 of one gate|up launch, scaled by bytes",
-                         "bytes_per_launch_avg": wbytes / n_gemm, "ms_per_launch_avg": gemm_ms / n_gemm,
-                         # the same launches back to back between two events (no other kernel, no event between them)
-                         "back_to_back": {"ms_per_step": chain_ms, "achieved": wbytes / (chain_ms * 1e-3) / 1e9,
-                                          "frac": wbytes / (chain_ms * 1e-3) / 1e9 / peak}},
+                         "bytes_per_launch_avg": wbytes / n_gemm, "ms_per_launch_avg": chain_ms / n_gemm,
+                         "ms_per_step": chain_ms,
+                         # the same launches with an event pair around each one (eager replay): a lower bound
+                         "per_launch_events": {"ms_per_step": gemm_ms, "achieved": per_launch, "frac": per_launch / peak}},
             "cpu_baseline": {"value": cpu_v, "unit": UNIT, "cores": cores, "kind": "port", "sample": cpu_desc,
                              "est_ms_per_step": None if cpu_est is None else cpu_est * 1e3},
             "clocks": clk,
