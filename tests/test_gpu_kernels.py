@@ -194,11 +194,15 @@ ATTN_TOL = 6e-3
 
 # impl 0: the tcgen05/TMEM kernel (the product path); impl 1: the mma.sync kernel kept as its cross-check
 @pytest.mark.parametrize("impl", [0, 1])
-@pytest.mark.parametrize("shape", ["toy", "27b"])
+@pytest.mark.parametrize("shape", ["toy", "toy64", "27b"])
 def test_tree_attention_matches_oracle(gpu, lb, lo, shape, impl):
     if shape == "toy":     # 4 q heads / 1 kv head of 64, 16-position pages
         cfg = lb.make_config(256, 704, 1, 4096, 4, 1, 64, 16, 2, 4, 64, 64, [1])
         contexts, page_tokens = (0, 3, 37, 511, 512, 1029), 16
+    elif shape == "toy64":  # 64 sequences: more work items than one wave of CTAs, so the step keeps the 512-key chunks
+        cfg = lb.make_config(256, 704, 1, 4096, 4, 1, 64, 16, 2, 4, 64, 64, [1])   # (two 256-key sub-chunks per chunk,
+        contexts = tuple(int(c) for c in np.random.default_rng(64).integers(520, 1900, 64))  # rows rescaled in between);
+        contexts, page_tokens = contexts[:60] + (0, 511, 512, 513), 16             # the other shapes run on 256-key chunks
     else:                  # 24 q heads / 4 kv heads of 256 (six query heads per kv head), 64-position pages
         cfg = lb.make_config(5120, 128, 1, 4096, 24, 4, 256, 64, 16, 48, 128, 128, [1])
         contexts, page_tokens = (1500, 17, 530), 64
