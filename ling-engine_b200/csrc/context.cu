@@ -323,7 +323,7 @@ int enqueue_step_body(ling_b200_ctx* c, int rows, int flags) {
     {
       Timed t(c, kFamStep);
       LB_TRY(gdn_commit_launch(c->sb, d, c->post, c->g, c->beta, size_t(d.rows_alloc) * d.C, size_t(d.rows_alloc) * d.HV,
-                               c->gdn_state, c->state_layer * d.n_gdn, c->state_layer, c->sm_count * 4, s));
+                               c->gdn_state, c->state_layer * d.n_gdn, c->state_layer, c->sm_count * 64, s));
     }
   }
   return LING_B200_OK;

@@ -448,6 +448,28 @@ struct GdnStage {
     o += __shfl_xor_sync(0xffffffffu, o, 16);
     return o;
   }
+  // The state update of token() alone, bit for bit (the commit needs no output): S *= decay; S += k ((v - S^T k) beta)^T.
+  __device__ __forceinline__ static void advance(float (&S)[KL], const float* qk_i, float v, float gval, float bval, int quarter) {
+    const float4* kp = reinterpret_cast<const float4*>(qk_i + 4 * SEG + quarter * SEG);
+    const float decay = __expf(gval);
+    float k[KL], part[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int i = 0; i < KL / 4; ++i) {
+      const float4 a = kp[i];
+      k[4 * i] = a.x, k[4 * i + 1] = a.y, k[4 * i + 2] = a.z, k[4 * i + 3] = a.w;
+    }
+#pragma unroll
+    for (int i = 0; i < KL; ++i) {
+      S[i] *= decay;
+      part[i & 3] = fmaf(S[i], k[i], part[i & 3]);
+    }
+    float kv = (part[0] + part[1]) + (part[2] + part[3]);
+    kv += __shfl_xor_sync(0xffffffffu, kv, 8);
+    kv += __shfl_xor_sync(0xffffffffu, kv, 16);
+    const float dlt = (v - kv) * bval;
+#pragma unroll
+    for (int i = 0; i < KL; ++i) S[i] = fmaf(dlt, k[i], S[i]);
+  }
   // The same step with one reduction round instead of two: o = S'^T q = (S d)^T q + delta (k . q), so the two dot products
   // over the decayed state run side by side and k . q (`kq`, the same for every value column) comes precomputed.  The
   // state update is the arithmetic of token() bit for bit; only o is rounded differently.
@@ -486,7 +508,7 @@ struct GdnStage {
     }
     return fmaf(dlt, kq, sq);
   }
-  static size_t smem_bytes(int Dv) { return size_t(2 * kTreeRows) * (ROW + Dv + 2) * 4; }
+  static size_t smem_bytes(int Dv, int steps = 2 * kTreeRows) { return size_t(steps) * (ROW + Dv + 2) * 4; }
 };
 
 // The verify's recurrence over every sequence's tree (src/core/kernels.cu:455-477): a work item is (sequence, DeltaNet
@@ -828,9 +850,16 @@ __global__ void __launch_bounds__(512)
 }
 
 // Engine::commit (src/core/speculate.cpp:516-529), the recurrence half: the accepted rows path[0..n) replayed from the
-// session's state over their saved conv outputs, the state written back.  Item = (sequence, layer, value head).
+// session's state over their saved conv outputs, the state written back.  Item = (sequence, layer, value head, 32 value
+// columns).  The commit reads and writes every session state once (151 MB each way per sequence of the 27B model), so it
+// is a bandwidth problem: the path's inputs are staged kCommitRows rows at a time, which keeps the block's shared memory
+// small enough for five blocks per SM (the registers' limit), and the grid has a block per item (two blocks per SM with the
+// whole path staged and a strided grid: 200 us per step; this form 130).  What bounds an item is its chain of dependent
+// loads (the path, then the path's rows) and its steps, not the tile's bytes: a form that moved the 64 KB tiles of whole
+// heads by bulk copies through two shared-memory buffers, one persistent block per SM, measured the same.
+constexpr int kCommitRows = 16;
 template <int DK>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, 5)
     gdn_commit_kernel(const float* __restrict__ post, const float* __restrict__ g, const float* __restrict__ beta,
                       size_t post_layer_stride, size_t g_layer_stride, StepBuffers sb, int Hk, int HV, int Dv, int n_gdn,
                       float* __restrict__ state, size_t slot_stride, size_t layer_stride) {
@@ -839,9 +868,9 @@ __global__ void __launch_bounds__(128)
   constexpr int KL = St::KL;
   extern __shared__ __align__(16) float gsm[];
   float* qk = gsm;
-  float* vv = qk + size_t(2 * kTreeRows) * St::ROW;
-  float* gb = vv + size_t(2 * kTreeRows) * Dv;
-  __shared__ int rows[2 * kTreeRows];
+  float* vv = qk + size_t(kCommitRows) * St::ROW;
+  float* gb = vv + size_t(kCommitRows) * Dv;
+  __shared__ int rows[kTreeRows];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, quarter = lane >> 3;
   const int nseq = *sb.n_seqs;
   const int C = 2 * Hk * DK + HV * Dv, groups = Dv / kGdnCols;
@@ -853,19 +882,22 @@ __global__ void __launch_bounds__(128)
     const ling_b200_seq_result* R = sb.results + s;
     if (R->status != 0) continue;  // block-uniform
     const size_t r0 = size_t(sb.row0[s]);
-    const int n = R->n_path;
+    const int n = min(R->n_path, kTreeRows);
     __syncthreads();
     for (int i = threadIdx.x; i < n; i += blockDim.x) rows[i] = R->path[i];
     float* st = state + size_t(sb.seqs[s].slot) * slot_stride + size_t(gl) * layer_stride + size_t(hv) * DK * Dv;
     float S[KL];
 #pragma unroll
     for (int i = 0; i < KL; ++i) S[i] = st[size_t(quarter * KL + i) * Dv + col];
-    __syncthreads();
-    St::load(post + size_t(gl) * post_layer_stride, g + size_t(gl) * g_layer_stride, beta + size_t(gl) * g_layer_stride, C, Hk, HV,
-             Dv, h, hv, r0, rows, n, qk, vv, gb);
-    __syncthreads();
-    for (int i = 0; i < n; ++i)
-      St::token(S, qk + size_t(i) * St::ROW, vv[size_t(i) * Dv + col], gb[2 * i], gb[2 * i + 1], quarter, true);
+    for (int c0 = 0; c0 < n; c0 += kCommitRows) {
+      const int cn = min(kCommitRows, n - c0);
+      __syncthreads();  // the path is staged / the previous rows have been consumed
+      St::load(post + size_t(gl) * post_layer_stride, g + size_t(gl) * g_layer_stride, beta + size_t(gl) * g_layer_stride, C, Hk,
+               HV, Dv, h, hv, r0, rows + c0, cn, qk, vv, gb);
+      __syncthreads();
+      for (int i = 0; i < cn; ++i)
+        St::advance(S, qk + size_t(i) * St::ROW, vv[size_t(i) * Dv + col], gb[2 * i], gb[2 * i + 1], quarter);
+    }
 #pragma unroll
     for (int i = 0; i < KL; ++i) st[size_t(quarter * KL + i) * Dv + col] = S[i];
   }
@@ -1793,8 +1825,8 @@ int kernels_init() {
   if (const int r = attention_tc_init()) return r;
   LB_CUDA(cudaFuncSetAttribute(gdn_tree_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(GdnStage<128>::smem_bytes(128))));
   LB_CUDA(cudaFuncSetAttribute(gdn_tree_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(GdnStage<64>::smem_bytes(128))));
-  LB_CUDA(cudaFuncSetAttribute(gdn_commit_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(GdnStage<128>::smem_bytes(128))));
-  LB_CUDA(cudaFuncSetAttribute(gdn_commit_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(GdnStage<64>::smem_bytes(128))));
+  LB_CUDA(cudaFuncSetAttribute(gdn_commit_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(GdnStage<128>::smem_bytes(128, kCommitRows))));
+  LB_CUDA(cudaFuncSetAttribute(gdn_commit_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(GdnStage<64>::smem_bytes(128, kCommitRows))));
   LB_CUDA(cudaFuncSetAttribute(gdn_fused_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(GdnFused<128>::smem_floats() * 4)));
   LB_CUDA(cudaFuncSetAttribute(gdn_fused_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(GdnFused<64>::smem_floats() * 4)));
   LB_CUDA(cudaFuncSetAttribute(attention_kernel<256, 6>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(attn_smem<256, 6>())));
@@ -1887,9 +1919,9 @@ int gdn_commit_launch(const StepBuffers& sb, const ModelDims& d, const float* po
                       size_t state_layer_stride, int grid, cudaStream_t s) {
   if (d.n_gdn == 0) return LING_B200_OK;
   if (d.Dk == 128)
-    LB_CUDA(launch_kernel(gdn_commit_kernel<128>, dim3(grid), dim3(128), GdnStage<128>::smem_bytes(d.Dv), s, post, g, beta, post_layer_stride, g_layer_stride, sb, d.Hk, d.HV, d.Dv, d.n_gdn, state, state_slot_stride, state_layer_stride));
+    LB_CUDA(launch_kernel(gdn_commit_kernel<128>, dim3(grid), dim3(128), GdnStage<128>::smem_bytes(d.Dv, kCommitRows), s, post, g, beta, post_layer_stride, g_layer_stride, sb, d.Hk, d.HV, d.Dv, d.n_gdn, state, state_slot_stride, state_layer_stride));
   else if (d.Dk == 64)
-    LB_CUDA(launch_kernel(gdn_commit_kernel<64>, dim3(grid), dim3(128), GdnStage<64>::smem_bytes(d.Dv), s, post, g, beta, post_layer_stride, g_layer_stride, sb, d.Hk, d.HV, d.Dv, d.n_gdn, state, state_slot_stride, state_layer_stride));
+    LB_CUDA(launch_kernel(gdn_commit_kernel<64>, dim3(grid), dim3(128), GdnStage<64>::smem_bytes(d.Dv, kCommitRows), s, post, g, beta, post_layer_stride, g_layer_stride, sb, d.Hk, d.HV, d.Dv, d.n_gdn, state, state_slot_stride, state_layer_stride));
   else {
     set_error("DeltaNet key dim must be 64 or 128");
     return LING_B200_ERR_UNSUPPORTED;
