@@ -619,6 +619,7 @@ int ling_b200_create(const ling_b200_model_config* cfg, const ling_b200_options*
   LB_TRY(c->alloc(&sb.cache_slot, size_t(d.rows_alloc)));
   LB_TRY(c->alloc(&sb.anc, size_t(d.rows_alloc)));
   LB_TRY(c->alloc(&sb.trees, ms));
+  LB_TRY(c->alloc(&sb.gdn_aux, ms));
   LB_TRY(c->alloc(&sb.argmax_id, size_t(d.rows_alloc)));
   LB_TRY(c->alloc(&sb.argmax_val, size_t(d.rows_alloc)));
   LB_TRY(c->alloc(&sb.results, ms));

@@ -186,6 +186,23 @@ __global__ void __launch_bounds__(32) pack_kernel(StepBuffers sb, ModelDims d) {
   }
   T.ngdn = ngdn;
   if (bad || written != (n == 32 ? 0xffffffffu : ((1u << n) - 1u))) dev_fail(sb.err, kDevBadTree);
+  // what the fused DeltaNet kernel needs per path and per row (GdnAux)
+  GdnAux& A = sb.gdn_aux[s];
+  for (int p = 0; p < ngdn; ++p) {
+    uint32_t seen = 0, wr = 0;
+    int np = 0;
+    for (int i = 0; i < T.gdn_len[p]; ++i) {
+      const int st = T.gdn_step[p][i], t = st & 0xff;
+      if (!((seen >> t) & 1u)) seen |= 1u << t, A.prow[p][np++] = uint8_t(t);
+      if (st & kWrite) wr |= 1u << t;
+    }
+    A.np[p] = np, A.wmask[p] = wr;
+  }
+  for (int t = 0; t < n && !bad; ++t)
+    for (int j = 0; j < 3; ++j) {
+      const int dj = dep[t] - 3 + j;
+      A.tap[t][j] = static_cast<signed char>(dj >= 0 ? T.path[T.var[t]][dj] : dj);
+    }
 }
 
 // ---------------------------------------------------------------------------------------------- norms
@@ -656,9 +673,8 @@ __global__ void __launch_bounds__(512)
   pdl_sync();
   if (stamp) stamps[1] = gtime_ns();
   __shared__ int pbase[LING_B200_MAX_SEQS + 1];
-  __shared__ int steps[2 * kTreeRows], taprow[3 * kTreeRows], prow[kTreeRows], pinfo[2];
+  __shared__ int steps[2 * kTreeRows], taprow[3 * kTreeRows], prow[kTreeRows];
   __shared__ float kqs[2 * kTreeRows];  // k^ . q^ per (head in block, row)
-  __shared__ int tdepth[kTreeRows], tvar[kTreeRows], tpath[LING_B200_MAX_TREE_VARIANTS * kTreeRows];  // the tree, staged once per item
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, quarter = lane >> 3;
   const int nseq = *sb.n_seqs;
   if (tid == 0) {
@@ -684,10 +700,13 @@ __global__ void __launch_bounds__(512)
     // of its value column), the raw inputs of every row of the sequence for the block's channels (no dependence on the
     // path: one round trip less than staging the path's rows only) and the gates -- and only then stored to shared
     // memory: a load behind a dependent store would cost a further round trip each time.
-    static_assert(2 * kTreeRows <= 512 && LING_B200_MAX_TREE_VARIANTS * kTreeRows == 1024 && NH * kTreeRows <= 512, "elements per thread");
+    static_assert(3 * kTreeRows <= 512 && NH * kTreeRows <= 512, "one element per thread");
+    const GdnAux* aux = sb.gdn_aux + s;
+    const int np = aux->np[pth];
+    const uint32_t wmask = aux->wmask[pth];
     const int v_step = tid < len ? td->gdn_step[pth][tid] : 0;
-    const int v_depth = tid < n ? td->depth[tid] : 0, v_var = tid < n ? td->var[tid] : 0;
-    const int v_path0 = td->path[tid / kTreeRows][tid % kTreeRows], v_path1 = td->path[(tid + 512) / kTreeRows][tid % kTreeRows];
+    const int v_prow = tid < kTreeRows ? aux->prow[pth][tid] : 0;
+    const int v_tap = tid < 3 * n ? aux->tap[tid / 3][tid % 3] : 0;
     const int colb = warp * 8 + (lane & 7);  // column inside the block's 128
     const int hb_t = colb / DK, hv_t = qb * NH + hb_t, col = colb % DK;
     if (item != int(blockIdx.x) || slot != spec_slot) load_conv_consts(qb, slot);
@@ -713,8 +732,8 @@ __global__ void __launch_bounds__(512)
         }
       }
       if (tid < len) steps[tid] = v_step;
-      if (tid < n) tdepth[tid] = v_depth, tvar[tid] = v_var;
-      tpath[tid] = v_path0, tpath[tid + 512] = v_path1;
+      if (tid < kTreeRows) prow[tid] = v_prow;
+      if (tid < 3 * n) taprow[tid] = v_tap;
       if (tid < NH * n) {
         const int hb = tid / n, t = tid % n;
         gb[(hb * kTreeRows + t) * 2] = v_g, gb[(hb * kTreeRows + t) * 2 + 1] = v_beta;
@@ -726,28 +745,8 @@ __global__ void __launch_bounds__(512)
       }
     }
     __syncthreads();
-    // the distinct rows of this path (a row's taps are its ancestors, which the path contains) and those it writes: only
-    // these are convolved and normalized here; a row's `pre` / `post` are stored by the path that writes the row
-    if (tid == 0) {
-      uint32_t seen = 0, wr = 0;
-      int np_ = 0;
-      for (int i = 0; i < len; ++i) {
-        const int t = steps[i] & 0xff;
-        if (!((seen >> t) & 1u)) seen |= 1u << t, prow[np_++] = t;
-        if (steps[i] & kWrite) wr |= 1u << t;
-      }
-      pinfo[0] = np_, pinfo[1] = int(wr);
-    }
-    __syncthreads();
-    const int np = pinfo[0];
-    const uint32_t wmask = uint32_t(pinfo[1]);
-    // taps of row t: its ancestors at depths d-3 .. d-1 (src/core/kernels.cu:365-383), or -1, -2, -3 for the session's
-    // window entries 2, 1, 0 before depth 0
-    for (int i = tid; i < np * 3; i += blockDim.x) {
-      const int t = prow[i / 3], j = i % 3, dj = tdepth[t] - 3 + j;
-      taprow[t * 3 + j] = dj >= 0 ? tpath[tvar[t] * kTreeRows + dj] : dj;
-    }
-    __syncthreads();
+    // (only the path's distinct rows -- prow, np of them -- are convolved and normalized here; a row's `pre` / `post` are
+    // stored by the path that writes the row: wmask)
     if (stamp && item == blockIdx.x) stamps[2] = gtime_ns();
     // ---- conv + SiLU: a thread owns a channel (its taps, window and destinations stay in registers) and walks a quarter
     // of the path's rows: 4 x 384 slots = three per thread

@@ -23,6 +23,17 @@ struct SeqDev {
 
 // The step's device-resident description.  Host-written parts arrive with one copy from pinned memory; the packed
 // arrays are built by pack_kernel.
+// Per sequence, built by pack_kernel beside the tree description for the fused DeltaNet kernel: of every DeltaNet path
+// its distinct rows in step order (a row's conv taps are its ancestors, which the path contains), their count and the
+// rows the path writes; of every row its three conv taps (the ancestors at depths d-3 .. d-1, or -3 .. -1 for the
+// session's window entries 0 .. 2 before depth 0; src/core/kernels.cu:365-383).
+struct GdnAux {
+  int np[LING_B200_MAX_TREE_VARIANTS];
+  uint32_t wmask[LING_B200_MAX_TREE_VARIANTS];
+  uint8_t prow[LING_B200_MAX_TREE_VARIANTS][LING_B200_MAX_TREE_ROWS];
+  signed char tap[LING_B200_MAX_TREE_ROWS][4];
+};
+
 struct StepBuffers {
   // host-written (one contiguous block, see Context::stage)
   int* n_seqs = nullptr;      // [1]
@@ -41,6 +52,7 @@ struct StepBuffers {
   int* cache_slot = nullptr;  // [rows]
   uint32_t* anc = nullptr;    // [rows]
   ling_b200_tree_desc* trees = nullptr;  // [max_seqs]
+  GdnAux* gdn_aux = nullptr;             // [max_seqs]
   // results
   int* argmax_id = nullptr;   // [rows]
   float* argmax_val = nullptr;
