@@ -93,7 +93,7 @@ struct TcSmem {
 template <int D, int G>
 __global__ void __launch_bounds__(kTcThreads, 1)
     attention_tc_kernel(const __half* __restrict__ q, StepBuffers sb, ModelDims d, int al, KvPoolDev kv, float* __restrict__ part_o,
-                        float* __restrict__ part_ml, int chunk_slots, unsigned long long* stamps) {
+                        float* __restrict__ part_ml, int chunk_slots, PrefetchPlan plan, unsigned long long* stamps) {
   // stamps (debugging aid, or nullptr): %globaltimer of block 0's first item: [0] entry, [1] set-up done, then per sub-chunk
   // [2 + 4 sub ..]: Q loaded, S complete, softmax done, O issued; [10] item stored
   const bool stamp = stamps != nullptr && blockIdx.x == 0 && threadIdx.x == 0;
@@ -164,6 +164,8 @@ __global__ void __launch_bounds__(kTcThreads, 1)
     tc_fence_after();
   };
 
+  // a CTA without an item asks the weights of the GEMMs behind this kernel into L2 (HBM is nearly idle while it runs)
+  if (int(blockIdx.x) >= ibase[nseq]) prefetch_plan_share(plan, int(blockIdx.x) - ibase[nseq], int(gridDim.x) - ibase[nseq]);
   for (int item = blockIdx.x; item < ibase[nseq]; item += gridDim.x) {
     int s = 0;
     while (ibase[s + 1] <= item) ++s;
@@ -510,9 +512,9 @@ __global__ void __launch_bounds__(kTcThreads, 1)
 
 template <int D, int G>
 int launch_tc_attention(const __half* q, const StepBuffers& sb, const ModelDims& d, int al, const KvPoolDev& kv, float* part_o,
-                        float* part_ml, int chunk_slots, int grid, unsigned long long* stamps, cudaStream_t s) {
+                        float* part_ml, int chunk_slots, int grid, const PrefetchPlan& plan, unsigned long long* stamps, cudaStream_t s) {
   LB_CUDA(launch_kernel(attention_tc_kernel<D, G>, dim3(grid), dim3(kTcThreads), TcSmem<D>::kBytes, s, q, sb, d, al, kv, part_o, part_ml,
-                        chunk_slots, stamps));
+                        chunk_slots, plan, stamps));
   LB_LAUNCH("attention_tc_kernel");
   return LING_B200_OK;
 }
@@ -533,12 +535,12 @@ bool attention_tc_supported(const ModelDims& d) {
 }
 
 int attention_tc_launch(const __half* q, const StepBuffers& sb, const ModelDims& d, int al, const KvPoolDev& kv, float* part_o,
-                        float* part_ml, int chunk_slots, int grid, unsigned long long* stamps, cudaStream_t s) {
+                        float* part_ml, int chunk_slots, int grid, const PrefetchPlan& plan, unsigned long long* stamps, cudaStream_t s) {
   const int G = d.Hq / d.Hkv;
-  if (d.D == 256 && G == 6) return launch_tc_attention<256, 6>(q, sb, d, al, kv, part_o, part_ml, chunk_slots, grid, stamps, s);
-  if (d.D == 64 && G == 4) return launch_tc_attention<64, 4>(q, sb, d, al, kv, part_o, part_ml, chunk_slots, grid, stamps, s);
-  if (d.D == 128 && G == 4) return launch_tc_attention<128, 4>(q, sb, d, al, kv, part_o, part_ml, chunk_slots, grid, stamps, s);
-  if (d.D == 128 && G == 8) return launch_tc_attention<128, 8>(q, sb, d, al, kv, part_o, part_ml, chunk_slots, grid, stamps, s);
+  if (d.D == 256 && G == 6) return launch_tc_attention<256, 6>(q, sb, d, al, kv, part_o, part_ml, chunk_slots, grid, plan, stamps, s);
+  if (d.D == 64 && G == 4) return launch_tc_attention<64, 4>(q, sb, d, al, kv, part_o, part_ml, chunk_slots, grid, plan, stamps, s);
+  if (d.D == 128 && G == 4) return launch_tc_attention<128, 4>(q, sb, d, al, kv, part_o, part_ml, chunk_slots, grid, plan, stamps, s);
+  if (d.D == 128 && G == 8) return launch_tc_attention<128, 8>(q, sb, d, al, kv, part_o, part_ml, chunk_slots, grid, plan, stamps, s);
   set_error("attention: unsupported (head_dim, q heads per kv head); built: (256,6), (64,4), (128,4), (128,8)");
   return LING_B200_ERR_UNSUPPORTED;
 }

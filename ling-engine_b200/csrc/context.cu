@@ -178,6 +178,10 @@ int run_gemm(ling_b200_ctx* c, const Fp8Matrix& w, const Fp8Acts& x, int which, 
 
 // The whole step on the context's stream.  rows = the capacity class (grids and GEMM extents); the kernels read the
 // real extents from device memory.  Order of the forward pass: src/core/engine.cpp:1288-1745 (verify branch).
+int env_int(const char* name, int dflt) {
+  const char* e = std::getenv(name);
+  return e ? std::atoi(e) : dflt;
+}
 int enqueue_step_body(ling_b200_ctx* c, int rows, int flags);
 int enqueue_step(ling_b200_ctx* c, int rows, int flags) {
   set_pdl(c->opt.pdl != 0);
@@ -219,8 +223,18 @@ int enqueue_step_body(ling_b200_ctx* c, int rows, int flags) {
       {
         Timed t(c, kFamAttn);
         // tcgen05/TMEM attention; the mma.sync form stays as the cross-check implementation (gemm_impl = 1)
+        PrefetchPlan plan;
+        if (tc && c->opt.pdl) {
+          static const int o_mb = env_int("LING_B200_PFA_O_MB", 32), gu_mb = env_int("LING_B200_PFA_GU_MB", 48);
+          static const int down_mb = env_int("LING_B200_PFA_DOWN_MB", 0), delay = env_int("LING_B200_PFA_DELAY_NS", 3000);
+          auto range = [&](int i, const Fp8Matrix& w, int mb) {
+            plan.p[i] = w.codes, plan.bytes[i] = std::min<size_t>(size_t(mb) << 20, size_t(w.N_pad) * w.K_pad);
+          };
+          range(0, L.o, o_mb), range(1, L.gu, gu_mb), range(2, L.down, down_mb);
+          plan.delay_ns = delay;
+        }
         if (tc)
-          LB_TRY(attention_tc_launch(c->qh, c->sb, d, al, c->kv, c->part_o, c->part_ml, c->chunk_slots, c->sm_count,
+          LB_TRY(attention_tc_launch(c->qh, c->sb, d, al, c->kv, c->part_o, c->part_ml, c->chunk_slots, c->sm_count, plan,
                                      c->timeline && al == 0 ? c->timeline + 4 * size_t(ling_b200_ctx::kTimelineLaunches - 16) : nullptr, s));
         else
           LB_TRY(attention_launch(c->qh, c->sb, d, al, c->kv, c->part_o, c->part_ml, c->chunk_slots, c->sm_count * 2, s));
@@ -249,9 +263,24 @@ int enqueue_step_body(ling_b200_ctx* c, int rows, int flags) {
       const Planes p0 = planes_of(c, 0, L.in);
       if (gdn_fused_supported(d)) {
         Timed t(c, kFamGdn);
+        PrefetchPlan plan;
+        if (c->opt.pdl) {
+          static const int out_mb = env_int("LING_B200_PF_OUT_MB", 0), gu_mb = env_int("LING_B200_PF_GU_MB", 48);
+          static const int down_mb = env_int("LING_B200_PF_DOWN_MB", 0), in_mb = env_int("LING_B200_PF_IN_MB", 0);
+          static const int delay = env_int("LING_B200_PF_DELAY_NS", 3000);
+          auto range = [&](int i, const Fp8Matrix& w, int mb) {
+            plan.p[i] = w.codes, plan.bytes[i] = std::min<size_t>(size_t(mb) << 20, size_t(w.N_pad) * w.K_pad);
+          };
+          range(0, L.out, out_mb), range(1, L.gu, gu_mb), range(2, L.down, down_mb);
+          if (l + 1 < c->cfg.layers) {
+            const LayerW& N = c->layers[l + 1];
+            range(3, N.full ? N.qkv : N.in, in_mb);
+          }
+          plan.delay_ns = delay;
+        }
         LB_TRY(gdn_fused_launch(p0, c->sb, d, L.conv, c->conv_state + size_t(gl) * c->conv_layer, c->conv_layer * d.n_gdn, g, beta,
                                 c->gdn_state + size_t(gl) * c->state_layer, c->state_layer * d.n_gdn, L.lin_norm, c->qout(c->xq_v),
-                                pre, post, c->opt.sessions, c->sm_count,
+                                pre, post, c->opt.sessions, c->sm_count, plan,
                                 c->timeline && gl == 0 ? c->timeline + 4 * size_t(ling_b200_ctx::kTimelineLaunches - 4) : nullptr, s));
       } else {
         {
@@ -1157,7 +1186,7 @@ int ling_b200_attention_host(ling_b200_ctx* c, const ling_b200_seq_step* seqs, i
   LB_TRY(f32_to_half_launch(c->upload, c->qh, n, c->stream));
   const bool tc = c->opt.gemm_impl == 0 && attention_tc_supported(d);
   if (tc)
-    LB_TRY(attention_tc_launch(c->qh, c->sb, d, attn_layer, c->kv, c->part_o, c->part_ml, c->chunk_slots, c->sm_count, nullptr, c->stream));
+    LB_TRY(attention_tc_launch(c->qh, c->sb, d, attn_layer, c->kv, c->part_o, c->part_ml, c->chunk_slots, c->sm_count, PrefetchPlan(), nullptr, c->stream));
   else
     LB_TRY(attention_launch(c->qh, c->sb, d, attn_layer, c->kv, c->part_o, c->part_ml, c->chunk_slots, c->sm_count * 2, c->stream));
   Planes none;

@@ -613,7 +613,7 @@ __global__ void __launch_bounds__(512)
                      const float* __restrict__ conv_state, size_t conv_slot_stride, const float* __restrict__ g,
                      const float* __restrict__ beta, const float* __restrict__ state, size_t state_slot_stride,
                      const __nv_bfloat16* __restrict__ norm_w, QuantOut q, float* __restrict__ pre, float* __restrict__ post,
-                     int n_slots, unsigned long long* stamps) {
+                     int n_slots, PrefetchPlan plan, unsigned long long* stamps) {
   const bool stamp = stamps != nullptr && blockIdx.x == 0 && threadIdx.x == 0;
   if (stamp) stamps[0] = gtime_ns();
   using F = GdnFused<DK>;
@@ -688,6 +688,13 @@ __global__ void __launch_bounds__(512)
   __syncthreads();
   const int C = d.C, Hk = d.Hk, HV = d.HV, ratio = HV / Hk, QB = HV / NH;  // QB: 128-column blocks of the value width
   const int total = pbase[nseq] * QB;
+  if (int(blockIdx.x) >= total) {
+    // A CTA without an item (a step of few sequences leaves a third of the SMs idle here) asks the weights of the GEMMs
+    // behind this kernel into L2: HBM has nothing else to do while the recurrence runs.  Bulk prefetches of 4 KB, this
+    // CTA's share of each range, after the working CTAs' first loads have gone out.
+    prefetch_plan_share(plan, int(blockIdx.x) - total, int(gridDim.x) - total);
+    return;
+  }
   for (int item = blockIdx.x; item < total; item += gridDim.x) {
     const int pg = item / QB, qb = item % QB;
     int s = 0;
@@ -1781,17 +1788,17 @@ bool gdn_fused_supported(const ModelDims& d) {
 int gdn_fused_launch(const Planes& in, const StepBuffers& sb, const ModelDims& d, const __nv_bfloat16* convw, const float* conv_state,
                      size_t conv_slot_stride, const float* g, const float* beta, const float* state, size_t state_slot_stride,
                      const __nv_bfloat16* norm_w, const QuantOut& q, float* pre, float* post, int n_slots, int grid,
-                     unsigned long long* stamps, cudaStream_t s) {
+                     const PrefetchPlan& plan, unsigned long long* stamps, cudaStream_t s) {
   if (!gdn_fused_supported(d)) {
     set_error("fused DeltaNet kernel: key dim = value dim = 64 or 128 expected");
     return LING_B200_ERR_UNSUPPORTED;
   }
   if (d.Dk == 128)
     LB_CUDA(launch_kernel(gdn_fused_kernel<128>, dim3(grid), dim3(512), GdnFused<128>::smem_floats() * 4, s, in, sb, d, convw, conv_state,
-                          conv_slot_stride, g, beta, state, state_slot_stride, norm_w, q, pre, post, n_slots, stamps));
+                          conv_slot_stride, g, beta, state, state_slot_stride, norm_w, q, pre, post, n_slots, plan, stamps));
   else
     LB_CUDA(launch_kernel(gdn_fused_kernel<64>, dim3(grid), dim3(512), GdnFused<64>::smem_floats() * 4, s, in, sb, d, convw, conv_state,
-                          conv_slot_stride, g, beta, state, state_slot_stride, norm_w, q, pre, post, n_slots, stamps));
+                          conv_slot_stride, g, beta, state, state_slot_stride, norm_w, q, pre, post, n_slots, plan, stamps));
   LB_LAUNCH("gdn_fused_kernel");
   return LING_B200_OK;
 }

@@ -34,6 +34,16 @@ struct GdnAux {
   signed char tap[LING_B200_MAX_TREE_ROWS][4];
 };
 
+// Weights that a long glue kernel's idle CTAs ask into L2 for the GEMMs behind it (HBM is idle while such a kernel runs):
+// up to four byte ranges, requested `delay_ns` after the kernel's dependency wait so that the kernel's own first loads
+// are not queued behind them.  Ranges are 16-byte aligned; bytes = 0 skips a range.
+struct PrefetchPlan {
+  static constexpr int kRanges = 4;
+  const void* p[kRanges] = {nullptr, nullptr, nullptr, nullptr};
+  unsigned long long bytes[kRanges] = {0, 0, 0, 0};
+  int delay_ns = 0;
+};
+
 struct StepBuffers {
   // host-written (one contiguous block, see Context::stage)
   int* n_seqs = nullptr;      // [1]
@@ -61,6 +71,16 @@ struct StepBuffers {
 };
 
 #ifdef __CUDACC__
+// What a CTA without work does with a PrefetchPlan: its share (CTA `me` of `idle`) of every range, as 4 KB bulk prefetches.
+__device__ __forceinline__ void prefetch_plan_share(const PrefetchPlan& plan, int me, int idle) {
+  if (plan.delay_ns > 0) asm volatile("nanosleep.u32 %0;" ::"r"(unsigned(plan.delay_ns)));
+  for (int r = 0; r < PrefetchPlan::kRanges; ++r) {
+    const unsigned long long pieces = plan.bytes[r] / 4096ull;
+    const char* base = static_cast<const char*>(plan.p[r]);
+    for (unsigned long long i = (unsigned long long)me * blockDim.x + threadIdx.x; i < pieces; i += (unsigned long long)idle * blockDim.x)
+      asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(base + i * 4096ull), "r"(4096u) : "memory");
+  }
+}
 // Keys per flash-decoding chunk of the staged step.  A step with few sequences has too few (sequence, kv head, 512-key
 // chunk) items to occupy the SMs, and its attention time is one item's latency: when the items of 256-key chunks still fit
 // one wave of `budget` CTAs the step uses those.  The attention kernel (tile_rows query rows per item) and the combine
@@ -141,7 +161,7 @@ bool gdn_fused_supported(const ModelDims& d);
 int gdn_fused_launch(const Planes& in, const StepBuffers& sb, const ModelDims& d, const __nv_bfloat16* convw, const float* conv_state,
                      size_t conv_slot_stride, const float* g, const float* beta, const float* state, size_t state_slot_stride,
                      const __nv_bfloat16* norm_w, const QuantOut& q, float* pre, float* post, int n_slots, int grid,
-                     unsigned long long* stamps, cudaStream_t s);  // n_slots: sessions the state holds; stamps: seven %globaltimer values of block 0's first item (debugging aid) or nullptr
+                     const PrefetchPlan& plan, unsigned long long* stamps, cudaStream_t s);  // n_slots: sessions the state holds; stamps: seven %globaltimer values of block 0's first item (debugging aid) or nullptr
 int gated_norm_quant_launch(const float* core, const Planes& z, int z_col, const __nv_bfloat16* w, const QuantOut& q,
                             const int* n_rows, int rows_grid, int HV, int Dv, float eps, cudaStream_t s);
 int attn_prepare_launch(const Planes& qkv, const StepBuffers& sb, const ModelDims& d, int al, const __nv_bfloat16* q_norm,
@@ -153,7 +173,8 @@ int attention_launch(const __half* q, const StepBuffers& sb, const ModelDims& d,
 int attention_tc_init();
 bool attention_tc_supported(const ModelDims& d);
 int attention_tc_launch(const __half* q, const StepBuffers& sb, const ModelDims& d, int al, const KvPoolDev& kv, float* part_o,
-                        float* part_ml, int chunk_slots, int grid, unsigned long long* stamps, cudaStream_t s);  // stamps: see the kernel
+                        float* part_ml, int chunk_slots, int grid, const PrefetchPlan& plan, unsigned long long* stamps,
+                        cudaStream_t s);  // plan: what CTAs without an item prefetch; stamps: see the kernel
 // max_chunks: the most flash-decoding chunks one sequence can have (context capacity / kAttnChunkShort + 2);
 // tile_rows, budget: the query rows per item and the grid of the attention kernel whose partials are merged (attn_chunk_keys)
 int attn_combine_launch(const float* part_o, const float* part_ml, const Planes& qkv, const StepBuffers& sb,
