@@ -75,8 +75,9 @@ void ling_b200_destroy(ling_b200_ctx* ctx);
 const char* ling_b200_last_error(void);
 /* Library/ABI version, and whether the CUDA kernels are present (always 1: there is no CPU path). */
 int ling_b200_abi_version(void);
-/* kernels::set_pdl / pdl_enabled (src/core/kernels.cuh:82-83): programmatic dependent launch for launches made outside a
- * context's step (the kernel-level entry points below); process-wide.  A context's step follows its own options.pdl. */
+/* kernels::set_pdl / pdl_enabled (src/core/kernels.cuh:82-83): programmatic dependent launch for launches that the calling
+ * host thread makes outside a context's step (the kernel-level entry points below).  A context's step follows its own
+ * options.pdl and leaves this setting as it found it. */
 void ling_b200_set_pdl(int on);
 int ling_b200_pdl_enabled(void);
 
@@ -253,15 +254,6 @@ int ling_b200_sync(ling_b200_ctx* ctx);
 int ling_b200_gemm_fp8_host(int device, int impl, int splits, const float* x, const float* w, float* y, int M, int N, int K);
 /* The same GEMM timed on the device with resident operands: ms per launch over `iters` launches. */
 int ling_b200_gemm_fp8_bench(int device, int impl, int splits, int M, int N, int K, int iters, float* ms_per_launch);
-/* The GEMM's response to weights already in L2: per iteration [flush 1: write 256 MiB, flush 2: read 256 MiB] -> ask for the first `slabs` K
- * blocks of every CTA's range to be brought into L2 (mode 0: TMA prefetch, 1: plain loads; slabs 0: nothing) -> a
- * one-thread kernel that spins delay_us -> the GEMM, timed alone with events.  Mean ms of the GEMM over iters.
- * stamps16 (or NULL): %globaltimer stamps of the last iteration's GEMM: [0] first CTA's start, [3] last CTA's end,
- * [4..9] CTA (0,0,0): start, set-up done, first stage landed, last MMA issued, last accumulator ready, end;
- * [10] max over CTAs of first-stage latency, [11] max CTA lifetime, [12] last CTA's start, [13] first CTA's end. */
-int ling_b200_gemm_prefetch_bench(int device, int M, int N, int K, int slabs, int mode, int delay_us, int flush, int iters,
-                                  float* ms_per_launch, unsigned long long* stamps16);
-
 /* No counterpart in the reference.  The same block-scaled FP8 GEMM for hosts that must not allocate device memory on
  * this path: a serving loop that gave the whole device to its own arena at start-up, a real-time thread for which an
  * allocation's implicit synchronization is not acceptable, a sandboxed plugin that receives buffers but may not create
@@ -287,6 +279,26 @@ int ling_b200_gemm_fp8_noalloc(const uint8_t* w_codes, const float* w_scales, co
  * with ling_b200_kv_write first); out [rows][heads][head_dim], before the output gate. */
 int ling_b200_attention_host(ling_b200_ctx* ctx, const ling_b200_seq_step* seqs, int n_seqs, int attn_layer, const float* q,
                              float* out);
+
+/* attn_prepare(_seqs) (kernels.cuh:223-236; kernels.cu:558-596, attention_body.cuh:54-99) for one full-attention layer:
+ * qkv [rows][heads * 2 * head_dim + 2 * kv_heads * head_dim] is the q|k|v projection's output (per q head: head_dim query
+ * values, then head_dim gate values); every row's K (normed, rotated at pos + depth + rope_delta) and V (raw) go to cache
+ * slot pos + row index of its sequence's slot (read them back with ling_b200_kv_read); q_out [rows][heads][head_dim] is
+ * the normed, rotated query as the attention kernel receives it (rounded to FP16). */
+int ling_b200_attn_prepare_host(ling_b200_ctx* ctx, const ling_b200_seq_step* seqs, int n_seqs, int attn_layer,
+                                const float* qkv, float* q_out);
+
+/* gdn_conv_tree + gdn_recurrent_tree + gated_rmsnorm (kernels.cuh:131-136, 478-480) as the step's single DeltaNet kernel
+ * runs them, for n_seqs sequences of one layer (the kernel covers key dim = value dim = 64 or 128).  n_rows, chain
+ * [n_seqs]; parent [rows] the sequences' trees one after another (a sequence's row 0 is its anchor); in [rows][C + HV*Dv]
+ * the in projection's output (conv channels q|k|v, then z); convw [C][4]; g, beta [rows][HV]; state [n_seqs][HV][Dk][Dv]
+ * and conv [n_seqs][C][3] (read, never written); norm_w [Dv].  Out: pre [rows][C] (the raw conv inputs kept for the
+ * commit), post [rows][C] (as ling_b200_gdn_tree_host), core [rows][HV*Dv] (the recurrence's output before the gated
+ * norm), and the out projection's FP8 input: out_codes [rows][HV*Dv], out_scales [rows][HV*Dv/128]. */
+int ling_b200_gdn_fused_host(int device, int Hk, int HV, int Dk, int Dv, int n_seqs, const int* n_rows, const int* chain,
+                             const int* parent, const float* in, const float* convw, const float* g, const float* beta,
+                             const float* state, const float* conv, const float* norm_w, float eps, float* pre, float* post,
+                             float* core, uint8_t* out_codes, float* out_scales);
 
 /* gdn_conv_tree + gdn_recurrent_tree (kernels.cuh:131-136): one sequence, one layer.  pre [n][C], g and beta
  * [n][HV] (g = log decay), state [HV][Dk][Dv], conv [C][3]; out core [n][HV*Dv] and post [n][C] (the conv outputs with

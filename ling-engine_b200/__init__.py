@@ -295,6 +295,16 @@ class Context:
         self.last_seqs = len(seqs)
         return out
 
+    def attn_prepare(self, seqs, attn_layer, qkv):
+        """attn_prepare alone: qkv [rows][heads*2*D + 2*kv_heads*D] -> q [rows][heads][D]; K and V go to the cache."""
+        arr, keep = make_steps(seqs)
+        qkv = np.ascontiguousarray(qkv, np.float32)
+        q = np.zeros((qkv.shape[0], self.cfg.heads, self.cfg.head_dim), np.float32)
+        check(lib().ling_b200_attn_prepare_host(self.h, arr, len(seqs), attn_layer, _fp(qkv), _fp(q)), "attn_prepare_host")
+        self.last_rows = sum(len(s["tokens"]) for s in seqs)
+        self.last_seqs = len(seqs)
+        return q
+
     def read_tree_desc(self, seq):
         t = TreeDesc()
         check(lib().ling_b200_read_tree_desc(self.h, seq, C.byref(t)), "read_tree_desc")
@@ -372,12 +382,21 @@ def gemm_fp8_bench(M, N, K, impl=0, splits=0, iters=20, device=0):
     return ms.value
 
 
-def gemm_prefetch_bench(M, N, K, slabs, mode=0, delay_us=30, flush=1, iters=10, device=0, stamps=False):
-    ms = C.c_float()
-    st = (C.c_ulonglong * 16)()
-    check(lib().ling_b200_gemm_prefetch_bench(device, M, N, K, slabs, mode, delay_us, flush, iters, C.byref(ms), st if stamps else None),
-          "gemm_prefetch_bench")
-    return (ms.value, list(st)) if stamps else ms.value
+def gdn_fused(Hk, HV, Dk, Dv, trees, inp, convw, g, beta, state, conv, norm_w, eps=1e-6, device=0):
+    """The step's single DeltaNet kernel on host buffers.  trees: list of (parent list, chain) per sequence; inp
+    [rows][C + HV*Dv]; state [n_seqs][HV][Dk][Dv]; conv [n_seqs][C][3].  Returns pre, post, core, codes, scales."""
+    n_rows = np.array([len(p) for p, _ in trees], np.int32)
+    chain = np.array([c for _, c in trees], np.int32)
+    parent = np.concatenate([np.asarray(p, np.int32) for p, _ in trees]).astype(np.int32)
+    rows, Cn, Vs = int(n_rows.sum()), 2 * Hk * Dk + HV * Dv, HV * Dv
+    arrs = [np.ascontiguousarray(a, np.float32) for a in (inp, convw, g, beta, state, conv, norm_w)]
+    pre, post = np.zeros((rows, Cn), np.float32), np.zeros((rows, Cn), np.float32)
+    core = np.zeros((rows, Vs), np.float32)
+    codes, scales = np.zeros((rows, Vs), np.uint8), np.zeros((rows, Vs // 128), np.float32)
+    check(lib().ling_b200_gdn_fused_host(device, Hk, HV, Dk, Dv, len(trees), _ip(n_rows), _ip(chain), _ip(parent),
+                                         *[_fp(a) for a in arrs], C.c_float(eps), _fp(pre), _fp(post), _fp(core), _bp(codes),
+                                         _fp(scales)), "gdn_fused_host")
+    return pre, post, core, codes, scales
 
 
 def describe_tree(parent, chain):

@@ -142,7 +142,7 @@ __device__ __forceinline__ void pdl_sync() {
   pdl_trigger();
   pdl_wait();
 }
-void set_pdl(bool on);  // process-wide, like the reference's kernels::set_pdl (src/core/kernels.cuh:82-83)
+void set_pdl(bool on);  // the calling host thread's switch (the reference's kernels::set_pdl, src/core/kernels.cuh:82-83, is process-wide)
 bool pdl_enabled();
 
 // cluster_x > 1: the grid's x dimension is grouped into thread-block clusters of that many CTAs (distributed shared memory).

@@ -16,7 +16,10 @@ namespace lb {
 
 thread_local std::string g_error;
 void set_error(const std::string& what) { g_error = what; }
-static bool g_pdl = false;
+// Programmatic dependent launch is a property of the launching host thread (one thread drives one context): a context's
+// step sets it for its own launches and puts the caller's setting back, so contexts on different threads (one per GPU) do
+// not see each other's choice.
+static thread_local bool g_pdl = false;
 void set_pdl(bool on) { g_pdl = on; }
 bool pdl_enabled() { return g_pdl; }
 
@@ -178,16 +181,21 @@ int run_gemm(ling_b200_ctx* c, const Fp8Matrix& w, const Fp8Acts& x, int which, 
 
 // The whole step on the context's stream.  rows = the capacity class (grids and GEMM extents); the kernels read the
 // real extents from device memory.  Order of the forward pass: src/core/engine.cpp:1288-1745 (verify branch).
-int env_int(const char* name, int dflt) {
-  const char* e = std::getenv(name);
-  return e ? std::atoi(e) : dflt;
-}
+// Sets the calling thread's dependent-launch switch for a scope and restores what the caller had set.
+struct PdlScope {
+  bool before;
+  explicit PdlScope(bool on) : before(pdl_enabled()) { set_pdl(on); }
+  ~PdlScope() { set_pdl(before); }
+};
+// Weights that the long glue kernels' idle CTAs ask into L2 for the GEMMs behind them, in MB (measured on the 27B
+// single-stream step: the DeltaNet kernel 48 MB of gate|up, 7.97 -> 7.59 ms per step; the attention kernel the whole o
+// projection and 48 MB of gate|up; more than ~64 MB per kernel, the down projection or the next layer's in projection were
+// slower), requested 3 us after the kernel's dependency wait.
+constexpr int kPfAttnOMb = 32, kPfAttnGuMb = 48, kPfGdnGuMb = 48, kPfDelayNs = 3000;
 int enqueue_step_body(ling_b200_ctx* c, int rows, int flags);
 int enqueue_step(ling_b200_ctx* c, int rows, int flags) {
-  set_pdl(c->opt.pdl != 0);
-  const int rc = enqueue_step_body(c, rows, flags);
-  set_pdl(false);
-  return rc;
+  PdlScope pdl(c->opt.pdl != 0);
+  return enqueue_step_body(c, rows, flags);
 }
 int enqueue_step_body(ling_b200_ctx* c, int rows, int flags) {
   const ModelDims& d = c->d;
@@ -225,13 +233,11 @@ int enqueue_step_body(ling_b200_ctx* c, int rows, int flags) {
         // tcgen05/TMEM attention; the mma.sync form stays as the cross-check implementation (gemm_impl = 1)
         PrefetchPlan plan;
         if (tc && c->opt.pdl) {
-          static const int o_mb = env_int("LING_B200_PFA_O_MB", 32), gu_mb = env_int("LING_B200_PFA_GU_MB", 48);
-          static const int down_mb = env_int("LING_B200_PFA_DOWN_MB", 0), delay = env_int("LING_B200_PFA_DELAY_NS", 3000);
           auto range = [&](int i, const Fp8Matrix& w, int mb) {
             plan.p[i] = w.codes, plan.bytes[i] = std::min<size_t>(size_t(mb) << 20, size_t(w.N_pad) * w.K_pad);
           };
-          range(0, L.o, o_mb), range(1, L.gu, gu_mb), range(2, L.down, down_mb);
-          plan.delay_ns = delay;
+          range(0, L.o, kPfAttnOMb), range(1, L.gu, kPfAttnGuMb);
+          plan.delay_ns = kPfDelayNs;
         }
         if (tc)
           LB_TRY(attention_tc_launch(c->qh, c->sb, d, al, c->kv, c->part_o, c->part_ml, c->chunk_slots, c->sm_count, plan,
@@ -265,22 +271,13 @@ int enqueue_step_body(ling_b200_ctx* c, int rows, int flags) {
         Timed t(c, kFamGdn);
         PrefetchPlan plan;
         if (c->opt.pdl) {
-          static const int out_mb = env_int("LING_B200_PF_OUT_MB", 0), gu_mb = env_int("LING_B200_PF_GU_MB", 48);
-          static const int down_mb = env_int("LING_B200_PF_DOWN_MB", 0), in_mb = env_int("LING_B200_PF_IN_MB", 0);
-          static const int delay = env_int("LING_B200_PF_DELAY_NS", 3000);
-          auto range = [&](int i, const Fp8Matrix& w, int mb) {
-            plan.p[i] = w.codes, plan.bytes[i] = std::min<size_t>(size_t(mb) << 20, size_t(w.N_pad) * w.K_pad);
-          };
-          range(0, L.out, out_mb), range(1, L.gu, gu_mb), range(2, L.down, down_mb);
-          if (l + 1 < c->cfg.layers) {
-            const LayerW& N = c->layers[l + 1];
-            range(3, N.full ? N.qkv : N.in, in_mb);
-          }
-          plan.delay_ns = delay;
+          plan.p[0] = L.gu.codes;
+          plan.bytes[0] = std::min<size_t>(size_t(kPfGdnGuMb) << 20, size_t(L.gu.N_pad) * L.gu.K_pad);
+          plan.delay_ns = kPfDelayNs;
         }
         LB_TRY(gdn_fused_launch(p0, c->sb, d, L.conv, c->conv_state + size_t(gl) * c->conv_layer, c->conv_layer * d.n_gdn, g, beta,
                                 c->gdn_state + size_t(gl) * c->state_layer, c->state_layer * d.n_gdn, L.lin_norm, c->qout(c->xq_v),
-                                pre, post, c->opt.sessions, c->sm_count, plan,
+                                pre, post, nullptr, c->opt.sessions, c->sm_count, plan,
                                 c->timeline && gl == 0 ? c->timeline + 4 * size_t(ling_b200_ctx::kTimelineLaunches - 4) : nullptr, s));
       } else {
         {
@@ -1102,7 +1099,7 @@ int ling_b200_gemm_chain_ms(ling_b200_ctx* c, int iters, float* ms) {
   }
   LB_TRY(finish(c));
   const int rows = row_class(c->staged_rows);
-  set_pdl(c->opt.pdl != 0);
+  PdlScope pdl(c->opt.pdl != 0);
   int rc = LING_B200_OK;
   auto chain = [&]() -> int {
     for (const LayerW& L : c->layers) {
@@ -1118,13 +1115,9 @@ int ling_b200_gemm_chain_ms(ling_b200_ctx* c, int iters, float* ms) {
   // captured once and replayed, like the step itself (launching 257 kernels from the host one by one would time the host)
   cudaGraph_t graph = nullptr;
   cudaGraphExec_t exec = nullptr;
-  if (!cuda_ok(cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal), "cudaStreamBeginCapture")) {
-    set_pdl(false);
-    return LING_B200_ERR_CUDA;
-  }
+  if (!cuda_ok(cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal), "cudaStreamBeginCapture")) return LING_B200_ERR_CUDA;
   rc = chain();
   const cudaError_t ce = cudaStreamEndCapture(c->stream, &graph);
-  set_pdl(false);
   if (rc == LING_B200_OK && !cuda_ok(ce, "cudaStreamEndCapture")) rc = LING_B200_ERR_CUDA;
   if (rc == LING_B200_OK && !cuda_ok(cudaGraphInstantiate(&exec, graph, 0), "cudaGraphInstantiate")) rc = LING_B200_ERR_CUDA;
   if (graph) cudaGraphDestroy(graph);
@@ -1196,6 +1189,41 @@ int ling_b200_attention_host(ling_b200_ctx* c, const ling_b200_seq_step* seqs, i
                              tc ? c->sm_count : c->sm_count * 2, c->stream));
   LB_CUDA(cudaMemcpyAsync(out, c->planes[0], n * 4, cudaMemcpyDeviceToHost, c->stream));
   return read_err(c);
+}
+
+// attn_prepare alone, for parity checks: packs `seqs` on the device, takes the q|k|v projection's rows from the host, runs
+// the prepare kernel of one attention layer (head norms, rotation at the rows' positions, K and V into the slot's cache
+// through its page table) and returns the queries as the attention kernel receives them (FP16, widened to fp32).
+int ling_b200_attn_prepare_host(ling_b200_ctx* c, const ling_b200_seq_step* seqs, int n_seqs, int attn_layer, const float* qkv,
+                                float* q_out) {
+  LB_TRY(ling_b200_step_stage(c, seqs, n_seqs, 0));
+  const ModelDims& d = c->d;
+  if (attn_layer < 0 || attn_layer >= d.n_attn || !qkv || !q_out) {
+    set_error("attn_prepare_host: bad argument");
+    return LING_B200_ERR_ARG;
+  }
+  int layer = -1;
+  for (int l = 0; l < c->cfg.layers; ++l)
+    if (c->attn_index[l] == attn_layer) layer = l;
+  const LayerW& L = c->layers[layer];
+  const int rows = c->staged_rows, W = d.Hq * 2 * d.D + 2 * d.Hkv * d.D;
+  if (size_t(rows) * W > c->plane_floats) {
+    set_error("attn_prepare_host: too many rows for the staging buffers");
+    return LING_B200_ERR_ARG;
+  }
+  c->last_rows = rows, c->last_seqs = n_seqs, c->last_flags = 0;
+  PdlScope pdl(c->opt.pdl != 0);
+  LB_TRY(pack_launch(c->sb, d, c->stream));
+  LB_CUDA(cudaMemcpyAsync(c->planes[0], qkv, size_t(rows) * W * 4, cudaMemcpyHostToDevice, c->stream));
+  Planes p;
+  p.p = c->planes[0], p.n = 1, p.stride = 0, p.ld = W;
+  LB_TRY(attn_prepare_launch(p, c->sb, d, attn_layer, L.q_norm, L.k_norm, c->qh, c->kv, row_class(rows), c->stream));
+  const size_t n = size_t(rows) * d.Hq * d.D;
+  std::vector<__half> hq(n);
+  LB_CUDA(cudaMemcpyAsync(hq.data(), c->qh, n * sizeof(__half), cudaMemcpyDeviceToHost, c->stream));
+  LB_TRY(read_err(c));
+  for (size_t i = 0; i < n; ++i) q_out[i] = __half2float(hq[i]);
+  return LING_B200_OK;
 }
 
 // ------------------------------------------------------------------------------------------------ read-backs

@@ -70,24 +70,11 @@ __global__ void __launch_bounds__(gemm_threads(NT), ctas_per_sm(NT))
     gemm_fp8_tcgen05_kernel(const __grid_constant__ CUtensorMap mapW, const __grid_constant__ CUtensorMap mapX,
                             const float* __restrict__ ws, const float* __restrict__ xs, float* __restrict__ out, int ld,
                             size_t split_stride, int M, int N, int N_pad, int KB, int splits, int xrows, HeadArgs head,
-                            int* err_flag, int pdl, int l2_slabs, unsigned long long* timeline, int detail) {
+                            int* err_flag, int pdl, int l2_slabs, unsigned long long* timeline) {
   pdl_trigger();  // the next kernel may be scheduled as soon as every CTA of this one has started
   // Optional timeline (debugging aid, like the reference's per-block %globaltimer stamps, src/core/engine.hpp:637-642):
   // [0] first CTA's start, [1] first producer past the dependency wait, [2] last producer past it, [3] last CTA's end.
-  // With `detail` (the isolated micro-benchmark only) twelve more: [4..9] CTA (0,0,0)'s start, end of set-up, first stage
-  // landed, last MMA issued, last accumulator ready, end; [10] max over CTAs of (first stage landed - start), [11] max CTA
-  // lifetime, [12] last CTA's start, [13] first CTA's end.
-  unsigned long long t_start = 0;
-  const bool cta0 = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
-  if (timeline && threadIdx.x == 0) {
-    t_start = global_ns();
-    atomicMin(timeline, t_start);
-    if (detail) {
-      atomicMax(timeline + 12, t_start);
-      if (cta0) timeline[4] = t_start;
-    }
-  }
-  if (timeline && detail && threadIdx.x == 32) t_start = global_ns();
+  if (timeline && threadIdx.x == 0) atomicMin(timeline, global_ns());
   constexpr int STAGES = stages_for(NT);
   constexpr int kScaleRing = scale_ring(NT), kScaleAhead = scale_ahead(NT);
   constexpr int kBBytes = NT * kBlockK;
@@ -140,7 +127,6 @@ __global__ void __launch_bounds__(gemm_threads(NT), ctas_per_sm(NT))
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  if (timeline && detail && cta0 && threadIdx.x == 0) timeline[5] = global_ns();
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -212,11 +198,6 @@ __global__ void __launch_bounds__(gemm_threads(NT), ctas_per_sm(NT))
           break;
         }
         tc_fence_after();
-        if (timeline && detail && i == 0) {
-          const unsigned long long t = global_ns();
-          atomicMax(timeline + 10, t - t_start);
-          if (cta0) timeline[6] = t;
-        }
         const uint64_t adesc = umma_desc_sw128(smem_u32(tiles + s * kStageBytes));
         const uint64_t bdesc = umma_desc_sw128(smem_u32(tiles + s * kStageBytes + kWBytes));
         const uint32_t d = tmem_base + uint32_t(buf * ACCW);
@@ -227,7 +208,6 @@ __global__ void __launch_bounds__(gemm_threads(NT), ctas_per_sm(NT))
         umma_commit(&empty[s]);         // the stage may be refilled once these MMAs have read it
         umma_commit(&tmem_full[buf]);   // the accumulator is complete
       }
-      if (timeline && detail && cta0) timeline[7] = global_ns();
     }
   } else {
     // ------------------------------------------------------------------ epilogue warps (TMEM lane quarter = warp % 4)
@@ -278,7 +258,6 @@ __global__ void __launch_bounds__(gemm_threads(NT), ctas_per_sm(NT))
         break;
       }
       tc_fence_after();
-      if (timeline && detail && cta0 && i == nslab - 1 && threadIdx.x == 64) timeline[8] = global_ns();
       const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(buf * ACCW + col0);
       // columns per TMEM read: the whole accumulator for the 32-row token tile, 16 at a time for the wider ones (registers)
       constexpr int CH = NTH == 32 ? 32 : 16;
@@ -369,71 +348,10 @@ __global__ void __launch_bounds__(gemm_threads(NT), ctas_per_sm(NT))
   }
   tc_fence_before();
   __syncthreads();
-  if (timeline && threadIdx.x == 0) {
-    const unsigned long long t = global_ns();
-    atomicMax(timeline + 3, t);
-    if (detail) {
-      atomicMax(timeline + 11, t - t_start);
-      atomicMin(timeline + 13, t);
-      if (cta0) timeline[9] = t;
-    }
-  }
+  if (timeline && threadIdx.x == 0) atomicMax(timeline + 3, global_ns());
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
-  }
-}
-
-// ---------------------------------------------------------------------------------------------- L2 prefetch
-// Brings the weight tiles a GEMM will read first into L2 ahead of the GEMM, from a parallel branch of the step's graph,
-// so that HBM keeps streaming weights while the small kernels between two GEMMs run.  Unit u = (K block j of every
-// CTA's range, CTA): the first `slabs` K blocks of every (tile, split) pair, earliest K blocks first -- the order in
-// which a one-wave GEMM consumes them.  mode 0: one TMA prefetch instruction per 16 KiB tile (no SM data path);
-// mode 1: plain loads of one word per 32-byte sector (the same bytes through the load/store units; a cross-check of
-// what the TMA prefetch achieves).  Reads weights only, which no kernel of a step writes.
-__global__ void __launch_bounds__(128)
-    weight_prefetch_kernel(const __grid_constant__ CUtensorMap mapW, const uint8_t* __restrict__ codes, int K_pad, int tiles,
-                           int splits, int KB, int slabs, int mode, int* sink) {
-  const int ctas = tiles * splits;
-  const int units = ctas * slabs;
-  if (mode == 0) {
-    for (int u = blockIdx.x * blockDim.x + threadIdx.x; u < units; u += gridDim.x * blockDim.x) {
-      const int j = u / ctas, c = u % ctas, split = c % splits, tile = c / splits;
-      const int kb0 = int(int64_t(KB) * split / splits), kb1 = int(int64_t(KB) * (split + 1) / splits);
-      if (kb0 + j < kb1) tma_prefetch_l2_2d(&mapW, (kb0 + j) * kBlockK, tile * kTileN);
-    }
-    return;
-  }
-  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31, warps = (gridDim.x * blockDim.x) >> 5;
-  int acc = 0;
-  for (int u = warp; u < units; u += warps) {
-    const int j = u / ctas, c = u % ctas, split = c % splits, tile = c / splits;
-    const int kb0 = int(int64_t(KB) * split / splits), kb1 = int(int64_t(KB) * (split + 1) / splits);
-    if (kb0 + j >= kb1) continue;
-    const uint8_t* base = codes + size_t(tile) * kTileN * K_pad + size_t(kb0 + j) * kBlockK;
-#pragma unroll 4
-    for (int i = lane; i < kTileN * 4; i += 32)  // 128 rows x 4 sectors
-      acc ^= __ldcg(reinterpret_cast<const int*>(base + size_t(i >> 2) * K_pad + (i & 3) * 32));
-  }
-  if (acc == 0x5a5a5a5a && sink) *sink = acc;  // keeps the loads alive
-}
-
-// Reads a buffer larger than L2: afterwards L2 holds clean lines of that buffer (a write flush leaves dirty lines whose
-// write-back then competes with the kernel being timed).
-__global__ void __launch_bounds__(256) read_flush_kernel(const int4* __restrict__ buf, size_t n, int* sink) {
-  int acc = 0;
-  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += size_t(gridDim.x) * blockDim.x) {
-    const int4 v = __ldcg(buf + i);
-    acc ^= v.x ^ v.y ^ v.z ^ v.w;
-  }
-  if (acc == 0x5a5a5a5a && sink) *sink = acc;
-}
-
-// Spins for about `ns` nanoseconds (bounded by construction); a stand-in for the kernels between two GEMMs in the
-// prefetch micro-benchmark.
-__global__ void delay_kernel(unsigned long long ns) {
-  const unsigned long long t0 = global_ns();
-  while (global_ns() - t0 < ns) {
   }
 }
 
@@ -563,21 +481,16 @@ int launch_tc(const GemmCall& c, cudaStream_t stream) {
   cfg.attrs = at;
   const bool pdl = pdl_enabled();
   cfg.numAttrs = pdl ? 1 : 0;
-  // L2 prefetch budget of one GEMM: about 40 MB of weight tiles beyond the pipeline stages, spread over its CTAs
+  // L2 prefetch budget of one GEMM before its dependency wait: 16 MB of weight tiles beyond the pipeline stages, spread
+  // over its CTAs (measured on the 27B shapes: 0 MB 8.75 ms per step, 16 MB 8.72, 40 MB 8.96, 80 MB 9.18), and every
+  // pipeline stage filled before the wait
   const int ctas = int(cfg.gridDim.z * cfg.gridDim.y);
-  static const int l2_mb = [] {
-    const char* e = std::getenv("LING_B200_L2_PREFETCH_MB");  // tuning aid; the default was measured best for the 27B shapes
-    return e ? std::atoi(e) : 16;
-  }();
-  const int l2_slabs = std::min(64, int((size_t(l2_mb) << 20) / (size_t(ctas) * kABytes)));
-  static const int pre_stages = [] {
-    const char* e = std::getenv("LING_B200_PREFILL_STAGES");  // tuning aid: pipeline stages filled before the dependency wait
-    return e ? std::max(0, std::min(30, std::atoi(e))) : 30;
-  }();
+  constexpr int kL2PrefetchMb = 16, pre_stages = 30;
+  const int l2_slabs = std::min(64, int((size_t(kL2PrefetchMb) << 20) / (size_t(ctas) * kABytes)));
   LB_CUDA(cudaLaunchKernelEx(&cfg, gemm_fp8_tcgen05_kernel<NT>, W.map, X.map[NT / 32 - 1], (const float*)W.scales,
                              (const float*)X.scales, c.out, c.ld, c.split_stride, c.M, W.N, W.N_pad, W.KB, splits,
                              X.rows_alloc, h, c.err_flag, pdl ? 1 + pre_stages : 0, pdl && cfg.gridDim.x == 1 ? l2_slabs : 0,
-                             c.timeline, c.timeline_detail ? 1 : 0));
+                             c.timeline));
   LB_LAUNCH("gemm_fp8_tcgen05_kernel");
   return LING_B200_OK;
 }
@@ -600,29 +513,6 @@ int make_acts_maps(Fp8Acts& x) {
     const int nt = 32 * (i + 1);
     if (const int r = encode_2d(&x.map[i], x.codes, uint64_t(x.K_pad), uint64_t(x.rows_alloc), uint32_t(nt))) return r;
   }
-  return LING_B200_OK;
-}
-
-int weight_prefetch_launch(const Fp8Matrix& W, int splits, int slabs, int mode, int* sink, cudaStream_t stream) {
-  if (slabs < 1) return LING_B200_OK;
-  const int tiles = W.N_pad / kTileN;
-  const int units = tiles * splits * slabs;
-  const int per_block = mode == 0 ? 128 : 4;
-  const int blocks = std::max(1, std::min(ceil_div(units, per_block), mode == 0 ? 148 : 148 * 8));
-  weight_prefetch_kernel<<<blocks, 128, 0, stream>>>(W.map, W.codes, W.K_pad, tiles, splits, W.KB, slabs, mode, sink);
-  LB_LAUNCH("weight_prefetch_kernel");
-  return LING_B200_OK;
-}
-
-int read_flush_launch(const float* buf, size_t n, int* sink, cudaStream_t stream) {
-  read_flush_kernel<<<148 * 8, 256, 0, stream>>>(reinterpret_cast<const int4*>(buf), n / 4, sink);
-  LB_LAUNCH("read_flush_kernel");
-  return LING_B200_OK;
-}
-
-int delay_launch(unsigned long long ns, cudaStream_t stream) {
-  delay_kernel<<<1, 1, 0, stream>>>(ns > 10000000ull ? 10000000ull : ns);
-  LB_LAUNCH("delay_kernel");
   return LING_B200_OK;
 }
 

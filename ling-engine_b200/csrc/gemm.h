@@ -52,7 +52,6 @@ struct GemmCall {
   int impl = 0;             // 0 tcgen05, 1 CUDA cores
   int* err_flag = nullptr;
   unsigned long long* timeline = nullptr;  // four stamps of this launch (debugging aid), or nullptr
-  bool timeline_detail = false;            // `timeline` has 16 slots; per-CTA phases are recorded too (micro-benchmark only)
 };
 
 // Creates the tensor maps (driver entry point fetched at run time; no link against libcuda).
@@ -62,13 +61,6 @@ int make_acts_maps(Fp8Acts& x);
 int choose_splits(int N_pad, int KB, int sm_count);
 int gemm_init();
 int gemm_launch(const GemmCall& c, cudaStream_t stream);
-// Asks for the first `slabs` K blocks of every (tile, split) CTA's range of W to be brought into L2 (mode 0: TMA prefetch,
-// mode 1: plain loads); `splits` as the GEMM that follows will use.  Reads weights only.
-int weight_prefetch_launch(const Fp8Matrix& W, int splits, int slabs, int mode, int* sink, cudaStream_t stream);
-// Reads n floats (a buffer larger than L2) so that L2 holds nothing else, and nothing dirty; benchmark plumbing.
-int read_flush_launch(const float* buf, size_t n, int* sink, cudaStream_t stream);
-// A one-thread kernel that spins for about `ns` nanoseconds (at most 10 ms); benchmark plumbing.
-int delay_launch(unsigned long long ns, cudaStream_t stream);
 // Token rows per MMA (the N of the instruction) used for M rows: 32, 64, 96 or 128.
 int token_tile(int M);
 

@@ -99,6 +99,9 @@ int ling_b200_gemm_fp8_host(int device, int impl, int splits, const float* x, co
   LB_PTR(dw && dx);
   LB_TRY(quant_weight_launch(dw, 0, 0.f, 0, g.W.codes, g.W.scales, 0, N, K, g.W.N_pad, g.W.K_pad, 0));
   LB_TRY(quant_acts_launch(dx, M, QuantOut{g.X.codes, g.X.scales, K, g.X.K_pad, g.X.rows_alloc}, 0));
+  // With dependent launch the GEMM loads weight tiles before its dependency wait, on the understanding that no kernel
+  // just ahead of it writes the weights: the quantizers must have completed before it is launched.
+  LB_CUDA(cudaStreamSynchronize(0));
   GemmCall c;
   c.W = &g.W, c.X = &g.X, c.M = M, c.out = g.out, c.ld = g.W.N_pad;
   c.split_stride = size_t(g.X.rows_alloc) * g.W.N_pad;
@@ -137,6 +140,7 @@ int ling_b200_gemm_fp8_bench(int device, int impl, int splits, int M, int N, int
   LB_TRY(fill_f32_launch(stream_key(1, 7), 1.f, dx, size_t(M) * K, 0));
   LB_TRY(quant_weight_launch(nullptr, stream_key(1, 9), 0.02f, 1, g.W.codes, g.W.scales, 0, N, K, g.W.N_pad, g.W.K_pad, 0));
   LB_TRY(quant_acts_launch(dx, M, QuantOut{g.X.codes, g.X.scales, K, g.X.K_pad, g.X.rows_alloc}, 0));
+  LB_CUDA(cudaStreamSynchronize(0));  // the weights are complete before a GEMM that may read them ahead of its dependency wait
   GemmCall c;
   c.W = &g.W, c.X = &g.X, c.M = M, c.out = g.out, c.ld = g.W.N_pad;
   c.split_stride = size_t(g.X.rows_alloc) * g.W.N_pad;
@@ -159,70 +163,6 @@ int ling_b200_gemm_fp8_bench(int device, int impl, int splits, int M, int N, int
     return LING_B200_ERR_DEVICE_FLAG;
   }
   *ms_per_launch = ms / iters;
-  return LING_B200_OK;
-}
-
-int ling_b200_gemm_prefetch_bench(int device, int M, int N, int K, int slabs, int mode, int delay_us, int flush, int iters,
-                                  float* ms_per_launch, unsigned long long* stamps16) {
-  if (M < 1 || N < 1 || K < 1 || iters < 1 || iters > 1000 || !ms_per_launch || M > LING_B200_MAX_ROWS || slabs < 0 ||
-      delay_us < 0 || delay_us > 10000) {
-    set_error("gemm_prefetch_bench: bad argument");
-    return LING_B200_ERR_ARG;
-  }
-  LB_TRY(check_device(device));
-  Scratch sc;
-  GemmSetup g;
-  LB_TRY(setup_gemm(sc, g, M, N, K, 0));
-  const size_t flush_n = size_t(64) << 20;  // 256 MiB of floats: twice the L2
-  float* dx = sc.get<float>(size_t(M) * K, false);
-  float* fl = sc.get<float>(flush_n, true);
-  int* sink = sc.get<int>(1);
-  LB_PTR(dx && fl && sink);
-  LB_TRY(fill_f32_launch(stream_key(1, 7), 1.f, dx, size_t(M) * K, 0));
-  LB_TRY(quant_weight_launch(nullptr, stream_key(1, 9), 0.02f, 1, g.W.codes, g.W.scales, 0, N, K, g.W.N_pad, g.W.K_pad, 0));
-  LB_TRY(quant_acts_launch(dx, M, QuantOut{g.X.codes, g.X.scales, K, g.X.K_pad, g.X.rows_alloc}, 0));
-  GemmCall c;
-  c.W = &g.W, c.X = &g.X, c.M = M, c.out = g.out, c.ld = g.W.N_pad;
-  c.split_stride = size_t(g.X.rows_alloc) * g.W.N_pad;
-  c.impl = 0, c.err_flag = g.err;
-  unsigned long long* tl = nullptr;
-  if (stamps16) {
-    tl = sc.get<unsigned long long>(16);
-    LB_PTR(tl);
-    c.timeline = tl, c.timeline_detail = true;
-  }
-  cudaEvent_t a, b;
-  LB_CUDA(cudaEventCreate(&a));
-  LB_CUDA(cudaEventCreate(&b));
-  double total = 0.0;
-  for (int i = 0; i < iters + 2; ++i) {
-    if (flush == 1) LB_TRY(flush_launch(fl, flush_n, 0));
-    if (flush == 2) LB_TRY(read_flush_launch(fl, flush_n, sink, 0));
-    LB_TRY(weight_prefetch_launch(g.W, g.W.splits, slabs, mode, sink, 0));
-    LB_TRY(delay_launch(uint64_t(delay_us) * 1000ull, 0));
-    if (tl) {
-      unsigned long long init[16];
-      for (int j = 0; j < 16; ++j) init[j] = (j == 0 || j == 1 || j == 13) ? ~0ull : 0ull;
-      LB_CUDA(cudaMemcpyAsync(tl, init, sizeof(init), cudaMemcpyHostToDevice, 0));
-      LB_CUDA(cudaStreamSynchronize(0));
-    }
-    LB_CUDA(cudaEventRecord(a, 0));
-    LB_TRY(gemm_launch(c, 0));
-    LB_CUDA(cudaEventRecord(b, 0));
-    LB_CUDA(cudaEventSynchronize(b));
-    float ms = 0.f;
-    LB_CUDA(cudaEventElapsedTime(&ms, a, b));
-    if (i >= 2) total += ms;
-  }
-  cudaEventDestroy(a), cudaEventDestroy(b);
-  int err = 0;
-  LB_CUDA(cudaMemcpy(&err, g.err, 4, cudaMemcpyDeviceToHost));
-  if (err) {
-    set_error("gemm: device error word = " + std::to_string(err));
-    return LING_B200_ERR_DEVICE_FLAG;
-  }
-  *ms_per_launch = float(total / iters);
-  if (tl) LB_CUDA(cudaMemcpy(stamps16, tl, 128, cudaMemcpyDeviceToHost));
   return LING_B200_OK;
 }
 
@@ -290,6 +230,117 @@ int ling_b200_gdn_tree_host(int device, int Hk, int HV, int Dk, int Dv, const li
   LB_CUDA(cudaDeviceSynchronize());
   LB_CUDA(cudaMemcpy(post, d_post, size_t(n) * C * 4, cudaMemcpyDeviceToHost));
   LB_CUDA(cudaMemcpy(core, d_core, size_t(n) * Vs * 4, cudaMemcpyDeviceToHost));
+  return LING_B200_OK;
+}
+
+namespace {
+// Device-side description of a step of n_seqs sequences for the kernels that read StepBuffers, packed on the device by
+// pack_kernel (tree descriptions, DeltaNet paths, conv taps) exactly as a context's step does.
+struct PackedSeqs {
+  StepBuffers sb;
+  ModelDims d{};
+  int rows = 0;
+  int build(Scratch& sc, int n_seqs, const int* n_rows, const int* chain, const int* parent, int vocab) {
+    if (n_seqs < 1 || n_seqs > LING_B200_MAX_SEQS) {
+      set_error("sequence count out of range");
+      return LING_B200_ERR_ARG;
+    }
+    std::vector<SeqDev> seqs(n_seqs);
+    std::vector<int> par(size_t(n_seqs) * kTreeRows, 0), tok(size_t(n_seqs) * kTreeRows, 0);
+    rows = 0;
+    for (int s = 0; s < n_seqs; ++s) {
+      if (n_rows[s] < 1 || n_rows[s] > kTreeRows) {
+        set_error("a tree of 1 to 32 rows expected");
+        return LING_B200_ERR_ARG;
+      }
+      seqs[s] = SeqDev{s, 0, 0, n_rows[s], chain[s], 0};
+      for (int r = 0; r < n_rows[s]; ++r) par[size_t(s) * kTreeRows + r] = r == 0 ? -1 : parent[rows + r];
+      rows += n_rows[s];
+    }
+    d.max_seqs = n_seqs, d.V = vocab, d.rows_alloc = round_up(rows, 128);
+    sb.n_seqs = sc.put(&n_seqs, 1);
+    sb.seqs = sc.put(seqs.data(), seqs.size());
+    sb.in_parent = sc.put(par.data(), par.size());
+    sb.in_token = sc.put(tok.data(), tok.size());
+    sb.in_force = sc.get<int>(par.size());
+    sb.row0 = sc.get<int>(n_seqs + 1);
+    sb.n_rows_total = sc.get<int>(1);
+    sb.token = sc.get<int>(d.rows_alloc), sb.seq_of = sc.get<int>(d.rows_alloc), sb.local = sc.get<int>(d.rows_alloc);
+    sb.depth = sc.get<int>(d.rows_alloc), sb.rope_pos = sc.get<int>(d.rows_alloc), sb.cache_slot = sc.get<int>(d.rows_alloc);
+    sb.anc = sc.get<uint32_t>(d.rows_alloc);
+    sb.trees = sc.get<ling_b200_tree_desc>(n_seqs);
+    sb.gdn_aux = sc.get<GdnAux>(n_seqs);
+    sb.argmax_id = sc.get<int>(d.rows_alloc), sb.argmax_val = sc.get<float>(d.rows_alloc);
+    sb.results = sc.get<ling_b200_seq_result>(n_seqs);
+    sb.err = sc.get<int>(1);
+    LB_PTR(sb.n_seqs && sb.seqs && sb.in_parent && sb.in_token && sb.in_force && sb.row0 && sb.n_rows_total && sb.token &&
+           sb.seq_of && sb.local && sb.depth && sb.rope_pos && sb.cache_slot && sb.anc && sb.trees && sb.gdn_aux &&
+           sb.argmax_id && sb.argmax_val && sb.results && sb.err);
+    return LING_B200_OK;
+  }
+};
+}  // namespace
+
+// The step's DeltaNet mixer as the 27B-class step runs it (one launch: conv over the trees + SiLU, q/k normalization,
+// the gated delta rule along every DeltaNet path, gated RMSNorm, FP8 copy), on host buffers; see include/ling_b200.h.
+int ling_b200_gdn_fused_host(int device, int Hk, int HV, int Dk, int Dv, int n_seqs, const int* n_rows, const int* chain,
+                             const int* parent, const float* in, const float* convw, const float* g, const float* beta,
+                             const float* state, const float* conv, const float* norm_w, float eps, float* pre, float* post,
+                             float* core, uint8_t* out_codes, float* out_scales) {
+  if (!n_rows || !chain || !parent || !in || !convw || !g || !beta || !state || !conv || !norm_w || !pre || !post || !core ||
+      !out_codes || !out_scales || !gdn_dims_ok(Hk, HV, Dk, Dv)) {
+    set_error("gdn_fused_host: bad argument");
+    return LING_B200_ERR_ARG;
+  }
+  LB_TRY(check_device(device));
+  Scratch sc;
+  PackedSeqs ps;
+  LB_TRY(ps.build(sc, n_seqs, n_rows, chain, parent, 1 << 30));
+  ModelDims& d = ps.d;
+  d.Hk = Hk, d.HV = HV, d.Dk = Dk, d.Dv = Dv, d.C = 2 * Hk * Dk + HV * Dv, d.Vs = HV * Dv, d.eps = eps, d.n_gdn = 1;
+  if (!gdn_fused_supported(d)) {
+    set_error("gdn_fused_host: the fused kernel covers key dim = value dim = 64 or 128 and value widths that are multiples of 128");
+    return LING_B200_ERR_UNSUPPORTED;
+  }
+  const int n = ps.rows, C = d.C, Vs = d.Vs, W = C + Vs, KB = Vs / 128;
+  float* d_in = sc.put(in, size_t(n) * W);
+  float* d_w32 = sc.put(convw, size_t(C) * 4);
+  float* d_n32 = sc.put(norm_w, size_t(Dv));
+  __nv_bfloat16* d_w = sc.get<__nv_bfloat16>(size_t(C) * 4);
+  __nv_bfloat16* d_nw = sc.get<__nv_bfloat16>(size_t(Dv));
+  float* d_g = sc.put(g, size_t(n) * HV);
+  float* d_b = sc.put(beta, size_t(n) * HV);
+  float* d_state = sc.put(state, size_t(n_seqs) * HV * Dk * Dv);
+  float* d_conv = sc.put(conv, size_t(n_seqs) * C * 3);
+  float* d_pre = sc.get<float>(size_t(n) * C);
+  float* d_post = sc.get<float>(size_t(n) * C);
+  float* d_core = sc.get<float>(size_t(n) * Vs);
+  uint8_t* d_codes = sc.get<uint8_t>(size_t(d.rows_alloc) * Vs);
+  float* d_scales = sc.get<float>(size_t(KB) * d.rows_alloc);
+  LB_PTR(d_in && d_w32 && d_n32 && d_w && d_nw && d_g && d_b && d_state && d_conv && d_pre && d_post && d_core && d_codes && d_scales);
+  LB_TRY(fill_bf16_launch(d_w32, 0, 0.f, 0.f, 0, d_w, size_t(C) * 4, 0));
+  LB_TRY(fill_bf16_launch(d_n32, 0, 0.f, 0.f, 0, d_nw, size_t(Dv), 0));
+  LB_CUDA(cudaStreamSynchronize(0));
+  Planes p_in;
+  p_in.p = d_in, p_in.n = 1, p_in.stride = 0, p_in.ld = W;
+  LB_TRY(pack_launch(ps.sb, d, 0));
+  LB_TRY(gdn_fused_launch(p_in, ps.sb, d, d_w, d_conv, size_t(C) * 3, d_g, d_b, d_state, size_t(HV) * Dk * Dv, d_nw,
+                          QuantOut{d_codes, d_scales, Vs, Vs, d.rows_alloc}, d_pre, d_post, d_core, n_seqs, 148, PrefetchPlan(), nullptr, 0));
+  LB_CUDA(cudaDeviceSynchronize());
+  int err = 0;
+  LB_CUDA(cudaMemcpy(&err, ps.sb.err, 4, cudaMemcpyDeviceToHost));
+  if (err) {
+    set_error("gdn_fused_host: device error word = " + std::to_string(err));
+    return LING_B200_ERR_DEVICE_FLAG;
+  }
+  LB_CUDA(cudaMemcpy(pre, d_pre, size_t(n) * C * 4, cudaMemcpyDeviceToHost));
+  LB_CUDA(cudaMemcpy(post, d_post, size_t(n) * C * 4, cudaMemcpyDeviceToHost));
+  LB_CUDA(cudaMemcpy(core, d_core, size_t(n) * Vs * 4, cudaMemcpyDeviceToHost));
+  LB_CUDA(cudaMemcpy(out_codes, d_codes, size_t(n) * Vs, cudaMemcpyDeviceToHost));
+  std::vector<float> sc_host(size_t(KB) * d.rows_alloc);
+  LB_CUDA(cudaMemcpy(sc_host.data(), d_scales, sc_host.size() * 4, cudaMemcpyDeviceToHost));
+  for (int m = 0; m < n; ++m)
+    for (int b = 0; b < KB; ++b) out_scales[size_t(m) * KB + b] = sc_host[size_t(b) * d.rows_alloc + m];
   return LING_B200_OK;
 }
 

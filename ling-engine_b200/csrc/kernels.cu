@@ -613,7 +613,7 @@ __global__ void __launch_bounds__(512)
                      const float* __restrict__ conv_state, size_t conv_slot_stride, const float* __restrict__ g,
                      const float* __restrict__ beta, const float* __restrict__ state, size_t state_slot_stride,
                      const __nv_bfloat16* __restrict__ norm_w, QuantOut q, float* __restrict__ pre, float* __restrict__ post,
-                     int n_slots, PrefetchPlan plan, unsigned long long* stamps) {
+                     float* __restrict__ core_out, int n_slots, PrefetchPlan plan, unsigned long long* stamps) {
   const bool stamp = stamps != nullptr && blockIdx.x == 0 && threadIdx.x == 0;
   if (stamp) stamps[0] = gtime_ns();
   using F = GdnFused<DK>;
@@ -829,7 +829,10 @@ __global__ void __launch_bounds__(512)
       const float kq = kqs[hb_t * kTreeRows + t];
       const float o = (st_i & kLeaf) ? St::token2(S, qkt, vv[t * 128 + colb], gbt[0], gbt[1], kq, quarter, false)   // block-uniform
                                      : St::token2(S, qkt, vv[t * 128 + colb], gbt[0], gbt[1], kq, quarter, true);
-      if ((st_i & kWrite) && quarter == 0) osm[t * 128 + colb] = o;
+      if ((st_i & kWrite) && quarter == 0) {
+        osm[t * 128 + colb] = o;
+        if (core_out) core_out[size_t(r0 + t) * d.Vs + qb * 128 + colb] = o;  // the recurrence's output before the gated norm (parity checks)
+      }
     }
     __syncthreads();
     if (stamp && item == blockIdx.x) stamps[5] = gtime_ns();
@@ -1787,7 +1790,7 @@ bool gdn_fused_supported(const ModelDims& d) {
 
 int gdn_fused_launch(const Planes& in, const StepBuffers& sb, const ModelDims& d, const __nv_bfloat16* convw, const float* conv_state,
                      size_t conv_slot_stride, const float* g, const float* beta, const float* state, size_t state_slot_stride,
-                     const __nv_bfloat16* norm_w, const QuantOut& q, float* pre, float* post, int n_slots, int grid,
+                     const __nv_bfloat16* norm_w, const QuantOut& q, float* pre, float* post, float* core_out, int n_slots, int grid,
                      const PrefetchPlan& plan, unsigned long long* stamps, cudaStream_t s) {
   if (!gdn_fused_supported(d)) {
     set_error("fused DeltaNet kernel: key dim = value dim = 64 or 128 expected");
@@ -1795,10 +1798,10 @@ int gdn_fused_launch(const Planes& in, const StepBuffers& sb, const ModelDims& d
   }
   if (d.Dk == 128)
     LB_CUDA(launch_kernel(gdn_fused_kernel<128>, dim3(grid), dim3(512), GdnFused<128>::smem_floats() * 4, s, in, sb, d, convw, conv_state,
-                          conv_slot_stride, g, beta, state, state_slot_stride, norm_w, q, pre, post, n_slots, plan, stamps));
+                          conv_slot_stride, g, beta, state, state_slot_stride, norm_w, q, pre, post, core_out, n_slots, plan, stamps));
   else
     LB_CUDA(launch_kernel(gdn_fused_kernel<64>, dim3(grid), dim3(512), GdnFused<64>::smem_floats() * 4, s, in, sb, d, convw, conv_state,
-                          conv_slot_stride, g, beta, state, state_slot_stride, norm_w, q, pre, post, n_slots, plan, stamps));
+                          conv_slot_stride, g, beta, state, state_slot_stride, norm_w, q, pre, post, core_out, n_slots, plan, stamps));
   LB_LAUNCH("gdn_fused_kernel");
   return LING_B200_OK;
 }

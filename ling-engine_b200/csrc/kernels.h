@@ -160,8 +160,8 @@ int gdn_tree_launch(const float* post, const float* g, const float* beta, const 
 bool gdn_fused_supported(const ModelDims& d);
 int gdn_fused_launch(const Planes& in, const StepBuffers& sb, const ModelDims& d, const __nv_bfloat16* convw, const float* conv_state,
                      size_t conv_slot_stride, const float* g, const float* beta, const float* state, size_t state_slot_stride,
-                     const __nv_bfloat16* norm_w, const QuantOut& q, float* pre, float* post, int n_slots, int grid,
-                     const PrefetchPlan& plan, unsigned long long* stamps, cudaStream_t s);  // n_slots: sessions the state holds; stamps: seven %globaltimer values of block 0's first item (debugging aid) or nullptr
+                     const __nv_bfloat16* norm_w, const QuantOut& q, float* pre, float* post, float* core_out, int n_slots, int grid,
+                     const PrefetchPlan& plan, unsigned long long* stamps, cudaStream_t s);  // core_out: [rows][HV * Dv] the recurrence's output before the gated norm, or nullptr; n_slots: sessions the state holds; stamps: seven %globaltimer values of block 0's first item (debugging aid) or nullptr
 int gated_norm_quant_launch(const float* core, const Planes& z, int z_col, const __nv_bfloat16* w, const QuantOut& q,
                             const int* n_rows, int rows_grid, int HV, int Dv, float eps, cudaStream_t s);
 int attn_prepare_launch(const Planes& qkv, const StepBuffers& sb, const ModelDims& d, int al, const __nv_bfloat16* q_norm,

@@ -728,15 +728,17 @@ int lo_kv_read(lo_model* m, int slot, int al, int from, int n, float* k, float* 
 
 int lo_synth_kv(lo_model* m, int slot, int n, uint64_t seed) {
   const int Hkv = m->cfg.kv_heads, D = m->cfg.head_dim;
-  std::vector<float> x(D);
   for (int al = 0; al < m->n_attn; ++al)
     for (int kv = 0; kv < 2; ++kv) {
-      const uint64_t stream = kStreamKv + (uint64_t(slot) * m->n_attn + al) * 2 + kv;
-      for (int p = 0; p < n; ++p)
-        for (int h = 0; h < Hkv; ++h) {
-          lo_synth(seed, stream, (size_t(p) * Hkv + h) * D, D, 1.f, 0.f, 0, x.data());
-          kv_store(m, slot, al, kv, h, p, x.data());
-        }
+      const uint64_t key = stream_key(seed, kStreamKv + (uint64_t(slot) * m->n_attn + al) * 2 + kv);
+      parallel_for(n, [&](int p_lo, int p_hi) {
+        std::vector<float> x(D);
+        for (int p = p_lo; p < p_hi; ++p)
+          for (int h = 0; h < Hkv; ++h) {
+            for (int d = 0; d < D; ++d) x[d] = synth_z(key, (size_t(p) * Hkv + h) * D + d);
+            kv_store(m, slot, al, kv, h, p, x.data());
+          }
+      });
     }
   return 0;
 }
@@ -850,67 +852,74 @@ int pack_step(lo_model* m, const lo_seq_step* seqs, int n_seqs) {
 
 // Row r sees the context [0, pos) and the rows of its own root-to-row path (src/core/attention_body.cuh:175-195,289-294);
 // scores q.k / sqrt(D), softmax and the value sum in double; K and V as the cache holds them (E4M3 codes x the
-// position's scale).  out [M][Hq][D], before the output gate.
+// position's scale).  out [M][Hq][D], before the output gate.  Per (sequence, kv head) the codes of every position the
+// sequence can see are decoded once and shared by its rows and the q heads of the group (the arithmetic per row is the
+// same as decoding them on the fly).
 void attend(lo_model* m, const lo_seq_step* seqs, int al, const float* q, float* out) {
   const lo_model_config& c = m->cfg;
-  const int Hq = c.heads, D = c.head_dim, G = c.heads / c.kv_heads, pt = m->opt.page_tokens, M = m->rows;
+  const int Hq = c.heads, Hkv = c.kv_heads, D = c.head_dim, G = Hq / Hkv, pt = m->opt.page_tokens;
   const float inv_sqrt_d = 1.f / std::sqrt(float(D));
-  parallel_for(M, [&](int r_lo, int r_hi) {
-    for (int r = r_lo; r < r_hi; ++r) {
-      const int s = m->seq_of[r], slot = seqs[s].slot, pos0 = seqs[s].pos;
-      std::vector<int> keys;
-      for (int p = 0; p < pos0; ++p) keys.push_back(p);
-      for (int j = 0; j < seqs[s].n_rows; ++j)
-        if (m->anc[r] >> j & 1) keys.push_back(pos0 + j);
-      std::vector<float> sc(keys.size());
-      std::vector<double> acc(D);
-      for (int hq = 0; hq < Hq; ++hq) {
-        const int hk = hq / G;
-        const float* qv = &q[(size_t(r) * Hq + hq) * D];
-        float mx = -INFINITY;
-        for (size_t i = 0; i < keys.size(); ++i) {
-          const size_t at = m->kv_index(al, 0, hk, m->tables[slot][keys[i] / pt], keys[i] % pt);
-          double dot = 0;
-          for (int d = 0; d < D; ++d) dot += double(qv[d]) * g_dec[m->kv_codes[at * D + d]];
-          sc[i] = float(dot) * m->kv_scales[at] * inv_sqrt_d;
-          mx = std::max(mx, sc[i]);
+  for (int s = 0; s < m->n_seqs; ++s) {
+    const int slot = seqs[s].slot, pos0 = seqs[s].pos, n = seqs[s].n_rows, nk = pos0 + n, r0 = m->row0[s];
+    std::vector<float> kd(size_t(nk) * D), vd(size_t(nk) * D), ksc(nk), vsc(nk);
+    for (int hk = 0; hk < Hkv; ++hk) {
+      parallel_for(nk, [&](int lo, int hi) {
+        for (int p = lo; p < hi; ++p) {
+          const size_t ak = m->kv_index(al, 0, hk, m->tables[slot][p / pt], p % pt);
+          const size_t av = m->kv_index(al, 1, hk, m->tables[slot][p / pt], p % pt);
+          ksc[p] = m->kv_scales[ak], vsc[p] = m->kv_scales[av];
+          for (int d = 0; d < D; ++d) kd[size_t(p) * D + d] = g_dec[m->kv_codes[ak * D + d]];
+          for (int d = 0; d < D; ++d) vd[size_t(p) * D + d] = g_dec[m->kv_codes[av * D + d]];
         }
-        double den = 0;
-        std::fill(acc.begin(), acc.end(), 0.0);
-        for (size_t i = 0; i < keys.size(); ++i) {
-          const size_t at = m->kv_index(al, 1, hk, m->tables[slot][keys[i] / pt], keys[i] % pt);
-          const double p = std::exp(double(sc[i] - mx));
-          den += p;
-          const double pv = p * m->kv_scales[at];
-          for (int d = 0; d < D; ++d) acc[d] += pv * g_dec[m->kv_codes[at * D + d]];
+      });
+      parallel_for(n * G, [&](int lo, int hi) {
+        std::vector<float> sc(nk);
+        std::vector<double> acc(D);
+        for (int u = lo; u < hi; ++u) {
+          const int r = r0 + u / G, hq = hk * G + u % G;
+          const float* qv = &q[(size_t(r) * Hq + hq) * D];
+          auto visible = [&](int p) { return p < pos0 || ((m->anc[r] >> (p - pos0)) & 1u); };
+          float mx = -INFINITY;
+          for (int p = 0; p < nk; ++p) {
+            if (!visible(p)) continue;
+            const float* kr = &kd[size_t(p) * D];
+            double dot = 0;
+            for (int d = 0; d < D; ++d) dot += double(qv[d]) * kr[d];
+            sc[p] = float(dot) * ksc[p] * inv_sqrt_d;
+            mx = std::max(mx, sc[p]);
+          }
+          double den = 0;
+          std::fill(acc.begin(), acc.end(), 0.0);
+          for (int p = 0; p < nk; ++p) {
+            if (!visible(p)) continue;
+            const double pr = std::exp(double(sc[p] - mx));
+            den += pr;
+            const double pv = pr * vsc[p];
+            const float* vr = &vd[size_t(p) * D];
+            for (int d = 0; d < D; ++d) acc[d] += pv * vr[d];
+          }
+          for (int d = 0; d < D; ++d) out[(size_t(r) * Hq + hq) * D + d] = float(acc[d] / den);
         }
-        for (int d = 0; d < D; ++d) out[(size_t(r) * Hq + hq) * D + d] = float(acc[d] / den);
-      }
+      });
     }
-  });
+  }
 }
 
-int step_impl(lo_model* m, const lo_seq_step* seqs, int n_seqs, int flags, lo_seq_result* results,
-              const StepScope& scope) {
+// What a DeltaNet layer keeps for the commit (src/core/engine.hpp:846-848): raw and convolved inputs, gates.
+struct Saved {
+  std::vector<std::vector<float>> pre, post, g, beta;
+  explicit Saved(int n_gdn) : pre(n_gdn), post(n_gdn), g(n_gdn), beta(n_gdn) {}
+};
+
+// One layer of the forward pass over the packed rows (src/core/engine.cpp:1361-1725): h [M][H] is the residual stream
+// before the layer on entry and after it on return.  pack_step() has run.
+void layer_forward(lo_model* m, const lo_seq_step* seqs, int n_seqs, int l, std::vector<float>& h, Saved& saved) {
   const lo_model_config& c = m->cfg;
   const int H = c.hidden, I = c.intermediate, Hq = c.heads, Hkv = c.kv_heads, D = c.head_dim;
   const int Hk = c.lin_k_heads, HV = c.lin_v_heads, Dk = c.lin_k_dim, Dv = c.lin_v_dim, C = m->C(), Vs = m->Vs();
-  const int G = Hq / Hkv, pt = m->opt.page_tokens;
-  if (const int rc = pack_step(m, seqs, n_seqs)) return rc;
   const int M = m->rows;
-
-  // B.1 embedding (src/core/kernels.cu:280-286)
-  std::vector<float> h(size_t(M) * H), xn(size_t(M) * H);
-  for (int r = 0; r < M; ++r)
-    for (int i = 0; i < H; ++i) h[size_t(r) * H + i] = m->embed[size_t(m->token[r]) * H + i];
-
-  const bool taps = flags & 4;
-  if (taps) m->taps.assign(c.layers + 1, {});
-  // per DeltaNet layer, saved for the commit (src/core/engine.hpp:846-848)
-  std::vector<std::vector<float>> s_pre(m->n_gdn), s_post(m->n_gdn), s_g(m->n_gdn), s_beta(m->n_gdn);
-
-  for (int l = 0; l < c.layers; ++l) {
-    if (!scope.run(l)) continue;
+  std::vector<float> xn(size_t(M) * H);
+  {
     const Layer& L = m->layers[l];
     for (int r = 0; r < M; ++r) rmsnorm(&h[size_t(r) * H], L.input_norm.data(), &xn[size_t(r) * H], H, c.eps, true);
     QAct xq;
@@ -987,7 +996,7 @@ int step_impl(lo_model* m, const lo_seq_step* seqs, int n_seqs, int flags, lo_se
       std::vector<float> o(size_t(M) * H);
       gemm(nq, L.out, o.data(), H, 0);
       for (size_t i = 0; i < h.size(); ++i) h[i] += o[i];
-      s_pre[gl] = std::move(pre), s_post[gl] = std::move(post), s_g[gl] = std::move(g), s_beta[gl] = std::move(beta);
+      saved.pre[gl] = std::move(pre), saved.post[gl] = std::move(post), saved.g[gl] = std::move(g), saved.beta[gl] = std::move(beta);
     }
     // B.5 SwiGLU FFN (src/core/engine.cpp:1698-1703, src/core/kernels.cu:308-312)
     for (int r = 0; r < M; ++r) rmsnorm(&h[size_t(r) * H], L.post_norm.data(), &xn[size_t(r) * H], H, c.eps, true);
@@ -1002,19 +1011,52 @@ int step_impl(lo_model* m, const lo_seq_step* seqs, int n_seqs, int flags, lo_se
     tq.set(t.data(), M, I);
     gemm(tq, L.down, dn.data(), H, 0);
     for (size_t i = 0; i < h.size(); ++i) h[i] += dn[i];
-    if (taps) m->taps[l] = h;
   }
+}
 
-  // B.6 final norm, head over every row, argmax (src/core/engine.cpp:1726-1733, src/core/topk.cu)
+// B.6 final norm and head over every row, argmax (src/core/engine.cpp:1726-1733, src/core/topk.cu): xn = the normed
+// rows, logits and argmax kept in the model for the read-backs.
+void head_forward(lo_model* m, const std::vector<float>& h, std::vector<float>& xn, int head_rows) {
+  const lo_model_config& c = m->cfg;
+  const int H = c.hidden, M = m->rows;
+  xn.resize(size_t(M) * H);
   for (int r = 0; r < M; ++r) rmsnorm(&h[size_t(r) * H], m->final_norm.data(), &xn[size_t(r) * H], H, c.eps, true);
-  if (taps) m->taps[c.layers] = xn;
   QAct hq8;
   hq8.set(xn.data(), M, H);
-  const int Vn = scope.head_rows >= 0 ? std::min(scope.head_rows, c.vocab) : c.vocab;
+  const int Vn = head_rows >= 0 ? std::min(head_rows, c.vocab) : c.vocab;
   m->logits.assign(size_t(M) * Vn, 0.f);
   gemm(hq8, m->head, m->logits.data(), Vn, 0, Vn);
   m->argmax_id.resize(M), m->argmax_val.resize(M);
   lo_argmax(m->logits.data(), M, Vn, m->argmax_id.data(), m->argmax_val.data());
+}
+
+int step_impl(lo_model* m, const lo_seq_step* seqs, int n_seqs, int flags, lo_seq_result* results,
+              const StepScope& scope) {
+  const lo_model_config& c = m->cfg;
+  const int H = c.hidden, Hkv = c.kv_heads, D = c.head_dim;
+  const int Hk = c.lin_k_heads, HV = c.lin_v_heads, Dk = c.lin_k_dim, Dv = c.lin_v_dim, C = m->C();
+  const int pt = m->opt.page_tokens;
+  if (const int rc = pack_step(m, seqs, n_seqs)) return rc;
+  const int M = m->rows;
+
+  // B.1 embedding (src/core/kernels.cu:280-286)
+  std::vector<float> h(size_t(M) * H), xn;
+  for (int r = 0; r < M; ++r)
+    for (int i = 0; i < H; ++i) h[size_t(r) * H + i] = m->embed[size_t(m->token[r]) * H + i];
+
+  const bool taps = flags & 4;
+  if (taps) m->taps.assign(c.layers + 1, {});
+  Saved saved(m->n_gdn);
+  std::vector<std::vector<float>>&s_pre = saved.pre, &s_post = saved.post, &s_g = saved.g, &s_beta = saved.beta;
+
+  for (int l = 0; l < c.layers; ++l) {
+    if (!scope.run(l)) continue;
+    layer_forward(m, seqs, n_seqs, l, h, saved);
+    if (taps) m->taps[l] = h;
+  }
+
+  head_forward(m, h, xn, scope.head_rows);
+  if (taps) m->taps[c.layers] = xn;
   if (!results) return 0;
 
   // B.7 accept, compaction, commit
@@ -1076,6 +1118,60 @@ int lo_attention(lo_model* m, const lo_seq_step* seqs, int n_seqs, int attn_laye
   if (attn_layer < 0 || attn_layer >= m->n_attn) return 1;
   if (const int rc = pack_step(m, seqs, n_seqs)) return rc;
   attend(m, seqs, attn_layer, q, out);
+  return 0;
+}
+
+// One layer alone on a given residual stream (teacher forcing): h_in [rows][hidden] is what stands before layer `layer`,
+// h_out what stands after it; the layer's weights, the sessions' KV and DeltaNet state must be in place.  layer ==
+// cfg.layers: the final norm and the head instead (h_out = the normed rows; logits and argmax for the read-backs;
+// head_rows < 0: the whole vocabulary).
+int lo_layer_forward(lo_model* m, const lo_seq_step* seqs, int n_seqs, int layer, const float* h_in, float* h_out,
+                     int head_rows) {
+  if (layer < 0 || layer > m->cfg.layers) return 1;
+  if (const int rc = pack_step(m, seqs, n_seqs)) return rc;
+  const size_t n = size_t(m->rows) * m->cfg.hidden;
+  std::vector<float> h(h_in, h_in + n), xn;
+  if (layer == m->cfg.layers) {
+    head_forward(m, h, xn, head_rows);
+    std::copy(xn.begin(), xn.end(), h_out);
+    return 0;
+  }
+  Saved saved(m->n_gdn);
+  layer_forward(m, seqs, n_seqs, layer, h, saved);
+  std::copy(h.begin(), h.end(), h_out);
+  return 0;
+}
+
+// attn_prepare alone (src/core/kernels.cu:558-596, src/core/attention_body.cuh:54-99) for one full-attention layer:
+// qkv [rows][Hq*2*D + 2*Hkv*D] is the q|k|v projection's output (per q head: D query values then D gate values);
+// q_out [rows][Hq][D] the normed, rotated queries; k_out [rows][Hkv][D] (may be NULL) the normed, rotated keys BEFORE
+// the cache rounding; K (rotated) and V (raw) go to cache slot pos + row index as the step stores them.
+int lo_attn_prepare(lo_model* m, const lo_seq_step* seqs, int n_seqs, int attn_layer, const float* qkv, float* q_out,
+                    float* k_out) {
+  if (attn_layer < 0 || attn_layer >= m->n_attn) return 1;
+  if (const int rc = pack_step(m, seqs, n_seqs)) return rc;
+  const lo_model_config& c = m->cfg;
+  const int Hq = c.heads, Hkv = c.kv_heads, D = c.head_dim, W = Hq * 2 * D + 2 * Hkv * D;
+  int layer = -1;
+  for (int l = 0; l < c.layers; ++l)
+    if (m->attn_index[l] == attn_layer) layer = l;
+  const Layer& L = m->layers[layer];
+  if (int(L.q_norm.size()) != D || int(L.k_norm.size()) != D) return 1;
+  std::vector<float> kr(D);
+  for (int r = 0; r < m->rows; ++r) {
+    const int s = m->seq_of[r];
+    const float* row = qkv + size_t(r) * W;
+    for (int hq = 0; hq < Hq; ++hq)
+      norm_rope(row + size_t(hq) * 2 * D, L.q_norm.data(), &q_out[(size_t(r) * Hq + hq) * D], D, c.rotary_dim, c.rope_theta,
+                c.eps, m->rope_pos[r]);
+    for (int hk = 0; hk < Hkv; ++hk) {
+      norm_rope(row + size_t(Hq) * 2 * D + size_t(hk) * D, L.k_norm.data(), kr.data(), D, c.rotary_dim, c.rope_theta, c.eps,
+                m->rope_pos[r]);
+      if (k_out) std::copy(kr.begin(), kr.end(), &k_out[(size_t(r) * Hkv + hk) * D]);
+      kv_store(m, seqs[s].slot, attn_layer, 0, hk, m->cache_slot[r], kr.data());
+      kv_store(m, seqs[s].slot, attn_layer, 1, hk, m->cache_slot[r], row + size_t(Hq) * 2 * D + size_t(Hkv) * D + size_t(hk) * D);
+    }
+  }
   return 0;
 }
 

@@ -117,6 +117,12 @@ int lo_verify_step(lo_model* m, const lo_seq_step* seqs, int n_seqs, int flags, 
 int lo_verify_step_sample(lo_model* m, const lo_seq_step* seqs, int n_seqs, const int* layers, int n_layers,
                           int head_rows);
 int lo_attention(lo_model* m, const lo_seq_step* seqs, int n_seqs, int attn_layer, const float* q, float* out);
+/* one layer alone on a given residual stream (teacher forcing); layer == cfg.layers: the final norm and the head */
+int lo_layer_forward(lo_model* m, const lo_seq_step* seqs, int n_seqs, int layer, const float* h_in, float* h_out,
+                     int head_rows);
+/* attn_prepare alone: q|k|v projection rows in, normed + rotated q (and k before the cache rounding) out, K/V stored */
+int lo_attn_prepare(lo_model* m, const lo_seq_step* seqs, int n_seqs, int attn_layer, const float* qkv, float* q_out,
+                    float* k_out);
 int lo_read_tree_desc(lo_model* m, int seq, lo_tree_desc* out);
 int lo_read_packing(lo_model* m, int* row0, int* token, int* seq_of, int* depth, int* rope_pos, int* cache_slot,
                     uint32_t* anc_mask);

@@ -203,6 +203,28 @@ class Model:
         self.last_seqs = len(seqs)
         return out
 
+    def layer_forward(self, seqs, layer, h_in, head_rows=-1, make_steps=None):
+        """One layer alone on the residual rows h_in (layer == cfg.layers: the final norm and the head)."""
+        arr, keep = make_steps(seqs)
+        h_in = np.ascontiguousarray(h_in, np.float32)
+        out = np.zeros_like(h_in)
+        assert lo().lo_layer_forward(self.h, arr, len(seqs), layer, _fp(h_in), _fp(out), head_rows) == 0
+        self.last_rows = sum(len(s["tokens"]) for s in seqs)
+        self.last_seqs = len(seqs)
+        return out
+
+    def attn_prepare(self, seqs, attn_layer, qkv, make_steps=None):
+        """attn_prepare alone: returns (q [rows][heads][D], k before the cache rounding [rows][kv_heads][D])."""
+        arr, keep = make_steps(seqs)
+        qkv = np.ascontiguousarray(qkv, np.float32)
+        c = self.cfg
+        q = np.zeros((qkv.shape[0], c.heads, c.head_dim), np.float32)
+        k = np.zeros((qkv.shape[0], c.kv_heads, c.head_dim), np.float32)
+        assert lo().lo_attn_prepare(self.h, arr, len(seqs), attn_layer, _fp(qkv), _fp(q), _fp(k)) == 0
+        self.last_rows = sum(len(s["tokens"]) for s in seqs)
+        self.last_seqs = len(seqs)
+        return q, k
+
     def read_tree_desc(self, seq):
         t = self.S.TreeDesc()
         assert lo().lo_read_tree_desc(self.h, seq, C.byref(t)) == 0

@@ -238,3 +238,189 @@ def test_tree_attention_matches_oracle(gpu, lb, lo, shape, impl):
     assert np.isfinite(out_g).all()
     assert (np.abs(flat_g - flat_o) <= ATTN_TOL * rms).all(), float((np.abs(flat_g - flat_o) / rms).max())
     ctx.close(), m.close()
+
+
+# ---------------------------------------------------------------------------------------------- the fused DeltaNet kernel
+def bf16_round(a):
+    u = np.ascontiguousarray(a, np.float32).view(np.uint32)
+    return ((u + 0x7fff + ((u >> 16) & 1)) & 0xffff0000).astype(np.uint32).view(np.float32)
+
+
+def decode_fp8(lo, codes, scales):
+    """codes [rows][K] and scales [rows][K/128] back to fp32."""
+    return lo.e4m3_decode_table()[codes] * np.repeat(scales, 128, axis=1)[:, :codes.shape[1]]
+
+
+@pytest.mark.parametrize("pdl", [0, 1])
+@pytest.mark.parametrize("Hk,HV,Dk,Dv", [(2, 4, 64, 64), (16, 48, 128, 128)])
+@pytest.mark.parametrize("shape", ["two_branch", "random", "single", "full32", "three_sequences"])
+def test_fused_deltanet_kernel_matches_oracle(gpu, lb, lo, Hk, HV, Dk, Dv, shape, pdl):
+    # the kernel the 27B-class step launches between the in and the out projection (conv over the trees, q/k normalization,
+    # the delta rule along every DeltaNet path, gated RMSNorm, FP8 copy), alone on identical inputs; with dependent launch
+    # on it also loads its first item's state before the packing kernel ahead of it has completed and re-checks the choice
+    rng = np.random.default_rng(Dk + len(shape) + 7 * pdl)
+    if shape == "two_branch":
+        trees = [(helpers.chain_plus_branch(16, 8), 15)]
+    elif shape == "random":
+        trees = [(helpers.random_tree(rng, 24, 7), 7)]
+    elif shape == "single":
+        trees = [([-1], 0)]
+    elif shape == "full32":
+        trees = [(helpers.random_tree(rng, 32, 11), 11)]
+    else:
+        trees = [(helpers.chain_plus_branch(12, 5), 11), (helpers.random_tree(rng, 9, 3), 3), ([-1], 0)]
+    rows, n_seqs = sum(len(p) for p, _ in trees), len(trees)
+    Cn, Vs = 2 * Hk * Dk + HV * Dv, HV * Dv
+    d = gdn_inputs(rng, Hk, HV, Dk, Dv, rows)
+    convw = bf16_round(d["convw"])
+    inp = np.concatenate([d["pre"], rng.standard_normal((rows, Vs)).astype(np.float32)], axis=1)
+    state = (rng.standard_normal((n_seqs, HV, Dk, Dv)) * 0.1).astype(np.float32)
+    conv = rng.standard_normal((n_seqs, Cn, 3)).astype(np.float32)
+    norm_w = bf16_round(1.0 + rng.standard_normal(Dv).astype(np.float32) * 0.02)
+    eps = 1e-6
+    lb.lib().ling_b200_set_pdl(pdl)
+    try:
+        pre_g, post_g, core_g, codes_g, scales_g = lb.gdn_fused(Hk, HV, Dk, Dv, trees, inp, convw, d["g"], d["beta"], state, conv,
+                                                                norm_w, eps)
+    finally:
+        lb.lib().ling_b200_set_pdl(0)
+    # the oracle, sequence by sequence
+    post_o, core_o = np.zeros((rows, Cn), np.float32), np.zeros((rows, Vs), np.float32)
+    r0 = 0
+    for s, (parent, chain) in enumerate(trees):
+        n = len(parent)
+        rc, td = lb.describe_tree(parent, chain)
+        assert rc == 0
+        po, co = np.zeros((n, Cn), np.float32), np.zeros((n, Vs), np.float32)
+        sl = slice(r0, r0 + n)
+        lo.lo().lo_gdn_tree(Hk, HV, Dk, Dv, C.byref(td), fp(np.ascontiguousarray(d["pre"][sl])), fp(convw),
+                            fp(np.ascontiguousarray(d["g"][sl])), fp(np.ascontiguousarray(d["beta"][sl])),
+                            fp(np.ascontiguousarray(state[s])), fp(np.ascontiguousarray(conv[s])), fp(po), fp(co))
+        post_o[sl], core_o[sl] = po, co
+        r0 += n
+    assert np.array_equal(pre_g, d["pre"])                         # the raw inputs kept for the commit: a copy
+    post_n = post_o.copy()                                         # the device's q and k are already L2-normalized
+    for h in range(2 * Hk):
+        seg = post_o[:, h * Dk:(h + 1) * Dk].astype(np.float64)
+        scale = 1.0 / np.sqrt((seg ** 2).sum(axis=1, keepdims=True) + 1e-6) / (np.sqrt(Dk) if h < Hk else 1.0)
+        post_n[:, h * Dk:(h + 1) * Dk] = (seg * scale).astype(np.float32)
+    assert np.abs(post_g - post_n).max() <= 1e-5 * max(1.0, np.abs(post_n).max())
+    assert np.abs(core_g - core_o).max() <= GDN_TOL * np.sqrt((core_o ** 2).mean())
+    # gated RMSNorm with the plain weight times silu(z), then the FP8 copy (one scale per row per 128 columns)
+    z = inp[:, Cn:].astype(np.float64)
+    co = core_o.astype(np.float64).reshape(rows, HV, Dv)
+    normed = (co / np.sqrt((co ** 2).mean(axis=2, keepdims=True) + eps) * norm_w.astype(np.float64)).reshape(rows, Vs)
+    normed = (normed * z / (1.0 + np.exp(-z))).astype(np.float32)
+    codes_o, scales_o = lo.quant_rows(normed)
+    assert np.allclose(scales_g, scales_o, rtol=1e-4, atol=1e-30)
+    deq_g, deq_o = decode_fp8(lo, codes_g, scales_g), decode_fp8(lo, codes_o, scales_o)
+    flipped = codes_g != codes_o
+    assert flipped.mean() <= 2e-3, float(flipped.mean())         # fp32-vs-double differences that straddle a rounding boundary
+    step = np.maximum(np.abs(deq_o), np.repeat(scales_o, 128, axis=1)) * 0.13   # one E4M3 step is at most 12.5% of the value
+    assert (np.abs(deq_g - deq_o) <= step + 1e-6).all()
+    rms = np.sqrt((normed.astype(np.float64) ** 2).mean(axis=1, keepdims=True)) + 1e-30
+    assert np.median(np.abs(deq_g - deq_o).max(axis=1) / rms[:, 0]) <= 0.07
+
+
+# ---------------------------------------------------------------------------------------------- attn_prepare
+def test_attn_prepare_matches_oracle_at_large_positions(gpu, lb, lo):
+    # the prepare kernel alone (head norms with (1 + w), rotation of the first 64 of 256 dims, K and V into the paged FP8
+    # cache) at positions 0 .. 131000 against the oracle's norm_rope / kv_store.  The rotation angle is position x
+    # theta^(-2i/rot); the device evaluates the power with powf (as the reference's kernel does, attention_body.cuh:87-93),
+    # the oracle with a correctly rounded pow, so the angles may differ by a few ulp of position x inv_freq: the bar on the
+    # rotated dims grows with the position (8 ulp of the largest angle), the unrotated dims are held to 1e-5.
+    cfg = lb.make_config(5120, 128, 1, 4096, 24, 4, 256, 64, 16, 48, 128, 128, [1])
+    positions, page_tokens = (0, 1529, 8192, 60000, 131000), 16
+    n_seq, max_ctx = len(positions), 131072 + 64
+    ctx = lb.Context(cfg, sessions=n_seq, max_context=max_ctx, page_tokens=page_tokens, pool_pages=64, max_seqs=n_seq,
+                     max_rows=32 * n_seq)
+    opt = lb.Options(n_seq, max_ctx, page_tokens, 64, n_seq, 32 * n_seq, 0, 0, 0, 0, 0)
+    m = lo.Model(cfg, opt, lb)
+    ctx.synth_weights(2), m.synth_weights(2)
+    rng = np.random.default_rng(21)
+    seqs, page = [], 1
+    for s, pos in enumerate(positions):
+        n = (32, 24, 9, 17, 32)[s]
+        chain = int(rng.integers(0, n))
+        seqs.append({"slot": s, "pos": pos, "tokens": np.zeros(n, np.int32), "parent": np.array(helpers.random_tree(rng, n, chain), np.int32),
+                     "chain": chain, "rope_delta": (0, 0, -5, 0, 0)[s]})
+        idx = np.arange(pos // page_tokens, (pos + n - 1) // page_tokens + 1, dtype=np.int32)   # only the pages the rows land in
+        pages = np.arange(page, page + len(idx), dtype=np.int32)
+        page += len(idx)
+        for t in (ctx, m):
+            t.kv_table_set(s, idx, pages)
+    rows = sum(len(q["tokens"]) for q in seqs)
+    W = cfg.heads * 2 * cfg.head_dim + 2 * cfg.kv_heads * cfg.head_dim
+    qkv = (rng.standard_normal((rows, W)) * np.exp(rng.standard_normal((rows, 1)))).astype(np.float32)
+    q_o, k_o = m.attn_prepare(seqs, 0, qkv, make_steps=lb.make_steps)
+    q_g = ctx.attn_prepare(seqs, 0, qkv)
+    pk = ctx.read_packing()
+    assert np.array_equal(pk["rope_pos"], m.read_packing()["rope_pos"])
+    rot, ulp = cfg.rotary_dim, 2.0 ** -23
+    for r in range(rows):
+        # per row: the unrotated dims at FP16 precision (q is kept as FP16 for the tensor-core product) ...
+        amax = np.abs(q_o[r]).max()
+        assert np.abs(q_g[r, :, rot:] - q_o[r, :, rot:]).max() <= 2.0 ** -10 * amax + 1e-5
+        # ... the rotated ones with the angle's uncertainty on top
+        ang_tol = 8 * ulp * max(1.0, abs(float(pk["rope_pos"][r])))
+        assert np.abs(q_g[r, :, :rot] - q_o[r, :, :rot]).max() <= (2.0 ** -10 + ang_tol) * amax * 1.5 + 1e-5, (r, int(pk["rope_pos"][r]))
+    flips_k = total = 0
+    for s, q in enumerate(seqs):
+        n = len(q["tokens"])
+        kc_g, ks_g, vc_g, vs_g = ctx.kv_read(s, 0, q["pos"], n, codes=True)
+        kc_o, ks_o, vc_o, vs_o = m.kv_read(s, 0, q["pos"], n, codes=True)
+        assert np.array_equal(vc_g, vc_o) and np.array_equal(vs_g, vs_o)      # V is stored raw: bit-exact
+        assert np.allclose(ks_g, ks_o, rtol=1e-4 + 8 * ulp * max(1, q["pos"]))
+        flips_k += int((kc_g != kc_o).sum())
+        total += kc_o.size
+        dec = lo.e4m3_decode_table()
+        kg, ko = dec[kc_g] * ks_g[..., None], dec[kc_o] * ks_o[..., None]
+        assert np.abs(kg - ko).max() <= 0.13 * np.abs(ko).max()              # a flipped code is one FP8 step
+        if q["pos"] <= 8192:
+            assert (kc_g != kc_o).mean() <= 2e-3
+    assert flips_k / total <= 0.05, flips_k / total
+    ctx.close(), m.close()
+
+
+# ---------------------------------------------------------------------------------------------- attention: the reference's matrix
+@pytest.mark.parametrize("page_tokens", [16, 64])
+def test_tree_attention_at_the_reference_matrix_of_contexts(gpu, lb, lo, page_tokens):
+    # contexts x rows of the reference's paged attention test (tests/paged_tests.cu:183-196: contexts around the page and
+    # range boundaries and up to 131072, rows 1..32), at the 27B head shape (24 q / 4 kv heads of 256): every context is one
+    # sequence of the same call, its tree a random one of the given size.  Hundreds of flash-decoding chunks per row at the
+    # long end, the page window across chunk boundaries, both page sizes.
+    cfg = lb.make_config(5120, 128, 1, 4096, 24, 4, 256, 64, 16, 48, 128, 128, [1])
+    contexts = (1, 33, 63, 64, 65, 127, 4095, 4096, 4097, 8192, 27000, 60000, 131008)
+    row_counts = (1, 12, 24, 32)
+    n_seq, max_ctx = len(contexts), 131072 + 64
+    pool = sum((c + 32 + page_tokens - 1) // page_tokens for c in contexts) + 1
+    ctx = lb.Context(cfg, sessions=n_seq, max_context=max_ctx, page_tokens=page_tokens, pool_pages=pool, max_seqs=n_seq,
+                     max_rows=32 * n_seq)
+    opt = lb.Options(n_seq, max_ctx, page_tokens, pool, n_seq, 32 * n_seq, 0, 0, 0, 0, 0)
+    m = lo.Model(cfg, opt, lb)
+    lo.lo().lo_set_threads(16)
+    rng = np.random.default_rng(100 + page_tokens)
+    seqs, page = [], 1
+    for s, c in enumerate(contexts):
+        n = row_counts[(s + 1) % 4]
+        chain = int(rng.integers(0, n))
+        seqs.append({"slot": s, "pos": c, "tokens": np.zeros(n, np.int32), "parent": np.array(helpers.random_tree(rng, n, chain), np.int32),
+                     "chain": chain})
+        page += helpers.map_pages([ctx, m], s, c + 32, page_tokens, page)
+        k = rng.standard_normal((n, cfg.kv_heads, cfg.head_dim)).astype(np.float32)
+        v = (rng.standard_normal((n, cfg.kv_heads, cfg.head_dim)) * 3).astype(np.float32)
+        for t in (ctx, m):
+            t.synth_kv(s, c, 9)
+            t.kv_write(s, 0, c, k, v)
+    rows = sum(len(q["tokens"]) for q in seqs)
+    q = rng.standard_normal((rows, cfg.heads, cfg.head_dim)).astype(np.float32)
+    out_o = m.attention(seqs, 0, q, make_steps=lb.make_steps).reshape(rows, -1)
+    out_g = ctx.attention(seqs, 0, q).reshape(rows, -1)
+    rms = np.sqrt((out_o.astype(np.float64) ** 2).mean(axis=1, keepdims=True))
+    err = np.abs(out_g - out_o) / rms
+    assert np.isfinite(out_g).all()
+    row0 = np.cumsum([0] + [len(q_["tokens"]) for q_ in seqs])
+    worst = {contexts[s]: float(err[row0[s]:row0[s + 1]].max()) for s in range(n_seq)}
+    assert err.max() <= ATTN_TOL, worst
+    lo.lo().lo_set_threads(1)
+    ctx.close(), m.close()
