@@ -75,7 +75,7 @@ def workload(name, rank, vocab):
         ctxs = np.clip(all_rng.lognormal(np.log(6000.0), 1.0, 64), 256, 131072 - 64).astype(int)
         sizes = all_rng.integers(1, 33, 64)
         specs = []
-        for i in range(rank, 64, world):
+        for i in shard_sequences([int(c) for c in ctxs], world)[rank]:   # whole sequences, KV positions balanced over the GPUs
             n = int(sizes[i])
             chain_rows = max(1, (2 * n + 2) // 3)
             specs.append((int(ctxs[i]), chain_plus_branch(chain_rows, n - chain_rows), chain_rows - 1))
@@ -226,6 +226,13 @@ class Dist:
     def sum(self, x):
         return self._reduce(x, self.dist.ReduceOp.SUM if self.world > 1 else None)
 
+    def select(self, rank, x):
+        """Rank `rank`'s value of x on every rank (a sum in which the others contribute zero)."""
+        if self.world == 1:
+            return x
+        me = self.dist.get_rank()
+        return self._reduce(x if me == rank else 0.0, self.dist.ReduceOp.SUM)
+
     def close(self):
         if self.world > 1:
             self.dist.destroy_process_group()
@@ -333,18 +340,11 @@ def run_reference(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
-def run_ours(args, rank, local_rank, world):
-    lbm = importlib.import_module("ling-engine_b200")
-    lbm.lib()
-    if lbm.lib().ling_b200_device_count() < 1:
-        raise SystemExit("bench.py: no CUDA device; the product has no CPU path")
-    dist = Dist(world, local_rank)
-    cfg = model_for(lbm, args.workload, args.layers)
-    seqs = workload(args.workload, rank, cfg.vocab)
+def setup_context(lbm, cfg, seqs, args, rank, local_rank, churn):
+    """A context sized for `seqs` with synthetic weights, page tables from the page pool, synthetic KV and DeltaNet state."""
     rows = sum(len(q["tokens"]) for q in seqs)
     page_tokens = 16
     pages = sum((q["pos"] + 64 + page_tokens - 1) // page_tokens for q in seqs) + 1
-    churn = args.workload == "churn64"
     max_context = 131072 if churn else max(q["pos"] for q in seqs) + 64
     if churn:
         pages = int(pages * 1.25)   # room for admissions that are longer than the completions they replace
@@ -358,24 +358,69 @@ def run_ours(args, rank, local_rank, world):
         ctx.kv_table_set(q["slot"], np.arange(len(table), dtype=np.int32), table)
         ctx.synth_kv(q["slot"], q["pos"], rank)
         ctx.synth_state(q["slot"], rank)
-    flags = lbm.STEP_COMMIT
-    clocks = ClockSampler(local_rank)
+    return ctx, pool, max_context
 
-    # ---- device-timed: descriptors staged once, K graph replays
+
+def device_timed_steps(ctx, dist, seqs, flags, steps, warmup):
+    """Descriptors staged once, `warmup` untimed graph replays, then `steps` replays between two CUDA events on the
+    context's stream, bracketed by a barrier + synchronize on both sides.  Returns this rank's milliseconds."""
     ctx.stage(seqs, flags)
-    for _ in range(args.warmup if args.quick else max(args.warmup, 3)):
+    for _ in range(warmup):
         ctx.launch()
     res = ctx.fetch()
     assert all(r.status == 0 and r.n_path == q["accept"] for r, q in zip(res, seqs)), "acceptance differs from the imposed paths"
     dist.barrier()
-    clocks.start()
     ctx.sync()
     ctx.timer_begin()
-    for _ in range(args.steps):
+    for _ in range(steps):
         ctx.launch()
     ms = ctx.timer_end()
     ctx.sync()
     dist.barrier()
+    return ms
+
+
+def churn64_sharded(lbm, dist, args, rank, local_rank, world):
+    """The 64-sequence batch (contexts lognormal up to 128k, trees of 1-32 rows) sharded by sequence over the ranks (whole
+    sequences, KV positions balanced: shard_sequences), timed on the device: total work fixed, so strong scaling.  Each
+    rank reads the full weights for its share of the rows; no data-path collective."""
+    cfg = model_for(lbm, "churn64", args.layers)
+    seqs = workload("churn64", rank, cfg.vocab)
+    ctx, _, _ = setup_context(lbm, cfg, seqs, args, rank, local_rank, True)
+    steps = max(3, min(args.steps, 10))
+    ms = device_timed_steps(ctx, dist, seqs, lbm.STEP_COMMIT, steps, 3) / steps
+    fam, _ = ctx.profile_step()
+    ctx.fetch()
+    ctx.close()
+    rows, kv_pos, accept = sum(len(q["tokens"]) for q in seqs), sum(q["pos"] for q in seqs), sum(q["accept"] for q in seqs)
+    worst = dist.max(ms)
+    per_rank = [dist.select(r, v) for r in range(world) for v in (rows, kv_pos, ms)]
+    return {"sequences": 64, "scaling": "strong", "sharding": "whole sequences, KV positions balanced (longest first onto the lightest GPU)",
+            "steps": steps, "ms_per_step": worst, "tokens_per_s": dist.sum(rows) / (worst * 1e-3),
+            "accepted_tokens_per_s": dist.sum(accept) / (worst * 1e-3),
+            "per_rank": [{"rows": int(per_rank[3 * r]), "kv_positions": int(per_rank[3 * r + 1]), "ms_per_step": per_rank[3 * r + 2]}
+                         for r in range(world)],
+            "rank0_family_ms": {"weight_gemms": fam[0], "attention": fam[1], "deltanet": fam[2], "norm_quant_elementwise": fam[3],
+                                "head_argmax": fam[4], "pack_accept_compact_commit": fam[5]}}
+
+
+def run_ours(args, rank, local_rank, world):
+    lbm = importlib.import_module("ling-engine_b200")
+    lbm.lib()
+    if lbm.lib().ling_b200_device_count() < 1:
+        raise SystemExit("bench.py: no CUDA device; the product has no CPU path")
+    dist = Dist(world, local_rank)
+    cfg = model_for(lbm, args.workload, args.layers)
+    seqs = workload(args.workload, rank, cfg.vocab)
+    rows = sum(len(q["tokens"]) for q in seqs)
+    churn = args.workload == "churn64"
+    ctx, pool, max_context = setup_context(lbm, cfg, seqs, args, rank, local_rank, churn)
+    flags = lbm.STEP_COMMIT
+    clocks = ClockSampler(local_rank)
+
+    # ---- device-timed: descriptors staged once, K graph replays
+    clocks.start()
+    ms = device_timed_steps(ctx, dist, seqs, flags, args.steps, args.warmup if args.quick else max(args.warmup, 3))
     ms = dist.max(ms)
     launches = ctx.launch_count()
 
@@ -419,6 +464,13 @@ def run_ours(args, rank, local_rank, world):
     step_ms = ms / args.steps
     total_rows = dist.sum(rows)
     total_accept = dist.sum(sum(q["accept"] for q in seqs))
+    churn_line = None
+    if args.workload == "single" and args.layers == 64 and not args.no_churn64:
+        # beside the headline: the 64-sequence batch sharded by sequence over the same GPUs (the contexts are closed one after
+        # the other: two sets of weights are never resident together)
+        ctx.close()
+        ctx = None
+        churn_line = churn64_sharded(lbm, dist, args, rank, local_rank, world)
     if rank == 0:
         cpu_v, cpu_est, cpu_desc = (None, None, "skipped (--no-cpu-baseline)")
         cores = max(1, min(os.cpu_count() or 1, 64))
@@ -449,7 +501,7 @@ def run_ours(args, rank, local_rank, world):
             "roofline": {"bound": "hbm", "kernel": "gemm_fp8_tcgen05_kernel (%d launches per step)" % n_gemm,
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind,
                          # DRAM read + write bytes per launch: 1.021 x the algorithmic bytes, the ratio ncu measured on the
-                         # gate|up launch (profiles/gemm_fp8_tcgen05_gateup_24x34816x5120.md), scaled to the average launch
+                         # gate|up launch (24 x 34816 x 5120), scaled to the average launch
                          "traffic": 1.021 * wbytes / n_gemm, "traffic_source": "ncu dram__bytes ratio 1.021 of one gate|up launch, scaled by bytes",
                          "bytes_per_launch_avg": wbytes / n_gemm, "ms_per_launch_avg": chain_ms / n_gemm,
                          "ms_per_step": chain_ms,
@@ -457,10 +509,12 @@ def run_ours(args, rank, local_rank, world):
                          "per_launch_events": {"ms_per_step": gemm_ms, "achieved": per_launch, "frac": per_launch / peak}},
             "cpu_baseline": {"value": cpu_v, "unit": UNIT, "cores": cores, "kind": "port", "sample": cpu_desc,
                              "est_ms_per_step": None if cpu_est is None else cpu_est * 1e3},
+            "churn64": churn_line,
             "clocks": clk,
         }
         print(json.dumps(line), flush=True)
-    ctx.close()
+    if ctx is not None:
+        ctx.close()
     dist.close()
 
 
@@ -515,6 +569,7 @@ def main():
     ap.add_argument("--gemm-impl", type=int, default=0)
     ap.add_argument("--pdl", type=int, default=1, help="programmatic dependent launch (bit-identical results; on by default)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-churn64", action="store_true", help="leave out the 64-sequence sharded batch reported beside the headline")
     ap.add_argument("--quick", action="store_true", help="device-timed steps only (no end-to-end, per-family or CPU legs): "
                     "the short run the profiler's launch list is taken from")
     ap.add_argument("--micro", default="", choices=["", "gemm"], help="time one kernel alone on resident operands")

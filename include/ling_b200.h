@@ -254,6 +254,12 @@ int ling_b200_sync(ling_b200_ctx* ctx);
 int ling_b200_gemm_fp8_host(int device, int impl, int splits, const float* x, const float* w, float* y, int M, int N, int K);
 /* The same GEMM timed on the device with resident operands: ms per launch over `iters` launches. */
 int ling_b200_gemm_fp8_bench(int device, int impl, int splits, int M, int N, int K, int iters, float* ms_per_launch);
+/* The kernels' bounded wait made to run out on purpose, harmlessly: one CTA waits at most limit_us microseconds on a barrier
+ * that nobody arrives at, records the code of an expired wait in the error word and returns.  The call returns
+ * LING_B200_ERR_DEVICE_FLAG with that code in *code (1) and the time the kernel waited in *waited_us; the device and its
+ * contexts stay usable.  (The reference's persistent kernels trap after 50 ms instead, stream_gemm.cu:865-882.) */
+int ling_b200_wait_probe(int device, unsigned limit_us, int* code, unsigned* waited_us);
+
 /* No counterpart in the reference.  The same block-scaled FP8 GEMM for hosts that must not allocate device memory on
  * this path: a serving loop that gave the whole device to its own arena at start-up, a real-time thread for which an
  * allocation's implicit synchronization is not acceptable, a sandboxed plugin that receives buffers but may not create
@@ -267,7 +273,8 @@ int ling_b200_gemm_fp8_bench(int device, int impl, int splits, int M, int N, int
  *   returns LING_B200_ERR_ARG and touches nothing.  The K split is the regular one unless the array holds fewer planes.
  *   The first call on a device looks the array's address up (cudaGetSymbolAddress) and sets kernel attributes: make it
  *   before any stream capture.  The call enqueues on `stream` (NULL = the default stream), waits for it and returns the
- *   status.  Every call shares the array: calls that overlap on the GPU race.  Nothing in it needs clearing by the caller. */
+ *   status; the device that owns the operands and `stream` must be the calling thread's current device.  Every call shares
+ *   the array: calls that overlap on the GPU race.  Nothing in it needs clearing by the caller. */
 #define LING_B200_NOALLOC_MAX_ROWS 128
 #define LING_B200_NOALLOC_SCRATCH_BYTES (16u << 20)
 int ling_b200_gemm_fp8_noalloc(const uint8_t* w_codes, const float* w_scales, const uint8_t* x_codes, const float* x_scales,
@@ -376,6 +383,17 @@ int ling_b200_choose_size(const ling_b200_model_config* cfg, size_t weight_bytes
                           int auto_size, int kv_on, size_t store_bytes, long pool_mb, int page_tokens,
                           int kv_elem_bytes, int* out_sessions, int* out_context, int* sessions_auto,
                           int* context_auto, int* sized);
+/* refuse_request (admission.hpp:312-319): the 503 text of a request that arrives while the host is below the admission
+ * reserve, into buf; returns its length, 0 when the request may run, -1 when buf is too small. */
+int ling_b200_refuse_request(long avail_mb, long reserve_mb, char* buf, int buf_len);
+/* kv_reclaim (src/serve/kv_policy.hpp:58-72) with the reference's std::function arguments as C callbacks over one user
+ * pointer: need / have return the unit's need and the free + pending pages now; evict(user, group) evicts the next holder
+ * of a group (1) or reports the group empty (0).  Groups [0, n_kept) may go without moving the unit's resume point,
+ * groups [n_kept, n_kept + n_source) are the unit's own source.  Returns 1 when the unit fits at the end. */
+typedef int (*ling_b200_count_fn)(void* user);
+typedef int (*ling_b200_evict_fn)(void* user, int group);
+int ling_b200_kv_reclaim(ling_b200_count_fn need, ling_b200_count_fn have, ling_b200_evict_fn evict, void* user, int n_kept,
+                         int need_kept, int reach_kept, int n_source, int need_all, int reach_all, int must);
 /* format_step (src/serve/step_trace.hpp:66-87): one trace line into buf; returns its length. */
 int ling_b200_format_step(double t, long pass, const char* kind, size_t turn, const int* sessions, const int* rows,
                           const int* tokens, const int* left, int n,

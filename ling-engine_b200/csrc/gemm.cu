@@ -355,6 +355,25 @@ __global__ void __launch_bounds__(gemm_threads(NT), ctas_per_sm(NT))
   }
 }
 
+// ---------------------------------------------------------------------------------------------- the bounded wait, alone
+// One CTA arms an mbarrier that nobody ever arrives at and waits on it with the kernels' bounded wait under a short limit:
+// the wait runs out, the thread records the code a GEMM consumer would record (kDevWaitFull) in the error word, notes how
+// long it waited, and the kernel returns normally.  What a hung producer looks like to the roles behind it, made on
+// purpose and harmlessly: the check that an expired wait leaves the context usable.
+__global__ void wait_probe_kernel(unsigned long long limit_ns, int* err_flag, unsigned long long* waited_ns) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned long long t0 = global_ns();
+    if (!mbar_wait_for(&bar, 0, nullptr, limit_ns)) dev_fail(err_flag, kDevWaitFull);
+    *waited_ns = global_ns() - t0;
+  }
+}
+
 // ---------------------------------------------------------------------------------------------- CUDA-core GEMM
 // The same arithmetic on CUDA cores: one block = one 128-row weight tile x 8 token rows, a warp per weight row,
 // lanes split the 128-wide block four codes each.  Exists to cross-check the tensor-core kernel, not to be fast.
@@ -513,6 +532,12 @@ int make_acts_maps(Fp8Acts& x) {
     const int nt = 32 * (i + 1);
     if (const int r = encode_2d(&x.map[i], x.codes, uint64_t(x.K_pad), uint64_t(x.rows_alloc), uint32_t(nt))) return r;
   }
+  return LING_B200_OK;
+}
+
+int wait_probe_launch(unsigned long long limit_ns, int* err_flag, unsigned long long* waited_ns, cudaStream_t stream) {
+  wait_probe_kernel<<<1, 32, 0, stream>>>(limit_ns, err_flag, waited_ns);
+  LB_LAUNCH("wait_probe_kernel");
   return LING_B200_OK;
 }
 

@@ -61,6 +61,9 @@ int make_acts_maps(Fp8Acts& x);
 int choose_splits(int N_pad, int KB, int sm_count);
 int gemm_init();
 int gemm_launch(const GemmCall& c, cudaStream_t stream);
+// One CTA waits, with the kernels' bounded wait and the given limit, on a barrier that nobody arrives at: records
+// kDevWaitFull in *err_flag and the nanoseconds it waited, and returns.
+int wait_probe_launch(unsigned long long limit_ns, int* err_flag, unsigned long long* waited_ns, cudaStream_t stream);
 // Token rows per MMA (the N of the instruction) used for M rows: 32, 64, 96 or 128.
 int token_tile(int M);
 

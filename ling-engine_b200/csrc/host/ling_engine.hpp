@@ -420,7 +420,33 @@ inline int kv_last_resort(const std::vector<KvRunner>& running, const KvPoolView
   return ling_b200_kv_last_resort(a.data(), w.data(), n.data(), static_cast<int>(running.size()), v.free, v.pending, v.idle);
 }
 
+// kv_reclaim (src/serve/kv_policy.hpp:58-72): the reference's signature; the closures travel behind one user pointer.
+using KvEvictNext = std::function<bool()>;
+inline bool kv_reclaim(const std::function<int()>& need, const std::function<int()>& have, const std::vector<KvEvictNext>& kept,
+                       int need_kept, int reach_kept, const std::vector<KvEvictNext>& source, int need_all, int reach_all, bool must) {
+  struct Calls {
+    const std::function<int()>*need, *have;
+    const std::vector<KvEvictNext>*kept, *source;
+  } calls{&need, &have, &kept, &source};
+  return ling_b200_kv_reclaim(
+             [](void* u) { return (*static_cast<Calls*>(u)->need)(); }, [](void* u) { return (*static_cast<Calls*>(u)->have)(); },
+             [](void* u, int g) {
+               const Calls& c = *static_cast<Calls*>(u);
+               const size_t nk = c.kept->size();
+               return int(size_t(g) < nk ? (*c.kept)[size_t(g)]() : (*c.source)[size_t(g) - nk]());
+             },
+             &calls, static_cast<int>(kept.size()), need_kept, reach_kept, static_cast<int>(source.size()), need_all, reach_all,
+             must) != 0;
+}
+
 // ---- src/serve/admission.hpp
+// refuse_request (admission.hpp:312-319): the 503 text while the host is below the admission reserve; empty: may run.
+inline std::string refuse_request(long avail_mb, long reserve_mb) {
+  std::string buf(256, '\0');
+  const int n = ling_b200_refuse_request(avail_mb, reserve_mb, buf.data(), static_cast<int>(buf.size()));
+  buf.resize(n > 0 ? size_t(n) : 0);
+  return buf;
+}
 struct MemoryPlan : ling_b200_memory_plan {};
 struct KvPlanInputs {
   bool on = false;

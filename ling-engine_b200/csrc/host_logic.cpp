@@ -340,53 +340,34 @@ int ling_b200_kvpool_net_need(const ling_b200_kvpool*, const int* table, int len
   }
   return std::max(need, 0);
 }
-// KvPool::resume_need (kv_pool.hpp:57-66): share(donor) -> truncate(pages) -> unshare(reuse) -> ensure(reuse, end)
-// replayed on a copy, counting pages taken minus pages the holder's own releases free.
+// KvPool::resume_need (kv_pool.hpp:57-66): what a prefill that resumes at position `reuse` and maps every page index below
+// `pages` draws from the free list, net.  The documented sequence -- share the donor's pages for [0, reuse), truncate to
+// `pages`, unshare from the resume point on, ensure [reuse, end) -- is carried out for real on a scratch copy of the pool
+// and of the table (the copy's free list is padded with stand-in pages so that ensure cannot run short), and the answer
+// is read off the copy: pages that left its free list, less pages the holder's own releases queued for retirement.
 int ling_b200_kvpool_resume_need(const ling_b200_kvpool* p, const int* table, int len, int reuse, int pages, const int* donor,
                                  int donor_len) {
-  std::map<int, int> delta;
-  auto count = [&](int page) {
-    auto it = delta.find(page);
-    return p->refs.at(size_t(page)) + (it == delta.end() ? 0 : it->second);
-  };
-  int taken = 0, freed = 0;
-  auto let_go = [&](int page) {
-    if (count(page) == 1) ++freed;
-    --delta[page];
-  };
-  std::vector<int> t(table, table + len);
-  const int reuse_pages = p->pages_for(std::max(reuse, 0));
-  if (donor) {
-    if (reuse_pages > donor_len) return -1;
-    if (int(t.size()) < reuse_pages) t.resize(size_t(reuse_pages), 0);
-    for (int i = 0; i < reuse_pages; ++i) {
-      if (donor[i] == 0) return -1;
-      if (t[i] == donor[i]) continue;
-      ++delta[donor[i]];
-      if (t[i] != 0) let_go(t[i]);
-      t[i] = donor[i];
-    }
-  }
-  for (int i = pages; i < int(t.size()); ++i)
-    if (t[i] != 0) {
-      let_go(t[i]);
-      t[i] = 0;
-    }
-  for (int i = reuse_pages; i < int(t.size()); ++i)
-    if (t[i] != 0 && count(t[i]) > 1) {
-      let_go(t[i]);
-      t[i] = 0;
-    }
-  const int first_written = p->index_of(std::max(reuse, 0));
-  for (int i = 0; i < pages; ++i) {
-    const int page = i < int(t.size()) ? t[i] : 0;
-    if (page == 0) ++taken;
-    else if (i >= first_written && count(page) > 1) {
-      ++taken;
-      let_go(page);
-    }
-  }
-  return std::max(taken - freed, 0);
+  reuse = std::max(reuse, 0), pages = std::max(pages, 0);
+  ling_b200_kvpool sim = *p;
+  const int real = int(sim.refs.size());
+  sim.refs.resize(size_t(real + pages + 1), 0);
+  std::vector<int> stock;  // the stand-ins go under the real free pages: they are handed out only when those run out
+  for (int id = real + pages; id >= real; --id) stock.push_back(id);
+  stock.insert(stock.end(), sim.free_stack.begin(), sim.free_stack.end());
+  sim.free_stack.swap(stock);
+  const size_t free_before = sim.free_stack.size(), pending_before = sim.pending.size();
+  const int cap = std::max({len, pages, sim.pages_for(reuse)}) + 1;
+  std::vector<int> t(size_t(cap), 0);
+  std::copy(table, table + len, t.begin());
+  int tl = len;
+  if (donor && ling_b200_kvpool_share(&sim, t.data(), &tl, cap, donor, donor_len, reuse) != 0) return -1;
+  const int end = pages * sim.page_tokens;
+  ling_b200_kvpool_truncate(&sim, t.data(), tl, end);
+  ling_b200_kvpool_unshare(&sim, t.data(), tl, reuse);
+  if (ling_b200_kvpool_ensure(&sim, t.data(), &tl, cap, std::min(reuse, end), end, nullptr, 0, nullptr) != 1) return -1;
+  const long taken = long(free_before) - long(sim.free_stack.size());
+  const long released = long(sim.pending.size()) - long(pending_before);
+  return int(std::max(taken - released, 0L));
 }
 // KvPool::reclaimable (kv_pool.hpp:67-70).
 int ling_b200_kvpool_reclaimable(const ling_b200_kvpool* p, const int* const* tables, const int* lens, int n) {
@@ -479,38 +460,49 @@ struct Sizes {  // the byte arithmetic of src/serve/admission.hpp:44-80 with the
   }
 };
 
-// start_plan (src/serve/admission.hpp:202-216): plan_memory, then the pool (plan_kv_pool, 109-124) and its floor
-// (refuse_kv_pool, 131-142), then refuse_start (170-186).
+// How many KV pages the pool gets (plan_kv_pool's rule, src/serve/admission.hpp:104-108): an explicit size in MB wins;
+// otherwise, when there is an available-memory figure and a reserve to judge by, whatever is left after the rest of the
+// plan, the prefix store's budget, the reserve and the pool's own reserved page 0; otherwise (and never more than) the
+// pages that every session at its full context would map.
+long pool_pages(const Sizes& z, int sessions, int max_context, long avail_mb, long reserve_mb, long pool_mb, size_t other_bytes) {
+  const long ceiling = long(sessions) * z.pages_for(max_context);
+  const size_t page = z.page_bytes();
+  const auto mb = [](long v) { return size_t(v) << 20; };
+  long pages = ceiling;
+  if (pool_mb >= 0) {
+    pages = long(mb(pool_mb) / page);
+  } else if (avail_mb >= 0 && reserve_mb > 0) {
+    const size_t spoken_for = other_bytes + mb(reserve_mb) + page;
+    pages = mb(avail_mb) > spoken_for ? long((mb(avail_mb) - spoken_for) / page) : 0;
+  }
+  return std::clamp(pages, 0L, ceiling);
+}
+
+// The pool's floor (refuse_kv_pool, admission.hpp:126-142): a pool sized from the plan must hold one conversation at the
+// full context plus the two growth pages a request is admitted with -- unless it already holds every session's context.
+long pool_floor(const Sizes& z, int sessions, int max_context) {
+  return std::min(z.pages_for(max_context) + 2, long(sessions) * z.pages_for(max_context));
+}
+
+// start_plan (src/serve/admission.hpp:202-216): the memory plan, the pool and its floor, then the host-memory check
+// (refuse_start, 170-186: the plan plus the reserve must fit what is available).
 void make_plan(const Sizes& z, size_t weight_bytes, size_t scratch, bool drafter, int sessions, int max_context, long avail_mb,
                long reserve_mb, bool kv_on, size_t store_bytes, long pool_mb, ling_b200_memory_plan* p) {
-  std::memset(p, 0, sizeof *p);
+  *p = ling_b200_memory_plan{};
   p->weights = weight_bytes, p->scratch = scratch, p->session_count = sessions;
   p->per_session = z.session_bytes(max_context, drafter, kv_on);
   p->sessions = p->per_session * size_t(sessions);
-  auto total = [&] { return p->weights + p->sessions + p->scratch + p->kv_pool; };
-  bool refused = false;
+  const bool judged = reserve_mb > 0 && avail_mb >= 0;
+  bool pool_too_small = false;
   if (kv_on) {
-    const long judged_avail = reserve_mb > 0 ? avail_mb : -1;
-    const size_t page = z.page_bytes();
-    const long cap = long(sessions) * z.pages_for(max_context);
-    long pages = cap;
-    if (pool_mb >= 0) {
-      pages = long((size_t(pool_mb) << 20) / page);
-    } else if (judged_avail >= 0 && reserve_mb > 0) {
-      const size_t have = size_t(judged_avail) << 20, keep = total() + store_bytes + (size_t(reserve_mb) << 20) + page;
-      pages = have > keep ? long((have - keep) / page) : 0;
-    }
-    pages = std::max(0L, std::min(pages, cap));
-    p->kv_pool_pages = pages;
-    p->kv_pool = size_t(pages + 1) * page;
-    if (pool_mb < 0 && reserve_mb > 0 && avail_mb >= 0) {
-      const long one = std::min(z.pages_for(max_context) + 2, cap);
-      refused = pages < one;
-    }
+    const size_t rest_of_plan = p->weights + p->sessions + p->scratch;
+    p->kv_pool_pages = pool_pages(z, sessions, max_context, avail_mb, reserve_mb, pool_mb, rest_of_plan + store_bytes);
+    p->kv_pool = size_t(p->kv_pool_pages + 1) * z.page_bytes();  // the reserved page 0 rides along
+    pool_too_small = pool_mb < 0 && judged && p->kv_pool_pages < pool_floor(z, sessions, max_context);
   }
-  if (!refused && reserve_mb > 0 && avail_mb >= 0) refused = long(total() >> 20) + reserve_mb > avail_mb;
-  p->total = total();
-  p->refused = refused ? 1 : 0;
+  p->total = p->weights + p->sessions + p->scratch + p->kv_pool;
+  const bool host_short = judged && long(p->total >> 20) + reserve_mb > avail_mb;
+  p->refused = (pool_too_small || host_short) ? 1 : 0;
 }
 }  // namespace
 
@@ -525,55 +517,91 @@ int ling_b200_start_plan(const ling_b200_model_config* cfg, size_t weight_bytes,
   return LING_B200_OK;
 }
 
-// choose_size (src/serve/admission.hpp:262-310): the context first (the full context, halved to a multiple of 2,048
-// down to 32,768, the first at which the given sessions, or one, fit), then as many sessions as fit, at most 4.
+// choose_size (src/serve/admission.hpp:253-262 for the rule): what was given stays as given; what was not is chosen by
+// the start check's own plan.  The context is chosen first, from a ladder that starts at the model's full context and
+// halves (rounded down to a multiple of 2,048) while it stays at or above 32,768: the first rung at which the given
+// session count, or one session, fits.  Then the most sessions that fit at that context, at most 4.  If no rung fits,
+// the last rung with the given (or one) session is returned and the start check refuses it.  Without auto-sizing, without
+// an available-memory figure or a reserve, or with both values given, the defaults (2 sessions, 65,536) fill the gaps.
 int ling_b200_choose_size(const ling_b200_model_config* cfg, size_t weight_bytes, size_t scratch, int drafter, long avail_mb,
                           long reserve_mb, int full_context, int sessions, int max_context, int auto_size, int kv_on,
                           size_t store_bytes, long pool_mb, int page_tokens, int kv_elem_bytes, int* out_sessions,
                           int* out_context, int* sessions_auto, int* context_auto, int* sized) {
-  constexpr int kCap = 4, kFloor = 32768, kDefSessions = 2, kDefContext = 65536;
-  const bool has_s = sessions >= 0, has_c = max_context >= 0;
-  *sessions_auto = !has_s, *context_auto = !has_c;
-  const bool can_judge = avail_mb >= 0 && reserve_mb > 0;
-  if (!auto_size || !can_judge || (has_s && has_c)) {
-    *out_sessions = has_s ? sessions : kDefSessions;
-    *out_context = has_c ? max_context : kDefContext;
+  constexpr int kMostSessions = 4, kShortestContext = 32768, kStep = 2048, kDefaultSessions = 2, kDefaultContext = 65536;
+  const bool sessions_given = sessions >= 0, context_given = max_context >= 0;
+  const bool measurable = avail_mb >= 0 && reserve_mb > 0;
+  *sized = (auto_size && measurable) ? 1 : 0;
+  if (!*sized || (sessions_given && context_given)) {
+    *out_sessions = sessions_given ? sessions : kDefaultSessions;
+    *out_context = context_given ? max_context : kDefaultContext;
     *sessions_auto = *context_auto = 0;
-    *sized = auto_size && can_judge;
     return LING_B200_OK;
   }
-  *sized = 1;
+  *sessions_auto = sessions_given ? 0 : 1, *context_auto = context_given ? 0 : 1;
   const Sizes z{cfg, page_tokens, kv_elem_bytes};
-  auto fits = [&](int n, int ctx) {
-    ling_b200_memory_plan p;
-    make_plan(z, weight_bytes, scratch, drafter != 0, n, ctx, avail_mb, reserve_mb, kv_on != 0, store_bytes, pool_mb, &p);
-    if (p.refused) return false;
-    if (!kv_on) return true;
-    // paged_sessions_fit (admission.hpp:236-239): one conversation at the full context and half of n conversations
-    const long one = std::min(z.pages_for(ctx) + 2, long(n) * z.pages_for(ctx));
-    return p.kv_pool_pages >= std::max(one, long(n) * z.pages_for(ctx) / 2);
+  const auto fits = [&](int n, int ctx) {
+    ling_b200_memory_plan plan;
+    make_plan(z, weight_bytes, scratch, drafter != 0, n, ctx, avail_mb, reserve_mb, kv_on != 0, store_bytes, pool_mb, &plan);
+    if (plan.refused) return false;
+    // paged_sessions_fit (admission.hpp:225-233): the pool must hold one conversation at the full context and half of
+    // what n conversations at the full context would map
+    return !kv_on || plan.kv_pool_pages >= std::max(pool_floor(z, n, ctx), long(n) * z.pages_for(ctx) / 2);
   };
-  if (full_context <= 0) full_context = kDefContext;
-  std::vector<int> tries;
-  if (has_c) tries.push_back(max_context);
-  else {
-    for (int ctx = full_context; ctx >= kFloor; ctx = ctx / 2 - (ctx / 2) % 2048) tries.push_back(ctx);
-    if (tries.empty()) tries.push_back(full_context);
+  std::vector<int> ladder;
+  if (context_given) {
+    ladder.push_back(max_context);
+  } else {
+    const int top = full_context > 0 ? full_context : kDefaultContext;
+    for (int rung = top; rung >= kShortestContext; rung = (rung / 2) / kStep * kStep) ladder.push_back(rung);
+    if (ladder.empty()) ladder.push_back(top);  // a model whose full context is below the shortest rung
   }
-  const int base = has_s ? sessions : 1;
-  for (int ctx : tries) {
-    if (!fits(base, ctx)) continue;
-    *out_context = ctx, *out_sessions = base;
-    if (!has_s)
-      for (int n = kCap; n > 1; --n)
-        if (fits(n, ctx)) {
-          *out_sessions = n;
-          break;
-        }
-    return LING_B200_OK;
+  const int least = sessions_given ? sessions : 1;
+  const auto rung = std::find_if(ladder.begin(), ladder.end(), [&](int ctx) { return fits(least, ctx); });
+  *out_context = rung != ladder.end() ? *rung : ladder.back();
+  *out_sessions = least;
+  if (rung != ladder.end() && !sessions_given) {
+    int n = kMostSessions;
+    while (n > 1 && !fits(n, *rung)) --n;
+    *out_sessions = n;
   }
-  *out_sessions = base, *out_context = tries.back();
   return LING_B200_OK;
+}
+
+// refuse_request (src/serve/admission.hpp:312-319): the text of the 503 a generation request gets while the host is below
+// the admission reserve, written to buf; returns its length, 0 when the request may run (an unknown figure, avail_mb < 0,
+// never refuses), -1 when buf is too small.
+int ling_b200_refuse_request(long avail_mb, long reserve_mb, char* buf, int buf_len) {
+  if (avail_mb < 0 || avail_mb >= reserve_mb) {
+    if (buf && buf_len > 0) buf[0] = 0;
+    return 0;
+  }
+  const std::string text = "host memory low: " + std::to_string(avail_mb) + " MB available, below the " + std::to_string(reserve_mb) +
+                           " MB this server keeps free; the request was not started (retry later)";
+  if (!buf || int(text.size()) + 1 > buf_len) return -1;
+  std::memcpy(buf, text.c_str(), text.size() + 1);
+  return int(text.size());
+}
+
+// kv_reclaim (src/serve/kv_policy.hpp:58-72): makes room for a unit by evicting holders.  need(user) and have(user) are
+// the unit's need and the free + pending pages NOW (both change as holders go); evict(user, group) evicts the next
+// holder of a group and returns 1, or 0 when the group has none left.  Groups 0 .. n_kept-1 are holders that may go
+// without moving the unit's resume point, groups n_kept .. n_kept+n_source-1 the unit's own source.  The kept groups are
+// enough when need_kept <= reach_kept; if they are not, the source groups join the order provided that evicting
+// everything suffices (need_all <= reach_all) or `must` says nothing else will ever free pages -- otherwise nothing at
+// all is evicted.  Along the order each group is drained while the unit still does not fit.  Returns 1 when it fits.
+int ling_b200_kv_reclaim(ling_b200_count_fn need, ling_b200_count_fn have, ling_b200_evict_fn evict, void* user, int n_kept,
+                         int need_kept, int reach_kept, int n_source, int need_all, int reach_all, int must) {
+  const auto fits = [&] { return need(user) <= have(user); };
+  if (fits()) return 1;
+  int groups = n_kept;
+  if (need_kept > reach_kept) {
+    if (!must && need_all > reach_all) return 0;
+    groups += n_source;
+  }
+  for (int g = 0; g < groups; ++g)
+    while (!fits() && evict(user, g)) {
+    }
+  return fits() ? 1 : 0;
 }
 
 // format_step (src/serve/step_trace.hpp:66-87): one JSON line of the per-step trace.

@@ -166,6 +166,31 @@ int ling_b200_gemm_fp8_bench(int device, int impl, int splits, int M, int N, int
   return LING_B200_OK;
 }
 
+// A bounded device wait made to run out on purpose (see wait_probe_kernel): returns LING_B200_ERR_DEVICE_FLAG with the
+// recorded code in *code and the time the kernel waited in *waited_us; the device stays usable.
+int ling_b200_wait_probe(int device, unsigned limit_us, int* code, unsigned* waited_us) {
+  if (!code || !waited_us || limit_us < 1 || limit_us > 100000) {
+    set_error("wait_probe: a limit of 1 .. 100000 microseconds expected");
+    return LING_B200_ERR_ARG;
+  }
+  LB_TRY(check_device(device));
+  Scratch sc;
+  int* err = sc.get<int>(1);
+  unsigned long long* waited = sc.get<unsigned long long>(1);
+  LB_PTR(err && waited);
+  LB_TRY(wait_probe_launch(uint64_t(limit_us) * 1000ull, err, waited, 0));
+  LB_CUDA(cudaDeviceSynchronize());
+  unsigned long long w = 0;
+  LB_CUDA(cudaMemcpy(code, err, 4, cudaMemcpyDeviceToHost));
+  LB_CUDA(cudaMemcpy(&w, waited, 8, cudaMemcpyDeviceToHost));
+  *waited_us = unsigned(w / 1000ull);
+  if (*code != 0) {
+    set_error("device error word = " + std::to_string(*code) + " (a bounded wait ran out)");
+    return LING_B200_ERR_DEVICE_FLAG;
+  }
+  return LING_B200_OK;
+}
+
 namespace {
 // A one-sequence StepBuffers for the DeltaNet kernels.
 struct OneSeq {

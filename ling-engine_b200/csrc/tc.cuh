@@ -39,17 +39,21 @@ __device__ __forceinline__ uint64_t global_ns() {
 }
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s: far beyond any healthy step
 
-// Bounded wait.  Returns false when the limit ran out or (with `abort`) another role already gave up.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort) {
+// Bounded wait.  Returns false when the limit (wall clock, nanoseconds) ran out or (with `abort`) another role already
+// gave up; the caller records a code in the device error word and unwinds.  Nothing traps, nothing waits forever.
+__device__ __forceinline__ bool mbar_wait_for(uint64_t* bar, uint32_t parity, volatile int* abort, uint64_t limit_ns) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = global_ns();
   for (uint32_t spin = 1;; ++spin) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((spin & 255u) == 0) {
       if (abort && *abort) return false;
-      if (global_ns() - t0 > kWaitLimitNs) return false;
+      if (global_ns() - t0 > limit_ns) return false;
     }
   }
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort) {
+  return mbar_wait_for(bar, parity, abort, kWaitLimitNs);
 }
 
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y, uint64_t policy) {

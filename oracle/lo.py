@@ -14,12 +14,17 @@ LIB = os.path.join(HERE, "libling_oracle.so")
 REF = os.path.join(HERE, "_ref", "libling_ref.so")
 
 
-def build(ref=True):
-    """Compiles the oracle, and the reference's host sources where the reference project is mounted."""
+REFCUDA = os.path.join(HERE, "_ref", "libling_refcuda.so")
+REF_TREE_TESTS = os.path.join(HERE, "_ref", "ling-tree-tests")
+
+
+def build(ref=True, reference=None):
+    """Compiles the oracle and, where a checkout of the reference project is named (`reference` or the environment's
+    LING_REFERENCE), the reference's host sources and its sm_100a-buildable CUDA kernels behind C wrappers."""
     subprocess.run(["make", "-C", HERE, "-s"], check=True)
-    if ref and os.path.isdir(os.environ.get("LING_REFERENCE", "/root/reference")):
-        subprocess.run(["make", "-C", HERE, "-s", "ref", "REF=" + os.environ.get("LING_REFERENCE", "/root/reference")],
-                       check=False)
+    reference = reference or os.environ.get("LING_REFERENCE", "")
+    if ref and reference and os.path.isdir(reference):
+        subprocess.run(["make", "-C", HERE, "-s", "ref", "ref_cuda", "REF=" + reference], check=False)
 
 
 _lo = None
@@ -53,6 +58,19 @@ def ref():
         L.ref_kvpool_create.restype = C.c_void_p
         _ref = L
     return _ref
+
+
+_refcuda = None
+
+
+def refcuda():
+    """The reference's own CUDA kernels (sm_100a build), or None where they were not built."""
+    global _refcuda
+    if _refcuda is None and os.path.exists(REFCUDA):
+        L = C.CDLL(REFCUDA)
+        L.refcuda_last_error.restype = C.c_char_p
+        _refcuda = L
+    return _refcuda
 
 
 def _ip(a):

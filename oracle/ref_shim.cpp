@@ -245,6 +245,35 @@ int ref_choose_size(const int* cfg, const unsigned char* full, size_t weight_byt
   return 0;
 }
 int ref_refuse_request(long avail_mb, long reserve_mb) { return !ling::serve::refuse_request(avail_mb, reserve_mb).empty(); }
+int ref_refuse_request_text(long avail_mb, long reserve_mb, char* buf, int buf_len) {
+  const std::string text = ling::serve::refuse_request(avail_mb, reserve_mb);
+  if (int(text.size()) + 1 > buf_len) return -1;
+  std::memcpy(buf, text.c_str(), text.size() + 1);
+  return int(text.size());
+}
+// kv_reclaim (src/serve/kv_policy.hpp:58-72) on a scripted scenario: group g holds group_size[g] holders; evicting the
+// e-th holder overall (groups concatenated) changes the unit's need by dneed[e] and the free + pending pages by dhave[e].
+// evicted[g] returns how many holders of each group went.
+int ref_kv_reclaim(int need0, int have0, const int* group_size, const int* dneed, const int* dhave, int n_kept, int need_kept,
+                   int reach_kept, int n_source, int need_all, int reach_all, int must, int* evicted) {
+  int need = need0, have = have0;
+  const int groups = n_kept + n_source;
+  std::vector<int> first(groups + 1, 0);
+  for (int g = 0; g < groups; ++g) first[g + 1] = first[g] + group_size[g], evicted[g] = 0;
+  auto group = [&](int g) {
+    return ling::serve::KvEvictNext([&, g]() {
+      if (evicted[g] >= group_size[g]) return false;
+      const int e = first[g] + evicted[g]++;
+      need += dneed[e], have += dhave[e];
+      return true;
+    });
+  };
+  std::vector<ling::serve::KvEvictNext> kept, source;
+  for (int g = 0; g < n_kept; ++g) kept.push_back(group(g));
+  for (int g = n_kept; g < groups; ++g) source.push_back(group(g));
+  return ling::serve::kv_reclaim([&] { return need; }, [&] { return have; }, kept, need_kept, reach_kept, source, need_all,
+                                 reach_all, must != 0) ? 1 : 0;
+}
 
 // ---- step trace
 int ref_format_step(double t, long pass, const char* kind, size_t turn, const int* sessions, const int* rows, const int* tokens,

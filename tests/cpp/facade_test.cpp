@@ -66,6 +66,17 @@ static void host_checks() {
   EXPECT(kv_verdict(3, {4, 0, 0}) == KvVerdict::Go && kv_verdict(5, {4, 2, 0}) == KvVerdict::Retire &&
          kv_verdict(9, {4, 2, 5}) == KvVerdict::Reclaim && kv_verdict(99, {4, 2, 5}) == KvVerdict::Wait);
   EXPECT(kv_last_resort({{1, true, 50}, {7, true, 60}}, {1, 1, 1}) == 1 && kv_last_resort({{1, true, 50}, {7, false, 60}}, {1, 1, 1}) == -1);
+  {
+    // kv_reclaim with the reference's std::function arguments: two idle sessions of 3 pages each; the unit needs 5
+    int need = 5, have = 1, idle_left = 2, source_left = 1;
+    const std::vector<KvEvictNext> kept = {[&] { return idle_left > 0 ? (--idle_left, have += 3, true) : false; }};
+    const std::vector<KvEvictNext> source = {[&] { return source_left > 0 ? (--source_left, have += 9, need += 2, true) : false; }};
+    EXPECT(kv_reclaim([&] { return need; }, [&] { return have; }, kept, 5, 7, source, 7, 16, false) && idle_left == 0 && source_left == 1);
+    need = 20, have = 1, idle_left = 2;
+    EXPECT(!kv_reclaim([&] { return need; }, [&] { return have; }, kept, 20, 7, source, 22, 16, false) && idle_left == 2);   // nothing evicted
+    EXPECT(refuse_request(9000, 8192).empty() && refuse_request(-1, 8192).empty());
+    EXPECT(refuse_request(100, 8192) == "host memory low: 100 MB available, below the 8192 MB this server keeps free; the request was not started (retry later)");
+  }
   StepRecord rec;
   rec.t = 1.5, rec.pass = 12, rec.turn = 1, rec.sessions = {0, 2}, rec.rows = {12, 12}, rec.tokens = {5, 7}, rec.left = {0, 0};
   rec.cand = {{0, 3, 1, 2, 11}}, rec.ms = 121.75, rec.side = false;

@@ -268,6 +268,31 @@ def trace_cases(ref, rng):
     return out
 
 
+def reclaim_cases(ref, rng):
+    """kv_reclaim on scripted scenarios and refuse_request's text."""
+    out = {"reclaim": [], "refuse": []}
+    for _ in range(300):
+        n_kept, n_source = int(rng.integers(0, 4)), int(rng.integers(0, 3))
+        sizes = [int(x) for x in rng.integers(0, 4, n_kept + n_source)]
+        total = sum(sizes)
+        dneed = [int(x) for x in rng.integers(-2, 2, total)]
+        dhave = [int(x) for x in rng.integers(0, 5, total)]
+        need0, have0 = int(rng.integers(0, 14)), int(rng.integers(0, 8))
+        need_kept, reach_kept, need_all, reach_all = (int(x) for x in rng.integers(0, 14, 4))
+        must = int(rng.integers(0, 2))
+        ev = (C.c_int * 8)()
+        ret = ref.ref_kv_reclaim(need0, have0, arr(sizes), arr(dneed), arr(dhave), n_kept, need_kept, reach_kept, n_source, need_all,
+                                 reach_all, must, ev)
+        out["reclaim"].append({"need0": need0, "have0": have0, "sizes": sizes, "dneed": dneed, "dhave": dhave, "n_kept": n_kept,
+                               "need_kept": need_kept, "reach_kept": reach_kept, "n_source": n_source, "need_all": need_all,
+                               "reach_all": reach_all, "must": must, "ret": ret, "evicted": list(ev)[:n_kept + n_source]})
+    for avail, reserve in ((-1, 8192), (0, 8192), (8191, 8192), (8192, 8192), (9000, 8192), (12, 0), (117000, 16384), (5, 16384)):
+        buf = C.create_string_buffer(512)
+        n = ref.ref_refuse_request_text(C.c_long(avail), C.c_long(reserve), buf, 512)
+        out["refuse"].append({"avail": avail, "reserve": reserve, "len": n, "text": buf.value.decode()})
+    return out
+
+
 def main():
     ref = lom.ref()
     if ref is None:
@@ -277,6 +302,7 @@ def main():
     golden = {"trees": tree_cases(ref, rng), "lookup": lookup_cases(ref, rng), "build_tree": build_cases(ref, rng),
               "kvpool": kvpool_traces(ref, rng), "policy": policy_cases(ref, rng), "admission": admission_cases(ref, rng),
               "trace": trace_cases(ref, rng)}
+    golden["reclaim"] = reclaim_cases(ref, rng)   # appended last: the sections above keep their random streams
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "host_logic.json")
     with open(path, "w") as f:
         json.dump(golden, f, separators=(",", ":"))

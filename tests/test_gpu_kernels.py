@@ -327,8 +327,9 @@ def test_attn_prepare_matches_oracle_at_large_positions(gpu, lb, lo):
     # the prepare kernel alone (head norms with (1 + w), rotation of the first 64 of 256 dims, K and V into the paged FP8
     # cache) at positions 0 .. 131000 against the oracle's norm_rope / kv_store.  The rotation angle is position x
     # theta^(-2i/rot); the device evaluates the power with powf (as the reference's kernel does, attention_body.cuh:87-93),
-    # the oracle with a correctly rounded pow, so the angles may differ by a few ulp of position x inv_freq: the bar on the
-    # rotated dims grows with the position (8 ulp of the largest angle), the unrotated dims are held to 1e-5.
+    # the oracle with a correctly rounded pow, so the angles may differ by an ulp or two of position x inv_freq: the bar on the
+    # rotated dims grows with the position (two ulp of the largest angle; measured against the reference's own kernel, which
+    # uses the same powf: 3.7e-3 of a row's largest value at position 131000), the unrotated dims are held to FP16 rounding.
     cfg = lb.make_config(5120, 128, 1, 4096, 24, 4, 256, 64, 16, 48, 128, 128, [1])
     positions, page_tokens = (0, 1529, 8192, 60000, 131000), 16
     n_seq, max_ctx = len(positions), 131072 + 64
@@ -362,7 +363,7 @@ def test_attn_prepare_matches_oracle_at_large_positions(gpu, lb, lo):
         amax = np.abs(q_o[r]).max()
         assert np.abs(q_g[r, :, rot:] - q_o[r, :, rot:]).max() <= 2.0 ** -10 * amax + 1e-5
         # ... the rotated ones with the angle's uncertainty on top
-        ang_tol = 8 * ulp * max(1.0, abs(float(pk["rope_pos"][r])))
+        ang_tol = 2 * ulp * max(1.0, abs(float(pk["rope_pos"][r])))
         assert np.abs(q_g[r, :, :rot] - q_o[r, :, :rot]).max() <= (2.0 ** -10 + ang_tol) * amax * 1.5 + 1e-5, (r, int(pk["rope_pos"][r]))
     flips_k = total = 0
     for s, q in enumerate(seqs):
@@ -370,7 +371,7 @@ def test_attn_prepare_matches_oracle_at_large_positions(gpu, lb, lo):
         kc_g, ks_g, vc_g, vs_g = ctx.kv_read(s, 0, q["pos"], n, codes=True)
         kc_o, ks_o, vc_o, vs_o = m.kv_read(s, 0, q["pos"], n, codes=True)
         assert np.array_equal(vc_g, vc_o) and np.array_equal(vs_g, vs_o)      # V is stored raw: bit-exact
-        assert np.allclose(ks_g, ks_o, rtol=1e-4 + 8 * ulp * max(1, q["pos"]))
+        assert np.allclose(ks_g, ks_o, rtol=1e-4 + 2 * ulp * max(1, q["pos"]))
         flips_k += int((kc_g != kc_o).sum())
         total += kc_o.size
         dec = lo.e4m3_decode_table()

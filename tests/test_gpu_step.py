@@ -543,3 +543,28 @@ def test_64_sequences_with_admissions_completions_and_page_reuse(gpu, lb, lo):
     assert reused > 0
     lo.lo().lo_set_threads(1)
     pool.close(), ctx.close(), m.close()
+
+
+def test_a_bounded_device_wait_runs_out_and_the_context_stays_usable(gpu, lb, lo):
+    # Failure made without a fault: a one-CTA kernel waits, with the kernels' own bounded wait and a 2 ms limit, on a
+    # barrier that nobody arrives at.  The wait must return, the status word must say so, and the device must go on
+    # working: a context created before the expired wait still steps, and a GEMM after it is still right.
+    import ctypes as C
+    cfg = lb.toy_config()
+    ctx = lb.Context(cfg, sessions=1, max_seqs=1, max_rows=32)
+    ctx.synth_weights(0)
+    q = {"slot": 0, "pos": 5, "tokens": np.zeros(4, np.int32), "parent": np.array([-1, 0, 1, 2], np.int32), "chain": 3}
+    helpers.map_pages([ctx], 0, 64, 16, 1)
+    ctx.synth_kv(0, 5, 0)
+    before = ctx.verify_step([q], flags=0)[0]
+    code, waited = C.c_int(-1), C.c_uint(0)
+    rc = lb.lib().ling_b200_wait_probe(0, 2000, C.byref(code), C.byref(waited))
+    assert rc == lb.ERR_DEVICE_FLAG and code.value == 1 and "bounded wait ran out" in lb.last_error()
+    assert 2000 <= waited.value < 50000, waited.value          # it waited its limit, not the kernels' 2 s and not forever
+    after = ctx.verify_step([q], flags=0)[0]
+    assert after.status == 0 and after.next_token == before.next_token and list(after.path) == list(before.path)
+    rng = np.random.default_rng(3)
+    x, w = rng.standard_normal((8, 256)).astype(np.float32), (rng.standard_normal((128, 256)) * 0.02).astype(np.float32)
+    ref = lo.gemm_fp8(x, w)
+    assert np.abs(lb.gemm_fp8(x, w) - ref).max() <= 1e-4 * np.sqrt((ref ** 2).mean())
+    ctx.close()

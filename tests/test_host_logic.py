@@ -291,3 +291,48 @@ def test_against_the_reference_host_code_itself(lb, lo):
         assert (ra != 0) == (rb != 0) == (rc != 0)
         if ra == 0:
             assert bytes(a) == bytes(b) == bytes(c)
+
+
+def run_reclaim(lib, c):
+    """kv_reclaim through the C ABI on a scripted scenario: the callbacks keep the counters the reference's closures keep."""
+    state = {"need": c["need0"], "have": c["have0"], "evicted": [0] * len(c["sizes"])}
+    first = np.concatenate([[0], np.cumsum(c["sizes"])]).astype(int)
+    COUNT, EVICT = C.CFUNCTYPE(C.c_int, C.c_void_p), C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_int)
+
+    def evict(_, g):
+        if state["evicted"][g] >= c["sizes"][g]:
+            return 0
+        e = int(first[g]) + state["evicted"][g]
+        state["evicted"][g] += 1
+        state["need"] += c["dneed"][e]
+        state["have"] += c["dhave"][e]
+        return 1
+
+    ret = lib.ling_b200_kv_reclaim(COUNT(lambda _: state["need"]), COUNT(lambda _: state["have"]), EVICT(evict), None, c["n_kept"],
+                                   c["need_kept"], c["reach_kept"], c["n_source"], c["need_all"], c["reach_all"], c["must"])
+    return ret, state["evicted"]
+
+
+def test_reclaim_and_refusal_match_golden(lb, lo):
+    lib = lb.lib()
+    for c in GOLDEN["reclaim"]["reclaim"]:
+        assert run_reclaim(lib, c) == (c["ret"], c["evicted"]), c
+    lib.ling_b200_refuse_request.argtypes = [C.c_long, C.c_long, C.c_char_p, C.c_int]
+    for c in GOLDEN["reclaim"]["refuse"]:
+        buf = C.create_string_buffer(512)
+        assert lib.ling_b200_refuse_request(c["avail"], c["reserve"], buf, 512) == c["len"] and buf.value.decode() == c["text"]
+    assert lib.ling_b200_refuse_request(5, 16384, C.create_string_buffer(8), 8) == -1       # a buffer too small is reported
+    ref = lo.ref()
+    if ref is not None:   # and against the reference's own code, live
+        rng = np.random.default_rng(77)
+        for _ in range(200):
+            n_kept, n_source = int(rng.integers(0, 4)), int(rng.integers(0, 3))
+            sizes = [int(x) for x in rng.integers(0, 4, n_kept + n_source)]
+            c = {"need0": int(rng.integers(0, 14)), "have0": int(rng.integers(0, 8)), "sizes": sizes,
+                 "dneed": [int(x) for x in rng.integers(-2, 2, sum(sizes))], "dhave": [int(x) for x in rng.integers(0, 5, sum(sizes))],
+                 "n_kept": n_kept, "n_source": n_source, "must": int(rng.integers(0, 2))}
+            c["need_kept"], c["reach_kept"], c["need_all"], c["reach_all"] = (int(x) for x in rng.integers(0, 14, 4))
+            ev = (C.c_int * 8)()
+            ret = ref.ref_kv_reclaim(c["need0"], c["have0"], arr(sizes), arr(c["dneed"]), arr(c["dhave"]), n_kept, c["need_kept"],
+                                     c["reach_kept"], n_source, c["need_all"], c["reach_all"], c["must"], ev)
+            assert run_reclaim(lib, c) == (ret, list(ev)[:len(sizes)])

@@ -22,9 +22,11 @@ rows = 10 * len(mine)                      # ten rows a sequence
 ms = 5.0 * (rank + 1)                      # the second rank is slower
 d.barrier()
 agg = bench.aggregate(d, rows, len(mine), ms * 4, 4)
+per_rank = [d.select(r, rows) for r in range(world)]      # what the 64-sequence report lists per rank
 d.barrier()
 if rank == 0:
-    print(json.dumps({"shards": shards, "agg": agg}))
+    print(json.dumps({"shards": shards, "agg": agg, "per_rank_rows": per_rank,
+                      "churn_mine": [len(bench.workload("churn64", r, 1000)) for r in range(world)]}))
 d.close()
 """
 
@@ -62,3 +64,6 @@ def test_two_gloo_ranks_aggregate_like_the_bench():
     # 10 sequences x 10 rows, 4 steps, the slower rank took 40 ms in all
     assert abs(got["agg"]["rows_per_s"] - 100 * 4 / 0.040) < 1e-6
     assert abs(got["agg"]["ms_per_step"] - 10.0) < 1e-9
+    assert got["per_rank_rows"] == [10 * len(s) for s in shards]
+    # the bench's 64-sequence workload is sharded by the same rule: both ranks' shares make up the 64 sequences
+    assert sum(got["churn_mine"]) == 64 and min(got["churn_mine"]) > 0
