@@ -350,7 +350,7 @@ def setup_context(lbm, cfg, seqs, args, rank, local_rank, churn):
         pages = int(pages * 1.25)   # room for admissions that are longer than the completions they replace
     ctx = lbm.Context(cfg, sessions=len(seqs), max_context=max_context, page_tokens=page_tokens,
                       pool_pages=pages, max_seqs=len(seqs), max_rows=max(rows, 32), gemm_impl=args.gemm_impl, use_graph=1,
-                      device=local_rank, debug_rows=0, pdl=args.pdl)
+                      device=local_rank, debug_rows=0, pdl=args.pdl, chain=args.chain)
     ctx.synth_weights(0)
     pool = PagePool(lbm, pages, page_tokens, len(seqs), max_context // page_tokens)  # ids 1 .. pages - 1 (page 0 is reserved)
     for q in seqs:
@@ -488,7 +488,7 @@ def run_ours(args, rank, local_rank, world):
                        "l2": "inputs larger than L2 (weights %.1f GB per step), no flush" % (wbytes / 1e9),
                        "churn": ({"admitted_per_step": admitted / args.steps, "pages_reused_per_step": reused / args.steps}
                                  if churn else None),
-                       "pdl": args.pdl, "gemm_impl": "tcgen05" if args.gemm_impl == 0 else "cuda-core cross-check"},
+                       "pdl": args.pdl, "chain": args.chain, "gemm_impl": "tcgen05" if args.gemm_impl == 0 else "cuda-core cross-check"},
             "accepted_tokens_per_s": total_accept / (step_ms * 1e-3),
             "hbm_fraction_weights_plus_kv": (alg["weights"] + alg["kv"]) / (step_ms * 1e-3) / 1e9 / peak,
             "algorithmic_bytes": alg,
@@ -568,6 +568,8 @@ def main():
     ap.add_argument("--layers", type=int, default=64, help="layers of the 27B-class stack (64 = the named configuration)")
     ap.add_argument("--gemm-impl", type=int, default=0)
     ap.add_argument("--pdl", type=int, default=1, help="programmatic dependent launch (bit-identical results; on by default)")
+    ap.add_argument("--chain", type=int, default=0, help="layer segments of steps of at most 32 rows as persistent kernels with counter "
+                    "dependencies (bit-identical results; measured slower than the separate launches, so off by default)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-churn64", action="store_true", help="leave out the 64-sequence sharded batch reported beside the headline")
     ap.add_argument("--quick", action="store_true", help="device-timed steps only (no end-to-end, per-family or CPU legs): "

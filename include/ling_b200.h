@@ -63,7 +63,11 @@ typedef struct ling_b200_options {
   int debug_rows;    /* rows for which logits and per-layer taps can be kept (0: neither is available)   */
   int pdl;           /* 1 = programmatic dependent launch (launch.cuh:1-98 in the reference): a GEMM prefetches its
                         weight tiles while the kernel before it finishes                                 */
-  int reserved[5];
+  int chain;         /* 1 = steps of at most 32 packed rows run each layer's segments (norm + in projection; out projection +
+                        norm + gate|up + SiLU + down) as persistent kernels with counter dependencies, the reference's
+                        ffn_persistent / gdn_persistent idea (stream_gemm.cu:841-851,1074-1086); bit-identical results,
+                        but on B200 slower than the separate launches (10.1 vs 7.6 ms per 27B step): off by default     */
+  int reserved[4];
 } ling_b200_options;
 
 typedef struct ling_b200_ctx ling_b200_ctx;

@@ -9,6 +9,7 @@
 #include <map>
 #include <vector>
 
+#include "chain.h"
 #include "gemm.h"
 #include "kernels.h"
 
@@ -104,6 +105,13 @@ struct ling_b200_ctx {
   int launches_per_step = 0;
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
 
+  // persistent layer segments (options.chain): dependency counters of every chain of a step, partial sums of squares
+  unsigned* chain_counters = nullptr;
+  size_t chain_words = 0;
+  float* chain_ssq = nullptr;
+  int chain_next = 0;  // chains enqueued so far in the step being built
+  int chain_ahead = 0;  // K blocks of L2 prefetch ahead of the loads (measured on the 27B single-stream step: 0 -> 10.1 ms, 8 -> 11.4, 32 -> 13.2)
+
   // GEMM timeline (LING_B200_TIMELINE=1 at creation): four %globaltimer stamps per GEMM launch of the last step
   unsigned long long* timeline = nullptr;
   int timeline_next = 0;
@@ -179,6 +187,74 @@ int run_gemm(ling_b200_ctx* c, const Fp8Matrix& w, const Fp8Acts& x, int which, 
   return gemm_launch(g, c->stream);
 }
 
+ChainGemm chain_gemm(const ling_b200_ctx* c, const Fp8Matrix& w, const Fp8Acts& x, int which) {
+  ChainGemm g;
+  g.mapW = w.map, g.mapX = x.map[0];
+  g.ws = w.scales, g.xs = x.scales;
+  g.out = c->planes[which];
+  g.split_stride = size_t(c->d.rows_alloc) * w.N_pad;
+  g.N = w.N, g.N_pad = w.N_pad, g.KB = w.KB, g.splits = w.splits, g.xrows = x.rows_alloc;
+  return g;
+}
+ChainProgram chain_base(ling_b200_ctx* c, int rows) {
+  ChainProgram P;
+  P.n_rows = c->sb.n_rows_total, P.rows_grid = rows;
+  P.counters = c->chain_counters + size_t(c->chain_next) * kChainCounterWords;
+  P.ssq = c->chain_ssq, P.err_flag = c->sb.err, P.l2_ahead = c->chain_ahead;
+  // with the timeline on, chain k's stamps take the slots of GEMM launches 4 (k + 1) .. 4 (k + 1) + 3 (16 words)
+  if (c->timeline && 4 * (c->chain_next + 2) <= ling_b200_ctx::kTimelineLaunches - 32) P.stamps = c->timeline + 16 * size_t(c->chain_next + 1);
+  return P;
+}
+// The head of a layer as one persistent kernel: residual add + input norm (+ the DeltaNet gating projections) and the in /
+// q|k|v projection.
+ChainProgram chain_front(ling_b200_ctx* c, int l, int rows, const Planes& carry) {
+  const ModelDims& d = c->d;
+  const LayerW& L = c->layers[l];
+  ChainProgram P = chain_base(c, rows);
+  P.n_gemm = 1, P.norm_gemm = 0;
+  P.norm = ChainNorm{c->h, carry, l == 0 ? c->sb.token : nullptr, c->embed, L.input_norm, L.full ? nullptr : c->xn, c->qout(c->xq_h), d.H, d.eps};
+  if (!L.full) {
+    const int gl = c->gdn_index[l];
+    P.has_ab = 1;
+    P.ab = ChainAb{c->xn, L.in_a, L.in_b, L.A_log, L.dt_bias, c->g + size_t(gl) * d.rows_alloc * d.HV, c->beta + size_t(gl) * d.rows_alloc * d.HV,
+                   d.H, d.HV};
+  }
+  P.g[0] = chain_gemm(c, L.full ? L.qkv : L.in, c->xq_h, 0);
+  return P;
+}
+// The rest of a layer behind its mixer as one persistent kernel: out / o projection, residual add + post norm, gate|up,
+// SiLU(gate) * up, down.
+ChainProgram chain_back(ling_b200_ctx* c, int l, int rows) {
+  const ModelDims& d = c->d;
+  const LayerW& L = c->layers[l];
+  ChainProgram P = chain_base(c, rows);
+  P.n_gemm = 3, P.norm_gemm = 1, P.has_silu = 1;
+  P.g[0] = chain_gemm(c, L.full ? L.o : L.out, L.full ? c->xq_a : c->xq_v, 1);
+  P.norm = ChainNorm{c->h, planes_of(c, 1, L.full ? L.o : L.out), nullptr, nullptr, L.post_norm, nullptr, c->qout(c->xq_h), d.H, d.eps};
+  P.g[1] = chain_gemm(c, L.gu, c->xq_h, 0);
+  P.silu = ChainSilu{d.I, round_up(d.I, kTileN), c->qout(c->xq_i)};
+  P.g[2] = chain_gemm(c, L.down, c->xq_i, 1);
+  return P;
+}
+int run_chain(ling_b200_ctx* c, const ChainProgram& P) {
+  Timed t(c, kFamGemm);
+  ++c->chain_next;
+  return chain_launch(P, c->sm_count, c->stream);
+}
+// Whether the step of this row class runs its layers' segments as persistent kernels: asked for, the tensor-core path,
+// one 32-row token tile, and shapes the chain kernel covers.
+bool use_chains(ling_b200_ctx* c, int rows) {
+  if (!c->opt.chain || c->opt.gemm_impl != 0 || rows > kChainRows) return false;
+  const int saved = c->chain_next;
+  bool ok = true;
+  Planes none;
+  none.p = nullptr;
+  for (int l = 0; l < c->cfg.layers && ok; ++l)
+    ok = chain_supported(chain_front(c, l, rows, none), c->sm_count) && chain_supported(chain_back(c, l, rows), c->sm_count);
+  c->chain_next = saved;
+  return ok;
+}
+
 // The whole step on the context's stream.  rows = the capacity class (grids and GEMM extents); the kernels read the
 // real extents from device memory.  Order of the forward pass: src/core/engine.cpp:1288-1745 (verify branch).
 // Sets the calling thread's dependent-launch switch for a scope and restores what the caller had set.
@@ -205,6 +281,9 @@ int enqueue_step_body(ling_b200_ctx* c, int rows, int flags) {
   const bool keep_logits = (flags & LING_B200_STEP_KEEP_LOGITS) != 0;
   c->launches_per_step = 0;
   c->timeline_next = 0;
+  c->chain_next = 0;
+  const bool chains = use_chains(c, rows);
+  if (chains) LB_CUDA(cudaMemsetAsync(c->chain_counters, 0, c->chain_words * sizeof(unsigned), s));  // every chain starts from zero counters
   {
     Timed t(c, kFamStep);
     LB_TRY(pack_launch(c->sb, d, s));
@@ -214,7 +293,9 @@ int enqueue_step_body(ling_b200_ctx* c, int rows, int flags) {
   Planes carry = none;  // the previous layer's down projection, still to be added to the residual
   for (int l = 0; l < c->cfg.layers; ++l) {
     const LayerW& L = c->layers[l];
-    {
+    if (chains) {
+      LB_TRY(run_chain(c, chain_front(c, l, rows, carry)));
+    } else {
       Timed t(c, kFamElem);
       LB_TRY(norm_quant_launch(c->h, carry, l == 0 ? c->sb.token : nullptr, c->embed, L.input_norm, L.full ? nullptr : c->xn,
                                c->qout(c->xq_h), n_rows, rows, d.H, d.eps, s));
@@ -222,7 +303,7 @@ int enqueue_step_body(ling_b200_ctx* c, int rows, int flags) {
     if (L.full) {
       const int al = c->attn_index[l];
       const bool tc = c->opt.gemm_impl == 0 && attention_tc_supported(d);
-      LB_TRY(run_gemm(c, L.qkv, c->xq_h, 0, rows));
+      if (!chains) LB_TRY(run_gemm(c, L.qkv, c->xq_h, 0, rows));
       const Planes p0 = planes_of(c, 0, L.qkv);
       {
         Timed t(c, kFamAttn);
@@ -251,7 +332,7 @@ int enqueue_step_body(ling_b200_ctx* c, int rows, int flags) {
                                    c->opt.max_context / kAttnChunkShort + 2, tc ? kAttnTcRows : kAttnRowTile,
                                    tc ? c->sm_count : c->sm_count * 2, s));
       }
-      LB_TRY(run_gemm(c, L.o, c->xq_a, 1, rows));
+      if (!chains) LB_TRY(run_gemm(c, L.o, c->xq_a, 1, rows));
       carry = planes_of(c, 1, L.o);
     } else {
       const int gl = c->gdn_index[l];
@@ -259,13 +340,13 @@ int enqueue_step_body(ling_b200_ctx* c, int rows, int flags) {
       float* post = c->post + size_t(gl) * d.rows_alloc * d.C;
       float* g = c->g + size_t(gl) * d.rows_alloc * d.HV;
       float* beta = c->beta + size_t(gl) * d.rows_alloc * d.HV;
-      {
+      if (!chains) {
         // the gating needs only the normalized row, so it runs before the in projection: with dependent launch the
         // GEMM's CTAs are already resident and stream their first weight tiles while it executes
         Timed t(c, kFamGdn);
         LB_TRY(ab_gating_launch(c->xn, L.in_a, L.in_b, L.A_log, L.dt_bias, g, beta, n_rows, rows, d.H, d.HV, s));
       }
-      LB_TRY(run_gemm(c, L.in, c->xq_h, 0, rows));
+      if (!chains) LB_TRY(run_gemm(c, L.in, c->xq_h, 0, rows));
       const Planes p0 = planes_of(c, 0, L.in);
       if (gdn_fused_supported(d)) {
         Timed t(c, kFamGdn);
@@ -295,19 +376,23 @@ int enqueue_step_body(ling_b200_ctx* c, int rows, int flags) {
           LB_TRY(gated_norm_quant_launch(c->core, p0, d.C, L.lin_norm, c->qout(c->xq_v), n_rows, rows, d.HV, d.Dv, d.eps, s));
         }
       }
-      LB_TRY(run_gemm(c, L.out, c->xq_v, 1, rows));
+      if (!chains) LB_TRY(run_gemm(c, L.out, c->xq_v, 1, rows));
       carry = planes_of(c, 1, L.out);
     }
-    {
-      Timed t(c, kFamElem);
-      LB_TRY(norm_quant_launch(c->h, carry, nullptr, nullptr, L.post_norm, nullptr, c->qout(c->xq_h), n_rows, rows, d.H, d.eps, s));
+    if (chains) {
+      LB_TRY(run_chain(c, chain_back(c, l, rows)));
+    } else {
+      {
+        Timed t(c, kFamElem);
+        LB_TRY(norm_quant_launch(c->h, carry, nullptr, nullptr, L.post_norm, nullptr, c->qout(c->xq_h), n_rows, rows, d.H, d.eps, s));
+      }
+      LB_TRY(run_gemm(c, L.gu, c->xq_h, 0, rows));
+      {
+        Timed t(c, kFamElem);
+        LB_TRY(silu_mul_quant_launch(planes_of(c, 0, L.gu), d.I, round_up(d.I, kTileN), c->qout(c->xq_i), n_rows, rows, s));
+      }
+      LB_TRY(run_gemm(c, L.down, c->xq_i, 1, rows));
     }
-    LB_TRY(run_gemm(c, L.gu, c->xq_h, 0, rows));
-    {
-      Timed t(c, kFamElem);
-      LB_TRY(silu_mul_quant_launch(planes_of(c, 0, L.gu), d.I, round_up(d.I, kTileN), c->qout(c->xq_i), n_rows, rows, s));
-    }
-    LB_TRY(run_gemm(c, L.down, c->xq_i, 1, rows));
     carry = planes_of(c, 1, L.down);
     if (taps) {
       Timed t(c, kFamElem);
@@ -602,6 +687,12 @@ int ling_b200_create(const ling_b200_model_config* cfg, const ling_b200_options*
   }
   c->flush_floats = size_t(192) << 18;  // 192 MiB: more than the 126 MB L2
   LB_TRY(c->alloc(&c->flush, c->flush_floats, false));
+  if (opt->chain) {
+    LB_TRY(chain_init());
+    c->chain_words = size_t(2 * cfg->layers + 2) * kChainCounterWords;
+    LB_TRY(c->alloc(&c->chain_counters, c->chain_words));
+    LB_TRY(c->alloc(&c->chain_ssq, size_t(kChainRows) * 8 * 8));
+  }
 
   // ---- sessions
   const size_t kv_slots = size_t(d.n_attn) * 2 * d.Hkv * (d.pool_pages + 1) * d.page_tokens;

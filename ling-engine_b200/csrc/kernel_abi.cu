@@ -3,6 +3,7 @@
 // (tests/stream_tests.cu, tests/tree_tests.cu in the reference project).  They allocate and free their own scratch.
 #include <vector>
 
+#include "chain.h"
 #include "gemm.h"
 #include "kernels.h"
 
@@ -144,13 +145,31 @@ int ling_b200_gemm_fp8_bench(int device, int impl, int splits, int M, int N, int
   GemmCall c;
   c.W = &g.W, c.X = &g.X, c.M = M, c.out = g.out, c.ld = g.W.N_pad;
   c.split_stride = size_t(g.X.rows_alloc) * g.W.N_pad;
-  c.impl = impl, c.err_flag = g.err;
+  c.impl = impl == 2 ? 0 : impl, c.err_flag = g.err;
   cudaEvent_t a, b;
   LB_CUDA(cudaEventCreate(&a));
   LB_CUDA(cudaEventCreate(&b));
-  for (int i = 0; i < 3; ++i) LB_TRY(gemm_launch(c, 0));
+  // impl 2: the same GEMM as a one-GEMM chain (chain.cu) for rows <= 32: what the persistent kernel's GEMM part costs alone
+  ChainProgram P;
+  unsigned* counters = nullptr;
+  if (impl == 2) {
+    LB_TRY(chain_init());
+    counters = sc.get<unsigned>(kChainCounterWords);
+    int* n_rows = sc.put(&M, 1);
+    LB_PTR(counters && n_rows);
+    P.n_gemm = 1, P.norm_gemm = -1, P.n_rows = n_rows, P.rows_grid = std::min(32, round_up(M, 32)), P.counters = counters, P.err_flag = g.err;
+    ChainGemm& G = P.g[0];
+    G.mapW = g.W.map, G.mapX = g.X.map[0], G.ws = g.W.scales, G.xs = g.X.scales, G.out = g.out, G.split_stride = c.split_stride;
+    G.N = g.W.N, G.N_pad = g.W.N_pad, G.KB = g.W.KB, G.splits = g.W.splits, G.xrows = g.X.rows_alloc;
+    if (M > 32 || !chain_supported(P, 148)) {
+      set_error("gemm_fp8_bench: the chain kernel does not cover this shape");
+      return LING_B200_ERR_UNSUPPORTED;
+    }
+  }
+  auto one = [&]() -> int { return impl == 2 ? chain_launch(P, 148, 0) : gemm_launch(c, 0); };
+  for (int i = 0; i < 3; ++i) LB_TRY(one());
   LB_CUDA(cudaEventRecord(a, 0));
-  for (int i = 0; i < iters; ++i) LB_TRY(gemm_launch(c, 0));
+  for (int i = 0; i < iters; ++i) LB_TRY(one());
   LB_CUDA(cudaEventRecord(b, 0));
   LB_CUDA(cudaEventSynchronize(b));
   float ms = 0.f;

@@ -132,3 +132,31 @@ def test_64_layer_model_layer_by_layer_with_teacher_forcing(gpu, lb, lo):
     print("head: %d of 24 rows have a clear top-2 margin; fused argmax equals the oracle's on all of them" % int(clear.sum()))
     lo.lo().lo_set_threads(1)
     ctx.close(), m.close()
+
+
+@pytest.mark.parametrize("pdl", [0, 1])
+def test_persistent_layer_segments_are_bit_identical_to_the_separate_launches(wide, lb, pdl):
+    # options.chain: the head of every layer (norm + in projection) and everything behind its mixer (out projection, norm,
+    # gate|up, SiLU, down) run as two persistent kernels with counter dependencies instead of nine launches.  Every unit
+    # computes what the stand-alone kernel computes, in the same order: logits, argmax, accepted paths and the committed
+    # DeltaNet states are bit for bit those of the separate launches, with and without dependent launch, on the first
+    # (captured) and on a replayed step.
+    cfg, base, _ = wide
+    kw = dict(sessions=4, max_context=60000 + 64, page_tokens=16, pool_pages=6600, max_seqs=4, max_rows=96, debug_rows=96)
+    chained = lb.Context(cfg, pdl=pdl, chain=1, **kw)
+    chained.synth_weights(SEED)
+    rng = np.random.default_rng(5)
+    q = {"slot": 0, "pos": 8192, "tokens": rng.integers(2, cfg.vocab, 24).astype(np.int32),
+         "parent": np.array(helpers.chain_plus_branch(16, 8), np.int32), "chain": 15}
+    imposed(rng, q, [0, 16, 17, 18, 19], cfg.vocab)
+    outs = []
+    for c in (base, chained, chained):
+        helpers.setup_sessions([c], cfg, [q], 16, SEED)
+        res = c.verify_step([q], flags=lb.STEP_COMMIT | lb.STEP_KEEP_LOGITS)
+        outs.append((c.read_logits(), c.read_argmax(), c.state_hash(0), list(res[0].path)[:res[0].n_path], res[0].next_token))
+    assert chained.launch_count() < base.launch_count() - 20, (chained.launch_count(), base.launch_count())
+    for got in outs[1:]:
+        assert np.array_equal(got[0], outs[0][0])
+        assert np.array_equal(got[1][0], outs[0][1][0]) and np.array_equal(got[1][1], outs[0][1][1])
+        assert got[2:] == outs[0][2:]
+    chained.close()
