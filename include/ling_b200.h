@@ -258,6 +258,11 @@ int ling_b200_sync(ling_b200_ctx* ctx);
 int ling_b200_gemm_fp8_host(int device, int impl, int splits, const float* x, const float* w, float* y, int M, int N, int K);
 /* The same GEMM timed on the device with resident operands: ms per launch over `iters` launches. */
 int ling_b200_gemm_fp8_bench(int device, int impl, int splits, int M, int N, int K, int iters, float* ms_per_launch);
+/* The FP8 tensor pipe's sustained dense rate on this GPU, measured: one CTA per SM issues `iters` groups of tcgen05.mma
+ * kind::f8f6f4 (128 x 256 x 128 each) on operands resident in shared memory, no loads and no epilogue, between two CUDA
+ * events.  The denominator for the many-row, tensor-bound configurations (the reference quotes none for B200). */
+int ling_b200_fp8_tensor_peak(int device, int iters, float* tflops, float* ms);
+
 /* The kernels' bounded wait made to run out on purpose, harmlessly: one CTA waits at most limit_us microseconds on a barrier
  * that nobody arrives at, records the code of an expired wait in the error word and returns.  The call returns
  * LING_B200_ERR_DEVICE_FLAG with that code in *code (1) and the time the kernel waited in *waited_us; the device and its

@@ -355,6 +355,52 @@ __global__ void __launch_bounds__(gemm_threads(NT), ctas_per_sm(NT))
   }
 }
 
+// ---------------------------------------------------------------------------------------------- tensor peak
+// What the FP8 tensor pipe sustains when nothing else is in the way: every CTA (one per SM) issues `iters` groups of four
+// tcgen05.mma kind::f8f6f4 (M = 128, N = 256, K = 32 each: one 128-wide K block) on two operand tiles that sit in shared
+// memory for the whole kernel, alternating between two TMEM accumulators; no loads, no epilogue.  The denominator for the
+// many-row (tensor-bound) configurations, measured rather than quoted.
+__global__ void __launch_bounds__(128, 1) tensor_peak_kernel(int iters, int* err_flag) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint8_t* a = smem;                    // [128 rows][128 B]
+  uint8_t* b = smem + 128 * 128;        // [256 rows][128 B]
+  uint64_t* bar = reinterpret_cast<uint64_t*>(b + 256 * 128);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + 1);
+  for (int i = threadIdx.x; i < (128 + 256) * 128; i += blockDim.x)
+    smem[i] = uint8_t(0x30 + ((i * 2654435761u) >> 28));  // E4M3 codes around 1: real switching activity, no NaN
+  if (threadIdx.x == 0) {
+    mbar_init(bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  if (threadIdx.x < 32) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    tc_fence_before();
+  }
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) {
+    constexpr uint32_t idesc = umma_idesc_e4m3(256);
+    const uint64_t adesc = umma_desc_sw128(smem_u32(a)), bdesc = umma_desc_sw128(smem_u32(b));
+    for (int i = 0; i < iters; ++i) {
+      const uint32_t d = tmem_base + uint32_t((i & 1) * 256);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) umma_f8(d, adesc + uint64_t(k * 2), bdesc + uint64_t(k * 2), idesc, (i > 1 || k > 0) ? 1u : 0u);
+    }
+    umma_commit(bar);
+    if (!mbar_wait(bar, 0, nullptr)) dev_fail(err_flag, kDevWaitTmemFull);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+  }
+}
+
 // ---------------------------------------------------------------------------------------------- the bounded wait, alone
 // One CTA arms an mbarrier that nobody ever arrives at and waits on it with the kernels' bounded wait under a short limit:
 // the wait runs out, the thread records the code a GEMM consumer would record (kDevWaitFull) in the error word, notes how
@@ -532,6 +578,18 @@ int make_acts_maps(Fp8Acts& x) {
     const int nt = 32 * (i + 1);
     if (const int r = encode_2d(&x.map[i], x.codes, uint64_t(x.K_pad), uint64_t(x.rows_alloc), uint32_t(nt))) return r;
   }
+  return LING_B200_OK;
+}
+
+int tensor_peak_launch(int ctas, int iters, int* err_flag, cudaStream_t stream) {
+  constexpr int smem = (128 + 256) * 128 + 1024 + 64;
+  static bool attr = false;
+  if (!attr) {
+    LB_CUDA(cudaFuncSetAttribute(tensor_peak_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    attr = true;
+  }
+  tensor_peak_kernel<<<ctas, 128, smem, stream>>>(iters, err_flag);
+  LB_LAUNCH("tensor_peak_kernel");
   return LING_B200_OK;
 }
 

@@ -61,6 +61,8 @@ int make_acts_maps(Fp8Acts& x);
 int choose_splits(int N_pad, int KB, int sm_count);
 int gemm_init();
 int gemm_launch(const GemmCall& c, cudaStream_t stream);
+// `ctas` CTAs each issue `iters` 128 x 256 x 128 FP8 MMA groups on resident operands (the tensor pipe's sustained rate).
+int tensor_peak_launch(int ctas, int iters, int* err_flag, cudaStream_t stream);
 // One CTA waits, with the kernels' bounded wait and the given limit, on a barrier that nobody arrives at: records
 // kDevWaitFull in *err_flag and the nanoseconds it waited, and returns.
 int wait_probe_launch(unsigned long long limit_ns, int* err_flag, unsigned long long* waited_ns, cudaStream_t stream);

@@ -185,6 +185,41 @@ int ling_b200_gemm_fp8_bench(int device, int impl, int splits, int M, int N, int
   return LING_B200_OK;
 }
 
+// The FP8 tensor pipe's sustained rate (tensor_peak_kernel): one CTA per SM, `iters` MMA groups each, timed with CUDA
+// events after a warm-up launch; dense TFLOP/s = 2 * 128 * 256 * 128 * iters * SMs / time.
+int ling_b200_fp8_tensor_peak(int device, int iters, float* tflops, float* ms) {
+  if (!tflops || iters < 1 || iters > (1 << 22)) {
+    set_error("fp8_tensor_peak: bad argument");
+    return LING_B200_ERR_ARG;
+  }
+  LB_TRY(check_device(device));
+  int sms = 148;
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+  Scratch sc;
+  int* err = sc.get<int>(1);
+  LB_PTR(err);
+  cudaEvent_t a, b;
+  LB_CUDA(cudaEventCreate(&a));
+  LB_CUDA(cudaEventCreate(&b));
+  LB_TRY(tensor_peak_launch(sms, iters, err, 0));
+  LB_CUDA(cudaEventRecord(a, 0));
+  LB_TRY(tensor_peak_launch(sms, iters, err, 0));
+  LB_CUDA(cudaEventRecord(b, 0));
+  LB_CUDA(cudaEventSynchronize(b));
+  float t = 0.f;
+  LB_CUDA(cudaEventElapsedTime(&t, a, b));
+  cudaEventDestroy(a), cudaEventDestroy(b);
+  int code = 0;
+  LB_CUDA(cudaMemcpy(&code, err, 4, cudaMemcpyDeviceToHost));
+  if (code) {
+    set_error("fp8_tensor_peak: device error word = " + std::to_string(code));
+    return LING_B200_ERR_DEVICE_FLAG;
+  }
+  *tflops = float(2.0 * 128 * 256 * 128 * double(iters) * sms / (double(t) * 1e-3) / 1e12);
+  if (ms) *ms = t;
+  return LING_B200_OK;
+}
+
 // A bounded device wait made to run out on purpose (see wait_probe_kernel): returns LING_B200_ERR_DEVICE_FLAG with the
 // recorded code in *code and the time the kernel waited in *waited_us; the device stays usable.
 int ling_b200_wait_probe(int device, unsigned limit_us, int* code, unsigned* waited_us) {
