@@ -263,6 +263,53 @@ int ling_b200_gemm_fp8_bench(int device, int impl, int splits, int M, int N, int
  * events.  The denominator for the many-row, tensor-bound configurations (the reference quotes none for B200). */
 int ling_b200_fp8_tensor_peak(int device, int iters, float* tflops, float* ms);
 
+/* ---- NVFP4 operands of the prefill chunk: E2M1 values two a byte (the first in the low nibble), one E4M3 scale per 16
+ * values, one fp32 scale per tensor.  The entry points below take the reference's layouts (values [rows][K/2], scales
+ * [rows][K/16] row-major, HOST buffers); on the device the library keeps the scales in the order tcgen05.cp reads. ---- */
+
+/* quantize_nvfp4 (src/core/model.hpp:29-41; model.cu:188-249): BF16 weights [N][K] (bit patterns) to NVFP4 in the
+ * checkpoints' rounding: *scale2 = amax / (448 * 6), block scales max(amax16 / 6 / scale2, 2^-9) as E4M3, codes nearest
+ * with a value halfway between two codes taking the smaller magnitude.  K % 16 == 0. */
+int ling_b200_quantize_nvfp4_host(int device, const uint16_t* w_bf16, int N, int K, uint8_t* values, uint8_t* scales, float* scale2);
+/* quant_act_nvfp4 and, with up != NULL, silu_mul_quant_nvfp4 (src/core/kernels.cuh:190-197; prefill_gemm.cu:383-420,
+ * 607-618): x (or silu(x) * up) [M][K] rounded to BF16, then NVFP4 under the global scale 1 / input_scale. */
+int ling_b200_quant_act_nvfp4_host(int device, const float* x, const float* up, int M, int K, float input_scale, uint8_t* q, uint8_t* sf);
+/* rmsnorm_quant with nvfp4 = true (src/core/kernels.cuh:203-204; prefill_gemm.cu:426-459,632-638): x * rstd * (1 + w) per row,
+ * into NVFP4 and, when out != NULL, into fp32 too.  w: BF16 bit patterns [H]. */
+int ling_b200_rmsnorm_quant_nvfp4_host(int device, const float* x, const uint16_t* w_bf16, float* out, int M, int H, float eps,
+                                       float input_scale, uint8_t* q, uint8_t* sf);
+/* prefill_gemm_nvfp4 (src/core/kernels.cuh:206-210; prefill_gemm.cu:685-690): y[m * ldy + n] = alpha * xq[m] . w[n] (or += with
+ * accumulate) over n < N; columns N .. ldy of y are left alone.  The weight is given in the checkpoint layout (the
+ * reference passes its tiled copy of the same values).  N % 128 == 0, K % 128 == 0, M = 0 returns at once. */
+int ling_b200_prefill_gemm_nvfp4_host(int device, const uint8_t* xq, const uint8_t* xs, int M, const uint8_t* wq, const uint8_t* ws,
+                                      float alpha, float* y, int ldy, int N, int K, int accumulate);
+/* prefill_swiglu_nvfp4 (src/core/kernels.cuh:215-221; prefill_gemm.cu:700-715): NVFP4(silu(alpha_gate * xq . G^T) *
+ * (alpha_up * xq . U^T)) under the global scale 1 / out_input_scale into q_out [M][N/2], sf_out [M][N/16]; byte for byte
+ * what the two plain GEMMs followed by ling_b200_quant_act_nvfp4_host(up != NULL) give. */
+int ling_b200_prefill_swiglu_nvfp4_host(int device, const uint8_t* xq, const uint8_t* xs, int M, const uint8_t* gate_q,
+                                        const uint8_t* gate_s, float alpha_gate, const uint8_t* up_q, const uint8_t* up_s, float alpha_up,
+                                        int N, int K, float out_input_scale, uint8_t* q_out, uint8_t* sf_out);
+/* The NVFP4 GEMM (fused != 0: the gate|up form) timed on the device with resident operands: ms per launch. */
+int ling_b200_nvfp4_gemm_bench(int device, int M, int N, int K, int fused, int iters, float* ms_per_launch);
+
+/* The prefill chunk's feed-forward stack held on the device: per layer h += down(swiglu(gate, up)(norm(h))), the three
+ * matrices NVFP4 with synthetic BF16 N(0, 0.02) values rounded as quantize_nvfp4 rounds (the quantized branch of the
+ * layer loop's MLP section, src/core/engine.cpp:1238-1247,1704-1711, taken for a chunk of more than 32 rows).  It owns a stream: launch() enqueues the whole stack
+ * over the resident residual and returns, wait() joins it and reports the device time between its events, so the stack can run
+ * beside a verify step of a ling_b200_ctx; forward() is the host-buffer call (pinned staging, copies inside). */
+typedef struct ling_b200_nvfp4_ffn ling_b200_nvfp4_ffn;
+int ling_b200_nvfp4_ffn_create(int device, int layers, int hidden, int intermediate, int max_rows, uint64_t seed,
+                               ling_b200_nvfp4_ffn** out);
+void ling_b200_nvfp4_ffn_destroy(ling_b200_nvfp4_ffn* f);
+int ling_b200_nvfp4_ffn_set_residual(ling_b200_nvfp4_ffn* f, const float* h, int rows);
+int ling_b200_nvfp4_ffn_launch(ling_b200_nvfp4_ffn* f, int rows);
+int ling_b200_nvfp4_ffn_wait(ling_b200_nvfp4_ffn* f, float* device_ms);
+int ling_b200_nvfp4_ffn_forward(ling_b200_nvfp4_ffn* f, const float* h_in, int rows, float* h_out);
+/* One layer's operands back on the host in the reference's layouts (any pointer may be NULL); scales5 = the static
+ * activation scales of the two GEMMs' inputs, then the tensor scales of gate, up and down. */
+int ling_b200_nvfp4_ffn_read_layer(ling_b200_nvfp4_ffn* f, int layer, uint16_t* norm_bf16, uint8_t* gate_q, uint8_t* gate_s,
+                                   uint8_t* up_q, uint8_t* up_s, uint8_t* down_q, uint8_t* down_s, float* scales5);
+
 /* The kernels' bounded wait made to run out on purpose, harmlessly: one CTA waits at most limit_us microseconds on a barrier
  * that nobody arrives at, records the code of an expired wait in the error word and returns.  The call returns
  * LING_B200_ERR_DEVICE_FLAG with that code in *code (1) and the time the kernel waited in *waited_us; the device and its

@@ -399,6 +399,127 @@ def gdn_fused(Hk, HV, Dk, Dv, trees, inp, convw, g, beta, state, conv, norm_w, e
     return pre, post, core, codes, scales
 
 
+# ---- NVFP4 operands of the prefill chunk (values [rows][K/2] two a byte, E4M3 scales [rows][K/16], fp32 tensor scale)
+def to_bf16_bits(x):
+    """fp32 array -> BF16 bit patterns (uint16), round to nearest even."""
+    u = np.ascontiguousarray(x, np.float32).view(np.uint32)
+    return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+
+
+def _up(a):
+    return a.ctypes.data_as(C.c_void_p) if a is not None else None
+
+
+def quantize_nvfp4(w_bf16_bits, device=0):
+    w = np.ascontiguousarray(w_bf16_bits, np.uint16)
+    N, K = w.shape
+    q, sf, s2 = np.zeros((N, K // 2), np.uint8), np.zeros((N, K // 16), np.uint8), C.c_float()
+    check(lib().ling_b200_quantize_nvfp4_host(device, _up(w), N, K, _bp(q), _bp(sf), C.byref(s2)), "quantize_nvfp4_host")
+    return q, sf, s2.value
+
+
+def quant_act_nvfp4(x, input_scale, up=None, device=0):
+    x = np.ascontiguousarray(x, np.float32)
+    up = None if up is None else np.ascontiguousarray(up, np.float32)
+    M, K = x.shape
+    q, sf = np.zeros((M, K // 2), np.uint8), np.zeros((M, K // 16), np.uint8)
+    check(lib().ling_b200_quant_act_nvfp4_host(device, _fp(x), _fp(up), M, K, C.c_float(input_scale), _bp(q), _bp(sf)),
+          "quant_act_nvfp4_host")
+    return q, sf
+
+
+def rmsnorm_quant_nvfp4(x, w_bf16_bits, eps, input_scale, want_out=True, device=0):
+    x = np.ascontiguousarray(x, np.float32)
+    w = np.ascontiguousarray(w_bf16_bits, np.uint16)
+    M, H = x.shape
+    out = np.zeros((M, H), np.float32) if want_out else None
+    q, sf = np.zeros((M, H // 2), np.uint8), np.zeros((M, H // 16), np.uint8)
+    check(lib().ling_b200_rmsnorm_quant_nvfp4_host(device, _fp(x), _up(w), _fp(out), M, H, C.c_float(eps), C.c_float(input_scale),
+                                                   _bp(q), _bp(sf)), "rmsnorm_quant_nvfp4_host")
+    return out, q, sf
+
+
+def prefill_gemm_nvfp4(xq, xs, wq, ws, alpha, y=None, ldy=None, accumulate=False, device=0):
+    """y [M][ldy] (columns [0, N) written).  y given: used as the starting contents (and added to with accumulate)."""
+    xq, xs, wq, ws = (np.ascontiguousarray(a, np.uint8) for a in (xq, xs, wq, ws))
+    M, N, K = xq.shape[0], wq.shape[0], xq.shape[1] * 2
+    ldy = ldy or N
+    y = np.zeros((M, ldy), np.float32) if y is None else np.ascontiguousarray(y, np.float32).copy()
+    check(lib().ling_b200_prefill_gemm_nvfp4_host(device, _bp(xq), _bp(xs), M, _bp(wq), _bp(ws), C.c_float(alpha), _fp(y), ldy, N, K,
+                                                  1 if accumulate else 0), "prefill_gemm_nvfp4_host")
+    return y
+
+
+def prefill_swiglu_nvfp4(xq, xs, gq, gs, alpha_gate, uq, us, alpha_up, out_input_scale, device=0):
+    xq, xs, gq, gs, uq, us = (np.ascontiguousarray(a, np.uint8) for a in (xq, xs, gq, gs, uq, us))
+    M, N, K = xq.shape[0], gq.shape[0], xq.shape[1] * 2
+    q, sf = np.zeros((M, N // 2), np.uint8), np.zeros((M, N // 16), np.uint8)
+    check(lib().ling_b200_prefill_swiglu_nvfp4_host(device, _bp(xq), _bp(xs), M, _bp(gq), _bp(gs), C.c_float(alpha_gate), _bp(uq),
+                                                    _bp(us), C.c_float(alpha_up), N, K, C.c_float(out_input_scale), _bp(q), _bp(sf)),
+          "prefill_swiglu_nvfp4_host")
+    return q, sf
+
+
+def nvfp4_gemm_bench(M, N, K, fused=False, iters=10, device=0):
+    ms = C.c_float()
+    check(lib().ling_b200_nvfp4_gemm_bench(device, M, N, K, 1 if fused else 0, iters, C.byref(ms)), "nvfp4_gemm_bench")
+    return ms.value
+
+
+class Nvfp4Ffn:
+    """The prefill chunk's NVFP4 feed-forward stack on the device (synthetic weights), on a stream of its own."""
+
+    def __init__(self, layers, hidden, intermediate, max_rows, seed=0, device=0):
+        self.h = C.c_void_p()
+        self.layers, self.hidden, self.intermediate, self.max_rows = layers, hidden, intermediate, max_rows
+        L = lib()
+        L.ling_b200_nvfp4_ffn_create.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_uint64, C.POINTER(C.c_void_p)]
+        for n in ("destroy", "set_residual", "launch", "wait", "forward", "read_layer"):
+            getattr(L, "ling_b200_nvfp4_ffn_" + n).argtypes = None
+        check(L.ling_b200_nvfp4_ffn_create(device, layers, hidden, intermediate, max_rows, seed, C.byref(self.h)), "nvfp4_ffn_create")
+
+    def close(self):
+        if self.h:
+            lib().ling_b200_nvfp4_ffn_destroy(self.h)
+            self.h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def set_residual(self, h):
+        h = np.ascontiguousarray(h, np.float32)
+        check(lib().ling_b200_nvfp4_ffn_set_residual(self.h, _fp(h), h.shape[0]), "nvfp4_ffn_set_residual")
+
+    def launch(self, rows):
+        check(lib().ling_b200_nvfp4_ffn_launch(self.h, rows), "nvfp4_ffn_launch")
+
+    def wait(self):
+        ms = C.c_float()
+        check(lib().ling_b200_nvfp4_ffn_wait(self.h, C.byref(ms)), "nvfp4_ffn_wait")
+        return ms.value
+
+    def forward(self, h):
+        h = np.ascontiguousarray(h, np.float32)
+        out = np.zeros_like(h)
+        check(lib().ling_b200_nvfp4_ffn_forward(self.h, _fp(h), h.shape[0], _fp(out)), "nvfp4_ffn_forward")
+        return out
+
+    def read_layer(self, layer):
+        H, I = self.hidden, self.intermediate
+        norm = np.zeros(H, np.uint16)
+        gq, gs = np.zeros((I, H // 2), np.uint8), np.zeros((I, H // 16), np.uint8)
+        uq, us = np.zeros((I, H // 2), np.uint8), np.zeros((I, H // 16), np.uint8)
+        dq, ds = np.zeros((H, I // 2), np.uint8), np.zeros((H, I // 16), np.uint8)
+        sc = np.zeros(5, np.float32)
+        check(lib().ling_b200_nvfp4_ffn_read_layer(self.h, layer, _up(norm), _bp(gq), _bp(gs), _bp(uq), _bp(us), _bp(dq), _bp(ds),
+                                                   _fp(sc)), "nvfp4_ffn_read_layer")
+        return dict(norm=norm, gate=(gq, gs), up=(uq, us), down=(dq, ds), in_scale=float(sc[0]), mid_scale=float(sc[1]),
+                    s_gate=float(sc[2]), s_up=float(sc[3]), s_down=float(sc[4]))
+
+
 def describe_tree(parent, chain):
     par = np.ascontiguousarray(parent, np.int32)
     t = TreeDesc()

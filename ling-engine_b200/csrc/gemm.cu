@@ -571,6 +571,10 @@ int gemm_init() {
   return init_tc<128>();
 }
 
+int encode_tile_map(CUtensorMap* map, void* base, uint64_t row_bytes, uint64_t rows, uint32_t box_rows) {
+  return encode_2d(map, base, row_bytes, rows, box_rows);
+}
+
 int make_weight_map(Fp8Matrix& w) { return encode_2d(&w.map, w.codes, uint64_t(w.K_pad), uint64_t(w.N_pad), kTileN); }
 
 int make_acts_maps(Fp8Acts& x) {

@@ -54,6 +54,9 @@ struct GemmCall {
   unsigned long long* timeline = nullptr;  // four stamps of this launch (debugging aid), or nullptr
 };
 
+// Tensor map of a row-major byte matrix [rows][row_bytes] read in boxes of 128 bytes x box_rows under the 128B swizzle
+// (row_bytes a multiple of 16; rows and bytes past the extent read zero).
+int encode_tile_map(CUtensorMap* map, void* base, uint64_t row_bytes, uint64_t rows, uint32_t box_rows);
 // Creates the tensor maps (driver entry point fetched at run time; no link against libcuda).
 int make_weight_map(Fp8Matrix& w);
 int make_acts_maps(Fp8Acts& x);

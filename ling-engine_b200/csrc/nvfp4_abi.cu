@@ -1,0 +1,400 @@
+// nvfp4_abi.cu -- C-ABI entry points of the NVFP4 prefill-chunk path: the quantizers and GEMMs on host buffers (copy in,
+// launch, copy out), as the reference's kernel tests drive them (tests/prefill_tests.cu in the reference project), and the
+// chunk's feed-forward stack (norm -> gate|up with fused SwiGLU -> down into the residual, layer after layer) held on the
+// device for the mixed prefill + decode pass.
+#include <cmath>
+#include <cstring>
+#include <memory>
+
+#include "abi_util.h"
+#include "nvfp4.h"
+
+using namespace lb;
+
+namespace {
+
+bool multiple(int v, int m) { return v > 0 && v % m == 0; }
+
+// An operand on the device built from host codes [rows][K/2] and row-major scales [rows][K/16].
+int upload_operand(Scratch& sc, Fp4Operand& o, const uint8_t* q, const uint8_t* sf, int rows, int K) {
+  o.rows = rows, o.K = K;
+  o.codes = sc.put(q, size_t(rows) * (K / 2));
+  o.sf = sc.get<uint8_t>(fp4_sf_bytes(rows, K));
+  uint8_t* raw = sc.put(sf, size_t(rows) * (K / 16));
+  LB_PTR(o.codes && o.sf && raw);
+  LB_TRY(fp4_sf_tile_launch(raw, o.sf, rows, K, 0));
+  return make_fp4_map(o);
+}
+
+int read_flag(const int* err, const char* what) {
+  int code = 0;
+  LB_CUDA(cudaMemcpy(&code, err, 4, cudaMemcpyDeviceToHost));
+  if (code) {
+    set_error(std::string(what) + ": device error word = " + std::to_string(code));
+    return LING_B200_ERR_DEVICE_FLAG;
+  }
+  return LING_B200_OK;
+}
+
+}  // namespace
+
+// The chunk's feed-forward stack: per layer the post-attention norm weight and the three NVFP4 matrices.
+struct ling_b200_nvfp4_ffn {
+  int device = 0, layers = 0, H = 0, I = 0, max_rows = 0;
+  float eps = 1e-6f;
+  struct Layer {
+    __nv_bfloat16* norm = nullptr;
+    Fp4Operand gate, up, down;
+    float in_scale = 1.f, mid_scale = 1.f;  // the activations' static input scales
+    float s_gate = 1.f, s_up = 1.f, s_down = 1.f;  // the weights' tensor scales
+  };
+  std::vector<Layer> L;
+  float* h = nullptr;      // residual [max_rows][H]
+  Fp4Operand x, mid;       // the two GEMMs' activations
+  int* err = nullptr;
+  float* pin_in = nullptr;   // pinned host staging for the end-to-end call
+  float* pin_out = nullptr;
+  cudaStream_t stream = nullptr;
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  Scratch mem;
+  ~ling_b200_nvfp4_ffn() {
+    if (pin_in) cudaFreeHost(pin_in);
+    if (pin_out) cudaFreeHost(pin_out);
+    if (ev0) cudaEventDestroy(ev0);
+    if (ev1) cudaEventDestroy(ev1);
+    if (stream) cudaStreamDestroy(stream);
+  }
+};
+
+namespace {
+
+int alloc_operand(Scratch& sc, Fp4Operand& o, int rows, int K) {
+  o.rows = rows, o.K = K;
+  o.codes = sc.get<uint8_t>(size_t(rows) * (K / 2));
+  o.sf = sc.get<uint8_t>(fp4_sf_bytes(rows, K));
+  LB_PTR(o.codes && o.sf);
+  return make_fp4_map(o);
+}
+
+// One synthetic NVFP4 matrix: BF16 N(0, 0.02) from the library's generator, rounded as a checkpoint's NVFP4 is.
+int synth_matrix(ling_b200_nvfp4_ffn* f, Fp4Operand& o, int N, int K, uint64_t key, __nv_bfloat16* tmp, unsigned* amax, float* scale2_dev,
+                 float* scale2) {
+  LB_TRY(alloc_operand(f->mem, o, N, K));
+  LB_TRY(fill_bf16_launch(nullptr, key, 0.02f, 0.f, 1, tmp, size_t(N) * K, f->stream));
+  LB_CUDA(cudaMemsetAsync(amax, 0, 4, f->stream));
+  LB_TRY(fp4_quant_weight_launch(tmp, N, K, o.codes, o.sf, true, scale2_dev, amax, f->stream));
+  LB_CUDA(cudaMemcpyAsync(scale2, scale2_dev, 4, cudaMemcpyDeviceToHost, f->stream));
+  LB_CUDA(cudaStreamSynchronize(f->stream));
+  return LING_B200_OK;
+}
+
+// The stack over rows [0, rows) of the residual, on the object's stream.
+int ffn_run(ling_b200_nvfp4_ffn* f, int rows) {
+  f->x.rows = rows, f->mid.rows = rows;
+  LB_TRY(make_fp4_map(f->x));
+  LB_TRY(make_fp4_map(f->mid));
+  for (const auto& L : f->L) {
+    LB_TRY(fp4_rmsnorm_quant_launch(f->h, L.norm, nullptr, rows, f->H, f->eps, 1.f / L.in_scale, f->x.codes, f->x.sf, true, f->stream));
+    Fp4GemmCall gu;
+    gu.X = &f->x, gu.W = &L.gate, gu.W2 = &L.up;
+    gu.alpha = L.in_scale * L.s_gate, gu.alpha2 = L.in_scale * L.s_up;
+    gu.q_out = f->mid.codes, gu.sf_out = f->mid.sf, gu.sf_out_tiled = true, gu.gscale_out = 1.f / L.mid_scale;
+    gu.err_flag = f->err;
+    LB_TRY(fp4_gemm_launch(gu, f->stream));
+    Fp4GemmCall dn;
+    dn.X = &f->mid, dn.W = &L.down;
+    dn.alpha = L.mid_scale * L.s_down;
+    dn.y = f->h, dn.ldy = f->H, dn.accumulate = true;
+    dn.err_flag = f->err;
+    LB_TRY(fp4_gemm_launch(dn, f->stream));
+  }
+  return LING_B200_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int ling_b200_quantize_nvfp4_host(int device, const uint16_t* w_bf16, int N, int K, uint8_t* values, uint8_t* scales, float* scale2) {
+  if (!w_bf16 || !values || !scales || !scale2 || N < 1 || !multiple(K, 16)) {
+    set_error("quantize_nvfp4: K must be a positive multiple of 16");
+    return LING_B200_ERR_ARG;
+  }
+  LB_TRY(check_device(device));
+  Scratch sc;
+  auto* w = reinterpret_cast<__nv_bfloat16*>(sc.put(w_bf16, size_t(N) * K));
+  uint8_t* q = sc.get<uint8_t>(size_t(N) * (K / 2));
+  uint8_t* sf = sc.get<uint8_t>(size_t(N) * (K / 16));
+  float* s2 = sc.get<float>(1);
+  unsigned* amax = sc.get<unsigned>(1);
+  LB_PTR(w && q && sf && s2 && amax);
+  LB_TRY(fp4_quant_weight_launch(w, N, K, q, sf, false, s2, amax, 0));
+  LB_CUDA(cudaMemcpy(values, q, size_t(N) * (K / 2), cudaMemcpyDeviceToHost));
+  LB_CUDA(cudaMemcpy(scales, sf, size_t(N) * (K / 16), cudaMemcpyDeviceToHost));
+  LB_CUDA(cudaMemcpy(scale2, s2, 4, cudaMemcpyDeviceToHost));
+  return LING_B200_OK;
+}
+
+int ling_b200_quant_act_nvfp4_host(int device, const float* x, const float* up, int M, int K, float input_scale, uint8_t* q, uint8_t* sf) {
+  if (!x || !q || !sf || M < 1 || !multiple(K, 16) || !(input_scale > 0.f)) {
+    set_error("quant_act_nvfp4: K must be a positive multiple of 16 and input_scale positive");
+    return LING_B200_ERR_ARG;
+  }
+  LB_TRY(check_device(device));
+  Scratch sc;
+  float* dx = sc.put(x, size_t(M) * K);
+  float* du = up ? sc.put(up, size_t(M) * K) : nullptr;
+  uint8_t* dq = sc.get<uint8_t>(size_t(M) * (K / 2));
+  uint8_t* ds = sc.get<uint8_t>(size_t(M) * (K / 16));
+  LB_PTR(dx && dq && ds && (!up || du));
+  LB_TRY(fp4_quant_act_launch(dx, du, M, K, 1.f / input_scale, dq, ds, false, 0));
+  LB_CUDA(cudaMemcpy(q, dq, size_t(M) * (K / 2), cudaMemcpyDeviceToHost));
+  LB_CUDA(cudaMemcpy(sf, ds, size_t(M) * (K / 16), cudaMemcpyDeviceToHost));
+  return LING_B200_OK;
+}
+
+int ling_b200_rmsnorm_quant_nvfp4_host(int device, const float* x, const uint16_t* w_bf16, float* out, int M, int H, float eps,
+                                       float input_scale, uint8_t* q, uint8_t* sf) {
+  if (!x || !w_bf16 || !q || !sf || M < 1 || !multiple(H, 16) || !(input_scale > 0.f)) {
+    set_error("rmsnorm_quant: H must be a positive multiple of 16 and input_scale positive");
+    return LING_B200_ERR_ARG;
+  }
+  LB_TRY(check_device(device));
+  Scratch sc;
+  float* dx = sc.put(x, size_t(M) * H);
+  auto* dw = reinterpret_cast<__nv_bfloat16*>(sc.put(w_bf16, size_t(H)));
+  float* dout = out ? sc.get<float>(size_t(M) * H) : nullptr;
+  uint8_t* dq = sc.get<uint8_t>(size_t(M) * (H / 2));
+  uint8_t* ds = sc.get<uint8_t>(size_t(M) * (H / 16));
+  LB_PTR(dx && dw && dq && ds && (!out || dout));
+  LB_TRY(fp4_rmsnorm_quant_launch(dx, dw, dout, M, H, eps, 1.f / input_scale, dq, ds, false, 0));
+  if (out) LB_CUDA(cudaMemcpy(out, dout, size_t(M) * H * 4, cudaMemcpyDeviceToHost));
+  LB_CUDA(cudaMemcpy(q, dq, size_t(M) * (H / 2), cudaMemcpyDeviceToHost));
+  LB_CUDA(cudaMemcpy(sf, ds, size_t(M) * (H / 16), cudaMemcpyDeviceToHost));
+  return LING_B200_OK;
+}
+
+int ling_b200_prefill_gemm_nvfp4_host(int device, const uint8_t* xq, const uint8_t* xs, int M, const uint8_t* wq, const uint8_t* ws,
+                                      float alpha, float* y, int ldy, int N, int K, int accumulate) {
+  if (!xq || !xs || !wq || !ws || !y || M < 0 || !multiple(N, 128) || !multiple(K, 128) || ldy < N || ldy % 4) {
+    set_error("prefill_gemm_nvfp4: N % 128 and K % 128 must be 0, ldy >= N and a multiple of 4");
+    return LING_B200_ERR_ARG;
+  }
+  if (M == 0) return LING_B200_OK;
+  LB_TRY(check_device(device));
+  Scratch sc;
+  Fp4Operand X, W;
+  LB_TRY(upload_operand(sc, X, xq, xs, M, K));
+  LB_TRY(upload_operand(sc, W, wq, ws, N, K));
+  float* dy = sc.put(y, size_t(M) * ldy);
+  int* err = sc.get<int>(1);
+  LB_PTR(dy && err);
+  Fp4GemmCall c;
+  c.X = &X, c.W = &W, c.alpha = alpha, c.y = dy, c.ldy = ldy, c.accumulate = accumulate != 0, c.err_flag = err;
+  LB_TRY(fp4_gemm_launch(c, 0));
+  LB_CUDA(cudaDeviceSynchronize());
+  LB_TRY(read_flag(err, "prefill_gemm_nvfp4"));
+  LB_CUDA(cudaMemcpy(y, dy, size_t(M) * ldy * 4, cudaMemcpyDeviceToHost));
+  return LING_B200_OK;
+}
+
+int ling_b200_prefill_swiglu_nvfp4_host(int device, const uint8_t* xq, const uint8_t* xs, int M, const uint8_t* gate_q,
+                                        const uint8_t* gate_s, float alpha_gate, const uint8_t* up_q, const uint8_t* up_s, float alpha_up,
+                                        int N, int K, float out_input_scale, uint8_t* q_out, uint8_t* sf_out) {
+  if (!xq || !xs || !gate_q || !gate_s || !up_q || !up_s || !q_out || !sf_out || M < 0 || !multiple(N, 128) || !multiple(K, 128) ||
+      !(out_input_scale > 0.f)) {
+    set_error("prefill_swiglu_nvfp4: N % 128 and K % 128 must be 0 and out_input_scale positive");
+    return LING_B200_ERR_ARG;
+  }
+  if (M == 0) return LING_B200_OK;
+  LB_TRY(check_device(device));
+  Scratch sc;
+  Fp4Operand X, G, U;
+  LB_TRY(upload_operand(sc, X, xq, xs, M, K));
+  LB_TRY(upload_operand(sc, G, gate_q, gate_s, N, K));
+  LB_TRY(upload_operand(sc, U, up_q, up_s, N, K));
+  uint8_t* dq = sc.get<uint8_t>(size_t(M) * (N / 2));
+  uint8_t* ds = sc.get<uint8_t>(size_t(M) * (N / 16));
+  int* err = sc.get<int>(1);
+  LB_PTR(dq && ds && err);
+  Fp4GemmCall c;
+  c.X = &X, c.W = &G, c.W2 = &U, c.alpha = alpha_gate, c.alpha2 = alpha_up;
+  c.q_out = dq, c.sf_out = ds, c.sf_out_tiled = false, c.gscale_out = 1.f / out_input_scale, c.err_flag = err;
+  LB_TRY(fp4_gemm_launch(c, 0));
+  LB_CUDA(cudaDeviceSynchronize());
+  LB_TRY(read_flag(err, "prefill_swiglu_nvfp4"));
+  LB_CUDA(cudaMemcpy(q_out, dq, size_t(M) * (N / 2), cudaMemcpyDeviceToHost));
+  LB_CUDA(cudaMemcpy(sf_out, ds, size_t(M) * (N / 16), cudaMemcpyDeviceToHost));
+  return LING_B200_OK;
+}
+
+int ling_b200_nvfp4_gemm_bench(int device, int M, int N, int K, int fused, int iters, float* ms_per_launch) {
+  if (!ms_per_launch || M < 1 || !multiple(N, 128) || !multiple(K, 128) || iters < 1) {
+    set_error("nvfp4_gemm_bench: bad argument");
+    return LING_B200_ERR_ARG;
+  }
+  LB_TRY(check_device(device));
+  Scratch sc;
+  Fp4Operand X, W, W2, Out;
+  auto make = [&](Fp4Operand& o, int rows, int Kk, int seed) -> int {
+    o.rows = rows, o.K = Kk;
+    o.codes = sc.get<uint8_t>(size_t(rows) * (Kk / 2));
+    o.sf = sc.get<uint8_t>(fp4_sf_bytes(rows, Kk));
+    LB_PTR(o.codes && o.sf);
+    // codes: every nibble pattern; scales: E4M3 codes 0x30..0x3f (0.5 .. 1.9)
+    std::vector<uint8_t> hq(size_t(rows) * (Kk / 2)), hs(fp4_sf_bytes(rows, Kk));
+    uint64_t s = 0x9E3779B97F4A7C15ull * uint64_t(seed + 1);
+    for (auto& b : hq) b = uint8_t((s = s * 6364136223846793005ull + 1442695040888963407ull) >> 56);
+    for (auto& b : hs) b = uint8_t(0x30 + (((s = s * 6364136223846793005ull + 1442695040888963407ull) >> 60) & 15));
+    LB_CUDA(cudaMemcpy(o.codes, hq.data(), hq.size(), cudaMemcpyHostToDevice));
+    LB_CUDA(cudaMemcpy(o.sf, hs.data(), hs.size(), cudaMemcpyHostToDevice));
+    return make_fp4_map(o);
+  };
+  LB_TRY(make(X, M, K, 1));
+  LB_TRY(make(W, N, K, 2));
+  if (fused) LB_TRY(make(W2, N, K, 3));
+  float* y = fused ? nullptr : sc.get<float>(size_t(M) * N);
+  if (fused) LB_TRY(make(Out, M, N, 4));
+  int* err = sc.get<int>(1);
+  LB_PTR(err && (fused || y));
+  Fp4GemmCall c;
+  c.X = &X, c.W = &W, c.W2 = fused ? &W2 : nullptr, c.alpha = 1e-3f, c.alpha2 = 1e-3f;
+  c.y = y, c.ldy = N, c.q_out = Out.codes, c.sf_out = Out.sf, c.err_flag = err;
+  cudaEvent_t a, b;
+  LB_CUDA(cudaEventCreate(&a));
+  LB_CUDA(cudaEventCreate(&b));
+  for (int i = 0; i < 3; ++i) LB_TRY(fp4_gemm_launch(c, 0));
+  LB_CUDA(cudaEventRecord(a, 0));
+  for (int i = 0; i < iters; ++i) LB_TRY(fp4_gemm_launch(c, 0));
+  LB_CUDA(cudaEventRecord(b, 0));
+  LB_CUDA(cudaEventSynchronize(b));
+  float t = 0.f;
+  LB_CUDA(cudaEventElapsedTime(&t, a, b));
+  cudaEventDestroy(a), cudaEventDestroy(b);
+  LB_TRY(read_flag(err, "nvfp4_gemm_bench"));
+  *ms_per_launch = t / iters;
+  return LING_B200_OK;
+}
+
+int ling_b200_nvfp4_ffn_create(int device, int layers, int hidden, int intermediate, int max_rows, uint64_t seed,
+                               ling_b200_nvfp4_ffn** out) {
+  if (!out || layers < 1 || !multiple(hidden, 256) || !multiple(intermediate, 128) || max_rows < 1) {
+    set_error("nvfp4_ffn_create: hidden % 256 and intermediate % 128 must be 0");
+    return LING_B200_ERR_ARG;
+  }
+  LB_TRY(check_device(device));
+  std::unique_ptr<ling_b200_nvfp4_ffn> f(new ling_b200_nvfp4_ffn);
+  f->device = device, f->layers = layers, f->H = hidden, f->I = intermediate, f->max_rows = max_rows;
+  LB_CUDA(cudaStreamCreateWithFlags(&f->stream, cudaStreamNonBlocking));
+  LB_CUDA(cudaEventCreate(&f->ev0));
+  LB_CUDA(cudaEventCreate(&f->ev1));
+  f->h = f->mem.get<float>(size_t(max_rows) * hidden);
+  f->err = f->mem.get<int>(1);
+  LB_PTR(f->h && f->err);
+  LB_TRY(alloc_operand(f->mem, f->x, max_rows, hidden));
+  LB_TRY(alloc_operand(f->mem, f->mid, max_rows, intermediate));
+  LB_CUDA(cudaMallocHost(&f->pin_in, size_t(max_rows) * hidden * 4));
+  LB_CUDA(cudaMallocHost(&f->pin_out, size_t(max_rows) * hidden * 4));
+  Scratch tmp;
+  auto* wtmp = tmp.get<__nv_bfloat16>(size_t(intermediate) * hidden, false);
+  unsigned* amax = tmp.get<unsigned>(1);
+  float* s2 = tmp.get<float>(1);
+  LB_PTR(wtmp && amax && s2);
+  f->L.resize(layers);
+  for (int l = 0; l < layers; ++l) {
+    auto& L = f->L[l];
+    L.norm = f->mem.get<__nv_bfloat16>(hidden);
+    LB_PTR(L.norm);
+    LB_TRY(fill_bf16_launch(nullptr, stream_key(seed, weight_stream(l, LING_B200_T_POST_NORM)), 0.02f, 0.f, 1, L.norm, hidden, f->stream));
+    LB_TRY(synth_matrix(f.get(), L.gate, intermediate, hidden, stream_key(seed, weight_stream(l, LING_B200_T_GATE)), wtmp, amax, s2, &L.s_gate));
+    LB_TRY(synth_matrix(f.get(), L.up, intermediate, hidden, stream_key(seed, weight_stream(l, LING_B200_T_UP)), wtmp, amax, s2, &L.s_up));
+    LB_TRY(synth_matrix(f.get(), L.down, hidden, intermediate, stream_key(seed, weight_stream(l, LING_B200_T_DOWN)), wtmp, amax, s2, &L.s_down));
+    // Static activation scales as a calibration would leave them: a block's scale E4M3(amax / 6 / input_scale) saturates
+    // at 448, so input_scale = A / (6 * 448) represents magnitudes up to A: 16 for the normed residual (unit variance), 64
+    // for the gated product.
+    L.in_scale = 16.f / (6.f * 448.f);
+    L.mid_scale = 64.f / (6.f * 448.f);
+  }
+  LB_CUDA(cudaStreamSynchronize(f->stream));
+  *out = f.release();
+  return LING_B200_OK;
+}
+
+void ling_b200_nvfp4_ffn_destroy(ling_b200_nvfp4_ffn* f) { delete f; }
+
+int ling_b200_nvfp4_ffn_set_residual(ling_b200_nvfp4_ffn* f, const float* h, int rows) {
+  if (!f || !h || rows < 1 || rows > f->max_rows) {
+    set_error("nvfp4_ffn_set_residual: bad argument");
+    return LING_B200_ERR_ARG;
+  }
+  LB_CUDA(cudaSetDevice(f->device));
+  LB_CUDA(cudaMemcpyAsync(f->h, h, size_t(rows) * f->H * 4, cudaMemcpyHostToDevice, f->stream));
+  LB_CUDA(cudaStreamSynchronize(f->stream));
+  return LING_B200_OK;
+}
+
+int ling_b200_nvfp4_ffn_launch(ling_b200_nvfp4_ffn* f, int rows) {
+  if (!f || rows < 1 || rows > f->max_rows) {
+    set_error("nvfp4_ffn_launch: bad argument");
+    return LING_B200_ERR_ARG;
+  }
+  LB_CUDA(cudaSetDevice(f->device));
+  LB_CUDA(cudaEventRecord(f->ev0, f->stream));
+  LB_TRY(ffn_run(f, rows));
+  LB_CUDA(cudaEventRecord(f->ev1, f->stream));
+  return LING_B200_OK;
+}
+
+int ling_b200_nvfp4_ffn_wait(ling_b200_nvfp4_ffn* f, float* device_ms) {
+  if (!f) return LING_B200_ERR_ARG;
+  LB_CUDA(cudaSetDevice(f->device));
+  LB_CUDA(cudaEventSynchronize(f->ev1));
+  if (device_ms) LB_CUDA(cudaEventElapsedTime(device_ms, f->ev0, f->ev1));
+  return read_flag(f->err, "nvfp4_ffn");
+}
+
+int ling_b200_nvfp4_ffn_forward(ling_b200_nvfp4_ffn* f, const float* h_in, int rows, float* h_out) {
+  if (!f || !h_in || !h_out || rows < 1 || rows > f->max_rows) {
+    set_error("nvfp4_ffn_forward: bad argument");
+    return LING_B200_ERR_ARG;
+  }
+  LB_CUDA(cudaSetDevice(f->device));
+  const size_t bytes = size_t(rows) * f->H * 4;
+  std::memcpy(f->pin_in, h_in, bytes);
+  LB_CUDA(cudaMemcpyAsync(f->h, f->pin_in, bytes, cudaMemcpyHostToDevice, f->stream));
+  LB_TRY(ffn_run(f, rows));
+  LB_CUDA(cudaMemcpyAsync(f->pin_out, f->h, bytes, cudaMemcpyDeviceToHost, f->stream));
+  LB_CUDA(cudaStreamSynchronize(f->stream));
+  LB_TRY(read_flag(f->err, "nvfp4_ffn_forward"));
+  std::memcpy(h_out, f->pin_out, bytes);
+  return LING_B200_OK;
+}
+
+int ling_b200_nvfp4_ffn_read_layer(ling_b200_nvfp4_ffn* f, int layer, uint16_t* norm_bf16, uint8_t* gate_q, uint8_t* gate_s,
+                                   uint8_t* up_q, uint8_t* up_s, uint8_t* down_q, uint8_t* down_s, float* scales5) {
+  if (!f || layer < 0 || layer >= f->layers) {
+    set_error("nvfp4_ffn_read_layer: bad layer");
+    return LING_B200_ERR_ARG;
+  }
+  LB_CUDA(cudaSetDevice(f->device));
+  const auto& L = f->L[layer];
+  Scratch sc;
+  auto read = [&](const Fp4Operand& o, uint8_t* q, uint8_t* s) -> int {
+    if (q) LB_CUDA(cudaMemcpy(q, o.codes, size_t(o.rows) * (o.K / 2), cudaMemcpyDeviceToHost));
+    if (s) {
+      uint8_t* raw = sc.get<uint8_t>(size_t(o.rows) * (o.K / 16));
+      LB_PTR(raw);
+      LB_TRY(fp4_sf_untile_launch(o.sf, raw, o.rows, o.K, 0));
+      LB_CUDA(cudaMemcpy(s, raw, size_t(o.rows) * (o.K / 16), cudaMemcpyDeviceToHost));
+    }
+    return LING_B200_OK;
+  };
+  if (norm_bf16) LB_CUDA(cudaMemcpy(norm_bf16, L.norm, size_t(f->H) * 2, cudaMemcpyDeviceToHost));
+  LB_TRY(read(L.gate, gate_q, gate_s));
+  LB_TRY(read(L.up, up_q, up_s));
+  LB_TRY(read(L.down, down_q, down_s));
+  if (scales5) scales5[0] = L.in_scale, scales5[1] = L.mid_scale, scales5[2] = L.s_gate, scales5[3] = L.s_up, scales5[4] = L.s_down;
+  return LING_B200_OK;
+}
+
+}  // extern "C"

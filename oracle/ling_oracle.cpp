@@ -1204,4 +1204,135 @@ int lo_read_tap(lo_model* m, int layer, float* out) {
   return 0;
 }
 
+// ---------------------------------------------------------------------------------------------- NVFP4 (prefill chunk)
+// E2M1 values, two a byte with the first in the low nibble, one E4M3 scale per 16 values, one fp32 scale per tensor.
+static const float kE2M1[16] = {0.f, 0.5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f, -0.f, -0.5f, -1.f, -1.5f, -2.f, -3.f, -4.f, -6.f};
+
+// E2M1 to nearest with ties to the even code and saturation at 6 (cvt.rn.satfinite.e2m1x2.f32); a negative value that
+// rounds to zero keeps its sign bit (tests/prefill_tests.cu:44-55 of the reference project writes out the same rule).
+static uint8_t e2m1_rne(float x) {
+  static const float mid[7] = {0.25f, 0.75f, 1.25f, 1.75f, 2.5f, 3.5f, 5.f};  // mid[i] lies between codes i and i + 1
+  if (std::isnan(x)) return 7;  // satfinite turns NaN into the largest positive magnitude
+  const float a = std::fabs(x);
+  int c = 0;
+  for (int i = 0; i < 7; ++i)
+    if (a > mid[i] || (a == mid[i] && (i & 1))) c = i + 1;  // on a midpoint: the even code of the two
+  return uint8_t(c | (std::signbit(x) ? 8 : 0));
+}
+
+// Weights to NVFP4 in the checkpoints' rounding (src/core/model.cu:188-249): g = amax / (448 * 6) (1 for an all-zero
+// matrix); per block of 16 the E4M3 scale of max(amax16 / 6 / g, 2^-9); each value's code is the first of the codes'
+// midpoints {0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5} that is not below |x / (scale * g)|, so a value on a midpoint takes
+// the smaller magnitude; zero magnitudes carry no sign.  w: BF16 bit patterns [N][K]; q [N][K/2]; sf [N][K/16].
+int lo_nvfp4_quantize_weight(const uint16_t* w, int N, int K, uint8_t* q, uint8_t* sf, float* scale2) {
+  if (N <= 0 || K <= 0 || K % 16) return 1;
+  init_dec();
+  auto val = [&](size_t i) {
+    const uint32_t u = uint32_t(w[i]) << 16;
+    float f;
+    std::memcpy(&f, &u, 4);
+    return f;
+  };
+  float mx = 0.f;
+  for (size_t i = 0; i < size_t(N) * K; ++i) mx = std::max(mx, std::fabs(val(i)));
+  const float g = mx > 0.f ? mx / (448.f * 6.f) : 1.f;
+  *scale2 = g;
+  static const float mid[7] = {0.25f, 0.75f, 1.25f, 1.75f, 2.5f, 3.5f, 5.f};
+  parallel_for(N, [&](int lo, int hi) {
+    for (int r = lo; r < hi; ++r)
+      for (int b = 0; b < K / 16; ++b) {
+        const size_t base = size_t(r) * K + size_t(b) * 16;
+        float bm = 0.f;
+        for (int j = 0; j < 16; ++j) bm = std::max(bm, std::fabs(val(base + j)));
+        const uint8_t sc = e4m3(std::max(bm / 6.f / g, 0x1p-9f));
+        sf[size_t(r) * (K / 16) + b] = sc;
+        const float s = g_dec[sc] * g;
+        for (int j = 0; j < 16; j += 2) {
+          uint8_t byte = 0;
+          for (int h = 0; h < 2; ++h) {
+            const float x = val(base + j + h), a = std::fabs(x / s);
+            int c = 0;
+            while (c < 7 && mid[c] < a) ++c;
+            if (x < 0.f && c > 0) c |= 8;
+            byte |= uint8_t(c << (4 * h));
+          }
+          q[(base + j) / 2] = byte;
+        }
+      }
+  });
+  return 0;
+}
+
+// Activations to NVFP4 under the global scale 1 / input_scale (src/core/prefill_gemm.cu:383-394,408-420; the host recipe
+// the reference's own test checks it against byte for byte: tests/prefill_tests.cu:72-85): values rounded to BF16, block
+// scale E4M3(gs * (amax * (1/6))), codes E2M1(v * os) with os = 1 / (scale * (1 / gs)) (0 for a zero scale).  With `up`
+// the value quantized is silu(x) * up.  q [M][K/2], sf [M][K/16].
+int lo_nvfp4_quant_act(const float* x, const float* up, int M, int K, float input_scale, uint8_t* q, uint8_t* sf) {
+  if (M <= 0 || K <= 0 || K % 16) return 1;
+  init_dec();
+  const float gs = 1.f / input_scale;
+  parallel_for(M, [&](int lo, int hi) {
+    for (size_t b = size_t(lo) * (K / 16); b < size_t(hi) * (K / 16); ++b) {
+      float v[16], amax = 0.f;
+      for (int j = 0; j < 16; ++j) {
+        float f = x[b * 16 + j];
+        if (up) f = (f / (1.f + std::exp(-f))) * up[b * 16 + j];
+        v[j] = bf16r(f);
+        amax = std::max(amax, std::fabs(v[j]));
+      }
+      const uint8_t sc = e4m3(gs * (amax * (1.f / 6.f)));
+      sf[b] = sc;
+      const float sv = g_dec[sc], os = sv != 0.f ? 1.f / (sv * (1.f / gs)) : 0.f;
+      for (int j = 0; j < 16; j += 2) q[b * 8 + j / 2] = uint8_t(e2m1_rne(v[j] * os) | (e2m1_rne(v[j + 1] * os) << 4));
+    }
+  });
+  return 0;
+}
+
+// NVFP4 codes and block scales back to fp32 (without the tensor scale).
+int lo_nvfp4_dequant(const uint8_t* q, const uint8_t* sf, int rows, int K, float* out) {
+  init_dec();
+  for (size_t i = 0; i < size_t(rows) * K; ++i) out[i] = kE2M1[(q[i / 2] >> (4 * (i & 1))) & 15] * g_dec[sf[i / 16]];
+  return 0;
+}
+
+// y[m][n] = alpha * sum_k x[m][k] * w[n][k] (+ y with accumulate) over the dequantized operands, the sum in double: the
+// check the reference's own test applies to prefill_gemm_nvfp4 (tests/prefill_tests.cu:176-205; the kernel:
+// src/core/prefill_gemm.cu:344-380,685-690).
+int lo_nvfp4_gemm(const uint8_t* xq, const uint8_t* xs, int M, const uint8_t* wq, const uint8_t* ws, int N, int K, float alpha,
+                  float* y, int ldy, int accumulate) {
+  if (K % 16) return 1;
+  std::vector<float> xa(size_t(M) * K), wa(size_t(N) * K);
+  lo_nvfp4_dequant(xq, xs, M, K, xa.data());
+  lo_nvfp4_dequant(wq, ws, N, K, wa.data());
+  parallel_for(M, [&](int lo, int hi) {
+    for (int m = lo; m < hi; ++m)
+      for (int n = 0; n < N; ++n) {
+        double acc = 0;
+        const float *a = &xa[size_t(m) * K], *b = &wa[size_t(n) * K];
+        for (int k = 0; k < K; ++k) acc += double(a[k]) * double(b[k]);
+        float& o = y[size_t(m) * ldy + n];
+        o = float(acc * double(alpha) + (accumulate ? double(o) : 0.0));
+      }
+  });
+  return 0;
+}
+
+// Gemma RMSNorm rows in fp32 with the sum of squares in double: x * rstd * (1 + w) (src/core/prefill_gemm.cu:426-459; the
+// quantization that follows it there is lo_nvfp4_quant_act of this output).  w: BF16 bit patterns [H].
+int lo_rmsnorm_rows(const float* x, const uint16_t* w, int M, int H, float eps, float* out) {
+  for (int r = 0; r < M; ++r) {
+    double ss = 0;
+    for (int i = 0; i < H; ++i) ss += double(x[size_t(r) * H + i]) * x[size_t(r) * H + i];
+    const float rstd = 1.f / std::sqrt(float(ss / H) + eps);
+    for (int i = 0; i < H; ++i) {
+      const uint32_t u = uint32_t(w[i]) << 16;
+      float wf;
+      std::memcpy(&wf, &u, 4);
+      out[size_t(r) * H + i] = x[size_t(r) * H + i] * rstd * (1.f + wf);
+    }
+  }
+  return 0;
+}
+
 }  // extern "C"

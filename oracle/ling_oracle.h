@@ -130,6 +130,14 @@ int lo_read_argmax(lo_model* m, int* ids, float* vals);
 int lo_read_logits(lo_model* m, float* out);
 int lo_read_tap(lo_model* m, int layer, float* out);
 
+/* NVFP4 operands of the prefill chunk (E2M1 values two a byte, low nibble first; E4M3 scale per 16; fp32 tensor scale). */
+int lo_nvfp4_quantize_weight(const uint16_t* w_bf16, int N, int K, uint8_t* q, uint8_t* sf, float* scale2);
+int lo_nvfp4_quant_act(const float* x, const float* up, int M, int K, float input_scale, uint8_t* q, uint8_t* sf);
+int lo_nvfp4_dequant(const uint8_t* q, const uint8_t* sf, int rows, int K, float* out);
+int lo_nvfp4_gemm(const uint8_t* xq, const uint8_t* xs, int M, const uint8_t* wq, const uint8_t* ws, int N, int K, float alpha,
+                  float* y, int ldy, int accumulate);
+int lo_rmsnorm_rows(const float* x, const uint16_t* w_bf16, int M, int H, float eps, float* out);
+
 #ifdef __cplusplus
 }
 #endif

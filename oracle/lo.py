@@ -16,6 +16,7 @@ REF = os.path.join(HERE, "_ref", "libling_ref.so")
 
 REFCUDA = os.path.join(HERE, "_ref", "libling_refcuda.so")
 REF_TREE_TESTS = os.path.join(HERE, "_ref", "ling-tree-tests")
+REFQUANT = os.path.join(HERE, "_ref", "libling_refquant.so")
 
 
 def build(ref=True, reference=None):
@@ -24,7 +25,7 @@ def build(ref=True, reference=None):
     subprocess.run(["make", "-C", HERE, "-s"], check=True)
     reference = reference or os.environ.get("LING_REFERENCE", "")
     if ref and reference and os.path.isdir(reference):
-        subprocess.run(["make", "-C", HERE, "-s", "ref", "ref_cuda", "REF=" + reference], check=False)
+        subprocess.run(["make", "-C", HERE, "-s", "ref", "ref_cuda", "ref_quant", "REF=" + reference], check=False)
 
 
 _lo = None
@@ -71,6 +72,20 @@ def refcuda():
         L.refcuda_last_error.restype = C.c_char_p
         _refcuda = L
     return _refcuda
+
+
+_refquant = None
+
+
+def refquant():
+    """The reference's host-side NVFP4 weight rounding (quantize_nvfp4), or None where it was not built.  The library
+    carries unresolved references to parts of the reference that are not built here: it is opened with lazy binding."""
+    global _refquant
+    if _refquant is None and os.path.exists(REFQUANT):
+        L = C.CDLL(REFQUANT, mode=os.RTLD_LAZY)
+        L.refquant_last_error.restype = C.c_char_p
+        _refquant = L
+    return _refquant
 
 
 def _ip(a):
@@ -272,3 +287,55 @@ class Model:
         out = np.zeros((self.last_rows, self.cfg.hidden), np.float32)
         assert lo().lo_read_tap(self.h, layer, _fp(out)) == 0
         return out
+
+
+# ---- NVFP4 (prefill chunk): values [rows][K/2] two a byte (low nibble first), E4M3 scales [rows][K/16]
+def _vp(a):
+    return a.ctypes.data_as(C.c_void_p) if a is not None else None
+
+
+def nvfp4_quantize_weight(w_bf16_bits, use_reference=False):
+    """BF16 bit patterns [N][K] -> (values, scales, scale2) by the oracle, or by the reference's own quantize_nvfp4."""
+    w = np.ascontiguousarray(w_bf16_bits, np.uint16)
+    N, K = w.shape
+    q, sf, s2 = np.zeros((N, K // 2), np.uint8), np.zeros((N, K // 16), np.uint8), C.c_float()
+    if use_reference:
+        rc = refquant().refquant_nvfp4(_vp(w), N, K, _bp(q), _bp(sf), C.byref(s2), None)
+    else:
+        rc = lo().lo_nvfp4_quantize_weight(_vp(w), N, K, _bp(q), _bp(sf), C.byref(s2))
+    assert rc == 0
+    return q, sf, s2.value
+
+
+def nvfp4_quant_act(x, input_scale, up=None):
+    x = np.ascontiguousarray(x, np.float32)
+    up = None if up is None else np.ascontiguousarray(up, np.float32)
+    M, K = x.shape
+    q, sf = np.zeros((M, K // 2), np.uint8), np.zeros((M, K // 16), np.uint8)
+    assert lo().lo_nvfp4_quant_act(_fp(x), _fp(up), M, K, C.c_float(input_scale), _bp(q), _bp(sf)) == 0
+    return q, sf
+
+
+def nvfp4_dequant(q, sf):
+    q, sf = np.ascontiguousarray(q, np.uint8), np.ascontiguousarray(sf, np.uint8)
+    rows, K = q.shape[0], q.shape[1] * 2
+    out = np.zeros((rows, K), np.float32)
+    lo().lo_nvfp4_dequant(_bp(q), _bp(sf), rows, K, _fp(out))
+    return out
+
+
+def nvfp4_gemm(xq, xs, wq, ws, alpha, y=None, ldy=None, accumulate=False):
+    xq, xs, wq, ws = (np.ascontiguousarray(a, np.uint8) for a in (xq, xs, wq, ws))
+    M, N, K = xq.shape[0], wq.shape[0], xq.shape[1] * 2
+    ldy = ldy or N
+    y = np.zeros((M, ldy), np.float32) if y is None else np.ascontiguousarray(y, np.float32).copy()
+    assert lo().lo_nvfp4_gemm(_bp(xq), _bp(xs), M, _bp(wq), _bp(ws), N, K, C.c_float(alpha), _fp(y), ldy, 1 if accumulate else 0) == 0
+    return y
+
+
+def rmsnorm_rows(x, w_bf16_bits, eps):
+    x = np.ascontiguousarray(x, np.float32)
+    w = np.ascontiguousarray(w_bf16_bits, np.uint16)
+    out = np.zeros_like(x)
+    lo().lo_rmsnorm_rows(_fp(x), _vp(w), x.shape[0], x.shape[1], C.c_float(eps), _fp(out))
+    return out
