@@ -79,6 +79,8 @@ def workload(name, rank, vocab):
             n = int(sizes[i])
             chain_rows = max(1, (2 * n + 2) // 3)
             specs.append((int(ctxs[i]), chain_plus_branch(chain_rows, n - chain_rows), chain_rows - 1))
+    elif name == "mixed":     # the decode half of the mixed pass: 8 sequences with 24-node trees, contexts uniform in 1k-32k
+        specs = [(int(c), chain_plus_branch(16, 8), 15) for c in rng.integers(1024, 32769, 8)]
     elif name == "toy":
         specs = [(c, chain_plus_branch(16, 4), 15) for c in (3, 37, 512, 1029)]
     else:
@@ -345,7 +347,7 @@ def setup_context(lbm, cfg, seqs, args, rank, local_rank, churn):
     rows = sum(len(q["tokens"]) for q in seqs)
     page_tokens = 16
     pages = sum((q["pos"] + 64 + page_tokens - 1) // page_tokens for q in seqs) + 1
-    max_context = 131072 if churn else max(q["pos"] for q in seqs) + 64
+    max_context = 131072 if churn else -(-(max(q["pos"] for q in seqs) + 64) // page_tokens) * page_tokens
     if churn:
         pages = int(pages * 1.25)   # room for admissions that are longer than the completions they replace
     ctx = lbm.Context(cfg, sessions=len(seqs), max_context=max_context, page_tokens=page_tokens,
@@ -518,6 +520,120 @@ def run_ours(args, rank, local_rank, world):
     dist.close()
 
 
+def run_mixed(args, rank, local_rank, world):
+    """The mixed ragged pass: one 4096-token prefill chunk through the NVFP4 feed-forward stack (norm + quantize, gate|up
+    with fused SwiGLU, down into the residual; 64 layers) beside 8 decoding sequences' verify step (24-node trees, contexts
+    uniform in 1k-32k) on every GPU.  The chunk's mixers (prefill attention, chunked delta rule) are not part of this
+    build, so a step's rows are the decode rows plus the chunk rows through the FFN half only: said in `config`.
+      value     rows per second with both halves launched together on their own streams (device events per half; the
+                step's time is the longer of the two totals, max over ranks)
+      e2e       the same through the host-buffer calls: the chunk's residual copied in and out (pinned staging) and the
+                verify step's descriptors in / results out, inside the timed region
+      roofline  the NVFP4 GEMMs (gemm_nvfp4_tcgen05_kernel) timed alone at the chunk's two shapes against the NVFP4 tensor
+                rate measured on this GPU in the same run (bound: tensor)."""
+    import threading
+    lbm = importlib.import_module("ling-engine_b200")
+    lbm.lib()
+    if lbm.lib().ling_b200_device_count() < 1:
+        raise SystemExit("bench.py: no CUDA device; the product has no CPU path")
+    dist = Dist(world, local_rank)
+    cfg = model_for(lbm, "mixed", args.layers)
+    seqs = workload("mixed", rank, cfg.vocab)
+    rows = sum(len(q["tokens"]) for q in seqs)
+    chunk = 4096
+    ctx, _, _ = setup_context(lbm, cfg, seqs, args, rank, local_rank, False)
+    ffn = lbm.Nvfp4Ffn(cfg.layers, cfg.hidden, cfg.intermediate, chunk, seed=rank, device=local_rank)
+    h0 = np.random.default_rng(50 + rank).standard_normal((chunk, cfg.hidden)).astype(np.float32)
+    ffn.set_residual(h0)
+    flags, K, W = lbm.STEP_COMMIT, args.steps, max(args.warmup, 3)
+    clocks = ClockSampler(local_rank)
+    ctx.stage(seqs, flags)
+    for _ in range(W):
+        ctx.launch()
+    ffn.launch(chunk, W)
+    ffn.wait()
+    res = ctx.fetch()
+    assert all(r.status == 0 and r.n_path == q["accept"] for r, q in zip(res, seqs)), "acceptance differs from the imposed paths"
+    # ---- each half alone
+    ffn.launch(chunk, K)
+    ffn_alone = ffn.wait() / K
+    ctx.timer_begin()
+    for _ in range(K):
+        ctx.launch()
+    verify_alone = ctx.timer_end() / K
+    # ---- both together: the chunk's stack is enqueued on its stream, the verify graphs on theirs
+    clocks.start()
+    dist.barrier()
+    ctx.sync()
+    ffn.launch(chunk, K)
+    ctx.timer_begin()
+    for _ in range(K):
+        ctx.launch()
+    verify_ms = ctx.timer_end()
+    ffn_ms = ffn.wait()
+    ctx.sync()
+    dist.barrier()
+    step_ms = dist.max(max(verify_ms, ffn_ms)) / K
+    launches = ctx.launch_count() + 3 * cfg.layers
+    # ---- end to end: host buffers in and out of both halves every step (two host threads, one per half)
+    out = [None]
+    def chunk_thread():
+        for _ in range(K):
+            out[0] = ffn.forward(h0)
+    ctx.verify_step(seqs, flags)
+    ffn.forward(h0)
+    dist.barrier()
+    t0 = time.perf_counter()
+    th = threading.Thread(target=chunk_thread)
+    th.start()
+    for _ in range(K):
+        ctx.verify_step(seqs, flags)
+    th.join()
+    e2e_s = dist.max(time.perf_counter() - t0)
+    clk = clocks.stop()
+    assert np.isfinite(out[0]).all()
+    # ---- the NVFP4 GEMMs alone, and the tensor pipe's measured rate
+    gu_ms = lbm.nvfp4_gemm_bench(chunk, cfg.intermediate, cfg.hidden, fused=True, iters=10, device=local_rank)
+    dn_ms = lbm.nvfp4_gemm_bench(chunk, cfg.hidden, cfg.intermediate, fused=False, iters=10, device=local_rank)
+    peak_burst, _ = lbm.fp4_tensor_peak(20000, device=local_rank)
+    peak_sustained, _ = lbm.fp4_tensor_peak(400000, device=local_rank)
+    flops = 2.0 * chunk * cfg.intermediate * cfg.hidden
+    achieved = 3 * flops / ((gu_ms + dn_ms) * 1e-3) / 1e12
+    total_rows = dist.sum(rows + chunk)
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": total_rows / (step_ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": step_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "nvfp4 (e2m1 x ue4m3 per 16, fp32 accumulate) chunk FFN + fp8_e4m3 verify", "data": "synthetic",
+            "config": {"workload": "mixed", "model": "27B-class hybrid, %d layers" % cfg.layers, "chunk_rows": chunk,
+                       "chunk_scope": "feed-forward stack only (norm+quantize, gate|up+SwiGLU, down); the chunk's attention / "
+                                      "DeltaNet mixers are not built",
+                       "decode_sequences": len(seqs), "decode_rows": rows, "contexts": [q["pos"] for q in seqs],
+                       "parallelism": "replicas, one chunk and one decode batch per GPU, no collective",
+                       "l2": "inputs larger than L2 (FP8 weights %.1f GB + NVFP4 FFN weights %.1f GB per step), no flush"
+                             % (ctx.weight_bytes() / 1e9, 3 * cfg.layers * cfg.intermediate * cfg.hidden * 0.5625 / 1e9)},
+            "halves_ms": {"chunk_ffn_alone": ffn_alone, "verify_alone": verify_alone, "serial": ffn_alone + verify_alone,
+                          "chunk_ffn_together": ffn_ms / K, "verify_together": verify_ms / K},
+            "e2e": {"value": total_rows * K / e2e_s, "unit": UNIT, "ms_per_step": e2e_s / K * 1e3,
+                    "h2d_bytes_per_step": int(h0.nbytes + ctx_stage_bytes(lbm, len(seqs))),
+                    "d2h_bytes_per_step": int(h0.nbytes + len(seqs) * __import__("ctypes").sizeof(lbm.SeqResult) + 4)},
+            "gpu_launches": launches * K, "launches_per_step": launches,
+            "roofline": {"bound": "tensor", "kernel": "gemm_nvfp4_tcgen05_kernel (gate|up fused %d x %d x %d, down %d x %d x %d)"
+                         % (chunk, 2 * cfg.intermediate, cfg.hidden, chunk, cfg.hidden, cfg.intermediate),
+                         "achieved": achieved, "peak": peak_burst, "unit": "TFLOP/s", "frac": achieved / peak_burst,
+                         "peak_kind": "measured in this run: tcgen05.mma kind::mxf4nvf4.block_scale on resident operands, 6 ms burst",
+                         "peak_sustained": peak_sustained, "traffic": None,
+                         "ms_per_launch": {"gate_up_swiglu": gu_ms, "down": dn_ms}},
+            "cpu_baseline": {"value": None, "unit": UNIT, "cores": 0, "kind": "port",
+                             "sample": "not timed for this workload (the single-stream line carries the CPU baseline)"},
+            "clocks": clk,
+        }
+        print(json.dumps(line), flush=True)
+    ffn.close()
+    ctx.close()
+    dist.close()
+
+
 def run_micro_gemm(args):
     """One weight GEMM alone (synthetic FP8 weights and activations resident in HBM), `iters` launches back to back after
     three warm-up launches; the small case the profiler captures.  A matrix smaller than L2 is served from L2 here."""
@@ -564,7 +680,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="single", choices=["single", "ragged4", "churn64", "toy"])
+    ap.add_argument("--workload", default="single", choices=["single", "ragged4", "churn64", "mixed", "toy"])
     ap.add_argument("--layers", type=int, default=64, help="layers of the 27B-class stack (64 = the named configuration)")
     ap.add_argument("--gemm-impl", type=int, default=0)
     ap.add_argument("--pdl", type=int, default=1, help="programmatic dependent launch (bit-identical results; on by default)")
@@ -586,6 +702,8 @@ def main():
         return
     if world != args.gpus and world > 1:
         raise SystemExit("bench.py: --gpus %d but WORLD_SIZE=%d" % (args.gpus, world))
+    if args.workload == "mixed":
+        return run_mixed(args, rank, local_rank, world)
     run_ours(args, rank, local_rank, world)
 
 

@@ -292,17 +292,23 @@ int ling_b200_prefill_swiglu_nvfp4_host(int device, const uint8_t* xq, const uin
 /* The NVFP4 GEMM (fused != 0: the gate|up form) timed on the device with resident operands: ms per launch. */
 int ling_b200_nvfp4_gemm_bench(int device, int M, int N, int K, int fused, int iters, float* ms_per_launch);
 
+/* The NVFP4 tensor pipe's dense rate on this GPU, measured like ling_b200_fp8_tensor_peak: tcgen05.mma kind::mxf4nvf4.block_scale
+ * (128 x 256 x 64, block scales of 16 in tensor memory) on resident operands.  The denominator for the NVFP4 GEMMs. */
+int ling_b200_fp4_tensor_peak(int device, int iters, float* tflops, float* ms);
+
 /* The prefill chunk's feed-forward stack held on the device: per layer h += down(swiglu(gate, up)(norm(h))), the three
  * matrices NVFP4 with synthetic BF16 N(0, 0.02) values rounded as quantize_nvfp4 rounds (the quantized branch of the
  * layer loop's MLP section, src/core/engine.cpp:1238-1247,1704-1711, taken for a chunk of more than 32 rows).  It owns a stream: launch() enqueues the whole stack
- * over the resident residual and returns, wait() joins it and reports the device time between its events, so the stack can run
+ * over the resident residual `repeats` times and returns, wait() joins it and reports the device time between its events, so the stack can run
  * beside a verify step of a ling_b200_ctx; forward() is the host-buffer call (pinned staging, copies inside). */
 typedef struct ling_b200_nvfp4_ffn ling_b200_nvfp4_ffn;
 int ling_b200_nvfp4_ffn_create(int device, int layers, int hidden, int intermediate, int max_rows, uint64_t seed,
                                ling_b200_nvfp4_ffn** out);
 void ling_b200_nvfp4_ffn_destroy(ling_b200_nvfp4_ffn* f);
 int ling_b200_nvfp4_ffn_set_residual(ling_b200_nvfp4_ffn* f, const float* h, int rows);
-int ling_b200_nvfp4_ffn_launch(ling_b200_nvfp4_ffn* f, int rows);
+int ling_b200_nvfp4_ffn_launch(ling_b200_nvfp4_ffn* f, int rows, int repeats);
+/* CTAs of each GEMM launch of the stack (0 = one per SM): fewer leave SMs to a verify step running beside it. */
+int ling_b200_nvfp4_ffn_set_ctas(ling_b200_nvfp4_ffn* f, int ctas);
 int ling_b200_nvfp4_ffn_wait(ling_b200_nvfp4_ffn* f, float* device_ms);
 int ling_b200_nvfp4_ffn_forward(ling_b200_nvfp4_ffn* f, const float* h_in, int rows, float* h_out);
 /* One layer's operands back on the host in the reference's layouts (any pointer may be NULL); scales5 = the static

@@ -466,6 +466,12 @@ def nvfp4_gemm_bench(M, N, K, fused=False, iters=10, device=0):
     return ms.value
 
 
+def fp4_tensor_peak(iters=20000, device=0):
+    tf, ms = C.c_float(), C.c_float()
+    check(lib().ling_b200_fp4_tensor_peak(device, iters, C.byref(tf), C.byref(ms)), "fp4_tensor_peak")
+    return tf.value, ms.value
+
+
 class Nvfp4Ffn:
     """The prefill chunk's NVFP4 feed-forward stack on the device (synthetic weights), on a stream of its own."""
 
@@ -474,7 +480,7 @@ class Nvfp4Ffn:
         self.layers, self.hidden, self.intermediate, self.max_rows = layers, hidden, intermediate, max_rows
         L = lib()
         L.ling_b200_nvfp4_ffn_create.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_uint64, C.POINTER(C.c_void_p)]
-        for n in ("destroy", "set_residual", "launch", "wait", "forward", "read_layer"):
+        for n in ("destroy", "set_residual", "launch", "set_ctas", "wait", "forward", "read_layer"):
             getattr(L, "ling_b200_nvfp4_ffn_" + n).argtypes = None
         check(L.ling_b200_nvfp4_ffn_create(device, layers, hidden, intermediate, max_rows, seed, C.byref(self.h)), "nvfp4_ffn_create")
 
@@ -493,8 +499,11 @@ class Nvfp4Ffn:
         h = np.ascontiguousarray(h, np.float32)
         check(lib().ling_b200_nvfp4_ffn_set_residual(self.h, _fp(h), h.shape[0]), "nvfp4_ffn_set_residual")
 
-    def launch(self, rows):
-        check(lib().ling_b200_nvfp4_ffn_launch(self.h, rows), "nvfp4_ffn_launch")
+    def launch(self, rows, repeats=1):
+        check(lib().ling_b200_nvfp4_ffn_launch(self.h, rows, repeats), "nvfp4_ffn_launch")
+
+    def set_ctas(self, ctas):
+        check(lib().ling_b200_nvfp4_ffn_set_ctas(self.h, ctas), "nvfp4_ffn_set_ctas")
 
     def wait(self):
         ms = C.c_float()

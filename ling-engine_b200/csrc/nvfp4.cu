@@ -289,6 +289,58 @@ __global__ void __launch_bounds__(kThreads, 1)
   }
 }
 
+// ---------------------------------------------------------------------------------------------- tensor peak
+// The NVFP4 tensor pipe's rate on this GPU, measured rather than quoted: every CTA issues `iters` groups of four
+// tcgen05.mma kind::mxf4nvf4.block_scale (M 128, N 256, K 64 each) on operand tiles and block scales that stay resident in
+// shared / tensor memory; no loads, no epilogue.  The denominator of the NVFP4 GEMMs' roofline fraction.
+__global__ void __launch_bounds__(128, 1) fp4_tensor_peak_kernel(int iters, int* err_flag) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint8_t* sf = smem + kABytes + kBBytes;  // [3 groups][4 atoms][512]
+  uint64_t* bar = reinterpret_cast<uint64_t*>(sf + 3 * kSfGroup);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + 1);
+  for (int i = threadIdx.x; i < kABytes + kBBytes; i += blockDim.x) smem[i] = uint8_t((i * 2654435761u) >> 24);  // every code
+  for (int i = threadIdx.x; i < 3 * kSfGroup; i += blockDim.x) sf[i] = uint8_t(0x30 + ((i * 2654435761u) >> 29));  // 0.5 .. 0.94
+  if (threadIdx.x == 0) {
+    mbar_init(bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  if (threadIdx.x < 32) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    tc_fence_before();
+  }
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) {
+    constexpr uint32_t idesc = umma_idesc_nvfp4(kFp4TileN);
+    const uint32_t st = smem_u32(smem), sfa = smem_u32(sf);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      sf_copy(tmem_base + kSfaCol + 4 * k, sf_desc(sfa + 512 * k));
+      sf_copy(tmem_base + kSfbCol + 8 * k, sf_desc(sfa + kSfGroup + 512 * k));
+      sf_copy(tmem_base + kSfbCol + 8 * k + 4, sf_desc(sfa + 2 * kSfGroup + 512 * k));
+    }
+    const uint64_t adesc = umma_desc_sw128(st), bdesc = umma_desc_sw128(st + kABytes);
+    for (int i = 0; i < iters; ++i) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        umma_nvfp4(tmem_base, adesc + uint64_t(k * 2), bdesc + uint64_t(k * 2), idesc, tmem_base + kSfaCol + 4 * k,
+                   tmem_base + kSfbCol + 8 * k, (i > 0 || k > 0) ? 1u : 0u);
+    }
+    umma_commit(bar);
+    if (!mbar_wait(bar, 0, nullptr)) dev_fail(err_flag, kDevWaitTmemFull);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+}
+
 // ---------------------------------------------------------------------------------------------- quantizers
 __device__ __forceinline__ void store_block(uint8_t* q, uint8_t* sf, bool tiled, int row, int blk, int K, int k_atoms, uint2 codes,
                                             uint8_t sc) {
@@ -500,6 +552,17 @@ int fp4_quant_weight_launch(const __nv_bfloat16* w, int N, int K, uint8_t* q, ui
   quant_weight_nvfp4_kernel<<<grid_for(size_t(N) * (K / 16)), 256, 0, stream>>>(w, N, K, amax_bits, q, sf, tiled ? 1 : 0,
                                                                                fp4_k_atoms(K), scale2);
   LB_LAUNCH("quant_weight_nvfp4_kernel");
+  return LING_B200_OK;
+}
+
+int fp4_tensor_peak_launch(int ctas, int iters, int* err_flag, cudaStream_t stream) {
+  constexpr int smem = kABytes + kBBytes + 3 * kSfGroup + 1024 + 64;
+  static std::once_flag once;
+  static cudaError_t attr = cudaSuccess;
+  std::call_once(once, [] { attr = cudaFuncSetAttribute(fp4_tensor_peak_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); });
+  LB_CUDA(attr);
+  fp4_tensor_peak_kernel<<<ctas, 128, smem, stream>>>(iters, err_flag);
+  LB_LAUNCH("fp4_tensor_peak_kernel");
   return LING_B200_OK;
 }
 

@@ -69,6 +69,8 @@ int fp4_rmsnorm_quant_launch(const float* x, const __nv_bfloat16* w, float* out,
 // max(amax16 / 6 / g, 2^-9) as E4M3, codes nearest with ties to the smaller magnitude.  `amax_bits` is one zeroed word.
 int fp4_quant_weight_launch(const __nv_bfloat16* w, int N, int K, uint8_t* q, uint8_t* sf, bool tiled, float* scale2,
                             unsigned* amax_bits, cudaStream_t stream);
+// `ctas` CTAs each issue `iters` groups of four 128 x 256 x 64 NVFP4 MMAs on resident operands (the tensor pipe's rate).
+int fp4_tensor_peak_launch(int ctas, int iters, int* err_flag, cudaStream_t stream);
 // Row-major block scales [rows][K / 16] <-> the layout above.
 int fp4_sf_tile_launch(const uint8_t* rowmajor, uint8_t* tiled, int rows, int K, cudaStream_t stream);
 int fp4_sf_untile_launch(const uint8_t* tiled, uint8_t* rowmajor, int rows, int K, cudaStream_t stream);

@@ -41,6 +41,7 @@ int read_flag(const int* err, const char* what) {
 // The chunk's feed-forward stack: per layer the post-attention norm weight and the three NVFP4 matrices.
 struct ling_b200_nvfp4_ffn {
   int device = 0, layers = 0, H = 0, I = 0, max_rows = 0;
+  int ctas = 0;  // CTAs of each GEMM launch (0: one per SM)
   float eps = 1e-6f;
   struct Layer {
     __nv_bfloat16* norm = nullptr;
@@ -99,13 +100,13 @@ int ffn_run(ling_b200_nvfp4_ffn* f, int rows) {
     gu.X = &f->x, gu.W = &L.gate, gu.W2 = &L.up;
     gu.alpha = L.in_scale * L.s_gate, gu.alpha2 = L.in_scale * L.s_up;
     gu.q_out = f->mid.codes, gu.sf_out = f->mid.sf, gu.sf_out_tiled = true, gu.gscale_out = 1.f / L.mid_scale;
-    gu.err_flag = f->err;
+    gu.err_flag = f->err, gu.ctas = f->ctas;
     LB_TRY(fp4_gemm_launch(gu, f->stream));
     Fp4GemmCall dn;
     dn.X = &f->mid, dn.W = &L.down;
     dn.alpha = L.mid_scale * L.s_down;
     dn.y = f->h, dn.ldy = f->H, dn.accumulate = true;
-    dn.err_flag = f->err;
+    dn.err_flag = f->err, dn.ctas = f->ctas;
     LB_TRY(fp4_gemm_launch(dn, f->stream));
   }
   return LING_B200_OK;
@@ -276,6 +277,36 @@ int ling_b200_nvfp4_gemm_bench(int device, int M, int N, int K, int fused, int i
   return LING_B200_OK;
 }
 
+// The NVFP4 tensor pipe's dense rate (fp4_tensor_peak_kernel): one CTA per SM, `iters` MMA groups each, timed with CUDA
+// events after a warm-up launch; TFLOP/s = 2 * 128 * 256 * 256 * iters * SMs / time.
+int ling_b200_fp4_tensor_peak(int device, int iters, float* tflops, float* ms) {
+  if (!tflops || iters < 1 || iters > (1 << 22)) {
+    set_error("fp4_tensor_peak: bad argument");
+    return LING_B200_ERR_ARG;
+  }
+  LB_TRY(check_device(device));
+  int sms = 148;
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+  Scratch sc;
+  int* err = sc.get<int>(1);
+  LB_PTR(err);
+  cudaEvent_t a, b;
+  LB_CUDA(cudaEventCreate(&a));
+  LB_CUDA(cudaEventCreate(&b));
+  LB_TRY(fp4_tensor_peak_launch(sms, iters, err, 0));
+  LB_CUDA(cudaEventRecord(a, 0));
+  LB_TRY(fp4_tensor_peak_launch(sms, iters, err, 0));
+  LB_CUDA(cudaEventRecord(b, 0));
+  LB_CUDA(cudaEventSynchronize(b));
+  float t = 0.f;
+  LB_CUDA(cudaEventElapsedTime(&t, a, b));
+  cudaEventDestroy(a), cudaEventDestroy(b);
+  LB_TRY(read_flag(err, "fp4_tensor_peak"));
+  *tflops = float(2.0 * 128 * 256 * 256 * double(iters) * sms / (double(t) * 1e-3) / 1e12);
+  if (ms) *ms = t;
+  return LING_B200_OK;
+}
+
 int ling_b200_nvfp4_ffn_create(int device, int layers, int hidden, int intermediate, int max_rows, uint64_t seed,
                                ling_b200_nvfp4_ffn** out) {
   if (!out || layers < 1 || !multiple(hidden, 256) || !multiple(intermediate, 128) || max_rows < 1) {
@@ -333,15 +364,21 @@ int ling_b200_nvfp4_ffn_set_residual(ling_b200_nvfp4_ffn* f, const float* h, int
   return LING_B200_OK;
 }
 
-int ling_b200_nvfp4_ffn_launch(ling_b200_nvfp4_ffn* f, int rows) {
-  if (!f || rows < 1 || rows > f->max_rows) {
+int ling_b200_nvfp4_ffn_launch(ling_b200_nvfp4_ffn* f, int rows, int repeats) {
+  if (!f || rows < 1 || rows > f->max_rows || repeats < 1) {
     set_error("nvfp4_ffn_launch: bad argument");
     return LING_B200_ERR_ARG;
   }
   LB_CUDA(cudaSetDevice(f->device));
   LB_CUDA(cudaEventRecord(f->ev0, f->stream));
-  LB_TRY(ffn_run(f, rows));
+  for (int i = 0; i < repeats; ++i) LB_TRY(ffn_run(f, rows));
   LB_CUDA(cudaEventRecord(f->ev1, f->stream));
+  return LING_B200_OK;
+}
+
+int ling_b200_nvfp4_ffn_set_ctas(ling_b200_nvfp4_ffn* f, int ctas) {
+  if (!f || ctas < 0) return LING_B200_ERR_ARG;
+  f->ctas = ctas;
   return LING_B200_OK;
 }
 

@@ -151,7 +151,7 @@ def test_chunk_ffn_stack_against_the_oracle_chain(gpu, lb, lo):
         h = lo.nvfp4_gemm(mq, ms, *L["down"], L["mid_scale"] * L["s_down"], y=h, accumulate=True)
     assert np.isfinite(got).all()
     delta = np.sqrt(((got - h0) ** 2).sum())
-    assert delta > 0.05 * np.sqrt((h0 ** 2).sum()), "the stack must change the residual for the comparison to mean anything"
+    assert delta > 0.01 * np.sqrt((h0 ** 2).sum()), "the stack must change the residual for the comparison to mean anything"
     assert np.sqrt(((got - h) ** 2).sum()) <= FFN_TOL * delta
 
 
