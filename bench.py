@@ -639,6 +639,15 @@ def run_micro_gemm(args):
     three warm-up launches; the small case the profiler captures.  A matrix smaller than L2 is served from L2 here."""
     lbm = importlib.import_module("ling-engine_b200")
     M, N, K = (int(x) for x in args.shape.split(","))
+    if args.micro in ("nvfp4", "nvfp4-swiglu"):
+        # one NVFP4 GEMM alone: N weight rows (N features from 2 N rows in the fused gate|up form), operands resident
+        fused = args.micro == "nvfp4-swiglu"
+        ms = lbm.nvfp4_gemm_bench(M, N, K, fused=fused, iters=args.iters)
+        flops = 2.0 * M * N * K * (2 if fused else 1)
+        print(json.dumps({"micro": "gemm_nvfp4_tcgen05_kernel", "fused_swiglu": fused, "shape": [M, N, K], "iters": args.iters,
+                          "us_per_launch": ms * 1e3, "TFLOP_per_s": flops / (ms * 1e-3) / 1e12,
+                          "operand_bytes": int((M + N * (2 if fused else 1)) * K * 0.5625)}), flush=True)
+        return
     lbm.lib().ling_b200_set_pdl(args.pdl)
     ms = lbm.gemm_fp8_bench(M, N, K, impl=args.gemm_impl, splits=0, iters=args.iters)
     lbm.lib().ling_b200_set_pdl(0)
@@ -690,12 +699,12 @@ def main():
     ap.add_argument("--no-churn64", action="store_true", help="leave out the 64-sequence sharded batch reported beside the headline")
     ap.add_argument("--quick", action="store_true", help="device-timed steps only (no end-to-end, per-family or CPU legs): "
                     "the short run the profiler's launch list is taken from")
-    ap.add_argument("--micro", default="", choices=["", "gemm"], help="time one kernel alone on resident operands")
+    ap.add_argument("--micro", default="", choices=["", "gemm", "nvfp4", "nvfp4-swiglu"], help="time one kernel alone on resident operands")
     ap.add_argument("--shape", default="24,34816,5120", help="--micro gemm: rows,N,K (default: the gate|up projection)")
     ap.add_argument("--iters", type=int, default=20)
     args = ap.parse_args()
     rank, local_rank, world = dist_env()
-    if args.micro == "gemm":
+    if args.micro:
         return run_micro_gemm(args)
     if args.impl == "reference":
         run_reference(args, rank, world)

@@ -289,12 +289,17 @@ int ling_b200_prefill_gemm_nvfp4_host(int device, const uint8_t* xq, const uint8
 int ling_b200_prefill_swiglu_nvfp4_host(int device, const uint8_t* xq, const uint8_t* xs, int M, const uint8_t* gate_q,
                                         const uint8_t* gate_s, float alpha_gate, const uint8_t* up_q, const uint8_t* up_s, float alpha_up,
                                         int N, int K, float out_input_scale, uint8_t* q_out, uint8_t* sf_out);
-/* The NVFP4 GEMM (fused != 0: the gate|up form) timed on the device with resident operands: ms per launch. */
-int ling_b200_nvfp4_gemm_bench(int device, int M, int N, int K, int fused, int iters, float* ms_per_launch);
+/* The NVFP4 GEMM (fused != 0: the gate|up form) timed on the device with resident operands: ms per launch.  cycle_shares
+ * (optional, 3 doubles): from one more launch with the kernel's cycle counters on, the shares of a CTA's time that the MMA
+ * issuer spent waiting for operand stages, that it spent waiting for the epilogue to free the accumulator, and that one
+ * epilogue warp was busy. */
+int ling_b200_nvfp4_gemm_bench(int device, int M, int N, int K, int fused, int iters, float* ms_per_launch, double* cycle_shares);
 
 /* The NVFP4 tensor pipe's dense rate on this GPU, measured like ling_b200_fp8_tensor_peak: tcgen05.mma kind::mxf4nvf4.block_scale
- * (128 x 256 x 64, block scales of 16 in tensor memory) on resident operands.  The denominator for the NVFP4 GEMMs. */
-int ling_b200_fp4_tensor_peak(int device, int iters, float* tflops, float* ms);
+ * (128 x 256 x 64, block scales of 16 in tensor memory) on resident operands.  mode 0 is the denominator for the NVFP4 GEMMs; mode 1 adds the GEMM's
+ * twelve scale copies (tcgen05.cp, shared -> tensor memory) before every group of four MMAs, into the one scale region the MMAs
+ * read; mode 2 alternates between two scale regions: what the copies cost the pipe. */
+int ling_b200_fp4_tensor_peak(int device, int iters, int mode, float* tflops, float* ms);
 
 /* The prefill chunk's feed-forward stack held on the device: per layer h += down(swiglu(gate, up)(norm(h))), the three
  * matrices NVFP4 with synthetic BF16 N(0, 0.02) values rounded as quantize_nvfp4 rounds (the quantized branch of the

@@ -460,15 +460,18 @@ def prefill_swiglu_nvfp4(xq, xs, gq, gs, alpha_gate, uq, us, alpha_up, out_input
     return q, sf
 
 
-def nvfp4_gemm_bench(M, N, K, fused=False, iters=10, device=0):
-    ms = C.c_float()
-    check(lib().ling_b200_nvfp4_gemm_bench(device, M, N, K, 1 if fused else 0, iters, C.byref(ms)), "nvfp4_gemm_bench")
-    return ms.value
+def nvfp4_gemm_bench(M, N, K, fused=False, iters=10, device=0, shares=False):
+    """ms per launch; with shares, also the kernel's own cycle shares (issuer waiting for stages, issuer waiting for the
+    epilogue, one epilogue warp busy) of a CTA's time."""
+    ms, sh = C.c_float(), (C.c_double * 3)()
+    check(lib().ling_b200_nvfp4_gemm_bench(device, M, N, K, 1 if fused else 0, iters, C.byref(ms), sh if shares else None),
+          "nvfp4_gemm_bench")
+    return (ms.value, list(sh)) if shares else ms.value
 
 
-def fp4_tensor_peak(iters=20000, device=0):
+def fp4_tensor_peak(iters=20000, device=0, mode=0):
     tf, ms = C.c_float(), C.c_float()
-    check(lib().ling_b200_fp4_tensor_peak(device, iters, C.byref(tf), C.byref(ms)), "fp4_tensor_peak")
+    check(lib().ling_b200_fp4_tensor_peak(device, iters, mode, C.byref(tf), C.byref(ms)), "fp4_tensor_peak")
     return tf.value, ms.value
 
 

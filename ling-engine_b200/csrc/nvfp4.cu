@@ -8,7 +8,7 @@
 //            512-byte atom becomes four TMEM columns, replicated over the four lane quarters), then four
 //            tcgen05.mma kind::mxf4nvf4.block_scale (M 128, N 256, K 64, scale vector 16) into the 256-column
 //            accumulator; tcgen05.commit releases the stage and, after the last stage, hands the tile to the epilogue.
-//   warps 2-5 epilogue: tcgen05.ld of the tile; plain form: alpha * acc to y (or added to it); fused form: the gate and up
+//   warps 2-9 epilogue (two per TMEM lane quarter, half of the columns each): tcgen05.ld of the tile; plain form: alpha * acc to y (or added to it); fused form: the gate and up
 //            halves of the tile become silu(alpha * gate) * (alpha2 * up), rounded to BF16 and written as the next GEMM's
 //            NVFP4 operand (16 features = one block scale, all in one thread).
 // TMEM: columns 0-255 accumulator, 256-271 activation scales of the stage, 272-303 weight scales.  One accumulator: the
@@ -34,7 +34,8 @@ constexpr int kBBytes = kFp4TileN * kRowBytes;    // 32 KiB
 constexpr int kSfGroup = (kFp4StageK / 64) * 512;  // one 128-row group's scales of a stage: 2 KiB
 constexpr int kStageBytes = kABytes + kBBytes + 3 * kSfGroup;
 constexpr int kSfaCol = 256, kSfbCol = 272, kTmemCols = 512;
-constexpr int kThreads = 192;
+constexpr int kEpiWarps = 8;  // two per TMEM lane quarter, each draining half of the tile's columns
+constexpr int kThreads = 64 + 32 * kEpiWarps;
 constexpr size_t kSmemBytes = size_t(kStages) * kStageBytes + 1024 /* alignment slack */ + 256 /* barriers */;
 static_assert(kStageBytes % 1024 == 0, "swizzled tiles start on 1024-byte boundaries");
 
@@ -107,6 +108,8 @@ struct GemmArgs {
   uint8_t* sf_out;
   int sf_out_tiled, out_atoms;
   int* err_flag;
+  unsigned long long* stats;  // optional cycle sums over all CTAs: [0] issuer waiting for stages, [1] issuer waiting for the
+                              // epilogue, [2] epilogue busy (one warp), [3] whole CTA
 };
 
 template <bool SWIGLU>
@@ -125,6 +128,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles = p.tiles_m * p.tiles_n;
   const int k_atoms = p.k_stages * 4;
+  const long long t_start = clock64();
 
   if (threadIdx.x == 0) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&mapA)) : "memory");
@@ -135,7 +139,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       mbar_init(&empty[s], 1);
     }
     mbar_init(tmem_full, 1);
-    mbar_init(tmem_empty, 4);
+    mbar_init(tmem_empty, kEpiWarps);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -187,21 +191,26 @@ __global__ void __launch_bounds__(kThreads, 1)
       constexpr uint32_t idesc = umma_idesc_nvfp4(kFp4TileN);
       int it = 0, ti = 0;
       bool ok = true;
+      long long w_full = 0, w_empty = 0;
       for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++ti) {
+        long long c0 = clock64();
         if (!mbar_wait(tmem_empty, (ti & 1) ^ 1, abort_flag)) {
           dev_fail(p.err_flag, kDevWaitTmemEmpty);
           *abort_flag = 1;
           break;
         }
         tc_fence_after();
+        w_empty += clock64() - c0;
         for (int ks = 0; ks < p.k_stages; ++ks, ++it) {
           const int s = it % kStages;
+          c0 = clock64();
           if (!mbar_wait(&full[s], (it / kStages) & 1, abort_flag)) {
             dev_fail(p.err_flag, kDevWaitFull);
             *abort_flag = 1;
             ok = false;
             break;
           }
+          w_full += clock64() - c0;
           tc_fence_after();
           const uint32_t st = smem_u32(smem + s * kStageBytes);
           const uint32_t sf = st + kABytes + kBBytes;
@@ -220,11 +229,16 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         if (ok) umma_commit(tmem_full);
       }
+      if (p.stats) {
+        atomicAdd(p.stats, (unsigned long long)w_full);
+        atomicAdd(p.stats + 1, (unsigned long long)w_empty);
+      }
     }
   } else {
     // ------------------------------------------------------------------ epilogue (TMEM lane quarter = warp % 4)
-    const int quarter = warp & 3;
+    const int quarter = warp & 3, half = (warp - 2) >> 2;
     int ti = 0;
+    long long busy = 0;
     for (int t = blockIdx.x; t < tiles; t += gridDim.x, ++ti) {
       const int tm = t % p.tiles_m, tn = t / p.tiles_m;
       if (!mbar_wait(tmem_full, ti & 1, abort_flag)) {
@@ -232,13 +246,14 @@ __global__ void __launch_bounds__(kThreads, 1)
         *abort_flag = 1;
         break;
       }
+      const long long c0 = clock64();
       tc_fence_after();
       const int row = tm * kFp4TileM + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16);
       if constexpr (SWIGLU) {
         const int f0 = tn * 128;  // the tile's first feature: columns 0-127 its gate products, 128-255 its up products
 #pragma unroll 1
-        for (int b = 0; b < 8; ++b) {
+        for (int b = 4 * half; b < 4 * half + 4; ++b) {
           uint32_t g[16], u[16];
           tmem_ld16(taddr + 16 * b, g);
           tmem_ld16(taddr + 128 + 16 * b, u);
@@ -257,7 +272,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       } else {
         const int n0 = tn * kFp4TileN;
 #pragma unroll 1
-        for (int c = 0; c < kFp4TileN / 32; ++c) {
+        for (int c = 4 * half; c < 4 * half + 4; ++c) {
           uint32_t v[32];
           tmem_ld32(taddr + 32 * c, v);
           tmem_ld_wait();
@@ -279,10 +294,13 @@ __global__ void __launch_bounds__(kThreads, 1)
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tmem_empty);
+      busy += clock64() - c0;
     }
+    if (p.stats && warp == 2 && lane == 0) atomicAdd(p.stats + 2, (unsigned long long)busy);
   }
   tc_fence_before();
   __syncthreads();
+  if (p.stats && threadIdx.x == 0) atomicAdd(p.stats + 3, (unsigned long long)(clock64() - t_start));
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
@@ -292,8 +310,9 @@ __global__ void __launch_bounds__(kThreads, 1)
 // ---------------------------------------------------------------------------------------------- tensor peak
 // The NVFP4 tensor pipe's rate on this GPU, measured rather than quoted: every CTA issues `iters` groups of four
 // tcgen05.mma kind::mxf4nvf4.block_scale (M 128, N 256, K 64 each) on operand tiles and block scales that stay resident in
-// shared / tensor memory; no loads, no epilogue.  The denominator of the NVFP4 GEMMs' roofline fraction.
-__global__ void __launch_bounds__(128, 1) fp4_tensor_peak_kernel(int iters, int* err_flag) {
+// shared / tensor memory; no loads, no epilogue.  The denominator of the NVFP4 GEMMs' roofline fraction (mode 0).  Modes 1
+// and 2 add the GEMM's per-stage scale copies (shared memory -> tensor memory) to every group, to price them.
+__global__ void __launch_bounds__(128, 1) fp4_tensor_peak_kernel(int iters, int mode, int* err_flag) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   uint8_t* sf = smem + kABytes + kBBytes;  // [3 groups][4 atoms][512]
@@ -325,10 +344,20 @@ __global__ void __launch_bounds__(128, 1) fp4_tensor_peak_kernel(int iters, int*
     }
     const uint64_t adesc = umma_desc_sw128(st), bdesc = umma_desc_sw128(st + kABytes);
     for (int i = 0; i < iters; ++i) {
+      // mode 1: the GEMM's twelve scale copies before every group, into the one scale region; mode 2: into two regions in turn
+      const uint32_t so = mode == 2 ? uint32_t(i & 1) * 48u : 0u;
+      if (mode) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          sf_copy(tmem_base + so + kSfaCol + 4 * k, sf_desc(sfa + 512 * k));
+          sf_copy(tmem_base + so + kSfbCol + 8 * k, sf_desc(sfa + kSfGroup + 512 * k));
+          sf_copy(tmem_base + so + kSfbCol + 8 * k + 4, sf_desc(sfa + 2 * kSfGroup + 512 * k));
+        }
+      }
 #pragma unroll
       for (int k = 0; k < 4; ++k)
-        umma_nvfp4(tmem_base, adesc + uint64_t(k * 2), bdesc + uint64_t(k * 2), idesc, tmem_base + kSfaCol + 4 * k,
-                   tmem_base + kSfbCol + 8 * k, (i > 0 || k > 0) ? 1u : 0u);
+        umma_nvfp4(tmem_base, adesc + uint64_t(k * 2), bdesc + uint64_t(k * 2), idesc, tmem_base + so + kSfaCol + 4 * k,
+                   tmem_base + so + kSfbCol + 8 * k, (i > 0 || k > 0) ? 1u : 0u);
     }
     umma_commit(bar);
     if (!mbar_wait(bar, 0, nullptr)) dev_fail(err_flag, kDevWaitTmemFull);
@@ -508,7 +537,7 @@ int fp4_gemm_launch(const Fp4GemmCall& c, cudaStream_t stream) {
   p.alpha = c.alpha, p.alpha2 = c.alpha2, p.gscale_out = c.gscale_out;
   p.y = c.y, p.ldy = c.ldy, p.accumulate = c.accumulate ? 1 : 0;
   p.q_out = c.q_out, p.sf_out = c.sf_out, p.sf_out_tiled = c.sf_out_tiled ? 1 : 0, p.out_atoms = fp4_k_atoms(W.rows);
-  p.err_flag = c.err_flag;
+  p.err_flag = c.err_flag, p.stats = c.stats;
   if (!fused && (c.ldy % 4 || (reinterpret_cast<uintptr_t>(c.y) & 15))) {
     set_error("NVFP4 GEMM: y must be 16-byte aligned and ldy a multiple of 4");
     return LING_B200_ERR_ARG;
@@ -555,13 +584,13 @@ int fp4_quant_weight_launch(const __nv_bfloat16* w, int N, int K, uint8_t* q, ui
   return LING_B200_OK;
 }
 
-int fp4_tensor_peak_launch(int ctas, int iters, int* err_flag, cudaStream_t stream) {
+int fp4_tensor_peak_launch(int ctas, int iters, int mode, int* err_flag, cudaStream_t stream) {
   constexpr int smem = kABytes + kBBytes + 3 * kSfGroup + 1024 + 64;
   static std::once_flag once;
   static cudaError_t attr = cudaSuccess;
   std::call_once(once, [] { attr = cudaFuncSetAttribute(fp4_tensor_peak_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); });
   LB_CUDA(attr);
-  fp4_tensor_peak_kernel<<<ctas, 128, smem, stream>>>(iters, err_flag);
+  fp4_tensor_peak_kernel<<<ctas, 128, smem, stream>>>(iters, mode, err_flag);
   LB_LAUNCH("fp4_tensor_peak_kernel");
   return LING_B200_OK;
 }

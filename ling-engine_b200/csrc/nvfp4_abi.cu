@@ -229,7 +229,7 @@ int ling_b200_prefill_swiglu_nvfp4_host(int device, const uint8_t* xq, const uin
   return LING_B200_OK;
 }
 
-int ling_b200_nvfp4_gemm_bench(int device, int M, int N, int K, int fused, int iters, float* ms_per_launch) {
+int ling_b200_nvfp4_gemm_bench(int device, int M, int N, int K, int fused, int iters, float* ms_per_launch, double* cycle_shares) {
   if (!ms_per_launch || M < 1 || !multiple(N, 128) || !multiple(K, 128) || iters < 1) {
     set_error("nvfp4_gemm_bench: bad argument");
     return LING_B200_ERR_ARG;
@@ -274,13 +274,22 @@ int ling_b200_nvfp4_gemm_bench(int device, int M, int N, int K, int fused, int i
   cudaEventDestroy(a), cudaEventDestroy(b);
   LB_TRY(read_flag(err, "nvfp4_gemm_bench"));
   *ms_per_launch = t / iters;
+  if (cycle_shares) {  // one more launch with the kernel's own cycle counters on
+    unsigned long long* st = sc.get<unsigned long long>(4);
+    LB_PTR(st);
+    c.stats = st;
+    LB_TRY(fp4_gemm_launch(c, 0));
+    unsigned long long h[4];
+    LB_CUDA(cudaMemcpy(h, st, sizeof h, cudaMemcpyDeviceToHost));
+    for (int i = 0; i < 3; ++i) cycle_shares[i] = h[3] ? double(h[i]) / double(h[3]) : 0.0;
+  }
   return LING_B200_OK;
 }
 
 // The NVFP4 tensor pipe's dense rate (fp4_tensor_peak_kernel): one CTA per SM, `iters` MMA groups each, timed with CUDA
 // events after a warm-up launch; TFLOP/s = 2 * 128 * 256 * 256 * iters * SMs / time.
-int ling_b200_fp4_tensor_peak(int device, int iters, float* tflops, float* ms) {
-  if (!tflops || iters < 1 || iters > (1 << 22)) {
+int ling_b200_fp4_tensor_peak(int device, int iters, int mode, float* tflops, float* ms) {
+  if (!tflops || iters < 1 || iters > (1 << 22) || mode < 0 || mode > 2) {
     set_error("fp4_tensor_peak: bad argument");
     return LING_B200_ERR_ARG;
   }
@@ -293,9 +302,9 @@ int ling_b200_fp4_tensor_peak(int device, int iters, float* tflops, float* ms) {
   cudaEvent_t a, b;
   LB_CUDA(cudaEventCreate(&a));
   LB_CUDA(cudaEventCreate(&b));
-  LB_TRY(fp4_tensor_peak_launch(sms, iters, err, 0));
+  LB_TRY(fp4_tensor_peak_launch(sms, iters, mode, err, 0));
   LB_CUDA(cudaEventRecord(a, 0));
-  LB_TRY(fp4_tensor_peak_launch(sms, iters, err, 0));
+  LB_TRY(fp4_tensor_peak_launch(sms, iters, mode, err, 0));
   LB_CUDA(cudaEventRecord(b, 0));
   LB_CUDA(cudaEventSynchronize(b));
   float t = 0.f;
