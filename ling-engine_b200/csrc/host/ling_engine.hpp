@@ -5,6 +5,7 @@
 #pragma once
 
 #include <algorithm>
+#include <chrono>
 #include <cstdint>
 #include <deque>
 #include <exception>
@@ -170,6 +171,149 @@ class KvPool {
 
 // ---- src/core/model.hpp, src/core/engine.hpp
 using ModelConfig = ling_b200_model_config;
+// The resident sessions and their KV pages as the scheduler sees them (the host-side half of Engine's session functions,
+// src/core/engine.cpp:581-648,724-800,881-912, and of its Session struct, engine.hpp:760-800).  No device work: Engine
+// keeps one and adds the device side; a scheduler test can keep one alone.  This build has no prefix KV store and no
+// donor sessions (a resumed prompt reuses only its own session's positions), so pages are never shared between holders
+// and a need planned "with holders gone" (Engine::KvGone) equals the need planned now.
+struct Session {
+  std::vector<int> history, table;  // tokens processed; page ids by page index (0 = unmapped)
+  int pos = 0;
+  bool owned = false;               // bound to a conversation (free_session hands out the others first)
+  std::string key;
+  uint64_t scope = 0;
+  int prompt_len = 0, turn_start = 0;
+  double last_used = 0;             // seconds on the book's clock
+};
+class SessionBook {
+ public:
+  static constexpr int kKvGrowthPages = 2;  // src/core/engine.hpp:433
+  SessionBook(int sessions, int pool_pages, int page_tokens, int max_context, int step_rows = kernels::kMaxStreamRows)
+      : pool_(pool_pages + 1, page_tokens), sess_(size_t(sessions)), page_tokens_(page_tokens), max_context_(max_context), step_rows_(step_rows) {}
+  std::function<double()> clock = [] {
+    return std::chrono::duration<double>(std::chrono::steady_clock::now().time_since_epoch()).count();
+  };
+  KvPool& pool() { return pool_; }
+  const KvPool& pool() const { return pool_; }
+  int sessions() const { return static_cast<int>(sess_.size()); }
+  int max_context() const { return max_context_; }
+  Session& at(int i) { return sess_.at(size_t(i)); }
+  const Session& at(int i) const { return sess_.at(size_t(i)); }
+
+  // Engine::match_session (engine.cpp:581-603): the owned session of the same scope whose history shares the longest prefix
+  // with the prompt, at least up to where its last turn began; a key breaks ties and, failing every prefix, names it.
+  int match_session(const std::vector<int>& prompt, const std::string& key, uint64_t scope) const {
+    int best = -1, best_lcp = 0;
+    for (int i = 0; i < sessions(); ++i) {
+      const Session& s = sess_[size_t(i)];
+      if (!s.owned || s.history.empty() || s.prompt_len == 0 || s.scope != scope) continue;
+      const int lcp = common_prefix(s.history, prompt);
+      if (lcp < s.turn_start) continue;
+      if (lcp > best_lcp || (lcp == best_lcp && !key.empty() && s.key == key)) best = i, best_lcp = lcp;
+    }
+    if (best >= 0 || key.empty()) return best;
+    for (int i = 0; i < sessions(); ++i)
+      if (sess_[size_t(i)].owned && sess_[size_t(i)].key == key && sess_[size_t(i)].scope == scope) return i;
+    return -1;
+  }
+  // Engine::free_session (engine.cpp:605-619): an unowned slot first; else the least recently used one that is neither
+  // pinned nor (keyed and used within protect_seconds).
+  int free_session(double protect_seconds, const std::vector<bool>& pinned) const {
+    auto is_pinned = [&](int i) { return size_t(i) < pinned.size() && pinned[size_t(i)]; };
+    for (int i = 0; i < sessions(); ++i)
+      if (!sess_[size_t(i)].owned && !is_pinned(i)) return i;
+    const double now = clock();
+    int best = -1;
+    for (int i = 0; i < sessions(); ++i) {
+      const Session& s = sess_[size_t(i)];
+      if (is_pinned(i) || (!s.key.empty() && now - s.last_used < protect_seconds)) continue;
+      if (best < 0 || s.last_used < sess_[size_t(best)].last_used) best = i;
+    }
+    return best;
+  }
+  // The bookkeeping of Engine::activate_session (engine.cpp:621-646); returns whether an owned session was taken over.
+  bool activate(int i, const std::string& key, bool fresh, uint64_t scope) {
+    Session& s = at(i);
+    bool took_over = false;
+    if (s.scope != scope) {  // another scope's history is never resumed from; its pages stay until the prefill rewrites them
+      s.history.clear();
+      s.prompt_len = s.turn_start = s.pos = 0;
+      s.scope = scope;
+    }
+    if (fresh) {
+      took_over = s.owned;
+      s.owned = true;
+      s.key = key;
+    } else if (!key.empty()) {
+      s.key = key;
+    }
+    touch(i);
+    return took_over;
+  }
+  void touch(int i) { at(i).last_used = clock(); }
+  int resident() const { return static_cast<int>(std::count_if(sess_.begin(), sess_.end(), [](const Session& s) { return s.owned; })); }
+
+  // ---- pages (engine.cpp:724-800,881-912)
+  int kv_admit_pages(size_t prompt_len) const { return pool_.pages_for(static_cast<int>(prompt_len)) + kKvGrowthPages; }
+  int kv_step_rows(const Session& s, bool spec) const {
+    const int room = max_context_ - s.pos;
+    return std::max(0, std::min(spec ? step_rows_ : 1, room));
+  }
+  int kv_step_need(int session, bool spec) const {
+    const Session& s = at(session);
+    return pool_.needed(s.table, s.pos, s.pos + kv_step_rows(s, spec));
+  }
+  // Positions of the session's own history that a prompt resumes from (the no-donor, no-store case of plan_resume,
+  // engine.cpp:1747-1842): the common prefix, never the whole prompt (its last token is processed again for the logits).
+  int resume_reuse(int session, const std::vector<int>& prompt, uint64_t scope, bool from_scratch) const {
+    const Session& s = at(session);
+    if (from_scratch || s.scope != scope || prompt.empty()) return 0;
+    return std::min(common_prefix(s.history, prompt), static_cast<int>(prompt.size()) - 1);
+  }
+  int kv_admit_need(int session, const std::vector<int>& prompt, uint64_t scope, bool from_scratch = false) const {
+    if (prompt.empty()) return 0;
+    return pool_.resume_need(at(session).table, resume_reuse(session, prompt, scope, from_scratch), kv_admit_pages(prompt.size()), nullptr);
+  }
+  int kv_reclaimable(const std::vector<int>& sessions) const {
+    KvPool::Refs refs;
+    for (int i : sessions) refs.push_back(&at(i).table);
+    return pool_.reclaimable(refs);
+  }
+  int kv_lru_idle(const std::vector<bool>& busy) const {
+    int best = -1;
+    for (int i = 0; i < sessions(); ++i) {
+      const Session& s = sess_[size_t(i)];
+      if (size_t(i) < busy.size() && busy[size_t(i)]) continue;
+      const bool holds = std::any_of(s.table.begin(), s.table.end(), [](int p) { return p != 0; });
+      if (holds && (best < 0 || s.last_used < sess_[size_t(best)].last_used)) best = i;
+    }
+    return best;
+  }
+  // Engine::kv_evict's bookkeeping (engine.cpp:881-898): pages released (deferred), history forgotten, slot unowned.
+  bool evict(int session) {
+    Session& s = at(session);
+    if (s.table.empty() && s.history.empty()) return false;
+    pool_.truncate(s.table, 0);
+    s.history.clear();
+    s.prompt_len = s.turn_start = s.pos = 0;
+    const bool was_owned = s.owned;
+    s.owned = false;
+    s.key.clear();
+    return was_owned;
+  }
+  static int common_prefix(const std::vector<int>& a, const std::vector<int>& b) {
+    const size_t n = std::min(a.size(), b.size());
+    size_t i = 0;
+    while (i < n && a[i] == b[i]) ++i;
+    return static_cast<int>(i);
+  }
+
+ private:
+  KvPool pool_;
+  std::vector<Session> sess_;
+  int page_tokens_, max_context_, step_rows_;
+};
+
 struct EngineOptions {
   int max_context = 65536;
   int sessions = 1;
@@ -180,6 +324,7 @@ struct EngineOptions {
   int page_tokens = 16;
   int max_seqs = 4, max_rows = 128;
   int device = 0;
+  int boundary_token = -1;  // the token that starts a message (engine.hpp:171); -1: prompts carry no boundaries
 };
 
 class Engine {
@@ -197,19 +342,20 @@ class Engine {
   // stands in for plan_draft + build_tree (src/core/speculate.cpp:970-987).
   using TreeSource = std::function<DraftTree(int session, int anchor, const std::vector<int>& history)>;
 
-  Engine(const ModelConfig& cfg, EngineOptions opts = {}) : cfg_(cfg), opts_(opts) {
+  static int pool_pages_for(const EngineOptions& o) {
+    return o.kv_pool_pages > 0 ? o.kv_pool_pages : (o.max_context + o.page_tokens - 1) / o.page_tokens * o.sessions;
+  }
+  Engine(const ModelConfig& cfg, EngineOptions opts = {})
+      : cfg_(cfg), opts_(opts), book_(opts.sessions, pool_pages_for(opts), opts.page_tokens, opts.max_context) {
     ling_b200_options o{};
     o.sessions = opts.sessions, o.max_context = opts.max_context, o.page_tokens = opts.page_tokens;
-    const int per = (opts.max_context + opts.page_tokens - 1) / opts.page_tokens;
-    o.pool_pages = opts.kv_pool_pages > 0 ? opts.kv_pool_pages : per * opts.sessions;
+    o.pool_pages = pool_pages_for(opts);
     o.max_seqs = opts.max_seqs, o.max_rows = opts.max_rows, o.use_graph = opts.step_graphs, o.device = opts.device, o.pdl = opts.pdl;
     if (ling_b200_create(&cfg_, &o, &ctx_) != LING_B200_OK) {
       const std::string why = ling_b200_last_error();
       ling_b200_destroy(ctx_);
       throw std::runtime_error("Engine: " + why);
     }
-    pool_ = std::make_unique<KvPool>(o.pool_pages + 1, opts.page_tokens);
-    sess_.resize(opts.sessions);
   }
   ~Engine() { ling_b200_destroy(ctx_); }
   Engine(const Engine&) = delete;
@@ -217,17 +363,18 @@ class Engine {
 
   ling_b200_ctx* handle() { return ctx_; }
   const ModelConfig& config() const { return cfg_; }
-  int sessions() const { return static_cast<int>(sess_.size()); }
+  int sessions() const { return book_.sessions(); }
+  SessionBook& book() { return book_; }
   int max_context() const { return opts_.max_context; }
   void set_tree_source(TreeSource f) { tree_source_ = std::move(f); }
   void select_session(int i) { active_ = i; }
   int active_session() const { return active_; }
-  const std::vector<int>& history() const { return sess_[active_].history; }
-  int position(int session) const { return sess_[session].pos; }
+  const std::vector<int>& history() const { return book_.at(active_).history; }
+  int position(int session) const { return book_.at(session).pos; }
   // What a prefill would leave: `tokens` become the session's history, its KV positions are mapped; the caller fills the
   // cache and the state through the handle (ling_b200_kv_write / ling_b200_state_write or the synthetic fills).
   void adopt_context(int session, const std::vector<int>& tokens) {
-    Session& s = sess_[session];
+    Session& s = book_.at(session);
     s.history = tokens;
     s.pos = static_cast<int>(tokens.size());
     kv_ensure(s, session, 0, s.pos);
@@ -236,34 +383,70 @@ class Engine {
   bool can_speculate(const SamplingParams& p) const { return p.temperature <= 0.f && static_cast<bool>(tree_source_); }
   bool can_batch(int session, const SamplingParams& p) const {
     return can_speculate(p) && session >= 0 && session < sessions() &&
-           sess_[session].pos + kernels::kMaxStreamRows <= opts_.max_context;
+           book_.at(session).pos + kernels::kMaxStreamRows <= opts_.max_context;
   }
 
   // ---- the KV page pool as the scheduler sees it (src/core/engine.hpp:428-493)
   bool kv_paged() const { return true; }
-  int kv_pages_total() const { return pool_->capacity(); }
-  int kv_pages_free() { return pool_->free_pages(); }
-  int kv_pages_pending() const { return pool_->pending_pages(); }
-  int kv_admit_pages(size_t prompt_len) const { return pool_->pages_for(static_cast<int>(prompt_len)) + kKvGrowthPages; }
-  int kv_step_need(int session, bool spec) const {
-    const Session& s = sess_[session];
-    return pool_->needed(s.table, s.pos, s.pos + (spec ? kernels::kMaxStreamRows : 1));
+  int kv_pages_total() const { return book_.pool().capacity(); }
+  int kv_pages_free() { return book_.pool().free_pages(); }
+  int kv_pages_pending() const { return book_.pool().pending_pages(); }
+  int kv_admit_pages(size_t prompt_len) const { return book_.kv_admit_pages(prompt_len); }
+  int kv_step_need(int session, bool spec) const { return book_.kv_step_need(session, spec); }
+  int kv_admit_need(int session, const std::vector<int>& prompt, uint64_t scope, bool from_scratch = false) const {
+    return book_.kv_admit_need(session, prompt, scope, from_scratch);
   }
-  int kv_session_pages(int session) const {
-    KvPool::Refs r{&sess_[session].table};
-    return pool_->reclaimable(r);
-  }
+  int kv_session_pages(int session) const { return book_.kv_reclaimable({session}); }
+  int kv_reclaimable(const std::vector<int>& sessions) const { return book_.kv_reclaimable(sessions); }
+  int kv_lru_idle(const std::vector<bool>& busy) const { return book_.kv_lru_idle(busy); }
   void kv_evict(int session) {
-    Session& s = sess_[session];
-    pool_->truncate(s.table, 0);
-    s.history.clear();
-    s.pos = 0;
-    ++kv_evictions_;
+    if (book_.evict(session)) ++kv_evictions_;
+  }
+  // ---- the session book (src/core/engine.hpp:380-426)
+  int match_session(const std::vector<int>& prompt, const std::string& key, uint64_t scope = 0) const {
+    return book_.match_session(prompt, key, scope);
+  }
+  int free_session(double protect_seconds, const std::vector<bool>& pinned) const { return book_.free_session(protect_seconds, pinned); }
+  void activate_session(int i, const std::string& key, bool fresh, uint64_t scope = 0) {
+    if (i < 0 || i >= sessions()) throw std::runtime_error("no such session");
+    if (book_.activate(i, key, fresh, scope)) ++evictions_;
+    active_ = i;
+  }
+  void touch_session(int i) { book_.touch(i); }
+  int sessions_resident() const { return book_.resident(); }
+  long session_evictions() const { return evictions_; }
+  int max_batch() const { return opts_.max_seqs; }
+  // What the prefill path would do for an admitted prompt (Engine::begin_prefill + prefill_chunk, engine.cpp:1747-1990): the
+  // session keeps the positions it shares with the prompt, maps pages for the rest plus the growth reserve and takes the
+  // prompt as its history.  The prefill pass itself is outside this build: `fill` stands in for it and leaves the KV of
+  // positions [from, to) and the DeltaNet state of the slot on the device (synthetic in the tests and the benchmark); it
+  // returns the first token.  Throws KvPoolExhausted with nothing changed when the pool is short.
+  using PrefillFill = std::function<int(ling_b200_ctx*, int session, int from, int to)>;
+  void set_prefill_fill(PrefillFill f) { prefill_fill_ = std::move(f); }
+  int begin_prefill(int session, const std::vector<int>& prompt, uint64_t scope = 0) {
+    Session& s = book_.at(session);
+    const int L = static_cast<int>(prompt.size());
+    const int reuse = book_.resume_reuse(session, prompt, scope, false);
+    const int target = std::min(L + SessionBook::kKvGrowthPages * opts_.page_tokens, opts_.max_context);
+    if (book_.kv_admit_need(session, prompt, scope) > book_.pool().free_pages()) book_.pool().retire();
+    if (book_.kv_admit_need(session, prompt, scope) > book_.pool().free_pages()) throw KvPoolExhausted("KV page pool exhausted: prefill");
+    book_.pool().truncate(s.table, book_.pool().pages_for(target) * opts_.page_tokens);
+    kv_ensure(s, session, reuse, target);
+    s.history = prompt;
+    s.prompt_len = L;
+    s.pos = L;
+    s.turn_start = L;  // a prompt without message boundaries is bound again only when extended whole (engine.cpp:2276-2282)
+    for (int k = L - 1; k >= 0; --k)
+      if (prompt[size_t(k)] == opts_.boundary_token) {
+        s.turn_start = k + 1;
+        break;
+      }
+    return prefill_fill_ ? prefill_fill_(ctx_, session, reuse, L) : 0;
   }
   long kv_evictions() const { return kv_evictions_; }
   bool kv_retire(bool) {
-    pool_->retire();  // the step has been fetched: no stream still reads a released page
-    return pool_->pending_pages() == 0;
+    book_.pool().retire();  // the step has been fetched: no stream still reads a released page
+    return book_.pool().pending_pages() == 0;
   }
   uint64_t state_hash() {
     uint64_t h = 0;
@@ -285,19 +468,19 @@ class Engine {
     std::vector<DraftTree> trees;
     int need = 0;
     for (const SeqStep& q : seqs) {
-      trees.push_back(tree_source_(q.session, q.anchor, sess_[q.session].history));
-      const Session& s = sess_[q.session];
-      need += pool_->needed(s.table, s.pos, s.pos + trees.back().rows());
+      trees.push_back(tree_source_(q.session, q.anchor, book_.at(q.session).history));
+      const Session& s = book_.at(q.session);
+      need += book_.pool().needed(s.table, s.pos, s.pos + trees.back().rows());
     }
-    if (need > pool_->free_pages()) pool_->retire();
-    if (need > pool_->free_pages())
+    if (need > book_.pool().free_pages()) book_.pool().retire();
+    if (need > book_.pool().free_pages())
       throw KvPoolExhausted("KV page pool exhausted: the batch's step needs " + std::to_string(need) + " pages, " +
-                            std::to_string(pool_->free_pages()) + " free");
+                            std::to_string(book_.pool().free_pages()) + " free");
     std::vector<ling_b200_seq_step> steps(seqs.size());
     std::vector<ling_b200_seq_result> res(seqs.size());
     bool logits = false;
     for (size_t i = 0; i < seqs.size(); ++i) {
-      Session& s = sess_[seqs[i].session];
+      Session& s = book_.at(seqs[i].session);
       kv_ensure(s, seqs[i].session, s.pos, s.pos + trees[i].rows());
       steps[i] = ling_b200_seq_step{seqs[i].session, s.pos, 0, trees[i].rows(), trees[i].E, trees[i].token.data(),
                                     trees[i].parent.data(), nullptr};
@@ -307,7 +490,7 @@ class Engine {
     if (ling_b200_verify_step(ctx_, steps.data(), static_cast<int>(steps.size()), flags, res.data()) != LING_B200_OK)
       throw std::runtime_error(std::string("speculate_batch: ") + ling_b200_last_error());
     for (size_t i = 0; i < seqs.size(); ++i) {
-      Session& s = sess_[seqs[i].session];
+      Session& s = book_.at(seqs[i].session);
       if (res[i].status != LING_B200_SEQ_OK) {  // nothing committed; the session is reset (speculate.cpp:1266-1272)
         seqs[i].error = std::make_exception_ptr(NonFiniteLogits());
         seqs[i].out.clear();
@@ -318,7 +501,7 @@ class Engine {
       for (int j = 0; j < res[i].n_path; ++j) s.history.push_back(trees[i].token[res[i].path[j]]);
       s.pos += res[i].n_path;
     }
-    pool_->retire();
+    book_.pool().retire();
   }
   std::vector<int> speculate(int anchor, const SamplingParams& p, std::vector<float>* row_logits = nullptr) {
     SeqStep q;
@@ -329,16 +512,12 @@ class Engine {
   }
 
  private:
-  struct Session {
-    std::vector<int> history, table;
-    int pos = 0;
-  };
   // kv_ensure (src/core/engine.cpp:841-869): pages for [from, to), copy-on-write copies made before the write, changed
   // table entries pushed to the device.
   void kv_ensure(Session& s, int slot, int from, int to) {
     const std::vector<int> before = s.table;
     std::vector<KvPool::Copy> copies;
-    if (!pool_->ensure(s.table, from, to, &copies)) throw KvPoolExhausted("KV page pool exhausted");
+    if (!book_.pool().ensure(s.table, from, to, &copies)) throw KvPoolExhausted("KV page pool exhausted");
     std::vector<int> src, dst, idx, val;
     for (const KvPool::Copy& c : copies) src.push_back(c.src), dst.push_back(c.dst);
     if (!src.empty()) ling_b200_kv_pages_copy(ctx_, src.data(), dst.data(), static_cast<int>(src.size()));
@@ -350,9 +529,10 @@ class Engine {
   ModelConfig cfg_;
   EngineOptions opts_;
   ling_b200_ctx* ctx_ = nullptr;
-  std::unique_ptr<KvPool> pool_;
-  std::vector<Session> sess_;
+  SessionBook book_;
   TreeSource tree_source_;
+  PrefillFill prefill_fill_;
+  long evictions_ = 0;
   int active_ = 0;
   long kv_evictions_ = 0;
 };

@@ -8,15 +8,16 @@ import pytest
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 PKG = os.path.join(ROOT, "ling-engine_b200")
 EXE = os.path.join(ROOT, "tests", "cpp", "facade_test")
+SCHED = os.path.join(ROOT, "tests", "cpp", "scheduler_test")
 
 
-def build(lb):
-    src = os.path.join(ROOT, "tests", "cpp", "facade_test.cpp")
-    hdr = os.path.join(PKG, "csrc", "host", "ling_engine.hpp")
-    if os.path.exists(EXE) and os.path.getmtime(EXE) > max(os.path.getmtime(src), os.path.getmtime(hdr), os.path.getmtime(lb.LIB_PATH)):
+def build(lb, exe=EXE):
+    src = exe + ".cpp"
+    hdrs = [os.path.join(PKG, "csrc", "host", h) for h in ("ling_engine.hpp", "ling_scheduler.hpp")]
+    if os.path.exists(exe) and os.path.getmtime(exe) > max([os.path.getmtime(f) for f in [src, lb.LIB_PATH] + hdrs]):
         return
     subprocess.run(["g++", "-std=c++20", "-O1", "-Wall", "-I", os.path.join(ROOT, "include"), "-I", os.path.join(PKG, "csrc", "host"),
-                    src, "-o", EXE, lb.LIB_PATH, "-Wl,-rpath," + PKG], check=True)
+                    src, "-o", exe, lb.LIB_PATH, "-Wl,-rpath," + PKG], check=True)
 
 
 def test_facade_host_logic(lb):
@@ -29,4 +30,19 @@ def test_facade_host_logic(lb):
 def test_facade_engine_speculate_batch(gpu, lb):
     build(lb)
     out = subprocess.run([EXE, "gpu"], capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stdout + out.stderr
+
+
+def test_scheduler_loop_on_a_host_engine(lb):
+    """The headless scheduler (admission, turns, batching, pairing, page pressure, last resort) against a host-only engine."""
+    build(lb, SCHED)
+    out = subprocess.run([SCHED, "host"], capture_output=True, text=True, timeout=120)
+    assert out.returncode == 0, out.stdout + out.stderr
+
+
+@pytest.mark.gpu
+def test_scheduler_continuous_batching_equals_serving_alone(gpu, lb):
+    """Six requests through four sessions under the scheduler's continuous batching give, token for token, what each gives alone."""
+    build(lb, SCHED)
+    out = subprocess.run([SCHED, "gpu"], capture_output=True, text=True, timeout=600)
     assert out.returncode == 0, out.stdout + out.stderr
