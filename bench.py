@@ -634,6 +634,43 @@ def run_mixed(args, rank, local_rank, world):
     dist.close()
 
 
+def run_served(args, rank, local_rank, world):
+    """The 64-sequence continuous-batching workload produced by the scheduler loop itself (the headless serving driver,
+    ling-engine_b200/ling_serve_headless: requests queue up, are admitted into session slots and the KV page pool, share
+    verify passes, finish and hand their pages on) instead of a scripted batch.  Sessions and requests are sharded over the
+    ranks (whole requests, no collective).  value = tree rows verified per second of pass time, summed over ranks with the
+    slowest rank's pass time; the driver's own counters ride along."""
+    exe = os.path.join(ROOT, "ling-engine_b200", "ling_serve_headless")
+    if not os.path.exists(exe):
+        importlib.import_module("ling-engine_b200.build").build()
+    dist = Dist(world, local_rank)
+    sessions, requests = max(1, 64 // world), max(1, 96 // world)
+    cmd = [exe, "--layers", str(args.layers), "--sessions", str(sessions), "--batch", str(sessions), "--requests", str(requests),
+           "--seed", str(1 + rank), "--device", str(local_rank), "--max-tokens", "128"]
+    clocks = ClockSampler(local_rank)
+    clocks.start()
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=3000)
+    clk = clocks.stop()
+    lines = [l for l in out.stdout.splitlines() if l.startswith("{")]
+    if out.returncode != 0 or not lines:
+        raise SystemExit("ling_serve_headless failed (%d): %s" % (out.returncode, out.stderr[-2000:]))
+    d = json.loads(lines[-1])
+    rows = d["rows_per_pass"] * d["decode_passes"]
+    pass_s = dist.max(d["pass_seconds"])
+    total_rows, total_tokens, passes = dist.sum(rows), dist.sum(d["produced_tokens"]), dist.sum(d["decode_passes"])
+    if rank == 0:
+        print(json.dumps({
+            "metric": METRIC, "value": total_rows / pass_s, "unit": UNIT, "n_gpus": world, "steps": int(passes), "warmup": 0,
+            "ms_per_step": pass_s / max(1.0, passes / world) * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "fp8_e4m3 (fp32 accumulate)", "data": "synthetic",
+            "config": {"workload": "served64: 96 queued requests through 64 session slots under the scheduler loop", "model":
+                       "27B-class hybrid, %d layers" % args.layers, "parallelism": "requests and sessions sharded over %d GPU(s), no collective" % world,
+                       "l2": "inputs larger than L2 (weights 26.4 GB per pass), no flush"},
+            "accepted_tokens_per_s": total_tokens / pass_s, "rank0_driver": d,
+            "gpu_launches": int(d["launches_last_pass"] * passes), "clocks": clk}), flush=True)
+    dist.close()
+
+
 def run_micro_gemm(args):
     """One weight GEMM alone (synthetic FP8 weights and activations resident in HBM), `iters` launches back to back after
     three warm-up launches; the small case the profiler captures.  A matrix smaller than L2 is served from L2 here."""
@@ -689,7 +726,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="single", choices=["single", "ragged4", "churn64", "mixed", "toy"])
+    ap.add_argument("--workload", default="single", choices=["single", "ragged4", "churn64", "served64", "mixed", "toy"])
     ap.add_argument("--layers", type=int, default=64, help="layers of the 27B-class stack (64 = the named configuration)")
     ap.add_argument("--gemm-impl", type=int, default=0)
     ap.add_argument("--pdl", type=int, default=1, help="programmatic dependent launch (bit-identical results; on by default)")
@@ -713,6 +750,8 @@ def main():
         raise SystemExit("bench.py: --gpus %d but WORLD_SIZE=%d" % (args.gpus, world))
     if args.workload == "mixed":
         return run_mixed(args, rank, local_rank, world)
+    if args.workload == "served64":
+        return run_served(args, rank, local_rank, world)
     run_ours(args, rank, local_rank, world)
 
 

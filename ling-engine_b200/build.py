@@ -58,7 +58,24 @@ def build(force=False, verbose=False):
                            capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError("link failed:\n%s\n%s" % (r.stdout, r.stderr))
+    build_serve(force)
     return OUT
+
+
+SERVE = os.path.join(HERE, "ling_serve_headless")
+
+
+def build_serve(force=False):
+    """The headless serving driver (csrc/host/serve_headless.cpp): plain C++ over the C ABI, linked to the library beside it."""
+    src = os.path.join(CSRC, "host", "serve_headless.cpp")
+    deps = [src, OUT] + [os.path.join(CSRC, "host", h) for h in ("ling_engine.hpp", "ling_scheduler.hpp")]
+    if not (force or _newer(deps, SERVE)):
+        return SERVE
+    r = subprocess.run([os.environ.get("CXX", "g++"), "-std=c++20", "-O2", "-Wall", "-I", os.path.join(HERE, "..", "include"),
+                        "-I", os.path.join(CSRC, "host"), src, "-o", SERVE, OUT, "-Wl,-rpath,$ORIGIN"], capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("serve_headless failed to build:\n%s\n%s" % (r.stdout, r.stderr))
+    return SERVE
 
 
 if __name__ == "__main__":
