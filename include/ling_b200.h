@@ -289,6 +289,11 @@ int ling_b200_prefill_gemm_nvfp4_host(int device, const uint8_t* xq, const uint8
 int ling_b200_prefill_swiglu_nvfp4_host(int device, const uint8_t* xq, const uint8_t* xs, int M, const uint8_t* gate_q,
                                         const uint8_t* gate_s, float alpha_gate, const uint8_t* up_q, const uint8_t* up_s, float alpha_up,
                                         int N, int K, float out_input_scale, uint8_t* q_out, uint8_t* sf_out);
+/* Which form of the NVFP4 GEMM the entry points below launch (process-wide): 0 = one CTA per 128 x 256 tile, 1 = the
+ * two-CTA form (tcgen05 cta_group::2 over a cluster of two: 256 x 256 per pair, each CTA loading its own rows of the
+ * activations and half of the weight tile by ordinary, non-multicast TMA).  Same results bit for bit.  Returns the previous
+ * setting. */
+int ling_b200_nvfp4_pair_mode(int mode);
 /* The NVFP4 GEMM (fused != 0: the gate|up form) timed on the device with resident operands: ms per launch.  cycle_shares
  * (optional, 3 doubles): from one more launch with the kernel's cycle counters on, the shares of a CTA's time that the MMA
  * issuer spent waiting for operand stages, that it spent waiting for the epilogue to free the accumulator, and that one

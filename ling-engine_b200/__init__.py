@@ -460,6 +460,11 @@ def prefill_swiglu_nvfp4(xq, xs, gq, gs, alpha_gate, uq, us, alpha_up, out_input
     return q, sf
 
 
+def nvfp4_pair_mode(mode):
+    """0: one CTA per tile; 1: the two-CTA (cta_group::2) form.  Returns the previous setting."""
+    return lib().ling_b200_nvfp4_pair_mode(int(mode))
+
+
 def nvfp4_gemm_bench(M, N, K, fused=False, iters=10, device=0, shares=False):
     """ms per launch; with shares, also the kernel's own cycle shares (issuer waiting for stages, issuer waiting for the
     epilogue, one epilogue warp busy) of a CTA's time."""

@@ -575,6 +575,25 @@ int encode_tile_map(CUtensorMap* map, void* base, uint64_t row_bytes, uint64_t r
   return encode_2d(map, base, row_bytes, rows, box_rows);
 }
 
+int encode_linear_map(CUtensorMap* map, void* base, uint64_t row_bytes, uint64_t rows, uint32_t box_bytes) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) {
+    set_error("cuTensorMapEncodeTiled is not available from the driver");
+    return LING_B200_ERR_CUDA;
+  }
+  const cuuint64_t dims[2] = {row_bytes / 8, rows};
+  const cuuint64_t strides[1] = {row_bytes};
+  const cuuint32_t box[2] = {box_bytes / 8, 1};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled (linear) failed with code " + std::to_string(int(r)));
+    return LING_B200_ERR_CUDA;
+  }
+  return LING_B200_OK;
+}
+
 int make_weight_map(Fp8Matrix& w) { return encode_2d(&w.map, w.codes, uint64_t(w.K_pad), uint64_t(w.N_pad), kTileN); }
 
 int make_acts_maps(Fp8Acts& x) {

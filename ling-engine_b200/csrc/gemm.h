@@ -57,6 +57,9 @@ struct GemmCall {
 // Tensor map of a row-major byte matrix [rows][row_bytes] read in boxes of 128 bytes x box_rows under the 128B swizzle
 // (row_bytes a multiple of 16; rows and bytes past the extent read zero).
 int encode_tile_map(CUtensorMap* map, void* base, uint64_t row_bytes, uint64_t rows, uint32_t box_rows);
+// Tensor map of a row-major byte matrix read in unswizzled boxes of box_bytes (at most 2048, a multiple of 16) of one row:
+// the box lands as box_bytes consecutive bytes.  Coordinates count 8-byte words.
+int encode_linear_map(CUtensorMap* map, void* base, uint64_t row_bytes, uint64_t rows, uint32_t box_bytes);
 // Creates the tensor maps (driver entry point fetched at run time; no link against libcuda).
 int make_weight_map(Fp8Matrix& w);
 int make_acts_maps(Fp8Acts& x);

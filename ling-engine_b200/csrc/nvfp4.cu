@@ -16,6 +16,7 @@
 // Every wait is bounded; a wait that runs out records a code in the device error word and the CTA unwinds.
 #include "nvfp4.h"
 
+#include <atomic>
 #include <mutex>
 
 #include "../../include/ling_b200.h"
@@ -111,6 +112,53 @@ struct GemmArgs {
   unsigned long long* stats;  // optional cycle sums over all CTAs: [0] issuer waiting for stages, [1] issuer waiting for the
                               // epilogue, [2] epilogue busy (one warp), [3] whole CTA
 };
+
+// One epilogue warp's part of a finished tile: TMEM lanes = token rows (this thread's row), columns = the tile's weight rows;
+// `half` selects which four of the tile's eight column groups this warp drains.
+template <bool SWIGLU>
+__device__ __forceinline__ void drain_tile(const GemmArgs& p, uint32_t taddr, int row, int tn, int half) {
+  if constexpr (SWIGLU) {
+  const int f0 = tn * 128;  // the tile's first feature: columns 0-127 its gate products, 128-255 its up products
+#pragma unroll 1
+  for (int b = 4 * half; b < 4 * half + 4; ++b) {
+    uint32_t g[16], u[16];
+    tmem_ld16(taddr + 16 * b, g);
+    tmem_ld16(taddr + 128 + 16 * b, u);
+    tmem_ld_wait();
+    float v[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) v[j] = bf16_round(silu(__uint_as_float(g[j]) * p.alpha) * (__uint_as_float(u[j]) * p.alpha2));
+    uint2 codes;
+    const uint8_t sc = encode_block(v, p.gscale_out, codes);
+    if (row < p.M) {
+      const int f = f0 + 16 * b;
+      *reinterpret_cast<uint2*>(p.q_out + size_t(row) * (p.N / 2) + f / 2) = codes;
+      p.sf_out[p.sf_out_tiled ? fp4_sf_offset(row, f / 16, p.out_atoms) : size_t(row) * (p.N / 16) + f / 16] = sc;
+    }
+  }
+} else {
+  const int n0 = tn * kFp4TileN;
+#pragma unroll 1
+  for (int c = 4 * half; c < 4 * half + 4; ++c) {
+    uint32_t v[32];
+    tmem_ld32(taddr + 32 * c, v);
+    tmem_ld_wait();
+    if (row < p.M && n0 + 32 * c < p.N) {
+      float4* dst = reinterpret_cast<float4*>(p.y + size_t(row) * p.ldy + n0 + 32 * c);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float4 o = make_float4(__uint_as_float(v[4 * j]) * p.alpha, __uint_as_float(v[4 * j + 1]) * p.alpha,
+                               __uint_as_float(v[4 * j + 2]) * p.alpha, __uint_as_float(v[4 * j + 3]) * p.alpha);
+        if (p.accumulate) {
+          const float4 old = dst[j];
+          o.x += old.x, o.y += old.y, o.z += old.z, o.w += old.w;
+        }
+        dst[j] = o;
+      }
+    }
+  }
+}
+}
 
 template <bool SWIGLU>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -250,47 +298,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       tc_fence_after();
       const int row = tm * kFp4TileM + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16);
-      if constexpr (SWIGLU) {
-        const int f0 = tn * 128;  // the tile's first feature: columns 0-127 its gate products, 128-255 its up products
-#pragma unroll 1
-        for (int b = 4 * half; b < 4 * half + 4; ++b) {
-          uint32_t g[16], u[16];
-          tmem_ld16(taddr + 16 * b, g);
-          tmem_ld16(taddr + 128 + 16 * b, u);
-          tmem_ld_wait();
-          float v[16];
-#pragma unroll
-          for (int j = 0; j < 16; ++j) v[j] = bf16_round(silu(__uint_as_float(g[j]) * p.alpha) * (__uint_as_float(u[j]) * p.alpha2));
-          uint2 codes;
-          const uint8_t sc = encode_block(v, p.gscale_out, codes);
-          if (row < p.M) {
-            const int f = f0 + 16 * b;
-            *reinterpret_cast<uint2*>(p.q_out + size_t(row) * (p.N / 2) + f / 2) = codes;
-            p.sf_out[p.sf_out_tiled ? fp4_sf_offset(row, f / 16, p.out_atoms) : size_t(row) * (p.N / 16) + f / 16] = sc;
-          }
-        }
-      } else {
-        const int n0 = tn * kFp4TileN;
-#pragma unroll 1
-        for (int c = 4 * half; c < 4 * half + 4; ++c) {
-          uint32_t v[32];
-          tmem_ld32(taddr + 32 * c, v);
-          tmem_ld_wait();
-          if (row < p.M && n0 + 32 * c < p.N) {
-            float4* dst = reinterpret_cast<float4*>(p.y + size_t(row) * p.ldy + n0 + 32 * c);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              float4 o = make_float4(__uint_as_float(v[4 * j]) * p.alpha, __uint_as_float(v[4 * j + 1]) * p.alpha,
-                                     __uint_as_float(v[4 * j + 2]) * p.alpha, __uint_as_float(v[4 * j + 3]) * p.alpha);
-              if (p.accumulate) {
-                const float4 old = dst[j];
-                o.x += old.x, o.y += old.y, o.z += old.z, o.w += old.w;
-              }
-              dst[j] = o;
-            }
-          }
-        }
-      }
+      drain_tile<SWIGLU>(p, taddr, row, tn, half);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tmem_empty);
@@ -304,6 +312,230 @@ __global__ void __launch_bounds__(kThreads, 1)
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------------------------- two-CTA form
+// The same GEMM with the MMA spanning a pair of CTAs (a cluster of two, tcgen05 cta_group::2): the pair's tile is 256 token
+// rows x 256 weight rows; each CTA keeps its own 128 token rows of A and HALF of B (128 weight rows) in shared memory, the
+// tensor cores of both read both halves.  Per CTA and stage 38 KiB arrive instead of 54, and the shared-memory reads of B
+// halve: the one-CTA tile is bound by exactly that traffic.  Every CTA issues its own ordinary TMA loads into its own shared
+// memory, completing on the LEADER's mbarrier (cta_group::2); the leader (cluster rank 0) arms it for both
+// CTAs' bytes, copies the scales and issues the MMAs for the pair; tcgen05.commit with a cluster mask releases the stage in
+// both CTAs and hands both accumulators to the two epilogues.  Fused form: the leader's half of B is the gate rows, the
+// peer's the up rows of the same 128 features.
+constexpr int kPairStages = 5;
+constexpr int kPairStageBytes = kABytes + kBBytes / 2 + 3 * kSfGroup;  // 38 KiB: A, half of B, scales of A and of both B halves
+constexpr size_t kPairSmemBytes = size_t(kPairStages) * kPairStageBytes + 1024 + 256;
+static_assert(kPairStageBytes % 1024 == 0, "swizzled tiles start on 1024-byte boundaries");
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {  // the same offset in another CTA of the cluster
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA tile load of a CTA pair: lands in this CTA's shared memory, completes on the barrier at `bar_cluster_addr` (the leader's).
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int x, int y, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(x), "r"(y), "l"(policy)
+      : "memory");
+}
+__device__ __forceinline__ void umma_nvfp4_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t sfa, uint32_t sfb,
+                                                uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n"
+      "}\n" ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+      : "memory");
+}
+__device__ __forceinline__ void sf_copy_pair(uint32_t tmem_col, uint64_t desc) {
+  asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(tmem_col), "l"(desc) : "memory");
+}
+// Arrives (once the pair's earlier tcgen05 operations are done) on the barrier at this offset in both CTAs of the pair.
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(smem_u32(bar)),
+               "h"(uint16_t(3))
+               : "memory");
+}
+__host__ __device__ constexpr uint32_t umma_idesc_nvfp4_pair(int n) {  // M = 256 over the pair
+  return (1u << 7) | (1u << 10) | (uint32_t(n >> 3) << 17) | (uint32_t(256 >> 4) << 24);
+}
+
+// The block scales travel as tensor-map tiles too (the completion must reach the leader's barrier, which the plain bulk copy
+// cannot address): the scale array of an operand seen as [row groups][k_atoms * 64] 8-byte words, one box = 256 words = the
+// 2 KiB of one row group's stage.
+template <bool SWIGLU>
+__global__ void __launch_bounds__(kThreads, 1)
+    gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB0,
+                           const __grid_constant__ CUtensorMap mapB1, const __grid_constant__ CUtensorMap mapSA,
+                           const __grid_constant__ CUtensorMap mapSB0, const __grid_constant__ CUtensorMap mapSB1, const GemmArgs p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + kPairStages * kPairStageBytes);  // used in the leader only
+  uint64_t* empty = full + kPairStages;
+  uint64_t* tmem_full = empty + kPairStages;
+  uint64_t* tmem_empty = tmem_full + 1;  // used in the leader only
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_rank();
+  const bool leader = rank == 0;
+  const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+  const int tiles = p.tiles_m * p.tiles_n;  // tiles_m counts 256-row pair tiles here
+  const long long t_start = clock64();
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kPairStages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(tmem_full, 1);
+    mbar_init(tmem_empty, 2 * kEpiWarps);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {  // both CTAs, the same warp and the same slot
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    tc_fence_before();
+  }
+  __syncthreads();
+  cluster_sync();  // the peer's barriers exist before anything signals them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ producer (each CTA loads its own operands)
+    if (lane == 0) {
+      const uint64_t pol = policy_evict_last();
+      const CUtensorMap* mapB = leader ? &mapB0 : &mapB1;
+      int it = 0;
+      bool ok = true;
+      for (int t = pair; t < tiles && ok; t += pairs) {
+        const int tm = t % p.tiles_m, tn = t / p.tiles_m;
+        const int arow = tm * 256 + int(rank) * 128;
+        const int brow = tn * p.b_step + (leader ? 0 : p.b1_off);
+        const int ga = arow >> 7, gb0 = tn * p.g_mul, gb1 = tn * p.g_mul + p.g1_off;
+        for (int ks = 0; ks < p.k_stages; ++ks, ++it) {
+          const int s = it % kPairStages;
+          ok = mbar_wait(&empty[s], ((it / kPairStages) & 1) ^ 1, abort_flag);
+          if (!ok) {
+            dev_fail(p.err_flag, kDevWaitEmpty);
+            *abort_flag = 1;
+            break;
+          }
+          uint8_t* st = smem + s * kPairStageBytes;
+          const uint32_t bar = map_to_cta(smem_u32(&full[s]), 0);
+          if (leader) mbar_expect_tx(&full[s], 2 * kPairStageBytes);
+          tma_load_2d_pair(st, &mapA, bar, ks * kRowBytes, arow, pol);
+          tma_load_2d_pair(st + kABytes, mapB, bar, ks * kRowBytes, brow, pol);
+          tma_load_2d_pair(st + kABytes + kBBytes / 2, &mapSA, bar, ks * 256, ga, pol);
+          tma_load_2d_pair(st + kABytes + kBBytes / 2 + kSfGroup, &mapSB0, bar, ks * 256, gb0, pol);
+          tma_load_2d_pair(st + kABytes + kBBytes / 2 + 2 * kSfGroup, &mapSB1, bar, ks * 256, gb1, pol);
+        }
+      }
+      // The leader waits for every stage it armed (both CTAs' copies have then landed); the peer's copies complete on the
+      // leader's barriers, so the closing cluster barrier below is what keeps the peer's shared memory alive until then.
+      if (leader)
+        for (int j = (it > kPairStages ? it - kPairStages : 0); j < it; ++j) mbar_wait(&full[j % kPairStages], (j / kPairStages) & 1, nullptr);
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (the leader, for the pair)
+    if (lane == 0 && leader) {
+      constexpr uint32_t idesc = umma_idesc_nvfp4_pair(kFp4TileN);
+      int it = 0, ti = 0;
+      bool ok = true;
+      long long w_full = 0, w_empty = 0;
+      for (int t = pair; t < tiles && ok; t += pairs, ++ti) {
+        long long c0 = clock64();
+        if (!mbar_wait(tmem_empty, (ti & 1) ^ 1, abort_flag)) {
+          dev_fail(p.err_flag, kDevWaitTmemEmpty);
+          *abort_flag = 1;
+          break;
+        }
+        tc_fence_after();
+        w_empty += clock64() - c0;
+        for (int ks = 0; ks < p.k_stages; ++ks, ++it) {
+          const int s = it % kPairStages;
+          c0 = clock64();
+          if (!mbar_wait(&full[s], (it / kPairStages) & 1, abort_flag)) {
+            dev_fail(p.err_flag, kDevWaitFull);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          w_full += clock64() - c0;
+          tc_fence_after();
+          const uint32_t st = smem_u32(smem + s * kPairStageBytes);
+          const uint32_t sf = st + kABytes + kBBytes / 2;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            sf_copy_pair(tmem_base + kSfaCol + 4 * k, sf_desc(sf + 512 * k));
+            sf_copy_pair(tmem_base + kSfbCol + 8 * k, sf_desc(sf + kSfGroup + 512 * k));
+            sf_copy_pair(tmem_base + kSfbCol + 8 * k + 4, sf_desc(sf + 2 * kSfGroup + 512 * k));
+          }
+          const uint64_t adesc = umma_desc_sw128(st), bdesc = umma_desc_sw128(st + kABytes);
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            umma_nvfp4_pair(tmem_base, adesc + uint64_t(k * 2), bdesc + uint64_t(k * 2), idesc, tmem_base + kSfaCol + 4 * k,
+                            tmem_base + kSfbCol + 8 * k, (ks > 0 || k > 0) ? 1u : 0u);
+          umma_commit_pair(&empty[s]);
+        }
+        if (ok) umma_commit_pair(tmem_full);
+      }
+      if (p.stats) {
+        atomicAdd(p.stats, (unsigned long long)w_full);
+        atomicAdd(p.stats + 1, (unsigned long long)w_empty);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue: each CTA drains its own 128 rows
+    const int quarter = warp & 3, half = (warp - 2) >> 2;
+    const uint32_t empty_bar = map_to_cta(smem_u32(tmem_empty), 0);
+    int ti = 0;
+    long long busy = 0;
+    for (int t = pair; t < tiles; t += pairs, ++ti) {
+      const int tm = t % p.tiles_m, tn = t / p.tiles_m;
+      if (!mbar_wait(tmem_full, ti & 1, abort_flag)) {
+        dev_fail(p.err_flag, kDevWaitTmemFull);
+        *abort_flag = 1;
+        break;
+      }
+      const long long c0 = clock64();
+      tc_fence_after();
+      const int row = tm * 256 + int(rank) * 128 + quarter * 32 + lane;
+      const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16);
+      drain_tile<SWIGLU>(p, taddr, row, tn, half);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(empty_bar);
+      busy += clock64() - c0;
+    }
+    if (p.stats && leader && warp == 2 && lane == 0) atomicAdd(p.stats + 2, (unsigned long long)busy);
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync();  // neither CTA leaves while the other may still signal its barriers or read its shared memory
+  if (p.stats && leader && threadIdx.x == 0) atomicAdd(p.stats + 3, (unsigned long long)(clock64() - t_start));
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
   }
 }
 
@@ -496,12 +728,17 @@ bool shape_ok(int rows, int K, const char* what) {
 
 }  // namespace
 
+static std::atomic<int> g_pair_mode{0};
+int fp4_set_pair_mode(int mode) { return g_pair_mode.exchange(mode); }
+
 int fp4_init() {
   static std::once_flag once;
   static int rc = LING_B200_OK;
   std::call_once(once, [] {
     if (cudaFuncSetAttribute(gemm_nvfp4_tcgen05_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemBytes)) != cudaSuccess ||
-        cudaFuncSetAttribute(gemm_nvfp4_tcgen05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemBytes)) != cudaSuccess) {
+        cudaFuncSetAttribute(gemm_nvfp4_tcgen05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemBytes)) != cudaSuccess ||
+        cudaFuncSetAttribute(gemm_nvfp4_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kPairSmemBytes)) != cudaSuccess ||
+        cudaFuncSetAttribute(gemm_nvfp4_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kPairSmemBytes)) != cudaSuccess) {
       set_error("cudaFuncSetAttribute failed for the NVFP4 GEMM");
       rc = LING_B200_ERR_CUDA;
     }
@@ -514,7 +751,8 @@ int make_fp4_map(Fp4Operand& o) {
     set_error("NVFP4 operand: K must be a multiple of 32 (16-byte rows for the tensor map)");
     return LING_B200_ERR_ARG;
   }
-  return encode_tile_map(&o.map, o.codes, uint64_t(o.K / 2), uint64_t(o.rows), 128);
+  if (const int r = encode_tile_map(&o.map, o.codes, uint64_t(o.K / 2), uint64_t(o.rows), 128)) return r;
+  return encode_linear_map(&o.sf_map, o.sf, uint64_t(fp4_k_atoms(o.K)) * 512, uint64_t(round_up(o.rows, kFp4TileN) / 128), kSfGroup);
 }
 
 int fp4_gemm_launch(const Fp4GemmCall& c, cudaStream_t stream) {
@@ -546,6 +784,16 @@ int fp4_gemm_launch(const Fp4GemmCall& c, cudaStream_t stream) {
   int dev = 0;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const bool pair = c.pair >= 0 ? c.pair > 0 : g_pair_mode.load() > 0;
+  if (pair) {
+    p.tiles_m = ceil_div(X.rows, 2 * kFp4TileM);
+    const int pairs = std::max(1, std::min((c.ctas > 0 ? c.ctas : sms) / 2, p.tiles_m * p.tiles_n));
+    const Fp4Operand& B1 = fused ? *c.W2 : W;
+    LB_CUDA(launch_kernel_cluster(fused ? gemm_nvfp4_pair_kernel<true> : gemm_nvfp4_pair_kernel<false>, dim3(2 * pairs), dim3(kThreads),
+                                  kPairSmemBytes, 2, stream, X.map, W.map, B1.map, X.sf_map, W.sf_map, B1.sf_map, p));
+    LB_LAUNCH("gemm_nvfp4_pair_kernel");
+    return LING_B200_OK;
+  }
   const int ctas = std::min(c.ctas > 0 ? c.ctas : sms, p.tiles_m * p.tiles_n);
   if (fused)
     gemm_nvfp4_tcgen05_kernel<true><<<ctas, kThreads, kSmemBytes, stream>>>(X.map, W.map, c.W2->map, p);

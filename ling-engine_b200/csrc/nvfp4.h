@@ -31,6 +31,7 @@ struct Fp4Operand {
   uint8_t* sf = nullptr;     // fp4_sf_bytes(rows_alloc, K), layout above; rows and K blocks past the extent hold zero
   int rows = 0, K = 0;
   CUtensorMap map;           // {K / 2 bytes, rows}, box {128 bytes, 128 rows}, 128B swizzle; rows past the extent read zero
+  CUtensorMap sf_map;        // the scales as [row groups][k_atoms * 512 bytes], box = one row group's 2 KiB of a stage
 };
 int make_fp4_map(Fp4Operand& o);
 
@@ -51,10 +52,14 @@ struct Fp4GemmCall {
   float gscale_out = 1.f;
   int* err_flag = nullptr;
   int ctas = 0;  // 0: one per SM
+  int pair = -1; // 1: the two-CTA form (cta_group::2, 256 x 256 tiles per pair); 0: one CTA per tile; -1: the library's choice
   unsigned long long* stats = nullptr;  // optional, 4 zeroed words: cycle sums over the CTAs (issuer waiting for stages,
                                         // issuer waiting for the epilogue, one epilogue warp busy, whole CTA)
 };
 int fp4_init();
+// The form used by calls that leave Fp4GemmCall::pair at -1 (process-wide): 0 one CTA per tile, 1 the two-CTA form.  Returns the
+// previous setting.
+int fp4_set_pair_mode(int mode);
 int fp4_gemm_launch(const Fp4GemmCall& c, cudaStream_t stream);
 
 // x (and, with up, silu(x) * up) [M][K] fp32 -> NVFP4 under the global scale gscale (= 1 / input_scale): values rounded

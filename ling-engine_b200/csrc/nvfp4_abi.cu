@@ -229,6 +229,8 @@ int ling_b200_prefill_swiglu_nvfp4_host(int device, const uint8_t* xq, const uin
   return LING_B200_OK;
 }
 
+int ling_b200_nvfp4_pair_mode(int mode) { return fp4_set_pair_mode(mode != 0 ? 1 : 0); }
+
 int ling_b200_nvfp4_gemm_bench(int device, int M, int N, int K, int fused, int iters, float* ms_per_launch, double* cycle_shares) {
   if (!ms_per_launch || M < 1 || !multiple(N, 128) || !multiple(K, 128) || iters < 1) {
     set_error("nvfp4_gemm_bench: bad argument");

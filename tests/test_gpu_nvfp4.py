@@ -179,3 +179,29 @@ def test_down_projection_at_the_27b_shape_sampled(gpu, lb, lo):
     rms = np.sqrt((ref ** 2).mean())
     assert np.abs(y[np.ix_(rows, cols)] - ref).max() <= GEMM_TOL * rms + 1e-6
     assert np.isfinite(y).all()
+
+
+@pytest.mark.parametrize("M,N,K", [(67, 256, 512), (300, 640, 384), (513, 2560, 2048), (128, 128, 128), (257, 384, 1024)])
+def test_two_cta_form_gives_the_same_bits(gpu, lb, lo, M, N, K):
+    """The cta_group::2 form (a pair of CTAs per 256 x 256 tile) against the one-CTA form: plain, accumulating and fused."""
+    rng = np.random.default_rng(M + 3 * N + K)
+    xq, xs = lo.nvfp4_quant_act(rng.standard_normal((M, K)).astype(np.float32), 0.05)
+    wq, ws = random_operand(rng, N, K)
+    uq, us = random_operand(rng, N, K)
+    y0 = rng.standard_normal((M, N + 64)).astype(np.float32)
+
+    def run():
+        return (lb.prefill_gemm_nvfp4(xq, xs, wq, ws, 0.37, y=y0, ldy=N + 64, accumulate=True),
+                lb.prefill_gemm_nvfp4(xq, xs, uq, us, 0.11),
+                lb.prefill_swiglu_nvfp4(xq, xs, wq, ws, 0.013, uq, us, 0.017, 0.3))
+    prev = lb.nvfp4_pair_mode(0)
+    try:
+        one = run()
+        lb.nvfp4_pair_mode(1)
+        two = run()
+    finally:
+        lb.nvfp4_pair_mode(prev)
+    assert np.array_equal(one[0], two[0]) and np.array_equal(one[1], two[1])
+    assert np.array_equal(one[2][0], two[2][0]) and np.array_equal(one[2][1], two[2][1])
+    ref = 0.11 * (dequant64(lo, xq, xs) @ dequant64(lo, uq, us).T)
+    assert np.abs(two[1] - ref).max() <= GEMM_TOL * np.sqrt((ref ** 2).mean()) + 1e-6
