@@ -8,7 +8,7 @@
 //            512-byte atom becomes four TMEM columns, replicated over the four lane quarters), then four
 //            tcgen05.mma kind::mxf4nvf4.block_scale (M 128, N 256, K 64, scale vector 16) into the 256-column
 //            accumulator; tcgen05.commit releases the stage and, after the last stage, hands the tile to the epilogue.
-//   warps 2-9 epilogue (two per TMEM lane quarter, half of the columns each): tcgen05.ld of the tile; plain form: alpha * acc to y (or added to it); fused form: the gate and up
+//   warps 2-17 epilogue (four per TMEM lane quarter, a quarter of the columns each): tcgen05.ld of the tile; plain form: alpha * acc to y (or added to it); fused form: the gate and up
 //            halves of the tile become silu(alpha * gate) * (alpha2 * up), rounded to BF16 and written as the next GEMM's
 //            NVFP4 operand (16 features = one block scale, all in one thread).
 // TMEM: columns 0-255 accumulator, 256-271 activation scales of the stage, 272-303 weight scales.  One accumulator: the
@@ -35,7 +35,7 @@ constexpr int kBBytes = kFp4TileN * kRowBytes;    // 32 KiB
 constexpr int kSfGroup = (kFp4StageK / 64) * 512;  // one 128-row group's scales of a stage: 2 KiB
 constexpr int kStageBytes = kABytes + kBBytes + 3 * kSfGroup;
 constexpr int kSfaCol = 256, kSfbCol = 272, kTmemCols = 512;
-constexpr int kEpiWarps = 8;  // two per TMEM lane quarter, each draining half of the tile's columns
+constexpr int kEpiWarps = 16;  // four per TMEM lane quarter, each draining a quarter of the tile's columns
 constexpr int kThreads = 64 + 32 * kEpiWarps;
 constexpr size_t kSmemBytes = size_t(kStages) * kStageBytes + 1024 /* alignment slack */ + 256 /* barriers */;
 static_assert(kStageBytes % 1024 == 0, "swizzled tiles start on 1024-byte boundaries");
@@ -114,13 +114,14 @@ struct GemmArgs {
 };
 
 // One epilogue warp's part of a finished tile: TMEM lanes = token rows (this thread's row), columns = the tile's weight rows;
-// `half` selects which four of the tile's eight column groups this warp drains.
+// `part` selects which of the tile's eight column groups this warp drains (8 / kEpiPerQuarter of them).
 template <bool SWIGLU>
-__device__ __forceinline__ void drain_tile(const GemmArgs& p, uint32_t taddr, int row, int tn, int half) {
+__device__ __forceinline__ void drain_tile(const GemmArgs& p, uint32_t taddr, int row, int tn, int part) {
+  constexpr int kGroups = 8 / (kEpiWarps / 4);  // column groups per warp
   if constexpr (SWIGLU) {
   const int f0 = tn * 128;  // the tile's first feature: columns 0-127 its gate products, 128-255 its up products
 #pragma unroll 1
-  for (int b = 4 * half; b < 4 * half + 4; ++b) {
+  for (int b = kGroups * part; b < kGroups * part + kGroups; ++b) {
     uint32_t g[16], u[16];
     tmem_ld16(taddr + 16 * b, g);
     tmem_ld16(taddr + 128 + 16 * b, u);
@@ -139,7 +140,7 @@ __device__ __forceinline__ void drain_tile(const GemmArgs& p, uint32_t taddr, in
 } else {
   const int n0 = tn * kFp4TileN;
 #pragma unroll 1
-  for (int c = 4 * half; c < 4 * half + 4; ++c) {
+  for (int c = kGroups * part; c < kGroups * part + kGroups; ++c) {
     uint32_t v[32];
     tmem_ld32(taddr + 32 * c, v);
     tmem_ld_wait();
@@ -284,7 +285,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
   } else {
     // ------------------------------------------------------------------ epilogue (TMEM lane quarter = warp % 4)
-    const int quarter = warp & 3, half = (warp - 2) >> 2;
+    const int quarter = warp & 3, part = (warp - 2) >> 2;
     int ti = 0;
     long long busy = 0;
     for (int t = blockIdx.x; t < tiles; t += gridDim.x, ++ti) {
@@ -298,7 +299,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       tc_fence_after();
       const int row = tm * kFp4TileM + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16);
-      drain_tile<SWIGLU>(p, taddr, row, tn, half);
+      drain_tile<SWIGLU>(p, taddr, row, tn, part);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tmem_empty);
@@ -506,7 +507,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
   } else {
     // ------------------------------------------------------------------ epilogue: each CTA drains its own 128 rows
-    const int quarter = warp & 3, half = (warp - 2) >> 2;
+    const int quarter = warp & 3, part = (warp - 2) >> 2;
     const uint32_t empty_bar = map_to_cta(smem_u32(tmem_empty), 0);
     int ti = 0;
     long long busy = 0;
@@ -521,7 +522,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       tc_fence_after();
       const int row = tm * 256 + int(rank) * 128 + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16);
-      drain_tile<SWIGLU>(p, taddr, row, tn, half);
+      drain_tile<SWIGLU>(p, taddr, row, tn, part);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(empty_bar);
