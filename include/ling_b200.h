@@ -343,9 +343,8 @@ int ling_b200_wait_probe(int device, unsigned limit_us, int* code, unsigned* wai
  *   x_scales [K_pad/128][128] fp32, y [M][N] fp32; N_pad, K_pad = N, K rounded up to 128.
  *   Limits: M <= LING_B200_NOALLOC_MAX_ROWS and N_pad <= 32768 (one plane must fit the array); beyond them the call
  *   returns LING_B200_ERR_ARG and touches nothing.  The K split is the regular one unless the array holds fewer planes.
- *   The first call on a device looks the array's address up (cudaGetSymbolAddress) and sets kernel attributes: make it
- *   before any stream capture.  The call enqueues on `stream` (NULL = the default stream), waits for it and returns the
- *   status; the device that owns the operands and `stream` must be the calling thread's current device.  Every call shares
+ *   The first call on a device looks the array's address up (cudaGetSymbolAddress) and sets kernel attributes.  Every
+ *   call enqueues on `stream` (NULL = the default stream), waits for the stream and returns the status; the device that owns the operands and `stream` must be the calling thread's current device.  Every call shares
  *   the array: calls that overlap on the GPU race.  Nothing in it needs clearing by the caller. */
 #define LING_B200_NOALLOC_MAX_ROWS 128
 #define LING_B200_NOALLOC_SCRATCH_BYTES (16u << 20)

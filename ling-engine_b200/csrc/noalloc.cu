@@ -9,8 +9,8 @@
 // passes only the operands and the output.
 //
 // The array's name is a host-side stand-in in host code, not a device address, so its address is taken once per device
-// with cudaGetSymbolAddress (with that device current) and cached; the first call on a device does this and should come
-// before any stream capture.  Every call uses the same array: two calls that overlap on the GPU (different streams, or
+// with cudaGetSymbolAddress (with that device current) and cached; the first call on a device does this.  Every call waits
+// for its stream before it returns.  Every call uses the same array: two calls that overlap on the GPU (different streams, or
 // two host threads) race on it.  The planes need no clearing (a call reads back only what it wrote); the error word is
 // cleared at the start of every call.
 #include <mutex>
