@@ -75,7 +75,8 @@ def workload(name, rank, vocab):
         ctxs = np.clip(all_rng.lognormal(np.log(6000.0), 1.0, 64), 256, 131072 - 64).astype(int)
         sizes = all_rng.integers(1, 33, 64)
         specs = []
-        for i in shard_sequences([int(c) for c in ctxs], world)[rank]:   # whole sequences, KV positions balanced over the GPUs
+        # whole sequences, the estimated step time (rows, KV positions, sequences) balanced over the GPUs
+        for i in shard_sequences([int(c) for c in ctxs], world, rows=[int(n) for n in sizes])[rank]:
             n = int(sizes[i])
             chain_rows = max(1, (2 * n + 2) // 3)
             specs.append((int(ctxs[i]), chain_plus_branch(chain_rows, n - chain_rows), chain_rows - 1))
@@ -384,7 +385,7 @@ def device_timed_steps(ctx, dist, seqs, flags, steps, warmup):
 
 def churn64_sharded(lbm, dist, args, rank, local_rank, world):
     """The 64-sequence batch (contexts lognormal up to 128k, trees of 1-32 rows) sharded by sequence over the ranks (whole
-    sequences, KV positions balanced: shard_sequences), timed on the device: total work fixed, so strong scaling.  Each
+    sequences, estimated step time balanced: shard_sequences), timed on the device: total work fixed, so strong scaling.  Each
     rank reads the full weights for its share of the rows; no data-path collective."""
     cfg = model_for(lbm, "churn64", args.layers)
     seqs = workload("churn64", rank, cfg.vocab)
@@ -397,7 +398,7 @@ def churn64_sharded(lbm, dist, args, rank, local_rank, world):
     rows, kv_pos, accept = sum(len(q["tokens"]) for q in seqs), sum(q["pos"] for q in seqs), sum(q["accept"] for q in seqs)
     worst = dist.max(ms)
     per_rank = [dist.select(r, v) for r in range(world) for v in (rows, kv_pos, ms)]
-    return {"sequences": 64, "scaling": "strong", "sharding": "whole sequences, KV positions balanced (longest first onto the lightest GPU)",
+    return {"sequences": 64, "scaling": "strong", "sharding": "whole sequences, estimated step time balanced (rows, KV positions, sequences; costliest first onto the lightest GPU)",
             "steps": steps, "ms_per_step": worst, "tokens_per_s": dist.sum(rows) / (worst * 1e-3),
             "accepted_tokens_per_s": dist.sum(accept) / (worst * 1e-3),
             "per_rank": [{"rows": int(per_rank[3 * r]), "kv_positions": int(per_rank[3 * r + 1]), "ms_per_step": per_rank[3 * r + 2]}
@@ -700,16 +701,28 @@ def ctx_stage_bytes(lbm, n_seqs):
     return 16 + ((n_seqs * 24 + 15) // 16) * 16 + 3 * n_seqs * 32 * 4
 
 
-def shard_sequences(contexts, world):
+# What one sequence costs a GPU per step, from the one-GPU family times of the 64-sequence batch (1135 rows, 785k KV
+# positions, 64 sequences: GEMMs + norms 77 ms, attention 41 ms, DeltaNet 41 ms): milliseconds per tree row, per KV position
+# and per sequence.  Only the ratios matter.
+COST_PER_ROW, COST_PER_KV, COST_PER_SEQ = 77.0 / 1135, 41.0 / 785524, 41.0 / 64
+
+
+def shard_sequences(contexts, world, rows=None):
     """Sequence sharding for a many-sequence batch: sequences are independent (own KV pages, own state slot, own tree), so
-    each goes whole to one GPU; longest context first onto the GPU with the fewest KV positions so far (KV bytes are what
-    differs between sequences; the weights are replicated).  Returns, per rank, the indices of its sequences."""
-    order = sorted(range(len(contexts)), key=lambda i: (-contexts[i], i))
-    load, shards = [0] * world, [[] for _ in range(world)]
+    each goes whole to one GPU; the costliest first onto the GPU with the least load so far (the weights are replicated).
+    Without `rows` the load is the KV positions (what differs most between sequences); with the sequences' tree rows it is
+    the estimated step time: rows (GEMMs, norms), KV positions (attention) and a per-sequence term (DeltaNet).  Returns, per
+    rank, the indices of its sequences."""
+    if rows is None:
+        cost = [float(c) for c in contexts]
+    else:
+        cost = [COST_PER_ROW * r + COST_PER_KV * c + COST_PER_SEQ for c, r in zip(contexts, rows)]
+    order = sorted(range(len(contexts)), key=lambda i: (-cost[i], i))
+    load, shards = [0.0] * world, [[] for _ in range(world)]
     for i in order:
         r = min(range(world), key=lambda k: (load[k], k))
         shards[r].append(i)
-        load[r] += contexts[i]
+        load[r] += cost[i]
     return [sorted(s) for s in shards]
 
 

@@ -550,11 +550,12 @@ __global__ void __launch_bounds__(128, 1) fp4_tensor_peak_kernel(int iters, int 
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   uint8_t* sf = smem + kABytes + kBBytes;  // [3 groups][4 atoms][512]
   uint64_t* bar = reinterpret_cast<uint64_t*>(sf + 3 * kSfGroup);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + 1);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + 2);
   for (int i = threadIdx.x; i < kABytes + kBBytes; i += blockDim.x) smem[i] = uint8_t((i * 2654435761u) >> 24);  // every code
   for (int i = threadIdx.x; i < 3 * kSfGroup; i += blockDim.x) sf[i] = uint8_t(0x30 + ((i * 2654435761u) >> 29));  // 0.5 .. 0.94
   if (threadIdx.x == 0) {
     mbar_init(bar, 1);
+    mbar_init(bar + 1, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -579,7 +580,7 @@ __global__ void __launch_bounds__(128, 1) fp4_tensor_peak_kernel(int iters, int 
     for (int i = 0; i < iters; ++i) {
       // mode 1: the GEMM's twelve scale copies before every group, into the one scale region; mode 2: into two regions in turn
       const uint32_t so = mode == 2 ? uint32_t(i & 1) * 48u : 0u;
-      if (mode) {
+      if (mode == 1 || mode == 2) {
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
           sf_copy(tmem_base + so + kSfaCol + 4 * k, sf_desc(sfa + 512 * k));
@@ -594,6 +595,20 @@ __global__ void __launch_bounds__(128, 1) fp4_tensor_peak_kernel(int iters, int 
     }
     umma_commit(bar);
     if (!mbar_wait(bar, 0, nullptr)) dev_fail(err_flag, kDevWaitTmemFull);
+  } else if (threadIdx.x == 32 && mode == 3) {
+    // mode 3: the same twelve copies per group, but issued by a thread of another warp into a second scale region while
+    // thread 0 issues MMAs that read the first: do copies and MMAs from different issuers run side by side?
+    const uint32_t sfa = smem_u32(sf);
+    for (int i = 0; i < iters; ++i) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        sf_copy(tmem_base + 48 + kSfaCol + 4 * k, sf_desc(sfa + 512 * k));
+        sf_copy(tmem_base + 48 + kSfbCol + 8 * k, sf_desc(sfa + kSfGroup + 512 * k));
+        sf_copy(tmem_base + 48 + kSfbCol + 8 * k + 4, sf_desc(sfa + 2 * kSfGroup + 512 * k));
+      }
+    }
+    umma_commit(bar + 1);
+    if (!mbar_wait(bar + 1, 0, nullptr)) dev_fail(err_flag, kDevWaitTmemFull);
   }
   tc_fence_before();
   __syncthreads();
@@ -834,7 +849,7 @@ int fp4_quant_weight_launch(const __nv_bfloat16* w, int N, int K, uint8_t* q, ui
 }
 
 int fp4_tensor_peak_launch(int ctas, int iters, int mode, int* err_flag, cudaStream_t stream) {
-  constexpr int smem = kABytes + kBBytes + 3 * kSfGroup + 1024 + 64;
+  constexpr int smem = kABytes + kBBytes + 3 * kSfGroup + 1024 + 128;
   static std::once_flag once;
   static cudaError_t attr = cudaSuccess;
   std::call_once(once, [] { attr = cudaFuncSetAttribute(fp4_tensor_peak_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); });
