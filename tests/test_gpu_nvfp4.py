@@ -205,3 +205,27 @@ def test_two_cta_form_gives_the_same_bits(gpu, lb, lo, M, N, K):
     assert np.array_equal(one[2][0], two[2][0]) and np.array_equal(one[2][1], two[2][1])
     ref = 0.11 * (dequant64(lo, xq, xs) @ dequant64(lo, uq, us).T)
     assert np.abs(two[1] - ref).max() <= GEMM_TOL * np.sqrt((ref ** 2).mean()) + 1e-6
+
+
+def test_chunk_ffn_layer_at_the_27b_width_on_sampled_rows(gpu, lb, lo):
+    """One layer of the chunk's stack at the named shape (4096 rows, hidden 5120, FFN 17408).  Every operation of the stack is
+    row-wise or a GEMM whose rows are independent, so the oracle chain on a handful of rows checks those rows of the full pass."""
+    H, I, rows = 5120, 17408, 4096
+    ffn = lb.Nvfp4Ffn(1, H, I, rows, seed=21)
+    rng = np.random.default_rng(22)
+    h0 = rng.standard_normal((rows, H)).astype(np.float32)
+    got = ffn.forward(h0)
+    L = ffn.read_layer(0)
+    pick = np.array([0, 1, 127, 128, 2049, rows - 1])
+    h = h0[pick]
+    n = lo.rmsnorm_rows(h, L["norm"], 1e-6)
+    xq, xs = lo.nvfp4_quant_act(n, L["in_scale"])
+    g = lo.nvfp4_gemm(xq, xs, *L["gate"], L["in_scale"] * L["s_gate"])
+    u = lo.nvfp4_gemm(xq, xs, *L["up"], L["in_scale"] * L["s_up"])
+    mq, ms = lo.nvfp4_quant_act(g, L["mid_scale"], up=u)
+    want = lo.nvfp4_gemm(mq, ms, *L["down"], L["mid_scale"] * L["s_down"], y=h, accumulate=True)
+    assert np.isfinite(got).all()
+    for i, r in enumerate(pick):
+        delta = np.sqrt(((want[i] - h0[r]) ** 2).sum())
+        assert delta > 0
+        assert np.sqrt(((got[r] - want[i]) ** 2).sum()) <= FFN_TOL * delta, "row %d" % r
