@@ -229,3 +229,20 @@ def test_chunk_ffn_layer_at_the_27b_width_on_sampled_rows(gpu, lb, lo):
         delta = np.sqrt(((want[i] - h0[r]) ** 2).sum())
         assert delta > 0
         assert np.sqrt(((got[r] - want[i]) ** 2).sum()) <= FFN_TOL * delta, "row %d" % r
+
+
+def test_gemm_edge_cases(gpu, lb, lo):
+    """All-zero activations (block scale 0) give exact zeros and leave an accumulated-into output as it was; 8192 rows (more than
+    one pass of the persistent grid over the row tiles) agree with the same rows computed 300 at a time."""
+    rng = np.random.default_rng(31)
+    N, K = 256, 512
+    wq, ws = random_operand(rng, N, K)
+    xq, xs = lo.nvfp4_quant_act(np.zeros((40, K), np.float32), 0.05)
+    assert not xs.any() and not xq.any()
+    assert not lb.prefill_gemm_nvfp4(xq, xs, wq, ws, 0.5).any()
+    y0 = rng.standard_normal((40, N)).astype(np.float32)
+    assert np.array_equal(lb.prefill_gemm_nvfp4(xq, xs, wq, ws, 0.5, y=y0, accumulate=True), y0)
+    xq, xs = random_operand(rng, 8192, K, 0x30, 0x3c)
+    whole = lb.prefill_gemm_nvfp4(xq, xs, wq, ws, 0.01)
+    for r0 in (0, 4000, 7892):
+        assert np.array_equal(lb.prefill_gemm_nvfp4(xq[r0:r0 + 300], xs[r0:r0 + 300], wq, ws, 0.01), whole[r0:r0 + 300])

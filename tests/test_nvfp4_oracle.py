@@ -129,3 +129,33 @@ def test_gemm_and_dequant(lo):
     assert np.abs(got - want).max() <= 1e-6 * np.abs(want).max()
     plain = lo.nvfp4_gemm(xq, xs, wq, ws, 0.37)
     assert np.abs(plain - 0.37 * (xa @ wa.T)).max() <= 1e-6 * np.abs(want).max()
+
+
+def test_entry_points_refuse_bad_shapes_before_touching_a_device(lb):
+    """Argument errors come back as LING_B200_ERR_ARG with nothing launched: N and K must be multiples of 128 (the
+    reference's rule, prefill_gemm.cu:596), K of 16 for the quantizers, scales positive; M = 0 is an empty success."""
+    import ctypes as C
+    L = lb.lib()
+    b = (C.c_ubyte * 64)()
+    f = (C.c_float * 64)()
+    h = (C.c_uint16 * 64)()
+    s2 = C.c_float()
+    assert L.ling_b200_quantize_nvfp4_host(0, h, 2, 24, b, b, C.byref(s2)) == lb.ERR_ARG          # K % 16
+    assert L.ling_b200_quant_act_nvfp4_host(0, f, None, 1, 40, C.c_float(1.0), b, b) == lb.ERR_ARG
+    assert L.ling_b200_quant_act_nvfp4_host(0, f, None, 1, 32, C.c_float(0.0), b, b) == lb.ERR_ARG  # input_scale
+    assert L.ling_b200_rmsnorm_quant_nvfp4_host(0, f, h, None, 1, 24, C.c_float(1e-6), C.c_float(1.0), b, b) == lb.ERR_ARG
+    gemm = L.ling_b200_prefill_gemm_nvfp4_host
+    assert gemm(0, b, b, 1, b, b, C.c_float(1.0), f, 192, 192, 128, 0) == lb.ERR_ARG      # N % 128
+    assert gemm(0, b, b, 1, b, b, C.c_float(1.0), f, 128, 128, 192, 0) == lb.ERR_ARG      # K % 128
+    assert gemm(0, b, b, 1, b, b, C.c_float(1.0), f, 64, 128, 128, 0) == lb.ERR_ARG       # ldy < N
+    assert gemm(0, b, b, 0, b, b, C.c_float(1.0), f, 128, 128, 128, 0) == lb.OK           # no rows: nothing to do
+    sw = L.ling_b200_prefill_swiglu_nvfp4_host
+    assert sw(0, b, b, 1, b, b, C.c_float(1.0), b, b, C.c_float(1.0), 100, 128, C.c_float(1.0), b, b) == lb.ERR_ARG
+    assert sw(0, b, b, 1, b, b, C.c_float(1.0), b, b, C.c_float(1.0), 128, 128, C.c_float(0.0), b, b) == lb.ERR_ARG
+    out = C.c_void_p()
+    L.ling_b200_nvfp4_ffn_create.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_uint64, C.POINTER(C.c_void_p)]
+    assert L.ling_b200_nvfp4_ffn_create(0, 1, 100, 512, 8, 0, C.byref(out)) == lb.ERR_ARG   # hidden % 256
+    assert L.ling_b200_nvfp4_ffn_create(0, 0, 256, 512, 8, 0, C.byref(out)) == lb.ERR_ARG   # no layers
+    tf = C.c_float()
+    assert L.ling_b200_fp4_tensor_peak(0, 0, 0, C.byref(tf), None) == lb.ERR_ARG
+    assert L.ling_b200_fp4_tensor_peak(0, 10, 7, C.byref(tf), None) == lb.ERR_ARG
