@@ -19,9 +19,18 @@ KV compaction and DeltaNet commit.  Rank 0 prints ONE JSON line.
              events on the launching stream around five passes (average launch duration = that time / 257), against the
              measured HBM copy bandwidth; per_launch_events = the same launches in one eager replay with an event pair
              around EACH launch (every launch then carries its own ramp-up and an event gap: a lower bound)
+             roofline.frac (0.87) is the GEMM chain's share of the copy bandwidth, NOT the step's: the step's own figure is
+             hbm_fraction_weights_plus_kv = (weight bytes + KV bytes) / step time / measured copy bandwidth (0.54), the
+             north star's fraction, printed beside it
   cpu_baseline the scalar C++ restatement of the same step (oracle/, test infrastructure) timed on this box's host
              cores on a bounded sample (one DeltaNet layer, one attention layer, a slice of the LM head), scaled by the
              layer counts; a reported baseline, not a target
+
+Other workloads (one JSON line each, same keys): --workload ragged4 (4 sequences, 74 rows), churn64 (64 sequences sharded over
+the ranks, ~10 % completions and admissions per step through the page pool), served64 (the same 64-sequence load produced by
+the scheduler loop: ling-engine_b200/ling_serve_headless), mixed (a 4096-row prefill chunk through the NVFP4 feed-forward stack
+beside an 8-sequence verify step; roofline against the NVFP4 tensor rate measured in the same run), toy.  --micro gemm |
+nvfp4 | nvfp4-swiglu times one kernel alone on resident operands (the small cases the profiler captures).
 
 Inputs are synthetic (seeded): they stand in for the reference's private replay workload, whose shapes they take.
 Weights are 26.4 GB, far larger than the 126 MB L2, so consecutive steps cannot hit in L2 (no flush between steps).
