@@ -11,8 +11,9 @@
 //   warps 2-17 epilogue (four per TMEM lane quarter, a quarter of the columns each): tcgen05.ld of the tile; plain form: alpha * acc to y (or added to it); fused form: the gate and up
 //            halves of the tile become silu(alpha * gate) * (alpha2 * up), rounded to BF16 and written as the next GEMM's
 //            NVFP4 operand (16 features = one block scale, all in one thread).
-// TMEM: columns 0-255 accumulator, 256-271 activation scales of the stage, 272-303 weight scales.  One accumulator: the
-// epilogue of a tile and the MMAs of the next do not overlap (the producer still runs ahead by the pipeline's depth).
+// TMEM: columns 0-255 accumulator, 256-271 activation scales of the stage, 272-303 weight scales.  One accumulator: an
+// epilogue warp reads its columns into registers, hands the accumulator back, and does its arithmetic and stores while
+// the next tile's MMAs run (what stays exposed is the TMEM read).
 // Every wait is bounded; a wait that runs out records a code in the device error word and the CTA unwinds.
 #include "nvfp4.h"
 
@@ -114,51 +115,60 @@ struct GemmArgs {
 };
 
 // One epilogue warp's part of a finished tile: TMEM lanes = token rows (this thread's row), columns = the tile's weight rows;
-// `part` selects which of the tile's eight column groups this warp drains (8 / kEpiPerQuarter of them).
-template <bool SWIGLU>
-__device__ __forceinline__ void drain_tile(const GemmArgs& p, uint32_t taddr, int row, int tn, int part) {
+// `part` selects which of the tile's eight column groups this warp drains (8 / (kEpiWarps / 4) of them).  The warp first
+// reads ALL of its columns into registers and calls release() -- the accumulator is then free for the next tile's MMAs --
+// and only then does the arithmetic and the stores, which so run under the next tile's main loop.
+template <bool SWIGLU, typename Release>
+__device__ __forceinline__ void drain_tile(const GemmArgs& p, uint32_t taddr, int row, int tn, int part, Release release) {
   constexpr int kGroups = 8 / (kEpiWarps / 4);  // column groups per warp
   if constexpr (SWIGLU) {
-  const int f0 = tn * 128;  // the tile's first feature: columns 0-127 its gate products, 128-255 its up products
-#pragma unroll 1
-  for (int b = kGroups * part; b < kGroups * part + kGroups; ++b) {
-    uint32_t g[16], u[16];
-    tmem_ld16(taddr + 16 * b, g);
-    tmem_ld16(taddr + 128 + 16 * b, u);
-    tmem_ld_wait();
-    float v[16];
+    const int f0 = tn * 128;  // the tile's first feature: columns 0-127 its gate products, 128-255 its up products
+    uint32_t g[kGroups][16], u[kGroups][16];
 #pragma unroll
-    for (int j = 0; j < 16; ++j) v[j] = bf16_round(silu(__uint_as_float(g[j]) * p.alpha) * (__uint_as_float(u[j]) * p.alpha2));
-    uint2 codes;
-    const uint8_t sc = encode_block(v, p.gscale_out, codes);
-    if (row < p.M) {
-      const int f = f0 + 16 * b;
-      *reinterpret_cast<uint2*>(p.q_out + size_t(row) * (p.N / 2) + f / 2) = codes;
-      p.sf_out[p.sf_out_tiled ? fp4_sf_offset(row, f / 16, p.out_atoms) : size_t(row) * (p.N / 16) + f / 16] = sc;
+    for (int i = 0; i < kGroups; ++i) {
+      tmem_ld16(taddr + 16 * (kGroups * part + i), g[i]);
+      tmem_ld16(taddr + 128 + 16 * (kGroups * part + i), u[i]);
     }
-  }
-} else {
-  const int n0 = tn * kFp4TileN;
-#pragma unroll 1
-  for (int c = kGroups * part; c < kGroups * part + kGroups; ++c) {
-    uint32_t v[32];
-    tmem_ld32(taddr + 32 * c, v);
     tmem_ld_wait();
-    if (row < p.M && n0 + 32 * c < p.N) {
-      float4* dst = reinterpret_cast<float4*>(p.y + size_t(row) * p.ldy + n0 + 32 * c);
+    release();
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        float4 o = make_float4(__uint_as_float(v[4 * j]) * p.alpha, __uint_as_float(v[4 * j + 1]) * p.alpha,
-                               __uint_as_float(v[4 * j + 2]) * p.alpha, __uint_as_float(v[4 * j + 3]) * p.alpha);
-        if (p.accumulate) {
-          const float4 old = dst[j];
-          o.x += old.x, o.y += old.y, o.z += old.z, o.w += old.w;
+    for (int i = 0; i < kGroups; ++i) {
+      float v[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) v[j] = bf16_round(silu(__uint_as_float(g[i][j]) * p.alpha) * (__uint_as_float(u[i][j]) * p.alpha2));
+      uint2 codes;
+      const uint8_t sc = encode_block(v, p.gscale_out, codes);
+      if (row < p.M) {
+        const int f = f0 + 16 * (kGroups * part + i);
+        *reinterpret_cast<uint2*>(p.q_out + size_t(row) * (p.N / 2) + f / 2) = codes;
+        p.sf_out[p.sf_out_tiled ? fp4_sf_offset(row, f / 16, p.out_atoms) : size_t(row) * (p.N / 16) + f / 16] = sc;
+      }
+    }
+  } else {
+    const int n0 = tn * kFp4TileN;
+    uint32_t v[kGroups][32];
+#pragma unroll
+    for (int i = 0; i < kGroups; ++i) tmem_ld32(taddr + 32 * (kGroups * part + i), v[i]);
+    tmem_ld_wait();
+    release();
+#pragma unroll
+    for (int i = 0; i < kGroups; ++i) {
+      const int c = kGroups * part + i;
+      if (row < p.M && n0 + 32 * c < p.N) {
+        float4* dst = reinterpret_cast<float4*>(p.y + size_t(row) * p.ldy + n0 + 32 * c);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          float4 o = make_float4(__uint_as_float(v[i][4 * j]) * p.alpha, __uint_as_float(v[i][4 * j + 1]) * p.alpha,
+                                 __uint_as_float(v[i][4 * j + 2]) * p.alpha, __uint_as_float(v[i][4 * j + 3]) * p.alpha);
+          if (p.accumulate) {
+            const float4 old = dst[j];
+            o.x += old.x, o.y += old.y, o.z += old.z, o.w += old.w;
+          }
+          dst[j] = o;
         }
-        dst[j] = o;
       }
     }
   }
-}
 }
 
 template <bool SWIGLU>
@@ -299,10 +309,11 @@ __global__ void __launch_bounds__(kThreads, 1)
       tc_fence_after();
       const int row = tm * kFp4TileM + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16);
-      drain_tile<SWIGLU>(p, taddr, row, tn, part);
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(tmem_empty);
+      drain_tile<SWIGLU>(p, taddr, row, tn, part, [&] {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tmem_empty);
+      });
       busy += clock64() - c0;
     }
     if (p.stats && warp == 2 && lane == 0) atomicAdd(p.stats + 2, (unsigned long long)busy);
@@ -522,10 +533,11 @@ __global__ void __launch_bounds__(kThreads, 1)
       tc_fence_after();
       const int row = tm * 256 + int(rank) * 128 + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16);
-      drain_tile<SWIGLU>(p, taddr, row, tn, part);
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(empty_bar);
+      drain_tile<SWIGLU>(p, taddr, row, tn, part, [&] {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(empty_bar);
+      });
       busy += clock64() - c0;
     }
     if (p.stats && leader && warp == 2 && lane == 0) atomicAdd(p.stats + 2, (unsigned long long)busy);
