@@ -301,9 +301,11 @@ int ling_b200_nvfp4_pair_mode(int mode);
 int ling_b200_nvfp4_gemm_bench(int device, int M, int N, int K, int fused, int iters, float* ms_per_launch, double* cycle_shares);
 
 /* The NVFP4 tensor pipe's dense rate on this GPU, measured like ling_b200_fp8_tensor_peak: tcgen05.mma kind::mxf4nvf4.block_scale
- * (128 x 256 x 64, block scales of 16 in tensor memory) on resident operands.  mode 0 is the denominator for the NVFP4 GEMMs; mode 1 adds the GEMM's
- * twelve scale copies (tcgen05.cp, shared -> tensor memory) before every group of four MMAs, into the one scale region the MMAs
- * read; mode 2 alternates between two scale regions: what the copies cost the pipe. */
+ * (128 x 256 x 64, block scales of 16 in tensor memory) on resident operands.  mode 0 is the denominator for the NVFP4 GEMMs.
+ * The other modes price the GEMM's scale copies (tcgen05.cp, shared -> tensor memory, 48 columns per group of four MMAs):
+ * 1 = twelve 32x128b.warpx4 copies before every group into the region the MMAs read; 2 = into two regions in turn; 3 = issued
+ * by a thread of another warp into a region the running MMAs do not read; 4 = the same 48 columns written by six 128x256b
+ * copies.  All four cost the pipe the same third: the price is per column written, whoever issues it and in whatever shape. */
 int ling_b200_fp4_tensor_peak(int device, int iters, int mode, float* tflops, float* ms);
 
 /* The prefill chunk's feed-forward stack held on the device: per layer h += down(swiglu(gate, up)(norm(h))), the three

@@ -592,6 +592,13 @@ __global__ void __launch_bounds__(128, 1) fp4_tensor_peak_kernel(int iters, int 
     for (int i = 0; i < iters; ++i) {
       // mode 1: the GEMM's twelve scale copies before every group, into the one scale region; mode 2: into two regions in turn
       const uint32_t so = mode == 2 ? uint32_t(i & 1) * 48u : 0u;
+      if (mode == 4) {  // the same 48 scale columns written by six 128-lane x 256-bit copies (a source replicated in shared memory)
+#pragma unroll
+        for (int k = 0; k < 6; ++k) {
+          uint64_t dsc = uint64_t(((st + 4096u * k) & 0x3FFFFu) >> 4) | (uint64_t(128 >> 4) << 16) | (uint64_t(256 >> 4) << 32) | (uint64_t(1) << 46);
+          asm volatile("tcgen05.cp.cta_group::1.128x256b [%0], %1;" ::"r"(tmem_base + kSfaCol + 8 * k), "l"(dsc) : "memory");
+        }
+      }
       if (mode == 1 || mode == 2) {
 #pragma unroll
         for (int k = 0; k < 4; ++k) {

@@ -77,7 +77,8 @@ int fp4_rmsnorm_quant_launch(const float* x, const __nv_bfloat16* w, float* out,
 int fp4_quant_weight_launch(const __nv_bfloat16* w, int N, int K, uint8_t* q, uint8_t* sf, bool tiled, float* scale2,
                             unsigned* amax_bits, cudaStream_t stream);
 // `ctas` CTAs each issue `iters` groups of four 128 x 256 x 64 NVFP4 MMAs on resident operands (the tensor pipe's rate).
-// mode 0: MMAs only; 1: with the GEMM's twelve scale copies per group into one TMEM region; 2: into two regions in turn.
+// mode 0: MMAs only; 1: with the GEMM's twelve scale copies per group into one TMEM region; 2: into two regions in turn; 3: the
+// copies issued by a second thread into a region the MMAs do not read; 4: the same 48 columns by six 128x256b copies.
 int fp4_tensor_peak_launch(int ctas, int iters, int mode, int* err_flag, cudaStream_t stream);
 // Row-major block scales [rows][K / 16] <-> the layout above.
 int fp4_sf_tile_launch(const uint8_t* rowmajor, uint8_t* tiled, int rows, int K, cudaStream_t stream);

@@ -291,7 +291,7 @@ int ling_b200_nvfp4_gemm_bench(int device, int M, int N, int K, int fused, int i
 // The NVFP4 tensor pipe's dense rate (fp4_tensor_peak_kernel): one CTA per SM, `iters` MMA groups each, timed with CUDA
 // events after a warm-up launch; TFLOP/s = 2 * 128 * 256 * 256 * iters * SMs / time.
 int ling_b200_fp4_tensor_peak(int device, int iters, int mode, float* tflops, float* ms) {
-  if (!tflops || iters < 1 || iters > (1 << 22) || mode < 0 || mode > 3) {
+  if (!tflops || iters < 1 || iters > (1 << 22) || mode < 0 || mode > 4) {
     set_error("fp4_tensor_peak: bad argument");
     return LING_B200_ERR_ARG;
   }
