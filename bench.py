@@ -710,28 +710,63 @@ def ctx_stage_bytes(lbm, n_seqs):
     return 16 + ((n_seqs * 24 + 15) // 16) * 16 + 3 * n_seqs * 32 * 4
 
 
-# What one sequence costs a GPU per step, from the one-GPU family times of the 64-sequence batch (1135 rows, 785k KV
-# positions, 64 sequences: GEMMs + norms 77 ms, attention 41 ms, DeltaNet 41 ms): milliseconds per tree row, per KV position
-# and per sequence.  Only the ratios matter.
-COST_PER_ROW, COST_PER_KV, COST_PER_SEQ = 77.0 / 1135, 41.0 / 785524, 41.0 / 64
+# What a GPU's share of a many-sequence step costs, from the one-GPU family times of the 64-sequence batch (1135 rows = nine
+# 128-row token tiles, 785k KV positions, 64 sequences: GEMMs + head 62.9 ms, norms 13.6, attention 41.1, DeltaNet 40.6):
+# milliseconds per token tile (the GEMMs run whole 128-row tiles: 260 rows cost what 384 do), per tree row (norms and the
+# DeltaNet paths), per KV position (attention) and per sequence.  Only the ratios matter.
+COST_PER_TILE, COST_PER_ROW, COST_PER_KV, COST_PER_SEQ = 62.9 / 9, (13.6 + 20.3) / 1135, 41.1 / 785524, 20.3 / 64
+
+
+def shard_cost(contexts, rows, members):
+    """Estimated step time of the GPU that gets the sequences `members`."""
+    r = sum(rows[i] for i in members)
+    return (COST_PER_TILE * -(-r // 128) + COST_PER_ROW * r + COST_PER_KV * sum(contexts[i] for i in members)
+            + COST_PER_SEQ * len(members))
 
 
 def shard_sequences(contexts, world, rows=None):
     """Sequence sharding for a many-sequence batch: sequences are independent (own KV pages, own state slot, own tree), so
-    each goes whole to one GPU; the costliest first onto the GPU with the least load so far (the weights are replicated).
-    Without `rows` the load is the KV positions (what differs most between sequences); with the sequences' tree rows it is
-    the estimated step time: rows (GEMMs, norms), KV positions (attention) and a per-sequence term (DeltaNet).  Returns, per
-    rank, the indices of its sequences."""
+    each goes whole to one GPU (the weights are replicated).  Without `rows`: longest context first onto the GPU with the
+    fewest KV positions so far.  With the sequences' tree rows the estimated step time (shard_cost) is balanced instead:
+    costliest sequence first onto the GPU whose estimate grows least, then single moves and swaps between the slowest GPU
+    and the others while they lower the slowest estimate.  Returns, per rank, the indices of its sequences."""
+    n = len(contexts)
+    shards = [[] for _ in range(world)]
     if rows is None:
-        cost = [float(c) for c in contexts]
-    else:
-        cost = [COST_PER_ROW * r + COST_PER_KV * c + COST_PER_SEQ for c, r in zip(contexts, rows)]
-    order = sorted(range(len(contexts)), key=lambda i: (-cost[i], i))
-    load, shards = [0.0] * world, [[] for _ in range(world)]
-    for i in order:
-        r = min(range(world), key=lambda k: (load[k], k))
+        load = [0] * world
+        for i in sorted(range(n), key=lambda i: (-contexts[i], i)):
+            r = min(range(world), key=lambda k: (load[k], k))
+            shards[r].append(i)
+            load[r] += contexts[i]
+        return [sorted(s) for s in shards]
+    cost = lambda m: shard_cost(contexts, rows, m)
+    for i in sorted(range(n), key=lambda i: (-cost([i]), i)):
+        r = min(range(world), key=lambda k: (cost(shards[k] + [i]), k))
         shards[r].append(i)
-        load[r] += cost[i]
+    for _ in range(200):   # local search on the slowest GPU
+        costs = [cost(m) for m in shards]
+        worst = max(range(world), key=lambda k: (costs[k], -k))
+        best = None
+        for k in range(world):
+            if k == worst:
+                continue
+            for i in shards[worst]:
+                moved = max(cost([x for x in shards[worst] if x != i]), cost(shards[k] + [i]))
+                cand = [(moved, i, None)]
+                for j in shards[k]:
+                    cand.append((max(cost([x for x in shards[worst] if x != i] + [j]), cost([x for x in shards[k] if x != j] + [i])), i, j))
+                for c, a, b_ in cand:
+                    others = max([costs[q] for q in range(world) if q not in (worst, k)] or [0.0])
+                    if max(c, others) < costs[worst] - 1e-9 and (best is None or max(c, others) < best[0]):
+                        best = (max(c, others), k, a, b_)
+        if best is None:
+            break
+        _, k, a, b_ = best
+        shards[worst].remove(a)
+        shards[k].append(a)
+        if b_ is not None:
+            shards[k].remove(b_)
+            shards[worst].append(b_)
     return [sorted(s) for s in shards]
 
 
