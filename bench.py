@@ -710,11 +710,11 @@ def ctx_stage_bytes(lbm, n_seqs):
     return 16 + ((n_seqs * 24 + 15) // 16) * 16 + 3 * n_seqs * 32 * 4
 
 
-# What a GPU's share of a many-sequence step costs, from the one-GPU family times of the 64-sequence batch (1135 rows = nine
-# 128-row token tiles, 785k KV positions, 64 sequences: GEMMs + head 62.9 ms, norms 13.6, attention 41.1, DeltaNet 40.6):
-# milliseconds per token tile (the GEMMs run whole 128-row tiles: 260 rows cost what 384 do), per tree row (norms and the
-# DeltaNet paths), per KV position (attention) and per sequence.  Only the ratios matter.
-COST_PER_TILE, COST_PER_ROW, COST_PER_KV, COST_PER_SEQ = 62.9 / 9, (13.6 + 20.3) / 1135, 41.1 / 785524, 20.3 / 64
+# What a GPU's share of a many-sequence step costs, in milliseconds: per 128-row token tile (the GEMMs run whole tiles: 260
+# rows cost what 384 do), per tree row (norms, the DeltaNet paths), per KV position (attention) and per sequence.  Fitted to
+# the per-rank step times of the 64-sequence batch on four GPUs (twelve shares of 233-328 rows, 104k-290k KV positions,
+# 14-18 sequences, 36.9-51.2 ms); only the ratios matter.
+COST_PER_TILE, COST_PER_ROW, COST_PER_KV, COST_PER_SEQ = 10.0, 0.03, 5.0e-5, 0.3
 
 
 def shard_cost(contexts, rows, members):
