@@ -710,17 +710,17 @@ def ctx_stage_bytes(lbm, n_seqs):
     return 16 + ((n_seqs * 24 + 15) // 16) * 16 + 3 * n_seqs * 32 * 4
 
 
-# What a GPU's share of a many-sequence step costs, in milliseconds: per 128-row token tile (the GEMMs run whole tiles: 260
-# rows cost what 384 do), per tree row (norms, the DeltaNet paths), per KV position (attention) and per sequence.  Fitted to
-# the per-rank step times of the 64-sequence batch on four GPUs (twelve shares of 233-328 rows, 104k-290k KV positions,
-# 14-18 sequences, 36.9-51.2 ms); only the ratios matter.
-COST_PER_TILE, COST_PER_ROW, COST_PER_KV, COST_PER_SEQ = 10.0, 0.03, 5.0e-5, 0.3
+# What a GPU's share of a many-sequence step costs, in milliseconds: per 32 tree rows (the step runs in capacity classes of 32
+# rows and the GEMMs pick the token tile with the least padding, so their time follows the padded rows: 63 ms for 1152),
+# per tree row (norms, the DeltaNet paths), per KV position (attention) and per sequence; the last three fitted to the
+# per-rank step times of the 64-sequence batch on four GPUs.  Only the ratios matter.
+COST_PER_32_ROWS, COST_PER_ROW, COST_PER_KV, COST_PER_SEQ = 63.0 / 36, 0.03, 5.0e-5, 0.3
 
 
 def shard_cost(contexts, rows, members):
     """Estimated step time of the GPU that gets the sequences `members`."""
     r = sum(rows[i] for i in members)
-    return (COST_PER_TILE * -(-r // 128) + COST_PER_ROW * r + COST_PER_KV * sum(contexts[i] for i in members)
+    return (COST_PER_32_ROWS * -(-r // 32) + COST_PER_ROW * r + COST_PER_KV * sum(contexts[i] for i in members)
             + COST_PER_SEQ * len(members))
 
 

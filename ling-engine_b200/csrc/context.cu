@@ -146,7 +146,10 @@ struct ling_b200_ctx {
 
 namespace {
 
-int row_class(int M) { return M <= 128 ? token_tile(M) : round_up(M, 128); }
+// The capacity class a step of M packed rows runs in (one graph per class and flag set; grids and the GEMMs' token tiles are
+// sized for it): the token tile up to 128 rows, multiples of 32 beyond -- fine enough for the GEMM to pick the tile size with
+// the least padding (token_tile), at most 64 classes in all.
+int row_class(int M) { return M <= 128 ? token_tile(M) : round_up(M, 32); }
 
 struct Timed {
   ling_b200_ctx* c;

@@ -622,7 +622,17 @@ int wait_probe_launch(unsigned long long limit_ns, int* err_flag, unsigned long 
   return LING_B200_OK;
 }
 
-int token_tile(int M) { return M <= 32 ? 32 : M <= 64 ? 64 : M <= 96 ? 96 : 128; }
+// Up to 128 rows: the smallest tile that holds them.  Beyond: the GEMM's time is its padded rows (tiles x tile rows; measured
+// per row 0.336 us at 96, 0.338 at 128, 0.344 at 64 on the gate|up shape), so the tile with the least padding, ties in
+// that order: 142 rows run as 2 x 96 (68 us) rather than 2 x 128 (88), 260 as 3 x 96 (99 vs 130), 300 as 5 x 64 (111 vs 130).
+// The result does not depend on the choice (a row's arithmetic is the same in every tile size).
+int token_tile(int M) {
+  if (M <= 128) return M <= 32 ? 32 : M <= 64 ? 64 : M <= 96 ? 96 : 128;
+  int best = 96;
+  for (int nt : {128, 64})
+    if (round_up(M, nt) < round_up(M, best)) best = nt;
+  return best;
+}
 
 int choose_splits(int N_pad, int KB, int sm_count) {
   const int tiles = N_pad / kTileN;
@@ -651,7 +661,7 @@ int gemm_launch(const GemmCall& c, cudaStream_t stream) {
                           W.K_pad, W.KB, X.rows_alloc, h));
     return LING_B200_OK;
   }
-  switch (token_tile(c.M)) {
+  switch (c.force_tile > 0 ? c.force_tile : token_tile(c.M)) {
     case 32: return launch_tc<32>(c, stream);
     case 64: return launch_tc<64>(c, stream);
     case 96: return launch_tc<96>(c, stream);

@@ -50,6 +50,7 @@ struct GemmCall {
   size_t split_stride = 0;  // floats between split planes
   const HeadEpilogue* head = nullptr;
   int impl = 0;             // 0 tcgen05, 1 CUDA cores
+  int force_tile = 0;       // 0: token_tile(M); else the token tile to use (32, 64, 96 or 128): results do not depend on it
   int* err_flag = nullptr;
   unsigned long long* timeline = nullptr;  // four stamps of this launch (debugging aid), or nullptr
 };
@@ -72,7 +73,8 @@ int tensor_peak_launch(int ctas, int iters, int* err_flag, cudaStream_t stream);
 // One CTA waits, with the kernels' bounded wait and the given limit, on a barrier that nobody arrives at: records
 // kDevWaitFull in *err_flag and the nanoseconds it waited, and returns.
 int wait_probe_launch(unsigned long long limit_ns, int* err_flag, unsigned long long* waited_ns, cudaStream_t stream);
-// Token rows per MMA (the N of the instruction) used for M rows: 32, 64, 96 or 128.
+// Token rows per MMA (the N of the instruction) used for M rows: 32, 64, 96 or 128 (beyond 128 rows: the one with the least
+// padding over ceil(M / tile) tiles).
 int token_tile(int M);
 
 }  // namespace lb

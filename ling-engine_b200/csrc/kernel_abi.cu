@@ -101,7 +101,9 @@ int ling_b200_gemm_fp8_bench(int device, int impl, int splits, int M, int N, int
   GemmCall c;
   c.W = &g.W, c.X = &g.X, c.M = M, c.out = g.out, c.ld = g.W.N_pad;
   c.split_stride = size_t(g.X.rows_alloc) * g.W.N_pad;
-  c.impl = impl == 2 ? 0 : impl, c.err_flag = g.err;
+  c.impl = (impl & 0xff) == 2 ? 0 : (impl & 0xff), c.err_flag = g.err;
+  c.force_tile = impl >> 8;  // (impl | tile << 8: the token tile forced, for tile-size comparisons)
+  impl &= 0xff;
   cudaEvent_t a, b;
   LB_CUDA(cudaEventCreate(&a));
   LB_CUDA(cudaEventCreate(&b));
