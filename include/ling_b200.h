@@ -475,6 +475,12 @@ int ling_b200_format_step(double t, long pass, const char* kind, size_t turn, co
 
 /* Device memory helpers for callers without a CUDA binding (tests): device count, and name of device 0. */
 int ling_b200_device_count(void);
+/* How a step of `rows` packed rows runs: the capacity class its graph is captured for (the token tile up to 128 rows,
+ * multiples of 32 beyond) and the token rows per MMA tile the weight GEMMs use for a class of that many rows (32, 64, 96 or
+ * 128: the smallest that holds up to 128 rows; beyond, the one with the least padding).  Results do not depend on either.
+ * No counterpart in the reference, whose rows path takes at most 32 rows (kernels.cuh:107). */
+int ling_b200_row_class(int rows);
+int ling_b200_token_tile(int rows);
 int ling_b200_device_name(int device, char* buf, int len);
 
 #ifdef __cplusplus

@@ -549,6 +549,8 @@ const char* ling_b200_last_error(void) { return g_error.c_str(); }
 void ling_b200_set_pdl(int on) { set_pdl(on != 0); }
 int ling_b200_pdl_enabled(void) { return pdl_enabled() ? 1 : 0; }
 int ling_b200_abi_version(void) { return 1; }
+int ling_b200_token_tile(int rows) { return rows < 1 ? 0 : token_tile(rows); }
+int ling_b200_row_class(int rows) { return rows < 1 ? 0 : row_class(rows); }
 
 int ling_b200_device_count(void) {
   int n = 0;

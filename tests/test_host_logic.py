@@ -336,3 +336,21 @@ def test_reclaim_and_refusal_match_golden(lb, lo):
             ret = ref.ref_kv_reclaim(c["need0"], c["have0"], arr(sizes), arr(c["dneed"]), arr(c["dhave"]), n_kept, c["need_kept"],
                                      c["reach_kept"], n_source, c["need_all"], c["reach_all"], c["must"], ev)
             assert run_reclaim(lib, c) == (ret, list(ev)[:len(sizes)])
+
+
+def test_row_classes_and_token_tiles(lb):
+    """Steps run in capacity classes and the GEMMs in token tiles of 32, 64, 96 or 128 rows: up to 128 rows the smallest tile that
+    holds them (the class is that tile); beyond, classes of 32 rows and the tile with the least padding, never more padding
+    than 128-row tiles would have."""
+    L = lb.lib()
+    assert [L.ling_b200_token_tile(m) for m in (1, 32, 33, 64, 65, 96, 97, 128)] == [32, 32, 64, 64, 96, 96, 128, 128]
+    assert [L.ling_b200_row_class(m) for m in (1, 24, 33, 74, 100, 128, 129, 142, 260, 1135, 2048)] == \
+        [32, 32, 64, 96, 128, 128, 160, 160, 288, 1152, 2048]
+    assert L.ling_b200_token_tile(0) == 0 and L.ling_b200_row_class(-3) == 0
+    for m in range(129, 2049):
+        cls = L.ling_b200_row_class(m)
+        nt = L.ling_b200_token_tile(cls)
+        assert cls % 32 == 0 and m <= cls < m + 32 and nt in (64, 96, 128)
+        pad = lambda t: -(-cls // t) * t
+        assert pad(nt) == min(pad(64), pad(96), pad(128)) and pad(nt) <= -(-m // 128) * 128
+    assert [L.ling_b200_token_tile(c) for c in (160, 192, 256, 288, 320, 1152)] == [96, 96, 128, 96, 64, 96]
