@@ -362,7 +362,7 @@ def setup_context(lbm, cfg, seqs, args, rank, local_rank, churn):
         pages = int(pages * 1.25)   # room for admissions that are longer than the completions they replace
     ctx = lbm.Context(cfg, sessions=len(seqs), max_context=max_context, page_tokens=page_tokens,
                       pool_pages=pages, max_seqs=len(seqs), max_rows=max(rows, 32), gemm_impl=args.gemm_impl, use_graph=1,
-                      device=local_rank, debug_rows=0, pdl=args.pdl, chain=args.chain)
+                      device=local_rank, debug_rows=0, pdl=args.pdl, chain=args.chain, gating_stream=args.gating_stream)
     ctx.synth_weights(0)
     pool = PagePool(lbm, pages, page_tokens, len(seqs), max_context // page_tokens)  # ids 1 .. pages - 1 (page 0 is reserved)
     for q in seqs:
@@ -789,6 +789,8 @@ def main():
     ap.add_argument("--pdl", type=int, default=1, help="programmatic dependent launch (bit-identical results; on by default)")
     ap.add_argument("--chain", type=int, default=0, help="layer segments of steps of at most 32 rows as persistent kernels with counter "
                     "dependencies (bit-identical results; measured slower than the separate launches, so off by default)")
+    ap.add_argument("--gating-stream", type=int, default=0, help="0/1: the DeltaNet gating projections on a second stream beside the in "
+                    "projection (default); -1: in the step's one stream")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-churn64", action="store_true", help="leave out the 64-sequence sharded batch reported beside the headline")
     ap.add_argument("--quick", action="store_true", help="device-timed steps only (no end-to-end, per-family or CPU legs): "

@@ -67,7 +67,10 @@ typedef struct ling_b200_options {
                         norm + gate|up + SiLU + down) as persistent kernels with counter dependencies, the reference's
                         ffn_persistent / gdn_persistent idea (stream_gemm.cu:841-851,1074-1086); bit-identical results,
                         but on B200 slower than the separate launches (10.1 vs 7.6 ms per 27B step): off by default     */
-  int reserved[4];
+  int gating_stream; /* 0 (default) or 1 = the DeltaNet gating projections (a, b -> g, beta: needed only by the DeltaNet kernel)
+                        run on a second stream beside the in projection, forked after the norm and joined before the DeltaNet
+                        kernel (7.61 -> 7.52 ms per 27B step; the same kernels, the same results); -1 = in the step's one stream   */
+  int reserved[3];
 } ling_b200_options;
 
 typedef struct ling_b200_ctx ling_b200_ctx;

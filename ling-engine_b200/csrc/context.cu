@@ -104,6 +104,8 @@ struct ling_b200_ctx {
   std::map<std::pair<int, int>, cudaGraphExec_t> graphs;  // (row class, flags)
   int launches_per_step = 0;
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  cudaStream_t side = nullptr;               // the gating projections run here beside the in projection (options.gating_stream)
+  cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
 
   // persistent layer segments (options.chain): dependency counters of every chain of a step, partial sums of squares
   unsigned* chain_counters = nullptr;
@@ -343,13 +345,23 @@ int enqueue_step_body(ling_b200_ctx* c, int rows, int flags) {
       float* post = c->post + size_t(gl) * d.rows_alloc * d.C;
       float* g = c->g + size_t(gl) * d.rows_alloc * d.HV;
       float* beta = c->beta + size_t(gl) * d.rows_alloc * d.HV;
-      if (!chains) {
+      const bool side_gating = !chains && c->opt.gating_stream >= 0 && !c->profiling;
+      if (side_gating) {
+        // the gating needs only the normalized row and only the DeltaNet kernel needs the gating: it runs on a second stream
+        // beside the in projection (fork after the norm, join before the DeltaNet kernel)
+        ++c->launches_per_step;
+        LB_CUDA(cudaEventRecord(c->ev_fork, s));
+        LB_CUDA(cudaStreamWaitEvent(c->side, c->ev_fork, 0));
+        LB_TRY(ab_gating_launch(c->xn, L.in_a, L.in_b, L.A_log, L.dt_bias, g, beta, n_rows, rows, d.H, d.HV, c->side));
+        LB_CUDA(cudaEventRecord(c->ev_join, c->side));
+      } else if (!chains) {
         // the gating needs only the normalized row, so it runs before the in projection: with dependent launch the
         // GEMM's CTAs are already resident and stream their first weight tiles while it executes
         Timed t(c, kFamGdn);
         LB_TRY(ab_gating_launch(c->xn, L.in_a, L.in_b, L.A_log, L.dt_bias, g, beta, n_rows, rows, d.H, d.HV, s));
       }
       if (!chains) LB_TRY(run_gemm(c, L.in, c->xq_h, 0, rows));
+      if (side_gating) LB_CUDA(cudaStreamWaitEvent(s, c->ev_join, 0));
       const Planes p0 = planes_of(c, 0, L.in);
       if (gdn_fused_supported(d)) {
         Timed t(c, kFamGdn);
@@ -615,6 +627,9 @@ int ling_b200_create(const ling_b200_model_config* cfg, const ling_b200_options*
   LB_TRY(gemm_init());
   LB_TRY(kernels_init());
   LB_CUDA(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
+  LB_CUDA(cudaStreamCreateWithFlags(&c->side, cudaStreamNonBlocking));
+  LB_CUDA(cudaEventCreateWithFlags(&c->ev_fork, cudaEventDisableTiming));
+  LB_CUDA(cudaEventCreateWithFlags(&c->ev_join, cudaEventDisableTiming));
   LB_CUDA(cudaEventCreate(&c->ev0));
   LB_CUDA(cudaEventCreate(&c->ev1));
 
@@ -762,6 +777,9 @@ void ling_b200_destroy(ling_b200_ctx* c) {
   if (c->err_host) cudaFreeHost(c->err_host);
   if (c->ev0) cudaEventDestroy(c->ev0);
   if (c->ev1) cudaEventDestroy(c->ev1);
+  if (c->side) cudaStreamDestroy(c->side);
+  if (c->ev_fork) cudaEventDestroy(c->ev_fork);
+  if (c->ev_join) cudaEventDestroy(c->ev_join);
   if (c->stream) cudaStreamDestroy(c->stream);
   delete c;
 }
