@@ -8,6 +8,7 @@
 #include <cstring>
 #include <map>
 #include <numeric>
+#include <random>
 
 #include "ling_scheduler.hpp"
 
@@ -274,10 +275,23 @@ static void setup(ling::Engine& e) {
   ling_b200_synth_weights(e.handle(), 0);
   e.set_tree_source([](int, int anchor, const std::vector<int>& history) { return chain_tree(anchor, 12, anchor + int(history.size())); });
   e.set_prefill_fill([](ling_b200_ctx* ctx, int session, int, int to) {
-    // synthetic stand-in for the prefill pass: the KV of [0, to) and the DeltaNet state as functions of the length alone,
-    // so that a request has the same context whichever slot and company it runs in
-    ling_b200_synth_kv(ctx, session, to, uint64_t(to));
-    ling_b200_synth_state(ctx, session, uint64_t(to));
+    // stand-in for the prefill pass: the KV of [0, to) and the DeltaNet state written from host values that are a function of
+    // the length alone (the library's synthetic fills are keyed by the slot), so that a request has the same context
+    // whichever slot and company it runs in
+    const ling::ModelConfig c = toy_config();
+    std::mt19937 rng{unsigned(to) * 2654435761u + 17u};
+    std::normal_distribution<float> nd(0.f, 1.f);
+    std::vector<float> k(size_t(to) * c.kv_heads * c.head_dim), v(k.size());
+    for (float& x : k) x = nd(rng);
+    for (float& x : v) x = nd(rng);
+    ling_b200_kv_write(ctx, session, 0, 0, to, k.data(), v.data());
+    const int C = 2 * c.lin_k_heads * c.lin_k_dim + c.lin_v_heads * c.lin_v_dim;
+    std::vector<float> st(size_t(c.lin_v_heads) * c.lin_k_dim * c.lin_v_dim), conv(size_t(C) * 3);
+    for (int gl = 0; gl < 3; ++gl) {
+      for (float& x : st) x = 0.1f * nd(rng);
+      for (float& x : conv) x = nd(rng);
+      ling_b200_state_write(ctx, session, gl, st.data(), conv.data());
+    }
     return (to * 37) % 4096;
   });
 }
@@ -316,6 +330,33 @@ static void gpu_checks() {
   EXPECT(batched > 0);
   std::printf("continuous batching: %ld decode passes, %ld of them shared, %.2f sequences a pass\n", sch.stats().decode_passes,
               sch.stats().batched_steps, double(sch.stats().rows) / double(sch.stats().decode_passes));
+  // The same requests through a page pool that cannot keep every finished session resident: admission evicts idle sessions,
+  // and what the running requests produce does not change.
+  ling::EngineOptions tight = o;
+  tight.kv_pool_pages = 44;
+  ling::Engine eng2(toy_config(), tight);
+  setup(eng2);
+  ling::serve::Scheduler sch2(eng2, 2);
+  std::map<long, int> len2;
+  for (const Request& r : reqs) len2[sch2.submit(r)] = int(r.prompt.size());
+  sch2.run_until_idle();
+  std::vector<Finished> done2 = sch2.take_finished();
+  EXPECT(done2.size() == 6 && sch2.stats().kv_evictions > 0);
+  for (const Finished& f : done2) {
+    EXPECT(f.finish == "length" && f.tokens == alone[len2[f.id]]);
+    if (f.tokens != alone[len2[f.id]]) {
+      std::printf("request %ld (prompt %d) in session %d: finish %s %s, %zu tokens, passes %d (%d shared):", f.id, len2[f.id], f.session,
+                  f.finish.c_str(), f.error.c_str(), f.tokens.size(), f.passes, f.batched);
+      for (size_t i = 0; i < f.tokens.size() && i < alone[len2[f.id]].size(); ++i)
+        if (f.tokens[i] != alone[len2[f.id]][i]) {
+          std::printf(" first difference at token %zu (%d vs %d)", i, f.tokens[i], alone[len2[f.id]][i]);
+          break;
+        }
+      std::printf("\n");
+    }
+  }
+  std::printf("tight pool (44 pages): %ld idle sessions evicted, %ld page waits, %ld ended by the last resort\n", sch2.stats().kv_evictions,
+              sch2.stats().kv_waits, sch2.stats().kv_pool_exhausted);
 }
 
 int main(int argc, char** argv) {
