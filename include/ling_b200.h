@@ -433,6 +433,70 @@ int ling_b200_kvpool_retain(ling_b200_kvpool* p, int page);
 int ling_b200_kvpool_release(ling_b200_kvpool* p, int page);
 void ling_b200_kvpool_retire(ling_b200_kvpool* p);
 
+/* ArenaAlloc (src/core/prefix_kv.hpp:35-49): first-fit byte offsets inside one region whose size is fixed at the start, freed
+ * ranges merged with their neighbours.  Host bookkeeping only; the region itself is the caller's (the saved DeltaNet states of
+ * the prefix KV store live in one: ling_b200_state_arena_reserve).  alloc returns the offset, or -1 when no free range fits. */
+typedef struct ling_b200_arena ling_b200_arena;
+ling_b200_arena* ling_b200_arena_create(size_t size, size_t align);
+void ling_b200_arena_destroy(ling_b200_arena* a);
+long long ling_b200_arena_alloc(ling_b200_arena* a, size_t bytes);
+void ling_b200_arena_release(ling_b200_arena* a, size_t offset);
+size_t ling_b200_arena_size(const ling_b200_arena* a);
+size_t ling_b200_arena_in_use(const ling_b200_arena* a);
+
+/* PrefixKvTree in its paged mode (src/core/prefix_kv.hpp:12-22,51-124; src/core/prefix_kv.cpp): a radix tree of token runs
+ * whose nodes hold a reference to each KV pool page their run overlaps, and at some node ends a saved recurrent state.  The
+ * byte budget covers the states only.  The reference's std::function Ops are C callbacks over one user pointer:
+ *   hold(user, from, to, pages, cap)  the active session's page ids for page indices from / page_tokens .. (to - 1) / page_tokens
+ *                                     into pages[], a reference taken on each; returns how many it wrote.  Another count than
+ *                                     the range's, or an id 0 among them, is a failure: the tree gives back the ids it got
+ *                                     and the insert stops there, keeping the nodes already made.
+ *   retain / drop(user, page)         take / give back one reference.
+ *   state_alloc(user, bytes)          storage for one saved state (any non-NULL token the caller can map to it), or NULL.
+ *   state_release(user, state)
+ * The reference's buffer mode (KV copied into the store's own buffers: an engine without a page pool) has no counterpart: the
+ * KV here always lives in pool pages.  Node ids are small integers; 0 is the root. */
+typedef struct ling_b200_prefix ling_b200_prefix;
+typedef struct ling_b200_prefix_ops {
+  void* user;
+  int (*hold)(void* user, int from, int to, int* pages, int cap);
+  void (*retain)(void* user, int page);
+  void (*drop)(void* user, int page);
+  void* (*state_alloc)(void* user, size_t bytes);
+  void (*state_release)(void* user, void* state);
+} ling_b200_prefix_ops;
+ling_b200_prefix* ling_b200_prefix_create(size_t budget_bytes, size_t state_bytes, int page_tokens, const ling_b200_prefix_ops* ops);
+void ling_b200_prefix_destroy(ling_b200_prefix* t); /* clears first */
+/* match (prefix_kv.hpp:82-83): the prompt's leading tokens held under `scope`; the nodes along them into path[] (as many as fit
+ * in cap), their number into *n_path.  Returns the matched length. */
+int ling_b200_prefix_match(const ling_b200_prefix* t, const int* prompt, int n, uint64_t scope, int* path, int cap, int* n_path);
+/* best_state (prefix_kv.hpp:84-85): the deepest node end on the path, at most min(len, limit), that has a state: its position
+ * (0: none) and, into *state, what state_alloc returned for it. */
+int ling_b200_prefix_best_state(const ling_b200_prefix* t, const int* path, int n_path, int len, int limit, void** state);
+/* pages (prefix_kv.hpp:88-95): one page id per page index below ceil(n / page_tokens), the deepest node's on the path where two
+ * overlap.  Returns the count, or -1 when cap is too small. */
+int ling_b200_prefix_pages(const ling_b200_prefix* t, const int* path, int n_path, int n, int* pages, int cap);
+void ling_b200_prefix_touch(ling_b200_prefix* t, const int* path, int n_path, uint64_t epoch);
+/* insert (prefix_kv.hpp:98-105): prompt[0, q) with every position of the ascending cuts[] in (0, q] a node end.  The cut nodes
+ * that have no state yet come back as (node, position) pairs; returns their number (at most cap are written). */
+int ling_b200_prefix_insert(ling_b200_prefix* t, const int* prompt, int n, int q, const int* cuts, int n_cuts, uint64_t epoch,
+                            uint64_t scope, int* want_node, int* want_pos, int cap);
+/* add_state (prefix_kv.hpp:106-107): makes room in the budget (evicting least recently used leaves stamped before `epoch`) and
+ * returns the node's new state storage, or NULL. */
+void* ling_b200_prefix_add_state(ling_b200_prefix* t, int node, uint64_t epoch);
+/* evict_lru_leaf (prefix_kv.hpp:109-112): 1 when a leaf outside keep[] went, 0 when none is left. */
+int ling_b200_prefix_evict_lru_leaf(ling_b200_prefix* t, const int* keep, int n_keep);
+void ling_b200_prefix_clear(ling_b200_prefix* t);
+size_t ling_b200_prefix_bytes(const ling_b200_prefix* t);
+size_t ling_b200_prefix_budget(const ling_b200_prefix* t);
+int ling_b200_prefix_nodes(const ling_b200_prefix* t);
+int ling_b200_prefix_states(const ling_b200_prefix* t);
+int ling_b200_prefix_pages_held(const ling_b200_prefix* t);
+/* page_lists (prefix_kv.hpp:122-124): every live node's page ids outside skip[], concatenated into pages[] with each node's
+ * count in lens[].  Returns the number of lists, or -1 when either array is too small. */
+int ling_b200_prefix_page_lists(const ling_b200_prefix* t, const int* skip, int n_skip, int* pages, int cap_pages, int* lens,
+                                int cap_lists);
+
 /* select_batch / pair_order (src/serve/pairing.hpp:46-75): candidates as three parallel arrays. Returns the count. */
 int ling_b200_pair_order(const int* batchable, const int* recent, const long* last, int n, int fair, int* order);
 int ling_b200_select_batch(const int* batchable, const int* recent, const long* last, int n, int self, int fit,

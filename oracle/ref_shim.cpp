@@ -2,13 +2,15 @@
 // oracle/_ref/libling_ref.so (see oracle/Makefile).  TEST INFRASTRUCTURE ONLY.  Nothing of the reference is copied
 // into this repository: this file only includes the reference's headers and calls its functions, so that the oracle
 // and the product's host logic can be compared with the real thing (tree description, greedy acceptance, context
-// lookup, tree building, the KV page pool's bookkeeping, pairing, pool policy, admission arithmetic, trace line).
+// lookup, tree building, the KV page pool's bookkeeping, pairing, pool policy, admission arithmetic, trace line, the prefix KV
+// store's tree in its paged mode and its arena).
 #include <cstring>
 #include <optional>
 #include <vector>
 
 #include "core/kv_pool.hpp"
 #include "core/lookup.hpp"
+#include "core/prefix_kv.hpp"
 #include "core/tree.hpp"
 #include "serve/admission.hpp"
 #include "serve/kv_policy.hpp"
@@ -289,5 +291,95 @@ int ref_format_step(double t, long pass, const char* kind, size_t turn, const in
   std::memcpy(buf, line.c_str(), line.size() + 1);
   return int(line.size());
 }
+
+// ---- the prefix KV store (core/prefix_kv.hpp), paged mode; the callbacks mirror the product's C interface
+struct ref_prefix_ops {
+  void* user;
+  int (*hold)(void* user, int from, int to, int* pages, int cap);
+  void (*retain)(void* user, int page);
+  void (*drop)(void* user, int page);
+  void* (*state_alloc)(void* user, size_t bytes);
+  void (*state_release)(void* user, void* state);
+};
+void* ref_prefix_create(size_t budget, size_t state_bytes, const ref_prefix_ops* o) {
+  const ref_prefix_ops c = *o;
+  ling::PrefixKvTree::Ops ops;
+  ops.alloc = [c](size_t n) { return c.state_alloc(c.user, n); };
+  ops.release = [c](void* p) { c.state_release(c.user, p); };
+  ops.store = [](void*, int, int, int, int) {};
+  ops.hold = [c](int from, int to) {
+    const int want = ling::KvPool::index_of(to - 1) - ling::KvPool::index_of(from) + 1;
+    std::vector<int> ids(want, 0);
+    const int got = c.hold(c.user, from, to, ids.data(), want);
+    ids.resize(got < 0 ? 0 : (got > want ? want : got));
+    return ids;
+  };
+  ops.retain = [c](int pg) { c.retain(c.user, pg); };
+  ops.drop = [c](int pg) { c.drop(c.user, pg); };
+  return new ling::PrefixKvTree(budget, 0, state_bytes, std::move(ops));
+}
+void ref_prefix_destroy(void* t) { delete static_cast<ling::PrefixKvTree*>(t); }
+static ling::PrefixKvTree::Match as_match(const int* path, int n_path, int len) {
+  ling::PrefixKvTree::Match m;
+  m.len = len;
+  m.path.assign(path, path + n_path);
+  return m;
+}
+int ref_prefix_match(void* t, const int* prompt, int n, uint64_t scope, int* path, int cap, int* n_path) {
+  const auto m = static_cast<ling::PrefixKvTree*>(t)->match(std::vector<int>(prompt, prompt + n), scope);
+  *n_path = int(m.path.size());
+  for (int i = 0; i < *n_path && i < cap; ++i) path[i] = m.path[i];
+  return m.len;
+}
+int ref_prefix_best_state(void* t, const int* path, int n_path, int len, int limit, void** state) {
+  const void* st = nullptr;
+  const int pos = static_cast<ling::PrefixKvTree*>(t)->best_state(as_match(path, n_path, len), limit, &st);
+  *state = const_cast<void*>(st);
+  return pos;
+}
+int ref_prefix_pages(void* t, const int* path, int n_path, int len, int n, int* pages, int cap) {
+  const std::vector<int> pg = static_cast<ling::PrefixKvTree*>(t)->pages(as_match(path, n_path, len), n);
+  if (int(pg.size()) > cap) return -1;
+  for (size_t i = 0; i < pg.size(); ++i) pages[i] = pg[i];
+  return int(pg.size());
+}
+void ref_prefix_touch(void* t, const int* path, int n_path, uint64_t epoch) {
+  static_cast<ling::PrefixKvTree*>(t)->touch(as_match(path, n_path, 0), epoch);
+}
+int ref_prefix_insert(void* t, const int* prompt, int n, int q, const int* cuts, int n_cuts, uint64_t epoch, uint64_t scope,
+                      int* want_node, int* want_pos, int cap) {
+  const auto want = static_cast<ling::PrefixKvTree*>(t)->insert(std::vector<int>(prompt, prompt + n), q,
+                                                                std::vector<int>(cuts, cuts + n_cuts), epoch, scope);
+  for (size_t i = 0; i < want.size() && int(i) < cap; ++i) want_node[i] = want[i].first, want_pos[i] = want[i].second;
+  return int(want.size());
+}
+void* ref_prefix_add_state(void* t, int node, uint64_t epoch) { return static_cast<ling::PrefixKvTree*>(t)->add_state(node, epoch); }
+int ref_prefix_evict_lru_leaf(void* t, const int* keep, int n_keep) {
+  return static_cast<ling::PrefixKvTree*>(t)->evict_lru_leaf(std::vector<int>(keep, keep + n_keep));
+}
+void ref_prefix_clear(void* t) { static_cast<ling::PrefixKvTree*>(t)->clear(); }
+size_t ref_prefix_bytes(void* t) { return static_cast<ling::PrefixKvTree*>(t)->bytes(); }
+int ref_prefix_nodes(void* t) { return static_cast<ling::PrefixKvTree*>(t)->nodes(); }
+int ref_prefix_states(void* t) { return static_cast<ling::PrefixKvTree*>(t)->states(); }
+int ref_prefix_pages_held(void* t) { return static_cast<ling::PrefixKvTree*>(t)->pages_held(); }
+int ref_prefix_page_lists(void* t, const int* skip, int n_skip, int* pages, int cap_pages, int* lens, int cap_lists) {
+  const auto lists = static_cast<ling::PrefixKvTree*>(t)->page_lists(std::vector<int>(skip, skip + n_skip));
+  int used = 0, n = 0;
+  for (const auto& l : lists) {
+    if (n >= cap_lists || used + int(l.size()) > cap_pages) return -1;
+    for (int pg : l) pages[used++] = pg;
+    lens[n++] = int(l.size());
+  }
+  return n;
+}
+void* ref_arena_create(size_t size, size_t align) { return new ling::ArenaAlloc(size, align); }
+void ref_arena_destroy(void* a) { delete static_cast<ling::ArenaAlloc*>(a); }
+long long ref_arena_alloc(void* a, size_t bytes) {
+  size_t off = 0;
+  return static_cast<ling::ArenaAlloc*>(a)->alloc(bytes, &off) ? (long long)off : -1;
+}
+void ref_arena_release(void* a, size_t off) { static_cast<ling::ArenaAlloc*>(a)->release(off); }
+size_t ref_arena_size(void* a) { return static_cast<ling::ArenaAlloc*>(a)->size(); }
+size_t ref_arena_in_use(void* a) { return static_cast<ling::ArenaAlloc*>(a)->in_use(); }
 
 }  // extern "C"
