@@ -156,6 +156,17 @@ int ling_b200_synth_state(ling_b200_ctx* ctx, int slot, uint64_t seed); /* state
 /* Engine::state_hash (engine.cpp:954-971): FNV-1a over every DeltaNet and conv state of a slot, bit for bit. */
 int ling_b200_state_hash(ling_b200_ctx* ctx, int slot, uint64_t* hash);
 
+/* A session's whole recurrent state (every DeltaNet layer's state, then every conv window) saved to and restored from a
+ * device arena, as the prefix KV store keeps states at its nodes' ends (Engine::copy_slot / state_view,
+ * engine.cpp:1061-1068,1125-1137; the arena is EngineOptions::prefix_kv_mb's, engine.cpp:380-425).  The arena is reserved once;
+ * offsets into it are the caller's bookkeeping (ling_b200_arena_*), multiples of 16.  The copies are queued on the
+ * context's stream, in order with the steps.  ling_b200_state_reset zeroes a slot (Engine::reset_state). */
+size_t ling_b200_state_bytes(const ling_b200_ctx* ctx);
+int ling_b200_state_arena_reserve(ling_b200_ctx* ctx, size_t bytes);
+int ling_b200_state_save(ling_b200_ctx* ctx, int slot, size_t offset);
+int ling_b200_state_restore(ling_b200_ctx* ctx, int slot, size_t offset);
+int ling_b200_state_reset(ling_b200_ctx* ctx, int slot);
+
 /* ------------------------------------------------------------------------------------------------ the step */
 /* One sequence of a step: Engine::SeqStep (engine.hpp:337-344) after the drafter has produced its tree
  * (DraftTree, tree.hpp:41-48: parent index < child index, row 0 the anchor, rows 1..chain the chain). */
@@ -168,7 +179,8 @@ typedef struct ling_b200_seq_step {
   const int* tokens; /* [n_rows]                                                                */
   const int* parent; /* [n_rows], parent[0] = -1                                                */
   const int* force_argmax; /* NULL, or [n_rows]: replaces the device argmax before acceptance (a test and
-                              benchmark hook that imposes an accepted length)                    */
+                              benchmark hook that imposes an accepted length); a negative entry leaves
+                              that row's own argmax                                              */
 } ling_b200_seq_step;
 
 typedef struct ling_b200_seq_result {

@@ -91,6 +91,8 @@ struct ling_b200_ctx {
   // sessions
   KvPoolDev kv;
   float *gdn_state = nullptr, *conv_state = nullptr;  // [slot][gdn layer][...]
+  uint8_t* state_arena = nullptr;  // saved states of the prefix KV store (ling_b200_state_arena_reserve)
+  size_t state_arena_bytes = 0;
   size_t state_layer = 0, conv_layer = 0;             // floats per layer
 
   // the step
@@ -1030,6 +1032,54 @@ int ling_b200_synth_state(ling_b200_ctx* c, int slot, uint64_t seed) {
                            c->conv_state + at * c->conv_layer, c->conv_layer, c->stream));
   }
   return finish(c);
+}
+// One session's recurrent state as the prefix KV store and the checkpoints keep it (Engine::copy_slot, engine.cpp:1125-1137):
+// every DeltaNet layer's state, then every conv window.  A slot's layers are consecutive, so each half is one run.
+size_t ling_b200_state_bytes(const ling_b200_ctx* c) {
+  return c ? size_t(c->d.n_gdn) * (c->state_layer + c->conv_layer) * sizeof(float) : 0;
+}
+int ling_b200_state_arena_reserve(ling_b200_ctx* c, size_t bytes) {
+  LB_TRY(check_ctx(c));
+  if (c->state_arena || bytes == 0) {
+    set_error("state_arena_reserve: already reserved, or an empty arena");
+    return LING_B200_ERR_ARG;
+  }
+  LB_TRY(c->alloc(&c->state_arena, bytes, false));
+  c->state_arena_bytes = bytes;
+  return LING_B200_OK;
+}
+static int state_move(ling_b200_ctx* c, int slot, size_t offset, bool save) {
+  LB_TRY(check_ctx(c));
+  const size_t gdn = size_t(c->d.n_gdn) * c->state_layer * sizeof(float), conv = size_t(c->d.n_gdn) * c->conv_layer * sizeof(float);
+  if (slot < 0 || slot >= c->opt.sessions || !c->state_arena || offset % 16 != 0 || offset > c->state_arena_bytes ||
+      gdn + conv > c->state_arena_bytes - offset) {
+    set_error("state save/restore: slot out of range, no arena, or a range outside it");
+    return LING_B200_ERR_ARG;
+  }
+  float* s_gdn = c->gdn_state + size_t(slot) * c->d.n_gdn * c->state_layer;
+  float* s_conv = c->conv_state + size_t(slot) * c->d.n_gdn * c->conv_layer;
+  uint8_t* a = c->state_arena + offset;
+  if (save) {
+    LB_CUDA(cudaMemcpyAsync(a, s_gdn, gdn, cudaMemcpyDeviceToDevice, c->stream));
+    LB_CUDA(cudaMemcpyAsync(a + gdn, s_conv, conv, cudaMemcpyDeviceToDevice, c->stream));
+  } else {
+    LB_CUDA(cudaMemcpyAsync(s_gdn, a, gdn, cudaMemcpyDeviceToDevice, c->stream));
+    LB_CUDA(cudaMemcpyAsync(s_conv, a + gdn, conv, cudaMemcpyDeviceToDevice, c->stream));
+  }
+  return LING_B200_OK;
+}
+int ling_b200_state_save(ling_b200_ctx* c, int slot, size_t offset) { return state_move(c, slot, offset, true); }
+int ling_b200_state_restore(ling_b200_ctx* c, int slot, size_t offset) { return state_move(c, slot, offset, false); }
+// Engine::reset_state (engine.cpp:944-952): a prompt that resumes from nothing starts from zero states and windows.
+int ling_b200_state_reset(ling_b200_ctx* c, int slot) {
+  LB_TRY(check_ctx(c));
+  if (slot < 0 || slot >= c->opt.sessions) {
+    set_error("state_reset: slot out of range");
+    return LING_B200_ERR_ARG;
+  }
+  LB_CUDA(cudaMemsetAsync(c->gdn_state + size_t(slot) * c->d.n_gdn * c->state_layer, 0, size_t(c->d.n_gdn) * c->state_layer * sizeof(float), c->stream));
+  LB_CUDA(cudaMemsetAsync(c->conv_state + size_t(slot) * c->d.n_gdn * c->conv_layer, 0, size_t(c->d.n_gdn) * c->conv_layer * sizeof(float), c->stream));
+  return LING_B200_OK;
 }
 // Engine::state_hash (src/core/engine.cpp:954-971): FNV-1a, byte by byte, each DeltaNet layer's state then its window.
 int ling_b200_state_hash(ling_b200_ctx* c, int slot, uint64_t* hash) {

@@ -14,6 +14,7 @@
 #include <span>
 #include <stdexcept>
 #include <string>
+#include <utility>
 #include <vector>
 
 #include "ling_b200.h"
@@ -169,13 +170,134 @@ class KvPool {
   int page_tokens_;
 };
 
+// ---- src/core/prefix_kv.hpp
+class ArenaAlloc {
+ public:
+  ArenaAlloc(size_t size, size_t align) : a_(ling_b200_arena_create(size, align)) {}
+  ~ArenaAlloc() { ling_b200_arena_destroy(a_); }
+  ArenaAlloc(const ArenaAlloc&) = delete;
+  ArenaAlloc& operator=(const ArenaAlloc&) = delete;
+  bool alloc(size_t bytes, size_t* offset) {  // false: no free range is large enough
+    const long long at = ling_b200_arena_alloc(a_, bytes);
+    if (at < 0) return false;
+    *offset = static_cast<size_t>(at);
+    return true;
+  }
+  void release(size_t offset) { ling_b200_arena_release(a_, offset); }
+  size_t size() const { return ling_b200_arena_size(a_); }
+  size_t in_use() const { return ling_b200_arena_in_use(a_); }
+
+ private:
+  ling_b200_arena* a_;
+};
+
+// The prefix KV store's tree, always in the reference's paged mode (prefix_kv.hpp:12-18): nodes hold references to pool
+// pages, the budget covers the saved states.  The buffer mode's members (Ops::store, segments, buffers) have no counterpart.
+class PrefixKvTree {
+ public:
+  struct Ops {
+    std::function<void*(size_t bytes)> alloc;  // storage for one state, or nullptr
+    std::function<void(void* p)> release;
+    std::function<std::vector<int>(int from, int to)> hold;
+    std::function<void(int page)> retain;
+    std::function<void(int page)> drop;
+  };
+  struct Match {
+    int len = 0;
+    std::vector<int> path;
+  };
+  PrefixKvTree(size_t budget_bytes, size_t /*bytes_per_token: the KV is the pool's*/, size_t state_bytes, Ops ops, int page_tokens = 64)
+      : ops_(std::move(ops)), page_tokens_(page_tokens) {
+    ling_b200_prefix_ops c{this, &hold_cb, &retain_cb, &drop_cb, &alloc_cb, &release_cb};
+    if (ops_.hold && ops_.retain && ops_.drop && ops_.alloc && ops_.release)
+      t_ = ling_b200_prefix_create(budget_bytes, state_bytes, page_tokens, &c);
+    if (!t_) throw std::invalid_argument("PrefixKvTree: hold, retain, drop, alloc and release are all needed");
+  }
+  ~PrefixKvTree() { ling_b200_prefix_destroy(t_); }
+  PrefixKvTree(const PrefixKvTree&) = delete;
+  PrefixKvTree& operator=(const PrefixKvTree&) = delete;
+
+  Match match(const std::vector<int>& prompt, uint64_t scope = 0) const {
+    Match m;
+    int n = 0;
+    m.path.resize(prompt.size() + 1);
+    m.len = ling_b200_prefix_match(t_, prompt.data(), static_cast<int>(prompt.size()), scope, m.path.data(),
+                                   static_cast<int>(m.path.size()), &n);
+    m.path.resize(size_t(n));
+    return m;
+  }
+  int best_state(const Match& m, int limit, const void** state) const {
+    void* st = nullptr;
+    const int pos = ling_b200_prefix_best_state(t_, m.path.data(), static_cast<int>(m.path.size()), m.len, limit, &st);
+    *state = st;
+    return pos;
+  }
+  std::vector<int> pages(const Match& m, int n) const {
+    std::vector<int> out(size_t((std::max(n, 0) + page_tokens_ - 1) / page_tokens_) + 1);
+    const int c = ling_b200_prefix_pages(t_, m.path.data(), static_cast<int>(m.path.size()), n, out.data(), static_cast<int>(out.size()));
+    out.resize(size_t(std::max(c, 0)));
+    return out;
+  }
+  void touch(const Match& m, uint64_t epoch) { ling_b200_prefix_touch(t_, m.path.data(), static_cast<int>(m.path.size()), epoch); }
+  std::vector<std::pair<int, int>> insert(const std::vector<int>& prompt, int q, const std::vector<int>& cuts, uint64_t epoch,
+                                          uint64_t scope = 0) {
+    std::vector<int> node(cuts.size() + 1), pos(cuts.size() + 1);
+    const int n = ling_b200_prefix_insert(t_, prompt.data(), static_cast<int>(prompt.size()), q, cuts.data(), static_cast<int>(cuts.size()),
+                                          epoch, scope, node.data(), pos.data(), static_cast<int>(node.size()));
+    std::vector<std::pair<int, int>> want;
+    for (int i = 0; i < std::min(n, static_cast<int>(node.size())); ++i) want.push_back({node[size_t(i)], pos[size_t(i)]});
+    return want;
+  }
+  void* add_state(int node, uint64_t epoch) { return ling_b200_prefix_add_state(t_, node, epoch); }
+  bool evict_lru_leaf(const std::vector<int>& keep = {}) {
+    return ling_b200_prefix_evict_lru_leaf(t_, keep.data(), static_cast<int>(keep.size())) != 0;
+  }
+  void clear() { ling_b200_prefix_clear(t_); }
+  size_t bytes() const { return ling_b200_prefix_bytes(t_); }
+  size_t budget() const { return ling_b200_prefix_budget(t_); }
+  int nodes() const { return ling_b200_prefix_nodes(t_); }
+  int states() const { return ling_b200_prefix_states(t_); }
+  bool paged() const { return true; }
+  int pages_held() const { return ling_b200_prefix_pages_held(t_); }
+  std::vector<std::vector<int>> page_lists(const std::vector<int>& skip = {}) const {
+    std::vector<int> pages(size_t(std::max(pages_held(), 1))), lens(size_t(std::max(nodes(), 1)));
+    const int n = ling_b200_prefix_page_lists(t_, skip.data(), static_cast<int>(skip.size()), pages.data(), static_cast<int>(pages.size()),
+                                              lens.data(), static_cast<int>(lens.size()));
+    std::vector<std::vector<int>> out;
+    size_t at = 0;
+    for (int i = 0; i < n; ++i) {
+      out.emplace_back(pages.begin() + static_cast<long>(at), pages.begin() + static_cast<long>(at) + lens[size_t(i)]);
+      at += size_t(lens[size_t(i)]);
+    }
+    return out;
+  }
+
+ private:
+  static PrefixKvTree& self(void* u) { return *static_cast<PrefixKvTree*>(u); }
+  static int hold_cb(void* u, int from, int to, int* pages, int cap) {
+    const std::vector<int> ids = self(u).ops_.hold(from, to);
+    for (size_t i = 0; i < ids.size(); ++i) {
+      if (static_cast<int>(i) < cap) pages[i] = ids[i];
+      else if (ids[i] != 0) self(u).ops_.drop(ids[i]);  // more than the range's pages: nothing may leak
+    }
+    return static_cast<int>(ids.size());
+  }
+  static void retain_cb(void* u, int page) { self(u).ops_.retain(page); }
+  static void drop_cb(void* u, int page) { self(u).ops_.drop(page); }
+  static void* alloc_cb(void* u, size_t bytes) { return self(u).ops_.alloc(bytes); }
+  static void release_cb(void* u, void* p) { self(u).ops_.release(p); }
+
+  Ops ops_;
+  int page_tokens_;
+  ling_b200_prefix* t_ = nullptr;
+};
+
 // ---- src/core/model.hpp, src/core/engine.hpp
 using ModelConfig = ling_b200_model_config;
 // The resident sessions and their KV pages as the scheduler sees them (the host-side half of Engine's session functions,
 // src/core/engine.cpp:581-648,724-800,881-912, and of its Session struct, engine.hpp:760-800).  No device work: Engine
-// keeps one and adds the device side; a scheduler test can keep one alone.  This build has no prefix KV store and no
-// donor sessions (a resumed prompt reuses only its own session's positions), so pages are never shared between holders
-// and a need planned "with holders gone" (Engine::KvGone) equals the need planned now.
+// keeps one and adds the device side and the prefix KV store; a scheduler test can keep one alone.  The book itself knows
+// no store and no donor sessions: its kv_admit_need is the plan of a prompt that resumes from its own session only.
 struct Session {
   std::vector<int> history, table;  // tokens processed; page ids by page index (0 = unmapped)
   int pos = 0;
@@ -264,11 +386,15 @@ class SessionBook {
     return pool_.needed(s.table, s.pos, s.pos + kv_step_rows(s, spec));
   }
   // Positions of the session's own history that a prompt resumes from (the no-donor, no-store case of plan_resume,
-  // engine.cpp:1747-1842): the common prefix, never the whole prompt (its last token is processed again for the logits).
+  // engine.cpp:1747-1842).  A recurrent state cannot be wound back, so a prompt resumes only from a position whose state is
+  // kept.  The reference keeps a snapshot at the end of the session's last prompt; here the kept state is the session's
+  // live one, after exactly its history (every pass of this build is the same verify pass, so the state does not depend on
+  // how it was reached): a prompt that extends the whole history by at least one token resumes at the history's end,
+  // any other prompt from nothing (or, in Engine, from the prefix KV store).
   int resume_reuse(int session, const std::vector<int>& prompt, uint64_t scope, bool from_scratch) const {
     const Session& s = at(session);
-    if (from_scratch || s.scope != scope || prompt.empty()) return 0;
-    return std::min(common_prefix(s.history, prompt), static_cast<int>(prompt.size()) - 1);
+    if (from_scratch || s.scope != scope || prompt.size() <= s.history.size()) return 0;
+    return common_prefix(s.history, prompt) == static_cast<int>(s.history.size()) ? static_cast<int>(s.history.size()) : 0;
   }
   int kv_admit_need(int session, const std::vector<int>& prompt, uint64_t scope, bool from_scratch = false) const {
     if (prompt.empty()) return 0;
@@ -325,6 +451,8 @@ struct EngineOptions {
   int max_seqs = 4, max_rows = 128;
   int device = 0;
   int boundary_token = -1;  // the token that starts a message (engine.hpp:171); -1: prompts carry no boundaries
+  int prefix_kv_mb = 0;     // the prefix KV store's budget for saved states (engine.hpp:97-103; 4096 there); 0: no store
+  int checkpoint_limit = 32768;  // no state is kept past this position (engine.hpp:87)
 };
 
 class Engine {
@@ -356,8 +484,12 @@ class Engine {
       ling_b200_destroy(ctx_);
       throw std::runtime_error("Engine: " + why);
     }
+    if (opts_.prefix_kv_mb > 0) kv_store_setup();
   }
-  ~Engine() { ling_b200_destroy(ctx_); }
+  ~Engine() {
+    kv_tree_.reset();  // drops its page references while the pool is still there
+    ling_b200_destroy(ctx_);
+  }
   Engine(const Engine&) = delete;
   Engine& operator=(const Engine&) = delete;
 
@@ -394,10 +526,29 @@ class Engine {
   int kv_admit_pages(size_t prompt_len) const { return book_.kv_admit_pages(prompt_len); }
   int kv_step_need(int session, bool spec) const { return book_.kv_step_need(session, spec); }
   int kv_admit_need(int session, const std::vector<int>& prompt, uint64_t scope, bool from_scratch = false) const {
-    return book_.kv_admit_need(session, prompt, scope, from_scratch);
+    if (prompt.empty()) return 0;
+    return kv_resume_need(session, plan_resume(session, prompt, scope, from_scratch), prompt);
   }
   int kv_session_pages(int session) const { return book_.kv_reclaimable({session}); }
   int kv_reclaimable(const std::vector<int>& sessions) const { return book_.kv_reclaimable(sessions); }
+  // ---- the prefix KV store as the scheduler sees it (src/core/engine.hpp:444-460; engine.cpp:761-768)
+  bool kv_store_on() const { return static_cast<bool>(kv_tree_); }
+  const PrefixKvTree* kv_store() const { return kv_tree_.get(); }
+  // The pages that evicting the whole store would free.
+  int kv_store_pages() const {
+    if (!kv_tree_) return 0;
+    const std::vector<std::vector<int>> lists = kv_tree_->page_lists();
+    KvPool::Refs refs;
+    for (const std::vector<int>& l : lists) refs.push_back(&l);
+    return book_.pool().reclaimable(refs);
+  }
+  // Evicts the store's least recently used leaf outside `keep` (the path an admitted prompt resumes from).
+  bool kv_store_evict(const std::vector<int>& keep = {}) { return kv_tree_ && kv_tree_->evict_lru_leaf(keep); }
+  // The store nodes a prompt admitted into `session` would resume from (empty: it resumes elsewhere or from nothing).
+  std::vector<int> kv_store_path(int session, const std::vector<int>& prompt, uint64_t scope) const {
+    const ResumePlan plan = plan_resume(session, prompt, scope, false);
+    return plan.from_kv ? plan.kvm.path : std::vector<int>{};
+  }
   int kv_lru_idle(const std::vector<bool>& busy) const { return book_.kv_lru_idle(busy); }
   void kv_evict(int session) {
     if (book_.evict(session)) ++kv_evictions_;
@@ -416,32 +567,114 @@ class Engine {
   int sessions_resident() const { return book_.resident(); }
   long session_evictions() const { return evictions_; }
   int max_batch() const { return opts_.max_seqs; }
-  // What the prefill path would do for an admitted prompt (Engine::begin_prefill + prefill_chunk, engine.cpp:1747-1990): the
-  // session keeps the positions it shares with the prompt, maps pages for the rest plus the growth reserve and takes the
-  // prompt as its history.  The prefill pass itself is outside this build: `fill` stands in for it and leaves the KV of
-  // positions [from, to) and the DeltaNet state of the slot on the device (synthetic in the tests and the benchmark); it
-  // returns the first token.  Throws KvPoolExhausted with nothing changed when the pool is short.
+  // What the prefill path does for an admitted prompt (Engine::begin_prefill + prefill_chunk, engine.cpp:1886-2300): the
+  // prompt resumes from the furthest kept state (the session's own, or one of the prefix KV store's, whose pages are then
+  // mapped by reference), pages are taken for the rest plus the growth reserve, the rest is processed in pieces that end
+  // at the positions the store will keep a state at, and the prompt's shareable beginning goes into the store.
+  // The pass that processes a piece is `fill`: it leaves the KV of positions [from, to) and the recurrent state after
+  // `to` on the device and returns the token after `to`.  The reference's prefill pass is outside this build; the fill is
+  // either chain_prefill below (the verify pass over linear chains, the real model) or a synthetic stand-in a test or
+  // benchmark sets.  Throws KvPoolExhausted with nothing changed when the pool is short.
   using PrefillFill = std::function<int(ling_b200_ctx*, int session, int from, int to)>;
   void set_prefill_fill(PrefillFill f) { prefill_fill_ = std::move(f); }
-  int begin_prefill(int session, const std::vector<int>& prompt, uint64_t scope = 0) {
+  void use_chain_prefill() {
+    prefill_fill_ = [this](ling_b200_ctx*, int session, int from, int to) { return chain_prefill(session, from, to); };
+  }
+  struct PrefillStats {  // src/core/engine.hpp:190-200, the fields this path has
+    int reused_tokens = 0, store_tokens = 0, prefill_tokens = 0, chunks = 0;
+  };
+  const PrefillStats& last_prefill() const { return last_prefill_; }
+  static constexpr int kResumeAlign = 32;  // kept states sit at multiples of this (engine.hpp:533)
+
+  int begin_prefill(int session, const std::vector<int>& prompt, uint64_t scope = 0, bool from_scratch = false) {
+    if (prompt.empty()) throw std::runtime_error("empty prompt");
     Session& s = book_.at(session);
     const int L = static_cast<int>(prompt.size());
-    const int reuse = book_.resume_reuse(session, prompt, scope, false);
+    const ResumePlan plan = plan_resume(session, prompt, scope, from_scratch);
+    const int reuse = plan.reuse;
     const int target = std::min(L + SessionBook::kKvGrowthPages * opts_.page_tokens, opts_.max_context);
-    if (book_.kv_admit_need(session, prompt, scope) > book_.pool().free_pages()) book_.pool().retire();
-    if (book_.kv_admit_need(session, prompt, scope) > book_.pool().free_pages()) throw KvPoolExhausted("KV page pool exhausted: prefill");
+    if (kv_resume_need(session, plan, prompt) > book_.pool().free_pages()) book_.pool().retire();
+    if (kv_resume_need(session, plan, prompt) > book_.pool().free_pages()) throw KvPoolExhausted("KV page pool exhausted: prefill");
+    const uint64_t epoch = ++kv_epoch_;
+    if (kv_tree_ && !from_scratch) kv_tree_->touch(plan.kvm, epoch);
+    last_prefill_ = PrefillStats{};
+    last_prefill_.reused_tokens = reuse, last_prefill_.prefill_tokens = L - reuse;
+    const std::vector<int> before = s.table;
+    if (plan.from_kv) {
+      // The store's pages for [0, reuse) mapped by reference, no copy (kv_restore, engine.cpp:1095-1104); the partly used
+      // last one is copied by kv_ensure below before this session writes into it.
+      book_.pool().share(s.table, kv_tree_->pages(plan.kvm, reuse), reuse);
+      if (ling_b200_state_restore(ctx_, session, state_offset(plan.kv_state)) != LING_B200_OK)
+        throw std::runtime_error(std::string("begin_prefill: ") + ling_b200_last_error());
+      last_prefill_.store_tokens = reuse;
+    } else if (reuse == 0) {
+      ling_b200_state_reset(ctx_, session);
+    }
+    // Pages past the target go back; shared pages past the resume point are let go (fresh ones are taken instead of
+    // copies of what is overwritten anyway); the page `reuse` falls in is copied if it is shared (engine.cpp:1997-2010).
     book_.pool().truncate(s.table, book_.pool().pages_for(target) * opts_.page_tokens);
+    book_.pool().unshare(s.table, reuse);
+    table_sync(s, session, before);
     kv_ensure(s, session, reuse, target);
     s.history = prompt;
+    s.scope = scope;
+    s.pos = reuse;
+    // Piece ends: the store's cuts past the resume point, then the prompt's end.  Each cut's state is saved when its piece ends.
+    const std::vector<int> cuts = kv_tree_ ? kv_store_cuts(prompt, plan.branch_at) : std::vector<int>{};
+    std::vector<std::pair<int, size_t>> kept;  // (position, arena offset) of the states saved on the way
+    int first = 0, from = reuse;
+    auto piece = [&](int to) {
+      if (to <= from) return;
+      first = prefill_fill_ ? prefill_fill_(ctx_, session, from, to) : 0;
+      ++last_prefill_.chunks;
+      s.pos = from = to;
+    };
+    for (int c : cuts) {
+      if (c <= reuse || c >= L) continue;
+      piece(c);
+      size_t off = 0;
+      if (kv_arena_->alloc(state_unit_, &off)) {
+        if (ling_b200_state_save(ctx_, session, off) == LING_B200_OK) kept.push_back({c, off});
+        else kv_arena_->release(off);
+      }
+    }
+    piece(L);
     s.prompt_len = L;
-    s.pos = L;
     s.turn_start = L;  // a prompt without message boundaries is bound again only when extended whole (engine.cpp:2276-2282)
     for (int k = L - 1; k >= 0; --k)
       if (prompt[size_t(k)] == opts_.boundary_token) {
         s.turn_start = k + 1;
         break;
       }
-    return prefill_fill_ ? prefill_fill_(ctx_, session, reuse, L) : 0;
+    if (kv_tree_ && !cuts.empty()) kv_insert(session, prompt, cuts, epoch, scope, kept);
+    for (const auto& k : kept) kv_arena_->release(k.second);  // the states no node took
+    return first;
+  }
+
+  // The verify pass as a prefill pass: positions [from, to) of the session's history as linear chains of at most
+  // kResumeAlign rows, each ending at a multiple of kResumeAlign, every row accepted (the next chain token imposed as
+  // the row's argmax) and committed; the last row's own argmax is the token after `to`.  A prompt resumed at a kept state
+  // runs the same passes over the same positions as one prefilled from nothing, so it reaches the same bits.
+  int chain_prefill(int session, int from, int to) {
+    const Session& s = book_.at(session);
+    if (from < 0 || to > static_cast<int>(s.history.size())) throw std::runtime_error("chain_prefill: positions outside the history");
+    int next = 0;
+    for (int at = from; at < to;) {
+      const int end = std::min(to, at - at % kResumeAlign + kResumeAlign), n = end - at;
+      const std::vector<int> tok(s.history.begin() + at, s.history.begin() + end);
+      std::vector<int> par(static_cast<size_t>(n), 0), force(static_cast<size_t>(n), -1);
+      for (int i = 0; i < n; ++i) par[size_t(i)] = i - 1;
+      for (int i = 0; i + 1 < n; ++i) force[size_t(i)] = tok[size_t(i) + 1];
+      ling_b200_seq_step step{session, at, 0, n, n - 1, tok.data(), par.data(), force.data()};
+      ling_b200_seq_result res{};
+      if (ling_b200_verify_step(ctx_, &step, 1, LING_B200_STEP_COMMIT, &res) != LING_B200_OK)
+        throw std::runtime_error(std::string("chain_prefill: ") + ling_b200_last_error());
+      if (res.status != LING_B200_SEQ_OK) throw NonFiniteLogits();
+      if (res.n_path != n) throw std::logic_error("chain_prefill: a chain row was not accepted");
+      next = res.next_token;
+      at = end;
+    }
+    return next;
   }
   long kv_evictions() const { return kv_evictions_; }
   bool kv_retire(bool) {
@@ -518,18 +751,142 @@ class Engine {
     const std::vector<int> before = s.table;
     std::vector<KvPool::Copy> copies;
     if (!book_.pool().ensure(s.table, from, to, &copies)) throw KvPoolExhausted("KV page pool exhausted");
-    std::vector<int> src, dst, idx, val;
+    std::vector<int> src, dst;
     for (const KvPool::Copy& c : copies) src.push_back(c.src), dst.push_back(c.dst);
     if (!src.empty()) ling_b200_kv_pages_copy(ctx_, src.data(), dst.data(), static_cast<int>(src.size()));
-    for (size_t i = 0; i < s.table.size(); ++i)
-      if (i >= before.size() || before[i] != s.table[i]) idx.push_back(static_cast<int>(i)), val.push_back(s.table[i]);
+    table_sync(s, slot, before);
+  }
+
+  void table_sync(const Session& s, int slot, const std::vector<int>& before) {
+    std::vector<int> idx, val;
+    for (size_t i = 0; i < std::max(s.table.size(), before.size()); ++i) {
+      const int now = i < s.table.size() ? s.table[i] : 0, was = i < before.size() ? before[i] : 0;
+      if (now != was) idx.push_back(static_cast<int>(i)), val.push_back(now);
+    }
     if (!idx.empty()) ling_b200_kv_table_set(ctx_, slot, idx.data(), val.data(), static_cast<int>(idx.size()));
+  }
+
+  // ---- the prefix KV store (engine.cpp:380-425,1095-1122,1747-1884)
+  // Where a prompt resumes: the furthest kept state inside what it shares with the session's own history or with the store.
+  struct ResumePlan {
+    int reuse = 0;
+    bool from_kv = false;
+    PrefixKvTree::Match kvm;
+    const void* kv_state = nullptr;
+    int branch_at = 0;  // where the prompt leaves the longest prefix it shares with another conversation, aligned
+  };
+  ResumePlan plan_resume(int session, const std::vector<int>& prompt, uint64_t scope, bool from_scratch) const {
+    ResumePlan plan;
+    const int L = static_cast<int>(prompt.size());
+    const int own = book_.resume_reuse(session, prompt, scope, from_scratch);
+    int kv_reuse = 0;
+    if (kv_tree_ && !from_scratch) {
+      plan.kvm = kv_tree_->match(prompt, scope);
+      kv_reuse = kv_tree_->best_state(plan.kvm, std::min(plan.kvm.len, L - 1), &plan.kv_state);
+    }
+    plan.from_kv = kv_reuse > own;
+    plan.reuse = plan.from_kv ? kv_reuse : own;
+    if (kv_tree_) {
+      const Session& self = book_.at(session);
+      for (int i = 0; i < book_.sessions(); ++i) {
+        const Session& o = book_.at(i);
+        if (o.history.empty() || o.scope != scope) continue;
+        const int l = SessionBook::common_prefix(o.history, prompt);
+        if (&o == &self && o.prompt_len > 0 && l >= o.turn_start) continue;  // its own next turn: its own state covers that
+        plan.branch_at = std::max(plan.branch_at, l);
+      }
+      plan.branch_at = std::max(plan.branch_at, plan.kvm.len);
+      plan.branch_at -= plan.branch_at % kResumeAlign;
+    }
+    return plan;
+  }
+  // The pages the admission takes beyond the free ones it may count on (kv_resume_need, engine.cpp:1844-1868).
+  int kv_resume_need(int session, const ResumePlan& plan, const std::vector<int>& prompt) const {
+    const int L = static_cast<int>(prompt.size()), pages = book_.kv_admit_pages(prompt.size());
+    std::vector<int> donor;
+    if (plan.from_kv) donor = kv_tree_->pages(plan.kvm, plan.reuse);
+    int need = book_.pool().resume_need(book_.at(session).table, plan.reuse, pages, plan.from_kv ? &donor : nullptr);
+    // The store's hold reaches up to its last cut: when that cut lies in the page position L is in, the store shares the page
+    // the first decode step writes, which copies it first: one page more.
+    if (kv_tree_ && L < opts_.max_context && pages < book_.pool().capacity()) {
+      const std::vector<int> cuts = kv_store_cuts(prompt, plan.branch_at);
+      if (!cuts.empty() && book_.pool().index_of(cuts.back() - 1) == book_.pool().index_of(L)) need += 1;
+    }
+    return need;
+  }
+  // The positions a prefill of `prompt` adds to the store with a state each (kv_store_cuts, engine.cpp:1870-1884): the end
+  // of each of its first two messages and its branch point, below its end and checkpoint_limit, at multiples of kResumeAlign.
+  std::vector<int> kv_store_cuts(const std::vector<int>& prompt, int branch_at) const {
+    const int L = static_cast<int>(prompt.size());
+    std::vector<int> cuts;
+    for (int i = 0, messages = 0; i < L && messages < 2; ++i)
+      if (prompt[size_t(i)] == opts_.boundary_token) {
+        const int c = i + 1 - (i + 1) % kResumeAlign;
+        if (c > 0) cuts.push_back(c);
+        ++messages;
+      }
+    if (branch_at > 0) cuts.push_back(branch_at);
+    std::erase_if(cuts, [&](int c) { return c >= L || c > opts_.checkpoint_limit; });
+    std::sort(cuts.begin(), cuts.end());
+    cuts.erase(std::unique(cuts.begin(), cuts.end()), cuts.end());
+    return cuts;
+  }
+  // A saved state is named by its arena offset + 1, so that offset 0 is not a null pointer.
+  static void* state_token(size_t offset) { return reinterpret_cast<void*>(offset + 1); }
+  static size_t state_offset(const void* token) { return reinterpret_cast<size_t>(token) - 1; }
+  static constexpr int kSpareStates = 3;  // states saved during a prefill before the tree takes them: two message ends and a branch point
+  void kv_store_setup() {
+    const size_t bytes = ling_b200_state_bytes(ctx_);
+    state_unit_ = (bytes + 255) / 256 * 256;
+    const size_t states = (size_t(opts_.prefix_kv_mb) << 20) / state_unit_;
+    kv_arena_ = std::make_unique<ArenaAlloc>((states + kSpareStates) * state_unit_, 256);
+    if (ling_b200_state_arena_reserve(ctx_, kv_arena_->size()) != LING_B200_OK)
+      throw std::runtime_error(std::string("Engine: prefix KV store: ") + ling_b200_last_error());
+    PrefixKvTree::Ops ops;
+    ops.alloc = [this](size_t n) -> void* {
+      if (handoff_) return std::exchange(handoff_, nullptr);  // a state this prefill already saved becomes the node's
+      size_t off = 0;
+      return kv_arena_->alloc(n, &off) ? state_token(off) : nullptr;
+    };
+    ops.release = [this](void* p) { kv_arena_->release(state_offset(p)); };
+    ops.hold = [this](int from, int to) -> std::vector<int> {
+      const std::vector<int>& table = book_.at(hold_session_).table;
+      const int a = book_.pool().index_of(from), b = book_.pool().index_of(to - 1);
+      if (b >= static_cast<int>(table.size())) return {};
+      for (int j = a; j <= b; ++j)
+        if (table[size_t(j)] == 0) return {};
+      for (int j = a; j <= b; ++j) book_.pool().retain(table[size_t(j)]);
+      return std::vector<int>(table.begin() + a, table.begin() + b + 1);
+    };
+    ops.retain = [this](int page) { book_.pool().retain(page); };
+    ops.drop = [this](int page) { book_.pool().release(page); };
+    kv_tree_ = std::make_unique<PrefixKvTree>(states * state_unit_, 0, state_unit_, std::move(ops), opts_.page_tokens);
+  }
+  // The prompt's shareable beginning (up to its last cut) into the store: new nodes hold the session's pages, and each cut's
+  // state saved during this prefill becomes its node's (kv_insert, engine.cpp:1108-1122).
+  void kv_insert(int session, const std::vector<int>& prompt, const std::vector<int>& cuts, uint64_t epoch, uint64_t scope,
+                 std::vector<std::pair<int, size_t>>& kept) {
+    hold_session_ = session;
+    for (const auto& [node, pos] : kv_tree_->insert(prompt, cuts.back(), cuts, epoch, scope)) {
+      const auto k = std::find_if(kept.begin(), kept.end(), [&](const auto& e) { return e.first == pos; });
+      if (k == kept.end()) continue;
+      handoff_ = state_token(k->second);
+      if (kv_tree_->add_state(node, epoch)) kept.erase(k);
+      handoff_ = nullptr;
+    }
   }
 
   ModelConfig cfg_;
   EngineOptions opts_;
   ling_b200_ctx* ctx_ = nullptr;
   SessionBook book_;
+  std::unique_ptr<ArenaAlloc> kv_arena_;
+  std::unique_ptr<PrefixKvTree> kv_tree_;
+  size_t state_unit_ = 0;
+  void* handoff_ = nullptr;
+  int hold_session_ = 0;
+  uint64_t kv_epoch_ = 0;
+  PrefillStats last_prefill_;
   TreeSource tree_source_;
   PrefillFill prefill_fill_;
   long evictions_ = 0;

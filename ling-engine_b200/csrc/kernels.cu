@@ -1564,7 +1564,7 @@ __global__ void accept_kernel(StepBuffers sb, int vocab) {
     int u = 0;
     R.path[R.n_path++] = 0;
     for (;;) {
-      const int x = q.has_force ? forced[u] : sb.argmax_id[r0 + u];
+      const int x = (q.has_force && forced[u] >= 0) ? forced[u] : sb.argmax_id[r0 + u];  // a negative entry imposes nothing
       int child = -1;
       for (int c = u + 1; c < n; ++c)
         if (par[c] == u && tok[c] == x) {

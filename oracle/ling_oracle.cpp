@@ -1071,7 +1071,7 @@ int step_impl(lo_model* m, const lo_seq_step* seqs, int n_seqs, int flags, lo_se
       if (!std::isfinite(v) || v == -FLT_MAX || id < 0 || id >= c.vocab) R.status = 1;
     }
     std::vector<int> am(n);
-    for (int r = 0; r < n; ++r) am[r] = seqs[s].force_argmax ? seqs[s].force_argmax[r] : m->argmax_id[r0 + r];
+    for (int r = 0; r < n; ++r) am[r] = (seqs[s].force_argmax && seqs[s].force_argmax[r] >= 0) ? seqs[s].force_argmax[r] : m->argmax_id[r0 + r];
     if (R.status) continue;  // nothing committed (src/core/speculate.cpp:1214-1219)
     R.n_path = lo_accept_tree_greedy(seqs[s].parent, seqs[s].tokens, n, am.data(), R.path, &R.next_token);
     // SeqStep::out: the accepted drafts, then the next token (src/core/speculate.cpp:1066-1067)

@@ -9,6 +9,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 PKG = os.path.join(ROOT, "ling-engine_b200")
 EXE = os.path.join(ROOT, "tests", "cpp", "facade_test")
 SCHED = os.path.join(ROOT, "tests", "cpp", "scheduler_test")
+PREFIX = os.path.join(ROOT, "tests", "cpp", "prefix_test")
 
 
 def build(lb, exe=EXE):
@@ -45,4 +46,20 @@ def test_scheduler_continuous_batching_equals_serving_alone(gpu, lb):
     """Six requests through four sessions under the scheduler's continuous batching give, token for token, what each gives alone."""
     build(lb, SCHED)
     out = subprocess.run([SCHED, "gpu"], capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stdout + out.stderr
+
+
+def test_prefix_store_classes_on_the_host(lb):
+    """PrefixKvTree and ArenaAlloc as C++ classes over a KvPool: page references and the copy of a page two prompts share."""
+    build(lb, PREFIX)
+    out = subprocess.run([PREFIX, "host"], capture_output=True, text=True, timeout=120)
+    assert out.returncode == 0, out.stdout + out.stderr
+
+
+@pytest.mark.gpu
+def test_prefix_store_resume_equals_prefill_from_nothing(gpu, lb):
+    """A prompt that resumes from the prefix KV store (pages by reference, state restored, shared page copied before the write)
+    reaches the same state bits and the same tokens as the prompt prefilled from nothing on an engine without a store."""
+    build(lb, PREFIX)
+    out = subprocess.run([PREFIX, "gpu"], capture_output=True, text=True, timeout=600)
     assert out.returncode == 0, out.stdout + out.stderr
