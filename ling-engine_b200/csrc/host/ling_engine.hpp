@@ -534,14 +534,18 @@ class Engine {
   // ---- the prefix KV store as the scheduler sees it (src/core/engine.hpp:444-460; engine.cpp:761-768)
   bool kv_store_on() const { return static_cast<bool>(kv_tree_); }
   const PrefixKvTree* kv_store() const { return kv_tree_.get(); }
-  // The pages that evicting the whole store would free.
-  int kv_store_pages() const {
-    if (!kv_tree_) return 0;
-    const std::vector<std::vector<int>> lists = kv_tree_->page_lists();
+  // The pages freed once the listed sessions and, with `store`, the store's nodes other than `store_keep` are gone: a page
+  // several of them hold counts when all its holders are among them (engine.cpp:741-759).
+  int kv_reclaimable(const std::vector<int>& sessions, bool store, const std::vector<int>& store_keep = {}) const {
+    std::vector<std::vector<int>> lists;
+    if (store && kv_tree_) lists = kv_tree_->page_lists(store_keep);
     KvPool::Refs refs;
+    for (int i : sessions) refs.push_back(&book_.at(i).table);
     for (const std::vector<int>& l : lists) refs.push_back(&l);
     return book_.pool().reclaimable(refs);
   }
+  // The pages that evicting the whole store would free.
+  int kv_store_pages() const { return kv_reclaimable({}, true); }
   // Evicts the store's least recently used leaf outside `keep` (the path an admitted prompt resumes from).
   bool kv_store_evict(const std::vector<int>& keep = {}) { return kv_tree_ && kv_tree_->evict_lru_leaf(keep); }
   // The store nodes a prompt admitted into `session` would resume from (empty: it resumes elsewhere or from nothing).

@@ -11,7 +11,8 @@
 // reference's by golden vectors; this file is the control flow around them.
 //
 // What differs, by design of this build: a prompt's prefill is one unit (the prefill pass is outside this build: the
-// engine's fill hook stands in for it), there is no side stream, no prefix KV store and no donor session, and a pass takes
+// engine's fill hook stands in for it), there is no side stream and no donor session (a prompt resumes from its own session
+// or from the prefix KV store, whose least recently used entries are the first thing given up for pages), and a pass takes
 // up to the engine's max_batch() sequences (the reference: kMaxStreamRows / draft_block = 2).  The loop is single-threaded
 // and step-driven (turn() runs one admission attempt and one unit), so tests and the benchmark replay it deterministically.
 #pragma once
@@ -51,6 +52,7 @@ struct Finished {
 };
 struct SchedulerStats {
   long turns = 0, decode_passes = 0, batched_steps = 0, kv_evictions = 0, kv_pool_exhausted = 0, kv_waits = 0;
+  long kv_store_evictions = 0;  // prefix KV store entries given up for pages
   long rows = 0;  // sequences summed over the decode passes
 };
 
@@ -326,13 +328,22 @@ class SchedulerT {
   }
 
   // ---- the KV page pool (main.cpp:676-843)
-  KvPoolView kv_view(int keep, std::vector<int>* idle = nullptr) {
+  // Whether the engine has a prefix KV store (the real Engine; a host-only test engine need not).
+  static constexpr bool kStore = requires(E& e, const std::vector<int>& v) {
+    e.kv_store_evict(v);
+    e.kv_reclaimable(v, true, v);
+    e.kv_store_path(0, v, uint64_t(0));
+  };
+  // The pool as a unit of session `keep` sees it: free, pending, and what the idle sessions and the store's nodes outside
+  // `store_keep` would free together.
+  KvPoolView kv_view(int keep, std::vector<int>* idle = nullptr, const std::vector<int>& store_keep = {}) {
     std::vector<bool> excl = running_sessions(keep);
     KvPoolView v;
     v.free = eng_.kv_pages_free(), v.pending = eng_.kv_pages_pending();
     std::vector<int> lru;
     for (int s; (s = eng_.kv_lru_idle(excl)) >= 0;) lru.push_back(s), excl[size_t(s)] = true;
-    v.idle = eng_.kv_reclaimable(lru);
+    if constexpr (kStore) v.idle = eng_.kv_reclaimable(lru, true, store_keep);
+    else v.idle = eng_.kv_reclaimable(lru);
     if (idle) *idle = std::move(lru);
     return v;
   }
@@ -342,12 +353,14 @@ class SchedulerT {
     if (keep >= 0) excl[size_t(keep)] = true;
     return excl;
   }
-  // Whether the pages of a unit of session `keep` are free now, evicting idle sessions least recently used first as
-  // kv_reclaim says (protection does not hold against the pool's need).  Without a store or donors the unit has no source
-  // of its own to spare: the kept and the source orders evict the same sessions, and the need does not change as they go.
-  bool kv_make_room(const std::function<int()>& need, int keep, bool cold, bool* evicted) {
+  // Whether the pages of a unit of session `keep` are free now, making room as kv_reclaim says (main.cpp:709-756): first the
+  // holders that may go without moving the unit's resume point -- the store's least recently used leaves outside the path
+  // the unit resumes from (`source`), then idle sessions least recently used first (protection does not hold against the
+  // pool's need) -- and, only when those cannot be enough but everything can (or nothing else will ever free a page), the
+  // unit's own source too, after which it needs `need_cold` pages.  Sessions are never a unit's source in this build.
+  bool kv_make_room(const std::function<int()>& need, int keep, int need_cold, bool* evicted, const std::vector<int>& source = {}) {
     if (need() > eng_.kv_pages_free() + eng_.kv_pages_pending()) {
-      const KvPoolView all = kv_view(keep);
+      const KvPoolView kept = kv_view(keep, nullptr, source), all = kv_view(keep);
       const std::vector<bool> excl = running_sessions(keep);
       const KvEvictNext session = [&] {
         const int s = eng_.kv_lru_idle(excl);
@@ -357,19 +370,37 @@ class SchedulerT {
         ++stats_.kv_evictions;
         return true;
       };
-      const int reach = all.free + all.pending + all.idle;
-      kv_reclaim(need, [&] { return eng_.kv_pages_free() + eng_.kv_pages_pending(); }, {session}, need(), reach, {session}, need(), reach,
-                 running_.empty() && cold);
+      std::vector<KvEvictNext> kept_order, source_order;
+      if constexpr (kStore) {
+        const auto store = [&](const std::vector<int>& keep_nodes) {
+          return [this, evicted, &keep_nodes] {
+            if (!eng_.kv_store_evict(keep_nodes)) return false;
+            if (evicted) *evicted = true;
+            ++stats_.kv_store_evictions;
+            return true;
+          };
+        };
+        static const std::vector<int> no_nodes;
+        kept_order.push_back(store(source));
+        source_order.push_back(store(no_nodes));
+      }
+      kept_order.push_back(session);
+      source_order.push_back(session);
+      kv_reclaim(need, [&] { return eng_.kv_pages_free() + eng_.kv_pages_pending(); }, kept_order, need(),
+                 kept.free + kept.pending + kept.idle, source_order, std::max(need_cold, need()), all.free + all.pending + all.idle,
+                 running_.empty() && need_cold > 0);
     }
     if (running_.empty()) eng_.kv_retire(true);
     return need() <= eng_.kv_pages_free();
   }
   bool kv_admit_room(int s, const Request& q, bool* evicted) {
     const int cold = eng_.kv_admit_need(s, q.prompt, q.share_scope, true);
-    return kv_make_room([&] { return eng_.kv_admit_need(s, q.prompt, q.share_scope); }, s, cold > 0, evicted);
+    std::vector<int> source;
+    if constexpr (kStore) source = eng_.kv_store_path(s, q.prompt, q.share_scope);
+    return kv_make_room([&] { return eng_.kv_admit_need(s, q.prompt, q.share_scope); }, s, cold, evicted, source);
   }
   bool kv_room(Running& r) {
-    return kv_make_room([&] { return eng_.kv_step_need(r.job.session, true); }, r.job.session, false, nullptr);
+    return kv_make_room([&] { return eng_.kv_step_need(r.job.session, true); }, r.job.session, 0, nullptr);
   }
   // main.cpp:791-822: a decode turn waited for pages.  While someone still makes progress, or released pages are on their
   // way, nothing; else the last resort ends the request admitted last as if it had reached the context limit.

@@ -9,7 +9,7 @@
 #include <cstring>
 #include <map>
 
-#include "ling_engine.hpp"
+#include "ling_scheduler.hpp"
 
 static int failures = 0;
 #define EXPECT(cond)                                                \
@@ -275,6 +275,54 @@ static void gpu_checks() {
   EXPECT(eng.kv_store_pages() >= 0 && eng.kv_store_evict() && !eng.kv_store_evict() && eng.kv_store()->nodes() == 0);
   EXPECT(eng.kv_store()->bytes() == 0 && eng.kv_store_pages() == 0);
   std::printf("prefix store: resumed %d of %zu tokens from the store, state and tokens equal to a prefill from nothing\n", 96, p2.size());
+
+  // Under the scheduler: conversations over three system messages queue up for two session slots and a pool of 11 pages
+  // (two running requests take up to 5 each), so the store's entries have to be given up for pages now and then.  Whatever
+  // is resumed, evicted or prefilled again, every request produces what it produces alone on an engine without a store.
+  std::vector<std::vector<int>> systems;
+  for (int k = 0; k < 3; ++k) {
+    std::vector<int> m{kBoundary};
+    for (int i = 0; i < 110; ++i) m.push_back(500 + 700 * k + i * 5);
+    m.push_back(kBoundary);
+    systems.push_back(m);
+  }
+  std::vector<ling::serve::Request> reqs;
+  const int order[8] = {0, 1, 0, 2, 1, 0, 2, 1};
+  for (int i = 0; i < 8; ++i) {
+    ling::serve::Request r;
+    r.prompt = prompt_of(systems[size_t(order[i])], 100 + i, 30 + 9 * i);
+    r.max_tokens = 8 + i;
+    r.sampling.temperature = 0.f;
+    reqs.push_back(r);
+  }
+  ling::EngineOptions small = o;
+  small.sessions = 2, small.kv_pool_pages = 11;
+  std::map<size_t, std::vector<int>> alone;  // by prompt length (all different)
+  {
+    ling::Engine plain(toy_config(), small);
+    setup(plain);
+    ling::serve::Scheduler sch(plain, 1);
+    for (const ling::serve::Request& r : reqs) {
+      sch.submit(r);
+      sch.run_until_idle();
+      const std::vector<ling::serve::Finished> f = sch.take_finished();
+      EXPECT(f.size() == 1 && f[0].finish == "length" && int(f[0].tokens.size()) == r.max_tokens);
+      alone[r.prompt.size()] = f[0].tokens;
+    }
+  }
+  small.prefix_kv_mb = 8;
+  ling::Engine shared_eng(toy_config(), small);
+  setup(shared_eng);
+  ling::serve::Scheduler sch(shared_eng, 2);
+  std::map<long, size_t> len_of;
+  for (const ling::serve::Request& r : reqs) len_of[sch.submit(r)] = r.prompt.size();
+  sch.run_until_idle();
+  const std::vector<ling::serve::Finished> done = sch.take_finished();
+  EXPECT(done.size() == 8);
+  for (const ling::serve::Finished& f : done) EXPECT(f.finish == "length" && f.tokens == alone[len_of[f.id]]);
+  EXPECT(sch.stats().kv_store_evictions > 0 && sch.stats().batched_steps > 0);
+  std::printf("scheduler with the store: %ld store entries and %ld idle sessions evicted for pages, %ld decode passes (%ld shared)\n",
+              sch.stats().kv_store_evictions, sch.stats().kv_evictions, sch.stats().decode_passes, sch.stats().batched_steps);
 }
 
 int main(int argc, char** argv) {
