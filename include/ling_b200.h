@@ -552,6 +552,31 @@ int ling_b200_format_step(double t, long pass, const char* kind, size_t turn, co
                           const int* cand /* [n_cand][3]: session, state, recent */, const long* cand_request,
                           const long* cand_last, int n_cand, double ms, int side, char* buf, int buf_len);
 
+/* ------------------------------------------------------------------------------------------------ the drafter's last stage */
+/* topk_rows (src/core/kernels.cuh:400-410, src/core/topk.cu:83-129) over host rows x [rows][vocab]: per row the k <= 64
+ * largest values, descending, ties to the lower index (entry 0 is the argmax); a row with fewer rankable values (NaN never
+ * ranks) ends in (-FLT_MAX, 0x7fffffff) pairs. */
+int ling_b200_topk_rows_host(int device, const float* x, int rows, int vocab, int k, float* vals, int* ids);
+/* The candidate selector (src/core/kernels.cuh:573-579, src/core/draft_kernels.cu:328-351): scores[e][p][c] = unary[e][c] +
+ * sum_r P[pred(e, p)][r] hp[e][r] S[cand[e][c]][r] over r < 256, pred(0, p) the anchor and pred(e, p) = cand[e - 1][p];
+ * cand / unary [E][16], scores [E][16][16], the predecessor / successor codebooks P, S [vocab][256] as BF16 bit patterns.
+ * With x [E][hidden] and proj_bf16 [256][hidden] given, hp [E][256] = x . proj^T is computed first (and returned in hp:
+ * linear_bf16_drafter over selector_projection, speculate.cpp:610); with x NULL, hp is the input. */
+int ling_b200_selector_lattice_host(int device, const float* x, const uint16_t* proj_bf16, int hidden, float* hp, const int* cand,
+                                    const float* unary, const uint16_t* pred_bf16, const uint16_t* succ_bf16, int vocab, int anchor,
+                                    int E, float* scores);
+/* Engine::draft_launch from its final norm on (src/core/speculate.cpp:598-617) on a context: x [E][hidden] are the drafted
+ * positions' rows after the drafter's final norm; they go through the context's LM head, the top 16 of each row are the
+ * candidates (cand, and their logits in unary when asked for), the selector gives scores [E][16][16]: what build_tree takes.
+ * The selector's weights (BF16 bit patterns: projection [256][hidden], codebooks [vocab][256]) are uploaded at creation; the
+ * handle's device memory belongs to the context and goes with it.  The drafter's transformer body, which produces x, is not
+ * part of this library. */
+typedef struct ling_b200_draft_head ling_b200_draft_head;
+int ling_b200_draft_head_create(ling_b200_ctx* ctx, const uint16_t* selector_projection, const uint16_t* predecessor_codebook,
+                                const uint16_t* successor_codebook, ling_b200_draft_head** out);
+void ling_b200_draft_head_destroy(ling_b200_draft_head* h);
+int ling_b200_draft_head_run(ling_b200_draft_head* h, const float* x, int E, int anchor, int* cand, float* unary, float* scores);
+
 /* Device memory helpers for callers without a CUDA binding (tests): device count, and name of device 0. */
 int ling_b200_device_count(void);
 /* How a step of `rows` packed rows runs: the capacity class its graph is captured for (the token tile up to 128 rows,

@@ -538,6 +538,57 @@ class Nvfp4Ffn:
                     s_gate=float(sc[2]), s_up=float(sc[3]), s_down=float(sc[4]))
 
 
+def topk_rows(x, k, device=0):
+    """Per row the k largest values, descending, ties to the lower index (ling_b200_topk_rows_host)."""
+    x = np.ascontiguousarray(x, np.float32)
+    vals, ids = np.zeros((x.shape[0], k), np.float32), np.zeros((x.shape[0], k), np.int32)
+    check(lib().ling_b200_topk_rows_host(device, _fp(x), x.shape[0], x.shape[1], k, _fp(vals), _ip(ids)), "topk_rows")
+    return vals, ids
+
+
+def _u16(a):
+    return a.ctypes.data_as(C.POINTER(C.c_uint16))
+
+
+def selector_lattice(cand, unary, pred_bits, succ_bits, anchor, hp=None, x=None, proj_bits=None, device=0):
+    """The candidate selector's 16 x 16 scores per position; with x and proj_bits the projection hp = x . proj^T is computed
+    first (returned as the second value).  Codebooks and projection as BF16 bit patterns (to_bf16_bits)."""
+    cand, unary = np.ascontiguousarray(cand, np.int32), np.ascontiguousarray(unary, np.float32)
+    E, vocab = cand.shape[0], pred_bits.shape[0]
+    scores = np.zeros((E, 16, 16), np.float32)
+    if x is not None:
+        x = np.ascontiguousarray(x, np.float32)
+        hp = np.zeros((E, 256), np.float32)
+        check(lib().ling_b200_selector_lattice_host(device, _fp(x), _u16(proj_bits), x.shape[1], _fp(hp), _ip(cand), _fp(unary),
+                                                    _u16(pred_bits), _u16(succ_bits), vocab, int(anchor), E, _fp(scores)), "selector_lattice")
+    else:
+        hp = np.ascontiguousarray(hp, np.float32)
+        check(lib().ling_b200_selector_lattice_host(device, None, None, 0, _fp(hp), _ip(cand), _fp(unary), _u16(pred_bits),
+                                                    _u16(succ_bits), vocab, int(anchor), E, _fp(scores)), "selector_lattice")
+    return scores, hp
+
+
+class DraftHead:
+    """The drafter's last stage on a Context (ling_b200_draft_head_*): rows after the drafter's final norm in, candidates and
+    selector scores out."""
+
+    def __init__(self, ctx, proj_bits, pred_bits, succ_bits):
+        self.ctx, self.h = ctx, C.c_void_p()
+        check(lib().ling_b200_draft_head_create(ctx.h, _u16(proj_bits), _u16(pred_bits), _u16(succ_bits), C.byref(self.h)), "draft_head_create")
+
+    def run(self, x, anchor):
+        x = np.ascontiguousarray(x, np.float32)
+        E = x.shape[0]
+        cand, unary, scores = np.zeros((E, 16), np.int32), np.zeros((E, 16), np.float32), np.zeros((E, 16, 16), np.float32)
+        check(lib().ling_b200_draft_head_run(self.h, _fp(x), E, int(anchor), _ip(cand), _fp(unary), _fp(scores)), "draft_head_run")
+        return cand, unary, scores
+
+    def close(self):
+        if self.h:
+            lib().ling_b200_draft_head_destroy(self.h)
+            self.h = C.c_void_p()
+
+
 def describe_tree(parent, chain):
     par = np.ascontiguousarray(parent, np.int32)
     t = TreeDesc()

@@ -10,6 +10,7 @@
 #include <vector>
 
 #include "chain.h"
+#include "draft_head.h"
 #include "gemm.h"
 #include "kernels.h"
 
@@ -1442,6 +1443,94 @@ int ling_b200_read_tap(ling_b200_ctx* c, int layer, float* out) {
   LB_CUDA(cudaMemcpy(out, c->taps + size_t(layer) * c->opt.debug_rows * c->d.H, size_t(c->last_rows) * c->d.H * 4,
                      cudaMemcpyDeviceToHost));
   return LING_B200_OK;
+}
+
+// ------------------------------------------------------------------------------------------------ the drafter's last stage
+// Engine::draft_launch from its final norm on (src/core/speculate.cpp:598-617) and draft_head's full-head branch
+// (speculate.cpp:405-416): the drafted rows through the target's LM head (this context's FP8 head and activation
+// quantizer), the top 16 of each row, the selector's projection and lattice; candidates and scores come back to the host,
+// where build_tree takes them.  The weights of the selector are uploaded once.
+}  // extern "C"
+
+struct ling_b200_draft_head {
+  ling_b200_ctx* c = nullptr;
+  __nv_bfloat16 *proj = nullptr, *pred = nullptr, *succ = nullptr;
+  float *x = nullptr, *logits = nullptr, *hp = nullptr, *unary = nullptr, *scores = nullptr, *scratch = nullptr;
+  int* cand = nullptr;
+  int max_rows = 0;
+};
+
+extern "C" {
+
+int ling_b200_draft_head_create(ling_b200_ctx* c, const uint16_t* selector_projection, const uint16_t* predecessor_codebook,
+                                const uint16_t* successor_codebook, ling_b200_draft_head** out) {
+  LB_TRY(check_ctx(c));
+  if (!selector_projection || !predecessor_codebook || !successor_codebook || !out || c->d.H % 256 != 0) {
+    set_error("draft_head_create: bad argument (the hidden size must be a multiple of 256)");
+    return LING_B200_ERR_ARG;
+  }
+  auto* h = new ling_b200_draft_head;
+  h->c = c;
+  h->max_rows = std::min(kTreeRows - 1, c->d.rows_alloc);
+  const size_t V = size_t(c->d.V), R = size_t(h->max_rows);
+  auto up = [&](__nv_bfloat16** dst, const uint16_t* src, size_t n) -> int {
+    LB_TRY(c->alloc(dst, n, false));
+    LB_CUDA(cudaMemcpy(*dst, src, n * 2, cudaMemcpyHostToDevice));
+    return LING_B200_OK;
+  };
+  int rc = up(&h->proj, selector_projection, size_t(kSelRank) * c->d.H);
+  if (rc == LING_B200_OK) rc = up(&h->pred, predecessor_codebook, V * kSelRank);
+  if (rc == LING_B200_OK) rc = up(&h->succ, successor_codebook, V * kSelRank);
+  if (rc == LING_B200_OK) rc = c->alloc(&h->x, R * c->d.H);
+  if (rc == LING_B200_OK) rc = c->alloc(&h->logits, R * V, false);
+  if (rc == LING_B200_OK) rc = c->alloc(&h->hp, R * kSelRank);
+  if (rc == LING_B200_OK) rc = c->alloc(&h->unary, R * kSelTop);
+  if (rc == LING_B200_OK) rc = c->alloc(&h->cand, R * kSelTop);
+  if (rc == LING_B200_OK) rc = c->alloc(&h->scores, R * kSelTop * kSelTop);
+  if (rc == LING_B200_OK) rc = c->alloc(&h->scratch, topk_scratch_floats(h->max_rows, c->d.V, kSelTop));
+  if (rc != LING_B200_OK) {  // what was allocated stays with the context and is freed with it
+    delete h;
+    return rc;
+  }
+  *out = h;
+  return LING_B200_OK;
+}
+void ling_b200_draft_head_destroy(ling_b200_draft_head* h) { delete h; }  // its device memory belongs to the context
+
+int ling_b200_draft_head_run(ling_b200_draft_head* h, const float* x, int E, int anchor, int* cand, float* unary, float* scores) {
+  if (!h) {
+    set_error("draft_head_run: no handle");
+    return LING_B200_ERR_ARG;
+  }
+  ling_b200_ctx* c = h->c;
+  LB_TRY(check_ctx(c));
+  if (!x || !cand || !scores || E < 1 || E > h->max_rows || anchor < 0 || anchor >= c->d.V) {
+    set_error("draft_head_run: bad argument (1 <= rows <= 31 and within the context's row capacity; the anchor a token id)");
+    return LING_B200_ERR_ARG;
+  }
+  LB_TRY(finish(c));  // the head's activation buffer is the step's
+  cudaStream_t s = c->stream;
+  LB_CUDA(cudaMemcpyAsync(h->x, x, size_t(E) * c->d.H * 4, cudaMemcpyHostToDevice, s));
+  LB_TRY(quant_acts_launch(h->x, E, c->qout(c->xq_h), s));
+  {
+    HeadEpilogue ep = c->head_ep;
+    ep.store_logits = true;
+    GemmCall g;
+    g.W = &c->head, g.X = &c->xq_h, g.M = E;
+    g.out = h->logits, g.ld = c->head.N;
+    g.split_stride = size_t(c->d.rows_alloc) * c->head.N_pad;
+    g.head = &ep;
+    g.impl = c->opt.gemm_impl;
+    g.err_flag = c->sb.err;
+    LB_TRY(gemm_launch(g, s));
+  }
+  LB_TRY(topk_rows_launch(h->logits, E, c->d.V, kSelTop, h->scratch, h->unary, h->cand, s));
+  LB_TRY(selector_project_launch(h->x, h->proj, E, c->d.H, h->hp, s));
+  LB_TRY(selector_lattice_launch(h->hp, h->cand, h->unary, h->pred, h->succ, c->d.V, anchor, nullptr, E, h->scores, c->sb.err, s));
+  LB_CUDA(cudaMemcpyAsync(cand, h->cand, size_t(E) * kSelTop * 4, cudaMemcpyDeviceToHost, s));
+  if (unary) LB_CUDA(cudaMemcpyAsync(unary, h->unary, size_t(E) * kSelTop * 4, cudaMemcpyDeviceToHost, s));
+  LB_CUDA(cudaMemcpyAsync(scores, h->scores, size_t(E) * kSelTop * kSelTop * 4, cudaMemcpyDeviceToHost, s));
+  return read_err(c);
 }
 
 }  // extern "C"

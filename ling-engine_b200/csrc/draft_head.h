@@ -1,0 +1,24 @@
+// The drafter's last stage (draft_head.cu): top-K of logit rows, the candidate selector's projection and its lattice.
+#pragma once
+
+#include "../../include/ling_b200.h"
+#include "common.cuh"
+
+namespace lb {
+
+constexpr int kTopMaxK = 64;   // topk_rows takes K <= 64 (src/core/kernels.cuh:400-410)
+constexpr int kSelTop = 16;    // candidates per drafted position (DraftConfig::selector_top_k)
+constexpr int kSelRank = 256;  // width of the selector's projection and of its two codebooks (draft_kernels.cu:330)
+
+// Top-K of each row of x [rows][V]: values descending, ties to the lower index; a row with fewer than K rankable values
+// (NaN never ranks) ends in (-FLT_MAX, 0x7fffffff) pairs.  scratch: topk_scratch_floats(rows, V, K) floats.
+size_t topk_scratch_floats(int rows, int V, int K);
+int topk_rows_launch(const float* x, int rows, int V, int K, float* scratch, float* vals, int* ids, cudaStream_t s);
+// hp [E][256] = x [E][H] . W^T, W [256][H] BF16, H a multiple of 256.
+int selector_project_launch(const float* x, const __nv_bfloat16* W, int E, int H, float* hp, cudaStream_t s);
+// scores [E][16][16] from hp [E][256], cand / unary [E][16] and the predecessor / successor codebooks [vocab][256] BF16.
+// anchor_dev, when given, is read instead of `anchor`.  An id outside [0, vocab) sets the error word (code 7) and is clamped.
+int selector_lattice_launch(const float* hp, const int* cand, const float* unary, const __nv_bfloat16* P, const __nv_bfloat16* S,
+                            int vocab, int anchor, const int* anchor_dev, int E, float* scores, int* err, cudaStream_t s);
+
+}  // namespace lb

@@ -4,6 +4,7 @@
 #include <vector>
 
 #include "abi_util.h"
+#include "draft_head.h"
 #include "chain.h"
 #include "gemm.h"
 #include "kernels.h"
@@ -426,6 +427,64 @@ int ling_b200_argmax_host(int device, const float* logits, int rows, int vocab, 
   LB_CUDA(cudaDeviceSynchronize());
   LB_CUDA(cudaMemcpy(ids, d_i, size_t(rows) * 4, cudaMemcpyDeviceToHost));
   LB_CUDA(cudaMemcpy(vals, d_v, size_t(rows) * 4, cudaMemcpyDeviceToHost));
+  return LING_B200_OK;
+}
+
+// topk_rows (src/core/topk.cu:83-129) over host rows.
+int ling_b200_topk_rows_host(int device, const float* x, int rows, int vocab, int k, float* vals, int* ids) {
+  if (!x || !ids || !vals || rows < 1 || vocab < 1 || k < 1 || k > kTopMaxK) {
+    set_error("topk_rows_host: bad argument (1 <= k <= 64)");
+    return LING_B200_ERR_ARG;
+  }
+  LB_TRY(check_device(device));
+  Scratch sc;
+  float* d_x = sc.put(x, size_t(rows) * vocab);
+  float* d_s = sc.get<float>(topk_scratch_floats(rows, vocab, k));
+  int* d_i = sc.get<int>(size_t(rows) * k);
+  float* d_v = sc.get<float>(size_t(rows) * k);
+  LB_PTR(d_x && d_s && d_i && d_v);
+  LB_TRY(topk_rows_launch(d_x, rows, vocab, k, d_s, d_v, d_i, 0));
+  LB_CUDA(cudaDeviceSynchronize());
+  LB_CUDA(cudaMemcpy(ids, d_i, size_t(rows) * k * 4, cudaMemcpyDeviceToHost));
+  LB_CUDA(cudaMemcpy(vals, d_v, size_t(rows) * k * 4, cudaMemcpyDeviceToHost));
+  return LING_B200_OK;
+}
+
+// The candidate selector over host buffers: its projection (x [E][hidden] . W^T, W [256][hidden] BF16) when x and W are
+// given (else hp is an input), then selector_lattice (src/core/draft_kernels.cu:328-351).
+int ling_b200_selector_lattice_host(int device, const float* x, const uint16_t* proj_bf16, int hidden, float* hp, const int* cand,
+                                    const float* unary, const uint16_t* pred_bf16, const uint16_t* succ_bf16, int vocab, int anchor,
+                                    int E, float* scores) {
+  if (!hp || !cand || !unary || !pred_bf16 || !succ_bf16 || !scores || E < 1 || vocab < 1 || (x && (!proj_bf16 || hidden % 256 != 0))) {
+    set_error("selector_lattice_host: bad argument");
+    return LING_B200_ERR_ARG;
+  }
+  LB_TRY(check_device(device));
+  Scratch sc;
+  float* d_hp = x ? sc.get<float>(size_t(E) * kSelRank) : sc.put(hp, size_t(E) * kSelRank);
+  const int* d_c = sc.put(cand, size_t(E) * kSelTop);
+  const float* d_u = sc.put(unary, size_t(E) * kSelTop);
+  const auto* d_p = reinterpret_cast<const __nv_bfloat16*>(sc.put(pred_bf16, size_t(vocab) * kSelRank));
+  const auto* d_s = reinterpret_cast<const __nv_bfloat16*>(sc.put(succ_bf16, size_t(vocab) * kSelRank));
+  float* d_o = sc.get<float>(size_t(E) * kSelTop * kSelTop);
+  int* d_err = sc.get<int>(1);
+  LB_PTR(d_hp && d_c && d_u && d_p && d_s && d_o && d_err);
+  if (x) {
+    const float* d_x = sc.put(x, size_t(E) * hidden);
+    const auto* d_w = reinterpret_cast<const __nv_bfloat16*>(sc.put(proj_bf16, size_t(kSelRank) * hidden));
+    LB_PTR(d_x && d_w);
+    LB_TRY(selector_project_launch(d_x, d_w, E, hidden, d_hp, 0));
+  }
+  LB_TRY(selector_lattice_launch(d_hp, d_c, d_u, d_p, d_s, vocab, anchor, nullptr, E, d_o, d_err, 0));
+  LB_CUDA(cudaDeviceSynchronize());
+  int err = 0;
+  LB_CUDA(cudaMemcpy(&err, d_err, 4, cudaMemcpyDeviceToHost));
+  LB_CUDA(cudaMemcpy(scores, d_o, size_t(E) * kSelTop * kSelTop * 4, cudaMemcpyDeviceToHost));
+  if (x) LB_CUDA(cudaMemcpy(hp, d_hp, size_t(E) * kSelRank * 4, cudaMemcpyDeviceToHost));
+  if (err) {
+    set_error("selector_lattice_host: a candidate or the anchor is not a token id (device error word = " + std::to_string(err) + ")");
+    return LING_B200_ERR_DEVICE_FLAG;
+  }
   return LING_B200_OK;
 }
 

@@ -521,6 +521,53 @@ void lo_argmax(const float* logits, int rows, int vocab, int* ids, float* vals) 
   }
 }
 
+// topk_rows for K <= 64 (src/core/topk.cu:83-129; kernels.cuh:400-410): per row the K largest values, descending, equal
+// values to the lower index, NaN skipped; past the rankable values (-FLT_MAX, 0x7fffffff).
+void lo_topk_rows(const float* x, int rows, int vocab, int k, float* vals, int* ids) {
+  for (int r = 0; r < rows; ++r) {
+    std::vector<std::pair<float, int>> best;  // kept in rank order
+    for (int i = 0; i < vocab; ++i) {
+      const float v = x[size_t(r) * vocab + i];
+      if (v != v || !(v > -FLT_MAX)) continue;
+      if (int(best.size()) == k && !(v > best.back().first)) continue;  // equal to the last: the earlier index stays
+      size_t at = best.size();
+      while (at > 0 && v > best[at - 1].first) --at;
+      best.insert(best.begin() + long(at), {v, i});
+      if (int(best.size()) > k) best.pop_back();
+    }
+    for (int j = 0; j < k; ++j) {
+      vals[size_t(r) * k + j] = j < int(best.size()) ? best[size_t(j)].first : -FLT_MAX;
+      ids[size_t(r) * k + j] = j < int(best.size()) ? best[size_t(j)].second : 0x7fffffff;
+    }
+  }
+}
+
+// The candidate selector (src/core/draft_kernels.cu:328-351): score[e][p][c] = unary[e][c] + sum_r P[pred(e, p)][r] *
+// hp[e][r] * S[cand[e][c]][r], pred(0, p) = the anchor, pred(e, p) = cand[e - 1][p]; 16 candidates, rank 256, the codebooks
+// rounded to BF16 as the reference keeps them, the sum in double.
+void lo_selector_lattice(const float* hp, const int* cand, const float* unary, const float* P, const float* S, int anchor, int E,
+                         float* scores) {
+  for (int e = 0; e < E; ++e)
+    for (int p = 0; p < 16; ++p)
+      for (int c = 0; c < 16; ++c) {
+        const int pid = e == 0 ? anchor : cand[(e - 1) * 16 + p], cid = cand[e * 16 + c];
+        double acc = 0;
+        for (int r = 0; r < 256; ++r)
+          acc += double(bf16r(P[size_t(pid) * 256 + r])) * double(hp[size_t(e) * 256 + r]) * double(bf16r(S[size_t(cid) * 256 + r]));
+        scores[(size_t(e) * 16 + p) * 16 + c] = float(double(unary[e * 16 + c]) + acc);
+      }
+}
+// hp[e][j] = x[e] . W[j] with W [256][H] rounded to BF16 (linear_bf16_drafter over the selector's projection,
+// src/core/speculate.cpp:610), the sum in double.
+void lo_selector_project(const float* x, const float* W, int E, int H, float* hp) {
+  for (int e = 0; e < E; ++e)
+    for (int j = 0; j < 256; ++j) {
+      double acc = 0;
+      for (int h = 0; h < H; ++h) acc += double(x[size_t(e) * H + h]) * double(bf16r(W[size_t(j) * H + h]));
+      hp[size_t(e) * 256 + j] = float(acc);
+    }
+}
+
 // ---------------------------------------------------------------------------------------------- model
 
 lo_model* lo_create(const lo_model_config* cfg, const lo_options* opt) {

@@ -92,6 +92,10 @@ void lo_gdn_tree(int Hk, int HV, int Dk, int Dv, const lo_tree_desc* td, const f
 void lo_gdn_commit(int Hk, int HV, int Dk, int Dv, const int* path, int n, int rows, const float* pre,
                    const float* post, const float* g, const float* beta, float* state, float* conv);
 void lo_argmax(const float* logits, int rows, int vocab, int* ids, float* vals);
+void lo_topk_rows(const float* x, int rows, int vocab, int k, float* vals, int* ids);
+void lo_selector_lattice(const float* hp, const int* cand, const float* unary, const float* P, const float* S, int anchor, int E,
+                         float* scores);
+void lo_selector_project(const float* x, const float* W, int E, int H, float* hp);
 
 /* model + sessions */
 lo_model* lo_create(const lo_model_config* cfg, const lo_options* opt);

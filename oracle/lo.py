@@ -138,6 +138,29 @@ def argmax(logits):
     return ids, vals
 
 
+def topk_rows(x, k):
+    x = np.ascontiguousarray(x, np.float32)
+    ids, vals = np.zeros((x.shape[0], k), np.int32), np.zeros((x.shape[0], k), np.float32)
+    lo().lo_topk_rows(_fp(x), x.shape[0], x.shape[1], k, _fp(vals), _ip(ids))
+    return vals, ids
+
+
+def selector_project(x, W):
+    x, W = np.ascontiguousarray(x, np.float32), np.ascontiguousarray(W, np.float32)
+    hp = np.zeros((x.shape[0], 256), np.float32)
+    lo().lo_selector_project(_fp(x), _fp(W), x.shape[0], x.shape[1], _fp(hp))
+    return hp
+
+
+def selector_lattice(hp, cand, unary, P, S, anchor):
+    hp, unary = np.ascontiguousarray(hp, np.float32), np.ascontiguousarray(unary, np.float32)
+    cand = np.ascontiguousarray(cand, np.int32)
+    P, S = np.ascontiguousarray(P, np.float32), np.ascontiguousarray(S, np.float32)
+    scores = np.zeros((hp.shape[0], 16, 16), np.float32)
+    lo().lo_selector_lattice(_fp(hp), _ip(cand), _fp(unary), _fp(P), _fp(S), int(anchor), hp.shape[0], _fp(scores))
+    return scores
+
+
 class Model:
     """The oracle's model + sessions; the same method names as the product binding's Context."""
 

@@ -1,8 +1,8 @@
-// ref_cuda_shim.cu -- C wrappers around the REFERENCE's own CUDA kernels (src/core/kernels.cu, src/core/topk.cu of
+// ref_cuda_shim.cu -- C wrappers around the REFERENCE's own CUDA kernels (src/core/kernels.cu, topk.cu, draft_kernels.cu of
 // dreamference/ling-engine), compiled for sm_100a from where the sources lie into oracle/_ref/libling_refcuda.so (see
 // oracle/Makefile, target ref_cuda).  TEST INFRASTRUCTURE ONLY.  Nothing of the reference is copied into this repository:
 // this file includes the reference's header and calls its launchers on device copies of host buffers, so that the CPU
-// oracle's fp32 math (conv over trees, gating, the gated delta rule, gated RMSNorm, head norms + rotation, top-1) and the
+// oracle's fp32 math (conv over trees, gating, the gated delta rule, gated RMSNorm, head norms + rotation, top-K, the candidate selector's lattice) and the
 // product's kernels can be compared with what the reference itself computes on the same GPU.
 //
 // The reference's kernels are built for its 27B shapes only (DeltaNet key/value dim 128, attention head dim 256 with six
@@ -203,6 +203,33 @@ int refcuda_top1(const float* logits, int rows, int V, int* ids, float* vals) {
     sync();
     fetch(ids, d_i, rows);
     fetch(vals, d_v, rows);
+  });
+}
+
+// topk_rows for any K <= 64 (src/core/topk.cu:83-129): values descending, ties to the lower index.
+int refcuda_topk(const float* logits, int rows, int V, int K_, int* ids, float* vals) {
+  return guarded([&] {
+    Dev d;
+    int* d_i = d.get<int>(size_t(rows) * K_);
+    float* d_v = d.get<float>(size_t(rows) * K_);
+    K::topk_rows(d.put(logits, size_t(rows) * V), rows, V, K_, d.get<float>(K::topk_scratch_floats(rows, K_)), d_v, d_i, 0);
+    sync();
+    fetch(ids, d_i, size_t(rows) * K_);
+    fetch(vals, d_v, size_t(rows) * K_);
+  });
+}
+
+// selector_lattice (src/core/draft_kernels.cu:328-351): hp [E][256], cand / unary [E][16], the two codebooks [vocab][256]
+// given as fp32 and rounded to BF16 here, scores [E][16][16].
+int refcuda_selector_lattice(const float* hp, const int* cand, const float* unary, const float* P, const float* S, int vocab,
+                             int anchor, int E, float* scores) {
+  return guarded([&] {
+    Dev d;
+    float* d_s = d.get<float>(size_t(E) * 256);
+    K::selector_lattice(d.put(hp, size_t(E) * 256), d.put(cand, size_t(E) * 16), d.put(unary, size_t(E) * 16),
+                        d.put_bf16(P, size_t(vocab) * 256), d.put_bf16(S, size_t(vocab) * 256), anchor, E, d_s, 0);
+    sync();
+    fetch(scores, d_s, size_t(E) * 256);
   });
 }
 
