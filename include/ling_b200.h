@@ -552,6 +552,19 @@ int ling_b200_format_step(double t, long pass, const char* kind, size_t turn, co
                           const int* cand /* [n_cand][3]: session, state, recent */, const long* cand_request,
                           const long* cand_last, int n_cand, double ms, int side, char* buf, int buf_len);
 
+/* ------------------------------------------------------------------------------------------------ the prefill path's DeltaNet core */
+/* gdn_conv_prefill + gdn_recurrent_prefill (src/core/kernels.cuh:445-456; src/core/prefill_gdn.cu:34-142) over the M rows
+ * of one sequence, host buffers: pre [M][C] the raw in-projection rows (q | k | v channels, C = 2 Hk Dk + HV Dv), convw_bf16
+ * [C][4] the conv taps as BF16 bit patterns, g / beta [M][HV]; conv [C][3] (the window) and state [HV][Dk][Dv] are read and
+ * advanced in place; post [M][C] (optional) = silu(conv(pre)), core [M][HV Dv] the recurrence's output.  The recurrence runs
+ * in its chunked (WY) form, 32-token chunks from the first row on, FP16 tensor-core products with fp32 accumulation, so its
+ * result differs from the token-by-token fp32 rule by FP16 operand rounding (the reference's prefill kernel likewise).
+ * Dk = Dv = 128. */
+int ling_b200_gdn_prefill_host(int device, int Hk, int HV, int Dk, int Dv, int M, const float* pre, const uint16_t* convw_bf16,
+                               const float* g, const float* beta, float* state, float* conv, float* post, float* core);
+/* Device time (ms per launch) of the chunked delta rule alone over M rows of synthetic inputs. */
+int ling_b200_gdn_chunk_bench(int device, int Hk, int HV, int M, int iters, float* ms);
+
 /* ------------------------------------------------------------------------------------------------ the drafter's last stage */
 /* topk_rows (src/core/kernels.cuh:400-410, src/core/topk.cu:83-129) over host rows x [rows][vocab]: per row the k <= 64
  * largest values, descending, ties to the lower index (entry 0 is the argmax); a row with fewer rankable values (NaN never

@@ -538,6 +538,24 @@ class Nvfp4Ffn:
                     s_gate=float(sc[2]), s_up=float(sc[3]), s_down=float(sc[4]))
 
 
+def gdn_prefill(Hk, HV, Dk, Dv, pre, convw_bits, g, beta, state, conv, device=0):
+    """The prefill path's DeltaNet core over the rows of one sequence (ling_b200_gdn_prefill_host): returns post, core and the
+    advanced state and window."""
+    pre, g, beta = (np.ascontiguousarray(a, np.float32) for a in (pre, g, beta))
+    state, conv = np.array(state, np.float32, order="C"), np.array(conv, np.float32, order="C")
+    M, Cc = pre.shape
+    post, core = np.zeros((M, Cc), np.float32), np.zeros((M, HV * Dv), np.float32)
+    check(lib().ling_b200_gdn_prefill_host(device, Hk, HV, Dk, Dv, M, _fp(pre), _u16(convw_bits), _fp(g), _fp(beta), _fp(state), _fp(conv),
+                                           _fp(post), _fp(core)), "gdn_prefill")
+    return post, core, state, conv
+
+
+def gdn_chunk_bench(Hk, HV, M, iters=10, device=0):
+    ms = C.c_float()
+    check(lib().ling_b200_gdn_chunk_bench(device, Hk, HV, M, iters, C.byref(ms)), "gdn_chunk_bench")
+    return ms.value
+
+
 def topk_rows(x, k, device=0):
     """Per row the k largest values, descending, ties to the lower index (ling_b200_topk_rows_host)."""
     x = np.ascontiguousarray(x, np.float32)

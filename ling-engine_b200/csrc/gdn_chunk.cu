@@ -1,0 +1,282 @@
+// gdn_chunk.cu -- the gated delta rule over many tokens of one sequence (a prefill chunk), in its chunked (WY) form.
+//
+// The verify step's kernels walk a tree's few rows token by token; 4096 rows of a prefill chunk would be 4096 dependent
+// steps per head.  Unrolled over a chunk of T = 32 tokens with start state S0 [Dk][Dv], cumulative log-decay G_i and
+// gamma_i = exp(G_i), the recurrence S_i = a_i S_(i-1) + k_i beta_i (v_i - a_i S_(i-1)^T k_i)^T, o_i = S_i^T q_i becomes
+//   A_ij   = beta_i exp(G_i - G_j) k_i . k_j  (j < i),        Tinv = (I + A)^-1  (forward substitution, fp32)
+//   U      = Tinv (beta v),   W = Tinv (beta gamma k),        Delta = U - W S0
+//   O      = diag(gamma) Q S0 + [exp(G_i - G_j) q_i . k_j]_(j <= i) Delta
+//   S_next = gamma_T S0 + K'^T Delta,   k'_i = (gamma_T / gamma_i) k_i
+// (the reference's chunk_gdn_kernel, src/core/prefill_gdn.cu:75-142, restated).  Every product is a small matrix product
+// with a 32-row operand: they run as FP16 m16n8k16 MMAs with fp32 accumulation from shared memory -- tiles of 32 rows are
+// below the 64-row minimum of tcgen05.mma, and the chain of chunks is bound by its dependent steps, not by tensor
+// throughput.  The state stays in fp32 registers (the accumulator layout of its own update) and is multiplied as an FP16
+// copy; q and k arrive un-normalized (the conv's output) and are L2-normalized here, q also scaled by 1/sqrt(Dk).
+// One CTA of 16 warps per value head walks the chunks in order.  Key and value dimension 128.
+#include <cuda_fp16.h>
+
+#include "gdn_chunk.h"
+
+namespace lb {
+namespace {
+
+constexpr int kD = 128, kT = 32, kThreads = 512;
+constexpr int kLdD = 136;  // halves per row of a [*][128] tile: rows 68 words apart, the 8 x 4 fragment loads hit 32 banks
+constexpr int kLdT = 40;   // halves per row of a [*][32] tile
+
+struct ChunkSmem {
+  __half q[kT * kLdD];     // q^ [i][d]
+  __half k[kT * kLdD];     // k^ [i][d]
+  __half w[kT * kLdD];     // W [i][d]
+  __half bvT[kD * kLdT];   // (beta v)^T [c][j]
+  __half bgkT[kD * kLdT];  // (beta gamma k^)^T [d][j]
+  __half kpT[kD * kLdT];   // k'^T [d][j]
+  __half dT[kD * kLdT];    // Delta^T [c][j]
+  __half sT[kD * kLdD];    // S0^T [c][d]
+  __half tinv[kT * kLdT];  // Tinv [i][j]
+  __half p[kT * kLdT];     // exp(G_i - G_j) q_i . k_j, j <= i
+  float a[kT][kT + 1];     // A, fp32 for the substitution
+  float G[kT], gam[kT], beta[kT];
+};
+
+__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t ld32(const __half* p) { return *reinterpret_cast<const uint32_t*>(p); }
+
+// c (16 x 8 at rows m0, columns n0) += A[m0 .., 0 .. K) . B[n0 .., 0 .. K)^T; A [m][k] and B [n][k], both with k contiguous.
+// Fragment layout of mma.m16n8k16: lane = 4 gq + tq holds A rows gq, gq + 8 at k = 2 tq, 2 tq + 1 (+8), B column gq at the
+// same k, and C rows gq, gq + 8 at columns 2 tq, 2 tq + 1.
+__device__ __forceinline__ void tile_mma(float (&c)[4], const __half* A, int lda, int m0, const __half* B, int ldb, int n0, int K,
+                                         int gq, int tq) {
+  const __half* ar = A + (m0 + gq) * lda + 2 * tq;
+  const __half* br = B + (n0 + gq) * ldb + 2 * tq;
+#pragma unroll
+  for (int k0 = 0; k0 < K; k0 += 16)
+    mma16816(c, ld32(ar + k0), ld32(ar + 8 * lda + k0), ld32(ar + k0 + 8), ld32(ar + 8 * lda + k0 + 8), ld32(br + k0), ld32(br + k0 + 8));
+}
+__device__ __forceinline__ uint32_t h2(float lo, float hi) {
+  const __half2 v = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+    gdn_chunk_kernel(const float* __restrict__ post, const float* __restrict__ g, const float* __restrict__ beta, int M, int Hk, int HV,
+                     float* __restrict__ state, float* __restrict__ core) {
+  pdl_sync();  // first statement: see common.cuh
+  extern __shared__ __align__(16) unsigned char raw_smem[];
+  ChunkSmem& sm = *reinterpret_cast<ChunkSmem*>(raw_smem);
+  const int hv = blockIdx.x, h = hv / (HV / Hk), tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int gq = lane >> 2, tq = lane & 3;
+  const int C = 2 * Hk * kD + HV * kD;
+  float* st = state + size_t(hv) * kD * kD;
+  // The state in the accumulator layout of its update: warp w owns the value columns 8 w .. 8 w + 7, S[mt][*] the key rows
+  // 16 mt + gq (two of them: +8) at columns 8 w + 2 tq, + 1.
+  float S[8][4];
+#pragma unroll
+  for (int mt = 0; mt < 8; ++mt) {
+    const int d = mt * 16 + gq, c = warp * 8 + 2 * tq;
+    const float2 lo = *reinterpret_cast<const float2*>(st + size_t(d) * kD + c);
+    const float2 hi = *reinterpret_cast<const float2*>(st + size_t(d + 8) * kD + c);
+    S[mt][0] = lo.x, S[mt][1] = lo.y, S[mt][2] = hi.x, S[mt][3] = hi.y;
+  }
+  auto publish_state = [&] {  // the FP16 copy, transposed: sT[c][d]
+#pragma unroll
+    for (int mt = 0; mt < 8; ++mt) {
+      const int d = mt * 16 + gq, c = warp * 8 + 2 * tq;
+      sm.sT[c * kLdD + d] = __float2half_rn(S[mt][0]), sm.sT[(c + 1) * kLdD + d] = __float2half_rn(S[mt][1]);
+      sm.sT[c * kLdD + d + 8] = __float2half_rn(S[mt][2]), sm.sT[(c + 1) * kLdD + d + 8] = __float2half_rn(S[mt][3]);
+    }
+  };
+  publish_state();
+
+  for (int c0 = 0; c0 < M; c0 += kT) {
+    const int n = min(kT, M - c0);  // rows past n: k = v = 0, beta = 0, g = 0 -- they change nothing and are not stored
+    // ---- gates: cumulative log-decay by warp 0
+    if (warp == 0) {
+      const float gi = lane < n ? g[size_t(c0 + lane) * HV + hv] : 0.f;
+      float G = gi;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const float up = __shfl_up_sync(0xffffffffu, G, o);
+        if (lane >= o) G += up;
+      }
+      sm.G[lane] = G, sm.gam[lane] = __expf(G);
+      sm.beta[lane] = lane < n ? beta[size_t(c0 + lane) * HV + hv] : 0.f;
+    }
+    __syncthreads();
+    // ---- q^, k^ (two rows a warp, four elements a lane), and k^ scaled for W and for the state update
+    const float G_last = sm.G[kT - 1];
+    for (int i = 2 * warp; i < 2 * warp + 2; ++i) {
+      float4 qv = make_float4(0.f, 0.f, 0.f, 0.f), kv = qv;
+      if (i < n) {
+        const float* row = post + size_t(c0 + i) * C;
+        qv = *reinterpret_cast<const float4*>(row + h * kD + 4 * lane);
+        kv = *reinterpret_cast<const float4*>(row + Hk * kD + h * kD + 4 * lane);
+      }
+      const float sq = warp_sum(qv.x * qv.x + qv.y * qv.y + qv.z * qv.z + qv.w * qv.w);
+      const float sk = warp_sum(kv.x * kv.x + kv.y * kv.y + kv.z * kv.z + kv.w * kv.w);
+      const float cq = rsqrtf(sq + 1e-6f) * rsqrtf(float(kD)), ck = rsqrtf(sk + 1e-6f);
+      const float kx[4] = {kv.x * ck, kv.y * ck, kv.z * ck, kv.w * ck};
+      uint32_t* qd = reinterpret_cast<uint32_t*>(sm.q + i * kLdD + 4 * lane);
+      uint32_t* kd = reinterpret_cast<uint32_t*>(sm.k + i * kLdD + 4 * lane);
+      qd[0] = h2(qv.x * cq, qv.y * cq), qd[1] = h2(qv.z * cq, qv.w * cq);
+      kd[0] = h2(kx[0], kx[1]), kd[1] = h2(kx[2], kx[3]);
+      const float bg = sm.beta[i] * sm.gam[i], kp = __expf(G_last - sm.G[i]);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        sm.bgkT[(4 * lane + e) * kLdT + i] = __float2half_rn(bg * kx[e]);
+        sm.kpT[(4 * lane + e) * kLdT + i] = __float2half_rn(kp * kx[e]);
+      }
+    }
+    for (int idx = tid; idx < kT * kD; idx += kThreads) {
+      const int i = idx / kD, c = idx % kD;
+      const float v = i < n ? post[size_t(c0 + i) * C + 2 * Hk * kD + hv * kD + c] : 0.f;
+      sm.bvT[c * kLdT + i] = __float2half_rn(sm.beta[i] * v);
+    }
+    __syncthreads();
+    // ---- Q S0 (every warp: its 8 value columns, both row halves), K K^T (warps 0-7) and Q K^T (warps 8-15)
+    float qs[2][4] = {};
+    tile_mma(qs[0], sm.q, kLdD, 0, sm.sT, kLdD, warp * 8, kD, gq, tq);
+    tile_mma(qs[1], sm.q, kLdD, 16, sm.sT, kLdD, warp * 8, kD, gq, tq);
+    {
+      const int t8 = warp & 7, m0 = (t8 >> 2) * 16, n0 = (t8 & 3) * 8;
+      float acc[4] = {};
+      tile_mma(acc, warp < 8 ? sm.k : sm.q, kLdD, m0, sm.k, kLdD, n0, kD, gq, tq);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int i = m0 + gq + (e >> 1) * 8, j = n0 + 2 * tq + (e & 1);
+        const float decay = __expf(sm.G[i] - sm.G[j]);  // <= 1 for j <= i
+        if (warp < 8) sm.a[i][j] = j < i ? sm.beta[i] * decay * acc[e] : 0.f;
+        else sm.p[i * kLdT + j] = __float2half_rn(j <= i ? decay * acc[e] : 0.f);
+      }
+    }
+    __syncthreads();
+    // ---- Tinv = (I + A)^-1 by forward substitution: lane l of warp 0 solves column l, x_i = [i == l] - sum_(j < i) A_ij x_j
+    if (warp == 0) {
+      float x[kT];
+#pragma unroll
+      for (int i = 0; i < kT; ++i) {
+        float acc = i == lane ? 1.f : 0.f;
+#pragma unroll
+        for (int j = 0; j < i; ++j) acc = fmaf(-sm.a[i][j], x[j], acc);
+        x[i] = acc;
+        sm.tinv[i * kLdT + lane] = __float2half_rn(acc);
+      }
+    }
+    __syncthreads();
+    // ---- U = Tinv (beta v) (kept in registers), W = Tinv (beta gamma k) (to shared memory)
+    float u[2][4] = {};
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt) {
+      tile_mma(u[mt], sm.tinv, kLdT, mt * 16, sm.bvT, kLdT, warp * 8, kT, gq, tq);
+      float wv[4] = {};
+      tile_mma(wv, sm.tinv, kLdT, mt * 16, sm.bgkT, kLdT, warp * 8, kT, gq, tq);
+      *reinterpret_cast<uint32_t*>(sm.w + (mt * 16 + gq) * kLdD + warp * 8 + 2 * tq) = h2(wv[0], wv[1]);
+      *reinterpret_cast<uint32_t*>(sm.w + (mt * 16 + gq + 8) * kLdD + warp * 8 + 2 * tq) = h2(wv[2], wv[3]);
+    }
+    __syncthreads();
+    // ---- Delta = U - W S0, transposed to shared memory
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt) {
+      float ws[4] = {};
+      tile_mma(ws, sm.w, kLdD, mt * 16, sm.sT, kLdD, warp * 8, kD, gq, tq);
+      const int i = mt * 16 + gq, c = warp * 8 + 2 * tq;
+      sm.dT[c * kLdT + i] = __float2half_rn(u[mt][0] - ws[0]), sm.dT[(c + 1) * kLdT + i] = __float2half_rn(u[mt][1] - ws[1]);
+      sm.dT[c * kLdT + i + 8] = __float2half_rn(u[mt][2] - ws[2]), sm.dT[(c + 1) * kLdT + i + 8] = __float2half_rn(u[mt][3] - ws[3]);
+    }
+    __syncthreads();
+    // ---- O = diag(gamma) Q S0 + P Delta; S = gamma_T S + K'^T Delta
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt) {
+      float pd[4] = {};
+      tile_mma(pd, sm.p, kLdT, mt * 16, sm.dT, kLdT, warp * 8, kT, gq, tq);
+      const int i = mt * 16 + gq, c = warp * 8 + 2 * tq;
+      if (i < n)
+        *reinterpret_cast<float2*>(core + size_t(c0 + i) * HV * kD + size_t(hv) * kD + c) =
+            make_float2(fmaf(sm.gam[i], qs[mt][0], pd[0]), fmaf(sm.gam[i], qs[mt][1], pd[1]));
+      if (i + 8 < n)
+        *reinterpret_cast<float2*>(core + size_t(c0 + i + 8) * HV * kD + size_t(hv) * kD + c) =
+            make_float2(fmaf(sm.gam[i + 8], qs[mt][2], pd[2]), fmaf(sm.gam[i + 8], qs[mt][3], pd[3]));
+    }
+    const float gT = sm.gam[kT - 1];
+#pragma unroll
+    for (int mt = 0; mt < 8; ++mt) {
+      float acc[4] = {};
+      tile_mma(acc, sm.kpT, kLdT, mt * 16, sm.dT, kLdT, warp * 8, kT, gq, tq);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) S[mt][e] = fmaf(gT, S[mt][e], acc[e]);
+    }
+    __syncthreads();  // every reader of sT and of the chunk's tiles is done
+    publish_state();
+  }
+#pragma unroll
+  for (int mt = 0; mt < 8; ++mt) {
+    const int d = mt * 16 + gq, c = warp * 8 + 2 * tq;
+    *reinterpret_cast<float2*>(st + size_t(d) * kD + c) = make_float2(S[mt][0], S[mt][1]);
+    *reinterpret_cast<float2*>(st + size_t(d + 8) * kD + c) = make_float2(S[mt][2], S[mt][3]);
+  }
+}
+
+// conv_prefill_kernel + conv_window_kernel (src/core/prefill_gdn.cu:34-72): the four-tap causal conv over M rows in parallel,
+// out of place, the first rows' taps from the session's window, then SiLU; the window afterwards holds the last three raw inputs.
+__global__ void __launch_bounds__(256)
+    conv_rows_kernel(const float* __restrict__ pre, const __nv_bfloat16* __restrict__ w, const float* __restrict__ win, int M, int C,
+                     float* __restrict__ post) {
+  pdl_sync();  // first statement: see common.cuh
+  const size_t total = size_t(M) * C;
+  for (size_t idx = size_t(blockIdx.x) * blockDim.x + threadIdx.x; idx < total; idx += size_t(gridDim.x) * blockDim.x) {
+    const int t = int(idx / C), c = int(idx % C);
+    float x[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int tt = t - 3 + j;
+      x[j] = tt >= 0 ? pre[size_t(tt) * C + c] : win[c * 3 + 3 + tt];
+    }
+    const float o = __bfloat162float(w[c * 4]) * x[0] + __bfloat162float(w[c * 4 + 1]) * x[1] + __bfloat162float(w[c * 4 + 2]) * x[2] +
+                    __bfloat162float(w[c * 4 + 3]) * x[3];
+    post[idx] = silu(o);
+  }
+}
+__global__ void __launch_bounds__(256) conv_window_kernel(const float* __restrict__ pre, float* __restrict__ win, int M, int C) {
+  pdl_sync();  // first statement: see common.cuh
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  float s[3];
+#pragma unroll
+  for (int j = 0; j < 3; ++j) {
+    const int tt = M - 3 + j;
+    s[j] = tt >= 0 ? pre[size_t(tt) * C + c] : win[c * 3 + 3 + tt];
+  }
+#pragma unroll
+  for (int j = 0; j < 3; ++j) win[c * 3 + j] = s[j];
+}
+
+}  // namespace
+
+int gdn_chunk_init() {
+  LB_CUDA(cudaFuncSetAttribute(gdn_chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(sizeof(ChunkSmem))));
+  return LING_B200_OK;
+}
+
+int gdn_chunk_launch(const float* post, const float* g, const float* beta, int M, int Hk, int HV, int Dk, int Dv, float* state, float* core,
+                     cudaStream_t s) {
+  if (Dk != kD || Dv != kD || M < 1 || Hk < 1 || HV % Hk != 0) return LING_B200_ERR_ARG;
+  LB_CUDA(launch_kernel(gdn_chunk_kernel, dim3(HV), dim3(kThreads), sizeof(ChunkSmem), s, post, g, beta, M, Hk, HV, state, core));
+  LB_LAUNCH("gdn_chunk_kernel");
+  return LING_B200_OK;
+}
+
+int conv_rows_launch(const float* pre, const __nv_bfloat16* w, float* window, int M, int C, float* post, cudaStream_t s) {
+  if (M < 1 || C < 1) return LING_B200_ERR_ARG;
+  const int grid = int(std::min<size_t>((size_t(M) * C + 255) / 256, size_t(148) * 16));
+  LB_CUDA(launch_kernel(conv_rows_kernel, dim3(grid), dim3(256), size_t(0), s, pre, w, (const float*)window, M, C, post));
+  LB_LAUNCH("conv_rows_kernel");
+  LB_CUDA(launch_kernel(conv_window_kernel, dim3(ceil_div(C, 256)), dim3(256), size_t(0), s, pre, window, M, C));
+  LB_LAUNCH("conv_window_kernel");
+  return LING_B200_OK;
+}
+
+}  // namespace lb

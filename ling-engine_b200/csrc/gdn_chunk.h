@@ -1,0 +1,20 @@
+// The DeltaNet mixer core of the prefill path (gdn_chunk.cu): the causal conv over many rows and the gated delta rule in its
+// chunked form.
+#pragma once
+
+#include "../../include/ling_b200.h"
+#include "common.cuh"
+
+namespace lb {
+
+int gdn_chunk_init();
+// post [M][C] = silu(conv(pre [M][C])) with the taps before row 0 from window [C][3], which then advances to the last three
+// raw inputs (gdn_conv_prefill, src/core/kernels.cuh:445-449).
+int conv_rows_launch(const float* pre, const __nv_bfloat16* w, float* window, int M, int C, float* post, cudaStream_t s);
+// The gated delta rule over the M rows of one sequence in 32-token chunks (gdn_recurrent_prefill, kernels.cuh:450-456):
+// post [M][C] (q | k | v channels, C = 2 Hk Dk + HV Dv), g and beta [M][HV], state [HV][Dk][Dv] updated in place,
+// core [M][HV Dv].  Dk = Dv = 128.
+int gdn_chunk_launch(const float* post, const float* g, const float* beta, int M, int Hk, int HV, int Dk, int Dv, float* state, float* core,
+                     cudaStream_t s);
+
+}  // namespace lb

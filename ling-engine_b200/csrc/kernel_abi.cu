@@ -5,6 +5,7 @@
 
 #include "abi_util.h"
 #include "draft_head.h"
+#include "gdn_chunk.h"
 #include "chain.h"
 #include "gemm.h"
 #include "kernels.h"
@@ -485,6 +486,71 @@ int ling_b200_selector_lattice_host(int device, const float* x, const uint16_t* 
     set_error("selector_lattice_host: a candidate or the anchor is not a token id (device error word = " + std::to_string(err) + ")");
     return LING_B200_ERR_DEVICE_FLAG;
   }
+  return LING_B200_OK;
+}
+
+// The prefill path's DeltaNet mixer core over host buffers: conv over the rows, then the chunked delta rule.
+int ling_b200_gdn_prefill_host(int device, int Hk, int HV, int Dk, int Dv, int M, const float* pre, const uint16_t* convw_bf16,
+                               const float* g, const float* beta, float* state, float* conv, float* post, float* core) {
+  if (!pre || !convw_bf16 || !g || !beta || !state || !conv || !core || M < 1 || Hk < 1 || HV < 1 || HV % Hk != 0 || Dk != 128 || Dv != 128) {
+    set_error("gdn_prefill_host: bad argument (key dim = value dim = 128)");
+    return LING_B200_ERR_ARG;
+  }
+  LB_TRY(check_device(device));
+  LB_TRY(gdn_chunk_init());
+  const int C = 2 * Hk * Dk + HV * Dv;
+  Scratch sc;
+  const float* d_pre = sc.put(pre, size_t(M) * C);
+  const auto* d_w = reinterpret_cast<const __nv_bfloat16*>(sc.put(convw_bf16, size_t(C) * 4));
+  const float* d_g = sc.put(g, size_t(M) * HV);
+  const float* d_b = sc.put(beta, size_t(M) * HV);
+  float* d_state = sc.put(state, size_t(HV) * Dk * Dv);
+  float* d_conv = sc.put(conv, size_t(C) * 3);
+  float* d_post = sc.get<float>(size_t(M) * C);
+  float* d_core = sc.get<float>(size_t(M) * HV * Dv);
+  LB_PTR(d_pre && d_w && d_g && d_b && d_state && d_conv && d_post && d_core);
+  LB_TRY(conv_rows_launch(d_pre, d_w, d_conv, M, C, d_post, 0));
+  LB_TRY(gdn_chunk_launch(d_post, d_g, d_b, M, Hk, HV, Dk, Dv, d_state, d_core, 0));
+  LB_CUDA(cudaDeviceSynchronize());
+  LB_CUDA(cudaMemcpy(state, d_state, size_t(HV) * Dk * Dv * 4, cudaMemcpyDeviceToHost));
+  LB_CUDA(cudaMemcpy(conv, d_conv, size_t(C) * 3 * 4, cudaMemcpyDeviceToHost));
+  LB_CUDA(cudaMemcpy(core, d_core, size_t(M) * HV * Dv * 4, cudaMemcpyDeviceToHost));
+  if (post) LB_CUDA(cudaMemcpy(post, d_post, size_t(M) * C * 4, cudaMemcpyDeviceToHost));
+  return LING_B200_OK;
+}
+
+// Device time of the chunked delta rule alone over M rows of synthetic inputs (ms per launch).
+int ling_b200_gdn_chunk_bench(int device, int Hk, int HV, int M, int iters, float* ms) {
+  if (M < 1 || Hk < 1 || HV % Hk != 0 || iters < 1 || !ms) {
+    set_error("gdn_chunk_bench: bad argument");
+    return LING_B200_ERR_ARG;
+  }
+  LB_TRY(check_device(device));
+  LB_TRY(gdn_chunk_init());
+  const int C = 2 * Hk * 128 + HV * 128;
+  Scratch sc;
+  float* d_post = sc.get<float>(size_t(M) * C, false);
+  float* d_g = sc.get<float>(size_t(M) * HV, false);
+  float* d_b = sc.get<float>(size_t(M) * HV, false);
+  float* d_state = sc.get<float>(size_t(HV) * 128 * 128);
+  float* d_core = sc.get<float>(size_t(M) * HV * 128, false);
+  LB_PTR(d_post && d_g && d_b && d_state && d_core);
+  LB_TRY(fill_f32_launch(stream_key(1, 1), 1.f, d_post, size_t(M) * C, 0));
+  LB_TRY(fill_f32_launch(stream_key(1, 2), 0.05f, d_g, size_t(M) * HV, 0));  // log-decays near 0 (|g| small), signs mixed
+  LB_TRY(fill_f32_launch(stream_key(1, 3), 0.2f, d_b, size_t(M) * HV, 0));
+  cudaEvent_t a, b;
+  LB_CUDA(cudaEventCreate(&a));
+  LB_CUDA(cudaEventCreate(&b));
+  LB_TRY(gdn_chunk_launch(d_post, d_g, d_b, M, Hk, HV, 128, 128, d_state, d_core, 0));
+  LB_CUDA(cudaMemsetAsync(d_state, 0, size_t(HV) * 128 * 128 * 4, 0));
+  LB_CUDA(cudaEventRecord(a, 0));
+  for (int i = 0; i < iters; ++i) LB_TRY(gdn_chunk_launch(d_post, d_g, d_b, M, Hk, HV, 128, 128, d_state, d_core, 0));
+  LB_CUDA(cudaEventRecord(b, 0));
+  LB_CUDA(cudaEventSynchronize(b));
+  float t = 0;
+  LB_CUDA(cudaEventElapsedTime(&t, a, b));
+  cudaEventDestroy(a), cudaEventDestroy(b);
+  *ms = t / iters;
   return LING_B200_OK;
 }
 

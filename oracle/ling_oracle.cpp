@@ -477,6 +477,44 @@ void lo_gdn_tree(int Hk, int HV, int Dk, int Dv, const lo_tree_desc* td, const f
   recurrent_tree(*td, post, g, beta, state, core, Hk, HV, Dk, Dv);
 }
 
+// gdn_conv_prefill + gdn_recurrent_prefill (src/core/kernels.cuh:445-456): the conv over M rows in order (taps before row 0
+// from the window, which then holds the last three raw inputs) and the delta rule token by token from the session's state,
+// which advances.  The reference's prefill kernel computes the same recurrence chunk-wise in FP16 products; this is the
+// exact token form it is unrolled from (src/core/prefill_gdn.cu:75-88), in the oracle's fp32/double arithmetic.
+void lo_gdn_prefill(int Hk, int HV, int Dk, int Dv, int M, const float* pre, const float* convw, const float* g, const float* beta,
+                    float* state, float* conv, float* post, float* core) {
+  const int C = 2 * Hk * Dk + HV * Dv;
+  for (int t = 0; t < M; ++t)
+    for (int c = 0; c < C; ++c) {
+      float x[4];
+      for (int j = 0; j < 4; ++j) {
+        const int tt = t - 3 + j;
+        x[j] = tt >= 0 ? pre[size_t(tt) * C + c] : conv[c * 3 + 3 + tt];
+      }
+      const float* w = convw + size_t(c) * 4;
+      post[size_t(t) * C + c] = silu(w[0] * x[0] + w[1] * x[1] + w[2] * x[2] + w[3] * x[3]);
+    }
+  for (int c = 0; c < C; ++c) {
+    float s[3];
+    for (int j = 0; j < 3; ++j) {
+      const int tt = M - 3 + j;
+      s[j] = tt >= 0 ? pre[size_t(tt) * C + c] : conv[c * 3 + 3 + tt];
+    }
+    for (int j = 0; j < 3; ++j) conv[c * 3 + j] = s[j];
+  }
+  parallel_for(HV, [&](int hv_lo, int hv_hi) {
+    for (int hv = hv_lo; hv < hv_hi; ++hv) {
+      const int h = hv / (HV / Hk);
+      float* S = state + size_t(hv) * Dk * Dv;
+      for (int t = 0; t < M; ++t) {
+        const float* row = post + size_t(t) * C;
+        delta_step(S, Dk, Dv, row + h * Dk, row + Hk * Dk + h * Dk, row + 2 * Hk * Dk + hv * Dv, g[size_t(t) * HV + hv],
+                   beta[size_t(t) * HV + hv], core + size_t(t) * HV * Dv + size_t(hv) * Dv, true);
+      }
+    }
+  });
+}
+
 // Engine::commit (src/core/speculate.cpp:516-529): the accepted rows path[0..n) replayed in order; the conv window
 // advances over their raw inputs (src/core/kernels.cu:320-338), the recurrence over their conv outputs, both written.
 void lo_gdn_commit(int Hk, int HV, int Dk, int Dv, const int* path, int n, int rows, const float* pre,

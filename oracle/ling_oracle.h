@@ -89,6 +89,8 @@ int lo_lookup_propose(const int* seq, int len, int max, int ngram, int* out, int
 void lo_gemm_fp8(const float* x, const float* w, float* y, int M, int N, int K);
 void lo_gdn_tree(int Hk, int HV, int Dk, int Dv, const lo_tree_desc* td, const float* pre, const float* convw,
                  const float* g, const float* beta, const float* state, const float* conv, float* post, float* core);
+void lo_gdn_prefill(int Hk, int HV, int Dk, int Dv, int M, const float* pre, const float* convw, const float* g, const float* beta,
+                    float* state, float* conv, float* post, float* core);
 void lo_gdn_commit(int Hk, int HV, int Dk, int Dv, const int* path, int n, int rows, const float* pre,
                    const float* post, const float* g, const float* beta, float* state, float* conv);
 void lo_argmax(const float* logits, int rows, int vocab, int* ids, float* vals);

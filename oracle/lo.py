@@ -138,6 +138,17 @@ def argmax(logits):
     return ids, vals
 
 
+def gdn_prefill(Hk, HV, Dk, Dv, pre, convw, g, beta, state, conv):
+    """conv over the rows + the delta rule token by token; returns post, core, and the advanced state and window."""
+    pre, g, beta = (np.ascontiguousarray(a, np.float32) for a in (pre, g, beta))
+    convw = np.ascontiguousarray(convw, np.float32)
+    state, conv = np.array(state, np.float32, order="C"), np.array(conv, np.float32, order="C")
+    M, C = pre.shape
+    post, core = np.zeros((M, C), np.float32), np.zeros((M, HV * Dv), np.float32)
+    lo().lo_gdn_prefill(Hk, HV, Dk, Dv, M, _fp(pre), _fp(convw), _fp(g), _fp(beta), _fp(state), _fp(conv), _fp(post), _fp(core))
+    return post, core, state, conv
+
+
 def topk_rows(x, k):
     x = np.ascontiguousarray(x, np.float32)
     ids, vals = np.zeros((x.shape[0], k), np.int32), np.zeros((x.shape[0], k), np.float32)

@@ -1,4 +1,4 @@
-// ref_cuda_shim.cu -- C wrappers around the REFERENCE's own CUDA kernels (src/core/kernels.cu, topk.cu, draft_kernels.cu of
+// ref_cuda_shim.cu -- C wrappers around the REFERENCE's own CUDA kernels (src/core/kernels.cu, topk.cu, draft_kernels.cu, prefill_gdn.cu of
 // dreamference/ling-engine), compiled for sm_100a from where the sources lie into oracle/_ref/libling_refcuda.so (see
 // oracle/Makefile, target ref_cuda).  TEST INFRASTRUCTURE ONLY.  Nothing of the reference is copied into this repository:
 // this file includes the reference's header and calls its launchers on device copies of host buffers, so that the CPU
@@ -230,6 +230,26 @@ int refcuda_selector_lattice(const float* hp, const int* cand, const float* unar
                         d.put_bf16(P, size_t(vocab) * 256), d.put_bf16(S, size_t(vocab) * 256), anchor, E, d_s, 0);
     sync();
     fetch(scores, d_s, size_t(E) * 256);
+  });
+}
+
+// gdn_conv_prefill + gdn_recurrent_prefill (src/core/prefill_gdn.cu): the reference's own prefill DeltaNet core over M rows.
+int refcuda_gdn_prefill(int Hk, int HV, int M, const float* pre, const float* convw, const float* g, const float* beta, float* state,
+                        float* conv, float* post, float* core) {
+  return guarded([&] {
+    Dev d;
+    const int C = 2 * Hk * 128 + HV * 128;
+    float* d_state = d.put(state, size_t(HV) * 128 * 128);
+    float* d_conv = d.put(conv, size_t(C) * 3);
+    float* d_post = d.get<float>(size_t(M) * C);
+    float* d_core = d.get<float>(size_t(M) * HV * 128);
+    K::gdn_conv_prefill(d.put(pre, size_t(M) * C), d_post, d_conv, d.put_bf16(convw, size_t(C) * 4), M, C, 0);
+    K::gdn_recurrent_prefill(d_post, d.put(g, size_t(M) * HV), d.put(beta, size_t(M) * HV), d_state, d_core, M, Hk, HV, 0, 0);
+    sync();
+    fetch(state, d_state, size_t(HV) * 128 * 128);
+    fetch(conv, d_conv, size_t(C) * 3);
+    fetch(post, d_post, size_t(M) * C);
+    fetch(core, d_core, size_t(M) * HV * 128);
   });
 }
 
