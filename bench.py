@@ -30,7 +30,8 @@ Other workloads (one JSON line each, same keys): --workload ragged4 (4 sequences
 the ranks, ~10 % completions and admissions per step through the page pool), served64 (the same 64-sequence load produced by
 the scheduler loop: ling-engine_b200/ling_serve_headless), mixed (a 4096-row prefill chunk through the NVFP4 feed-forward stack
 beside an 8-sequence verify step; roofline against the NVFP4 tensor rate measured in the same run), toy.  --micro gemm |
-nvfp4 | nvfp4-swiglu times one kernel alone on resident operands (the small cases the profiler captures).
+nvfp4 | nvfp4-swiglu | gdn-chunk times one kernel alone on resident operands (the small cases the profiler captures;
+gdn-chunk takes its row count from --shape's first number).
 
 Inputs are synthetic (seeded): they stand in for the reference's private replay workload, whose shapes they take.
 Weights are 26.4 GB, far larger than the 126 MB L2, so consecutive steps cannot hit in L2 (no flush between steps).
@@ -686,6 +687,12 @@ def run_micro_gemm(args):
     three warm-up launches; the small case the profiler captures.  A matrix smaller than L2 is served from L2 here."""
     lbm = importlib.import_module("ling-engine_b200")
     M, N, K = (int(x) for x in args.shape.split(","))
+    if args.micro == "gdn-chunk":
+        # the prefill path's chunked delta rule alone: M rows of one sequence, the 27B model's 16 key / 48 value heads of 128
+        ms = lbm.gdn_chunk_bench(16, 48, M, iters=args.iters)
+        print(json.dumps({"micro": "gdn_chunk_kernel", "rows": M, "heads": [16, 48], "iters": args.iters, "us_per_launch": ms * 1e3,
+                          "us_per_32_token_chunk": ms * 1e3 / ((M + 31) // 32), "rows_per_s": M / (ms * 1e-3)}), flush=True)
+        return
     if args.micro in ("nvfp4", "nvfp4-swiglu"):
         # one NVFP4 GEMM alone: N weight rows (N features from 2 N rows in the fused gate|up form), operands resident
         fused = args.micro == "nvfp4-swiglu"
@@ -795,7 +802,7 @@ def main():
     ap.add_argument("--no-churn64", action="store_true", help="leave out the 64-sequence sharded batch reported beside the headline")
     ap.add_argument("--quick", action="store_true", help="device-timed steps only (no end-to-end, per-family or CPU legs): "
                     "the short run the profiler's launch list is taken from")
-    ap.add_argument("--micro", default="", choices=["", "gemm", "nvfp4", "nvfp4-swiglu"], help="time one kernel alone on resident operands")
+    ap.add_argument("--micro", default="", choices=["", "gemm", "nvfp4", "nvfp4-swiglu", "gdn-chunk"], help="time one kernel alone on resident operands")
     ap.add_argument("--shape", default="24,34816,5120", help="--micro gemm: rows,N,K (default: the gate|up projection)")
     ap.add_argument("--iters", type=int, default=20)
     args = ap.parse_args()

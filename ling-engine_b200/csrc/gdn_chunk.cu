@@ -37,6 +37,8 @@ struct ChunkSmem {
   __half p[kT * kLdT];     // exp(G_i - G_j) q_i . k_j, j <= i
   float a[kT][kT + 1];     // A, fp32 for the substitution
   float G[kT], gam[kT], beta[kT];
+  // the next chunk's raw rows, copied in (cp.async) while the current chunk is computed
+  float rq[kT * kD], rk[kT * kD], rv[kT * kD], rg[kT], rb[kT];
 };
 
 __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -57,6 +59,13 @@ __device__ __forceinline__ void tile_mma(float (&c)[4], const __half* A, int lda
   for (int k0 = 0; k0 < K; k0 += 16)
     mma16816(c, ld32(ar + k0), ld32(ar + 8 * lda + k0), ld32(ar + k0 + 8), ld32(ar + 8 * lda + k0 + 8), ld32(br + k0), ld32(br + k0 + 8));
 }
+__device__ __forceinline__ void copy16(void* dst, const void* src, bool real) {  // zero-filled when the row does not exist
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(uint32_t(__cvta_generic_to_shared(dst))), "l"(src), "r"(real ? 16 : 0) : "memory");
+}
+__device__ __forceinline__ void copy4(void* dst, const void* src, bool real) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(uint32_t(__cvta_generic_to_shared(dst))), "l"(src), "r"(real ? 4 : 0) : "memory");
+}
+__device__ __forceinline__ void copies_done() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 __device__ __forceinline__ uint32_t h2(float lo, float hi) {
   const __half2 v = __floats2half2_rn(lo, hi);
   return *reinterpret_cast<const uint32_t*>(&v);
@@ -91,52 +100,73 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
   };
   publish_state();
+  // Requests the raw rows of the chunk that starts at row r0: q, k (this key head) and v (this value head), g and beta.
+  auto fetch_chunk = [&](int r0) {
+    const int rows = min(kT, M - r0);
+    for (int idx = tid; idx < 3 * kT * (kD / 4); idx += kThreads) {
+      const int part = idx / (kT * (kD / 4)), i = (idx / (kD / 4)) % kT, e = (idx % (kD / 4)) * 4;
+      const bool real = i < rows;
+      const float* row = post + size_t(r0 + (real ? i : 0)) * C;
+      const float* src = part == 0 ? row + h * kD + e : part == 1 ? row + Hk * kD + h * kD + e : row + 2 * Hk * kD + hv * kD + e;
+      copy16((part == 0 ? sm.rq : part == 1 ? sm.rk : sm.rv) + i * kD + e, src, real);
+    }
+    if (tid < 2 * kT) {
+      const int i = tid % kT;
+      const bool real = i < rows;
+      copy4((tid < kT ? sm.rg : sm.rb) + i, (tid < kT ? g : beta) + size_t(r0 + (real ? i : 0)) * HV + hv, real);
+    }
+  };
+  fetch_chunk(0);
 
   for (int c0 = 0; c0 < M; c0 += kT) {
     const int n = min(kT, M - c0);  // rows past n: k = v = 0, beta = 0, g = 0 -- they change nothing and are not stored
-    // ---- gates: cumulative log-decay by warp 0
-    if (warp == 0) {
-      const float gi = lane < n ? g[size_t(c0 + lane) * HV + hv] : 0.f;
-      float G = gi;
+    copies_done();
+    __syncthreads();  // the chunk's raw rows are in shared memory; the previous chunk's readers of the tiles are done
+    // ---- gates: every warp scans the log-decays (lane i ends with G_i); warp 0 also keeps them for the later phases
+    float G = sm.rg[lane];
 #pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const float up = __shfl_up_sync(0xffffffffu, G, o);
-        if (lane >= o) G += up;
+    for (int o = 1; o < 32; o <<= 1) {
+      const float up = __shfl_up_sync(0xffffffffu, G, o);
+      if (lane >= o) G += up;
+    }
+    const float G_last = __shfl_sync(0xffffffffu, G, kT - 1);
+    if (warp == 0) sm.G[lane] = G, sm.gam[lane] = __expf(G), sm.beta[lane] = sm.rb[lane];
+    // ---- q^, k^ (two rows a warp; lane l holds the elements l, l + 32, l + 64, l + 96), k^ scaled for W and for the state update
+    {
+      const int i0 = 2 * warp;
+      float kx[2][4], bg[2], kp[2];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const int i = i0 + r;
+        float qv[4], kv[4], sq = 0.f, sk = 0.f;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          qv[e] = sm.rq[i * kD + lane + 32 * e], kv[e] = sm.rk[i * kD + lane + 32 * e];
+          sq = fmaf(qv[e], qv[e], sq), sk = fmaf(kv[e], kv[e], sk);
+        }
+        sq = warp_sum(sq), sk = warp_sum(sk);
+        const float cq = rsqrtf(sq + 1e-6f) * rsqrtf(float(kD)), ck = rsqrtf(sk + 1e-6f);
+        const float Gi = __shfl_sync(0xffffffffu, G, i);
+        bg[r] = sm.rb[i] * __expf(Gi), kp[r] = __expf(G_last - Gi);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          kx[r][e] = kv[e] * ck;
+          sm.q[i * kLdD + lane + 32 * e] = __float2half_rn(qv[e] * cq);
+          sm.k[i * kLdD + lane + 32 * e] = __float2half_rn(kx[r][e]);
+        }
       }
-      sm.G[lane] = G, sm.gam[lane] = __expf(G);
-      sm.beta[lane] = lane < n ? beta[size_t(c0 + lane) * HV + hv] : 0.f;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {  // the two rows of a transposed tile as one 32-bit store
+        *reinterpret_cast<uint32_t*>(sm.bgkT + (lane + 32 * e) * kLdT + i0) = h2(bg[0] * kx[0][e], bg[1] * kx[1][e]);
+        *reinterpret_cast<uint32_t*>(sm.kpT + (lane + 32 * e) * kLdT + i0) = h2(kp[0] * kx[0][e], kp[1] * kx[1][e]);
+      }
+    }
+    for (int idx = tid; idx < (kT / 2) * kD; idx += kThreads) {
+      const int i = (idx / kD) * 2, c = idx % kD;
+      *reinterpret_cast<uint32_t*>(sm.bvT + c * kLdT + i) = h2(sm.rb[i] * sm.rv[i * kD + c], sm.rb[i + 1] * sm.rv[(i + 1) * kD + c]);
     }
     __syncthreads();
-    // ---- q^, k^ (two rows a warp, four elements a lane), and k^ scaled for W and for the state update
-    const float G_last = sm.G[kT - 1];
-    for (int i = 2 * warp; i < 2 * warp + 2; ++i) {
-      float4 qv = make_float4(0.f, 0.f, 0.f, 0.f), kv = qv;
-      if (i < n) {
-        const float* row = post + size_t(c0 + i) * C;
-        qv = *reinterpret_cast<const float4*>(row + h * kD + 4 * lane);
-        kv = *reinterpret_cast<const float4*>(row + Hk * kD + h * kD + 4 * lane);
-      }
-      const float sq = warp_sum(qv.x * qv.x + qv.y * qv.y + qv.z * qv.z + qv.w * qv.w);
-      const float sk = warp_sum(kv.x * kv.x + kv.y * kv.y + kv.z * kv.z + kv.w * kv.w);
-      const float cq = rsqrtf(sq + 1e-6f) * rsqrtf(float(kD)), ck = rsqrtf(sk + 1e-6f);
-      const float kx[4] = {kv.x * ck, kv.y * ck, kv.z * ck, kv.w * ck};
-      uint32_t* qd = reinterpret_cast<uint32_t*>(sm.q + i * kLdD + 4 * lane);
-      uint32_t* kd = reinterpret_cast<uint32_t*>(sm.k + i * kLdD + 4 * lane);
-      qd[0] = h2(qv.x * cq, qv.y * cq), qd[1] = h2(qv.z * cq, qv.w * cq);
-      kd[0] = h2(kx[0], kx[1]), kd[1] = h2(kx[2], kx[3]);
-      const float bg = sm.beta[i] * sm.gam[i], kp = __expf(G_last - sm.G[i]);
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        sm.bgkT[(4 * lane + e) * kLdT + i] = __float2half_rn(bg * kx[e]);
-        sm.kpT[(4 * lane + e) * kLdT + i] = __float2half_rn(kp * kx[e]);
-      }
-    }
-    for (int idx = tid; idx < kT * kD; idx += kThreads) {
-      const int i = idx / kD, c = idx % kD;
-      const float v = i < n ? post[size_t(c0 + i) * C + 2 * Hk * kD + hv * kD + c] : 0.f;
-      sm.bvT[c * kLdT + i] = __float2half_rn(sm.beta[i] * v);
-    }
-    __syncthreads();
+    if (c0 + kT < M) fetch_chunk(c0 + kT);  // lands while this chunk is computed
     // ---- Q S0 (every warp: its 8 value columns, both row halves), K K^T (warps 0-7) and Q K^T (warps 8-15)
     float qs[2][4] = {};
     tile_mma(qs[0], sm.q, kLdD, 0, sm.sT, kLdD, warp * 8, kD, gq, tq);
@@ -159,11 +189,11 @@ __global__ void __launch_bounds__(kThreads, 1)
       float x[kT];
 #pragma unroll
       for (int i = 0; i < kT; ++i) {
-        float acc = i == lane ? 1.f : 0.f;
+        float part[4] = {i == lane ? 1.f : 0.f, 0.f, 0.f, 0.f};  // four interleaved sums: a quarter of the dependent chain
 #pragma unroll
-        for (int j = 0; j < i; ++j) acc = fmaf(-sm.a[i][j], x[j], acc);
-        x[i] = acc;
-        sm.tinv[i * kLdT + lane] = __float2half_rn(acc);
+        for (int j = 0; j < i; ++j) part[j & 3] = fmaf(-sm.a[i][j], x[j], part[j & 3]);
+        x[i] = (part[0] + part[1]) + (part[2] + part[3]);
+        sm.tinv[i * kLdT + lane] = __float2half_rn(x[i]);
       }
     }
     __syncthreads();
