@@ -658,6 +658,10 @@ def run_served(args, rank, local_rank, world):
     sessions, requests = max(1, 64 // world), max(1, 96 // world)
     cmd = [exe, "--layers", str(args.layers), "--sessions", str(sessions), "--batch", str(sessions), "--requests", str(requests),
            "--seed", str(1 + rank), "--device", str(local_rank), "--max-tokens", "128"]
+    if args.systems > 0:  # prompts begin with one of a few shared system messages; the prefix KV store keeps each once
+        cmd += ["--systems", str(args.systems), "--prefix-kv-mb", str(args.prefix_kv_mb)]
+    if args.pool_pages > 0:
+        cmd += ["--pool-pages", str(args.pool_pages)]
     clocks = ClockSampler(local_rank)
     clocks.start()
     out = subprocess.run(cmd, capture_output=True, text=True, timeout=3000)
@@ -802,6 +806,9 @@ def main():
     ap.add_argument("--no-churn64", action="store_true", help="leave out the 64-sequence sharded batch reported beside the headline")
     ap.add_argument("--quick", action="store_true", help="device-timed steps only (no end-to-end, per-family or CPU legs): "
                     "the short run the profiler's launch list is taken from")
+    ap.add_argument("--systems", type=int, default=0, help="served64: prompts begin with one of this many shared system messages")
+    ap.add_argument("--prefix-kv-mb", type=int, default=0, help="served64 with --systems: the prefix KV store's budget for saved states (0: store off)")
+    ap.add_argument("--pool-pages", type=int, default=0, help="served64: KV page pool size (0: sized for the resident sessions)")
     ap.add_argument("--micro", default="", choices=["", "gemm", "nvfp4", "nvfp4-swiglu", "gdn-chunk"], help="time one kernel alone on resident operands")
     ap.add_argument("--shape", default="24,34816,5120", help="--micro gemm: rows,N,K (default: the gate|up projection)")
     ap.add_argument("--iters", type=int, default=20)

@@ -70,7 +70,10 @@ typedef struct ling_b200_options {
   int gating_stream; /* 0 (default) or 1 = the DeltaNet gating projections (a, b -> g, beta: needed only by the DeltaNet kernel)
                         run on a second stream beside the in projection, forked after the norm and joined before the DeltaNet
                         kernel (7.61 -> 7.52 ms per 27B step; the same kernels, the same results); -1 = in the step's one stream   */
-  int reserved[3];
+  int attn_positions; /* 0, or the cached positions summed over a step's sequences that the attention's partial buffers are
+                        sized for, when larger than the pool's positions: sessions that share pages (the prefix KV store)
+                        can hold more context between them than the pool has pages for                              */
+  int reserved[2];
 } ling_b200_options;
 
 typedef struct ling_b200_ctx ling_b200_ctx;
@@ -148,6 +151,9 @@ int ling_b200_kv_read(ling_b200_ctx* ctx, int slot, int attn_layer, int from, in
                       uint8_t* kcodes, float* kscales, uint8_t* vcodes, float* vscales);
 /* Positions [0, n) of every attention layer of a slot filled on the device from the generator (N(0,1) values). */
 int ling_b200_synth_kv(ling_b200_ctx* ctx, int slot, int n, uint64_t seed);
+/* The same over positions [from, from + n) only (a prefill stand-in that resumed at `from` must not write the positions it
+ * shares with another holder); values are a function of the seed, the slot, the layer and the position. */
+int ling_b200_synth_kv_range(ling_b200_ctx* ctx, int slot, int from, int n, uint64_t seed);
 /* One DeltaNet layer's (index among the DeltaNet layers) state [HV][Dk][Dv] and conv window [C][3] of a slot
  * (engine.cpp:226-229).  NULL pointers are skipped. */
 int ling_b200_state_write(ling_b200_ctx* ctx, int slot, int gdn_layer, const float* state, const float* conv);
@@ -191,6 +197,13 @@ typedef struct ling_b200_seq_result {
   int n_out;                                    /* = n_path                                          */
   int out[LING_B200_MAX_TREE_ROWS + 1];         /* SeqStep::out: accepted drafts, then next_token    */
 } ling_b200_seq_result;
+
+/* The attention kernels keep one partial result per (kv head, 512-key chunk of a sequence's context) of a step: the slots a
+ * sequence with `pos` cached positions takes, and the slots the context has.  A step whose sequences need more is refused
+ * (LING_B200_ERR_ARG) before anything is launched; a scheduler counts them when it chooses a pass's partners.  No counterpart
+ * in the reference, whose attention scratch is sized for the rows and the context capacity of a pass (engine.cpp:109-111). */
+int ling_b200_attn_slot_need(const ling_b200_ctx* ctx, int pos);
+int ling_b200_attn_slot_capacity(const ling_b200_ctx* ctx);
 
 /* Flags of ling_b200_verify_step. */
 enum {

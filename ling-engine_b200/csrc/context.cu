@@ -104,6 +104,7 @@ struct ling_b200_ctx {
   ling_b200_seq_result* results_host = nullptr;  // pinned
   int* err_host = nullptr;                       // pinned
   int staged_seqs = 0, staged_rows = 0, staged_flags = 0, last_rows = 0, last_seqs = 0, last_flags = 0;
+  long staged_slots = 0;  // attention partial slots the staged sequences' contexts take
   std::map<std::pair<int, int>, cudaGraphExec_t> graphs;  // (row class, flags)
   int launches_per_step = 0;
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
@@ -338,7 +339,7 @@ int enqueue_step_body(ling_b200_ctx* c, int rows, int flags) {
         Timed t(c, kFamAttn);
         LB_TRY(attn_combine_launch(c->part_o, c->part_ml, p0, c->sb, d, c->qout(c->xq_a), nullptr, rows,
                                    c->opt.max_context / kAttnChunkShort + 2, tc ? kAttnTcRows : kAttnRowTile,
-                                   tc ? c->sm_count : c->sm_count * 2, s));
+                                   tc ? c->sm_count : c->sm_count * 2, c->chunk_slots, s));
       }
       if (!chains) LB_TRY(run_gemm(c, L.o, c->xq_a, 1, rows));
       carry = planes_of(c, 1, L.o);
@@ -692,7 +693,8 @@ int ling_b200_create(const ling_b200_model_config* cfg, const ling_b200_options*
   // Chunk slots of the flash-decoding partials: every mapped position in chunks of kAttnChunk plus, per sequence, one
   // partly filled chunk and the in-flight chunk; per kv head.  A step on the short chunks (attn_chunk_keys) has at most
   // one slot per CTA of the attention grid.
-  const size_t pool_positions = size_t(d.pool_pages) * d.page_tokens;
+  // (pages shared between sessions let a batch's contexts add up to more than the pool holds: options.attn_positions)
+  const size_t pool_positions = std::max(size_t(d.pool_pages) * d.page_tokens, size_t(std::max(opt->attn_positions, 0)));
   c->chunk_slots = std::max(int((pool_positions / kAttnChunk + size_t(2) * d.max_seqs) * d.Hkv), 2 * c->sm_count);
   const size_t rmax = size_t(kTreeRows) * (d.Hq / d.Hkv);
   LB_TRY(c->alloc(&c->part_o, size_t(c->chunk_slots) * rmax * d.D, false));
@@ -947,18 +949,19 @@ int ling_b200_kv_write(ling_b200_ctx* c, int slot, int al, int from, int n, cons
   return read_err(c);
 }
 
-int ling_b200_synth_kv(ling_b200_ctx* c, int slot, int n, uint64_t seed) {
+int ling_b200_synth_kv_range(ling_b200_ctx* c, int slot, int from, int n, uint64_t seed) {
   LB_TRY(check_ctx(c));
   const ModelDims& d = c->d;
   if (d.n_attn == 0) return LING_B200_OK;
-  LB_TRY(check_positions(c, slot, 0, 0, n));
+  LB_TRY(check_positions(c, slot, 0, from, n));
   for (int al = 0; al < d.n_attn; ++al) {
     const uint64_t base = kStreamKv + (uint64_t(slot) * d.n_attn + al) * 2;
-    LB_TRY(kv_write_launch(nullptr, nullptr, stream_key(seed, base), stream_key(seed, base + 1), 1, d, al, slot, 0, n, c->kv,
+    LB_TRY(kv_write_launch(nullptr, nullptr, stream_key(seed, base), stream_key(seed, base + 1), 1, d, al, slot, from, n, c->kv,
                            c->sb.err, c->stream));
   }
   return read_err(c);
 }
+int ling_b200_synth_kv(ling_b200_ctx* c, int slot, int n, uint64_t seed) { return ling_b200_synth_kv_range(c, slot, 0, n, seed); }
 
 int ling_b200_kv_read(ling_b200_ctx* c, int slot, int al, int from, int n, float* k, float* v, uint8_t* kcodes, float* kscales,
                       uint8_t* vcodes, float* vscales) {
@@ -1107,6 +1110,12 @@ int ling_b200_state_hash(ling_b200_ctx* c, int slot, uint64_t* hash) {
 }
 
 // ------------------------------------------------------------------------------------------------ the step
+// Attention partial slots: what a sequence with `pos` cached positions takes in a step, and what the context holds.
+int ling_b200_attn_slot_need(const ling_b200_ctx* c, int pos) {
+  if (!c || c->d.n_attn == 0) return 0;
+  return ((std::max(pos, 0) + kAttnChunk - 1) / kAttnChunk + 1) * c->d.Hkv;
+}
+int ling_b200_attn_slot_capacity(const ling_b200_ctx* c) { return c ? c->chunk_slots : 0; }
 int ling_b200_step_stage(ling_b200_ctx* c, const ling_b200_seq_step* seqs, int n_seqs, int flags) {
   LB_TRY(check_ctx(c));
   const ModelDims& d = c->d;
@@ -1159,7 +1168,20 @@ int ling_b200_step_stage(ling_b200_ctx* c, const ling_b200_seq_step* seqs, int n
     }
   }
   c->staged_seqs = n_seqs, c->staged_rows = rows, c->staged_flags = flags;
+  c->staged_slots = 0;
+  for (int i = 0; i < n_seqs; ++i) c->staged_slots += long(ling_b200_attn_slot_need(c, seqs[i].pos));
   LB_CUDA(cudaMemcpyAsync(c->stage_dev, c->stage_host, c->stage_bytes, cudaMemcpyHostToDevice, c->stream));
+  return LING_B200_OK;
+}
+
+// The flash-decoding partials have a slot per (kv head, chunk of a sequence's context) (chunk_slots): a staged step whose
+// contexts need more is refused here, before anything that runs the attention kernels is launched.
+static int check_attn_slots(ling_b200_ctx* c) {
+  if (c->d.n_attn > 0 && c->staged_slots > c->chunk_slots) {
+    set_error("step: the batch's contexts need " + std::to_string(c->staged_slots) + " attention partial slots, the context has " +
+              std::to_string(c->chunk_slots) + " (sized for the pool's positions or options.attn_positions)");
+    return LING_B200_ERR_ARG;
+  }
   return LING_B200_OK;
 }
 
@@ -1169,6 +1191,7 @@ int ling_b200_step_launch(ling_b200_ctx* c) {
     set_error("step: nothing staged");
     return LING_B200_ERR_ARG;
   }
+  LB_TRY(check_attn_slots(c));
   const int rows = row_class(c->staged_rows), flags = c->staged_flags;
   c->last_rows = c->staged_rows, c->last_seqs = c->staged_seqs, c->last_flags = flags;
   if (!c->opt.use_graph) return enqueue_step(c, rows, flags);
@@ -1238,6 +1261,7 @@ int ling_b200_profile_step(ling_b200_ctx* c, float ms[8], int* launches) {
     set_error("profile: nothing staged");
     return LING_B200_ERR_ARG;
   }
+  LB_TRY(check_attn_slots(c));
   LB_TRY(finish(c));
   c->profiling = true;
   c->prof.clear();
@@ -1338,6 +1362,7 @@ int ling_b200_attention_host(ling_b200_ctx* c, const ling_b200_seq_step* seqs, i
     set_error("attention_host: too many rows for the staging buffers");
     return LING_B200_ERR_ARG;
   }
+  LB_TRY(check_attn_slots(c));
   c->last_rows = rows, c->last_seqs = n_seqs, c->last_flags = 0;
   LB_TRY(pack_launch(c->sb, d, c->stream));
   LB_CUDA(cudaMemcpyAsync(c->upload, q, n * 4, cudaMemcpyHostToDevice, c->stream));
@@ -1351,7 +1376,7 @@ int ling_b200_attention_host(ling_b200_ctx* c, const ling_b200_seq_step* seqs, i
   none.p = nullptr;
   LB_TRY(attn_combine_launch(c->part_o, c->part_ml, none, c->sb, d, c->qout(c->xq_a), c->planes[0], cls,
                              c->opt.max_context / kAttnChunkShort + 2, tc ? kAttnTcRows : kAttnRowTile,
-                             tc ? c->sm_count : c->sm_count * 2, c->stream));
+                             tc ? c->sm_count : c->sm_count * 2, c->chunk_slots, c->stream));
   LB_CUDA(cudaMemcpyAsync(out, c->planes[0], n * 4, cudaMemcpyDeviceToHost, c->stream));
   return read_err(c);
 }

@@ -479,6 +479,12 @@ class Engine {
     o.sessions = opts.sessions, o.max_context = opts.max_context, o.page_tokens = opts.page_tokens;
     o.pool_pages = pool_pages_for(opts);
     o.max_seqs = opts.max_seqs, o.max_rows = opts.max_rows, o.use_graph = opts.step_graphs, o.device = opts.device, o.pdl = opts.pdl;
+    if (opts.prefix_kv_mb > 0) {
+      // Sessions that resume from the store share pages, so a pass's sequences can hold more context between them than the
+      // pool has positions: the attention's partial buffers are sized for twice the pool (at most every sequence at the limit).
+      const long long pool = 1LL * o.pool_pages * opts.page_tokens, all = 1LL * opts.max_seqs * opts.max_context;
+      o.attn_positions = static_cast<int>(std::min<long long>(std::min(2 * pool, all), 2000000000LL));
+    }
     if (ling_b200_create(&cfg_, &o, &ctx_) != LING_B200_OK) {
       const std::string why = ling_b200_last_error();
       ling_b200_destroy(ctx_);
@@ -571,6 +577,10 @@ class Engine {
   int sessions_resident() const { return book_.resident(); }
   long session_evictions() const { return evictions_; }
   int max_batch() const { return opts_.max_seqs; }
+  // The attention kernels' partial-result slots a session's next step takes, and how many a pass has (a scheduler counts them
+  // when it picks a pass's partners: shared pages let the pass's contexts exceed the pool).
+  int attn_slot_need(int session) const { return ling_b200_attn_slot_need(ctx_, book_.at(session).pos); }
+  int attn_slot_capacity() const { return ling_b200_attn_slot_capacity(ctx_); }
   // What the prefill path does for an admitted prompt (Engine::begin_prefill + prefill_chunk, engine.cpp:1886-2300): the
   // prompt resumes from the furthest kept state (the session's own, or one of the prefix KV store's, whose pages are then
   // mapped by reference), pages are taken for the rest plus the growth reserve, the rest is processed in pieces that end

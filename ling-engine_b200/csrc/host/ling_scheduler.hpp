@@ -277,6 +277,9 @@ class SchedulerT {
     b.push_back(&r);
     int kv_need = eng_.kv_step_need(r.job.session, true);
     const int kv_free = eng_.kv_pages_free(), fit = eng_.max_batch();
+    constexpr bool kSlots = requires(E& e) { e.attn_slot_need(0); e.attn_slot_capacity(); };  // a pass's attention partial slots
+    long slots = 0, slot_cap = 0;
+    if constexpr (kSlots) slots = eng_.attn_slot_need(r.job.session), slot_cap = eng_.attn_slot_capacity();
     std::vector<PairCandidate> c;
     std::vector<Running*> by_index;
     for (Running& o : running_) {
@@ -288,6 +291,11 @@ class SchedulerT {
       if (o == &r || static_cast<int>(b.size()) >= fit || !batchable(*o)) continue;
       const int n = eng_.kv_step_need(o->job.session, true);
       if (kv_need + n > kv_free) continue;  // only requests whose step's pages are free join
+      if constexpr (kSlots) {
+        const long need = eng_.attn_slot_need(o->job.session);
+        if (slots + need > slot_cap) continue;  // the pass's contexts would not fit the attention's partial buffers
+        slots += need;
+      }
       kv_need += n;
       b.push_back(o);
     }

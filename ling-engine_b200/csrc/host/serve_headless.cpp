@@ -7,7 +7,11 @@
 //
 //   ling_serve_headless [--layers 64] [--requests 96] [--sessions 64] [--batch 64] [--max-context 131072] [--pool-pages 0]
 //                       [--median 6000] [--max-tokens 32] [--seed 1] [--fair 0] [--toy]
-// Prompts: lengths lognormal around --median (at most max-context - 64), token ids uniform.  The prefill pass is outside this
+//                       [--systems 0] [--system-tokens 3000] [--prefix-kv-mb 0]
+// Prompts: lengths lognormal around --median (at most max-context - 64), token ids uniform.  With --systems K every prompt
+// begins with one of K system messages of --system-tokens tokens (boundary token, message, boundary token), the way
+// conversations of a few agents share their instructions; --prefix-kv-mb > 0 turns the engine's prefix KV store on, which
+// then keeps each system message's pages and state once and lets later prompts resume behind it.  The prefill pass is outside this
 // build: an admitted prompt's KV and DeltaNet state are filled synthetically on the device.  Draft trees: a chain plus a lookup
 // branch off the anchor, 1-32 rows, random tokens (so a pass accepts what the random-weight model happens to agree with:
 // nearly always the anchor alone).  One JSON line on stdout.
@@ -84,17 +88,32 @@ int main(int argc, char** argv) {
   reqs.resize(size_t(n_req));
   const ling::ModelConfig cfg = model(toy, layers);
   long prompt_tokens = 0;
+  constexpr int kBoundary = 1;
+  const int n_sys = arg(argc, argv, "--systems", 0), sys_tokens = arg(argc, argv, "--system-tokens", toy ? 150 : 3000);
+  const int prefix_kv_mb = arg(argc, argv, "--prefix-kv-mb", 0);
+  std::vector<std::vector<int>> systems(size_t(std::max(n_sys, 0)));
+  for (auto& m : systems) {
+    m.push_back(kBoundary);
+    for (int i = 0; i < sys_tokens; ++i) m.push_back(2 + int(rng() % unsigned(cfg.vocab - 2)));
+    m.push_back(kBoundary);
+  }
   for (auto& r : reqs) {
-    const int L = std::clamp(int(len(rng)), 16, max_context - 64);
-    r.prompt.resize(size_t(L));
-    for (int& t : r.prompt) t = int(rng() % unsigned(cfg.vocab));
+    const int L = std::clamp(int(len(rng)), 16, max_context - 64 - (n_sys > 0 ? sys_tokens + 2 : 0));
+    if (n_sys > 0) r.prompt = systems[size_t(rng() % unsigned(n_sys))];
+    const size_t head = r.prompt.size();
+    r.prompt.resize(head + size_t(L));
+    for (size_t i = head; i < r.prompt.size(); ++i) r.prompt[i] = 2 + int(rng() % unsigned(cfg.vocab - 2));
+    // a later message of the conversation's own: its last message then starts past what it shares with the others, so it is
+    // a conversation of its own to match_session and not the next turn of another one with the same system message
+    if (n_sys > 0 && L >= 4) r.prompt[head + size_t(L) / 2] = kBoundary;
     r.max_tokens = 1 + int(rng() % unsigned(max_tokens));
     r.sampling.temperature = 0.f;
-    prompt_tokens += L;
+    prompt_tokens += long(r.prompt.size());
   }
   ling::EngineOptions o;
   o.max_context = max_context, o.sessions = sessions, o.max_seqs = std::min(batch, ling::kernels::kMaxSeqs), o.max_rows = 32 * o.max_seqs;
   o.page_tokens = 16, o.device = device, o.pdl = true;
+  o.boundary_token = kBoundary, o.prefix_kv_mb = prefix_kv_mb;
   if (pool_pages <= 0) {  // room for the resident sessions at the workload's mean length, plus a quarter: long prompts force evictions
     pool_pages = int(double(prompt_tokens) / n_req / 16.0 * sessions * 1.25) + 8 * sessions;
     pool_pages = std::max(pool_pages, (max_context + 15) / 16 + 8);
@@ -110,9 +129,11 @@ int main(int argc, char** argv) {
       return chain_plus_branch(anchor, rows, rng, cfg.vocab);
     });
     double fill_s = 0;
-    eng.set_prefill_fill([&](ling_b200_ctx* ctx, int session, int, int to) {
+    long filled_tokens = 0;
+    eng.set_prefill_fill([&](ling_b200_ctx* ctx, int session, int from, int to) {
       const auto t0 = std::chrono::steady_clock::now();
-      ling_b200_synth_kv(ctx, session, to, uint64_t(to));
+      filled_tokens += to - from;
+      ling_b200_synth_kv_range(ctx, session, from, to - from, uint64_t(to));  // only what this prompt does not share
       ling_b200_synth_state(ctx, session, uint64_t(to));
       ling_b200_sync(ctx);
       fill_s += std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
@@ -141,6 +162,7 @@ int main(int argc, char** argv) {
     long produced = 0, errors = 0, at_length = 0;
     for (const auto& f : done) {
       produced += long(f.tokens.size());
+      if (f.finish == "error" && errors < 3) std::fprintf(stderr, "ling_serve_headless: request %ld ended in error: %s\n", f.id, f.error.c_str());
       errors += f.finish == "error";
       at_length += f.finish == "length";
     }
@@ -151,12 +173,15 @@ int main(int argc, char** argv) {
         "\"shared_passes\": %ld, \"sequences_per_pass\": %.2f, \"max_sequences_in_pass\": %ld, \"rows_per_pass\": %.1f, "
         "\"kv_evictions\": %ld, \"kv_waits\": %ld, \"kv_pool_exhausted\": %ld, \"session_evictions\": %ld, \"pass_seconds\": %.4f, "
         "\"ms_per_pass\": %.3f, \"rows_per_s\": %.1f, \"tokens_per_s\": %.1f, \"prefill_fill_seconds\": %.3f, \"wall_seconds\": %.3f, "
-        "\"not_finished\": %zu, \"launches_last_pass\": %d}\n",
+        "\"not_finished\": %zu, \"launches_last_pass\": %d, \"systems\": %d, \"prefix_kv_mb\": %d, \"prefilled_tokens\": %ld, "
+        "\"store_evictions\": %ld, \"store_nodes\": %d, \"store_states\": %d, \"store_pages_held\": %d}\n",
         toy ? "toy" : "27B-class", n_req, done.size(), errors, sessions, batch, pool_pages, prompt_tokens, produced, turns, st.decode_passes,
         st.batched_steps, st.decode_passes ? double(st.rows) / double(st.decode_passes) : 0.0, max_seqs_in_pass,
         st.decode_passes ? double(tree_rows) / double(st.decode_passes) : 0.0, st.kv_evictions, st.kv_waits, st.kv_pool_exhausted,
         eng.session_evictions(), pass_s, st.decode_passes ? pass_s / double(st.decode_passes) * 1e3 : 0.0,
-        pass_s > 0 ? double(tree_rows) / pass_s : 0.0, pass_s > 0 ? double(produced) / pass_s : 0.0, fill_s, wall, sch.queued() + sch.running(), ling_b200_step_launch_count(eng.handle()));
+        pass_s > 0 ? double(tree_rows) / pass_s : 0.0, pass_s > 0 ? double(produced) / pass_s : 0.0, fill_s, wall, sch.queued() + sch.running(), ling_b200_step_launch_count(eng.handle()),
+        n_sys, prefix_kv_mb, filled_tokens, st.kv_store_evictions, eng.kv_store_on() ? eng.kv_store()->nodes() : 0,
+        eng.kv_store_on() ? eng.kv_store()->states() : 0, eng.kv_store_on() ? eng.kv_store()->pages_held() : 0);
     return done.size() == size_t(n_req) ? 0 : 1;
   } catch (const std::exception& e) {
     std::fprintf(stderr, "ling_serve_headless: %s\n", e.what());

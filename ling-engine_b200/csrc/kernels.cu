@@ -1403,7 +1403,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2)
 template <int G>
 __global__ void __launch_bounds__(256)
     attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, Planes qkv, StepBuffers sb,
-                        ModelDims d, QuantOut q, float* __restrict__ raw, int max_chunks, int tile_rows, int budget) {
+                        ModelDims d, QuantOut q, float* __restrict__ raw, int max_chunks, int tile_rows, int budget, int chunk_slots) {
   pdl_sync();  // first statement: see common.cuh
   constexpr int RMAX = kTreeRows * G;
   extern __shared__ __align__(16) float csm[];  // [HB][max_chunks] chunk weights, [4] denominators, [NG][CB] partial sums (max_chunks a multiple of 4)
@@ -1434,11 +1434,15 @@ __global__ void __launch_bounds__(256)
     }
     const int hk = hq / G, r = local * G + hq % G;
     const float* ml = part_ml + ((size_t(cb) * d.Hkv + size_t(hk) * nch) * RMAX + r) * 2;
+    // chunk slots past the buffers' end were never written (the attention kernel skipped their items and set the error
+    // word): they are not read either
+    const int nlim = max(0, min(nch, chunk_slots - (cb * d.Hkv + hk * nch)));
+    for (int ch = nlim + threadIdx.x; ch < nch; ch += blockDim.x) wgt[hb * max_chunks + ch] = 0.f;
     float mx = -INFINITY;
-    for (int ch = threadIdx.x; ch < nch; ch += blockDim.x) mx = fmaxf(mx, ml[size_t(ch) * RMAX * 2]);
+    for (int ch = threadIdx.x; ch < nlim; ch += blockDim.x) mx = fmaxf(mx, ml[size_t(ch) * RMAX * 2]);
     mx = block_max(mx, red);
     float dsum = 0.f;
-    for (int ch = threadIdx.x; ch < nch; ch += blockDim.x) {
+    for (int ch = threadIdx.x; ch < nlim; ch += blockDim.x) {
       const float mc = ml[size_t(ch) * RMAX * 2];
       const float w = mc == -INFINITY ? 0.f : __expf(mc - mx);  // an empty chunk weighs nothing
       wgt[hb * max_chunks + ch] = w;
@@ -1456,8 +1460,9 @@ __global__ void __launch_bounds__(256)
     const int hq = c / D, dd = c % D, hk = hq / G, r = local * G + hq % G;
     const float* po = part_o + ((size_t(cb) * d.Hkv + size_t(hk) * nch) * RMAX + r) * D + dd;
     const float* w = wgt + hb * max_chunks;
+    const int nlim = max(0, min(nch, chunk_slots - (cb * d.Hkv + hk * nch)));
 #pragma unroll 4
-    for (int ch = grp; ch < nch; ch += NG) {
+    for (int ch = grp; ch < nlim; ch += NG) {
       const float4 o = *reinterpret_cast<const float4*>(po + size_t(ch) * RMAX * D);
       const float wc = w[ch];
       num.x = fmaf(o.x, wc, num.x), num.y = fmaf(o.y, wc, num.y), num.z = fmaf(o.z, wc, num.z), num.w = fmaf(o.w, wc, num.w);
@@ -1858,7 +1863,7 @@ int attention_launch(const __half* q, const StepBuffers& sb, const ModelDims& d,
 
 int attn_combine_launch(const float* part_o, const float* part_ml, const Planes& qkv, const StepBuffers& sb,
                         const ModelDims& d, const QuantOut& q, float* raw, int rows_grid, int max_chunks, int tile_rows, int budget,
-                        cudaStream_t s) {
+                        int chunk_slots, cudaStream_t s) {
   const int G = d.Hq / d.Hkv;
   const int CB = d.D > 128 ? d.D : 128, HB = CB / d.D, NG = 256 / (CB / 4);
   if (CB % 128 != 0 || 256 % (CB / 4) != 0 || CB % d.D != 0) {
@@ -1872,9 +1877,9 @@ int attn_combine_launch(const float* part_o, const float* part_ml, const Planes&
     set_error("attention combine: too many chunks for one sequence");
     return LING_B200_ERR_UNSUPPORTED;
   }
-  if (G == 6) LB_CUDA(launch_kernel(attn_combine_kernel<6>, grid, dim3(256), smem, s, part_o, part_ml, qkv, sb, d, q, raw, max_chunks, tile_rows, budget));
-  else if (G == 4) LB_CUDA(launch_kernel(attn_combine_kernel<4>, grid, dim3(256), smem, s, part_o, part_ml, qkv, sb, d, q, raw, max_chunks, tile_rows, budget));
-  else if (G == 8) LB_CUDA(launch_kernel(attn_combine_kernel<8>, grid, dim3(256), smem, s, part_o, part_ml, qkv, sb, d, q, raw, max_chunks, tile_rows, budget));
+  if (G == 6) LB_CUDA(launch_kernel(attn_combine_kernel<6>, grid, dim3(256), smem, s, part_o, part_ml, qkv, sb, d, q, raw, max_chunks, tile_rows, budget, chunk_slots));
+  else if (G == 4) LB_CUDA(launch_kernel(attn_combine_kernel<4>, grid, dim3(256), smem, s, part_o, part_ml, qkv, sb, d, q, raw, max_chunks, tile_rows, budget, chunk_slots));
+  else if (G == 8) LB_CUDA(launch_kernel(attn_combine_kernel<8>, grid, dim3(256), smem, s, part_o, part_ml, qkv, sb, d, q, raw, max_chunks, tile_rows, budget, chunk_slots));
   else {
     set_error("attention combine: unsupported group size");
     return LING_B200_ERR_UNSUPPORTED;

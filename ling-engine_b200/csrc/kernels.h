@@ -179,7 +179,7 @@ int attention_tc_launch(const __half* q, const StepBuffers& sb, const ModelDims&
 // tile_rows, budget: the query rows per item and the grid of the attention kernel whose partials are merged (attn_chunk_keys)
 int attn_combine_launch(const float* part_o, const float* part_ml, const Planes& qkv, const StepBuffers& sb,
                         const ModelDims& d, const QuantOut& q, float* raw, int rows_grid, int max_chunks, int tile_rows, int budget,
-                        cudaStream_t s);
+                        int chunk_slots, cudaStream_t s);  // chunk_slots: the partial buffers' capacity (slots past it are not read)
 int f32_to_half_launch(const float* src, __half* dst, size_t n, cudaStream_t s);
 int silu_mul_quant_launch(const Planes& gu, int I, int up_col0, const QuantOut& q, const int* n_rows, int rows_grid, cudaStream_t s);
 int argmax_reduce_launch(const float* tile_val, const int* tile_idx, int tiles, int rows_alloc, int* ids, float* vals,
