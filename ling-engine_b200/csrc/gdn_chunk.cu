@@ -46,18 +46,39 @@ __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-__device__ __forceinline__ uint32_t ld32(const __half* p) { return *reinterpret_cast<const uint32_t*>(p); }
-
-// c (16 x 8 at rows m0, columns n0) += A[m0 .., 0 .. K) . B[n0 .., 0 .. K)^T; A [m][k] and B [n][k], both with k contiguous.
-// Fragment layout of mma.m16n8k16: lane = 4 gq + tq holds A rows gq, gq + 8 at k = 2 tq, 2 tq + 1 (+8), B column gq at the
-// same k, and C rows gq, gq + 8 at columns 2 tq, 2 tq + 1.
-__device__ __forceinline__ void tile_mma(float (&c)[4], const __half* A, int lda, int m0, const __half* B, int ldb, int n0, int K,
-                                         int gq, int tq) {
-  const __half* ar = A + (m0 + gq) * lda + 2 * tq;
-  const __half* br = B + (n0 + gq) * ldb + 2 * tq;
+// ldmatrix.x4: four 8 x 8 FP16 matrices; lane l supplies the address of row l % 8 of matrix l / 8 (16 bytes, 16-byte aligned),
+// and receives from each matrix the pair at (row l / 4, columns 2 (l % 4), + 1) -- the fragment layout of mma.m16n8k16.
+__device__ __forceinline__ void ldsm4(uint32_t (&r)[4], const __half* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(uint32_t(__cvta_generic_to_shared(p))));
+}
+// The A fragment (16 x 16) of a row-major [m][k] tile at (m0, k0): matrices rows 0-7 / 8-15 at k0, then the same at k0 + 8.
+__device__ __forceinline__ void frag_a(uint32_t (&a)[4], const __half* A, int lda, int m0, int k0, int lane) {
+  ldsm4(a, A + (m0 + (lane & 7) + 8 * ((lane >> 3) & 1)) * lda + k0 + 8 * (lane >> 4));
+}
+// The B fragments of two consecutive k steps (k0 .. k0 + 31) for the 8 columns n0 .. n0 + 7 of an [n][k] tile (k contiguous):
+// b[0], b[1] belong to k0, b[2], b[3] to k0 + 16.
+__device__ __forceinline__ void frag_b2(uint32_t (&b)[4], const __half* B, int ldb, int n0, int k0, int lane) {
+  ldsm4(b, B + (n0 + (lane & 7)) * ldb + k0 + 8 * (lane >> 3));
+}
+// c[t] (rows 16 t .. 16 t + 15 of the MT row tiles from mt0 on, columns n0 .. n0 + 7) += A . B^T over K (a multiple of 32);
+// A [m][k], B [n][k], both with k contiguous.  The row tiles share the B fragments.
+template <int MT, int K>
+__device__ __forceinline__ void tiles_mma(float (&c)[MT][4], const __half* A, int lda, int mt0, const __half* B, int ldb, int n0, int lane) {
 #pragma unroll
-  for (int k0 = 0; k0 < K; k0 += 16)
-    mma16816(c, ld32(ar + k0), ld32(ar + 8 * lda + k0), ld32(ar + k0 + 8), ld32(ar + 8 * lda + k0 + 8), ld32(br + k0), ld32(br + k0 + 8));
+  for (int k0 = 0; k0 < K; k0 += 32) {
+    uint32_t b[4];
+    frag_b2(b, B, ldb, n0, k0, lane);
+#pragma unroll
+    for (int t = 0; t < MT; ++t) {
+      uint32_t a[4];
+      frag_a(a, A, lda, (mt0 + t) * 16, k0, lane);
+      mma16816(c[t], a[0], a[1], a[2], a[3], b[0], b[1]);
+      frag_a(a, A, lda, (mt0 + t) * 16, k0 + 16, lane);
+      mma16816(c[t], a[0], a[1], a[2], a[3], b[2], b[3]);
+    }
+  }
 }
 __device__ __forceinline__ void copy16(void* dst, const void* src, bool real) {  // zero-filled when the row does not exist
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(uint32_t(__cvta_generic_to_shared(dst))), "l"(src), "r"(real ? 16 : 0) : "memory");
@@ -169,18 +190,17 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (c0 + kT < M) fetch_chunk(c0 + kT);  // lands while this chunk is computed
     // ---- Q S0 (every warp: its 8 value columns, both row halves), K K^T (warps 0-7) and Q K^T (warps 8-15)
     float qs[2][4] = {};
-    tile_mma(qs[0], sm.q, kLdD, 0, sm.sT, kLdD, warp * 8, kD, gq, tq);
-    tile_mma(qs[1], sm.q, kLdD, 16, sm.sT, kLdD, warp * 8, kD, gq, tq);
+    tiles_mma<2, kD>(qs, sm.q, kLdD, 0, sm.sT, kLdD, warp * 8, lane);
     {
       const int t8 = warp & 7, m0 = (t8 >> 2) * 16, n0 = (t8 & 3) * 8;
-      float acc[4] = {};
-      tile_mma(acc, warp < 8 ? sm.k : sm.q, kLdD, m0, sm.k, kLdD, n0, kD, gq, tq);
+      float acc[1][4] = {};
+      tiles_mma<1, kD>(acc, warp < 8 ? sm.k : sm.q, kLdD, t8 >> 2, sm.k, kLdD, n0, lane);
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int i = m0 + gq + (e >> 1) * 8, j = n0 + 2 * tq + (e & 1);
         const float decay = __expf(sm.G[i] - sm.G[j]);  // <= 1 for j <= i
-        if (warp < 8) sm.a[i][j] = j < i ? sm.beta[i] * decay * acc[e] : 0.f;
-        else sm.p[i * kLdT + j] = __float2half_rn(j <= i ? decay * acc[e] : 0.f);
+        if (warp < 8) sm.a[i][j] = j < i ? sm.beta[i] * decay * acc[0][e] : 0.f;
+        else sm.p[i * kLdT + j] = __float2half_rn(j <= i ? decay * acc[0][e] : 0.f);
       }
     }
     __syncthreads();
@@ -199,45 +219,52 @@ __global__ void __launch_bounds__(kThreads, 1)
     __syncthreads();
     // ---- U = Tinv (beta v) (kept in registers), W = Tinv (beta gamma k) (to shared memory)
     float u[2][4] = {};
+    tiles_mma<2, kT>(u, sm.tinv, kLdT, 0, sm.bvT, kLdT, warp * 8, lane);
+    {
+      float wv[2][4] = {};
+      tiles_mma<2, kT>(wv, sm.tinv, kLdT, 0, sm.bgkT, kLdT, warp * 8, lane);
 #pragma unroll
-    for (int mt = 0; mt < 2; ++mt) {
-      tile_mma(u[mt], sm.tinv, kLdT, mt * 16, sm.bvT, kLdT, warp * 8, kT, gq, tq);
-      float wv[4] = {};
-      tile_mma(wv, sm.tinv, kLdT, mt * 16, sm.bgkT, kLdT, warp * 8, kT, gq, tq);
-      *reinterpret_cast<uint32_t*>(sm.w + (mt * 16 + gq) * kLdD + warp * 8 + 2 * tq) = h2(wv[0], wv[1]);
-      *reinterpret_cast<uint32_t*>(sm.w + (mt * 16 + gq + 8) * kLdD + warp * 8 + 2 * tq) = h2(wv[2], wv[3]);
+      for (int mt = 0; mt < 2; ++mt) {
+        *reinterpret_cast<uint32_t*>(sm.w + (mt * 16 + gq) * kLdD + warp * 8 + 2 * tq) = h2(wv[mt][0], wv[mt][1]);
+        *reinterpret_cast<uint32_t*>(sm.w + (mt * 16 + gq + 8) * kLdD + warp * 8 + 2 * tq) = h2(wv[mt][2], wv[mt][3]);
+      }
     }
     __syncthreads();
     // ---- Delta = U - W S0, transposed to shared memory
+    {
+      float ws[2][4] = {};
+      tiles_mma<2, kD>(ws, sm.w, kLdD, 0, sm.sT, kLdD, warp * 8, lane);
 #pragma unroll
-    for (int mt = 0; mt < 2; ++mt) {
-      float ws[4] = {};
-      tile_mma(ws, sm.w, kLdD, mt * 16, sm.sT, kLdD, warp * 8, kD, gq, tq);
-      const int i = mt * 16 + gq, c = warp * 8 + 2 * tq;
-      sm.dT[c * kLdT + i] = __float2half_rn(u[mt][0] - ws[0]), sm.dT[(c + 1) * kLdT + i] = __float2half_rn(u[mt][1] - ws[1]);
-      sm.dT[c * kLdT + i + 8] = __float2half_rn(u[mt][2] - ws[2]), sm.dT[(c + 1) * kLdT + i + 8] = __float2half_rn(u[mt][3] - ws[3]);
+      for (int mt = 0; mt < 2; ++mt) {
+        const int i = mt * 16 + gq, c = warp * 8 + 2 * tq;
+        sm.dT[c * kLdT + i] = __float2half_rn(u[mt][0] - ws[mt][0]), sm.dT[(c + 1) * kLdT + i] = __float2half_rn(u[mt][1] - ws[mt][1]);
+        sm.dT[c * kLdT + i + 8] = __float2half_rn(u[mt][2] - ws[mt][2]), sm.dT[(c + 1) * kLdT + i + 8] = __float2half_rn(u[mt][3] - ws[mt][3]);
+      }
     }
     __syncthreads();
     // ---- O = diag(gamma) Q S0 + P Delta; S = gamma_T S + K'^T Delta
+    {
+      float pd[2][4] = {};
+      tiles_mma<2, kT>(pd, sm.p, kLdT, 0, sm.dT, kLdT, warp * 8, lane);
 #pragma unroll
-    for (int mt = 0; mt < 2; ++mt) {
-      float pd[4] = {};
-      tile_mma(pd, sm.p, kLdT, mt * 16, sm.dT, kLdT, warp * 8, kT, gq, tq);
-      const int i = mt * 16 + gq, c = warp * 8 + 2 * tq;
-      if (i < n)
-        *reinterpret_cast<float2*>(core + size_t(c0 + i) * HV * kD + size_t(hv) * kD + c) =
-            make_float2(fmaf(sm.gam[i], qs[mt][0], pd[0]), fmaf(sm.gam[i], qs[mt][1], pd[1]));
-      if (i + 8 < n)
-        *reinterpret_cast<float2*>(core + size_t(c0 + i + 8) * HV * kD + size_t(hv) * kD + c) =
-            make_float2(fmaf(sm.gam[i + 8], qs[mt][2], pd[2]), fmaf(sm.gam[i + 8], qs[mt][3], pd[3]));
+      for (int mt = 0; mt < 2; ++mt) {
+        const int i = mt * 16 + gq, c = warp * 8 + 2 * tq;
+        if (i < n)
+          *reinterpret_cast<float2*>(core + size_t(c0 + i) * HV * kD + size_t(hv) * kD + c) =
+              make_float2(fmaf(sm.gam[i], qs[mt][0], pd[mt][0]), fmaf(sm.gam[i], qs[mt][1], pd[mt][1]));
+        if (i + 8 < n)
+          *reinterpret_cast<float2*>(core + size_t(c0 + i + 8) * HV * kD + size_t(hv) * kD + c) =
+              make_float2(fmaf(sm.gam[i + 8], qs[mt][2], pd[mt][2]), fmaf(sm.gam[i + 8], qs[mt][3], pd[mt][3]));
+      }
     }
     const float gT = sm.gam[kT - 1];
+    {
+      float acc[8][4] = {};
+      tiles_mma<8, kT>(acc, sm.kpT, kLdT, 0, sm.dT, kLdT, warp * 8, lane);
 #pragma unroll
-    for (int mt = 0; mt < 8; ++mt) {
-      float acc[4] = {};
-      tile_mma(acc, sm.kpT, kLdT, mt * 16, sm.dT, kLdT, warp * 8, kT, gq, tq);
+      for (int mt = 0; mt < 8; ++mt)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) S[mt][e] = fmaf(gT, S[mt][e], acc[e]);
+        for (int e = 0; e < 4; ++e) S[mt][e] = fmaf(gT, S[mt][e], acc[mt][e]);
     }
     __syncthreads();  // every reader of sT and of the chunk's tiles is done
     publish_state();
