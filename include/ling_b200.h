@@ -575,6 +575,23 @@ int ling_b200_format_step(double t, long pass, const char* kind, size_t turn, co
  * Dk = Dv = 128. */
 int ling_b200_gdn_prefill_host(int device, int Hk, int HV, int Dk, int Dv, int M, const float* pre, const uint16_t* convw_bf16,
                                const float* g, const float* beta, float* state, float* conv, float* post, float* core);
+/* One DeltaNet layer's mixer on the prefill path, held on the device with synthetic weights (Engine::forward's
+ * linear-attention branch over many rows, quantized path: rmsnorm, NVFP4 in projections, gdn_conv_prefill, gdn_gating,
+ * gdn_recurrent_prefill, gated_rmsnorm, NVFP4 out projection; src/core/kernels.cuh:190-221,436-456,543-554):
+ *   h += out( gated_norm( delta_rule( conv(in_qkv(norm(h))), gating(in_a, in_b) ), in_z(norm(h)) ) )
+ * for rows of one sequence; the session's state [HV][128][128] and conv window [C][3] advance.  forward takes and returns
+ * host rows; read_stages gives what the last forward left between the stages and read_weights the weights as the device
+ * holds them, both for parity checks; bench times passes over the resident residual. */
+typedef struct ling_b200_prefill_gdn ling_b200_prefill_gdn;
+int ling_b200_prefill_gdn_create(int device, int hidden, int k_heads, int v_heads, int max_rows, uint64_t seed, ling_b200_prefill_gdn** out);
+void ling_b200_prefill_gdn_destroy(ling_b200_prefill_gdn* f);
+int ling_b200_prefill_gdn_state(ling_b200_prefill_gdn* f, int write, float* state, float* conv);
+int ling_b200_prefill_gdn_forward(ling_b200_prefill_gdn* f, const float* h_in, int rows, float* h_out);
+int ling_b200_prefill_gdn_bench(ling_b200_prefill_gdn* f, int rows, int repeats, float* ms);
+int ling_b200_prefill_gdn_read_stages(ling_b200_prefill_gdn* f, int rows, float* xn, float* pre, float* z, float* g, float* beta, float* core);
+int ling_b200_prefill_gdn_read_weights(ling_b200_prefill_gdn* f, uint16_t* norm, uint16_t* convw, uint16_t* wa, uint16_t* wb, uint16_t* A_log,
+                                       uint16_t* dt_bias, uint16_t* lin_norm, uint8_t* qkv_q, uint8_t* qkv_s, uint8_t* z_q, uint8_t* z_s,
+                                       uint8_t* out_q, uint8_t* out_s, float* scales5);
 /* Device time (ms per launch) of the chunked delta rule alone over M rows of synthetic inputs. */
 int ling_b200_gdn_chunk_bench(int device, int Hk, int HV, int M, int iters, float* ms);
 

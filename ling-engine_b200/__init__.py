@@ -558,6 +558,60 @@ def gdn_chunk_bench(Hk, HV, M, iters=10, device=0):
     return ms.value
 
 
+class PrefillGdnLayer:
+    """One DeltaNet layer's mixer on the prefill path with synthetic weights (ling_b200_prefill_gdn_*)."""
+
+    def __init__(self, hidden, k_heads, v_heads, max_rows, seed=0, device=0):
+        self.H, self.Hk, self.HV, self.max_rows = hidden, k_heads, v_heads, max_rows
+        self.C, self.Vs = (2 * k_heads + v_heads) * 128, v_heads * 128
+        self.h = C.c_void_p()
+        check(lib().ling_b200_prefill_gdn_create(device, hidden, k_heads, v_heads, max_rows, C.c_uint64(seed), C.byref(self.h)), "prefill_gdn_create")
+
+    def close(self):
+        if self.h:
+            lib().ling_b200_prefill_gdn_destroy(self.h)
+            self.h = C.c_void_p()
+
+    def set_state(self, state=None, conv=None):
+        s = None if state is None else np.ascontiguousarray(state, np.float32)
+        c = None if conv is None else np.ascontiguousarray(conv, np.float32)
+        check(lib().ling_b200_prefill_gdn_state(self.h, 1, None if s is None else _fp(s), None if c is None else _fp(c)), "prefill_gdn_state")
+
+    def get_state(self):
+        s, c = np.zeros((self.HV, 128, 128), np.float32), np.zeros((self.C, 3), np.float32)
+        check(lib().ling_b200_prefill_gdn_state(self.h, 0, _fp(s), _fp(c)), "prefill_gdn_state")
+        return s, c
+
+    def forward(self, h):
+        h = np.ascontiguousarray(h, np.float32)
+        out = np.zeros_like(h)
+        check(lib().ling_b200_prefill_gdn_forward(self.h, _fp(h), h.shape[0], _fp(out)), "prefill_gdn_forward")
+        return out
+
+    def bench(self, rows, repeats=3):
+        ms = C.c_float()
+        check(lib().ling_b200_prefill_gdn_bench(self.h, rows, repeats, C.byref(ms)), "prefill_gdn_bench")
+        return ms.value / repeats
+
+    def stages(self, rows):
+        o = {"xn": np.zeros((rows, self.H), np.float32), "pre": np.zeros((rows, self.C), np.float32), "z": np.zeros((rows, self.Vs), np.float32),
+             "g": np.zeros((rows, self.HV), np.float32), "beta": np.zeros((rows, self.HV), np.float32), "core": np.zeros((rows, self.Vs), np.float32)}
+        check(lib().ling_b200_prefill_gdn_read_stages(self.h, rows, *[_fp(o[k]) for k in ("xn", "pre", "z", "g", "beta", "core")]), "read_stages")
+        return o
+
+    def weights(self):
+        H, Cc, Vs, HV = self.H, self.C, self.Vs, self.HV
+        w = {"norm": np.zeros(H, np.uint16), "convw": np.zeros((Cc, 4), np.uint16), "wa": np.zeros((HV, H), np.uint16), "wb": np.zeros((HV, H), np.uint16),
+             "A_log": np.zeros(HV, np.uint16), "dt_bias": np.zeros(HV, np.uint16), "lin_norm": np.zeros(128, np.uint16),
+             "qkv_q": np.zeros((Cc, H // 2), np.uint8), "qkv_s": np.zeros((Cc, H // 16), np.uint8), "z_q": np.zeros((Vs, H // 2), np.uint8),
+             "z_s": np.zeros((Vs, H // 16), np.uint8), "out_q": np.zeros((H, Vs // 2), np.uint8), "out_s": np.zeros((H, Vs // 16), np.uint8)}
+        sc = np.zeros(5, np.float32)
+        check(lib().ling_b200_prefill_gdn_read_weights(self.h, *[_u16(w[k]) for k in ("norm", "convw", "wa", "wb", "A_log", "dt_bias", "lin_norm")],
+                                                       *[_bp(w[k]) for k in ("qkv_q", "qkv_s", "z_q", "z_s", "out_q", "out_s")], _fp(sc)), "read_weights")
+        w["in_scale"], w["mid_scale"], w["s_qkv"], w["s_z"], w["s_out"] = (float(v) for v in sc)
+        return w
+
+
 def topk_rows(x, k, device=0):
     """Per row the k largest values, descending, ties to the lower index (ling_b200_topk_rows_host)."""
     x = np.ascontiguousarray(x, np.float32)

@@ -670,6 +670,37 @@ __global__ void __launch_bounds__(256)
   }
 }
 
+// The DeltaNet mixer's gated RMSNorm in front of its out projection (src/core/kernels.cu:543-554) straight into NVFP4:
+// y = core * rstd(core over the head's 128 values) * w * silu(z), rounded to BF16 and encoded.  A thread holds a block of 16
+// values, eight neighbouring threads a head.
+__global__ void __launch_bounds__(256)
+    gated_norm_quant_nvfp4_kernel(const float* __restrict__ core, const float* __restrict__ z, const __nv_bfloat16* __restrict__ w, int M,
+                                  int K, float eps, float gscale, uint8_t* __restrict__ q, uint8_t* __restrict__ sf, int tiled, int k_atoms) {
+  const int bpr = K / 16;
+  const size_t blocks = size_t(M) * bpr;
+  const size_t span = (blocks + 31) / 32 * 32;  // whole warps stay in the loop together (the shuffles name every lane)
+  for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < span; i += size_t(gridDim.x) * blockDim.x) {
+    const bool real = i < blocks;
+    const int row = int((real ? i : 0) / bpr), blk = int((real ? i : 0) % bpr);
+    float v[16], ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float4 f = real ? reinterpret_cast<const float4*>(core + i * 16)[j] : make_float4(0.f, 0.f, 0.f, 0.f);
+      v[4 * j] = f.x, v[4 * j + 1] = f.y, v[4 * j + 2] = f.z, v[4 * j + 3] = f.w;
+      ss = fmaf(f.x, f.x, fmaf(f.y, f.y, fmaf(f.z, f.z, fmaf(f.w, f.w, ss))));
+    }
+    ss += __shfl_xor_sync(0xffffffffu, ss, 1), ss += __shfl_xor_sync(0xffffffffu, ss, 2), ss += __shfl_xor_sync(0xffffffffu, ss, 4);
+    if (!real) continue;
+    const float rstd = rsqrtf(ss / 128.f + eps);
+    const int d0 = (blk % 8) * 16;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) v[j] = bf16_round(v[j] * rstd * __bfloat162float(w[d0 + j]) * silu(z[i * 16 + j]));
+    uint2 codes;
+    const uint8_t sc = encode_block(v, gscale, codes);
+    store_block(q, sf, tiled != 0, row, blk, K, k_atoms, codes, sc);
+  }
+}
+
 // One CTA per row: sum of squares (per-thread fp32 partials over strided float4s, then the block), then one thread per
 // block of 16 normalizes, rounds and encodes.
 __global__ void __launch_bounds__(256)
@@ -845,6 +876,15 @@ int fp4_quant_act_launch(const float* x, const float* up, int M, int K, float gs
   if (up) quant_act_nvfp4_kernel<true><<<g, 256, 0, stream>>>(x, up, M, K, gscale, q, sf, tiled ? 1 : 0, fp4_k_atoms(K));
   else quant_act_nvfp4_kernel<false><<<g, 256, 0, stream>>>(x, nullptr, M, K, gscale, q, sf, tiled ? 1 : 0, fp4_k_atoms(K));
   LB_LAUNCH("quant_act_nvfp4_kernel");
+  return LING_B200_OK;
+}
+
+int fp4_gated_norm_quant_launch(const float* core, const float* z, const __nv_bfloat16* w, int M, int K, float eps, float gscale,
+                                uint8_t* q, uint8_t* sf, bool tiled, cudaStream_t stream) {
+  if (!shape_ok(M, K, "gated_norm_quant_nvfp4") || K % 128 != 0) return LING_B200_ERR_ARG;
+  gated_norm_quant_nvfp4_kernel<<<grid_for(size_t(M) * (K / 16)), 256, 0, stream>>>(core, z, w, M, K, eps, gscale, q, sf, tiled ? 1 : 0,
+                                                                                   fp4_k_atoms(K));
+  LB_LAUNCH("gated_norm_quant_nvfp4_kernel");
   return LING_B200_OK;
 }
 

@@ -71,6 +71,10 @@ int fp4_quant_act_launch(const float* x, const float* up, int M, int K, float gs
 // (src/core/prefill_gemm.cu:426-459).
 int fp4_rmsnorm_quant_launch(const float* x, const __nv_bfloat16* w, float* out, int M, int H, float eps, float gscale, uint8_t* q,
                              uint8_t* sf, bool tiled, cudaStream_t stream);
+// The DeltaNet mixer's gated RMSNorm per head of 128 (src/core/kernels.cu:543-554), core [M][K] and z [M][K] fp32, the plain
+// weight w [128], into NVFP4 as above: the out projection's input on the prefill path.
+int fp4_gated_norm_quant_launch(const float* core, const float* z, const __nv_bfloat16* w, int M, int K, float eps, float gscale,
+                                uint8_t* q, uint8_t* sf, bool tiled, cudaStream_t stream);
 // BF16 weights [N][K] on the device -> NVFP4 in the checkpoints' rounding (the reference's host-side quantize_nvfp4,
 // src/core/model.cu:188-249): tensor scale g = amax / (448 * 6) into *scale2 (device), block scales
 // max(amax16 / 6 / g, 2^-9) as E4M3, codes nearest with ties to the smaller magnitude.  `amax_bits` is one zeroed word.

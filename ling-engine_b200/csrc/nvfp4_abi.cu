@@ -1,12 +1,14 @@
 // nvfp4_abi.cu -- C-ABI entry points of the NVFP4 prefill-chunk path: the quantizers and GEMMs on host buffers (copy in,
 // launch, copy out), as the reference's kernel tests drive them (tests/prefill_tests.cu in the reference project), and the
 // chunk's feed-forward stack (norm -> gate|up with fused SwiGLU -> down into the residual, layer after layer) held on the
-// device for the mixed prefill + decode pass.
+// device for the mixed prefill + decode pass, and one DeltaNet layer's mixer on the prefill path (norm -> in projections ->
+// conv, gating, chunked delta rule -> gated norm -> out projection into the residual).
 #include <cmath>
 #include <cstring>
 #include <memory>
 
 #include "abi_util.h"
+#include "gdn_chunk.h"
 #include "nvfp4.h"
 
 using namespace lb;
@@ -442,6 +444,222 @@ int ling_b200_nvfp4_ffn_read_layer(ling_b200_nvfp4_ffn* f, int layer, uint16_t* 
   LB_TRY(read(L.up, up_q, up_s));
   LB_TRY(read(L.down, down_q, down_s));
   if (scales5) scales5[0] = L.in_scale, scales5[1] = L.mid_scale, scales5[2] = L.s_gate, scales5[3] = L.s_up, scales5[4] = L.s_down;
+  return LING_B200_OK;
+}
+
+// ------------------------------------------------------------------------------------------------ a DeltaNet layer's mixer, prefill path
+// Engine::forward's linear-attention branch for many rows (src/core/engine.cpp, the quantized path: rmsnorm + NVFP4
+// projections, gdn_conv_prefill, gdn_gating, gdn_recurrent_prefill, gated_rmsnorm, out projection) with synthetic weights:
+// h += out( gated_norm( delta_rule( conv(in_qkv(norm(h))) ), in_z(norm(h)) ) ).
+}  // extern "C"
+
+struct ling_b200_prefill_gdn {
+  int device = 0, H = 0, Hk = 0, HV = 0, C = 0, Vs = 0, max_rows = 0;
+  float eps = 1e-6f, in_scale = 1.f, mid_scale = 1.f, s_qkv = 1.f, s_z = 1.f, s_out = 1.f;
+  __nv_bfloat16 *norm = nullptr, *convw = nullptr, *wa = nullptr, *wb = nullptr, *A_log = nullptr, *dt_bias = nullptr, *lin_norm = nullptr;
+  Fp4Operand in_qkv, in_z, out, x, mid;
+  float *h = nullptr, *xn = nullptr, *pre = nullptr, *post = nullptr, *z = nullptr, *g = nullptr, *beta = nullptr, *core = nullptr;
+  float *state = nullptr, *conv = nullptr;
+  int *err = nullptr, *n_rows = nullptr;
+  cudaStream_t stream = nullptr;
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  Scratch mem;
+  ~ling_b200_prefill_gdn() {
+    if (ev0) cudaEventDestroy(ev0);
+    if (ev1) cudaEventDestroy(ev1);
+    if (stream) cudaStreamDestroy(stream);
+  }
+};
+
+namespace {
+
+int synth_operand(Scratch& mem, cudaStream_t st, Fp4Operand& o, int N, int K, uint64_t key, __nv_bfloat16* tmp, unsigned* amax, float* scale2_dev,
+                  float* scale2) {
+  LB_TRY(alloc_operand(mem, o, N, K));
+  LB_TRY(fill_bf16_launch(nullptr, key, 0.02f, 0.f, 1, tmp, size_t(N) * K, st));
+  LB_CUDA(cudaMemsetAsync(amax, 0, 4, st));
+  LB_TRY(fp4_quant_weight_launch(tmp, N, K, o.codes, o.sf, true, scale2_dev, amax, st));
+  LB_CUDA(cudaMemcpyAsync(scale2, scale2_dev, 4, cudaMemcpyDeviceToHost, st));
+  LB_CUDA(cudaStreamSynchronize(st));
+  return LING_B200_OK;
+}
+
+int gdn_layer_run(ling_b200_prefill_gdn* f, int rows) {
+  f->x.rows = rows, f->mid.rows = rows;
+  LB_TRY(make_fp4_map(f->x));
+  LB_TRY(make_fp4_map(f->mid));
+  cudaStream_t st = f->stream;
+  LB_CUDA(cudaMemcpyAsync(f->n_rows, &rows, 4, cudaMemcpyHostToDevice, st));  // (a pageable source: copied before the call returns)
+  LB_TRY(fp4_rmsnorm_quant_launch(f->h, f->norm, f->xn, rows, f->H, f->eps, 1.f / f->in_scale, f->x.codes, f->x.sf, true, st));
+  Fp4GemmCall a;
+  a.X = &f->x, a.W = &f->in_qkv, a.alpha = f->in_scale * f->s_qkv, a.y = f->pre, a.ldy = f->C, a.err_flag = f->err;
+  LB_TRY(fp4_gemm_launch(a, st));
+  Fp4GemmCall b;
+  b.X = &f->x, b.W = &f->in_z, b.alpha = f->in_scale * f->s_z, b.y = f->z, b.ldy = f->Vs, b.err_flag = f->err;
+  LB_TRY(fp4_gemm_launch(b, st));
+  LB_TRY(ab_gating_launch(f->xn, f->wa, f->wb, f->A_log, f->dt_bias, f->g, f->beta, f->n_rows, rows, f->H, f->HV, st));
+  LB_TRY(conv_rows_launch(f->pre, f->convw, f->conv, rows, f->C, f->post, st));
+  LB_TRY(gdn_chunk_launch(f->post, f->g, f->beta, rows, f->Hk, f->HV, 128, 128, f->state, f->core, st));
+  LB_TRY(fp4_gated_norm_quant_launch(f->core, f->z, f->lin_norm, rows, f->Vs, f->eps, 1.f / f->mid_scale, f->mid.codes, f->mid.sf, true, st));
+  Fp4GemmCall o;
+  o.X = &f->mid, o.W = &f->out, o.alpha = f->mid_scale * f->s_out, o.y = f->h, o.ldy = f->H, o.accumulate = true, o.err_flag = f->err;
+  return fp4_gemm_launch(o, st);
+}
+
+}  // namespace
+
+extern "C" {
+
+int ling_b200_prefill_gdn_create(int device, int hidden, int k_heads, int v_heads, int max_rows, uint64_t seed, ling_b200_prefill_gdn** out) {
+  if (!out || !multiple(hidden, 256) || k_heads < 1 || v_heads < 1 || v_heads % k_heads != 0 || !multiple(v_heads * 128, 256) ||
+      !multiple((2 * k_heads + v_heads) * 128, 256) || max_rows < 1) {
+    set_error("prefill_gdn_create: hidden, the mixer's channels and its value width must be multiples of 256 (heads of 128)");
+    return LING_B200_ERR_ARG;
+  }
+  LB_TRY(check_device(device));
+  LB_TRY(gdn_chunk_init());
+  std::unique_ptr<ling_b200_prefill_gdn> f(new ling_b200_prefill_gdn);
+  f->device = device, f->H = hidden, f->Hk = k_heads, f->HV = v_heads, f->max_rows = max_rows;
+  f->C = (2 * k_heads + v_heads) * 128, f->Vs = v_heads * 128;
+  LB_CUDA(cudaStreamCreateWithFlags(&f->stream, cudaStreamNonBlocking));
+  LB_CUDA(cudaEventCreate(&f->ev0));
+  LB_CUDA(cudaEventCreate(&f->ev1));
+  Scratch& m = f->mem;
+  const size_t R = size_t(max_rows);
+  f->h = m.get<float>(R * hidden), f->xn = m.get<float>(R * hidden), f->pre = m.get<float>(R * f->C), f->post = m.get<float>(R * f->C);
+  f->z = m.get<float>(R * f->Vs), f->g = m.get<float>(R * v_heads), f->beta = m.get<float>(R * v_heads), f->core = m.get<float>(R * f->Vs);
+  f->state = m.get<float>(size_t(v_heads) * 128 * 128), f->conv = m.get<float>(size_t(f->C) * 3);
+  f->err = m.get<int>(1), f->n_rows = m.get<int>(1);
+  f->norm = m.get<__nv_bfloat16>(hidden), f->convw = m.get<__nv_bfloat16>(size_t(f->C) * 4);
+  f->wa = m.get<__nv_bfloat16>(size_t(v_heads) * hidden), f->wb = m.get<__nv_bfloat16>(size_t(v_heads) * hidden);
+  f->A_log = m.get<__nv_bfloat16>(v_heads), f->dt_bias = m.get<__nv_bfloat16>(v_heads), f->lin_norm = m.get<__nv_bfloat16>(128);
+  LB_PTR(f->h && f->xn && f->pre && f->post && f->z && f->g && f->beta && f->core && f->state && f->conv && f->err && f->n_rows && f->norm &&
+         f->convw && f->wa && f->wb && f->A_log && f->dt_bias && f->lin_norm);
+  LB_TRY(alloc_operand(m, f->x, max_rows, hidden));
+  LB_TRY(alloc_operand(m, f->mid, max_rows, f->Vs));
+  cudaStream_t st = f->stream;
+  auto key = [&](int t) { return stream_key(seed, weight_stream(0, t)); };
+  LB_TRY(fill_bf16_launch(nullptr, key(LING_B200_T_INPUT_NORM), 0.02f, 0.f, 1, f->norm, hidden, st));
+  LB_TRY(fill_bf16_launch(nullptr, key(LING_B200_T_CONV), 0.3f, 0.f, 1, f->convw, size_t(f->C) * 4, st));
+  LB_TRY(fill_bf16_launch(nullptr, key(LING_B200_T_IN_A), 0.02f, 0.f, 1, f->wa, size_t(v_heads) * hidden, st));
+  LB_TRY(fill_bf16_launch(nullptr, key(LING_B200_T_IN_B), 0.02f, 0.f, 1, f->wb, size_t(v_heads) * hidden, st));
+  LB_TRY(fill_bf16_launch(nullptr, key(LING_B200_T_A_LOG), 0.5f, -1.f, 1, f->A_log, v_heads, st));  // decays exp(-exp(A) softplus(.)) near 1
+  LB_TRY(fill_bf16_launch(nullptr, key(LING_B200_T_DT_BIAS), 0.5f, 0.f, 1, f->dt_bias, v_heads, st));
+  LB_TRY(fill_bf16_launch(nullptr, key(LING_B200_T_LIN_NORM), 0.1f, 1.f, 1, f->lin_norm, 128, st));
+  Scratch tmp;
+  auto* wtmp = tmp.get<__nv_bfloat16>(size_t(std::max(f->C, hidden)) * std::max(hidden, f->Vs), false);
+  unsigned* amax = tmp.get<unsigned>(1);
+  float* s2 = tmp.get<float>(1);
+  LB_PTR(wtmp && amax && s2);
+  LB_TRY(synth_operand(m, st, f->in_qkv, f->C, hidden, key(LING_B200_T_IN_QKV), wtmp, amax, s2, &f->s_qkv));
+  LB_TRY(synth_operand(m, st, f->in_z, f->Vs, hidden, key(LING_B200_T_IN_Z), wtmp, amax, s2, &f->s_z));
+  LB_TRY(synth_operand(m, st, f->out, hidden, f->Vs, key(LING_B200_T_OUT), wtmp, amax, s2, &f->s_out));
+  f->in_scale = 16.f / (6.f * 448.f);  // as the feed-forward stack: magnitudes up to 16 for the normed residual, 64 for the mixer's output
+  f->mid_scale = 64.f / (6.f * 448.f);
+  LB_CUDA(cudaStreamSynchronize(st));
+  *out = f.release();
+  return LING_B200_OK;
+}
+
+void ling_b200_prefill_gdn_destroy(ling_b200_prefill_gdn* f) { delete f; }
+
+// The session's state [HV][128][128] and conv window [C][3]: set (NULL: zero) or read back.
+int ling_b200_prefill_gdn_state(ling_b200_prefill_gdn* f, int write, float* state, float* conv) {
+  if (!f) return LING_B200_ERR_ARG;
+  LB_CUDA(cudaSetDevice(f->device));
+  const size_t sb = size_t(f->HV) * 128 * 128 * 4, cb = size_t(f->C) * 3 * 4;
+  if (write) {
+    if (state) LB_CUDA(cudaMemcpyAsync(f->state, state, sb, cudaMemcpyHostToDevice, f->stream));
+    else LB_CUDA(cudaMemsetAsync(f->state, 0, sb, f->stream));
+    if (conv) LB_CUDA(cudaMemcpyAsync(f->conv, conv, cb, cudaMemcpyHostToDevice, f->stream));
+    else LB_CUDA(cudaMemsetAsync(f->conv, 0, cb, f->stream));
+  } else {
+    if (state) LB_CUDA(cudaMemcpyAsync(state, f->state, sb, cudaMemcpyDeviceToHost, f->stream));
+    if (conv) LB_CUDA(cudaMemcpyAsync(conv, f->conv, cb, cudaMemcpyDeviceToHost, f->stream));
+  }
+  LB_CUDA(cudaStreamSynchronize(f->stream));
+  return LING_B200_OK;
+}
+
+// h [rows][hidden] in, the layer's mixer applied (h += ...), h out; the state and the window advance.
+int ling_b200_prefill_gdn_forward(ling_b200_prefill_gdn* f, const float* h_in, int rows, float* h_out) {
+  if (!f || !h_in || !h_out || rows < 1 || rows > f->max_rows) {
+    set_error("prefill_gdn_forward: bad argument");
+    return LING_B200_ERR_ARG;
+  }
+  LB_CUDA(cudaSetDevice(f->device));
+  const size_t bytes = size_t(rows) * f->H * 4;
+  LB_CUDA(cudaMemcpyAsync(f->h, h_in, bytes, cudaMemcpyHostToDevice, f->stream));
+  LB_TRY(gdn_layer_run(f, rows));
+  LB_CUDA(cudaMemcpyAsync(h_out, f->h, bytes, cudaMemcpyDeviceToHost, f->stream));
+  LB_CUDA(cudaStreamSynchronize(f->stream));
+  return read_flag(f->err, "prefill_gdn_forward");
+}
+
+// `repeats` passes over the resident residual, timed on the device (ms in all); the state keeps advancing.
+int ling_b200_prefill_gdn_bench(ling_b200_prefill_gdn* f, int rows, int repeats, float* ms) {
+  if (!f || rows < 1 || rows > f->max_rows || repeats < 1 || !ms) {
+    set_error("prefill_gdn_bench: bad argument");
+    return LING_B200_ERR_ARG;
+  }
+  LB_CUDA(cudaSetDevice(f->device));
+  LB_TRY(gdn_layer_run(f, rows));
+  LB_CUDA(cudaEventRecord(f->ev0, f->stream));
+  for (int i = 0; i < repeats; ++i) LB_TRY(gdn_layer_run(f, rows));
+  LB_CUDA(cudaEventRecord(f->ev1, f->stream));
+  LB_CUDA(cudaEventSynchronize(f->ev1));
+  LB_CUDA(cudaEventElapsedTime(ms, f->ev0, f->ev1));
+  return read_flag(f->err, "prefill_gdn_bench");
+}
+
+// What the last forward left between the stages, for parity checks (any pointer may be NULL): xn [rows][hidden], pre [rows][C],
+// z [rows][Vs], g / beta [rows][HV], core [rows][Vs].
+int ling_b200_prefill_gdn_read_stages(ling_b200_prefill_gdn* f, int rows, float* xn, float* pre, float* z, float* g, float* beta, float* core) {
+  if (!f || rows < 1 || rows > f->max_rows) return LING_B200_ERR_ARG;
+  LB_CUDA(cudaSetDevice(f->device));
+  const size_t R = size_t(rows);
+  if (xn) LB_CUDA(cudaMemcpy(xn, f->xn, R * f->H * 4, cudaMemcpyDeviceToHost));
+  if (pre) LB_CUDA(cudaMemcpy(pre, f->pre, R * f->C * 4, cudaMemcpyDeviceToHost));
+  if (z) LB_CUDA(cudaMemcpy(z, f->z, R * f->Vs * 4, cudaMemcpyDeviceToHost));
+  if (g) LB_CUDA(cudaMemcpy(g, f->g, R * f->HV * 4, cudaMemcpyDeviceToHost));
+  if (beta) LB_CUDA(cudaMemcpy(beta, f->beta, R * f->HV * 4, cudaMemcpyDeviceToHost));
+  if (core) LB_CUDA(cudaMemcpy(core, f->core, R * f->Vs * 4, cudaMemcpyDeviceToHost));
+  return LING_B200_OK;
+}
+
+// The layer's weights as the device holds them: BF16 bit patterns of the small tensors, and the three NVFP4 matrices (codes
+// [N][K/2], block scales row-major [N][K/16]) with their tensor scales; scales5 = {in_scale, mid_scale, s_qkv, s_z, s_out}.
+int ling_b200_prefill_gdn_read_weights(ling_b200_prefill_gdn* f, uint16_t* norm, uint16_t* convw, uint16_t* wa, uint16_t* wb, uint16_t* A_log,
+                                       uint16_t* dt_bias, uint16_t* lin_norm, uint8_t* qkv_q, uint8_t* qkv_s, uint8_t* z_q, uint8_t* z_s,
+                                       uint8_t* out_q, uint8_t* out_s, float* scales5) {
+  if (!f) return LING_B200_ERR_ARG;
+  LB_CUDA(cudaSetDevice(f->device));
+  Scratch sc;
+  auto small = [&](uint16_t* dst, const __nv_bfloat16* src, size_t n) -> int {
+    if (dst) LB_CUDA(cudaMemcpy(dst, src, n * 2, cudaMemcpyDeviceToHost));
+    return LING_B200_OK;
+  };
+  LB_TRY(small(norm, f->norm, f->H));
+  LB_TRY(small(convw, f->convw, size_t(f->C) * 4));
+  LB_TRY(small(wa, f->wa, size_t(f->HV) * f->H));
+  LB_TRY(small(wb, f->wb, size_t(f->HV) * f->H));
+  LB_TRY(small(A_log, f->A_log, f->HV));
+  LB_TRY(small(dt_bias, f->dt_bias, f->HV));
+  LB_TRY(small(lin_norm, f->lin_norm, 128));
+  auto read = [&](const Fp4Operand& o, uint8_t* q, uint8_t* s) -> int {
+    if (q) LB_CUDA(cudaMemcpy(q, o.codes, size_t(o.rows) * (o.K / 2), cudaMemcpyDeviceToHost));
+    if (s) {
+      uint8_t* raw = sc.get<uint8_t>(size_t(o.rows) * (o.K / 16));
+      LB_PTR(raw);
+      LB_TRY(fp4_sf_untile_launch(o.sf, raw, o.rows, o.K, 0));
+      LB_CUDA(cudaMemcpy(s, raw, size_t(o.rows) * (o.K / 16), cudaMemcpyDeviceToHost));
+    }
+    return LING_B200_OK;
+  };
+  LB_TRY(read(f->in_qkv, qkv_q, qkv_s));
+  LB_TRY(read(f->in_z, z_q, z_s));
+  LB_TRY(read(f->out, out_q, out_s));
+  if (scales5) scales5[0] = f->in_scale, scales5[1] = f->mid_scale, scales5[2] = f->s_qkv, scales5[3] = f->s_z, scales5[4] = f->s_out;
   return LING_B200_OK;
 }
 

@@ -97,3 +97,63 @@ def test_gdn_prefill_rejects_other_head_sizes(gpu, lb):
     pre, convw, g, beta, state, conv = case(1, 1, 1, 4, 0.0)
     with pytest.raises(lb.LingError):
         lb.gdn_prefill(1, 1, 64, 64, pre, lb.to_bf16_bits(convw), g, beta, state, conv)
+
+
+def bf(bits):
+    return (np.asarray(bits).astype(np.uint32) << 16).view(np.float32).reshape(np.shape(bits))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M", [70, 128])
+def test_prefill_gdn_layer_matches_the_oracle_stage_by_stage(gpu, lb, M):
+    """One DeltaNet layer's mixer on the prefill path: norm -> NVFP4 in projections -> conv, gating, chunked delta rule -> gated
+    norm -> NVFP4 out projection.  Each stage is held to the oracle on the inputs the device fed it (so that a block-scale or
+    4-bit code that flips on a last-bit difference upstream does not blur the stages behind it); the whole chain to a looser bar."""
+    H, Hk, HV = 512, 2, 4
+    layer = lb.PrefillGdnLayer(H, Hk, HV, 128, seed=3)
+    w = layer.weights()
+    rng = np.random.default_rng(M)
+    h = rng.standard_normal((M, H)).astype(np.float32)
+    state = (rng.standard_normal((HV, DK, DV)) * 0.1).astype(np.float32)
+    conv = rng.standard_normal((layer.C, 3)).astype(np.float32)
+    layer.set_state(state, conv)
+    out = layer.forward(h)
+    st = layer.stages(M)
+    s1, c1 = layer.get_state()
+    layer.close()
+
+    def gemm(x, scale, q, s, wscale):
+        xq, xs = lo.nvfp4_quant_act(x, scale)
+        return lo.nvfp4_gemm(xq, xs, q, s, scale * wscale)
+
+    def gating(xn):
+        a = xn.astype(np.float64) @ bf(w["wa"]).astype(np.float64).T + bf(w["dt_bias"]).astype(np.float64)
+        b = xn.astype(np.float64) @ bf(w["wb"]).astype(np.float64).T
+        sp = np.where(a <= 20, np.log1p(np.exp(np.minimum(a, 20))), a)  # softplus (src/core/kernels.cu:385-395)
+        return (-np.exp(bf(w["A_log"]).astype(np.float64)) * sp).astype(np.float32), (1 / (1 + np.exp(-b))).astype(np.float32)
+
+    def gated(core, z):  # rmsnorm over each head of 128 with the plain weight, times silu(z) (src/core/kernels.cu:543-554)
+        c = core.astype(np.float64).reshape(M, HV, 128)
+        rstd = 1.0 / np.sqrt((c * c).mean(-1, keepdims=True) + 1e-6)
+        zz = z.astype(np.float64).reshape(M, HV, 128)
+        return (c * rstd * bf(w["lin_norm"]).astype(np.float64) * (zz / (1 + np.exp(-zz)))).reshape(M, HV * 128).astype(np.float32)
+
+    # stage by stage, each from the device's own inputs
+    xn = lo.rmsnorm_rows(h, w["norm"], 1e-6)
+    assert rel(st["xn"], xn) <= 1e-5
+    assert rel(st["pre"], gemm(st["xn"], w["in_scale"], w["qkv_q"], w["qkv_s"], w["s_qkv"])) <= 1e-4
+    assert rel(st["z"], gemm(st["xn"], w["in_scale"], w["z_q"], w["z_s"], w["s_z"])) <= 1e-4
+    g, beta = gating(st["xn"])
+    assert np.abs(st["g"] - g).max() <= 1e-5 * max(1.0, float(np.abs(g).max())) and np.abs(st["beta"] - beta).max() <= 1e-5
+    post, core, os1, oc1 = lo.gdn_prefill(Hk, HV, DK, DV, st["pre"], bf(w["convw"]), st["g"], st["beta"], state, conv)
+    assert close(st["core"], core), (rms_rel(st["core"], core), rel(st["core"], core))
+    assert close(s1, os1) and np.array_equal(c1, oc1)
+    mixed = gemm(gated(st["core"], st["z"]), w["mid_scale"], w["out_q"], w["out_s"], w["s_out"])
+    assert rms_rel(out - h, mixed) <= 2e-3 and rel(out - h, mixed) <= 1e-1  # (a 4-bit code may flip on the last bit of the norm)
+    # the whole chain from the oracle's own stages
+    pre_o = gemm(xn, w["in_scale"], w["qkv_q"], w["qkv_s"], w["s_qkv"])
+    z_o = gemm(xn, w["in_scale"], w["z_q"], w["z_s"], w["s_z"])
+    g_o, b_o = gating(xn)
+    _, core_o, _, _ = lo.gdn_prefill(Hk, HV, DK, DV, pre_o, bf(w["convw"]), g_o, b_o, state, conv)
+    chain = gemm(gated(core_o, z_o), w["mid_scale"], w["out_q"], w["out_s"], w["s_out"])
+    assert rms_rel(out - h, chain) <= 3e-2, rms_rel(out - h, chain)
