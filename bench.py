@@ -28,9 +28,9 @@ KV compaction and DeltaNet commit.  Rank 0 prints ONE JSON line.
 
 Other workloads (one JSON line each, same keys): --workload ragged4 (4 sequences, 74 rows), churn64 (64 sequences sharded over
 the ranks, ~10 % completions and admissions per step through the page pool), served64 (the same 64-sequence load produced by
-the scheduler loop: ling-engine_b200/ling_serve_headless), mixed (a 4096-row prefill chunk through the NVFP4 feed-forward stack
+the scheduler loop: ling-engine_b200/ling_serve_headless), mixed (a 4096-row prefill chunk through the NVFP4 prefill path -- DeltaNet mixers and feed-forward blocks --
 beside an 8-sequence verify step; roofline against the NVFP4 tensor rate measured in the same run), toy.  --micro gemm |
-nvfp4 | nvfp4-swiglu | gdn-chunk times one kernel alone on resident operands (the small cases the profiler captures;
+nvfp4 | nvfp4-swiglu | gdn-chunk | gdn-layer times one kernel (gdn-layer: one DeltaNet layer's prefill mixer) alone on resident operands (the small cases the profiler captures;
 gdn-chunk takes its row count from --shape's first number).
 
 Inputs are synthetic (seeded): they stand in for the reference's private replay workload, whose shapes they take.
@@ -532,10 +532,12 @@ def run_ours(args, rank, local_rank, world):
 
 
 def run_mixed(args, rank, local_rank, world):
-    """The mixed ragged pass: one 4096-token prefill chunk through the NVFP4 feed-forward stack (norm + quantize, gate|up
-    with fused SwiGLU, down into the residual; 64 layers) beside 8 decoding sequences' verify step (24-node trees, contexts
-    uniform in 1k-32k) on every GPU.  The chunk's mixers (prefill attention, chunked delta rule) are not part of this
-    build, so a step's rows are the decode rows plus the chunk rows through the FFN half only: said in `config`.
+    """The mixed ragged pass: one 4096-token prefill chunk through the NVFP4 prefill path -- in the 48 DeltaNet layers the mixer
+    (norm, in projections, conv, gating, chunked delta rule, gated norm, out projection), in all 64 layers the feed-forward
+    block (norm + quantize, gate|up with fused SwiGLU, down into the residual) -- beside 8 decoding sequences' verify step
+    (24-node trees, contexts uniform in 1k-32k) on every GPU.  The 16 full-attention layers' mixer on the prefill path
+    (attention over the chunk's 4096 query rows) is not part of this build: said in `config`.  --chunk-scope ffn leaves the
+    DeltaNet mixers out too (the feed-forward blocks alone).
       value     rows per second with both halves launched together on their own streams (device events per half; the
                 step's time is the longer of the two totals, max over ranks)
       e2e       the same through the host-buffer calls: the chunk's residual copied in and out (pinned staging) and the
@@ -554,6 +556,10 @@ def run_mixed(args, rank, local_rank, world):
     chunk = 4096
     ctx, _, _ = setup_context(lbm, cfg, seqs, args, rank, local_rank, False)
     ffn = lbm.Nvfp4Ffn(cfg.layers, cfg.hidden, cfg.intermediate, chunk, seed=rank, device=local_rank)
+    with_mixers = args.chunk_scope != "ffn"
+    n_mix = sum(1 for l in range(cfg.layers) if l % 4 != 3) if with_mixers else 0
+    if with_mixers:
+        ffn.add_mixers(cfg.lin_k_heads, cfg.lin_v_heads, 4, seed=rank)
     h0 = np.random.default_rng(50 + rank).standard_normal((chunk, cfg.hidden)).astype(np.float32)
     ffn.set_residual(h0)
     flags, K, W = lbm.STEP_COMMIT, args.steps, max(args.warmup, 3)
@@ -585,7 +591,7 @@ def run_mixed(args, rank, local_rank, world):
     ctx.sync()
     dist.barrier()
     step_ms = dist.max(max(verify_ms, ffn_ms)) / K
-    launches = ctx.launch_count() + 3 * cfg.layers
+    launches = ctx.launch_count() + 3 * cfg.layers + 8 * n_mix
     # ---- end to end: host buffers in and out of both halves every step (two host threads, one per half)
     out = [None]
     def chunk_thread():
@@ -615,16 +621,19 @@ def run_mixed(args, rank, local_rank, world):
         line = {
             "metric": METRIC, "value": total_rows / (step_ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
             "ms_per_step": step_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "nvfp4 (e2m1 x ue4m3 per 16, fp32 accumulate) chunk FFN + fp8_e4m3 verify", "data": "synthetic",
+            "dtype": "nvfp4 (e2m1 x ue4m3 per 16, fp32 accumulate) chunk + fp8_e4m3 verify", "data": "synthetic",
             "config": {"workload": "mixed", "model": "27B-class hybrid, %d layers" % cfg.layers, "chunk_rows": chunk,
-                       "chunk_scope": "feed-forward stack only (norm+quantize, gate|up+SwiGLU, down); the chunk's attention / "
-                                      "DeltaNet mixers are not built",
+                       "chunk_scope": ("the %d DeltaNet layers' mixers (norm, NVFP4 in projections, conv, gating, chunked delta rule, gated "
+                                       "norm, NVFP4 out projection) and every layer's feed-forward block; the %d full-attention layers' "
+                                       "mixer on the prefill path is not built" % (n_mix, cfg.layers - n_mix)) if with_mixers else
+                                      "feed-forward blocks only (norm+quantize, gate|up+SwiGLU, down)",
                        "decode_sequences": len(seqs), "decode_rows": rows, "contexts": [q["pos"] for q in seqs],
                        "parallelism": "replicas, one chunk and one decode batch per GPU, no collective",
-                       "l2": "inputs larger than L2 (FP8 weights %.1f GB + NVFP4 FFN weights %.1f GB per step), no flush"
-                             % (ctx.weight_bytes() / 1e9, 3 * cfg.layers * cfg.intermediate * cfg.hidden * 0.5625 / 1e9)},
-            "halves_ms": {"chunk_ffn_alone": ffn_alone, "verify_alone": verify_alone, "serial": ffn_alone + verify_alone,
-                          "chunk_ffn_together": ffn_ms / K, "verify_together": verify_ms / K},
+                       "l2": "inputs larger than L2 (FP8 weights %.1f GB + NVFP4 chunk weights %.1f GB per step), no flush"
+                             % (ctx.weight_bytes() / 1e9, (3 * cfg.layers * cfg.intermediate + n_mix * (4 * cfg.lin_v_heads + 2 * cfg.lin_k_heads) * 128)
+                                * cfg.hidden * 0.5625 / 1e9)},
+            "halves_ms": {"chunk_alone": ffn_alone, "verify_alone": verify_alone, "serial": ffn_alone + verify_alone,
+                          "chunk_together": ffn_ms / K, "verify_together": verify_ms / K},
             "e2e": {"value": total_rows * K / e2e_s, "unit": UNIT, "ms_per_step": e2e_s / K * 1e3,
                     "h2d_bytes_per_step": int(h0.nbytes + ctx_stage_bytes(lbm, len(seqs))),
                     "d2h_bytes_per_step": int(h0.nbytes + len(seqs) * __import__("ctypes").sizeof(lbm.SeqResult) + 4)},
@@ -696,6 +705,14 @@ def run_micro_gemm(args):
         ms = lbm.gdn_chunk_bench(16, 48, M, iters=args.iters)
         print(json.dumps({"micro": "gdn_chunk_kernel", "rows": M, "heads": [16, 48], "iters": args.iters, "us_per_launch": ms * 1e3,
                           "us_per_32_token_chunk": ms * 1e3 / ((M + 31) // 32), "rows_per_s": M / (ms * 1e-3)}), flush=True)
+        return
+    if args.micro == "gdn-layer":
+        # one DeltaNet layer's whole mixer on the prefill path (eight launches), M rows, the 27B model's widths
+        layer = lbm.PrefillGdnLayer(5120, 16, 48, M, seed=1)
+        ms = layer.bench(M, args.iters)
+        layer.close()
+        print(json.dumps({"micro": "prefill DeltaNet mixer (rmsnorm_quant, 2 NVFP4 GEMMs, ab_gating, conv_rows, gdn_chunk, gated_norm_quant, NVFP4 GEMM)",
+                          "rows": M, "iters": args.iters, "ms_per_layer": ms, "rows_per_s": M / (ms * 1e-3)}), flush=True)
         return
     if args.micro in ("nvfp4", "nvfp4-swiglu"):
         # one NVFP4 GEMM alone: N weight rows (N features from 2 N rows in the fused gate|up form), operands resident
@@ -806,10 +823,11 @@ def main():
     ap.add_argument("--no-churn64", action="store_true", help="leave out the 64-sequence sharded batch reported beside the headline")
     ap.add_argument("--quick", action="store_true", help="device-timed steps only (no end-to-end, per-family or CPU legs): "
                     "the short run the profiler's launch list is taken from")
+    ap.add_argument("--chunk-scope", default="ffn+gdn", choices=["ffn+gdn", "ffn"], help="mixed: what the prefill chunk runs through")
     ap.add_argument("--systems", type=int, default=0, help="served64: prompts begin with one of this many shared system messages")
     ap.add_argument("--prefix-kv-mb", type=int, default=0, help="served64 with --systems: the prefix KV store's budget for saved states (0: store off)")
     ap.add_argument("--pool-pages", type=int, default=0, help="served64: KV page pool size (0: sized for the resident sessions)")
-    ap.add_argument("--micro", default="", choices=["", "gemm", "nvfp4", "nvfp4-swiglu", "gdn-chunk"], help="time one kernel alone on resident operands")
+    ap.add_argument("--micro", default="", choices=["", "gemm", "nvfp4", "nvfp4-swiglu", "gdn-chunk", "gdn-layer"], help="time one kernel alone on resident operands")
     ap.add_argument("--shape", default="24,34816,5120", help="--micro gemm: rows,N,K (default: the gate|up projection)")
     ap.add_argument("--iters", type=int, default=20)
     args = ap.parse_args()

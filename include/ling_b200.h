@@ -345,6 +345,10 @@ typedef struct ling_b200_nvfp4_ffn ling_b200_nvfp4_ffn;
 int ling_b200_nvfp4_ffn_create(int device, int layers, int hidden, int intermediate, int max_rows, uint64_t seed,
                                ling_b200_nvfp4_ffn** out);
 void ling_b200_nvfp4_ffn_destroy(ling_b200_nvfp4_ffn* f);
+/* Adds the DeltaNet layers' prefill-path mixers (see ling_b200_prefill_gdn below) in front of their feed-forward blocks: every
+ * layer except each full_every-th (0: every layer) gets synthetic mixer weights and a zero state.  The full-attention layers'
+ * mixer on the prefill path is not built: those layers keep their feed-forward block only. */
+int ling_b200_nvfp4_ffn_add_mixers(ling_b200_nvfp4_ffn* f, int k_heads, int v_heads, int full_every, uint64_t seed);
 int ling_b200_nvfp4_ffn_set_residual(ling_b200_nvfp4_ffn* f, const float* h, int rows);
 int ling_b200_nvfp4_ffn_launch(ling_b200_nvfp4_ffn* f, int rows, int repeats);
 /* CTAs of each GEMM launch of the stack (0 = one per SM): fewer leave SMs to a verify step running beside it. */

@@ -510,6 +510,10 @@ class Nvfp4Ffn:
         h = np.ascontiguousarray(h, np.float32)
         check(lib().ling_b200_nvfp4_ffn_set_residual(self.h, _fp(h), h.shape[0]), "nvfp4_ffn_set_residual")
 
+    def add_mixers(self, k_heads, v_heads, full_every=4, seed=0):
+        """The DeltaNet layers' prefill-path mixers in front of their feed-forward blocks (every layer but each full_every-th)."""
+        check(lib().ling_b200_nvfp4_ffn_add_mixers(self.h, k_heads, v_heads, full_every, C.c_uint64(seed)), "nvfp4_ffn_add_mixers")
+
     def launch(self, rows, repeats=1):
         check(lib().ling_b200_nvfp4_ffn_launch(self.h, rows, repeats), "nvfp4_ffn_launch")
 

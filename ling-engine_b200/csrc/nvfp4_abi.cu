@@ -40,6 +40,22 @@ int read_flag(const int* err, const char* what) {
 
 }  // namespace
 
+// A DeltaNet layer's mixer on the prefill path (Engine::forward's linear-attention branch over many rows, quantized path):
+// one layer's weights and session state, and the activation buffers every layer shares.
+struct GdnWeights {
+  __nv_bfloat16 *norm = nullptr, *convw = nullptr, *wa = nullptr, *wb = nullptr, *A_log = nullptr, *dt_bias = nullptr, *lin_norm = nullptr;
+  Fp4Operand in_qkv, in_z, out;
+  float s_qkv = 1.f, s_z = 1.f, s_out = 1.f;
+  float *state = nullptr, *conv = nullptr;  // [HV][128][128], [C][3]
+};
+struct GdnBuffers {
+  int H = 0, Hk = 0, HV = 0, C = 0, Vs = 0, max_rows = 0;
+  float eps = 1e-6f, in_scale = 16.f / (6.f * 448.f), mid_scale = 64.f / (6.f * 448.f);  // as the feed-forward stack's
+  float *xn = nullptr, *pre = nullptr, *post = nullptr, *z = nullptr, *g = nullptr, *beta = nullptr, *core = nullptr;
+  Fp4Operand x, mid;
+  int* n_rows = nullptr;
+};
+
 // The chunk's feed-forward stack: per layer the post-attention norm weight and the three NVFP4 matrices.
 struct ling_b200_nvfp4_ffn {
   int device = 0, layers = 0, H = 0, I = 0, max_rows = 0;
@@ -52,6 +68,8 @@ struct ling_b200_nvfp4_ffn {
     float s_gate = 1.f, s_up = 1.f, s_down = 1.f;  // the weights' tensor scales
   };
   std::vector<Layer> L;
+  GdnBuffers mix;                // with mixers (ling_b200_nvfp4_ffn_add_mixers): the DeltaNet layers' mixer runs before their FFN
+  std::vector<GdnWeights> mixers;  // by layer; a full-attention layer's entry stays empty (its mixer is not built)
   float* h = nullptr;      // residual [max_rows][H]
   Fp4Operand x, mid;       // the two GEMMs' activations
   int* err = nullptr;
@@ -91,12 +109,87 @@ int synth_matrix(ling_b200_nvfp4_ffn* f, Fp4Operand& o, int N, int K, uint64_t k
   return LING_B200_OK;
 }
 
+bool gdn_shape_ok(int hidden, int k_heads, int v_heads) {
+  return multiple(hidden, 256) && k_heads >= 1 && v_heads >= 1 && v_heads % k_heads == 0 && multiple(v_heads * 128, 256) &&
+         multiple((2 * k_heads + v_heads) * 128, 256);
+}
+
+int synth_operand(Scratch& mem, cudaStream_t st, Fp4Operand& o, int N, int K, uint64_t key, __nv_bfloat16* tmp, unsigned* amax, float* scale2_dev,
+                  float* scale2) {
+  LB_TRY(alloc_operand(mem, o, N, K));
+  LB_TRY(fill_bf16_launch(nullptr, key, 0.02f, 0.f, 1, tmp, size_t(N) * K, st));
+  LB_CUDA(cudaMemsetAsync(amax, 0, 4, st));
+  LB_TRY(fp4_quant_weight_launch(tmp, N, K, o.codes, o.sf, true, scale2_dev, amax, st));
+  LB_CUDA(cudaMemcpyAsync(scale2, scale2_dev, 4, cudaMemcpyDeviceToHost, st));
+  LB_CUDA(cudaStreamSynchronize(st));
+  return LING_B200_OK;
+}
+
+int gdn_buffers_create(Scratch& m, int hidden, int k_heads, int v_heads, int max_rows, GdnBuffers& b) {
+  b.H = hidden, b.Hk = k_heads, b.HV = v_heads, b.max_rows = max_rows;
+  b.C = (2 * k_heads + v_heads) * 128, b.Vs = v_heads * 128;
+  const size_t R = size_t(max_rows);
+  b.xn = m.get<float>(R * hidden), b.pre = m.get<float>(R * b.C), b.post = m.get<float>(R * b.C);
+  b.z = m.get<float>(R * b.Vs), b.g = m.get<float>(R * v_heads), b.beta = m.get<float>(R * v_heads), b.core = m.get<float>(R * b.Vs);
+  b.n_rows = m.get<int>(1);
+  LB_PTR(b.xn && b.pre && b.post && b.z && b.g && b.beta && b.core && b.n_rows);
+  LB_TRY(alloc_operand(m, b.x, max_rows, hidden));
+  return alloc_operand(m, b.mid, max_rows, b.Vs);
+}
+
+// One layer's synthetic weights (the library's generator under the layer's tensor streams) and a zero state.
+int gdn_weights_create(Scratch& m, cudaStream_t st, const GdnBuffers& b, int layer, uint64_t seed, __nv_bfloat16* wtmp, unsigned* amax, float* s2,
+                       GdnWeights& w) {
+  const int H = b.H, HV = b.HV;
+  w.norm = m.get<__nv_bfloat16>(H), w.convw = m.get<__nv_bfloat16>(size_t(b.C) * 4);
+  w.wa = m.get<__nv_bfloat16>(size_t(HV) * H), w.wb = m.get<__nv_bfloat16>(size_t(HV) * H);
+  w.A_log = m.get<__nv_bfloat16>(HV), w.dt_bias = m.get<__nv_bfloat16>(HV), w.lin_norm = m.get<__nv_bfloat16>(128);
+  w.state = m.get<float>(size_t(HV) * 128 * 128), w.conv = m.get<float>(size_t(b.C) * 3);
+  LB_PTR(w.norm && w.convw && w.wa && w.wb && w.A_log && w.dt_bias && w.lin_norm && w.state && w.conv);
+  auto key = [&](int t) { return stream_key(seed, weight_stream(layer, t)); };
+  LB_TRY(fill_bf16_launch(nullptr, key(LING_B200_T_INPUT_NORM), 0.02f, 0.f, 1, w.norm, H, st));
+  LB_TRY(fill_bf16_launch(nullptr, key(LING_B200_T_CONV), 0.3f, 0.f, 1, w.convw, size_t(b.C) * 4, st));
+  LB_TRY(fill_bf16_launch(nullptr, key(LING_B200_T_IN_A), 0.02f, 0.f, 1, w.wa, size_t(HV) * H, st));
+  LB_TRY(fill_bf16_launch(nullptr, key(LING_B200_T_IN_B), 0.02f, 0.f, 1, w.wb, size_t(HV) * H, st));
+  LB_TRY(fill_bf16_launch(nullptr, key(LING_B200_T_A_LOG), 0.5f, -1.f, 1, w.A_log, HV, st));
+  LB_TRY(fill_bf16_launch(nullptr, key(LING_B200_T_DT_BIAS), 0.5f, 0.f, 1, w.dt_bias, HV, st));
+  LB_TRY(fill_bf16_launch(nullptr, key(LING_B200_T_LIN_NORM), 0.1f, 1.f, 1, w.lin_norm, 128, st));
+  LB_TRY(synth_operand(m, st, w.in_qkv, b.C, H, key(LING_B200_T_IN_QKV), wtmp, amax, s2, &w.s_qkv));
+  LB_TRY(synth_operand(m, st, w.in_z, b.Vs, H, key(LING_B200_T_IN_Z), wtmp, amax, s2, &w.s_z));
+  return synth_operand(m, st, w.out, H, b.Vs, key(LING_B200_T_OUT), wtmp, amax, s2, &w.s_out);
+}
+
+// h [rows][H] += out( gated_norm( delta_rule( conv(in_qkv(norm(h))), gating(in_a, in_b) ), in_z(norm(h)) ) ); the layer's state and
+// window advance.  Eight launches on `st`.
+int gdn_mixer_run(GdnBuffers& b, const GdnWeights& w, float* h, int rows, int* err, int ctas, cudaStream_t st) {
+  b.x.rows = rows, b.mid.rows = rows;
+  LB_TRY(make_fp4_map(b.x));
+  LB_TRY(make_fp4_map(b.mid));
+  LB_CUDA(cudaMemcpyAsync(b.n_rows, &rows, 4, cudaMemcpyHostToDevice, st));  // (a pageable source: copied before the call returns)
+  LB_TRY(fp4_rmsnorm_quant_launch(h, w.norm, b.xn, rows, b.H, b.eps, 1.f / b.in_scale, b.x.codes, b.x.sf, true, st));
+  Fp4GemmCall a;
+  a.X = &b.x, a.W = &w.in_qkv, a.alpha = b.in_scale * w.s_qkv, a.y = b.pre, a.ldy = b.C, a.err_flag = err, a.ctas = ctas;
+  LB_TRY(fp4_gemm_launch(a, st));
+  Fp4GemmCall zc;
+  zc.X = &b.x, zc.W = &w.in_z, zc.alpha = b.in_scale * w.s_z, zc.y = b.z, zc.ldy = b.Vs, zc.err_flag = err, zc.ctas = ctas;
+  LB_TRY(fp4_gemm_launch(zc, st));
+  LB_TRY(ab_gating_launch(b.xn, w.wa, w.wb, w.A_log, w.dt_bias, b.g, b.beta, b.n_rows, rows, b.H, b.HV, st));
+  LB_TRY(conv_rows_launch(b.pre, w.convw, w.conv, rows, b.C, b.post, st));
+  LB_TRY(gdn_chunk_launch(b.post, b.g, b.beta, rows, b.Hk, b.HV, 128, 128, w.state, b.core, st));
+  LB_TRY(fp4_gated_norm_quant_launch(b.core, b.z, w.lin_norm, rows, b.Vs, b.eps, 1.f / b.mid_scale, b.mid.codes, b.mid.sf, true, st));
+  Fp4GemmCall o;
+  o.X = &b.mid, o.W = &w.out, o.alpha = b.mid_scale * w.s_out, o.y = h, o.ldy = b.H, o.accumulate = true, o.err_flag = err, o.ctas = ctas;
+  return fp4_gemm_launch(o, st);
+}
+
 // The stack over rows [0, rows) of the residual, on the object's stream.
 int ffn_run(ling_b200_nvfp4_ffn* f, int rows) {
   f->x.rows = rows, f->mid.rows = rows;
   LB_TRY(make_fp4_map(f->x));
   LB_TRY(make_fp4_map(f->mid));
-  for (const auto& L : f->L) {
+  for (size_t l = 0; l < f->L.size(); ++l) {
+    const auto& L = f->L[l];
+    if (l < f->mixers.size() && f->mixers[l].in_qkv.codes) LB_TRY(gdn_mixer_run(f->mix, f->mixers[l], f->h, rows, f->err, f->ctas, f->stream));
     LB_TRY(fp4_rmsnorm_quant_launch(f->h, L.norm, nullptr, rows, f->H, f->eps, 1.f / L.in_scale, f->x.codes, f->x.sf, true, f->stream));
     Fp4GemmCall gu;
     gu.X = &f->x, gu.W = &L.gate, gu.W2 = &L.up;
@@ -366,6 +459,28 @@ int ling_b200_nvfp4_ffn_create(int device, int layers, int hidden, int intermedi
 
 void ling_b200_nvfp4_ffn_destroy(ling_b200_nvfp4_ffn* f) { delete f; }
 
+// The DeltaNet layers' mixers in front of their feed-forward blocks: every layer except each `full_every`-th (the full-attention
+// layers, whose mixer on the prefill path is not built) gets synthetic mixer weights and a zero state; the activation buffers are shared.
+int ling_b200_nvfp4_ffn_add_mixers(ling_b200_nvfp4_ffn* f, int k_heads, int v_heads, int full_every, uint64_t seed) {
+  if (!f || !gdn_shape_ok(f->H, k_heads, v_heads) || full_every < 0 || !f->mixers.empty()) {
+    set_error("nvfp4_ffn_add_mixers: bad argument, or mixers already added");
+    return LING_B200_ERR_ARG;
+  }
+  LB_CUDA(cudaSetDevice(f->device));
+  LB_TRY(gdn_chunk_init());
+  LB_TRY(gdn_buffers_create(f->mem, f->H, k_heads, v_heads, f->max_rows, f->mix));
+  Scratch tmp;
+  auto* wtmp = tmp.get<__nv_bfloat16>(size_t(std::max(f->mix.C, f->H)) * std::max(f->H, f->mix.Vs), false);
+  unsigned* amax = tmp.get<unsigned>(1);
+  float* s2 = tmp.get<float>(1);
+  LB_PTR(wtmp && amax && s2);
+  f->mixers.resize(size_t(f->layers));
+  for (int l = 0; l < f->layers; ++l)
+    if (full_every == 0 || l % full_every != full_every - 1) LB_TRY(gdn_weights_create(f->mem, f->stream, f->mix, l, seed, wtmp, amax, s2, f->mixers[size_t(l)]));
+  LB_CUDA(cudaStreamSynchronize(f->stream));
+  return LING_B200_OK;
+}
+
 int ling_b200_nvfp4_ffn_set_residual(ling_b200_nvfp4_ffn* f, const float* h, int rows) {
   if (!f || !h || rows < 1 || rows > f->max_rows) {
     set_error("nvfp4_ffn_set_residual: bad argument");
@@ -454,13 +569,11 @@ int ling_b200_nvfp4_ffn_read_layer(ling_b200_nvfp4_ffn* f, int layer, uint16_t* 
 }  // extern "C"
 
 struct ling_b200_prefill_gdn {
-  int device = 0, H = 0, Hk = 0, HV = 0, C = 0, Vs = 0, max_rows = 0;
-  float eps = 1e-6f, in_scale = 1.f, mid_scale = 1.f, s_qkv = 1.f, s_z = 1.f, s_out = 1.f;
-  __nv_bfloat16 *norm = nullptr, *convw = nullptr, *wa = nullptr, *wb = nullptr, *A_log = nullptr, *dt_bias = nullptr, *lin_norm = nullptr;
-  Fp4Operand in_qkv, in_z, out, x, mid;
-  float *h = nullptr, *xn = nullptr, *pre = nullptr, *post = nullptr, *z = nullptr, *g = nullptr, *beta = nullptr, *core = nullptr;
-  float *state = nullptr, *conv = nullptr;
-  int *err = nullptr, *n_rows = nullptr;
+  int device = 0;
+  GdnBuffers b;
+  GdnWeights w;
+  float* h = nullptr;
+  int* err = nullptr;
   cudaStream_t stream = nullptr;
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   Scratch mem;
@@ -472,91 +585,33 @@ struct ling_b200_prefill_gdn {
 };
 
 namespace {
-
-int synth_operand(Scratch& mem, cudaStream_t st, Fp4Operand& o, int N, int K, uint64_t key, __nv_bfloat16* tmp, unsigned* amax, float* scale2_dev,
-                  float* scale2) {
-  LB_TRY(alloc_operand(mem, o, N, K));
-  LB_TRY(fill_bf16_launch(nullptr, key, 0.02f, 0.f, 1, tmp, size_t(N) * K, st));
-  LB_CUDA(cudaMemsetAsync(amax, 0, 4, st));
-  LB_TRY(fp4_quant_weight_launch(tmp, N, K, o.codes, o.sf, true, scale2_dev, amax, st));
-  LB_CUDA(cudaMemcpyAsync(scale2, scale2_dev, 4, cudaMemcpyDeviceToHost, st));
-  LB_CUDA(cudaStreamSynchronize(st));
-  return LING_B200_OK;
-}
-
-int gdn_layer_run(ling_b200_prefill_gdn* f, int rows) {
-  f->x.rows = rows, f->mid.rows = rows;
-  LB_TRY(make_fp4_map(f->x));
-  LB_TRY(make_fp4_map(f->mid));
-  cudaStream_t st = f->stream;
-  LB_CUDA(cudaMemcpyAsync(f->n_rows, &rows, 4, cudaMemcpyHostToDevice, st));  // (a pageable source: copied before the call returns)
-  LB_TRY(fp4_rmsnorm_quant_launch(f->h, f->norm, f->xn, rows, f->H, f->eps, 1.f / f->in_scale, f->x.codes, f->x.sf, true, st));
-  Fp4GemmCall a;
-  a.X = &f->x, a.W = &f->in_qkv, a.alpha = f->in_scale * f->s_qkv, a.y = f->pre, a.ldy = f->C, a.err_flag = f->err;
-  LB_TRY(fp4_gemm_launch(a, st));
-  Fp4GemmCall b;
-  b.X = &f->x, b.W = &f->in_z, b.alpha = f->in_scale * f->s_z, b.y = f->z, b.ldy = f->Vs, b.err_flag = f->err;
-  LB_TRY(fp4_gemm_launch(b, st));
-  LB_TRY(ab_gating_launch(f->xn, f->wa, f->wb, f->A_log, f->dt_bias, f->g, f->beta, f->n_rows, rows, f->H, f->HV, st));
-  LB_TRY(conv_rows_launch(f->pre, f->convw, f->conv, rows, f->C, f->post, st));
-  LB_TRY(gdn_chunk_launch(f->post, f->g, f->beta, rows, f->Hk, f->HV, 128, 128, f->state, f->core, st));
-  LB_TRY(fp4_gated_norm_quant_launch(f->core, f->z, f->lin_norm, rows, f->Vs, f->eps, 1.f / f->mid_scale, f->mid.codes, f->mid.sf, true, st));
-  Fp4GemmCall o;
-  o.X = &f->mid, o.W = &f->out, o.alpha = f->mid_scale * f->s_out, o.y = f->h, o.ldy = f->H, o.accumulate = true, o.err_flag = f->err;
-  return fp4_gemm_launch(o, st);
-}
-
+int gdn_layer_run(ling_b200_prefill_gdn* f, int rows) { return gdn_mixer_run(f->b, f->w, f->h, rows, f->err, 0, f->stream); }
 }  // namespace
 
 extern "C" {
 
 int ling_b200_prefill_gdn_create(int device, int hidden, int k_heads, int v_heads, int max_rows, uint64_t seed, ling_b200_prefill_gdn** out) {
-  if (!out || !multiple(hidden, 256) || k_heads < 1 || v_heads < 1 || v_heads % k_heads != 0 || !multiple(v_heads * 128, 256) ||
-      !multiple((2 * k_heads + v_heads) * 128, 256) || max_rows < 1) {
+  if (!out || !gdn_shape_ok(hidden, k_heads, v_heads) || max_rows < 1) {
     set_error("prefill_gdn_create: hidden, the mixer's channels and its value width must be multiples of 256 (heads of 128)");
     return LING_B200_ERR_ARG;
   }
   LB_TRY(check_device(device));
   LB_TRY(gdn_chunk_init());
   std::unique_ptr<ling_b200_prefill_gdn> f(new ling_b200_prefill_gdn);
-  f->device = device, f->H = hidden, f->Hk = k_heads, f->HV = v_heads, f->max_rows = max_rows;
-  f->C = (2 * k_heads + v_heads) * 128, f->Vs = v_heads * 128;
+  f->device = device;
   LB_CUDA(cudaStreamCreateWithFlags(&f->stream, cudaStreamNonBlocking));
   LB_CUDA(cudaEventCreate(&f->ev0));
   LB_CUDA(cudaEventCreate(&f->ev1));
-  Scratch& m = f->mem;
-  const size_t R = size_t(max_rows);
-  f->h = m.get<float>(R * hidden), f->xn = m.get<float>(R * hidden), f->pre = m.get<float>(R * f->C), f->post = m.get<float>(R * f->C);
-  f->z = m.get<float>(R * f->Vs), f->g = m.get<float>(R * v_heads), f->beta = m.get<float>(R * v_heads), f->core = m.get<float>(R * f->Vs);
-  f->state = m.get<float>(size_t(v_heads) * 128 * 128), f->conv = m.get<float>(size_t(f->C) * 3);
-  f->err = m.get<int>(1), f->n_rows = m.get<int>(1);
-  f->norm = m.get<__nv_bfloat16>(hidden), f->convw = m.get<__nv_bfloat16>(size_t(f->C) * 4);
-  f->wa = m.get<__nv_bfloat16>(size_t(v_heads) * hidden), f->wb = m.get<__nv_bfloat16>(size_t(v_heads) * hidden);
-  f->A_log = m.get<__nv_bfloat16>(v_heads), f->dt_bias = m.get<__nv_bfloat16>(v_heads), f->lin_norm = m.get<__nv_bfloat16>(128);
-  LB_PTR(f->h && f->xn && f->pre && f->post && f->z && f->g && f->beta && f->core && f->state && f->conv && f->err && f->n_rows && f->norm &&
-         f->convw && f->wa && f->wb && f->A_log && f->dt_bias && f->lin_norm);
-  LB_TRY(alloc_operand(m, f->x, max_rows, hidden));
-  LB_TRY(alloc_operand(m, f->mid, max_rows, f->Vs));
-  cudaStream_t st = f->stream;
-  auto key = [&](int t) { return stream_key(seed, weight_stream(0, t)); };
-  LB_TRY(fill_bf16_launch(nullptr, key(LING_B200_T_INPUT_NORM), 0.02f, 0.f, 1, f->norm, hidden, st));
-  LB_TRY(fill_bf16_launch(nullptr, key(LING_B200_T_CONV), 0.3f, 0.f, 1, f->convw, size_t(f->C) * 4, st));
-  LB_TRY(fill_bf16_launch(nullptr, key(LING_B200_T_IN_A), 0.02f, 0.f, 1, f->wa, size_t(v_heads) * hidden, st));
-  LB_TRY(fill_bf16_launch(nullptr, key(LING_B200_T_IN_B), 0.02f, 0.f, 1, f->wb, size_t(v_heads) * hidden, st));
-  LB_TRY(fill_bf16_launch(nullptr, key(LING_B200_T_A_LOG), 0.5f, -1.f, 1, f->A_log, v_heads, st));  // decays exp(-exp(A) softplus(.)) near 1
-  LB_TRY(fill_bf16_launch(nullptr, key(LING_B200_T_DT_BIAS), 0.5f, 0.f, 1, f->dt_bias, v_heads, st));
-  LB_TRY(fill_bf16_launch(nullptr, key(LING_B200_T_LIN_NORM), 0.1f, 1.f, 1, f->lin_norm, 128, st));
+  f->h = f->mem.get<float>(size_t(max_rows) * hidden), f->err = f->mem.get<int>(1);
+  LB_PTR(f->h && f->err);
+  LB_TRY(gdn_buffers_create(f->mem, hidden, k_heads, v_heads, max_rows, f->b));
   Scratch tmp;
-  auto* wtmp = tmp.get<__nv_bfloat16>(size_t(std::max(f->C, hidden)) * std::max(hidden, f->Vs), false);
+  auto* wtmp = tmp.get<__nv_bfloat16>(size_t(std::max(f->b.C, hidden)) * std::max(hidden, f->b.Vs), false);
   unsigned* amax = tmp.get<unsigned>(1);
   float* s2 = tmp.get<float>(1);
   LB_PTR(wtmp && amax && s2);
-  LB_TRY(synth_operand(m, st, f->in_qkv, f->C, hidden, key(LING_B200_T_IN_QKV), wtmp, amax, s2, &f->s_qkv));
-  LB_TRY(synth_operand(m, st, f->in_z, f->Vs, hidden, key(LING_B200_T_IN_Z), wtmp, amax, s2, &f->s_z));
-  LB_TRY(synth_operand(m, st, f->out, hidden, f->Vs, key(LING_B200_T_OUT), wtmp, amax, s2, &f->s_out));
-  f->in_scale = 16.f / (6.f * 448.f);  // as the feed-forward stack: magnitudes up to 16 for the normed residual, 64 for the mixer's output
-  f->mid_scale = 64.f / (6.f * 448.f);
-  LB_CUDA(cudaStreamSynchronize(st));
+  LB_TRY(gdn_weights_create(f->mem, f->stream, f->b, 0, seed, wtmp, amax, s2, f->w));
+  LB_CUDA(cudaStreamSynchronize(f->stream));
   *out = f.release();
   return LING_B200_OK;
 }
@@ -567,15 +622,15 @@ void ling_b200_prefill_gdn_destroy(ling_b200_prefill_gdn* f) { delete f; }
 int ling_b200_prefill_gdn_state(ling_b200_prefill_gdn* f, int write, float* state, float* conv) {
   if (!f) return LING_B200_ERR_ARG;
   LB_CUDA(cudaSetDevice(f->device));
-  const size_t sb = size_t(f->HV) * 128 * 128 * 4, cb = size_t(f->C) * 3 * 4;
+  const size_t sb = size_t(f->b.HV) * 128 * 128 * 4, cb = size_t(f->b.C) * 3 * 4;
   if (write) {
-    if (state) LB_CUDA(cudaMemcpyAsync(f->state, state, sb, cudaMemcpyHostToDevice, f->stream));
-    else LB_CUDA(cudaMemsetAsync(f->state, 0, sb, f->stream));
-    if (conv) LB_CUDA(cudaMemcpyAsync(f->conv, conv, cb, cudaMemcpyHostToDevice, f->stream));
-    else LB_CUDA(cudaMemsetAsync(f->conv, 0, cb, f->stream));
+    if (state) LB_CUDA(cudaMemcpyAsync(f->w.state, state, sb, cudaMemcpyHostToDevice, f->stream));
+    else LB_CUDA(cudaMemsetAsync(f->w.state, 0, sb, f->stream));
+    if (conv) LB_CUDA(cudaMemcpyAsync(f->w.conv, conv, cb, cudaMemcpyHostToDevice, f->stream));
+    else LB_CUDA(cudaMemsetAsync(f->w.conv, 0, cb, f->stream));
   } else {
-    if (state) LB_CUDA(cudaMemcpyAsync(state, f->state, sb, cudaMemcpyDeviceToHost, f->stream));
-    if (conv) LB_CUDA(cudaMemcpyAsync(conv, f->conv, cb, cudaMemcpyDeviceToHost, f->stream));
+    if (state) LB_CUDA(cudaMemcpyAsync(state, f->w.state, sb, cudaMemcpyDeviceToHost, f->stream));
+    if (conv) LB_CUDA(cudaMemcpyAsync(conv, f->w.conv, cb, cudaMemcpyDeviceToHost, f->stream));
   }
   LB_CUDA(cudaStreamSynchronize(f->stream));
   return LING_B200_OK;
@@ -583,12 +638,12 @@ int ling_b200_prefill_gdn_state(ling_b200_prefill_gdn* f, int write, float* stat
 
 // h [rows][hidden] in, the layer's mixer applied (h += ...), h out; the state and the window advance.
 int ling_b200_prefill_gdn_forward(ling_b200_prefill_gdn* f, const float* h_in, int rows, float* h_out) {
-  if (!f || !h_in || !h_out || rows < 1 || rows > f->max_rows) {
+  if (!f || !h_in || !h_out || rows < 1 || rows > f->b.max_rows) {
     set_error("prefill_gdn_forward: bad argument");
     return LING_B200_ERR_ARG;
   }
   LB_CUDA(cudaSetDevice(f->device));
-  const size_t bytes = size_t(rows) * f->H * 4;
+  const size_t bytes = size_t(rows) * f->b.H * 4;
   LB_CUDA(cudaMemcpyAsync(f->h, h_in, bytes, cudaMemcpyHostToDevice, f->stream));
   LB_TRY(gdn_layer_run(f, rows));
   LB_CUDA(cudaMemcpyAsync(h_out, f->h, bytes, cudaMemcpyDeviceToHost, f->stream));
@@ -598,7 +653,7 @@ int ling_b200_prefill_gdn_forward(ling_b200_prefill_gdn* f, const float* h_in, i
 
 // `repeats` passes over the resident residual, timed on the device (ms in all); the state keeps advancing.
 int ling_b200_prefill_gdn_bench(ling_b200_prefill_gdn* f, int rows, int repeats, float* ms) {
-  if (!f || rows < 1 || rows > f->max_rows || repeats < 1 || !ms) {
+  if (!f || rows < 1 || rows > f->b.max_rows || repeats < 1 || !ms) {
     set_error("prefill_gdn_bench: bad argument");
     return LING_B200_ERR_ARG;
   }
@@ -615,15 +670,15 @@ int ling_b200_prefill_gdn_bench(ling_b200_prefill_gdn* f, int rows, int repeats,
 // What the last forward left between the stages, for parity checks (any pointer may be NULL): xn [rows][hidden], pre [rows][C],
 // z [rows][Vs], g / beta [rows][HV], core [rows][Vs].
 int ling_b200_prefill_gdn_read_stages(ling_b200_prefill_gdn* f, int rows, float* xn, float* pre, float* z, float* g, float* beta, float* core) {
-  if (!f || rows < 1 || rows > f->max_rows) return LING_B200_ERR_ARG;
+  if (!f || rows < 1 || rows > f->b.max_rows) return LING_B200_ERR_ARG;
   LB_CUDA(cudaSetDevice(f->device));
   const size_t R = size_t(rows);
-  if (xn) LB_CUDA(cudaMemcpy(xn, f->xn, R * f->H * 4, cudaMemcpyDeviceToHost));
-  if (pre) LB_CUDA(cudaMemcpy(pre, f->pre, R * f->C * 4, cudaMemcpyDeviceToHost));
-  if (z) LB_CUDA(cudaMemcpy(z, f->z, R * f->Vs * 4, cudaMemcpyDeviceToHost));
-  if (g) LB_CUDA(cudaMemcpy(g, f->g, R * f->HV * 4, cudaMemcpyDeviceToHost));
-  if (beta) LB_CUDA(cudaMemcpy(beta, f->beta, R * f->HV * 4, cudaMemcpyDeviceToHost));
-  if (core) LB_CUDA(cudaMemcpy(core, f->core, R * f->Vs * 4, cudaMemcpyDeviceToHost));
+  if (xn) LB_CUDA(cudaMemcpy(xn, f->b.xn, R * f->b.H * 4, cudaMemcpyDeviceToHost));
+  if (pre) LB_CUDA(cudaMemcpy(pre, f->b.pre, R * f->b.C * 4, cudaMemcpyDeviceToHost));
+  if (z) LB_CUDA(cudaMemcpy(z, f->b.z, R * f->b.Vs * 4, cudaMemcpyDeviceToHost));
+  if (g) LB_CUDA(cudaMemcpy(g, f->b.g, R * f->b.HV * 4, cudaMemcpyDeviceToHost));
+  if (beta) LB_CUDA(cudaMemcpy(beta, f->b.beta, R * f->b.HV * 4, cudaMemcpyDeviceToHost));
+  if (core) LB_CUDA(cudaMemcpy(core, f->b.core, R * f->b.Vs * 4, cudaMemcpyDeviceToHost));
   return LING_B200_OK;
 }
 
@@ -639,13 +694,13 @@ int ling_b200_prefill_gdn_read_weights(ling_b200_prefill_gdn* f, uint16_t* norm,
     if (dst) LB_CUDA(cudaMemcpy(dst, src, n * 2, cudaMemcpyDeviceToHost));
     return LING_B200_OK;
   };
-  LB_TRY(small(norm, f->norm, f->H));
-  LB_TRY(small(convw, f->convw, size_t(f->C) * 4));
-  LB_TRY(small(wa, f->wa, size_t(f->HV) * f->H));
-  LB_TRY(small(wb, f->wb, size_t(f->HV) * f->H));
-  LB_TRY(small(A_log, f->A_log, f->HV));
-  LB_TRY(small(dt_bias, f->dt_bias, f->HV));
-  LB_TRY(small(lin_norm, f->lin_norm, 128));
+  LB_TRY(small(norm, f->w.norm, f->b.H));
+  LB_TRY(small(convw, f->w.convw, size_t(f->b.C) * 4));
+  LB_TRY(small(wa, f->w.wa, size_t(f->b.HV) * f->b.H));
+  LB_TRY(small(wb, f->w.wb, size_t(f->b.HV) * f->b.H));
+  LB_TRY(small(A_log, f->w.A_log, f->b.HV));
+  LB_TRY(small(dt_bias, f->w.dt_bias, f->b.HV));
+  LB_TRY(small(lin_norm, f->w.lin_norm, 128));
   auto read = [&](const Fp4Operand& o, uint8_t* q, uint8_t* s) -> int {
     if (q) LB_CUDA(cudaMemcpy(q, o.codes, size_t(o.rows) * (o.K / 2), cudaMemcpyDeviceToHost));
     if (s) {
@@ -656,10 +711,10 @@ int ling_b200_prefill_gdn_read_weights(ling_b200_prefill_gdn* f, uint16_t* norm,
     }
     return LING_B200_OK;
   };
-  LB_TRY(read(f->in_qkv, qkv_q, qkv_s));
-  LB_TRY(read(f->in_z, z_q, z_s));
-  LB_TRY(read(f->out, out_q, out_s));
-  if (scales5) scales5[0] = f->in_scale, scales5[1] = f->mid_scale, scales5[2] = f->s_qkv, scales5[3] = f->s_z, scales5[4] = f->s_out;
+  LB_TRY(read(f->w.in_qkv, qkv_q, qkv_s));
+  LB_TRY(read(f->w.in_z, z_q, z_s));
+  LB_TRY(read(f->w.out, out_q, out_s));
+  if (scales5) scales5[0] = f->b.in_scale, scales5[1] = f->b.mid_scale, scales5[2] = f->w.s_qkv, scales5[3] = f->w.s_z, scales5[4] = f->w.s_out;
   return LING_B200_OK;
 }
 
