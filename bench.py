@@ -591,7 +591,7 @@ def run_mixed(args, rank, local_rank, world):
     ctx.sync()
     dist.barrier()
     step_ms = dist.max(max(verify_ms, ffn_ms)) / K
-    launches = ctx.launch_count() + 3 * cfg.layers + 8 * n_mix
+    launches = ctx.launch_count() + 3 * cfg.layers + 9 * n_mix
     # ---- end to end: host buffers in and out of both halves every step (two host threads, one per half)
     out = [None]
     def chunk_thread():

@@ -279,22 +279,42 @@ __global__ void __launch_bounds__(kThreads, 1)
 
 // conv_prefill_kernel + conv_window_kernel (src/core/prefill_gdn.cu:34-72): the four-tap causal conv over M rows in parallel,
 // out of place, the first rows' taps from the session's window, then SiLU; the window afterwards holds the last three raw inputs.
+constexpr int kConvRows = 16;  // rows a thread walks: every raw input is read once (plus three a tile for the taps before it)
 __global__ void __launch_bounds__(256)
     conv_rows_kernel(const float* __restrict__ pre, const __nv_bfloat16* __restrict__ w, const float* __restrict__ win, int M, int C,
                      float* __restrict__ post) {
   pdl_sync();  // first statement: see common.cuh
-  const size_t total = size_t(M) * C;
-  for (size_t idx = size_t(blockIdx.x) * blockDim.x + threadIdx.x; idx < total; idx += size_t(gridDim.x) * blockDim.x) {
-    const int t = int(idx / C), c = int(idx % C);
-    float x[4];
+  const int c4 = blockIdx.x * blockDim.x + threadIdx.x, t0 = blockIdx.y * kConvRows;
+  if (c4 * 4 >= C) return;
+  const int c = c4 * 4;
+  float wt[4][4], x[3][4];  // [channel][tap], [age: oldest first][channel]
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int tt = t - 3 + j;
-      x[j] = tt >= 0 ? pre[size_t(tt) * C + c] : win[c * 3 + 3 + tt];
+  for (int e = 0; e < 4; ++e) {
+    const uint2 wr = *reinterpret_cast<const uint2*>(w + size_t(c + e) * 4);
+    const __nv_bfloat162 w01 = *reinterpret_cast<const __nv_bfloat162*>(&wr.x), w23 = *reinterpret_cast<const __nv_bfloat162*>(&wr.y);
+    wt[e][0] = __low2float(w01), wt[e][1] = __high2float(w01), wt[e][2] = __low2float(w23), wt[e][3] = __high2float(w23);
+  }
+#pragma unroll
+  for (int j = 0; j < 3; ++j) {
+    const int tt = t0 - 3 + j;
+    if (tt >= 0) {
+      const float4 v = *reinterpret_cast<const float4*>(pre + size_t(tt) * C + c);
+      x[j][0] = v.x, x[j][1] = v.y, x[j][2] = v.z, x[j][3] = v.w;
+    } else {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) x[j][e] = win[(c + e) * 3 + 3 + tt];
     }
-    const float o = __bfloat162float(w[c * 4]) * x[0] + __bfloat162float(w[c * 4 + 1]) * x[1] + __bfloat162float(w[c * 4 + 2]) * x[2] +
-                    __bfloat162float(w[c * 4 + 3]) * x[3];
-    post[idx] = silu(o);
+  }
+  for (int t = t0; t < min(t0 + kConvRows, M); ++t) {
+    const float4 v = *reinterpret_cast<const float4*>(pre + size_t(t) * C + c);
+    const float cur[4] = {v.x, v.y, v.z, v.w};
+    float o[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      o[e] = silu(wt[e][0] * x[0][e] + wt[e][1] * x[1][e] + wt[e][2] * x[2][e] + wt[e][3] * cur[e]);
+      x[0][e] = x[1][e], x[1][e] = x[2][e], x[2][e] = cur[e];
+    }
+    *reinterpret_cast<float4*>(post + size_t(t) * C + c) = make_float4(o[0], o[1], o[2], o[3]);
   }
 }
 __global__ void __launch_bounds__(256) conv_window_kernel(const float* __restrict__ pre, float* __restrict__ win, int M, int C) {
@@ -328,8 +348,9 @@ int gdn_chunk_launch(const float* post, const float* g, const float* beta, int M
 
 int conv_rows_launch(const float* pre, const __nv_bfloat16* w, float* window, int M, int C, float* post, cudaStream_t s) {
   if (M < 1 || C < 1) return LING_B200_ERR_ARG;
-  const int grid = int(std::min<size_t>((size_t(M) * C + 255) / 256, size_t(148) * 16));
-  LB_CUDA(launch_kernel(conv_rows_kernel, dim3(grid), dim3(256), size_t(0), s, pre, w, (const float*)window, M, C, post));
+  if (C % 4 != 0) return LING_B200_ERR_ARG;
+  LB_CUDA(launch_kernel(conv_rows_kernel, dim3(ceil_div(C / 4, 256), ceil_div(M, kConvRows)), dim3(256), size_t(0), s, pre, w, (const float*)window,
+                        M, C, post));
   LB_LAUNCH("conv_rows_kernel");
   LB_CUDA(launch_kernel(conv_window_kernel, dim3(ceil_div(C, 256)), dim3(256), size_t(0), s, pre, window, M, C));
   LB_LAUNCH("conv_window_kernel");

@@ -353,6 +353,60 @@ __global__ void __launch_bounds__(128)
   }
 }
 
+// The same for the many rows of a prefill chunk: a block takes four rows and four value heads, so a row of xn is read once per
+// four heads and a weight row once per four rows (the per-(row, head) blocks above move 40 KB for 10 K multiply-adds, which at
+// 4096 rows is 8 GB of L2 traffic).  The products and sums are the same fp32 ones; only their order differs.
+__global__ void __launch_bounds__(128)
+    ab_gating_rows_kernel(const float* __restrict__ xn, const __nv_bfloat16* __restrict__ wa, const __nv_bfloat16* __restrict__ wb,
+                          const __nv_bfloat16* __restrict__ A_log, const __nv_bfloat16* __restrict__ dt_bias, float* __restrict__ g,
+                          float* __restrict__ beta, int M, int H, int HV) {
+  pdl_sync();  // first statement: see common.cuh
+  __shared__ float red[4][32];
+  const int hv0 = blockIdx.x * 4, m0 = blockIdx.y * 4, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float sa[4][4] = {}, sb[4][4] = {};  // [row][head]
+  for (int c = threadIdx.x * 4; c < H; c += 512) {
+    float4 xv[4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) xv[r] = m0 + r < M ? *reinterpret_cast<const float4*>(xn + size_t(m0 + r) * H + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int hh = 0; hh < 4; ++hh) {
+      if (hv0 + hh >= HV) break;
+      const uint2 ar = *reinterpret_cast<const uint2*>(wa + size_t(hv0 + hh) * H + c), br = *reinterpret_cast<const uint2*>(wb + size_t(hv0 + hh) * H + c);
+      const __nv_bfloat162 a01 = *reinterpret_cast<const __nv_bfloat162*>(&ar.x), a23 = *reinterpret_cast<const __nv_bfloat162*>(&ar.y);
+      const __nv_bfloat162 b01 = *reinterpret_cast<const __nv_bfloat162*>(&br.x), b23 = *reinterpret_cast<const __nv_bfloat162*>(&br.y);
+      const float a0 = __low2float(a01), a1 = __high2float(a01), a2 = __low2float(a23), a3 = __high2float(a23);
+      const float b0 = __low2float(b01), b1 = __high2float(b01), b2 = __low2float(b23), b3 = __high2float(b23);
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        sa[r][hh] += xv[r].x * a0 + xv[r].y * a1 + xv[r].z * a2 + xv[r].w * a3;
+        sb[r][hh] += xv[r].x * b0 + xv[r].y * b1 + xv[r].z * b2 + xv[r].w * b3;
+      }
+    }
+  }
+  // 32 sums over the block's 128 threads: warps first, then lane v of warp 0 adds the four warps' value v
+#pragma unroll
+  for (int r = 0; r < 4; ++r)
+#pragma unroll
+    for (int hh = 0; hh < 4; ++hh) {
+      const float va = warp_sum(sa[r][hh]), vb = warp_sum(sb[r][hh]);
+      if (lane == 0) red[warp][(r * 4 + hh) * 2] = va, red[warp][(r * 4 + hh) * 2 + 1] = vb;
+    }
+  __syncthreads();
+  if (warp == 0) {
+    const float tot = red[0][lane] + red[1][lane] + red[2][lane] + red[3][lane];
+    const int r = lane / 8, hh = (lane / 2) % 4, isb = lane & 1, m = m0 + r, hv = hv0 + hh;
+    if (m < M && hv < HV) {
+      if (isb) {
+        beta[size_t(m) * HV + hv] = 1.f / (1.f + __expf(-tot));
+      } else {
+        const float xx = tot + __bfloat162float(dt_bias[hv]);
+        const float sp = xx <= 20.f ? log1pf(__expf(xx)) : xx;
+        g[size_t(m) * HV + hv] = -__expf(__bfloat162float(A_log[hv])) * sp;
+      }
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------------------------- DeltaNet
 // The verify's conv over each sequence's tree (src/core/kernels.cu:365-383): a row's taps are the raw inputs of its
 // ancestors at depths d-3 .. d-1 (the variant's path) or the session's window before depth 0; the window is left
@@ -1757,6 +1811,14 @@ int copy_rows_launch(const float* src, float* out, const int* n_rows, int rows_g
   Planes none;
   LB_CUDA(launch_kernel(tap_kernel, dim3(rows_grid), dim3(256), size_t(0), s, src, none, out, n_rows, H));
   LB_LAUNCH("tap_kernel");
+  return LING_B200_OK;
+}
+
+int ab_gating_rows_launch(const float* xn, const __nv_bfloat16* wa, const __nv_bfloat16* wb, const __nv_bfloat16* A_log,
+                          const __nv_bfloat16* dt_bias, float* g, float* beta, int M, int H, int HV, cudaStream_t s) {
+  if (M < 1 || H % 4 != 0) return LING_B200_ERR_ARG;
+  LB_CUDA(launch_kernel(ab_gating_rows_kernel, dim3(ceil_div(HV, 4), ceil_div(M, 4)), dim3(128), size_t(0), s, xn, wa, wb, A_log, dt_bias, g, beta, M, H, HV));
+  LB_LAUNCH("ab_gating_rows_kernel");
   return LING_B200_OK;
 }
 

@@ -149,6 +149,9 @@ int norm_quant_launch(float* h, const Planes& add, const int* ids, const __nv_bf
 int tap_launch(const float* h, const Planes& add, float* out, const int* n_rows, int rows_grid, int H, cudaStream_t s);
 int copy_rows_launch(const float* src, float* out, const int* n_rows, int rows_grid, int H, cudaStream_t s);
 int kernels_norm_stamps(unsigned long long* stamps);  // debugging aid: five %globaltimer stamps of norm_quant's block (0, 0), or nullptr
+// the same for the many rows of a prefill chunk (four rows x four heads a block)
+int ab_gating_rows_launch(const float* xn, const __nv_bfloat16* wa, const __nv_bfloat16* wb, const __nv_bfloat16* A_log,
+                          const __nv_bfloat16* dt_bias, float* g, float* beta, int M, int H, int HV, cudaStream_t s);
 int ab_gating_launch(const float* xn, const __nv_bfloat16* wa, const __nv_bfloat16* wb, const __nv_bfloat16* A_log,
                      const __nv_bfloat16* dt_bias, float* g, float* beta, const int* n_rows, int rows_grid, int H, int HV,
                      cudaStream_t s);

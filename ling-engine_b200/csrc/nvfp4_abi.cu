@@ -160,12 +160,11 @@ int gdn_weights_create(Scratch& m, cudaStream_t st, const GdnBuffers& b, int lay
 }
 
 // h [rows][H] += out( gated_norm( delta_rule( conv(in_qkv(norm(h))), gating(in_a, in_b) ), in_z(norm(h)) ) ); the layer's state and
-// window advance.  Eight launches on `st`.
+// window advance.  Nine launches on `st`.
 int gdn_mixer_run(GdnBuffers& b, const GdnWeights& w, float* h, int rows, int* err, int ctas, cudaStream_t st) {
   b.x.rows = rows, b.mid.rows = rows;
   LB_TRY(make_fp4_map(b.x));
   LB_TRY(make_fp4_map(b.mid));
-  LB_CUDA(cudaMemcpyAsync(b.n_rows, &rows, 4, cudaMemcpyHostToDevice, st));  // (a pageable source: copied before the call returns)
   LB_TRY(fp4_rmsnorm_quant_launch(h, w.norm, b.xn, rows, b.H, b.eps, 1.f / b.in_scale, b.x.codes, b.x.sf, true, st));
   Fp4GemmCall a;
   a.X = &b.x, a.W = &w.in_qkv, a.alpha = b.in_scale * w.s_qkv, a.y = b.pre, a.ldy = b.C, a.err_flag = err, a.ctas = ctas;
@@ -173,7 +172,7 @@ int gdn_mixer_run(GdnBuffers& b, const GdnWeights& w, float* h, int rows, int* e
   Fp4GemmCall zc;
   zc.X = &b.x, zc.W = &w.in_z, zc.alpha = b.in_scale * w.s_z, zc.y = b.z, zc.ldy = b.Vs, zc.err_flag = err, zc.ctas = ctas;
   LB_TRY(fp4_gemm_launch(zc, st));
-  LB_TRY(ab_gating_launch(b.xn, w.wa, w.wb, w.A_log, w.dt_bias, b.g, b.beta, b.n_rows, rows, b.H, b.HV, st));
+  LB_TRY(ab_gating_rows_launch(b.xn, w.wa, w.wb, w.A_log, w.dt_bias, b.g, b.beta, rows, b.H, b.HV, st));
   LB_TRY(conv_rows_launch(b.pre, w.convw, w.conv, rows, b.C, b.post, st));
   LB_TRY(gdn_chunk_launch(b.post, b.g, b.beta, rows, b.Hk, b.HV, 128, 128, w.state, b.core, st));
   LB_TRY(fp4_gated_norm_quant_launch(b.core, b.z, w.lin_norm, rows, b.Vs, b.eps, 1.f / b.mid_scale, b.mid.codes, b.mid.sf, true, st));
