@@ -591,7 +591,7 @@ def run_mixed(args, rank, local_rank, world):
     ctx.sync()
     dist.barrier()
     step_ms = dist.max(max(verify_ms, ffn_ms)) / K
-    launches = ctx.launch_count() + 3 * cfg.layers + 9 * n_mix
+    launches = ctx.launch_count() + 3 * cfg.layers + 10 * n_mix
     # ---- end to end: host buffers in and out of both halves every step (two host threads, one per half)
     out = [None]
     def chunk_thread():
@@ -703,7 +703,7 @@ def run_micro_gemm(args):
     if args.micro == "gdn-chunk":
         # the prefill path's chunked delta rule alone: M rows of one sequence, the 27B model's 16 key / 48 value heads of 128
         ms = lbm.gdn_chunk_bench(16, 48, M, iters=args.iters)
-        print(json.dumps({"micro": "gdn_chunk_kernel", "rows": M, "heads": [16, 48], "iters": args.iters, "us_per_launch": ms * 1e3,
+        print(json.dumps({"micro": "gdn_chunk_prepare_kernel + gdn_chunk_apply_kernel", "rows": M, "heads": [16, 48], "iters": args.iters, "us_per_launch": ms * 1e3,
                           "us_per_32_token_chunk": ms * 1e3 / ((M + 31) // 32), "rows_per_s": M / (ms * 1e-3)}), flush=True)
         return
     if args.micro == "gdn-layer":

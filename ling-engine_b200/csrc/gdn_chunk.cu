@@ -12,7 +12,9 @@
 // below the 64-row minimum of tcgen05.mma, and the chain of chunks is bound by its dependent steps, not by tensor
 // throughput.  The state stays in fp32 registers (the accumulator layout of its own update) and is multiplied as an FP16
 // copy; q and k arrive un-normalized (the conv's output) and are L2-normalized here, q also scaled by 1/sqrt(Dk).
-// One CTA of 16 warps per value head walks the chunks in order.  Key and value dimension 128.
+// Two kernels: A, P, Tinv, U and W do not depend on the state, so one CTA per (chunk, value head) prepares them for every chunk at
+// once (the GPU is full), and one CTA of 16 warps per value head then walks the chunks in order with only the state-dependent
+// products left (two barriers a chunk), the prepared records arriving by cp.async three chunks ahead.  Key and value dimension 128.
 #include <cuda_fp16.h>
 
 #include "gdn_chunk.h"
@@ -20,25 +22,40 @@
 namespace lb {
 namespace {
 
-constexpr int kD = 128, kT = 32, kThreads = 512;
+constexpr int kD = 128, kT = 32, kThreads = 512, kPrepThreads = 256;
 constexpr int kLdD = 136;  // halves per row of a [*][128] tile: rows 68 words apart, the 8 x 4 fragment loads hit 32 banks
 constexpr int kLdT = 40;   // halves per row of a [*][32] tile
 
-struct ChunkSmem {
+// What the state-independent half leaves per (chunk, value head) for the state-dependent half, in the padded layouts the MMAs
+// read from shared memory (so the record is copied there as it is): 46720 bytes.
+struct ChunkTiles {
   __half q[kT * kLdD];     // q^ [i][d]
+  __half w[kT * kLdD];     // W = Tinv (beta gamma k^) [i][d]
+  __half p[kT * kLdT];     // exp(G_i - G_j) q_i . k_j, j <= i
+  __half kpT[kD * kLdT];   // k'^T [d][j]
+};
+struct ChunkRecord {
+  ChunkTiles t;
+  float u[kT * kD];        // U = Tinv (beta v) [i][c]
+  float gam[kT];           // gamma_i
+};
+static_assert(sizeof(ChunkRecord) % 16 == 0 && sizeof(ChunkTiles) % 16 == 0, "records are copied in 16-byte pieces");
+
+struct PrepSmem {  // the prepare kernel's working tiles (the record's q, w, p, kpT are built in `t`; u goes straight to global memory)
+  ChunkTiles t;
   __half k[kT * kLdD];     // k^ [i][d]
-  __half w[kT * kLdD];     // W [i][d]
   __half bvT[kD * kLdT];   // (beta v)^T [c][j]
   __half bgkT[kD * kLdT];  // (beta gamma k^)^T [d][j]
-  __half kpT[kD * kLdT];   // k'^T [d][j]
-  __half dT[kD * kLdT];    // Delta^T [c][j]
-  __half sT[kD * kLdD];    // S0^T [c][d]
   __half tinv[kT * kLdT];  // Tinv [i][j]
-  __half p[kT * kLdT];     // exp(G_i - G_j) q_i . k_j, j <= i
   float a[kT][kT + 1];     // A, fp32 for the substitution
   float G[kT], gam[kT], beta[kT];
-  // the next chunk's raw rows, copied in (cp.async) while the current chunk is computed
-  float rq[kT * kD], rk[kT * kD], rv[kT * kD], rg[kT], rb[kT];
+};
+
+constexpr int kStages = 3;  // records in flight in the apply kernel
+struct ApplySmem {
+  ChunkRecord rec[kStages];
+  __half sT[kD * kLdD];    // S0^T [c][d], the state's FP16 copy
+  __half dT[kD * kLdT];    // Delta^T [c][j]
 };
 
 __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -83,24 +100,134 @@ __device__ __forceinline__ void tiles_mma(float (&c)[MT][4], const __half* A, in
 __device__ __forceinline__ void copy16(void* dst, const void* src, bool real) {  // zero-filled when the row does not exist
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(uint32_t(__cvta_generic_to_shared(dst))), "l"(src), "r"(real ? 16 : 0) : "memory");
 }
-__device__ __forceinline__ void copy4(void* dst, const void* src, bool real) {
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(uint32_t(__cvta_generic_to_shared(dst))), "l"(src), "r"(real ? 4 : 0) : "memory");
-}
-__device__ __forceinline__ void copies_done() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 __device__ __forceinline__ uint32_t h2(float lo, float hi) {
   const __half2 v = __floats2half2_rn(lo, hi);
   return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-__global__ void __launch_bounds__(kThreads, 1)
-    gdn_chunk_kernel(const float* __restrict__ post, const float* __restrict__ g, const float* __restrict__ beta, int M, int Hk, int HV,
-                     float* __restrict__ state, float* __restrict__ core) {
+// The state-independent half, one CTA of 8 warps per (chunk, value head): L2 norms, the decays, A and P, the substitution, U and
+// W.  6144 independent CTAs for 4096 rows of the 27B model: this half fills the GPU.
+__global__ void __launch_bounds__(kPrepThreads)
+    gdn_chunk_prepare_kernel(const float* __restrict__ post, const float* __restrict__ g, const float* __restrict__ beta, int M, int Hk, int HV,
+                             ChunkRecord* __restrict__ records) {
   pdl_sync();  // first statement: see common.cuh
   extern __shared__ __align__(16) unsigned char raw_smem[];
-  ChunkSmem& sm = *reinterpret_cast<ChunkSmem*>(raw_smem);
-  const int hv = blockIdx.x, h = hv / (HV / Hk), tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  PrepSmem& sm = *reinterpret_cast<PrepSmem*>(raw_smem);
+  const int chunk = blockIdx.x, hv = blockIdx.y, h = hv / (HV / Hk), tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int gq = lane >> 2, tq = lane & 3;
-  const int C = 2 * Hk * kD + HV * kD;
+  const int C = 2 * Hk * kD + HV * kD, c0 = chunk * kT, n = min(kT, M - c0);
+  // rows past n: k = v = 0, beta = 0, g = 0 -- they change nothing and are not stored
+  // ---- gates: every warp scans the log-decays (lane i ends with G_i); warp 0 keeps them for the later phases
+  float G = lane < n ? g[size_t(c0 + lane) * HV + hv] : 0.f;
+  const float b_lane = lane < n ? beta[size_t(c0 + lane) * HV + hv] : 0.f;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const float up = __shfl_up_sync(0xffffffffu, G, o);
+    if (lane >= o) G += up;
+  }
+  const float G_last = __shfl_sync(0xffffffffu, G, kT - 1);
+  if (warp == 0) sm.G[lane] = G, sm.gam[lane] = __expf(G), sm.beta[lane] = b_lane;
+  // ---- q^, k^ (four rows a warp, in two pairs; lane l holds the elements l, l + 32, l + 64, l + 96), k^ scaled for W and the state
+  for (int pr = 0; pr < 2; ++pr) {
+    const int i0 = 4 * warp + 2 * pr;
+    float kx[2][4], bg[2], kp[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int i = i0 + r;
+      float qv[4], kv[4], sq = 0.f, sk = 0.f;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float* row = post + size_t(c0 + min(i, n - 1)) * C;
+        qv[e] = i < n ? row[h * kD + lane + 32 * e] : 0.f, kv[e] = i < n ? row[Hk * kD + h * kD + lane + 32 * e] : 0.f;
+        sq = fmaf(qv[e], qv[e], sq), sk = fmaf(kv[e], kv[e], sk);
+      }
+      sq = warp_sum(sq), sk = warp_sum(sk);
+      const float cq = rsqrtf(sq + 1e-6f) * rsqrtf(float(kD)), ck = rsqrtf(sk + 1e-6f);
+      const float Gi = __shfl_sync(0xffffffffu, G, i), bi = __shfl_sync(0xffffffffu, b_lane, i);
+      bg[r] = bi * __expf(Gi), kp[r] = __expf(G_last - Gi);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        kx[r][e] = kv[e] * ck;
+        sm.t.q[i * kLdD + lane + 32 * e] = __float2half_rn(qv[e] * cq);
+        sm.k[i * kLdD + lane + 32 * e] = __float2half_rn(kx[r][e]);
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {  // the two rows of a transposed tile as one 32-bit store
+      *reinterpret_cast<uint32_t*>(sm.bgkT + (lane + 32 * e) * kLdT + i0) = h2(bg[0] * kx[0][e], bg[1] * kx[1][e]);
+      *reinterpret_cast<uint32_t*>(sm.t.kpT + (lane + 32 * e) * kLdT + i0) = h2(kp[0] * kx[0][e], kp[1] * kx[1][e]);
+    }
+  }
+  for (int idx = tid; idx < (kT / 2) * kD; idx += kPrepThreads) {
+    const int i = (idx / kD) * 2, c = idx % kD;
+    const float b0 = __shfl_sync(0xffffffffu, b_lane, i), b1 = __shfl_sync(0xffffffffu, b_lane, i + 1);  // (i is warp-uniform: 128 columns a row pair)
+    const float v0 = i < n ? post[size_t(c0 + i) * C + 2 * Hk * kD + hv * kD + c] : 0.f;
+    const float v1 = i + 1 < n ? post[size_t(c0 + i + 1) * C + 2 * Hk * kD + hv * kD + c] : 0.f;
+    *reinterpret_cast<uint32_t*>(sm.bvT + c * kLdT + i) = h2(b0 * v0, b1 * v1);
+  }
+  __syncthreads();
+  // ---- K K^T (warps 0-3, two tiles each) and Q K^T (warps 4-7)
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int t8 = (warp & 3) * 2 + half, m0 = (t8 >> 2) * 16, n0 = (t8 & 3) * 8;
+    float acc[1][4] = {};
+    tiles_mma<1, kD>(acc, warp < 4 ? sm.k : sm.t.q, kLdD, t8 >> 2, sm.k, kLdD, n0, lane);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int i = m0 + gq + (e >> 1) * 8, j = n0 + 2 * tq + (e & 1);
+      const float decay = __expf(sm.G[i] - sm.G[j]);  // <= 1 for j <= i
+      if (warp < 4) sm.a[i][j] = j < i ? sm.beta[i] * decay * acc[0][e] : 0.f;
+      else sm.t.p[i * kLdT + j] = __float2half_rn(j <= i ? decay * acc[0][e] : 0.f);
+    }
+  }
+  __syncthreads();
+  // ---- Tinv = (I + A)^-1 by forward substitution: lane l of warp 0 solves column l, x_i = [i == l] - sum_(j < i) A_ij x_j
+  if (warp == 0) {
+    float x[kT];
+#pragma unroll
+    for (int i = 0; i < kT; ++i) {
+      float part[4] = {i == lane ? 1.f : 0.f, 0.f, 0.f, 0.f};  // four interleaved sums: a quarter of the dependent chain
+#pragma unroll
+      for (int j = 0; j < i; ++j) part[j & 3] = fmaf(-sm.a[i][j], x[j], part[j & 3]);
+      x[i] = (part[0] + part[1]) + (part[2] + part[3]);
+      sm.tinv[i * kLdT + lane] = __float2half_rn(x[i]);
+    }
+  }
+  __syncthreads();
+  // ---- U = Tinv (beta v) and W = Tinv (beta gamma k): warp w takes the columns 16 w .. 16 w + 15
+  ChunkRecord* out = records + size_t(chunk) * HV + hv;
+#pragma unroll
+  for (int nt = 0; nt < 2; ++nt) {
+    const int n0 = warp * 16 + nt * 8;
+    float u[2][4] = {}, wv[2][4] = {};
+    tiles_mma<2, kT>(u, sm.tinv, kLdT, 0, sm.bvT, kLdT, n0, lane);
+    tiles_mma<2, kT>(wv, sm.tinv, kLdT, 0, sm.bgkT, kLdT, n0, lane);
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt) {
+      *reinterpret_cast<float2*>(out->u + (mt * 16 + gq) * kD + n0 + 2 * tq) = make_float2(u[mt][0], u[mt][1]);
+      *reinterpret_cast<float2*>(out->u + (mt * 16 + gq + 8) * kD + n0 + 2 * tq) = make_float2(u[mt][2], u[mt][3]);
+      *reinterpret_cast<uint32_t*>(sm.t.w + (mt * 16 + gq) * kLdD + n0 + 2 * tq) = h2(wv[mt][0], wv[mt][1]);
+      *reinterpret_cast<uint32_t*>(sm.t.w + (mt * 16 + gq + 8) * kLdD + n0 + 2 * tq) = h2(wv[mt][2], wv[mt][3]);
+    }
+  }
+  __syncthreads();
+  // ---- the record's shared-memory tiles out (q, w, p, kpT: the record's first bytes) and the decays
+  const uint4* src = reinterpret_cast<const uint4*>(&sm.t);
+  uint4* dst = reinterpret_cast<uint4*>(&out->t);
+  for (int idx = tid; idx < int(sizeof(ChunkTiles) / 16); idx += kPrepThreads) dst[idx] = src[idx];
+  if (tid < kT) out->gam[tid] = sm.gam[tid];
+}
+
+// The state-dependent half, one CTA of 16 warps per value head walking the chunks in order: Delta = U - W S0, O = diag(gamma) Q S0 +
+// P Delta, S = gamma_T S0 + K'^T Delta.  The records arrive by cp.async three chunks ahead; two barriers per chunk.
+__global__ void __launch_bounds__(kThreads, 1)
+    gdn_chunk_apply_kernel(const ChunkRecord* __restrict__ records, int M, int HV, float* __restrict__ state, float* __restrict__ core) {
+  pdl_sync();  // first statement: see common.cuh
+  extern __shared__ __align__(16) unsigned char raw_smem[];
+  ApplySmem& sm = *reinterpret_cast<ApplySmem*>(raw_smem);
+  const int hv = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int gq = lane >> 2, tq = lane & 3;
+  const int n_chunks = (M + kT - 1) / kT;
   float* st = state + size_t(hv) * kD * kD;
   // The state in the accumulator layout of its update: warp w owns the value columns 8 w .. 8 w + 7, S[mt][*] the key rows
   // 16 mt + gq (two of them: +8) at columns 8 w + 2 tq, + 1.
@@ -121,154 +248,64 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
   };
   publish_state();
-  // Requests the raw rows of the chunk that starts at row r0: q, k (this key head) and v (this value head), g and beta.
-  auto fetch_chunk = [&](int r0) {
-    const int rows = min(kT, M - r0);
-    for (int idx = tid; idx < 3 * kT * (kD / 4); idx += kThreads) {
-      const int part = idx / (kT * (kD / 4)), i = (idx / (kD / 4)) % kT, e = (idx % (kD / 4)) * 4;
-      const bool real = i < rows;
-      const float* row = post + size_t(r0 + (real ? i : 0)) * C;
-      const float* src = part == 0 ? row + h * kD + e : part == 1 ? row + Hk * kD + h * kD + e : row + 2 * Hk * kD + hv * kD + e;
-      copy16((part == 0 ? sm.rq : part == 1 ? sm.rk : sm.rv) + i * kD + e, src, real);
+  auto fetch = [&](int chunk) {  // one cp.async group per chunk (an empty group past the end keeps the count uniform)
+    if (chunk < n_chunks) {
+      const char* src = reinterpret_cast<const char*>(records + size_t(chunk) * HV + hv);
+      char* dst = reinterpret_cast<char*>(&sm.rec[chunk % kStages]);
+      for (int idx = tid; idx < int(sizeof(ChunkRecord) / 16); idx += kThreads) copy16(dst + idx * 16, src + idx * 16, true);
     }
-    if (tid < 2 * kT) {
-      const int i = tid % kT;
-      const bool real = i < rows;
-      copy4((tid < kT ? sm.rg : sm.rb) + i, (tid < kT ? g : beta) + size_t(r0 + (real ? i : 0)) * HV + hv, real);
-    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
   };
-  fetch_chunk(0);
-
-  for (int c0 = 0; c0 < M; c0 += kT) {
-    const int n = min(kT, M - c0);  // rows past n: k = v = 0, beta = 0, g = 0 -- they change nothing and are not stored
-    copies_done();
-    __syncthreads();  // the chunk's raw rows are in shared memory; the previous chunk's readers of the tiles are done
-    // ---- gates: every warp scans the log-decays (lane i ends with G_i); warp 0 also keeps them for the later phases
-    float G = sm.rg[lane];
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const float up = __shfl_up_sync(0xffffffffu, G, o);
-      if (lane >= o) G += up;
-    }
-    const float G_last = __shfl_sync(0xffffffffu, G, kT - 1);
-    if (warp == 0) sm.G[lane] = G, sm.gam[lane] = __expf(G), sm.beta[lane] = sm.rb[lane];
-    // ---- q^, k^ (two rows a warp; lane l holds the elements l, l + 32, l + 64, l + 96), k^ scaled for W and for the state update
-    {
-      const int i0 = 2 * warp;
-      float kx[2][4], bg[2], kp[2];
-#pragma unroll
-      for (int r = 0; r < 2; ++r) {
-        const int i = i0 + r;
-        float qv[4], kv[4], sq = 0.f, sk = 0.f;
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          qv[e] = sm.rq[i * kD + lane + 32 * e], kv[e] = sm.rk[i * kD + lane + 32 * e];
-          sq = fmaf(qv[e], qv[e], sq), sk = fmaf(kv[e], kv[e], sk);
-        }
-        sq = warp_sum(sq), sk = warp_sum(sk);
-        const float cq = rsqrtf(sq + 1e-6f) * rsqrtf(float(kD)), ck = rsqrtf(sk + 1e-6f);
-        const float Gi = __shfl_sync(0xffffffffu, G, i);
-        bg[r] = sm.rb[i] * __expf(Gi), kp[r] = __expf(G_last - Gi);
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          kx[r][e] = kv[e] * ck;
-          sm.q[i * kLdD + lane + 32 * e] = __float2half_rn(qv[e] * cq);
-          sm.k[i * kLdD + lane + 32 * e] = __float2half_rn(kx[r][e]);
-        }
-      }
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {  // the two rows of a transposed tile as one 32-bit store
-        *reinterpret_cast<uint32_t*>(sm.bgkT + (lane + 32 * e) * kLdT + i0) = h2(bg[0] * kx[0][e], bg[1] * kx[1][e]);
-        *reinterpret_cast<uint32_t*>(sm.kpT + (lane + 32 * e) * kLdT + i0) = h2(kp[0] * kx[0][e], kp[1] * kx[1][e]);
-      }
-    }
-    for (int idx = tid; idx < (kT / 2) * kD; idx += kThreads) {
-      const int i = (idx / kD) * 2, c = idx % kD;
-      *reinterpret_cast<uint32_t*>(sm.bvT + c * kLdT + i) = h2(sm.rb[i] * sm.rv[i * kD + c], sm.rb[i + 1] * sm.rv[(i + 1) * kD + c]);
-    }
-    __syncthreads();
-    if (c0 + kT < M) fetch_chunk(c0 + kT);  // lands while this chunk is computed
-    // ---- Q S0 (every warp: its 8 value columns, both row halves), K K^T (warps 0-7) and Q K^T (warps 8-15)
+  fetch(0);
+  fetch(1);
+  for (int ch = 0; ch < n_chunks; ++ch) {
+    const int c0 = ch * kT, n = min(kT, M - c0);
+    asm volatile("cp.async.wait_group 1;" ::: "memory");  // this chunk's record has landed (the next one may still be on its way)
+    __syncthreads();  // ... for every thread; the state's copy of the previous chunk is published; its readers of rec / dT are done
+    fetch(ch + 2);    // into the stage chunk ch - 1 used
+    const ChunkRecord& r = sm.rec[ch % kStages];
+    // ---- Q S0 and W S0 (every warp: its 8 value columns, both row halves), Delta = U - W S0 transposed to shared memory
     float qs[2][4] = {};
-    tiles_mma<2, kD>(qs, sm.q, kLdD, 0, sm.sT, kLdD, warp * 8, lane);
-    {
-      const int t8 = warp & 7, m0 = (t8 >> 2) * 16, n0 = (t8 & 3) * 8;
-      float acc[1][4] = {};
-      tiles_mma<1, kD>(acc, warp < 8 ? sm.k : sm.q, kLdD, t8 >> 2, sm.k, kLdD, n0, lane);
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int i = m0 + gq + (e >> 1) * 8, j = n0 + 2 * tq + (e & 1);
-        const float decay = __expf(sm.G[i] - sm.G[j]);  // <= 1 for j <= i
-        if (warp < 8) sm.a[i][j] = j < i ? sm.beta[i] * decay * acc[0][e] : 0.f;
-        else sm.p[i * kLdT + j] = __float2half_rn(j <= i ? decay * acc[0][e] : 0.f);
-      }
-    }
-    __syncthreads();
-    // ---- Tinv = (I + A)^-1 by forward substitution: lane l of warp 0 solves column l, x_i = [i == l] - sum_(j < i) A_ij x_j
-    if (warp == 0) {
-      float x[kT];
-#pragma unroll
-      for (int i = 0; i < kT; ++i) {
-        float part[4] = {i == lane ? 1.f : 0.f, 0.f, 0.f, 0.f};  // four interleaved sums: a quarter of the dependent chain
-#pragma unroll
-        for (int j = 0; j < i; ++j) part[j & 3] = fmaf(-sm.a[i][j], x[j], part[j & 3]);
-        x[i] = (part[0] + part[1]) + (part[2] + part[3]);
-        sm.tinv[i * kLdT + lane] = __float2half_rn(x[i]);
-      }
-    }
-    __syncthreads();
-    // ---- U = Tinv (beta v) (kept in registers), W = Tinv (beta gamma k) (to shared memory)
-    float u[2][4] = {};
-    tiles_mma<2, kT>(u, sm.tinv, kLdT, 0, sm.bvT, kLdT, warp * 8, lane);
-    {
-      float wv[2][4] = {};
-      tiles_mma<2, kT>(wv, sm.tinv, kLdT, 0, sm.bgkT, kLdT, warp * 8, lane);
-#pragma unroll
-      for (int mt = 0; mt < 2; ++mt) {
-        *reinterpret_cast<uint32_t*>(sm.w + (mt * 16 + gq) * kLdD + warp * 8 + 2 * tq) = h2(wv[mt][0], wv[mt][1]);
-        *reinterpret_cast<uint32_t*>(sm.w + (mt * 16 + gq + 8) * kLdD + warp * 8 + 2 * tq) = h2(wv[mt][2], wv[mt][3]);
-      }
-    }
-    __syncthreads();
-    // ---- Delta = U - W S0, transposed to shared memory
+    tiles_mma<2, kD>(qs, r.t.q, kLdD, 0, sm.sT, kLdD, warp * 8, lane);
     {
       float ws[2][4] = {};
-      tiles_mma<2, kD>(ws, sm.w, kLdD, 0, sm.sT, kLdD, warp * 8, lane);
+      tiles_mma<2, kD>(ws, r.t.w, kLdD, 0, sm.sT, kLdD, warp * 8, lane);
 #pragma unroll
       for (int mt = 0; mt < 2; ++mt) {
         const int i = mt * 16 + gq, c = warp * 8 + 2 * tq;
-        sm.dT[c * kLdT + i] = __float2half_rn(u[mt][0] - ws[mt][0]), sm.dT[(c + 1) * kLdT + i] = __float2half_rn(u[mt][1] - ws[mt][1]);
-        sm.dT[c * kLdT + i + 8] = __float2half_rn(u[mt][2] - ws[mt][2]), sm.dT[(c + 1) * kLdT + i + 8] = __float2half_rn(u[mt][3] - ws[mt][3]);
+        const float2 ua = *reinterpret_cast<const float2*>(r.u + i * kD + c), ub = *reinterpret_cast<const float2*>(r.u + (i + 8) * kD + c);
+        sm.dT[c * kLdT + i] = __float2half_rn(ua.x - ws[mt][0]), sm.dT[(c + 1) * kLdT + i] = __float2half_rn(ua.y - ws[mt][1]);
+        sm.dT[c * kLdT + i + 8] = __float2half_rn(ub.x - ws[mt][2]), sm.dT[(c + 1) * kLdT + i + 8] = __float2half_rn(ub.y - ws[mt][3]);
       }
     }
-    __syncthreads();
+    __syncthreads();  // Delta is complete; nobody reads the state's FP16 copy any more
     // ---- O = diag(gamma) Q S0 + P Delta; S = gamma_T S + K'^T Delta
     {
       float pd[2][4] = {};
-      tiles_mma<2, kT>(pd, sm.p, kLdT, 0, sm.dT, kLdT, warp * 8, lane);
+      tiles_mma<2, kT>(pd, r.t.p, kLdT, 0, sm.dT, kLdT, warp * 8, lane);
 #pragma unroll
       for (int mt = 0; mt < 2; ++mt) {
         const int i = mt * 16 + gq, c = warp * 8 + 2 * tq;
         if (i < n)
           *reinterpret_cast<float2*>(core + size_t(c0 + i) * HV * kD + size_t(hv) * kD + c) =
-              make_float2(fmaf(sm.gam[i], qs[mt][0], pd[mt][0]), fmaf(sm.gam[i], qs[mt][1], pd[mt][1]));
+              make_float2(fmaf(r.gam[i], qs[mt][0], pd[mt][0]), fmaf(r.gam[i], qs[mt][1], pd[mt][1]));
         if (i + 8 < n)
           *reinterpret_cast<float2*>(core + size_t(c0 + i + 8) * HV * kD + size_t(hv) * kD + c) =
-              make_float2(fmaf(sm.gam[i + 8], qs[mt][2], pd[mt][2]), fmaf(sm.gam[i + 8], qs[mt][3], pd[mt][3]));
+              make_float2(fmaf(r.gam[i + 8], qs[mt][2], pd[mt][2]), fmaf(r.gam[i + 8], qs[mt][3], pd[mt][3]));
       }
     }
-    const float gT = sm.gam[kT - 1];
+    const float gT = r.gam[kT - 1];
     {
       float acc[8][4] = {};
-      tiles_mma<8, kT>(acc, sm.kpT, kLdT, 0, sm.dT, kLdT, warp * 8, lane);
+      tiles_mma<8, kT>(acc, r.t.kpT, kLdT, 0, sm.dT, kLdT, warp * 8, lane);
 #pragma unroll
       for (int mt = 0; mt < 8; ++mt)
 #pragma unroll
         for (int e = 0; e < 4; ++e) S[mt][e] = fmaf(gT, S[mt][e], acc[mt][e]);
     }
-    __syncthreads();  // every reader of sT and of the chunk's tiles is done
     publish_state();
   }
+  asm volatile("cp.async.wait_all;" ::: "memory");
 #pragma unroll
   for (int mt = 0; mt < 8; ++mt) {
     const int d = mt * 16 + gq, c = warp * 8 + 2 * tq;
@@ -334,15 +371,21 @@ __global__ void __launch_bounds__(256) conv_window_kernel(const float* __restric
 }  // namespace
 
 int gdn_chunk_init() {
-  LB_CUDA(cudaFuncSetAttribute(gdn_chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(sizeof(ChunkSmem))));
+  LB_CUDA(cudaFuncSetAttribute(gdn_chunk_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(sizeof(PrepSmem))));
+  LB_CUDA(cudaFuncSetAttribute(gdn_chunk_apply_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(sizeof(ApplySmem))));
   return LING_B200_OK;
 }
 
+size_t gdn_chunk_scratch_bytes(int M, int HV) { return size_t(ceil_div(std::max(M, 1), kT)) * std::max(HV, 1) * sizeof(ChunkRecord); }
+
 int gdn_chunk_launch(const float* post, const float* g, const float* beta, int M, int Hk, int HV, int Dk, int Dv, float* state, float* core,
-                     cudaStream_t s) {
-  if (Dk != kD || Dv != kD || M < 1 || Hk < 1 || HV % Hk != 0) return LING_B200_ERR_ARG;
-  LB_CUDA(launch_kernel(gdn_chunk_kernel, dim3(HV), dim3(kThreads), sizeof(ChunkSmem), s, post, g, beta, M, Hk, HV, state, core));
-  LB_LAUNCH("gdn_chunk_kernel");
+                     void* scratch, cudaStream_t s) {
+  if (Dk != kD || Dv != kD || M < 1 || Hk < 1 || HV % Hk != 0 || !scratch) return LING_B200_ERR_ARG;
+  ChunkRecord* rec = static_cast<ChunkRecord*>(scratch);
+  LB_CUDA(launch_kernel(gdn_chunk_prepare_kernel, dim3(ceil_div(M, kT), HV), dim3(kPrepThreads), sizeof(PrepSmem), s, post, g, beta, M, Hk, HV, rec));
+  LB_LAUNCH("gdn_chunk_prepare_kernel");
+  LB_CUDA(launch_kernel(gdn_chunk_apply_kernel, dim3(HV), dim3(kThreads), sizeof(ApplySmem), s, (const ChunkRecord*)rec, M, HV, state, core));
+  LB_LAUNCH("gdn_chunk_apply_kernel");
   return LING_B200_OK;
 }
 

@@ -14,7 +14,10 @@ int conv_rows_launch(const float* pre, const __nv_bfloat16* w, float* window, in
 // The gated delta rule over the M rows of one sequence in 32-token chunks (gdn_recurrent_prefill, kernels.cuh:450-456):
 // post [M][C] (q | k | v channels, C = 2 Hk Dk + HV Dv), g and beta [M][HV], state [HV][Dk][Dv] updated in place,
 // core [M][HV Dv].  Dk = Dv = 128.
+// scratch: gdn_chunk_scratch_bytes(M, HV) bytes on the device (what the state-independent half leaves for the other: 46 KB per
+// chunk and value head).
+size_t gdn_chunk_scratch_bytes(int M, int HV);
 int gdn_chunk_launch(const float* post, const float* g, const float* beta, int M, int Hk, int HV, int Dk, int Dv, float* state, float* core,
-                     cudaStream_t s);
+                     void* scratch, cudaStream_t s);
 
 }  // namespace lb

@@ -508,9 +508,10 @@ int ling_b200_gdn_prefill_host(int device, int Hk, int HV, int Dk, int Dv, int M
   float* d_conv = sc.put(conv, size_t(C) * 3);
   float* d_post = sc.get<float>(size_t(M) * C);
   float* d_core = sc.get<float>(size_t(M) * HV * Dv);
-  LB_PTR(d_pre && d_w && d_g && d_b && d_state && d_conv && d_post && d_core);
+  uint8_t* d_scr = sc.get<uint8_t>(gdn_chunk_scratch_bytes(M, HV), false);
+  LB_PTR(d_pre && d_w && d_g && d_b && d_state && d_conv && d_post && d_core && d_scr);
   LB_TRY(conv_rows_launch(d_pre, d_w, d_conv, M, C, d_post, 0));
-  LB_TRY(gdn_chunk_launch(d_post, d_g, d_b, M, Hk, HV, Dk, Dv, d_state, d_core, 0));
+  LB_TRY(gdn_chunk_launch(d_post, d_g, d_b, M, Hk, HV, Dk, Dv, d_state, d_core, d_scr, 0));
   LB_CUDA(cudaDeviceSynchronize());
   LB_CUDA(cudaMemcpy(state, d_state, size_t(HV) * Dk * Dv * 4, cudaMemcpyDeviceToHost));
   LB_CUDA(cudaMemcpy(conv, d_conv, size_t(C) * 3 * 4, cudaMemcpyDeviceToHost));
@@ -534,17 +535,18 @@ int ling_b200_gdn_chunk_bench(int device, int Hk, int HV, int M, int iters, floa
   float* d_b = sc.get<float>(size_t(M) * HV, false);
   float* d_state = sc.get<float>(size_t(HV) * 128 * 128);
   float* d_core = sc.get<float>(size_t(M) * HV * 128, false);
-  LB_PTR(d_post && d_g && d_b && d_state && d_core);
+  uint8_t* d_scr = sc.get<uint8_t>(gdn_chunk_scratch_bytes(M, HV), false);
+  LB_PTR(d_post && d_g && d_b && d_state && d_core && d_scr);
   LB_TRY(fill_f32_launch(stream_key(1, 1), 1.f, d_post, size_t(M) * C, 0));
   LB_TRY(fill_f32_launch(stream_key(1, 2), 0.05f, d_g, size_t(M) * HV, 0));  // log-decays near 0 (|g| small), signs mixed
   LB_TRY(fill_f32_launch(stream_key(1, 3), 0.2f, d_b, size_t(M) * HV, 0));
   cudaEvent_t a, b;
   LB_CUDA(cudaEventCreate(&a));
   LB_CUDA(cudaEventCreate(&b));
-  LB_TRY(gdn_chunk_launch(d_post, d_g, d_b, M, Hk, HV, 128, 128, d_state, d_core, 0));
+  LB_TRY(gdn_chunk_launch(d_post, d_g, d_b, M, Hk, HV, 128, 128, d_state, d_core, d_scr, 0));
   LB_CUDA(cudaMemsetAsync(d_state, 0, size_t(HV) * 128 * 128 * 4, 0));
   LB_CUDA(cudaEventRecord(a, 0));
-  for (int i = 0; i < iters; ++i) LB_TRY(gdn_chunk_launch(d_post, d_g, d_b, M, Hk, HV, 128, 128, d_state, d_core, 0));
+  for (int i = 0; i < iters; ++i) LB_TRY(gdn_chunk_launch(d_post, d_g, d_b, M, Hk, HV, 128, 128, d_state, d_core, d_scr, 0));
   LB_CUDA(cudaEventRecord(b, 0));
   LB_CUDA(cudaEventSynchronize(b));
   float t = 0;

@@ -53,7 +53,7 @@ struct GdnBuffers {
   float eps = 1e-6f, in_scale = 16.f / (6.f * 448.f), mid_scale = 64.f / (6.f * 448.f);  // as the feed-forward stack's
   float *xn = nullptr, *pre = nullptr, *post = nullptr, *z = nullptr, *g = nullptr, *beta = nullptr, *core = nullptr;
   Fp4Operand x, mid;
-  int* n_rows = nullptr;
+  uint8_t* chunk_scratch = nullptr;  // gdn_chunk_scratch_bytes(max_rows, HV)
 };
 
 // The chunk's feed-forward stack: per layer the post-attention norm weight and the three NVFP4 matrices.
@@ -131,8 +131,8 @@ int gdn_buffers_create(Scratch& m, int hidden, int k_heads, int v_heads, int max
   const size_t R = size_t(max_rows);
   b.xn = m.get<float>(R * hidden), b.pre = m.get<float>(R * b.C), b.post = m.get<float>(R * b.C);
   b.z = m.get<float>(R * b.Vs), b.g = m.get<float>(R * v_heads), b.beta = m.get<float>(R * v_heads), b.core = m.get<float>(R * b.Vs);
-  b.n_rows = m.get<int>(1);
-  LB_PTR(b.xn && b.pre && b.post && b.z && b.g && b.beta && b.core && b.n_rows);
+  b.chunk_scratch = m.get<uint8_t>(gdn_chunk_scratch_bytes(max_rows, v_heads), false);
+  LB_PTR(b.xn && b.pre && b.post && b.z && b.g && b.beta && b.core && b.chunk_scratch);
   LB_TRY(alloc_operand(m, b.x, max_rows, hidden));
   return alloc_operand(m, b.mid, max_rows, b.Vs);
 }
@@ -160,7 +160,7 @@ int gdn_weights_create(Scratch& m, cudaStream_t st, const GdnBuffers& b, int lay
 }
 
 // h [rows][H] += out( gated_norm( delta_rule( conv(in_qkv(norm(h))), gating(in_a, in_b) ), in_z(norm(h)) ) ); the layer's state and
-// window advance.  Nine launches on `st`.
+// window advance.  Ten launches on `st`.
 int gdn_mixer_run(GdnBuffers& b, const GdnWeights& w, float* h, int rows, int* err, int ctas, cudaStream_t st) {
   b.x.rows = rows, b.mid.rows = rows;
   LB_TRY(make_fp4_map(b.x));
@@ -174,7 +174,7 @@ int gdn_mixer_run(GdnBuffers& b, const GdnWeights& w, float* h, int rows, int* e
   LB_TRY(fp4_gemm_launch(zc, st));
   LB_TRY(ab_gating_rows_launch(b.xn, w.wa, w.wb, w.A_log, w.dt_bias, b.g, b.beta, rows, b.H, b.HV, st));
   LB_TRY(conv_rows_launch(b.pre, w.convw, w.conv, rows, b.C, b.post, st));
-  LB_TRY(gdn_chunk_launch(b.post, b.g, b.beta, rows, b.Hk, b.HV, 128, 128, w.state, b.core, st));
+  LB_TRY(gdn_chunk_launch(b.post, b.g, b.beta, rows, b.Hk, b.HV, 128, 128, w.state, b.core, b.chunk_scratch, st));
   LB_TRY(fp4_gated_norm_quant_launch(b.core, b.z, w.lin_norm, rows, b.Vs, b.eps, 1.f / b.mid_scale, b.mid.codes, b.mid.sf, true, st));
   Fp4GemmCall o;
   o.X = &b.mid, o.W = &w.out, o.alpha = b.mid_scale * w.s_out, o.y = h, o.ldy = b.H, o.accumulate = true, o.err_flag = err, o.ctas = ctas;
