@@ -363,7 +363,7 @@ def setup_context(lbm, cfg, seqs, args, rank, local_rank, churn):
         pages = int(pages * 1.25)   # room for admissions that are longer than the completions they replace
     ctx = lbm.Context(cfg, sessions=len(seqs), max_context=max_context, page_tokens=page_tokens,
                       pool_pages=pages, max_seqs=len(seqs), max_rows=max(rows, 32), gemm_impl=args.gemm_impl, use_graph=1,
-                      device=local_rank, debug_rows=0, pdl=args.pdl, chain=args.chain, gating_stream=args.gating_stream)
+                      device=local_rank, debug_rows=0, pdl=args.pdl, chain=args.chain, gating_stream=args.gating_stream, fuse_swiglu=args.fuse_swiglu)
     ctx.synth_weights(0)
     pool = PagePool(lbm, pages, page_tokens, len(seqs), max_context // page_tokens)  # ids 1 .. pages - 1 (page 0 is reserved)
     for q in seqs:
@@ -823,6 +823,7 @@ def main():
     ap.add_argument("--no-churn64", action="store_true", help="leave out the 64-sequence sharded batch reported beside the headline")
     ap.add_argument("--quick", action="store_true", help="device-timed steps only (no end-to-end, per-family or CPU legs): "
                     "the short run the profiler's launch list is taken from")
+    ap.add_argument("--fuse-swiglu", type=int, default=0, help="1: silu(gate)*up and its FP8 copy written by the gate|up GEMM itself (measured slower; default 0: a kernel of its own)")
     ap.add_argument("--chunk-scope", default="ffn+gdn", choices=["ffn+gdn", "ffn"], help="mixed: what the prefill chunk runs through")
     ap.add_argument("--systems", type=int, default=0, help="served64: prompts begin with one of this many shared system messages")
     ap.add_argument("--prefix-kv-mb", type=int, default=0, help="served64 with --systems: the prefix KV store's budget for saved states (0: store off)")

@@ -73,7 +73,12 @@ typedef struct ling_b200_options {
   int attn_positions; /* 0, or the cached positions summed over a step's sequences that the attention's partial buffers are
                         sized for, when larger than the pool's positions: sessions that share pages (the prefix KV store)
                         can hold more context between them than the pool has pages for                              */
-  int reserved[2];
+  int fuse_swiglu;   /* 1 = silu(gate) * up and its FP8 copy are written by the gate|up GEMM itself: the CTA that completes a pair
+                        of gate and up tiles last (a ticket per pair) adds the K splits' planes and applies them; one launch
+                        less per layer, the same bits.  Measured slower than the kernel of its own behind the GEMM (7.96
+                        against 7.49 ms per 27B step: the last CTA's round trips to L2 sit on the critical path, the
+                        separate kernel's launch is hidden by dependent launch): 0 = off (default)                  */
+  int reserved[1];
 } ling_b200_options;
 
 typedef struct ling_b200_ctx ling_b200_ctx;

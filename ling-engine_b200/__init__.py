@@ -47,7 +47,7 @@ class Options(C.Structure):
     _fields_ = [("sessions", C.c_int), ("max_context", C.c_int), ("page_tokens", C.c_int), ("pool_pages", C.c_int),
                 ("max_seqs", C.c_int), ("max_rows", C.c_int), ("gemm_impl", C.c_int), ("use_graph", C.c_int),
                 ("device", C.c_int), ("debug_rows", C.c_int), ("pdl", C.c_int), ("chain", C.c_int), ("gating_stream", C.c_int), ("attn_positions", C.c_int),
-                ("reserved", C.c_int * 2)]
+                ("fuse_swiglu", C.c_int), ("reserved", C.c_int * 1)]
 
 
 class SeqStep(C.Structure):
@@ -166,7 +166,7 @@ class Context:
     """One engine context on one GPU (ling_b200_create .. ling_b200_destroy)."""
 
     def __init__(self, cfg, sessions=4, max_context=2048, page_tokens=16, pool_pages=512, max_seqs=4, max_rows=128,
-                 gemm_impl=None, use_graph=1, device=0, debug_rows=0, pdl=0, chain=0, gating_stream=0, attn_positions=0):
+                 gemm_impl=None, use_graph=1, device=0, debug_rows=0, pdl=0, chain=0, gating_stream=0, attn_positions=0, fuse_swiglu=0):
         if gemm_impl is None:  # a debugging knob: LING_B200_GEMM_IMPL=1 runs the CUDA-core cross-check GEMM instead
             gemm_impl = int(os.environ.get("LING_B200_GEMM_IMPL", "0"))
         self.cfg = cfg
@@ -174,6 +174,7 @@ class Context:
                            device, debug_rows, pdl, chain)
         self.opt.gating_stream = gating_stream
         self.opt.attn_positions = attn_positions
+        self.opt.fuse_swiglu = fuse_swiglu
         self.h = C.c_void_p()
         rc = lib().ling_b200_create(C.byref(cfg), C.byref(self.opt), C.byref(self.h))
         if rc != OK:

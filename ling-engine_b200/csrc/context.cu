@@ -92,6 +92,7 @@ struct ling_b200_ctx {
   // sessions
   KvPoolDev kv;
   float *gdn_state = nullptr, *conv_state = nullptr;  // [slot][gdn layer][...]
+  unsigned* swiglu_tickets = nullptr;  // [token tiles][gate tiles], zero between launches (GemmCall::swiglu)
   uint8_t* state_arena = nullptr;  // saved states of the prefix KV store (ling_b200_state_arena_reserve)
   size_t state_arena_bytes = 0;
   size_t state_layer = 0, conv_layer = 0;             // floats per layer
@@ -182,7 +183,8 @@ Planes planes_of(const ling_b200_ctx* c, int which, const Fp8Matrix& w, bool hea
   return p;
 }
 
-int run_gemm(ling_b200_ctx* c, const Fp8Matrix& w, const Fp8Acts& x, int which, int rows, const HeadEpilogue* head = nullptr) {
+int run_gemm(ling_b200_ctx* c, const Fp8Matrix& w, const Fp8Acts& x, int which, int rows, const HeadEpilogue* head = nullptr,
+             const SwigluEpilogue* swiglu = nullptr) {
   Timed t(c, head ? kFamHead : kFamGemm);
   GemmCall g;
   g.W = &w, g.X = &x, g.M = rows;
@@ -190,6 +192,7 @@ int run_gemm(ling_b200_ctx* c, const Fp8Matrix& w, const Fp8Acts& x, int which, 
   g.ld = head ? w.N : w.N_pad;
   g.split_stride = size_t(c->d.rows_alloc) * w.N_pad;
   g.head = head;
+  g.swiglu = swiglu;
   g.impl = c->opt.gemm_impl;
   g.err_flag = c->sb.err;
   if (c->timeline && c->timeline_next < ling_b200_ctx::kTimelineLaunches) g.timeline = c->timeline + 4 * size_t(c->timeline_next++);
@@ -405,8 +408,14 @@ int enqueue_step_body(ling_b200_ctx* c, int rows, int flags) {
         Timed t(c, kFamElem);
         LB_TRY(norm_quant_launch(c->h, carry, nullptr, nullptr, L.post_norm, nullptr, c->qout(c->xq_h), n_rows, rows, d.H, d.eps, s));
       }
-      LB_TRY(run_gemm(c, L.gu, c->xq_h, 0, rows));
-      {
+      if (c->opt.fuse_swiglu > 0 && c->opt.gemm_impl == 0) {
+        // the activation and its FP8 copy inside the GEMM: the CTA that completes a (gate tile, up tile) pair writes them
+        // (measured slower than the kernel of its own on the 27B single-stream step: 7.96 against 7.49 ms; off by default)
+        const QuantOut q = c->qout(c->xq_i);
+        const SwigluEpilogue sw{c->swiglu_tickets, d.I, round_up(d.I, kTileN), q.codes, q.scales, q.K_pad, q.rows_alloc};
+        LB_TRY(run_gemm(c, L.gu, c->xq_h, 0, rows, nullptr, &sw));
+      } else {
+        LB_TRY(run_gemm(c, L.gu, c->xq_h, 0, rows));
         Timed t(c, kFamElem);
         LB_TRY(silu_mul_quant_launch(planes_of(c, 0, L.gu), d.I, round_up(d.I, kTileN), c->qout(c->xq_i), n_rows, rows, s));
       }
@@ -726,6 +735,7 @@ int ling_b200_create(const ling_b200_model_config* cfg, const ling_b200_options*
   LB_TRY(c->alloc(&c->kv.tables, size_t(opt->sessions) * d.max_pages));
   c->state_layer = size_t(d.HV) * d.Dk * d.Dv;
   c->conv_layer = size_t(d.C) * 3;
+  LB_TRY(c->alloc(&c->swiglu_tickets, size_t(d.rows_alloc / 32 + 1) * (round_up(d.I, kTileN) / kTileN)));
   LB_TRY(c->alloc(&c->gdn_state, size_t(opt->sessions) * d.n_gdn * c->state_layer));
   LB_TRY(c->alloc(&c->conv_state, size_t(opt->sessions) * d.n_gdn * c->conv_layer));
 

@@ -60,6 +60,15 @@ struct HeadArgs {
   int rows_alloc;
   int store_logits;
 };
+// The gate|up projection's activation fused into the GEMM (GemmCall::swiglu): see the kernel's epilogue.
+constexpr int kFusePlanes = 8;  // most K splits (choose_splits): the planes are added in plane order, absent ones as zero, as every consumer does
+struct SwigluArgs {
+  unsigned* tickets;   // nullptr: off
+  int I, up_col0;      // gate columns [0, I), up columns [up_col0, up_col0 + I); up_col0 a multiple of the weight tile
+  uint8_t* codes;      // E4M3 [rows_alloc][K_pad]
+  float* scales;       // [K_pad / 128][rows_alloc]
+  int K_pad, rows_alloc;
+};
 constexpr size_t gemm_smem_bytes(int nt) {
   return size_t(stages_for(nt)) * (kABytes + nt * kBlockK) + 1024 /* alignment slack */ + 512 /* barriers */ +
          size_t(4) * nt * 8 /* head argmax scratch */ + size_t(4) * scale_ring(nt) * nt * 4 /* activation-scale rings */;
@@ -70,7 +79,7 @@ __global__ void __launch_bounds__(gemm_threads(NT), ctas_per_sm(NT))
     gemm_fp8_tcgen05_kernel(const __grid_constant__ CUtensorMap mapW, const __grid_constant__ CUtensorMap mapX,
                             const float* __restrict__ ws, const float* __restrict__ xs, float* __restrict__ out, int ld,
                             size_t split_stride, int M, int N, int N_pad, int KB, int splits, int xrows, HeadArgs head,
-                            int* err_flag, int pdl, int l2_slabs, unsigned long long* timeline) {
+                            int* err_flag, int pdl, int l2_slabs, unsigned long long* timeline, SwigluArgs sw) {
   pdl_trigger();  // the next kernel may be scheduled as soon as every CTA of this one has started
   // Optional timeline (debugging aid, like the reference's per-block %globaltimer stamps, src/core/engine.hpp:637-642):
   // [0] first CTA's start, [1] first producer past the dependency wait, [2] last producer past it, [3] last CTA's end.
@@ -305,6 +314,75 @@ __global__ void __launch_bounds__(gemm_threads(NT), ctas_per_sm(NT))
         for (int j = 0; j < NTH; ++j)
           if (m0 + j < M) o[size_t(m0 + j) * ld] = acc[j];
       }
+      if (sw.tickets != nullptr) {
+        // silu(gate) * up and its FP8 copy by the CTA that finishes a (gate tile, up tile) pair last: the 2 x splits CTAs
+        // of the pair take a ticket once their partial sums are stored; the last one adds the planes in plane order, applies
+        // the activation and quantizes the block of 128 features -- the arithmetic of silu_mul_quant_kernel, bit for bit,
+        // without that kernel's launch and its round trip.  Every epilogue warp takes part whatever happened before, so the
+        // named barriers are complete; the ticket word returns to zero for the next launch.
+        const int T = sw.up_col0 / kTileN, pair = tile_n % T;
+        unsigned* ticket = sw.tickets + size_t(tile_m) * T + pair;
+        __threadfence();
+        asm volatile("bar.sync 1, %0;" ::"n"(EW * 32) : "memory");
+        if (warp == 2 && lane == 0) {
+          const unsigned t = atomicAdd(ticket, 1u);
+          const bool last = t == unsigned(2 * splits - 1);
+          if (last) *ticket = 0u;
+          red_idx[0] = last ? 1 : 0;
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(EW * 32) : "memory");
+        if (red_idx[0] != 0) {
+          __threadfence();
+          // A warp takes a token row at a time, lane l its features 4 l .. 4 l + 3 of the pair's 128: the planes' loads of a row
+          // are issued together (one round trip to L2, where the other CTAs' partial sums are), and two rows are in flight where the registers allow.
+          const int f = pair * kTileN + lane * 4, ew = warp - 2;
+          const int m_end = min(M, (tile_m + 1) * NT);
+          auto load_row = [&](int m, float4 (&tg)[kFusePlanes], float4 (&tu)[kFusePlanes]) {
+            const float* gp = out + size_t(m) * ld + f;
+#pragma unroll
+            for (int p = 0; p < kFusePlanes; ++p) {
+              const bool on = p < splits && m < m_end && f < sw.I;
+              tg[p] = on ? __ldcg(reinterpret_cast<const float4*>(gp + size_t(p) * split_stride)) : make_float4(0.f, 0.f, 0.f, 0.f);
+              tu[p] = on ? __ldcg(reinterpret_cast<const float4*>(gp + size_t(p) * split_stride + sw.up_col0)) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+          };
+          auto finish_row = [&](int m, const float4 (&tg)[kFusePlanes], const float4 (&tu)[kFusePlanes]) {
+            if (m >= m_end) return;  // warp-uniform
+            float4 g4 = make_float4(0.f, 0.f, 0.f, 0.f), u4 = g4;
+#pragma unroll
+            for (int p = 0; p < kFusePlanes; ++p) {
+              g4.x += tg[p].x, g4.y += tg[p].y, g4.z += tg[p].z, g4.w += tg[p].w;
+              u4.x += tu[p].x, u4.y += tu[p].y, u4.z += tu[p].z, u4.w += tu[p].w;
+            }
+            float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (f < sw.I) x = make_float4(silu(g4.x) * u4.x, silu(g4.y) * u4.y, silu(g4.z) * u4.z, silu(g4.w) * u4.w);
+            const float amax = warp_max(fmaxf(fmaxf(fabsf(x.x), fabsf(x.y)), fmaxf(fabsf(x.z), fabsf(x.w))));
+            const float sc = amax > 0.f ? amax / 448.f : 1.f;
+            if (f < sw.K_pad) {
+              uchar4 o;
+              o.x = to_e4m3(__fdiv_rn(x.x, sc)), o.y = to_e4m3(__fdiv_rn(x.y, sc));
+              o.z = to_e4m3(__fdiv_rn(x.z, sc)), o.w = to_e4m3(__fdiv_rn(x.w, sc));
+              *reinterpret_cast<uchar4*>(sw.codes + size_t(m) * sw.K_pad + f) = o;
+              if (lane == 0) sw.scales[size_t(pair) * sw.rows_alloc + m] = sc;
+            }
+          };
+          if constexpr (NT == 32) {  // the latency-bound few-row step: two rows in flight (the wider tiles have no registers for that)
+            for (int m = tile_m * NT + ew; m < m_end; m += 2 * EW) {
+              float4 ag[kFusePlanes], au[kFusePlanes], bg[kFusePlanes], bu[kFusePlanes];
+              load_row(m, ag, au);
+              load_row(m + EW, bg, bu);
+              finish_row(m, ag, au);
+              finish_row(m + EW, bg, bu);
+            }
+          } else {
+            for (int m = tile_m * NT + ew; m < m_end; m += EW) {
+              float4 ag[kFusePlanes], au[kFusePlanes];
+              load_row(m, ag, au);
+              finish_row(m, ag, au);
+            }
+          }
+        }
+      }
       if (head.tile_val != nullptr) {
         // Per token row: the best (value, id) among this tile's 128 vocabulary rows; larger value first, equal
         // values to the lower id, NaN skipped.  All epilogue warps take part whatever happened before, so the
@@ -535,6 +613,14 @@ int launch_tc(const GemmCall& c, cudaStream_t stream) {
   HeadArgs h{nullptr, nullptr, 0, 0};
   if (c.head) h = HeadArgs{c.head->tile_val, c.head->tile_idx, c.head->rows_alloc, c.head->store_logits ? 1 : 0};
   const int splits = c.head ? 1 : W.splits;
+  SwigluArgs sw{nullptr, 0, 0, nullptr, nullptr, 0, 0};
+  if (c.swiglu) {
+    if (c.head || c.swiglu->up_col0 % kTileN != 0 || c.swiglu->up_col0 < c.swiglu->I || !c.swiglu->tickets) {
+      set_error("gemm: the fused activation needs the up columns on a tile boundary behind the gate columns");
+      return LING_B200_ERR_ARG;
+    }
+    sw = SwigluArgs{c.swiglu->tickets, c.swiglu->I, c.swiglu->up_col0, c.swiglu->codes, c.swiglu->scales, c.swiglu->K_pad, c.swiglu->rows_alloc};
+  }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(ceil_div(c.M, NT), splits, W.N_pad / kTileN);
   cfg.blockDim = dim3(gemm_threads(NT));
@@ -555,7 +641,7 @@ int launch_tc(const GemmCall& c, cudaStream_t stream) {
   LB_CUDA(cudaLaunchKernelEx(&cfg, gemm_fp8_tcgen05_kernel<NT>, W.map, X.map[NT / 32 - 1], (const float*)W.scales,
                              (const float*)X.scales, c.out, c.ld, c.split_stride, c.M, W.N, W.N_pad, W.KB, splits,
                              X.rows_alloc, h, c.err_flag, pdl ? 1 + pre_stages : 0, pdl && cfg.gridDim.x == 1 ? l2_slabs : 0,
-                             c.timeline));
+                             c.timeline, sw));
   LB_LAUNCH("gemm_fp8_tcgen05_kernel");
   return LING_B200_OK;
 }

@@ -41,6 +41,17 @@ struct HeadEpilogue {
   bool store_logits = false;
 };
 
+// The gate|up projection with its activation fused in: the CTA that finishes a (gate tile, up tile) pair last adds the K
+// splits' planes, applies silu(gate) * up and writes the FP8 copy the down projection reads (what silu_mul_quant_kernel
+// does as a launch of its own, bit for bit).  tickets: one zeroed word per (token tile, gate tile); they return to zero.
+struct SwigluEpilogue {
+  unsigned* tickets = nullptr;
+  int I = 0, up_col0 = 0;
+  uint8_t* codes = nullptr;
+  float* scales = nullptr;
+  int K_pad = 0, rows_alloc = 0;
+};
+
 struct GemmCall {
   const Fp8Matrix* W = nullptr;
   const Fp8Acts* X = nullptr;
@@ -49,6 +60,7 @@ struct GemmCall {
   int ld = 0;
   size_t split_stride = 0;  // floats between split planes
   const HeadEpilogue* head = nullptr;
+  const SwigluEpilogue* swiglu = nullptr;  // tcgen05 path only
   int impl = 0;             // 0 tcgen05, 1 CUDA cores
   int force_tile = 0;       // 0: token_tile(M); else the token tile to use (32, 64, 96 or 128): results do not depend on it
   int* err_flag = nullptr;

@@ -284,7 +284,9 @@ def test_variants_agree(gpu, toy, lb, lo):
     helpers.setup_sessions([ctx], cfg, seqs, 16, 0)
     ctx.verify_step(seqs, flags=lb.STEP_KEEP_LOGITS)
     base = ctx.read_logits()
-    for kw, exact in ((dict(gemm_impl=1), False), (dict(pdl=1), True), (dict(pdl=1, use_graph=0), True)):
+    # ... the gate|up activation written by the GEMM's last CTA of a tile pair instead of a kernel of its own: bit-exact
+    for kw, exact in ((dict(gemm_impl=1), False), (dict(pdl=1), True), (dict(pdl=1, use_graph=0), True), (dict(fuse_swiglu=1), True),
+                      (dict(fuse_swiglu=1, pdl=1), True)):
         other = lb.Context(cfg, debug_rows=128, **kw)
         helpers.load_weights_from_host(lb, lo, cfg, 0, [other])
         helpers.setup_sessions([other], cfg, seqs, 16, 0)
