@@ -574,6 +574,14 @@ int ling_b200_format_step(double t, long pass, const char* kind, size_t turn, co
                           const int* cand /* [n_cand][3]: session, state, recent */, const long* cand_request,
                           const long* cand_last, int n_cand, double ms, int side, char* buf, int buf_len);
 
+/* Attention over the M rows of a prefill chunk of one session (positions pos0 .. pos0 + M - 1) in one attention layer, through
+ * the step's own prepare / attention / combine kernels in slices of 32 query rows, as the reference's prefill runs its rows
+ * kernel "in slices of queries" (src/core/kernels.cuh:486-490; Engine::forward's full-attention branch, engine.cpp:1395-1460):
+ * qkv [M][Hq * 2 D + 2 Hkv D] are the q|gate, k, v projection's rows; the rows' K and V go into the session's cache (its page
+ * table must map [0, pos0 + M)), out [M][Hq * D] is the gated attention output in front of the o projection.  Correct, not
+ * fast: every slice reads the whole context again. */
+int ling_b200_prefill_attention_host(ling_b200_ctx* ctx, int slot, int attn_layer, int pos0, int M, const float* qkv, float* out);
+
 /* ------------------------------------------------------------------------------------------------ the prefill path's DeltaNet core */
 /* gdn_conv_prefill + gdn_recurrent_prefill (src/core/kernels.cuh:445-456; src/core/prefill_gdn.cu:34-142) over the M rows
  * of one sequence, host buffers: pre [M][C] the raw in-projection rows (q | k | v channels, C = 2 Hk Dk + HV Dv), convw_bf16

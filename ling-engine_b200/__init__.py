@@ -309,6 +309,14 @@ class Context:
         self.last_seqs = len(seqs)
         return q
 
+    def prefill_attention(self, slot, attn_layer, pos0, qkv):
+        """Attention over a prefill chunk's rows at positions pos0.. of one session, in 32-row slices through the step's kernels:
+        qkv [M][heads*2*D + 2*kv_heads*D] -> gated output [M][heads][D]; the rows' K and V go to the cache."""
+        qkv = np.ascontiguousarray(qkv, np.float32)
+        out = np.zeros((qkv.shape[0], self.cfg.heads, self.cfg.head_dim), np.float32)
+        check(lib().ling_b200_prefill_attention_host(self.h, slot, attn_layer, pos0, qkv.shape[0], _fp(qkv), _fp(out)), "prefill_attention_host")
+        return out
+
     def read_tree_desc(self, seq):
         t = TreeDesc()
         check(lib().ling_b200_read_tree_desc(self.h, seq, C.byref(t)), "read_tree_desc")

@@ -1126,7 +1126,7 @@ int ling_b200_attn_slot_need(const ling_b200_ctx* c, int pos) {
   return ((std::max(pos, 0) + kAttnChunk - 1) / kAttnChunk + 1) * c->d.Hkv;
 }
 int ling_b200_attn_slot_capacity(const ling_b200_ctx* c) { return c ? c->chunk_slots : 0; }
-int ling_b200_step_stage(ling_b200_ctx* c, const ling_b200_seq_step* seqs, int n_seqs, int flags) {
+static int stage_impl(ling_b200_ctx* c, const ling_b200_seq_step* seqs, int n_seqs, int flags, bool same_slot_ok) {
   LB_TRY(check_ctx(c));
   const ModelDims& d = c->d;
   if (!seqs || n_seqs < 1 || n_seqs > d.max_seqs) {
@@ -1145,7 +1145,7 @@ int ling_b200_step_stage(ling_b200_ctx* c, const ling_b200_seq_step* seqs, int n
       set_error("step: bad sequence entry");
       return LING_B200_ERR_ARG;
     }
-    for (int t = 0; t < s; ++t)
+    for (int t = 0; t < s && !same_slot_ok; ++t)
       if (seqs[t].slot == q.slot) {
         set_error("step: a session twice");  // speculate_batch's rule (src/core/speculate.cpp:1107-1108)
         return LING_B200_ERR_ARG;
@@ -1182,6 +1182,10 @@ int ling_b200_step_stage(ling_b200_ctx* c, const ling_b200_seq_step* seqs, int n
   for (int i = 0; i < n_seqs; ++i) c->staged_slots += long(ling_b200_attn_slot_need(c, seqs[i].pos));
   LB_CUDA(cudaMemcpyAsync(c->stage_dev, c->stage_host, c->stage_bytes, cudaMemcpyHostToDevice, c->stream));
   return LING_B200_OK;
+}
+
+int ling_b200_step_stage(ling_b200_ctx* c, const ling_b200_seq_step* seqs, int n_seqs, int flags) {
+  return stage_impl(c, seqs, n_seqs, flags, false);
 }
 
 // The flash-decoding partials have a slot per (kv head, chunk of a sequence's context) (chunk_slots): a staged step whose
@@ -1423,6 +1427,70 @@ int ling_b200_attn_prepare_host(ling_b200_ctx* c, const ling_b200_seq_step* seqs
   LB_CUDA(cudaMemcpyAsync(hq.data(), c->qh, n * sizeof(__half), cudaMemcpyDeviceToHost, c->stream));
   LB_TRY(read_err(c));
   for (size_t i = 0; i < n; ++i) q_out[i] = __half2float(hq[i]);
+  return LING_B200_OK;
+}
+
+// Attention over the rows of a prefill chunk through the step's own kernels, 32 query rows at a time: the reference's prefill
+// path runs its rows kernel "in slices of queries" the same way (src/core/kernels.cuh:486-490).  The chunk's M rows of one
+// session, at positions pos0 .. pos0 + M - 1, are cut into linear chains of 32 rows; as many chains as the step's capacity and
+// the attention's partial buffers hold go through prepare (head norms, rotation, K and V into the cache), attention and
+// combine (with the output gate) at once, each chain seeing the cache up to its own first row -- the rows of the chains
+// before it included, which the same prepare launch has just written -- and its own rows under the causal (chain) mask.
+int ling_b200_prefill_attention_host(ling_b200_ctx* c, int slot, int attn_layer, int pos0, int M, const float* qkv, float* out) {
+  LB_TRY(check_ctx(c));
+  const ModelDims& d = c->d;
+  if (slot < 0 || slot >= c->opt.sessions || attn_layer < 0 || attn_layer >= d.n_attn || pos0 < 0 || M < 1 || !qkv || !out ||
+      pos0 + M > d.max_pages * d.page_tokens) {
+    set_error("prefill_attention_host: bad argument");
+    return LING_B200_ERR_ARG;
+  }
+  int layer = -1;
+  for (int l = 0; l < c->cfg.layers; ++l)
+    if (c->attn_index[l] == attn_layer) layer = l;
+  const LayerW& L = c->layers[layer];
+  const int W = d.Hq * 2 * d.D + 2 * d.Hkv * d.D, O = d.Hq * d.D;
+  const bool tc = c->opt.gemm_impl == 0 && attention_tc_supported(d);
+  std::vector<int> zeros(kTreeRows, 0), chain(kTreeRows);
+  for (int i = 0; i < kTreeRows; ++i) chain[i] = i - 1;
+  PdlScope pdl(c->opt.pdl != 0);
+  for (int done = 0; done < M;) {
+    // the chains of this pass: within the step's sequences and rows, the staging buffers and the partial buffers' slots
+    std::vector<ling_b200_seq_step> seqs;
+    long slots = 0;
+    int rows = 0;
+    while (done + rows < M && int(seqs.size()) < d.max_seqs) {
+      const int n = std::min(kTreeRows, M - done - rows), pos = pos0 + done + rows;
+      const long need = ling_b200_attn_slot_need(c, pos);
+      if (rows + n > c->opt.max_rows || size_t(rows + n) * W > c->plane_floats || size_t(rows + n) * O > c->plane_floats ||
+          (slots + need > c->chunk_slots && !seqs.empty()))
+        break;
+      seqs.push_back(ling_b200_seq_step{slot, pos, 0, n, n - 1, zeros.data(), chain.data(), nullptr});
+      slots += need, rows += n;
+    }
+    if (seqs.empty()) {
+      set_error("prefill_attention_host: the context's step capacity holds no chain of the chunk");
+      return LING_B200_ERR_ARG;
+    }
+    LB_TRY(stage_impl(c, seqs.data(), int(seqs.size()), 0, true));
+    LB_TRY(check_attn_slots(c));
+    const int cls = row_class(rows);
+    c->last_rows = rows, c->last_seqs = int(seqs.size()), c->last_flags = 0;
+    LB_TRY(pack_launch(c->sb, d, c->stream));
+    LB_CUDA(cudaMemcpyAsync(c->planes[0], qkv + size_t(done) * W, size_t(rows) * W * 4, cudaMemcpyHostToDevice, c->stream));
+    Planes p;
+    p.p = c->planes[0], p.n = 1, p.stride = 0, p.ld = W;
+    LB_TRY(attn_prepare_launch(p, c->sb, d, attn_layer, L.q_norm, L.k_norm, c->qh, c->kv, cls, c->stream));
+    if (tc)
+      LB_TRY(attention_tc_launch(c->qh, c->sb, d, attn_layer, c->kv, c->part_o, c->part_ml, c->chunk_slots, c->sm_count, PrefetchPlan(), nullptr, c->stream));
+    else
+      LB_TRY(attention_launch(c->qh, c->sb, d, attn_layer, c->kv, c->part_o, c->part_ml, c->chunk_slots, c->sm_count * 2, c->stream));
+    LB_TRY(attn_combine_launch(c->part_o, c->part_ml, p, c->sb, d, c->qout(c->xq_a), c->planes[1], cls,
+                               c->opt.max_context / kAttnChunkShort + 2, tc ? kAttnTcRows : kAttnRowTile,
+                               tc ? c->sm_count : c->sm_count * 2, c->chunk_slots, c->stream));
+    LB_CUDA(cudaMemcpyAsync(out + size_t(done) * O, c->planes[1], size_t(rows) * O * 4, cudaMemcpyDeviceToHost, c->stream));
+    LB_TRY(read_err(c));
+    done += rows;
+  }
   return LING_B200_OK;
 }
 

@@ -1533,13 +1533,12 @@ __global__ void __launch_bounds__(256)
     }
     const float inv = 1.f / (den[hb] * kPScale);
     x = make_float4(x.x * inv, x.y * inv, x.z * inv, x.w * inv);
-    if (raw) {
-      *reinterpret_cast<float4*>(raw + size_t(m) * q.K + c) = x;
-    } else {
+    if (qkv.p) {  // the output gate, where the q|gate projection is given (a parity entry may ask for the ungated rows)
       const int hq = c / D, dd = c % D;
       const float4 gate = plane_sum4(qkv, m, hq * 2 * D + D + dd);
       x = make_float4(x.x * sigmoidf(gate.x), x.y * sigmoidf(gate.y), x.z * sigmoidf(gate.z), x.w * sigmoidf(gate.w));
     }
+    if (raw) *reinterpret_cast<float4*>(raw + size_t(m) * q.K + c) = x;
   }
   quant_store4(x, c, m, q);
 }

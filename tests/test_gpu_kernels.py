@@ -425,3 +425,45 @@ def test_tree_attention_at_the_reference_matrix_of_contexts(gpu, lb, lo, page_to
     assert err.max() <= ATTN_TOL, worst
     lo.lo().lo_set_threads(1)
     ctx.close(), m.close()
+
+
+@pytest.mark.parametrize("shape,pos0,M", [("toy", 0, 100), ("toy", 37, 200), ("27b", 0, 70), ("27b", 530, 96)])
+def test_prefill_attention_in_slices_matches_oracle(gpu, lb, lo, shape, pos0, M):
+    # A prefill chunk's rows through the step's prepare / attention / combine kernels in slices of 32 query rows (several
+    # slices per launch), against the oracle taking the slices one at a time through its own prepare and attention: every row
+    # sees the cache up to itself, the rows of earlier slices included.  The output gate is applied in numpy on the oracle's side.
+    if shape == "toy":
+        cfg = lb.make_config(256, 704, 1, 4096, 4, 1, 64, 16, 2, 4, 64, 64, [1])
+        page_tokens = 16
+    else:
+        cfg = lb.make_config(5120, 128, 1, 4096, 24, 4, 256, 64, 16, 48, 128, 128, [1])
+        page_tokens = 64
+    pool = (pos0 + M) // page_tokens + 3
+    ctx = lb.Context(cfg, sessions=1, max_context=1024, page_tokens=page_tokens, pool_pages=pool, max_seqs=4, max_rows=128)
+    opt = lb.Options(1, 1024, page_tokens, pool, 4, 128, 0, 0, 0, 0, 0)
+    m = lo.Model(cfg, opt, lb)
+    ctx.synth_weights(3), m.synth_weights(3)
+    helpers.map_pages([ctx, m], 0, pos0 + M, page_tokens, 1)
+    if pos0:
+        ctx.synth_kv(0, pos0, 7), m.synth_kv(0, pos0, 7)
+    rng = np.random.default_rng(pos0 + M)
+    D, Hq, Hkv = cfg.head_dim, cfg.heads, cfg.kv_heads
+    W = Hq * 2 * D + 2 * Hkv * D
+    qkv = (rng.standard_normal((M, W)) * np.exp(0.5 * rng.standard_normal((M, 1)))).astype(np.float32)
+    out = ctx.prefill_attention(0, 0, pos0, qkv)
+    want = np.zeros_like(out)
+    for r0 in range(0, M, 32):
+        n = min(32, M - r0)
+        seq = [{"slot": 0, "pos": pos0 + r0, "tokens": np.zeros(n, np.int32), "parent": np.arange(-1, n - 1, dtype=np.int32), "chain": n - 1}]
+        q_o, _ = m.attn_prepare(seq, 0, qkv[r0:r0 + n], make_steps=lb.make_steps)
+        o = m.attention(seq, 0, q_o, make_steps=lb.make_steps)
+        gate = qkv[r0:r0 + n, :Hq * 2 * D].reshape(n, Hq, 2 * D)[:, :, D:]
+        want[r0:r0 + n] = o / (1.0 + np.exp(-gate.astype(np.float64)))
+    flat_o, flat_g = want.reshape(M, -1), out.reshape(M, -1)
+    rms = np.sqrt((flat_o.astype(np.float64) ** 2).mean(axis=1, keepdims=True))
+    assert np.isfinite(out).all()
+    assert (np.abs(flat_g - flat_o) <= 2 * ATTN_TOL * rms).all(), float((np.abs(flat_g - flat_o) / rms).max())
+    # the cache holds the chunk's keys and values as a verify step's prepare would have left them
+    for a, b in zip(ctx.kv_read(0, 0, 0, pos0 + M), m.kv_read(0, 0, 0, pos0 + M)):
+        assert np.abs(a - b).max() <= 0.13 * np.abs(b).max()  # FP8 codes may differ by a step where the norm's last bit differs
+    ctx.close(), m.close()
