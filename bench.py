@@ -353,19 +353,28 @@ def run_reference(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
-def setup_context(lbm, cfg, seqs, args, rank, local_rank, churn):
-    """A context sized for `seqs` with synthetic weights, page tables from the page pool, synthetic KV and DeltaNet state."""
+def setup_context(lbm, cfg, seqs, args, rank, local_rank, churn, chunk_rows=0):
+    """A context sized for `seqs` with synthetic weights, page tables from the page pool, synthetic KV and DeltaNet state.
+    chunk_rows > 0: one more session (slot len(seqs)) with pages for a prefill chunk of that many positions, and a step
+    capacity of 64 chains / 2048 rows for the chunk's attention layers."""
     rows = sum(len(q["tokens"]) for q in seqs)
     page_tokens = 16
     pages = sum((q["pos"] + 64 + page_tokens - 1) // page_tokens for q in seqs) + 1
     max_context = 131072 if churn else -(-(max(q["pos"] for q in seqs) + 64) // page_tokens) * page_tokens
     if churn:
         pages = int(pages * 1.25)   # room for admissions that are longer than the completions they replace
-    ctx = lbm.Context(cfg, sessions=len(seqs), max_context=max_context, page_tokens=page_tokens,
-                      pool_pages=pages, max_seqs=len(seqs), max_rows=max(rows, 32), gemm_impl=args.gemm_impl, use_graph=1,
+    n_sessions, max_seqs, max_rows = len(seqs), len(seqs), max(rows, 32)
+    if chunk_rows:
+        pages += chunk_rows // page_tokens + 1
+        n_sessions, max_seqs, max_rows, max_context = n_sessions + 1, max(max_seqs, 64), max(max_rows, 2048), max(max_context, chunk_rows + 64)
+    ctx = lbm.Context(cfg, sessions=n_sessions, max_context=max_context, page_tokens=page_tokens,
+                      pool_pages=pages, max_seqs=max_seqs, max_rows=max_rows, gemm_impl=args.gemm_impl, use_graph=1,
                       device=local_rank, debug_rows=0, pdl=args.pdl, chain=args.chain, gating_stream=args.gating_stream, fuse_swiglu=args.fuse_swiglu)
     ctx.synth_weights(0)
-    pool = PagePool(lbm, pages, page_tokens, len(seqs), max_context // page_tokens)  # ids 1 .. pages - 1 (page 0 is reserved)
+    pool = PagePool(lbm, pages, page_tokens, n_sessions, max_context // page_tokens)  # ids 1 .. pages - 1 (page 0 is reserved)
+    if chunk_rows:
+        table = pool.ensure(len(seqs), chunk_rows)
+        ctx.kv_table_set(len(seqs), np.arange(len(table), dtype=np.int32), table)
     for q in seqs:
         table = pool.ensure(q["slot"], q["pos"] + 64)
         ctx.kv_table_set(q["slot"], np.arange(len(table), dtype=np.int32), table)
@@ -554,12 +563,15 @@ def run_mixed(args, rank, local_rank, world):
     seqs = workload("mixed", rank, cfg.vocab)
     rows = sum(len(q["tokens"]) for q in seqs)
     chunk = 4096
-    ctx, _, _ = setup_context(lbm, cfg, seqs, args, rank, local_rank, False)
+    whole = args.chunk_scope == "all"
+    ctx, _, _ = setup_context(lbm, cfg, seqs, args, rank, local_rank, False, chunk if whole else 0)
     ffn = lbm.Nvfp4Ffn(cfg.layers, cfg.hidden, cfg.intermediate, chunk, seed=rank, device=local_rank)
     with_mixers = args.chunk_scope != "ffn"
     n_mix = sum(1 for l in range(cfg.layers) if l % 4 != 3) if with_mixers else 0
     if with_mixers:
         ffn.add_mixers(cfg.lin_k_heads, cfg.lin_v_heads, 4, seed=rank)
+    if whole:
+        return run_mixed_whole(args, lbm, dist, cfg, ctx, ffn, seqs, rows, chunk, n_mix, rank, local_rank, world)
     h0 = np.random.default_rng(50 + rank).standard_normal((chunk, cfg.hidden)).astype(np.float32)
     ffn.set_residual(h0)
     flags, K, W = lbm.STEP_COMMIT, args.steps, max(args.warmup, 3)
@@ -644,6 +656,92 @@ def run_mixed(args, rank, local_rank, world):
                          "peak_kind": "measured in this run: tcgen05.mma kind::mxf4nvf4.block_scale on resident operands, 6 ms burst",
                          "peak_sustained": peak_sustained, "traffic": None,
                          "ms_per_launch": {"gate_up_swiglu": gu_ms, "down": dn_ms}},
+            "cpu_baseline": {"value": None, "unit": UNIT, "cores": 0, "kind": "port",
+                             "sample": "not timed for this workload (the single-stream line carries the CPU baseline)"},
+            "clocks": clk,
+        }
+        print(json.dumps(line), flush=True)
+    ffn.close()
+    ctx.close()
+    dist.close()
+
+
+def run_mixed_whole(args, lbm, dist, cfg, ctx, ffn, seqs, rows, chunk, n_mix, rank, local_rank, world):
+    """--chunk-scope all: the prefill chunk through EVERY layer -- the DeltaNet layers' NVFP4 mixers, the full-attention layers'
+    mixers (the verify context's own FP8 q|k|v and o projections, the step's prepare / attention / combine kernels over the
+    chunk's rows as 32-row chains of the chunk's session, 64 chains a launch) and all NVFP4 feed-forward blocks -- and then the 8
+    decoding sequences' verify step.  The chunk's attention layers work in the verify context's buffers, so the two halves
+    run one after the other: a step's time is the chunk's device time plus the verify step's (max over ranks)."""
+    n_attn = cfg.layers - n_mix
+    ffn.attach_context(ctx, len(seqs), 0, 4)
+    h0 = np.random.default_rng(50 + rank).standard_normal((chunk, cfg.hidden)).astype(np.float32)
+    ffn.set_residual(h0)
+    flags, K, W = lbm.STEP_COMMIT, args.steps, max(args.warmup, 3)
+    clocks = ClockSampler(local_rank)
+
+    def one_step():
+        ffn.launch(chunk, 1)
+        f_ms = ffn.wait()
+        ctx.stage(seqs, flags)
+        ctx.timer_begin()
+        ctx.launch()
+        return f_ms, ctx.timer_end()
+    for _ in range(W):
+        one_step()
+    res = ctx.fetch()
+    assert all(r.status == 0 and r.n_path == q["accept"] for r, q in zip(res, seqs)), "acceptance differs from the imposed paths"
+    clocks.start()
+    dist.barrier()
+    ctx.sync()
+    f_tot = v_tot = 0.0
+    for _ in range(K):
+        f_ms, v_ms = one_step()
+        f_tot, v_tot = f_tot + f_ms, v_tot + v_ms
+    ctx.sync()
+    dist.barrier()
+    step_ms = dist.max(f_tot + v_tot) / K
+    passes = -(-chunk // 2048)
+    launches = ctx.launch_count() + 3 * cfg.layers + 10 * n_mix + 8 * passes * n_attn
+    # end to end: the chunk's residual in and out of host memory, the verify step's descriptors in and results out, every step
+    ffn.forward(h0), ctx.verify_step(seqs, flags)
+    dist.barrier()
+    t0 = time.perf_counter()
+    for _ in range(K):
+        out = ffn.forward(h0)
+        ctx.verify_step(seqs, flags)
+    e2e_s = dist.max(time.perf_counter() - t0)
+    clk = clocks.stop()
+    assert np.isfinite(out).all()
+    gu_ms = lbm.nvfp4_gemm_bench(chunk, cfg.intermediate, cfg.hidden, fused=True, iters=10, device=local_rank)
+    dn_ms = lbm.nvfp4_gemm_bench(chunk, cfg.hidden, cfg.intermediate, fused=False, iters=10, device=local_rank)
+    peak_burst, _ = lbm.fp4_tensor_peak(20000, device=local_rank)
+    flops = 2.0 * chunk * cfg.intermediate * cfg.hidden
+    achieved = 3 * flops / ((gu_ms + dn_ms) * 1e-3) / 1e12
+    total_rows = dist.sum(rows + chunk)
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": total_rows / (step_ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": step_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "nvfp4 (e2m1 x ue4m3 per 16, fp32 accumulate) chunk, fp8_e4m3 attention projections and KV + fp8_e4m3 verify",
+            "data": "synthetic",
+            "config": {"workload": "mixed", "model": "27B-class hybrid, %d layers" % cfg.layers, "chunk_rows": chunk,
+                       "chunk_scope": "every layer: %d DeltaNet mixers (NVFP4), %d full-attention mixers (FP8 projections, attention over the "
+                                      "chunk's rows as 32-row chains through the step's kernels, %d launches of up to 64 chains a layer) and "
+                                      "%d NVFP4 feed-forward blocks; then the verify step (the two halves in turn)"
+                                      % (n_mix, n_attn, passes, cfg.layers),
+                       "decode_sequences": len(seqs), "decode_rows": rows, "contexts": [q["pos"] for q in seqs],
+                       "parallelism": "replicas, one chunk and one decode batch per GPU, no collective",
+                       "l2": "inputs larger than L2 (FP8 weights %.1f GB + NVFP4 chunk weights per step), no flush" % (ctx.weight_bytes() / 1e9)},
+            "halves_ms": {"chunk": f_tot / K, "verify": v_tot / K},
+            "e2e": {"value": total_rows * K / e2e_s, "unit": UNIT, "ms_per_step": e2e_s / K * 1e3,
+                    "h2d_bytes_per_step": int(h0.nbytes + ctx_stage_bytes(lbm, len(seqs))),
+                    "d2h_bytes_per_step": int(h0.nbytes + len(seqs) * __import__("ctypes").sizeof(lbm.SeqResult) + 4)},
+            "gpu_launches": launches * K, "launches_per_step": launches,
+            "roofline": {"bound": "tensor", "kernel": "gemm_nvfp4_tcgen05_kernel (gate|up fused %d x %d x %d, down %d x %d x %d)"
+                         % (chunk, 2 * cfg.intermediate, cfg.hidden, chunk, cfg.hidden, cfg.intermediate),
+                         "achieved": achieved, "peak": peak_burst, "unit": "TFLOP/s", "frac": achieved / peak_burst,
+                         "peak_kind": "measured in this run: tcgen05.mma kind::mxf4nvf4.block_scale on resident operands, 6 ms burst",
+                         "traffic": None, "ms_per_launch": {"gate_up_swiglu": gu_ms, "down": dn_ms}},
             "cpu_baseline": {"value": None, "unit": UNIT, "cores": 0, "kind": "port",
                              "sample": "not timed for this workload (the single-stream line carries the CPU baseline)"},
             "clocks": clk,
@@ -824,7 +922,7 @@ def main():
     ap.add_argument("--quick", action="store_true", help="device-timed steps only (no end-to-end, per-family or CPU legs): "
                     "the short run the profiler's launch list is taken from")
     ap.add_argument("--fuse-swiglu", type=int, default=0, help="1: silu(gate)*up and its FP8 copy written by the gate|up GEMM itself (measured slower; default 0: a kernel of its own)")
-    ap.add_argument("--chunk-scope", default="ffn+gdn", choices=["ffn+gdn", "ffn"], help="mixed: what the prefill chunk runs through")
+    ap.add_argument("--chunk-scope", default="ffn+gdn", choices=["ffn+gdn", "ffn", "all"], help="mixed: what the prefill chunk runs through")
     ap.add_argument("--systems", type=int, default=0, help="served64: prompts begin with one of this many shared system messages")
     ap.add_argument("--prefix-kv-mb", type=int, default=0, help="served64 with --systems: the prefix KV store's budget for saved states (0: store off)")
     ap.add_argument("--pool-pages", type=int, default=0, help="served64: KV page pool size (0: sized for the resident sessions)")

@@ -581,6 +581,17 @@ int ling_b200_format_step(double t, long pass, const char* kind, size_t turn, co
  * table must map [0, pos0 + M)), out [M][Hq * D] is the gated attention output in front of the o projection.  Correct, not
  * fast: every slice reads the whole context again. */
 int ling_b200_prefill_attention_host(ling_b200_ctx* ctx, int slot, int attn_layer, int pos0, int M, const float* qkv, float* out);
+/* A full-attention layer's whole mixer over a prefill chunk (Engine::forward's full-attention branch over many rows,
+ * src/core/engine.cpp:1424-1469): h [M][hidden] fp32 in DEVICE memory, the residual rows at positions pos0.. of session `slot`
+ * (pages mapped by the caller), += o(gate * attention(prepare(q|k|v(norm(h))))) with the layer's FP8 projections; K and V of the
+ * rows go to the session's pages.  The rows go through the step's kernels as 32-row chains, many chains a launch.  The call
+ * returns when the work is complete; a staged verify step is replaced (stage again).  _host: h in host memory, in and out. */
+int ling_b200_chunk_attention_layer(ling_b200_ctx* ctx, int slot, int layer, int pos0, int M, float* h_device);
+int ling_b200_chunk_attention_layer_host(ling_b200_ctx* ctx, int slot, int layer, int pos0, int M, float* h);
+/* Attaches a verify context to the chunk stack: every `full_every`-th layer (the full-attention layers) then runs
+ * ling_b200_chunk_attention_layer on that context ahead of its feed-forward block, the chunk being positions pos0.. of `slot`.
+ * No counterpart of its own in the reference: there one engine holds both paths. */
+int ling_b200_nvfp4_ffn_attach_context(ling_b200_nvfp4_ffn* ffn, ling_b200_ctx* ctx, int slot, int pos0, int full_every);
 
 /* ------------------------------------------------------------------------------------------------ the prefill path's DeltaNet core */
 /* gdn_conv_prefill + gdn_recurrent_prefill (src/core/kernels.cuh:445-456; src/core/prefill_gdn.cu:34-142) over the M rows

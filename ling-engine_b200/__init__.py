@@ -317,6 +317,13 @@ class Context:
         check(lib().ling_b200_prefill_attention_host(self.h, slot, attn_layer, pos0, qkv.shape[0], _fp(qkv), _fp(out)), "prefill_attention_host")
         return out
 
+    def chunk_attention_layer(self, slot, layer, pos0, h):
+        """A full-attention layer's whole mixer over a prefill chunk's residual rows h [M][hidden] at positions pos0.. of one
+        session (norm, FP8 q|k|v, prepare, attention in 32-row chains, gate, FP8 o, residual add): returns the rows after it."""
+        h = np.array(h, np.float32, order="C")
+        check(lib().ling_b200_chunk_attention_layer_host(self.h, slot, layer, pos0, h.shape[0], _fp(h)), "chunk_attention_layer_host")
+        return h
+
     def read_tree_desc(self, seq):
         t = TreeDesc()
         check(lib().ling_b200_read_tree_desc(self.h, seq, C.byref(t)), "read_tree_desc")
@@ -522,6 +529,12 @@ class Nvfp4Ffn:
     def add_mixers(self, k_heads, v_heads, full_every=4, seed=0):
         """The DeltaNet layers' prefill-path mixers in front of their feed-forward blocks (every layer but each full_every-th)."""
         check(lib().ling_b200_nvfp4_ffn_add_mixers(self.h, k_heads, v_heads, full_every, C.c_uint64(seed)), "nvfp4_ffn_add_mixers")
+
+    def attach_context(self, ctx, slot, pos0, full_every=4):
+        """The full-attention layers' mixers (each full_every-th layer) through a verify context's own projections and attention
+        kernels: the chunk is positions pos0.. of the context's session `slot`."""
+        check(lib().ling_b200_nvfp4_ffn_attach_context(self.h, ctx.h, slot, pos0, full_every), "nvfp4_ffn_attach_context")
+        self._ctx = ctx  # keeps the context alive as long as the stack
 
     def launch(self, rows, repeats=1):
         check(lib().ling_b200_nvfp4_ffn_launch(self.h, rows, repeats), "nvfp4_ffn_launch")

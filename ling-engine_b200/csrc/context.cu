@@ -1430,12 +1430,53 @@ int ling_b200_attn_prepare_host(ling_b200_ctx* c, const ling_b200_seq_step* seqs
   return LING_B200_OK;
 }
 
-// Attention over the rows of a prefill chunk through the step's own kernels, 32 query rows at a time: the reference's prefill
-// path runs its rows kernel "in slices of queries" the same way (src/core/kernels.cuh:486-490).  The chunk's M rows of one
-// session, at positions pos0 .. pos0 + M - 1, are cut into linear chains of 32 rows; as many chains as the step's capacity and
-// the attention's partial buffers hold go through prepare (head norms, rotation, K and V into the cache), attention and
-// combine (with the output gate) at once, each chain seeing the cache up to its own first row -- the rows of the chains
-// before it included, which the same prepare launch has just written -- and its own rows under the causal (chain) mask.
+// The next pass over a prefill chunk's rows: chains of up to 32 rows of one session at consecutive positions, as many as the
+// step's sequences and rows, `row_floats` floats a row in one staging plane, and the attention partials' slots hold.  A
+// later chain's context covers the earlier chains' rows: the prepare kernel has written them when the attention kernel starts.
+// Returns the rows taken (0: the step's capacity holds no chain).
+static int chunk_pass(ling_b200_ctx* c, int slot, int pos, int left, size_t row_floats, const int* zeros, const int* chain,
+                      std::vector<ling_b200_seq_step>& seqs) {
+  seqs.clear();
+  long slots = 0;
+  int rows = 0;
+  while (rows < left && int(seqs.size()) < c->d.max_seqs) {
+    const int n = std::min(kTreeRows, left - rows);
+    const long need = ling_b200_attn_slot_need(c, pos + rows);
+    if (rows + n > c->opt.max_rows || size_t(rows + n) * row_floats > c->plane_floats || (slots + need > c->chunk_slots && !seqs.empty())) break;
+    seqs.push_back(ling_b200_seq_step{slot, pos + rows, 0, n, n - 1, zeros, chain, nullptr});
+    slots += need, rows += n;
+  }
+  return rows;
+}
+struct ChunkChains {
+  std::vector<int> zeros, chain;
+  ChunkChains() : zeros(kTreeRows, 0), chain(kTreeRows) {
+    for (int i = 0; i < kTreeRows; ++i) chain[i] = i - 1;
+  }
+};
+static int attn_layer_of(const ling_b200_ctx* c, int attn_layer) {
+  for (int l = 0; l < c->cfg.layers; ++l)
+    if (c->attn_index[l] == attn_layer) return l;
+  return -1;
+}
+// the step's three attention launches over the staged rows: q|k|v planes -> cache and queries -> partials -> merged rows
+// (gated; FP8 copy for the o projection in xq_a, fp32 copy in `raw` if given)
+static int attention_over_planes(ling_b200_ctx* c, const LayerW& L, int al, const Planes& p, float* raw, int cls) {
+  const ModelDims& d = c->d;
+  const bool tc = c->opt.gemm_impl == 0 && attention_tc_supported(d);
+  LB_TRY(attn_prepare_launch(p, c->sb, d, al, L.q_norm, L.k_norm, c->qh, c->kv, cls, c->stream));
+  if (tc)
+    LB_TRY(attention_tc_launch(c->qh, c->sb, d, al, c->kv, c->part_o, c->part_ml, c->chunk_slots, c->sm_count, PrefetchPlan(), nullptr, c->stream));
+  else
+    LB_TRY(attention_launch(c->qh, c->sb, d, al, c->kv, c->part_o, c->part_ml, c->chunk_slots, c->sm_count * 2, c->stream));
+  return attn_combine_launch(c->part_o, c->part_ml, p, c->sb, d, c->qout(c->xq_a), raw, cls, c->opt.max_context / kAttnChunkShort + 2,
+                             tc ? kAttnTcRows : kAttnRowTile, tc ? c->sm_count : c->sm_count * 2, c->chunk_slots, c->stream);
+}
+
+// Attention over a prefill chunk: the M rows at positions pos0.. of one session, q|k|v rows in (host, the q|k|v
+// projection's layout), gated attention rows out (host, [M][heads][head_dim]); K and V of the rows go to the session's pages.
+// The rows pass through the step's own kernels as chains of 32 (the reference runs its prefill attention in slices of
+// queries as well, src/core/engine.cpp:1448-1460): correct for any M, not a many-row attention kernel.
 int ling_b200_prefill_attention_host(ling_b200_ctx* c, int slot, int attn_layer, int pos0, int M, const float* qkv, float* out) {
   LB_TRY(check_ctx(c));
   const ModelDims& d = c->d;
@@ -1444,30 +1485,14 @@ int ling_b200_prefill_attention_host(ling_b200_ctx* c, int slot, int attn_layer,
     set_error("prefill_attention_host: bad argument");
     return LING_B200_ERR_ARG;
   }
-  int layer = -1;
-  for (int l = 0; l < c->cfg.layers; ++l)
-    if (c->attn_index[l] == attn_layer) layer = l;
-  const LayerW& L = c->layers[layer];
+  const LayerW& L = c->layers[attn_layer_of(c, attn_layer)];
   const int W = d.Hq * 2 * d.D + 2 * d.Hkv * d.D, O = d.Hq * d.D;
-  const bool tc = c->opt.gemm_impl == 0 && attention_tc_supported(d);
-  std::vector<int> zeros(kTreeRows, 0), chain(kTreeRows);
-  for (int i = 0; i < kTreeRows; ++i) chain[i] = i - 1;
+  ChunkChains cc;
+  std::vector<ling_b200_seq_step> seqs;
   PdlScope pdl(c->opt.pdl != 0);
   for (int done = 0; done < M;) {
-    // the chains of this pass: within the step's sequences and rows, the staging buffers and the partial buffers' slots
-    std::vector<ling_b200_seq_step> seqs;
-    long slots = 0;
-    int rows = 0;
-    while (done + rows < M && int(seqs.size()) < d.max_seqs) {
-      const int n = std::min(kTreeRows, M - done - rows), pos = pos0 + done + rows;
-      const long need = ling_b200_attn_slot_need(c, pos);
-      if (rows + n > c->opt.max_rows || size_t(rows + n) * W > c->plane_floats || size_t(rows + n) * O > c->plane_floats ||
-          (slots + need > c->chunk_slots && !seqs.empty()))
-        break;
-      seqs.push_back(ling_b200_seq_step{slot, pos, 0, n, n - 1, zeros.data(), chain.data(), nullptr});
-      slots += need, rows += n;
-    }
-    if (seqs.empty()) {
+    const int rows = chunk_pass(c, slot, pos0 + done, M - done, size_t(std::max(W, O)), cc.zeros.data(), cc.chain.data(), seqs);
+    if (rows == 0) {
       set_error("prefill_attention_host: the context's step capacity holds no chain of the chunk");
       return LING_B200_ERR_ARG;
     }
@@ -1479,19 +1504,78 @@ int ling_b200_prefill_attention_host(ling_b200_ctx* c, int slot, int attn_layer,
     LB_CUDA(cudaMemcpyAsync(c->planes[0], qkv + size_t(done) * W, size_t(rows) * W * 4, cudaMemcpyHostToDevice, c->stream));
     Planes p;
     p.p = c->planes[0], p.n = 1, p.stride = 0, p.ld = W;
-    LB_TRY(attn_prepare_launch(p, c->sb, d, attn_layer, L.q_norm, L.k_norm, c->qh, c->kv, cls, c->stream));
-    if (tc)
-      LB_TRY(attention_tc_launch(c->qh, c->sb, d, attn_layer, c->kv, c->part_o, c->part_ml, c->chunk_slots, c->sm_count, PrefetchPlan(), nullptr, c->stream));
-    else
-      LB_TRY(attention_launch(c->qh, c->sb, d, attn_layer, c->kv, c->part_o, c->part_ml, c->chunk_slots, c->sm_count * 2, c->stream));
-    LB_TRY(attn_combine_launch(c->part_o, c->part_ml, p, c->sb, d, c->qout(c->xq_a), c->planes[1], cls,
-                               c->opt.max_context / kAttnChunkShort + 2, tc ? kAttnTcRows : kAttnRowTile,
-                               tc ? c->sm_count : c->sm_count * 2, c->chunk_slots, c->stream));
+    LB_TRY(attention_over_planes(c, L, attn_layer, p, c->planes[1], cls));
     LB_CUDA(cudaMemcpyAsync(out + size_t(done) * O, c->planes[1], size_t(rows) * O * 4, cudaMemcpyDeviceToHost, c->stream));
+    LB_TRY(read_err(c));  // also: the staging buffers are free for the next pass
+    done += rows;
+  }
+  return LING_B200_OK;
+}
+
+// A full-attention layer's whole mixer over a prefill chunk: h [M][hidden] (DEVICE memory, fp32; the residual rows at positions
+// pos0.. of one session) += o( gate * attention( prepare( q|k|v( norm(h) ) ) ) ) with the layer's own FP8 projections -- the
+// reference keeps the attention projections in FP8 on the prefill path too (src/core/kernels.cuh:1-4).  The rows pass through
+// the step's kernels as chains of 32, many chains a launch (see ling_b200_prefill_attention_host); the work is ordered on the
+// context's stream and the call returns when it is complete.  A staged verify step is replaced: stage again before the next launch.
+int ling_b200_chunk_attention_layer(ling_b200_ctx* c, int slot, int layer, int pos0, int M, float* h) {
+  LB_TRY(check_ctx(c));
+  const ModelDims& d = c->d;
+  if (slot < 0 || slot >= c->opt.sessions || layer < 0 || layer >= c->cfg.layers || !c->layers[layer].full || pos0 < 0 || M < 1 || !h ||
+      pos0 + M > d.max_pages * d.page_tokens) {
+    set_error("chunk_attention_layer: bad argument (the layer must be a full-attention layer)");
+    return LING_B200_ERR_ARG;
+  }
+  const LayerW& L = c->layers[layer];
+  const int al = c->attn_index[layer];
+  struct KeepCount {  // the verify step's launch count stays what its capture counted
+    ling_b200_ctx* c;
+    int n;
+    ~KeepCount() { c->launches_per_step = n; }
+  } keep{c, c->launches_per_step};
+  ChunkChains cc;
+  std::vector<ling_b200_seq_step> seqs;
+  Planes none;
+  none.p = nullptr;
+  PdlScope pdl(c->opt.pdl != 0);
+  for (int done = 0; done < M;) {
+    const int rows = chunk_pass(c, slot, pos0 + done, M - done, 0, cc.zeros.data(), cc.chain.data(), seqs);
+    if (rows == 0) {
+      set_error("chunk_attention_layer: the context's step capacity holds no chain of the chunk");
+      return LING_B200_ERR_ARG;
+    }
+    LB_TRY(stage_impl(c, seqs.data(), int(seqs.size()), 0, true));
+    LB_TRY(check_attn_slots(c));
+    const int cls = row_class(rows);
+    c->last_rows = rows, c->last_seqs = int(seqs.size()), c->last_flags = 0;
+    float* hs = h + size_t(done) * d.H;
+    LB_TRY(pack_launch(c->sb, d, c->stream));
+    LB_TRY(norm_quant_launch(hs, none, nullptr, c->embed, L.input_norm, nullptr, c->qout(c->xq_h), c->sb.n_rows_total, cls, d.H, d.eps, c->stream));
+    LB_TRY(run_gemm(c, L.qkv, c->xq_h, 0, cls));
+    LB_TRY(attention_over_planes(c, L, al, planes_of(c, 0, L.qkv), nullptr, cls));
+    LB_TRY(run_gemm(c, L.o, c->xq_a, 1, cls));
+    // the o projection's partial sums into the residual rows (the norm's residual add; its normed copy is not used)
+    LB_TRY(norm_quant_launch(hs, planes_of(c, 1, L.o), nullptr, c->embed, L.post_norm, nullptr, c->qout(c->xq_h), c->sb.n_rows_total, cls, d.H,
+                             d.eps, c->stream));
     LB_TRY(read_err(c));
     done += rows;
   }
   return LING_B200_OK;
+}
+// The same with the residual rows in host memory (in and out).
+int ling_b200_chunk_attention_layer_host(ling_b200_ctx* c, int slot, int layer, int pos0, int M, float* h) {
+  LB_TRY(check_ctx(c));
+  if (!h || M < 1) {
+    set_error("chunk_attention_layer_host: bad argument");
+    return LING_B200_ERR_ARG;
+  }
+  float* dev = nullptr;
+  const size_t bytes = size_t(M) * c->d.H * 4;
+  LB_CUDA(cudaMalloc(&dev, bytes));
+  int rc = cudaMemcpy(dev, h, bytes, cudaMemcpyHostToDevice) == cudaSuccess ? LING_B200_OK : LING_B200_ERR_CUDA;
+  if (rc == LING_B200_OK) rc = ling_b200_chunk_attention_layer(c, slot, layer, pos0, M, dev);
+  if (rc == LING_B200_OK && cudaMemcpy(h, dev, bytes, cudaMemcpyDeviceToHost) != cudaSuccess) rc = LING_B200_ERR_CUDA;
+  cudaFree(dev);
+  return rc;
 }
 
 // ------------------------------------------------------------------------------------------------ read-backs

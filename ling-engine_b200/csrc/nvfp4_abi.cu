@@ -69,7 +69,11 @@ struct ling_b200_nvfp4_ffn {
   };
   std::vector<Layer> L;
   GdnBuffers mix;                // with mixers (ling_b200_nvfp4_ffn_add_mixers): the DeltaNet layers' mixer runs before their FFN
-  std::vector<GdnWeights> mixers;  // by layer; a full-attention layer's entry stays empty (its mixer is not built)
+  std::vector<GdnWeights> mixers;  // by layer; a full-attention layer's entry stays empty
+  // with a verify context attached (ling_b200_nvfp4_ffn_attach_context): the full-attention layers' mixer runs through that
+  // context's own FP8 projections and attention kernels, on the chunk session's pages
+  ling_b200_ctx* attn_ctx = nullptr;
+  int attn_slot = 0, attn_pos0 = 0, attn_every = 0;
   float* h = nullptr;      // residual [max_rows][H]
   Fp4Operand x, mid;       // the two GEMMs' activations
   int* err = nullptr;
@@ -189,6 +193,13 @@ int ffn_run(ling_b200_nvfp4_ffn* f, int rows) {
   for (size_t l = 0; l < f->L.size(); ++l) {
     const auto& L = f->L[l];
     if (l < f->mixers.size() && f->mixers[l].in_qkv.codes) LB_TRY(gdn_mixer_run(f->mix, f->mixers[l], f->h, rows, f->err, f->ctas, f->stream));
+    if (f->attn_ctx && f->attn_every > 0 && int(l) % f->attn_every == f->attn_every - 1) {
+      // the attention layer works on the context's stream and returns when it is complete; what this stream has queued
+      // on the residual comes first
+      LB_CUDA(cudaStreamSynchronize(f->stream));
+      LB_TRY(ling_b200_chunk_attention_layer(f->attn_ctx, f->attn_slot, int(l), f->attn_pos0, rows, f->h));
+      LB_CUDA(cudaSetDevice(f->device));
+    }
     LB_TRY(fp4_rmsnorm_quant_launch(f->h, L.norm, nullptr, rows, f->H, f->eps, 1.f / L.in_scale, f->x.codes, f->x.sf, true, f->stream));
     Fp4GemmCall gu;
     gu.X = &f->x, gu.W = &L.gate, gu.W2 = &L.up;
@@ -477,6 +488,17 @@ int ling_b200_nvfp4_ffn_add_mixers(ling_b200_nvfp4_ffn* f, int k_heads, int v_he
   for (int l = 0; l < f->layers; ++l)
     if (full_every == 0 || l % full_every != full_every - 1) LB_TRY(gdn_weights_create(f->mem, f->stream, f->mix, l, seed, wtmp, amax, s2, f->mixers[size_t(l)]));
   LB_CUDA(cudaStreamSynchronize(f->stream));
+  return LING_B200_OK;
+}
+
+// The full-attention layers' mixers (every `full_every`-th layer of the stack = the same layer of the verify context, which
+// must have as many layers): the chunk's rows are positions pos0.. of session `slot`, whose pages the caller has mapped.
+int ling_b200_nvfp4_ffn_attach_context(ling_b200_nvfp4_ffn* f, ling_b200_ctx* ctx, int slot, int pos0, int full_every) {
+  if (!f || slot < 0 || pos0 < 0 || full_every < 1) {
+    set_error("nvfp4_ffn_attach_context: bad argument");
+    return LING_B200_ERR_ARG;
+  }
+  f->attn_ctx = ctx, f->attn_slot = slot, f->attn_pos0 = pos0, f->attn_every = full_every;
   return LING_B200_OK;
 }
 

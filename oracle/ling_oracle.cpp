@@ -998,7 +998,7 @@ struct Saved {
 
 // One layer of the forward pass over the packed rows (src/core/engine.cpp:1361-1725): h [M][H] is the residual stream
 // before the layer on entry and after it on return.  pack_step() has run.
-void layer_forward(lo_model* m, const lo_seq_step* seqs, int n_seqs, int l, std::vector<float>& h, Saved& saved) {
+void layer_forward(lo_model* m, const lo_seq_step* seqs, int n_seqs, int l, std::vector<float>& h, Saved& saved, bool ffn = true) {
   const lo_model_config& c = m->cfg;
   const int H = c.hidden, I = c.intermediate, Hq = c.heads, Hkv = c.kv_heads, D = c.head_dim;
   const int Hk = c.lin_k_heads, HV = c.lin_v_heads, Dk = c.lin_k_dim, Dv = c.lin_v_dim, C = m->C(), Vs = m->Vs();
@@ -1083,6 +1083,7 @@ void layer_forward(lo_model* m, const lo_seq_step* seqs, int n_seqs, int l, std:
       for (size_t i = 0; i < h.size(); ++i) h[i] += o[i];
       saved.pre[gl] = std::move(pre), saved.post[gl] = std::move(post), saved.g[gl] = std::move(g), saved.beta[gl] = std::move(beta);
     }
+    if (!ffn) return;  // the mixer alone
     // B.5 SwiGLU FFN (src/core/engine.cpp:1698-1703, src/core/kernels.cu:308-312)
     for (int r = 0; r < M; ++r) rmsnorm(&h[size_t(r) * H], L.post_norm.data(), &xn[size_t(r) * H], H, c.eps, true);
     QAct fq;
@@ -1223,6 +1224,17 @@ int lo_layer_forward(lo_model* m, const lo_seq_step* seqs, int n_seqs, int layer
   }
   Saved saved(m->n_gdn);
   layer_forward(m, seqs, n_seqs, layer, h, saved);
+  std::copy(h.begin(), h.end(), h_out);
+  return 0;
+}
+// The layer's mixer alone (attention or DeltaNet with its projections and the residual add), without the feed-forward block.
+int lo_mixer_forward(lo_model* m, const lo_seq_step* seqs, int n_seqs, int layer, const float* h_in, float* h_out) {
+  if (layer < 0 || layer >= m->cfg.layers) return 1;
+  if (const int rc = pack_step(m, seqs, n_seqs)) return rc;
+  const size_t n = size_t(m->rows) * m->cfg.hidden;
+  std::vector<float> h(h_in, h_in + n);
+  Saved saved(m->n_gdn);
+  layer_forward(m, seqs, n_seqs, layer, h, saved, false);
   std::copy(h.begin(), h.end(), h_out);
   return 0;
 }

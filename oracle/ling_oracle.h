@@ -126,6 +126,8 @@ int lo_attention(lo_model* m, const lo_seq_step* seqs, int n_seqs, int attn_laye
 /* one layer alone on a given residual stream (teacher forcing); layer == cfg.layers: the final norm and the head */
 int lo_layer_forward(lo_model* m, const lo_seq_step* seqs, int n_seqs, int layer, const float* h_in, float* h_out,
                      int head_rows);
+/* the layer's mixer alone: h_out = h_in + mixer(norm(h_in)), no feed-forward block */
+int lo_mixer_forward(lo_model* m, const lo_seq_step* seqs, int n_seqs, int layer, const float* h_in, float* h_out);
 /* attn_prepare alone: q|k|v projection rows in, normed + rotated q (and k before the cache rounding) out, K/V stored */
 int lo_attn_prepare(lo_model* m, const lo_seq_step* seqs, int n_seqs, int attn_layer, const float* qkv, float* q_out,
                     float* k_out);

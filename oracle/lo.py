@@ -280,6 +280,16 @@ class Model:
         self.last_seqs = len(seqs)
         return out
 
+    def mixer_forward(self, seqs, layer, h_in, make_steps=None):
+        """The layer's mixer alone on the residual rows h_in (no feed-forward block)."""
+        arr, keep = make_steps(seqs)
+        h_in = np.ascontiguousarray(h_in, np.float32)
+        out = np.zeros_like(h_in)
+        assert lo().lo_mixer_forward(self.h, arr, len(seqs), layer, _fp(h_in), _fp(out)) == 0
+        self.last_rows = sum(len(s["tokens"]) for s in seqs)
+        self.last_seqs = len(seqs)
+        return out
+
     def attn_prepare(self, seqs, attn_layer, qkv, make_steps=None):
         """attn_prepare alone: returns (q [rows][heads][D], k before the cache rounding [rows][kv_heads][D])."""
         arr, keep = make_steps(seqs)

@@ -160,3 +160,19 @@ def test_persistent_layer_segments_are_bit_identical_to_the_separate_launches(wi
         assert np.array_equal(got[1][0], outs[0][1][0]) and np.array_equal(got[1][1], outs[0][1][1])
         assert got[2:] == outs[0][2:]
     chained.close()
+
+
+@pytest.mark.parametrize("pos0,M", [(0, 70), (530, 128)])
+def test_chunk_attention_layer_27b_width_matches_oracle(wide, lb, pos0, M):
+    # the prefill chunk's full-attention mixer at the 27B widths (5120 hidden, 24 query / 4 kv heads of 256, FP8 q|k|v and o
+    # projections): passes of three 32-row chains (the fixture's 96-row step), against the oracle's mixer chain by chain
+    from test_gpu_kernels import chunk_layer_errors
+    cfg, ctx, m = wide
+    helpers.map_pages([ctx, m], 0, pos0 + M, 16, 6000)
+    if pos0:
+        ctx.synth_kv(0, pos0, 7), m.synth_kv(0, pos0, 7)
+    rng = np.random.default_rng(pos0 + M)
+    h = (rng.standard_normal((M, cfg.hidden)) * np.exp(0.5 * rng.standard_normal((M, 1)))).astype(np.float32)
+    err = chunk_layer_errors(lb, ctx, m, 3, pos0, h)
+    print("chunk attention layer at the 27B widths: row error max %.2e median %.2e" % (err.max(), np.median(err)))
+    assert err.max() <= ATTN_LAYER_TOL and np.median(err) <= 1e-2, (float(err.max()), float(np.median(err)))

@@ -467,3 +467,43 @@ def test_prefill_attention_in_slices_matches_oracle(gpu, lb, lo, shape, pos0, M)
     for a, b in zip(ctx.kv_read(0, 0, 0, pos0 + M), m.kv_read(0, 0, 0, pos0 + M)):
         assert np.abs(a - b).max() <= 0.13 * np.abs(b).max()  # FP8 codes may differ by a step where the norm's last bit differs
     ctx.close(), m.close()
+
+
+def chunk_layer_errors(lb, ctx, m, layer, pos0, h):
+    """Row errors of what a full-attention layer's chunk mixer adds to the residual rows h, device against the oracle's mixer
+    taking the 32-row chains one at a time (session 0)."""
+    M = h.shape[0]
+    got = ctx.chunk_attention_layer(0, layer, pos0, h)
+    want = np.zeros_like(h)
+    for r0 in range(0, M, 32):
+        n = min(32, M - r0)
+        seq = [{"slot": 0, "pos": pos0 + r0, "tokens": np.zeros(n, np.int32), "parent": np.arange(-1, n - 1, dtype=np.int32), "chain": n - 1}]
+        want[r0:r0 + n] = m.mixer_forward(seq, layer, h[r0:r0 + n], make_steps=lb.make_steps)
+    assert np.isfinite(got).all()
+    d_got, d_want = got - h, want - h
+    rms = np.sqrt((d_want.astype(np.float64) ** 2).mean(axis=1, keepdims=True))
+    assert (rms > 0).all()
+    return np.sqrt(((d_got - d_want).astype(np.float64) ** 2).mean(axis=1, keepdims=True)) / rms
+
+
+@pytest.mark.parametrize("pos0,M", [(0, 100), (37, 150)])
+def test_chunk_attention_layer_matches_oracle(gpu, lb, lo, pos0, M):
+    # A full-attention layer's mixer over a prefill chunk's residual rows (norm, FP8 q|k|v projection, prepare, attention, gate,
+    # FP8 o projection, residual add) through the step's kernels, several 32-row chains of the session per launch, against the
+    # oracle's mixer taking the chains one at a time.  Bars on what the mixer added, row by row against its rms: the o
+    # projection's FP8 input rounds a last-bit difference of the attention output to the next code now and then.
+    cfg = lb.make_config(256, 704, 1, 4096, 4, 1, 64, 16, 2, 4, 64, 64, [1])
+    page_tokens = 16
+    pool = (pos0 + M) // page_tokens + 3
+    ctx = lb.Context(cfg, sessions=1, max_context=1024, page_tokens=page_tokens, pool_pages=pool, max_seqs=4, max_rows=128)
+    opt = lb.Options(1, 1024, page_tokens, pool, 4, 128, 0, 0, 0, 0, 0)
+    m = lo.Model(cfg, opt, lb)
+    ctx.synth_weights(3), m.synth_weights(3)
+    helpers.map_pages([ctx, m], 0, pos0 + M, page_tokens, 1)
+    if pos0:
+        ctx.synth_kv(0, pos0, 7), m.synth_kv(0, pos0, 7)
+    rng = np.random.default_rng(pos0 + M)
+    h = (rng.standard_normal((M, cfg.hidden)) * np.exp(0.5 * rng.standard_normal((M, 1)))).astype(np.float32)
+    err = chunk_layer_errors(lb, ctx, m, 0, pos0, h)
+    assert err.max() <= 2e-2 and np.median(err) <= 5e-3, (float(err.max()), float(np.median(err)))
+    ctx.close(), m.close()
