@@ -588,6 +588,9 @@ int ling_b200_prefill_attention_host(ling_b200_ctx* ctx, int slot, int attn_laye
  * returns when the work is complete; a staged verify step is replaced (stage again).  _host: h in host memory, in and out. */
 int ling_b200_chunk_attention_layer(ling_b200_ctx* ctx, int slot, int layer, int pos0, int M, float* h_device);
 int ling_b200_chunk_attention_layer_host(ling_b200_ctx* ctx, int slot, int layer, int pos0, int M, float* h);
+/* Measurement aid: the layer over M zero rows with an event pair around every launch.  ms[0] the two FP8 projections, ms[1] the
+ * attention kernel, ms[2] the combine, ms[3] the two norms, ms[5] the prepare kernel; *passes = launches of chains. */
+int ling_b200_chunk_attention_layer_profile(ling_b200_ctx* ctx, int slot, int layer, int pos0, int M, float ms[8], int* passes);
 /* Attaches a verify context to the chunk stack: every `full_every`-th layer (the full-attention layers) then runs
  * ling_b200_chunk_attention_layer on that context ahead of its feed-forward block, the chunk being positions pos0.. of `slot`.
  * No counterpart of its own in the reference: there one engine holds both paths. */

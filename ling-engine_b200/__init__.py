@@ -324,6 +324,12 @@ class Context:
         check(lib().ling_b200_chunk_attention_layer_host(self.h, slot, layer, pos0, h.shape[0], _fp(h)), "chunk_attention_layer_host")
         return h
 
+    def chunk_attention_layer_profile(self, slot, layer, pos0, M):
+        """Device milliseconds of one chunk attention layer by kernel family, and the number of chain launches."""
+        ms, passes = (C.c_float * 8)(), C.c_int(0)
+        check(lib().ling_b200_chunk_attention_layer_profile(self.h, slot, layer, pos0, M, ms, C.byref(passes)), "chunk_attention_layer_profile")
+        return {"projections": ms[0], "attention": ms[1], "combine": ms[2], "norms": ms[3], "prepare": ms[5]}, passes.value
+
     def read_tree_desc(self, seq):
         t = TreeDesc()
         check(lib().ling_b200_read_tree_desc(self.h, seq, C.byref(t)), "read_tree_desc")

@@ -1464,11 +1464,18 @@ static int attn_layer_of(const ling_b200_ctx* c, int attn_layer) {
 static int attention_over_planes(ling_b200_ctx* c, const LayerW& L, int al, const Planes& p, float* raw, int cls) {
   const ModelDims& d = c->d;
   const bool tc = c->opt.gemm_impl == 0 && attention_tc_supported(d);
-  LB_TRY(attn_prepare_launch(p, c->sb, d, al, L.q_norm, L.k_norm, c->qh, c->kv, cls, c->stream));
-  if (tc)
-    LB_TRY(attention_tc_launch(c->qh, c->sb, d, al, c->kv, c->part_o, c->part_ml, c->chunk_slots, c->sm_count, PrefetchPlan(), nullptr, c->stream));
-  else
-    LB_TRY(attention_launch(c->qh, c->sb, d, al, c->kv, c->part_o, c->part_ml, c->chunk_slots, c->sm_count * 2, c->stream));
+  {
+    Timed t(c, kFamStep);  // (a profile of the chunk layer reads: Step = prepare, Attn = attention, Gdn = combine, Elem = norms)
+    LB_TRY(attn_prepare_launch(p, c->sb, d, al, L.q_norm, L.k_norm, c->qh, c->kv, cls, c->stream));
+  }
+  {
+    Timed t(c, kFamAttn);
+    if (tc)
+      LB_TRY(attention_tc_launch(c->qh, c->sb, d, al, c->kv, c->part_o, c->part_ml, c->chunk_slots, c->sm_count, PrefetchPlan(), nullptr, c->stream));
+    else
+      LB_TRY(attention_launch(c->qh, c->sb, d, al, c->kv, c->part_o, c->part_ml, c->chunk_slots, c->sm_count * 2, c->stream));
+  }
+  Timed t(c, kFamGdn);
   return attn_combine_launch(c->part_o, c->part_ml, p, c->sb, d, c->qout(c->xq_a), raw, cls, c->opt.max_context / kAttnChunkShort + 2,
                              tc ? kAttnTcRows : kAttnRowTile, tc ? c->sm_count : c->sm_count * 2, c->chunk_slots, c->stream);
 }
@@ -1549,17 +1556,54 @@ int ling_b200_chunk_attention_layer(ling_b200_ctx* c, int slot, int layer, int p
     c->last_rows = rows, c->last_seqs = int(seqs.size()), c->last_flags = 0;
     float* hs = h + size_t(done) * d.H;
     LB_TRY(pack_launch(c->sb, d, c->stream));
-    LB_TRY(norm_quant_launch(hs, none, nullptr, c->embed, L.input_norm, nullptr, c->qout(c->xq_h), c->sb.n_rows_total, cls, d.H, d.eps, c->stream));
+    {
+      Timed t(c, kFamElem);
+      LB_TRY(norm_quant_launch(hs, none, nullptr, c->embed, L.input_norm, nullptr, c->qout(c->xq_h), c->sb.n_rows_total, cls, d.H, d.eps, c->stream));
+    }
     LB_TRY(run_gemm(c, L.qkv, c->xq_h, 0, cls));
     LB_TRY(attention_over_planes(c, L, al, planes_of(c, 0, L.qkv), nullptr, cls));
     LB_TRY(run_gemm(c, L.o, c->xq_a, 1, cls));
     // the o projection's partial sums into the residual rows (the norm's residual add; its normed copy is not used)
-    LB_TRY(norm_quant_launch(hs, planes_of(c, 1, L.o), nullptr, c->embed, L.post_norm, nullptr, c->qout(c->xq_h), c->sb.n_rows_total, cls, d.H,
-                             d.eps, c->stream));
+    {
+      Timed t(c, kFamElem);
+      LB_TRY(norm_quant_launch(hs, planes_of(c, 1, L.o), nullptr, c->embed, L.post_norm, nullptr, c->qout(c->xq_h), c->sb.n_rows_total, cls,
+                               d.H, d.eps, c->stream));
+    }
     LB_TRY(read_err(c));
     done += rows;
   }
   return LING_B200_OK;
+}
+// Where a chunk layer's device time goes: the layer over M zero rows with an event pair around every launch; ms[0] the two
+// FP8 projections, [1] the attention kernel, [2] the combine, [3] the two norms, [5] the prepare kernel; *passes = launches of chains.
+int ling_b200_chunk_attention_layer_profile(ling_b200_ctx* c, int slot, int layer, int pos0, int M, float ms[8], int* passes) {
+  LB_TRY(check_ctx(c));
+  if (!ms || M < 1) {
+    set_error("chunk_attention_layer_profile: bad argument");
+    return LING_B200_ERR_ARG;
+  }
+  float* dev = nullptr;
+  const size_t bytes = size_t(M) * c->d.H * 4;
+  LB_CUDA(cudaMalloc(&dev, bytes));
+  cudaMemset(dev, 0, bytes);
+  LB_TRY(finish(c));
+  c->profiling = true;
+  c->prof.clear();
+  const int rc = ling_b200_chunk_attention_layer(c, slot, layer, pos0, M, dev);
+  c->profiling = false;
+  for (int i = 0; i < 8; ++i) ms[i] = 0.f;
+  int norms = 0;
+  for (auto& p : c->prof) {
+    float t = 0.f;
+    if (rc == LING_B200_OK) cudaEventElapsedTime(&t, p.second.first, p.second.second);
+    ms[p.first] += t;
+    norms += p.first == kFamElem;
+    cudaEventDestroy(p.second.first), cudaEventDestroy(p.second.second);
+  }
+  if (passes) *passes = norms / 2;
+  c->prof.clear();
+  cudaFree(dev);
+  return rc;
 }
 // The same with the residual rows in host memory (in and out).
 int ling_b200_chunk_attention_layer_host(ling_b200_ctx* c, int slot, int layer, int pos0, int M, float* h) {
