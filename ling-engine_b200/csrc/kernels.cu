@@ -1471,8 +1471,11 @@ __global__ void __launch_bounds__(256)
   if (c0 >= q.K_pad) return;
   const int s = sb.seq_of[m], local = sb.local[m];
   const int chunk = attn_chunk_keys(sb, *sb.n_seqs, d.Hkv, G, tile_rows, budget);
+  // chunk slots of the sequences ahead of this one: every warp adds them up for itself, a lane per sequence (a serial loop
+  // over up to 64 sequences in every block of a thousand-row step was a sixth of the kernel's time there)
   int cb = 0;
-  for (int t = 0; t < s; ++t) cb += (sb.seqs[t].pos + chunk - 1) / chunk + 1;
+  for (int t = threadIdx.x & 31; t < s; t += 32) cb += (sb.seqs[t].pos + chunk - 1) / chunk + 1;
+  cb = __reduce_add_sync(0xffffffffu, cb);
   const int nch = min(max_chunks, (sb.seqs[s].pos + chunk - 1) / chunk + 1);
   float* wgt = csm;                       // [HB][max_chunks]
   float* den = csm + HB * max_chunks;     // [HB]

@@ -313,6 +313,33 @@ def test_rows_do_not_depend_on_batch_mates(toy, lb):
         assert np.array_equal(ctx.read_logits(), batch[row0[s]:row0[s + 1]]), s
 
 
+def test_rows_do_not_depend_on_batch_mates_in_a_many_row_step(gpu, lb):
+    # a step of several hundred rows (128-row token tiles in the GEMMs, many work items a CTA in the attention and DeltaNet
+    # kernels): a sequence's logits there are bit for bit what it gets alone in a 32-row step
+    cfg = lb.toy_config()
+    n_seq = 16
+    contexts = [3, 37, 512, 1029] + [int(c) for c in np.random.default_rng(9).integers(1, 900, n_seq - 4)]
+    pool = sum((c + 32) // 16 + 2 for c in contexts) + 2
+    ctx = lb.Context(cfg, sessions=n_seq, max_context=2048, page_tokens=16, pool_pages=pool, max_seqs=n_seq, max_rows=32 * n_seq,
+                     debug_rows=32 * n_seq)
+    ctx.synth_weights(4)
+    rng = np.random.default_rng(6)
+    seqs = []
+    for s, c in enumerate(contexts):
+        n = int(rng.integers(20, 33))
+        chain = int(rng.integers(0, n))
+        seqs.append({"slot": s, "pos": c, "tokens": rng.integers(0, cfg.vocab, n).astype(np.int32),
+                     "parent": np.array(helpers.random_tree(rng, n, chain), np.int32), "chain": chain})
+    assert sum(len(q["tokens"]) for q in seqs) > 256
+    helpers.setup_sessions([ctx], cfg, seqs, 16, 0)
+    ctx.verify_step(seqs, flags=lb.STEP_KEEP_LOGITS)
+    batch, row0 = ctx.read_logits(), ctx.read_packing()["row0"]
+    for s in (0, 3, 9, 15):
+        ctx.verify_step([seqs[s]], flags=lb.STEP_KEEP_LOGITS)
+        assert np.array_equal(ctx.read_logits(), batch[row0[s]:row0[s + 1]]), s
+    ctx.close()
+
+
 def test_ragged_random_trees_and_multiple_steps(toy, lb):
     cfg, ctx, m = toy
     rng = np.random.default_rng(6)
