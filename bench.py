@@ -804,6 +804,17 @@ def run_micro_gemm(args):
         print(json.dumps({"micro": "gdn_chunk_prepare_kernel + gdn_chunk_apply_kernel", "rows": M, "heads": [16, 48], "iters": args.iters, "us_per_launch": ms * 1e3,
                           "us_per_32_token_chunk": ms * 1e3 / ((M + 31) // 32), "rows_per_s": M / (ms * 1e-3)}), flush=True)
         return
+    if args.micro == "sparse-head":
+        # the drafter's sparse head: the selection of the rows a draft step scores (M step rows against the 248,320 x 256 BF16 factor)
+        V, dyn, cap = 248320, 16384, 32768
+        sc_ms, all_ms = lbm.sparse_select_bench(V, M, dyn, cap, iters=args.iters)
+        peak = measured_peaks()[0]
+        gbs = V * 512 / (sc_ms * 1e-3) / 1e9
+        print(json.dumps({"micro": "sparse_scores_kernel (+ sparse_level x 3, count, scan, scatter)", "vocab": V, "step_rows": M, "dynamic": dyn, "cap": cap,
+                          "iters": args.iters, "us_scores": sc_ms * 1e3, "us_selection": all_ms * 1e3,
+                          "roofline": {"bound": "hbm", "achieved": gbs, "unit": "GB/s", "peak": peak, "frac": gbs / peak if peak else None,
+                                       "bytes": "vocab x 512 (the factor, read once)"}}), flush=True)
+        return
     if args.micro == "gdn-layer":
         # one DeltaNet layer's whole mixer on the prefill path (eight launches), M rows, the 27B model's widths
         layer = lbm.PrefillGdnLayer(5120, 16, 48, M, seed=1)
@@ -926,7 +937,7 @@ def main():
     ap.add_argument("--systems", type=int, default=0, help="served64: prompts begin with one of this many shared system messages")
     ap.add_argument("--prefix-kv-mb", type=int, default=0, help="served64 with --systems: the prefix KV store's budget for saved states (0: store off)")
     ap.add_argument("--pool-pages", type=int, default=0, help="served64: KV page pool size (0: sized for the resident sessions)")
-    ap.add_argument("--micro", default="", choices=["", "gemm", "nvfp4", "nvfp4-swiglu", "gdn-chunk", "gdn-layer"], help="time one kernel alone on resident operands")
+    ap.add_argument("--micro", default="", choices=["", "gemm", "nvfp4", "nvfp4-swiglu", "gdn-chunk", "gdn-layer", "sparse-head"], help="time one kernel alone on resident operands")
     ap.add_argument("--shape", default="24,34816,5120", help="--micro gemm: rows,N,K (default: the gate|up projection)")
     ap.add_argument("--iters", type=int, default=20)
     args = ap.parse_args()

@@ -651,6 +651,29 @@ int ling_b200_draft_head_create(ling_b200_ctx* ctx, const uint16_t* selector_pro
 void ling_b200_draft_head_destroy(ling_b200_draft_head* h);
 int ling_b200_draft_head_run(ling_b200_draft_head* h, const float* x, int E, int anchor, int* cand, float* unary, float* scores);
 
+/* ---- the drafter's sparse head (src/core/sparse_head.cu; Engine::draft_launch, src/core/speculate.cpp:598-610) ----
+ * Instead of the whole vocabulary a draft step scores the rows its session's mask marks (a fixed list of frequent tokens joined
+ * with the ids of the session's prompt and output) and the `dynamic` rows a rank-256 factor of the head rates best for the step's
+ * rows: approx[n] = max_m p[m] . us[n], p = x . vt^T (BF16 factors, fp32 sums; ties at the threshold all taken; if fewer
+ * unmarked rows than `dynamic` exist none of them is taken, as in the reference's radix walk).  The selected rows' logits are the
+ * full head's, bit for bit: they are gathered into a compact matrix that the head GEMM multiplies. */
+/* sparse_head_select (kernels.cuh:296-306) over host buffers: masks = n_masks arrays of N bytes; rows [cap] ascending ids,
+ * *nrows their count; keys (may be NULL) [N] the ranked 32-bit keys, 0 = marked. */
+int ling_b200_sparse_select_host(int device, const float* p, int M, const uint16_t* us_bf16, int N, const uint8_t* masks, int n_masks,
+                                 int dynamic, int cap, int* rows, int* nrows, uint32_t* keys);
+/* Timing aid: the selection on synthetic factors resident in HBM; ms[0] the scores kernel alone (reads N x 512 bytes), ms[1] the
+ * whole selection.  No counterpart in the reference. */
+int ling_b200_sparse_select_bench(int device, int N, int M, int dynamic, int cap, int iters, float ms[2]);
+/* SparseHeadBufs (kernels.cuh:318-334) on a draft head: us [vocab][256], vt [256][hidden] BF16; every session starts with an empty mask. */
+int ling_b200_draft_head_enable_sparse(ling_b200_draft_head* h, const uint16_t* us_bf16, const uint16_t* vt_bf16, int dynamic, int cap);
+/* sparse_head_mark (kernels.cuh:310): reset clears the session's mask first. */
+int ling_b200_draft_head_mask_reset(ling_b200_draft_head* h, int session, const int* ids, int n);
+int ling_b200_draft_head_mask_mark(ling_b200_draft_head* h, int session, const int* ids, int n);
+/* draft_head_rows' sparse branch (sparse_head.cu:262-276) followed by the selector, as ling_b200_draft_head_run; *n_selected and
+ * selected [cap] (both may be NULL): the rows that were scored. */
+int ling_b200_draft_head_run_sparse(ling_b200_draft_head* h, int session, const float* x, int E, int anchor, int* cand, float* unary,
+                                    float* scores, int* n_selected, int* selected);
+
 /* Device memory helpers for callers without a CUDA binding (tests): device count, and name of device 0. */
 int ling_b200_device_count(void);
 /* How a step of `rows` packed rows runs: the capacity class its graph is captured for (the token tile up to 128 rows,

@@ -674,6 +674,26 @@ def selector_lattice(cand, unary, pred_bits, succ_bits, anchor, hp=None, x=None,
     return scores, hp
 
 
+def sparse_select(p, us_bits, masks, dynamic, cap, device=0):
+    """The sparse head's selection (ling_b200_sparse_select_host): p [M][256], us_bits [N][256] BF16 bits, masks [n][N] bytes.
+    Returns (rows ascending, keys [N] uint32: what the selection ranked, 0 = marked)."""
+    p = np.ascontiguousarray(p, np.float32)
+    us_bits = np.ascontiguousarray(us_bits, np.uint16)
+    masks = np.ascontiguousarray(np.atleast_2d(masks), np.uint8)
+    N = us_bits.shape[0]
+    rows, n, keys = np.zeros(cap, np.int32), C.c_int(0), np.zeros(N, np.uint32)
+    check(lib().ling_b200_sparse_select_host(device, _fp(p), p.shape[0], _u16(us_bits), N, _bp(masks), masks.shape[0], dynamic, cap,
+                                             _ip(rows), C.byref(n), keys.ctypes.data_as(C.POINTER(C.c_uint32))), "sparse_select")
+    return rows[:n.value].copy(), keys
+
+
+def sparse_select_bench(N, M, dynamic, cap, iters=20, device=0):
+    """(ms of the scores kernel alone, ms of the whole selection) on synthetic factors resident in HBM."""
+    ms = (C.c_float * 2)()
+    check(lib().ling_b200_sparse_select_bench(device, N, M, dynamic, cap, iters, ms), "sparse_select_bench")
+    return ms[0], ms[1]
+
+
 class DraftHead:
     """The drafter's last stage on a Context (ling_b200_draft_head_*): rows after the drafter's final norm in, candidates and
     selector scores out."""
@@ -688,6 +708,30 @@ class DraftHead:
         cand, unary, scores = np.zeros((E, 16), np.int32), np.zeros((E, 16), np.float32), np.zeros((E, 16, 16), np.float32)
         check(lib().ling_b200_draft_head_run(self.h, _fp(x), E, int(anchor), _ip(cand), _fp(unary), _fp(scores)), "draft_head_run")
         return cand, unary, scores
+
+    def enable_sparse(self, us_bits, vt_bits, dynamic, cap):
+        """The sparse head: us [vocab][256] and vt [256][hidden] BF16 bits (the head's rank-256 factors)."""
+        check(lib().ling_b200_draft_head_enable_sparse(self.h, _u16(np.ascontiguousarray(us_bits, np.uint16)),
+                                                       _u16(np.ascontiguousarray(vt_bits, np.uint16)), dynamic, cap), "draft_head_enable_sparse")
+        self.cap = cap
+
+    def mask_reset(self, session, ids):
+        ids = np.ascontiguousarray(ids, np.int32)
+        check(lib().ling_b200_draft_head_mask_reset(self.h, session, _ip(ids), len(ids)), "draft_head_mask_reset")
+
+    def mask_mark(self, session, ids):
+        ids = np.ascontiguousarray(ids, np.int32)
+        check(lib().ling_b200_draft_head_mask_mark(self.h, session, _ip(ids), len(ids)), "draft_head_mask_mark")
+
+    def run_sparse(self, session, x, anchor):
+        """As run, scoring only the session's mask and the rows the rank-256 factors rate best; also returns the scored rows."""
+        x = np.ascontiguousarray(x, np.float32)
+        E = x.shape[0]
+        cand, unary, scores = np.zeros((E, 16), np.int32), np.zeros((E, 16), np.float32), np.zeros((E, 16, 16), np.float32)
+        n, sel = C.c_int(0), np.zeros(self.cap, np.int32)
+        check(lib().ling_b200_draft_head_run_sparse(self.h, session, _fp(x), E, int(anchor), _ip(cand), _fp(unary), _fp(scores), C.byref(n),
+                                                    _ip(sel)), "draft_head_run_sparse")
+        return cand, unary, scores, sel[:n.value].copy()
 
     def close(self):
         if self.h:

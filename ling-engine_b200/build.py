@@ -13,7 +13,7 @@ from concurrent.futures import ThreadPoolExecutor
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libling_b200.so")
-SOURCES = ["gemm.cu", "nvfp4.cu", "nvfp4_abi.cu", "chain.cu", "kernels.cu", "attention_tc.cu", "context.cu", "kernel_abi.cu", "noalloc.cu", "draft_head.cu", "gdn_chunk.cu", "host_logic.cpp", "prefix_store.cpp"]
+SOURCES = ["gemm.cu", "nvfp4.cu", "nvfp4_abi.cu", "chain.cu", "kernels.cu", "attention_tc.cu", "context.cu", "kernel_abi.cu", "noalloc.cu", "draft_head.cu", "draft_sparse.cu", "gdn_chunk.cu", "host_logic.cpp", "prefix_store.cpp"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
          "-Xcompiler", "-fvisibility=default"]

@@ -1689,6 +1689,15 @@ struct ling_b200_draft_head {
   float *x = nullptr, *logits = nullptr, *hp = nullptr, *unary = nullptr, *scores = nullptr, *scratch = nullptr;
   int* cand = nullptr;
   int max_rows = 0;
+  // the sparse head (ling_b200_draft_head_enable_sparse): the rank-256 factors, one mask per session, the selection and the
+  // compact matrix of the selected rows
+  __nv_bfloat16 *us = nullptr, *vt = nullptr;
+  uint8_t* masks = nullptr;   // [sessions][vocab]
+  float *p = nullptr, *sparse_logits = nullptr;
+  void* sel_scratch = nullptr;
+  int *rows = nullptr, *nrows = nullptr, *ids_tmp = nullptr;
+  int dynamic = 0, cap = 0;
+  Fp8Matrix compact;
 };
 
 extern "C" {
@@ -1762,6 +1771,117 @@ int ling_b200_draft_head_run(ling_b200_draft_head* h, const float* x, int E, int
   if (unary) LB_CUDA(cudaMemcpyAsync(unary, h->unary, size_t(E) * kSelTop * 4, cudaMemcpyDeviceToHost, s));
   LB_CUDA(cudaMemcpyAsync(scores, h->scores, size_t(E) * kSelTop * kSelTop * 4, cudaMemcpyDeviceToHost, s));
   return read_err(c);
+}
+
+// The sparse head (src/core/sparse_head.cu; EngineOptions::sparse_head_dynamic, src/core/engine.hpp:160-173): us [vocab][256] and
+// vt [256][hidden] are the rank-256 factors of the head (BF16); `dynamic` rows are chosen by the factors every step, `cap` bounds
+// the selection.  Every session gets an empty mask.
+int ling_b200_draft_head_enable_sparse(ling_b200_draft_head* h, const uint16_t* us_bf16, const uint16_t* vt_bf16, int dynamic, int cap) {
+  if (!h || !us_bf16 || !vt_bf16 || dynamic < 0 || cap < kSelTop || h->us) {
+    set_error("draft_head_enable_sparse: bad argument (capacity >= 16), or enabled already");
+    return LING_B200_ERR_ARG;
+  }
+  ling_b200_ctx* c = h->c;
+  LB_TRY(check_ctx(c));
+  const size_t V = size_t(c->d.V);
+  const Fp8Matrix& W = c->head;
+  LB_TRY(c->alloc(&h->us, V * kSelRank, false));
+  LB_TRY(c->alloc(&h->vt, size_t(kSelRank) * c->d.H, false));
+  LB_CUDA(cudaMemcpy(h->us, us_bf16, V * kSelRank * 2, cudaMemcpyHostToDevice));
+  LB_CUDA(cudaMemcpy(h->vt, vt_bf16, size_t(kSelRank) * c->d.H * 2, cudaMemcpyHostToDevice));
+  LB_TRY(c->alloc(&h->masks, size_t(c->opt.sessions) * V));
+  LB_TRY(c->alloc(&h->p, size_t(32) * kSelRank));
+  uint8_t* scratch = nullptr;
+  LB_TRY(c->alloc(&scratch, sparse_scratch_bytes(int(V))));
+  h->sel_scratch = scratch;
+  LB_TRY(c->alloc(&h->rows, size_t(cap)));
+  LB_TRY(c->alloc(&h->nrows, size_t(1)));
+  LB_TRY(c->alloc(&h->ids_tmp, size_t(c->d.V > 65536 ? 65536 : c->d.V)));
+  Fp8Matrix& m = h->compact;
+  m.N = cap, m.K = W.K, m.N_pad = round_up(cap, kTileN), m.K_pad = W.K_pad, m.KB = W.KB, m.splits = 1;
+  LB_TRY(c->alloc(&m.codes, size_t(m.N_pad) * m.K_pad));
+  LB_TRY(c->alloc(&m.scales, size_t(m.KB) * m.N_pad));
+  LB_TRY(make_weight_map(m));
+  LB_TRY(c->alloc(&h->sparse_logits, size_t(h->max_rows) * cap, false));
+  h->dynamic = dynamic, h->cap = cap;
+  return LING_B200_OK;
+}
+
+// A session's mask: reset = cleared, then the ids marked (the fixed list and the prompt's ids); mark = more ids (its output).
+static int mask_ids(ling_b200_draft_head* h, int session, const int* ids, int n, bool clear) {
+  if (!h || !h->us || session < 0 || session >= h->c->opt.sessions || n < 0 || (n > 0 && !ids)) {
+    set_error("draft_head_mask: bad argument, or the sparse head is not enabled");
+    return LING_B200_ERR_ARG;
+  }
+  ling_b200_ctx* c = h->c;
+  LB_TRY(check_ctx(c));
+  uint8_t* mask = h->masks + size_t(session) * c->d.V;
+  if (clear) LB_CUDA(cudaMemsetAsync(mask, 0, size_t(c->d.V), c->stream));
+  for (int done = 0; done < n; done += 65536) {
+    const int m = std::min(65536, n - done);
+    LB_CUDA(cudaMemcpyAsync(h->ids_tmp, ids + done, size_t(m) * 4, cudaMemcpyHostToDevice, c->stream));
+    LB_TRY(sparse_mark_launch(mask, h->ids_tmp, m, c->d.V, c->stream));
+    LB_CUDA(cudaStreamSynchronize(c->stream));  // ids_tmp and the caller's array are free again
+  }
+  return LING_B200_OK;
+}
+int ling_b200_draft_head_mask_reset(ling_b200_draft_head* h, int session, const int* ids, int n) { return mask_ids(h, session, ids, n, true); }
+int ling_b200_draft_head_mask_mark(ling_b200_draft_head* h, int session, const int* ids, int n) { return mask_ids(h, session, ids, n, false); }
+
+// ling_b200_draft_head_run through the sparse head for one session's rows (draft_head_rows' sparse branch,
+// src/core/sparse_head.cu:262-276): p = x . vt^T, the selection under the session's mask, the selected rows gathered and multiplied by the head
+// GEMM (their logits are the full head's bits), top 16 among them mapped back to token ids, then the selector as before.
+// *n_selected (may be NULL): how many rows were scored; selected (may be NULL): their ids, up to the capacity.
+int ling_b200_draft_head_run_sparse(ling_b200_draft_head* h, int session, const float* x, int E, int anchor, int* cand, float* unary,
+                                    float* scores, int* n_selected, int* selected) {
+  if (!h || !h->us) {
+    set_error("draft_head_run_sparse: the sparse head is not enabled");
+    return LING_B200_ERR_ARG;
+  }
+  ling_b200_ctx* c = h->c;
+  LB_TRY(check_ctx(c));
+  if (!x || !cand || !scores || E < 1 || E > h->max_rows || anchor < 0 || anchor >= c->d.V || session < 0 || session >= c->opt.sessions) {
+    set_error("draft_head_run_sparse: bad argument");
+    return LING_B200_ERR_ARG;
+  }
+  LB_TRY(finish(c));
+  cudaStream_t s = c->stream;
+  LB_CUDA(cudaMemcpyAsync(h->x, x, size_t(E) * c->d.H * 4, cudaMemcpyHostToDevice, s));
+  LB_TRY(selector_project_launch(h->x, h->vt, E, c->d.H, h->p, s));
+  SparseMasks ms;
+  ms.n = 1, ms.m[0] = h->masks + size_t(session) * c->d.V;
+  for (int i = 1; i < kSparseMasks; ++i) ms.m[i] = ms.m[0];
+  LB_TRY(sparse_select_launch(h->p, E, h->us, c->d.V, ms, h->dynamic, h->cap, h->sel_scratch, c->sm_count, h->rows, h->nrows, s));
+  const Fp8Matrix& W = c->head;
+  Fp8Matrix& m = h->compact;
+  LB_TRY(sparse_gather_launch(W.codes, W.scales, W.N_pad, W.K_pad, W.KB, h->rows, h->nrows, h->cap, m.codes, m.scales, m.N_pad, s));
+  LB_TRY(quant_acts_launch(h->x, E, c->qout(c->xq_h), s));
+  {
+    HeadEpilogue ep = c->head_ep;
+    ep.store_logits = true;
+    GemmCall g;
+    g.W = &m, g.X = &c->xq_h, g.M = E;
+    g.out = h->sparse_logits, g.ld = m.N;
+    g.split_stride = size_t(c->d.rows_alloc) * m.N_pad;
+    g.head = &ep;
+    g.impl = c->opt.gemm_impl;
+    g.err_flag = c->sb.err;
+    LB_TRY(gemm_launch(g, s));
+  }
+  LB_TRY(sparse_tail_launch(h->sparse_logits, E, h->cap, h->cap, h->nrows, s));
+  LB_TRY(topk_rows_launch(h->sparse_logits, E, h->cap, kSelTop, h->scratch, h->unary, h->cand, s));
+  LB_TRY(sparse_ids_launch(h->rows, h->nrows, h->cand, E * kSelTop, s));
+  LB_TRY(selector_project_launch(h->x, h->proj, E, c->d.H, h->hp, s));
+  LB_TRY(selector_lattice_launch(h->hp, h->cand, h->unary, h->pred, h->succ, c->d.V, anchor, nullptr, E, h->scores, c->sb.err, s));
+  LB_CUDA(cudaMemcpyAsync(cand, h->cand, size_t(E) * kSelTop * 4, cudaMemcpyDeviceToHost, s));
+  if (unary) LB_CUDA(cudaMemcpyAsync(unary, h->unary, size_t(E) * kSelTop * 4, cudaMemcpyDeviceToHost, s));
+  LB_CUDA(cudaMemcpyAsync(scores, h->scores, size_t(E) * kSelTop * kSelTop * 4, cudaMemcpyDeviceToHost, s));
+  LB_TRY(read_err(c));
+  int n = 0;
+  LB_CUDA(cudaMemcpy(&n, h->nrows, 4, cudaMemcpyDeviceToHost));
+  if (n_selected) *n_selected = n;
+  if (selected && n > 0) LB_CUDA(cudaMemcpy(selected, h->rows, size_t(n) * 4, cudaMemcpyDeviceToHost));
+  return LING_B200_OK;
 }
 
 }  // extern "C"

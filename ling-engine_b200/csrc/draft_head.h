@@ -21,4 +21,23 @@ int selector_project_launch(const float* x, const __nv_bfloat16* W, int E, int H
 int selector_lattice_launch(const float* hp, const int* cand, const float* unary, const __nv_bfloat16* P, const __nv_bfloat16* S,
                             int vocab, int anchor, const int* anchor_dev, int E, float* scores, int* err, cudaStream_t s);
 
+
+// ---- the sparse head (draft_sparse.cu)
+constexpr int kSparseMasks = 4;  // masks one selection joins (kMaxSeqs, src/core/kernels.cuh:52,300-303)
+struct SparseMasks {
+  const uint8_t* m[kSparseMasks];  // [vocab] bytes each, non-zero = the row is always scored
+  int n;
+};
+size_t sparse_scratch_bytes(int N);
+// rows [cap] = the ids every mask marks and the `dynamic` best of the others under approx[n] = max_m p[m] . us[n] (ties at the
+// threshold all taken), ascending; *nrows their count, at most cap.  p [M][256] fp32, us [N][256] BF16, 1 <= M <= 32.
+int sparse_select_launch(const float* p, int M, const __nv_bfloat16* us, int N, const SparseMasks& masks, int dynamic, int cap, void* scratch,
+                         int sm_count, int* rows, int* nrows, cudaStream_t s, bool scores_only = false);  // scores_only: the keys alone (a timing aid)
+// the selected rows' codes [cap][K_pad] and block scales [KB][cap_pad] out of an FP8 matrix (codes [N_pad][K_pad], scales [KB][N_pad])
+int sparse_gather_launch(const uint8_t* codes, const float* scales, int N_pad, int K_pad, int KB, const int* rows, const int* nrows, int cap,
+                         uint8_t* out_codes, float* out_scales, int cap_pad, cudaStream_t s);
+int sparse_tail_launch(float* logits, int E, int ld, int cap, const int* nrows, cudaStream_t s);   // columns >= *nrows := -inf
+int sparse_ids_launch(const int* rows, const int* nrows, int* ids, int n, cudaStream_t s);         // ids[i] = rows[ids[i]]
+int sparse_mark_launch(uint8_t* mask, const int* ids, int n, int vocab, cudaStream_t s);           // mask[ids[i]] = 1
+
 }  // namespace lb

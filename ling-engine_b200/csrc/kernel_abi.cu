@@ -451,6 +451,84 @@ int ling_b200_topk_rows_host(int device, const float* x, int rows, int vocab, in
   return LING_B200_OK;
 }
 
+// The sparse head's selection over host buffers (sparse_head_select, src/core/kernels.cuh:296-306): p [M][256] fp32, us [N][256]
+// BF16, n_masks masks of N bytes each (one after the other); rows [cap] and *nrows out; keys (may be NULL) [N]: the 32-bit keys
+// the selection ranks (0 = marked).
+int ling_b200_sparse_select_host(int device, const float* p, int M, const uint16_t* us_bf16, int N, const uint8_t* masks, int n_masks,
+                                 int dynamic, int cap, int* rows, int* nrows, uint32_t* keys) {
+  if (!p || !us_bf16 || !masks || !rows || !nrows || M < 1 || M > 32 || N < 1 || n_masks < 1 || n_masks > kSparseMasks || cap < 1 || dynamic < 0) {
+    set_error("sparse_select_host: bad argument (1 <= M <= 32, 1 to 4 masks)");
+    return LING_B200_ERR_ARG;
+  }
+  LB_TRY(check_device(device));
+  int sms = 148;
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+  Scratch sc;
+  float* d_p = sc.put(p, size_t(M) * kSelRank);
+  auto* d_us = reinterpret_cast<__nv_bfloat16*>(sc.put(us_bf16, size_t(N) * kSelRank));
+  uint8_t* d_m = sc.put(masks, size_t(n_masks) * N);
+  uint8_t* d_s = sc.get<uint8_t>(sparse_scratch_bytes(N));
+  int* d_rows = sc.get<int>(size_t(cap));
+  int* d_n = sc.get<int>(1);
+  LB_PTR(d_p && d_us && d_m && d_s && d_rows && d_n);
+  SparseMasks ms;
+  ms.n = n_masks;
+  for (int i = 0; i < kSparseMasks; ++i) ms.m[i] = d_m + size_t(i < n_masks ? i : 0) * N;
+  LB_TRY(sparse_select_launch(d_p, M, d_us, N, ms, dynamic, cap, d_s, sms, d_rows, d_n, 0));
+  LB_CUDA(cudaDeviceSynchronize());
+  LB_CUDA(cudaMemcpy(nrows, d_n, 4, cudaMemcpyDeviceToHost));
+  if (*nrows > 0) LB_CUDA(cudaMemcpy(rows, d_rows, size_t(*nrows) * 4, cudaMemcpyDeviceToHost));
+  if (keys) LB_CUDA(cudaMemcpy(keys, d_s, size_t(N) * 4, cudaMemcpyDeviceToHost));
+  return LING_B200_OK;
+}
+
+// Timing aid: the selection on synthetic factors resident in HBM (N rows, M step rows, 2 % of the rows marked), `iters` times
+// after a warm-up: ms[0] the scores kernel alone (it reads us once: N x 512 bytes), ms[1] the whole selection (scores, three
+// radix levels, count / scan / scatter).
+int ling_b200_sparse_select_bench(int device, int N, int M, int dynamic, int cap, int iters, float ms[2]) {
+  if (!ms || N < 1 || M < 1 || M > 32 || iters < 1 || cap < 1 || dynamic < 0) {
+    set_error("sparse_select_bench: bad argument");
+    return LING_B200_ERR_ARG;
+  }
+  LB_TRY(check_device(device));
+  int sms = 148;
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+  const size_t n_us = size_t(N) * kSelRank, n_p = size_t(M) * kSelRank, n_mask = size_t(N);
+  std::vector<uint16_t> us(n_us);
+  std::vector<float> p(n_p);
+  std::vector<uint8_t> mask(n_mask);
+  uint64_t r = 0x9E3779B97F4A7C15ull;
+  auto next = [&]() { return r = r * 6364136223846793005ull + 1442695040888963407ull; };
+  for (auto& v : us) v = uint16_t(0x3c00 + ((next() >> 40) & 0x83ff));  // BF16 values of magnitude ~0.01, both signs
+  for (auto& v : p) v = float(int((next() >> 40) & 0xffff) - 32768) / 32768.f;
+  for (auto& v : mask) v = (next() >> 40) % 50 == 0;
+  Scratch sc;
+  float* d_p = sc.put(p.data(), p.size());
+  auto* d_us = reinterpret_cast<__nv_bfloat16*>(sc.put(us.data(), us.size()));
+  uint8_t* d_m = sc.put(mask.data(), mask.size());
+  uint8_t* d_s = sc.get<uint8_t>(sparse_scratch_bytes(N));
+  int* d_rows = sc.get<int>(size_t(cap));
+  int* d_n = sc.get<int>(1);
+  LB_PTR(d_p && d_us && d_m && d_s && d_rows && d_n);
+  SparseMasks msk;
+  msk.n = 1;
+  for (int i = 0; i < kSparseMasks; ++i) msk.m[i] = d_m;
+  cudaEvent_t a, b;
+  LB_CUDA(cudaEventCreate(&a));
+  LB_CUDA(cudaEventCreate(&b));
+  for (int part = 0; part < 2; ++part) {
+    LB_TRY(sparse_select_launch(d_p, M, d_us, N, msk, dynamic, cap, d_s, sms, d_rows, d_n, 0, part == 0));
+    LB_CUDA(cudaEventRecord(a, 0));
+    for (int i = 0; i < iters; ++i) LB_TRY(sparse_select_launch(d_p, M, d_us, N, msk, dynamic, cap, d_s, sms, d_rows, d_n, 0, part == 0));
+    LB_CUDA(cudaEventRecord(b, 0));
+    LB_CUDA(cudaEventSynchronize(b));
+    LB_CUDA(cudaEventElapsedTime(&ms[part], a, b));
+    ms[part] /= iters;
+  }
+  cudaEventDestroy(a), cudaEventDestroy(b);
+  return LING_B200_OK;
+}
+
 // The candidate selector over host buffers: its projection (x [E][hidden] . W^T, W [256][hidden] BF16) when x and W are
 // given (else hp is an input), then selector_lattice (src/core/draft_kernels.cu:328-351).
 int ling_b200_selector_lattice_host(int device, const float* x, const uint16_t* proj_bf16, int hidden, float* hp, const int* cand,

@@ -156,6 +156,31 @@ def topk_rows(x, k):
     return vals, ids
 
 
+def bf16_round_np(a):
+    """fp32 -> BF16 (round to nearest even) -> fp32."""
+    u = np.ascontiguousarray(a, np.float32).view(np.uint32).astype(np.uint64)
+    return ((u + 0x7FFF + ((u >> 16) & 1)) & 0xFFFF0000).astype(np.uint32).view(np.float32)
+
+
+def sparse_select(p, us, masks, dynamic, cap):
+    """The sparse head's selection (src/core/sparse_head.cu:1-11,120-230; src/core/kernels.cuh:296-306): approx[n] = max over the
+    rows m of bf16(p[m]) . bf16(us[n]) (float64 sums here), rows = every n a mask marks plus the `dynamic` best of the others (every
+    tie at the threshold taken; if fewer unmarked rows than `dynamic` exist, none), ascending, at most cap.
+    Returns (rows, approx, marked)."""
+    pb = bf16_round_np(p).astype(np.float64)
+    ub = bf16_round_np(us).astype(np.float64)
+    approx = (ub @ pb.T).max(axis=1)
+    marked = np.zeros(us.shape[0], bool)
+    for m in np.atleast_2d(masks):
+        marked |= np.asarray(m) != 0
+    free = np.flatnonzero(~marked)
+    take = marked.copy()
+    if dynamic > 0 and len(free) >= dynamic:
+        thr = np.sort(approx[free].astype(np.float32))[-dynamic]
+        take[free[approx[free].astype(np.float32) >= thr]] = True
+    return np.flatnonzero(take)[:cap].astype(np.int32), approx, marked
+
+
 def selector_project(x, W):
     x, W = np.ascontiguousarray(x, np.float32), np.ascontiguousarray(W, np.float32)
     hp = np.zeros((x.shape[0], 256), np.float32)

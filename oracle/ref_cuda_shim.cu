@@ -70,6 +70,19 @@ int guarded(F&& body) {
 }
 }  // namespace
 
+// sparse_head.cu's draft_head_rows calls the rows-path GEMMs of stream_gemm.cu, which does not build for sm_100a; the shim
+// never calls draft_head_rows, so these only satisfy the linker.
+namespace ling::kernels {
+void to_half_rows(const float*, int, int, __half*, float*, cudaStream_t) { throw std::runtime_error("to_half_rows: not built here"); }
+void stream_gemm_nvfp4(const __half*, const float*, int, const uint8_t*, const uint8_t*, float, float*, int, int, cudaStream_t) {
+  throw std::runtime_error("stream_gemm_nvfp4: not built here");
+}
+void stream_gemm_gather_nvfp4(const __half*, const float*, int, const uint8_t*, const uint8_t*, float, const int*, const int*, int, float*, int,
+                              cudaStream_t) {
+  throw std::runtime_error("stream_gemm_gather_nvfp4: not built here");
+}
+}  // namespace ling::kernels
+
 extern "C" {
 
 const char* refcuda_last_error() { return g_err.c_str(); }
@@ -216,6 +229,25 @@ int refcuda_topk(const float* logits, int rows, int V, int K_, int* ids, float* 
     sync();
     fetch(ids, d_i, size_t(rows) * K_);
     fetch(vals, d_v, size_t(rows) * K_);
+  });
+}
+
+// sparse_head_select (src/core/sparse_head.cu:183-230): p [M][256] fp32, us [N][256] given as fp32 and rounded to BF16 here, one
+// mask of N bytes; rows [cap] (ascending ids) and their count.
+int refcuda_sparse_select(const float* p, int M, const float* us, int N, const unsigned char* mask, int dynamic, int cap, int* rows,
+                          int* nrows) {
+  return guarded([&] {
+    Dev d;
+    int* d_rows = d.get<int>(size_t(N));
+    int* d_n = d.get<int>(1);
+    K::SelMasks ms{};
+    ms.n = 1;
+    ms.m[0] = d.put(mask, size_t(N));
+    K::sparse_head_select(d.put(p, size_t(M) * 256), M, d.put_bf16(us, size_t(N) * 256), N, 256, ms, dynamic, cap,
+                          d.get<unsigned char>(K::sparse_head_scratch_bytes(N)), d_rows, d_n, 0);
+    sync();
+    fetch(nrows, d_n, 1);
+    fetch(rows, d_rows, size_t(*nrows));
   });
 }
 

@@ -186,3 +186,151 @@ def test_draft_head_on_a_context_feeds_build_tree_and_a_verify_step(gpu, lb):
     assert res[0].status == 0 and 1 <= res[0].n_path <= tree["rows"]
     head.close()
     ctx.close()
+
+
+# ---------------------------------------------------------------------------------------------- the sparse head
+def key_to_float(keys):
+    """The selection's order-preserving keys back to the fp32 scores (0 = marked: NaN here)."""
+    k = keys.astype(np.uint32)
+    bits = np.where(k & 0x80000000, k & 0x7FFFFFFF, ~k).astype(np.uint32)
+    out = bits.view(np.float32).copy()
+    out[k == 0] = np.nan
+    return out
+
+
+def sparse_case(rng, N, M, marked_share=0.02):
+    p = (rng.standard_normal((M, 256)) * 0.7).astype(np.float32)
+    us = (rng.standard_normal((N, 256)) * 0.1).astype(np.float32)
+    mask = (rng.random(N) < marked_share).astype(np.uint8)
+    return p, us, mask
+
+
+def test_sparse_select_oracle_on_a_hand_case():
+    # four rows of us against one row of p: scores 3, 1, 2, -1; row 3 is marked; the best one of the others is row 0
+    p = np.zeros((1, 256), np.float32)
+    p[0, 0] = 1.0
+    us = np.zeros((4, 256), np.float32)
+    us[:, 0] = [3, 1, 2, -1]
+    mask = np.array([0, 0, 0, 1], np.uint8)
+    rows, approx, marked = lo.sparse_select(p, us, mask, 1, 8)
+    assert list(rows) == [0, 3] and list(approx) == [3, 1, 2, -1] and list(marked) == [False, False, False, True]
+    assert list(lo.sparse_select(p, us, mask, 2, 8)[0]) == [0, 2, 3]
+    assert list(lo.sparse_select(p, us, mask, 3, 8)[0]) == [0, 1, 2, 3]
+    assert list(lo.sparse_select(p, us, mask, 4, 8)[0]) == [3]          # fewer unmarked rows than asked for: none of them
+    assert list(lo.sparse_select(p, us, mask, 3, 2)[0]) == [0, 1]       # the capacity cuts the id-ordered list
+    us[1, 0] = 2                                                        # a tie at the threshold: both taken
+    assert list(lo.sparse_select(p, us, mask, 2, 8)[0]) == [0, 1, 2, 3]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("N,M,dynamic,cap", [(5000, 1, 300, 4096), (40000, 7, 2048, 8192), (248320, 15, 16384, 32768), (248320, 31, 16384, 20000),
+                                             (3000, 9, 2990, 4096), (3000, 9, 0, 4096)])
+def test_sparse_select_matches_oracle(gpu, lb, N, M, dynamic, cap):
+    rng = np.random.default_rng(N + M)
+    p, us, mask = sparse_case(rng, N, M)
+    rows, keys = lb.sparse_select(p, lb.to_bf16_bits(us), mask, dynamic, cap)
+    want, approx, marked = lo.sparse_select(p, us, mask, dynamic, cap)
+    # the scores: BF16 products, fp32 sums in the tensor core against float64 sums
+    got = key_to_float(keys)
+    assert np.array_equal(np.isnan(got), marked)
+    free = ~marked
+    assert np.abs(got[free] - approx[free]).max() <= 2e-6 * float(np.abs(approx).max()) + 1e-6
+    # the selection, exactly, on the keys the device ranked: the marked rows and every key at or above the dynamic-th largest
+    take = marked.copy()
+    fk = keys[free]
+    if dynamic > 0 and free.sum() >= dynamic:
+        take[np.flatnonzero(free)[fk >= np.sort(fk)[-dynamic]]] = True
+    assert np.array_equal(rows, np.flatnonzero(take)[:cap])
+    # and against the oracle's own selection: the same rows but for scores within the summation error of the threshold
+    if dynamic > 0 and free.sum() >= dynamic:
+        thr = np.sort(approx[free])[-dynamic]
+        band = np.abs(approx - thr) <= 4e-6 * float(np.abs(approx).max())
+        diff = np.setxor1d(rows, want) if len(rows) < cap and len(want) < cap else np.array([], np.int64)
+        assert band[diff].all()
+    else:
+        assert np.array_equal(rows, want)
+
+
+@pytest.mark.gpu
+def test_sparse_select_matches_the_reference_kernel(gpu, lb):
+    R = lo.refcuda()
+    if R is None or not hasattr(R, "refcuda_sparse_select"):
+        pytest.skip("the reference's CUDA kernels are not built here")
+    f = lambda a: a.ctypes.data_as(C.POINTER(C.c_float))
+    for N, M, dynamic, cap in [(40000, 7, 2048, 8192), (248320, 15, 16384, 32768), (3000, 9, 2990, 4096)]:
+        rng = np.random.default_rng(N + M)
+        p, us, mask = sparse_case(rng, N, M)
+        rows, keys = lb.sparse_select(p, lb.to_bf16_bits(us), mask, dynamic, cap)
+        ref, n = np.zeros(N, np.int32), C.c_int(0)
+        assert R.refcuda_sparse_select(f(p), M, f(us), N, mask.ctypes.data_as(C.POINTER(C.c_ubyte)), dynamic, cap,
+                                       ref.ctypes.data_as(C.POINTER(C.c_int)), C.byref(n)) == 0
+        ref = ref[:n.value]
+        # both sum the rank in a permuted order on the tensor core; a row within that error of the threshold may fall either way
+        _, approx, marked = lo.sparse_select(p, us, mask, dynamic, cap)
+        free = ~marked
+        if free.sum() >= dynamic:
+            thr = np.sort(approx[free])[-dynamic]
+            band = np.abs(approx - thr) <= 4e-6 * float(np.abs(approx).max())
+            assert band[np.setxor1d(rows, ref)].all(), (N, len(rows), len(ref))
+        else:
+            assert np.array_equal(rows, ref)
+
+
+@pytest.mark.gpu
+def test_sparse_draft_head_scores_the_full_heads_bits(gpu, lb):
+    """The sparse head on a context: the rows it scores are the session's mask plus the factors' choice; the logits of its 16
+    candidates are bit for bit the full head's, and where the full head's top 16 lie inside the selection the candidates are
+    the same."""
+    cfg = lb.toy_config()
+    rng = np.random.default_rng(14)
+    V, H, E = cfg.vocab, cfg.hidden, 7
+    ctx = lb.Context(cfg, sessions=2, max_context=256, page_tokens=16, pool_pages=17, max_seqs=1, max_rows=32)
+    ctx.synth_weights(0)
+    # a head with a low-rank part that the factors reproduce, plus noise they do not
+    A, B = (rng.standard_normal((V, 256)) * 0.05).astype(np.float32), (rng.standard_normal((256, H)) * 0.3).astype(np.float32)
+    head_w = (A @ B + rng.standard_normal((V, H)) * 0.01).astype(np.float32)
+    ctx.set_tensor(-1, lb.T_LM_HEAD, head_w)
+    W = (rng.standard_normal((256, H)) * 0.05).astype(np.float32)
+    P = (rng.standard_normal((V, 256)) * 0.2).astype(np.float32)
+    S = (rng.standard_normal((V, 256)) * 0.2).astype(np.float32)
+    head = lb.DraftHead(ctx, lb.to_bf16_bits(W), lb.to_bf16_bits(P), lb.to_bf16_bits(S))
+    dynamic, cap = 512, 1024
+    head.enable_sparse(lb.to_bf16_bits(A), lb.to_bf16_bits(B), dynamic, cap)
+    fixed = rng.choice(V, 200, replace=False).astype(np.int32)
+    head.mask_reset(1, fixed)
+    head.mask_mark(1, np.array([3, 5, 7], np.int32))
+    x = rng.standard_normal((E, H)).astype(np.float32)
+    anchor = 77
+    full_c, full_u, full_s = head.run(x, anchor)
+    cand, unary, scores, sel = head.run_sparse(1, x, anchor)
+    marked = np.zeros(V, np.uint8)
+    marked[fixed] = 1
+    marked[[3, 5, 7]] = 1
+    # the rows scored: the kernel-level selection on p = x . B^T (the projection kernel's own output differs from numpy's in
+    # the last bits, so rows within that error of the threshold may differ: the band of the oracle test)
+    want, approx, _ = lo.sparse_select(lo.selector_project(x, B), A, marked, dynamic, cap)
+    assert set(np.flatnonzero(marked)) <= set(sel) and np.all(np.diff(sel) > 0) and len(sel) <= cap
+    free = marked == 0
+    thr = np.sort(approx[free])[-dynamic]
+    band = np.abs(approx - thr) <= 1e-4 * float(np.abs(approx).max())
+    assert band[np.setxor1d(sel, want)].all()
+    # every candidate is a scored row, and its logit is the full head's bits for that row
+    full_logits = np.full((E, V), np.nan, np.float32)
+    for e in range(E):
+        full_logits[e, full_c[e]] = full_u[e]
+        assert set(cand[e]) <= set(sel)
+        both = np.intersect1d(cand[e], full_c[e])
+        assert len(both) > 0
+        for t in both:
+            assert unary[e][list(cand[e]).index(t)] == full_u[e][list(full_c[e]).index(t)]
+        if set(full_c[e]) <= set(sel):      # the full head's top 16 all inside the selection: the same list, the same scores
+            assert np.array_equal(cand[e], full_c[e]) and np.array_equal(unary[e], full_u[e])
+            assert np.array_equal(scores[e], full_s[e]) or e == 0 or not set(full_c[e - 1]) <= set(sel)
+    inside = sum(set(full_c[e]) <= set(sel) for e in range(E))
+    print("sparse head: %d rows scored of %d; the full head's top 16 inside the selection for %d of %d positions" % (len(sel), V, inside, E))
+    assert inside >= 1
+    # another session's mask is its own (empty): only the dynamic rows
+    _, _, _, sel0 = head.run_sparse(0, x, anchor)
+    assert abs(len(sel0) - dynamic) <= 2 and not set(np.flatnonzero(marked)) <= set(sel0)
+    head.close()
+    ctx.close()
