@@ -1851,7 +1851,7 @@ int ling_b200_draft_head_run_sparse(ling_b200_draft_head* h, int session, const 
   SparseMasks ms;
   ms.n = 1, ms.m[0] = h->masks + size_t(session) * c->d.V;
   for (int i = 1; i < kSparseMasks; ++i) ms.m[i] = ms.m[0];
-  LB_TRY(sparse_select_launch(h->p, E, h->us, c->d.V, ms, h->dynamic, h->cap, h->sel_scratch, c->sm_count, h->rows, h->nrows, s));
+  LB_TRY(sparse_select_launch(h->p, E, h->us, c->d.V, ms, h->dynamic, h->cap, h->sel_scratch, c->sm_count, h->rows, h->nrows, c->sb.err, s));
   const Fp8Matrix& W = c->head;
   Fp8Matrix& m = h->compact;
   LB_TRY(sparse_gather_launch(W.codes, W.scales, W.N_pad, W.K_pad, W.KB, h->rows, h->nrows, h->cap, m.codes, m.scales, m.N_pad, s));

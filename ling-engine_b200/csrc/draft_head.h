@@ -30,9 +30,10 @@ struct SparseMasks {
 };
 size_t sparse_scratch_bytes(int N);
 // rows [cap] = the ids every mask marks and the `dynamic` best of the others under approx[n] = max_m p[m] . us[n] (ties at the
-// threshold all taken), ascending; *nrows their count, at most cap.  p [M][256] fp32, us [N][256] BF16, 1 <= M <= 32.
+// threshold all taken), ascending; *nrows their count, at most cap.  p [M][256] fp32, us [N][256] BF16 (16-byte aligned), 1 <= M <= 32.
+// err: the device error word a bounded wait that runs out records its code in (may be null).
 int sparse_select_launch(const float* p, int M, const __nv_bfloat16* us, int N, const SparseMasks& masks, int dynamic, int cap, void* scratch,
-                         int sm_count, int* rows, int* nrows, cudaStream_t s, bool scores_only = false);  // scores_only: the keys alone (a timing aid)
+                         int sm_count, int* rows, int* nrows, int* err, cudaStream_t s, bool scores_only = false);  // scores_only: the keys alone (a timing aid)
 // the selected rows' codes [cap][K_pad] and block scales [KB][cap_pad] out of an FP8 matrix (codes [N_pad][K_pad], scales [KB][N_pad])
 int sparse_gather_launch(const uint8_t* codes, const float* scales, int N_pad, int K_pad, int KB, const int* rows, const int* nrows, int cap,
                          uint8_t* out_codes, float* out_scales, int cap_pad, cudaStream_t s);

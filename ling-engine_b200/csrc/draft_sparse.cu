@@ -7,8 +7,8 @@
 // selector_project kernel), us [vocab][256] BF16.  The selected rows, in id order, are gathered into a compact FP8
 // matrix which the head GEMM then multiplies like any other: a selected row's logit is the full head's, bit for bit.
 //
-//   sparse_scores_kernel   HBM-bound: reads us once (vocab x 512 bytes); BF16 mma.sync m16n8k16 with the K index permuted so
-//                          that a lane's fragments are 16-byte loads; writes an order-preserving 32-bit key per row, 0 = marked
+//   sparse_scores_kernel   HBM-bound: reads us once (vocab x 512 bytes) through a cp.async ring in shared memory; BF16 mma.sync
+//                          m16n8k16 with ldmatrix fragments; writes an order-preserving 32-bit key per row, 0 = marked
 //   sparse_level_kernel    radix select of the `dynamic`-th largest key, 11 + 11 + 10 bits: per level one histogram launch whose
 //                          last block (a ticket) finds the bin the threshold falls in
 //   sparse_count / _scan / _scatter   the ids of (marked or key >= threshold) in ascending order, at most `cap`
@@ -16,9 +16,11 @@
 #include <cfloat>
 
 #include "draft_head.h"
+#include "tc.cuh"
 
 namespace lb {
 namespace {
+using tc::smem_u32;
 
 constexpr int kRank = kSelRank;
 constexpr int kBins = 2048;
@@ -40,49 +42,101 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint3
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// keys[n] = marked ? 0 : order_key(max_m p[m] . us[n]).  A warp takes 16 rows of us at a time as the MMA's A tile and the
-// step's rows (BF16, in shared memory) as B, eight rows per MMA column tile.  The sum over the rank runs in a permuted
-// order: lane (g, t) of the fragment layout supplies, at k-step s, the rank indices 64 t + 4 s .. + 3 of rows g and g + 8 --
-// a lane's 64 values of a row are then four 16-byte loads per half row, and B's matching four values are 8 contiguous bytes.
+// keys[n] = marked ? 0 : order_key(max_m p[m] . us[n]).  One block per SM streams its share of us through a three-stage ring
+// in shared memory, 128 rows (64 KB) a stage, by bulk copies (cp.async.bulk, one 512-byte row each, no multicast) that complete
+// on the stage's mbarrier; warp w of the block then owns rows 16 w .. 16 w + 15 of the stage: A fragments by ldmatrix.x4 (rows
+// padded to 528 bytes, so the eight rows of a matrix fall in different banks), the step's rows (BF16, converted once) as the B
+// operand by ldmatrix as well, sixteen k-steps of mma.sync m16n8k16 a column tile.  Every wait is bounded: one that runs out
+// records a code in the error word, and the block makes no further waits and writes no further keys.
+// (Earlier forms: fragments loaded straight from global memory, a lane per 128-byte quarter of a row -- 32 lines an
+// instruction, load-unit bound at a third of the copy bandwidth; the same ring filled by 16-byte cp.async -- 0.44: the copies
+// a block can have in flight through L1 did not cover the latency.)
+constexpr int kScoreRows = 128, kScoreStages = 3, kScoreLd = kRank + 8;  // halves per padded row
 template <int NT>
-__global__ void __launch_bounds__(256) sparse_scores_kernel(const float* __restrict__ p, int M, const __nv_bfloat16* __restrict__ us,
-                                                            int N, SparseMasks masks, uint32_t* __restrict__ keys) {
+constexpr size_t score_smem() { return size_t(kScoreStages * kScoreRows + NT * 8) * kScoreLd * 2; }
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldsm_x2(uint32_t (&r)[2], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(smem_u32(p)));
+}
+template <int NT>
+__global__ void __launch_bounds__(256, 1) sparse_scores_kernel(const float* __restrict__ p, int M, const __nv_bfloat16* __restrict__ us,
+                                                               int N, SparseMasks masks, uint32_t* __restrict__ keys, int* err) {
   pdl_sync();  // first statement: see common.cuh
-  constexpr int LD = kRank + 8;  // padded: the eight rows g of a B fragment read fall in different banks
-  __shared__ __align__(16) __nv_bfloat16 ps[NT * 8 * LD];
-  for (int i = threadIdx.x; i < NT * 8 * kRank; i += blockDim.x) {
-    const int m = i / kRank, r = i % kRank;
-    ps[m * LD + r] = __float2bfloat16(m < M ? p[size_t(m) * kRank + r] : 0.f);
+  extern __shared__ __align__(16) uint8_t score_raw[];
+  __shared__ __align__(8) uint64_t full[kScoreStages];
+  __shared__ volatile int failed;
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kScoreStages; ++i) tc::mbar_init(&full[i], 1);
+    failed = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
-  const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-  const int n_warps = gridDim.x * (blockDim.x >> 5), warp = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  for (int n0 = warp * 16; n0 < N; n0 += n_warps * 16) {
-    uint4 lo[8], hi[8];  // rows n0 + g and n0 + g + 8: rank indices 64 t .. 64 t + 63
-    {
-      const uint4* a = reinterpret_cast<const uint4*>(us + size_t(min(n0 + g, N - 1)) * kRank + t * 64);
-      const uint4* b = reinterpret_cast<const uint4*>(us + size_t(min(n0 + g + 8, N - 1)) * kRank + t * 64);
-#pragma unroll
-      for (int q = 0; q < 8; ++q) lo[q] = __ldg(a + q), hi[q] = __ldg(b + q);
+  __nv_bfloat16* ring = reinterpret_cast<__nv_bfloat16*>(score_raw);          // [stages][128][264]
+  __nv_bfloat16* ps = ring + size_t(kScoreStages) * kScoreRows * kScoreLd;    // [NT * 8][264]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+  const int tiles = (N + kScoreRows - 1) / kScoreRows;
+  const int mine = blockIdx.x < tiles ? (tiles - 1 - int(blockIdx.x)) / int(gridDim.x) + 1 : 0;  // tiles blockIdx.x, + gridDim.x, ...
+  // stage i % 3 of the ring <- this block's i-th tile: thread r < 128 copies row r; rows past N are not copied (their
+  // products are computed on what the stage held and never written)
+  auto send = [&](int i) {
+    if (i >= mine || failed) return;
+    const int row0 = (int(blockIdx.x) + i * int(gridDim.x)) * kScoreRows;
+    const int rows_in = min(kScoreRows, N - row0);
+    uint64_t* bar = &full[i % kScoreStages];
+    if (threadIdx.x == 0) tc::mbar_expect_tx(bar, uint32_t(rows_in) * kRank * 2);
+    if (int(threadIdx.x) < rows_in) {
+      __nv_bfloat16* dst = ring + (size_t(i % kScoreStages) * kScoreRows + threadIdx.x) * kScoreLd;
+      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)),
+                   "l"(us + size_t(row0 + threadIdx.x) * kRank), "r"(kRank * 2), "r"(smem_u32(bar))
+                   : "memory");
     }
-    // the two rows' mask bytes travel with the rows (lanes t = 0 write the keys): asked for now, needed after the products
+  };
+  send(0), send(1);
+  for (int i = threadIdx.x; i < NT * 8 * kRank; i += blockDim.x) {
+    const int m = i / kRank, r = i % kRank;
+    ps[m * kScoreLd + r] = __float2bfloat16(m < M ? p[size_t(m) * kRank + r] : 0.f);
+  }
+  for (int i = 0; i < mine; ++i) {
+    send(i + 2);  // into the stage that iteration i - 1 read: every warp is past it (the barrier that ended that iteration)
+    if (i == 0) __syncthreads();  // ps is written
+    if (!failed && !tc::mbar_wait(&full[i % kScoreStages], uint32_t(i / kScoreStages) & 1u, &failed)) {
+      dev_fail(err, kDevWaitFull);
+      failed = 1;
+    }
+    if (failed) {  // block-uniform once the barrier below has been passed; until then a thread that saw it only skips work
+      __syncthreads();
+      continue;
+    }
+    const int row0 = (int(blockIdx.x) + i * int(gridDim.x)) * kScoreRows + warp * 16;
+    // lanes t = 0 write the keys of rows g and g + 8: their mask bytes are asked for now, needed after the products
     bool m0 = false, m1 = false;
     if (t == 0) {
-      if (n0 + g < N) m0 = any_mask(masks, n0 + g);
-      if (n0 + g + 8 < N) m1 = any_mask(masks, n0 + g + 8);
+      if (row0 + g < N) m0 = any_mask(masks, row0 + g);
+      if (row0 + g + 8 < N) m1 = any_mask(masks, row0 + g + 8);
     }
+    const __nv_bfloat16* tile = ring + (size_t(i % kScoreStages) * kScoreRows + warp * 16) * kScoreLd;
     float acc[NT][4];
 #pragma unroll
     for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+#pragma unroll 4
+    for (int ks = 0; ks < kRank / 16; ++ks) {
+      // A: rows 0-15 x k 16 ks .. + 15 as four 8 x 8 matrices (rows 0-7 / 8-15, k low / high): lane l addresses row l % 16, k half l / 16
+      uint32_t a[4];
+      ldsm_x4(a, tile + size_t(lane & 15) * kScoreLd + ks * 16 + (lane >> 4) * 8);
+      if constexpr (NT == 1) {
+        uint32_t b[2];  // step rows 0-7: k low / high; lanes 0-15 give the addresses
+        ldsm_x2(b, ps + size_t(lane & 7) * kScoreLd + ks * 16 + ((lane >> 3) & 1) * 8);
+        mma_bf16_16816(acc[0], a[0], a[1], a[2], a[3], b[0], b[1]);
+      } else {
 #pragma unroll
-    for (int s = 0; s < 16; ++s) {
-      const uint4 &x = lo[s >> 1], &y = hi[s >> 1];
-      const uint32_t a0 = (s & 1) ? x.z : x.x, a2 = (s & 1) ? x.w : x.y;
-      const uint32_t a1 = (s & 1) ? y.z : y.x, a3 = (s & 1) ? y.w : y.y;
-#pragma unroll
-      for (int j = 0; j < NT; ++j) {
-        const uint2 b = *reinterpret_cast<const uint2*>(ps + (j * 8 + g) * LD + t * 64 + 4 * s);
-        mma_bf16_16816(acc[j], a0, a1, a2, a3, b.x, b.y);
+        for (int j = 0; j < NT; j += 2) {
+          uint32_t b[4];  // step rows 8 j .. 8 j + 15: (rows low, k low), (rows low, k high), (rows high, k low), (rows high, k high)
+          ldsm_x4(b, ps + size_t(j * 8 + (lane & 7) + ((lane >> 4) & 1) * 8) * kScoreLd + ks * 16 + ((lane >> 3) & 1) * 8);
+          mma_bf16_16816(acc[j], a[0], a[1], a[2], a[3], b[0], b[1]);
+          mma_bf16_16816(acc[j + 1], a[0], a[1], a[2], a[3], b[2], b[3]);
+        }
       }
     }
     // acc[j][e]: us row g (e = 0, 1) / g + 8 (e = 2, 3) against the step's row 8 j + 2 t + (e & 1)
@@ -95,9 +149,10 @@ __global__ void __launch_bounds__(256) sparse_scores_kernel(const float* __restr
     top0 = fmaxf(top0, __shfl_xor_sync(0xffffffffu, top0, 1)), top0 = fmaxf(top0, __shfl_xor_sync(0xffffffffu, top0, 2));
     top1 = fmaxf(top1, __shfl_xor_sync(0xffffffffu, top1, 1)), top1 = fmaxf(top1, __shfl_xor_sync(0xffffffffu, top1, 2));
     if (t == 0) {
-      if (n0 + g < N) keys[n0 + g] = m0 ? 0u : order_key(top0);
-      if (n0 + g + 8 < N) keys[n0 + g + 8] = m1 ? 0u : order_key(top1);
+      if (row0 + g < N) keys[row0 + g] = m0 ? 0u : order_key(top0);
+      if (row0 + g + 8 < N) keys[row0 + g + 8] = m1 ? 0u : order_key(top1);
     }
+    __syncthreads();  // every warp is done with the stage before iteration i + 1 sends tile i + 3 into it
   }
 }
 
@@ -275,7 +330,7 @@ size_t sparse_scratch_bytes(int N) {
 }
 
 int sparse_select_launch(const float* p, int M, const __nv_bfloat16* us, int N, const SparseMasks& masks, int dynamic, int cap, void* scratch,
-                         int sm_count, int* rows, int* nrows, cudaStream_t s, bool scores_only) {
+                         int sm_count, int* rows, int* nrows, int* err, cudaStream_t s, bool scores_only) {
   if (M < 1 || M > 32 || N < 1 || masks.n < 1 || masks.n > kSparseMasks || dynamic < 0 || cap < 1) {
     set_error("sparse_select: 1 to 32 rows, 1 to 4 masks, a positive capacity");
     return LING_B200_ERR_ARG;
@@ -287,10 +342,17 @@ int sparse_select_launch(const float* p, int M, const __nv_bfloat16* us, int N, 
   int* counts = reinterpret_cast<int*>(hist + 3 * kBins);
   const int blocks = (N + 1023) / 1024;
   LB_CUDA(cudaMemsetAsync(state, 0, (16 + 3 * size_t(kBins)) * 4, s));
-  const dim3 grid(sm_count * 2);
-  if (M <= 8) LB_CUDA(launch_kernel(sparse_scores_kernel<1>, grid, dim3(256), size_t(0), s, p, M, us, N, masks, keys));
-  else if (M <= 16) LB_CUDA(launch_kernel(sparse_scores_kernel<2>, grid, dim3(256), size_t(0), s, p, M, us, N, masks, keys));
-  else LB_CUDA(launch_kernel(sparse_scores_kernel<4>, grid, dim3(256), size_t(0), s, p, M, us, N, masks, keys));
+  static bool attr_set = false;
+  if (!attr_set) {
+    LB_CUDA(cudaFuncSetAttribute(sparse_scores_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(score_smem<1>())));
+    LB_CUDA(cudaFuncSetAttribute(sparse_scores_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(score_smem<2>())));
+    LB_CUDA(cudaFuncSetAttribute(sparse_scores_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(score_smem<4>())));
+    attr_set = true;
+  }
+  const dim3 grid(sm_count);
+  if (M <= 8) LB_CUDA(launch_kernel(sparse_scores_kernel<1>, grid, dim3(256), score_smem<1>(), s, p, M, us, N, masks, keys, err));
+  else if (M <= 16) LB_CUDA(launch_kernel(sparse_scores_kernel<2>, grid, dim3(256), score_smem<2>(), s, p, M, us, N, masks, keys, err));
+  else LB_CUDA(launch_kernel(sparse_scores_kernel<4>, grid, dim3(256), score_smem<4>(), s, p, M, us, N, masks, keys, err));
   LB_LAUNCH("sparse_scores_kernel");
   if (scores_only) return LING_B200_OK;
   for (int level = 0; level < 3; ++level) {

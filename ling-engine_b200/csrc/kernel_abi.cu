@@ -474,8 +474,18 @@ int ling_b200_sparse_select_host(int device, const float* p, int M, const uint16
   SparseMasks ms;
   ms.n = n_masks;
   for (int i = 0; i < kSparseMasks; ++i) ms.m[i] = d_m + size_t(i < n_masks ? i : 0) * N;
-  LB_TRY(sparse_select_launch(d_p, M, d_us, N, ms, dynamic, cap, d_s, sms, d_rows, d_n, 0));
+  int* d_err = sc.get<int>(1);
+  LB_PTR(d_err);
+  LB_TRY(sparse_select_launch(d_p, M, d_us, N, ms, dynamic, cap, d_s, sms, d_rows, d_n, d_err, 0));
   LB_CUDA(cudaDeviceSynchronize());
+  {
+    int code = 0;
+    LB_CUDA(cudaMemcpy(&code, d_err, 4, cudaMemcpyDeviceToHost));
+    if (code) {
+      set_error("sparse_select: device error word = " + std::to_string(code));
+      return LING_B200_ERR_DEVICE_FLAG;
+    }
+  }
   LB_CUDA(cudaMemcpy(nrows, d_n, 4, cudaMemcpyDeviceToHost));
   if (*nrows > 0) LB_CUDA(cudaMemcpy(rows, d_rows, size_t(*nrows) * 4, cudaMemcpyDeviceToHost));
   if (keys) LB_CUDA(cudaMemcpy(keys, d_s, size_t(N) * 4, cudaMemcpyDeviceToHost));
@@ -517,9 +527,9 @@ int ling_b200_sparse_select_bench(int device, int N, int M, int dynamic, int cap
   LB_CUDA(cudaEventCreate(&a));
   LB_CUDA(cudaEventCreate(&b));
   for (int part = 0; part < 2; ++part) {
-    LB_TRY(sparse_select_launch(d_p, M, d_us, N, msk, dynamic, cap, d_s, sms, d_rows, d_n, 0, part == 0));
+    LB_TRY(sparse_select_launch(d_p, M, d_us, N, msk, dynamic, cap, d_s, sms, d_rows, d_n, nullptr, 0, part == 0));
     LB_CUDA(cudaEventRecord(a, 0));
-    for (int i = 0; i < iters; ++i) LB_TRY(sparse_select_launch(d_p, M, d_us, N, msk, dynamic, cap, d_s, sms, d_rows, d_n, 0, part == 0));
+    for (int i = 0; i < iters; ++i) LB_TRY(sparse_select_launch(d_p, M, d_us, N, msk, dynamic, cap, d_s, sms, d_rows, d_n, nullptr, 0, part == 0));
     LB_CUDA(cudaEventRecord(b, 0));
     LB_CUDA(cudaEventSynchronize(b));
     LB_CUDA(cudaEventElapsedTime(&ms[part], a, b));
