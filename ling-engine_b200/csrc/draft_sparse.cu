@@ -43,7 +43,7 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint3
 }
 
 // keys[n] = marked ? 0 : order_key(max_m p[m] . us[n]).  One block per SM streams its share of us through a three-stage ring
-// in shared memory, 128 rows (64 KB) a stage, by bulk copies (cp.async.bulk, one 512-byte row each, no multicast) that complete
+// in shared memory, 128 rows (64 KB) a stage, by plain bulk copies (one 512-byte row each, this CTA's shared memory only) that complete
 // on the stage's mbarrier; warp w of the block then owns rows 16 w .. 16 w + 15 of the stage: A fragments by ldmatrix.x4 (rows
 // padded to 528 bytes, so the eight rows of a matrix fall in different banks), the step's rows (BF16, converted once) as the B
 // operand by ldmatrix as well, sixteen k-steps of mma.sync m16n8k16 a column tile.  Every wait is bounded: one that runs out
