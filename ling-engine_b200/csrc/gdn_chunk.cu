@@ -218,14 +218,17 @@ __global__ void __launch_bounds__(kPrepThreads)
   if (tid < kT) out->gam[tid] = sm.gam[tid];
 }
 
-// The state-dependent half, one CTA of 16 warps per value head walking the chunks in order: Delta = U - W S0, O = diag(gamma) Q S0 +
-// P Delta, S = gamma_T S0 + K'^T Delta.  The records arrive by cp.async three chunks ahead; two barriers per chunk.
+// The state-dependent half, per value head walking the chunks in order: Delta = U - W S0, O = diag(gamma) Q S0 + P Delta,
+// S = gamma_T S0 + K'^T Delta.  Every value column is independent of the others, so a head's 128 columns are split over
+// gridDim.y CTAs (blockDim.x / 32 warps of 8 columns each): 48 heads alone leave two thirds of the SMs idle, and a chunk's
+// time is mostly its mma.sync instructions.  The records arrive by cp.async three chunks ahead; two barriers per chunk.
 __global__ void __launch_bounds__(kThreads, 1)
     gdn_chunk_apply_kernel(const ChunkRecord* __restrict__ records, int M, int HV, float* __restrict__ state, float* __restrict__ core) {
   pdl_sync();  // first statement: see common.cuh
   extern __shared__ __align__(16) unsigned char raw_smem[];
   ApplySmem& sm = *reinterpret_cast<ApplySmem*>(raw_smem);
-  const int hv = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int hv = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, threads = blockDim.x;
+  const int col0 = int(blockIdx.y) * (threads >> 5) * 8;  // this CTA's first value column of the head
   const int gq = lane >> 2, tq = lane & 3;
   const int n_chunks = (M + kT - 1) / kT;
   float* st = state + size_t(hv) * kD * kD;
@@ -234,7 +237,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   float S[8][4];
 #pragma unroll
   for (int mt = 0; mt < 8; ++mt) {
-    const int d = mt * 16 + gq, c = warp * 8 + 2 * tq;
+    const int d = mt * 16 + gq, c = col0 + warp * 8 + 2 * tq;
     const float2 lo = *reinterpret_cast<const float2*>(st + size_t(d) * kD + c);
     const float2 hi = *reinterpret_cast<const float2*>(st + size_t(d + 8) * kD + c);
     S[mt][0] = lo.x, S[mt][1] = lo.y, S[mt][2] = hi.x, S[mt][3] = hi.y;
@@ -252,7 +255,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (chunk < n_chunks) {
       const char* src = reinterpret_cast<const char*>(records + size_t(chunk) * HV + hv);
       char* dst = reinterpret_cast<char*>(&sm.rec[chunk % kStages]);
-      for (int idx = tid; idx < int(sizeof(ChunkRecord) / 16); idx += kThreads) copy16(dst + idx * 16, src + idx * 16, true);
+      for (int idx = tid; idx < int(sizeof(ChunkRecord) / 16); idx += threads) copy16(dst + idx * 16, src + idx * 16, true);
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
@@ -272,8 +275,8 @@ __global__ void __launch_bounds__(kThreads, 1)
       tiles_mma<2, kD>(ws, r.t.w, kLdD, 0, sm.sT, kLdD, warp * 8, lane);
 #pragma unroll
       for (int mt = 0; mt < 2; ++mt) {
-        const int i = mt * 16 + gq, c = warp * 8 + 2 * tq;
-        const float2 ua = *reinterpret_cast<const float2*>(r.u + i * kD + c), ub = *reinterpret_cast<const float2*>(r.u + (i + 8) * kD + c);
+        const int i = mt * 16 + gq, c = warp * 8 + 2 * tq;  // (column inside the CTA: the shared-memory tiles hold the CTA's columns)
+        const float2 ua = *reinterpret_cast<const float2*>(r.u + i * kD + col0 + c), ub = *reinterpret_cast<const float2*>(r.u + (i + 8) * kD + col0 + c);
         sm.dT[c * kLdT + i] = __float2half_rn(ua.x - ws[mt][0]), sm.dT[(c + 1) * kLdT + i] = __float2half_rn(ua.y - ws[mt][1]);
         sm.dT[c * kLdT + i + 8] = __float2half_rn(ub.x - ws[mt][2]), sm.dT[(c + 1) * kLdT + i + 8] = __float2half_rn(ub.y - ws[mt][3]);
       }
@@ -285,7 +288,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       tiles_mma<2, kT>(pd, r.t.p, kLdT, 0, sm.dT, kLdT, warp * 8, lane);
 #pragma unroll
       for (int mt = 0; mt < 2; ++mt) {
-        const int i = mt * 16 + gq, c = warp * 8 + 2 * tq;
+        const int i = mt * 16 + gq, c = col0 + warp * 8 + 2 * tq;
         if (i < n)
           *reinterpret_cast<float2*>(core + size_t(c0 + i) * HV * kD + size_t(hv) * kD + c) =
               make_float2(fmaf(r.gam[i], qs[mt][0], pd[mt][0]), fmaf(r.gam[i], qs[mt][1], pd[mt][1]));
@@ -308,7 +311,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   asm volatile("cp.async.wait_all;" ::: "memory");
 #pragma unroll
   for (int mt = 0; mt < 8; ++mt) {
-    const int d = mt * 16 + gq, c = warp * 8 + 2 * tq;
+    const int d = mt * 16 + gq, c = col0 + warp * 8 + 2 * tq;
     *reinterpret_cast<float2*>(st + size_t(d) * kD + c) = make_float2(S[mt][0], S[mt][1]);
     *reinterpret_cast<float2*>(st + size_t(d + 8) * kD + c) = make_float2(S[mt][2], S[mt][3]);
   }
@@ -384,7 +387,10 @@ int gdn_chunk_launch(const float* post, const float* g, const float* beta, int M
   ChunkRecord* rec = static_cast<ChunkRecord*>(scratch);
   LB_CUDA(launch_kernel(gdn_chunk_prepare_kernel, dim3(ceil_div(M, kT), HV), dim3(kPrepThreads), sizeof(PrepSmem), s, post, g, beta, M, Hk, HV, rec));
   LB_LAUNCH("gdn_chunk_prepare_kernel");
-  LB_CUDA(launch_kernel(gdn_chunk_apply_kernel, dim3(HV), dim3(kThreads), sizeof(ApplySmem), s, (const ChunkRecord*)rec, M, HV, state, core));
+  // a head's columns over as many CTAs as still run in one wave (one CTA per SM: its shared memory): 48 heads x 2 CTAs of 8 warps
+  // (measured at 4096 rows x 48 heads: 661 us with one CTA a head, 459 with two, 531 with four = 192 CTAs for 148 SMs)
+  const int parts = HV <= 37 ? 4 : HV <= 74 ? 2 : 1;
+  LB_CUDA(launch_kernel(gdn_chunk_apply_kernel, dim3(HV, parts), dim3(kThreads / parts), sizeof(ApplySmem), s, (const ChunkRecord*)rec, M, HV, state, core));
   LB_LAUNCH("gdn_chunk_apply_kernel");
   return LING_B200_OK;
 }
