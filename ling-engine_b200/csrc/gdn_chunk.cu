@@ -373,7 +373,91 @@ __global__ void __launch_bounds__(256) conv_window_kernel(const float* __restric
 
 }  // namespace
 
+// The gating projections of a prefill chunk on tensor cores (a = xn . W_a^T, b = xn . W_b^T, then g = -exp(A_log) softplus(a +
+// dt_bias), beta = sigmoid(b): src/core/kernels.cu:200-253,385-395): 4096 rows x 96 outputs x 5120 is two billion multiply-adds,
+// 240 us on the CUDA cores.  The fp32 rows are split into two BF16 terms (x = hi + lo, |lo| <= 2^-9 |x|): with BF16 weights both
+// products are exact in fp32, so the sum differs from the fp32 one by the accumulation order and by 2^-17 of a term.  A CTA takes
+// 32 rows and every output; its eight warps split the hidden dimension and meet in shared memory.  The k index of an MMA step
+// is permuted (lane t of the fragment layout supplies the columns 4 t .. 4 t + 3 of the step's 16) so that a lane's A values are
+// one 16-byte load and its B values one 8-byte load.
+constexpr int kGateRows = 32, kGateCols = 96, kGateWarps = 8;
+__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void split_bf16(float x, float y, uint32_t& hi, uint32_t& lo) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(x, y);
+  const __nv_bfloat162 l = __floats2bfloat162_rn(x - __low2float(h), y - __high2float(h));
+  hi = *reinterpret_cast<const uint32_t*>(&h), lo = *reinterpret_cast<const uint32_t*>(&l);
+}
+__global__ void __launch_bounds__(kGateWarps * 32)
+    ab_gating_mma_kernel(const float* __restrict__ xn, const __nv_bfloat16* __restrict__ wa, const __nv_bfloat16* __restrict__ wb,
+                         const __nv_bfloat16* __restrict__ A_log, const __nv_bfloat16* __restrict__ dt_bias, float* __restrict__ g,
+                         float* __restrict__ beta, int M, int H, int HV, int col0) {
+  pdl_sync();  // first statement: see common.cuh
+  extern __shared__ __align__(16) float gate_red[];  // [warps][32 rows][97]
+  constexpr int LDR = kGateCols + 1, NTL = kGateCols / 8;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, gq = lane >> 2, tq = lane & 3;
+  const int m0 = blockIdx.x * kGateRows, ncols = min(kGateCols, 2 * HV - col0);
+  const int kw = H / kGateWarps, k_lo = warp * kw;
+  // this lane's rows of x (clamped: a row past M contributes to outputs that are not written) and rows of W per column tile
+  const float* xr[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) xr[i] = xn + size_t(min(m0 + (i >> 1) * 16 + (i & 1) * 8 + gq, M - 1)) * H + 4 * tq;
+  const __nv_bfloat16* wr[NTL];
+#pragma unroll
+  for (int nt = 0; nt < NTL; ++nt) {
+    const int c = min(col0 + nt * 8 + gq, 2 * HV - 1);
+    wr[nt] = (c < HV ? wa + size_t(c) * H : wb + size_t(c - HV) * H) + 4 * tq;
+  }
+  float acc[2][NTL][4] = {};
+  for (int k = k_lo; k < k_lo + kw; k += 16) {
+    uint32_t ah[2][4], al[2][4];
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt) {
+      const float4 top = *reinterpret_cast<const float4*>(xr[2 * mt] + k), bot = *reinterpret_cast<const float4*>(xr[2 * mt + 1] + k);
+      split_bf16(top.x, top.y, ah[mt][0], al[mt][0]), split_bf16(bot.x, bot.y, ah[mt][1], al[mt][1]);
+      split_bf16(top.z, top.w, ah[mt][2], al[mt][2]), split_bf16(bot.z, bot.w, ah[mt][3], al[mt][3]);
+    }
+#pragma unroll
+    for (int nt = 0; nt < NTL; ++nt) {
+      const uint2 b = __ldg(reinterpret_cast<const uint2*>(wr[nt] + k));
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt) {
+        mma_bf16(acc[mt][nt], ah[mt][0], ah[mt][1], ah[mt][2], ah[mt][3], b.x, b.y);
+        mma_bf16(acc[mt][nt], al[mt][0], al[mt][1], al[mt][2], al[mt][3], b.x, b.y);
+      }
+    }
+  }
+  float* mine = gate_red + size_t(warp) * kGateRows * LDR;
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int nt = 0; nt < NTL; ++nt) {
+      const int r = mt * 16 + gq, c = nt * 8 + 2 * tq;
+      mine[r * LDR + c] = acc[mt][nt][0], mine[r * LDR + c + 1] = acc[mt][nt][1];
+      mine[(r + 8) * LDR + c] = acc[mt][nt][2], mine[(r + 8) * LDR + c + 1] = acc[mt][nt][3];
+    }
+  __syncthreads();
+  for (int i = threadIdx.x; i < kGateRows * kGateCols; i += blockDim.x) {
+    const int r = i / kGateCols, c = i % kGateCols, m = m0 + r, col = col0 + c;
+    if (m >= M || c >= ncols) continue;
+    float tot = 0.f;
+#pragma unroll
+    for (int w = 0; w < kGateWarps; ++w) tot += gate_red[(size_t(w) * kGateRows + r) * LDR + c];
+    if (col < HV) {
+      const float xx = tot + __bfloat162float(dt_bias[col]);
+      const float sp = xx <= 20.f ? log1pf(__expf(xx)) : xx;
+      g[size_t(m) * HV + col] = -__expf(__bfloat162float(A_log[col])) * sp;
+    } else {
+      beta[size_t(m) * HV + col - HV] = 1.f / (1.f + __expf(-tot));
+    }
+  }
+}
+
 int gdn_chunk_init() {
+  LB_CUDA(cudaFuncSetAttribute(ab_gating_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kGateWarps * kGateRows * (kGateCols + 1) * 4)));
   LB_CUDA(cudaFuncSetAttribute(gdn_chunk_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(sizeof(PrepSmem))));
   LB_CUDA(cudaFuncSetAttribute(gdn_chunk_apply_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(sizeof(ApplySmem))));
   return LING_B200_OK;
@@ -392,6 +476,18 @@ int gdn_chunk_launch(const float* post, const float* g, const float* beta, int M
   const int parts = HV <= 37 ? 4 : HV <= 74 ? 2 : 1;
   LB_CUDA(launch_kernel(gdn_chunk_apply_kernel, dim3(HV, parts), dim3(kThreads / parts), sizeof(ApplySmem), s, (const ChunkRecord*)rec, M, HV, state, core));
   LB_LAUNCH("gdn_chunk_apply_kernel");
+  return LING_B200_OK;
+}
+
+// g, beta [M][HV] from the normalized rows xn [M][H] (fp32) and the two BF16 projections [HV][H]; H a multiple of 128.
+int ab_gating_mma_launch(const float* xn, const __nv_bfloat16* wa, const __nv_bfloat16* wb, const __nv_bfloat16* A_log, const __nv_bfloat16* dt_bias,
+                         float* g, float* beta, int M, int H, int HV, cudaStream_t s) {
+  if (M < 1 || HV < 1 || H % (kGateWarps * 16) != 0) return LING_B200_ERR_ARG;
+  for (int col0 = 0; col0 < 2 * HV; col0 += kGateCols) {  // 96 outputs a launch (the 27B model's 48 + 48 in one)
+    LB_CUDA(launch_kernel(ab_gating_mma_kernel, dim3(ceil_div(M, kGateRows)), dim3(kGateWarps * 32), size_t(kGateWarps) * kGateRows * (kGateCols + 1) * 4, s,
+                          xn, wa, wb, A_log, dt_bias, g, beta, M, H, HV, col0));
+    LB_LAUNCH("ab_gating_mma_kernel");
+  }
   return LING_B200_OK;
 }
 

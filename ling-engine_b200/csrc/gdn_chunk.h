@@ -8,6 +8,10 @@
 namespace lb {
 
 int gdn_chunk_init();
+// The DeltaNet gating of many rows on tensor cores: g, beta [M][HV] from the normalized rows xn [M][H] (fp32, split into two BF16
+// terms) and the BF16 projections wa, wb [HV][H] (src/core/kernels.cu:200-253,385-395); H a multiple of 128.
+int ab_gating_mma_launch(const float* xn, const __nv_bfloat16* wa, const __nv_bfloat16* wb, const __nv_bfloat16* A_log, const __nv_bfloat16* dt_bias,
+                         float* g, float* beta, int M, int H, int HV, cudaStream_t s);
 // post [M][C] = silu(conv(pre [M][C])) with the taps before row 0 from window [C][3], which then advances to the last three
 // raw inputs (gdn_conv_prefill, src/core/kernels.cuh:445-449).
 int conv_rows_launch(const float* pre, const __nv_bfloat16* w, float* window, int M, int C, float* post, cudaStream_t s);

@@ -176,7 +176,8 @@ int gdn_mixer_run(GdnBuffers& b, const GdnWeights& w, float* h, int rows, int* e
   Fp4GemmCall zc;
   zc.X = &b.x, zc.W = &w.in_z, zc.alpha = b.in_scale * w.s_z, zc.y = b.z, zc.ldy = b.Vs, zc.err_flag = err, zc.ctas = ctas;
   LB_TRY(fp4_gemm_launch(zc, st));
-  LB_TRY(ab_gating_rows_launch(b.xn, w.wa, w.wb, w.A_log, w.dt_bias, b.g, b.beta, rows, b.H, b.HV, st));
+  if (b.H % 128 == 0) LB_TRY(ab_gating_mma_launch(b.xn, w.wa, w.wb, w.A_log, w.dt_bias, b.g, b.beta, rows, b.H, b.HV, st));
+  else LB_TRY(ab_gating_rows_launch(b.xn, w.wa, w.wb, w.A_log, w.dt_bias, b.g, b.beta, rows, b.H, b.HV, st));
   LB_TRY(conv_rows_launch(b.pre, w.convw, w.conv, rows, b.C, b.post, st));
   LB_TRY(gdn_chunk_launch(b.post, b.g, b.beta, rows, b.Hk, b.HV, 128, 128, w.state, b.core, b.chunk_scratch, st));
   LB_TRY(fp4_gated_norm_quant_launch(b.core, b.z, w.lin_norm, rows, b.Vs, b.eps, 1.f / b.mid_scale, b.mid.codes, b.mid.sf, true, st));
