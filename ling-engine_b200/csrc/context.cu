@@ -1563,11 +1563,10 @@ int ling_b200_chunk_attention_layer(ling_b200_ctx* c, int slot, int layer, int p
     LB_TRY(run_gemm(c, L.qkv, c->xq_h, 0, cls));
     LB_TRY(attention_over_planes(c, L, al, planes_of(c, 0, L.qkv), nullptr, cls));
     LB_TRY(run_gemm(c, L.o, c->xq_a, 1, cls));
-    // the o projection's partial sums into the residual rows (the norm's residual add; its normed copy is not used)
+    // the o projection's partial sums into the residual rows, in place
     {
       Timed t(c, kFamElem);
-      LB_TRY(norm_quant_launch(hs, planes_of(c, 1, L.o), nullptr, c->embed, L.post_norm, nullptr, c->qout(c->xq_h), c->sb.n_rows_total, cls,
-                               d.H, d.eps, c->stream));
+      LB_TRY(add_planes_launch(hs, planes_of(c, 1, L.o), c->sb.n_rows_total, cls, d.H, c->stream));
     }
     LB_TRY(read_err(c));
     done += rows;

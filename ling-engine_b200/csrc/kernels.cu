@@ -308,6 +308,19 @@ __global__ void __launch_bounds__(256)
     out[size_t(m) * H + c] = h[size_t(m) * H + c] + (add.p ? plane_sum(add, m, c) : 0.f);
 }
 
+// h[m][:] += planes, in place (a GEMM's partial sums into residual rows that no norm follows in the same pass)
+__global__ void __launch_bounds__(256) add_planes_kernel(float* h, Planes add, const int* __restrict__ n_rows, int H) {
+  pdl_sync();  // first statement: see common.cuh
+  const int m = blockIdx.x;
+  if (m >= *n_rows) return;
+  for (int c = threadIdx.x * 4; c < H; c += blockDim.x * 4) {
+    float4 v = *reinterpret_cast<const float4*>(h + size_t(m) * H + c);
+    const float4 t = plane_sum4(add, m, c);
+    v.x += t.x, v.y += t.y, v.z += t.z, v.w += t.w;
+    *reinterpret_cast<float4*>(h + size_t(m) * H + c) = v;
+  }
+}
+
 // a = xn . W_a^T, b = xn . W_b^T against BF16 weights with fp32 accumulation (src/core/kernels.cu:200-253), then the
 // gating g = -exp(A_log) * softplus(a + dt_bias), beta = sigmoid(b) (src/core/kernels.cu:385-395).  One block per
 // (value head, row): 128 threads split the hidden dimension four columns at a time.
@@ -1800,6 +1813,13 @@ int norm_quant_launch(float* h, const Planes& add, const int* ids, const __nv_bf
   LB_CUDA(launch_kernel_cluster(norm_quant_kernel, dim3(chunks, rows_grid), dim3(256), size_t(0), chunks, s, h, add, ids, embed, w, xn,
                                 q, n_rows, H, eps));
   LB_LAUNCH("norm_quant_kernel");
+  return LING_B200_OK;
+}
+
+int add_planes_launch(float* h, const Planes& add, const int* n_rows, int rows_grid, int H, cudaStream_t s) {
+  if (H % 4 != 0 || !add.p) return LING_B200_ERR_ARG;
+  LB_CUDA(launch_kernel(add_planes_kernel, dim3(rows_grid), dim3(256), size_t(0), s, h, add, n_rows, H));
+  LB_LAUNCH("add_planes_kernel");
   return LING_B200_OK;
 }
 

@@ -146,6 +146,8 @@ int pack_launch(const StepBuffers& sb, const ModelDims& d, cudaStream_t s);
 int norm_quant_launch(float* h, const Planes& add, const int* ids, const __nv_bfloat16* embed, const __nv_bfloat16* w,
                       float* xn, const QuantOut& q, const int* n_rows, int rows_grid, int H, float eps, cudaStream_t s);
 // tap[m][:] = h[m][:] + planes (debug copy of the residual after a layer)
+// h[m][:] += planes, in place
+int add_planes_launch(float* h, const Planes& add, const int* n_rows, int rows_grid, int H, cudaStream_t s);
 int tap_launch(const float* h, const Planes& add, float* out, const int* n_rows, int rows_grid, int H, cudaStream_t s);
 int copy_rows_launch(const float* src, float* out, const int* n_rows, int rows_grid, int H, cudaStream_t s);
 int kernels_norm_stamps(unsigned long long* stamps);  // debugging aid: five %globaltimer stamps of norm_quant's block (0, 0), or nullptr
