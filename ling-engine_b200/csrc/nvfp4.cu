@@ -694,25 +694,36 @@ __global__ void __launch_bounds__(256)
     const float rstd = rsqrtf(ss / 128.f + eps);
     const int d0 = (blk % 8) * 16;
 #pragma unroll
-    for (int j = 0; j < 16; ++j) v[j] = bf16_round(v[j] * rstd * __bfloat162float(w[d0 + j]) * silu(z[i * 16 + j]));
+    for (int j = 0; j < 4; ++j) {
+      const float4 zz = reinterpret_cast<const float4*>(z + i * 16)[j];
+      const float zv[4] = {zz.x, zz.y, zz.z, zz.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) v[4 * j + e] = bf16_round(v[4 * j + e] * rstd * __bfloat162float(w[d0 + 4 * j + e]) * silu(zv[e]));
+    }
     uint2 codes;
     const uint8_t sc = encode_block(v, gscale, codes);
     store_block(q, sf, tiled != 0, row, blk, K, k_atoms, codes, sc);
   }
 }
 
-// One CTA per row: sum of squares (per-thread fp32 partials over strided float4s, then the block), then one thread per
-// block of 16 normalizes, rounds and encodes.
-__global__ void __launch_bounds__(256)
+// One CTA per row, a thread per block of 16 (H / 16 threads, whole warps): the sum of squares from float4s that are all
+// requested before the first is used (per-thread fp32 partials in the order of the strided loop this replaces, then the block),
+// then each thread normalizes, rounds and encodes its block, whose values the first pass left in L1.
+__global__ void __launch_bounds__(1024)
     rmsnorm_quant_nvfp4_kernel(const float* __restrict__ x, const __nv_bfloat16* __restrict__ w, float* __restrict__ out, int H,
                                float eps, float gscale, uint8_t* __restrict__ q, uint8_t* __restrict__ sf, int tiled, int k_atoms) {
   __shared__ float red[32];
   const int row = blockIdx.x;
   const float4* src = reinterpret_cast<const float4*>(x + size_t(row) * H);
   float ss = 0.f;
-  for (int i = threadIdx.x; i < H / 4; i += blockDim.x) {
-    const float4 f = src[i];
-    ss = fmaf(f.x, f.x, fmaf(f.y, f.y, fmaf(f.z, f.z, fmaf(f.w, f.w, ss))));
+  for (int i0 = threadIdx.x; i0 < H / 4; i0 += 8 * blockDim.x) {
+    float4 f[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+      if (i0 + k * int(blockDim.x) < H / 4) f[k] = src[i0 + k * blockDim.x];
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+      if (i0 + k * int(blockDim.x) < H / 4) ss = fmaf(f[k].x, f[k].x, fmaf(f[k].y, f[k].y, fmaf(f[k].z, f[k].z, fmaf(f[k].w, f[k].w, ss))));
   }
   const float rstd = rsqrtf(block_sum(ss, red) / float(H) + eps);
   for (int blk = threadIdx.x; blk < H / 16; blk += blockDim.x) {
@@ -721,9 +732,11 @@ __global__ void __launch_bounds__(256)
     for (int j = 0; j < 4; ++j) {
       const float4 f = src[blk * 4 + j];
       const int c = blk * 16 + 4 * j;
+      const uint2 wr = *reinterpret_cast<const uint2*>(w + c);
+      const __nv_bfloat162 w01 = *reinterpret_cast<const __nv_bfloat162*>(&wr.x), w23 = *reinterpret_cast<const __nv_bfloat162*>(&wr.y);
       float4 n;
-      n.x = f.x * rstd * (1.f + __bfloat162float(w[c])), n.y = f.y * rstd * (1.f + __bfloat162float(w[c + 1]));
-      n.z = f.z * rstd * (1.f + __bfloat162float(w[c + 2])), n.w = f.w * rstd * (1.f + __bfloat162float(w[c + 3]));
+      n.x = f.x * rstd * (1.f + __low2float(w01)), n.y = f.y * rstd * (1.f + __high2float(w01));
+      n.z = f.z * rstd * (1.f + __low2float(w23)), n.w = f.w * rstd * (1.f + __high2float(w23));
       if (out) reinterpret_cast<float4*>(out + size_t(row) * H)[blk * 4 + j] = n;
       v[4 * j] = bf16_round(n.x), v[4 * j + 1] = bf16_round(n.y), v[4 * j + 2] = bf16_round(n.z), v[4 * j + 3] = bf16_round(n.w);
     }
@@ -891,7 +904,8 @@ int fp4_gated_norm_quant_launch(const float* core, const float* z, const __nv_bf
 int fp4_rmsnorm_quant_launch(const float* x, const __nv_bfloat16* w, float* out, int M, int H, float eps, float gscale, uint8_t* q,
                              uint8_t* sf, bool tiled, cudaStream_t stream) {
   if (!shape_ok(M, H, "rmsnorm_quant")) return LING_B200_ERR_ARG;
-  rmsnorm_quant_nvfp4_kernel<<<M, 256, 0, stream>>>(x, w, out, H, eps, gscale, q, sf, tiled ? 1 : 0, fp4_k_atoms(H));
+  const int threads = std::min(1024, std::max(64, (H / 16 + 31) / 32 * 32));
+  rmsnorm_quant_nvfp4_kernel<<<M, threads, 0, stream>>>(x, w, out, H, eps, gscale, q, sf, tiled ? 1 : 0, fp4_k_atoms(H));
   LB_LAUNCH("rmsnorm_quant_nvfp4_kernel");
   return LING_B200_OK;
 }
