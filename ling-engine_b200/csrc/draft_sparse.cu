@@ -7,7 +7,7 @@
 // selector_project kernel), us [vocab][256] BF16.  The selected rows, in id order, are gathered into a compact FP8
 // matrix which the head GEMM then multiplies like any other: a selected row's logit is the full head's, bit for bit.
 //
-//   sparse_scores_kernel   HBM-bound: reads us once (vocab x 512 bytes) through a cp.async ring in shared memory; BF16 mma.sync
+//   sparse_scores_kernel   HBM-bound: reads us once (vocab x 512 bytes) by TMA into a swizzled ring in shared memory; BF16 mma.sync
 //                          m16n8k16 with ldmatrix fragments; writes an order-preserving 32-bit key per row, 0 = marked
 //   sparse_level_kernel    radix select of the `dynamic`-th largest key, 11 + 11 + 10 bits: per level one histogram launch whose
 //                          last block (a ticket) finds the bin the threshold falls in
@@ -16,6 +16,7 @@
 #include <cfloat>
 
 #include "draft_head.h"
+#include "gemm.h"
 #include "tc.cuh"
 
 namespace lb {
@@ -43,17 +44,19 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint3
 }
 
 // keys[n] = marked ? 0 : order_key(max_m p[m] . us[n]).  One block per SM streams its share of us through a three-stage ring
-// in shared memory, 128 rows (64 KB) a stage, by plain bulk copies (one 512-byte row each, this CTA's shared memory only) that complete
-// on the stage's mbarrier; warp w of the block then owns rows 16 w .. 16 w + 15 of the stage: A fragments by ldmatrix.x4 (rows
-// padded to 528 bytes, so the eight rows of a matrix fall in different banks), the step's rows (BF16, converted once) as the B
-// operand by ldmatrix as well, sixteen k-steps of mma.sync m16n8k16 a column tile.  Every wait is bounded: one that runs out
-// records a code in the error word, and the block makes no further waits and writes no further keys.
+// in shared memory, 128 rows (64 KB) a stage, as four TMA tiles of 128 rows x 128 bytes under the 128-byte swizzle (a
+// byte-typed map of the factor, plain loads: this CTA's shared memory only), completing on the stage's mbarrier; warp w of the
+// block then owns rows 16 w .. 16 w + 15 of the stage: A fragments by ldmatrix.x4 with the swizzle's XOR in the address (the
+// eight rows of a matrix fall in different banks), the step's rows (BF16, converted once, rows padded) as the B operand by
+// ldmatrix as well, sixteen k-steps of mma.sync m16n8k16 a column tile.  Every wait is bounded: one that runs out records a
+// code in the error word, and the block makes no further waits and writes no further keys.
 // (Earlier forms: fragments loaded straight from global memory, a lane per 128-byte quarter of a row -- 32 lines an
-// instruction, load-unit bound at a third of the copy bandwidth; the same ring filled by 16-byte cp.async -- 0.44: the copies
-// a block can have in flight through L1 did not cover the latency.)
-constexpr int kScoreRows = 128, kScoreStages = 3, kScoreLd = kRank + 8;  // halves per padded row
+// instruction, load-unit bound at a third of the copy bandwidth; the ring filled by 16-byte cp.async -- 0.44; by one 512-byte
+// bulk copy a row into padded rows -- 0.49: 128 small copies a stage.)
+constexpr int kScoreRows = 128, kScoreStages = 3, kScoreLd = kRank + 8;  // (halves per padded row of the step's rows)
+constexpr int kScoreStageBytes = kScoreRows * kRank * 2;                  // 64 KB: [k quarter][row][128 B]
 template <int NT>
-constexpr size_t score_smem() { return size_t(kScoreStages * kScoreRows + NT * 8) * kScoreLd * 2; }
+constexpr size_t score_smem() { return size_t(kScoreStages) * kScoreStageBytes + size_t(NT * 8) * kScoreLd * 2 + 1024 /* alignment */; }
 __device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
 }
@@ -61,37 +64,34 @@ __device__ __forceinline__ void ldsm_x2(uint32_t (&r)[2], const void* p) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(smem_u32(p)));
 }
 template <int NT>
-__global__ void __launch_bounds__(256, 1) sparse_scores_kernel(const float* __restrict__ p, int M, const __nv_bfloat16* __restrict__ us,
+__global__ void __launch_bounds__(256, 1) sparse_scores_kernel(const float* __restrict__ p, int M, const __grid_constant__ CUtensorMap map_us,
                                                                int N, SparseMasks masks, uint32_t* __restrict__ keys, int* err) {
   pdl_sync();  // first statement: see common.cuh
-  extern __shared__ __align__(16) uint8_t score_raw[];
+  extern __shared__ uint8_t score_raw[];
+  uint8_t* ring = score_raw + ((1024u - (smem_u32(score_raw) & 1023u)) & 1023u);  // swizzled tiles: 1024-byte aligned
+  __nv_bfloat16* ps = reinterpret_cast<__nv_bfloat16*>(ring + size_t(kScoreStages) * kScoreStageBytes);  // [NT * 8][264]
   __shared__ __align__(8) uint64_t full[kScoreStages];
   __shared__ volatile int failed;
   if (threadIdx.x == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_us)) : "memory");
     for (int i = 0; i < kScoreStages; ++i) tc::mbar_init(&full[i], 1);
     failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
-  __nv_bfloat16* ring = reinterpret_cast<__nv_bfloat16*>(score_raw);          // [stages][128][264]
-  __nv_bfloat16* ps = ring + size_t(kScoreStages) * kScoreRows * kScoreLd;    // [NT * 8][264]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
   const int tiles = (N + kScoreRows - 1) / kScoreRows;
   const int mine = blockIdx.x < tiles ? (tiles - 1 - int(blockIdx.x)) / int(gridDim.x) + 1 : 0;  // tiles blockIdx.x, + gridDim.x, ...
-  // stage i % 3 of the ring <- this block's i-th tile: thread r < 128 copies row r; rows past N are not copied (their
-  // products are computed on what the stage held and never written)
+  // stage i % 3 of the ring <- this block's i-th tile: four tiles of 128 bytes x 128 rows (rows past N arrive as zeros)
   auto send = [&](int i) {
-    if (i >= mine || failed) return;
+    if (i >= mine || failed || threadIdx.x != 0) return;
     const int row0 = (int(blockIdx.x) + i * int(gridDim.x)) * kScoreRows;
-    const int rows_in = min(kScoreRows, N - row0);
     uint64_t* bar = &full[i % kScoreStages];
-    if (threadIdx.x == 0) tc::mbar_expect_tx(bar, uint32_t(rows_in) * kRank * 2);
-    if (int(threadIdx.x) < rows_in) {
-      __nv_bfloat16* dst = ring + (size_t(i % kScoreStages) * kScoreRows + threadIdx.x) * kScoreLd;
-      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)),
-                   "l"(us + size_t(row0 + threadIdx.x) * kRank), "r"(kRank * 2), "r"(smem_u32(bar))
-                   : "memory");
-    }
+    uint8_t* dst = ring + size_t(i % kScoreStages) * kScoreStageBytes;
+    const uint64_t pol = tc::policy_evict_first();  // the factor is read once
+    tc::mbar_expect_tx(bar, uint32_t(kScoreStageBytes));
+#pragma unroll
+    for (int kq = 0; kq < 4; ++kq) tc::tma_load_2d(dst + kq * (kScoreRows * 128), &map_us, bar, kq * 128, row0, pol);
   };
   send(0), send(1);
   for (int i = threadIdx.x; i < NT * 8 * kRank; i += blockDim.x) {
@@ -116,15 +116,18 @@ __global__ void __launch_bounds__(256, 1) sparse_scores_kernel(const float* __re
       if (row0 + g < N) m0 = any_mask(masks, row0 + g);
       if (row0 + g + 8 < N) m1 = any_mask(masks, row0 + g + 8);
     }
-    const __nv_bfloat16* tile = ring + (size_t(i % kScoreStages) * kScoreRows + warp * 16) * kScoreLd;
+    const uint8_t* stage = ring + size_t(i % kScoreStages) * kScoreStageBytes;
+    const int arow = warp * 16 + (lane & 15);  // this lane's row of the stage for the A fragments
     float acc[NT][4];
 #pragma unroll
     for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
 #pragma unroll 4
     for (int ks = 0; ks < kRank / 16; ++ks) {
-      // A: rows 0-15 x k 16 ks .. + 15 as four 8 x 8 matrices (rows 0-7 / 8-15, k low / high): lane l addresses row l % 16, k half l / 16
+      // A: rows 0-15 x k 16 ks .. + 15 as four 8 x 8 matrices (rows 0-7 / 8-15, k low / high): lane l addresses row l % 16 and the
+      // 16-byte chunk 2 ks + l / 16 of its 512 bytes = chunk c % 8 of k quarter c / 8, at the swizzled position (c % 8) ^ (row % 8)
       uint32_t a[4];
-      ldsm_x4(a, tile + size_t(lane & 15) * kScoreLd + ks * 16 + (lane >> 4) * 8);
+      const int c = 2 * ks + (lane >> 4);
+      ldsm_x4(a, stage + (c >> 3) * (kScoreRows * 128) + arow * 128 + (((c & 7) ^ (arow & 7)) << 4));
       if constexpr (NT == 1) {
         uint32_t b[2];  // step rows 0-7: k low / high; lanes 0-15 give the addresses
         ldsm_x2(b, ps + size_t(lane & 7) * kScoreLd + ks * 16 + ((lane >> 3) & 1) * 8);
@@ -349,10 +352,12 @@ int sparse_select_launch(const float* p, int M, const __nv_bfloat16* us, int N, 
     LB_CUDA(cudaFuncSetAttribute(sparse_scores_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(score_smem<4>())));
     attr_set = true;
   }
+  CUtensorMap map_us;  // the factor as bytes: rows of 512, tiles of 128 bytes x 128 rows, 128-byte swizzle
+  if (const int rc = encode_tile_map(&map_us, const_cast<__nv_bfloat16*>(us), uint64_t(kRank) * 2, uint64_t(N), kScoreRows)) return rc;
   const dim3 grid(sm_count);
-  if (M <= 8) LB_CUDA(launch_kernel(sparse_scores_kernel<1>, grid, dim3(256), score_smem<1>(), s, p, M, us, N, masks, keys, err));
-  else if (M <= 16) LB_CUDA(launch_kernel(sparse_scores_kernel<2>, grid, dim3(256), score_smem<2>(), s, p, M, us, N, masks, keys, err));
-  else LB_CUDA(launch_kernel(sparse_scores_kernel<4>, grid, dim3(256), score_smem<4>(), s, p, M, us, N, masks, keys, err));
+  if (M <= 8) LB_CUDA(launch_kernel(sparse_scores_kernel<1>, grid, dim3(256), score_smem<1>(), s, p, M, map_us, N, masks, keys, err));
+  else if (M <= 16) LB_CUDA(launch_kernel(sparse_scores_kernel<2>, grid, dim3(256), score_smem<2>(), s, p, M, map_us, N, masks, keys, err));
+  else LB_CUDA(launch_kernel(sparse_scores_kernel<4>, grid, dim3(256), score_smem<4>(), s, p, M, map_us, N, masks, keys, err));
   LB_LAUNCH("sparse_scores_kernel");
   if (scores_only) return LING_B200_OK;
   for (int level = 0; level < 3; ++level) {

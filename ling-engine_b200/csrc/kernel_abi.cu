@@ -514,12 +514,15 @@ int ling_b200_sparse_select_bench(int device, int N, int M, int dynamic, int cap
   for (auto& v : mask) v = (next() >> 40) % 50 == 0;
   Scratch sc;
   float* d_p = sc.put(p.data(), p.size());
-  auto* d_us = reinterpret_cast<__nv_bfloat16*>(sc.put(us.data(), us.size()));
+  // three copies of the factor, read in turn: the working set (3 x 127 MB at the 27B vocabulary) is then larger than L2, so a
+  // launch finds little of its copy there
+  __nv_bfloat16* d_us[3];
+  for (auto& u : d_us) u = reinterpret_cast<__nv_bfloat16*>(sc.put(us.data(), us.size()));
   uint8_t* d_m = sc.put(mask.data(), mask.size());
   uint8_t* d_s = sc.get<uint8_t>(sparse_scratch_bytes(N));
   int* d_rows = sc.get<int>(size_t(cap));
   int* d_n = sc.get<int>(1);
-  LB_PTR(d_p && d_us && d_m && d_s && d_rows && d_n);
+  LB_PTR(d_p && d_us[0] && d_us[1] && d_us[2] && d_m && d_s && d_rows && d_n);
   SparseMasks msk;
   msk.n = 1;
   for (int i = 0; i < kSparseMasks; ++i) msk.m[i] = d_m;
@@ -527,9 +530,9 @@ int ling_b200_sparse_select_bench(int device, int N, int M, int dynamic, int cap
   LB_CUDA(cudaEventCreate(&a));
   LB_CUDA(cudaEventCreate(&b));
   for (int part = 0; part < 2; ++part) {
-    LB_TRY(sparse_select_launch(d_p, M, d_us, N, msk, dynamic, cap, d_s, sms, d_rows, d_n, nullptr, 0, part == 0));
+    LB_TRY(sparse_select_launch(d_p, M, d_us[0], N, msk, dynamic, cap, d_s, sms, d_rows, d_n, nullptr, 0, part == 0));
     LB_CUDA(cudaEventRecord(a, 0));
-    for (int i = 0; i < iters; ++i) LB_TRY(sparse_select_launch(d_p, M, d_us, N, msk, dynamic, cap, d_s, sms, d_rows, d_n, nullptr, 0, part == 0));
+    for (int i = 0; i < iters; ++i) LB_TRY(sparse_select_launch(d_p, M, d_us[(i + 1) % 3], N, msk, dynamic, cap, d_s, sms, d_rows, d_n, nullptr, 0, part == 0));
     LB_CUDA(cudaEventRecord(b, 0));
     LB_CUDA(cudaEventSynchronize(b));
     LB_CUDA(cudaEventElapsedTime(&ms[part], a, b));
