@@ -338,6 +338,10 @@ int sparse_select_launch(const float* p, int M, const __nv_bfloat16* us, int N, 
     set_error("sparse_select: 1 to 32 rows, 1 to 4 masks, a positive capacity");
     return LING_B200_ERR_ARG;
   }
+  if (N < kScoreRows || (reinterpret_cast<uintptr_t>(us) & 15u) != 0) {
+    set_error("sparse_select: the factor must have at least 128 rows and start on a 16-byte boundary (it is read by TMA tiles)");
+    return LING_B200_ERR_ARG;
+  }
   uint8_t* base = static_cast<uint8_t*>(scratch);
   uint32_t* keys = reinterpret_cast<uint32_t*>(base);
   uint32_t* state = reinterpret_cast<uint32_t*>(base + ((size_t(N) * 4 + 63) & ~size_t(63)));
