@@ -15,6 +15,7 @@
 
 #include <cfloat>
 #include <mutex>
+#include <utility>
 
 #include "../../include/ling_b200.h"
 #include "tc.cuh"
@@ -708,15 +709,20 @@ int wait_probe_launch(unsigned long long limit_ns, int* err_flag, unsigned long 
   return LING_B200_OK;
 }
 
-// Up to 128 rows: the smallest tile that holds them.  Beyond: the GEMM's time is its padded rows (tiles x tile rows; measured
-// per row 0.336 us at 96, 0.338 at 128, 0.344 at 64 on the gate|up shape), so the tile with the least padding, ties in
-// that order: 142 rows run as 2 x 96 (68 us) rather than 2 x 128 (88), 260 as 3 x 96 (99 vs 130), 300 as 5 x 64 (111 vs 130).
-// The result does not depend on the choice (a row's arithmetic is the same in every tile size).
+// Up to 128 rows: the smallest tile that holds them.  Beyond: the GEMM's time is its padded rows (tiles x tile rows) times the
+// tile's cost per row -- measured at 2048 rows, where no tile pads: in projection 320 us with 96-row tiles, 360 with 128; out
+// projection 178 / 216; gate|up 605 / 620; per row 0.336 us at 96, 0.344 at 64 on the gate|up shape -- so the tile with the least
+// weighted padding: 142 rows run as 2 x 96 (68 us) rather than 2 x 128 (88), 260 as 3 x 96 (99 vs 130), 300 as 5 x 64 (111 vs
+// 130), 2048 as 22 x 96 rather than 16 x 128.  The result does not depend on the choice (a row's arithmetic is the same in
+// every tile size).
 int token_tile(int M) {
   if (M <= 128) return M <= 32 ? 32 : M <= 64 ? 64 : M <= 96 ? 96 : 128;
   int best = 96;
-  for (int nt : {128, 64})
-    if (round_up(M, nt) < round_up(M, best)) best = nt;
+  double best_cost = double(round_up(M, 96));
+  for (const auto& [nt, per_row] : {std::pair<int, double>{128, 1.08}, {64, 1.05}}) {
+    const double cost = double(round_up(M, nt)) * per_row;
+    if (cost < best_cost) best = nt, best_cost = cost;
+  }
   return best;
 }
 
