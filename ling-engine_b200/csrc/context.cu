@@ -1494,6 +1494,10 @@ int ling_b200_prefill_attention_host(ling_b200_ctx* c, int slot, int attn_layer,
   }
   const LayerW& L = c->layers[attn_layer_of(c, attn_layer)];
   const int W = d.Hq * 2 * d.D + 2 * d.Hkv * d.D, O = d.Hq * d.D;
+  struct Unstage {  // the chains staged here are no step to launch: a verify step is staged again afterwards
+    ling_b200_ctx* c;
+    ~Unstage() { c->staged_seqs = 0, c->staged_rows = 0; }
+  } unstage{c};
   ChunkChains cc;
   std::vector<ling_b200_seq_step> seqs;
   PdlScope pdl(c->opt.pdl != 0);
@@ -1534,10 +1538,10 @@ int ling_b200_chunk_attention_layer(ling_b200_ctx* c, int slot, int layer, int p
   }
   const LayerW& L = c->layers[layer];
   const int al = c->attn_index[layer];
-  struct KeepCount {  // the verify step's launch count stays what its capture counted
+  struct KeepCount {  // the verify step's launch count stays what its capture counted; the chains staged here are no step to launch
     ling_b200_ctx* c;
     int n;
-    ~KeepCount() { c->launches_per_step = n; }
+    ~KeepCount() { c->launches_per_step = n, c->staged_seqs = 0, c->staged_rows = 0; }
   } keep{c, c->launches_per_step};
   ChunkChains cc;
   std::vector<ling_b200_seq_step> seqs;

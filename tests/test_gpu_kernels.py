@@ -506,4 +506,6 @@ def test_chunk_attention_layer_matches_oracle(gpu, lb, lo, pos0, M):
     h = (rng.standard_normal((M, cfg.hidden)) * np.exp(0.5 * rng.standard_normal((M, 1)))).astype(np.float32)
     err = chunk_layer_errors(lb, ctx, m, 0, pos0, h)
     assert err.max() <= 2e-2 and np.median(err) <= 5e-3, (float(err.max()), float(np.median(err)))
+    with pytest.raises(lb.LingError):   # the chunk's chains are not a staged step: a launch without staging again is refused
+        ctx.launch()
     ctx.close(), m.close()
