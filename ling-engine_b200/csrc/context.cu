@@ -1561,8 +1561,11 @@ int ling_b200_chunk_attention_layer(ling_b200_ctx* c, int slot, int layer, int p
     float* hs = h + size_t(done) * d.H;
     LB_TRY(pack_launch(c->sb, d, c->stream));
     {
+      // the norm reads every row of its grid before it knows the row count (the step's residual buffer has them all): the pass's
+      // rows go through that buffer, since the caller's array ends with the chunk
       Timed t(c, kFamElem);
-      LB_TRY(norm_quant_launch(hs, none, nullptr, c->embed, L.input_norm, nullptr, c->qout(c->xq_h), c->sb.n_rows_total, cls, d.H, d.eps, c->stream));
+      LB_CUDA(cudaMemcpyAsync(c->h, hs, size_t(rows) * d.H * 4, cudaMemcpyDeviceToDevice, c->stream));
+      LB_TRY(norm_quant_launch(c->h, none, nullptr, c->embed, L.input_norm, nullptr, c->qout(c->xq_h), c->sb.n_rows_total, cls, d.H, d.eps, c->stream));
     }
     LB_TRY(run_gemm(c, L.qkv, c->xq_h, 0, cls));
     LB_TRY(attention_over_planes(c, L, al, planes_of(c, 0, L.qkv), nullptr, cls));

@@ -713,15 +713,17 @@ int wait_probe_launch(unsigned long long limit_ns, int* err_flag, unsigned long 
 // tile's cost per row -- measured at 2048 rows, where no tile pads: in projection 320 us with 96-row tiles, 360 with 128; out
 // projection 178 / 216; gate|up 605 / 620; per row 0.336 us at 96, 0.344 at 64 on the gate|up shape -- so the tile with the least
 // weighted padding: 142 rows run as 2 x 96 (68 us) rather than 2 x 128 (88), 260 as 3 x 96 (99 vs 130), 300 as 5 x 64 (111 vs
-// 130), 2048 as 22 x 96 rather than 16 x 128.  The result does not depend on the choice (a row's arithmetic is the same in
+// 130), 2048 as 32 x 64 rather than 16 x 128 (22 x 96 would pad past the buffers' 128-row granularity).  The result does not depend on the choice (a row's arithmetic is the same in
 // every tile size).
 int token_tile(int M) {
   if (M <= 128) return M <= 32 ? 32 : M <= 64 ? 64 : M <= 96 ? 96 : 128;
-  int best = 96;
-  double best_cost = double(round_up(M, 96));
-  for (const auto& [nt, per_row] : {std::pair<int, double>{128, 1.08}, {64, 1.05}}) {
+  // (never more padded rows than 128-row tiles would have: the activation buffers are allocated in whole 128-row tiles)
+  const int limit = round_up(M, 128);
+  int best = 128;
+  double best_cost = double(limit) * 1.08;
+  for (const auto& [nt, per_row] : {std::pair<int, double>{96, 1.0}, {64, 1.05}}) {
     const double cost = double(round_up(M, nt)) * per_row;
-    if (cost < best_cost) best = nt, best_cost = cost;
+    if (round_up(M, nt) <= limit && cost < best_cost) best = nt, best_cost = cost;
   }
   return best;
 }
