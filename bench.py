@@ -355,8 +355,7 @@ def run_reference(args, rank, world):
 
 def setup_context(lbm, cfg, seqs, args, rank, local_rank, churn, chunk_rows=0):
     """A context sized for `seqs` with synthetic weights, page tables from the page pool, synthetic KV and DeltaNet state.
-    chunk_rows > 0: one more session (slot len(seqs)) with pages for a prefill chunk of that many positions, and a step
-    capacity of 64 chains / 2048 rows for the chunk's attention layers."""
+    chunk_rows > 0: one more session (slot len(seqs)) with pages for a prefill chunk of that many positions."""
     rows = sum(len(q["tokens"]) for q in seqs)
     page_tokens = 16
     pages = sum((q["pos"] + 64 + page_tokens - 1) // page_tokens for q in seqs) + 1
@@ -366,7 +365,7 @@ def setup_context(lbm, cfg, seqs, args, rank, local_rank, churn, chunk_rows=0):
     n_sessions, max_seqs, max_rows = len(seqs), len(seqs), max(rows, 32)
     if chunk_rows:
         pages += chunk_rows // page_tokens + 1
-        n_sessions, max_seqs, max_rows, max_context = n_sessions + 1, max(max_seqs, 64), max(max_rows, 2048), max(max_context, chunk_rows + 64)
+        n_sessions, max_context = n_sessions + 1, max(max_context, chunk_rows + 64)
     ctx = lbm.Context(cfg, sessions=n_sessions, max_context=max_context, page_tokens=page_tokens,
                       pool_pages=pages, max_seqs=max_seqs, max_rows=max_rows, gemm_impl=args.gemm_impl, use_graph=1,
                       device=local_rank, debug_rows=0, pdl=args.pdl, chain=args.chain, gating_stream=args.gating_stream, fuse_swiglu=args.fuse_swiglu)
@@ -668,48 +667,72 @@ def run_mixed(args, rank, local_rank, world):
 
 def run_mixed_whole(args, lbm, dist, cfg, ctx, ffn, seqs, rows, chunk, n_mix, rank, local_rank, world):
     """--chunk-scope all: the prefill chunk through EVERY layer -- the DeltaNet layers' NVFP4 mixers, the full-attention layers'
-    mixers (the verify context's own FP8 q|k|v and o projections, the step's prepare / attention / combine kernels over the
-    chunk's rows as 32-row chains of the chunk's session, 64 chains a launch) and all NVFP4 feed-forward blocks -- and then the 8
-    decoding sequences' verify step.  The chunk's attention layers work in the verify context's buffers, so the two halves
-    run one after the other: a step's time is the chunk's device time plus the verify step's (max over ranks)."""
+    mixers (the verify model's own FP8 q|k|v and o projections, the step's prepare / attention / combine kernels over the chunk's
+    rows as 32-row chains of the chunk's session, 64 chains a launch) and all NVFP4 feed-forward blocks -- beside the 8 decoding
+    sequences' verify step.  The chunk's attention layers run on a sibling context (its own step buffers on the verify
+    context's weights, pages and sessions), so the two halves run together as in the default scope: the chunk's stack from a
+    second host thread (its attention layers wait for the device between launches of chains), the verify graphs from the main
+    one; a step's time is the longer of the two halves' device times (max over ranks)."""
+    import threading
     n_attn = cfg.layers - n_mix
-    ffn.attach_context(ctx, len(seqs), 0, 4)
+    sib = ctx.sibling(64, 2048)
+    ffn.attach_context(sib, len(seqs), 0, 4)
     h0 = np.random.default_rng(50 + rank).standard_normal((chunk, cfg.hidden)).astype(np.float32)
     ffn.set_residual(h0)
     flags, K, W = lbm.STEP_COMMIT, args.steps, max(args.warmup, 3)
     clocks = ClockSampler(local_rank)
-
-    def one_step():
-        ffn.launch(chunk, 1)
-        f_ms = ffn.wait()
-        ctx.stage(seqs, flags)
-        ctx.timer_begin()
-        ctx.launch()
-        return f_ms, ctx.timer_end()
+    ctx.stage(seqs, flags)
     for _ in range(W):
-        one_step()
+        ctx.launch()
+    ffn.launch(chunk, W)
+    ffn.wait()
     res = ctx.fetch()
     assert all(r.status == 0 and r.n_path == q["accept"] for r, q in zip(res, seqs)), "acceptance differs from the imposed paths"
+    # each half alone
+    ffn.launch(chunk, K)
+    f_alone = ffn.wait() / K
+    ctx.timer_begin()
+    for _ in range(K):
+        ctx.launch()
+    v_alone = ctx.timer_end() / K
+    # both together
     clocks.start()
     dist.barrier()
     ctx.sync()
-    f_tot = v_tot = 0.0
+    box = [0.0]
+
+    def chunk_half():
+        ffn.launch(chunk, K)
+        box[0] = ffn.wait()
+    th = threading.Thread(target=chunk_half)
+    th.start()
+    ctx.timer_begin()
     for _ in range(K):
-        f_ms, v_ms = one_step()
-        f_tot, v_tot = f_tot + f_ms, v_tot + v_ms
+        ctx.launch()
+    v_tot = ctx.timer_end()
+    th.join()
+    f_tot = box[0]
     ctx.sync()
     dist.barrier()
-    step_ms = dist.max(f_tot + v_tot) / K
+    step_ms = dist.max(max(f_tot, v_tot)) / K
     passes = -(-chunk // 2048)
     launches = ctx.launch_count() + 3 * cfg.layers + 10 * n_mix + 8 * passes * n_attn
-    # end to end: the chunk's residual in and out of host memory, the verify step's descriptors in and results out, every step
+    # end to end: the chunk's residual in and out of host memory (second thread), the verify step's descriptors in and results out
+    outs = [None]
+
+    def chunk_thread():
+        for _ in range(K):
+            outs[0] = ffn.forward(h0)
     ffn.forward(h0), ctx.verify_step(seqs, flags)
     dist.barrier()
     t0 = time.perf_counter()
+    th = threading.Thread(target=chunk_thread)
+    th.start()
     for _ in range(K):
-        out = ffn.forward(h0)
         ctx.verify_step(seqs, flags)
+    th.join()
     e2e_s = dist.max(time.perf_counter() - t0)
+    out = outs[0]
     clk = clocks.stop()
     assert np.isfinite(out).all()
     gu_ms = lbm.nvfp4_gemm_bench(chunk, cfg.intermediate, cfg.hidden, fused=True, iters=10, device=local_rank)
@@ -727,12 +750,13 @@ def run_mixed_whole(args, lbm, dist, cfg, ctx, ffn, seqs, rows, chunk, n_mix, ra
             "config": {"workload": "mixed", "model": "27B-class hybrid, %d layers" % cfg.layers, "chunk_rows": chunk,
                        "chunk_scope": "every layer: %d DeltaNet mixers (NVFP4), %d full-attention mixers (FP8 projections, attention over the "
                                       "chunk's rows as 32-row chains through the step's kernels, %d launches of up to 64 chains a layer) and "
-                                      "%d NVFP4 feed-forward blocks; then the verify step (the two halves in turn)"
+                                      "%d NVFP4 feed-forward blocks; beside the verify step (the attention layers on a sibling context)"
                                       % (n_mix, n_attn, passes, cfg.layers),
                        "decode_sequences": len(seqs), "decode_rows": rows, "contexts": [q["pos"] for q in seqs],
                        "parallelism": "replicas, one chunk and one decode batch per GPU, no collective",
                        "l2": "inputs larger than L2 (FP8 weights %.1f GB + NVFP4 chunk weights per step), no flush" % (ctx.weight_bytes() / 1e9)},
-            "halves_ms": {"chunk": f_tot / K, "verify": v_tot / K},
+            "halves_ms": {"chunk_alone": f_alone, "verify_alone": v_alone, "serial": f_alone + v_alone, "chunk_together": f_tot / K,
+                          "verify_together": v_tot / K},
             "e2e": {"value": total_rows * K / e2e_s, "unit": UNIT, "ms_per_step": e2e_s / K * 1e3,
                     "h2d_bytes_per_step": int(h0.nbytes + ctx_stage_bytes(lbm, len(seqs))),
                     "d2h_bytes_per_step": int(h0.nbytes + len(seqs) * __import__("ctypes").sizeof(lbm.SeqResult) + 4)},
@@ -748,6 +772,7 @@ def run_mixed_whole(args, lbm, dist, cfg, ctx, ffn, seqs, rows, chunk, n_mix, ra
         }
         print(json.dumps(line), flush=True)
     ffn.close()
+    sib.close()
     ctx.close()
     dist.close()
 

@@ -85,6 +85,12 @@ typedef struct ling_b200_ctx ling_b200_ctx;
 
 /* Engine::Engine (src/core/engine.cpp:129-434): everything is allocated here, nothing while serving. */
 int ling_b200_create(const ling_b200_model_config* cfg, const ling_b200_options* opt, ling_b200_ctx** out);
+/* A second set of step buffers (activations, descriptors, streams, graphs) on a context's weights, KV pool, page tables and state
+ * slots: for work that runs beside that context's verify steps on the same GPU without touching its staged step (a prefill
+ * chunk's attention layers).  The sibling owns none of the shared memory: destroy it before the parent; it takes no weight
+ * uploads.  No counterpart of its own in the reference, where the prefill and the verify path share one engine's buffers in
+ * turn. */
+int ling_b200_create_sibling(const ling_b200_ctx* parent, int max_seqs, int max_rows, ling_b200_ctx** out);
 void ling_b200_destroy(ling_b200_ctx* ctx);
 /* The last error's text (thread-local for calls without a context). */
 const char* ling_b200_last_error(void);

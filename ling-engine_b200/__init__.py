@@ -186,6 +186,22 @@ class Context:
         self.last_rows = 0
         self.last_seqs = 0
 
+    def sibling(self, max_seqs, max_rows):
+        """A second set of step buffers on this context's weights, KV pool and sessions (ling_b200_create_sibling): for work that
+        runs beside this context's verify steps.  Close it before this context."""
+        sib = Context.__new__(Context)
+        sib.cfg, sib.opt, sib.h, sib.last_rows, sib.last_seqs, sib.parent = self.cfg, self.opt, C.c_void_p(), 0, 0, self
+        L = lib()
+        L.ling_b200_create_sibling.argtypes = [C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_void_p)]
+        rc = L.ling_b200_create_sibling(self.h, max_seqs, max_rows, C.byref(sib.h))
+        if rc != OK:
+            err = last_error()
+            if sib.h:
+                L.ling_b200_destroy(sib.h)
+            sib.h = None
+            raise LingError("ling_b200_create_sibling failed (status %d): %s" % (rc, err))
+        return sib
+
     def close(self):
         if self.h:
             lib().ling_b200_destroy(self.h)

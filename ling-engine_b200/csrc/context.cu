@@ -83,6 +83,7 @@ struct ling_b200_ctx {
   float *pre = nullptr, *post = nullptr, *g = nullptr, *beta = nullptr;  // [n_gdn][rows][..], saved for the commit
   float *part_o = nullptr, *part_ml = nullptr;
   int chunk_slots = 0;
+  bool sibling = false;  // weights, KV pool, page tables and state slots belong to another context
   HeadEpilogue head_ep;
   float* logits = nullptr;
   float* taps = nullptr;
@@ -589,7 +590,9 @@ int ling_b200_device_name(int device, char* buf, int len) {
   return LING_B200_OK;
 }
 
-int ling_b200_create(const ling_b200_model_config* cfg, const ling_b200_options* opt, ling_b200_ctx** out) {
+// share != nullptr: a sibling context -- the weights, the KV pool, the page tables and the DeltaNet state slots are `share`'s (not
+// owned, not freed here); the activations, step buffers, streams and graphs are its own.
+static int create_impl(const ling_b200_model_config* cfg, const ling_b200_options* opt, const ling_b200_ctx* share, ling_b200_ctx** out) {
   if (!cfg || !opt || !out) {
     set_error("create: null argument");
     return LING_B200_ERR_ARG;
@@ -619,6 +622,7 @@ int ling_b200_create(const ling_b200_model_config* cfg, const ling_b200_options*
   ling_b200_ctx* c = new ling_b200_ctx;
   *out = c;  // the caller destroys it also after a failed creation
   c->cfg = *cfg, c->opt = *opt;
+  c->sibling = share != nullptr;
   c->sm_count = prop.multiProcessorCount;
   ModelDims& d = c->d;
   d.H = cfg->hidden, d.I = cfg->intermediate, d.V = cfg->vocab, d.Hq = cfg->heads, d.Hkv = cfg->kv_heads, d.D = cfg->head_dim;
@@ -648,40 +652,51 @@ int ling_b200_create(const ling_b200_model_config* cfg, const ling_b200_options*
 
   // ---- weights
   size_t biggest = size_t(d.V) * d.H;
-  LB_TRY(c->alloc(&c->embed, size_t(d.V) * d.H));
-  LB_TRY(c->alloc(&c->final_norm, size_t(d.H)));
-  LB_TRY(c->alloc_matrix(c->head, d.V, d.H));
-  c->head.splits = 1;
+  if (share) {
+    c->embed = share->embed, c->final_norm = share->final_norm, c->head = share->head;
+    for (int l = 0; l < cfg->layers; ++l) c->layers[l] = share->layers[l];
+  } else {
+    LB_TRY(c->alloc(&c->embed, size_t(d.V) * d.H));
+    LB_TRY(c->alloc(&c->final_norm, size_t(d.H)));
+    LB_TRY(c->alloc_matrix(c->head, d.V, d.H));
+    c->head.splits = 1;
+  }
   size_t max_plane = 0;  // floats of the largest GEMM output (all K splits); the head writes no planes
   for (int l = 0; l < cfg->layers; ++l) {
     LayerW& L = c->layers[l];
-    LB_TRY(c->alloc(&L.input_norm, size_t(d.H)));
-    LB_TRY(c->alloc(&L.post_norm, size_t(d.H)));
-    LB_TRY(c->alloc_matrix(L.gu, round_up(d.I, kTileN) + d.I, d.H));
-    LB_TRY(c->alloc_matrix(L.down, d.H, d.I));
     std::vector<Fp8Matrix*> mats = {&L.gu, &L.down};
+    if (!share) {
+      LB_TRY(c->alloc(&L.input_norm, size_t(d.H)));
+      LB_TRY(c->alloc(&L.post_norm, size_t(d.H)));
+      LB_TRY(c->alloc_matrix(L.gu, round_up(d.I, kTileN) + d.I, d.H));
+      LB_TRY(c->alloc_matrix(L.down, d.H, d.I));
+    }
     if (L.full) {
-      LB_TRY(c->alloc_matrix(L.qkv, d.Hq * 2 * d.D + 2 * d.Hkv * d.D, d.H));
-      LB_TRY(c->alloc_matrix(L.o, d.H, d.Hq * d.D));
-      LB_TRY(c->alloc(&L.q_norm, size_t(d.D)));
-      LB_TRY(c->alloc(&L.k_norm, size_t(d.D)));
+      if (!share) {
+        LB_TRY(c->alloc_matrix(L.qkv, d.Hq * 2 * d.D + 2 * d.Hkv * d.D, d.H));
+        LB_TRY(c->alloc_matrix(L.o, d.H, d.Hq * d.D));
+        LB_TRY(c->alloc(&L.q_norm, size_t(d.D)));
+        LB_TRY(c->alloc(&L.k_norm, size_t(d.D)));
+      }
       mats.push_back(&L.qkv), mats.push_back(&L.o);
     } else {
-      LB_TRY(c->alloc_matrix(L.in, d.C + d.Vs, d.H));
-      LB_TRY(c->alloc_matrix(L.out, d.H, d.Vs));
-      LB_TRY(c->alloc(&L.in_a, size_t(d.HV) * d.H));
-      LB_TRY(c->alloc(&L.in_b, size_t(d.HV) * d.H));
-      LB_TRY(c->alloc(&L.conv, size_t(d.C) * 4));
-      LB_TRY(c->alloc(&L.A_log, size_t(d.HV)));
-      LB_TRY(c->alloc(&L.dt_bias, size_t(d.HV)));
-      LB_TRY(c->alloc(&L.lin_norm, size_t(d.Dv)));
+      if (!share) {
+        LB_TRY(c->alloc_matrix(L.in, d.C + d.Vs, d.H));
+        LB_TRY(c->alloc_matrix(L.out, d.H, d.Vs));
+        LB_TRY(c->alloc(&L.in_a, size_t(d.HV) * d.H));
+        LB_TRY(c->alloc(&L.in_b, size_t(d.HV) * d.H));
+        LB_TRY(c->alloc(&L.conv, size_t(d.C) * 4));
+        LB_TRY(c->alloc(&L.A_log, size_t(d.HV)));
+        LB_TRY(c->alloc(&L.dt_bias, size_t(d.HV)));
+        LB_TRY(c->alloc(&L.lin_norm, size_t(d.Dv)));
+      }
       mats.push_back(&L.in), mats.push_back(&L.out);
     }
     for (Fp8Matrix* w : mats) max_plane = std::max(max_plane, size_t(w->splits) * d.rows_alloc * w->N_pad);
   }
   biggest = std::max(biggest, size_t(2) * d.I * d.H);
-  c->upload_floats = std::min(biggest, size_t(64) << 20);  // 256 MB of staging; larger tensors go in row bands
-  LB_TRY(c->alloc(&c->upload, c->upload_floats, false));
+  c->upload_floats = share ? 0 : std::min(biggest, size_t(64) << 20);  // 256 MB of staging; larger tensors go in row bands (a sibling takes no uploads)
+  if (!share) LB_TRY(c->alloc(&c->upload, c->upload_floats, false));
 
   // ---- activations
   LB_TRY(c->alloc(&c->h, size_t(d.rows_alloc) * d.H));
@@ -730,14 +745,18 @@ int ling_b200_create(const ling_b200_model_config* cfg, const ling_b200_options*
 
   // ---- sessions
   const size_t kv_slots = size_t(d.n_attn) * 2 * d.Hkv * (d.pool_pages + 1) * d.page_tokens;
-  LB_TRY(c->alloc(&c->kv.codes, kv_slots * d.D));
-  LB_TRY(c->alloc(&c->kv.scales, kv_slots));
-  LB_TRY(c->alloc(&c->kv.tables, size_t(opt->sessions) * d.max_pages));
   c->state_layer = size_t(d.HV) * d.Dk * d.Dv;
   c->conv_layer = size_t(d.C) * 3;
   LB_TRY(c->alloc(&c->swiglu_tickets, size_t(d.rows_alloc / 32 + 1) * (round_up(d.I, kTileN) / kTileN)));
-  LB_TRY(c->alloc(&c->gdn_state, size_t(opt->sessions) * d.n_gdn * c->state_layer));
-  LB_TRY(c->alloc(&c->conv_state, size_t(opt->sessions) * d.n_gdn * c->conv_layer));
+  if (share) {
+    c->kv = share->kv, c->gdn_state = share->gdn_state, c->conv_state = share->conv_state;
+  } else {
+    LB_TRY(c->alloc(&c->kv.codes, kv_slots * d.D));
+    LB_TRY(c->alloc(&c->kv.scales, kv_slots));
+    LB_TRY(c->alloc(&c->kv.tables, size_t(opt->sessions) * d.max_pages));
+    LB_TRY(c->alloc(&c->gdn_state, size_t(opt->sessions) * d.n_gdn * c->state_layer));
+    LB_TRY(c->alloc(&c->conv_state, size_t(opt->sessions) * d.n_gdn * c->conv_layer));
+  }
 
   // ---- the step's descriptors: one host-written block
   const size_t ms = size_t(d.max_seqs);
@@ -780,6 +799,23 @@ int ling_b200_create(const ling_b200_model_config* cfg, const ling_b200_options*
   return LING_B200_OK;
 }
 
+int ling_b200_create(const ling_b200_model_config* cfg, const ling_b200_options* opt, ling_b200_ctx** out) {
+  return create_impl(cfg, opt, nullptr, out);
+}
+
+// A second set of step buffers on a context's model and sessions: what runs beside that context's verify steps on the same
+// GPU (a prefill chunk's attention layers) without touching its staged step.  The sibling shares the parent's weights, KV
+// pool, page tables and state slots -- it must be destroyed before the parent, and takes no weight uploads.
+int ling_b200_create_sibling(const ling_b200_ctx* parent, int max_seqs, int max_rows, ling_b200_ctx** out) {
+  if (!parent || !out) {
+    set_error("create_sibling: null argument");
+    return LING_B200_ERR_ARG;
+  }
+  ling_b200_options opt = parent->opt;
+  opt.max_seqs = max_seqs, opt.max_rows = max_rows, opt.debug_rows = 0;
+  return create_impl(&parent->cfg, &opt, parent, out);
+}
+
 void ling_b200_destroy(ling_b200_ctx* c) {
   if (!c) return;
   cudaSetDevice(c->opt.device);
@@ -813,6 +849,10 @@ size_t ling_b200_weight_bytes(const ling_b200_ctx* c) {
 
 int ling_b200_set_tensor(ling_b200_ctx* c, int layer, int tensor, const float* host, int rows, int cols) {
   LB_TRY(check_ctx(c));
+  if (c->sibling) {
+    set_error("a sibling context takes no weights and owns no state arena: use its parent");
+    return LING_B200_ERR_ARG;
+  }
   if (!host || rows < 1 || cols < 1) {
     set_error("set_tensor: bad argument");
     return LING_B200_ERR_ARG;
@@ -849,6 +889,10 @@ int ling_b200_set_tensor(ling_b200_ctx* c, int layer, int tensor, const float* h
 
 int ling_b200_synth_weights(ling_b200_ctx* c, uint64_t seed) {
   LB_TRY(check_ctx(c));
+  if (c->sibling) {
+    set_error("a sibling context takes no weights and owns no state arena: use its parent");
+    return LING_B200_ERR_ARG;
+  }
   LB_TRY(synth_tensor(c, seed, -1, LING_B200_T_EMBED));
   LB_TRY(synth_tensor(c, seed, -1, LING_B200_T_FINAL_NORM));
   LB_TRY(synth_tensor(c, seed, -1, LING_B200_T_LM_HEAD));
@@ -1054,6 +1098,10 @@ size_t ling_b200_state_bytes(const ling_b200_ctx* c) {
 }
 int ling_b200_state_arena_reserve(ling_b200_ctx* c, size_t bytes) {
   LB_TRY(check_ctx(c));
+  if (c->sibling) {
+    set_error("a sibling context takes no weights and owns no state arena: use its parent");
+    return LING_B200_ERR_ARG;
+  }
   if (c->state_arena || bytes == 0) {
     set_error("state_arena_reserve: already reserved, or an empty arena");
     return LING_B200_ERR_ARG;

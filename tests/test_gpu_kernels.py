@@ -509,3 +509,33 @@ def test_chunk_attention_layer_matches_oracle(gpu, lb, lo, pos0, M):
     with pytest.raises(lb.LingError):   # the chunk's chains are not a staged step: a launch without staging again is refused
         ctx.launch()
     ctx.close(), m.close()
+
+
+def test_sibling_context_works_beside_a_staged_step(gpu, lb):
+    # a sibling context (own step buffers on the parent's weights, pages and state slots) runs a chunk's attention layer while the
+    # parent keeps a verify step staged: the parent's step is untouched and replays to the same result, and the sibling's output is
+    # bit for bit what the parent computes for the same rows
+    cfg = lb.toy_config()
+    ctx = lb.Context(cfg, sessions=5, max_context=2048, page_tokens=16, pool_pages=400, max_seqs=4, max_rows=128, debug_rows=128)
+    ctx.synth_weights(2)
+    rng = np.random.default_rng(21)
+    seqs = helpers.toy_sequences(rng, cfg.vocab)
+    page = helpers.setup_sessions([ctx], cfg, seqs, 16, 0)
+    ctx.stage(seqs, lb.STEP_KEEP_LOGITS)
+    ctx.launch()
+    first, logits = ctx.fetch(), ctx.read_logits()
+    sib = ctx.sibling(4, 128)
+    M, layer = 100, 3
+    helpers.map_pages([ctx], 4, M, 16, page)
+    h = rng.standard_normal((M, cfg.hidden)).astype(np.float32)
+    out_sib = sib.chunk_attention_layer(4, layer, 0, h)
+    ctx.launch()    # still staged: the sibling staged its chains in its own buffers
+    again = ctx.fetch()
+    for a, b in zip(first, again):
+        assert a.status == b.status == 0 and a.n_path == b.n_path and a.next_token == b.next_token
+    assert np.array_equal(ctx.read_logits(), logits)
+    out_par = ctx.chunk_attention_layer(4, layer, 0, h)
+    assert np.isfinite(out_sib).all() and np.array_equal(out_sib, out_par)
+    with pytest.raises(lb.LingError):
+        sib.synth_weights(3)    # a sibling takes no weight uploads
+    sib.close(), ctx.close()
